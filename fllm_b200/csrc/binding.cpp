@@ -1,0 +1,220 @@
+// torch.ops.fllm_b200.* : thin argument checking around the kernel launchers.
+// No kernel is implemented here and nothing falls back to ATen math: when the
+// library is loaded, every op below runs the hand-written sm_100a code.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/library.h>
+
+#include "fllm_ops.h"
+
+namespace {
+
+using at::Tensor;
+using c10::optional;
+
+inline cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+inline void check_bf16(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
+}
+inline void check_i32(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == at::kInt, name, " must be int32");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+inline void check_rows(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.dim() == 2 && t.stride(1) == 1, name, " must be 2-D with a unit inner stride");
+}
+template <typename T>
+inline const T* opt_ptr(const optional<Tensor>& t) {
+  return t.has_value() && t->defined() ? reinterpret_cast<const T*>(t->data_ptr()) : nullptr;
+}
+
+// y = x @ w^T (+ bias). `workspace` (uint8) enables split-K; `status` (int32[1]) receives a
+// non-zero code if a pipeline wait inside the kernel ran out.
+void linear(const Tensor& x, const Tensor& w, const optional<Tensor>& bias, Tensor y,
+            const optional<Tensor>& workspace, const optional<Tensor>& status, int64_t force_splits) {
+  check_bf16(x, "x"); check_bf16(w, "w"); check_bf16(y, "y");
+  check_rows(x, "x"); check_rows(w, "w"); check_rows(y, "y");
+  TORCH_CHECK(x.size(1) == w.size(1), "linear: K mismatch");
+  TORCH_CHECK(y.size(0) == x.size(0) && y.size(1) == w.size(0), "linear: output shape mismatch");
+  c10::cuda::CUDAGuard guard(x.device());
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  if (workspace.has_value() && workspace->defined()) {
+    ws = workspace->data_ptr();
+    ws_bytes = workspace->nbytes();
+  }
+  int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  fllm::linear_bf16(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), opt_ptr<void>(bias),
+                    y.data_ptr(), y.stride(0), (int)x.size(0), (int)w.size(0), (int)x.size(1), ws,
+                    ws_bytes, st, (int)force_splits, cur_stream());
+}
+
+void embed(const Tensor& ids, const Tensor& table, Tensor out, double scale) {
+  check_i32(ids, "ids"); check_bf16(table, "table"); check_bf16(out, "out");
+  TORCH_CHECK(table.is_contiguous() && out.is_contiguous(), "embed: contiguous tensors expected");
+  c10::cuda::CUDAGuard guard(out.device());
+  fllm::embed_bf16(ids.data_ptr<int>(), table.data_ptr(), out.data_ptr(), (int)ids.numel(),
+                   (int)table.size(1), (int)table.size(0), (float)scale, cur_stream());
+}
+
+// y = rmsnorm(residual [+ delta]) * w ; with delta the sum is written back to residual.
+void rmsnorm(Tensor residual, const optional<Tensor>& delta, const Tensor& w, Tensor y, double eps,
+             double w_offset) {
+  check_bf16(residual, "residual"); check_bf16(w, "w"); check_bf16(y, "y");
+  check_rows(residual, "residual"); check_rows(y, "y");
+  const Tensor* d = delta.has_value() && delta->defined() ? &*delta : nullptr;
+  if (d) { check_bf16(*d, "delta"); check_rows(*d, "delta"); }
+  c10::cuda::CUDAGuard guard(y.device());
+  fllm::rmsnorm_bf16(residual.data_ptr(), residual.stride(0), d ? d->data_ptr() : nullptr,
+                     d ? d->stride(0) : 0, w.data_ptr(), y.data_ptr(), y.stride(0),
+                     (int)residual.size(0), (int)residual.size(1), (float)eps, (float)w_offset,
+                     cur_stream());
+}
+
+void rope_kv_write(Tensor qkv, const Tensor& positions, const optional<Tensor>& slots,
+                   const Tensor& inv_freq, const optional<Tensor>& q_norm_w,
+                   const optional<Tensor>& k_norm_w, Tensor k_cache, Tensor v_cache, int64_t hq,
+                   int64_t hkv, int64_t head_dim, int64_t rot_dim, int64_t rope_style, double eps,
+                   double attn_factor) {
+  check_bf16(qkv, "qkv"); check_rows(qkv, "qkv"); check_i32(positions, "positions");
+  check_bf16(k_cache, "k_cache"); check_bf16(v_cache, "v_cache");
+  TORCH_CHECK(inv_freq.scalar_type() == at::kFloat && inv_freq.is_cuda(), "inv_freq must be fp32 CUDA");
+  TORCH_CHECK(qkv.size(1) == (hq + 2 * hkv) * head_dim, "rope_kv_write: qkv width mismatch");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous(),
+              "caches must be [blocks, kv_heads, block_size, head_dim]");
+  c10::cuda::CUDAGuard guard(qkv.device());
+  fllm::rope_qknorm_kvwrite_bf16(
+      qkv.data_ptr(), qkv.stride(0), positions.data_ptr<int>(), opt_ptr<int>(slots),
+      inv_freq.data_ptr<float>(), opt_ptr<void>(q_norm_w), opt_ptr<void>(k_norm_w),
+      k_cache.data_ptr(), v_cache.data_ptr(), (int)qkv.size(0), (int)hq, (int)hkv, (int)head_dim,
+      (int)k_cache.size(2), (int)rot_dim, (int)rope_style, (float)eps, (float)attn_factor,
+      cur_stream());
+}
+
+void glu(const Tensor& x, Tensor out, int64_t act_kind, double alpha, double limit) {
+  check_bf16(x, "x"); check_bf16(out, "out"); check_rows(x, "x"); check_rows(out, "out");
+  TORCH_CHECK(x.size(1) == 2 * out.size(1) && x.size(0) == out.size(0), "glu: shape mismatch");
+  c10::cuda::CUDAGuard guard(x.device());
+  fllm::glu_bf16(x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), (int)x.size(0),
+                 (int)out.size(1), (int)act_kind, (float)alpha, (float)limit, cur_stream());
+}
+
+void gather_rows(const Tensor& x, const Tensor& rows, Tensor out) {
+  check_bf16(x, "x"); check_rows(x, "x"); check_i32(rows, "rows"); check_bf16(out, "out");
+  TORCH_CHECK(out.is_contiguous() && out.size(1) == x.size(1), "gather_rows: bad output");
+  c10::cuda::CUDAGuard guard(x.device());
+  fllm::gather_rows_bf16(x.data_ptr(), x.stride(0), rows.data_ptr<int>(), out.data_ptr(),
+                         (int)rows.numel(), (int)x.size(1), cur_stream());
+}
+
+void attention_generic(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
+                       const Tensor& block_tables, const Tensor& row_seq, const Tensor& positions,
+                       Tensor out, int64_t hq, int64_t hkv, int64_t head_dim, double scale,
+                       int64_t window, const optional<Tensor>& sinks, double softcap) {
+  check_bf16(q, "q"); check_rows(q, "q"); check_bf16(out, "out"); check_rows(out, "out");
+  check_i32(block_tables, "block_tables"); check_i32(row_seq, "row_seq");
+  check_i32(positions, "positions");
+  c10::cuda::CUDAGuard guard(q.device());
+  fllm::attention_generic_bf16(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+                               block_tables.data_ptr<int>(), (int)block_tables.size(1),
+                               row_seq.data_ptr<int>(), positions.data_ptr<int>(), out.data_ptr(),
+                               out.stride(0), (int)q.size(0), (int)hq, (int)hkv, (int)head_dim,
+                               (int)k_cache.size(2), (float)scale, (int)window,
+                               opt_ptr<float>(sinks), (float)softcap, cur_stream());
+}
+
+void argmax(const Tensor& logits, Tensor out_ids, const optional<Tensor>& out_vals,
+            int64_t id_offset) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "argmax: bad logits");
+  const bool f32 = logits.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || logits.scalar_type() == at::kBFloat16, "argmax: logits must be fp32 or bf16");
+  check_i32(out_ids, "out_ids");
+  c10::cuda::CUDAGuard guard(logits.device());
+  float* ov = out_vals.has_value() && out_vals->defined() ? out_vals->data_ptr<float>() : nullptr;
+  fllm::argmax_rows(logits.data_ptr(), f32, logits.stride(0), (int)logits.size(0),
+                    (int)logits.size(1), out_ids.data_ptr<int>(), ov, (int)id_offset, cur_stream());
+}
+
+// params: uint8 tensor holding rows x sizeof(SampleRow) bytes laid out like fllm::SampleRow.
+void sample(Tensor logits, const Tensor& params, const optional<Tensor>& pen_ids,
+            const optional<Tensor>& pen_counts, const optional<Tensor>& bias_ids,
+            const optional<Tensor>& bias_vals, const optional<Tensor>& allow_mask, Tensor out_ids,
+            const optional<Tensor>& out_logprobs) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "sample: bad logits");
+  const bool f32 = logits.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || logits.scalar_type() == at::kBFloat16, "sample: logits must be fp32 or bf16");
+  const int rows = (int)logits.size(0);
+  TORCH_CHECK(params.is_cuda() && params.nbytes() >= rows * sizeof(fllm::SampleRow),
+              "sample: params too small");
+  check_i32(out_ids, "out_ids");
+  c10::cuda::CUDAGuard guard(logits.device());
+  const bool pen = pen_ids.has_value() && pen_ids->defined();
+  const bool bias = bias_ids.has_value() && bias_ids->defined();
+  const bool mask = allow_mask.has_value() && allow_mask->defined();
+  fllm::sample_rows(
+      logits.data_ptr(), f32, logits.stride(0), rows, (int)logits.size(1),
+      reinterpret_cast<const fllm::SampleRow*>(params.data_ptr()),
+      pen ? pen_ids->data_ptr<int>() : nullptr, pen ? pen_counts->data_ptr<int>() : nullptr,
+      pen ? (int)pen_ids->size(1) : 0, bias ? bias_ids->data_ptr<int>() : nullptr,
+      bias ? bias_vals->data_ptr<float>() : nullptr, bias ? (int)bias_ids->size(1) : 0,
+      mask ? reinterpret_cast<const uint32_t*>(allow_mask->data_ptr()) : nullptr,
+      mask ? (int)allow_mask->size(1) : 0, out_ids.data_ptr<int>(),
+      out_logprobs.has_value() && out_logprobs->defined() ? out_logprobs->data_ptr<float>() : nullptr,
+      cur_stream());
+}
+
+void spec_verify_greedy(const Tensor& draft_ids, const Tensor& target_ids,
+                        const optional<Tensor>& n_draft, Tensor n_accept, Tensor out_tokens) {
+  check_i32(draft_ids, "draft_ids"); check_i32(target_ids, "target_ids");
+  check_i32(n_accept, "n_accept"); check_i32(out_tokens, "out_tokens");
+  const int batch = (int)draft_ids.size(0), k = (int)draft_ids.size(1);
+  TORCH_CHECK(target_ids.size(1) == k + 1 && out_tokens.size(1) == k + 1, "spec_verify: shapes");
+  c10::cuda::CUDAGuard guard(draft_ids.device());
+  fllm::spec_verify_greedy(draft_ids.data_ptr<int>(), target_ids.data_ptr<int>(), batch, k,
+                           opt_ptr<int>(n_draft), n_accept.data_ptr<int>(),
+                           out_tokens.data_ptr<int>(), cur_stream());
+}
+
+void spec_verify_sampled(const Tensor& target_logits, const Tensor& draft_logits,
+                         const Tensor& draft_ids, const optional<Tensor>& n_draft,
+                         const Tensor& params, Tensor n_accept, Tensor out_tokens) {
+  const bool f32 = target_logits.scalar_type() == at::kFloat;
+  TORCH_CHECK(target_logits.scalar_type() == draft_logits.scalar_type(), "spec_verify: dtype mismatch");
+  check_i32(draft_ids, "draft_ids");
+  const int batch = (int)draft_ids.size(0), k = (int)draft_ids.size(1);
+  TORCH_CHECK(target_logits.dim() == 2 && target_logits.size(0) == (int64_t)batch * (k + 1),
+              "spec_verify: target rows");
+  TORCH_CHECK(draft_logits.dim() == 2 && draft_logits.size(0) == (int64_t)batch * k,
+              "spec_verify: draft rows");
+  c10::cuda::CUDAGuard guard(draft_ids.device());
+  fllm::spec_verify_sampled(target_logits.data_ptr(), target_logits.stride(0),
+                            draft_logits.data_ptr(), draft_logits.stride(0), f32,
+                            (int)target_logits.size(1), draft_ids.data_ptr<int>(), batch, k,
+                            opt_ptr<int>(n_draft),
+                            reinterpret_cast<const fllm::SampleRow*>(params.data_ptr()),
+                            n_accept.data_ptr<int>(), out_tokens.data_ptr<int>(), cur_stream());
+}
+
+int64_t sample_row_bytes() { return (int64_t)sizeof(fllm::SampleRow); }
+
+}  // namespace
+
+TORCH_LIBRARY(fllm_b200, m) {
+  m.def("linear(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status, int force_splits) -> ()", &linear);
+  m.def("embed(Tensor ids, Tensor table, Tensor(a!) out, float scale) -> ()", &embed);
+  m.def("rmsnorm(Tensor(a!) residual, Tensor? delta, Tensor w, Tensor(b!) y, float eps, float w_offset) -> ()", &rmsnorm);
+  m.def("rope_kv_write(Tensor(a!) qkv, Tensor positions, Tensor? slots, Tensor inv_freq, Tensor? q_norm_w, Tensor? k_norm_w, Tensor(b!) k_cache, Tensor(c!) v_cache, int hq, int hkv, int head_dim, int rot_dim, int rope_style, float eps, float attn_factor) -> ()", &rope_kv_write);
+  m.def("glu(Tensor x, Tensor(a!) out, int act_kind, float alpha, float limit) -> ()", &glu);
+  m.def("gather_rows(Tensor x, Tensor rows, Tensor(a!) out) -> ()", &gather_rows);
+  m.def("attention_generic(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor row_seq, Tensor positions, Tensor(a!) out, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap) -> ()", &attention_generic);
+  m.def("argmax(Tensor logits, Tensor(a!) out_ids, Tensor? out_vals, int id_offset) -> ()", &argmax);
+  m.def("sample(Tensor(a!) logits, Tensor params, Tensor? pen_ids, Tensor? pen_counts, Tensor? bias_ids, Tensor? bias_vals, Tensor? allow_mask, Tensor(b!) out_ids, Tensor? out_logprobs) -> ()", &sample);
+  m.def("spec_verify_greedy(Tensor draft_ids, Tensor target_ids, Tensor? n_draft, Tensor(a!) n_accept, Tensor(b!) out_tokens) -> ()", &spec_verify_greedy);
+  m.def("spec_verify_sampled(Tensor target_logits, Tensor draft_logits, Tensor draft_ids, Tensor? n_draft, Tensor params, Tensor(a!) n_accept, Tensor(b!) out_tokens) -> ()", &spec_verify_sampled);
+  m.def("sample_row_bytes() -> int", &sample_row_bytes);
+}

@@ -1,0 +1,402 @@
+// Memory-bound bf16 kernels of the decoder: embedding gather, RMSNorm with fused
+// residual add, per-head QK-RMSNorm + RoPE + paged KV write, SwiGLU variants.
+// All of them move 16 bytes per thread per access and keep reductions in fp32.
+//
+// Reference counterparts: rust/engine/cuda/elementwise.cu:271-293 (rms_norm_*),
+// :470-530 (rope_kv_f16_kernel), rust/engine/cuda/fused.cu:68 (add_rms_norm_kernel),
+// rust/engine/cuda/act_narrow.cu (bf16 activation pipeline). There the activation
+// dtype is a run-time switch; here bf16 is the only activation dtype.
+#include "fllm_ops.h"
+#include "ptx.cuh"
+#include "tma_host.h"
+
+namespace fllm {
+
+// ---------------------------------------------------------------------------- embedding
+__global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                             __nv_bfloat16* __restrict__ out, int hidden, int vocab, float scale) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;
+  const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)id * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * hidden);
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) {
+    uint4 v = src[i];
+    if (scale != 1.f) {
+      uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = unpack_bf16x2(w[j]);
+        w[j] = pack_bf16x2(f.x * scale, f.y * scale);
+      }
+    }
+    dst[i] = v;
+  }
+}
+
+void embed_bf16(const int* ids, const void* table, void* out, int tokens, int hidden, int vocab,
+                float scale, cudaStream_t s) {
+  if (tokens <= 0) return;
+  embed_kernel<<<tokens, 256, 0, s>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out,
+                                      hidden, vocab, scale);
+  cuda_check(cudaGetLastError(), "embed_kernel");
+}
+
+// ---------------------------------------------------------------------------- RMSNorm
+// One CTA per row. y = x_new * rsqrt(mean(x_new^2) + eps) * w, where
+// x_new = residual + delta when `delta` is given (and residual is updated in place).
+// `w_offset` = 1 for Gemma-style (1 + w) weights.
+template <int VEC_ITERS>
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ delta,
+               const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int hidden,
+               long long ld_res, long long ld_delta, long long ld_y, float eps, float w_offset) {
+  const int row = blockIdx.x;
+  __nv_bfloat16* xr = residual + (size_t)row * ld_res;
+  const __nv_bfloat16* dr = delta ? delta + (size_t)row * ld_delta : nullptr;
+  const int nvec = hidden / 8;
+  float vals[VEC_ITERS][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < VEC_ITERS; ++it) {
+    const int i = threadIdx.x + it * 256;
+    if (i < nvec) {
+      uint4 v = reinterpret_cast<const uint4*>(xr)[i];
+      const uint32_t* vw = reinterpret_cast<const uint32_t*>(&v);
+      uint4 d = make_uint4(0, 0, 0, 0);
+      if (dr) d = reinterpret_cast<const uint4*>(dr)[i];
+      const uint32_t* dw = reinterpret_cast<const uint32_t*>(&d);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 a = unpack_bf16x2(vw[j]);
+        if (dr) {
+          float2 b = unpack_bf16x2(dw[j]);
+          // the updated residual is stored as bf16, so normalise the rounded value
+          const uint32_t packed = pack_bf16x2(a.x + b.x, a.y + b.y);
+          a = unpack_bf16x2(packed);
+        }
+        vals[it][2 * j] = a.x;
+        vals[it][2 * j + 1] = a.y;
+        ss += a.x * a.x + a.y * a.y;
+      }
+      if (dr) {
+        uint4 o;
+        o.x = pack_bf16x2(vals[it][0], vals[it][1]);
+        o.y = pack_bf16x2(vals[it][2], vals[it][3]);
+        o.z = pack_bf16x2(vals[it][4], vals[it][5]);
+        o.w = pack_bf16x2(vals[it][6], vals[it][7]);
+        reinterpret_cast<uint4*>(xr)[i] = o;
+      }
+    }
+  }
+  __shared__ float red[8];
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float inv = rsqrtf(tot / (float)hidden + eps);
+  __nv_bfloat16* yr = y + (size_t)row * ld_y;
+#pragma unroll
+  for (int it = 0; it < VEC_ITERS; ++it) {
+    const int i = threadIdx.x + it * 256;
+    if (i < nvec) {
+      const uint4 wv = reinterpret_cast<const uint4*>(w)[i];
+      const uint32_t* ww = reinterpret_cast<const uint32_t*>(&wv);
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 g = unpack_bf16x2(ww[j]);
+        o[j] = pack_bf16x2(vals[it][2 * j] * inv * (g.x + w_offset),
+                           vals[it][2 * j + 1] * inv * (g.y + w_offset));
+      }
+      reinterpret_cast<uint4*>(yr)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+void rmsnorm_bf16(void* residual, long long ld_res, const void* delta, long long ld_delta,
+                  const void* w, void* y, long long ld_y, int rows, int hidden, float eps,
+                  float w_offset, cudaStream_t s) {
+  if (rows <= 0) return;
+  if (hidden % 8 || hidden > 8 * 256 * 8)
+    throw std::runtime_error("rmsnorm_bf16: hidden must be a multiple of 8 and at most 16384");
+  const int iters = (hidden / 8 + 255) / 256;
+  auto* r = (__nv_bfloat16*)residual;
+  auto* d = (const __nv_bfloat16*)delta;
+  auto* ww = (const __nv_bfloat16*)w;
+  auto* yy = (__nv_bfloat16*)y;
+#define FLLM_RMS(IT)                                                                          \
+  rmsnorm_kernel<IT><<<rows, 256, 0, s>>>(r, d, ww, yy, hidden, ld_res, ld_delta, ld_y, eps, \
+                                           w_offset)
+  switch (iters) {
+    case 1: FLLM_RMS(1); break;
+    case 2: FLLM_RMS(2); break;
+    case 3: FLLM_RMS(3); break;
+    case 4: FLLM_RMS(4); break;
+    default: FLLM_RMS(8); break;
+  }
+#undef FLLM_RMS
+  cuda_check(cudaGetLastError(), "rmsnorm_kernel");
+}
+
+// ---------------------------------------------------------------------------- RoPE + QK-norm + KV write
+// One warp per (token, head). Heads [0, hq) are query heads (rotated in place),
+// [hq, hq+hkv) key heads (normalised, rotated, written to the paged cache),
+// [hq+hkv, hq+2hkv) value heads (copied to the cache).
+// Cache layout: [block][kv_head][block_size][head_dim] (a head's page is contiguous).
+// rope_style: 0 = rotate-half ("neox": pairs (i, i + rot/2)), 1 = interleaved pairs (2i, 2i+1).
+template <int D>
+__global__ void __launch_bounds__(128)
+rope_kv_kernel(__nv_bfloat16* __restrict__ qkv, long long ld_qkv, const int* __restrict__ positions,
+               const int* __restrict__ slots, const float* __restrict__ inv_freq,
+               const __nv_bfloat16* __restrict__ q_norm_w, const __nv_bfloat16* __restrict__ k_norm_w,
+               __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int tokens,
+               int hq, int hkv, int block_size, int rot_dim, int rope_style, float eps,
+               float attn_factor) {
+  constexpr int EPL = D / 32;  // elements per lane
+  const int heads = hq + 2 * hkv;
+  const long long gw = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (gw >= (long long)tokens * heads) return;
+  const int t = (int)(gw / heads);
+  const int h = (int)(gw - (long long)t * heads);
+  const int lane = threadIdx.x & 31;
+  __nv_bfloat16* src = qkv + (size_t)t * ld_qkv + (size_t)h * D;
+  const int slot = slots ? slots[t] : -1;
+
+  if (h >= hq + hkv) {  // value head: straight copy
+    if (slot < 0) return;
+    const int kvh = h - hq - hkv;
+    const int blk = slot / block_size, off = slot - blk * block_size;
+    __nv_bfloat16* dst = v_cache + (((size_t)blk * hkv + kvh) * block_size + off) * D;
+    if (EPL == 4) {
+      reinterpret_cast<uint2*>(dst)[lane] = reinterpret_cast<const uint2*>(src)[lane];
+    } else {
+      for (int i = lane; i < D / 2; i += 32)
+        reinterpret_cast<uint32_t*>(dst)[i] = reinterpret_cast<const uint32_t*>(src)[i];
+    }
+    return;
+  }
+
+  // Load the head with lanes striding so that lane l owns elements {l + 32*j}: the
+  // rotate-half partner of element i (i + rot/2) then sits in the same lane whenever
+  // rot/2 is a multiple of 32, and in lane l for the interleaved style we use pairs.
+  float v[EPL];
+  if (rope_style == 0) {
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) v[j] = __bfloat162float(src[lane + 32 * j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < EPL; j += 2) {
+      float2 f = unpack_bf16x2(reinterpret_cast<const uint32_t*>(src)[lane + 32 * (j / 2)]);
+      v[j] = f.x;
+      v[j + 1] = f.y;
+    }
+  }
+  const bool is_q = h < hq;
+  const __nv_bfloat16* nw = is_q ? q_norm_w : k_norm_w;
+  if (nw) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) ss += v[j] * v[j];
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)D + eps);
+    if (rope_style == 0) {
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) {
+        // round through bf16 like an unfused norm would
+        v[j] = __bfloat162float(__float2bfloat16(v[j] * inv * __bfloat162float(nw[lane + 32 * j])));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < EPL; j += 2) {
+        const int e = 2 * (lane + 32 * (j / 2));
+        v[j] = __bfloat162float(__float2bfloat16(v[j] * inv * __bfloat162float(nw[e])));
+        v[j + 1] = __bfloat162float(__float2bfloat16(v[j + 1] * inv * __bfloat162float(nw[e + 1])));
+      }
+    }
+  }
+  const float pos = (float)positions[t];
+  const int half = rot_dim / 2;
+  if (rope_style == 0) {
+    // element index e = lane + 32*j ; partner e + half when e < half
+    if (half % 32 == 0) {
+      const int jh = half / 32;
+#pragma unroll
+      for (int j = 0; j < EPL / 2; ++j) {
+        if (j < jh) {
+          const int e = lane + 32 * j;
+          float sn, cs;
+          sincosf(pos * inv_freq[e], &sn, &cs);
+          sn *= attn_factor;
+          cs *= attn_factor;
+          const float a = v[j], b = v[j + jh];
+          v[j] = a * cs - b * sn;
+          v[j + jh] = b * cs + a * sn;
+        }
+      }
+    } else {
+      // partner lives in another lane (half = 16, head_dim 32 or partial rotary): shuffle
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) {
+        const int e = lane + 32 * j;
+        const int pe = e < half ? e + half : e - half;
+        const float other = __shfl_sync(0xffffffffu, v[j], pe & 31);  // same j only when half<32
+        if (e < rot_dim && half < 32) {
+          float sn, cs;
+          sincosf(pos * inv_freq[e < half ? e : e - half], &sn, &cs);
+          sn *= attn_factor;
+          cs *= attn_factor;
+          v[j] = e < half ? v[j] * cs - other * sn : v[j] * cs + other * sn;
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < EPL; j += 2) {
+      const int pair = lane + 32 * (j / 2);
+      if (2 * pair < rot_dim) {
+        float sn, cs;
+        sincosf(pos * inv_freq[pair], &sn, &cs);
+        sn *= attn_factor;
+        cs *= attn_factor;
+        const float a = v[j], b = v[j + 1];
+        v[j] = a * cs - b * sn;
+        v[j + 1] = b * cs + a * sn;
+      }
+    }
+  }
+  __nv_bfloat16* dst;
+  if (is_q) {
+    dst = src;
+  } else {
+    if (slot < 0) return;
+    const int kvh = h - hq;
+    const int blk = slot / block_size, off = slot - blk * block_size;
+    dst = k_cache + (((size_t)blk * hkv + kvh) * block_size + off) * D;
+  }
+  if (rope_style == 0) {
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) dst[lane + 32 * j] = __float2bfloat16(v[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < EPL; j += 2)
+      reinterpret_cast<uint32_t*>(dst)[lane + 32 * (j / 2)] = pack_bf16x2(v[j], v[j + 1]);
+  }
+}
+
+void rope_qknorm_kvwrite_bf16(void* qkv, long long ld_qkv, const int* positions, const int* slots,
+                              const float* inv_freq, const void* q_norm_w, const void* k_norm_w,
+                              void* k_cache, void* v_cache, int tokens, int hq, int hkv,
+                              int head_dim, int block_size, int rot_dim, int rope_style, float eps,
+                              float attn_factor, cudaStream_t s) {
+  if (tokens <= 0) return;
+  const long long warps = (long long)tokens * (hq + 2 * hkv);
+  const int blocks = (int)((warps + 3) / 4);
+  auto* x = (__nv_bfloat16*)qkv;
+  auto* qn = (const __nv_bfloat16*)q_norm_w;
+  auto* kn = (const __nv_bfloat16*)k_norm_w;
+  auto* kc = (__nv_bfloat16*)k_cache;
+  auto* vc = (__nv_bfloat16*)v_cache;
+#define FLLM_ROPE(DD)                                                                            \
+  rope_kv_kernel<DD><<<blocks, 128, 0, s>>>(x, ld_qkv, positions, slots, inv_freq, qn, kn, kc, \
+                                            vc, tokens, hq, hkv, block_size, rot_dim,           \
+                                            rope_style, eps, attn_factor)
+  switch (head_dim) {
+    case 64: FLLM_ROPE(64); break;
+    case 128: FLLM_ROPE(128); break;
+    case 256: FLLM_ROPE(256); break;
+    default: throw std::runtime_error("rope_qknorm_kvwrite_bf16: head_dim must be 64, 128 or 256");
+  }
+#undef FLLM_ROPE
+  cuda_check(cudaGetLastError(), "rope_kv_kernel");
+}
+
+// ---------------------------------------------------------------------------- GLU activations
+// act_kind 0: silu(gate) * up with gate = x[:, :I], up = x[:, I:2I]
+// act_kind 1: gelu_tanh(gate) * up (GeGLU)
+// act_kind 2: gpt-oss clamped SwiGLU on interleaved columns (gate = x[2i], up = x[2i+1]):
+//             g = min(g, limit); u = clamp(u, -limit, limit); out = g * sigmoid(alpha g) * (u + 1)
+__global__ void glu_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                           __nv_bfloat16* __restrict__ out, long long ldo, int inter, int act_kind,
+                           float alpha, float limit) {
+  const int row = blockIdx.y;
+  const int i8 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i8 >= inter) return;
+  const __nv_bfloat16* xr = x + (size_t)row * ldx;
+  float g[8], u[8];
+  if (act_kind == 2) {
+    const uint4 a = *reinterpret_cast<const uint4*>(xr + 2 * i8);
+    const uint4 b = *reinterpret_cast<const uint4*>(xr + 2 * i8 + 8);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float2 f = unpack_bf16x2(w[j]);
+      g[j] = f.x;
+      u[j] = f.y;
+    }
+  } else {
+    const uint4 a = *reinterpret_cast<const uint4*>(xr + i8);
+    const uint4 b = *reinterpret_cast<const uint4*>(xr + inter + i8);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+    const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = unpack_bf16x2(aw[j]);
+      float2 h = unpack_bf16x2(bw[j]);
+      g[2 * j] = f.x; g[2 * j + 1] = f.y;
+      u[2 * j] = h.x; u[2 * j + 1] = h.y;
+    }
+  }
+  float o[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (act_kind == 0) {
+      o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    } else if (act_kind == 1) {
+      const float c = 0.7978845608028654f * (g[j] + 0.044715f * g[j] * g[j] * g[j]);
+      o[j] = 0.5f * g[j] * (1.f + tanhf(c)) * u[j];
+    } else {
+      const float gg = fminf(g[j], limit);
+      const float uu = fminf(fmaxf(u[j], -limit), limit);
+      o[j] = gg / (1.f + __expf(-alpha * gg)) * (uu + 1.f);
+    }
+  }
+  uint4 r;
+  r.x = pack_bf16x2(o[0], o[1]);
+  r.y = pack_bf16x2(o[2], o[3]);
+  r.z = pack_bf16x2(o[4], o[5]);
+  r.w = pack_bf16x2(o[6], o[7]);
+  *reinterpret_cast<uint4*>(out + (size_t)row * ldo + i8) = r;
+}
+
+void glu_bf16(const void* x, long long ldx, void* out, long long ldo, int rows, int inter,
+              int act_kind, float alpha, float limit, cudaStream_t s) {
+  if (rows <= 0) return;
+  if (inter % 8) throw std::runtime_error("glu_bf16: intermediate size must be a multiple of 8");
+  dim3 grid((inter / 8 + 127) / 128, rows);
+  glu_kernel<<<grid, 128, 0, s>>>((const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)out, ldo, inter,
+                                  act_kind, alpha, limit);
+  cuda_check(cudaGetLastError(), "glu_kernel");
+}
+
+// ---------------------------------------------------------------------------- row gather (logit rows)
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                   const int* __restrict__ rows, __nv_bfloat16* __restrict__ out,
+                                   int hidden) {
+  const int r = rows[blockIdx.x];
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)r * ldx);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * hidden);
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+void gather_rows_bf16(const void* x, long long ldx, const int* rows, void* out, int n_rows,
+                      int hidden, cudaStream_t s) {
+  if (n_rows <= 0) return;
+  gather_rows_kernel<<<n_rows, 128, 0, s>>>((const __nv_bfloat16*)x, ldx, rows,
+                                            (__nv_bfloat16*)out, hidden);
+  cuda_check(cudaGetLastError(), "gather_rows_kernel");
+}
+
+}  // namespace fllm

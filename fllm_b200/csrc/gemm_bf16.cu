@@ -1,0 +1,413 @@
+// Dense bf16 GEMM on the 5th-generation tensor cores:  D[M,N] = A[M,K] * B[N,K]^T
+//
+//   * both operands are K-major (row-major with K contiguous) and are staged into
+//     shared memory by TMA with the 128-byte swizzle (no cluster multicast);
+//   * one elected thread issues tcgen05.mma (128 x BN x 16 per instruction), the
+//     fp32 accumulator lives in TMEM and is double buffered so the epilogue of
+//     tile i overlaps the main loop of tile i+1;
+//   * warp roles: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+//     warps 2..5 = epilogue (tcgen05.ld -> bf16 -> global);
+//   * persistent grid: CTAs walk a linear list of (split, n-tile, m-tile) items.
+//
+// Output modes
+//   row-major   out[m * ldc + n]           (prefill: A = activations, B = weight)
+//   transposed  out[n * ldc + m]           (decode "swap-AB": A = weight so that
+//                                           the 128-row MMA dimension is filled by
+//                                           output features and the few tokens sit
+//                                           in the N dimension)
+//   split-K     fp32 partial sums in a workspace, reduced by splitk_reduce_kernel.
+//
+// Role in the reference: dense F16/BF16 products go to cuBLASLt for >= 9 tokens
+// (rust/engine/cuda/cublaslt_gemm.cu:11-14) and to an mma.sync skinny kernel below
+// that (rust/engine/cuda/linear.cu:396-507); here both cases are one tcgen05 kernel.
+#include "fllm_ops.h"
+#include "ptx.cuh"
+#include "tma_host.h"
+
+namespace fllm {
+
+constexpr int BM = 128;
+constexpr int BK = 64;       // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kGemmThreads = 192;
+
+struct GemmArgs {
+  int M, N, K;
+  int m_tiles, n_tiles;
+  int k_blocks;            // ceil(K / BK)
+  int kb_per_split;
+  int k_splits;
+  int transposed;          // 0: out[m*ldc+n], 1: out[n*ldc+m]
+  long long ldc;
+  __nv_bfloat16* out;
+  float* ws;               // split-K partials, [k_splits][M*N] in output orientation (dense)
+  const __nv_bfloat16* bias;  // per output feature (n when row-major, m when transposed)
+  int* status;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  // narrow token tiles (decode) keep two CTAs resident per SM so that a tile list
+  // that is not a multiple of the SM count still drains evenly; wide tiles own the SM
+  static constexpr int kCtasPerSm = BN <= 64 ? 2 : 1;
+  static constexpr int kBudget = (BN <= 64 ? 98 : 200) * 1024;
+  static constexpr int kStagesRaw = kBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
+  static constexpr int kTmemCols = (2 * BN) < 32 ? 32 : (2 * BN);
+  static constexpr int kBarBytes = 256;
+  static constexpr int kTotal = kStages * kStageBytes + kBarBytes + 1024;  // +1024 alignment slack
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
+                 const __grid_constant__ CUtensorMap tma_b, const GemmArgs p) {
+  using S = GemmSmem<BN>;
+  constexpr int STAGES = S::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * S::kABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tfull_bar = bars + 2 * STAGES;
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 128);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, S::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles = p.m_tiles * p.n_tiles;
+  const int total = tiles * p.k_splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+        const int split = w / tiles;
+        const int t = w - split * tiles;
+        const int n_idx = t / p.m_tiles;
+        const int m_idx = t - n_idx * p.m_tiles;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&full_bar[stage], S::kStageBytes);
+          tma_load_2d(sA + stage * S::kABytes, &tma_a, &full_bar[stage], kb * BK, m_idx * BM);
+          tma_load_2d(sB + stage * S::kBBytes, &tma_b, &full_bar[stage], kb * BK, n_idx * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN, 1, 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+        const int split = w / tiles;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint64_t da = make_smem_desc_sw128(smem_u32(sA + stage * S::kABytes));
+          const uint64_t db = make_smem_desc_sw128(smem_u32(sB + stage * S::kBBytes));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing 16 bf16 = 32 bytes inside the swizzle row: +2 in 16-byte units
+            tc_mma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&tfull_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+      const int split = w / tiles;
+      const int t = w - split * tiles;
+      const int n_idx = t / p.m_tiles;
+      const int m_idx = t - n_idx * p.m_tiles;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int m = m_idx * BM + q * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      float* wsp = p.k_splits > 1 ? p.ws + (size_t)split * p.M * p.N : nullptr;
+      constexpr int CH = BN < 32 ? 16 : 32;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += CH) {
+        uint32_t r[32];
+        if constexpr (CH == 32) {
+          tmem_ld_32x32(t_row + c0, r);
+        } else {
+          uint32_t r16[16];
+          tmem_ld_32x16(t_row + c0, r16);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) { r[i] = r16[i]; r[i + 16] = 0; }
+        }
+        tmem_ld_wait();
+        const int n0 = n_idx * BN + c0;
+        if (!p.transposed) {
+          if (m < p.M) {
+            if (wsp) {
+              float* dst = wsp + (size_t)m * p.N + n0;
+#pragma unroll
+              for (int c = 0; c < CH; c += 4) {
+                if (n0 + c < p.N)
+                  *reinterpret_cast<float4*>(dst + c) =
+                      make_float4(__uint_as_float(r[c]), __uint_as_float(r[c + 1]),
+                                  __uint_as_float(r[c + 2]), __uint_as_float(r[c + 3]));
+              }
+            } else {
+              __nv_bfloat16* dst = p.out + (size_t)m * p.ldc + n0;
+#pragma unroll
+              for (int c = 0; c < CH; c += 8) {
+                if (n0 + c < p.N) {
+                  float v[8];
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[c + i]);
+                  if (p.bias) {
+                    const uint4 bb = *reinterpret_cast<const uint4*>(p.bias + n0 + c);
+                    const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                      float2 f = unpack_bf16x2(bw[i]);
+                      v[2 * i] += f.x;
+                      v[2 * i + 1] += f.y;
+                    }
+                  }
+                  uint4 o;
+                  o.x = pack_bf16x2(v[0], v[1]);
+                  o.y = pack_bf16x2(v[2], v[3]);
+                  o.z = pack_bf16x2(v[4], v[5]);
+                  o.w = pack_bf16x2(v[6], v[7]);
+                  *reinterpret_cast<uint4*>(dst + c) = o;
+                }
+              }
+            }
+          }
+        } else {
+          if (wsp) {
+            if (m < p.M) {
+#pragma unroll
+              for (int c = 0; c < CH; ++c)
+                if (n0 + c < p.N) wsp[(size_t)(n0 + c) * p.M + m] = __uint_as_float(r[c]);
+            }
+          } else {
+            // pair exchange: even lanes store (m, m+1) of column c, odd lanes of column c+1,
+            // so every store is one bf16x2 and 16 lanes cover 64 contiguous bytes
+            const float bias_m = (p.bias && m < p.M) ? __bfloat162float(p.bias[m]) : 0.f;
+            const bool odd = lane & 1;
+#pragma unroll
+            for (int c = 0; c < CH; c += 2) {
+              const float own0 = __uint_as_float(r[c]) + bias_m;
+              const float own1 = __uint_as_float(r[c + 1]) + bias_m;
+              const float send = odd ? own0 : own1;
+              const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+              const int n = n0 + c + (odd ? 1 : 0);
+              const int mm = odd ? m - 1 : m;
+              const uint32_t packed = odd ? pack_bf16x2(recv, own1) : pack_bf16x2(own0, recv);
+              if (n < p.N && mm < p.M)
+                *reinterpret_cast<uint32_t*>(p.out + (size_t)n * p.ldc + mm) = packed;
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tempty_bar[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, S::kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, FLLM_ERR_MBAR_TIMEOUT);
+}
+
+// out[i] = bf16(sum_s ws[s][i] + bias), i over a dense [rows][cols] array written with pitch ldc.
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, int rows, int cols,
+                                     long long ldc, const __nv_bfloat16* __restrict__ bias,
+                                     __nv_bfloat16* __restrict__ out) {
+  const size_t n = (size_t)rows * cols;
+  const size_t i4 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i4 >= n) return;
+  float4 acc = *reinterpret_cast<const float4*>(ws + i4);
+  for (int s = 1; s < splits; ++s) {
+    const float4 v = *reinterpret_cast<const float4*>(ws + (size_t)s * n + i4);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  const int r = (int)(i4 / cols);
+  const int c = (int)(i4 - (size_t)r * cols);
+  if (bias) {
+    acc.x += __bfloat162float(bias[c]);
+    acc.y += __bfloat162float(bias[c + 1]);
+    acc.z += __bfloat162float(bias[c + 2]);
+    acc.w += __bfloat162float(bias[c + 3]);
+  }
+  uint2 o;
+  o.x = pack_bf16x2(acc.x, acc.y);
+  o.y = pack_bf16x2(acc.z, acc.w);
+  *reinterpret_cast<uint2*>(out + (size_t)r * ldc + c) = o;
+}
+
+template <int BN>
+static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, int grid,
+                        cudaStream_t stream) {
+  using S = GemmSmem<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cuda_check(cudaFuncSetAttribute(gemm_bf16_kernel<BN>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal),
+               "cudaFuncSetAttribute(gemm_bf16_kernel)");
+    configured = true;
+  }
+  gemm_bf16_kernel<BN><<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, a);
+  cuda_check(cudaGetLastError(), "gemm_bf16_kernel launch");
+}
+
+size_t gemm_bf16_workspace_bytes(int tokens, int features) {
+  // upper bound: 16 splits of a dense fp32 [tokens][features] array
+  return (size_t)16 * tokens * features * sizeof(float);
+}
+
+static int pick_bn_tokens(int t) {
+  if (t <= 16) return 16;
+  if (t <= 32) return 32;
+  if (t <= 64) return 64;
+  if (t <= 128) return 128;
+  return 256;
+}
+
+// y[T, N] = x[T, K] * w[N, K]^T (+ bias[N]);  x row pitch ldx, y row pitch ldy (elements).
+void linear_bf16(const void* x, long long ldx, const void* w, long long ldw, const void* bias,
+                 void* y, long long ldy, int T, int N, int K, void* workspace,
+                 size_t workspace_bytes, int* status, int force_splits, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return;
+  if ((K & 7) || (N & 7) || (ldx & 7) || (ldw & 7) || (ldy & 1))
+    throw std::runtime_error("linear_bf16: K, N and the row pitches must be multiples of 8");
+  const int sms = sm_count();
+  GemmArgs a{};
+  a.K = K;
+  a.k_blocks = (K + BK - 1) / BK;
+  a.out = reinterpret_cast<__nv_bfloat16*>(y);
+  a.ldc = ldy;
+  a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  a.status = status;
+  a.ws = reinterpret_cast<float*>(workspace);
+
+  const bool swap = T <= 128;
+  int bn;
+  CUtensorMap ta, tb;
+  if (swap) {
+    bn = pick_bn_tokens(T);
+    a.M = N;  // MMA rows = output features
+    a.N = T;
+    a.transposed = 1;
+    ta = make_tmap_2d(w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldw * 2, BM, BK, true);
+    tb = make_tmap_2d(x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, K, ldx * 2, bn, BK, true);
+  } else {
+    bn = N >= 256 * 64 || (N % 256 == 0 && ((T + BM - 1) / BM) * (N / 256) >= sms) ? 256 : 128;
+    if (N < 128) bn = 64;
+    a.M = T;
+    a.N = N;
+    a.transposed = 0;
+    ta = make_tmap_2d(x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, K, ldx * 2, BM, BK, true);
+    tb = make_tmap_2d(w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldw * 2, bn, BK, true);
+  }
+  a.m_tiles = (a.M + BM - 1) / BM;
+  a.n_tiles = (a.N + bn - 1) / bn;
+  const int tiles = a.m_tiles * a.n_tiles;
+
+  // split-K when the tile list cannot fill the machine and K is deep enough
+  int splits = 1;
+  if (force_splits > 0) {
+    splits = force_splits;
+  } else if (tiles * 2 <= sms && a.k_blocks >= 8) {
+    const int slots = sms * (bn <= 64 ? 2 : 1);
+    splits = min(min(slots / tiles, a.k_blocks / 4), 16);
+  }
+  if (splits > 1) {
+    const size_t need = (size_t)splits * a.M * a.N * sizeof(float);
+    if (!workspace || need > workspace_bytes || (a.M & 3) || (a.N & 3)) splits = 1;
+  }
+  a.kb_per_split = (a.k_blocks + splits - 1) / splits;
+  a.k_splits = (a.k_blocks + a.kb_per_split - 1) / a.kb_per_split;
+  if (a.k_splits == 1) a.ws = nullptr;
+
+  const int grid = min(tiles * a.k_splits, sms * (bn <= 64 ? 2 : 1));
+  switch (bn) {
+    case 16: launch_gemm<16>(ta, tb, a, grid, stream); break;
+    case 32: launch_gemm<32>(ta, tb, a, grid, stream); break;
+    case 64: launch_gemm<64>(ta, tb, a, grid, stream); break;
+    case 128: launch_gemm<128>(ta, tb, a, grid, stream); break;
+    default: launch_gemm<256>(ta, tb, a, grid, stream); break;
+  }
+  if (a.k_splits > 1) {
+    // the partials are a dense [T][N] (row-major) or, when transposed, [N_tok=T][features] array:
+    // in both cases "rows" are tokens and "cols" are features of y.
+    const size_t n = (size_t)T * N;
+    const int threads = 256;
+    const int blocks = (int)((n / 4 + threads - 1) / threads);
+    splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(a.ws, a.k_splits, T, N, ldy, a.bias,
+                                                         a.out);
+    cuda_check(cudaGetLastError(), "splitk_reduce_kernel launch");
+  }
+}
+
+}  // namespace fllm

@@ -1,0 +1,71 @@
+// Host-side helpers shared by the kernel launchers: tensor-map encoding through
+// the driver entry point (so the library never links libcuda directly), SM count
+// cache and error reporting.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdexcept>
+#include <string>
+
+namespace fllm {
+
+inline void cuda_check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) {
+    throw std::runtime_error(std::string("fllm_b200: ") + what + ": " + cudaGetErrorString(e));
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cuda_check(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q),
+               "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+    if (q != cudaDriverEntryPointSuccess || !p)
+      throw std::runtime_error("fllm_b200: cuTensorMapEncodeTiled is not available");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D row-major tensor [rows][cols] of `elem_bytes` elements with a row pitch of
+// `pitch_bytes`; box = [box_rows][box_cols]; 128-byte swizzle (box_cols*elem_bytes
+// must be 128) or none. Out-of-range elements read as zero.
+inline CUtensorMap make_tmap_2d(const void* base, CUtensorMapDataType dt, int elem_bytes,
+                                uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+                                uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+  CUtensorMap m;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch_bytes & 15))
+    throw std::runtime_error("fllm_b200: TMA operand must be 16-byte aligned with a 16-byte pitch");
+  CUresult r = get_encode_tiled()(
+      &m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    throw std::runtime_error("fllm_b200: cuTensorMapEncodeTiled failed with code " +
+                             std::to_string((int)r));
+  (void)elem_bytes;
+  return m;
+}
+
+inline int sm_count() {
+  static int n[16] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) dev = 0;
+  if (!n[dev]) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+  return n[dev];
+}
+
+}  // namespace fllm
