@@ -35,7 +35,7 @@ inline const T* opt_ptr(const optional<Tensor>& t) {
 
 // y = x @ w^T (+ bias). `workspace` (uint8) enables split-K; `status` (int32[1]) receives a
 // non-zero code if a pipeline wait inside the kernel ran out.
-void linear(const Tensor& x, const Tensor& w, const optional<Tensor>& bias, Tensor y,
+int64_t linear(const Tensor& x, const Tensor& w, const optional<Tensor>& bias, Tensor y,
             const optional<Tensor>& workspace, const optional<Tensor>& status, int64_t force_splits) {
   check_bf16(x, "x"); check_bf16(w, "w"); check_bf16(y, "y");
   check_rows(x, "x"); check_rows(w, "w"); check_rows(y, "y");
@@ -49,7 +49,7 @@ void linear(const Tensor& x, const Tensor& w, const optional<Tensor>& bias, Tens
     ws_bytes = workspace->nbytes();
   }
   int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
-  fllm::linear_bf16(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), opt_ptr<void>(bias),
+  return fllm::linear_bf16(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), opt_ptr<void>(bias),
                     y.data_ptr(), y.stride(0), (int)x.size(0), (int)w.size(0), (int)x.size(1), ws,
                     ws_bytes, st, (int)force_splits, cur_stream());
 }
@@ -205,7 +205,7 @@ int64_t sample_row_bytes() { return (int64_t)sizeof(fllm::SampleRow); }
 }  // namespace
 
 TORCH_LIBRARY(fllm_b200, m) {
-  m.def("linear(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status, int force_splits) -> ()", &linear);
+  m.def("linear(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status, int force_splits) -> int", &linear);
   m.def("embed(Tensor ids, Tensor table, Tensor(a!) out, float scale) -> ()", &embed);
   m.def("rmsnorm(Tensor(a!) residual, Tensor? delta, Tensor w, Tensor(b!) y, float eps, float w_offset) -> ()", &rmsnorm);
   m.def("rope_kv_write(Tensor(a!) qkv, Tensor positions, Tensor? slots, Tensor inv_freq, Tensor? q_norm_w, Tensor? k_norm_w, Tensor(b!) k_cache, Tensor(c!) v_cache, int hq, int hkv, int head_dim, int rot_dim, int rope_style, float eps, float attn_factor) -> ()", &rope_kv_write);

@@ -9,7 +9,8 @@
 namespace fllm {
 
 // ---- dense bf16 GEMM (tcgen05) ------------------------------------------------------
-void linear_bf16(const void* x, long long ldx, const void* w, long long ldw, const void* bias,
+// returns the number of kernels launched (2 when split-K adds its reduction)
+int linear_bf16(const void* x, long long ldx, const void* w, long long ldw, const void* bias,
                  void* y, long long ldy, int T, int N, int K, void* workspace,
                  size_t workspace_bytes, int* status, int force_splits, cudaStream_t stream);
 size_t gemm_bf16_workspace_bytes(int tokens, int features);

@@ -335,10 +335,10 @@ static int pick_bn_tokens(int t) {
 }
 
 // y[T, N] = x[T, K] * w[N, K]^T (+ bias[N]);  x row pitch ldx, y row pitch ldy (elements).
-void linear_bf16(const void* x, long long ldx, const void* w, long long ldw, const void* bias,
+int linear_bf16(const void* x, long long ldx, const void* w, long long ldw, const void* bias,
                  void* y, long long ldy, int T, int N, int K, void* workspace,
                  size_t workspace_bytes, int* status, int force_splits, cudaStream_t stream) {
-  if (T <= 0 || N <= 0) return;
+  if (T <= 0 || N <= 0) return 0;
   if ((K & 7) || (N & 7) || (ldx & 7) || (ldw & 7) || (ldy & 1))
     throw std::runtime_error("linear_bf16: K, N and the row pitches must be multiples of 8");
   const int sms = sm_count();
@@ -407,7 +407,9 @@ void linear_bf16(const void* x, long long ldx, const void* w, long long ldw, con
     splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(a.ws, a.k_splits, T, N, ldy, a.bias,
                                                          a.out);
     cuda_check(cudaGetLastError(), "splitk_reduce_kernel launch");
+    return 2;
   }
+  return 1;
 }
 
 }  // namespace fllm

@@ -22,9 +22,15 @@ enum : int {
   FLLM_ERR_BAD_ARGS = 3,
 };
 
-// Poll budget for intra-CTA pipeline barriers (each try_wait already blocks for
-// a hardware-defined slice, so this is seconds, not microseconds).
-constexpr uint32_t kMbarSpinLimit = 1u << 24;
+// Time budget for intra-CTA pipeline barriers. A healthy wait lasts microseconds; a
+// wait that exceeds this is a protocol error and the kernel drains instead of hanging.
+constexpr unsigned long long kMbarTimeoutNs = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -92,7 +98,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile int* abort_flag) {
   uint32_t addr = smem_u32(bar);
-  for (uint32_t it = 0; it < kMbarSpinLimit; ++it) {
+  unsigned long long t0 = 0;
+  for (uint32_t it = 0;; ++it) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -102,7 +109,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
         : "r"(addr), "r"(parity)
         : "memory");
     if (ok) return true;
-    if ((it & 1023u) == 1023u && *abort_flag) return false;
+    if ((it & 255u) == 255u) {
+      if (*abort_flag) return false;
+      const unsigned long long now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kMbarTimeoutNs) break;
+    }
   }
   *abort_flag = 1;
   return false;

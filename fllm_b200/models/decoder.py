@@ -1,0 +1,168 @@
+"""One decoder runner for every supported family (Llama, Qwen3, gpt-oss).
+
+The step contract is the reference's ragged batch (``RustDecoder::forward_with_hidden``,
+rust/engine/src/rust_decoder.rs:8480): token ids, positions, KV slots, block tables and
+the rows whose logits are wanted. The layer loop is the one of
+rust/engine/src/rust_decoder.rs:4467-6050, re-cut for bf16 activations and fused
+kernels: each norm consumes the previous projection's output as a residual delta, QK
+norm + RoPE + KV write are one kernel, and under tensor parallelism the projection
+outputs are combined either by the fused peer-memory kernels or by a library
+all-reduce (baseline).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from ..config import ModelConfig, rope_inv_freq
+from .weights import DecoderWeights, ShardSpec, make_shard_spec
+
+ACT_KIND = {"swiglu": 0, "geglu": 1, "swiglu_oai": 2}
+
+
+@dataclass
+class StepBatch:
+    """Device-side description of one engine step."""
+    token_ids: torch.Tensor          # [T] int32
+    positions: torch.Tensor          # [T] int32, position of each token in its sequence
+    slots: torch.Tensor              # [T] int32, KV slot = block * block_size + offset (-1 = skip)
+    row_seq: torch.Tensor            # [T] int32, index into block_tables
+    block_tables: torch.Tensor       # [B, max_blocks] int32
+    logit_rows: torch.Tensor         # [R] int32, token rows whose logits are needed
+    # host-side facts used to pick kernels (never read by kernels)
+    num_seqs: int = 0
+    num_tokens: int = 0
+    max_kv_len: int = 0
+    all_decode: bool = False
+    seq_lens: Optional[torch.Tensor] = None      # [B] int32 visible KV length per sequence
+    q_starts: Optional[torch.Tensor] = None      # [B+1] int32 first token row of each sequence
+
+
+class KVCache:
+    """Paged KV pool: one K and one V tensor per local layer,
+    [num_blocks, kv_heads_local, block_size, head_dim]."""
+
+    def __init__(self, num_layers: int, num_blocks: int, kv_heads: int, block_size: int, head_dim: int,
+                 device, dtype=torch.bfloat16):
+        self.num_blocks, self.block_size = num_blocks, block_size
+        self.store = torch.zeros(num_layers, 2, num_blocks, kv_heads, block_size, head_dim,
+                                 device=device, dtype=dtype)
+
+    def k(self, layer: int) -> torch.Tensor:
+        return self.store[layer, 0]
+
+    def v(self, layer: int) -> torch.Tensor:
+        return self.store[layer, 1]
+
+    @staticmethod
+    def bytes_per_block(num_layers, kv_heads, block_size, head_dim, elem=2) -> int:
+        return num_layers * 2 * kv_heads * block_size * head_dim * elem
+
+
+class Decoder:
+    def __init__(self, cfg: ModelConfig, weights: DecoderWeights, kv: KVCache, ops, spec: Optional[ShardSpec] = None,
+                 tp_group=None, layer_range: Optional[range] = None, first_stage: bool = True,
+                 last_stage: bool = True):
+        self.cfg, self.w, self.kv, self.ops = cfg, weights, kv, ops
+        self.spec = spec or make_shard_spec(cfg)
+        self.tp = tp_group            # object with all_reduce / all_gather (or None)
+        self.layer_range = layer_range or range(cfg.num_layers)
+        self.first_stage, self.last_stage = first_stage, last_stage
+        dev = weights.final_norm.device
+        inv, attn = rope_inv_freq(cfg)
+        self.inv_freq = torch.tensor(inv, dtype=torch.float32, device=dev)
+        self.attn_factor = attn
+        self.scale = cfg.head_dim ** -0.5
+        self.rope_style = 0 if cfg.rope_style == "neox" else 1
+        self.act_kind = ACT_KIND[cfg.act]
+
+    # ------------------------------------------------------------------ pieces
+    def _reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp is not None and self.tp.size > 1:
+            return self.tp.all_reduce(x)
+        return x
+
+    def _attention_block(self, li: int, lw, h: torch.Tensor, b: StepBatch) -> torch.Tensor:
+        cfg, sp, ops = self.cfg, self.spec, self.ops
+        qkv = ops.linear(h, lw.wqkv, lw.bqkv)
+        local = li - self.layer_range.start
+        kc, vc = self.kv.k(local), self.kv.v(local)
+        ops.rope_kv_write(qkv, b.positions, b.slots, self.inv_freq, lw.q_norm, lw.k_norm, kc, vc,
+                          sp.hq_local, sp.hkv_local, cfg.head_dim, cfg.rot_dim, self.rope_style,
+                          cfg.rms_eps, self.attn_factor)
+        q = qkv[:, : sp.hq_local * cfg.head_dim]
+        a = ops.attention(q, kc, vc, b.block_tables, b.row_seq, b.positions, sp.hq_local, sp.hkv_local,
+                          cfg.head_dim, self.scale, cfg.layer_window(li), lw.sinks, cfg.attn_softcap,
+                          meta=b)
+        return ops.linear(a, lw.wo, lw.bo)
+
+    def _ffn_block(self, lw, h: torch.Tensor) -> torch.Tensor:
+        cfg, ops = self.cfg, self.ops
+        if cfg.is_moe:
+            from .moe import moe_ffn
+            return moe_ffn(self, lw, h)
+        gu = ops.linear(h, lw.w_gate_up)
+        act = ops.glu(gu, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit)
+        return ops.linear(act, lw.w_down)
+
+    # ------------------------------------------------------------------ forward
+    def forward_hidden(self, b: StepBatch, hidden_in: Optional[torch.Tensor] = None,
+                       delta_in: Optional[torch.Tensor] = None):
+        """Runs this stage's layers. Returns (residual, pending_delta): the residual
+        stream and the last projection output that has not been added yet."""
+        cfg, ops = self.cfg, self.ops
+        if self.first_stage:
+            x = ops.embed(b.token_ids, self.w.embed, cfg.embed_scale)
+            delta = None
+        else:
+            x, delta = hidden_in, delta_in
+        for li, lw in zip(self.layer_range, self.w.layers):
+            h = ops.rmsnorm(x, delta, lw.attn_norm, cfg.rms_eps, cfg.norm_weight_offset)
+            o = self._reduce(self._attention_block(li, lw, h, b))
+            h = ops.rmsnorm(x, o, lw.ffn_norm, cfg.rms_eps, cfg.norm_weight_offset)
+            delta = self._reduce(self._ffn_block(lw, h))
+        return x, delta
+
+    def logits(self, x: torch.Tensor, delta: Optional[torch.Tensor], b: StepBatch) -> torch.Tensor:
+        """Final norm + LM head on the requested rows -> [R, vocab_local]."""
+        cfg, ops = self.cfg, self.ops
+        h = ops.rmsnorm(x, delta, self.w.final_norm, cfg.rms_eps, cfg.norm_weight_offset)
+        if b.all_decode and b.logit_rows.numel() == h.shape[0]:
+            hs = h                     # every row is a decode row: no gather needed
+        else:
+            hs = ops.gather_rows(h, b.logit_rows)
+        lg = ops.linear(hs, self.w.lm_head)
+        if cfg.logit_softcap > 0:
+            lg = (cfg.logit_softcap * torch.tanh(lg.float() / cfg.logit_softcap)).to(lg.dtype)
+        return lg
+
+    def forward(self, b: StepBatch) -> torch.Tensor:
+        x, delta = self.forward_hidden(b)
+        return self.logits(x, delta, b)
+
+    # ------------------------------------------------------------------ heads
+    def greedy_tokens(self, logits_local: torch.Tensor) -> torch.Tensor:
+        """Greedy token per row. With a vocabulary-parallel head only (value, index) pairs
+        travel between ranks, never the logits
+        (cf. rust/engine/src/parallel/decoder_shard.rs:546-585)."""
+        tp = self.tp
+        if tp is None or tp.size == 1:
+            return self.ops.argmax(logits_local[:, : self.w.vocab_local] if logits_local.shape[1] != self.w.vocab_local else logits_local)
+        view = logits_local[:, : max(self.w.vocab_local, 1)]
+        ids, vals = self.ops.argmax(view, id_offset=self.w.vocab_start, want_vals=True)
+        if self.w.vocab_local == 0:
+            vals = torch.full_like(vals, float("-inf"))
+        pair = torch.stack([vals, ids.float()], 1).contiguous()         # ids < 2^24 fit fp32 exactly
+        allp = tp.all_gather(pair)                                       # [tp, R, 2]
+        best = allp[:, :, 0].argmax(0)
+        # ties between ranks resolve to the lowest rank = lowest token id, like a global argmax
+        return allp[best, torch.arange(pair.shape[0], device=pair.device), 1].int()
+
+    def full_logits(self, logits_local: torch.Tensor) -> torch.Tensor:
+        tp = self.tp
+        if tp is None or tp.size == 1:
+            return logits_local[:, : self.cfg.vocab_size]
+        allp = tp.all_gather(logits_local.contiguous())                  # [tp, R, chunk]
+        return allp.permute(1, 0, 2).reshape(logits_local.shape[0], -1)[:, : self.cfg.vocab_size]

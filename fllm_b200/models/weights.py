@@ -1,0 +1,240 @@
+"""Decoder weights: containers, deterministic random initialisation and the
+tensor-parallel sharding rules.
+
+Sharding follows the reference's plan (rust/engine/src/parallel/plan.rs:26-45,
+rust/engine/src/parallel/decoder_shard.rs:112-214): query heads are divided by
+``tp``; KV heads are divided, or replicated when ``tp`` exceeds their count;
+q/k/v/gate/up are cut by output rows (column-parallel), o/down by input columns
+(row-parallel) with the bias kept on tp-rank 0; norms are replicated; the LM head
+is cut by vocabulary rows in equal padded chunks; experts are either cut like a
+dense FFN (expert-TP) or assigned whole to ranks (expert parallel).
+"""
+from __future__ import annotations
+
+import hashlib
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config import ModelConfig
+
+
+@dataclass
+class LayerWeights:
+    attn_norm: torch.Tensor
+    wqkv: torch.Tensor
+    wo: torch.Tensor
+    ffn_norm: torch.Tensor
+    bqkv: Optional[torch.Tensor] = None
+    bo: Optional[torch.Tensor] = None
+    q_norm: Optional[torch.Tensor] = None
+    k_norm: Optional[torch.Tensor] = None
+    sinks: Optional[torch.Tensor] = None
+    w_gate_up: Optional[torch.Tensor] = None
+    w_down: Optional[torch.Tensor] = None
+    # mixture of experts
+    router_w: Optional[torch.Tensor] = None
+    router_b: Optional[torch.Tensor] = None
+    exp_gate_up: Optional[torch.Tensor] = None      # [E_local, 2*I, H]
+    exp_gate_up_b: Optional[torch.Tensor] = None    # [E_local, 2*I]
+    exp_down: Optional[torch.Tensor] = None         # [E_local, H, I]
+    exp_down_b: Optional[torch.Tensor] = None       # [E_local, H]
+    # packed formats keep their payload here (format name -> tensors)
+    packed: Dict[str, object] = field(default_factory=dict)
+
+
+@dataclass
+class DecoderWeights:
+    embed: torch.Tensor
+    layers: List[LayerWeights]
+    final_norm: torch.Tensor
+    lm_head: torch.Tensor               # [vocab_local(padded), H]
+    vocab_start: int = 0
+    vocab_local: int = 0
+
+    def nbytes(self) -> int:
+        n = 0
+        seen = set()
+
+        def add(t):
+            nonlocal n
+            if isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                n += t.numel() * t.element_size()
+
+        add(self.embed); add(self.final_norm); add(self.lm_head)
+        for l in self.layers:
+            for v in vars(l).values():
+                add(v)
+        return n
+
+
+@dataclass
+class ShardSpec:
+    """Per-rank head / column ranges for one tensor-parallel rank."""
+    tp: int
+    tp_rank: int
+    hq_local: int
+    hkv_local: int
+    q_head_start: int
+    kv_head_start: int
+    inter_start: int
+    inter_local: int
+    vocab_chunk: int
+    expert_start: int = 0
+    expert_local: int = 0
+    expert_parallel: bool = False
+
+
+def attention_split(cfg: ModelConfig, tp: int, tp_rank: int):
+    """(q heads, kv heads, first q head, first kv head) of one rank."""
+    if cfg.num_heads % tp:
+        raise ValueError(f"{cfg.num_heads} query heads cannot be divided over tp={tp}")
+    hq = cfg.num_heads // tp
+    if cfg.num_kv_heads >= tp:
+        if cfg.num_kv_heads % tp:
+            raise ValueError(f"{cfg.num_kv_heads} KV heads cannot be divided over tp={tp}")
+        hkv = cfg.num_kv_heads // tp
+        kv0 = tp_rank * hkv
+    else:
+        if tp % cfg.num_kv_heads:
+            raise ValueError(f"tp={tp} must be a multiple of {cfg.num_kv_heads} KV heads")
+        hkv = 1
+        kv0 = tp_rank // (tp // cfg.num_kv_heads)
+    return hq, hkv, tp_rank * hq, kv0
+
+
+def expert_range(num_experts: int, tp: int, rank: int):
+    """Contiguous expert range of a rank, remainder to the first ranks
+    (rust/engine/src/parallel/ctx.rs:100-105)."""
+    per, rem = divmod(num_experts, tp)
+    start = rank * per + min(rank, rem)
+    return start, per + (1 if rank < rem else 0)
+
+
+def make_shard_spec(cfg: ModelConfig, tp: int = 1, tp_rank: int = 0, expert_parallel: bool = False,
+                    align: int = 8) -> ShardSpec:
+    hq, hkv, q0, kv0 = attention_split(cfg, tp, tp_rank)
+    inter = cfg.moe_intermediate_size if cfg.is_moe else cfg.intermediate_size
+    ep = bool(expert_parallel and cfg.is_moe and tp > 1)
+    if ep:
+        i0, il = 0, inter
+    else:
+        if inter % (tp * align):
+            raise ValueError(f"intermediate size {inter} cannot be cut into {tp} aligned parts")
+        il = inter // tp
+        i0 = tp_rank * il
+    chunk = -(-cfg.vocab_size // tp)
+    chunk = -(-chunk // 128) * 128 if tp > 1 else cfg.vocab_size
+    e0, el = expert_range(cfg.num_experts, tp, tp_rank) if ep else (0, cfg.num_experts)
+    return ShardSpec(tp, tp_rank, hq, hkv, q0, kv0, i0, il, chunk, e0, el, ep)
+
+
+def _randn(shape, gen, device, dtype, std=0.02):
+    return (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std).to(dtype)
+
+
+def init_random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: int = 0,
+                        tp: int = 1, tp_rank: int = 0, expert_parallel: bool = False,
+                        layers: Optional[range] = None, first_stage: bool = True,
+                        last_stage: bool = True) -> DecoderWeights:
+    """N(0, 0.02) weights, norm weights 1. Every tensor is drawn at full size from a
+    generator seeded by (seed, layer, tensor) and then cut, so any (tp, pp) layout
+    holds exactly the same model as the single-device one."""
+    device = torch.device(device)
+    sp = make_shard_spec(cfg, tp, tp_rank, expert_parallel)
+    D, H = cfg.head_dim, cfg.hidden_size
+    layers = range(cfg.num_layers) if layers is None else layers
+
+    def gen_for(*key):
+        g = torch.Generator(device=device)
+        digest = hashlib.sha256(repr((seed,) + key).encode()).digest()
+        g.manual_seed(int.from_bytes(digest[:6], "little"))
+        return g
+
+    def full(shape, *key, std=0.02):
+        return _randn(shape, gen_for(*key), device, dtype, std)
+
+    ones = lambda n: torch.ones(n, device=device, dtype=dtype)
+    out_layers = []
+    for li in layers:
+        wq = full((cfg.q_size, H), li, 0)
+        wk = full((cfg.kv_size, H), li, 1)
+        wv = full((cfg.kv_size, H), li, 2)
+        qs = slice(sp.q_head_start * D, (sp.q_head_start + sp.hq_local) * D)
+        ks = slice(sp.kv_head_start * D, (sp.kv_head_start + sp.hkv_local) * D)
+        wqkv = torch.cat([wq[qs], wk[ks], wv[ks]], 0).contiguous()
+        wo = full((H, cfg.q_size), li, 3)[:, qs].contiguous()
+        lw = LayerWeights(attn_norm=ones(H), wqkv=wqkv, wo=wo, ffn_norm=ones(H))
+        del wq, wk, wv
+        if cfg.attn_bias:
+            bq = full((cfg.q_size,), li, 10)
+            bk = full((cfg.kv_size,), li, 11)
+            bv = full((cfg.kv_size,), li, 12)
+            lw.bqkv = torch.cat([bq[qs], bk[ks], bv[ks]]).contiguous()
+            bo = full((H,), li, 13)
+            lw.bo = bo if tp_rank == 0 else torch.zeros_like(bo)
+        if cfg.qk_norm:
+            lw.q_norm, lw.k_norm = ones(D), ones(D)
+        if cfg.attn_sinks:
+            s = torch.randn(cfg.num_heads, generator=gen_for(li, 14), device=device) * 0.5
+            lw.sinks = s[sp.q_head_start: sp.q_head_start + sp.hq_local].float().contiguous()
+        if cfg.is_moe:
+            E, I = cfg.num_experts, cfg.moe_intermediate_size
+            lw.router_w = full((E, H), li, 20)
+            lw.router_b = full((E,), li, 21) if cfg.expert_bias else None
+            gu = full((E, 2 * I, H), li, 22)
+            dn = full((E, H, I), li, 23)
+            gub = full((E, 2 * I), li, 24) if cfg.expert_bias else None
+            dnb = full((E, H), li, 25) if cfg.expert_bias else None
+            if sp.expert_parallel:
+                es = slice(sp.expert_start, sp.expert_start + sp.expert_local)
+                lw.exp_gate_up, lw.exp_down = gu[es].contiguous(), dn[es].contiguous()
+                lw.exp_gate_up_b = gub[es].contiguous() if gub is not None else None
+                lw.exp_down_b = dnb[es].contiguous() if dnb is not None else None
+            else:
+                lw.exp_gate_up = _cut_gate_up(gu, cfg, sp, dim=1)
+                lw.exp_down = dn[:, :, sp.inter_start: sp.inter_start + sp.inter_local].contiguous()
+                lw.exp_gate_up_b = _cut_gate_up(gub, cfg, sp, dim=1) if gub is not None else None
+                if dnb is not None:
+                    lw.exp_down_b = dnb if tp_rank == 0 else torch.zeros_like(dnb)
+        else:
+            I = cfg.intermediate_size
+            g = full((I, H), li, 4)
+            u = full((I, H), li, 5)
+            isl = slice(sp.inter_start, sp.inter_start + sp.inter_local)
+            lw.w_gate_up = torch.cat([g[isl], u[isl]], 0).contiguous()
+            lw.w_down = full((H, I), li, 6)[:, isl].contiguous()
+        out_layers.append(lw)
+
+    embed = full((cfg.vocab_size, H), "embed") if first_stage or cfg.tie_embeddings else \
+        torch.empty(0, H, device=device, dtype=dtype)
+    head_full = embed if cfg.tie_embeddings else (full((cfg.vocab_size, H), "head") if last_stage else None)
+    v0 = tp_rank * sp.vocab_chunk if tp > 1 else 0
+    if head_full is None:
+        lm_head = torch.empty(0, H, device=device, dtype=dtype)
+        v_local = 0
+    elif tp > 1:
+        v1 = min(v0 + sp.vocab_chunk, cfg.vocab_size)
+        v_local = max(v1 - v0, 0)
+        lm_head = torch.zeros(sp.vocab_chunk, H, device=device, dtype=dtype)
+        if v_local:
+            lm_head[:v_local] = head_full[v0:v1]
+    else:
+        lm_head, v_local = head_full, cfg.vocab_size
+    if not first_stage and not cfg.tie_embeddings:
+        embed = torch.empty(0, H, device=device, dtype=dtype)
+    return DecoderWeights(embed=embed, layers=out_layers, final_norm=ones(H), lm_head=lm_head,
+                          vocab_start=v0, vocab_local=v_local)
+
+
+def _cut_gate_up(t, cfg: ModelConfig, sp: ShardSpec, dim: int):
+    """Cut a fused gate/up tensor along `dim` (size 2*I). For the interleaved gpt-oss layout the
+    (gate, up) pairs stay together; otherwise the gate half and the up half are cut separately."""
+    I = t.shape[dim] // 2
+    if cfg.act == "swiglu_oai":
+        return t.narrow(dim, 2 * sp.inter_start, 2 * sp.inter_local).contiguous()
+    g = t.narrow(dim, sp.inter_start, sp.inter_local)
+    u = t.narrow(dim, I + sp.inter_start, sp.inter_local)
+    return torch.cat([g, u], dim).contiguous()

@@ -1,0 +1,104 @@
+"""Python face of the sm_100a kernels (``torch.ops.fllm_b200``).
+
+Every method mirrors :class:`fllm_b200.ops.reference.RefOps`; the model runner is
+written once against this interface. There is no fallback inside this class: if
+the library is missing the constructor raises.
+"""
+from __future__ import annotations
+
+import struct
+from typing import Optional
+
+import torch
+
+from ._lib import load_cuda
+
+
+class NativeOps:
+    name = "sm100a"
+
+    def __init__(self, device: torch.device, workspace_bytes: int = 96 << 20):
+        self.k = load_cuda()
+        self.device = torch.device(device)
+        self.workspace = torch.empty(workspace_bytes, dtype=torch.uint8, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.use_tc_attention = True
+        self.launches = 0            # kernels launched through this object (graph capture included)
+
+    # ---------------------------------------------------------------- dense
+    def linear(self, x, w, bias=None, out=None, force_splits: int = 0):
+        if out is None:
+            out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
+        self.launches += self.k.linear(x, w, bias, out, self.workspace, self.status, force_splits)
+        return out
+
+    def embed(self, ids, table, scale=1.0):
+        out = torch.empty(ids.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+        self.k.embed(ids, table, out, float(scale))
+        self.launches += 1
+        return out
+
+    def rmsnorm(self, residual, delta, w, eps, w_offset=0.0):
+        y = torch.empty_like(residual)
+        self.k.rmsnorm(residual, delta, w, y, float(eps), float(w_offset))
+        self.launches += 1
+        return y
+
+    def rope_kv_write(self, qkv, positions, slots, inv_freq, q_norm_w, k_norm_w, k_cache, v_cache,
+                      hq, hkv, head_dim, rot_dim, rope_style, eps, attn_factor=1.0):
+        self.k.rope_kv_write(qkv, positions, slots, inv_freq, q_norm_w, k_norm_w, k_cache, v_cache,
+                             hq, hkv, head_dim, rot_dim, rope_style, float(eps), float(attn_factor))
+        self.launches += 1
+        return qkv
+
+    def glu(self, x, act_kind=0, alpha=1.702, limit=7.0):
+        out = torch.empty(x.shape[0], x.shape[1] // 2, dtype=x.dtype, device=x.device)
+        self.k.glu(x, out, act_kind, float(alpha), float(limit))
+        self.launches += 1
+        return out
+
+    def gather_rows(self, x, rows):
+        out = torch.empty(rows.numel(), x.shape[1], dtype=x.dtype, device=x.device)
+        self.k.gather_rows(x, rows, out)
+        self.launches += 1
+        return out
+
+    # ---------------------------------------------------------------- attention
+    def attention(self, q, k_cache, v_cache, block_tables, row_seq, positions, hq, hkv, head_dim,
+                  scale, window=0, sinks=None, softcap=0.0, meta=None):
+        out = torch.empty(q.shape[0], hq * head_dim, dtype=q.dtype, device=q.device)
+        self.k.attention_generic(q, k_cache, v_cache, block_tables, row_seq, positions, out, hq, hkv,
+                                 head_dim, float(scale), int(window), sinks, float(softcap))
+        self.launches += 1
+        return out
+
+    # ---------------------------------------------------------------- sampling
+    def argmax(self, logits, id_offset=0, want_vals=False):
+        ids = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+        vals = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device) if want_vals else None
+        self.k.argmax(logits, ids, vals, id_offset)
+        self.launches += 1
+        return (ids, vals) if want_vals else ids
+
+    def sample(self, logits, params, pen_ids=None, pen_counts=None, bias_ids=None, bias_vals=None,
+               allow_mask=None, want_logprobs=False):
+        ids = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+        lp = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device) if want_logprobs else None
+        self.k.sample(logits, params, pen_ids, pen_counts, bias_ids, bias_vals, allow_mask, ids, lp)
+        self.launches += 1
+        return (ids, lp) if want_logprobs else ids
+
+    def check_status(self) -> int:
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+        return code
+
+
+SAMPLE_ROW_FMT = "<6fiIQ"      # mirrors struct fllm::SampleRow (40 bytes)
+
+
+def pack_sample_rows(rows) -> bytes:
+    """rows: iterable of (temperature, top_p, min_p, repetition_penalty, presence_penalty,
+    frequency_penalty, top_k, draw, seed)."""
+    return b"".join(struct.pack(SAMPLE_ROW_FMT, *r) for r in rows)

@@ -1,0 +1,176 @@
+"""Plain PyTorch fp32 restatement of every op. It is the numerics oracle of the
+CUDA kernels and the engine's compute path on machines without a GPU (tests,
+gloo-rank parallel equivalence); it is never used when a GPU is present.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+
+class RefOps:
+    name = "reference"
+
+    # ---------------------------------------------------------------- dense
+    def linear(self, x, w, bias=None, out=None):
+        y = x.float() @ w.float().t()
+        if bias is not None:
+            y = y + bias.float()
+        y = y.to(x.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
+    def embed(self, ids, table, scale=1.0):
+        x = table[ids.long()]
+        if scale != 1.0:
+            x = (x.float() * scale).to(table.dtype)
+        return x
+
+    def rmsnorm(self, residual, delta, w, eps, w_offset=0.0):
+        """Returns y; when delta is given, residual += delta in place first."""
+        if delta is not None:
+            residual.copy_((residual.float() + delta.float()).to(residual.dtype))
+        x = residual.float()
+        inv = torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+        return (x * inv * (w.float() + w_offset)).to(residual.dtype)
+
+    # ---------------------------------------------------------------- rope + kv
+    def rope_kv_write(self, qkv, positions, slots, inv_freq, q_norm_w, k_norm_w, k_cache, v_cache,
+                      hq, hkv, head_dim, rot_dim, rope_style, eps, attn_factor=1.0):
+        T = qkv.shape[0]
+        x = qkv.float().view(T, hq + 2 * hkv, head_dim)
+        q, k, v = x[:, :hq], x[:, hq:hq + hkv], x[:, hq + hkv:]
+
+        def norm(t, w):
+            if w is None:
+                return t
+            inv = torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps)
+            return (t * inv * w.float()).to(qkv.dtype).float()
+
+        q, k = norm(q, q_norm_w), norm(k, k_norm_w)
+        ang = positions.float()[:, None] * inv_freq.float()[None, :]      # [T, rot/2]
+        cos, sin = ang.cos() * attn_factor, ang.sin() * attn_factor
+
+        def rot(t):
+            r, rest = t[..., :rot_dim], t[..., rot_dim:]
+            c, s = cos[:, None, :], sin[:, None, :]
+            if rope_style == 0:
+                a, b = r[..., : rot_dim // 2], r[..., rot_dim // 2:]
+                r2 = torch.cat([a * c - b * s, b * c + a * s], -1)
+            else:
+                a, b = r[..., 0::2], r[..., 1::2]
+                r2 = torch.stack([a * c - b * s, b * c + a * s], -1).flatten(-2)
+            return torch.cat([r2, rest], -1)
+
+        q, k = rot(q), rot(k)
+        qkv.view(T, hq + 2 * hkv, head_dim)[:, :hq] = q.to(qkv.dtype)
+        if slots is not None:
+            bs = k_cache.shape[2]
+            ok = slots >= 0
+            sl = slots[ok].long()
+            blk, off = sl // bs, sl % bs
+            k_cache[blk, :, off] = k[ok].to(k_cache.dtype)
+            v_cache[blk, :, off] = v[ok].to(v_cache.dtype)
+        return qkv
+
+    def glu(self, x, act_kind=0, alpha=1.702, limit=7.0):
+        xf = x.float()
+        if act_kind == 2:
+            g, u = xf[:, 0::2], xf[:, 1::2]
+            g = g.clamp(max=limit)
+            u = u.clamp(min=-limit, max=limit)
+            y = g * torch.sigmoid(alpha * g) * (u + 1)
+        else:
+            inter = x.shape[1] // 2
+            g, u = xf[:, :inter], xf[:, inter:]
+            y = (F.silu(g) if act_kind == 0 else F.gelu(g, approximate="tanh")) * u
+        return y.to(x.dtype)
+
+    def gather_rows(self, x, rows):
+        return x[rows.long()].contiguous()
+
+    # ---------------------------------------------------------------- attention
+    def attention(self, q, k_cache, v_cache, block_tables, row_seq, positions, hq, hkv, head_dim,
+                  scale, window=0, sinks=None, softcap=0.0, meta=None):
+        T = q.shape[0]
+        bs = k_cache.shape[2]
+        out = torch.empty(T, hq * head_dim, dtype=q.dtype, device=q.device)
+        qf = q.float().view(T, hq, head_dim)
+        g = hq // hkv
+        for t in range(T):
+            seq = int(row_seq[t])
+            n = int(positions[t]) + 1
+            begin = max(0, n - window) if window > 0 else 0
+            nblk = (n + bs - 1) // bs
+            blocks = block_tables[seq, :nblk].long()
+            k = k_cache[blocks].float().permute(1, 0, 2, 3).reshape(hkv, nblk * bs, head_dim)[:, begin:n]
+            v = v_cache[blocks].float().permute(1, 0, 2, 3).reshape(hkv, nblk * bs, head_dim)[:, begin:n]
+            k = k.repeat_interleave(g, 0)
+            v = v.repeat_interleave(g, 0)
+            s = torch.einsum("hd,hnd->hn", qf[t], k) * scale
+            if softcap > 0:
+                s = softcap * torch.tanh(s / softcap)
+            if sinks is not None:
+                s = torch.cat([s, sinks.float()[:, None]], 1)
+                p = torch.softmax(s, -1)[:, :-1]
+            else:
+                p = torch.softmax(s, -1)
+            out[t] = torch.einsum("hn,hnd->hd", p, v).reshape(-1).to(q.dtype)
+        return out
+
+    # ---------------------------------------------------------------- sampling
+    def argmax(self, logits, id_offset=0, want_vals=False):
+        vals, ids = logits.float().max(-1)
+        ids = (ids + id_offset).int()
+        return (ids, vals) if want_vals else ids
+
+
+def philox_uniform(seed: int, draw: int, idx: int) -> float:
+    """Host restatement of the device sampler's counter-based uniform."""
+    M = 0xFFFFFFFF
+    c = [idx & M, draw & M, 0x9E3779B9, 0xBB67AE85]
+    k0, k1 = seed & M, (seed >> 32) & M
+    for _ in range(10):
+        p0 = 0xD2511F53 * c[0]
+        p1 = 0xCD9E8D57 * c[2]
+        hi0, lo0 = p0 >> 32, p0 & M
+        hi1, lo1 = p1 >> 32, p1 & M
+        c = [(hi1 ^ c[1] ^ k0) & M, lo1, (hi0 ^ c[3] ^ k1) & M, lo0]
+        k0 = (k0 + 0x9E3779B9) & M
+        k1 = (k1 + 0xBB67AE85) & M
+    return ((c[0] >> 8) + 0.5) / 16777216.0
+
+
+def sample_reference(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float,
+                     seed: int, draw: int) -> int:
+    """Filter order and Gumbel-max draw of the device sampler, on one fp32 row."""
+    x = logits.float().cpu()
+    if temperature <= 0:
+        return int(x.argmax())
+    vmax = float(x.max())
+    thr = -math.inf
+    if min_p > 0:
+        thr = max(thr, vmax + temperature * math.log(min_p))
+    if 0 < top_k < x.numel():
+        thr = max(thr, float(torch.topk(x, top_k).values[-1]))
+    if 0 < top_p < 1:
+        keep = x >= thr
+        w = torch.where(keep, torch.exp((x - vmax) / temperature), torch.zeros_like(x))
+        need = top_p * float(w.sum())
+        sv, si = torch.sort(x, descending=True)
+        cw = torch.cumsum(w[si], 0)
+        j = int(torch.searchsorted(cw, torch.tensor(need * (1 - 1e-6))))
+        j = min(j, x.numel() - 1)
+        thr = max(thr, float(sv[j]))
+    best, best_i = -math.inf, -1
+    for i in torch.nonzero(x >= thr).flatten().tolist():
+        u = philox_uniform(seed, draw, i)
+        g = (float(x[i]) - vmax) / temperature - math.log(-math.log(u))
+        if g > best:
+            best, best_i = g, i
+    return best_i

@@ -1,0 +1,377 @@
+"""The engine: owns weights, paged KV, scheduler and the step loop.
+
+``step()`` is the hot loop of the reference's ``InferenceRuntime::step``
+(rust/engine/src/runtime.rs:2141-2150, :2212-3150): schedule -> build the ragged batch
+-> forward -> sample / verify -> commit -> token events. Differences that matter on a
+B200: per-step arrays travel in ONE pinned-host -> device copy; pure-decode steps
+replay a captured CUDA graph per batch bucket (also inside a tensor-parallel group,
+where the reference switches graphs off, docs/multi-gpu.md:94-96); greedy tokens are
+picked on the device and only the ids come back.
+
+Every rank of a tensor-parallel group runs this same class on the same request
+stream (SPMD scheduling), so no step descriptor has to be broadcast; rank 0 is the
+only one that reports events.
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from typing import Dict, Iterable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..config import EngineConfig, ModelConfig, ParallelConfig
+from ..models.decoder import Decoder, KVCache, StepBatch
+from ..models.weights import DecoderWeights, init_random_weights, make_shard_spec
+from ..ops import get_ops
+from .block_manager import BlockManager
+from .request import Request, RequestStatus, SamplingParams, TokenEvent
+from .scheduler import ScheduledSeq, ScheduledStep, Scheduler
+
+
+class EngineStats:
+    def __init__(self):
+        self.steps = 0
+        self.graph_steps = 0
+        self.prefill_tokens = 0
+        self.decode_tokens = 0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.schedule_ns = 0
+        self.forward_calls = 0
+        self.kernel_launches = 0
+
+
+class LLMEngine:
+    def __init__(self, model_cfg: ModelConfig, engine_cfg: Optional[EngineConfig] = None,
+                 parallel: Optional[ParallelConfig] = None, device="cuda", weights: Optional[DecoderWeights] = None,
+                 tp_group=None, tp_rank: int = 0, seed: int = 0, eos_token_id: Optional[int] = None,
+                 ops=None):
+        self.model_cfg = model_cfg
+        self.cfg = engine_cfg or EngineConfig()
+        self.par = parallel or ParallelConfig()
+        self.device = torch.device(device)
+        self.is_cuda = self.device.type == "cuda"
+        if self.is_cuda:
+            torch.cuda.set_device(self.device)
+        self.ops = ops or get_ops(self.device)
+        self.tp_group, self.tp_rank = tp_group, tp_rank
+        tp = self.par.tp
+        self.spec = make_shard_spec(model_cfg, tp, tp_rank, self.par.expert_parallel)
+        self.weights = weights or init_random_weights(
+            model_cfg, self.device, torch.bfloat16, seed, tp, tp_rank, self.par.expert_parallel)
+        self.eos_token_id = eos_token_id
+        self.block_size = self.cfg.block_size
+        self.max_blocks_per_seq = -(-self.cfg.max_model_len // self.block_size)
+        num_blocks = self.cfg.num_kv_blocks or self._size_kv_pool()
+        self.kv = KVCache(model_cfg.num_layers, num_blocks, self.spec.hkv_local, self.block_size,
+                          model_cfg.head_dim, self.device)
+        self.decoder = Decoder(model_cfg, self.weights, self.kv, self.ops, self.spec, tp_group)
+        self.blocks = BlockManager(num_blocks, self.block_size, self.cfg.enable_prefix_caching,
+                                   self.cfg.watermark)
+        window = model_cfg.sliding_window if (model_cfg.sliding_window and model_cfg.window_pattern is None) else 0
+        self.scheduler = Scheduler(self.cfg, self.blocks, window)
+        self.requests: Dict[str, Request] = {}
+        self._seq_ids = itertools.count()
+        self._req_ids = itertools.count()
+        self.stats = EngineStats()
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._graph_pool = None
+        # staging: [ids | positions | slots | row_seq | logit_rows | block tables]
+        max_rows = max(self.cfg.max_num_seqs, self._bucket_for(self.cfg.max_num_seqs))
+        cap = 5 * max(self.cfg.max_num_batched_tokens, max_rows) + max_rows * self.max_blocks_per_seq + 64
+        self._host = torch.empty(cap, dtype=torch.int32, pin_memory=self.is_cuda)
+        self._host_np = self._host.numpy()
+        self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        self._out_host = torch.empty(self.cfg.max_num_batched_tokens + 64, dtype=torch.int32,
+                                     pin_memory=self.is_cuda)
+
+    # ------------------------------------------------------------------ sizing
+    def _size_kv_pool(self) -> int:
+        per_block = KVCache.bytes_per_block(self.model_cfg.num_layers, self.spec.hkv_local,
+                                            self.block_size, self.model_cfg.head_dim)
+        if self.is_cuda:
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = int(total * self.cfg.gpu_memory_utilization) - (total - free)
+            budget -= 4 << 30           # activations, graphs, workspaces
+        else:
+            budget = 256 << 20
+        want = self.cfg.max_num_seqs * self.max_blocks_per_seq
+        return max(64, min(budget // per_block, want))
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    request_id: Optional[str] = None) -> str:
+        params = params or SamplingParams()
+        params.validate(self.model_cfg.vocab_size)
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            raise ValueError("empty prompt")
+        if len(prompt) + 1 > self.cfg.max_model_len:
+            raise ValueError(f"prompt of {len(prompt)} tokens exceeds max_model_len={self.cfg.max_model_len}")
+        rid = request_id or f"req-{next(self._req_ids)}"
+        req = Request(rid, next(self._seq_ids), prompt, params)
+        self.requests[rid] = req
+        self.scheduler.add(req)
+        return rid
+
+    def abort_request(self, request_id: str) -> bool:
+        r = self.scheduler.abort(request_id)
+        self.requests.pop(request_id, None)
+        return r is not None
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ------------------------------------------------------------------ batch building
+    def _build_batch(self, step: ScheduledStep, pad_to: int = 0) -> StepBatch:
+        seqs = step.seqs
+        T = step.num_tokens
+        B = len(seqs)
+        Tp = max(T, pad_to)
+        Bp = max(B, pad_to) if pad_to else B
+        bs = self.block_size
+        h = self._host_np
+        ids = h[0:Tp]
+        pos = h[Tp:2 * Tp]
+        slots = h[2 * Tp:3 * Tp]
+        rseq = h[3 * Tp:4 * Tp]
+        rows: List[int] = []
+        max_kv = 0
+        max_blocks = 1
+        for s in seqs:
+            max_blocks = max(max_blocks, len(self.blocks.table(s.req.seq_id)))
+        if pad_to:
+            max_blocks = self.max_blocks_per_seq
+        R_cap = Tp
+        lrow = h[4 * Tp:4 * Tp + R_cap]
+        tab = h[5 * Tp:5 * Tp + Bp * max_blocks].reshape(Bp, max_blocks)
+        t = 0
+        for i, s in enumerate(seqs):
+            r = s.req
+            n = s.count
+            tb = self.blocks.np_table(r.seq_id)
+            if n == 1 and not s.verify and r.output:       # decode row: no list building
+                p0 = s.start
+                ids[t] = r.output[-1] if p0 == r.num_tokens - 1 else r.all_tokens[p0]
+                pos[t] = p0
+                slots[t] = tb[p0 // bs] * bs + p0 % bs
+            else:
+                toks = r.prompt + r.output if not s.verify else r.prompt + r.output + r.draft
+                ids[t:t + n] = toks[s.start:s.start + n]
+                p = np.arange(s.start, s.start + n, dtype=np.int32)
+                pos[t:t + n] = p
+                slots[t:t + n] = tb[p // bs] * bs + p % bs
+            rseq[t:t + n] = i
+            tab[i, :tb.shape[0]] = tb
+            if s.wants_logits:
+                if s.verify:
+                    rows.extend(range(t, t + n))
+                else:
+                    rows.append(t + n - 1)
+            max_kv = max(max_kv, s.start + n)
+            t += n
+        if Tp > T:           # padding rows of a graph bucket: no KV write, row 0's table
+            ids[T:Tp] = 0
+            pos[T:Tp] = 0
+            slots[T:Tp] = -1
+            rseq[T:Tp] = 0
+            rows.extend(range(T, Tp))
+        R = len(rows)
+        lrow[:R] = rows
+        used = 5 * Tp + Bp * max_blocks
+        dev = self._dev
+        if self.is_cuda:
+            dev[:used].copy_(self._host[:used], non_blocking=True)
+        else:
+            dev[:used] = self._host[:used]
+        self.stats.h2d_bytes += used * 4
+        return StepBatch(
+            token_ids=dev[0:Tp], positions=dev[Tp:2 * Tp], slots=dev[2 * Tp:3 * Tp],
+            row_seq=dev[3 * Tp:4 * Tp], logit_rows=dev[4 * Tp:4 * Tp + R],
+            block_tables=dev[5 * Tp:5 * Tp + Bp * max_blocks].view(Bp, max_blocks),
+            num_seqs=B, num_tokens=T, max_kv_len=max_kv, all_decode=step.all_decode)
+
+    # ------------------------------------------------------------------ graphs
+    def _bucket_for(self, n: int) -> int:
+        for b in self.cfg.graph_buckets:
+            if b >= n:
+                return b
+        return 0
+
+    def _decode_with_graph(self, step: ScheduledStep) -> torch.Tensor:
+        """Pure-decode step through a captured graph; returns greedy ids for the bucket rows."""
+        n = len(step.seqs)
+        bucket = self._bucket_for(n)
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = _DecodeGraph(self, bucket)
+            self._graphs[bucket] = g
+        batch = self._build_batch(step, pad_to=bucket)     # fills the static staging buffer
+        g.replay()
+        self.stats.graph_steps += 1
+        return g.tokens, g.logits, batch
+
+    # ------------------------------------------------------------------ step
+    @torch.inference_mode()
+    def step(self) -> List[TokenEvent]:
+        t0 = time.perf_counter_ns()
+        step = self.scheduler.schedule()
+        self.stats.schedule_ns += time.perf_counter_ns() - t0
+        events: List[TokenEvent] = []
+        for r in step.expired:
+            events.append(TokenEvent(r.request_id, [], True, r.finish_reason, error=r.finish_reason))
+            self.requests.pop(r.request_id, None)
+        if step.empty:
+            return events
+        for src, dst in step.cow:
+            self.kv.store[:, :, dst].copy_(self.kv.store[:, :, src])
+        use_graph = (self.is_cuda and self.cfg.use_cuda_graphs and step.all_decode
+                     and not any(s.verify for s in step.seqs)
+                     and self._bucket_for(len(step.seqs)) > 0)
+        l0 = getattr(self.ops, "launches", 0)
+        if use_graph:
+            tokens_dev, logits, batch = self._decode_with_graph(step)
+            self.stats.kernel_launches += self._graphs[self._bucket_for(len(step.seqs))].launches
+        else:
+            batch = self._build_batch(step)
+            logits = self.decoder.forward(batch)
+            tokens_dev = self.decoder.greedy_tokens(logits)
+        self.stats.forward_calls += 1
+        needs_sampler = any(s.wants_logits and s.req.params.needs_full_sampler for s in step.seqs)
+        if needs_sampler:
+            tokens_dev = self._sample(step, logits, tokens_dev)
+        n_rows = tokens_dev.shape[0]
+        out = self._out_host[:n_rows]
+        out.copy_(tokens_dev, non_blocking=self.is_cuda)
+        if self.is_cuda:
+            torch.cuda.current_stream().synchronize()
+        self.stats.d2h_bytes += n_rows * 4
+        self.stats.kernel_launches += getattr(self.ops, "launches", 0) - l0
+        toks = out.tolist()
+        events.extend(self._commit(step, toks))
+        self.stats.steps += 1
+        return events
+
+    def _sample(self, step: ScheduledStep, logits: torch.Tensor, greedy: torch.Tensor) -> torch.Tensor:
+        from .sampler import sample_step
+        full = self.decoder.full_logits(logits)
+        return sample_step(self, step, full, greedy)
+
+    def _commit(self, step: ScheduledStep, toks: List[int]) -> List[TokenEvent]:
+        events: List[TokenEvent] = []
+        now = time.monotonic()
+        row = 0
+        for s in step.seqs:
+            r = s.req
+            if not s.wants_logits:
+                self.scheduler.commit(s, [])
+                self.stats.prefill_tokens += s.count
+                continue
+            if s.verify:
+                target = toks[row:row + s.count]
+                row += s.count
+                acc = 0
+                while acc < s.verify and r.draft[acc] == target[acc]:
+                    acc += 1
+                new = r.draft[:acc] + [target[acc]]
+                self.scheduler.commit(s, new, accepted_drafts=acc)
+            else:
+                new = [toks[row]]
+                row += 1
+                self.scheduler.commit(s, new)
+            if s.count > 1 and not s.verify:
+                self.stats.prefill_tokens += s.count
+            else:
+                self.stats.decode_tokens += len(new)
+            if r.first_token_time is None:
+                r.first_token_time = now
+            r.last_token_time = now
+            r.token_times.append(now)
+            reason = self._finish_reason(r, new)
+            if reason:
+                # drop tokens generated past a stop inside a multi-token (speculative) commit
+                self.scheduler.finish(r, reason)
+                self.requests.pop(r.request_id, None)
+            if self.tp_rank == 0:
+                events.append(TokenEvent(r.request_id, new, bool(reason), reason))
+        return events
+
+    def _finish_reason(self, r: Request, new: List[int]) -> Optional[str]:
+        p = r.params
+        n_out = len(r.output)
+        for i, t in enumerate(new):
+            idx = n_out - len(new) + i + 1
+            if idx < p.min_tokens:
+                continue
+            if (not p.ignore_eos and self.eos_token_id is not None and t == self.eos_token_id) \
+                    or t in p.stop_token_ids:
+                del r.output[idx:]
+                del new[i + 1:]
+                return "stop"
+        if n_out >= p.max_tokens:
+            del r.output[p.max_tokens:]
+            return "length"
+        if r.num_tokens >= self.cfg.max_model_len:
+            return "length"
+        return None
+
+    # ------------------------------------------------------------------ convenience
+    def generate(self, prompts: Iterable[Sequence[int]], params: Optional[SamplingParams] = None) -> List[List[int]]:
+        ids = [self.add_request(p, params) for p in prompts]
+        outs: Dict[str, List[int]] = {i: [] for i in ids}
+        while self.has_unfinished():
+            for ev in self.step():
+                if ev.request_id in outs:
+                    outs[ev.request_id].extend(ev.token_ids)
+        if self.tp_rank != 0:
+            return []
+        return [outs[i] for i in ids]
+
+    def warm_up(self, buckets: Optional[Sequence[int]] = None) -> None:
+        """Capture decode graphs ahead of traffic (rust/engine/src/runtime.rs:1085-1175)."""
+        if not (self.is_cuda and self.cfg.use_cuda_graphs):
+            return
+        for b in buckets or self.cfg.graph_buckets:
+            if b <= self.cfg.max_num_seqs and b not in self._graphs:
+                self._graphs[b] = _DecodeGraph(self, b)
+
+
+class _DecodeGraph:
+    """One captured decode step for a fixed number of rows. Inputs are read from the engine's
+    device staging buffer at the fixed offsets `_build_batch(pad_to=bucket)` uses."""
+
+    def __init__(self, eng: LLMEngine, bucket: int):
+        self.bucket = bucket
+        dev = eng._dev
+        n, mb = bucket, eng.max_blocks_per_seq
+        self.batch = StepBatch(
+            token_ids=dev[0:n], positions=dev[n:2 * n], slots=dev[2 * n:3 * n], row_seq=dev[3 * n:4 * n],
+            logit_rows=dev[4 * n:5 * n], block_tables=dev[5 * n:5 * n + n * mb].view(n, mb),
+            num_seqs=n, num_tokens=n, max_kv_len=eng.cfg.max_model_len, all_decode=True)
+        # harmless contents for warm-up / capture: all rows padded
+        dev[0:2 * n].zero_()
+        dev[2 * n:3 * n].fill_(-1)
+        dev[3 * n:4 * n].zero_()
+        dev[4 * n:5 * n].copy_(torch.arange(n, dtype=torch.int32, device=dev.device))
+        dev[5 * n:5 * n + n * mb].zero_()
+        stream = torch.cuda.Stream(device=eng.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                lg = eng.decoder.forward(self.batch)
+                eng.decoder.greedy_tokens(lg)
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        if eng._graph_pool is None:
+            eng._graph_pool = torch.cuda.graph_pool_handle()
+        l0 = getattr(eng.ops, "launches", 0)
+        with torch.cuda.graph(self.graph, pool=eng._graph_pool):
+            self.logits = eng.decoder.forward(self.batch)
+            self.tokens = eng.decoder.greedy_tokens(self.logits)
+        self.launches = getattr(eng.ops, "launches", 0) - l0     # kernels replayed per step
+
+    def replay(self) -> None:
+        self.graph.replay()

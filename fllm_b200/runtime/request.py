@@ -1,0 +1,127 @@
+"""Request-side data: the one sampling contract shared by every API dialect
+(rust/engine/src/sampling.rs:6-49, rust/engine/src/parameters.rs:1) and the
+per-request state tracked by the scheduler."""
+from __future__ import annotations
+
+import enum
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 0.0
+    top_p: float = 1.0
+    top_k: int = 0
+    min_p: float = 0.0
+    repetition_penalty: float = 1.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    seed: Optional[int] = None
+    max_tokens: int = 256
+    min_tokens: int = 0
+    ignore_eos: bool = False
+    stop_token_ids: Sequence[int] = ()
+    stop: Sequence[str] = ()
+    logit_bias: Optional[Dict[int, float]] = None
+    allowed_token_ids: Optional[Sequence[int]] = None
+    bad_words_ids: Optional[Sequence[int]] = None
+    logprobs: bool = False
+    top_logprobs: int = 0
+    n: int = 1
+    priority: int = 0
+    timeout_s: Optional[float] = None
+    cache_salt: str = ""
+    speculative: bool = True
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0.0
+
+    @property
+    def needs_full_sampler(self) -> bool:
+        return (not self.greedy or self.repetition_penalty != 1.0 or self.presence_penalty != 0.0
+                or self.frequency_penalty != 0.0 or bool(self.logit_bias)
+                or self.allowed_token_ids is not None or bool(self.bad_words_ids) or self.logprobs)
+
+    def validate(self, vocab_size: int) -> None:
+        if self.temperature < 0:
+            raise ValueError("temperature must be >= 0")
+        if not 0 < self.top_p <= 1:
+            raise ValueError("top_p must be in (0, 1]")
+        if self.top_k < 0:
+            raise ValueError("top_k must be >= 0")
+        if not 0 <= self.min_p <= 1:
+            raise ValueError("min_p must be in [0, 1]")
+        if self.repetition_penalty <= 0:
+            raise ValueError("repetition_penalty must be > 0")
+        if self.max_tokens < 1:
+            raise ValueError("max_tokens must be >= 1")
+        if self.n != 1:
+            raise ValueError("n > 1 is served by submitting n requests")
+        for t in list(self.stop_token_ids) + list((self.logit_bias or {}).keys()):
+            if not 0 <= int(t) < vocab_size:
+                raise ValueError(f"token id {t} outside the vocabulary")
+
+
+class RequestStatus(enum.Enum):
+    WAITING = "waiting"
+    RUNNING = "running"
+    PREEMPTED = "preempted"
+    FINISHED = "finished"
+    ABORTED = "aborted"
+
+
+@dataclass
+class Request:
+    request_id: str
+    seq_id: int
+    prompt: List[int]
+    params: SamplingParams
+    arrival: float = field(default_factory=time.monotonic)
+    status: RequestStatus = RequestStatus.WAITING
+    output: List[int] = field(default_factory=list)
+    num_computed: int = 0            # tokens (prompt + output) whose KV is stored
+    num_cached: int = 0              # prompt tokens served from the prefix cache
+    finish_reason: Optional[str] = None
+    first_token_time: Optional[float] = None
+    last_token_time: Optional[float] = None
+    token_times: List[float] = field(default_factory=list)
+    preemptions: int = 0
+    draft: List[int] = field(default_factory=list)   # proposed tokens awaiting verification
+    logprobs: List[float] = field(default_factory=list)
+
+    @property
+    def all_tokens(self) -> List[int]:
+        return self.prompt + self.output
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    @property
+    def remaining(self) -> int:
+        """Tokens that still have to be fed to the model before the next one can be sampled."""
+        return self.num_tokens - self.num_computed
+
+    @property
+    def is_decode(self) -> bool:
+        return self.remaining == 1 and bool(self.output)
+
+    @property
+    def finished(self) -> bool:
+        return self.status in (RequestStatus.FINISHED, RequestStatus.ABORTED)
+
+    def deadline_passed(self, now: float) -> bool:
+        return self.params.timeout_s is not None and now - self.arrival > self.params.timeout_s
+
+
+@dataclass
+class TokenEvent:
+    request_id: str
+    token_ids: List[int]
+    finished: bool = False
+    finish_reason: Optional[str] = None
+    logprobs: Optional[List[float]] = None
+    error: Optional[str] = None

@@ -1,0 +1,219 @@
+"""Continuous batching: admit -> prefill chunks -> decode / verify rows under a
+token budget, with preemption when KV blocks run out.
+
+Same contract as the reference scheduler (rust/engine/src/scheduler.rs:156-249 config,
+:340-470 ``schedule``, :494-625 admission, :933-968 preemption): a step holds prefill
+chunks, decode rows and speculative verify rows; decode rows are scheduled first and
+reserve their budget; at most ``max_partial_prefills`` prompts are being chunked at a
+time; when blocks run out the lowest-priority running request is preempted by
+recompute (its blocks are freed and it re-enters the waiting queue keeping its output).
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Tuple
+
+from ..config import EngineConfig
+from .block_manager import BlockManager
+from .request import Request, RequestStatus
+
+
+@dataclass
+class ScheduledSeq:
+    req: Request
+    start: int                 # first token position fed this step
+    count: int                 # number of tokens fed this step
+    wants_logits: bool         # sample after this chunk
+    verify: int = 0            # number of draft tokens among `count` (rows count = 1 + verify)
+
+
+@dataclass
+class ScheduledStep:
+    seqs: List[ScheduledSeq] = field(default_factory=list)
+    preempted: List[Request] = field(default_factory=list)
+    cow: List[Tuple[int, int]] = field(default_factory=list)     # (src block, dst block) copies
+    expired: List[Request] = field(default_factory=list)
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(s.count for s in self.seqs)
+
+    @property
+    def all_decode(self) -> bool:
+        return bool(self.seqs) and all(s.count == 1 and s.req.output for s in self.seqs)
+
+    @property
+    def empty(self) -> bool:
+        return not self.seqs
+
+
+class Scheduler:
+    def __init__(self, cfg: EngineConfig, blocks: BlockManager, window: int = 0):
+        self.cfg, self.blocks = cfg, blocks
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []
+        self.window = window         # model-wide sliding window (0 when any layer attends fully)
+        self.stats = {"steps": 0, "preemptions": 0, "scheduled_tokens": 0}
+
+    # ------------------------------------------------------------------ queue
+    def add(self, req: Request) -> None:
+        req.status = RequestStatus.WAITING
+        if self.cfg.scheduling_policy == "priority":
+            # stable insert by (priority, arrival)
+            idx = len(self.waiting)
+            for i, r in enumerate(self.waiting):
+                if (req.params.priority, req.arrival) < (r.params.priority, r.arrival):
+                    idx = i
+                    break
+            self.waiting.insert(idx, req)
+        else:
+            self.waiting.append(req)
+
+    def abort(self, request_id: str) -> Optional[Request]:
+        for q in (self.running, self.waiting):
+            for r in list(q):
+                if r.request_id == request_id:
+                    q.remove(r)
+                    self.blocks.free_seq(r.seq_id)
+                    r.status = RequestStatus.ABORTED
+                    r.finish_reason = "abort"
+                    return r
+        return None
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------ helpers
+    def _salt(self, req: Request) -> bytes:
+        return req.params.cache_salt.encode()
+
+    def _preempt_one(self, step: ScheduledStep, protect: Request) -> bool:
+        """Evict the most recently admitted / lowest-priority running request."""
+        cands = [r for r in self.running if r is not protect]
+        if not cands:
+            return False
+        victim = max(cands, key=lambda r: (r.params.priority, r.arrival))
+        self.running.remove(victim)
+        self.blocks.free_seq(victim.seq_id)
+        victim.num_computed = 0
+        victim.draft = []
+        victim.status = RequestStatus.PREEMPTED
+        victim.preemptions += 1
+        self.waiting.appendleft(victim)
+        step.preempted.append(victim)
+        step.seqs = [s for s in step.seqs if s.req is not victim]
+        self.stats["preemptions"] += 1
+        return True
+
+    def _reserve(self, step: ScheduledStep, req: Request, total_tokens: int) -> bool:
+        while not self.blocks.ensure_capacity(req.seq_id, total_tokens):
+            if not self._preempt_one(step, protect=req):
+                return False
+        return True
+
+    # ------------------------------------------------------------------ main
+    def schedule(self) -> ScheduledStep:
+        cfg = self.cfg
+        step = ScheduledStep()
+        now = time.monotonic()
+        budget = cfg.max_num_batched_tokens
+
+        # deadlines
+        for q in (self.running, self.waiting):
+            for r in list(q):
+                if r.deadline_passed(now):
+                    q.remove(r)
+                    self.blocks.free_seq(r.seq_id)
+                    r.status = RequestStatus.ABORTED
+                    r.finish_reason = "timeout"
+                    step.expired.append(r)
+
+        # 1. decode / verify rows of running requests (decode-first)
+        decoders = [r for r in self.running if r.is_decode]
+        prefilling = [r for r in self.running if not r.is_decode]
+        for r in list(decoders):
+            if r not in self.running:
+                continue            # preempted while making room for an earlier one
+            n_draft = len(r.draft)
+            count = 1 + n_draft
+            if budget < count:
+                break
+            if not self._reserve(step, r, r.num_tokens + n_draft):
+                continue
+            cow = self.blocks.cow_last_block(r.seq_id)
+            if cow:
+                step.cow.append(cow)
+            step.seqs.append(ScheduledSeq(r, r.num_computed, count, True, verify=n_draft))
+            budget -= count
+
+        # 2. continue partially prefilled prompts
+        partial = 0
+        for r in prefilling:
+            if r not in self.running or budget <= 0:
+                continue
+            n = min(r.remaining, budget)
+            if not self._reserve(step, r, r.num_computed + n):
+                continue
+            step.seqs.append(ScheduledSeq(r, r.num_computed, n, n == r.remaining))
+            budget -= n
+            if n < r.remaining:
+                partial += 1
+
+        # 3. admit waiting requests
+        while self.waiting and budget > 0 and len(self.running) < cfg.max_num_seqs:
+            if partial >= cfg.max_partial_prefills:
+                break
+            r = self.waiting[0]
+            if r.seq_id not in self.blocks.seqs:
+                cached = self.blocks.allocate(r.seq_id, r.all_tokens, self._salt(r))
+                r.num_computed = cached
+                r.num_cached = cached
+            n = min(r.remaining, budget)
+            need = self.blocks.blocks_needed(r.num_computed + n) - len(self.blocks.table(r.seq_id))
+            if not self.blocks.can_allocate(max(need, 0)) or not self.blocks.ensure_capacity(r.seq_id, r.num_computed + n):
+                # not enough room right now: leave it queued (its cached prefix stays referenced)
+                if not self.running and not step.seqs:
+                    # nothing else holds memory: the prompt can never fit
+                    self.waiting.popleft()
+                    self.blocks.free_seq(r.seq_id)
+                    r.status = RequestStatus.ABORTED
+                    r.finish_reason = "kv_capacity"
+                    step.expired.append(r)
+                    continue
+                break
+            self.waiting.popleft()
+            r.status = RequestStatus.RUNNING
+            self.running.append(r)
+            step.seqs.append(ScheduledSeq(r, r.num_computed, n, n == r.remaining))
+            budget -= n
+            if n < r.remaining:
+                partial += 1
+
+        self.stats["steps"] += 1
+        self.stats["scheduled_tokens"] += step.num_tokens
+        return step
+
+    # ------------------------------------------------------------------ commit
+    def commit(self, s: ScheduledSeq, new_tokens: List[int], accepted_drafts: int = 0) -> None:
+        """Account for a finished step of one sequence: `count - verify + accepted` fed tokens now
+        have KV; `new_tokens` (possibly empty for a non-final prefill chunk) are appended."""
+        r = s.req
+        fed = s.count - s.verify + accepted_drafts
+        r.num_computed = s.start + fed
+        if s.verify:
+            # tokens fed as drafts and accepted are already in new_tokens; rejected KV is rolled back
+            self.blocks.truncate(r.seq_id, r.num_computed)
+            r.draft = []
+        r.output.extend(new_tokens)
+        self.blocks.commit_tokens(r.seq_id, r.all_tokens, r.num_computed, self._salt(r))
+        if self.window:
+            self.blocks.prune_window(r.seq_id, self.window)
+
+    def finish(self, r: Request, reason: str) -> None:
+        if r in self.running:
+            self.running.remove(r)
+        self.blocks.free_seq(r.seq_id)
+        r.status = RequestStatus.FINISHED
+        r.finish_reason = reason

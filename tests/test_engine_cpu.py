@@ -1,0 +1,89 @@
+"""Engine logic on CPU (reference ops): paged KV, chunked prefill, continuous batching and
+prefix caching must reproduce an independent dense decoder token for token."""
+import torch
+
+from fllm_b200.config import EngineConfig, preset
+from fllm_b200.models.weights import init_random_weights
+from fllm_b200.runtime import LLMEngine, SamplingParams
+
+from oracle import dense_forward, greedy_generate
+
+
+def _prompts(vocab, lens, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
+
+
+def _engine(cfg, **kw):
+    ec = EngineConfig(max_num_seqs=8, max_num_batched_tokens=32, max_model_len=256, num_kv_blocks=96, **kw)
+    return LLMEngine(cfg, ec, device="cpu")
+
+
+def test_generate_matches_dense_oracle():
+    cfg = preset("qwen3-tiny")
+    eng = _engine(cfg)
+    prompts = _prompts(cfg.vocab_size, (3, 17, 50, 33))
+    outs = eng.generate(prompts, SamplingParams(max_tokens=6))
+    for p, o in zip(prompts, outs):
+        ref = greedy_generate(cfg, eng.weights, p, 6)
+        assert o == ref
+
+
+def test_chunked_prefill_equals_single_pass():
+    cfg = preset("qwen3-tiny")
+    w = init_random_weights(cfg, "cpu")
+    p = _prompts(cfg.vocab_size, (90,))
+    small = LLMEngine(cfg, EngineConfig(max_num_batched_tokens=16, max_model_len=256, num_kv_blocks=64), device="cpu", weights=w)
+    big = LLMEngine(cfg, EngineConfig(max_num_batched_tokens=256, max_model_len=256, num_kv_blocks=64), device="cpu", weights=w)
+    assert small.generate(p, SamplingParams(max_tokens=5)) == big.generate(p, SamplingParams(max_tokens=5))
+    assert small.stats.steps > big.stats.steps
+
+
+def test_prefix_cache_hit_keeps_output():
+    cfg = preset("qwen3-tiny")
+    eng = _engine(cfg)
+    p = _prompts(cfg.vocab_size, (70,))
+    a = eng.generate(p, SamplingParams(max_tokens=4))
+    b = eng.generate(p, SamplingParams(max_tokens=4))
+    assert a == b
+    assert eng.blocks.stats["prefix_hits"] >= 1
+
+
+def test_preemption_by_recompute_keeps_output():
+    cfg = preset("qwen3-tiny")
+    w = init_random_weights(cfg, "cpu")
+    prompts = _prompts(cfg.vocab_size, (40, 44, 48, 52))
+    roomy = LLMEngine(cfg, EngineConfig(max_num_batched_tokens=64, max_model_len=128, num_kv_blocks=64,
+                                        enable_prefix_caching=False), device="cpu", weights=w)
+    tight = LLMEngine(cfg, EngineConfig(max_num_batched_tokens=64, max_model_len=128, num_kv_blocks=13,
+                                        enable_prefix_caching=False, watermark=0.0), device="cpu", weights=w)
+    sp = SamplingParams(max_tokens=12)
+    assert tight.generate(prompts, sp) == roomy.generate(prompts, sp)
+    assert tight.scheduler.stats["preemptions"] > 0
+
+
+def test_llama_and_window_models_match_oracle():
+    for name in ("tiny-llama",):
+        cfg = preset(name)
+        cfg.vocab_size = 512
+        eng = _engine(cfg)
+        prompts = _prompts(cfg.vocab_size, (9, 30))
+        outs = eng.generate(prompts, SamplingParams(max_tokens=5))
+        for p, o in zip(prompts, outs):
+            assert o == greedy_generate(cfg, eng.weights, p, 5)
+    cfg = preset("qwen3-tiny")
+    cfg.sliding_window = 24
+    eng = _engine(cfg)
+    prompts = _prompts(cfg.vocab_size, (60,))
+    outs = eng.generate(prompts, SamplingParams(max_tokens=5))
+    assert outs[0] == greedy_generate(cfg, eng.weights, prompts[0], 5)
+
+
+def test_stop_and_max_tokens():
+    cfg = preset("qwen3-tiny")
+    eng = _engine(cfg)
+    p = _prompts(cfg.vocab_size, (10,))
+    full = eng.generate(p, SamplingParams(max_tokens=8))[0]
+    stop_tok = full[3]
+    cut = eng.generate(p, SamplingParams(max_tokens=8, stop_token_ids=(stop_tok,)))[0]
+    assert cut == full[: full.index(stop_tok) + 1]

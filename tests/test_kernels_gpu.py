@@ -1,0 +1,194 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same ops.
+Shapes include odd row counts, partial tiles and forced split-K."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from fllm_b200.ops.native import NativeOps
+    return NativeOps(torch.device("cuda:0"))
+
+
+@pytest.fixture(scope="module")
+def ref():
+    from fllm_b200.ops.reference import RefOps
+    return RefOps()
+
+
+def _rand(shape, seed, scale=1.0, dtype=torch.bfloat16):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda") * scale).to(dtype)
+
+
+def _close(y, r, tol=2e-2):
+    err = (y.float() - r.float()).abs().max().item()
+    scale = r.float().abs().max().item() + 1e-6
+    assert err <= tol * scale, f"max abs err {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("T", [1, 7, 16, 33, 64, 100, 128, 129, 300, 2048])
+@pytest.mark.parametrize("N,K", [(256, 128), (1024, 4096), (1000, 320), (6144, 4096)])
+def test_linear(ops, T, N, K):
+    x = _rand((T, K), 1)
+    w = _rand((N, K), 2, 0.05)
+    y = ops.linear(x, w)
+    _close(y, x.float() @ w.float().t())
+    assert ops.check_status() == 0
+
+
+@pytest.mark.parametrize("T,splits", [(5, 2), (64, 4), (128, 7), (16, 16)])
+def test_linear_split_k_and_bias(ops, T, splits):
+    x = _rand((T, 4096), 3)
+    w = _rand((512, 4096), 4, 0.05)
+    b = _rand((512,), 5)
+    y = ops.linear(x, w, b, force_splits=splits)
+    _close(y, x.float() @ w.float().t() + b.float())
+    y1 = ops.linear(x, w, b, force_splits=1)
+    _close(y1, x.float() @ w.float().t() + b.float())
+
+
+def test_linear_strided_operands(ops):
+    big = _rand((70, 3 * 512), 6)
+    x = big[:, 512:1024]                       # row pitch 1536, offset 512 elements
+    w = _rand((768, 512), 7, 0.05)
+    out_big = torch.zeros(70, 2048, dtype=torch.bfloat16, device="cuda")
+    y = out_big[:, 256:1024]
+    ops.linear(x, w, out=y)
+    _close(y, x.float() @ w.float().t())
+    assert out_big[:, :256].abs().max() == 0 and out_big[:, 1024:].abs().max() == 0
+
+
+def test_linear_deterministic(ops):
+    x = _rand((64, 4096), 8)
+    w = _rand((4096, 4096), 9, 0.05)
+    assert torch.equal(ops.linear(x, w), ops.linear(x, w))
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 256), (13, 4096), (64, 2880), (5, 8192)])
+def test_rmsnorm(ops, ref, rows, hidden):
+    x = _rand((rows, hidden), 1)
+    d = _rand((rows, hidden), 2)
+    w = _rand((hidden,), 3)
+    xr, xn = x.clone(), x.clone()
+    y = ops.rmsnorm(xn, d, w, 1e-6)
+    yr = ref.rmsnorm(xr, d, w, 1e-6)
+    _close(y, yr, 1e-2)
+    assert torch.equal(xn, xr)
+    _close(ops.rmsnorm(x.clone(), None, w, 1e-5), ref.rmsnorm(x.clone(), None, w, 1e-5), 1e-2)
+
+
+@pytest.mark.parametrize("D,style,qknorm,rot", [(128, 0, True, 128), (64, 0, False, 64), (128, 1, False, 128),
+                                                 (64, 1, True, 64), (128, 0, False, 64), (256, 0, True, 256)])
+def test_rope_kv_write(ops, ref, D, style, qknorm, rot):
+    T, hq, hkv, bs, nb = 37, 8, 2, 16, 12
+    qkv = _rand((T, (hq + 2 * hkv) * D), 1)
+    pos = torch.randint(0, 5000, (T,), device="cuda", dtype=torch.int32)
+    slots = torch.randperm(nb * bs, device="cuda")[:T].int()
+    slots[3] = -1
+    inv = (10000.0 ** (-torch.arange(0, rot, 2, device="cuda").float() / rot))
+    qn = _rand((D,), 2) if qknorm else None
+    kn = _rand((D,), 3) if qknorm else None
+    kc = torch.zeros(nb, hkv, bs, D, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    kc_r, vc_r, qkv_r = kc.clone(), vc.clone(), qkv.clone()
+    ops.rope_kv_write(qkv, pos, slots, inv, qn, kn, kc, vc, hq, hkv, D, rot, style, 1e-6, 1.0)
+    ref.rope_kv_write(qkv_r, pos, slots, inv, qn, kn, kc_r, vc_r, hq, hkv, D, rot, style, 1e-6, 1.0)
+    _close(qkv[:, : hq * D], qkv_r[:, : hq * D], 2e-2)
+    _close(kc, kc_r, 2e-2)
+    assert torch.equal(vc, vc_r)
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2])
+def test_glu(ops, ref, kind):
+    x = _rand((19, 2 * 1376), 1, 2.0)
+    _close(ops.glu(x, kind, 1.702, 7.0), ref.glu(x, kind, 1.702, 7.0), 1e-2)
+
+
+def _paged_setup(B, lens, hkv, D, bs=16, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    max_blocks = max((l + bs - 1) // bs for l in lens)
+    nb = sum((l + bs - 1) // bs for l in lens) + 3
+    perm = torch.randperm(nb, generator=g, device="cuda").int()
+    tables = torch.zeros(B, max_blocks, dtype=torch.int32, device="cuda")
+    o = 0
+    for i, l in enumerate(lens):
+        n = (l + bs - 1) // bs
+        tables[i, :n] = perm[o:o + n]
+        o += n
+    kc = (torch.randn(nb, hkv, bs, D, generator=g, device="cuda")).to(torch.bfloat16)
+    vc = (torch.randn(nb, hkv, bs, D, generator=g, device="cuda")).to(torch.bfloat16)
+    return tables, kc, vc
+
+
+@pytest.mark.parametrize("D,hq,hkv", [(128, 8, 2), (64, 8, 8), (128, 4, 1)])
+@pytest.mark.parametrize("window,sinks,softcap", [(0, False, 0.0), (20, True, 0.0), (0, False, 30.0)])
+def test_attention_generic(ops, ref, D, hq, hkv, window, sinks, softcap):
+    lens = [1, 17, 64, 130]
+    tables, kc, vc = _paged_setup(len(lens), lens, hkv, D)
+    # mixed rows: last token of every sequence plus a few prefill rows of the longest one
+    row_seq = torch.tensor([0, 1, 2, 3, 3, 3], dtype=torch.int32, device="cuda")
+    pos = torch.tensor([0, 16, 63, 129, 50, 7], dtype=torch.int32, device="cuda")
+    q = _rand((6, hq * D), 5)
+    sk = torch.randn(hq, device="cuda") if sinks else None
+    y = ops.attention(q, kc, vc, tables, row_seq, pos, hq, hkv, D, D ** -0.5, window, sk, softcap)
+    yr = ref.attention(q, kc, vc, tables, row_seq, pos, hq, hkv, D, D ** -0.5, window, sk, softcap)
+    _close(y, yr, 2e-2)
+
+
+def test_argmax_and_sampler(ops):
+    from fllm_b200.ops.native import pack_sample_rows
+    from fllm_b200.ops.reference import sample_reference
+    R, V = 9, 5003
+    lg = _rand((R, V), 1, 3.0, torch.float32)
+    ids = ops.argmax(lg)
+    assert torch.equal(ids.long(), lg.argmax(-1))
+    ids_b = ops.argmax(lg.to(torch.bfloat16), id_offset=100)
+    assert torch.equal(ids_b.long() - 100, lg.to(torch.bfloat16).float().argmax(-1))
+    rows = []
+    for r in range(R):
+        rows.append((0.8 + 0.1 * r, [1.0, 0.9, 0.5][r % 3], [0.0, 0.05][r % 2], 1.0, 0.0, 0.0, [0, 5, 50][r % 3], r, 1234 + r))
+    prm = torch.frombuffer(bytearray(pack_sample_rows(rows)), dtype=torch.uint8).cuda()
+    got = ops.sample(lg.clone(), prm).tolist()
+    want = [sample_reference(lg[r], *[rows[r][i] for i in (0, 6, 1, 2, 8, 7)]) for r in range(R)]
+    assert sum(g == w for g, w in zip(got, want)) >= R - 1, (got, want)
+    # greedy rows through the full sampler, with a penalty that flips the winner
+    rows = [(0.0, 1.0, 0.0, 1.0, 0.0, 0.0, 0, 0, 1)] * R
+    prm = torch.frombuffer(bytearray(pack_sample_rows(rows)), dtype=torch.uint8).cuda()
+    top = lg.argmax(-1)
+    pen_ids = top.int().view(R, 1).contiguous()
+    pen_cnt = torch.ones_like(pen_ids)
+    rows_pen = [(0.0, 1.0, 0.0, 1.0, 100.0, 0.0, 0, 0, 1)] * R
+    prm_pen = torch.frombuffer(bytearray(pack_sample_rows(rows_pen)), dtype=torch.uint8).cuda()
+    assert torch.equal(ops.sample(lg.clone(), prm).long(), top)
+    second = lg.clone().scatter_(1, top.view(-1, 1), -1e30).argmax(-1)
+    assert torch.equal(ops.sample(lg.clone(), prm_pen, pen_ids, pen_cnt).long(), second)
+
+
+def test_sampler_distribution(ops):
+    """Gumbel-max draws follow softmax(logits / T) (chi-square style bound on 4 tokens)."""
+    from fllm_b200.ops.native import pack_sample_rows
+    R = 4000
+    base = torch.tensor([2.0, 1.0, 0.0, -1.0], device="cuda")
+    lg = base.repeat(R, 1).contiguous()
+    rows = [(1.0, 1.0, 0.0, 1.0, 0.0, 0.0, 0, r, 99) for r in range(R)]
+    prm = torch.frombuffer(bytearray(pack_sample_rows(rows)), dtype=torch.uint8).cuda()
+    ids = ops.sample(lg, prm)
+    freq = torch.bincount(ids.long(), minlength=4).float() / R
+    want = torch.softmax(base, 0)
+    assert (freq - want).abs().max().item() < 0.03, (freq, want)
+
+
+def test_spec_verify_greedy(ops):
+    k = 4
+    draft = torch.tensor([[5, 6, 7, 8], [1, 2, 3, 4], [9, 9, 9, 9]], dtype=torch.int32, device="cuda")
+    target = torch.tensor([[5, 6, 0, 8, 1], [1, 2, 3, 4, 77], [3, 9, 9, 9, 9]], dtype=torch.int32, device="cuda")
+    n_acc = torch.zeros(3, dtype=torch.int32, device="cuda")
+    out = torch.full((3, k + 1), -1, dtype=torch.int32, device="cuda")
+    ops.k.spec_verify_greedy(draft, target, None, n_acc, out)
+    assert n_acc.tolist() == [2, 4, 0]
+    assert out[0, :3].tolist() == [5, 6, 0] and out[1].tolist() == [1, 2, 3, 4, 77] and out[2, 0].item() == 3
