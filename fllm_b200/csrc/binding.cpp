@@ -128,6 +128,31 @@ void attention_generic(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
                                opt_ptr<float>(sinks), (float)softcap, cur_stream());
 }
 
+int64_t attention_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
+                     const Tensor& block_tables, const Tensor& q_starts, const Tensor& kv_lens, Tensor out,
+                     int64_t num_seqs, int64_t max_q_len, int64_t min_q_len, int64_t max_kv_len, int64_t hq,
+                     int64_t hkv, int64_t head_dim, double scale, int64_t window,
+                     const optional<Tensor>& sinks, double softcap, const optional<Tensor>& workspace) {
+  check_bf16(q, "q"); check_rows(q, "q"); check_bf16(out, "out"); check_rows(out, "out");
+  check_bf16(k_cache, "k_cache"); check_bf16(v_cache, "v_cache");
+  check_i32(q_starts, "q_starts"); check_i32(kv_lens, "kv_lens");
+  TORCH_CHECK(block_tables.scalar_type() == at::kInt && block_tables.dim() == 2 &&
+              block_tables.stride(1) == 1 && block_tables.stride(0) == block_tables.size(1),
+              "block_tables must be a dense int32 matrix");
+  TORCH_CHECK(q_starts.numel() >= num_seqs + 1 && kv_lens.numel() >= num_seqs, "attention_tc: metadata too short");
+  c10::cuda::CUDAGuard guard(q.device());
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  if (workspace.has_value() && workspace->defined()) { ws = workspace->data_ptr(); ws_bytes = workspace->nbytes(); }
+  return fllm::attention_tc_bf16(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+                                 block_tables.data_ptr<int>(), (int)block_tables.size(1),
+                                 q_starts.data_ptr<int>(), kv_lens.data_ptr<int>(), out.data_ptr(),
+                                 out.stride(0), (int)q.size(0), (int)num_seqs, (int)max_q_len,
+                                 (int)min_q_len, (int)max_kv_len, (int)hq, (int)hkv, (int)head_dim,
+                                 (int)k_cache.size(2), (float)scale, (int)window, opt_ptr<float>(sinks),
+                                 (float)softcap, ws, ws_bytes, cur_stream());
+}
+
 void argmax(const Tensor& logits, Tensor out_ids, const optional<Tensor>& out_vals,
             int64_t id_offset) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "argmax: bad logits");
@@ -212,6 +237,7 @@ TORCH_LIBRARY(fllm_b200, m) {
   m.def("glu(Tensor x, Tensor(a!) out, int act_kind, float alpha, float limit) -> ()", &glu);
   m.def("gather_rows(Tensor x, Tensor rows, Tensor(a!) out) -> ()", &gather_rows);
   m.def("attention_generic(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor row_seq, Tensor positions, Tensor(a!) out, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap) -> ()", &attention_generic);
+  m.def("attention_tc(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor q_starts, Tensor kv_lens, Tensor(a!) out, int num_seqs, int max_q_len, int min_q_len, int max_kv_len, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap, Tensor? workspace) -> int", &attention_tc);
   m.def("argmax(Tensor logits, Tensor(a!) out_ids, Tensor? out_vals, int id_offset) -> ()", &argmax);
   m.def("sample(Tensor(a!) logits, Tensor params, Tensor? pen_ids, Tensor? pen_counts, Tensor? bias_ids, Tensor? bias_vals, Tensor? allow_mask, Tensor(b!) out_ids, Tensor? out_logprobs) -> ()", &sample);
   m.def("spec_verify_greedy(Tensor draft_ids, Tensor target_ids, Tensor? n_draft, Tensor(a!) n_accept, Tensor(b!) out_tokens) -> ()", &spec_verify_greedy);

@@ -38,6 +38,16 @@ void attention_generic_bf16(const void* q, long long ldq, const void* k_cache, c
                             int hkv, int head_dim, int block_size, float scale, int window,
                             const float* sinks, float softcap, cudaStream_t s);
 
+// Tensor-core paged attention over a ragged batch described per sequence (q_starts, kv_lens).
+// Returns the number of kernels launched.
+int attention_tc_bf16(const void* q, long long ldq, const void* k_cache, const void* v_cache,
+                      const int* block_tables, int max_blocks, const int* q_starts, const int* kv_lens,
+                      void* out, long long ldo, int tokens, int num_seqs, int max_q_len, int min_q_len,
+                      int max_kv_len, int hq, int hkv, int head_dim, int block_size, float scale,
+                      int window, const float* sinks, float softcap, void* workspace,
+                      size_t workspace_bytes, cudaStream_t s);
+size_t attention_tc_workspace_bytes(int tokens, int hq, int head_dim, int max_splits);
+
 // ---- sampling -----------------------------------------------------------------------
 struct SampleRow {
   float temperature;         // <= 0: greedy

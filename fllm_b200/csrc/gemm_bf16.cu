@@ -384,7 +384,8 @@ int linear_bf16(const void* x, long long ldx, const void* w, long long ldw, cons
   }
   if (splits > 1) {
     const size_t need = (size_t)splits * a.M * a.N * sizeof(float);
-    if (!workspace || need > workspace_bytes || (a.M & 3) || (a.N & 3)) splits = 1;
+    // the reduction reads the partials as float4 along the feature axis (N % 8 == 0 above)
+    if (!workspace || need > workspace_bytes) splits = 1;
   }
   a.kb_per_split = (a.k_blocks + splits - 1) / splits;
   a.k_splits = (a.k_blocks + a.kb_per_split - 1) / a.kb_per_split;

@@ -36,6 +36,8 @@ class StepBatch:
     num_tokens: int = 0
     max_kv_len: int = 0
     all_decode: bool = False
+    max_q_len: int = 1
+    min_q_len: int = 1
     seq_lens: Optional[torch.Tensor] = None      # [B] int32 visible KV length per sequence
     q_starts: Optional[torch.Tensor] = None      # [B+1] int32 first token row of each sequence
 

@@ -23,6 +23,7 @@ class NativeOps:
         self.workspace = torch.empty(workspace_bytes, dtype=torch.uint8, device=self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.use_tc_attention = True
+        self.attn_ws = None
         self.launches = 0            # kernels launched through this object (graph capture included)
 
     # ---------------------------------------------------------------- dense
@@ -67,6 +68,15 @@ class NativeOps:
     def attention(self, q, k_cache, v_cache, block_tables, row_seq, positions, hq, hkv, head_dim,
                   scale, window=0, sinks=None, softcap=0.0, meta=None):
         out = torch.empty(q.shape[0], hq * head_dim, dtype=q.dtype, device=q.device)
+        if (self.use_tc_attention and meta is not None and meta.q_starts is not None
+                and head_dim in (64, 128) and hq // hkv <= 16):
+            if self.attn_ws is None:
+                self.attn_ws = torch.empty(64 << 20, dtype=torch.uint8, device=self.device)
+            self.launches += self.k.attention_tc(
+                q, k_cache, v_cache, block_tables, meta.q_starts, meta.seq_lens, out, meta.num_seqs,
+                meta.max_q_len, meta.min_q_len, meta.max_kv_len, hq, hkv, head_dim, float(scale),
+                int(window), sinks, float(softcap), self.attn_ws)
+            return out
         self.k.attention_generic(q, k_cache, v_cache, block_tables, row_seq, positions, out, hq, hkv,
                                  head_dim, float(scale), int(window), sinks, float(softcap))
         self.launches += 1

@@ -80,7 +80,7 @@ class LLMEngine:
         self._graph_pool = None
         # staging: [ids | positions | slots | row_seq | logit_rows | block tables]
         max_rows = max(self.cfg.max_num_seqs, self._bucket_for(self.cfg.max_num_seqs))
-        cap = 5 * max(self.cfg.max_num_batched_tokens, max_rows) + max_rows * self.max_blocks_per_seq + 64
+        cap = 5 * max(self.cfg.max_num_batched_tokens, max_rows) + max_rows * (self.max_blocks_per_seq + 2) + 64
         self._host = torch.empty(cap, dtype=torch.int32, pin_memory=self.is_cuda)
         self._host_np = self._host.numpy()
         self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
@@ -146,7 +146,11 @@ class LLMEngine:
             max_blocks = self.max_blocks_per_seq
         R_cap = Tp
         lrow = h[4 * Tp:4 * Tp + R_cap]
-        tab = h[5 * Tp:5 * Tp + Bp * max_blocks].reshape(Bp, max_blocks)
+        o_qs, o_kl, o_tab = 5 * Tp, 5 * Tp + Bp + 1, 5 * Tp + 2 * Bp + 1
+        qst = h[o_qs:o_qs + Bp + 1]
+        kvl = h[o_kl:o_kl + Bp]
+        tab = h[o_tab:o_tab + Bp * max_blocks].reshape(Bp, max_blocks)
+        max_q, min_q = 1, 1 << 30
         t = 0
         for i, s in enumerate(seqs):
             r = s.req
@@ -165,6 +169,9 @@ class LLMEngine:
                 slots[t:t + n] = tb[p // bs] * bs + p % bs
             rseq[t:t + n] = i
             tab[i, :tb.shape[0]] = tb
+            qst[i] = t
+            kvl[i] = s.start + n
+            max_q, min_q = max(max_q, n), min(min_q, n)
             if s.wants_logits:
                 if s.verify:
                     rows.extend(range(t, t + n))
@@ -178,9 +185,13 @@ class LLMEngine:
             slots[T:Tp] = -1
             rseq[T:Tp] = 0
             rows.extend(range(T, Tp))
+            qst[B:Bp] = np.arange(T, Tp, dtype=np.int32)      # one padding row per padding sequence
+            kvl[B:Bp] = 1
+            min_q = 1
+        qst[Bp] = Tp
         R = len(rows)
         lrow[:R] = rows
-        used = 5 * Tp + Bp * max_blocks
+        used = o_tab + Bp * max_blocks
         dev = self._dev
         if self.is_cuda:
             dev[:used].copy_(self._host[:used], non_blocking=True)
@@ -190,8 +201,10 @@ class LLMEngine:
         return StepBatch(
             token_ids=dev[0:Tp], positions=dev[Tp:2 * Tp], slots=dev[2 * Tp:3 * Tp],
             row_seq=dev[3 * Tp:4 * Tp], logit_rows=dev[4 * Tp:4 * Tp + R],
-            block_tables=dev[5 * Tp:5 * Tp + Bp * max_blocks].view(Bp, max_blocks),
-            num_seqs=B, num_tokens=T, max_kv_len=max_kv, all_decode=step.all_decode)
+            block_tables=dev[o_tab:o_tab + Bp * max_blocks].view(Bp, max_blocks),
+            q_starts=dev[o_qs:o_qs + Bp + 1], seq_lens=dev[o_kl:o_kl + Bp],
+            num_seqs=Bp, num_tokens=T, max_kv_len=max_kv, all_decode=step.all_decode,
+            max_q_len=max_q, min_q_len=min(min_q, max_q))
 
     # ------------------------------------------------------------------ graphs
     def _bucket_for(self, n: int) -> int:
@@ -346,16 +359,21 @@ class _DecodeGraph:
         self.bucket = bucket
         dev = eng._dev
         n, mb = bucket, eng.max_blocks_per_seq
+        o_qs, o_kl, o_tab = 5 * n, 6 * n + 1, 7 * n + 1
         self.batch = StepBatch(
             token_ids=dev[0:n], positions=dev[n:2 * n], slots=dev[2 * n:3 * n], row_seq=dev[3 * n:4 * n],
-            logit_rows=dev[4 * n:5 * n], block_tables=dev[5 * n:5 * n + n * mb].view(n, mb),
-            num_seqs=n, num_tokens=n, max_kv_len=eng.cfg.max_model_len, all_decode=True)
+            logit_rows=dev[4 * n:5 * n], block_tables=dev[o_tab:o_tab + n * mb].view(n, mb),
+            q_starts=dev[o_qs:o_qs + n + 1], seq_lens=dev[o_kl:o_kl + n],
+            num_seqs=n, num_tokens=n, max_kv_len=eng.cfg.max_model_len, all_decode=True,
+            max_q_len=1, min_q_len=1)
         # harmless contents for warm-up / capture: all rows padded
         dev[0:2 * n].zero_()
         dev[2 * n:3 * n].fill_(-1)
         dev[3 * n:4 * n].zero_()
         dev[4 * n:5 * n].copy_(torch.arange(n, dtype=torch.int32, device=dev.device))
-        dev[5 * n:5 * n + n * mb].zero_()
+        dev[o_qs:o_qs + n + 1].copy_(torch.arange(n + 1, dtype=torch.int32, device=dev.device))
+        dev[o_kl:o_kl + n].fill_(1)
+        dev[o_tab:o_tab + n * mb].zero_()
         stream = torch.cuda.Stream(device=eng.device)
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):

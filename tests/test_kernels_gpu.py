@@ -192,3 +192,48 @@ def test_spec_verify_greedy(ops):
     ops.k.spec_verify_greedy(draft, target, None, n_acc, out)
     assert n_acc.tolist() == [2, 4, 0]
     assert out[0, :3].tolist() == [5, 6, 0] and out[1].tolist() == [1, 2, 3, 4, 77] and out[2, 0].item() == 3
+
+
+class _Meta:
+    pass
+
+
+def _tc_meta(q_lens, kv_lens):
+    m = _Meta()
+    qs = [0]
+    for n in q_lens:
+        qs.append(qs[-1] + n)
+    m.q_starts = torch.tensor(qs, dtype=torch.int32, device="cuda")
+    m.seq_lens = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+    m.num_seqs, m.max_q_len, m.min_q_len, m.max_kv_len = len(q_lens), max(q_lens), min(q_lens), max(kv_lens)
+    return m
+
+
+@pytest.mark.parametrize("D,hq,hkv", [(128, 8, 2), (64, 8, 8), (128, 4, 1), (64, 16, 2), (128, 32, 8)])
+@pytest.mark.parametrize("window,sinks,softcap", [(0, False, 0.0), (40, True, 0.0), (0, False, 30.0)])
+@pytest.mark.parametrize("case", ["decode", "decode_few", "prefill", "mixed", "verify"])
+def test_attention_tc(ops, ref, D, hq, hkv, window, sinks, softcap, case):
+    if case == "decode":
+        kv_lens, q_lens = [1, 17, 64, 130, 700, 33, 16, 257], [1] * 8
+    elif case == "decode_few":            # few sequences: exercises the split-KV path + merge
+        kv_lens, q_lens = [900, 35], [1, 1]
+    elif case == "prefill":
+        kv_lens, q_lens = [200, 64, 130, 17], [200, 64, 100, 17]
+    elif case == "mixed":
+        kv_lens, q_lens = [300, 90, 45, 128], [1, 90, 1, 64]
+    else:                                  # speculative verify rows: up to 16 / group queries
+        n = max(1, min(4, 16 // (hq // hkv)))
+        kv_lens, q_lens = [100, 37, 260], [n, n, n]
+    tables, kc, vc = _paged_setup(len(kv_lens), kv_lens, hkv, D, seed=3)
+    T = sum(q_lens)
+    row_seq = torch.tensor([i for i, n in enumerate(q_lens) for _ in range(n)], dtype=torch.int32, device="cuda")
+    pos = torch.tensor([kv - n + j for kv, n in zip(kv_lens, q_lens) for j in range(n)], dtype=torch.int32, device="cuda")
+    q = _rand((T, hq * D), 5)
+    sk = torch.randn(hq, device="cuda") if sinks else None
+    meta = _tc_meta(q_lens, kv_lens)
+    y = ops.attention(q, kc, vc, tables, row_seq, pos, hq, hkv, D, D ** -0.5, window, sk, softcap, meta=meta)
+    yr = ref.attention(q, kc, vc, tables, row_seq, pos, hq, hkv, D, D ** -0.5, window, sk, softcap)
+    _close(y, yr, 2e-2)
+    # the always-correct generic kernel agrees too
+    yg = ops.attention(q, kc, vc, tables, row_seq, pos, hq, hkv, D, D ** -0.5, window, sk, softcap)
+    _close(yg, yr, 2e-2)
