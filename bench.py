@@ -195,8 +195,11 @@ def main() -> None:
     sync_all()
     t0 = time.perf_counter()
     e0.record()
+    step_ms = []
     for _ in range(args.steps):
+        ts = time.perf_counter()
         eng.step()
+        step_ms.append((time.perf_counter() - ts) * 1e3)
     e1.record()
     sync_all()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
@@ -229,7 +232,8 @@ def main() -> None:
             "e2e": {"value": round(e2e_value, 1), "unit": "tok/s",
                     "h2d_bytes_per_step": (eng.stats.h2d_bytes - h2d0) // args.steps,
                     "d2h_bytes_per_step": (eng.stats.d2h_bytes - d2h0) // args.steps,
-                    "ms_per_step": round(e2e_s * 1e3 / args.steps, 4)},
+                    "ms_per_step": round(e2e_s * 1e3 / args.steps, 4),
+                    "step_ms_p50": round(statistics.median(step_ms), 4), "step_ms_max": round(max(step_ms), 4)},
             "gpu_launches": (launches_per_step or 0) * args.steps + (eng.stats.kernel_launches - l0),
             "prefill_tok_s": round(prefill_tok_s, 1), "ttft_s_first": round(ttft or 0.0, 4),
             "itl_p50_ms": round(statistics.median(itl) * 1e3, 4) if itl else None,

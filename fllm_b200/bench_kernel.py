@@ -95,10 +95,28 @@ def main(argv=None) -> None:
     q = torch.randn(B, hq * D, device="cuda", dtype=torch.bfloat16)
     row_seq = torch.arange(B, device="cuda", dtype=torch.int32)
     pos = torch.full((B,), L - 1, device="cuda", dtype=torch.int32)
-    ms = timer(lambda: ops.attention(q, kc, vc, tables, row_seq, pos, hq, hkv, D, D ** -0.5))
+    from .models.decoder import StepBatch
+    meta = StepBatch(None, pos, None, row_seq, tables, None, num_seqs=B, num_tokens=B, max_kv_len=L, all_decode=True,
+                     seq_lens=torch.full((B,), L, device="cuda", dtype=torch.int32),
+                     q_starts=torch.arange(B + 1, device="cuda", dtype=torch.int32))
     byts = 2.0 * kc.numel() * 2
-    print(f"{'attn_dec':10s} {B:6d} ctx={L} {ms:9.4f} ms  {byts / ms / 1e6:7.0f} GB/s  frac {byts / (hbm * 1e9) / (ms / 1e3):.2f}")
-    rows.append({"op": "attention_decode", "B": B, "ctx": L, "ms": ms, "gbs": byts / ms / 1e6})
+    for label, m in (("attn_dec_tc", meta), ("attn_dec_generic", None)):
+        ms = timer(lambda: ops.attention(q, kc, vc, tables, row_seq, pos, hq, hkv, D, D ** -0.5, meta=m))
+        print(f"{label:18s} {B:4d} ctx={L} {ms:9.4f} ms  {byts / ms / 1e6:7.0f} GB/s  frac {byts / (hbm * 1e9) / (ms / 1e3):.2f}")
+        rows.append({"op": label, "B": B, "ctx": L, "ms": ms, "gbs": byts / ms / 1e6})
+    # prefill attention: one 2048-token chunk of two 1024-token prompts
+    Tq = 2048
+    qp = torch.randn(Tq, hq * D, device="cuda", dtype=torch.bfloat16)
+    metap = StepBatch(None, None, None, None, tables, None, num_seqs=2, num_tokens=Tq, max_kv_len=1024,
+                      seq_lens=torch.full((2,), 1024, device="cuda", dtype=torch.int32),
+                      q_starts=torch.tensor([0, 1024, 2048], device="cuda", dtype=torch.int32),
+                      max_q_len=1024, min_q_len=1024)
+    rs = torch.arange(2, device="cuda", dtype=torch.int32).repeat_interleave(1024)
+    ps = torch.arange(1024, device="cuda", dtype=torch.int32).repeat(2)
+    ms = timer(lambda: ops.attention(qp, kc, vc, tables, rs, ps, hq, hkv, D, D ** -0.5, meta=metap))
+    fl = 4.0 * 2 * (1024 * 1025 / 2) * D * hq
+    print(f"{'attn_prefill_tc':18s} 2x1024 {ms:9.4f} ms  {fl / ms / 1e9:7.1f} TFLOP/s")
+    rows.append({"op": "attention_prefill", "ms": ms, "tflops": fl / ms / 1e9})
     # elementwise
     for T in (64, 2048):
         x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
