@@ -1,0 +1,61 @@
+// C entry point for callers that must not allocate device memory.
+//
+// This entry point has no counterpart in the reference engine. It exists for hosts that
+// embed the kernels from plain C/C++ (no torch, no caching allocator) inside a serving
+// process whose device memory is already fully handed out - typically to the paged KV
+// pool, sized to a fraction of HBM at start-up. In such a process a cudaMalloc at request
+// time can fail outright, and even when it succeeds it synchronises the whole device and
+// stalls every other stream. So the split-K GEMM is offered here with its fp32 partial-sum
+// scratch living in a fixed array inside the library image instead of a caller- or
+// allocator-provided workspace.
+//
+//   y[tokens, features] = x[tokens, k] * w[features, k]^T (+ bias[features]), bf16 in/out,
+//   computed as `splits` partial products over slices of k that are summed in fp32.
+//
+// Contract
+//   * The caller passes inputs and outputs only (device pointers, leading dimensions in
+//     elements, a CUDA stream). Nothing is allocated or freed: no cudaMalloc / cudaFree and
+//     no allocating library routine is called, on any path.
+//   * The scratch array is FLLM_NOALLOC_SCRATCH_BYTES (8 MiB) per device; every GPU on which
+//     the library is loaded holds it until the process exits. A call needs
+//     splits * tokens * features * 4 bytes of it; a call that needs more is rejected with
+//     FLLM_NOALLOC_E_TOO_LARGE and a message naming both numbers (nothing is launched).
+//   * The first call on each device looks up the device address of the scratch array (with
+//     that device current). Make that first call outside any stream capture.
+//   * All calls on a device share the one array and it keeps whatever the previous call left
+//     there. Nothing has to start at zero: each call overwrites every partial it later reads.
+//     Two calls that overlap on the GPU (different streams, no ordering between them) would
+//     race on the array - order them on one stream or with events.
+//   * k, features and the leading dimensions must be multiples of 8; x, w, y 16-byte aligned.
+#pragma once
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FLLM_NOALLOC_SCRATCH_BYTES (8u << 20)
+
+enum {
+  FLLM_NOALLOC_OK = 0,
+  FLLM_NOALLOC_E_ARGS = -1,       // null pointer, non-positive size, bad alignment or multiple
+  FLLM_NOALLOC_E_TOO_LARGE = -2,  // splits * tokens * features * 4 exceeds the scratch array
+  FLLM_NOALLOC_E_CUDA = -3,       // a CUDA call failed (symbol lookup, launch)
+};
+
+// `stream` is a cudaStream_t (0 = default stream). `status` may be null; when given it is a
+// device int that receives a non-zero code if a pipeline wait inside the kernel ran out.
+// Returns FLLM_NOALLOC_OK or one of the negative codes above.
+int fllm_linear_bf16_splitk_noalloc(const void* x, long long ldx, const void* w, long long ldw,
+                                    const void* bias, void* y, long long ldy, int tokens,
+                                    int features, int k, int splits, int* status, void* stream);
+
+// Message of the most recent failure on the calling thread ("" if none).
+const char* fllm_noalloc_last_error(void);
+
+// Size of the per-device scratch array, for callers that size their calls at run time.
+size_t fllm_noalloc_scratch_bytes(void);
+
+#ifdef __cplusplus
+}
+#endif
