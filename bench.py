@@ -125,7 +125,8 @@ def main() -> None:
                       use_cuda_graphs=not args.no_graphs)
     ec.num_kv_blocks = args.batch * (-(-ec.max_model_len // 16)) + 16
     par = ParallelConfig(tp=world)
-    tp_rt = make_tp_runtime(world, rank, dev, backend=args.backend)
+    tp_rt = make_tp_runtime(world, rank, dev, backend=args.backend, hidden=cfg.hidden_size,
+                            max_tokens=ec.max_num_batched_tokens)
     eng = LLMEngine(cfg, ec, par, device=dev, tp_group=tp_rt, tp_rank=rank, seed=0)
 
     g = torch.Generator().manual_seed(1234)

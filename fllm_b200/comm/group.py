@@ -83,9 +83,10 @@ class Group:
         """Returns [size, *x.shape]."""
         if self.size == 1:
             return x.unsqueeze(0)
-        out = torch.empty((self.size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-        self._wrap(dist.all_gather_into_tensor, out, x.contiguous(), group=self.pg)
-        return out
+        flat = x.contiguous().view(-1)
+        out = torch.empty(self.size * flat.numel(), dtype=x.dtype, device=x.device)
+        self._wrap(dist.all_gather_into_tensor, out, flat, group=self.pg)
+        return out.view((self.size,) + tuple(x.shape))
 
     def reduce_scatter(self, x: torch.Tensor) -> torch.Tensor:
         """x: [size * n, ...] -> this rank's reduced [n, ...] slice."""

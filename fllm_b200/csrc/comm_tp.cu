@@ -1,0 +1,278 @@
+// Tensor-parallel glue that runs between the two fused GEMMs of a layer half, plus the
+// peer-memory plumbing (CUDA IPC) and a small-message all-reduce.
+//
+//   tp_reduce_norm_ag_kernel   one CTA per token row this rank owns: wait (bounded) until every
+//       rank's GEMM epilogue has delivered its partial sums for the row block, add them to the
+//       sequence-sharded residual in rank order (so every rank computes identical bits),
+//       RMS-normalise, and store the normalised row into EVERY rank's gathered-activation buffer
+//       over NVLink, then bump that rank's arrival counter. The next GEMM's TMA producer waits
+//       on those counters, so reduce-scatter -> norm -> all-gather costs one small kernel and no
+//       library collective.
+//   tp_allreduce_kernel        one-shot all-reduce for small messages: every rank pushes its
+//       vector into all peers' slots, then sums the slots in rank order (bounded wait).
+//
+// The reference reduces after o_proj / down_proj with one all-reduce each
+// (rust/engine/src/rust_decoder.rs:5396, :5700) and its own one-shot kernel spins without a
+// bound (rust/engine/cuda/comm_kernels.cu:134-202); here every wait gives up after a fixed
+// number of polls and reports FLLM_ERR_PEER_TIMEOUT in the status word.
+#include "fllm_ops.h"
+#include "ptx.cuh"
+#include "tma_host.h"
+
+namespace fllm {
+
+constexpr uint32_t kPeerPolls = 1u << 22;
+
+__device__ __forceinline__ int tp_rows_owned(int tokens, int rows_per, int rank) {
+  const int lo = rank * rows_per;
+  return max(0, min(tokens, lo + rows_per) - lo);
+}
+
+__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+template <int VEC_ITERS>
+__global__ void __launch_bounds__(256) tp_reduce_norm_ag_kernel(const TpNormArgs a) {
+  const int my_rows = tp_rows_owned(a.tokens, a.rows_per, a.my_rank);
+  const int row = blockIdx.x;                         // local row index
+  __shared__ float red[8];
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  if (a.rs_buf && threadIdx.x < a.tp) {
+    const int s = threadIdx.x;
+    if (!wait_flag_ge(a.rs_flags + s, a.rs_consumed[s] + a.rs_expected, kPeerPolls)) {
+      failed = 1;
+      if (a.status) atomicCAS(a.status, FLLM_OK, FLLM_ERR_PEER_TIMEOUT);
+    }
+  }
+  __syncthreads();
+  if (row < my_rows) {
+    const int nvec = a.hidden / 8;
+    __nv_bfloat16* xr = reinterpret_cast<__nv_bfloat16*>(a.residual) + (size_t)row * a.hidden;
+    float vals[VEC_ITERS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < VEC_ITERS; ++it) {
+      const int i = threadIdx.x + it * 256;
+      if (i < nvec) {
+        const uint4 xv = reinterpret_cast<const uint4*>(xr)[i];
+        const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xv);
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(xw[j]);
+          acc[2 * j] = f.x;
+          acc[2 * j + 1] = f.y;
+        }
+        if (a.rs_buf && !failed) {
+          float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int s = 0; s < a.tp; ++s) {            // fixed order: same bits on every rank
+            const __nv_bfloat16* pr = reinterpret_cast<const __nv_bfloat16*>(a.rs_buf) +
+                                      ((size_t)s * a.rows_per + row) * a.hidden;
+            const uint4 pv = ld_cg_u4(reinterpret_cast<const uint4*>(pr) + i);   // L2: written by a peer
+            const uint32_t* pw = reinterpret_cast<const uint32_t*>(&pv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack_bf16x2(pw[j]);
+              d[2 * j] += f.x;
+              d[2 * j + 1] += f.y;
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            // the projection output is a bf16 tensor on one GPU; round the reduced sum the same way
+            acc[j] += __bfloat162float(__float2bfloat16(d[j]));
+          }
+          uint4 o;
+          o.x = pack_bf16x2(acc[0], acc[1]);
+          o.y = pack_bf16x2(acc[2], acc[3]);
+          o.z = pack_bf16x2(acc[4], acc[5]);
+          o.w = pack_bf16x2(acc[6], acc[7]);
+          reinterpret_cast<uint4*>(xr)[i] = o;
+          const uint32_t* ow = reinterpret_cast<const uint32_t*>(&o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = unpack_bf16x2(ow[j]);
+            acc[2 * j] = f.x;
+            acc[2 * j + 1] = f.y;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          vals[it][j] = acc[j];
+          ss += acc[j] * acc[j];
+        }
+      }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float inv = rsqrtf(tot / (float)a.hidden + a.eps);
+    const int grow = a.my_rank * a.rows_per + row;    // global token row
+    const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(a.norm_w);
+#pragma unroll
+    for (int it = 0; it < VEC_ITERS; ++it) {
+      const int i = threadIdx.x + it * 256;
+      if (i < nvec) {
+        const uint4 wv = reinterpret_cast<const uint4*>(w)[i];
+        const uint32_t* ww = reinterpret_cast<const uint32_t*>(&wv);
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 g = unpack_bf16x2(ww[j]);
+          ow[j] = pack_bf16x2(vals[it][2 * j] * inv * (g.x + a.w_offset),
+                              vals[it][2 * j + 1] * inv * (g.y + a.w_offset));
+        }
+        for (int d = 0; d < a.tp; ++d) {
+          const int dst = (a.my_rank + d) % a.tp;     // stagger destinations across ranks
+          reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.ag_bufs[dst]) + (size_t)grow * a.hidden)[i] = o;
+        }
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < a.tp)
+      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.ag_flags[threadIdx.x] + a.my_rank) : "memory");
+  }
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(a.cta_done, 1u) == gridDim.x - 1) {
+      if (a.rs_buf)
+        for (int s = 0; s < a.tp; ++s) a.rs_consumed[s] += a.rs_expected;
+      *a.cta_done = 0;
+      __threadfence();
+    }
+  }
+}
+
+void tp_reduce_norm_allgather(const TpNormArgs& a, cudaStream_t s) {
+  if (a.hidden % 8 || a.hidden > 8 * 256 * 8)
+    throw std::runtime_error("tp_reduce_norm_allgather: hidden must be a multiple of 8 and at most 16384");
+  if (a.tp < 1 || a.tp > 8) throw std::runtime_error("tp_reduce_norm_allgather: tp must be in [1, 8]");
+  const int lo = a.my_rank * a.rows_per;
+  const int my_rows = std::max(0, std::min(a.tokens, lo + a.rows_per) - lo);
+  const int grid = std::max(my_rows, 1);              // a rank without rows still does the bookkeeping
+  const int iters = (a.hidden / 8 + 255) / 256;
+  switch (iters) {
+    case 1: tp_reduce_norm_ag_kernel<1><<<grid, 256, 0, s>>>(a); break;
+    case 2: tp_reduce_norm_ag_kernel<2><<<grid, 256, 0, s>>>(a); break;
+    case 3: tp_reduce_norm_ag_kernel<3><<<grid, 256, 0, s>>>(a); break;
+    case 4: tp_reduce_norm_ag_kernel<4><<<grid, 256, 0, s>>>(a); break;
+    default: tp_reduce_norm_ag_kernel<8><<<grid, 256, 0, s>>>(a); break;
+  }
+  cuda_check(cudaGetLastError(), "tp_reduce_norm_ag_kernel");
+}
+
+// ---------------------------------------------------------------------------- one-shot all-reduce
+// slots: every rank's buffer [tp][n] (bf16 or fp32 per `is_fp32`); flags: every rank's [tp] counters.
+__global__ void __launch_bounds__(256) tp_allreduce_kernel(const TpAllReduceArgs a) {
+  const size_t n16 = a.bytes / 16;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
+  // push my vector into slot [my_rank] of every rank
+  for (size_t i = tid; i < n16; i += stride) {
+    const uint4 v = reinterpret_cast<const uint4*>(a.input)[i];
+    for (int d = 0; d < a.tp; ++d) {
+      const int dst = (a.my_rank + d) % a.tp;
+      reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.slots[dst]) + (size_t)a.my_rank * a.slot_bytes)[i] = v;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < a.tp)
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.flags[threadIdx.x] + a.my_rank) : "memory");
+  // wait for every source's gridDim.x bumps
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  if (threadIdx.x < a.tp) {
+    if (!wait_flag_ge(a.my_flags + threadIdx.x, a.consumed[threadIdx.x] + gridDim.x, kPeerPolls)) {
+      failed = 1;
+      if (a.status) atomicCAS(a.status, FLLM_OK, FLLM_ERR_PEER_TIMEOUT);
+    }
+  }
+  __syncthreads();
+  if (!failed) {
+    const uint8_t* mine = reinterpret_cast<const uint8_t*>(a.slots[a.my_rank]);
+    for (size_t i = tid; i < n16; i += stride) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < a.tp; ++s) {
+        const uint4 v = ld_cg_u4(reinterpret_cast<const uint4*>(mine + (size_t)s * a.slot_bytes) + i);
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
+        if (a.is_fp32) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[j] += __uint_as_float(w[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = unpack_bf16x2(w[j]);
+            acc[2 * j] += f.x;
+            acc[2 * j + 1] += f.y;
+          }
+        }
+      }
+      uint4 o;
+      if (a.is_fp32) {
+        o = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
+      } else {
+        o.x = pack_bf16x2(acc[0], acc[1]);
+        o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]);
+        o.w = pack_bf16x2(acc[6], acc[7]);
+      }
+      reinterpret_cast<uint4*>(a.output)[i] = o;
+    }
+  }
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(a.cta_done, 1u) == gridDim.x - 1) {
+      for (int s = 0; s < a.tp; ++s) a.consumed[s] += gridDim.x;
+      *a.cta_done = 0;
+      __threadfence();
+    }
+  }
+}
+
+void tp_allreduce(const TpAllReduceArgs& a, cudaStream_t s) {
+  if (a.bytes % 16 || a.bytes > a.slot_bytes) throw std::runtime_error("tp_allreduce: message must be a multiple of 16 bytes and fit a slot");
+  // All ranks must use the same grid (the flag protocol counts one bump per CTA); it depends on the size only.
+  const int grid = (int)std::min<size_t>(32, (a.bytes / 16 + 255) / 256);
+  tp_allreduce_kernel<<<std::max(grid, 1), 256, 0, s>>>(a);
+  cuda_check(cudaGetLastError(), "tp_allreduce_kernel");
+}
+
+// ---------------------------------------------------------------------------- CUDA IPC plumbing
+void* symm_alloc(size_t bytes) {
+  void* p = nullptr;
+  cuda_check(cudaMalloc(&p, bytes), "cudaMalloc(symmetric buffer)");
+  cuda_check(cudaMemset(p, 0, bytes), "cudaMemset(symmetric buffer)");
+  return p;
+}
+
+void symm_free(void* p) { cudaFree(p); }
+
+void symm_export(void* p, unsigned char out[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  cuda_check(cudaIpcGetMemHandle(&h, p), "cudaIpcGetMemHandle");
+  memcpy(out, &h, 64);
+}
+
+void* symm_import(const unsigned char in[64]) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, in, 64);
+  void* p = nullptr;
+  cuda_check(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+  return p;
+}
+
+void symm_close(void* p) { cudaIpcCloseMemHandle(p); }
+
+}  // namespace fllm

@@ -15,6 +15,65 @@ int linear_bf16(const void* x, long long ldx, const void* w, long long ldw, cons
                  size_t workspace_bytes, int* status, int force_splits, cudaStream_t stream);
 size_t gemm_bf16_workspace_bytes(int tokens, int features);
 
+// Tensor-parallel hooks of the GEMM (see gemm_bf16.cu). Zero-initialise, then fill the half
+// that is wanted: rs_* turns the epilogue into a reduce-scatter over peer memory, ag_* makes the
+// TMA producer wait for rows that peers deliver into the (local) activation operand.
+struct TpLinearArgs {
+  void* rs_bufs[8];
+  uint32_t* rs_flags[8];
+  int tp, my_rank, rows_per;
+  long long rs_ld;
+  const uint32_t* ag_flags;
+  uint32_t* ag_consumed;
+  unsigned int* cta_done;
+};
+int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, const void* bias,
+                   void* y, long long ldy, int T, int N, int K, void* workspace,
+                   size_t workspace_bytes, int* status, int force_splits, const TpLinearArgs* tpa,
+                   cudaStream_t stream);
+int linear_rs_expected_signals(int T, int N, int rows_per, int dest);
+
+// Sequence-sharded residual update + RMSNorm + all-gather of the normalised rows (comm_tp.cu).
+struct TpNormArgs {
+  void* residual;            // [rows_per][hidden] bf16, this rank's rows of the residual stream
+  const void* rs_buf;        // local receive buffer [tp][rows_per][hidden]; null = nothing to add
+  const uint32_t* rs_flags;  // [tp] bumped by the sources' GEMM epilogues
+  uint32_t* rs_consumed;     // [tp]
+  uint32_t rs_expected;      // bumps expected from each source for this step
+  const void* norm_w;
+  float eps, w_offset;
+  void* ag_bufs[8];          // every rank's gathered-activation buffer [tokens][hidden]
+  uint32_t* ag_flags[8];     // every rank's arrival counters; this rank bumps entry [my_rank]
+  int tp, my_rank, rows_per, tokens, hidden;
+  unsigned int* cta_done;
+  int* status;
+};
+void tp_reduce_norm_allgather(const TpNormArgs& a, cudaStream_t s);
+
+// One-shot all-reduce (sum) of a small message through peer slots.
+struct TpAllReduceArgs {
+  const void* input;
+  void* output;
+  size_t bytes;              // multiple of 16, at most slot_bytes
+  size_t slot_bytes;
+  int is_fp32;               // else bf16
+  void* slots[8];            // every rank's slot buffer [tp][slot_bytes]
+  uint32_t* flags[8];        // every rank's arrival counters [tp]
+  const uint32_t* my_flags;  // == flags[my_rank]
+  uint32_t* consumed;        // local [tp]
+  int tp, my_rank;
+  unsigned int* cta_done;
+  int* status;
+};
+void tp_allreduce(const TpAllReduceArgs& a, cudaStream_t s);
+
+// Peer memory through CUDA IPC (one process per GPU on one node).
+void* symm_alloc(size_t bytes);
+void symm_free(void* p);
+void symm_export(void* p, unsigned char out[64]);
+void* symm_import(const unsigned char in[64]);
+void symm_close(void* p);
+
 // ---- elementwise --------------------------------------------------------------------
 void embed_bf16(const int* ids, const void* table, void* out, int tokens, int hidden, int vocab,
                 float scale, cudaStream_t s);

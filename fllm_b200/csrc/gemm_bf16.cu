@@ -30,6 +30,13 @@ constexpr int BM = 128;
 constexpr int BK = 64;       // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kGemmThreads = 192;
+constexpr int kMaxTp = 8;
+constexpr uint32_t kPeerWaitPolls = 1u << 22;   // bounded: a few seconds with back-off, then give up
+
+__device__ __forceinline__ int rows_owned(int tokens, int rows_per, int rank) {
+  const int lo = rank * rows_per;
+  return max(0, min(tokens, lo + rows_per) - lo);
+}
 
 struct GemmArgs {
   int M, N, K;
@@ -43,6 +50,20 @@ struct GemmArgs {
   float* ws;               // split-K partials, [k_splits][M*N] in output orientation (dense)
   const __nv_bfloat16* bias;  // per output feature (n when row-major, m when transposed)
   int* status;
+  // ---- tensor parallel (all null / zero on a single GPU) ----
+  // GEMM -> reduce-scatter: token row t belongs to rank t / rows_per; its partial sums are
+  // stored straight into that rank's receive buffer [src rank][rows_per][rs_ld] over NVLink,
+  // then the rank's flag word for this source is bumped once per epilogue warp per tile.
+  __nv_bfloat16* rs_bufs[kMaxTp];
+  uint32_t* rs_flags[kMaxTp];
+  int tp, my_rank, rows_per;
+  long long rs_ld;
+  // all-gather -> GEMM: the activation operand lives in a local buffer that peers fill row
+  // block by row block; the TMA producer waits for the owning rank's flag before it loads.
+  const uint32_t* ag_flags;     // [tp], bumped once per delivered row by the owning rank
+  uint32_t* ag_consumed;        // [tp], rows of each source consumed by earlier launches
+  int ag_tokens;                // token rows in this step (defines how many rows each rank owns)
+  unsigned int* cta_done;       // last-CTA bookkeeping
 };
 
 template <int BN>
@@ -117,6 +138,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      uint32_t arrived = 0;      // bit s: rank s delivered all of its rows of the gathered operand
       for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
         const int split = w / tiles;
         const int t = w - split * tiles;
@@ -124,6 +146,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
         const int m_idx = t - n_idx * p.m_tiles;
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
+        if (p.ag_flags) {
+          // token rows this tile reads: all of them when tokens sit in the N dimension
+          const int t_lo = p.transposed ? n_idx * BN : m_idx * BM;
+          const int t_hi = min(p.ag_tokens, t_lo + (p.transposed ? BN : BM));
+          if (t_hi > t_lo) {
+            for (int s = t_lo / p.rows_per; s <= (t_hi - 1) / p.rows_per && ok; ++s) {
+              if (arrived & (1u << s)) continue;
+              const uint32_t target = p.ag_consumed[s] + (uint32_t)rows_owned(p.ag_tokens, p.rows_per, s);
+              if (!wait_flag_ge(p.ag_flags + s, target, kPeerWaitPolls)) {
+                if (p.status) atomicExch(p.status, FLLM_ERR_PEER_TIMEOUT);
+                *abort_flag = 1;
+                ok = false;
+              }
+              arrived |= 1u << s;
+            }
+            // rows were written by peers through the generic proxy; TMA reads them through the async proxy
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+          if (!ok) break;
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&full_bar[stage], S::kStageBytes);
@@ -185,6 +227,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
       float* wsp = p.k_splits > 1 ? p.ws + (size_t)split * p.M * p.N : nullptr;
       constexpr int CH = BN < 32 ? 16 : 32;
+      // where the bf16 row of a token goes: the local output, or the owning rank's receive buffer
+      const bool rs = p.rs_bufs[0] != nullptr;
+      auto row_ptr = [&](int token) -> __nv_bfloat16* {
+        if (!rs) return p.out + (size_t)token * p.ldc;
+        const int owner = token / p.rows_per;
+        return p.rs_bufs[owner] + ((size_t)p.my_rank * p.rows_per + (token - owner * p.rows_per)) * p.rs_ld;
+      };
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += CH) {
         uint32_t r[32];
@@ -210,7 +259,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
                                   __uint_as_float(r[c + 2]), __uint_as_float(r[c + 3]));
               }
             } else {
-              __nv_bfloat16* dst = p.out + (size_t)m * p.ldc + n0;
+              __nv_bfloat16* dst = row_ptr(m) + n0;
 #pragma unroll
               for (int c = 0; c < CH; c += 8) {
                 if (n0 + c < p.N) {
@@ -259,13 +308,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
               const int mm = odd ? m - 1 : m;
               const uint32_t packed = odd ? pack_bf16x2(recv, own1) : pack_bf16x2(own0, recv);
               if (n < p.N && mm < p.M)
-                *reinterpret_cast<uint32_t*>(p.out + (size_t)n * p.ldc + mm) = packed;
+                *reinterpret_cast<uint32_t*>(row_ptr(n) + mm) = packed;
             }
           }
         }
       }
       tc_fence_before_sync();
       mbar_arrive(&tempty_bar[acc]);
+      if (rs) {
+        // publish this warp's share of the tile: stores -> system fence -> one flag bump per
+        // destination rank that owns token rows of the tile
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int tokens = p.transposed ? p.N : p.M;
+          const int t_lo = p.transposed ? n_idx * BN : m_idx * BM;
+          const int t_hi = min(tokens, t_lo + (p.transposed ? BN : BM));
+          if (t_hi > t_lo)
+            for (int d = t_lo / p.rows_per; d <= (t_hi - 1) / p.rows_per; ++d)
+              asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.rs_flags[d] + p.my_rank) : "memory");
+        }
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
@@ -277,7 +340,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, S::kTmemCols);
   }
-  if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, FLLM_ERR_MBAR_TIMEOUT);
+  if (threadIdx.x == 0 && *abort_flag && p.status) atomicCAS(p.status, FLLM_OK, FLLM_ERR_MBAR_TIMEOUT);
+  if (threadIdx.x == 0 && p.ag_flags) {
+    // the last CTA to leave records that this launch consumed every rank's rows
+    __threadfence();
+    if (atomicAdd(p.cta_done, 1u) == gridDim.x - 1) {
+      for (int s = 0; s < p.tp; ++s) p.ag_consumed[s] += (uint32_t)rows_owned(p.ag_tokens, p.rows_per, s);
+      *p.cta_done = 0;
+      __threadfence();
+    }
+  }
 }
 
 // out[i] = bf16(sum_s ws[s][i] + bias), i over a dense [rows][cols] array written with pitch ldc.
@@ -334,10 +406,44 @@ static int pick_bn_tokens(int t) {
   return 256;
 }
 
+// Tile plan of a linear layer: tokens <= 128 put the weight in the 128-row MMA dimension
+// ("swap-AB") and the tokens in a narrow N tile; larger batches use the usual orientation.
+static void plan_linear(int T, int N, int sms, bool* swap, int* bn) {
+  *swap = T <= 128;
+  if (*swap) {
+    *bn = pick_bn_tokens(T);
+  } else {
+    *bn = N >= 256 * 64 || (N % 256 == 0 && ((T + BM - 1) / BM) * (N / 256) >= sms) ? 256 : 128;
+    if (N < 128) *bn = 64;
+  }
+}
+
+// Flag bumps rank `dest` receives from EACH source rank for one reduce-scatter linear of this
+// shape: 4 epilogue warps x feature tiles x token tiles that overlap the rows `dest` owns.
+int linear_rs_expected_signals(int T, int N, int rows_per, int dest) {
+  bool swap;
+  int bn;
+  plan_linear(T, N, sm_count(), &swap, &bn);
+  const int tok_tile = swap ? bn : BM;
+  const int feat_tiles = swap ? (N + BM - 1) / BM : (N + bn - 1) / bn;
+  const int lo = dest * rows_per, hi = min(T, lo + rows_per);
+  if (hi <= lo) return 0;
+  const int overlapping = (hi - 1) / tok_tile - lo / tok_tile + 1;
+  return 4 * overlapping * feat_tiles;
+}
+
 // y[T, N] = x[T, K] * w[N, K]^T (+ bias[N]);  x row pitch ldx, y row pitch ldy (elements).
 int linear_bf16(const void* x, long long ldx, const void* w, long long ldw, const void* bias,
                  void* y, long long ldy, int T, int N, int K, void* workspace,
                  size_t workspace_bytes, int* status, int force_splits, cudaStream_t stream) {
+  return linear_bf16_tp(x, ldx, w, ldw, bias, y, ldy, T, N, K, workspace, workspace_bytes, status,
+                        force_splits, nullptr, stream);
+}
+
+int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, const void* bias,
+                   void* y, long long ldy, int T, int N, int K, void* workspace,
+                   size_t workspace_bytes, int* status, int force_splits, const TpLinearArgs* tpa,
+                   cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
   if ((K & 7) || (N & 7) || (ldx & 7) || (ldw & 7) || (ldy & 1))
     throw std::runtime_error("linear_bf16: K, N and the row pitches must be multiples of 8");
@@ -350,20 +456,30 @@ int linear_bf16(const void* x, long long ldx, const void* w, long long ldw, cons
   a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   a.status = status;
   a.ws = reinterpret_cast<float*>(workspace);
+  const bool rs = tpa && tpa->rs_bufs[0];
+  if (tpa) {
+    if (tpa->tp > kMaxTp) throw std::runtime_error("linear_bf16: tensor-parallel degree above 8");
+    a.tp = tpa->tp; a.my_rank = tpa->my_rank; a.rows_per = tpa->rows_per; a.rs_ld = tpa->rs_ld;
+    for (int i = 0; i < kMaxTp; ++i) {
+      a.rs_bufs[i] = reinterpret_cast<__nv_bfloat16*>(tpa->rs_bufs[i]);
+      a.rs_flags[i] = tpa->rs_flags[i];
+    }
+    a.ag_flags = tpa->ag_flags; a.ag_consumed = tpa->ag_consumed; a.cta_done = tpa->cta_done;
+    a.ag_tokens = T;
+    if (rs) force_splits = 1;          // partial sums leave the GPU from the epilogue: no split-K
+  }
 
-  const bool swap = T <= 128;
+  bool swap;
   int bn;
+  plan_linear(T, N, sms, &swap, &bn);
   CUtensorMap ta, tb;
   if (swap) {
-    bn = pick_bn_tokens(T);
     a.M = N;  // MMA rows = output features
     a.N = T;
     a.transposed = 1;
     ta = make_tmap_2d(w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldw * 2, BM, BK, true);
     tb = make_tmap_2d(x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, K, ldx * 2, bn, BK, true);
   } else {
-    bn = N >= 256 * 64 || (N % 256 == 0 && ((T + BM - 1) / BM) * (N / 256) >= sms) ? 256 : 128;
-    if (N < 128) bn = 64;
     a.M = T;
     a.N = N;
     a.transposed = 0;

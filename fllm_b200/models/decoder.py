@@ -127,6 +127,56 @@ class Decoder:
             delta = self._reduce(self._ffn_block(lw, h))
         return x, delta
 
+    # ------------------------------------------------------------------ fused tensor parallel
+    @property
+    def fused_tp(self) -> bool:
+        return (self.tp is not None and getattr(self.tp, "backend", "") == "fused" and self.tp.size > 1
+                and not self.cfg.is_moe and self.first_stage and self.last_stage)
+
+    def forward_fused(self, b: StepBatch) -> torch.Tensor:
+        """Whole forward with the sequence-sharded residual: every projection output leaves the
+        GPU from the GEMM epilogue (reduce-scatter over peer memory), one small kernel reduces,
+        adds the residual, normalises and pushes the rows to all ranks, and the next GEMM's TMA
+        producer waits for those rows. Returns the local vocabulary slice of the logits."""
+        cfg, ops, tp, sp = self.cfg, self.ops, self.tp, self.spec
+        T = b.token_ids.shape[0]
+        lo, hi = tp.my_rows(T)
+        if hi > lo:
+            x = ops.embed(b.token_ids[lo:hi].contiguous(), self.w.embed, cfg.embed_scale)
+        else:
+            x = torch.zeros(1, cfg.hidden_size, dtype=self.w.embed.dtype, device=self.w.embed.device)
+        partials = False
+        for li, lw in zip(self.layer_range, self.w.layers):
+            tp.norm(x, T, partials, lw.attn_norm, cfg.rms_eps, cfg.norm_weight_offset)
+            qkv = tp.linear_ag(T, lw.wqkv, lw.bqkv)
+            local = li - self.layer_range.start
+            kc, vc = self.kv.k(local), self.kv.v(local)
+            ops.rope_kv_write(qkv, b.positions, b.slots, self.inv_freq, lw.q_norm, lw.k_norm, kc, vc,
+                              sp.hq_local, sp.hkv_local, cfg.head_dim, cfg.rot_dim, self.rope_style,
+                              cfg.rms_eps, self.attn_factor)
+            q = qkv[:, : sp.hq_local * cfg.head_dim]
+            a = ops.attention(q, kc, vc, b.block_tables, b.row_seq, b.positions, sp.hq_local, sp.hkv_local,
+                              cfg.head_dim, self.scale, cfg.layer_window(li), lw.sinks, cfg.attn_softcap, meta=b)
+            tp.linear_rs(a, lw.wo, lw.bo)
+            tp.norm(x, T, True, lw.ffn_norm, cfg.rms_eps, cfg.norm_weight_offset)
+            gu = tp.linear_ag(T, lw.w_gate_up)
+            act = ops.glu(gu, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit)
+            tp.linear_rs(act, lw.w_down)
+            partials = True
+            if hasattr(ops, "launches"):
+                ops.launches += 6
+        tp.norm(x, T, partials, self.w.final_norm, cfg.rms_eps, cfg.norm_weight_offset)
+        # the head runs on every row (it is the consumer that retires the gathered rows); the
+        # wanted rows are selected afterwards
+        lg = tp.linear_ag(T, self.w.lm_head)
+        if hasattr(ops, "launches"):
+            ops.launches += 2
+        if not (b.all_decode and b.logit_rows.numel() == T):
+            lg = lg.index_select(0, b.logit_rows.long())
+        if cfg.logit_softcap > 0:
+            lg = (cfg.logit_softcap * torch.tanh(lg.float() / cfg.logit_softcap)).to(lg.dtype)
+        return lg
+
     def logits(self, x: torch.Tensor, delta: Optional[torch.Tensor], b: StepBatch) -> torch.Tensor:
         """Final norm + LM head on the requested rows -> [R, vocab_local]."""
         cfg, ops = self.cfg, self.ops
@@ -141,6 +191,8 @@ class Decoder:
         return lg
 
     def forward(self, b: StepBatch) -> torch.Tensor:
+        if self.fused_tp:
+            return self.forward_fused(b)
         x, delta = self.forward_hidden(b)
         return self.logits(x, delta, b)
 

@@ -47,7 +47,8 @@ class LibraryTP:
         pass
 
 
-def make_tp_runtime(world: int, rank: int, device, backend: str = "auto", group: Optional[Group] = None):
+def make_tp_runtime(world: int, rank: int, device, backend: str = "auto", group: Optional[Group] = None,
+                    hidden: int = 0, max_tokens: int = 2048):
     if world <= 1:
         return SingleRank()
     group = group or Group()
@@ -57,7 +58,7 @@ def make_tp_runtime(world: int, rank: int, device, backend: str = "auto", group:
     if backend == "fused" and device.type == "cuda":
         try:
             from ..comm.symm import FusedTP
-            rt = FusedTP(group, device)
+            rt = FusedTP(group, device, hidden, max_tokens)
             if rt.self_check():
                 return rt
             rt.close()

@@ -237,3 +237,60 @@ def test_attention_tc(ops, ref, D, hq, hkv, window, sinks, softcap, case):
     # the always-correct generic kernel agrees too
     yg = ops.attention(q, kc, vc, tables, row_seq, pos, hq, hkv, D, D ** -0.5, window, sk, softcap)
     _close(yg, yr, 2e-2)
+
+
+@pytest.mark.parametrize("tp,T", [(2, 64), (4, 13), (8, 64), (8, 5), (4, 300), (2, 2048)])
+def test_fused_tp_chain_single_device_emulation(tp, T):
+    """GEMM->reduce-scatter, reduce+norm+all-gather and all-gather->GEMM for `tp` virtual ranks on
+    one GPU, launched phase by phase (a kernel never waits for a kernel that has not been
+    launched yet). Run twice: the counters are monotonic, so the second pass checks replay."""
+    from fllm_b200.comm.symm import FusedTP
+    H, K, N2 = 512, 256, 384
+    ranks = FusedTP.local_group(tp, H, 2048)
+    g = torch.Generator(device="cuda").manual_seed(tp * 1000 + T)
+    rnd = lambda *s, sc=1.0: (torch.randn(*s, generator=g, device="cuda") * sc).to(torch.bfloat16)
+    for it in range(2):
+        xs = [rnd(T, K, sc=0.5) for _ in range(tp)]
+        ws = [rnd(H, K, sc=0.05) for _ in range(tp)]
+        w2 = rnd(N2, H, sc=0.05)
+        res_full = rnd(T, H)
+        normw = rnd(H)
+        shards = []
+        for r in ranks:
+            lo, hi = r.my_rows(T)
+            sh = torch.zeros(max(hi - lo, 1), H, dtype=torch.bfloat16, device="cuda")
+            sh[: hi - lo] = res_full[lo:hi]
+            shards.append(sh)
+        for r, x, w in zip(ranks, xs, ws):
+            r.linear_rs(x, w)
+        for r, sh in zip(ranks, shards):
+            r.norm(sh, T, True, normw, 1e-6)
+        outs = [r.linear_ag(T, w2) for r in ranks]
+        torch.cuda.synchronize()
+        part = sum(x.float() @ w.float().t() for x, w in zip(xs, ws))
+        new_res = (res_full.float() + part.to(torch.bfloat16).float()).to(torch.bfloat16)
+        hn = new_res.float() * torch.rsqrt(new_res.float().pow(2).mean(-1, keepdim=True) + 1e-6) * normw.float()
+        want = hn.to(torch.bfloat16).float() @ w2.float().t()
+        for r, sh, o in zip(ranks, shards, outs):
+            lo, hi = r.my_rows(T)
+            _close(sh[: hi - lo], new_res[lo:hi], 3e-2)
+            _close(o, want, 3e-2)
+            assert r.check_status() == 0
+        # every rank computed bit-identical gathered activations
+        for o in outs[1:]:
+            assert torch.equal(o, outs[0])
+
+
+def test_fused_tp_allreduce_single_device_emulation():
+    """All virtual ranks push first (phase 1 is part of the same kernel), so on one device the
+    kernel of rank r can only complete once every rank has pushed: launch order would deadlock a
+    real wait, hence this test only exercises the time-out path of the first rank and checks
+    that the status word reports it and the context stays usable."""
+    from fllm_b200.comm.symm import FusedTP
+    ranks = FusedTP.local_group(2, 256, 64)
+    x = torch.ones(64, dtype=torch.float32, device="cuda")
+    out = ranks[0].all_reduce(x)          # rank 1 never arrives: bounded wait, then error status
+    torch.cuda.synchronize()
+    assert ranks[0].check_status() == 2
+    y = torch.ones(8, device="cuda") * 2  # the CUDA context still works
+    assert float(y.sum()) == 16.0

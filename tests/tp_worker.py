@@ -1,0 +1,67 @@
+"""Child process of the tensor-parallel tests: one rank of a TP group (gloo on CPU, NCCL or the
+fused peer-memory path on GPUs). Compares this layout's greedy tokens and last-step logits with
+a single-device run of the same model on the same rank, and prints one line of JSON on rank 0."""
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from fllm_b200.comm import Group, init_distributed  # noqa: E402
+from fllm_b200.config import EngineConfig, ParallelConfig, preset  # noqa: E402
+from fllm_b200.parallel.tp import LibraryTP, make_tp_runtime  # noqa: E402
+from fllm_b200.runtime import LLMEngine, SamplingParams  # noqa: E402
+
+
+def main():
+    device_kind, backend, model = sys.argv[1], sys.argv[2], sys.argv[3]
+    rank, world, local = init_distributed("gloo" if device_kind == "cpu" else "nccl", timeout_s=120)
+    dev = torch.device("cpu") if device_kind == "cpu" else torch.device("cuda", local)
+    cfg = preset(model)
+    if model == "tiny-llama":
+        cfg.vocab_size = 2048
+    ec = EngineConfig(max_num_seqs=8, max_num_batched_tokens=48, max_model_len=256, num_kv_blocks=96,
+                      use_cuda_graphs=(device_kind != "cpu" and backend != "nccl-eager"))
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (7, 40, 21, 90, 3)]
+    sp = SamplingParams(max_tokens=10)
+    single = LLMEngine(cfg, ec, ParallelConfig(tp=1), device=dev, seed=3)
+    want = single.generate(prompts, sp)
+    grp = Group()
+    if backend == "fused":
+        tp_rt = make_tp_runtime(world, rank, dev, backend="fused", group=grp, hidden=cfg.hidden_size,
+                                max_tokens=ec.max_num_batched_tokens)
+    else:
+        tp_rt = LibraryTP(grp)
+    eng = LLMEngine(cfg, ec, ParallelConfig(tp=world), device=dev, tp_group=tp_rt, tp_rank=rank, seed=3)
+    got = eng.generate(prompts, sp)
+
+    def last_logits(e):
+        e.add_request(prompts[3][:40], SamplingParams(max_tokens=1))
+        step = e.scheduler.schedule()
+        batch = e._build_batch(step)
+        lg = e.decoder.full_logits(e.decoder.forward(batch)).float()
+        toks = e.decoder.greedy_tokens(e.decoder.forward(batch)) if False else lg.argmax(-1).int()
+        e._commit(step, toks.tolist())
+        return lg[-1].cpu()
+
+    a, b_ = last_logits(single), last_logits(eng)
+    logit_err = float((a - b_).abs().max() / (a.abs().max() + 1e-6))
+    status = 0
+    if hasattr(tp_rt, "check_status"):
+        status = tp_rt.check_status()
+    if rank == 0:
+        agree = sum(a == b for o, r in zip(got, want) for a, b in zip(o, r))
+        total = sum(len(o) for o in want)
+        print(json.dumps({"backend": getattr(tp_rt, "backend", "?"), "world": world, "agree": agree, "total": total,
+                          "status": status, "graph_steps": eng.stats.graph_steps, "logit_err": logit_err}), flush=True)
+    grp.barrier()
+    if hasattr(tp_rt, "close"):
+        tp_rt.close()
+    torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
