@@ -1,0 +1,587 @@
+"""One HTTP port speaking the OpenAI, Anthropic, Ollama, llama.cpp, TGI and SGLang dialects.
+
+Architecture (cf. rust/engine/src/server.rs:765-823, :926-1140): HTTP handlers run on the
+asyncio loop; the engine step loop runs on ONE worker thread and is the only code that touches
+the engine. Handlers talk to it through a command queue (submit / abort) and get tokens back
+through per-request asyncio queues. An exception inside a step is contained: every in-flight
+request fails with an error id, their sequences are dropped and the loop continues; three
+consecutive failures stop the worker so a supervisor can restart the process. ``/health`` is
+liveness, ``/ready`` additionally requires a fresh worker heartbeat and no drain in progress.
+"""
+from __future__ import annotations
+
+import asyncio
+import contextlib
+import json
+import queue
+import threading
+import time
+import uuid
+from typing import Any, AsyncIterator, Dict, List, Optional
+
+from fastapi import FastAPI, HTTPException, Request as HttpRequest
+from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+from .. import __version__
+from ..runtime.request import SamplingParams
+from ..tokenizer import render_chat
+from ..utils.metrics import Metrics
+
+
+class EngineWorker:
+    """Owns the engine on a dedicated thread."""
+
+    STALL_S = 30.0
+
+    def __init__(self, engine, metrics: Metrics):
+        self.engine, self.metrics = engine, metrics
+        self.cmds: "queue.Queue[tuple]" = queue.Queue()
+        self.streams: Dict[str, tuple] = {}          # request id -> (loop, asyncio.Queue, t_submit, n_prompt)
+        self.heartbeat = time.monotonic()
+        self.draining = False
+        self.consecutive_failures = 0
+        self.stopped = threading.Event()
+        self.inject_failure = 0                       # test hook: number of steps that raise
+        self.thread = threading.Thread(target=self._run, name="fllm-engine", daemon=True)
+
+    def start(self) -> None:
+        self.thread.start()
+
+    def stop(self) -> None:
+        self.stopped.set()
+        self.cmds.put(("wake",))
+        self.thread.join(timeout=10)
+
+    # called from the asyncio side
+    def submit(self, loop, rid: str, prompt: List[int], params: SamplingParams) -> "asyncio.Queue":
+        q: asyncio.Queue = asyncio.Queue()
+        self.cmds.put(("submit", rid, prompt, params, loop, q))
+        return q
+
+    def abort(self, rid: str) -> None:
+        self.cmds.put(("abort", rid))
+
+    def ready(self) -> bool:
+        return (not self.draining and not self.stopped.is_set()
+                and time.monotonic() - self.heartbeat < self.STALL_S)
+
+    def _emit(self, rid: str, item: dict, final: bool) -> None:
+        ent = self.streams.get(rid)
+        if ent is None:
+            return
+        loop, q = ent[0], ent[1]
+        loop.call_soon_threadsafe(q.put_nowait, item)
+        if final:
+            self.streams.pop(rid, None)
+
+    def _drain_cmds(self, block: bool) -> None:
+        try:
+            cmd = self.cmds.get(timeout=0.05) if block else self.cmds.get_nowait()
+        except queue.Empty:
+            return
+        while True:
+            if cmd[0] == "submit":
+                _, rid, prompt, params, loop, q = cmd
+                self.streams[rid] = (loop, q, time.monotonic(), len(prompt))
+                try:
+                    self.engine.add_request(prompt, params, request_id=rid)
+                    self.metrics.inc("fllm_prompt_tokens_total", len(prompt))
+                except Exception as e:                                   # validation errors
+                    self._emit(rid, {"error": str(e), "status": 400}, True)
+            elif cmd[0] == "abort":
+                self.engine.abort_request(cmd[1])
+                self.streams.pop(cmd[1], None)
+            try:
+                cmd = self.cmds.get_nowait()
+            except queue.Empty:
+                return
+
+    def _run(self) -> None:
+        eng = self.engine
+        while not self.stopped.is_set():
+            self.heartbeat = time.monotonic()
+            self._drain_cmds(block=not eng.has_unfinished())
+            if not eng.has_unfinished():
+                continue
+            try:
+                if self.inject_failure > 0:
+                    self.inject_failure -= 1
+                    raise RuntimeError("injected step failure")
+                events = eng.step()
+                self.consecutive_failures = 0
+            except Exception as e:                                       # contain, fail in-flight, continue
+                self.consecutive_failures += 1
+                self.metrics.inc("fllm_worker_panics_total")
+                err_id = uuid.uuid4().hex[:12]
+                for rid in list(self.streams):
+                    eng.abort_request(rid)
+                    self._emit(rid, {"error": f"internal error {err_id}: {type(e).__name__}", "status": 500}, True)
+                if self.consecutive_failures >= 3:
+                    self.stopped.set()
+                continue
+            now = time.monotonic()
+            for ev in events:
+                ent = self.streams.get(ev.request_id)
+                if ent is not None and ev.token_ids:
+                    self.metrics.inc("fllm_generation_tokens_total", len(ev.token_ids))
+                if ev.finished:
+                    self.metrics.inc("fllm_requests_total")
+                    if ent is not None:
+                        self.metrics.observe("fllm_e2e_request_latency_seconds", now - ent[2])
+                self._emit(ev.request_id, {"tokens": ev.token_ids, "finished": ev.finished,
+                                           "reason": ev.finish_reason, "error": ev.error}, ev.finished)
+            bm = eng.blocks
+            self.metrics.set("fllm_kv_cache_usage", bm.num_used() / max(bm.num_blocks, 1))
+            self.metrics.set("fllm_requests_running", len(eng.scheduler.running))
+            self.metrics.set("fllm_requests_waiting", len(eng.scheduler.waiting))
+            self.metrics.set("fllm_prefix_cache_hits", bm.stats["prefix_hits"])
+
+
+# ---------------------------------------------------------------------------- helpers
+def _sampling_from(body: dict, default_max: int = 256, dialect: str = "openai") -> SamplingParams:
+    g = body.get
+    opts = body.get("options", {}) if dialect == "ollama" else {}
+    pick = lambda *names, default=None: next((src[n] for src in (body, opts) for n in names if src.get(n) is not None), default)
+    stop = pick("stop", "stop_sequences", default=[])
+    if isinstance(stop, str):
+        stop = [stop]
+    sp = SamplingParams(
+        temperature=float(pick("temperature", default=1.0 if dialect != "llamacpp" else 0.8)),
+        top_p=float(pick("top_p", default=1.0)), top_k=int(pick("top_k", default=0) or 0),
+        min_p=float(pick("min_p", default=0.0)),
+        repetition_penalty=float(pick("repetition_penalty", "repeat_penalty", default=1.0)),
+        presence_penalty=float(pick("presence_penalty", default=0.0)),
+        frequency_penalty=float(pick("frequency_penalty", default=0.0)),
+        seed=pick("seed"), max_tokens=int(pick("max_tokens", "max_completion_tokens", "num_predict", "n_predict",
+                                               "max_new_tokens", default=default_max)),
+        min_tokens=int(pick("min_tokens", default=0)), ignore_eos=bool(pick("ignore_eos", default=False)),
+        stop_token_ids=tuple(pick("stop_token_ids", default=()) or ()), stop=tuple(stop or ()),
+        logit_bias={int(k): float(v) for k, v in (g("logit_bias") or {}).items()} or None,
+        allowed_token_ids=g("allowed_token_ids"), logprobs=bool(g("logprobs")),
+        priority=int(g("priority") or 0), timeout_s=g("timeout"), cache_salt=str(g("cache_salt") or ""))
+    if sp.max_tokens < 1:
+        sp.max_tokens = default_max
+    return sp
+
+
+class StopChecker:
+    """Incremental detokenisation with stop strings (text is held back while it could still
+    turn into a stop sequence)."""
+
+    def __init__(self, tokenizer, stops):
+        self.tk, self.stops = tokenizer, [s for s in stops if s]
+        self.ids: List[int] = []
+        self.sent = 0
+        self.hit = False
+
+    def push(self, tokens: List[int], final: bool) -> str:
+        self.ids.extend(tokens)
+        text = self.tk.decode(self.ids)
+        if text.endswith("�") and not final:        # incomplete UTF-8 sequence: wait
+            text = text[:-1]
+        for s in self.stops:
+            i = text.find(s, max(0, self.sent - len(s)))
+            if i >= 0:
+                self.hit = True
+                out = text[self.sent:i]
+                self.sent = i
+                return out
+        hold = 0 if final else max((len(s) - 1 for s in self.stops), default=0)
+        end = max(self.sent, len(text) - hold)
+        out = text[self.sent:end]
+        self.sent = end
+        return out
+
+
+def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Optional[str] = None) -> FastAPI:
+    metrics = Metrics()
+    worker = EngineWorker(engine, metrics)
+
+    @contextlib.asynccontextmanager
+    async def lifespan(_app):
+        if not worker.thread.is_alive():
+            worker.start()
+        yield
+        worker.stop()
+
+    app = FastAPI(title="fllm_b200", version=__version__, lifespan=lifespan)
+    app.state.worker, app.state.metrics, app.state.engine = worker, metrics, engine
+    started = time.time()
+
+    @app.middleware("http")
+    async def _auth(request: HttpRequest, call_next):
+        if api_key and request.url.path not in ("/health", "/ready", "/metrics", "/version"):
+            tok = request.headers.get("authorization", "").removeprefix("Bearer ").strip() or \
+                request.headers.get("x-api-key", "")
+            if tok != api_key:
+                return JSONResponse({"error": {"message": "invalid API key", "type": "authentication_error"}}, 401)
+        return await call_next(request)
+
+    # ------------------------------------------------------------------ core generation
+    def encode_prompt(p) -> List[int]:
+        if isinstance(p, list) and p and isinstance(p[0], int):
+            return [int(t) for t in p]
+        if isinstance(p, list) and p and isinstance(p[0], str):
+            p = p[0]
+        if not isinstance(p, str):
+            raise HTTPException(400, "prompt must be a string or a list of token ids")
+        return tokenizer.encode(p, add_bos=True)
+
+    async def generate(prompt_ids: List[int], sp: SamplingParams, request: Optional[HttpRequest] = None) -> AsyncIterator[dict]:
+        """Yields {"text", "tokens", "finished", "reason"} pieces."""
+        if worker.draining:
+            raise HTTPException(503, "server is draining")
+        if worker.stopped.is_set():
+            raise HTTPException(503, "engine worker stopped")
+        try:
+            sp.validate(engine.model_cfg.vocab_size)
+        except ValueError as e:
+            raise HTTPException(400, str(e))
+        rid = "req-" + uuid.uuid4().hex
+        q = worker.submit(asyncio.get_running_loop(), rid, prompt_ids, sp)
+        chk = StopChecker(tokenizer, sp.stop)
+        t0, first, last = time.monotonic(), True, None
+        try:
+            while True:
+                item = await q.get()
+                if item.get("error"):
+                    raise HTTPException(item.get("status", 500), item["error"])
+                now = time.monotonic()
+                if item["tokens"]:
+                    if first:
+                        metrics.observe("fllm_time_to_first_token_seconds", now - t0)
+                        first = False
+                    elif last is not None:
+                        metrics.observe("fllm_inter_token_latency_seconds", (now - last) / max(len(item["tokens"]), 1))
+                    last = now
+                toks = [t for t in item["tokens"] if t != getattr(tokenizer, "eos_token_id", None) or sp.ignore_eos]
+                text = chk.push(toks, item["finished"])
+                if chk.hit and not item["finished"]:
+                    worker.abort(rid)
+                    yield {"text": text, "tokens": item["tokens"], "finished": True, "reason": "stop"}
+                    return
+                yield {"text": text, "tokens": item["tokens"], "finished": item["finished"],
+                       "reason": "stop" if chk.hit else item["reason"]}
+                if item["finished"]:
+                    return
+        except (asyncio.CancelledError, GeneratorExit):
+            worker.abort(rid)
+            raise
+
+    async def collect(prompt_ids, sp):
+        text, toks, reason = [], [], None
+        async for piece in generate(prompt_ids, sp):
+            text.append(piece["text"])
+            toks.extend(piece["tokens"])
+            reason = piece["reason"] or reason
+        return "".join(text), toks, reason or "stop"
+
+    def sse(gen) -> StreamingResponse:
+        return StreamingResponse(gen, media_type="text/event-stream")
+
+    # ------------------------------------------------------------------ health / admin
+    @app.get("/health")
+    async def health():
+        return {"status": "ok"}
+
+    @app.get("/ready")
+    async def ready():
+        if worker.ready():
+            return {"status": "ready"}
+        return JSONResponse({"status": "not ready", "draining": worker.draining}, 503)
+
+    @app.get("/version")
+    async def version():
+        return {"version": __version__}
+
+    @app.get("/metrics")
+    async def prom():
+        metrics.set("fllm_uptime_seconds", time.time() - started)
+        metrics.set("fllm_draining", 1.0 if worker.draining else 0.0)
+        return PlainTextResponse(metrics.render())
+
+    @app.post("/admin/drain")
+    async def drain(body: dict = {}):
+        worker.draining = bool(body.get("enable", True)) if body else True
+        return {"draining": worker.draining}
+
+    @app.get("/admin/config")
+    async def admin_config():
+        from ..config import dump_effective
+        return json.loads(dump_effective(engine.model_cfg, engine.cfg, engine.par))
+
+    @app.get("/admin/prefix-cache")
+    async def admin_prefix():
+        return dict(engine.blocks.stats, cached_blocks=len(engine.blocks.cached), free_blocks=engine.blocks.num_free())
+
+    @app.post("/admin/cache")
+    async def admin_cache_reset():
+        return {"freed_blocks": engine.blocks.reset_prefix_cache()}
+
+    # ------------------------------------------------------------------ OpenAI
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model", "created": int(started),
+                                            "owned_by": "fllm_b200", "max_model_len": engine.cfg.max_model_len}]}
+
+    def usage(n_prompt, n_out):
+        return {"prompt_tokens": n_prompt, "completion_tokens": n_out, "total_tokens": n_prompt + n_out}
+
+    @app.post("/v1/completions")
+    async def completions(body: dict):
+        ids = encode_prompt(body.get("prompt", ""))
+        sp = _sampling_from(body, 16)
+        cid = "cmpl-" + uuid.uuid4().hex
+        if body.get("stream"):
+            async def gen():
+                async for piece in generate(ids, sp):
+                    chunk = {"id": cid, "object": "text_completion", "created": int(time.time()), "model": model_name,
+                             "choices": [{"index": 0, "text": piece["text"], "token_ids": piece["tokens"],
+                                          "finish_reason": piece["reason"] if piece["finished"] else None}]}
+                    yield f"data: {json.dumps(chunk)}\n\n"
+                yield "data: [DONE]\n\n"
+            return sse(gen())
+        text, toks, reason = await collect(ids, sp)
+        return {"id": cid, "object": "text_completion", "created": int(time.time()), "model": model_name,
+                "choices": [{"index": 0, "text": text, "token_ids": toks, "finish_reason": reason, "logprobs": None}],
+                "usage": usage(len(ids), len(toks))}
+
+    def chat_prompt(messages, tools=None) -> List[int]:
+        try:
+            text = render_chat(getattr(tokenizer, "chat_template", None), messages, True, tools)
+        except Exception as e:
+            raise HTTPException(400, f"chat template error: {e}")
+        return tokenizer.encode(text, add_bos=True)
+
+    @app.post("/v1/chat/completions")
+    async def chat_completions(body: dict):
+        msgs = body.get("messages")
+        if not isinstance(msgs, list) or not msgs:
+            raise HTTPException(400, "messages must be a non-empty list")
+        ids = chat_prompt(msgs, body.get("tools"))
+        sp = _sampling_from(body, 256)
+        cid = "chatcmpl-" + uuid.uuid4().hex
+        if body.get("stream"):
+            async def gen():
+                head = {"id": cid, "object": "chat.completion.chunk", "created": int(time.time()), "model": model_name,
+                        "choices": [{"index": 0, "delta": {"role": "assistant", "content": ""}, "finish_reason": None}]}
+                yield f"data: {json.dumps(head)}\n\n"
+                n = 0
+                async for piece in generate(ids, sp):
+                    n += len(piece["tokens"])
+                    chunk = {"id": cid, "object": "chat.completion.chunk", "created": int(time.time()), "model": model_name,
+                             "choices": [{"index": 0, "delta": {"content": piece["text"]},
+                                          "finish_reason": piece["reason"] if piece["finished"] else None}]}
+                    if piece["finished"] and (body.get("stream_options") or {}).get("include_usage"):
+                        chunk["usage"] = usage(len(ids), n)
+                    yield f"data: {json.dumps(chunk)}\n\n"
+                yield "data: [DONE]\n\n"
+            return sse(gen())
+        text, toks, reason = await collect(ids, sp)
+        return {"id": cid, "object": "chat.completion", "created": int(time.time()), "model": model_name,
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": reason}],
+                "usage": usage(len(ids), len(toks))}
+
+    @app.post("/v1/chat/completions/render")
+    async def chat_render(body: dict):
+        ids = chat_prompt(body.get("messages", []), body.get("tools"))
+        return {"prompt_token_ids": ids, "prompt": tokenizer.decode(ids)}
+
+    @app.post("/v1/embeddings")
+    async def embeddings(body: dict):
+        raise HTTPException(501, "this model is a decoder served for generation; no embedding head is loaded")
+
+    # ------------------------------------------------------------------ Anthropic
+    def anthropic_messages(body: dict) -> List[dict]:
+        msgs = []
+        sysm = body.get("system")
+        if sysm:
+            if isinstance(sysm, list):
+                sysm = "".join(p.get("text", "") for p in sysm)
+            msgs.append({"role": "system", "content": sysm})
+        for m in body.get("messages", []):
+            c = m.get("content")
+            if isinstance(c, list):
+                c = "".join(p.get("text", "") for p in c if p.get("type") == "text")
+            msgs.append({"role": m.get("role", "user"), "content": c})
+        return msgs
+
+    @app.post("/v1/messages")
+    async def messages(body: dict):
+        if "max_tokens" not in body:
+            raise HTTPException(400, "max_tokens is required")
+        ids = chat_prompt(anthropic_messages(body))
+        sp = _sampling_from(body, 1024)
+        mid = "msg_" + uuid.uuid4().hex
+        stop_map = {"length": "max_tokens", "stop": "end_turn"}
+        if body.get("stream"):
+            async def gen():
+                def ev(name, data):
+                    return f"event: {name}\ndata: {json.dumps(data)}\n\n"
+                yield ev("message_start", {"type": "message_start", "message": {
+                    "id": mid, "type": "message", "role": "assistant", "content": [], "model": model_name,
+                    "stop_reason": None, "usage": {"input_tokens": len(ids), "output_tokens": 0}}})
+                yield ev("content_block_start", {"type": "content_block_start", "index": 0,
+                                                 "content_block": {"type": "text", "text": ""}})
+                n, reason = 0, "stop"
+                async for piece in generate(ids, sp):
+                    n += len(piece["tokens"])
+                    if piece["text"]:
+                        yield ev("content_block_delta", {"type": "content_block_delta", "index": 0,
+                                                         "delta": {"type": "text_delta", "text": piece["text"]}})
+                    reason = piece["reason"] or reason
+                yield ev("content_block_stop", {"type": "content_block_stop", "index": 0})
+                yield ev("message_delta", {"type": "message_delta", "delta": {"stop_reason": stop_map.get(reason, "end_turn")},
+                                           "usage": {"output_tokens": n}})
+                yield ev("message_stop", {"type": "message_stop"})
+            return sse(gen())
+        text, toks, reason = await collect(ids, sp)
+        return {"id": mid, "type": "message", "role": "assistant", "model": model_name,
+                "content": [{"type": "text", "text": text}], "stop_reason": stop_map.get(reason, "end_turn"),
+                "stop_sequence": None, "usage": {"input_tokens": len(ids), "output_tokens": len(toks)}}
+
+    @app.post("/v1/messages/count_tokens")
+    async def count_tokens(body: dict):
+        return {"input_tokens": len(chat_prompt(anthropic_messages(body)))}
+
+    # ------------------------------------------------------------------ Ollama
+    @app.get("/api/version")
+    async def ollama_version():
+        return {"version": __version__}
+
+    @app.get("/api/tags")
+    async def ollama_tags():
+        return {"models": [{"name": model_name, "model": model_name, "size": engine.weights.nbytes(),
+                            "details": {"family": engine.model_cfg.arch, "parameter_size": f"{engine.model_cfg.param_count() / 1e9:.1f}B",
+                                        "quantization_level": engine.model_cfg.weight_format}}]}
+
+    @app.get("/api/ps")
+    async def ollama_ps():
+        return {"models": [{"name": model_name, "model": model_name, "size_vram": engine.weights.nbytes()}]}
+
+    @app.post("/api/show")
+    async def ollama_show(body: dict):
+        return {"modelfile": "", "template": getattr(tokenizer, "chat_template", None) or "", "details": {
+            "family": engine.model_cfg.arch}, "model_info": engine.model_cfg.to_dict()}
+
+    def ollama_stream(ids, sp, make):
+        async def gen():
+            t0 = time.time()
+            n = 0
+            async for piece in generate(ids, sp):
+                n += len(piece["tokens"])
+                d = make(piece["text"], piece["finished"])
+                if piece["finished"]:
+                    d.update({"done_reason": piece["reason"], "prompt_eval_count": len(ids), "eval_count": n,
+                              "total_duration": int((time.time() - t0) * 1e9)})
+                yield json.dumps(d) + "\n"
+        return StreamingResponse(gen(), media_type="application/x-ndjson")
+
+    @app.post("/api/generate")
+    async def ollama_generate(body: dict):
+        ids = encode_prompt(body.get("prompt", "")) if body.get("raw") or not body.get("system") else \
+            chat_prompt([{"role": "system", "content": body["system"]}, {"role": "user", "content": body.get("prompt", "")}])
+        sp = _sampling_from(body, 128, "ollama")
+        now = lambda: time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime())
+        if body.get("stream", True):
+            return ollama_stream(ids, sp, lambda t, done: {"model": model_name, "created_at": now(), "response": t, "done": done})
+        text, toks, reason = await collect(ids, sp)
+        return {"model": model_name, "created_at": now(), "response": text, "done": True, "done_reason": reason,
+                "prompt_eval_count": len(ids), "eval_count": len(toks)}
+
+    @app.post("/api/chat")
+    async def ollama_chat(body: dict):
+        ids = chat_prompt(body.get("messages", []), body.get("tools"))
+        sp = _sampling_from(body, 128, "ollama")
+        now = lambda: time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime())
+        if body.get("stream", True):
+            return ollama_stream(ids, sp, lambda t, done: {"model": model_name, "created_at": now(),
+                                                           "message": {"role": "assistant", "content": t}, "done": done})
+        text, toks, reason = await collect(ids, sp)
+        return {"model": model_name, "created_at": now(), "message": {"role": "assistant", "content": text},
+                "done": True, "done_reason": reason, "prompt_eval_count": len(ids), "eval_count": len(toks)}
+
+    # ------------------------------------------------------------------ llama.cpp
+    @app.post("/completion")
+    async def llamacpp_completion(body: dict):
+        ids = encode_prompt(body.get("prompt", ""))
+        sp = _sampling_from(body, 128, "llamacpp")
+        if body.get("stream"):
+            async def gen():
+                async for piece in generate(ids, sp):
+                    yield f"data: {json.dumps({'content': piece['text'], 'stop': piece['finished']})}\n\n"
+            return sse(gen())
+        text, toks, reason = await collect(ids, sp)
+        return {"content": text, "stop": True, "tokens_predicted": len(toks), "tokens_evaluated": len(ids),
+                "stopped_limit": reason == "length", "stopped_eos": reason == "stop", "model": model_name}
+
+    @app.post("/tokenize")
+    async def tokenize(body: dict):
+        return {"tokens": tokenizer.encode(body.get("content", ""), add_bos=bool(body.get("add_special")))}
+
+    @app.post("/detokenize")
+    async def detokenize(body: dict):
+        return {"content": tokenizer.decode(body.get("tokens", []))}
+
+    @app.get("/props")
+    async def props():
+        return {"model_path": model_name, "n_ctx": engine.cfg.max_model_len, "total_slots": engine.cfg.max_num_seqs,
+                "chat_template": getattr(tokenizer, "chat_template", None) or ""}
+
+    @app.get("/slots")
+    async def slots():
+        return [{"id": i, "is_processing": True, "n_decoded": len(r.output)} for i, r in enumerate(engine.scheduler.running)]
+
+    @app.post("/apply-template")
+    async def apply_template(body: dict):
+        return {"prompt": render_chat(getattr(tokenizer, "chat_template", None), body.get("messages", []))}
+
+    # ------------------------------------------------------------------ TGI / SGLang (shared /generate)
+    @app.post("/generate")
+    async def tgi_or_sglang_generate(body: dict):
+        if "inputs" in body:                                   # TGI
+            p = body.get("parameters", {}) or {}
+            ids = encode_prompt(body["inputs"])
+            sp = _sampling_from(p, 20)
+            text, toks, reason = await collect(ids, sp)
+            return {"generated_text": text, "details": {"finish_reason": "length" if reason == "length" else "eos_token",
+                                                         "generated_tokens": len(toks)}}
+        ids = body.get("input_ids") or encode_prompt(body.get("text", ""))     # SGLang
+        sp = _sampling_from(body.get("sampling_params", {}) or {}, 128)
+        text, toks, reason = await collect(ids, sp)
+        return {"text": text, "meta_info": {"prompt_tokens": len(ids), "completion_tokens": len(toks),
+                                            "finish_reason": {"type": reason}}}
+
+    @app.post("/generate_stream")
+    async def tgi_stream(body: dict):
+        ids = encode_prompt(body.get("inputs", ""))
+        sp = _sampling_from(body.get("parameters", {}) or {}, 20)
+
+        async def gen():
+            acc = []
+            async for piece in generate(ids, sp):
+                acc.append(piece["text"])
+                d = {"token": {"id": piece["tokens"][-1] if piece["tokens"] else None, "text": piece["text"], "special": False},
+                     "generated_text": "".join(acc) if piece["finished"] else None}
+                yield f"data: {json.dumps(d)}\n\n"
+        return sse(gen())
+
+    @app.get("/info")
+    async def tgi_info():
+        return {"model_id": model_name, "max_total_tokens": engine.cfg.max_model_len, "version": __version__}
+
+    @app.get("/get_model_info")
+    async def sglang_model_info():
+        return {"model_path": model_name, "is_generation": True}
+
+    @app.get("/get_server_info")
+    async def sglang_server_info():
+        return {"version": __version__, "max_total_num_tokens": engine.blocks.num_blocks * engine.block_size}
+
+    return app
+
+
+def serve(engine, tokenizer, host: str = "127.0.0.1", port: int = 8000, model_name: str = "fllm-b200",
+          api_key: Optional[str] = None, log_level: str = "info") -> None:
+    import uvicorn
+    uvicorn.run(create_app(engine, tokenizer, model_name, api_key), host=host, port=port, log_level=log_level)
