@@ -1,0 +1,255 @@
+"""Command line: ``python -m fllm_b200 <command>``.
+
+Sub-commands keep the reference's names (rust/engine/src/cli.rs:16-170,
+rust/engine/src/bin/serve.rs:85-119): serve, run, bench, bench-kernel, devices, formats,
+inspect, quantize, make-tiny-model, plan-cluster, selftest-cpu / -gpu / -comm / -parallel.
+Serve flags use the reference's spellings (--model --host --port --model-name --api-key --ctx
+--max-seqs --max-batched-tokens -tp -pp --expert-parallel --kv-cache-type ...).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+from typing import List, Optional
+
+
+def _add_engine_flags(p: argparse.ArgumentParser) -> None:
+    p.add_argument("--model", required=True, help="preset name (random weights), .gguf file or checkpoint directory")
+    p.add_argument("--device", default=None, help="cuda[:i] or cpu (default: cuda when available)")
+    p.add_argument("--ctx", "--max-model-len", dest="ctx", type=int, default=8192)
+    p.add_argument("--max-seqs", "--max-num-seqs", dest="max_seqs", type=int, default=256)
+    p.add_argument("--max-batched-tokens", "--max-num-batched-tokens", dest="max_batched_tokens", type=int, default=2048)
+    p.add_argument("--gpu-memory-utilization", type=float, default=0.90)
+    p.add_argument("--kv-cache-type", default="bf16")
+    p.add_argument("--kv-blocks", type=int, default=0)
+    p.add_argument("--no-prefix-cache", action="store_true")
+    p.add_argument("--no-cuda-graphs", action="store_true")
+    p.add_argument("--scheduling-policy", default="fcfs", choices=["fcfs", "priority"])
+    p.add_argument("--preemption", default="recompute", choices=["recompute", "swap"])
+    p.add_argument("--speculative", default="off", choices=["off", "ngram", "draft"])
+    p.add_argument("--draft-model", default=None)
+    p.add_argument("--draft-tokens", type=int, default=4)
+    p.add_argument("-tp", "--tensor-parallel", dest="tp", type=int, default=1)
+    p.add_argument("-pp", "--pipeline-parallel", dest="pp", type=int, default=1)
+    p.add_argument("--expert-parallel", action="store_true")
+    p.add_argument("--ep-dispatch", default="alltoall", choices=["alltoall", "allreduce"])
+    p.add_argument("--distributed-backend", default="fused", choices=["fused", "nccl"])
+    p.add_argument("--tokenizer", default=None, help="tokenizer.json / directory / .gguf (default: embedded or byte-level)")
+    p.add_argument("--seed", type=int, default=0)
+
+
+def build_engine(args):
+    import torch
+    from .config import EngineConfig, ParallelConfig, preset
+    from .runtime import LLMEngine
+    from .tokenizer import load_tokenizer
+
+    device = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    ec = EngineConfig.from_env(
+        max_num_seqs=args.max_seqs, max_num_batched_tokens=args.max_batched_tokens, max_model_len=args.ctx,
+        gpu_memory_utilization=args.gpu_memory_utilization, kv_cache_dtype=args.kv_cache_type,
+        num_kv_blocks=args.kv_blocks, enable_prefix_caching=not args.no_prefix_cache,
+        use_cuda_graphs=not args.no_cuda_graphs, scheduling_policy=args.scheduling_policy,
+        preemption=args.preemption, speculative=args.speculative, draft_tokens=args.draft_tokens, seed=args.seed)
+    par = ParallelConfig(tp=args.tp, pp=args.pp, expert_parallel=args.expert_parallel, ep_dispatch=args.ep_dispatch,
+                         distributed_backend=args.distributed_backend)
+    weights, tok_path = None, args.tokenizer
+    if args.model.endswith(".gguf") or os.path.isdir(args.model):
+        from .formats.loader import load_model
+        cfg, weights, embedded_tok = load_model(args.model, device)
+        tok_path = tok_path or embedded_tok
+    else:
+        cfg = preset(args.model)
+    tp_rt, rank = None, 0
+    if par.world > 1:
+        from .comm import init_distributed
+        from .parallel.tp import make_tp_runtime
+        rank, world, local = init_distributed()
+        if world != par.world:
+            raise SystemExit(f"tp x pp = {par.world} but WORLD_SIZE = {world}; launch one process per GPU with torchrun")
+        device = f"cuda:{local}" if torch.cuda.is_available() else "cpu"
+        tp_rt = make_tp_runtime(par.tp, rank % par.tp, device, par.distributed_backend, hidden=cfg.hidden_size,
+                                max_tokens=ec.max_num_batched_tokens)
+    try:
+        tokenizer = load_tokenizer(tok_path, cfg.vocab_size)
+    except Exception as e:
+        print(f"[fllm_b200] tokenizer unavailable ({e}); falling back to the byte tokenizer", file=sys.stderr)
+        tokenizer = load_tokenizer(None, max(cfg.vocab_size, 258))
+    eng = LLMEngine(cfg, ec, par, device=device, weights=weights, tp_group=tp_rt, tp_rank=rank, seed=args.seed,
+                    eos_token_id=getattr(tokenizer, "eos_token_id", None))
+    return eng, tokenizer
+
+
+def cmd_serve(args) -> int:
+    from .server.app import serve
+    eng, tok = build_engine(args)
+    eng.warm_up(buckets=[b for b in eng.cfg.graph_buckets if b <= 64])
+    serve(eng, tok, args.host, args.port, args.model_name or os.path.basename(args.model), args.api_key, args.log_level)
+    return 0
+
+
+def cmd_run(args) -> int:
+    from .runtime import SamplingParams
+    from .tokenizer import render_chat
+    eng, tok = build_engine(args)
+    text = args.prompt if args.raw else render_chat(getattr(tok, "chat_template", None), [{"role": "user", "content": args.prompt}])
+    ids = tok.encode(text, add_bos=True)
+    sp = SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
+                        seed=args.seed)
+    out = eng.generate([ids], sp)[0]
+    print(tok.decode(out))
+    return 0
+
+
+def cmd_devices(args) -> int:
+    import torch
+    info = {"cuda_available": torch.cuda.is_available(), "devices": []}
+    for i in range(torch.cuda.device_count()):
+        p = torch.cuda.get_device_properties(i)
+        peers = [j for j in range(torch.cuda.device_count()) if j != i and torch.cuda.can_device_access_peer(i, j)]
+        info["devices"].append({"index": i, "name": p.name, "sm": f"{p.major}.{p.minor}", "sms": p.multi_processor_count,
+                                "memory_gib": round(p.total_memory / 2 ** 30, 1), "p2p_peers": peers})
+    from .ops import _lib
+    info["native_cuda_library"] = _lib.have_cuda_lib()
+    print(json.dumps(info, indent=1) if args.json else "\n".join(
+        [f"cuda:{d['index']} {d['name']} sm_{d['sm']} {d['sms']} SMs {d['memory_gib']} GiB p2p->{d['p2p_peers']}"
+         for d in info["devices"]] or ["no CUDA device; the CPU engine is available"]))
+    return 0
+
+
+def cmd_formats(args) -> int:
+    from .formats.gguf import GGML_TYPES
+    print("weight formats (name, values/block, bytes/block):")
+    for tid, (name, bs, bb) in sorted(GGML_TYPES.items()):
+        print(f"  {tid:4d} {name:8s} {bs:4d} {bb:4d}")
+    print("  1001 NVFP4      16    9   (e2m1 x16 + e4m3 scale; fp32 tensor scale kept apart)")
+    print("  1002 FP8_E4M3    1    1   (block-wise fp32 scales kept apart, 128x128 typical)")
+    return 0
+
+
+def cmd_inspect(args) -> int:
+    from .formats.gguf import GgufReader
+    r = GgufReader(args.file)
+    print(f"{args.file}: {len(r.tensors)} tensors, {len(r.metadata)} metadata keys")
+    for k, v in r.metadata.items():
+        s = repr(v)
+        print(f"  {k} = {s[:100] + '...' if len(s) > 100 else s}")
+    if args.tensors:
+        for t in r.tensors.values():
+            print(f"  {t.name:40s} {t.type_name:6s} {tuple(t.shape)} @{t.offset} {t.nbytes} B")
+    return 0
+
+
+def cmd_quantize(args) -> int:
+    """Re-quantise the 2-D tensors of a GGUF file to another packed type."""
+    import numpy as np
+    from .formats import quant
+    from .formats.gguf import TYPE_ID, GgufReader, GgufWriter
+    r = GgufReader(args.input)
+    w = GgufWriter(args.output)
+    for k, v in r.metadata.items():
+        if k != "general.alignment":
+            w.add(k, v if not isinstance(v, np.generic) else v.item())
+    target = TYPE_ID[args.type.upper()]
+    qt = {"Q4_K": quant.Q4_K, "Q5_K": quant.Q5_K, "Q6_K": quant.Q6_K, "Q8_0": quant.Q8_0, "Q4_0": quant.Q4_0,
+          "F16": quant.F16, "BF16": quant.BF16, "MXFP4": quant.MXFP4}[args.type.upper()]
+    for t in r.tensors.values():
+        bs = quant._lib().fllm_block_size(qt)
+        if len(t.shape) == 2 and t.shape[-1] % bs == 0 and "norm" not in t.name:
+            x = r.tensor_f32(t.name)
+            w.add_tensor(t.name, t.shape, target, quant.quantize(x, qt))
+        else:
+            w.add_tensor(t.name, t.shape, t.ggml_type, np.array(r.tensor_bytes(t.name)))
+    w.write()
+    print(f"wrote {args.output}")
+    return 0
+
+
+def cmd_make_tiny(args) -> int:
+    from .cpu_engine import write_tiny_llama_gguf
+    cfg = write_tiny_llama_gguf(args.output, seed=args.seed)
+    print(f"wrote {args.output}: {cfg.num_layers} layers, hidden {cfg.hidden_size}, vocab {cfg.vocab_size}, Q4_K")
+    return 0
+
+
+def cmd_plan_cluster(args) -> int:
+    from .config import preset
+    from .parallel.planner import GPU_PRESETS, plan_cluster
+    plans = plan_cluster(preset(args.model), args.gpus, GPU_PRESETS[args.gpu], batch=args.batch, ctx=args.ctx,
+                         weight_bits=args.weight_bits)
+    for p in plans[: args.top]:
+        print(json.dumps(p))
+    return 0
+
+
+def _pytest(marker: str, pattern: str) -> int:
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    return subprocess.call([sys.executable, "-m", "pytest", os.path.join(root, "tests"), "-q", "-m", marker, "-k", pattern])
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    ap = argparse.ArgumentParser(prog="fllm_b200")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    s = sub.add_parser("serve", help="HTTP server (OpenAI / Anthropic / Ollama dialects on one port)")
+    _add_engine_flags(s)
+    s.add_argument("--host", default="127.0.0.1")
+    s.add_argument("--port", type=int, default=8000)
+    s.add_argument("--model-name", default=None)
+    s.add_argument("--api-key", default=os.environ.get("FLLM_API_KEY"))
+    s.add_argument("--log-level", default="info")
+    s.set_defaults(fn=cmd_serve)
+    r = sub.add_parser("run", help="generate once from a prompt")
+    _add_engine_flags(r)
+    r.add_argument("prompt")
+    r.add_argument("--raw", action="store_true", help="do not apply the chat template")
+    r.add_argument("--max-tokens", type=int, default=128)
+    r.add_argument("--temperature", type=float, default=0.0)
+    r.add_argument("--top-p", type=float, default=1.0)
+    r.add_argument("--top-k", type=int, default=0)
+    r.set_defaults(fn=cmd_run)
+    d = sub.add_parser("devices")
+    d.add_argument("--json", action="store_true")
+    d.set_defaults(fn=cmd_devices)
+    sub.add_parser("formats").set_defaults(fn=cmd_formats)
+    i = sub.add_parser("inspect")
+    i.add_argument("file")
+    i.add_argument("--tensors", action="store_true")
+    i.set_defaults(fn=cmd_inspect)
+    q = sub.add_parser("quantize")
+    q.add_argument("input")
+    q.add_argument("output")
+    q.add_argument("type")
+    q.set_defaults(fn=cmd_quantize)
+    t = sub.add_parser("make-tiny-model")
+    t.add_argument("output")
+    t.add_argument("--seed", type=int, default=0)
+    t.set_defaults(fn=cmd_make_tiny)
+    pc = sub.add_parser("plan-cluster")
+    pc.add_argument("--model", default="qwen3-8b")
+    pc.add_argument("--gpus", type=int, default=8)
+    pc.add_argument("--gpu", default="b200")
+    pc.add_argument("--batch", type=int, default=64)
+    pc.add_argument("--ctx", type=int, default=2048)
+    pc.add_argument("--weight-bits", type=float, default=16)
+    pc.add_argument("--top", type=int, default=5)
+    pc.set_defaults(fn=cmd_plan_cluster)
+    bk = sub.add_parser("bench-kernel")
+    bk.add_argument("rest", nargs=argparse.REMAINDER)
+    bk.set_defaults(fn=lambda a: __import__("fllm_b200.bench_kernel", fromlist=["main"]).main(a.rest) or 0)
+    b = sub.add_parser("bench")
+    b.add_argument("rest", nargs=argparse.REMAINDER)
+    b.set_defaults(fn=lambda a: subprocess.call([sys.executable, os.path.join(os.path.dirname(os.path.dirname(
+        os.path.abspath(__file__))), "bench.py")] + a.rest))
+    sub.add_parser("selftest-cpu").set_defaults(fn=lambda a: _pytest("not gpu", "formats or engine_cpu"))
+    sub.add_parser("selftest-gpu").set_defaults(fn=lambda a: _pytest("gpu", "kernels or engine_gpu"))
+    sub.add_parser("selftest-comm").set_defaults(fn=lambda a: _pytest("not gpu", "comm"))
+    sub.add_parser("selftest-parallel").set_defaults(fn=lambda a: _pytest("not gpu", "tp_cpu or parallel"))
+    args = ap.parse_args(argv)
+    return int(args.fn(args) or 0)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
