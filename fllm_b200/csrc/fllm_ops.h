@@ -74,6 +74,20 @@ void symm_export(void* p, unsigned char out[64]);
 void* symm_import(const unsigned char in[64]);
 void symm_close(void* p);
 
+// ---- mixture of experts ---------------------------------------------------------------
+int moe_grouped_linear_bf16(const void* xp, long long ldx, const void* w_stack, long long ldw,
+                            const void* bias_stack, void* y, long long ldy, int rows_cap, int n_out, int K,
+                            int experts, const int* tile_expert, const int* tile_row0, const int* num_tiles,
+                            int max_tiles, int bn, int* status, cudaStream_t stream);
+void moe_route(const void* logits, long long ld, const void* bias, int tokens, int experts, int k, int softmax_all,
+               int* ids, float* weights, cudaStream_t s);
+void moe_align(const int* ids, int tokens, int k, int experts, int expert_lo, int expert_hi, int bn, int* row_of,
+               int* token_of, int rows_cap, int* tile_expert, int* tile_row0, int* num_tiles, int max_tiles,
+               cudaStream_t s);
+void moe_gather(const void* x, long long ldx, const int* token_of, void* xp, int rows_cap, int hidden, cudaStream_t s);
+void moe_combine(const void* y, long long ldy, const int* row_of, const float* weights, int tokens, int k, void* out,
+                 long long ldo, int hidden, cudaStream_t s);
+
 // ---- elementwise --------------------------------------------------------------------
 void embed_bf16(const int* ids, const void* table, void* out, int tokens, int hidden, int vocab,
                 float scale, cudaStream_t s);

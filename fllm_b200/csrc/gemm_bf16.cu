@@ -64,6 +64,14 @@ struct GemmArgs {
   uint32_t* ag_consumed;        // [tp], rows of each source consumed by earlier launches
   int ag_tokens;                // token rows in this step (defines how many rows each rank owns)
   unsigned int* cta_done;       // last-CTA bookkeeping
+  // ---- grouped (mixture of experts): swap-AB tiles over a device-built tile list ----
+  // The A operand is the stack of expert matrices [experts * g_rows][K]; tile g of the list
+  // multiplies expert g_tile_expert[g] with the BN permuted token rows starting at
+  // g_tile_row0[g]. The number of tiles is only known on the device.
+  const int* g_tile_expert;
+  const int* g_tile_row0;
+  const int* g_num_tiles;
+  int g_rows;                   // output features per expert
 };
 
 template <int BN>
@@ -130,7 +138,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
   const uint32_t tmem_base = *tmem_slot;
 
   const int tiles = p.m_tiles * p.n_tiles;
-  const int total = tiles * p.k_splits;
+  const bool grouped = p.g_num_tiles != nullptr;
+  const int total = grouped ? *p.g_num_tiles * p.m_tiles : tiles * p.k_splits;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -169,8 +178,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&full_bar[stage], S::kStageBytes);
-          tma_load_2d(sA + stage * S::kABytes, &tma_a, &full_bar[stage], kb * BK, m_idx * BM);
-          tma_load_2d(sB + stage * S::kBBytes, &tma_b, &full_bar[stage], kb * BK, n_idx * BN);
+          const int a_row = grouped ? p.g_tile_expert[n_idx] * p.g_rows + m_idx * BM : m_idx * BM;
+          const int b_row = grouped ? p.g_tile_row0[n_idx] : n_idx * BN;
+          tma_load_2d(sA + stage * S::kABytes, &tma_a, &full_bar[stage], kb * BK, a_row);
+          tma_load_2d(sB + stage * S::kBBytes, &tma_b, &full_bar[stage], kb * BK, b_row);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -246,7 +257,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
           for (int i = 0; i < 16; ++i) { r[i] = r16[i]; r[i + 16] = 0; }
         }
         tmem_ld_wait();
-        const int n0 = n_idx * BN + c0;
+        const int n0 = (grouped ? p.g_tile_row0[n_idx] : n_idx * BN) + c0;
         if (!p.transposed) {
           if (m < p.M) {
             if (wsp) {
@@ -296,7 +307,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
           } else {
             // pair exchange: even lanes store (m, m+1) of column c, odd lanes of column c+1,
             // so every store is one bf16x2 and 16 lanes cover 64 contiguous bytes
-            const float bias_m = (p.bias && m < p.M) ? __bfloat162float(p.bias[m]) : 0.f;
+            const float bias_m = (p.bias && m < p.M)
+                                     ? __bfloat162float(p.bias[grouped ? p.g_tile_expert[n_idx] * p.g_rows + m : m])
+                                     : 0.f;
             const bool odd = lane & 1;
 #pragma unroll
             for (int c = 0; c < CH; c += 2) {
@@ -525,6 +538,51 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
                                                          a.out);
     cuda_check(cudaGetLastError(), "splitk_reduce_kernel launch");
     return 2;
+  }
+  return 1;
+}
+
+// Grouped swap-AB linear over a device-built tile list (mixture of experts):
+//   y[row, :] = w_stack[expert(row)] * xp[row, :] (+ bias_stack[expert(row)])
+// for the permuted, per-expert padded rows of xp. `bn` is the token-tile width the tile list was
+// built for; `max_tiles` bounds the list (the real count is read on the device).
+int moe_grouped_linear_bf16(const void* xp, long long ldx, const void* w_stack, long long ldw,
+                            const void* bias_stack, void* y, long long ldy, int rows_cap, int n_out, int K,
+                            int experts, const int* tile_expert, const int* tile_row0, const int* num_tiles,
+                            int max_tiles, int bn, int* status, cudaStream_t stream) {
+  if (rows_cap <= 0 || max_tiles <= 0) return 0;
+  if ((K & 7) || (n_out & 7) || (ldx & 7) || (ldw & 7) || (ldy & 1))
+    throw std::runtime_error("moe_grouped_linear_bf16: K, n_out and the row pitches must be multiples of 8");
+  GemmArgs a{};
+  a.K = K;
+  a.k_blocks = (K + BK - 1) / BK;
+  a.kb_per_split = a.k_blocks;
+  a.k_splits = 1;
+  a.out = reinterpret_cast<__nv_bfloat16*>(y);
+  a.ldc = ldy;
+  a.bias = reinterpret_cast<const __nv_bfloat16*>(bias_stack);
+  a.status = status;
+  a.M = n_out;
+  a.N = rows_cap;
+  a.transposed = 1;
+  a.m_tiles = (n_out + BM - 1) / BM;
+  a.n_tiles = max_tiles;
+  a.g_tile_expert = tile_expert;
+  a.g_tile_row0 = tile_row0;
+  a.g_num_tiles = num_tiles;
+  a.g_rows = n_out;
+  // When n_out is not a multiple of 128 the last feature tile of an expert also reads rows of the
+  // next expert's matrix (or zero fill past the stack); the epilogue never stores those rows.
+  CUtensorMap ta = make_tmap_2d(w_stack, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)experts * n_out, K,
+                                ldw * 2, BM, BK, true);
+  CUtensorMap tb = make_tmap_2d(xp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_cap, K, ldx * 2, bn, BK, true);
+  const int grid = min(max_tiles * a.m_tiles, sm_count() * (bn <= 64 ? 2 : 1));
+  switch (bn) {
+    case 16: launch_gemm<16>(ta, tb, a, grid, stream); break;
+    case 32: launch_gemm<32>(ta, tb, a, grid, stream); break;
+    case 64: launch_gemm<64>(ta, tb, a, grid, stream); break;
+    case 128: launch_gemm<128>(ta, tb, a, grid, stream); break;
+    default: throw std::runtime_error("moe_grouped_linear_bf16: token tile must be 16, 32, 64 or 128");
   }
   return 1;
 }

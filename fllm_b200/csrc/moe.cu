@@ -1,0 +1,205 @@
+// Mixture-of-experts routing and data movement around the grouped tcgen05 GEMM:
+//
+//   moe_route_kernel    one warp per token: top-k over the router logits, weights = softmax over
+//                       the selected logits (gpt-oss) or softmax over all experts renormalised
+//                       over the selection (Mixtral / Qwen-MoE);
+//   moe_align_kernel    one CTA: count rows per expert, lay the experts' row segments out back to
+//                       back, each padded to the token-tile width, and emit the tile list
+//                       (expert, first row) that the grouped GEMM walks; sizes stay on the device
+//                       so the whole layer can live in a CUDA graph;
+//   moe_gather_kernel   permuted activations xp[row] = x[token(row)] (zero rows for padding);
+//   moe_combine_kernel  out[token] = sum_j weight[token, j] * y[row(token, j)] in slot order, so
+//                       the result does not depend on scheduling.
+//
+// Reference counterparts: rust/engine/cuda/moe.cu:40-150 (moe_route2), :159-205 (moe_align),
+// :533-597 (combine2). The reference routes on the host inside a device group
+// (rust/engine/src/rust_decoder.rs:7621-7729); here nothing leaves the device.
+#include "fllm_ops.h"
+#include "ptx.cuh"
+#include "tma_host.h"
+
+namespace fllm {
+
+__global__ void moe_route_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, const __nv_bfloat16* __restrict__ bias,
+                                 int tokens, int experts, int k, int softmax_all, int* __restrict__ ids,
+                                 float* __restrict__ weights) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  constexpr int MAXPL = 8;                      // up to 256 experts
+  float v[MAXPL];
+#pragma unroll
+  for (int i = 0; i < MAXPL; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < experts ? __bfloat162float(logits[(size_t)t * ld + e]) + (bias ? __bfloat162float(bias[e]) : 0.f) : -INFINITY;
+  }
+  float denom_all = 0.f, vmax = -INFINITY;
+  if (softmax_all) {
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) vmax = fmaxf(vmax, v[i]);
+    vmax = warp_max(vmax);
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) denom_all += v[i] == -INFINITY ? 0.f : __expf(v[i] - vmax);
+    denom_all = warp_sum(denom_all);
+  }
+  float sel_v[8];
+  int sel_e[8];
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) {
+      const int e = lane + 32 * i;
+      if (v[i] > best || (v[i] == best && e < best_e)) { best = v[i]; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    sel_v[j] = best;
+    sel_e[j] = best_e;
+    if ((best_e & 31) == lane) v[best_e >> 5] = -INFINITY;    // remove the winner
+  }
+  if (lane == 0) {
+    float w[8], sum = 0.f;
+    for (int j = 0; j < k; ++j) {
+      w[j] = softmax_all ? __expf(sel_v[j] - vmax) / denom_all : __expf(sel_v[j] - sel_v[0]);
+      sum += w[j];
+    }
+    for (int j = 0; j < k; ++j) {
+      ids[(size_t)t * k + j] = sel_e[j];
+      weights[(size_t)t * k + j] = w[j] / sum;
+    }
+  }
+}
+
+void moe_route(const void* logits, long long ld, const void* bias, int tokens, int experts, int k, int softmax_all,
+               int* ids, float* weights, cudaStream_t s) {
+  if (tokens <= 0) return;
+  if (experts > 256 || k > 8) throw std::runtime_error("moe_route: at most 256 experts and top-8");
+  moe_route_kernel<<<(tokens + 3) / 4, 128, 0, s>>>((const __nv_bfloat16*)logits, ld, (const __nv_bfloat16*)bias,
+                                                     tokens, experts, k, softmax_all, ids, weights);
+  cuda_check(cudaGetLastError(), "moe_route_kernel");
+}
+
+// Single CTA. expert_lo/expert_hi select the experts this rank holds; entries routed elsewhere get
+// row -1. Outputs: row_of[tokens*k] (permuted row of each (token, slot) or -1), token_of[rows_cap]
+// (token of each permuted row, -1 = padding), tile_expert / tile_row0 / num_tiles, total_rows.
+__global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ ids, int entries, int experts,
+                                                         int expert_lo, int expert_hi, int bn, int k,
+                                                         int* __restrict__ row_of, int* __restrict__ token_of,
+                                                         int rows_cap, int* __restrict__ tile_expert,
+                                                         int* __restrict__ tile_row0, int* __restrict__ num_tiles,
+                                                         int max_tiles) {
+  __shared__ int cnt[256], off[257], fill[256];
+  for (int e = threadIdx.x; e < 256; e += blockDim.x) { cnt[e] = 0; fill[e] = 0; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= expert_lo && e < expert_hi) atomicAdd(&cnt[e - expert_lo], 1);
+  }
+  __syncthreads();
+  const int local = expert_hi - expert_lo;
+  if (threadIdx.x == 0) {
+    int o = 0, nt = 0;
+    for (int e = 0; e < local; ++e) {
+      off[e] = o;
+      const int padded = (cnt[e] + bn - 1) / bn * bn;
+      for (int r = 0; r < padded && nt < max_tiles; r += bn) {
+        tile_expert[nt] = e;
+        tile_row0[nt] = o + r;
+        ++nt;
+      }
+      o += padded;
+    }
+    off[local] = o;
+    num_tiles[0] = nt;
+    num_tiles[1] = o;                         // total permuted rows (incl. padding)
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < rows_cap; i += blockDim.x) token_of[i] = -1;
+  __syncthreads();
+  // deterministic placement: entries of an expert keep their (token, slot) order
+  for (int e = threadIdx.x; e < local; e += blockDim.x) {
+    int pos = off[e];
+    for (int i = 0; i < entries; ++i) {
+      if (ids[i] == e + expert_lo) {
+        row_of[i] = pos;
+        if (pos < rows_cap) token_of[pos] = i / k;
+        ++pos;
+      }
+    }
+  }
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+    const int e = ids[i];
+    if (e < expert_lo || e >= expert_hi) row_of[i] = -1;
+  }
+}
+
+void moe_align(const int* ids, int tokens, int k, int experts, int expert_lo, int expert_hi, int bn, int* row_of,
+               int* token_of, int rows_cap, int* tile_expert, int* tile_row0, int* num_tiles, int max_tiles,
+               cudaStream_t s) {
+  if (expert_hi - expert_lo > 256) throw std::runtime_error("moe_align: at most 256 local experts");
+  moe_align_kernel<<<1, 1024, 0, s>>>(ids, tokens * k, experts, expert_lo, expert_hi, bn, k, row_of, token_of,
+                                      rows_cap, tile_expert, tile_row0, num_tiles, max_tiles);
+  cuda_check(cudaGetLastError(), "moe_align_kernel");
+}
+
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ token_of,
+                                  __nv_bfloat16* __restrict__ xp, int hidden) {
+  const int row = blockIdx.x;
+  const int t = token_of[row];
+  uint4* dst = reinterpret_cast<uint4*>(xp + (size_t)row * hidden);
+  if (t < 0) {
+    for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * ldx);
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+void moe_gather(const void* x, long long ldx, const int* token_of, void* xp, int rows_cap, int hidden, cudaStream_t s) {
+  if (rows_cap <= 0) return;
+  moe_gather_kernel<<<rows_cap, 128, 0, s>>>((const __nv_bfloat16*)x, ldx, token_of, (__nv_bfloat16*)xp, hidden);
+  cuda_check(cudaGetLastError(), "moe_gather_kernel");
+}
+
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, long long ldy, const int* __restrict__ row_of,
+                                   const float* __restrict__ weights, int k, __nv_bfloat16* __restrict__ out,
+                                   long long ldo, int hidden) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < k; ++j) {
+      const int row = row_of[(size_t)t * k + j];
+      if (row < 0) continue;                                  // expert lives on another rank
+      const float w = weights[(size_t)t * k + j];
+      const uint4 v = reinterpret_cast<const uint4*>(y + (size_t)row * ldy)[i];
+      const uint32_t* vw = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = unpack_bf16x2(vw[q]);
+        acc[2 * q] += w * f.x;
+        acc[2 * q + 1] += w * f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out + (size_t)t * ldo)[i] = o;
+  }
+}
+
+void moe_combine(const void* y, long long ldy, const int* row_of, const float* weights, int tokens, int k, void* out,
+                 long long ldo, int hidden, cudaStream_t s) {
+  if (tokens <= 0) return;
+  moe_combine_kernel<<<tokens, 128, 0, s>>>((const __nv_bfloat16*)y, ldy, row_of, weights, k, (__nv_bfloat16*)out, ldo,
+                                            hidden);
+  cuda_check(cudaGetLastError(), "moe_combine_kernel");
+}
+
+}  // namespace fllm

@@ -1,0 +1,107 @@
+"""Mixture-of-experts feed-forward: router top-k, expert FFNs, weighted combine.
+
+``moe_reference`` is the fp32 PyTorch oracle. ``moe_ffn`` is what the decoder calls: on a GPU it
+runs route -> align -> gather -> grouped tcgen05 GEMM (gate/up) -> GLU -> grouped GEMM (down) ->
+combine, all sizes staying on the device. Under tensor parallelism each rank holds either a
+column slice of every expert (expert-TP) or a contiguous range of whole experts (expert
+parallel, rust/engine/src/parallel/decoder_shard.rs:165-211); in both cases the rank's output is
+a partial sum that the caller reduces like a dense FFN output.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+
+def _act(cfg, gu: torch.Tensor) -> torch.Tensor:
+    if cfg.act == "swiglu_oai":
+        g, u = gu[..., 0::2], gu[..., 1::2]
+        g = g.clamp(max=cfg.swiglu_limit)
+        u = u.clamp(min=-cfg.swiglu_limit, max=cfg.swiglu_limit)
+        return g * torch.sigmoid(cfg.swiglu_alpha * g) * (u + 1)
+    I = gu.shape[-1] // 2
+    g, u = gu[..., :I], gu[..., I:]
+    return (F.silu(g) if cfg.act == "swiglu" else F.gelu(g, approximate="tanh")) * u
+
+
+def route_reference(cfg, logits: torch.Tensor):
+    """Top-k ids [T, k] and weights [T, k] (fp32)."""
+    k = cfg.experts_per_token
+    lf = logits.float()
+    vals, ids = torch.topk(lf, k, dim=-1)
+    if cfg.router_kind == "softmax_topk":
+        w = torch.softmax(vals, -1)
+    else:
+        p = torch.softmax(lf, -1).gather(-1, ids)
+        w = p / p.sum(-1, keepdim=True)
+    return ids.int(), w
+
+
+def moe_reference(cfg, lw, h: torch.Tensor, expert_lo: int = 0, round_bf16: bool = True) -> torch.Tensor:
+    """fp32 math on the experts stored in `lw` (global ids expert_lo .. expert_lo + E_local)."""
+    r = (lambda t: t.to(torch.bfloat16).float()) if round_bf16 else (lambda t: t)
+    hf = h.float()
+    logits = hf @ lw.router_w.float().t()
+    if lw.router_b is not None:
+        logits = logits + lw.router_b.float()
+    ids, w = route_reference(cfg, r(logits))
+    out = torch.zeros(h.shape[0], lw.exp_down.shape[1], dtype=torch.float32, device=h.device)
+    e_local = lw.exp_gate_up.shape[0]
+    for e in range(e_local):
+        sel = (ids == e + expert_lo)
+        tok = sel.any(-1).nonzero().flatten()
+        if tok.numel() == 0:
+            continue
+        gu = hf[tok] @ lw.exp_gate_up[e].float().t()
+        if lw.exp_gate_up_b is not None:
+            gu = gu + lw.exp_gate_up_b[e].float()
+        a = r(_act(cfg, r(gu)))
+        y = a @ lw.exp_down[e].float().t()
+        if lw.exp_down_b is not None:
+            y = y + lw.exp_down_b[e].float()
+        wt = (w * sel.float()).sum(-1)[tok]
+        out[tok] += r(y) * wt[:, None]
+    return out
+
+
+def _token_tile(rows_per_expert: float) -> int:
+    for bn in (16, 32, 64):
+        if rows_per_expert <= bn:
+            return bn
+    return 128
+
+
+def moe_ffn(dec, lw, h: torch.Tensor) -> torch.Tensor:
+    cfg, ops, sp = dec.cfg, dec.ops, dec.spec
+    lo = sp.expert_start if sp.expert_parallel else 0
+    if not hasattr(ops, "k") or not h.is_cuda:
+        return moe_reference(cfg, lw, h, lo).to(h.dtype)
+    k_ops = ops.k
+    T, H = h.shape
+    k = cfg.experts_per_token
+    e_local = lw.exp_gate_up.shape[0]
+    logits = ops.linear(h, lw.router_w, lw.router_b)
+    ids = torch.empty(T, k, dtype=torch.int32, device=h.device)
+    wts = torch.empty(T, k, dtype=torch.float32, device=h.device)
+    k_ops.moe_route(logits, None, k, cfg.router_kind != "softmax_topk", ids, wts)
+    share = e_local / cfg.num_experts
+    bn = _token_tile(T * k * share / max(e_local, 1))
+    rows_cap = -(-(T * k + e_local * (bn - 1)) // bn) * bn
+    max_tiles = rows_cap // bn
+    i32 = dict(dtype=torch.int32, device=h.device)
+    row_of = torch.empty(T, k, **i32)
+    token_of = torch.empty(rows_cap, **i32)
+    tile_e, tile_r = torch.empty(max_tiles, **i32), torch.empty(max_tiles, **i32)
+    ntiles = torch.zeros(2, **i32)
+    k_ops.moe_align(ids, cfg.num_experts, lo, lo + e_local, bn, row_of, token_of, tile_e, tile_r, ntiles)
+    xp = torch.empty(rows_cap, H, dtype=h.dtype, device=h.device)
+    k_ops.moe_gather(h, token_of, xp)
+    gu = torch.empty(rows_cap, lw.exp_gate_up.shape[1], dtype=h.dtype, device=h.device)
+    k_ops.moe_grouped_linear(xp, lw.exp_gate_up, lw.exp_gate_up_b, gu, tile_e, tile_r, ntiles, bn, ops.status)
+    act = ops.glu(gu, dec.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit)
+    y = torch.empty(rows_cap, H, dtype=h.dtype, device=h.device)
+    k_ops.moe_grouped_linear(act, lw.exp_down, lw.exp_down_b, y, tile_e, tile_r, ntiles, bn, ops.status)
+    out = torch.empty(T, H, dtype=h.dtype, device=h.device)
+    k_ops.moe_combine(y, row_of, wts, out)
+    ops.launches += 6
+    return out

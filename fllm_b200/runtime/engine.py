@@ -41,6 +41,8 @@ class EngineStats:
         self.schedule_ns = 0
         self.forward_calls = 0
         self.kernel_launches = 0
+        self.spec_proposed = 0
+        self.spec_accepted = 0
 
 
 class LLMEngine:
@@ -76,6 +78,12 @@ class LLMEngine:
         self._seq_ids = itertools.count()
         self._req_ids = itertools.count()
         self.stats = EngineStats()
+        self.proposer = None                 # speculative drafts: NgramProposer / DraftModelProposer
+        self.adaptive = None
+        if self.cfg.speculative == "ngram":
+            from .speculative import AdaptiveDraft, NgramProposer
+            self.proposer = NgramProposer(self.cfg.draft_tokens)
+            self.adaptive = AdaptiveDraft(self.cfg.draft_tokens)
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self._graph_pool = None
         # staging: [ids | positions | slots | row_seq | logit_rows | block tables]
@@ -227,9 +235,42 @@ class LLMEngine:
         return g.tokens, g.logits, batch
 
     # ------------------------------------------------------------------ step
+    def enable_draft_model(self, draft_cfg, weights=None, k: Optional[int] = None, seed: int = 1) -> None:
+        """Speculate with a small decoder (rust/engine/src/runtime.rs:1568 ``enable_draft``)."""
+        from .speculative import AdaptiveDraft, DraftModelProposer
+        if draft_cfg.vocab_size != self.model_cfg.vocab_size:
+            raise ValueError("draft and target must share the vocabulary")
+        self.proposer = DraftModelProposer(self, draft_cfg, k or self.cfg.draft_tokens, seed, weights)
+        self.adaptive = AdaptiveDraft(k or self.cfg.draft_tokens)
+
+    def _propose_drafts(self) -> None:
+        cands = [r for r in self.scheduler.running
+                 if r.is_decode and not r.draft and r.params.greedy and r.params.speculative
+                 and not r.params.needs_full_sampler]
+        if not cands:
+            return
+        k = self.adaptive.length() if self.adaptive else self.cfg.draft_tokens
+        ok = []
+        for r in cands:
+            room = min(k, r.params.max_tokens - len(r.output) - 1, self.cfg.max_model_len - r.num_tokens - 1)
+            if room >= 1 and self.blocks.ensure_capacity(r.seq_id, r.num_tokens + room):
+                ok.append((r, room))
+        if not ok:
+            return
+        if hasattr(self.proposer, "propose_batch"):
+            kk = min(room for _, room in ok)
+            drafts = self.proposer.propose_batch([r for r, _ in ok], kk)
+            for r, _ in ok:
+                r.draft = drafts.get(r.seq_id, [])[:kk]
+        else:
+            for r, room in ok:
+                r.draft = self.proposer.propose(r.all_tokens, room)[:room]
+
     @torch.inference_mode()
     def step(self) -> List[TokenEvent]:
         t0 = time.perf_counter_ns()
+        if self.proposer is not None:
+            self._propose_drafts()
         step = self.scheduler.schedule()
         self.stats.schedule_ns += time.perf_counter_ns() - t0
         events: List[TokenEvent] = []
@@ -289,6 +330,10 @@ class LLMEngine:
                 while acc < s.verify and r.draft[acc] == target[acc]:
                     acc += 1
                 new = r.draft[:acc] + [target[acc]]
+                if self.adaptive is not None:
+                    self.adaptive.update(s.verify, acc)
+                self.stats.spec_proposed += s.verify
+                self.stats.spec_accepted += acc
                 self.scheduler.commit(s, new, accepted_drafts=acc)
             else:
                 new = [toks[row]]
@@ -306,6 +351,8 @@ class LLMEngine:
             if reason:
                 # drop tokens generated past a stop inside a multi-token (speculative) commit
                 self.scheduler.finish(r, reason)
+                if hasattr(self.proposer, "forget"):
+                    self.proposer.forget(r.seq_id)
                 self.requests.pop(r.request_id, None)
             if self.tp_rank == 0:
                 events.append(TokenEvent(r.request_id, new, bool(reason), reason))

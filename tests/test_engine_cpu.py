@@ -87,3 +87,44 @@ def test_stop_and_max_tokens():
     stop_tok = full[3]
     cut = eng.generate(p, SamplingParams(max_tokens=8, stop_token_ids=(stop_tok,)))[0]
     assert cut == full[: full.index(stop_tok) + 1]
+
+
+def test_gpt_oss_moe_model_matches_oracle():
+    """Sinks, alternating sliding window, biased experts, clamped SwiGLU, top-4 softmax router."""
+    cfg = preset("gpt-oss-tiny")
+    eng = _engine(cfg)
+    prompts = _prompts(cfg.vocab_size, (9, 150))
+    outs = eng.generate(prompts, SamplingParams(max_tokens=4))
+    for p, o in zip(prompts, outs):
+        assert o == greedy_generate(cfg, eng.weights, p, 4)
+
+
+def test_speculative_ngram_and_draft_model_keep_greedy_output():
+    """Speculation must not change greedy text; a draft equal to the target accepts everything."""
+    from fllm_b200.runtime.speculative import AdaptiveDraft, NgramProposer
+    cfg = preset("qwen3-tiny")
+    w = init_random_weights(cfg, "cpu")
+    prompts = _prompts(cfg.vocab_size, (12, 40))
+    prompts[0] = prompts[0][:6] * 4                      # repetition gives the n-gram lookup something to find
+    sp = SamplingParams(max_tokens=14)
+    base = LLMEngine(cfg, EngineConfig(max_num_batched_tokens=64, max_model_len=256, num_kv_blocks=96), device="cpu", weights=w)
+    want = base.generate(prompts, sp)
+    ng = LLMEngine(cfg, EngineConfig(max_num_batched_tokens=64, max_model_len=256, num_kv_blocks=96, speculative="ngram"),
+                   device="cpu", weights=w)
+    assert ng.generate(prompts, sp) == want
+    dm = LLMEngine(cfg, EngineConfig(max_num_batched_tokens=64, max_model_len=256, num_kv_blocks=96), device="cpu", weights=w)
+    dm.enable_draft_model(cfg, weights=w, k=3)           # draft == target: every draft is accepted
+    assert dm.generate(prompts, sp) == want
+    assert dm.stats.spec_proposed > 0 and dm.stats.spec_accepted == dm.stats.spec_proposed
+    assert dm.stats.steps < base.stats.steps
+    other = LLMEngine(cfg, EngineConfig(max_num_batched_tokens=64, max_model_len=256, num_kv_blocks=96), device="cpu", weights=w)
+    other.enable_draft_model(cfg, k=4, seed=99)          # unrelated draft: mostly rejected, text unchanged
+    assert other.generate(prompts, sp) == want
+    assert NgramProposer(3).propose([1, 2, 3, 9, 1, 2, 3]) == [9, 1, 2]
+    a = AdaptiveDraft(6)
+    for _ in range(20):
+        a.update(4, 0)
+    assert a.length() == 1
+    for _ in range(40):
+        a.update(4, 4)
+    assert a.length() == 6

@@ -75,3 +75,24 @@ def test_sampled_generation_is_seeded():
     b = eng.generate(p, sp)
     c = eng.generate(p, SamplingParams(max_tokens=10, temperature=0.9, top_p=0.95, top_k=40, seed=8))
     assert a == b and a != c
+
+
+def test_gpt_oss_tiny_logits_match_oracle():
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    from oracle import dense_forward
+    cfg = preset("gpt-oss-tiny")
+    ec = EngineConfig(max_num_seqs=8, max_num_batched_tokens=64, max_model_len=256, num_kv_blocks=64)
+    eng = LLMEngine(cfg, ec, device="cuda:0")
+    p = _prompts(cfg.vocab_size, (150,))[0]
+    eng.add_request(p, SamplingParams(max_tokens=1))
+    logits = None
+    while eng.has_unfinished():
+        step = eng.scheduler.schedule()
+        batch = eng._build_batch(step)
+        logits = eng.decoder.forward(batch)
+        eng._commit(step, eng.decoder.greedy_tokens(logits).tolist())
+    want = dense_forward(cfg, eng.weights, p)[-1]
+    err = (logits[-1].float() - want).abs().max().item()
+    assert err < 0.06 * want.abs().max().item() + 1e-3, err
+    assert eng.ops.check_status() == 0

@@ -296,3 +296,30 @@ def test_fused_tp_allreduce_single_device_emulation():
     assert ranks[0].check_status() == 2
     y = torch.ones(8, device="cuda") * 2  # the CUDA context still works
     assert float(y.sum()) == 16.0
+
+
+@pytest.mark.parametrize("T,E,k,H,I,act", [(5, 8, 4, 256, 256, "swiglu_oai"), (64, 32, 4, 512, 384, "swiglu"),
+                                            (300, 16, 2, 256, 128, "swiglu"), (33, 128, 4, 384, 192, "swiglu_oai")])
+@pytest.mark.parametrize("lo_frac", [0.0, 0.5])
+def test_moe_native_matches_reference(ops, T, E, k, H, I, act, lo_frac):
+    """Device MoE (route, align, gather, grouped tcgen05 GEMMs, combine) against the fp32 oracle,
+    for all experts local and for the upper half of the experts only (expert parallel shard)."""
+    from types import SimpleNamespace
+    from fllm_b200.config import ModelConfig
+    from fllm_b200.models.moe import moe_ffn, moe_reference
+    from fllm_b200.models.weights import LayerWeights
+    cfg = ModelConfig(hidden_size=H, num_experts=E, experts_per_token=k, moe_intermediate_size=I, act=act,
+                      expert_bias=True)
+    lo = int(E * lo_frac)
+    el = E - lo
+    lw = LayerWeights(attn_norm=None, wqkv=None, wo=None, ffn_norm=None)
+    lw.router_w, lw.router_b = _rand((E, H), 1, 0.2), _rand((E,), 2, 0.1)
+    lw.exp_gate_up, lw.exp_gate_up_b = _rand((el, 2 * I, H), 3, 0.05), _rand((el, 2 * I), 4, 0.1)
+    lw.exp_down, lw.exp_down_b = _rand((el, H, I), 5, 0.05), _rand((el, H), 6, 0.1)
+    h = _rand((T, H), 7)
+    dec = SimpleNamespace(cfg=cfg, ops=ops, act_kind={"swiglu": 0, "swiglu_oai": 2}[act],
+                          spec=SimpleNamespace(expert_parallel=lo > 0, expert_start=lo))
+    got = moe_ffn(dec, lw, h)
+    want = moe_reference(cfg, lw, h, lo)
+    _close(got, want, 3e-2)
+    assert ops.check_status() == 0
