@@ -49,7 +49,7 @@ class LLMEngine:
     def __init__(self, model_cfg: ModelConfig, engine_cfg: Optional[EngineConfig] = None,
                  parallel: Optional[ParallelConfig] = None, device="cuda", weights: Optional[DecoderWeights] = None,
                  tp_group=None, tp_rank: int = 0, seed: int = 0, eos_token_id: Optional[int] = None,
-                 ops=None):
+                 ops=None, pp_group=None, stage: int = 0):
         self.model_cfg = model_cfg
         self.cfg = engine_cfg or EngineConfig()
         self.par = parallel or ParallelConfig()
@@ -61,15 +61,22 @@ class LLMEngine:
         self.tp_group, self.tp_rank = tp_group, tp_rank
         tp = self.par.tp
         self.spec = make_shard_spec(model_cfg, tp, tp_rank, self.par.expert_parallel)
+        # pipeline stage: contiguous layer range, embedding on the first stage, head on the last
+        self.pp_group, self.stage = pp_group, stage
+        self.first_stage, self.last_stage = stage == 0, stage == self.par.pp - 1
+        self.layer_range = self.par.stage_layers(model_cfg.num_layers, stage)
         self.weights = weights or init_random_weights(
-            model_cfg, self.device, torch.bfloat16, seed, tp, tp_rank, self.par.expert_parallel)
+            model_cfg, self.device, torch.bfloat16, seed, tp, tp_rank, self.par.expert_parallel,
+            layers=self.layer_range, first_stage=self.first_stage, last_stage=self.last_stage)
         self.eos_token_id = eos_token_id
         self.block_size = self.cfg.block_size
         self.max_blocks_per_seq = -(-self.cfg.max_model_len // self.block_size)
         num_blocks = self.cfg.num_kv_blocks or self._size_kv_pool()
-        self.kv = KVCache(model_cfg.num_layers, num_blocks, self.spec.hkv_local, self.block_size,
+        self.kv = KVCache(len(self.layer_range), num_blocks, self.spec.hkv_local, self.block_size,
                           model_cfg.head_dim, self.device)
-        self.decoder = Decoder(model_cfg, self.weights, self.kv, self.ops, self.spec, tp_group)
+        self.decoder = Decoder(model_cfg, self.weights, self.kv, self.ops, self.spec, tp_group,
+                               layer_range=self.layer_range, first_stage=self.first_stage,
+                               last_stage=self.last_stage)
         self.blocks = BlockManager(num_blocks, self.block_size, self.cfg.enable_prefix_caching,
                                    self.cfg.watermark)
         window = model_cfg.sliding_window if (model_cfg.sliding_window and model_cfg.window_pattern is None) else 0
@@ -89,15 +96,18 @@ class LLMEngine:
         # staging: [ids | positions | slots | row_seq | logit_rows | block tables]
         max_rows = max(self.cfg.max_num_seqs, self._bucket_for(self.cfg.max_num_seqs))
         cap = 5 * max(self.cfg.max_num_batched_tokens, max_rows) + max_rows * (self.max_blocks_per_seq + 2) + 64
-        self._host = torch.empty(cap, dtype=torch.int32, pin_memory=self.is_cuda)
-        self._host_np = self._host.numpy()
-        self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        # one staging pair per pipeline micro-batch in flight (slot 0 is the only one without PP)
+        self._stage_bufs = []
+        for _ in range(max(1, self.par.pp)):
+            hbuf = torch.empty(cap, dtype=torch.int32, pin_memory=self.is_cuda)
+            self._stage_bufs.append((hbuf, hbuf.numpy(), torch.empty(cap, dtype=torch.int32, device=self.device)))
+        self._host, self._host_np, self._dev = self._stage_bufs[0]
         self._out_host = torch.empty(self.cfg.max_num_batched_tokens + 64, dtype=torch.int32,
                                      pin_memory=self.is_cuda)
 
     # ------------------------------------------------------------------ sizing
     def _size_kv_pool(self) -> int:
-        per_block = KVCache.bytes_per_block(self.model_cfg.num_layers, self.spec.hkv_local,
+        per_block = KVCache.bytes_per_block(len(self.layer_range), self.spec.hkv_local,
                                             self.block_size, self.model_cfg.head_dim)
         if self.is_cuda:
             free, total = torch.cuda.mem_get_info(self.device)
@@ -133,14 +143,14 @@ class LLMEngine:
         return self.scheduler.has_work()
 
     # ------------------------------------------------------------------ batch building
-    def _build_batch(self, step: ScheduledStep, pad_to: int = 0) -> StepBatch:
+    def _build_batch(self, step: ScheduledStep, pad_to: int = 0, slot: int = 0) -> StepBatch:
         seqs = step.seqs
         T = step.num_tokens
         B = len(seqs)
         Tp = max(T, pad_to)
         Bp = max(B, pad_to) if pad_to else B
         bs = self.block_size
-        h = self._host_np
+        host_t, h, dev = self._stage_bufs[slot]
         ids = h[0:Tp]
         pos = h[Tp:2 * Tp]
         slots = h[2 * Tp:3 * Tp]
@@ -200,11 +210,10 @@ class LLMEngine:
         R = len(rows)
         lrow[:R] = rows
         used = o_tab + Bp * max_blocks
-        dev = self._dev
         if self.is_cuda:
-            dev[:used].copy_(self._host[:used], non_blocking=True)
+            dev[:used].copy_(host_t[:used], non_blocking=True)
         else:
-            dev[:used] = self._host[:used]
+            dev[:used] = host_t[:used]
         self.stats.h2d_bytes += used * 4
         return StepBatch(
             token_ids=dev[0:Tp], positions=dev[Tp:2 * Tp], slots=dev[2 * Tp:3 * Tp],
@@ -281,20 +290,22 @@ class LLMEngine:
             return events
         for src, dst in step.cow:
             self.kv.store[:, :, dst].copy_(self.kv.store[:, :, src])
-        use_graph = (self.is_cuda and self.cfg.use_cuda_graphs and step.all_decode
+        use_graph = (self.is_cuda and self.cfg.use_cuda_graphs and step.all_decode and self.par.pp == 1
                      and not any(s.verify for s in step.seqs)
                      and self._bucket_for(len(step.seqs)) > 0)
         l0 = getattr(self.ops, "launches", 0)
         if use_graph:
             tokens_dev, logits, batch = self._decode_with_graph(step)
             self.stats.kernel_launches += self._graphs[self._bucket_for(len(step.seqs))].launches
+        elif self.par.pp > 1:
+            tokens_dev = self._pipeline_forward(step)
         else:
             batch = self._build_batch(step)
             logits = self.decoder.forward(batch)
             tokens_dev = self.decoder.greedy_tokens(logits)
         self.stats.forward_calls += 1
         needs_sampler = any(s.wants_logits and s.req.params.needs_full_sampler for s in step.seqs)
-        if needs_sampler:
+        if needs_sampler and self.par.pp == 1:
             tokens_dev = self._sample(step, logits, tokens_dev)
         n_rows = tokens_dev.shape[0]
         out = self._out_host[:n_rows]
@@ -307,6 +318,50 @@ class LLMEngine:
         events.extend(self._commit(step, toks))
         self.stats.steps += 1
         return events
+
+    def _pipeline_forward(self, step: ScheduledStep) -> torch.Tensor:
+        """One step over pipeline stages. The step is cut into micro-batches by sequence
+        (rust/engine/src/parallel/decoder_shard.rs:313-341); every stage runs them in order, so
+        stage s works on micro-batch i while stage s+1 works on i-1. The hand-over is the bf16
+        residual stream [rows, hidden] sent device to device with the library's p2p (the reference
+        copies it through host memory, rust/engine/src/rust_decoder.rs:5900-5911). The last stage
+        samples; the ids are broadcast so that every rank commits the same tokens."""
+        from .scheduler import ScheduledStep as _Step
+        pp, g = self.par.pp, self.pp_group
+        n_mb = min(self.par.pipeline_microbatches or pp, len(step.seqs))
+        per = -(-len(step.seqs) // n_mb)
+        chunks = [step.seqs[i:i + per] for i in range(0, len(step.seqs), per)]
+        subs = [_Step(seqs=c) for c in chunks]
+        batches = [self._build_batch(sub, slot=i % len(self._stage_bufs)) if i < len(self._stage_bufs) else None
+                   for i, sub in enumerate(subs)]
+        H = self.model_cfg.hidden_size
+        toks, pending = [], []
+        for i, sub in enumerate(subs):
+            b = batches[i] if batches[i] is not None else self._build_batch(sub, slot=i % len(self._stage_bufs))
+            x_in = None
+            if not self.first_stage:
+                x_in = torch.empty(sub.num_tokens, H, dtype=torch.bfloat16, device=self.device)
+                g.recv(x_in, self.stage - 1)
+            x, delta = self.decoder.forward_hidden(b, hidden_in=x_in)
+            if not self.last_stage:
+                out = (x.float() + delta.float()).to(x.dtype) if delta is not None else x
+                pending.append((g.isend(out, self.stage + 1), out))
+            else:
+                lg = self.decoder.logits(x, delta, b)
+                t = self.decoder.greedy_tokens(lg)
+                if any(s.wants_logits and s.req.params.needs_full_sampler for s in sub.seqs):
+                    t = self._sample(sub, lg, t)
+                toks.append(t)
+        for w, _ in pending:
+            w.wait()
+        n_rows = sum(len(range(s.count)) if s.verify else 1 for s in step.seqs if s.wants_logits)
+        if self.last_stage:
+            out = torch.cat(toks) if toks else torch.empty(0, dtype=torch.int32, device=self.device)
+        else:
+            out = torch.empty(n_rows, dtype=torch.int32, device=self.device)
+        if n_rows:
+            g.broadcast(out, src=pp - 1)
+        return out
 
     def _sample(self, step: ScheduledStep, logits: torch.Tensor, greedy: torch.Tensor) -> torch.Tensor:
         from .sampler import sample_step

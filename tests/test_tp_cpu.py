@@ -52,3 +52,13 @@ def test_tp_matches_single_device_on_cpu(world, model):
     # sequence; the logits themselves must agree closely
     assert res["logit_err"] < 2e-2, res
     assert res["agree"] >= 0.8 * res["total"], res
+
+
+@pytest.mark.parametrize("world,pp", [(2, 2), (3, 3), (4, 2)])
+def test_pipeline_and_tp_x_pp_match_single_device_on_cpu(world, pp):
+    """Pipeline stages hand the residual stream over with send/recv; 4 ranks = TP2 x PP2."""
+    res = run_ranks(world, ["cpu", "gloo", "qwen3-tiny", str(pp)])
+    if world == pp:
+        assert res["agree"] == res["total"], res          # pure PP computes the same bits
+    else:
+        assert res["agree"] >= 0.8 * res["total"], res

@@ -17,6 +17,7 @@ from fllm_b200.runtime import LLMEngine, SamplingParams  # noqa: E402
 
 def main():
     device_kind, backend, model = sys.argv[1], sys.argv[2], sys.argv[3]
+    pp = int(sys.argv[4]) if len(sys.argv) > 4 else 1
     rank, world, local = init_distributed("gloo" if device_kind == "cpu" else "nccl", timeout_s=120)
     dev = torch.device("cpu") if device_kind == "cpu" else torch.device("cuda", local)
     cfg = preset(model)
@@ -29,16 +30,21 @@ def main():
     sp = SamplingParams(max_tokens=10)
     single = LLMEngine(cfg, ec, ParallelConfig(tp=1), device=dev, seed=3)
     want = single.generate(prompts, sp)
-    grp = Group()
+    from fllm_b200.comm import make_tp_pp_groups
+    tp = world // pp
+    grp, pp_grp, stage, tp_rank = make_tp_pp_groups(tp, pp)
     if backend == "fused":
-        tp_rt = make_tp_runtime(world, rank, dev, backend="fused", group=grp, hidden=cfg.hidden_size,
+        tp_rt = make_tp_runtime(tp, tp_rank, dev, backend="fused", group=grp, hidden=cfg.hidden_size,
                                 max_tokens=ec.max_num_batched_tokens)
     else:
         tp_rt = LibraryTP(grp)
-    eng = LLMEngine(cfg, ec, ParallelConfig(tp=world), device=dev, tp_group=tp_rt, tp_rank=rank, seed=3)
+    eng = LLMEngine(cfg, ec, ParallelConfig(tp=tp, pp=pp), device=dev, tp_group=tp_rt, tp_rank=tp_rank, seed=3,
+                    pp_group=pp_grp, stage=stage)
     got = eng.generate(prompts, sp)
 
     def last_logits(e):
+        if pp > 1:
+            return torch.zeros(1)
         e.add_request(prompts[3][:40], SamplingParams(max_tokens=1))
         step = e.scheduler.schedule()
         batch = e._build_batch(step)
@@ -57,7 +63,8 @@ def main():
         total = sum(len(o) for o in want)
         print(json.dumps({"backend": getattr(tp_rt, "backend", "?"), "world": world, "agree": agree, "total": total,
                           "status": status, "graph_steps": eng.stats.graph_steps, "logit_err": logit_err}), flush=True)
-    grp.barrier()
+    if torch.distributed.is_initialized():
+        torch.distributed.barrier()
     if hasattr(tp_rt, "close"):
         tp_rt.close()
     torch.distributed.destroy_process_group()
