@@ -1,0 +1,42 @@
+// torch.ops.fllm_b200 bindings of the low-precision GEMMs (block-scaled FP8; FP4 formats).
+#include <ATen/ATen.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/library.h>
+
+#include "fllm_ops.h"
+
+namespace {
+using at::Tensor;
+using c10::optional;
+inline cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+// x bf16 [T, K] -> (xq uint8 [T, K] holding e4m3, sx fp32 [T, K/128])
+void quant_fp8_1x128(const Tensor& x, Tensor xq, Tensor sx) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "x: bf16 rows");
+  TORCH_CHECK(xq.is_contiguous() && xq.element_size() == 1 && xq.numel() == x.numel(), "xq: contiguous 1-byte [T, K]");
+  TORCH_CHECK(sx.is_contiguous() && sx.scalar_type() == at::kFloat && sx.numel() == x.size(0) * (x.size(1) / 128), "sx: [T, K/128]");
+  c10::cuda::CUDAGuard guard(x.device());
+  fllm::quant_fp8_1x128(x.data_ptr(), x.stride(0), xq.data_ptr(), sx.data_ptr<float>(), (int)x.size(0), (int)x.size(1), cur_stream());
+}
+
+int64_t linear_fp8_block(const Tensor& xq, const Tensor& sx, const Tensor& wq, const Tensor& sw, const optional<Tensor>& bias,
+                         Tensor y, const optional<Tensor>& status) {
+  TORCH_CHECK(xq.is_cuda() && xq.is_contiguous() && wq.is_contiguous() && xq.element_size() == 1 && wq.element_size() == 1, "xq, wq: contiguous e4m3 bytes");
+  TORCH_CHECK(xq.dim() == 2 && wq.dim() == 2 && xq.size(1) == wq.size(1), "K mismatch");
+  const int64_t T = xq.size(0), N = wq.size(0), K = xq.size(1);
+  TORCH_CHECK(sx.scalar_type() == at::kFloat && sx.is_contiguous() && sx.numel() == T * (K / 128), "sx: [T, K/128]");
+  TORCH_CHECK(sw.scalar_type() == at::kFloat && sw.is_contiguous() && sw.numel() == (N / 128) * (K / 128), "sw: [N/128, K/128]");
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.stride(1) == 1 && y.size(0) == T && y.size(1) == N, "y: [T, N] bf16");
+  c10::cuda::CUDAGuard guard(xq.device());
+  const void* b = bias.has_value() && bias->defined() ? bias->data_ptr() : nullptr;
+  int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  return fllm::linear_fp8_block(xq.data_ptr(), sx.data_ptr<float>(), wq.data_ptr(), sw.data_ptr<float>(), b, y.data_ptr(),
+                                y.stride(0), (int)T, (int)N, (int)K, st, cur_stream());
+}
+}  // namespace
+
+TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
+  m.def("quant_fp8_1x128(Tensor x, Tensor(a!) xq, Tensor(b!) sx) -> ()", &quant_fp8_1x128);
+  m.def("linear_fp8_block(Tensor xq, Tensor sx, Tensor wq, Tensor sw, Tensor? bias, Tensor(a!) y, Tensor? status) -> int", &linear_fp8_block);
+}

@@ -74,6 +74,11 @@ void symm_export(void* p, unsigned char out[64]);
 void* symm_import(const unsigned char in[64]);
 void symm_close(void* p);
 
+// ---- block-scaled FP8 ------------------------------------------------------------------
+void quant_fp8_1x128(const void* x, long long ldx, void* xq, float* sx, int tokens, int K, cudaStream_t s);
+int linear_fp8_block(const void* xq, const float* sx, const void* wq, const float* sw, const void* bias, void* y,
+                     long long ldy, int T, int N, int K, int* status, cudaStream_t stream);
+
 // ---- mixture of experts ---------------------------------------------------------------
 int moe_grouped_linear_bf16(const void* xp, long long ldx, const void* w_stack, long long ldw,
                             const void* bias_stack, void* y, long long ldy, int rows_cap, int n_out, int K,

@@ -112,3 +112,32 @@ def pack_sample_rows(rows) -> bytes:
     """rows: iterable of (temperature, top_p, min_p, repetition_penalty, presence_penalty,
     frequency_penalty, top_k, draw, seed)."""
     return b"".join(struct.pack(SAMPLE_ROW_FMT, *r) for r in rows)
+
+
+def quantize_weight_fp8_block(w: torch.Tensor, block: int = 128):
+    """bf16/fp32 [N, K] -> (e4m3 bytes [N, K] as uint8, fp32 scales [N/128, K/128]); amax / 448 per block."""
+    N, K = w.shape
+    wf = w.float().view(N // block, block, K // block, block)
+    amax = wf.abs().amax(dim=(1, 3)).clamp_min(1e-10)
+    scale = amax / 448.0
+    q = (wf / scale[:, None, :, None]).to(torch.float8_e4m3fn)
+    return q.view(N, K).view(torch.uint8).contiguous(), scale.contiguous()
+
+
+class Fp8BlockLinear:
+    """y = x W^T with W stored as block-scaled e4m3: activations are quantised per token per 128
+    values on the fly, the product runs on the FP8 tensor cores."""
+
+    def __init__(self, ops: NativeOps, wq: torch.Tensor, sw: torch.Tensor, bias=None):
+        self.ops, self.wq, self.sw, self.bias = ops, wq, sw, bias
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        T, K = x.shape
+        xq = torch.empty(T, K, dtype=torch.uint8, device=x.device)
+        sx = torch.empty(T, K // 128, dtype=torch.float32, device=x.device)
+        k = self.ops.k
+        k.quant_fp8_1x128(x, xq, sx)
+        y = torch.empty(T, self.wq.shape[0], dtype=torch.bfloat16, device=x.device)
+        k.linear_fp8_block(xq, sx, self.wq, self.sw, self.bias, y, self.ops.status)
+        self.ops.launches += 2
+        return y

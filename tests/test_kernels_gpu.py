@@ -323,3 +323,30 @@ def test_moe_native_matches_reference(ops, T, E, k, H, I, act, lo_frac):
     want = moe_reference(cfg, lw, h, lo)
     _close(got, want, 3e-2)
     assert ops.check_status() == 0
+
+
+@pytest.mark.parametrize("T", [1, 16, 33, 64, 100, 300, 2048])
+@pytest.mark.parametrize("N,K", [(256, 256), (1024, 4096), (3584, 8192)])
+def test_linear_fp8_block(ops, T, N, K):
+    """Block-scaled e4m3 GEMM against fp32 math on the de-quantised operands (so only the
+    accumulation order and the bf16 output rounding differ), and against the unquantised product
+    with the tolerance FP8 allows."""
+    from fllm_b200.ops.native import Fp8BlockLinear, quantize_weight_fp8_block
+    x = _rand((T, K), 1)
+    w = _rand((N, K), 2, 0.05)
+    wq, sw = quantize_weight_fp8_block(w)
+    lin = Fp8BlockLinear(ops, wq, sw)
+    y = lin(x)
+    # oracle on the same quantised values
+    xq = torch.empty(T, K, dtype=torch.uint8, device="cuda")
+    sx = torch.empty(T, K // 128, dtype=torch.float32, device="cuda")
+    ops.k.quant_fp8_1x128(x, xq, sx)
+    xd = xq.view(torch.float8_e4m3fn).float().view(T, K // 128, 128) * sx[:, :, None]
+    wd = wq.view(torch.float8_e4m3fn).float().view(N // 128, 128, K // 128, 128) * sw[:, None, :, None]
+    ref = xd.view(T, K) @ wd.view(N, K).t()
+    _close(y, ref, 1e-2)
+    _close(y, x.float() @ w.float().t(), 8e-2)
+    # the activation quantiser itself: amax / 448 scales, values within one e4m3 step
+    amax = x.float().view(T, K // 128, 128).abs().amax(-1).clamp_min(1e-10)
+    assert torch.allclose(sx, amax / 448.0, rtol=1e-6)
+    assert ops.check_status() == 0
