@@ -88,7 +88,7 @@ class FusedTP:
                                         self.ar_slot_bytes, self.status)
         self.ag_local = self.k.symm_view(ag[self.rank], self.max_tokens * self.hidden * 2,
                                          self.device.index or 0).view(torch.bfloat16).view(self.max_tokens, self.hidden)
-        self.workspace = torch.empty(64 << 20, dtype=torch.uint8, device=self.device)
+        self.workspace = torch.zeros(64 << 20, dtype=torch.uint8, device=self.device)
 
     @classmethod
     def local_group(cls, tp: int, hidden: int, max_tokens: int, device="cuda:0", ar_slot_bytes: int = 1 << 20):
@@ -122,7 +122,7 @@ class FusedTP:
 
     # ------------------------------------------------------------------ fused steps
     def linear_rs(self, x: torch.Tensor, w: torch.Tensor, bias=None) -> int:
-        return self.k.tp_linear_rs(self.ctx, x, w, bias)
+        return self.k.tp_linear_rs(self.ctx, x, w, bias, self.workspace)
 
     def norm(self, residual_shard: torch.Tensor, tokens: int, has_partials: bool, norm_w, eps, w_offset=0.0) -> None:
         self.k.tp_norm(self.ctx, residual_shard, tokens, has_partials, norm_w, float(eps), float(w_offset))
@@ -176,24 +176,18 @@ class FusedTP:
         dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group.pg)
         return bool(ok.item())
 
-    def close(self) -> None:
+    def close(self, release: bool = False) -> None:
+        """Quiesce. Peer mappings and buffers are left to process exit unless `release` is set:
+        un-mapping while a peer still tears down its own side gained nothing and cost a hang."""
         try:
             torch.cuda.synchronize(self.device)
         except Exception:
             pass
-        if self.group is not None and self.group.size > 1:
-            try:
-                self.group.barrier()
-            except Exception:
-                pass
+        if not release:
+            return
         for p in self._imported:
             self.k.symm_close(p)
         self._imported = []
-        if self.group is not None and self.group.size > 1:
-            try:
-                self.group.barrier()
-            except Exception:
-                pass
         for p in self._owned:
             self.k.symm_free(p)
         self._owned = []

@@ -90,7 +90,8 @@ int64_t tp_ctx_create(int64_t tp, int64_t rank, int64_t hidden, int64_t max_toke
 int64_t rows_per(const TpContext& c, int64_t tokens) { return (tokens + c.tp - 1) / c.tp; }
 
 // Row-parallel linear whose partial sums go straight to the owning ranks (no local output).
-int64_t tp_linear_rs(int64_t h, const Tensor& x, const Tensor& w, const optional<Tensor>& bias) {
+int64_t tp_linear_rs(int64_t h, const Tensor& x, const Tensor& w, const optional<Tensor>& bias,
+                     const optional<Tensor>& workspace) {
   TpContext& c = ctx_at(h);
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "x: bf16 rows");
   TORCH_CHECK(w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.stride(1) == 1 && w.size(0) == c.hidden, "w: [hidden, k]");
@@ -100,8 +101,11 @@ int64_t tp_linear_rs(int64_t h, const Tensor& x, const Tensor& w, const optional
   a.tp = c.tp; a.my_rank = c.rank; a.rows_per = (int)rows_per(c, x.size(0)); a.rs_ld = c.hidden;
   for (int i = 0; i < c.tp; ++i) { a.rs_bufs[i] = c.rs_bufs[i]; a.rs_flags[i] = c.flags[i] + kRsFlags; }
   const void* b = bias.has_value() && bias->defined() ? bias->data_ptr() : nullptr;
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  if (workspace.has_value() && workspace->defined()) { ws = workspace->data_ptr(); ws_bytes = workspace->nbytes(); }
   return fllm::linear_bf16_tp(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), b, nullptr, c.hidden,
-                              (int)x.size(0), (int)w.size(0), (int)x.size(1), nullptr, 0, c.status, 1, &a, cur_stream());
+                              (int)x.size(0), (int)w.size(0), (int)x.size(1), ws, ws_bytes, c.status, 0, &a, cur_stream());
 }
 
 // Column-parallel linear whose activation operand is the gathered buffer peers fill.
@@ -177,7 +181,7 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("symm_view(int ptr, int bytes, int device) -> Tensor", &symm_view);
   m.def("flag_words() -> int", &flag_words);
   m.def("tp_ctx_create(int tp, int rank, int hidden, int max_tokens, int device, int[] rs_bufs, int[] ag_bufs, int[] flag_bufs, int[] ar_slots, int ar_slot_bytes, Tensor status) -> int", &tp_ctx_create);
-  m.def("tp_linear_rs(int ctx, Tensor x, Tensor w, Tensor? bias) -> int", &tp_linear_rs);
+  m.def("tp_linear_rs(int ctx, Tensor x, Tensor w, Tensor? bias, Tensor? workspace) -> int", &tp_linear_rs);
   m.def("tp_linear_ag(int ctx, int tokens, Tensor w, Tensor? bias, Tensor(a!) y, Tensor? workspace) -> int", &tp_linear_ag);
   m.def("tp_norm(int ctx, Tensor(a!) residual_shard, int tokens, bool has_partials, Tensor norm_w, float eps, float w_offset) -> ()", &tp_norm);
   m.def("tp_allreduce(int ctx, Tensor input, Tensor(a!) output) -> ()", &tp_allreduce);

@@ -17,13 +17,16 @@
 //     elements, a CUDA stream). Nothing is allocated or freed: no cudaMalloc / cudaFree and
 //     no allocating library routine is called, on any path.
 //   * The scratch array is FLLM_NOALLOC_SCRATCH_BYTES (8 MiB) per device; every GPU on which
-//     the library is loaded holds it until the process exits. A call needs
-//     splits * tokens * features * 4 bytes of it; a call that needs more is rejected with
-//     FLLM_NOALLOC_E_TOO_LARGE and a message naming both numbers (nothing is launched).
+//     the library is loaded holds it until the process exits. A call needs 64 KiB (per-tile
+//     arrival counters) + splits * tokens' * features' * 4 bytes of it, where tokens' is tokens
+//     rounded up to 16 / 32 / 64 / a multiple of 128 and features' is features rounded up to a
+//     multiple of 128; a call that needs more is rejected with FLLM_NOALLOC_E_TOO_LARGE and a
+//     message naming both numbers (nothing is launched).
 //   * The first call on each device looks up the device address of the scratch array (with
 //     that device current). Make that first call outside any stream capture.
 //   * All calls on a device share the one array and it keeps whatever the previous call left
-//     there. Nothing has to start at zero: each call overwrites every partial it later reads.
+//     there. Only the arrival counters must be zero between calls, and every call leaves them at
+//     zero again; the partial sums need no clearing because each call overwrites all it reads.
 //     Two calls that overlap on the GPU (different streams, no ordering between them) would
 //     race on the array - order them on one stream or with events.
 //   * k, features and the leading dimensions must be multiples of 8; x, w, y 16-byte aligned.

@@ -15,7 +15,9 @@
 //                                           the 128-row MMA dimension is filled by
 //                                           output features and the few tokens sit
 //                                           in the N dimension)
-//   split-K     fp32 partial sums in a workspace, reduced by splitk_reduce_kernel.
+//   split-K     fp32 partial sums in a workspace: for a local output a second small kernel adds
+//               them; when the output leaves the GPU (reduce-scatter epilogue) the CTA that arrives
+//               last for a tile adds the partial tiles in split order and runs the epilogue itself.
 //
 // Role in the reference: dense F16/BF16 products go to cuBLASLt for >= 9 tokens
 // (rust/engine/cuda/cublaslt_gemm.cu:11-14) and to an mma.sync skinny kernel below
@@ -47,7 +49,10 @@ struct GemmArgs {
   int transposed;          // 0: out[m*ldc+n], 1: out[n*ldc+m]
   long long ldc;
   __nv_bfloat16* out;
-  float* ws;               // split-K partials, [k_splits][M*N] in output orientation (dense)
+  float* ws;               // split-K partials, [k_splits][tiles][BN][128] fp32 (tile-local, column-major)
+  unsigned int* tile_counters;   // one arrival counter per tile; zero between launches
+  int fixup;               // split-K: 1 = last-arriving CTA finishes the tile, 0 = dense partials + reduce kernel
+  int vec16;               // 1: output rows are 16-byte aligned (transposed stores use uint4)
   const __nv_bfloat16* bias;  // per output feature (n when row-major, m when transposed)
   int* status;
   // ---- tensor parallel (all null / zero on a single GPU) ----
@@ -87,7 +92,8 @@ struct GemmSmem {
   static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
   static constexpr int kTmemCols = (2 * BN) < 32 ? 32 : (2 * BN);
   static constexpr int kBarBytes = 256;
-  static constexpr int kTotal = kStages * kStageBytes + kBarBytes + 1024;  // +1024 alignment slack
+  static constexpr int kStageOutBytes = 4 * 32 * 32 * 2;   // per-epilogue-warp transpose tile
+  static constexpr int kTotal = kStages * kStageBytes + kBarBytes + kStageOutBytes + 1024;  // +1024 alignment slack
 };
 
 template <int BN>
@@ -108,6 +114,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
   uint64_t* tempty_bar = bars + 2 * STAGES + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  __nv_bfloat16* stage_out = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(bars) + S::kBarBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -236,7 +244,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
       tc_fence_after_sync();
       const int m = m_idx * BM + q * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-      float* wsp = p.k_splits > 1 ? p.ws + (size_t)split * p.M * p.N : nullptr;
       constexpr int CH = BN < 32 ? 16 : 32;
       // where the bf16 row of a token goes: the local output, or the owning rank's receive buffer
       const bool rs = p.rs_bufs[0] != nullptr;
@@ -245,8 +252,72 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
         const int owner = token / p.rows_per;
         return p.rs_bufs[owner] + ((size_t)p.my_rank * p.rows_per + (token - owner * p.rows_per)) * p.rs_ld;
       };
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += CH) {
+      const int n_base = grouped ? p.g_tile_row0[n_idx] : n_idx * BN;
+      const float bias_m = (p.transposed && p.bias && m < p.M)
+                               ? __bfloat162float(p.bias[grouped ? p.g_tile_expert[n_idx] * p.g_rows + m : m])
+                               : 0.f;
+      __nv_bfloat16* stg = stage_out + (warp - 2) * (32 * 32);
+      // final values of CH columns of this thread's row -> bias, bf16, memory
+      auto emit = [&](int c0, const float (&v)[32]) {
+        const int n0 = n_base + c0;
+        if (!p.transposed) {
+          if (m < p.M) {
+            __nv_bfloat16* dst = row_ptr(m) + n0;
+#pragma unroll
+            for (int c = 0; c < CH; c += 8) {
+              if (n0 + c < p.N) {
+                float o8[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o8[i] = v[c + i];
+                if (p.bias) {
+                  const uint4 bb = *reinterpret_cast<const uint4*>(p.bias + n0 + c);
+                  const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const float2 f = unpack_bf16x2(bw[i]);
+                    o8[2 * i] += f.x;
+                    o8[2 * i + 1] += f.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(o8[0], o8[1]);
+                o.y = pack_bf16x2(o8[2], o8[3]);
+                o.z = pack_bf16x2(o8[4], o8[5]);
+                o.w = pack_bf16x2(o8[6], o8[7]);
+                *reinterpret_cast<uint4*>(dst + c) = o;
+              }
+            }
+          }
+        } else {
+          // Transpose through a per-warp staging tile so that every store is 16 bytes: lanes hold
+          // features (rows of D), memory wants 8 consecutive features of one token per store. Four
+          // lanes then cover the 64 contiguous bytes a token gets from this warp, which matters
+          // most when the destination is a peer GPU.
+#pragma unroll
+          for (int c = 0; c < CH; ++c) stg[c * 32 + lane] = __float2bfloat16(v[c] + bias_m);
+          __syncwarp();
+          const int f0 = 8 * (lane & 3);
+          const int mm0 = m_idx * BM + q * 32 + f0;
+#pragma unroll
+          for (int rnd = 0; rnd < CH / 8; ++rnd) {
+            const int c = (lane >> 2) + 8 * rnd;
+            const int n = n0 + c;
+            if (n < p.N && mm0 < p.M) {
+              const uint4 val = *reinterpret_cast<const uint4*>(stg + c * 32 + f0);
+              __nv_bfloat16* dst = row_ptr(n) + mm0;
+              if (p.vec16) {
+                *reinterpret_cast<uint4*>(dst) = val;
+              } else {
+                const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) reinterpret_cast<uint32_t*>(dst)[i] = w4[i];
+              }
+            }
+          }
+          __syncwarp();
+        }
+      };
+      auto load_chunk = [&](int c0, float (&v)[32]) {
         uint32_t r[32];
         if constexpr (CH == 32) {
           tmem_ld_32x32(t_row + c0, r);
@@ -257,78 +328,101 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
           for (int i = 0; i < 16; ++i) { r[i] = r16[i]; r[i + 16] = 0; }
         }
         tmem_ld_wait();
-        const int n0 = (grouped ? p.g_tile_row0[n_idx] : n_idx * BN) + c0;
-        if (!p.transposed) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+      };
+      bool emitted = true;       // false for split-K CTAs that were not the last to arrive
+      if (p.k_splits == 1) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          float v[32];
+          load_chunk(c0, v);
+          emit(c0, v);
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&tempty_bar[acc]);
+      } else if (!p.fixup) {
+        // split-K, local output: dense fp32 partials [split][token][feature]; a second kernel adds them
+        float* wsp = p.ws + (size_t)split * p.M * p.N;
+        emitted = false;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          float v[32];
+          load_chunk(c0, v);
+          const int n0 = n_base + c0;
           if (m < p.M) {
-            if (wsp) {
-              float* dst = wsp + (size_t)m * p.N + n0;
+            if (!p.transposed) {
 #pragma unroll
-              for (int c = 0; c < CH; c += 4) {
+              for (int c = 0; c < CH; c += 4)
                 if (n0 + c < p.N)
-                  *reinterpret_cast<float4*>(dst + c) =
-                      make_float4(__uint_as_float(r[c]), __uint_as_float(r[c + 1]),
-                                  __uint_as_float(r[c + 2]), __uint_as_float(r[c + 3]));
-              }
+                  *reinterpret_cast<float4*>(wsp + (size_t)m * p.N + n0 + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
             } else {
-              __nv_bfloat16* dst = row_ptr(m) + n0;
-#pragma unroll
-              for (int c = 0; c < CH; c += 8) {
-                if (n0 + c < p.N) {
-                  float v[8];
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[c + i]);
-                  if (p.bias) {
-                    const uint4 bb = *reinterpret_cast<const uint4*>(p.bias + n0 + c);
-                    const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                      float2 f = unpack_bf16x2(bw[i]);
-                      v[2 * i] += f.x;
-                      v[2 * i + 1] += f.y;
-                    }
-                  }
-                  uint4 o;
-                  o.x = pack_bf16x2(v[0], v[1]);
-                  o.y = pack_bf16x2(v[2], v[3]);
-                  o.z = pack_bf16x2(v[4], v[5]);
-                  o.w = pack_bf16x2(v[6], v[7]);
-                  *reinterpret_cast<uint4*>(dst + c) = o;
-                }
-              }
-            }
-          }
-        } else {
-          if (wsp) {
-            if (m < p.M) {
 #pragma unroll
               for (int c = 0; c < CH; ++c)
-                if (n0 + c < p.N) wsp[(size_t)(n0 + c) * p.M + m] = __uint_as_float(r[c]);
-            }
-          } else {
-            // pair exchange: even lanes store (m, m+1) of column c, odd lanes of column c+1,
-            // so every store is one bf16x2 and 16 lanes cover 64 contiguous bytes
-            const float bias_m = (p.bias && m < p.M)
-                                     ? __bfloat162float(p.bias[grouped ? p.g_tile_expert[n_idx] * p.g_rows + m : m])
-                                     : 0.f;
-            const bool odd = lane & 1;
-#pragma unroll
-            for (int c = 0; c < CH; c += 2) {
-              const float own0 = __uint_as_float(r[c]) + bias_m;
-              const float own1 = __uint_as_float(r[c + 1]) + bias_m;
-              const float send = odd ? own0 : own1;
-              const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
-              const int n = n0 + c + (odd ? 1 : 0);
-              const int mm = odd ? m - 1 : m;
-              const uint32_t packed = odd ? pack_bf16x2(recv, own1) : pack_bf16x2(own0, recv);
-              if (n < p.N && mm < p.M)
-                *reinterpret_cast<uint32_t*>(row_ptr(n) + mm) = packed;
+                if (n0 + c < p.N) wsp[(size_t)(n0 + c) * p.M + m] = v[c];
             }
           }
         }
+        tc_fence_before_sync();
+        mbar_arrive(&tempty_bar[acc]);
+      } else {
+        // split-K with a remote destination: park this split's fp32 tile ([column][row], lanes
+        // contiguous), then the CTA that arrives last for the tile adds the splits in split order
+        // and finishes the tile (so partial sums leave the GPU once, already reduced over K).
+        const int row_l = q * 32 + lane;
+        float* mine = p.ws + ((size_t)split * tiles + t) * (BM * BN);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          float v[32];
+          load_chunk(c0, v);
+#pragma unroll
+          for (int c = 0; c < CH; ++c) mine[(size_t)(c0 + c) * BM + row_l] = v[c];
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&tempty_bar[acc]);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          const unsigned int old = atomicAdd(p.tile_counters + t, 1u);
+          const int last = old == (unsigned int)(p.k_splits - 1);
+          if (last) p.tile_counters[t] = 0;          // ready for the next launch
+          *last_flag = last;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        emitted = *last_flag != 0;
+        if (emitted) {
+          __threadfence();
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += CH) {
+            float v[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) v[c] = 0.f;
+            // 4 splits x 16 columns of independent loads per round keep L2 latency off the critical path
+#pragma unroll
+            for (int h = 0; h < CH; h += 16) {
+              for (int sp0 = 0; sp0 < p.k_splits; sp0 += 4) {
+                float tv[4][16];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int sp = min(sp0 + j, p.k_splits - 1);
+                  const float* src = p.ws + ((size_t)sp * tiles + t) * (BM * BN) + (size_t)(c0 + h) * BM + row_l;
+#pragma unroll
+                  for (int c = 0; c < 16; ++c) tv[j][c] = __ldcg(src + (size_t)c * BM);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  if (sp0 + j < p.k_splits) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) v[h + c] += tv[j][c];
+                  }
+              }
+            }
+            emit(c0, v);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is reused by the next tile
       }
-      tc_fence_before_sync();
-      mbar_arrive(&tempty_bar[acc]);
-      if (rs) {
+      if (rs && emitted) {
         // publish this warp's share of the tile: stores -> system fence -> one flag bump per
         // destination rank that owns token rows of the tile
         __threadfence_system();
@@ -407,8 +501,9 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
 }
 
 size_t gemm_bf16_workspace_bytes(int tokens, int features) {
-  // upper bound: 16 splits of a dense fp32 [tokens][features] array
-  return (size_t)16 * tokens * features * sizeof(float);
+  // counters + upper bound of 16 splits of fp32 tiles padded to the tile grid
+  const size_t t = (size_t)((tokens + 15) / 16 * 16), f = (size_t)((features + BM - 1) / BM * BM);
+  return 64 * 1024 + (size_t)16 * t * f * sizeof(float);
 }
 
 static int pick_bn_tokens(int t) {
@@ -479,7 +574,6 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
     }
     a.ag_flags = tpa->ag_flags; a.ag_consumed = tpa->ag_consumed; a.cta_done = tpa->cta_done;
     a.ag_tokens = T;
-    if (rs) force_splits = 1;          // partial sums leave the GPU from the epilogue: no split-K
   }
 
   bool swap;
@@ -511,14 +605,21 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
     const int slots = sms * (bn <= 64 ? 2 : 1);
     splits = min(min(slots / tiles, a.k_blocks / 4), 16);
   }
-  if (splits > 1) {
-    const size_t need = (size_t)splits * a.M * a.N * sizeof(float);
-    // the reduction reads the partials as float4 along the feature axis (N % 8 == 0 above)
-    if (!workspace || need > workspace_bytes) splits = 1;
-  }
+  // workspace = [tile counters (kCounterBytes, zero between launches)] [fp32 partial tiles]
+  constexpr size_t kCounterBytes = 64 * 1024;
+  if (splits > 1 && (!workspace || workspace_bytes <= kCounterBytes || (size_t)tiles * 4 > kCounterBytes || bn > 128))
+    splits = 1;
+  while (splits > 1 && kCounterBytes + (size_t)splits * tiles * BM * bn * sizeof(float) > workspace_bytes) --splits;
+  a.fixup = rs ? 1 : 0;
+  if (!a.fixup)
+    while (splits > 1 && kCounterBytes + (size_t)splits * a.M * a.N * sizeof(float) > workspace_bytes) --splits;
   a.kb_per_split = (a.k_blocks + splits - 1) / splits;
   a.k_splits = (a.k_blocks + a.kb_per_split - 1) / a.kb_per_split;
-  if (a.k_splits == 1) a.ws = nullptr;
+  a.tile_counters = reinterpret_cast<unsigned int*>(workspace);
+  a.ws = a.k_splits > 1 ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + kCounterBytes) : nullptr;
+  // 16-byte stores of the transposed epilogue need 16-byte aligned token rows
+  a.vec16 = rs ? ((a.rs_ld & 7) == 0)
+               : ((ldy & 7) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0);
 
   const int grid = min(tiles * a.k_splits, sms * (bn <= 64 ? 2 : 1));
   switch (bn) {
@@ -528,14 +629,12 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
     case 128: launch_gemm<128>(ta, tb, a, grid, stream); break;
     default: launch_gemm<256>(ta, tb, a, grid, stream); break;
   }
-  if (a.k_splits > 1) {
-    // the partials are a dense [T][N] (row-major) or, when transposed, [N_tok=T][features] array:
-    // in both cases "rows" are tokens and "cols" are features of y.
+  if (a.k_splits > 1 && !a.fixup) {
+    // dense [token][feature] partials in both orientations
     const size_t n = (size_t)T * N;
     const int threads = 256;
     const int blocks = (int)((n / 4 + threads - 1) / threads);
-    splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(a.ws, a.k_splits, T, N, ldy, a.bias,
-                                                         a.out);
+    splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(a.ws, a.k_splits, T, N, ldy, a.bias, a.out);
     cuda_check(cudaGetLastError(), "splitk_reduce_kernel launch");
     return 2;
   }
@@ -571,6 +670,7 @@ int moe_grouped_linear_bf16(const void* xp, long long ldx, const void* w_stack, 
   a.g_tile_row0 = tile_row0;
   a.g_num_tiles = num_tiles;
   a.g_rows = n_out;
+  a.vec16 = (ldy & 7) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
   // When n_out is not a multiple of 128 the last feature tile of an expert also reads rows of the
   // next expert's matrix (or zero fill past the stack); the epilogue never stores those rows.
   CUtensorMap ta = make_tmap_2d(w_stack, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)experts * n_out, K,

@@ -68,11 +68,15 @@ FLLM_EXPORT int fllm_linear_bf16_splitk_noalloc(const void* x, long long ldx, co
   if ((k & 7) || (features & 7) || (ldx & 7) || (ldw & 7) || (ldy & 7))
     return fail(FLLM_NOALLOC_E_ARGS, "k, features and the leading dimensions must be multiples of 8");
   if (splits > 16) return fail(FLLM_NOALLOC_E_ARGS, "splits must be at most 16 (got %lld)", splits);
-  const unsigned long long need = 4ull * (unsigned long long)splits * (unsigned long long)tokens *
-                                  (unsigned long long)features;
+  // partial sums are kept per tile: tokens round up to the tile width, features to 128; the first
+  // 64 KiB of the array hold the per-tile arrival counters
+  const unsigned long long tok_pad = tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64
+                                     : (unsigned long long)((tokens + 127) / 128) * 128;
+  const unsigned long long feat_pad = (unsigned long long)((features + 127) / 128) * 128;
+  const unsigned long long need = 65536ull + 4ull * (unsigned long long)splits * tok_pad * feat_pad;
   if (need > FLLM_NOALLOC_SCRATCH_BYTES)
     return fail(FLLM_NOALLOC_E_TOO_LARGE,
-                "splits * tokens * features * 4 = %lld bytes exceeds the %lld-byte scratch array",
+                "64 KiB + splits * padded tokens * padded features * 4 = %lld bytes exceeds the %lld-byte scratch array",
                 (long long)need, (long long)FLLM_NOALLOC_SCRATCH_BYTES);
   void* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);

@@ -20,7 +20,8 @@ class NativeOps:
     def __init__(self, device: torch.device, workspace_bytes: int = 96 << 20):
         self.k = load_cuda()
         self.device = torch.device(device)
-        self.workspace = torch.empty(workspace_bytes, dtype=torch.uint8, device=self.device)
+        # first 64 KiB = split-K tile counters (must start at zero; the kernels re-zero them)
+        self.workspace = torch.zeros(workspace_bytes, dtype=torch.uint8, device=self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.use_tc_attention = True
         self.attn_ws = None

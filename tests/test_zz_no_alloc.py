@@ -47,7 +47,7 @@ def _call(lib, x, w, bias, y, splits, status=None):
 def test_matches_regular_entry_point_on_two_calls_in_a_row(lib):
     torch.cuda.set_device(0)
     g = torch.Generator(device="cuda").manual_seed(11)
-    ws = torch.empty(32 << 20, dtype=torch.uint8, device="cuda")
+    ws = torch.zeros(32 << 20, dtype=torch.uint8, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     # second call: other shape, other data, fewer splits - stale partials must not leak in
     for T, N, K, splits, with_bias in [(64, 2048, 4096, 4, True), (24, 1024, 2048, 2, False)]:
