@@ -21,6 +21,7 @@ no Rust toolchain is installed and pip cannot install it).
 from __future__ import annotations
 
 import argparse
+import faulthandler
 import json
 import os
 import statistics
@@ -89,6 +90,8 @@ def reference_arm(args) -> None:
 
 
 def main() -> None:
+    if os.environ.get("FLLM_HANG_DUMP"):      # debugging aid: dump all Python stacks and exit if the run stalls
+        faulthandler.dump_traceback_later(int(os.environ["FLLM_HANG_DUMP"]), exit=True)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -241,9 +244,11 @@ def main() -> None:
             "kernel_status": status,
         }))
     if world > 1:
+        from fllm_b200.comm import shutdown_distributed
+        eng.close()
         torch.distributed.barrier()
         tp_rt.close()
-        torch.distributed.destroy_process_group()
+        shutdown_distributed()
 
 
 if __name__ == "__main__":

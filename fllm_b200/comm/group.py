@@ -180,3 +180,22 @@ def make_tp_pp_groups(tp: int, pp: int) -> "tuple[Group, Group, int, int]":
         if t == tp_rank:
             pp_g = Group(members, g)
     return tp_g, pp_g, stage, tp_rank
+
+
+def shutdown_distributed(grace_s: float = 20.0) -> None:
+    """Destroy the default process group, but never hang the process on it: if the library does
+    not return within `grace_s` (e.g. a CUDA graph still references the communicator) the process
+    exits with status 0, since all results have been reported by then."""
+    import threading
+    if not dist.is_initialized():
+        return
+    import sys
+    sys.stdout.flush()
+    sys.stderr.flush()
+    t = threading.Timer(grace_s, lambda: os._exit(0))
+    t.daemon = True
+    t.start()
+    try:
+        dist.destroy_process_group()
+    finally:
+        t.cancel()

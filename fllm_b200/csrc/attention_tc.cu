@@ -204,6 +204,8 @@ __global__ void __launch_bounds__(128) fa_decode_kernel(const FaParams p) {
   const int kvh = blockIdx.x, seq = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.group;
+  pdl_launch_dependents();
+  pdl_wait();
   const int q0 = p.q_starts[seq];
   const int qn = p.q_starts[seq + 1] - q0;
   if (qn <= 0 || qn > p.decode_max_q) return;
@@ -554,7 +556,7 @@ static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int mi
     p.ws_o = reinterpret_cast<float*>(workspace);
     p.ws_ml = p.ws_o ? p.ws_o + (size_t)tokens * p.hq * splits * D : nullptr;
     dim3 grid(p.hkv, num_seqs, splits);
-    fa_decode_kernel<D><<<grid, 128, DecodeSmem<D>::kTotal, s>>>(p);
+    launch_pdl(fa_decode_kernel<D>, grid, dim3(128), DecodeSmem<D>::kTotal, s, p);
     ++launches;
     if (splits > 1) {
       fa_merge_kernel<D><<<dim3(p.hq, tokens), D < 128 ? D : 128, 0, s>>>(p, tokens);

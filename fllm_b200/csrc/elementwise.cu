@@ -51,6 +51,8 @@ __global__ void __launch_bounds__(256)
 rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ delta,
                const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int hidden,
                long long ld_res, long long ld_delta, long long ld_y, float eps, float w_offset) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   __nv_bfloat16* xr = residual + (size_t)row * ld_res;
   const __nv_bfloat16* dr = delta ? delta + (size_t)row * ld_delta : nullptr;
@@ -128,8 +130,8 @@ void rmsnorm_bf16(void* residual, long long ld_res, const void* delta, long long
   auto* ww = (const __nv_bfloat16*)w;
   auto* yy = (__nv_bfloat16*)y;
 #define FLLM_RMS(IT)                                                                          \
-  rmsnorm_kernel<IT><<<rows, 256, 0, s>>>(r, d, ww, yy, hidden, ld_res, ld_delta, ld_y, eps, \
-                                           w_offset)
+  launch_pdl(rmsnorm_kernel<IT>, dim3(rows), dim3(256), 0, s, r, d, ww, yy, hidden, ld_res, ld_delta, ld_y, eps, \
+             w_offset)
   switch (iters) {
     case 1: FLLM_RMS(1); break;
     case 2: FLLM_RMS(2); break;
@@ -156,6 +158,8 @@ rope_kv_kernel(__nv_bfloat16* __restrict__ qkv, long long ld_qkv, const int* __r
                int hq, int hkv, int block_size, int rot_dim, int rope_style, float eps,
                float attn_factor) {
   constexpr int EPL = D / 32;  // elements per lane
+  pdl_launch_dependents();
+  pdl_wait();
   const int heads = hq + 2 * hkv;
   const long long gw = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (gw >= (long long)tokens * heads) return;
@@ -300,9 +304,8 @@ void rope_qknorm_kvwrite_bf16(void* qkv, long long ld_qkv, const int* positions,
   auto* kc = (__nv_bfloat16*)k_cache;
   auto* vc = (__nv_bfloat16*)v_cache;
 #define FLLM_ROPE(DD)                                                                            \
-  rope_kv_kernel<DD><<<blocks, 128, 0, s>>>(x, ld_qkv, positions, slots, inv_freq, qn, kn, kc, \
-                                            vc, tokens, hq, hkv, block_size, rot_dim,           \
-                                            rope_style, eps, attn_factor)
+  launch_pdl(rope_kv_kernel<DD>, dim3(blocks), dim3(128), 0, s, x, ld_qkv, positions, slots, inv_freq, qn, kn, kc, \
+             vc, tokens, hq, hkv, block_size, rot_dim, rope_style, eps, attn_factor)
   switch (head_dim) {
     case 64: FLLM_ROPE(64); break;
     case 128: FLLM_ROPE(128); break;
@@ -321,6 +324,8 @@ void rope_qknorm_kvwrite_bf16(void* qkv, long long ld_qkv, const int* positions,
 __global__ void glu_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                            __nv_bfloat16* __restrict__ out, long long ldo, int inter, int act_kind,
                            float alpha, float limit) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.y;
   const int i8 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i8 >= inter) return;
@@ -376,8 +381,8 @@ void glu_bf16(const void* x, long long ldx, void* out, long long ldo, int rows, 
   if (rows <= 0) return;
   if (inter % 8) throw std::runtime_error("glu_bf16: intermediate size must be a multiple of 8");
   dim3 grid((inter / 8 + 127) / 128, rows);
-  glu_kernel<<<grid, 128, 0, s>>>((const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)out, ldo, inter,
-                                  act_kind, alpha, limit);
+  launch_pdl(glu_kernel, grid, dim3(128), 0, s, (const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)out, ldo, inter,
+             act_kind, alpha, limit);
   cuda_check(cudaGetLastError(), "glu_kernel");
 }
 

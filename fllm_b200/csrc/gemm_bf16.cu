@@ -147,6 +147,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
 
   const int tiles = p.m_tiles * p.n_tiles;
   const bool grouped = p.g_num_tiles != nullptr;
+  // Let the next kernel in the stream start its own prologue now. Everything this kernel reads
+  // that a predecessor may have written (activations, tile lists, counters) is touched only after
+  // griddepcontrol.wait; weights are static, so their first tiles are requested before the wait.
+  pdl_launch_dependents();
+  if (grouped) pdl_wait();
   const int total = grouped ? *p.g_num_tiles * p.m_tiles : tiles * p.k_splits;
 
   if (warp == 0) {
@@ -156,6 +161,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
       uint32_t phase = 0;
       bool ok = true;
       uint32_t arrived = 0;      // bit s: rank s delivered all of its rows of the gathered operand
+      int pre = 0;               // leading k-blocks of the first item whose weight tile is already in flight
+      if (!grouped) {
+        const int w = blockIdx.x;
+        if (w < total) {
+          const int split = w / tiles;
+          const int t = w - split * tiles;
+          const int n_idx = t / p.m_tiles;
+          const int m_idx = t - n_idx * p.m_tiles;
+          const int kb0 = split * p.kb_per_split;
+          const int kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
+          pre = min(kb1 - kb0, STAGES);
+          for (int i = 0; i < pre; ++i) {
+            mbar_expect_tx(&full_bar[i], S::kStageBytes);
+            if (p.transposed) tma_load_2d(sA + i * S::kABytes, &tma_a, &full_bar[i], (kb0 + i) * BK, m_idx * BM);
+            else tma_load_2d(sB + i * S::kBBytes, &tma_b, &full_bar[i], (kb0 + i) * BK, n_idx * BN);
+          }
+        }
+        pdl_wait();
+      }
       for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
         const int split = w / tiles;
         const int t = w - split * tiles;
@@ -184,12 +208,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
           if (!ok) break;
         }
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(&full_bar[stage], S::kStageBytes);
+          const bool prefetched = w == (int)blockIdx.x && kb - kb0 < pre;   // weight half already requested
+          if (!prefetched) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+            mbar_expect_tx(&full_bar[stage], S::kStageBytes);
+          }
           const int a_row = grouped ? p.g_tile_expert[n_idx] * p.g_rows + m_idx * BM : m_idx * BM;
           const int b_row = grouped ? p.g_tile_row0[n_idx] : n_idx * BN;
-          tma_load_2d(sA + stage * S::kABytes, &tma_a, &full_bar[stage], kb * BK, a_row);
-          tma_load_2d(sB + stage * S::kBBytes, &tma_b, &full_bar[stage], kb * BK, b_row);
+          if (!(prefetched && p.transposed))
+            tma_load_2d(sA + stage * S::kABytes, &tma_a, &full_bar[stage], kb * BK, a_row);
+          if (!(prefetched && !p.transposed))
+            tma_load_2d(sB + stage * S::kBBytes, &tma_b, &full_bar[stage], kb * BK, b_row);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -232,6 +261,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
   } else {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    if (!grouped) pdl_wait();  // outputs and workspaces may still be in use by the predecessor
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -496,8 +526,7 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
                "cudaFuncSetAttribute(gemm_bf16_kernel)");
     configured = true;
   }
-  gemm_bf16_kernel<BN><<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, a);
-  cuda_check(cudaGetLastError(), "gemm_bf16_kernel launch");
+  launch_pdl(gemm_bf16_kernel<BN>, dim3(grid), dim3(kGemmThreads), S::kTotal, stream, ta, tb, a);
 }
 
 size_t gemm_bf16_workspace_bytes(int tokens, int features) {
@@ -601,7 +630,8 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
   int splits = 1;
   if (force_splits > 0) {
     splits = force_splits;
-  } else if (tiles * 2 <= sms && a.k_blocks >= 8) {
+  } else if (tiles * 4 <= sms * (bn <= 64 ? 2 : 1) * 3 && a.k_blocks >= 8) {
+    // fewer tiles than 3/4 of the resident CTA slots: cut K so that every SM streams weights
     const int slots = sms * (bn <= 64 ? 2 : 1);
     splits = min(min(slots / tiles, a.k_blocks / 4), 16);
   }

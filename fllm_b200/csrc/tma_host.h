@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdexcept>
+#include <stdlib.h>
+#include <utility>
 #include <string>
 
 namespace fllm {
@@ -57,6 +59,34 @@ inline CUtensorMap make_tmap_2d(const void* base, CUtensorMapDataType dt, int el
                              std::to_string((int)r));
   (void)elem_bytes;
   return m;
+}
+
+// Programmatic dependent launch: the kernel may start while its predecessor in the stream is
+// still running; it must execute griddepcontrol.wait before it touches anything the predecessor
+// produces. FLLM_PDL=0 turns the attribute off (plain stream order).
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("FLLM_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cuda_check(cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...), "cudaLaunchKernelEx");
 }
 
 inline int sm_count() {

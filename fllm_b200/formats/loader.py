@@ -1,0 +1,152 @@
+"""Model loading: a Hugging Face checkpoint directory (config.json + *.safetensors) or a GGUF file
+-> (ModelConfig, DecoderWeights for this tensor-parallel rank, tokenizer path).
+
+Projections are fused the way the kernels want them (q|k|v rows, gate|up rows) and cut for tensor
+parallelism with the rules of ``models.weights``. Block-wise FP8 checkpoints (``weight_scale_inv``
+tensors, 128 x 128 blocks) stay packed: the e4m3 bytes and their scales go to the GPU untouched
+and run on the FP8 tensor cores. GGUF K-quants are consumed packed by the CPU engine; for the GPU
+path they are expanded to bf16 once at load time
+(rust/checkpoint/src/convert.rs:1290-1559 is the reference's importer).
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+from ..config import ModelConfig
+from ..models.weights import DecoderWeights, LayerWeights, make_shard_spec
+
+
+def _cut_rows(t: torch.Tensor, start: int, n: int) -> torch.Tensor:
+    return t[start:start + n]
+
+
+def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16):
+    from .safetensors_io import open_checkpoint
+    cfg = ModelConfig.from_hf_config(json.load(open(os.path.join(directory, "config.json"))))
+    sp = make_shard_spec(cfg, tp, tp_rank)
+    ck = open_checkpoint(directory)
+    D = cfg.head_dim
+
+    def get(name, required=True):
+        if name not in ck:
+            if required:
+                raise KeyError(f"checkpoint has no tensor {name!r}")
+            return None
+        f, n = ck[name]
+        return f.tensor(n)
+
+    def dev(t):
+        return t.to(device=device, dtype=dtype if t.is_floating_point() and t.element_size() > 1 else t.dtype).contiguous()
+
+    qs = slice(sp.q_head_start * D, (sp.q_head_start + sp.hq_local) * D)
+    ks = slice(sp.kv_head_start * D, (sp.kv_head_start + sp.hkv_local) * D)
+    isl = slice(sp.inter_start, sp.inter_start + sp.inter_local)
+    layers = []
+    for l in range(cfg.num_layers):
+        p = f"model.layers.{l}."
+        q, k, v = (get(p + f"self_attn.{n}_proj.weight") for n in "qkv")
+        fp8 = q.dtype == torch.float8_e4m3fn
+        lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
+                          ffn_norm=dev(get(p + "post_attention_layernorm.weight")))
+        o = get(p + "self_attn.o_proj.weight")
+        g, u, d = (get(p + f"mlp.{n}_proj.weight") for n in ("gate", "up", "down"))
+        if fp8:
+            def sc(name):
+                return get(p + name + ".weight_scale_inv").float()
+            def rows(t, s, sl):            # cut rows of codes and of their 128-row scale blocks
+                return t[sl], s[sl.start // 128: -(-sl.stop // 128)]
+            def cols(t, s, sl):
+                return t[:, sl], s[:, sl.start // 128: -(-sl.stop // 128)]
+            parts = [rows(q, sc("self_attn.q_proj"), qs), rows(k, sc("self_attn.k_proj"), ks), rows(v, sc("self_attn.v_proj"), ks)]
+            lw.packed["wqkv"] = ("fp8_block", torch.cat([a for a, _ in parts]).view(torch.uint8).to(device).contiguous(),
+                                 torch.cat([b for _, b in parts]).to(device).contiguous())
+            a, b = cols(o, sc("self_attn.o_proj"), qs)
+            lw.packed["wo"] = ("fp8_block", a.view(torch.uint8).to(device).contiguous(), b.to(device).contiguous())
+            parts = [rows(g, sc("mlp.gate_proj"), isl), rows(u, sc("mlp.up_proj"), isl)]
+            lw.packed["w_gate_up"] = ("fp8_block", torch.cat([a for a, _ in parts]).view(torch.uint8).to(device).contiguous(),
+                                      torch.cat([b for _, b in parts]).to(device).contiguous())
+            a, b = cols(d, sc("mlp.down_proj"), isl)
+            lw.packed["w_down"] = ("fp8_block", a.view(torch.uint8).to(device).contiguous(), b.to(device).contiguous())
+        else:
+            lw.wqkv = dev(torch.cat([q[qs], k[ks], v[ks]], 0))
+            lw.wo = dev(o[:, qs])
+            lw.w_gate_up = dev(torch.cat([g[isl], u[isl]], 0))
+            lw.w_down = dev(d[:, isl])
+        if cfg.attn_bias:
+            bq, bk, bv = (get(p + f"self_attn.{n}_proj.bias", False) for n in "qkv")
+            if bq is not None:
+                lw.bqkv = dev(torch.cat([bq[qs], bk[ks], bv[ks]]))
+            bo = get(p + "self_attn.o_proj.bias", False)
+            if bo is not None:
+                lw.bo = dev(bo if tp_rank == 0 else torch.zeros_like(bo))
+        if cfg.qk_norm:
+            lw.q_norm, lw.k_norm = dev(get(p + "self_attn.q_norm.weight")), dev(get(p + "self_attn.k_norm.weight"))
+        layers.append(lw)
+    embed = get("model.embed_tokens.weight")
+    head = get("lm_head.weight", False)
+    if head is None or cfg.tie_embeddings:
+        head = embed
+    v0, vl = 0, cfg.vocab_size
+    if tp > 1:
+        v0 = tp_rank * sp.vocab_chunk
+        v1 = min(v0 + sp.vocab_chunk, cfg.vocab_size)
+        vl = max(v1 - v0, 0)
+        hl = torch.zeros(sp.vocab_chunk, cfg.hidden_size, dtype=head.dtype)
+        hl[:vl] = head[v0:v1]
+        head = hl
+    w = DecoderWeights(embed=dev(embed), layers=layers, final_norm=dev(get("model.norm.weight")), lm_head=dev(head),
+                       vocab_start=v0, vocab_local=vl)
+    tok = directory if os.path.exists(os.path.join(directory, "tokenizer.json")) else None
+    return cfg, w, tok
+
+
+def load_gguf(path: str, device="cuda", tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16):
+    from ..cpu_engine import config_from_gguf
+    from .gguf import GgufReader
+    r = GgufReader(path)
+    cfg = config_from_gguf(r)
+    sp = make_shard_spec(cfg, tp, tp_rank)
+    D = cfg.head_dim
+    t = lambda n: torch.from_numpy(r.tensor_f32(n))
+    dev = lambda x: x.to(device=device, dtype=dtype).contiguous()
+    qs = slice(sp.q_head_start * D, (sp.q_head_start + sp.hq_local) * D)
+    ks = slice(sp.kv_head_start * D, (sp.kv_head_start + sp.hkv_local) * D)
+    isl = slice(sp.inter_start, sp.inter_start + sp.inter_local)
+    layers = []
+    for l in range(cfg.num_layers):
+        p = f"blk.{l}."
+        lw = LayerWeights(
+            attn_norm=dev(t(p + "attn_norm.weight")),
+            wqkv=dev(torch.cat([t(p + "attn_q.weight")[qs], t(p + "attn_k.weight")[ks], t(p + "attn_v.weight")[ks]], 0)),
+            wo=dev(t(p + "attn_output.weight")[:, qs]), ffn_norm=dev(t(p + "ffn_norm.weight")),
+            w_gate_up=dev(torch.cat([t(p + "ffn_gate.weight")[isl], t(p + "ffn_up.weight")[isl]], 0)),
+            w_down=dev(t(p + "ffn_down.weight")[:, isl]))
+        if p + "attn_q_norm.weight" in r.tensors:
+            lw.q_norm, lw.k_norm = dev(t(p + "attn_q_norm.weight")), dev(t(p + "attn_k_norm.weight"))
+        layers.append(lw)
+    embed = t("token_embd.weight")
+    head = t("output.weight") if "output.weight" in r.tensors and not cfg.tie_embeddings else embed
+    v0, vl = 0, cfg.vocab_size
+    if tp > 1:
+        v0 = tp_rank * sp.vocab_chunk
+        v1 = min(v0 + sp.vocab_chunk, cfg.vocab_size)
+        vl = max(v1 - v0, 0)
+        hl = torch.zeros(sp.vocab_chunk, cfg.hidden_size)
+        hl[:vl] = head[v0:v1]
+        head = hl
+    w = DecoderWeights(embed=dev(embed), layers=layers, final_norm=dev(t("output_norm.weight")), lm_head=dev(head),
+                       vocab_start=v0, vocab_local=vl)
+    has_tok = "tokenizer.ggml.tokens" in r.metadata
+    r.close()
+    return cfg, w, (path if has_tok else None)
+
+
+def load_model(path: str, device="cuda", tp: int = 1, tp_rank: int = 0):
+    if path.endswith(".gguf"):
+        return load_gguf(path, device, tp, tp_rank)
+    return load_hf_checkpoint(path, device, tp, tp_rank)

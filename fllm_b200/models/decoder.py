@@ -79,6 +79,12 @@ class Decoder:
         self.scale = cfg.head_dim ** -0.5
         self.rope_style = 0 if cfg.rope_style == "neox" else 1
         self.act_kind = ACT_KIND[cfg.act]
+        # packed payloads loaded from a checkpoint become weight objects that pick their own kernel
+        for lw in self.w.layers:
+            for name, packed in list(lw.packed.items()):
+                if packed[0] == "fp8_block":
+                    from ..ops.native import Fp8BlockWeight
+                    setattr(lw, name, Fp8BlockWeight(packed[1], packed[2]))
 
     # ------------------------------------------------------------------ pieces
     def _reduce(self, x: torch.Tensor) -> torch.Tensor:

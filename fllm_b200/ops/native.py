@@ -29,6 +29,8 @@ class NativeOps:
 
     # ---------------------------------------------------------------- dense
     def linear(self, x, w, bias=None, out=None, force_splits: int = 0):
+        if not isinstance(w, torch.Tensor):          # packed weight (FP8 block, FP4, ...): it knows its kernel
+            return w.apply(self, x, bias, out)
         if out is None:
             out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
         self.launches += self.k.linear(x, w, bias, out, self.workspace, self.status, force_splits)
@@ -125,20 +127,33 @@ def quantize_weight_fp8_block(w: torch.Tensor, block: int = 128):
     return q.view(N, K).view(torch.uint8).contiguous(), scale.contiguous()
 
 
-class Fp8BlockLinear:
-    """y = x W^T with W stored as block-scaled e4m3: activations are quantised per token per 128
-    values on the fly, the product runs on the FP8 tensor cores."""
+class Fp8BlockWeight:
+    """A weight stored as block-scaled e4m3 (codes [N, K] as bytes + fp32 scales per 128 x 128).
+    ``ops.linear`` accepts it in place of a bf16 tensor: activations are quantised per token per
+    128 values on the fly and the product runs on the FP8 tensor cores."""
 
-    def __init__(self, ops: NativeOps, wq: torch.Tensor, sw: torch.Tensor, bias=None):
-        self.ops, self.wq, self.sw, self.bias = ops, wq, sw, bias
+    def __init__(self, wq: torch.Tensor, sw: torch.Tensor):
+        self.wq, self.sw = wq, sw
+        self.shape = wq.shape
 
-    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+    def apply(self, ops, x, bias=None, out=None):
         T, K = x.shape
+        if not x.is_cuda:                                           # CPU oracle path
+            wd = self.wq.view(torch.float8_e4m3fn).float().view(self.shape[0] // 128, 128, K // 128, 128) * self.sw[:, None, :, None]
+            y = x.float() @ wd.view(self.shape[0], K).t()
+            return (y + bias.float() if bias is not None else y).to(x.dtype)
         xq = torch.empty(T, K, dtype=torch.uint8, device=x.device)
         sx = torch.empty(T, K // 128, dtype=torch.float32, device=x.device)
-        k = self.ops.k
-        k.quant_fp8_1x128(x, xq, sx)
-        y = torch.empty(T, self.wq.shape[0], dtype=torch.bfloat16, device=x.device)
-        k.linear_fp8_block(xq, sx, self.wq, self.sw, self.bias, y, self.ops.status)
-        self.ops.launches += 2
+        ops.k.quant_fp8_1x128(x.contiguous(), xq, sx)
+        y = out if out is not None else torch.empty(T, self.shape[0], dtype=torch.bfloat16, device=x.device)
+        ops.k.linear_fp8_block(xq, sx, self.wq, self.sw, bias, y, ops.status)
+        ops.launches += 2
         return y
+
+
+class Fp8BlockLinear:
+    def __init__(self, ops: NativeOps, wq: torch.Tensor, sw: torch.Tensor, bias=None):
+        self.ops, self.w, self.bias = ops, Fp8BlockWeight(wq, sw), bias
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        return self.w.apply(self.ops, x, self.bias)

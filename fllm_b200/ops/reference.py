@@ -16,6 +16,8 @@ class RefOps:
 
     # ---------------------------------------------------------------- dense
     def linear(self, x, w, bias=None, out=None):
+        if not isinstance(w, torch.Tensor):
+            return w.apply(self, x, bias, out)
         y = x.float() @ w.float().t()
         if bias is not None:
             y = y + bias.float()

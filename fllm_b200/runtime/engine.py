@@ -444,6 +444,16 @@ class LLMEngine:
             return []
         return [outs[i] for i in ids]
 
+    def close(self) -> None:
+        """Drop captured graphs (they pin the library communicator: it cannot be destroyed while a
+        graph that captured one of its collectives is alive) and wait for the device."""
+        self._graphs.clear()
+        self._graph_pool = None
+        import gc
+        gc.collect()
+        if self.is_cuda:
+            torch.cuda.synchronize(self.device)
+
     def warm_up(self, buckets: Optional[Sequence[int]] = None) -> None:
         """Capture decode graphs ahead of traffic (rust/engine/src/runtime.rs:1085-1175)."""
         if not (self.is_cuda and self.cfg.use_cuda_graphs):

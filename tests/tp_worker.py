@@ -1,6 +1,7 @@
 """Child process of the tensor-parallel tests: one rank of a TP group (gloo on CPU, NCCL or the
 fused peer-memory path on GPUs). Compares this layout's greedy tokens and last-step logits with
 a single-device run of the same model on the same rank, and prints one line of JSON on rank 0."""
+import faulthandler
 import json
 import os
 import sys
@@ -16,6 +17,7 @@ from fllm_b200.runtime import LLMEngine, SamplingParams  # noqa: E402
 
 
 def main():
+    faulthandler.dump_traceback_later(int(os.environ.get("FLLM_HANG_DUMP", "150")), exit=True)
     device_kind, backend, model = sys.argv[1], sys.argv[2], sys.argv[3]
     pp = int(sys.argv[4]) if len(sys.argv) > 4 else 1
     rank, world, local = init_distributed("gloo" if device_kind == "cpu" else "nccl", timeout_s=120)
@@ -63,11 +65,14 @@ def main():
         total = sum(len(o) for o in want)
         print(json.dumps({"backend": getattr(tp_rt, "backend", "?"), "world": world, "agree": agree, "total": total,
                           "status": status, "graph_steps": eng.stats.graph_steps, "logit_err": logit_err}), flush=True)
+    from fllm_b200.comm import shutdown_distributed
+    eng.close()
+    single.close()
     if torch.distributed.is_initialized():
         torch.distributed.barrier()
     if hasattr(tp_rt, "close"):
         tp_rt.close()
-    torch.distributed.destroy_process_group()
+    shutdown_distributed()
 
 
 if __name__ == "__main__":
