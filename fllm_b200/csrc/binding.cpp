@@ -225,6 +225,8 @@ void spec_verify_sampled(const Tensor& target_logits, const Tensor& draft_logits
                             n_accept.data_ptr<int>(), out_tokens.data_ptr<int>(), cur_stream());
 }
 
+int64_t gemm_occupancy(int64_t bn) { return fllm::gemm_bf16_occupancy((int)bn); }
+
 int64_t sample_row_bytes() { return (int64_t)sizeof(fllm::SampleRow); }
 
 }  // namespace
@@ -243,4 +245,5 @@ TORCH_LIBRARY(fllm_b200, m) {
   m.def("spec_verify_greedy(Tensor draft_ids, Tensor target_ids, Tensor? n_draft, Tensor(a!) n_accept, Tensor(b!) out_tokens) -> ()", &spec_verify_greedy);
   m.def("spec_verify_sampled(Tensor target_logits, Tensor draft_logits, Tensor draft_ids, Tensor? n_draft, Tensor params, Tensor(a!) n_accept, Tensor(b!) out_tokens) -> ()", &spec_verify_sampled);
   m.def("sample_row_bytes() -> int", &sample_row_bytes);
+  m.def("gemm_occupancy(int bn) -> int", &gemm_occupancy);
 }

@@ -14,6 +14,7 @@ int linear_bf16(const void* x, long long ldx, const void* w, long long ldw, cons
                  void* y, long long ldy, int T, int N, int K, void* workspace,
                  size_t workspace_bytes, int* status, int force_splits, cudaStream_t stream);
 size_t gemm_bf16_workspace_bytes(int tokens, int features);
+int gemm_bf16_occupancy(int bn);
 
 // Tensor-parallel hooks of the GEMM (see gemm_bf16.cu). Zero-initialise, then fill the half
 // that is wanted: rs_* turns the epilogue into a reduce-scatter over peer memory, ag_* makes the

@@ -52,6 +52,7 @@ struct GemmArgs {
   float* ws;               // split-K partials, [k_splits][tiles][BN][128] fp32 (tile-local, column-major)
   unsigned int* tile_counters;   // one arrival counter per tile; zero between launches
   int fixup;               // split-K: 1 = last-arriving CTA finishes the tile, 0 = dense partials + reduce kernel
+  int tune;                // bit 0: 4-byte pair-exchange stores instead of the staged 16-byte ones; bit 1: no weight prefetch
   int vec16;               // 1: output rows are 16-byte aligned (transposed stores use uint4)
   const __nv_bfloat16* bias;  // per output feature (n when row-major, m when transposed)
   int* status;
@@ -97,7 +98,7 @@ struct GemmSmem {
 };
 
 template <int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads, BN <= 64 ? 2 : 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
                  const __grid_constant__ CUtensorMap tma_b, const GemmArgs p) {
   using S = GemmSmem<BN>;
@@ -164,7 +165,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
       int pre = 0;               // leading k-blocks of the first item whose weight tile is already in flight
       if (!grouped) {
         const int w = blockIdx.x;
-        if (w < total) {
+        if (w < total && !(p.tune & 2)) {
           const int split = w / tiles;
           const int t = w - split * tiles;
           const int n_idx = t / p.m_tiles;
@@ -318,6 +319,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
               }
             }
           }
+        } else if (p.tune & 1) {
+          const bool odd = lane & 1;
+#pragma unroll
+          for (int c = 0; c < CH; c += 2) {
+            const float own0 = v[c] + bias_m, own1 = v[c + 1] + bias_m;
+            const float recv = __shfl_xor_sync(0xffffffffu, odd ? own0 : own1, 1);
+            const int n = n0 + c + (odd ? 1 : 0);
+            const int mm = odd ? m - 1 : m;
+            const uint32_t packed = odd ? pack_bf16x2(recv, own1) : pack_bf16x2(own0, recv);
+            if (n < p.N && mm < p.M) *reinterpret_cast<uint32_t*>(row_ptr(n) + mm) = packed;
+          }
         } else {
           // Transpose through a per-warp staging tile so that every store is 16 bytes: lanes hold
           // features (rows of D), memory wants 8 consecutive features of one token per store. Four
@@ -427,20 +439,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
             float v[32];
 #pragma unroll
             for (int c = 0; c < 32; ++c) v[c] = 0.f;
-            // 4 splits x 16 columns of independent loads per round keep L2 latency off the critical path
-#pragma unroll
+            // 2 splits x 16 columns of independent loads per round keep L2 latency off the critical path
+#pragma unroll 1
             for (int h = 0; h < CH; h += 16) {
-              for (int sp0 = 0; sp0 < p.k_splits; sp0 += 4) {
-                float tv[4][16];
+              for (int sp0 = 0; sp0 < p.k_splits; sp0 += 2) {
+                float tv[2][16];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < 2; ++j) {
                   const int sp = min(sp0 + j, p.k_splits - 1);
                   const float* src = p.ws + ((size_t)sp * tiles + t) * (BM * BN) + (size_t)(c0 + h) * BM + row_l;
 #pragma unroll
                   for (int c = 0; c < 16; ++c) tv[j][c] = __ldcg(src + (size_t)c * BM);
                 }
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < 2; ++j)
                   if (sp0 + j < p.k_splits) {
 #pragma unroll
                     for (int c = 0; c < 16; ++c) v[h + c] += tv[j][c];
@@ -524,9 +536,28 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
     cuda_check(cudaFuncSetAttribute(gemm_bf16_kernel<BN>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal),
                "cudaFuncSetAttribute(gemm_bf16_kernel)");
+    // ask for the largest shared-memory carve-out: the narrow decode tiles rely on two CTAs per SM
+    cuda_check(cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                    cudaSharedmemCarveoutMaxShared),
+               "cudaFuncSetAttribute(carveout)");
     configured = true;
   }
   launch_pdl(gemm_bf16_kernel<BN>, dim3(grid), dim3(kGemmThreads), S::kTotal, stream, ta, tb, a);
+}
+
+// Resident CTAs per SM of the GEMM kernel for a token-tile width (diagnostics).
+int gemm_bf16_occupancy(int bn) {
+  int n = 0;
+#define FLLM_OCC(B) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemm_bf16_kernel<B>, kGemmThreads, GemmSmem<B>::kTotal)
+  switch (bn) {
+    case 16: cudaFuncSetAttribute(gemm_bf16_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<16>::kTotal); FLLM_OCC(16); break;
+    case 32: cudaFuncSetAttribute(gemm_bf16_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<32>::kTotal); FLLM_OCC(32); break;
+    case 64: cudaFuncSetAttribute(gemm_bf16_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<64>::kTotal); FLLM_OCC(64); break;
+    case 128: cudaFuncSetAttribute(gemm_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<128>::kTotal); FLLM_OCC(128); break;
+    default: cudaFuncSetAttribute(gemm_bf16_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256>::kTotal); FLLM_OCC(256); break;
+  }
+#undef FLLM_OCC
+  return n;
 }
 
 size_t gemm_bf16_workspace_bytes(int tokens, int features) {
@@ -641,6 +672,11 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
     splits = 1;
   while (splits > 1 && kCounterBytes + (size_t)splits * tiles * BM * bn * sizeof(float) > workspace_bytes) --splits;
   a.fixup = rs ? 1 : 0;
+  {
+    static int tune = -1;
+    if (tune < 0) { const char* e = getenv("FLLM_GEMM_TUNE"); tune = e ? atoi(e) : 0; }
+    a.tune = tune;
+  }
   if (!a.fixup)
     while (splits > 1 && kCounterBytes + (size_t)splits * a.M * a.N * sizeof(float) > workspace_bytes) --splits;
   a.kb_per_split = (a.k_blocks + splits - 1) / splits;
