@@ -53,8 +53,10 @@ class FusedTP:
             self.setup(hidden, max_tokens)
 
     # ------------------------------------------------------------------ setup
+    BCAST_ROWS = 128        # steps with at most this many tokens use the one-shot (broadcast) layout
+
     def _sizes(self):
-        rows_per_max = -(-self.max_tokens // self.size)
+        rows_per_max = max(-(-self.max_tokens // self.size), self.BCAST_ROWS)
         return (self.size * rows_per_max * self.hidden * 2, self.max_tokens * self.hidden * 2,
                 self.k.flag_words() * 4, self.size * self.ar_slot_bytes)
 
@@ -83,7 +85,7 @@ class FusedTP:
 
     def _make_ctx(self, rs, ag, flags, ar) -> None:
         self._tables = (list(rs), list(ag), list(flags), list(ar))
-        self.ctx = self.k.tp_ctx_create(self.size, self.rank, self.hidden, self.max_tokens,
+        self.ctx = self.k.tp_ctx_create(self.size, self.rank, self.hidden, self.max_tokens, self.BCAST_ROWS,
                                         self.device.index or 0, list(rs), list(ag), list(flags), list(ar),
                                         self.ar_slot_bytes, self.status)
         self.ag_local = self.k.symm_view(ag[self.rank], self.max_tokens * self.hidden * 2,
@@ -121,11 +123,21 @@ class FusedTP:
         return lo, min(tokens, lo + rp)
 
     # ------------------------------------------------------------------ fused steps
-    def linear_rs(self, x: torch.Tensor, w: torch.Tensor, bias=None) -> int:
-        return self.k.tp_linear_rs(self.ctx, x, w, bias, self.workspace)
+    def use_bcast(self, tokens: int) -> bool:
+        """Small steps (decode) are latency-bound: every rank pushes its partial sums to every
+        rank and reduces all rows itself - one cross-GPU dependency per projection instead of
+        two. Large steps (prefill) are bandwidth-bound: reduce-scatter + all-gather."""
+        return tokens <= self.BCAST_ROWS
 
-    def norm(self, residual_shard: torch.Tensor, tokens: int, has_partials: bool, norm_w, eps, w_offset=0.0) -> None:
-        self.k.tp_norm(self.ctx, residual_shard, tokens, has_partials, norm_w, float(eps), float(w_offset))
+    def linear_rs(self, x: torch.Tensor, w: torch.Tensor, bias=None, bcast: bool = False) -> int:
+        return self.k.tp_linear_rs(self.ctx, x, w, bias, self.workspace, bcast)
+
+    def norm(self, residual: torch.Tensor, tokens: int, has_partials: bool, norm_w, eps, w_offset=0.0,
+             bcast: bool = False) -> None:
+        """bcast=False: `residual` holds this rank's rows; normalised rows go to every rank's
+        gathered buffer. bcast=True: `residual` holds all rows; the output stays in the local
+        gathered buffer (``ag_local[:tokens]``)."""
+        self.k.tp_norm(self.ctx, residual, tokens, has_partials, norm_w, float(eps), float(w_offset), bcast)
 
     def linear_ag(self, tokens: int, w: torch.Tensor, bias=None, out=None) -> torch.Tensor:
         if out is None:

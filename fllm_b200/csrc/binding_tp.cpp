@@ -25,6 +25,7 @@ enum : int { kRsFlags = 0, kAgFlags = 8, kArFlags = 16, kRsConsumed = 24, kAgCon
 
 struct TpContext {
   int tp = 1, rank = 0, hidden = 0, max_tokens = 0, device = 0;
+  int bcast_rows = 0;        // row capacity per source of the receive buffer in broadcast mode
   void* rs_bufs[8] = {nullptr};
   void* ag_bufs[8] = {nullptr};
   uint32_t* flags[8] = {nullptr};
@@ -66,7 +67,7 @@ Tensor symm_view(int64_t p, int64_t bytes, int64_t device) {
 
 int64_t flag_words() { return kFlagWords; }
 
-int64_t tp_ctx_create(int64_t tp, int64_t rank, int64_t hidden, int64_t max_tokens, int64_t device,
+int64_t tp_ctx_create(int64_t tp, int64_t rank, int64_t hidden, int64_t max_tokens, int64_t bcast_rows, int64_t device,
                       std::vector<int64_t> rs_bufs, std::vector<int64_t> ag_bufs, std::vector<int64_t> flag_bufs,
                       std::vector<int64_t> ar_slots, int64_t ar_slot_bytes, const Tensor& status) {
   TORCH_CHECK(tp >= 1 && tp <= 8, "tensor-parallel degree must be in [1, 8]");
@@ -74,6 +75,7 @@ int64_t tp_ctx_create(int64_t tp, int64_t rank, int64_t hidden, int64_t max_toke
               (int64_t)ar_slots.size() == tp, "one address per rank expected");
   TpContext c;
   c.tp = (int)tp; c.rank = (int)rank; c.hidden = (int)hidden; c.max_tokens = (int)max_tokens; c.device = (int)device;
+  c.bcast_rows = (int)bcast_rows;
   for (int i = 0; i < tp; ++i) {
     c.rs_bufs[i] = reinterpret_cast<void*>(rs_bufs[i]);
     c.ag_bufs[i] = reinterpret_cast<void*>(ag_bufs[i]);
@@ -91,14 +93,16 @@ int64_t rows_per(const TpContext& c, int64_t tokens) { return (tokens + c.tp - 1
 
 // Row-parallel linear whose partial sums go straight to the owning ranks (no local output).
 int64_t tp_linear_rs(int64_t h, const Tensor& x, const Tensor& w, const optional<Tensor>& bias,
-                     const optional<Tensor>& workspace) {
+                     const optional<Tensor>& workspace, bool bcast) {
   TpContext& c = ctx_at(h);
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "x: bf16 rows");
   TORCH_CHECK(w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.stride(1) == 1 && w.size(0) == c.hidden, "w: [hidden, k]");
   TORCH_CHECK(x.size(0) <= c.max_tokens, "more tokens than the tensor-parallel buffers hold");
   c10::cuda::CUDAGuard guard(x.device());
   fllm::TpLinearArgs a{};
-  a.tp = c.tp; a.my_rank = c.rank; a.rows_per = (int)rows_per(c, x.size(0)); a.rs_ld = c.hidden;
+  a.tp = c.tp; a.my_rank = c.rank; a.rows_per = bcast ? c.bcast_rows : (int)rows_per(c, x.size(0)); a.rs_ld = c.hidden;
+  a.rs_bcast = bcast ? 1 : 0;
+  TORCH_CHECK(!bcast || x.size(0) <= c.bcast_rows, "too many tokens for the broadcast receive buffer");
   for (int i = 0; i < c.tp; ++i) { a.rs_bufs[i] = c.rs_bufs[i]; a.rs_flags[i] = c.flags[i] + kRsFlags; }
   const void* b = bias.has_value() && bias->defined() ? bias->data_ptr() : nullptr;
   void* ws = nullptr;
@@ -131,7 +135,7 @@ int64_t tp_linear_ag(int64_t h, int64_t tokens, const Tensor& w, const optional<
 
 // residual_shard (+= reduced partials) -> RMSNorm -> every rank's gathered buffer.
 void tp_norm(int64_t h, Tensor residual_shard, int64_t tokens, bool has_partials, const Tensor& norm_w, double eps,
-             double w_offset) {
+             double w_offset, bool bcast) {
   TpContext& c = ctx_at(h);
   TORCH_CHECK(residual_shard.scalar_type() == at::kBFloat16 && residual_shard.is_contiguous(), "residual shard: contiguous bf16");
   TORCH_CHECK(tokens <= c.max_tokens, "more tokens than the tensor-parallel buffers hold");
@@ -141,12 +145,13 @@ void tp_norm(int64_t h, Tensor residual_shard, int64_t tokens, bool has_partials
   uint32_t* f = c.flags[c.rank];
   a.rs_buf = has_partials ? c.rs_bufs[c.rank] : nullptr;
   a.rs_flags = f + kRsFlags; a.rs_consumed = f + kRsConsumed;
-  a.tp = c.tp; a.my_rank = c.rank; a.rows_per = (int)rows_per(c, tokens); a.tokens = (int)tokens; a.hidden = c.hidden;
-  a.rs_expected = has_partials ? (uint32_t)fllm::linear_rs_expected_signals((int)tokens, c.hidden, a.rows_per, c.rank) : 0;
+  a.tp = c.tp; a.my_rank = c.rank; a.rows_per = bcast ? c.bcast_rows : (int)rows_per(c, tokens); a.tokens = (int)tokens; a.hidden = c.hidden;
+  a.bcast = bcast ? 1 : 0;
+  a.rs_expected = has_partials ? (uint32_t)fllm::linear_rs_expected_signals((int)tokens, c.hidden, a.rows_per, bcast ? 0 : c.rank) : 0;
   a.norm_w = norm_w.data_ptr(); a.eps = (float)eps; a.w_offset = (float)w_offset;
   for (int i = 0; i < c.tp; ++i) { a.ag_bufs[i] = c.ag_bufs[i]; a.ag_flags[i] = c.flags[i] + kAgFlags; }
   a.cta_done = f + kNormDone; a.status = c.status;
-  const int my_rows = std::max<int64_t>(0, std::min<int64_t>(tokens, (int64_t)(c.rank + 1) * a.rows_per) - (int64_t)c.rank * a.rows_per);
+  const int my_rows = bcast ? (int)tokens : (int)std::max<int64_t>(0, std::min<int64_t>(tokens, (int64_t)(c.rank + 1) * a.rows_per) - (int64_t)c.rank * a.rows_per);
   TORCH_CHECK(residual_shard.numel() >= (int64_t)my_rows * c.hidden, "residual shard too small");
   fllm::tp_reduce_norm_allgather(a, cur_stream());
 }
@@ -180,10 +185,10 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("symm_close(int ptr) -> ()", &symm_close);
   m.def("symm_view(int ptr, int bytes, int device) -> Tensor", &symm_view);
   m.def("flag_words() -> int", &flag_words);
-  m.def("tp_ctx_create(int tp, int rank, int hidden, int max_tokens, int device, int[] rs_bufs, int[] ag_bufs, int[] flag_bufs, int[] ar_slots, int ar_slot_bytes, Tensor status) -> int", &tp_ctx_create);
-  m.def("tp_linear_rs(int ctx, Tensor x, Tensor w, Tensor? bias, Tensor? workspace) -> int", &tp_linear_rs);
+  m.def("tp_ctx_create(int tp, int rank, int hidden, int max_tokens, int bcast_rows, int device, int[] rs_bufs, int[] ag_bufs, int[] flag_bufs, int[] ar_slots, int ar_slot_bytes, Tensor status) -> int", &tp_ctx_create);
+  m.def("tp_linear_rs(int ctx, Tensor x, Tensor w, Tensor? bias, Tensor? workspace, bool bcast) -> int", &tp_linear_rs);
   m.def("tp_linear_ag(int ctx, int tokens, Tensor w, Tensor? bias, Tensor(a!) y, Tensor? workspace) -> int", &tp_linear_ag);
-  m.def("tp_norm(int ctx, Tensor(a!) residual_shard, int tokens, bool has_partials, Tensor norm_w, float eps, float w_offset) -> ()", &tp_norm);
+  m.def("tp_norm(int ctx, Tensor(a!) residual_shard, int tokens, bool has_partials, Tensor norm_w, float eps, float w_offset, bool bcast) -> ()", &tp_norm);
   m.def("tp_allreduce(int ctx, Tensor input, Tensor(a!) output) -> ()", &tp_allreduce);
   m.def("linear_rs_expected(int tokens, int n, int rows_per, int dest) -> int", &linear_rs_expected);
 }

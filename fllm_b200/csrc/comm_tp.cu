@@ -36,7 +36,7 @@ __device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
 
 template <int VEC_ITERS>
 __global__ void __launch_bounds__(256) tp_reduce_norm_ag_kernel(const TpNormArgs a) {
-  const int my_rows = tp_rows_owned(a.tokens, a.rows_per, a.my_rank);
+  const int my_rows = a.bcast ? a.tokens : tp_rows_owned(a.tokens, a.rows_per, a.my_rank);
   const int row = blockIdx.x;                         // local row index
   __shared__ float red[8];
   __shared__ int failed;
@@ -70,16 +70,26 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_ag_kernel(const TpNormArgs
         }
         if (a.rs_buf && !failed) {
           float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int s = 0; s < a.tp; ++s) {            // fixed order: same bits on every rank
-            const __nv_bfloat16* pr = reinterpret_cast<const __nv_bfloat16*>(a.rs_buf) +
-                                      ((size_t)s * a.rows_per + row) * a.hidden;
-            const uint4 pv = ld_cg_u4(reinterpret_cast<const uint4*>(pr) + i);   // L2: written by a peer
-            const uint32_t* pw = reinterpret_cast<const uint32_t*>(&pv);
+          // all sources' vectors are requested before any is used (one L2 round trip, not tp)
+          uint4 pv[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = unpack_bf16x2(pw[j]);
-              d[2 * j] += f.x;
-              d[2 * j + 1] += f.y;
+          for (int s = 0; s < 8; ++s) {
+            if (s < a.tp) {
+              const __nv_bfloat16* pr = reinterpret_cast<const __nv_bfloat16*>(a.rs_buf) +
+                                        ((size_t)s * a.rows_per + row) * a.hidden;
+              pv[s] = ld_cg_u4(reinterpret_cast<const uint4*>(pr) + i);   // L2: written by a peer
+            }
+          }
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {                 // fixed order: same bits on every rank
+            if (s < a.tp) {
+              const uint32_t* pw = reinterpret_cast<const uint32_t*>(&pv[s]);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = unpack_bf16x2(pw[j]);
+                d[2 * j] += f.x;
+                d[2 * j + 1] += f.y;
+              }
             }
           }
 #pragma unroll
@@ -115,7 +125,7 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_ag_kernel(const TpNormArgs
 #pragma unroll
     for (int i = 0; i < 8; ++i) tot += red[i];
     const float inv = rsqrtf(tot / (float)a.hidden + a.eps);
-    const int grow = a.my_rank * a.rows_per + row;    // global token row
+    const int grow = a.bcast ? row : a.my_rank * a.rows_per + row;    // global token row
     const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(a.norm_w);
 #pragma unroll
     for (int it = 0; it < VEC_ITERS; ++it) {
@@ -131,16 +141,20 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_ag_kernel(const TpNormArgs
           ow[j] = pack_bf16x2(vals[it][2 * j] * inv * (g.x + a.w_offset),
                               vals[it][2 * j + 1] * inv * (g.y + a.w_offset));
         }
-        for (int d = 0; d < a.tp; ++d) {
-          const int dst = (a.my_rank + d) % a.tp;     // stagger destinations across ranks
-          reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.ag_bufs[dst]) + (size_t)grow * a.hidden)[i] = o;
+        if (a.bcast) {
+          reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.ag_bufs[a.my_rank]) + (size_t)grow * a.hidden)[i] = o;
+        } else {
+          for (int d = 0; d < a.tp; ++d) {
+            const int dst = (a.my_rank + d) % a.tp;     // stagger destinations across ranks
+            reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.ag_bufs[dst]) + (size_t)grow * a.hidden)[i] = o;
+          }
         }
       }
     }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x < a.tp)
-      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.ag_flags[threadIdx.x] + a.my_rank) : "memory");
+    if (!a.bcast) __syncthreads();            // every thread's peer stores precede the fences below
+    if (!a.bcast && threadIdx.x < a.tp) __threadfence_system();
+    if (!a.bcast && threadIdx.x < a.tp)
+      asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(a.ag_flags[threadIdx.x] + a.my_rank) : "memory");
   }
   if (threadIdx.x == 0) {
     __threadfence();
@@ -158,7 +172,7 @@ void tp_reduce_norm_allgather(const TpNormArgs& a, cudaStream_t s) {
     throw std::runtime_error("tp_reduce_norm_allgather: hidden must be a multiple of 8 and at most 16384");
   if (a.tp < 1 || a.tp > 8) throw std::runtime_error("tp_reduce_norm_allgather: tp must be in [1, 8]");
   const int lo = a.my_rank * a.rows_per;
-  const int my_rows = std::max(0, std::min(a.tokens, lo + a.rows_per) - lo);
+  const int my_rows = a.bcast ? a.tokens : std::max(0, std::min(a.tokens, lo + a.rows_per) - lo);
   const int grid = std::max(my_rows, 1);              // a rank without rows still does the bookkeeping
   const int iters = (a.hidden / 8 + 255) / 256;
   switch (iters) {
@@ -184,10 +198,11 @@ __global__ void __launch_bounds__(256) tp_allreduce_kernel(const TpAllReduceArgs
       reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.slots[dst]) + (size_t)a.my_rank * a.slot_bytes)[i] = v;
     }
   }
-  __threadfence_system();
   __syncthreads();
-  if (threadIdx.x < a.tp)
-    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.flags[threadIdx.x] + a.my_rank) : "memory");
+  if (threadIdx.x < a.tp) {
+    __threadfence_system();
+    asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(a.flags[threadIdx.x] + a.my_rank) : "memory");
+  }
   // wait for every source's gridDim.x bumps
   __shared__ int failed;
   if (threadIdx.x == 0) failed = 0;

@@ -23,6 +23,7 @@ struct TpLinearArgs {
   void* rs_bufs[8];
   uint32_t* rs_flags[8];
   int tp, my_rank, rows_per;
+  int rs_bcast;              // 1: push every row to every rank (one-shot all-reduce layout)
   long long rs_ld;
   const uint32_t* ag_flags;
   uint32_t* ag_consumed;
@@ -46,6 +47,7 @@ struct TpNormArgs {
   void* ag_bufs[8];          // every rank's gathered-activation buffer [tokens][hidden]
   uint32_t* ag_flags[8];     // every rank's arrival counters; this rank bumps entry [my_rank]
   int tp, my_rank, rows_per, tokens, hidden;
+  int bcast;                 // 1: all rows are local (partials were broadcast); output stays local
   unsigned int* cta_done;
   int* status;
 };

@@ -63,6 +63,7 @@ struct GemmArgs {
   __nv_bfloat16* rs_bufs[kMaxTp];
   uint32_t* rs_flags[kMaxTp];
   int tp, my_rank, rows_per;
+  int rs_bcast;                 // 1: every rank receives every row (rows_per = row capacity per source)
   long long rs_ld;
   // all-gather -> GEMM: the activation operand lives in a local buffer that peers fill row
   // block by row block; the TMA producer waits for the owning rank's flag before it loads.
@@ -157,30 +158,48 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
+    int pre = 0;                 // leading k-blocks of the first item whose weight tile is already in flight
+    if (lane == 0 && !grouped) {
+      const int w = blockIdx.x;
+      if (w < total && !(p.tune & 2)) {
+        const int split = w / tiles;
+        const int t = w - split * tiles;
+        const int n_idx = t / p.m_tiles;
+        const int m_idx = t - n_idx * p.m_tiles;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
+        pre = min(kb1 - kb0, STAGES);
+        for (int i = 0; i < pre; ++i) {
+          mbar_expect_tx(&full_bar[i], S::kStageBytes);
+          if (p.transposed) tma_load_2d(sA + i * S::kABytes, &tma_a, &full_bar[i], (kb0 + i) * BK, m_idx * BM);
+          else tma_load_2d(sB + i * S::kBBytes, &tma_b, &full_bar[i], (kb0 + i) * BK, n_idx * BN);
+        }
+      }
+    }
+    if (!grouped) pdl_wait();
+    uint32_t arrived = 0;        // bit s: rank s delivered all of its rows of the gathered operand
+    if (p.ag_flags && p.transposed) {
+      // decode orientation: every tile needs every rank's rows, so the whole warp polls the
+      // arrival counters at once (one lane per source rank) instead of one after the other
+      bool mine_ok = true;
+      if (lane < p.tp) {
+        const int rows = rows_owned(p.ag_tokens, p.rows_per, lane);
+        if (rows > 0) mine_ok = wait_flag_ge(p.ag_flags + lane, p.ag_consumed[lane] + (uint32_t)rows, kPeerWaitPolls);
+      }
+      if (!__all_sync(0xffffffffu, mine_ok)) {
+        if (lane == 0) {
+          if (p.status) atomicCAS(p.status, FLLM_OK, FLLM_ERR_PEER_TIMEOUT);
+          *abort_flag = 1;
+        }
+      }
+      arrived = 0xffffffffu;
+      asm volatile("fence.proxy.async;" ::: "memory");
+      __syncwarp();
+    }
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      bool ok = true;
-      uint32_t arrived = 0;      // bit s: rank s delivered all of its rows of the gathered operand
-      int pre = 0;               // leading k-blocks of the first item whose weight tile is already in flight
-      if (!grouped) {
-        const int w = blockIdx.x;
-        if (w < total && !(p.tune & 2)) {
-          const int split = w / tiles;
-          const int t = w - split * tiles;
-          const int n_idx = t / p.m_tiles;
-          const int m_idx = t - n_idx * p.m_tiles;
-          const int kb0 = split * p.kb_per_split;
-          const int kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
-          pre = min(kb1 - kb0, STAGES);
-          for (int i = 0; i < pre; ++i) {
-            mbar_expect_tx(&full_bar[i], S::kStageBytes);
-            if (p.transposed) tma_load_2d(sA + i * S::kABytes, &tma_a, &full_bar[i], (kb0 + i) * BK, m_idx * BM);
-            else tma_load_2d(sB + i * S::kBBytes, &tma_b, &full_bar[i], (kb0 + i) * BK, n_idx * BN);
-          }
-        }
-        pdl_wait();
-      }
+      bool ok = *abort_flag == 0;
       for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
         const int split = w / tiles;
         const int t = w - split * tiles;
@@ -278,8 +297,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
       constexpr int CH = BN < 32 ? 16 : 32;
       // where the bf16 row of a token goes: the local output, or the owning rank's receive buffer
       const bool rs = p.rs_bufs[0] != nullptr;
-      auto row_ptr = [&](int token) -> __nv_bfloat16* {
+      // bcast: every rank receives every row (one-shot all-reduce layout [src][token][hidden]);
+      // otherwise a row goes to the single rank that owns it (reduce-scatter layout)
+      const int ndst = (rs && p.rs_bcast) ? p.tp : 1;
+      auto row_ptr = [&](int token, int d) -> __nv_bfloat16* {
         if (!rs) return p.out + (size_t)token * p.ldc;
+        if (p.rs_bcast) {
+          const int dst = (p.my_rank + d) % p.tp;      // stagger destinations across ranks
+          return p.rs_bufs[dst] + ((size_t)p.my_rank * p.rows_per + token) * p.rs_ld;
+        }
         const int owner = token / p.rows_per;
         return p.rs_bufs[owner] + ((size_t)p.my_rank * p.rows_per + (token - owner * p.rows_per)) * p.rs_ld;
       };
@@ -293,7 +319,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
         const int n0 = n_base + c0;
         if (!p.transposed) {
           if (m < p.M) {
-            __nv_bfloat16* dst = row_ptr(m) + n0;
 #pragma unroll
             for (int c = 0; c < CH; c += 8) {
               if (n0 + c < p.N) {
@@ -315,7 +340,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
                 o.y = pack_bf16x2(o8[2], o8[3]);
                 o.z = pack_bf16x2(o8[4], o8[5]);
                 o.w = pack_bf16x2(o8[6], o8[7]);
-                *reinterpret_cast<uint4*>(dst + c) = o;
+                for (int d = 0; d < ndst; ++d) *reinterpret_cast<uint4*>(row_ptr(m, d) + n0 + c) = o;
               }
             }
           }
@@ -328,7 +353,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
             const int n = n0 + c + (odd ? 1 : 0);
             const int mm = odd ? m - 1 : m;
             const uint32_t packed = odd ? pack_bf16x2(recv, own1) : pack_bf16x2(own0, recv);
-            if (n < p.N && mm < p.M) *reinterpret_cast<uint32_t*>(row_ptr(n) + mm) = packed;
+            if (n < p.N && mm < p.M)
+              for (int d = 0; d < ndst; ++d) *reinterpret_cast<uint32_t*>(row_ptr(n, d) + mm) = packed;
           }
         } else {
           // Transpose through a per-warp staging tile so that every store is 16 bytes: lanes hold
@@ -346,13 +372,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
             const int n = n0 + c;
             if (n < p.N && mm0 < p.M) {
               const uint4 val = *reinterpret_cast<const uint4*>(stg + c * 32 + f0);
-              __nv_bfloat16* dst = row_ptr(n) + mm0;
-              if (p.vec16) {
-                *reinterpret_cast<uint4*>(dst) = val;
-              } else {
-                const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
+              for (int d = 0; d < ndst && !(p.tune & 16); ++d) {
+                __nv_bfloat16* dst = row_ptr(n, d) + mm0;
+                if (p.vec16) {
+                  *reinterpret_cast<uint4*>(dst) = val;
+                } else {
+                  const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
 #pragma unroll
-                for (int i = 0; i < 4; ++i) reinterpret_cast<uint32_t*>(dst)[i] = w4[i];
+                  for (int i = 0; i < 4; ++i) reinterpret_cast<uint32_t*>(dst)[i] = w4[i];
+                }
               }
             }
           }
@@ -453,7 +481,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
                 }
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
-                  if (sp0 + j < p.k_splits) {
+                  if (sp0 + j < p.k_splits && !(p.tune & 8)) {
 #pragma unroll
                     for (int c = 0; c < 16; ++c) v[h + c] += tv[j][c];
                   }
@@ -464,18 +492,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is reused by the next tile
       }
-      if (rs && emitted) {
+      if (rs && emitted && !(p.tune & 4)) {
         // publish this warp's share of the tile: stores -> system fence -> one flag bump per
         // destination rank that owns token rows of the tile
-        __threadfence_system();
+        // One system-scope fence per warp, not per thread: the warp barrier orders the lanes'
+        // stores before lane 0's fence, the second barrier orders the fence before the bumps.
         __syncwarp();
-        if (lane == 0) {
-          const int tokens = p.transposed ? p.N : p.M;
-          const int t_lo = p.transposed ? n_idx * BN : m_idx * BM;
-          const int t_hi = min(tokens, t_lo + (p.transposed ? BN : BM));
-          if (t_hi > t_lo)
-            for (int d = t_lo / p.rows_per; d <= (t_hi - 1) / p.rows_per; ++d)
-              asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.rs_flags[d] + p.my_rank) : "memory");
+        if (lane == 0) __threadfence_system();
+        __syncwarp();
+        const int tokens = p.transposed ? p.N : p.M;
+        const int t_lo = p.transposed ? n_idx * BN : m_idx * BM;
+        const int t_hi = min(tokens, t_lo + (p.transposed ? BN : BM));
+        if (t_hi > t_lo) {
+          // the bump itself can be relaxed, one lane per destination
+          const int d = p.rs_bcast ? lane : t_lo / p.rows_per + lane;
+          const int d_hi = p.rs_bcast ? p.tp - 1 : (t_hi - 1) / p.rows_per;
+          if (d <= d_hi)
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(p.rs_flags[d] + p.my_rank) : "memory");
         }
       }
       acc ^= 1;
@@ -628,6 +661,7 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
   if (tpa) {
     if (tpa->tp > kMaxTp) throw std::runtime_error("linear_bf16: tensor-parallel degree above 8");
     a.tp = tpa->tp; a.my_rank = tpa->my_rank; a.rows_per = tpa->rows_per; a.rs_ld = tpa->rs_ld;
+    a.rs_bcast = tpa->rs_bcast;
     for (int i = 0; i < kMaxTp; ++i) {
       a.rs_bufs[i] = reinterpret_cast<__nv_bfloat16*>(tpa->rs_bufs[i]);
       a.rs_flags[i] = tpa->rs_flags[i];
@@ -672,6 +706,7 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
     splits = 1;
   while (splits > 1 && kCounterBytes + (size_t)splits * tiles * BM * bn * sizeof(float) > workspace_bytes) --splits;
   a.fixup = rs ? 1 : 0;
+  if (rs && force_splits <= 0) splits = min(splits, max(1, min(4, a.k_blocks / 8)));   // the in-kernel fixup is serial per tile: keep it short
   {
     static int tune = -1;
     if (tune < 0) { const char* e = getenv("FLLM_GEMM_TUNE"); tune = e ? atoi(e) : 0; }

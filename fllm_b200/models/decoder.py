@@ -146,15 +146,26 @@ class Decoder:
         producer waits for those rows. Returns the local vocabulary slice of the logits."""
         cfg, ops, tp, sp = self.cfg, self.ops, self.tp, self.spec
         T = b.token_ids.shape[0]
-        lo, hi = tp.my_rows(T)
-        if hi > lo:
-            x = ops.embed(b.token_ids[lo:hi].contiguous(), self.w.embed, cfg.embed_scale)
-        else:
-            x = torch.zeros(1, cfg.hidden_size, dtype=self.w.embed.dtype, device=self.w.embed.device)
+        bc = tp.use_bcast(T)
+        if bc:                       # residual replicated: all rows on every rank
+            x = ops.embed(b.token_ids, self.w.embed, cfg.embed_scale)
+        else:                        # residual sequence-sharded: only the rows this rank owns
+            lo, hi = tp.my_rows(T)
+            if hi > lo:
+                x = ops.embed(b.token_ids[lo:hi].contiguous(), self.w.embed, cfg.embed_scale)
+            else:
+                x = torch.zeros(1, cfg.hidden_size, dtype=self.w.embed.dtype, device=self.w.embed.device)
+        h_all = tp.ag_local[:T]      # normalised activations of all rows (local buffer)
+
+        def col_linear(w, bias=None):
+            # broadcast mode: the norm kernel already reduced everything locally -> plain GEMM;
+            # scatter/gather mode: the GEMM's TMA producer waits for the peers' rows
+            return ops.linear(h_all, w, bias) if bc else tp.linear_ag(T, w, bias)
+
         partials = False
         for li, lw in zip(self.layer_range, self.w.layers):
-            tp.norm(x, T, partials, lw.attn_norm, cfg.rms_eps, cfg.norm_weight_offset)
-            qkv = tp.linear_ag(T, lw.wqkv, lw.bqkv)
+            tp.norm(x, T, partials, lw.attn_norm, cfg.rms_eps, cfg.norm_weight_offset, bc)
+            qkv = col_linear(lw.wqkv, lw.bqkv)
             local = li - self.layer_range.start
             kc, vc = self.kv.k(local), self.kv.v(local)
             ops.rope_kv_write(qkv, b.positions, b.slots, self.inv_freq, lw.q_norm, lw.k_norm, kc, vc,
@@ -163,15 +174,23 @@ class Decoder:
             q = qkv[:, : sp.hq_local * cfg.head_dim]
             a = ops.attention(q, kc, vc, b.block_tables, b.row_seq, b.positions, sp.hq_local, sp.hkv_local,
                               cfg.head_dim, self.scale, cfg.layer_window(li), lw.sinks, cfg.attn_softcap, meta=b)
-            tp.linear_rs(a, lw.wo, lw.bo)
-            tp.norm(x, T, True, lw.ffn_norm, cfg.rms_eps, cfg.norm_weight_offset)
-            gu = tp.linear_ag(T, lw.w_gate_up)
+            tp.linear_rs(a, lw.wo, lw.bo, bc)
+            tp.norm(x, T, True, lw.ffn_norm, cfg.rms_eps, cfg.norm_weight_offset, bc)
+            gu = col_linear(lw.w_gate_up)
             act = ops.glu(gu, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit)
-            tp.linear_rs(act, lw.w_down)
+            tp.linear_rs(act, lw.w_down, None, bc)
             partials = True
             if hasattr(ops, "launches"):
-                ops.launches += 6
-        tp.norm(x, T, partials, self.w.final_norm, cfg.rms_eps, cfg.norm_weight_offset)
+                ops.launches += 4 if bc else 6
+        tp.norm(x, T, partials, self.w.final_norm, cfg.rms_eps, cfg.norm_weight_offset, bc)
+        if bc:
+            hs = h_all if (b.all_decode and b.logit_rows.numel() == T) else ops.gather_rows(h_all, b.logit_rows)
+            lg = ops.linear(hs, self.w.lm_head)
+            if hasattr(ops, "launches"):
+                ops.launches += 1
+            if cfg.logit_softcap > 0:
+                lg = (cfg.logit_softcap * torch.tanh(lg.float() / cfg.logit_softcap)).to(lg.dtype)
+            return lg
         # the head runs on every row (it is the consumer that retires the gathered rows); the
         # wanted rows are selected afterwards
         lg = tp.linear_ag(T, self.w.lm_head)

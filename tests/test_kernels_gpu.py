@@ -269,6 +269,15 @@ def test_fused_tp_chain_single_device_emulation(tp, T):
             r.norm(sh, T, True, normw, 1e-6)
         outs = [r.linear_ag(T, w2) for r in ranks]
         torch.cuda.synchronize()
+        if T <= 128:
+            # one-shot layout: partial sums broadcast to every rank, every rank reduces all rows
+            fulls = [res_full.clone() for _ in ranks]
+            for r, x, w in zip(ranks, xs, ws):
+                r.linear_rs(x, w, None, True)
+            for r, f in zip(ranks, fulls):
+                r.norm(f, T, True, normw, 1e-6, 0.0, True)
+            torch.cuda.synchronize()
+            gathered = [r.ag_local[:T].clone() for r in ranks]
         part = sum(x.float() @ w.float().t() for x, w in zip(xs, ws))
         new_res = (res_full.float() + part.to(torch.bfloat16).float()).to(torch.bfloat16)
         hn = new_res.float() * torch.rsqrt(new_res.float().pow(2).mean(-1, keepdim=True) + 1e-6) * normw.float()
@@ -281,6 +290,11 @@ def test_fused_tp_chain_single_device_emulation(tp, T):
         # every rank computed bit-identical gathered activations
         for o in outs[1:]:
             assert torch.equal(o, outs[0])
+        if T <= 128:
+            for f, gth in zip(fulls, gathered):
+                _close(f, new_res, 3e-2)
+                _close(gth, hn, 3e-2)
+                assert torch.equal(gth, gathered[0])
 
 
 def test_fused_tp_allreduce_single_device_emulation():
