@@ -39,6 +39,7 @@ class FusedTP:
         self.group = group
         self.hidden, self.max_tokens, self.ar_slot_bytes = hidden, max_tokens, ar_slot_bytes
         self.workspace = None
+        self._rs_expected = 0
         self._owned: List[int] = []
         self._imported: List[int] = []
         self.ctx = -1
@@ -130,14 +131,19 @@ class FusedTP:
         return tokens <= self.BCAST_ROWS
 
     def linear_rs(self, x: torch.Tensor, w: torch.Tensor, bias=None, bcast: bool = False) -> int:
-        return self.k.tp_linear_rs(self.ctx, x, w, bias, self.workspace, bcast)
+        """Returns (and remembers) how many arrival-counter bumps each destination receives from
+        a source for this projection: the following ``norm`` waits for exactly that many. Every
+        rank runs the same shapes, so the local value equals the peers'."""
+        self._rs_expected = int(self.k.tp_linear_rs(self.ctx, x, w, bias, self.workspace, bcast))
+        return self._rs_expected
 
     def norm(self, residual: torch.Tensor, tokens: int, has_partials: bool, norm_w, eps, w_offset=0.0,
              bcast: bool = False) -> None:
         """bcast=False: `residual` holds this rank's rows; normalised rows go to every rank's
         gathered buffer. bcast=True: `residual` holds all rows; the output stays in the local
         gathered buffer (``ag_local[:tokens]``)."""
-        self.k.tp_norm(self.ctx, residual, tokens, has_partials, norm_w, float(eps), float(w_offset), bcast)
+        expected = self._rs_expected if has_partials else 0
+        self.k.tp_norm(self.ctx, residual, tokens, expected, norm_w, float(eps), float(w_offset), bcast)
 
     def linear_ag(self, tokens: int, w: torch.Tensor, bias=None, out=None) -> torch.Tensor:
         if out is None:

@@ -547,7 +547,8 @@ static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int mi
     const int ctas = num_seqs * p.hkv;
     const int pages = (max_kv_len + kPage - 1) / kPage;
     int splits = 1;
-    if (ctas < 2 * sm_count()) splits = min(min((2 * sm_count() + ctas - 1) / ctas, (pages + 7) / 8), 32);
+    // a grid of at least one CTA per SM streams KV well enough; splitting costs a merge launch
+    if (ctas < sm_count()) splits = min(min((2 * sm_count() + ctas - 1) / ctas, (pages + 7) / 8), 32);
     splits = max(splits, 1);
     // partials of prefill sequences do not exist, so a mixed batch is never split
     if (max_q_len > decode_max_q || !workspace) splits = 1;

@@ -108,8 +108,11 @@ int64_t tp_linear_rs(int64_t h, const Tensor& x, const Tensor& w, const optional
   void* ws = nullptr;
   size_t ws_bytes = 0;
   if (workspace.has_value() && workspace->defined()) { ws = workspace->data_ptr(); ws_bytes = workspace->nbytes(); }
-  return fllm::linear_bf16_tp(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), b, nullptr, c.hidden,
-                              (int)x.size(0), (int)w.size(0), (int)x.size(1), ws, ws_bytes, c.status, 0, &a, cur_stream());
+  int expected = 0;
+  a.expected_out = &expected;
+  fllm::linear_bf16_tp(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), b, nullptr, c.hidden,
+                       (int)x.size(0), (int)w.size(0), (int)x.size(1), ws, ws_bytes, c.status, 0, &a, cur_stream());
+  return expected;      // what the consumer's norm kernel has to wait for from every source rank
 }
 
 // Column-parallel linear whose activation operand is the gathered buffer peers fill.
@@ -134,8 +137,9 @@ int64_t tp_linear_ag(int64_t h, int64_t tokens, const Tensor& w, const optional<
 }
 
 // residual_shard (+= reduced partials) -> RMSNorm -> every rank's gathered buffer.
-void tp_norm(int64_t h, Tensor residual_shard, int64_t tokens, bool has_partials, const Tensor& norm_w, double eps,
+void tp_norm(int64_t h, Tensor residual_shard, int64_t tokens, int64_t expected, const Tensor& norm_w, double eps,
              double w_offset, bool bcast) {
+  const bool has_partials = expected > 0;
   TpContext& c = ctx_at(h);
   TORCH_CHECK(residual_shard.scalar_type() == at::kBFloat16 && residual_shard.is_contiguous(), "residual shard: contiguous bf16");
   TORCH_CHECK(tokens <= c.max_tokens, "more tokens than the tensor-parallel buffers hold");
@@ -147,7 +151,7 @@ void tp_norm(int64_t h, Tensor residual_shard, int64_t tokens, bool has_partials
   a.rs_flags = f + kRsFlags; a.rs_consumed = f + kRsConsumed;
   a.tp = c.tp; a.my_rank = c.rank; a.rows_per = bcast ? c.bcast_rows : (int)rows_per(c, tokens); a.tokens = (int)tokens; a.hidden = c.hidden;
   a.bcast = bcast ? 1 : 0;
-  a.rs_expected = has_partials ? (uint32_t)fllm::linear_rs_expected_signals((int)tokens, c.hidden, a.rows_per, bcast ? 0 : c.rank) : 0;
+  a.rs_expected = (uint32_t)expected;
   a.norm_w = norm_w.data_ptr(); a.eps = (float)eps; a.w_offset = (float)w_offset;
   for (int i = 0; i < c.tp; ++i) { a.ag_bufs[i] = c.ag_bufs[i]; a.ag_flags[i] = c.flags[i] + kAgFlags; }
   a.cta_done = f + kNormDone; a.status = c.status;
@@ -188,7 +192,7 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("tp_ctx_create(int tp, int rank, int hidden, int max_tokens, int bcast_rows, int device, int[] rs_bufs, int[] ag_bufs, int[] flag_bufs, int[] ar_slots, int ar_slot_bytes, Tensor status) -> int", &tp_ctx_create);
   m.def("tp_linear_rs(int ctx, Tensor x, Tensor w, Tensor? bias, Tensor? workspace, bool bcast) -> int", &tp_linear_rs);
   m.def("tp_linear_ag(int ctx, int tokens, Tensor w, Tensor? bias, Tensor(a!) y, Tensor? workspace) -> int", &tp_linear_ag);
-  m.def("tp_norm(int ctx, Tensor(a!) residual_shard, int tokens, bool has_partials, Tensor norm_w, float eps, float w_offset, bool bcast) -> ()", &tp_norm);
+  m.def("tp_norm(int ctx, Tensor(a!) residual_shard, int tokens, int expected, Tensor norm_w, float eps, float w_offset, bool bcast) -> ()", &tp_norm);
   m.def("tp_allreduce(int ctx, Tensor input, Tensor(a!) output) -> ()", &tp_allreduce);
   m.def("linear_rs_expected(int tokens, int n, int rows_per, int dest) -> int", &linear_rs_expected);
 }

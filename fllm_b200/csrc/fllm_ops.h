@@ -28,6 +28,7 @@ struct TpLinearArgs {
   const uint32_t* ag_flags;
   uint32_t* ag_consumed;
   unsigned int* cta_done;
+  int* expected_out;         // host int: arrival-counter bumps every destination will see from this rank
 };
 int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, const void* bias,
                    void* y, long long ldy, int T, int N, int K, void* workspace,

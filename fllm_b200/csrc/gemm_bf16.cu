@@ -560,6 +560,53 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, i
   *reinterpret_cast<uint2*>(out + (size_t)r * ldc + c) = o;
 }
 
+// Split-K reduction whose result leaves the GPU: out[token][feature] (bf16) is stored into the
+// receive buffer of EVERY rank (one-shot all-reduce layout [src][token][hidden]) and each CTA then
+// bumps every rank's arrival counter once. Many CTAs push at the same time, so the NVLink stores
+// of a small decode step are spread over the whole machine instead of a few epilogue warps.
+struct ReducePushArgs {
+  __nv_bfloat16* rs_bufs[kMaxTp];
+  uint32_t* rs_flags[kMaxTp];
+  int tp, my_rank, rows_cap;
+  long long rs_ld;
+};
+
+__global__ void __launch_bounds__(256)
+splitk_reduce_push_kernel(const float* __restrict__ ws, int splits, int rows, int cols,
+                          const __nv_bfloat16* __restrict__ bias, const ReducePushArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t n = (size_t)rows * cols;
+  const size_t i4 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i4 < n) {
+    float4 acc = __ldcg(reinterpret_cast<const float4*>(ws + i4));
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(ws + (size_t)s * n + i4));
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const int r = (int)(i4 / cols);
+    const int c = (int)(i4 - (size_t)r * cols);
+    if (bias) {
+      acc.x += __bfloat162float(bias[c]);
+      acc.y += __bfloat162float(bias[c + 1]);
+      acc.z += __bfloat162float(bias[c + 2]);
+      acc.w += __bfloat162float(bias[c + 3]);
+    }
+    uint2 o;
+    o.x = pack_bf16x2(acc.x, acc.y);
+    o.y = pack_bf16x2(acc.z, acc.w);
+    for (int d = 0; d < a.tp; ++d) {
+      const int dst = (a.my_rank + d) % a.tp;
+      *reinterpret_cast<uint2*>(a.rs_bufs[dst] + ((size_t)a.my_rank * a.rows_cap + r) * a.rs_ld + c) = o;
+    }
+  }
+  __syncthreads();                       // all stores of the CTA precede the fences below
+  if (threadIdx.x < a.tp) {
+    __threadfence_system();
+    asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(a.rs_flags[threadIdx.x] + a.my_rank) : "memory");
+  }
+}
+
 template <int BN>
 static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, int grid,
                         cudaStream_t stream) {
@@ -705,8 +752,11 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
   if (splits > 1 && (!workspace || workspace_bytes <= kCounterBytes || (size_t)tiles * 4 > kCounterBytes || bn > 128))
     splits = 1;
   while (splits > 1 && kCounterBytes + (size_t)splits * tiles * BM * bn * sizeof(float) > workspace_bytes) --splits;
-  a.fixup = rs ? 1 : 0;
-  if (rs && force_splits <= 0) splits = min(splits, max(1, min(4, a.k_blocks / 8)));   // the in-kernel fixup is serial per tile: keep it short
+  // Broadcast destination + split-K: the GEMM keeps its fast local split path and the reduction
+  // kernel does the pushing. Scatter destination + split-K: the last-arriving CTA finishes the tile.
+  const bool push_reduce = rs && tpa->rs_bcast && splits > 1;
+  a.fixup = (rs && !push_reduce) ? 1 : 0;
+  if (a.fixup && force_splits <= 0) splits = min(splits, max(1, min(4, a.k_blocks / 8)));   // the in-kernel fixup is serial per tile: keep it short
   {
     static int tune = -1;
     if (tune < 0) { const char* e = getenv("FLLM_GEMM_TUNE"); tune = e ? atoi(e) : 0; }
@@ -722,6 +772,14 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
   a.vec16 = rs ? ((a.rs_ld & 7) == 0)
                : ((ldy & 7) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0);
 
+  const bool push = push_reduce && a.k_splits > 1;
+  if (push) {                      // the GEMM itself writes local partials only
+    for (int i = 0; i < kMaxTp; ++i) { a.rs_bufs[i] = nullptr; a.rs_flags[i] = nullptr; }
+  }
+  if (tpa && tpa->expected_out) {
+    if (push) *tpa->expected_out = (int)(((size_t)T * N / 4 + 255) / 256);
+    else if (rs) *tpa->expected_out = linear_rs_expected_signals(T, N, tpa->rs_bcast ? T : tpa->rows_per, tpa->rs_bcast ? 0 : tpa->my_rank);
+  }
   const int grid = min(tiles * a.k_splits, sms * (bn <= 64 ? 2 : 1));
   switch (bn) {
     case 16: launch_gemm<16>(ta, tb, a, grid, stream); break;
@@ -729,6 +787,18 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
     case 64: launch_gemm<64>(ta, tb, a, grid, stream); break;
     case 128: launch_gemm<128>(ta, tb, a, grid, stream); break;
     default: launch_gemm<256>(ta, tb, a, grid, stream); break;
+  }
+  if (push) {
+    ReducePushArgs ra{};
+    for (int i = 0; i < tpa->tp; ++i) {
+      ra.rs_bufs[i] = reinterpret_cast<__nv_bfloat16*>(tpa->rs_bufs[i]);
+      ra.rs_flags[i] = tpa->rs_flags[i];
+    }
+    ra.tp = tpa->tp; ra.my_rank = tpa->my_rank; ra.rows_cap = tpa->rows_per; ra.rs_ld = tpa->rs_ld;
+    const int blocks = (int)(((size_t)T * N / 4 + 255) / 256);
+    launch_pdl(splitk_reduce_push_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)a.ws, a.k_splits, T, N,
+               a.bias, ra);
+    return 2;
   }
   if (a.k_splits > 1 && !a.fixup) {
     // dense [token][feature] partials in both orientations
