@@ -169,6 +169,7 @@ def main() -> None:
     # ---- warm-up decode steps (captures the graph)
     for _ in range(args.warmup):
         eng.step()
+    eng.drain()
     assert len(eng.scheduler.running) == args.batch, "batch shrank during warm-up"
 
     # ---- kernel-only: K replays of the captured decode step of the live batch
@@ -204,6 +205,7 @@ def main() -> None:
         ts = time.perf_counter()
         eng.step()
         step_ms.append((time.perf_counter() - ts) * 1e3)
+    eng.drain()                 # the last launched step's ids are read inside the timed region
     e1.record()
     sync_all()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
@@ -230,14 +232,15 @@ def main() -> None:
             "config": {"model": cfg.name, "global_batch": args.batch, "seq_len": args.prompt_len,
                        "parallelism": f"tp{world}", "tp_backend": getattr(tp_rt, "backend", "none"),
                        "kv": "paged bf16, 16-token blocks", "chunked_prefill": 2048,
-                       "cuda_graphs": not args.no_graphs,
+                       "cuda_graphs": not args.no_graphs, "async_scheduling": eng._async_ok(),
                        "l2": "inputs larger than L2: 16 GB of weights + KV streamed per step"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 1), "unit": "tok/s",
                     "h2d_bytes_per_step": (eng.stats.h2d_bytes - h2d0) // args.steps,
                     "d2h_bytes_per_step": (eng.stats.d2h_bytes - d2h0) // args.steps,
                     "ms_per_step": round(e2e_s * 1e3 / args.steps, 4),
-                    "step_ms_p50": round(statistics.median(step_ms), 4), "step_ms_max": round(max(step_ms), 4)},
+                    "step_ms_p50": round(statistics.median(step_ms), 4), "step_ms_max": round(max(step_ms), 4),
+                    "slowest_steps": sorted(((round(v, 2), i) for i, v in enumerate(step_ms)), reverse=True)[:4]},
             "gpu_launches": (launches_per_step or 0) * args.steps + (eng.stats.kernel_launches - l0),
             "prefill_tok_s": round(prefill_tok_s, 1), "ttft_s_first": round(ttft or 0.0, 4),
             "itl_p50_ms": round(statistics.median(itl) * 1e3, 4) if itl else None,

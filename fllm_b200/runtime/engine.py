@@ -93,6 +93,7 @@ class LLMEngine:
             self.adaptive = AdaptiveDraft(self.cfg.draft_tokens)
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self._graph_pool = None
+        self._inflight = None                # launch-ahead: the decode step whose ids are still on the device
         # staging: [ids | positions | slots | row_seq | logit_rows | block tables]
         max_rows = max(self.cfg.max_num_seqs, self._bucket_for(self.cfg.max_num_seqs))
         cap = 5 * max(self.cfg.max_num_batched_tokens, max_rows) + max_rows * (self.max_blocks_per_seq + 2) + 64
@@ -102,6 +103,13 @@ class LLMEngine:
             hbuf = torch.empty(cap, dtype=torch.int32, pin_memory=self.is_cuda)
             self._stage_bufs.append((hbuf, hbuf.numpy(), torch.empty(cap, dtype=torch.int32, device=self.device)))
         self._host, self._host_np, self._dev = self._stage_bufs[0]
+        # launch-ahead alternates two pinned host buffers (and two result buffers) over ONE device
+        # staging buffer: the copy for step t+1 is queued behind step t's graph on the stream
+        if self.par.pp == 1:
+            halt = torch.empty(cap, dtype=torch.int32, pin_memory=self.is_cuda)
+            self._stage_bufs.append((halt, halt.numpy(), self._dev))
+        self._out_alt = torch.empty(512, dtype=torch.int32, pin_memory=self.is_cuda)
+        self._flip = 0
         self._out_host = torch.empty(self.cfg.max_num_batched_tokens + 64, dtype=torch.int32,
                                      pin_memory=self.is_cuda)
 
@@ -140,7 +148,7 @@ class LLMEngine:
         return r is not None
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
     # ------------------------------------------------------------------ batch building
     def _build_batch(self, step: ScheduledStep, pad_to: int = 0, slot: int = 0) -> StepBatch:
@@ -275,8 +283,134 @@ class LLMEngine:
             for r, room in ok:
                 r.draft = self.proposer.propose(r.all_tokens, room)[:room]
 
+    # ------------------------------------------------------------------ launch-ahead decode
+    PLACEHOLDER = -1
+
+    def _async_ok(self) -> bool:
+        return (self.cfg.async_scheduling and self.is_cuda and self.cfg.use_cuda_graphs and self.par.pp == 1
+                and self.proposer is None)
+
+    def _graph_eligible(self, step: ScheduledStep) -> bool:
+        return (self.is_cuda and self.cfg.use_cuda_graphs and step.all_decode and self.par.pp == 1
+                and not any(s.verify for s in step.seqs) and self._bucket_for(len(step.seqs)) > 0)
+
+    def _precommit(self, fl) -> None:
+        """Account for the in-flight step as if it had finished: every sequence advances by one
+        token whose id is not known yet (a placeholder in its output)."""
+        fl["slots"] = []
+        for s in fl["step"].seqs:
+            r = s.req
+            if r.finished or r.status != RequestStatus.RUNNING:
+                fl["slots"].append(-1)
+                continue
+            fl["slots"].append(len(r.output))
+            self.scheduler.commit(s, [self.PLACEHOLDER], register=False)
+
+    def _finalize(self, fl) -> List[TokenEvent]:
+        """Read the in-flight step's ids, patch the placeholders, apply stop conditions."""
+        fl["event"].synchronize()
+        toks = fl["out"][: fl["n"]].tolist()
+        self.stats.d2h_bytes += fl["n"] * 4
+        events: List[TokenEvent] = []
+        now = time.monotonic()
+        for i, s in enumerate(fl["step"].seqs):
+            r, slot = s.req, fl["slots"][i]
+            if slot < 0 or r.finished or slot >= len(r.output):
+                continue
+            r.output[slot] = toks[i]
+            self.blocks.commit_tokens(r.seq_id, r.all_tokens, r.num_computed, r.params.cache_salt.encode())
+            self.stats.decode_tokens += 1
+            if r.first_token_time is None:
+                r.first_token_time = now
+            r.last_token_time = now
+            r.token_times.append(now)
+            new = [toks[i]]
+            reason = self._finish_reason(r, new)
+            if reason:
+                self.scheduler.finish(r, reason)
+                self.requests.pop(r.request_id, None)
+            if self.tp_rank == 0:
+                events.append(TokenEvent(r.request_id, new, bool(reason), reason))
+        self.stats.steps += 1
+        return events
+
+    def _launch_ahead(self, step: ScheduledStep, prev) -> dict:
+        """Queue a decode step behind the in-flight one. Ids of rows that continue a placeholder
+        are taken from the previous step's device-side result, never from the host."""
+        n = len(step.seqs)
+        bucket = self._bucket_for(n)
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = _DecodeGraph(self, bucket)
+            self._graphs[bucket] = g
+        self._flip ^= 1
+        self._build_batch(step, pad_to=bucket, slot=0 if self._flip == 0 else len(self._stage_bufs) - 1)
+        if prev is not None:
+            prev_row = {s.req.seq_id: i for i, s in enumerate(prev["step"].seqs)}
+            src = [prev_row.get(s.req.seq_id, -1) for s in step.seqs]
+            need = [i for i, (s, j) in enumerate(zip(step.seqs, src))
+                    if j >= 0 and s.req.output and s.req.output[-1] == self.PLACEHOLDER]
+            if need:
+                if len(need) == n and src == list(range(n)) and prev["graph"].tokens.shape[0] >= n:
+                    self._dev[0:n].copy_(prev["tokens"][:n])
+                else:
+                    idx = torch.tensor([src[i] for i in need], dtype=torch.long, device=self.device)
+                    dst = torch.tensor(need, dtype=torch.long, device=self.device)
+                    self._dev[0:n].index_copy_(0, dst, prev["tokens"].index_select(0, idx))
+        g.replay()
+        self.stats.graph_steps += 1
+        self.stats.forward_calls += 1
+        self.stats.kernel_launches += g.launches
+        # a private copy: the graph's static result is overwritten by the next replay
+        toks_dev = g.tokens.clone()
+        out = self._out_host if self._flip == 0 else self._out_alt
+        out[:bucket].copy_(toks_dev, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return {"step": step, "graph": g, "tokens": toks_dev, "out": out, "n": n, "event": ev, "slots": []}
+
     @torch.inference_mode()
     def step(self) -> List[TokenEvent]:
+        if not self._async_ok():
+            return self._step_sync()
+        events: List[TokenEvent] = []
+        prev = self._inflight
+        if prev is not None:
+            self._precommit(prev)
+        t0 = time.perf_counter_ns()
+        step = self.scheduler.schedule()
+        self.stats.schedule_ns += time.perf_counter_ns() - t0
+        for r in step.expired:
+            events.append(TokenEvent(r.request_id, [], True, r.finish_reason, error=r.finish_reason))
+            self.requests.pop(r.request_id, None)
+        eligible = (not step.empty and self._graph_eligible(step) and not step.cow
+                    and not any(s.req.params.needs_full_sampler for s in step.seqs))
+        if eligible:
+            nxt = self._launch_ahead(step, prev)
+            if prev is not None:
+                events.extend(self._finalize(prev))
+            self._inflight = nxt
+            return events
+        # not a pure decode step: drain the pipeline, then run this step the ordinary way
+        if prev is not None:
+            events.extend(self._finalize(prev))
+            self._inflight = None
+            step.seqs = [s for s in step.seqs if not s.req.finished and s.req.status == RequestStatus.RUNNING]
+        if not step.empty:
+            events.extend(self._run_scheduled(step))
+        return events
+
+    def drain(self) -> List[TokenEvent]:
+        """Wait for the launch-ahead step (if any) and commit it; returns its events."""
+        fl = self._inflight
+        if fl is None:
+            return []
+        self._precommit(fl)
+        self._inflight = None
+        return self._finalize(fl)
+
+    @torch.inference_mode()
+    def _step_sync(self) -> List[TokenEvent]:
         t0 = time.perf_counter_ns()
         if self.proposer is not None:
             self._propose_drafts()
@@ -288,11 +422,15 @@ class LLMEngine:
             self.requests.pop(r.request_id, None)
         if step.empty:
             return events
+        events.extend(self._run_scheduled(step))
+        return events
+
+    def _run_scheduled(self, step: ScheduledStep) -> List[TokenEvent]:
+        """Forward + sample + commit of one scheduled step, waiting for its result."""
+        events: List[TokenEvent] = []
         for src, dst in step.cow:
             self.kv.store[:, :, dst].copy_(self.kv.store[:, :, src])
-        use_graph = (self.is_cuda and self.cfg.use_cuda_graphs and step.all_decode and self.par.pp == 1
-                     and not any(s.verify for s in step.seqs)
-                     and self._bucket_for(len(step.seqs)) > 0)
+        use_graph = self._graph_eligible(step)
         l0 = getattr(self.ops, "launches", 0)
         if use_graph:
             tokens_dev, logits, batch = self._decode_with_graph(step)

@@ -131,7 +131,7 @@ class Scheduler:
                     step.expired.append(r)
 
         # 1. decode / verify rows of running requests (decode-first)
-        decoders = [r for r in self.running if r.is_decode]
+        decoders = [r for r in self.running if r.is_decode and r.num_tokens < cfg.max_model_len]
         prefilling = [r for r in self.running if not r.is_decode]
         for r in list(decoders):
             if r not in self.running:
@@ -196,7 +196,7 @@ class Scheduler:
         return step
 
     # ------------------------------------------------------------------ commit
-    def commit(self, s: ScheduledSeq, new_tokens: List[int], accepted_drafts: int = 0) -> None:
+    def commit(self, s: ScheduledSeq, new_tokens: List[int], accepted_drafts: int = 0, register: bool = True) -> None:
         """Account for a finished step of one sequence: `count - verify + accepted` fed tokens now
         have KV; `new_tokens` (possibly empty for a non-final prefill chunk) are appended."""
         r = s.req
@@ -207,7 +207,8 @@ class Scheduler:
             self.blocks.truncate(r.seq_id, r.num_computed)
             r.draft = []
         r.output.extend(new_tokens)
-        self.blocks.commit_tokens(r.seq_id, r.all_tokens, r.num_computed, self._salt(r))
+        if register:          # launch-ahead commits a placeholder first and registers once the id is known
+            self.blocks.commit_tokens(r.seq_id, r.all_tokens, r.num_computed, self._salt(r))
         if self.window:
             self.blocks.prune_window(r.seq_id, self.window)
 
