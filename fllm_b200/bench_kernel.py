@@ -50,6 +50,7 @@ def main(argv=None) -> None:
     ap.add_argument("--tokens", default="1,16,64,128,256,2048,8192")
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--json", default="")
+    ap.add_argument("--fp4", action="store_true", help="only the packed FP4 (NVFP4 / MXFP4) decode GEMMs")
     args = ap.parse_args(argv)
     from .config import preset
     from .ops.native import NativeOps
@@ -63,6 +64,29 @@ def main(argv=None) -> None:
     shapes = {"qkv": (qkv, H), "o": (H, cfg.q_size // args.tp), "gate_up": (2 * I, H), "down": (H, I),
               "lm_head": (cfg.vocab_size // args.tp // 8 * 8, H)}
     rows = []
+    if args.fp4:
+        from .ops.fp4 import Fp4Weight
+        print(f"# peaks ({src}): {hbm} GB/s; bytes = packed weight + scales + activations")
+        for name, (N, K) in shapes.items():
+            if name == "lm_head":
+                continue
+            w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+            for fmt in ("nvfp4", "mxfp4"):
+                q = Fp4Weight.from_dense(w, fmt)
+                for T in (1, 16, 64, 128):
+                    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+                    y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+                    ms = timer(lambda: ops.linear(x, q, out=y))
+                    ms16 = timer(lambda: ops.linear(x, w, out=y))
+                    byts = q.nbytes() + 2.0 * (T * K + T * N)
+                    print(f"{name:8s} {fmt:6s} T={T:4d} N={N:6d} K={K:6d} {ms * 1e3:8.1f} us  (bf16 {ms16 * 1e3:7.1f} us)  "
+                          f"{byts / ms / 1e6:6.0f} GB/s  frac {byts / (hbm * 1e9) / (ms / 1e3):.2f}")
+                    rows.append({"op": name, "fmt": fmt, "T": T, "us": ms * 1e3, "bf16_us": ms16 * 1e3, "gbs": byts / ms / 1e6})
+            del w
+        print("kernel status word:", ops.check_status())
+        if args.json:
+            json.dump({"rows": rows}, open(args.json, "w"), indent=1)
+        return
     print(f"# peaks ({src}): {hbm} GB/s, {tflops} TFLOP/s bf16")
     print(f"{'op':10s} {'T':>6s} {'N':>7s} {'K':>6s} {'ours ms':>9s} {'cublas ms':>9s} {'TFLOP/s':>8s} {'GB/s':>7s} {'frac':>6s} {'bound':>5s}")
     for name, (N, K) in shapes.items():

@@ -34,9 +34,41 @@ int64_t linear_fp8_block(const Tensor& xq, const Tensor& sx, const Tensor& wq, c
   return fllm::linear_fp8_block(xq.data_ptr(), sx.data_ptr<float>(), wq.data_ptr(), sw.data_ptr<float>(), b, y.data_ptr(),
                                 y.stride(0), (int)T, (int)N, (int)K, st, cur_stream());
 }
+
+// codes uint8 [N, K/2] (two e2m1 per byte, low nibble first), scales uint8 [N, K/16] e4m3 (fmt 0) or [N, K/32] e8m0 (fmt 1)
+int64_t linear_w4a16(const Tensor& x, const Tensor& codes, const Tensor& scales, int64_t fmt, double alpha,
+                     const optional<Tensor>& bias, Tensor y, const optional<Tensor>& workspace, const optional<Tensor>& status) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "x: bf16 rows");
+  TORCH_CHECK(codes.is_contiguous() && codes.element_size() == 1 && codes.dim() == 2 && codes.size(1) * 2 == x.size(1), "codes: [N, K/2] bytes");
+  const int64_t T = x.size(0), N = codes.size(0), K = x.size(1);
+  TORCH_CHECK(scales.is_contiguous() && scales.element_size() == 1 && scales.numel() == N * (K / (fmt == 0 ? 16 : 32)), "scales: one byte per block");
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.stride(1) == 1 && y.size(0) == T && y.size(1) == N, "y: [T, N] bf16");
+  c10::cuda::CUDAGuard guard(x.device());
+  const void* b = bias.has_value() && bias->defined() ? bias->data_ptr() : nullptr;
+  int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  // the first 64 KiB of the shared workspace hold the dense GEMM's tile counters: partial sums go after them
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  if (workspace.has_value() && workspace->defined() && workspace->numel() * workspace->element_size() > (64 << 10)) {
+    ws = static_cast<char*>(workspace->data_ptr()) + (64 << 10);
+    ws_bytes = workspace->numel() * workspace->element_size() - (64 << 10);
+  }
+  return fllm::linear_w4a16(x.data_ptr(), x.stride(0), codes.data_ptr(), scales.data_ptr(), (int)fmt, (float)alpha, b,
+                            y.data_ptr(), y.stride(0), (int)T, (int)N, (int)K, ws, ws_bytes, st, cur_stream());
+}
+
+void w4_dequant(const Tensor& codes, const Tensor& scales, int64_t fmt, double alpha, Tensor out) {
+  TORCH_CHECK(codes.is_cuda() && codes.is_contiguous() && codes.dim() == 2 && out.is_contiguous() && out.scalar_type() == at::kBFloat16, "codes [N, K/2], out bf16 [N, K]");
+  TORCH_CHECK(out.numel() == codes.numel() * 2 && (codes.size(1) * 2) % 32 == 0, "out: [N, K], K % 32 == 0");
+  c10::cuda::CUDAGuard guard(codes.device());
+  fllm::w4_dequant_bf16(codes.data_ptr(), scales.data_ptr(), (int)fmt, (float)alpha, out.data_ptr(), codes.size(0),
+                        (int)codes.size(1) * 2, cur_stream());
+}
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("quant_fp8_1x128(Tensor x, Tensor(a!) xq, Tensor(b!) sx) -> ()", &quant_fp8_1x128);
   m.def("linear_fp8_block(Tensor xq, Tensor sx, Tensor wq, Tensor sw, Tensor? bias, Tensor(a!) y, Tensor? status) -> int", &linear_fp8_block);
+  m.def("linear_w4a16(Tensor x, Tensor codes, Tensor scales, int fmt, float alpha, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status) -> int", &linear_w4a16);
+  m.def("w4_dequant(Tensor codes, Tensor scales, int fmt, float alpha, Tensor(a!) out) -> ()", &w4_dequant);
 }

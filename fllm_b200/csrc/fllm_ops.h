@@ -83,6 +83,13 @@ void quant_fp8_1x128(const void* x, long long ldx, void* xq, float* sx, int toke
 int linear_fp8_block(const void* xq, const float* sx, const void* wq, const float* sw, const void* bias, void* y,
                      long long ldy, int T, int N, int K, int* status, cudaStream_t stream);
 
+// ---- packed 4-bit weights x bf16 activations (fmt 0 = NVFP4: e4m3 scale per 16; 1 = MXFP4: e8m0 per 32)
+int linear_w4a16(const void* x, long long ldx, const void* codes, const void* scales, int fmt, float alpha,
+                 const void* bias, void* y, long long ldy, int T, int N, int K, void* workspace, size_t workspace_bytes,
+                 int* status, cudaStream_t stream);
+void w4_dequant_bf16(const void* codes, const void* scales, int fmt, float alpha, void* out, long long rows, int K,
+                     cudaStream_t s);
+
 // ---- mixture of experts ---------------------------------------------------------------
 int moe_grouped_linear_bf16(const void* xp, long long ldx, const void* w_stack, long long ldw,
                             const void* bias_stack, void* y, long long ldy, int rows_cap, int n_out, int K,

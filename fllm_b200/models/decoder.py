@@ -85,6 +85,11 @@ class Decoder:
                 if packed[0] == "fp8_block":
                     from ..ops.native import Fp8BlockWeight
                     setattr(lw, name, Fp8BlockWeight(packed[1], packed[2]))
+                elif packed[0] in ("nvfp4", "mxfp4"):
+                    from ..ops.fp4 import FMT_NAMES, Fp4Weight
+                    setattr(lw, name, Fp4Weight(packed[1], packed[2], FMT_NAMES[packed[0]], packed[3] if len(packed) > 3 else 1.0))
+        self._dense_weights = all(isinstance(getattr(lw, n, None), torch.Tensor) for lw in self.w.layers
+                                  for n in ("wqkv", "wo", "w_gate_up", "w_down") if getattr(lw, n, None) is not None)
 
     # ------------------------------------------------------------------ pieces
     def _reduce(self, x: torch.Tensor) -> torch.Tensor:
@@ -137,7 +142,7 @@ class Decoder:
     @property
     def fused_tp(self) -> bool:
         return (self.tp is not None and getattr(self.tp, "backend", "") == "fused" and self.tp.size > 1
-                and not self.cfg.is_moe and self.first_stage and self.last_stage)
+                and not self.cfg.is_moe and self.first_stage and self.last_stage and self._dense_weights)
 
     def forward_fused(self, b: StepBatch) -> torch.Tensor:
         """Whole forward with the sequence-sharded residual: every projection output leaves the

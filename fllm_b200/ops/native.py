@@ -26,6 +26,14 @@ class NativeOps:
         self.use_tc_attention = True
         self.attn_ws = None
         self.launches = 0            # kernels launched through this object (graph capture included)
+        self._scratch = None
+
+    def scratch_bf16(self, numel: int) -> torch.Tensor:
+        """Grow-only bf16 scratch (expanded weights of packed formats during prefill). Stream-ordered
+        reuse: the dense GEMM that reads it is queued before the next expansion overwrites it."""
+        if self._scratch is None or self._scratch.numel() < numel:
+            self._scratch = torch.empty(numel, dtype=torch.bfloat16, device=self.device)
+        return self._scratch[:numel]
 
     # ---------------------------------------------------------------- dense
     def linear(self, x, w, bias=None, out=None, force_splits: int = 0):

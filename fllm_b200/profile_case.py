@@ -3,7 +3,7 @@
 Each case launches ONE kernel family a handful of times on inputs larger than L2 but far below a
 GB-scale footprint, so a multi-pass capture (``ncu --set full -k regex:<kernel> -c 1``) finishes
 in seconds. Cases: gemm_decode (64 tokens x gate_up of an 8B model), gemm_prefill (2048 tokens),
-attn_decode (64 sequences at 1152 context), attn_prefill, fp8_prefill, tp_norm.
+attn_decode (64 sequences at 1152 context), attn_prefill, fp8_prefill, gemm_fp4_decode (64 tokens x NVFP4 gate_up).
 """
 from __future__ import annotations
 
@@ -25,6 +25,14 @@ def main(argv=None) -> None:
         w = torch.randn(24576, 4096, **bf) * 0.02
         y = torch.empty(T, 24576, **bf)
         fn = lambda: ops.linear(x, w, out=y)
+    elif case == "gemm_fp4_decode":
+        from .ops.fp4 import Fp4Weight
+        x = torch.randn(64, 4096, **bf)
+        codes = torch.randint(0, 256, (24576, 2048), device="cuda", dtype=torch.uint8)
+        scales = torch.full((24576, 256), 0x38, device="cuda", dtype=torch.uint8)      # e4m3 1.0
+        q = Fp4Weight(codes, scales, 0, 0.01)
+        y = torch.empty(64, 24576, **bf)
+        fn = lambda: ops.linear(x, q, out=y)
     elif case == "fp8_prefill":
         x = torch.randn(2048, 4096, **bf)
         wq, sw = quantize_weight_fp8_block(torch.randn(8192, 4096, **bf) * 0.02)

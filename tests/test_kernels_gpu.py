@@ -364,3 +364,38 @@ def test_linear_fp8_block(ops, T, N, K):
     amax = x.float().view(T, K // 128, 128).abs().amax(-1).clamp_min(1e-10)
     assert torch.allclose(sx, amax / 448.0, rtol=1e-6)
     assert ops.check_status() == 0
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+@pytest.mark.parametrize("T", [1, 16, 33, 64, 100, 128, 300])
+@pytest.mark.parametrize("N,K", [(256, 256), (1000, 320), (1024, 4096), (6144, 4096), (512, 12288)])
+def test_linear_w4a16(ops, fmt, T, N, K):
+    """Packed FP4 weights x bf16 activations against fp32 math on the de-quantised matrix (the
+    expansion inside the kernel is exact, so only accumulation order and output rounding differ).
+    Covers partial feature tiles, every token-tile width, the split-K path (few feature tiles,
+    long K) and the expand-then-dense route of long steps."""
+    from fllm_b200.ops.fp4 import Fp4Weight
+    if fmt == "mxfp4" and K % 32:
+        pytest.skip("block of 32")
+    x = _rand((T, K), 1)
+    w = _rand((N, K), 2, 0.05)
+    bias = _rand((N,), 3, 0.1) if N == 1024 else None
+    q = Fp4Weight.from_dense(w, fmt)
+    y = ops.linear(x, q, bias)
+    ref = x.float() @ q.dense().t()
+    if bias is not None:
+        ref = ref + bias.float()
+    _close(y, ref, 1e-2)
+    # FP4 itself: block-scaled e2m1 keeps the product within ~10 % of the unquantised one
+    _close(y, x.float() @ w.float().t() + (bias.float() if bias is not None else 0), 0.2)
+    assert ops.check_status() == 0
+
+
+def test_w4_dequant_matches_reference(ops):
+    from fllm_b200.ops.fp4 import Fp4Weight
+    for fmt in ("nvfp4", "mxfp4"):
+        w = _rand((384, 512), 5, 0.3)
+        q = Fp4Weight.from_dense(w, fmt)
+        out = torch.empty(384, 512, dtype=torch.bfloat16, device="cuda")
+        ops.k.w4_dequant(q.codes, q.scales, q.fmt, q.alpha, out)
+        assert torch.equal(out.float(), q.dense().to(torch.bfloat16).float())
