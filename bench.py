@@ -103,6 +103,9 @@ def main() -> None:
     ap.add_argument("--backend", default=os.environ.get("FLLM_TP_BACKEND", "auto"),
                     help="tensor-parallel collectives: auto | fused | nccl")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--profile-step", action="store_true",
+                    help="bracket ONE replay of the decode step with cudaProfilerStart/Stop (for a profiler's "
+                         "launch list, run with --profile-from-start off) and exit")
     args = ap.parse_args()
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) == 0:
@@ -188,6 +191,15 @@ def main() -> None:
         e1.record()
         sync_all()
         dev_ms = max_over_ranks(e0.elapsed_time(e1))
+        if args.profile_step:
+            torch.cuda.profiler.start()
+            graph.replay()
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+            sampler.stop()
+            print(json.dumps({"profiled_step": True, "ms_per_step": dev_ms / args.steps, "launches": launches_per_step}))
+            eng.close()
+            return
         # finish the scheduled-but-not-committed step so the engine state stays consistent
         toks = graph.tokens.tolist()
         eng._commit(step_desc, toks)

@@ -112,7 +112,30 @@ argmax_rows_kernel(const T* __restrict__ logits, long long ld, int vocab, int* _
   __shared__ ArgMax sm[32];
   const T* row = logits + (size_t)blockIdx.x * ld;
   ArgMax a{-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) a = better(a, ArgMax{ld_logit(row, i), i});
+  int i0 = 0;
+  if constexpr (sizeof(T) == 2) {
+    // 16-byte loads (8 logits) when the row allows it; a strict '>' inside a vector and `better`
+    // across threads keep the lowest index among equal maxima
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+      const int nvec = vocab >> 3;
+      const uint4* rv = reinterpret_cast<const uint4*>(row);
+      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        const uint4 u = rv[v];
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        float best = -INFINITY;
+        int bi = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(w[j]);
+          if (f.x > best) { best = f.x; bi = 2 * j; }
+          if (f.y > best) { best = f.y; bi = 2 * j + 1; }
+        }
+        a = better(a, ArgMax{best, 8 * v + bi});
+      }
+      i0 = nvec << 3;
+    }
+  }
+  for (int i = i0 + threadIdx.x; i < vocab; i += blockDim.x) a = better(a, ArgMax{ld_logit(row, i), i});
   a = block_argmax(a, sm);
   if (threadIdx.x == 0) {
     out_ids[blockIdx.x] = a.i + id_offset;
