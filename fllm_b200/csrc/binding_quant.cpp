@@ -35,13 +35,14 @@ int64_t linear_fp8_block(const Tensor& xq, const Tensor& sx, const Tensor& wq, c
                                 y.stride(0), (int)T, (int)N, (int)K, st, cur_stream());
 }
 
-// codes uint8 [N, K/2] (two e2m1 per byte, low nibble first), scales uint8 [N, K/16] e4m3 (fmt 0) or [N, K/32] e8m0 (fmt 1)
+// codes uint8 [N, K/2]; scales uint8 [N, K/16] e4m3 (fmt 0), [N, K/32] e8m0 (fmt 1) or bf16 [N, K/32, 2] = {scale, min} (fmt 2)
 int64_t linear_w4a16(const Tensor& x, const Tensor& codes, const Tensor& scales, int64_t fmt, double alpha,
                      const optional<Tensor>& bias, Tensor y, const optional<Tensor>& workspace, const optional<Tensor>& status) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "x: bf16 rows");
   TORCH_CHECK(codes.is_contiguous() && codes.element_size() == 1 && codes.dim() == 2 && codes.size(1) * 2 == x.size(1), "codes: [N, K/2] bytes");
   const int64_t T = x.size(0), N = codes.size(0), K = x.size(1);
-  TORCH_CHECK(scales.is_contiguous() && scales.element_size() == 1 && scales.numel() == N * (K / (fmt == 0 ? 16 : 32)), "scales: one byte per block");
+  TORCH_CHECK(scales.is_contiguous() && scales.numel() * scales.element_size() == N * (K / (fmt == 0 ? 16 : 32)) * (fmt == 2 ? 4 : 1),
+              "scales: one byte per block (FP4) or {bf16 scale, bf16 min} per 32 values (INT4G)");
   TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.stride(1) == 1 && y.size(0) == T && y.size(1) == N, "y: [T, N] bf16");
   c10::cuda::CUDAGuard guard(x.device());
   const void* b = bias.has_value() && bias->defined() ? bias->data_ptr() : nullptr;

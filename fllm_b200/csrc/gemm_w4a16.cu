@@ -2,6 +2,9 @@
 //
 //   NVFP4   e2m1 codes, two per byte, + one e4m3 scale per 16 values + an fp32 tensor scale
 //   MXFP4   e2m1 codes, two per byte, + one e8m0 (power of two) scale per 32 values
+//   INT4G   unsigned 4-bit codes + one (scale, min) pair of bf16 per 32 values: value = q * scale - min.
+//           This is the device form of GGUF Q4_K / Q4_0 / Q4_1 and of AWQ / GPTQ int4 groups, re-laid at
+//           load time (planar codes, nibbles ordered so that two shifts-and-masks yield K-ordered pairs).
 //
 // Decode is bound by the bytes of weight read, so reading 4.5 bit/weight instead of 16 is the
 // point. The kernel is the swap-AB GEMM of gemm_bf16.cu with one extra stage in the operand path:
@@ -33,10 +36,10 @@ struct W4Args {
   int m_tiles, k_blocks;
   int k_splits, kb_per_split;         // grid.y splits of the K loop; partial sums go to `ws`
   float* ws;                          // [k_splits][N][M] fp32 when k_splits > 1
-  int fmt;                            // 0 NVFP4 (e4m3 / 16), 1 MXFP4 (e8m0 / 32)
+  int fmt;                            // 0 NVFP4 (e4m3 / 16), 1 MXFP4 (e8m0 / 32), 2 INT4G ((scale, min) bf16 / 32)
   long long ldc;
   __nv_bfloat16* out;
-  const uint8_t* scales;              // [M][K/16] or [M][K/32]
+  const uint8_t* scales;              // [M][K/16] bytes, [M][K/32] bytes, or [M][K/32] x {bf16 scale, bf16 min}
   float alpha;                        // tensor scale (NVFP4), 1 otherwise
   const __nv_bfloat16* bias;
   int* status;
@@ -98,6 +101,23 @@ __device__ __forceinline__ void e2m1x8_to_bf16(uint32_t codes, uint32_t s2, uint
     __nv_bfloat162 r1 = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&v1), sc);
     out[2 * h] = *reinterpret_cast<uint32_t*>(&r0);
     out[2 * h + 1] = *reinterpret_cast<uint32_t*>(&r1);
+  }
+}
+
+// 8 unsigned 4-bit codes -> 8 bf16 of q * s - m. Storage order: nibble j of the word holds value 2j (j < 4)
+// or 2(j - 4) + 1, so ((w >> 4j) & 0x000F000F) is the K-ordered pair (2j, 2j + 1). OR-ing 0x4300 makes the
+// bf16 number 128 + q exactly; one subtract and one fused multiply-add finish it.
+__device__ __forceinline__ void int4x8_to_bf16(uint32_t w, uint32_t s2, uint32_t negm2, uint32_t (&out)[4]) {
+  const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162*>(&s2);
+  const __nv_bfloat162 nm = *reinterpret_cast<const __nv_bfloat162*>(&negm2);
+  const uint32_t c128 = 0x43004300u;
+  const __nv_bfloat162 b128 = *reinterpret_cast<const __nv_bfloat162*>(&c128);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t t = ((w >> (4 * j)) & 0x000F000Fu) | c128;
+    const __nv_bfloat162 q = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&t), b128);
+    const __nv_bfloat162 r = __hfma2(q, sc, nm);
+    out[j] = *reinterpret_cast<const uint32_t*>(&r);
   }
 }
 
@@ -214,18 +234,19 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_raw, const __grid_cons
     const int g = e >> 2;                               // group
     const int row = q * 32 + lane;
     const int m_row = min(m_idx * W4_BM + row, p.M - 1);
-    const int sbytes = p.fmt == 0 ? 4 : 2;              // scale bytes per row per step
+    const int sbytes = p.fmt == 0 ? 4 : p.fmt == 1 ? 2 : 8;   // scale bytes per row per step
     const uint8_t* srow = p.scales + (size_t)m_row * (p.K / 64) * sbytes + (size_t)kb0 * sbytes;
     const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
-    auto load_scales = [&](int kb) -> uint32_t {        // this row's scales of step kb
-      if (kb >= nkb) return 0;
-      return p.fmt == 0 ? __ldg(reinterpret_cast<const uint32_t*>(srow + kb * 4))
-                        : (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(srow + kb * 2));
+    auto load_scales = [&](int kb) -> uint2 {           // this row's scales of step kb
+      if (kb >= nkb) return make_uint2(0, 0);
+      if (p.fmt == 0) return make_uint2(__ldg(reinterpret_cast<const uint32_t*>(srow + kb * 4)), 0);
+      if (p.fmt == 1) return make_uint2((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(srow + kb * 2)), 0);
+      return __ldg(reinterpret_cast<const uint2*>(srow + kb * 8));
     };
     bool ok = true;
-    uint32_t sc_cur = load_scales(g), sc_next = load_scales(g + G);
+    uint2 sc_cur = load_scales(g), sc_next = load_scales(g + G);
     for (int kb = g; kb < nkb && ok; kb += G) {
-      const uint32_t sraw = sc_cur;
+      const uint32_t sraw = sc_cur.x, sraw2 = sc_cur.y;
       sc_cur = sc_next;
       sc_next = load_scales(kb + 2 * G);                // two of this group's steps ahead
       const int rb = kb >> 2, sub = kb & 3;
@@ -235,9 +256,14 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_raw, const __grid_cons
       if (p.fmt == 0) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) s2[i] = lut[(sraw >> (8 * i)) & 0xFF];
-      } else {
+      } else if (p.fmt == 1) {
         s2[0] = s2[1] = lut[sraw & 0xFF];
         s2[2] = s2[3] = lut[(sraw >> 8) & 0xFF];
+      } else {                                          // {scale, min} bf16 of the two 32-value groups
+        s2[0] = __byte_perm(sraw, 0, 0x1010);           // (s, s)
+        s2[1] = __byte_perm(sraw, 0, 0x3232) ^ 0x80008000u;   // (-m, -m)
+        s2[2] = __byte_perm(sraw2, 0, 0x1010);
+        s2[3] = __byte_perm(sraw2, 0, 0x3232) ^ 0x80008000u;
       }
       if (!mbar_wait(&rfull_bar[rs], rphase, abort_flag)) { ok = false; break; }
       const uint8_t* rrow = sR + rs * S::kRawBytes + row * 128;
@@ -251,7 +277,8 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_raw, const __grid_cons
 #pragma unroll
         for (int c = 0; c < 4; ++c) {                   // 8 codes -> 4 cells of two bf16 each
           uint32_t o4[4];
-          e2m1x8_to_bf16(words[c], s2[c >> 1], o4);
+          if (p.fmt == 2) int4x8_to_bf16(words[c], s2[0], s2[1], o4);
+          else e2m1x8_to_bf16(words[c], s2[c >> 1], o4);
 #pragma unroll
           for (int i = 0; i < 4; ++i) o[4 * c + i] = o4[i];
         }
@@ -263,7 +290,8 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_raw, const __grid_cons
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t o4[4];
-          e2m1x8_to_bf16(words[c], s2[2 + (c >> 1)], o4);
+          if (p.fmt == 2) int4x8_to_bf16(words[c], s2[2], s2[3], o4);
+          else e2m1x8_to_bf16(words[c], s2[2 + (c >> 1)], o4);
 #pragma unroll
           for (int i = 0; i < 4; ++i) o[4 * c + i] = o4[i];
         }
@@ -357,6 +385,13 @@ __global__ void w4_dequant_kernel(const uint8_t* __restrict__ codes, const uint8
   const long long row = e0 / K;
   const int k = (int)(e0 - row * K);
   const uint32_t w = reinterpret_cast<const uint32_t*>(codes)[g];
+  if (fmt == 2) {
+    const uint32_t sm = reinterpret_cast<const uint32_t*>(scales)[row * (K / 32) + k / 32];
+    uint32_t o[4];
+    int4x8_to_bf16(w, __byte_perm(sm, 0, 0x1010), __byte_perm(sm, 0, 0x3232) ^ 0x80008000u, o);
+    *reinterpret_cast<uint4*>(out + e0) = make_uint4(o[0], o[1], o[2], o[3]);
+    return;
+  }
   const int bs = fmt == 0 ? 16 : 32;
   const float sf = scale_to_float(scales[row * (K / bs) + k / bs], fmt) * alpha;
   uint32_t o[4];
@@ -399,7 +434,7 @@ int linear_w4a16(const void* x, long long ldx, const void* codes, const void* sc
   if (T <= 0 || N <= 0) return 0;
   if (T > 128) throw std::runtime_error("linear_w4a16: at most 128 tokens per call (expand the weight for prefill)");
   if (K % 64 || N % 8 || (ldx & 7) || (ldy & 7)) throw std::runtime_error("linear_w4a16: K % 64, N % 8 and 16-byte rows required");
-  if (fmt != 0 && fmt != 1) throw std::runtime_error("linear_w4a16: fmt must be 0 (NVFP4) or 1 (MXFP4)");
+  if (fmt < 0 || fmt > 2) throw std::runtime_error("linear_w4a16: fmt must be 0 (NVFP4), 1 (MXFP4) or 2 (INT4G)");
   W4Args a{};
   a.M = N; a.N = T; a.K = K; a.m_tiles = (N + W4_BM - 1) / W4_BM; a.k_blocks = K / W4_BK; a.fmt = fmt;
   a.ldc = ldy; a.out = reinterpret_cast<__nv_bfloat16*>(y); a.scales = reinterpret_cast<const uint8_t*>(scales);

@@ -105,8 +105,11 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
     return cfg, w, tok
 
 
-def load_gguf(path: str, device="cuda", tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16):
+def load_gguf(path: str, device="cuda", tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16, keep_packed: bool = True):
+    """GGUF -> weights. On a GPU, projections whose tensors are all 4-bit group types (Q4_K, Q4_0,
+    Q4_1) stay packed as ``Int4Weight`` when `keep_packed`; every other type is expanded to bf16."""
     from ..cpu_engine import config_from_gguf
+    from ..ops.int4 import Int4Weight
     from .gguf import GgufReader
     r = GgufReader(path)
     cfg = config_from_gguf(r)
@@ -117,15 +120,39 @@ def load_gguf(path: str, device="cuda", tp: int = 1, tp_rank: int = 0, dtype=tor
     qs = slice(sp.q_head_start * D, (sp.q_head_start + sp.hq_local) * D)
     ks = slice(sp.kv_head_start * D, (sp.kv_head_start + sp.hkv_local) * D)
     isl = slice(sp.inter_start, sp.inter_start + sp.inter_local)
+    packed_ok = keep_packed and torch.device(device).type == "cuda"
+
+    def int4(name):
+        info = r.tensors[name]
+        if not packed_ok or info.type_name not in ("Q4_K", "Q4_0", "Q4_1"):
+            return None
+        rows, cols = int(info.shape[-2] if len(info.shape) > 1 else 1), int(info.shape[-1])
+        if cols % 64:
+            return None
+        return Int4Weight.from_gguf(info.type_name, r.tensor_bytes(name), rows, cols)
+
+    def fused_rows(names, cuts):
+        """Row-concatenation of row-cut tensors: packed when every part has an INT4 form."""
+        parts = [int4(n) for n in names]
+        if all(p is not None for p in parts):
+            return Int4Weight.cat([p.rows(c) for p, c in zip(parts, cuts)]).to(device)
+        return dev(torch.cat([t(n)[c] for n, c in zip(names, cuts)], 0))
+
+    def col_cut(name, cut):
+        p = int4(name)
+        if p is not None and cut.start % 64 == 0 and cut.stop % 64 == 0:
+            return p.cols(cut).to(device)
+        return dev(t(name)[:, cut])
+
     layers = []
     for l in range(cfg.num_layers):
         p = f"blk.{l}."
         lw = LayerWeights(
             attn_norm=dev(t(p + "attn_norm.weight")),
-            wqkv=dev(torch.cat([t(p + "attn_q.weight")[qs], t(p + "attn_k.weight")[ks], t(p + "attn_v.weight")[ks]], 0)),
-            wo=dev(t(p + "attn_output.weight")[:, qs]), ffn_norm=dev(t(p + "ffn_norm.weight")),
-            w_gate_up=dev(torch.cat([t(p + "ffn_gate.weight")[isl], t(p + "ffn_up.weight")[isl]], 0)),
-            w_down=dev(t(p + "ffn_down.weight")[:, isl]))
+            wqkv=fused_rows([p + "attn_q.weight", p + "attn_k.weight", p + "attn_v.weight"], [qs, ks, ks]),
+            wo=col_cut(p + "attn_output.weight", qs), ffn_norm=dev(t(p + "ffn_norm.weight")),
+            w_gate_up=fused_rows([p + "ffn_gate.weight", p + "ffn_up.weight"], [isl, isl]),
+            w_down=col_cut(p + "ffn_down.weight", isl))
         if p + "attn_q_norm.weight" in r.tensors:
             lw.q_norm, lw.k_norm = dev(t(p + "attn_q_norm.weight")), dev(t(p + "attn_k_norm.weight"))
         layers.append(lw)

@@ -96,3 +96,35 @@ def test_gpt_oss_tiny_logits_match_oracle():
     err = (logits[-1].float() - want).abs().max().item()
     assert err < 0.06 * want.abs().max().item() + 1e-3, err
     assert eng.ops.check_status() == 0
+
+
+def test_gguf_q4_k_stays_packed_on_the_gpu(tmp_path):
+    """A Q4_K GGUF file loaded with its 4-bit projections packed (INT4 group-affine GEMM) gives the same
+    logits as the same file expanded to bf16 at load time."""
+    from fllm_b200.config import EngineConfig
+    from fllm_b200.cpu_engine import write_tiny_llama_gguf
+    from fllm_b200.formats.loader import load_gguf
+    from fllm_b200.ops.int4 import Int4Weight
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    path = str(tmp_path / "tiny.gguf")
+    write_tiny_llama_gguf(path, seed=3)
+    outs = []
+    for packed in (True, False):
+        cfg, w, _ = load_gguf(path, "cuda:0", keep_packed=packed)
+        assert isinstance(w.layers[0].wqkv, Int4Weight) == packed
+        ec = EngineConfig(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256, num_kv_blocks=64)
+        eng = LLMEngine(cfg, ec, device="cuda:0", weights=w)
+        p = _prompts(cfg.vocab_size, (90,))[0]
+        eng.add_request(p, SamplingParams(max_tokens=4))
+        rows = []
+        while eng.has_unfinished():
+            step = eng.scheduler.schedule()
+            batch = eng._build_batch(step)
+            logits = eng.decoder.forward(batch)
+            if logits.shape[0]:
+                rows.append(logits[-1].float().clone())
+            eng._commit(step, eng.decoder.greedy_tokens(logits).tolist())
+        assert eng.ops.check_status() == 0
+        outs.append(rows[0])          # the prompt's last position: identical inputs in both runs
+    err = (outs[0] - outs[1]).abs().max().item()
+    assert err < 0.05 * outs[1].abs().max().item() + 1e-3, err

@@ -399,3 +399,34 @@ def test_w4_dequant_matches_reference(ops):
         out = torch.empty(384, 512, dtype=torch.bfloat16, device="cuda")
         ops.k.w4_dequant(q.codes, q.scales, q.fmt, q.alpha, out)
         assert torch.equal(out.float(), q.dense().to(torch.bfloat16).float())
+
+
+@pytest.mark.parametrize("T", [1, 16, 33, 64, 128, 300])
+@pytest.mark.parametrize("N,K", [(256, 256), (1000, 320), (6144, 4096), (512, 12288)])
+def test_linear_int4_group_affine(ops, T, N, K):
+    """INT4 codes with a (scale, min) pair per 32 values (the device form of Q4_K / Q4_0 / AWQ): the
+    packed GEMM against fp32 math on the matrix the kernel expands to (bf16 of q * s - m)."""
+    from fllm_b200.ops.int4 import Int4Weight
+    x = _rand((T, K), 1)
+    w = _rand((N, K), 2, 0.05)
+    q = Int4Weight.from_dense(w)
+    y = ops.linear(x, q)
+    ref = x.float() @ q.dense().to(torch.bfloat16).float().t()
+    _close(y, ref, 1e-2)
+    _close(y, x.float() @ w.float().t(), 0.15)
+    assert ops.check_status() == 0
+
+
+def test_int4_from_q4_k_file_blocks(ops):
+    """Q4_K super-blocks as a GGUF file stores them -> device form -> packed GEMM, against the
+    native codec's de-quantisation."""
+    import numpy as np
+    from fllm_b200.formats import quant as Q
+    from fllm_b200.ops.int4 import Int4Weight
+    rng = np.random.default_rng(1)
+    w = (rng.standard_normal((384, 1024)) * 0.05).astype(np.float32)
+    raw = Q.quantize(w, Q.Q4_K)
+    want = torch.from_numpy(Q.dequantize(raw, Q.Q4_K, 384, 1024)).cuda()
+    q = Int4Weight.from_gguf("Q4_K", raw, 384, 1024, device="cuda")
+    x = _rand((20, 1024), 3)
+    _close(ops.linear(x, q), x.float() @ want.t(), 2e-2)
