@@ -87,7 +87,9 @@ def cmd_serve(args) -> int:
     from .server.app import serve
     eng, tok = build_engine(args)
     eng.warm_up(buckets=[b for b in eng.cfg.graph_buckets if b <= 64])
-    serve(eng, tok, args.host, args.port, args.model_name or os.path.basename(args.model), args.api_key, args.log_level)
+    serve(eng, tok, args.host, args.port, args.model_name or os.path.basename(args.model), args.api_key, args.log_level,
+          tool_parser=args.tool_parser, reasoning_parser=args.reasoning_parser,
+          response_cache_entries=args.response_cache_entries)
     return 0
 
 
@@ -200,6 +202,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     s.add_argument("--model-name", default=None)
     s.add_argument("--api-key", default=os.environ.get("FLLM_API_KEY"))
     s.add_argument("--log-level", default="info")
+    s.add_argument("--tool-parser", default=None, choices=["hermes", "llama3_json", "mistral"])
+    s.add_argument("--reasoning-parser", default=None, choices=["think"])
+    s.add_argument("--response-cache-entries", type=int, default=256, help="0 disables the response cache")
     s.set_defaults(fn=cmd_serve)
     r = sub.add_parser("run", help="generate once from a prompt")
     _add_engine_flags(r)

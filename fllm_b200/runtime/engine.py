@@ -536,6 +536,9 @@ class LLMEngine:
                 self.stats.prefill_tokens += s.count
             else:
                 self.stats.decode_tokens += len(new)
+            if r.params.guided is not None:
+                for t in new:
+                    r.params.guided.advance(t)
             if r.first_token_time is None:
                 r.first_token_time = now
             r.last_token_time = now

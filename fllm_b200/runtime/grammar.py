@@ -1,0 +1,230 @@
+"""Structured output: JSON-constrained decoding.
+
+A character-level incremental JSON recogniser (``json_step``) is walked over a trie of the
+tokenizer's pieces to find, for the current state, every token whose characters keep the output a
+prefix of a valid JSON document. The result is a bit mask (one bit per vocabulary entry) handed to
+the sampler's allowed-token input, so the constraint costs nothing on the device side. Masks are
+cached per recogniser state: the state is a small hashable tuple and the same states (inside a
+string, after a comma in an object, ...) come back all the time.
+
+The reference delegates this to xgrammar / llguidance (rust/engine/src/structured.rs); here the
+recogniser covers ``response_format: {"type": "json_object"}`` (OpenAI), ``format: "json"`` (Ollama)
+and the shape of ``json_schema`` requests (any valid JSON object; schema keywords are not enforced).
+"""
+from __future__ import annotations
+
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+# state = (mode, aux, stack); stack is a str of 'o' / 'a' (innermost last)
+State = Tuple[str, object, str]
+_WS = " \t\n\r"
+_DIG = "0123456789"
+_HEX = "0123456789abcdefABCDEF"
+_NUM_END = ("N0", "NI", "NF", "NE")          # modes in which a number may end
+
+
+def json_start(require_object: bool = True) -> State:
+    return ("V{" if require_object else "V", None, "")
+
+
+def _after_value(stack: str) -> State:
+    return ("A", None, stack) if stack else ("D", None, "")
+
+
+def json_step(st: State, ch: str) -> Optional[State]:
+    """The state after reading `ch`, or None when `ch` cannot follow."""
+    mode, aux, stack = st
+    if mode in ("V", "V{"):
+        if ch in _WS:
+            return st
+        if ch == "{":
+            return ("K", None, stack + "o")
+        if mode == "V{":
+            return None
+        if ch == "[":
+            return ("V]", None, stack + "a")
+        if ch == '"':
+            return ("S", "v", stack)
+        if ch == "-":
+            return ("N-", None, stack)
+        if ch == "0":
+            return ("N0", None, stack)
+        if ch in _DIG:
+            return ("NI", None, stack)
+        if ch == "t":
+            return ("L", "rue", stack)
+        if ch == "f":
+            return ("L", "alse", stack)
+        if ch == "n":
+            return ("L", "ull", stack)
+        return None
+    if mode == "V]":                             # first element of an array, or its end
+        if ch == "]":
+            return _after_value(stack[:-1])
+        if ch in _WS:
+            return st
+        return json_step(("V", None, stack), ch)
+    if mode == "S":
+        if ch == '"':
+            return ("C", None, stack) if aux == "k" else _after_value(stack)
+        if ch == "\\":
+            return ("E", aux, stack)
+        return st if ord(ch) >= 0x20 else None
+    if mode == "E":
+        if ch in '"\\/bfnrt':
+            return ("S", aux, stack)
+        if ch == "u":
+            return ("U", (aux, 4), stack)
+        return None
+    if mode == "U":
+        kind, left = aux
+        if ch not in _HEX:
+            return None
+        return ("S", kind, stack) if left == 1 else ("U", (kind, left - 1), stack)
+    if mode == "L":
+        if ch != aux[0]:
+            return None
+        return ("L", aux[1:], stack) if len(aux) > 1 else _after_value(stack)
+    if mode == "N-":
+        return ("N0", None, stack) if ch == "0" else ("NI", None, stack) if ch in _DIG else None
+    if mode in _NUM_END or mode in ("N.", "Ne", "Ns"):
+        if mode in ("NI", "NF", "NE") and ch in _DIG:
+            return st
+        if mode in ("N0", "NI") and ch == ".":
+            return ("N.", None, stack)
+        if mode == "N.":
+            return ("NF", None, stack) if ch in _DIG else None
+        if mode in ("N0", "NI", "NF") and ch in "eE":
+            return ("Ne", None, stack)
+        if mode == "Ne":
+            return ("Ns", None, stack) if ch in "+-" else ("NE", None, stack) if ch in _DIG else None
+        if mode == "Ns":
+            return ("NE", None, stack) if ch in _DIG else None
+        # a complete number ends at the first character that is not part of it
+        return json_step(_after_value(stack), ch)
+    if mode == "A":
+        if ch in _WS:
+            return st
+        top = stack[-1]
+        if ch == ",":
+            return ("K2", None, stack) if top == "o" else ("V", None, stack)
+        if ch == "}" and top == "o" or ch == "]" and top == "a":
+            return _after_value(stack[:-1])
+        return None
+    if mode in ("K", "K2"):
+        if ch in _WS:
+            return st
+        if ch == '"':
+            return ("S", "k", stack)
+        if ch == "}" and mode == "K":
+            return _after_value(stack[:-1])
+        return None
+    if mode == "C":
+        if ch in _WS:
+            return st
+        return ("V", None, stack) if ch == ":" else None
+    if mode == "D":
+        return st if ch in _WS else None
+    return None
+
+
+def json_complete(st: State) -> bool:
+    return st[0] == "D" or (st[0] in _NUM_END and not st[2])
+
+
+def json_feed(st: Optional[State], text: str) -> Optional[State]:
+    for ch in text:
+        if st is None:
+            return None
+        st = json_step(st, ch)
+    return st
+
+
+class TokenTrie:
+    """Trie over the text of every ordinary token. Tokens whose text is empty, contains the
+    replacement character (a partial UTF-8 sequence) or that are control tokens are left out."""
+
+    def __init__(self, pieces: Sequence[Optional[str]]):
+        self.vocab = len(pieces)
+        self.children: List[Dict[str, int]] = [{}]
+        self.ids: List[List[int]] = [[]]
+        for tid, text in enumerate(pieces):
+            if not text or "�" in text:
+                continue
+            node = 0
+            for ch in text:
+                nxt = self.children[node].get(ch)
+                if nxt is None:
+                    nxt = len(self.children)
+                    self.children[node][ch] = nxt
+                    self.children.append({})
+                    self.ids.append([])
+                node = nxt
+            self.ids[node].append(tid)
+
+    @classmethod
+    def from_tokenizer(cls, tokenizer, special_ids: Iterable[int] = ()) -> "TokenTrie":
+        special = set(int(s) for s in special_ids)
+        for name in ("bos_token_id", "eos_token_id"):
+            v = getattr(tokenizer, name, None)
+            if v is not None:
+                special.add(int(v))
+        pieces = [None if i in special else tokenizer.decode([i]) for i in range(tokenizer.vocab_size)]
+        return cls(pieces)
+
+    def allowed(self, st: State) -> List[int]:
+        out: List[int] = []
+        stack = [(0, st)]
+        children, ids = self.children, self.ids
+        while stack:
+            node, s = stack.pop()
+            for ch, nxt in children[node].items():
+                s2 = json_step(s, ch)
+                if s2 is None:
+                    continue
+                if ids[nxt]:
+                    out.extend(ids[nxt])
+                if children[nxt]:
+                    stack.append((nxt, s2))
+        return out
+
+
+class GuidedJson:
+    """Per-request constraint object: ``mask_words`` for the sampler, ``advance`` after each token."""
+
+    def __init__(self, trie: TokenTrie, tokenizer, eos_ids: Sequence[int], require_object: bool = True,
+                 cache: Optional[dict] = None):
+        self.trie, self.tok = trie, tokenizer
+        self.eos_ids = [int(e) for e in eos_ids if e is not None]
+        self.state: Optional[State] = json_start(require_object)
+        self.cache = cache if cache is not None else {}
+
+    @property
+    def complete(self) -> bool:
+        return self.state is not None and json_complete(self.state)
+
+    def mask_words(self, vocab: int) -> np.ndarray:
+        words = (vocab + 31) // 32
+        key = (self.state, vocab)
+        m = self.cache.get(key)
+        if m is None:
+            m = np.zeros(words, dtype=np.uint32)
+            if self.state is not None:
+                ids = np.asarray([t for t in self.trie.allowed(self.state) if t < vocab], dtype=np.int64)
+                if ids.size:
+                    np.bitwise_or.at(m, ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
+            if self.state is None or json_complete(self.state):
+                for e in self.eos_ids:
+                    if e < vocab:
+                        m[e >> 5] |= np.uint32(1 << (e & 31))
+            if len(self.cache) > 4096:
+                self.cache.clear()
+            self.cache[key] = m
+        return m
+
+    def advance(self, token_id: int) -> None:
+        if token_id in self.eos_ids or self.state is None:
+            return
+        self.state = json_feed(self.state, self.tok.decode([int(token_id)]))

@@ -34,6 +34,7 @@ class SamplingParams:
     timeout_s: Optional[float] = None
     cache_salt: str = ""
     speculative: bool = True
+    guided: Optional[object] = None      # runtime.grammar.GuidedJson: per-step allowed-token mask + advance()
 
     @property
     def greedy(self) -> bool:
@@ -43,7 +44,8 @@ class SamplingParams:
     def needs_full_sampler(self) -> bool:
         return (not self.greedy or self.repetition_penalty != 1.0 or self.presence_penalty != 0.0
                 or self.frequency_penalty != 0.0 or bool(self.logit_bias)
-                or self.allowed_token_ids is not None or bool(self.bad_words_ids) or self.logprobs)
+                or self.allowed_token_ids is not None or bool(self.bad_words_ids) or self.logprobs
+                or self.guided is not None)
 
     def validate(self, vocab_size: int) -> None:
         if self.temperature < 0:

@@ -56,7 +56,7 @@ def sample_step(engine, step, logits: torch.Tensor, greedy: torch.Tensor) -> tor
             bias[int(t)] = float("-inf")
         bias_lists.append(bias)
     allow = None
-    if any(req.params.allowed_token_ids is not None for _, req, _ in rows):
+    if any(req.params.allowed_token_ids is not None or req.params.guided is not None for _, req, _ in rows):
         words = (vocab + 31) // 32
         allow_np = np.full((len(rows), words), 0xFFFFFFFF, dtype=np.uint32)
         for i, (_, req, _) in enumerate(rows):
@@ -65,6 +65,8 @@ def sample_step(engine, step, logits: torch.Tensor, greedy: torch.Tensor) -> tor
                 allow_np[i] = 0
                 for t in a:
                     allow_np[i, t >> 5] |= np.uint32(1 << (t & 31))
+            if req.params.guided is not None:          # structured output: the grammar's mask for this state
+                allow_np[i] &= req.params.guided.mask_words(vocab)
         allow = allow_np
     if logits.is_cuda:
         from ..ops.native import pack_sample_rows
@@ -108,10 +110,9 @@ def sample_step(engine, step, logits: torch.Tensor, greedy: torch.Tensor) -> tor
                 x[t] = v
             for t, bv in bias_lists[i].items():
                 x[t] = x[t] + bv
-            if allow is not None and p.allowed_token_ids is not None:
-                mask = torch.full_like(x, float("-inf"))
-                mask[list(p.allowed_token_ids)] = 0
-                x = x + mask
+            if allow is not None and (p.allowed_token_ids is not None or p.guided is not None):
+                bits = np.unpackbits(allow[i].view(np.uint8), bitorder="little")[:vocab].astype(bool)
+                x = torch.where(torch.from_numpy(bits), x, torch.full_like(x, float("-inf")))
             prm = params[i]
             picked.append(sample_reference(x, prm[0], prm[6], prm[1], prm[2], prm[8], prm[7]))
         ids = torch.tensor(picked, dtype=torch.int32, device=logits.device)

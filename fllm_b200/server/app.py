@@ -193,9 +193,19 @@ class StopChecker:
         return out
 
 
-def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Optional[str] = None) -> FastAPI:
+def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Optional[str] = None,
+               tool_parser: Optional[str] = None, reasoning_parser: Optional[str] = None,
+               response_cache_entries: int = 256, response_cache_ttl_s: float = 600.0) -> FastAPI:
+    from .cache import ResponseCache, request_key
+    from .parsers import REASONING_PARSERS, TOOL_PARSERS, ReasoningStream, parse_tool_calls, split_reasoning
+    if tool_parser and tool_parser not in TOOL_PARSERS:
+        raise ValueError(f"--tool-parser must be one of {TOOL_PARSERS}")
+    if reasoning_parser and reasoning_parser not in REASONING_PARSERS:
+        raise ValueError(f"--reasoning-parser must be one of {REASONING_PARSERS}")
     metrics = Metrics()
     worker = EngineWorker(engine, metrics)
+    rcache = ResponseCache(response_cache_entries, response_cache_ttl_s)
+    guided_shared: dict = {}                     # token trie + mask cache, built on first use
 
     @contextlib.asynccontextmanager
     async def lifespan(_app):
@@ -269,12 +279,47 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
             raise
 
     async def collect(prompt_ids, sp):
-        text, toks, reason = [], [], None
-        async for piece in generate(prompt_ids, sp):
-            text.append(piece["text"])
-            toks.extend(piece["tokens"])
-            reason = piece["reason"] or reason
-        return "".join(text), toks, reason or "stop"
+        """Whole response of a non-streaming request; deterministic requests go through the
+        response cache and identical requests in flight share one generation."""
+        async def run():
+            text, toks, reason = [], [], None
+            async for piece in generate(prompt_ids, sp):
+                text.append(piece["text"])
+                toks.extend(piece["tokens"])
+                reason = piece["reason"] or reason
+            return "".join(text), toks, reason or "stop"
+        return await rcache.get_or_compute(request_key(model_name, prompt_ids, sp), run)
+
+    def attach_guided(sp: SamplingParams, body: dict) -> None:
+        """response_format json_object / json_schema (OpenAI) and format: "json" (Ollama) constrain the
+        output to a JSON object through the sampler's allowed-token mask."""
+        rf = body.get("response_format")
+        kind = rf.get("type") if isinstance(rf, dict) else None
+        fmt = body.get("format")
+        if kind not in ("json_object", "json_schema") and fmt != "json" and not isinstance(fmt, dict) \
+                and not body.get("guided_json"):
+            return
+        from ..runtime.grammar import GuidedJson, TokenTrie
+        if "trie" not in guided_shared:
+            guided_shared["trie"] = TokenTrie.from_tokenizer(tokenizer)
+            guided_shared["masks"] = {}
+        eos = [getattr(tokenizer, "eos_token_id", None), getattr(engine, "eos_token_id", None)]
+        sp.guided = GuidedJson(guided_shared["trie"], tokenizer, eos, require_object=True, cache=guided_shared["masks"])
+
+    def shape_message(text: str) -> "tuple[dict, bool]":
+        """Assistant message of a finished chat turn: reasoning split off, tool calls parsed."""
+        msg = {"role": "assistant"}
+        if reasoning_parser:
+            r, text = split_reasoning(text, reasoning_parser)
+            if r:
+                msg["reasoning_content"] = r
+        calls = []
+        if tool_parser:
+            text, calls = parse_tool_calls(text, tool_parser)
+        msg["content"] = text if (text or not calls) else None
+        if calls:
+            msg["tool_calls"] = calls
+        return msg, bool(calls)
 
     def sse(gen) -> StreamingResponse:
         return StreamingResponse(gen, media_type="text/event-stream")
@@ -316,7 +361,11 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
 
     @app.post("/admin/cache")
     async def admin_cache_reset():
-        return {"freed_blocks": engine.blocks.reset_prefix_cache()}
+        return {"freed_blocks": engine.blocks.reset_prefix_cache(), "dropped_responses": rcache.clear()}
+
+    @app.get("/admin/cache")
+    async def admin_cache_stats():
+        return {"responses": rcache.stats(), "prefix": dict(engine.blocks.stats)}
 
     # ------------------------------------------------------------------ OpenAI
     @app.get("/v1/models")
@@ -331,6 +380,7 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
     async def completions(body: dict):
         ids = encode_prompt(body.get("prompt", ""))
         sp = _sampling_from(body, 16)
+        attach_guided(sp, body)
         cid = "cmpl-" + uuid.uuid4().hex
         if body.get("stream"):
             async def gen():
@@ -360,6 +410,7 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
             raise HTTPException(400, "messages must be a non-empty list")
         ids = chat_prompt(msgs, body.get("tools"))
         sp = _sampling_from(body, 256)
+        attach_guided(sp, body)
         cid = "chatcmpl-" + uuid.uuid4().hex
         if body.get("stream"):
             async def gen():
@@ -367,19 +418,40 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
                         "choices": [{"index": 0, "delta": {"role": "assistant", "content": ""}, "finish_reason": None}]}
                 yield f"data: {json.dumps(head)}\n\n"
                 n = 0
+                rs = ReasoningStream(reasoning_parser) if reasoning_parser else None
+                held: List[str] = []                 # with a tool parser the text is held back and parsed at the end
                 async for piece in generate(ids, sp):
                     n += len(piece["tokens"])
+                    delta, fin = {}, piece["reason"] if piece["finished"] else None
+                    text = piece["text"]
+                    if rs is not None:
+                        r, text = rs.push(text, piece["finished"])
+                        if r:
+                            delta["reasoning_content"] = r
+                    if tool_parser:
+                        held.append(text)
+                        if piece["finished"]:
+                            rest, calls = parse_tool_calls("".join(held), tool_parser)
+                            if rest:
+                                delta["content"] = rest
+                            if calls:
+                                delta["tool_calls"] = [dict(c, index=i) for i, c in enumerate(calls)]
+                                fin = "tool_calls"
+                    elif text:
+                        delta["content"] = text
+                    if not delta and not piece["finished"]:
+                        continue
                     chunk = {"id": cid, "object": "chat.completion.chunk", "created": int(time.time()), "model": model_name,
-                             "choices": [{"index": 0, "delta": {"content": piece["text"]},
-                                          "finish_reason": piece["reason"] if piece["finished"] else None}]}
+                             "choices": [{"index": 0, "delta": delta, "finish_reason": fin}]}
                     if piece["finished"] and (body.get("stream_options") or {}).get("include_usage"):
                         chunk["usage"] = usage(len(ids), n)
                     yield f"data: {json.dumps(chunk)}\n\n"
                 yield "data: [DONE]\n\n"
             return sse(gen())
         text, toks, reason = await collect(ids, sp)
+        msg, has_calls = shape_message(text)
         return {"id": cid, "object": "chat.completion", "created": int(time.time()), "model": model_name,
-                "choices": [{"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": reason}],
+                "choices": [{"index": 0, "message": msg, "finish_reason": "tool_calls" if has_calls else reason}],
                 "usage": usage(len(ids), len(toks))}
 
     @app.post("/v1/chat/completions/render")
@@ -482,6 +554,7 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
         ids = encode_prompt(body.get("prompt", "")) if body.get("raw") or not body.get("system") else \
             chat_prompt([{"role": "system", "content": body["system"]}, {"role": "user", "content": body.get("prompt", "")}])
         sp = _sampling_from(body, 128, "ollama")
+        attach_guided(sp, body)
         now = lambda: time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime())
         if body.get("stream", True):
             return ollama_stream(ids, sp, lambda t, done: {"model": model_name, "created_at": now(), "response": t, "done": done})
@@ -493,6 +566,7 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
     async def ollama_chat(body: dict):
         ids = chat_prompt(body.get("messages", []), body.get("tools"))
         sp = _sampling_from(body, 128, "ollama")
+        attach_guided(sp, body)
         now = lambda: time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime())
         if body.get("stream", True):
             return ollama_stream(ids, sp, lambda t, done: {"model": model_name, "created_at": now(),
@@ -582,6 +656,7 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
 
 
 def serve(engine, tokenizer, host: str = "127.0.0.1", port: int = 8000, model_name: str = "fllm-b200",
-          api_key: Optional[str] = None, log_level: str = "info") -> None:
+          api_key: Optional[str] = None, log_level: str = "info", **app_options) -> None:
     import uvicorn
-    uvicorn.run(create_app(engine, tokenizer, model_name, api_key), host=host, port=port, log_level=log_level)
+    uvicorn.run(create_app(engine, tokenizer, model_name, api_key, **app_options), host=host, port=port,
+                log_level=log_level)

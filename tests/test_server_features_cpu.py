@@ -1,0 +1,180 @@
+"""Structured output, output parsers and the response cache (CPU)."""
+import asyncio
+import json
+
+import numpy as np
+import pytest
+
+from fllm_b200.runtime.grammar import GuidedJson, TokenTrie, json_complete, json_feed, json_start
+from fllm_b200.server.cache import ResponseCache, request_key
+from fllm_b200.server.parsers import ReasoningStream, parse_tool_calls, split_reasoning
+
+
+# ------------------------------------------------------------------ JSON recogniser
+@pytest.mark.parametrize("doc", ['{}', '{"a": 1}', ' {"a":[1,2.5e-3,true,null,"x\\n\\u00e9"],"b":{"c":[]}} ',
+                                 '{"k":"v","n":-0.5}', '{"a":[ ]}'])
+def test_valid_json_objects_are_accepted(doc):
+    st = json_feed(json_start(True), doc)
+    assert st is not None and json_complete(st)
+    json.loads(doc)
+
+
+@pytest.mark.parametrize("doc", ['[1]', '{"a" 1}', '{"a":01}', '{,}', '{"a":tru }', '{"a":"\\x"}', '{"a":1}}', '{"a":1,}'])
+def test_invalid_prefixes_are_rejected(doc):
+    assert json_feed(json_start(True), doc) is None
+
+
+def test_top_level_values_and_numbers_end_implicitly():
+    st = json_feed(json_start(False), "12.5")
+    assert st is not None and json_complete(st)
+    assert json_feed(json_start(False), "[1, 2") is not None and not json_complete(json_feed(json_start(False), "[1, 2"))
+
+
+class _Tok:
+    """Tiny vocabulary with multi-character pieces."""
+    pieces = ['{', '}', '"', 'a', 'b', '":', ' ', '1', '23', ',', '{"', 'tr', 'ue', '[', ']', '</s>', 'x}', '":1}']
+    vocab_size = len(pieces)
+    eos_token_id = 15
+
+    def decode(self, ids):
+        return "".join(self.pieces[i] for i in ids)
+
+
+def test_guided_json_masks_follow_the_grammar():
+    tok = _Tok()
+    trie = TokenTrie.from_tokenizer(tok)
+    g = GuidedJson(trie, tok, [tok.eos_token_id])
+
+    def allowed():
+        m = g.mask_words(tok.vocab_size)
+        return {tok.pieces[i] for i in range(tok.vocab_size) if (int(m[i >> 5]) >> (i & 31)) & 1}
+    assert allowed() == {'{', ' ', '{"'}                    # an object must start
+    g.advance(10)                                           # {"
+    assert allowed() >= {'a', 'b', '"', '":', ' ', '1', '23', ',', '{', '}', 'tr', 'ue', '[', ']', 'x}', '":1}'} - {'</s>'}
+    assert '</s>' not in allowed()
+    g.advance(3)                                            # a
+    g.advance(17)                                           # ":1}
+    assert g.complete and allowed() == {' ', '</s>'}
+    # random walks under the mask always produce parseable JSON once complete
+    rng = np.random.default_rng(0)
+    for _ in range(50):
+        g = GuidedJson(trie, tok, [tok.eos_token_id])
+        out = []
+        for _ in range(40):
+            m = g.mask_words(tok.vocab_size)
+            ids = [i for i in range(tok.vocab_size) if (int(m[i >> 5]) >> (i & 31)) & 1]
+            assert ids, "the grammar must never dead-end"
+            t = tok.eos_token_id if (g.complete and rng.random() < 0.7) else int(rng.choice(ids))
+            if t == tok.eos_token_id:
+                break
+            out.append(t)
+            g.advance(t)
+        if g.complete:
+            assert isinstance(json.loads(tok.decode(out)), dict)
+
+
+# ------------------------------------------------------------------ parsers
+def test_split_reasoning_and_stream_agree():
+    text = "<think>\nfirst, add.\n</think>\n\nThe answer is 4."
+    r, a = split_reasoning(text)
+    assert r == "first, add." and a == "The answer is 4."
+    assert split_reasoning("plain answer") == (None, "plain answer")
+    assert split_reasoning("thinking only</think>done") == ("thinking only", "done")
+    for cut in (1, 3, 7, 11):
+        rs = ReasoningStream()
+        pieces = [text[i:i + cut] for i in range(0, len(text), cut)]
+        rr, cc = "", ""
+        for i, p in enumerate(pieces):
+            x, y = rs.push(p, i == len(pieces) - 1)
+            rr += x
+            cc += y
+        assert rr.strip() == "first, add." and cc == "The answer is 4."
+
+
+def test_tool_call_styles():
+    h = 'Sure.\n<tool_call>\n{"name": "get_weather", "arguments": {"city": "Paris"}}\n</tool_call>'
+    rest, calls = parse_tool_calls(h, "hermes")
+    assert rest == "Sure." and calls[0]["function"]["name"] == "get_weather"
+    assert json.loads(calls[0]["function"]["arguments"]) == {"city": "Paris"}
+    rest, calls = parse_tool_calls('{"name": "f", "parameters": {"x": 1}}; {"name": "g", "parameters": {}}', "llama3_json")
+    assert rest == "" and [c["function"]["name"] for c in calls] == ["f", "g"]
+    rest, calls = parse_tool_calls('ok [TOOL_CALLS] [{"name": "f", "arguments": {"x": 2}}]', "mistral")
+    assert rest == "ok" and json.loads(calls[0]["function"]["arguments"]) == {"x": 2}
+    # malformed markup stays text
+    assert parse_tool_calls("<tool_call>{not json}</tool_call>", "hermes") == ("<tool_call>{not json}</tool_call>", [])
+    assert parse_tool_calls("just text", "llama3_json") == ("just text", [])
+
+
+# ------------------------------------------------------------------ response cache
+def test_response_cache_keys_ttl_lru_and_coalescing():
+    from fllm_b200.runtime import SamplingParams
+    greedy, sampled = SamplingParams(temperature=0.0), SamplingParams(temperature=0.8)
+    assert request_key("m", [1, 2], sampled) is None
+    assert request_key("m", [1, 2], SamplingParams(temperature=0.8, seed=3)) is not None
+    k1, k2 = request_key("m", [1, 2], greedy), request_key("m", [1, 3], greedy)
+    assert k1 != k2 and k1 == request_key("m", [1, 2], SamplingParams(temperature=0.0))
+    assert k1 != request_key("m", [1, 2], SamplingParams(temperature=0.0, cache_salt="tenant-b"))
+    now = [0.0]
+    c = ResponseCache(max_entries=2, ttl_s=10.0, clock=lambda: now[0])
+    c.put("a", 1); c.put("b", 2); c.put("c", 3)
+    assert c.get("a") is None and c.get("b") == 2 and c.get("c") == 3
+    now[0] = 11.0
+    assert c.get("b") is None
+
+    async def scenario():
+        cache, runs = ResponseCache(), []
+
+        async def compute():
+            runs.append(1)
+            await asyncio.sleep(0.01)
+            return "result"
+        got = await asyncio.gather(*[cache.get_or_compute("k", compute) for _ in range(5)])
+        assert got == ["result"] * 5 and len(runs) == 1 and cache.coalesced == 4
+        assert await cache.get_or_compute("k", compute) == "result" and len(runs) == 1 and cache.hits == 1
+        assert await cache.get_or_compute(None, compute) == "result" and len(runs) == 2
+    asyncio.run(scenario())
+
+
+# ------------------------------------------------------------------ through the HTTP API
+@pytest.fixture(scope="module")
+def client():
+    from fastapi.testclient import TestClient
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.runtime import LLMEngine
+    from fllm_b200.server.app import create_app
+    from fllm_b200.tokenizer import ByteTokenizer
+    cfg = preset("qwen3-tiny")
+    cfg.vocab_size = 512
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=8, max_num_batched_tokens=64, max_model_len=512, num_kv_blocks=128),
+                    device="cpu", eos_token_id=257)
+    app = create_app(eng, ByteTokenizer(512), "tiny", tool_parser="hermes", reasoning_parser="think")
+    with TestClient(app) as c:
+        yield c
+
+
+def test_json_mode_output_is_always_a_json_prefix(client):
+    for temp, seed in ((0.0, None), (1.0, 7), (1.5, 11)):
+        body = {"messages": [{"role": "user", "content": "give me json"}], "max_tokens": 24, "temperature": temp,
+                "response_format": {"type": "json_object"}}
+        if seed is not None:
+            body["seed"] = seed
+        r = client.post("/v1/chat/completions", json=body).json()
+        text = r["choices"][0]["message"]["content"] or ""
+        st = json_feed(json_start(True), text)
+        assert st is not None, text                       # a random model cannot leave the grammar
+        if r["choices"][0]["finish_reason"] == "stop":
+            assert isinstance(json.loads(text), dict)
+    o = client.post("/api/generate", json={"prompt": "x", "format": "json", "stream": False,
+                                           "options": {"num_predict": 12, "temperature": 0}}).json()
+    assert json_feed(json_start(True), o["response"]) is not None
+
+
+def test_identical_greedy_requests_hit_the_response_cache(client):
+    before = client.get("/admin/cache").json()["responses"]
+    body = {"prompt": "cache me", "max_tokens": 6, "temperature": 0}
+    a = client.post("/v1/completions", json=body).json()
+    b = client.post("/v1/completions", json=body).json()
+    after = client.get("/admin/cache").json()["responses"]
+    assert a["choices"][0]["token_ids"] == b["choices"][0]["token_ids"]
+    assert after["hits"] == before["hits"] + 1 and after["entries"] >= 1
+    assert client.post("/admin/cache").json()["dropped_responses"] >= 1
