@@ -258,7 +258,7 @@ class ParallelConfig:
     tp: int = 1
     pp: int = 1
     expert_parallel: bool = False
-    ep_dispatch: str = "alltoall"        # alltoall | allreduce
+    ep_dispatch: str = "allreduce"       # allreduce (partial sums reduced like a dense FFN) | alltoall (rows travel to the experts' ranks and back over peer memory)
     pipeline_microbatches: int = 0       # 0 = one per stage
     distributed_backend: str = "fused"   # fused (peer-memory kernels) | nccl (baseline)
     nnodes: int = 1

@@ -4,6 +4,8 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
 
+#include <vector>
+
 #include "fllm_ops.h"
 
 namespace {
@@ -58,6 +60,64 @@ void moe_combine(const Tensor& y, const Tensor& row_of, const Tensor& weights, T
   fllm::moe_combine(y.data_ptr(), y.stride(0), row_of.data_ptr<int>(), weights.data_ptr<float>(), (int)out.size(0),
                     (int)row_of.size(1), out.data_ptr(), out.stride(0), (int)out.size(1), cur_stream());
 }
+
+// ---- expert-parallel all-to-all: a context of every rank's buffer addresses, then the four steps
+std::vector<fllm::EpArgs> g_ep;
+
+int64_t ep_ctx_create(int64_t ranks, int64_t my_rank, int64_t cap, int64_t hidden, int64_t experts_per_rank,
+                      std::vector<int64_t> recv_x, std::vector<int64_t> recv_meta, std::vector<int64_t> ctrl,
+                      std::vector<int64_t> comb_y) {
+  TORCH_CHECK(ranks >= 1 && ranks <= fllm::kMaxEp, "1..8 ranks");
+  TORCH_CHECK((int64_t)recv_x.size() == ranks && (int64_t)recv_meta.size() == ranks && (int64_t)ctrl.size() == ranks &&
+              (int64_t)comb_y.size() == ranks, "one address per rank expected");
+  fllm::EpArgs a{};
+  for (int i = 0; i < ranks; ++i) {
+    a.recv_x[i] = reinterpret_cast<void*>(recv_x[i]);
+    a.recv_meta[i] = reinterpret_cast<void*>(recv_meta[i]);
+    a.ctrl[i] = reinterpret_cast<void*>(ctrl[i]);
+    a.comb_y[i] = reinterpret_cast<void*>(comb_y[i]);
+  }
+  a.ranks = (int)ranks; a.my_rank = (int)my_rank; a.cap = (int)cap; a.hidden = (int)hidden;
+  a.experts_per_rank = (int)experts_per_rank;
+  g_ep.push_back(a);
+  return (int64_t)g_ep.size() - 1;
+}
+
+const fllm::EpArgs& ep_at(int64_t h) {
+  TORCH_CHECK(h >= 0 && h < (int64_t)g_ep.size(), "invalid expert-parallel context handle");
+  return g_ep[h];
+}
+
+void ep_dispatch(int64_t h, const Tensor& x, const Tensor& ids, int64_t epoch, const optional<Tensor>& status) {
+  const auto& a = ep_at(h);
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 && x.size(1) == a.hidden, "x: [tokens, hidden] bf16");
+  TORCH_CHECK(ids.scalar_type() == at::kInt && ids.is_contiguous() && ids.dim() == 2 && ids.size(0) == x.size(0), "ids: [tokens, k] int32");
+  c10::cuda::CUDAGuard guard(x.device());
+  fllm::ep_dispatch(a, x.data_ptr(), x.stride(0), ids.data_ptr<int>(), (int)x.size(0), (int)ids.size(1), (unsigned)epoch,
+                    status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr, cur_stream());
+}
+
+void ep_ingest(int64_t h, int64_t epoch, Tensor ids_out, Tensor count_out, const optional<Tensor>& status) {
+  const auto& a = ep_at(h);
+  TORCH_CHECK(ids_out.scalar_type() == at::kInt && ids_out.is_contiguous() && ids_out.numel() == a.cap, "ids_out: [cap] int32");
+  TORCH_CHECK(count_out.scalar_type() == at::kInt && count_out.numel() >= 1, "count_out: int32");
+  c10::cuda::CUDAGuard guard(ids_out.device());
+  fllm::ep_ingest(a, (unsigned)epoch, ids_out.data_ptr<int>(), count_out.data_ptr<int>(),
+                  status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr, cur_stream());
+}
+
+void ep_return(int64_t h, const Tensor& y, const Tensor& row_of, const Tensor& count, int64_t epoch) {
+  const auto& a = ep_at(h);
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.stride(1) == 1 && y.size(1) == a.hidden, "y: [rows, hidden] bf16");
+  TORCH_CHECK(row_of.scalar_type() == at::kInt && row_of.is_contiguous() && row_of.numel() == a.cap, "row_of: [cap] int32");
+  c10::cuda::CUDAGuard guard(y.device());
+  fllm::ep_return(a, y.data_ptr(), y.stride(0), row_of.data_ptr<int>(), count.data_ptr<int>(), (unsigned)epoch, cur_stream());
+}
+
+void ep_wait_returns(int64_t h, int64_t epoch, const Tensor& status) {
+  c10::cuda::CUDAGuard guard(status.device());
+  fllm::ep_wait_returns(ep_at(h), (unsigned)epoch, status.data_ptr<int>(), cur_stream());
+}
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
@@ -66,4 +126,9 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("moe_gather(Tensor x, Tensor token_of, Tensor(a!) xp) -> ()", &moe_gather);
   m.def("moe_grouped_linear(Tensor xp, Tensor w_stack, Tensor? bias_stack, Tensor(a!) y, Tensor tile_expert, Tensor tile_row0, Tensor num_tiles, int bn, Tensor? status) -> int", &moe_grouped_linear);
   m.def("moe_combine(Tensor y, Tensor row_of, Tensor weights, Tensor(a!) out) -> ()", &moe_combine);
+  m.def("ep_ctx_create(int ranks, int my_rank, int cap, int hidden, int experts_per_rank, int[] recv_x, int[] recv_meta, int[] ctrl, int[] comb_y) -> int", &ep_ctx_create);
+  m.def("ep_dispatch(int ctx, Tensor x, Tensor ids, int epoch, Tensor? status) -> ()", &ep_dispatch);
+  m.def("ep_ingest(int ctx, int epoch, Tensor(a!) ids_out, Tensor(b!) count_out, Tensor? status) -> ()", &ep_ingest);
+  m.def("ep_return(int ctx, Tensor y, Tensor row_of, Tensor count, int epoch) -> ()", &ep_return);
+  m.def("ep_wait_returns(int ctx, int epoch, Tensor(a!) status) -> ()", &ep_wait_returns);
 }

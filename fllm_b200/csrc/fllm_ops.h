@@ -90,6 +90,22 @@ int linear_w4a16(const void* x, long long ldx, const void* codes, const void* sc
 void w4_dequant_bf16(const void* codes, const void* scales, int fmt, float alpha, void* out, long long rows, int K,
                      cudaStream_t s);
 
+// ---- expert-parallel all-to-all over peer memory (csrc/moe_a2a.cu) -----------------------
+constexpr int kMaxEp = 8;
+struct EpArgs {
+  void* recv_x[kMaxEp];       // [cap][hidden] bf16 on each rank
+  void* recv_meta[kMaxEp];    // [cap] int4 on each rank
+  void* ctrl[kMaxEp];         // 32 uint32 on each rank, zero-initialised
+  void* comb_y[kMaxEp];       // [max entries][hidden] bf16 on each rank
+  int ranks, my_rank, cap, hidden, experts_per_rank;
+};
+void ep_dispatch(const EpArgs& a, const void* x, long long ldx, const int* ids, int tokens, int k, unsigned epoch,
+                 int* status, cudaStream_t s);
+void ep_ingest(const EpArgs& a, unsigned epoch, int* ids_out, int* count_out, int* status, cudaStream_t s);
+void ep_return(const EpArgs& a, const void* y, long long ldy, const int* row_of, const int* count, unsigned epoch,
+               cudaStream_t s);
+void ep_wait_returns(const EpArgs& a, unsigned epoch, int* status, cudaStream_t s);
+
 // ---- mixture of experts ---------------------------------------------------------------
 int moe_grouped_linear_bf16(const void* xp, long long ldx, const void* w_stack, long long ldw,
                             const void* bias_stack, void* y, long long ldy, int rows_cap, int n_out, int K,

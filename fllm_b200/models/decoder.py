@@ -88,11 +88,16 @@ class Decoder:
                 elif packed[0] in ("nvfp4", "mxfp4"):
                     from ..ops.fp4 import FMT_NAMES, Fp4Weight
                     setattr(lw, name, Fp4Weight(packed[1], packed[2], FMT_NAMES[packed[0]], packed[3] if len(packed) > 3 else 1.0))
+        self.ep_a2a = None            # comm.ep_a2a.EpAllToAll when expert parallelism dispatches rows all-to-all
+        self._reduced = False
         self._dense_weights = all(isinstance(getattr(lw, n, None), torch.Tensor) for lw in self.w.layers
                                   for n in ("wqkv", "wo", "w_gate_up", "w_down") if getattr(lw, n, None) is not None)
 
     # ------------------------------------------------------------------ pieces
     def _reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self._reduced:
+            self._reduced = False
+            return x
         if self.tp is not None and self.tp.size > 1:
             return self.tp.all_reduce(x)
         return x
@@ -114,7 +119,10 @@ class Decoder:
     def _ffn_block(self, lw, h: torch.Tensor) -> torch.Tensor:
         cfg, ops = self.cfg, self.ops
         if cfg.is_moe:
-            from .moe import moe_ffn
+            from .moe import moe_ffn, moe_ffn_alltoall
+            if self.ep_a2a is not None:
+                self._reduced = True                 # rows come back complete: nothing left to reduce
+                return moe_ffn_alltoall(self, lw, h)
             return moe_ffn(self, lw, h)
         gu = ops.linear(h, lw.w_gate_up)
         act = ops.glu(gu, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit)

@@ -105,3 +105,24 @@ def moe_ffn(dec, lw, h: torch.Tensor) -> torch.Tensor:
     k_ops.moe_combine(y, row_of, wts, out)
     ops.launches += 6
     return out
+
+
+def moe_ffn_alltoall(dec, lw, h: torch.Tensor) -> torch.Tensor:
+    """Expert parallelism with all-to-all dispatch. Activations are replicated across the group, so
+    each rank treats an equal slice of the rows as its own, sends those rows to the ranks that hold
+    their experts, receives the expert outputs back, forms the weighted sum for its rows and
+    all-gathers the result. Every (token, expert) pair is computed once in the whole group and only
+    routed rows cross NVLink (rust/engine/src/parallel/decoder_shard.rs:442-508)."""
+    from ..comm.ep_a2a import moe_ffn_a2a_phases
+    ep, tp = dec.ep_a2a, dec.tp
+    T, H = h.shape
+    per = -(-T // ep.ranks)
+    own = torch.zeros(per, H, dtype=h.dtype, device=h.device)          # rows past T stay zero (padding)
+    lo = min(ep.rank * per, T)
+    n = max(min(lo + per, T) - lo, 0)
+    if n:
+        own[:n] = h[lo:lo + n]
+    out = None
+    for out in moe_ffn_a2a_phases(dec, lw, ep, own):
+        pass
+    return tp.all_gather(out.contiguous()).reshape(ep.ranks * per, H)[:T]

@@ -77,6 +77,13 @@ class LLMEngine:
         self.decoder = Decoder(model_cfg, self.weights, self.kv, self.ops, self.spec, tp_group,
                                layer_range=self.layer_range, first_stage=self.first_stage,
                                last_stage=self.last_stage)
+        # expert parallel with all-to-all dispatch: peer buffers for the rows each rank owns
+        if (self.is_cuda and model_cfg.is_moe and self.par.expert_parallel and self.par.ep_dispatch == "alltoall"
+                and tp > 1 and getattr(tp_group, "group", None) is not None):
+            from ..comm.ep_a2a import EpAllToAll
+            rows = -(-self.cfg.max_num_batched_tokens // tp)
+            self.decoder.ep_a2a = EpAllToAll(tp, tp_rank, model_cfg.hidden_size, model_cfg.num_experts // tp, rows,
+                                             model_cfg.experts_per_token, self.device, group=tp_group.group)
         self.blocks = BlockManager(num_blocks, self.block_size, self.cfg.enable_prefix_caching,
                                    self.cfg.watermark)
         window = model_cfg.sliding_window if (model_cfg.sliding_window and model_cfg.window_pattern is None) else 0
@@ -291,7 +298,9 @@ class LLMEngine:
                 and self.proposer is None)
 
     def _graph_eligible(self, step: ScheduledStep) -> bool:
+        # the all-to-all kernels take the call number from the host, which a captured graph would freeze
         return (self.is_cuda and self.cfg.use_cuda_graphs and step.all_decode and self.par.pp == 1
+                and getattr(self.decoder, "ep_a2a", None) is None
                 and not any(s.verify for s in step.seqs) and self._bucket_for(len(step.seqs)) > 0)
 
     def _precommit(self, fl) -> None:

@@ -430,3 +430,45 @@ def test_int4_from_q4_k_file_blocks(ops):
     q = Int4Weight.from_gguf("Q4_K", raw, 384, 1024, device="cuda")
     x = _rand((20, 1024), 3)
     _close(ops.linear(x, q), x.float() @ want.t(), 2e-2)
+
+
+@pytest.mark.parametrize("ranks,T,E,k", [(2, 24, 8, 2), (4, 40, 16, 4), (4, 7, 8, 4)])
+def test_expert_parallel_all_to_all_emulated(ops, ranks, T, E, k):
+    """Dispatch / return over peer buffers with `ranks` virtual ranks on one GPU (their kernels run
+    phase by phase, never waiting on each other): every rank's rows, routed to experts held by other
+    ranks and back, must equal the fp32 oracle computed with all experts local. Run twice to cover
+    the counter reset and the monotonic flags."""
+    from types import SimpleNamespace
+    from fllm_b200.comm.ep_a2a import EpAllToAll, moe_ffn_a2a_phases
+    from fllm_b200.config import ModelConfig
+    from fllm_b200.models.moe import moe_reference
+    from fllm_b200.models.weights import LayerWeights
+    H, I = 256, 128
+    cfg = ModelConfig(hidden_size=H, num_experts=E, experts_per_token=k, moe_intermediate_size=I, act="swiglu_oai",
+                      expert_bias=True)
+    full = LayerWeights(attn_norm=None, wqkv=None, wo=None, ffn_norm=None)
+    full.router_w, full.router_b = _rand((E, H), 1, 0.2), _rand((E,), 2, 0.1)
+    full.exp_gate_up, full.exp_gate_up_b = _rand((E, 2 * I, H), 3, 0.05), _rand((E, 2 * I), 4, 0.1)
+    full.exp_down, full.exp_down_b = _rand((E, H, I), 5, 0.05), _rand((E, H), 6, 0.1)
+    per = E // ranks
+    shards = []
+    for r in range(ranks):
+        lw = LayerWeights(attn_norm=None, wqkv=None, wo=None, ffn_norm=None)
+        lw.router_w, lw.router_b = full.router_w, full.router_b
+        sl = slice(r * per, (r + 1) * per)
+        lw.exp_gate_up, lw.exp_gate_up_b = full.exp_gate_up[sl].contiguous(), full.exp_gate_up_b[sl].contiguous()
+        lw.exp_down, lw.exp_down_b = full.exp_down[sl].contiguous(), full.exp_down_b[sl].contiguous()
+        shards.append(lw)
+    eps = EpAllToAll.local_group(ranks, H, per, max_tokens=64, k=k)
+    dec = SimpleNamespace(cfg=cfg, ops=ops, act_kind=2)
+    for round_ in range(2):
+        hs = [_rand((T, H), 10 + 7 * round_ + r) for r in range(ranks)]
+        gens = [moe_ffn_a2a_phases(dec, shards[r], eps[r], hs[r]) for r in range(ranks)]
+        assert [next(g) for g in gens] == ["dispatched"] * ranks
+        assert [next(g) for g in gens] == ["returned"] * ranks
+        outs = [next(g) for g in gens]
+        torch.cuda.synchronize()
+        for r in range(ranks):
+            _close(outs[r], moe_reference(cfg, full, hs[r], 0), 3e-2)
+            assert eps[r].check_status() == 0
+    assert ops.check_status() == 0

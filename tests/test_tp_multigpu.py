@@ -26,3 +26,24 @@ def test_tp_matches_single_device_on_gpus(world, backend):
     assert res["logit_err"] < 3e-2, res
     assert res["agree"] >= 0.7 * res["total"], res
     assert res["graph_steps"] > 0
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_all_to_all_on_gpus(world):
+    """Token rows dispatched to the experts' ranks and returned through CUDA-IPC peer buffers
+    (system-scope atomics for the row counter, release stores for the flags), three rounds."""
+    _need(world)
+    res = run_ranks(world, ["cuda", "ep_a2a"], timeout=300)
+    assert res["status"] == 0, res
+    assert res["err"] < 3e-2, res
+
+
+@pytest.mark.parametrize("mode", ["allreduce", "alltoall"])
+def test_gpt_oss_expert_parallel_modes_on_gpus(mode):
+    """gpt-oss-tiny with its experts partitioned over 2 GPUs: partial sums reduced like a dense FFN,
+    or rows dispatched all-to-all over peer memory; both must reproduce the single-device model."""
+    _need(2)
+    res = run_ranks(2, ["cuda", "nccl", "gpt-oss-tiny", "1", mode], timeout=300)
+    assert res["status"] == 0, res
+    assert res["logit_err"] < 3e-2, res
+    assert res["agree"] >= 0.7 * res["total"], res

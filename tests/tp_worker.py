@@ -16,10 +16,65 @@ from fllm_b200.parallel.tp import LibraryTP, make_tp_runtime  # noqa: E402
 from fllm_b200.runtime import LLMEngine, SamplingParams  # noqa: E402
 
 
+def ep_a2a_main():
+    """Expert-parallel all-to-all across real GPUs: every rank owns a slice of the experts and a set
+    of rows; rows travel to the experts' ranks and back through peer memory. Compared with the fp32
+    oracle that has all experts local."""
+    from types import SimpleNamespace
+    from fllm_b200.comm.ep_a2a import EpAllToAll, moe_ffn_a2a_phases
+    from fllm_b200.config import ModelConfig
+    from fllm_b200.models.moe import moe_reference
+    from fllm_b200.models.weights import LayerWeights
+    from fllm_b200.ops.native import NativeOps
+    rank, world, local = init_distributed("nccl", timeout_s=120)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    grp = Group()
+    H, I, E, k, T = 256, 128, 16, 4, 40
+    cfg = ModelConfig(hidden_size=H, num_experts=E, experts_per_token=k, moe_intermediate_size=I, act="swiglu_oai",
+                      expert_bias=True)
+
+    def rnd(shape, seed, scale=1.0):
+        g = torch.Generator().manual_seed(seed)
+        return (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).to(dev)
+    full = LayerWeights(attn_norm=None, wqkv=None, wo=None, ffn_norm=None)
+    full.router_w, full.router_b = rnd((E, H), 1, 0.2), rnd((E,), 2, 0.1)
+    full.exp_gate_up, full.exp_gate_up_b = rnd((E, 2 * I, H), 3, 0.05), rnd((E, 2 * I), 4, 0.1)
+    full.exp_down, full.exp_down_b = rnd((E, H, I), 5, 0.05), rnd((E, H), 6, 0.1)
+    per = E // world
+    sl = slice(rank * per, (rank + 1) * per)
+    lw = LayerWeights(attn_norm=None, wqkv=None, wo=None, ffn_norm=None)
+    lw.router_w, lw.router_b = full.router_w, full.router_b
+    lw.exp_gate_up, lw.exp_gate_up_b = full.exp_gate_up[sl].contiguous(), full.exp_gate_up_b[sl].contiguous()
+    lw.exp_down, lw.exp_down_b = full.exp_down[sl].contiguous(), full.exp_down_b[sl].contiguous()
+    ops = NativeOps(dev)
+    ep = EpAllToAll(world, rank, H, per, max_tokens=64, k=k, device=dev, group=grp)
+    dec = SimpleNamespace(cfg=cfg, ops=ops, act_kind=2)
+    worst = 0.0
+    for round_ in range(3):
+        h = rnd((T, H), 100 + 13 * round_ + rank)
+        out = None
+        for out in moe_ffn_a2a_phases(dec, lw, ep, h):
+            pass
+        torch.cuda.synchronize()
+        want = moe_reference(cfg, full, h, 0)
+        worst = max(worst, float((out.float() - want).abs().max() / (want.abs().max() + 1e-6)))
+    st = torch.tensor([ep.check_status() | ops.check_status(), int(worst * 1e6)], device=dev)
+    torch.distributed.all_reduce(st, op=torch.distributed.ReduceOp.MAX)
+    if rank == 0:
+        print(json.dumps({"world": world, "status": int(st[0]), "err": int(st[1]) / 1e6}))
+    torch.distributed.barrier()
+    from fllm_b200.comm import shutdown_distributed
+    shutdown_distributed()
+
+
 def main():
     faulthandler.dump_traceback_later(int(os.environ.get("FLLM_HANG_DUMP", "150")), exit=True)
+    if len(sys.argv) > 2 and sys.argv[2] == "ep_a2a":
+        return ep_a2a_main()
     device_kind, backend, model = sys.argv[1], sys.argv[2], sys.argv[3]
     pp = int(sys.argv[4]) if len(sys.argv) > 4 else 1
+    ep_mode = sys.argv[5] if len(sys.argv) > 5 else "none"          # none | allreduce | alltoall
     rank, world, local = init_distributed("gloo" if device_kind == "cpu" else "nccl", timeout_s=120)
     dev = torch.device("cpu") if device_kind == "cpu" else torch.device("cuda", local)
     cfg = preset(model)
@@ -40,7 +95,9 @@ def main():
                                 max_tokens=ec.max_num_batched_tokens)
     else:
         tp_rt = LibraryTP(grp)
-    eng = LLMEngine(cfg, ec, ParallelConfig(tp=tp, pp=pp), device=dev, tp_group=tp_rt, tp_rank=tp_rank, seed=3,
+    par = ParallelConfig(tp=tp, pp=pp, expert_parallel=ep_mode != "none",
+                         ep_dispatch=ep_mode if ep_mode != "none" else "allreduce")
+    eng = LLMEngine(cfg, ec, par, device=dev, tp_group=tp_rt, tp_rank=tp_rank, seed=3,
                     pp_group=pp_grp, stage=stage)
     got = eng.generate(prompts, sp)
 
