@@ -47,6 +47,8 @@ struct GemmArgs {
   int kb_per_split;
   int k_splits;
   int transposed;          // 0: out[m*ldc+n], 1: out[n*ldc+m]
+  int cluster_red;         // split-K reduced on chip: the k_splits CTAs of a tile form a thread-block cluster,
+                           // park their fp32 tiles in shared memory and each adds a slice through DSMEM
   long long ldc;
   __nv_bfloat16* out;
   float* ws;               // split-K partials, [k_splits][tiles][BN][128] fp32 (tile-local, column-major)
@@ -162,8 +164,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
     if (lane == 0 && !grouped) {
       const int w = blockIdx.x;
       if (w < total && !(p.tune & 2)) {
-        const int split = w / tiles;
-        const int t = w - split * tiles;
+        const int split = p.cluster_red ? w % p.k_splits : w / tiles;
+        const int t = p.cluster_red ? w / p.k_splits : w - split * tiles;
         const int n_idx = t / p.m_tiles;
         const int m_idx = t - n_idx * p.m_tiles;
         const int kb0 = split * p.kb_per_split;
@@ -201,8 +203,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
       uint32_t phase = 0;
       bool ok = *abort_flag == 0;
       for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
-        const int split = w / tiles;
-        const int t = w - split * tiles;
+        const int split = p.cluster_red ? w % p.k_splits : w / tiles;
+        const int t = p.cluster_red ? w / p.k_splits : w - split * tiles;
         const int n_idx = t / p.m_tiles;
         const int m_idx = t - n_idx * p.m_tiles;
         const int kb0 = split * p.kb_per_split;
@@ -253,7 +255,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
-        const int split = w / tiles;
+        const int split = p.cluster_red ? w % p.k_splits : w / tiles;
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
@@ -286,8 +288,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
-      const int split = w / tiles;
-      const int t = w - split * tiles;
+      const int split = p.cluster_red ? w % p.k_splits : w / tiles;
+      const int t = p.cluster_red ? w / p.k_splits : w - split * tiles;
       const int n_idx = t / p.m_tiles;
       const int m_idx = t - n_idx * p.m_tiles;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
@@ -411,6 +413,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
         }
         tc_fence_before_sync();
         mbar_arrive(&tempty_bar[acc]);
+      } else if (p.cluster_red) {
+        // split-K inside a cluster: park the fp32 tile ([token column][feature row], lanes contiguous) in
+        // the operand ring, which is idle once this CTA's only accumulator is complete; the cluster
+        // adds the tiles after the barrier at the end of the kernel
+        float* red = reinterpret_cast<float*>(smem);
+        emitted = false;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          float v[32];
+          load_chunk(c0, v);
+#pragma unroll
+          for (int c = 0; c < CH; ++c) red[(c0 + c) * BM + q * 32 + lane] = v[c];
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&tempty_bar[acc]);
       } else if (!p.fixup) {
         // split-K, local output: dense fp32 partials [split][token][feature]; a second kernel adds them
         float* wsp = p.ws + (size_t)split * p.M * p.N;
@@ -522,6 +539,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, S::kTmemCols);
   }
+  if (p.cluster_red) {
+    // Every thread of every CTA of the cluster comes here (waits that gave up leave their tile
+    // unfinished but still arrive), so the hardware barrier cannot be left hanging.
+    cluster_sync();
+    if (warp >= 2 && !*abort_flag) {
+      const int w = blockIdx.x;
+      const int t = w / p.k_splits, rank = w % p.k_splits;
+      const int n_idx = t / p.m_tiles, m_idx = t - n_idx * p.m_tiles;
+      const int tid = threadIdx.x - 64;
+      constexpr int kVec = BN * BM / 4;                       // float4 items of the tile
+      const int v0 = (int)((long long)kVec * rank / p.k_splits), v1 = (int)((long long)kVec * (rank + 1) / p.k_splits);
+      const uint32_t red_local = smem_u32(smem);
+      for (int i = v0 + tid; i < v1; i += 128) {
+        float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sp = 0; sp < p.k_splits; ++sp) {              // split order, like the reduction kernel
+          const float4 x = ld_dsmem_f4(red_local + (uint32_t)i * 16u, (uint32_t)sp);
+          acc4.x += x.x; acc4.y += x.y; acc4.z += x.z; acc4.w += x.w;
+        }
+        const int c = i / (BM / 4), mrow = m_idx * BM + (i % (BM / 4)) * 4;
+        const int n = n_idx * BN + c;
+        if (n < p.N && mrow < p.M) {
+          if (p.bias) {
+            acc4.x += __bfloat162float(p.bias[mrow]);     acc4.y += __bfloat162float(p.bias[mrow + 1]);
+            acc4.z += __bfloat162float(p.bias[mrow + 2]); acc4.w += __bfloat162float(p.bias[mrow + 3]);
+          }
+          uint2 o;
+          o.x = pack_bf16x2(acc4.x, acc4.y);
+          o.y = pack_bf16x2(acc4.z, acc4.w);
+          *reinterpret_cast<uint2*>(p.out + (size_t)n * p.ldc + mrow) = o;
+        }
+      }
+    }
+    cluster_sync();                                            // peers may still be reading this CTA's tile
+  }
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicCAS(p.status, FLLM_OK, FLLM_ERR_MBAR_TIMEOUT);
   if (threadIdx.x == 0 && p.ag_flags) {
     // the last CTA to leave records that this launch consumed every rank's rows
@@ -607,6 +658,20 @@ splitk_reduce_push_kernel(const float* __restrict__ ws, int splits, int rows, in
   }
 }
 
+// FLLM_CLUSTER_SPLITK=1 reduces split-K on chip (cluster + distributed shared memory) instead of through
+// partial sums in global memory + a reduction kernel. Off by default: measured on B200 it gains ~1 us on
+// the 32-tile projections but clusters of 6-8 CTAs do not all fit the GPCs at once for 48 tiles
+// (34.8 vs 25.6 us), and a cluster launch waits for whole-GPC room, which costs the overlap between
+// consecutive kernels of a decode step (6.28 vs 5.66 ms per step).
+static bool cluster_splitk_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("FLLM_CLUSTER_SPLITK");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+
 template <int BN>
 static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, int grid,
                         cudaStream_t stream) {
@@ -622,7 +687,11 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
                "cudaFuncSetAttribute(carveout)");
     configured = true;
   }
-  launch_pdl(gemm_bf16_kernel<BN>, dim3(grid), dim3(kGemmThreads), S::kTotal, stream, ta, tb, a);
+  if (a.cluster_red)
+    launch_pdl_cluster(gemm_bf16_kernel<BN>, dim3(grid), dim3(kGemmThreads), S::kTotal, stream, (unsigned)a.k_splits, ta,
+                       tb, a);
+  else
+    launch_pdl(gemm_bf16_kernel<BN>, dim3(grid), dim3(kGemmThreads), S::kTotal, stream, ta, tb, a);
 }
 
 // Resident CTAs per SM of the GEMM kernel for a token-tile width (diagnostics).
@@ -764,8 +833,17 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
   }
   if (!a.fixup)
     while (splits > 1 && kCounterBytes + (size_t)splits * a.M * a.N * sizeof(float) > workspace_bytes) --splits;
+  // On-chip reduction: the splits of a tile run as one thread-block cluster (at most 8 CTAs, one unit
+  // per CTA) and add their tiles through distributed shared memory: no partial sums in global memory
+  // and no second kernel. Decode orientation with a local output only.
+  const int slots_now = sms * (bn <= 64 ? 2 : 1);
+  bool cluster = cluster_splitk_enabled() && swap && !rs && splits > 1 && bn <= 128 && (N % 4) == 0 &&
+                 (ldy % 4) == 0 && (reinterpret_cast<uintptr_t>(y) % 8) == 0;
+  if (cluster && splits > 8) splits = 8;
   a.kb_per_split = (a.k_blocks + splits - 1) / splits;
   a.k_splits = (a.k_blocks + a.kb_per_split - 1) / a.kb_per_split;
+  if (cluster && (a.k_splits < 2 || tiles * a.k_splits > slots_now)) cluster = false;
+  a.cluster_red = cluster ? 1 : 0;
   a.tile_counters = reinterpret_cast<unsigned int*>(workspace);
   a.ws = a.k_splits > 1 ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + kCounterBytes) : nullptr;
   // 16-byte stores of the transposed epilogue need 16-byte aligned token rows
@@ -800,6 +878,7 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
                a.bias, ra);
     return 2;
   }
+  if (a.cluster_red) return 1;
   if (a.k_splits > 1 && !a.fixup) {
     // dense [token][feature] partials in both orientations
     const size_t n = (size_t)T * N;

@@ -89,6 +89,27 @@ inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
   cuda_check(cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...), "cudaLaunchKernelEx");
 }
 
+// Same, with the grid cut into thread-block clusters of `cluster_x` consecutive CTAs.
+template <typename... KArgs, typename... Args>
+inline void launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               unsigned cluster_x, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = cluster_x;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  cuda_check(cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...), "cudaLaunchKernelEx(cluster)");
+}
+
 inline int sm_count() {
   static int n[16] = {0};
   int dev = 0;

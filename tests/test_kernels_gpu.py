@@ -472,3 +472,32 @@ def test_expert_parallel_all_to_all_emulated(ops, ranks, T, E, k):
             _close(outs[r], moe_reference(cfg, full, hs[r], 0), 3e-2)
             assert eps[r].check_status() == 0
     assert ops.check_status() == 0
+
+
+def test_cluster_splitk_reduction_opt_in():
+    """The on-chip split-K reduction (thread-block cluster + distributed shared memory) is opt-in through
+    the environment, which the library reads once: run it in a child process against fp32 math."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import torch\n"
+        "from fllm_b200.ops.native import NativeOps\n"
+        "ops = NativeOps(torch.device('cuda:0'))\n"
+        "g = torch.Generator(device='cuda').manual_seed(0)\n"
+        "worst = 0.0\n"
+        "for T, N, K in ((1, 4096, 4096), (33, 4096, 12288), (64, 6144, 4096), (128, 1000, 2048)):\n"
+        "    x = torch.randn(T, K, generator=g, device='cuda').to(torch.bfloat16)\n"
+        "    w = (torch.randn(N, K, generator=g, device='cuda') * 0.05).to(torch.bfloat16)\n"
+        "    b = torch.randn(N, generator=g, device='cuda').to(torch.bfloat16)\n"
+        "    y = ops.linear(x, w, b)\n"
+        "    r = x.float() @ w.float().t() + b.float()\n"
+        "    worst = max(worst, ((y.float() - r).abs().max() / r.abs().max()).item())\n"
+        "    assert ops.launches >= 1\n"
+        "print('WORST', worst, 'STATUS', ops.check_status(), 'LAUNCHES', ops.launches)\n")
+    env = dict(os.environ, FLLM_CLUSTER_SPLITK="1", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = [l for l in out.stdout.splitlines() if l.startswith("WORST")][-1].split()
+    assert float(line[1]) < 1e-2 and int(line[3]) == 0
+    assert int(line[5]) == 4          # one launch per product: no separate reduction kernel ran
