@@ -4,18 +4,28 @@
 // logit soft-capping. This is the always-correct path and the oracle for the
 // tensor-core kernels; its role matches rust/engine/cuda/attention.cu:41-115.
 //
-// KV cache layout: [block][kv_head][block_size][head_dim], bf16.
+// KV cache layout: [block][kv_head][block_size][head_dim], bf16 or e4m3 bytes (fp8 KV cache: values are
+// stored unscaled, e4m3 covers +-448; the reference's counterpart is rust/engine/cuda/kv_quant.cu).
+#include <cuda_fp8.h>
+
 #include "fllm_ops.h"
 #include "ptx.cuh"
 #include "tma_host.h"
 
 namespace fllm {
 
-template <int D>
+__device__ __forceinline__ float kv_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float kv_to_float(uint8_t v) {
+  __nv_fp8_e4m3 f;
+  f.__x = v;
+  return static_cast<float>(f);
+}
+
+template <int D, typename KV>
 __global__ void __launch_bounds__(128)
 attn_generic_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
-                    const __nv_bfloat16* __restrict__ k_cache,
-                    const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_tables,
+                    const KV* __restrict__ k_cache,
+                    const KV* __restrict__ v_cache, const int* __restrict__ block_tables,
                     int max_blocks, const int* __restrict__ row_seq,
                     const int* __restrict__ positions, __nv_bfloat16* __restrict__ out,
                     long long ldo, int hq, int hkv, int block_size, float scale, int window,
@@ -53,12 +63,12 @@ attn_generic_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
       if (j < kv_len) {
         const int blk = table[j / block_size];
         const size_t off = (((size_t)blk * hkv + kvh) * block_size + (j % block_size)) * D + lane * EPL;
-        const __nv_bfloat16* kp = k_cache + off;
-        const __nv_bfloat16* vp = v_cache + off;
+        const KV* kp = k_cache + off;
+        const KV* vp = v_cache + off;
 #pragma unroll
         for (int e = 0; e < EPL; ++e) {
-          s[u] += qv[e] * __bfloat162float(kp[e]);
-          vv[u][e] = __bfloat162float(vp[e]);
+          s[u] += qv[e] * kv_to_float(kp[e]);
+          vv[u][e] = kv_to_float(vp[e]);
         }
       } else {
 #pragma unroll
@@ -118,14 +128,21 @@ void attention_generic_bf16(const void* q, long long ldq, const void* k_cache, c
                             const int* block_tables, int max_blocks, const int* row_seq,
                             const int* positions, void* out, long long ldo, int tokens, int hq,
                             int hkv, int head_dim, int block_size, float scale, int window,
-                            const float* sinks, float softcap, cudaStream_t s) {
+                            const float* sinks, float softcap, cudaStream_t s, int kv_fp8) {
   if (tokens <= 0) return;
   dim3 grid(hq, tokens);
 #define FLLM_ATT(DD)                                                                           \
-  attn_generic_kernel<DD><<<grid, 128, 0, s>>>(                                                \
-      (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
-      block_tables, max_blocks, row_seq, positions, (__nv_bfloat16*)out, ldo, hq, hkv,        \
-      block_size, scale, window, sinks, softcap)
+  do {                                                                                         \
+    if (kv_fp8)                                                                                \
+      attn_generic_kernel<DD, uint8_t><<<grid, 128, 0, s>>>(                                   \
+          (const __nv_bfloat16*)q, ldq, (const uint8_t*)k_cache, (const uint8_t*)v_cache, block_tables, max_blocks, \
+          row_seq, positions, (__nv_bfloat16*)out, ldo, hq, hkv, block_size, scale, window, sinks, softcap); \
+    else                                                                                       \
+      attn_generic_kernel<DD, __nv_bfloat16><<<grid, 128, 0, s>>>(                             \
+          (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_tables, \
+          max_blocks, row_seq, positions, (__nv_bfloat16*)out, ldo, hq, hkv, block_size, scale, window, sinks, \
+          softcap);                                                                            \
+  } while (0)
   switch (head_dim) {
     case 64: FLLM_ATT(64); break;
     case 128: FLLM_ATT(128); break;

@@ -82,7 +82,9 @@ void rope_kv_write(Tensor qkv, const Tensor& positions, const optional<Tensor>& 
                    int64_t hkv, int64_t head_dim, int64_t rot_dim, int64_t rope_style, double eps,
                    double attn_factor) {
   check_bf16(qkv, "qkv"); check_rows(qkv, "qkv"); check_i32(positions, "positions");
-  check_bf16(k_cache, "k_cache"); check_bf16(v_cache, "v_cache");
+  const bool kv_fp8 = k_cache.element_size() == 1;            // e4m3 cache
+  TORCH_CHECK(k_cache.is_cuda() && k_cache.element_size() == v_cache.element_size() &&
+              (kv_fp8 || k_cache.scalar_type() == at::kBFloat16), "caches must be bf16 or 1-byte e4m3 tensors");
   TORCH_CHECK(inv_freq.scalar_type() == at::kFloat && inv_freq.is_cuda(), "inv_freq must be fp32 CUDA");
   TORCH_CHECK(qkv.size(1) == (hq + 2 * hkv) * head_dim, "rope_kv_write: qkv width mismatch");
   TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous(),
@@ -93,7 +95,7 @@ void rope_kv_write(Tensor qkv, const Tensor& positions, const optional<Tensor>& 
       inv_freq.data_ptr<float>(), opt_ptr<void>(q_norm_w), opt_ptr<void>(k_norm_w),
       k_cache.data_ptr(), v_cache.data_ptr(), (int)qkv.size(0), (int)hq, (int)hkv, (int)head_dim,
       (int)k_cache.size(2), (int)rot_dim, (int)rope_style, (float)eps, (float)attn_factor,
-      cur_stream());
+      cur_stream(), kv_fp8 ? 1 : 0);
 }
 
 void glu(const Tensor& x, Tensor out, int64_t act_kind, double alpha, double limit) {
@@ -119,13 +121,17 @@ void attention_generic(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
   check_bf16(q, "q"); check_rows(q, "q"); check_bf16(out, "out"); check_rows(out, "out");
   check_i32(block_tables, "block_tables"); check_i32(row_seq, "row_seq");
   check_i32(positions, "positions");
+  const bool kv_fp8 = k_cache.element_size() == 1;            // e4m3 bytes instead of bf16
+  TORCH_CHECK(k_cache.is_cuda() && k_cache.is_contiguous() && v_cache.is_contiguous() &&
+              k_cache.element_size() == v_cache.element_size() && (kv_fp8 || k_cache.scalar_type() == at::kBFloat16),
+              "caches must be contiguous bf16 or 1-byte e4m3 tensors");
   c10::cuda::CUDAGuard guard(q.device());
   fllm::attention_generic_bf16(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
                                block_tables.data_ptr<int>(), (int)block_tables.size(1),
                                row_seq.data_ptr<int>(), positions.data_ptr<int>(), out.data_ptr(),
                                out.stride(0), (int)q.size(0), (int)hq, (int)hkv, (int)head_dim,
                                (int)k_cache.size(2), (float)scale, (int)window,
-                               opt_ptr<float>(sinks), (float)softcap, cur_stream());
+                               opt_ptr<float>(sinks), (float)softcap, cur_stream(), kv_fp8 ? 1 : 0);
 }
 
 int64_t attention_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,

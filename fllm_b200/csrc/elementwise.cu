@@ -6,6 +6,8 @@
 // :470-530 (rope_kv_f16_kernel), rust/engine/cuda/fused.cu:68 (add_rms_norm_kernel),
 // rust/engine/cuda/act_narrow.cu (bf16 activation pipeline). There the activation
 // dtype is a run-time switch; here bf16 is the only activation dtype.
+#include <cuda_fp8.h>
+
 #include "fllm_ops.h"
 #include "ptx.cuh"
 #include "tma_host.h"
@@ -156,7 +158,7 @@ rope_kv_kernel(__nv_bfloat16* __restrict__ qkv, long long ld_qkv, const int* __r
                const __nv_bfloat16* __restrict__ q_norm_w, const __nv_bfloat16* __restrict__ k_norm_w,
                __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int tokens,
                int hq, int hkv, int block_size, int rot_dim, int rope_style, float eps,
-               float attn_factor) {
+               float attn_factor, int kv_fp8) {
   constexpr int EPL = D / 32;  // elements per lane
   pdl_launch_dependents();
   pdl_wait();
@@ -174,6 +176,14 @@ rope_kv_kernel(__nv_bfloat16* __restrict__ qkv, long long ld_qkv, const int* __r
     const int kvh = h - hq - hkv;
     const int blk = slot / block_size, off = slot - blk * block_size;
     __nv_bfloat16* dst = v_cache + (((size_t)blk * hkv + kvh) * block_size + off) * D;
+    if (kv_fp8) {                  // e4m3 cache: one byte per value, same [block][head][slot][dim] order
+      uint8_t* d8 = reinterpret_cast<uint8_t*>(v_cache) + (((size_t)blk * hkv + kvh) * block_size + off) * D;
+      for (int i = lane; i < D / 2; i += 32) {
+        const float2 f = unpack_bf16x2(reinterpret_cast<const uint32_t*>(src)[i]);
+        reinterpret_cast<uint16_t*>(d8)[i] = (uint16_t)__nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
+      }
+      return;
+    }
     if (EPL == 4) {
       reinterpret_cast<uint2*>(dst)[lane] = reinterpret_cast<const uint2*>(src)[lane];
     } else {
@@ -279,6 +289,19 @@ rope_kv_kernel(__nv_bfloat16* __restrict__ qkv, long long ld_qkv, const int* __r
     const int kvh = h - hq;
     const int blk = slot / block_size, off = slot - blk * block_size;
     dst = k_cache + (((size_t)blk * hkv + kvh) * block_size + off) * D;
+    if (kv_fp8) {
+      uint8_t* d8 = reinterpret_cast<uint8_t*>(k_cache) + (((size_t)blk * hkv + kvh) * block_size + off) * D;
+      if (rope_style == 0) {
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) d8[lane + 32 * j] = (uint8_t)__nv_cvt_float_to_fp8(v[j], __NV_SATFINITE, __NV_E4M3);
+      } else {
+#pragma unroll
+        for (int j = 0; j < EPL; j += 2)
+          reinterpret_cast<uint16_t*>(d8)[lane + 32 * (j / 2)] =
+              (uint16_t)__nv_cvt_float2_to_fp8x2(make_float2(v[j], v[j + 1]), __NV_SATFINITE, __NV_E4M3);
+      }
+      return;
+    }
   }
   if (rope_style == 0) {
 #pragma unroll
@@ -294,7 +317,7 @@ void rope_qknorm_kvwrite_bf16(void* qkv, long long ld_qkv, const int* positions,
                               const float* inv_freq, const void* q_norm_w, const void* k_norm_w,
                               void* k_cache, void* v_cache, int tokens, int hq, int hkv,
                               int head_dim, int block_size, int rot_dim, int rope_style, float eps,
-                              float attn_factor, cudaStream_t s) {
+                              float attn_factor, cudaStream_t s, int kv_fp8) {
   if (tokens <= 0) return;
   const long long warps = (long long)tokens * (hq + 2 * hkv);
   const int blocks = (int)((warps + 3) / 4);
@@ -305,7 +328,7 @@ void rope_qknorm_kvwrite_bf16(void* qkv, long long ld_qkv, const int* positions,
   auto* vc = (__nv_bfloat16*)v_cache;
 #define FLLM_ROPE(DD)                                                                            \
   launch_pdl(rope_kv_kernel<DD>, dim3(blocks), dim3(128), 0, s, x, ld_qkv, positions, slots, inv_freq, qn, kn, kc, \
-             vc, tokens, hq, hkv, block_size, rot_dim, rope_style, eps, attn_factor)
+             vc, tokens, hq, hkv, block_size, rot_dim, rope_style, eps, attn_factor, kv_fp8)
   switch (head_dim) {
     case 64: FLLM_ROPE(64); break;
     case 128: FLLM_ROPE(128); break;

@@ -130,7 +130,7 @@ void rope_qknorm_kvwrite_bf16(void* qkv, long long ld_qkv, const int* positions,
                               const float* inv_freq, const void* q_norm_w, const void* k_norm_w,
                               void* k_cache, void* v_cache, int tokens, int hq, int hkv,
                               int head_dim, int block_size, int rot_dim, int rope_style, float eps,
-                              float attn_factor, cudaStream_t s);
+                              float attn_factor, cudaStream_t s, int kv_fp8 = 0);   // kv_fp8: caches hold e4m3 bytes
 void glu_bf16(const void* x, long long ldx, void* out, long long ldo, int rows, int inter,
               int act_kind, float alpha, float limit, cudaStream_t s);
 void gather_rows_bf16(const void* x, long long ldx, const int* rows, void* out, int n_rows,
@@ -141,7 +141,7 @@ void attention_generic_bf16(const void* q, long long ldq, const void* k_cache, c
                             const int* block_tables, int max_blocks, const int* row_seq,
                             const int* positions, void* out, long long ldo, int tokens, int hq,
                             int hkv, int head_dim, int block_size, float scale, int window,
-                            const float* sinks, float softcap, cudaStream_t s);
+                            const float* sinks, float softcap, cudaStream_t s, int kv_fp8 = 0);
 
 // Tensor-core paged attention over a ragged batch described per sequence (q_starts, kv_lens).
 // Returns the number of kernels launched.

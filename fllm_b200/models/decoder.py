@@ -48,6 +48,8 @@ class KVCache:
 
     def __init__(self, num_layers: int, num_blocks: int, kv_heads: int, block_size: int, head_dim: int,
                  device, dtype=torch.bfloat16):
+        """dtype torch.float8_e4m3fn halves the pool (values stored unscaled; written by the rope kernel,
+        read by the generic attention kernel)."""
         self.num_blocks, self.block_size = num_blocks, block_size
         self.store = torch.zeros(num_layers, 2, num_blocks, kv_heads, block_size, head_dim,
                                  device=device, dtype=dtype)

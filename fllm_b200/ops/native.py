@@ -80,7 +80,8 @@ class NativeOps:
                   scale, window=0, sinks=None, softcap=0.0, meta=None):
         out = torch.empty(q.shape[0], hq * head_dim, dtype=q.dtype, device=q.device)
         if (self.use_tc_attention and meta is not None and meta.q_starts is not None
-                and head_dim in (64, 128) and hq // hkv <= 16):
+                and head_dim in (64, 128) and hq // hkv <= 16 and k_cache.element_size() == 2):
+            # (an fp8 KV cache is read by the generic kernel: the tensor-core kernels load bf16 tiles)
             if self.attn_ws is None:
                 self.attn_ws = torch.empty(64 << 20, dtype=torch.uint8, device=self.device)
             self.launches += self.k.attention_tc(

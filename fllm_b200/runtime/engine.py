@@ -72,8 +72,11 @@ class LLMEngine:
         self.block_size = self.cfg.block_size
         self.max_blocks_per_seq = -(-self.cfg.max_model_len // self.block_size)
         num_blocks = self.cfg.num_kv_blocks or self._size_kv_pool()
+        if self.cfg.kv_cache_dtype not in ("bf16", "fp8", "fp8_e4m3"):
+            raise ValueError("kv_cache_dtype must be bf16 or fp8_e4m3")
+        kv_dtype = torch.bfloat16 if self.cfg.kv_cache_dtype == "bf16" else torch.float8_e4m3fn
         self.kv = KVCache(len(self.layer_range), num_blocks, self.spec.hkv_local, self.block_size,
-                          model_cfg.head_dim, self.device)
+                          model_cfg.head_dim, self.device, kv_dtype)
         self.decoder = Decoder(model_cfg, self.weights, self.kv, self.ops, self.spec, tp_group,
                                layer_range=self.layer_range, first_stage=self.first_stage,
                                last_stage=self.last_stage)
@@ -123,7 +126,8 @@ class LLMEngine:
     # ------------------------------------------------------------------ sizing
     def _size_kv_pool(self) -> int:
         per_block = KVCache.bytes_per_block(len(self.layer_range), self.spec.hkv_local,
-                                            self.block_size, self.model_cfg.head_dim)
+                                            self.block_size, self.model_cfg.head_dim,
+                                            2 if self.cfg.kv_cache_dtype == "bf16" else 1)
         if self.is_cuda:
             free, total = torch.cuda.mem_get_info(self.device)
             budget = int(total * self.cfg.gpu_memory_utilization) - (total - free)

@@ -128,3 +128,30 @@ def test_speculative_ngram_and_draft_model_keep_greedy_output():
     for _ in range(40):
         a.update(4, 4)
     assert a.length() == 6
+
+
+def test_fp8_kv_cache_stays_close_to_bf16_kv():
+    """An e4m3 KV pool (half the bytes) must reproduce the bf16-KV logits within fp8 precision."""
+    import torch
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    cfg = preset("qwen3-tiny")
+    outs = []
+    for kvd in ("bf16", "fp8_e4m3"):
+        ec = EngineConfig(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128, num_kv_blocks=32, kv_cache_dtype=kvd)
+        eng = LLMEngine(cfg, ec, device="cpu", seed=1)
+        assert eng.kv.store.element_size() == (2 if kvd == "bf16" else 1)
+        g = torch.Generator().manual_seed(0)
+        p = torch.randint(0, cfg.vocab_size, (70,), generator=g).tolist()
+        eng.add_request(p, SamplingParams(max_tokens=1))
+        rows = []
+        while eng.has_unfinished():
+            step = eng.scheduler.schedule()
+            batch = eng._build_batch(step)
+            logits = eng.decoder.forward(batch)
+            if logits.shape[0]:
+                rows.append(logits[-1].float())
+            eng._commit(step, eng.decoder.greedy_tokens(logits).tolist())
+        outs.append(rows[-1])
+    err = (outs[0] - outs[1]).abs().max().item() / (outs[0].abs().max().item() + 1e-6)
+    assert 0 < err < 0.08, err

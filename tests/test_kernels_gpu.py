@@ -501,3 +501,29 @@ def test_cluster_splitk_reduction_opt_in():
     line = [l for l in out.stdout.splitlines() if l.startswith("WORST")][-1].split()
     assert float(line[1]) < 1e-2 and int(line[3]) == 0
     assert int(line[5]) == 4          # one launch per product: no separate reduction kernel ran
+
+
+@pytest.mark.parametrize("style", [0, 1])
+def test_fp8_kv_write_and_generic_attention_read(ops, ref, style):
+    """e4m3 KV cache: the rope kernel's stores equal PyTorch's float8 rounding of the same values, and
+    the generic attention kernel on that cache equals the fp32 oracle reading the same bytes."""
+    T, hq, hkv, D, bs, nb = 40, 8, 2, 128, 16, 8
+    qkv = _rand((T, (hq + 2 * hkv) * D), 1)
+    pos = torch.arange(T, device="cuda", dtype=torch.int32)
+    slots = torch.arange(T, device="cuda", dtype=torch.int32)
+    inv = (10000.0 ** (-torch.arange(0, D, 2, device="cuda").float() / D))
+    kc = torch.zeros(nb, hkv, bs, D, dtype=torch.float8_e4m3fn, device="cuda")
+    vc = torch.zeros_like(kc)
+    kc_r, vc_r, qkv_r = kc.clone(), vc.clone(), qkv.clone()
+    ops.rope_kv_write(qkv, pos, slots, inv, None, None, kc, vc, hq, hkv, D, D, style, 1e-6, 1.0)
+    ref.rope_kv_write(qkv_r, pos, slots, inv, None, None, kc_r, vc_r, hq, hkv, D, D, style, 1e-6, 1.0)
+    assert torch.equal(vc.view(torch.uint8), vc_r.view(torch.uint8))
+    # keys pass through sin/cos in fp32 on both sides: allow one e4m3 step on a few elements
+    dk = (kc.float() - kc_r.float()).abs()
+    assert (dk > 0).float().mean().item() < 0.02 and dk.max().item() <= 0.13 * kc_r.float().abs().max().item()
+    tables = torch.arange(nb, device="cuda", dtype=torch.int32).view(1, nb)
+    row_seq = torch.zeros(T, device="cuda", dtype=torch.int32)
+    q = qkv[:, : hq * D].contiguous()
+    got = ops.attention(q, kc, vc, tables, row_seq, pos, hq, hkv, D, D ** -0.5)
+    want = ref.attention(q, kc, vc, tables, row_seq, pos, hq, hkv, D, D ** -0.5)
+    _close(got, want, 2e-2)
