@@ -42,6 +42,9 @@ class ClockSampler(threading.Thread):
         self.index, self.period = index, period
         self.samples, self.reasons, self.max_mhz = [], set(), 0
         self._halt = threading.Event()
+        if os.environ.get("FLLM_BENCH_SAMPLER", "thread") == "off":
+            self.nv = None
+            return
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -207,6 +210,16 @@ def main() -> None:
         dev_ms = None
 
     # ---- end to end: K engine steps through the public API
+    import gc
+    eng.settle_host()
+    gc_events = []
+
+    def _gc_cb(phase, info, _t=[0.0]):
+        if phase == "start":
+            _t[0] = time.perf_counter()
+        else:
+            gc_events.append([info.get("generation"), round((time.perf_counter() - _t[0]) * 1e3, 2)])
+    gc.callbacks.append(_gc_cb)
     h2d0, d2h0 = eng.stats.h2d_bytes, eng.stats.d2h_bytes
     l0 = eng.stats.kernel_launches
     sync_all()
@@ -220,6 +233,7 @@ def main() -> None:
     eng.drain()                 # the last launched step's ids are read inside the timed region
     e1.record()
     sync_all()
+    gc.callbacks.remove(_gc_cb)
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     e2e_dev_ms = max_over_ranks(e0.elapsed_time(e1))
     clocks = sampler.stop()
@@ -252,7 +266,8 @@ def main() -> None:
                     "d2h_bytes_per_step": (eng.stats.d2h_bytes - d2h0) // args.steps,
                     "ms_per_step": round(e2e_s * 1e3 / args.steps, 4),
                     "step_ms_p50": round(statistics.median(step_ms), 4), "step_ms_max": round(max(step_ms), 4),
-                    "slowest_steps": sorted(((round(v, 2), i) for i, v in enumerate(step_ms)), reverse=True)[:4]},
+                    "slowest_steps": sorted(((round(v, 2), i) for i, v in enumerate(step_ms)), reverse=True)[:4],
+                    "gc_pauses_ms": sorted(gc_events, key=lambda e: -e[1])[:4]},
             "gpu_launches": (launches_per_step or 0) * args.steps + (eng.stats.kernel_launches - l0),
             "prefill_tok_s": round(prefill_tok_s, 1), "ttft_s_first": round(ttft or 0.0, 4),
             "itl_p50_ms": round(statistics.median(itl) * 1e3, 4) if itl else None,

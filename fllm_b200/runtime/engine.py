@@ -615,6 +615,16 @@ class LLMEngine:
         for b in buckets or self.cfg.graph_buckets:
             if b <= self.cfg.max_num_seqs and b not in self._graphs:
                 self._graphs[b] = _DecodeGraph(self, b)
+        self.settle_host()
+
+    @staticmethod
+    def settle_host() -> None:
+        """Move everything allocated so far (weights, graphs, modules) out of the garbage collector's
+        young generations. A full collection over a loaded engine walks millions of objects and showed
+        up as 40 - 60 ms stalls of single decode steps at deterministic step numbers."""
+        import gc
+        gc.collect()
+        gc.freeze()
 
 
 class _DecodeGraph:
