@@ -128,7 +128,11 @@ def main() -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     cfg = preset(args.model)
-    out_len = args.warmup + args.steps + 8
+    # Prompts are prefilled 2048 tokens per step while the sequences that are already through decode
+    # along (decode-first scheduling), so the first sequences are `stagger` tokens ahead of the last when
+    # the timed region starts: leave room for that, or they would reach the length limit inside it.
+    stagger = -(-args.batch * args.prompt_len // 2048) + 2
+    out_len = args.warmup + 2 * args.steps + 8 + stagger
     ec = EngineConfig(max_num_seqs=args.batch, max_num_batched_tokens=2048, block_size=16,
                       max_model_len=args.prompt_len + out_len + 16, enable_prefix_caching=False,
                       use_cuda_graphs=not args.no_graphs)
@@ -234,6 +238,7 @@ def main() -> None:
     e1.record()
     sync_all()
     gc.callbacks.remove(_gc_cb)
+    assert len(eng.scheduler.running) == args.batch, "batch shrank inside the timed region"
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     e2e_dev_ms = max_over_ranks(e0.elapsed_time(e1))
     clocks = sampler.stop()

@@ -162,6 +162,13 @@ class FusedTP:
         return self.group.all_reduce(x)
 
     def all_gather(self, x: torch.Tensor) -> torch.Tensor:
+        """Small messages (the (value, id) pairs of a vocabulary-parallel argmax) go through the
+        one-shot peer kernel; anything else through the library."""
+        nbytes = x.numel() * x.element_size()
+        if x.is_contiguous() and nbytes and nbytes % 16 == 0 and nbytes <= self.ar_slot_bytes:
+            out = torch.empty((self.size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+            self.k.tp_allgather(self.ctx, x, out)
+            return out
         return self.group.all_gather(x)
 
     def check_status(self) -> int:

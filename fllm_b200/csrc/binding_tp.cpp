@@ -175,6 +175,20 @@ void tp_allreduce(int64_t h, const Tensor& input, Tensor output) {
   fllm::tp_allreduce(a, cur_stream());
 }
 
+// output [tp, ...input shape]: every rank's `input`, through the same peer slots and flags.
+void tp_allgather(int64_t h, const Tensor& input, Tensor output) {
+  TpContext& c = ctx_at(h);
+  TORCH_CHECK(input.is_contiguous() && output.is_contiguous() && output.nbytes() == input.nbytes() * (size_t)c.tp, "tp_allgather: shapes");
+  c10::cuda::CUDAGuard guard(input.device());
+  fllm::TpAllReduceArgs a{};
+  a.input = input.data_ptr(); a.output = output.data_ptr(); a.bytes = input.nbytes(); a.slot_bytes = c.ar_slot_bytes;
+  a.is_fp32 = 1; a.gather = 1; a.tp = c.tp; a.my_rank = c.rank;
+  for (int i = 0; i < c.tp; ++i) { a.slots[i] = c.ar_slots[i]; a.flags[i] = c.flags[i] + kArFlags; }
+  uint32_t* f = c.flags[c.rank];
+  a.my_flags = f + kArFlags; a.consumed = f + kArConsumed; a.cta_done = f + kArDone; a.status = c.status;
+  fllm::tp_allreduce(a, cur_stream());
+}
+
 int64_t linear_rs_expected(int64_t tokens, int64_t n, int64_t rows_per, int64_t dest) {
   return fllm::linear_rs_expected_signals((int)tokens, (int)n, (int)rows_per, (int)dest);
 }
@@ -194,5 +208,6 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("tp_linear_ag(int ctx, int tokens, Tensor w, Tensor? bias, Tensor(a!) y, Tensor? workspace) -> int", &tp_linear_ag);
   m.def("tp_norm(int ctx, Tensor(a!) residual_shard, int tokens, int expected, Tensor norm_w, float eps, float w_offset, bool bcast) -> ()", &tp_norm);
   m.def("tp_allreduce(int ctx, Tensor input, Tensor(a!) output) -> ()", &tp_allreduce);
+  m.def("tp_allgather(int ctx, Tensor input, Tensor(a!) output) -> ()", &tp_allgather);
   m.def("linear_rs_expected(int tokens, int n, int rows_per, int dest) -> int", &linear_rs_expected);
 }

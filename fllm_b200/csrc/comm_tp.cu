@@ -9,7 +9,9 @@
 //       on those counters, so reduce-scatter -> norm -> all-gather costs one small kernel and no
 //       library collective.
 //   tp_allreduce_kernel        one-shot all-reduce for small messages: every rank pushes its
-//       vector into all peers' slots, then sums the slots in rank order (bounded wait).
+//       vector into all peers' slots, then sums the slots in rank order (bounded wait). In gather
+//       mode the slots are copied out instead of summed: the vocabulary-parallel head exchanges its
+//       per-rank (value, token id) pairs this way, so no logits and no library call are involved.
 //
 // The reference reduces after o_proj / down_proj with one all-reduce each
 // (rust/engine/src/rust_decoder.rs:5396, :5700) and its own one-shot kernel spins without a
@@ -214,7 +216,14 @@ __global__ void __launch_bounds__(256) tp_allreduce_kernel(const TpAllReduceArgs
     }
   }
   __syncthreads();
-  if (!failed) {
+  if (!failed && a.gather) {
+    // all-gather: output [tp][bytes] = the slots in rank order (vocab-parallel argmax pairs, small lists)
+    const uint8_t* mine = reinterpret_cast<const uint8_t*>(a.slots[a.my_rank]);
+    for (int s = 0; s < a.tp; ++s)
+      for (size_t i = tid; i < n16; i += stride)
+        reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.output) + (size_t)s * a.bytes)[i] =
+            ld_cg_u4(reinterpret_cast<const uint4*>(mine + (size_t)s * a.slot_bytes) + i);
+  } else if (!failed) {
     const uint8_t* mine = reinterpret_cast<const uint8_t*>(a.slots[a.my_rank]);
     for (size_t i = tid; i < n16; i += stride) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};

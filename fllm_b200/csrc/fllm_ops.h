@@ -61,6 +61,7 @@ struct TpAllReduceArgs {
   size_t bytes;              // multiple of 16, at most slot_bytes
   size_t slot_bytes;
   int is_fp32;               // else bf16
+  int gather;                // 1: output [tp][bytes] = every rank's vector (no sum)
   void* slots[8];            // every rank's slot buffer [tp][slot_bytes]
   uint32_t* flags[8];        // every rank's arrival counters [tp]
   const uint32_t* my_flags;  // == flags[my_rank]
