@@ -3,7 +3,7 @@
 Each case launches ONE kernel family a handful of times on inputs larger than L2 but far below a
 GB-scale footprint, so a multi-pass capture (``ncu --set full -k regex:<kernel> -c 1``) finishes
 in seconds. Cases: gemm_decode (64 tokens x gate_up of an 8B model), gemm_prefill (2048 tokens),
-attn_decode (64 sequences at 1152 context), attn_prefill, fp8_prefill, gemm_fp4_decode (64 tokens x NVFP4 gate_up).
+attn_decode (64 sequences at 1152 context), attn_prefill, fp8_prefill, gemm_fp4_decode (64 tokens x NVFP4 gate_up), tp_rs_gemm / tp_norm / tp_ag_gemm (fused tensor-parallel kernels, two virtual ranks).
 """
 from __future__ import annotations
 
@@ -33,6 +33,26 @@ def main(argv=None) -> None:
         q = Fp4Weight(codes, scales, 0, 0.01)
         y = torch.empty(64, 24576, **bf)
         fn = lambda: ops.linear(x, q, out=y)
+    elif case in ("tp_rs_gemm", "tp_norm", "tp_ag_gemm"):
+        # the fused tensor-parallel kernels with two virtual ranks on this one device (plain pointers instead
+        # of IPC mappings; the ranks' kernels run phase by phase): 2048 tokens, o_proj shard -> norm -> gate_up shard
+        from .comm.symm import FusedTP
+        T, H, I = 2048, 4096, 12288
+        ranks = FusedTP.local_group(2, H, T)
+        a = [torch.randn(T, H // 2, **bf) for _ in range(2)]
+        wo = [torch.randn(H, H // 2, **bf) * 0.02 for _ in range(2)]
+        wgu = torch.randn(I, H, **bf) * 0.02
+        nw = torch.ones(H, **bf)
+        res = [torch.zeros(T // 2, H, **bf) for _ in range(2)]
+
+        def fn():
+            for r in range(2):
+                ranks[r].linear_rs(a[r], wo[r], None, False)
+            for r in range(2):
+                ranks[r]._rs_expected = ranks[0]._rs_expected
+                ranks[r].norm(res[r], T, True, nw, 1e-6, 0.0, False)
+            for r in range(2):
+                ranks[r].linear_ag(T, wgu)
     elif case == "fp8_prefill":
         x = torch.randn(2048, 4096, **bf)
         wq, sw = quantize_weight_fp8_block(torch.randn(8192, 4096, **bf) * 0.02)
