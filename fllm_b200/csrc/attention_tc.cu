@@ -549,6 +549,11 @@ static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int mi
     int splits = 1;
     // a grid of at least one CTA per SM streams KV well enough; splitting costs a merge launch
     if (ctas < sm_count()) splits = min(min((2 * sm_count() + ctas - 1) / ctas, (pages + 7) / 8), 32);
+    {
+      static int forced = -1;
+      if (forced < 0) { const char* e = getenv("FLLM_ATTN_SPLITS"); forced = e ? atoi(e) : 0; }
+      if (forced > 0) splits = min(forced, max(pages / 2, 1));
+    }
     splits = max(splits, 1);
     // partials of prefill sequences do not exist, so a mixed batch is never split
     if (max_q_len > decode_max_q || !workspace) splits = 1;

@@ -25,10 +25,11 @@ def _cut_rows(t: torch.Tensor, start: int, n: int) -> torch.Tensor:
     return t[start:start + n]
 
 
-def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16):
+def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16,
+                       expert_parallel: bool = False):
     from .safetensors_io import open_checkpoint
     cfg = ModelConfig.from_hf_config(json.load(open(os.path.join(directory, "config.json"))))
-    sp = make_shard_spec(cfg, tp, tp_rank)
+    sp = make_shard_spec(cfg, tp, tp_rank, expert_parallel)
     ck = open_checkpoint(directory)
     D = cfg.head_dim
 
@@ -54,8 +55,16 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
         lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
                           ffn_norm=dev(get(p + "post_attention_layernorm.weight")))
         o = get(p + "self_attn.o_proj.weight")
-        g, u, d = (get(p + f"mlp.{n}_proj.weight") for n in ("gate", "up", "down"))
-        if fp8:
+        if cfg.is_moe:
+            _load_moe_layer(cfg, sp, tp_rank, lw, p, get, dev)
+            lw.wqkv = dev(torch.cat([q[qs], k[ks], v[ks]], 0))
+            lw.wo = dev(o[:, qs])
+            g = u = d = None
+        else:
+            g, u, d = (get(p + f"mlp.{n}_proj.weight") for n in ("gate", "up", "down"))
+        if cfg.is_moe:
+            pass
+        elif fp8:
             def sc(name):
                 return get(p + name + ".weight_scale_inv").float()
             def rows(t, s, sl):            # cut rows of codes and of their 128-row scale blocks
@@ -86,6 +95,10 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
                 lw.bo = dev(bo if tp_rank == 0 else torch.zeros_like(bo))
         if cfg.qk_norm:
             lw.q_norm, lw.k_norm = dev(get(p + "self_attn.q_norm.weight")), dev(get(p + "self_attn.k_norm.weight"))
+        if cfg.attn_sinks:
+            sk = get(p + "self_attn.sinks", False)
+            if sk is not None:
+                lw.sinks = sk[sp.q_head_start: sp.q_head_start + sp.hq_local].float().to(device).contiguous()
         layers.append(lw)
     embed = get("model.embed_tokens.weight")
     head = get("lm_head.weight", False)
@@ -103,6 +116,44 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
                        vocab_start=v0, vocab_local=vl)
     tok = directory if os.path.exists(os.path.join(directory, "tokenizer.json")) else None
     return cfg, w, tok
+
+
+def _mxfp4_stack(blocks: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """gpt-oss expert tensor: blocks uint8 [E, rows, K/32, 16] (two e2m1 per byte, low nibble first) and
+    scales uint8 [E, rows, K/32] (e8m0) -> fp32 [E, rows, K]."""
+    from ..ops.fp4 import MXFP4, dequantize_fp4
+    E, R, G, _ = blocks.shape
+    d = dequantize_fp4(blocks.reshape(E * R, G * 16), scales.reshape(E * R, G), MXFP4)
+    return d.view(E, R, G * 32)
+
+
+def _load_moe_layer(cfg, sp, tp_rank, lw, p, get, dev) -> None:
+    """Router and experts of a gpt-oss style layer (`mlp.router`, `mlp.experts.{gate_up,down}_proj`): bf16
+    tensors are taken as they are ([E, in, out] in the checkpoint), MXFP4 `_blocks` / `_scales` pairs
+    ([E, out, in/32, 16]) are expanded to bf16. The grouped expert GEMM runs bf16 stacks."""
+    from ..models.weights import _cut_gate_up
+    lw.router_w = dev(get(p + "mlp.router.weight"))
+    rb = get(p + "mlp.router.bias", False)
+    lw.router_b = dev(rb) if rb is not None else None
+
+    def expert(name):
+        blk = get(p + f"mlp.experts.{name}_blocks", False)
+        if blk is not None:
+            return _mxfp4_stack(blk, get(p + f"mlp.experts.{name}_scales"))          # [E, out, in]
+        return get(p + f"mlp.experts.{name}").float().transpose(1, 2)                # stored [E, in, out]
+    gu, dn = expert("gate_up_proj"), expert("down_proj")
+    gub, dnb = get(p + "mlp.experts.gate_up_proj_bias", False), get(p + "mlp.experts.down_proj_bias", False)
+    if sp.expert_parallel:
+        es = slice(sp.expert_start, sp.expert_start + sp.expert_local)
+        lw.exp_gate_up, lw.exp_down = dev(gu[es]), dev(dn[es])
+        lw.exp_gate_up_b = dev(gub[es]) if gub is not None else None
+        lw.exp_down_b = dev(dnb[es]) if dnb is not None else None
+    else:
+        lw.exp_gate_up = dev(_cut_gate_up(gu, cfg, sp, dim=1))
+        lw.exp_down = dev(dn[:, :, sp.inter_start: sp.inter_start + sp.inter_local])
+        lw.exp_gate_up_b = dev(_cut_gate_up(gub, cfg, sp, dim=1)) if gub is not None else None
+        if dnb is not None:
+            lw.exp_down_b = dev(dnb if tp_rank == 0 else torch.zeros_like(dnb))
 
 
 def load_gguf(path: str, device="cuda", tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16, keep_packed: bool = True):

@@ -184,3 +184,62 @@ def test_gguf_loader_feeds_the_torch_engine(tmp_path):
     b = c.generate(prompt, 6)
     c.close()
     assert sum(x == y for x, y in zip(a, b)) >= 4       # int8-activation dots vs bf16 math: near ties may flip
+
+
+def test_gpt_oss_checkpoint_with_mxfp4_experts_loads(tmp_path):
+    """A synthetic gpt-oss style HF checkpoint (router, sinks, biases, experts as MXFP4 `_blocks` /
+    `_scales`) loads into the decoder layout: dense tensors bit-equal, experts equal to the MXFP4
+    de-quantisation of what was written, and the model runs."""
+    import json
+    import torch
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    from fllm_b200.formats.safetensors_io import save_file
+    from fllm_b200.models.weights import init_random_weights
+    from fllm_b200.ops.fp4 import MXFP4, dequantize_fp4, quantize_mxfp4
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    cfg = preset("gpt-oss-tiny")
+    w = init_random_weights(cfg, device="cpu", seed=4)
+    D, hq, hkv, H, I, E = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads, cfg.hidden_size, cfg.moe_intermediate_size, cfg.num_experts
+    t = {"model.embed_tokens.weight": w.embed, "model.norm.weight": w.final_norm, "lm_head.weight": w.lm_head}
+    want_gu = []
+    for l, lw in enumerate(w.layers):
+        p = f"model.layers.{l}."
+        q, k, v = lw.wqkv[: hq * D], lw.wqkv[hq * D: (hq + hkv) * D], lw.wqkv[(hq + hkv) * D:]
+        bq, bk, bv = lw.bqkv[: hq * D], lw.bqkv[hq * D: (hq + hkv) * D], lw.bqkv[(hq + hkv) * D:]
+        t.update({p + "input_layernorm.weight": lw.attn_norm, p + "post_attention_layernorm.weight": lw.ffn_norm,
+                  p + "self_attn.q_proj.weight": q, p + "self_attn.k_proj.weight": k, p + "self_attn.v_proj.weight": v,
+                  p + "self_attn.q_proj.bias": bq, p + "self_attn.k_proj.bias": bk, p + "self_attn.v_proj.bias": bv,
+                  p + "self_attn.o_proj.weight": lw.wo, p + "self_attn.o_proj.bias": lw.bo,
+                  p + "self_attn.sinks": lw.sinks.to(torch.bfloat16),
+                  p + "mlp.router.weight": lw.router_w, p + "mlp.router.bias": lw.router_b,
+                  p + "mlp.experts.gate_up_proj_bias": lw.exp_gate_up_b, p + "mlp.experts.down_proj_bias": lw.exp_down_b})
+        for name, stack in (("gate_up_proj", lw.exp_gate_up), ("down_proj", lw.exp_down)):
+            Ee, R, K = stack.shape
+            codes, scales, _ = quantize_mxfp4(stack.reshape(Ee * R, K).float())
+            t[p + f"mlp.experts.{name}_blocks"] = codes.view(Ee, R, K // 32, 16)
+            t[p + f"mlp.experts.{name}_scales"] = scales.view(Ee, R, K // 32)
+            if name == "gate_up_proj":
+                want_gu.append(dequantize_fp4(codes, scales, MXFP4).view(Ee, R, K).to(torch.bfloat16))
+    save_file({k: v.contiguous() for k, v in t.items()}, str(tmp_path / "model.safetensors"))
+    hf = {"model_type": "gpt_oss", "vocab_size": cfg.vocab_size, "hidden_size": H, "num_hidden_layers": cfg.num_layers,
+          "num_attention_heads": hq, "num_key_value_heads": hkv, "head_dim": D, "intermediate_size": I,
+          "rms_norm_eps": cfg.rms_eps, "rope_theta": cfg.rope_theta, "max_position_embeddings": cfg.max_position,
+          "num_local_experts": E, "num_experts_per_tok": cfg.experts_per_token, "sliding_window": 128,
+          "layer_types": ["sliding_attention", "full_attention"], "attention_bias": True,
+          "rope_scaling": {"rope_type": "yarn", "factor": 32.0, "beta_fast": 32.0, "beta_slow": 1.0,
+                           "original_max_position_embeddings": 4096}}
+    json.dump(hf, open(tmp_path / "config.json", "w"))
+    cfg2, w2, _ = load_hf_checkpoint(str(tmp_path), device="cpu")
+    assert cfg2.is_moe and cfg2.num_experts == E and cfg2.act == "swiglu_oai"
+    for l in range(cfg.num_layers):
+        a, b = w.layers[l], w2.layers[l]
+        assert torch.equal(a.wqkv, b.wqkv) and torch.equal(a.wo, b.wo) and torch.equal(a.bqkv, b.bqkv)
+        assert torch.equal(a.router_w, b.router_w) and torch.equal(a.exp_down_b, b.exp_down_b)
+        assert torch.allclose(a.sinks, b.sinks, atol=1e-2)
+        assert torch.equal(b.exp_gate_up, want_gu[l])
+        assert ((b.exp_down.float() - a.exp_down.float()).norm() / a.exp_down.float().norm()).item() < 0.2
+    eng = LLMEngine(cfg2, EngineConfig(max_num_seqs=2, max_num_batched_tokens=32, max_model_len=64, num_kv_blocks=16),
+                    device="cpu", weights=w2)
+    out = eng.generate([[5, 6, 7, 8, 9]], SamplingParams(max_tokens=4))
+    assert len(out[0]) == 4
