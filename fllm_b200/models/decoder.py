@@ -90,6 +90,7 @@ class Decoder:
                 elif packed[0] in ("nvfp4", "mxfp4"):
                     from ..ops.fp4 import FMT_NAMES, Fp4Weight
                     setattr(lw, name, Fp4Weight(packed[1], packed[2], FMT_NAMES[packed[0]], packed[3] if len(packed) > 3 else 1.0))
+        self.capture_hidden, self.last_hidden = False, None
         self.ep_a2a = None            # comm.ep_a2a.EpAllToAll when expert parallelism dispatches rows all-to-all
         self._reduced = False
         self._dense_weights = all(isinstance(getattr(lw, n, None), torch.Tensor) for lw in self.w.layers
@@ -225,6 +226,8 @@ class Decoder:
             hs = h                     # every row is a decode row: no gather needed
         else:
             hs = ops.gather_rows(h, b.logit_rows)
+        if self.capture_hidden:
+            self.last_hidden = hs                  # [logit rows, hidden]: the embeddings API reads it
         lg = ops.linear(hs, self.w.lm_head)
         if cfg.logit_softcap > 0:
             lg = (cfg.logit_softcap * torch.tanh(lg.float() / cfg.logit_softcap)).to(lg.dtype)

@@ -451,9 +451,23 @@ class LLMEngine:
         elif self.par.pp > 1:
             tokens_dev = self._pipeline_forward(step)
         else:
+            want_hidden = any(s.wants_logits and s.req.params.embed for s in step.seqs)
+            if want_hidden and self.decoder.fused_tp:
+                raise RuntimeError("embeddings are not available on the fused tensor-parallel path")
+            self.decoder.capture_hidden = want_hidden
             batch = self._build_batch(step)
             logits = self.decoder.forward(batch)
             tokens_dev = self.decoder.greedy_tokens(logits)
+            if want_hidden:
+                self.decoder.capture_hidden = False
+                hid = self.decoder.last_hidden.float().cpu()
+                row = 0
+                for s in step.seqs:
+                    if not s.wants_logits:
+                        continue
+                    if s.req.params.embed:
+                        s.req.embedding = hid[row].tolist()
+                    row += s.count if s.verify else 1
         self.stats.forward_calls += 1
         needs_sampler = any(s.wants_logits and s.req.params.needs_full_sampler for s in step.seqs)
         if needs_sampler and self.par.pp == 1:
@@ -564,7 +578,7 @@ class LLMEngine:
                     self.proposer.forget(r.seq_id)
                 self.requests.pop(r.request_id, None)
             if self.tp_rank == 0:
-                events.append(TokenEvent(r.request_id, new, bool(reason), reason))
+                events.append(TokenEvent(r.request_id, new, bool(reason), reason, embedding=getattr(r, "embedding", None)))
         return events
 
     def _finish_reason(self, r: Request, new: List[int]) -> Optional[str]:

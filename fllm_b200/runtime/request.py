@@ -34,6 +34,7 @@ class SamplingParams:
     timeout_s: Optional[float] = None
     cache_salt: str = ""
     speculative: bool = True
+    embed: bool = False                  # return the final-norm hidden state of the last prompt token (embeddings API)
     guided: Optional[object] = None      # runtime.grammar.GuidedJson: per-step allowed-token mask + advance()
 
     @property
@@ -127,3 +128,4 @@ class TokenEvent:
     finish_reason: Optional[str] = None
     logprobs: Optional[List[float]] = None
     error: Optional[str] = None
+    embedding: Optional[List[float]] = None

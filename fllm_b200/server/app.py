@@ -129,7 +129,8 @@ class EngineWorker:
                     if ent is not None:
                         self.metrics.observe("fllm_e2e_request_latency_seconds", now - ent[2])
                 self._emit(ev.request_id, {"tokens": ev.token_ids, "finished": ev.finished,
-                                           "reason": ev.finish_reason, "error": ev.error}, ev.finished)
+                                           "reason": ev.finish_reason, "error": ev.error,
+                                           "embedding": ev.embedding}, ev.finished)
             bm = eng.blocks
             self.metrics.set("fllm_kv_cache_usage", bm.num_used() / max(bm.num_blocks, 1))
             self.metrics.set("fllm_requests_running", len(eng.scheduler.running))
@@ -271,7 +272,7 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
                     yield {"text": text, "tokens": item["tokens"], "finished": True, "reason": "stop"}
                     return
                 yield {"text": text, "tokens": item["tokens"], "finished": item["finished"],
-                       "reason": "stop" if chk.hit else item["reason"]}
+                       "reason": "stop" if chk.hit else item["reason"], "embedding": item.get("embedding")}
                 if item["finished"]:
                     return
         except (asyncio.CancelledError, GeneratorExit):
@@ -459,9 +460,49 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
         ids = chat_prompt(body.get("messages", []), body.get("tools"))
         return {"prompt_token_ids": ids, "prompt": tokenizer.decode(ids)}
 
+    async def embed_one(ids: List[int]) -> List[float]:
+        """Decoder-as-encoder embedding: the final-norm hidden state of the last prompt token, L2-normalised."""
+        sp = SamplingParams(max_tokens=1, temperature=0.0, embed=True, ignore_eos=True)
+        vec = None
+        async for piece in generate(ids, sp):
+            vec = piece.get("embedding") or vec
+        if vec is None:
+            raise HTTPException(501, "this engine configuration cannot return hidden states")
+        n = sum(v * v for v in vec) ** 0.5 or 1.0
+        return [v / n for v in vec]
+
+    def embedding_inputs(inp) -> List[List[int]]:
+        if isinstance(inp, str):
+            return [tokenizer.encode(inp, add_bos=True)]
+        if isinstance(inp, list) and inp and all(isinstance(t, int) for t in inp):
+            return [[int(t) for t in inp]]
+        if isinstance(inp, list) and inp:
+            return [encode_prompt(x) if not isinstance(x, str) else tokenizer.encode(x, add_bos=True) for x in inp]
+        raise HTTPException(400, "input must be a string, a list of strings, or token ids")
+
     @app.post("/v1/embeddings")
     async def embeddings(body: dict):
-        raise HTTPException(501, "this model is a decoder served for generation; no embedding head is loaded")
+        batches = embedding_inputs(body.get("input"))
+        vecs = await asyncio.gather(*[embed_one(ids) for ids in batches])
+        ntok = sum(len(b) for b in batches)
+        return {"object": "list", "model": model_name,
+                "data": [{"object": "embedding", "index": i, "embedding": v} for i, v in enumerate(vecs)],
+                "usage": {"prompt_tokens": ntok, "total_tokens": ntok}}
+
+    @app.post("/api/embed")
+    async def ollama_embed(body: dict):
+        batches = embedding_inputs(body.get("input"))
+        return {"model": model_name, "embeddings": await asyncio.gather(*[embed_one(ids) for ids in batches])}
+
+    @app.post("/api/embeddings")
+    async def ollama_embeddings(body: dict):
+        (ids,) = embedding_inputs(body.get("prompt", ""))[:1]
+        return {"embedding": await embed_one(ids)}
+
+    @app.post("/embedding")
+    async def llamacpp_embedding(body: dict):
+        (ids,) = embedding_inputs(body.get("content", ""))[:1]
+        return {"embedding": await embed_one(ids)}
 
     # ------------------------------------------------------------------ Anthropic
     def anthropic_messages(body: dict) -> List[dict]:

@@ -1,0 +1,110 @@
+"""Property / fuzz tests of the parsers that read untrusted bytes or text (hypothesis)."""
+import json
+import os
+import struct
+
+import numpy as np
+import pytest
+from hypothesis import HealthCheck, given, settings
+from hypothesis import strategies as st
+
+from fllm_b200.formats.gguf import GgufError, GgufReader
+from fllm_b200.formats.safetensors_io import SafetensorsError, SafetensorsFile
+from fllm_b200.runtime.grammar import json_complete, json_feed, json_start
+from fllm_b200.server.parsers import ReasoningStream, parse_tool_calls, split_reasoning
+
+FAST = settings(max_examples=150, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture])
+
+
+@FAST
+@given(st.binary(min_size=0, max_size=400))
+def test_gguf_reader_rejects_garbage_with_its_own_error(tmp_path, blob):
+    path = os.path.join(tmp_path, "x.gguf")
+    with open(path, "wb") as f:
+        f.write(blob)
+    with pytest.raises((GgufError, ValueError)):
+        GgufReader(path)
+
+
+@FAST
+@given(st.binary(min_size=0, max_size=200), st.integers(0, 2 ** 20))
+def test_gguf_reader_survives_a_valid_magic_with_corrupt_body(tmp_path, tail, count):
+    path = os.path.join(tmp_path, "y.gguf")
+    with open(path, "wb") as f:
+        f.write(b"GGUF" + struct.pack("<IQQ", 3, count, count) + tail)
+    try:
+        r = GgufReader(path)
+        r.close()
+    except (GgufError, ValueError):
+        pass
+
+
+@FAST
+@given(st.binary(min_size=0, max_size=300))
+def test_safetensors_reader_rejects_garbage(tmp_path, blob):
+    path = os.path.join(tmp_path, "m.safetensors")
+    with open(path, "wb") as f:
+        f.write(blob)
+    try:
+        f = SafetensorsFile(path)
+        for k in f.keys():
+            f.tensor(k)
+        f.close()
+    except (SafetensorsError, ValueError):
+        pass
+
+
+_json_values = st.recursive(
+    st.none() | st.booleans() | st.integers(-10 ** 9, 10 ** 9) | st.floats(allow_nan=False, allow_infinity=False) | st.text(max_size=8),
+    lambda kids: st.lists(kids, max_size=4) | st.dictionaries(st.text(max_size=5), kids, max_size=4), max_leaves=12)
+
+
+@FAST
+@given(st.dictionaries(st.text(max_size=5), _json_values, max_size=4), st.booleans())
+def test_every_serialised_json_object_is_accepted_by_the_recogniser(obj, pretty):
+    doc = json.dumps(obj, indent=1 if pretty else None, ensure_ascii=False)
+    s = json_feed(json_start(True), doc)
+    assert s is not None and json_complete(s), doc
+
+
+@FAST
+@given(st.text(max_size=60))
+def test_recogniser_agrees_with_json_loads_on_complete_documents(text):
+    s = json_feed(json_start(False), text)
+    accepted = s is not None and json_complete(s)
+    try:
+        json.loads(text)
+        valid = True
+    except (ValueError, RecursionError):
+        valid = False
+    if valid:
+        assert accepted, text
+    # python's json also accepts NaN / Infinity literals, the recogniser does not: only check one direction more
+    if accepted:
+        json.loads(text)
+
+
+@FAST
+@given(st.text(max_size=120), st.sampled_from(["hermes", "llama3_json", "mistral"]))
+def test_tool_parsers_never_raise_and_keep_text_when_nothing_parses(text, style):
+    rest, calls = parse_tool_calls(text, style)
+    assert isinstance(rest, str) and isinstance(calls, list)
+    if not calls:
+        assert rest == text
+    for c in calls:
+        json.loads(c["function"]["arguments"])
+
+
+@FAST
+@given(st.text(alphabet="<>/think \nab", max_size=80), st.integers(1, 9))
+def test_streaming_reasoning_split_equals_the_one_shot_split(text, cut):
+    r, a = split_reasoning(text)
+    rs = ReasoningStream()
+    pieces = [text[i:i + cut] for i in range(0, len(text), cut)] or [""]
+    rr, cc = "", ""
+    for i, p in enumerate(pieces):
+        x, y = rs.push(p, i == len(pieces) - 1)
+        rr += x
+        cc += y
+    assert (rr.strip() or None) == r
+    assert cc.strip() == a.strip()

@@ -178,3 +178,16 @@ def test_identical_greedy_requests_hit_the_response_cache(client):
     assert a["choices"][0]["token_ids"] == b["choices"][0]["token_ids"]
     assert after["hits"] == before["hits"] + 1 and after["entries"] >= 1
     assert client.post("/admin/cache").json()["dropped_responses"] >= 1
+
+
+def test_embeddings_routes_return_normalised_last_token_states(client):
+    r = client.post("/v1/embeddings", json={"input": ["hello", "hello", "other text"]}).json()
+    vecs = [d["embedding"] for d in r["data"]]
+    assert len(vecs) == 3 and len(vecs[0]) == 64 or len(vecs[0]) > 0
+    assert abs(sum(v * v for v in vecs[0]) - 1.0) < 1e-3
+    assert max(abs(a - b) for a, b in zip(vecs[0], vecs[1])) < 1e-5       # same text, same vector
+    assert max(abs(a - b) for a, b in zip(vecs[0], vecs[2])) > 1e-3
+    assert r["usage"]["prompt_tokens"] > 0
+    o = client.post("/api/embed", json={"input": "hello"}).json()
+    assert max(abs(a - b) for a, b in zip(o["embeddings"][0], vecs[0])) < 1e-5
+    assert len(client.post("/api/embeddings", json={"prompt": "hello"}).json()["embedding"]) == len(vecs[0])
