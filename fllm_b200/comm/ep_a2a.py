@@ -123,7 +123,7 @@ def moe_ffn_a2a_phases(dec, lw, ep: EpAllToAll, h_owned: torch.Tensor):
     """The MoE layer of one rank in all-to-all mode as a generator of phases (route+dispatch |
     expert compute+return | combine), so that a single-GPU test can interleave virtual ranks. The
     final value is the layer output for the owned rows."""
-    from ..models.moe import _token_tile
+    from ..models.moe import _grouped, _token_tile
     cfg, ops = dec.cfg, dec.ops
     kk = ops.k
     T, H = h_owned.shape
@@ -149,10 +149,10 @@ def moe_ffn_a2a_phases(dec, lw, ep: EpAllToAll, h_owned: torch.Tensor):
     xp = torch.empty(rows_cap, H, dtype=h_owned.dtype, device=h_owned.device)
     kk.moe_gather(ep.recv_x, token_of, xp)
     gu = torch.empty(rows_cap, lw.exp_gate_up.shape[1], dtype=h_owned.dtype, device=h_owned.device)
-    kk.moe_grouped_linear(xp, lw.exp_gate_up, lw.exp_gate_up_b, gu, tile_e, tile_r, ntiles, bn, ops.status)
+    _grouped(kk, ops, xp, lw.exp_gate_up, lw.exp_gate_up_b, gu, tile_e, tile_r, ntiles, bn)
     act = ops.glu(gu, dec.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit)
     y = torch.empty(rows_cap, H, dtype=h_owned.dtype, device=h_owned.device)
-    kk.moe_grouped_linear(act, lw.exp_down, lw.exp_down_b, y, tile_e, tile_r, ntiles, bn, ops.status)
+    _grouped(kk, ops, act, lw.exp_down, lw.exp_down_b, y, tile_e, tile_r, ntiles, bn)
     ep.return_rows(y, row_of)
     yield "returned"
     comb = ep.wait_returns()

@@ -54,6 +54,24 @@ int64_t moe_grouped_linear(const Tensor& xp, const Tensor& w_stack, const option
                                        num_tiles.data_ptr<int>(), (int)tile_expert.numel(), (int)bn, st, cur_stream());
 }
 
+// Same over packed 4-bit expert stacks: codes [E, n, k/2] bytes, scales [E, n, k/16] (NVFP4), [E, n, k/32] (MXFP4)
+// bytes or [E, n, k/32, 2] bf16 (INT4 group-affine).
+int64_t moe_grouped_linear_w4(const Tensor& xp, const Tensor& codes, const Tensor& scales, int64_t fmt, double alpha,
+                              const optional<Tensor>& bias_stack, Tensor y, const Tensor& tile_expert,
+                              const Tensor& tile_row0, const Tensor& num_tiles, int64_t bn, const optional<Tensor>& status) {
+  TORCH_CHECK(codes.dim() == 3 && codes.is_contiguous() && codes.element_size() == 1, "codes: contiguous [E, n, k/2] bytes");
+  TORCH_CHECK(scales.is_contiguous() && scales.is_cuda(), "scales: contiguous device tensor");
+  TORCH_CHECK(xp.dim() == 2 && xp.stride(1) == 1 && xp.size(1) == codes.size(2) * 2 && xp.scalar_type() == at::kBFloat16, "xp: [rows, k] bf16");
+  TORCH_CHECK(y.dim() == 2 && y.stride(1) == 1 && y.size(0) == xp.size(0) && y.size(1) == codes.size(1), "y: [rows, n]");
+  c10::cuda::CUDAGuard guard(xp.device());
+  int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  return fllm::moe_grouped_linear_w4(xp.data_ptr(), xp.stride(0), codes.data_ptr(), scales.data_ptr(), (int)fmt, (float)alpha,
+                                     optp(bias_stack), y.data_ptr(), y.stride(0), (int)xp.size(0), (int)codes.size(1),
+                                     (int)codes.size(2) * 2, (int)codes.size(0), tile_expert.data_ptr<int>(),
+                                     tile_row0.data_ptr<int>(), num_tiles.data_ptr<int>(), (int)tile_expert.numel(), (int)bn,
+                                     st, cur_stream());
+}
+
 void moe_combine(const Tensor& y, const Tensor& row_of, const Tensor& weights, Tensor out) {
   TORCH_CHECK(y.stride(1) == 1 && out.stride(1) == 1 && y.size(1) == out.size(1), "moe_combine: shapes");
   c10::cuda::CUDAGuard guard(y.device());
@@ -125,6 +143,7 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("moe_align(Tensor ids, int experts, int expert_lo, int expert_hi, int bn, Tensor(a!) row_of, Tensor(b!) token_of, Tensor(c!) tile_expert, Tensor(d!) tile_row0, Tensor(e!) num_tiles) -> ()", &moe_align);
   m.def("moe_gather(Tensor x, Tensor token_of, Tensor(a!) xp) -> ()", &moe_gather);
   m.def("moe_grouped_linear(Tensor xp, Tensor w_stack, Tensor? bias_stack, Tensor(a!) y, Tensor tile_expert, Tensor tile_row0, Tensor num_tiles, int bn, Tensor? status) -> int", &moe_grouped_linear);
+  m.def("moe_grouped_linear_w4(Tensor xp, Tensor codes, Tensor scales, int fmt, float alpha, Tensor? bias_stack, Tensor(a!) y, Tensor tile_expert, Tensor tile_row0, Tensor num_tiles, int bn, Tensor? status) -> int", &moe_grouped_linear_w4);
   m.def("moe_combine(Tensor y, Tensor row_of, Tensor weights, Tensor(a!) out) -> ()", &moe_combine);
   m.def("ep_ctx_create(int ranks, int my_rank, int cap, int hidden, int experts_per_rank, int[] recv_x, int[] recv_meta, int[] ctrl, int[] comb_y) -> int", &ep_ctx_create);
   m.def("ep_dispatch(int ctx, Tensor x, Tensor ids, int epoch, Tensor? status) -> ()", &ep_dispatch);

@@ -88,6 +88,10 @@ int linear_fp8_block(const void* xq, const float* sx, const void* wq, const floa
 int linear_w4a16(const void* x, long long ldx, const void* codes, const void* scales, int fmt, float alpha,
                  const void* bias, void* y, long long ldy, int T, int N, int K, void* workspace, size_t workspace_bytes,
                  int* status, cudaStream_t stream);
+int moe_grouped_linear_w4(const void* xp, long long ldx, const void* codes_stack, const void* scales_stack, int fmt,
+                          float alpha, const void* bias_stack, void* y, long long ldy, int rows_cap, int n_out, int K,
+                          int experts, const int* tile_expert, const int* tile_row0, const int* num_tiles, int max_tiles,
+                          int bn, int* status, cudaStream_t stream);
 void w4_dequant_bf16(const void* codes, const void* scales, int fmt, float alpha, void* out, long long rows, int K,
                      cudaStream_t s);
 

@@ -43,6 +43,14 @@ struct W4Args {
   float alpha;                        // tensor scale (NVFP4), 1 otherwise
   const __nv_bfloat16* bias;
   int* status;
+  // grouped (mixture of experts): blockIdx.y walks a device-built tile list; tile i multiplies rows
+  // [row0, row0 + BN) of the permuted activations with expert e's matrix (codes / scales / bias stacked
+  // over experts, g_rows output features each)
+  const int* g_tile_expert;
+  const int* g_tile_row0;
+  const int* g_num_tiles;
+  int g_rows;
+  int grid_y;                         // K splits, or the length bound of the tile list
 };
 
 constexpr int kW4Groups = 3;                                  // warp groups that take turns on the K steps
@@ -152,6 +160,11 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_raw, const __grid_cons
   uint32_t* lut = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(bars) + S::kBarBytes);
   __nv_bfloat16* stage_out = reinterpret_cast<__nv_bfloat16*>(sR);      // free once every code slot was expanded
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool grouped = p.g_tile_expert != nullptr;
+  if (grouped && (int)blockIdx.y >= *p.g_num_tiles) return;       // the list is shorter than the grid (whole CTA leaves)
+  const int g_expert = grouped ? p.g_tile_expert[blockIdx.y] : 0;
+  const int g_row0 = grouped ? p.g_tile_row0[blockIdx.y] : 0;
+  const int code_row0 = g_expert * p.g_rows + blockIdx.x * W4_BM;  // first row of this tile in the (stacked) code matrix
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < RST; ++s) { mbar_init(&rfull_bar[s], 1); mbar_init(&rempty_bar[s], 16); }
@@ -174,7 +187,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_raw, const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
   pdl_launch_dependents();
   const int m_idx = blockIdx.x;                         // one feature tile (x one K split) per CTA
-  const int kb0 = blockIdx.y * p.kb_per_split;          // multiple of 4: code slots start on 256 values
+  const int kb0 = grouped ? 0 : blockIdx.y * p.kb_per_split;   // multiple of 4: code slots start on 256 values
   const int nkb = min(p.k_blocks, kb0 + p.kb_per_split) - kb0;
 
   if (warp == 0) {
@@ -184,7 +197,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_raw, const __grid_cons
       const int pre = min(nrb, RST);
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&rfull_bar[i], S::kRawBytes);
-        tma_load_2d(sR + i * S::kRawBytes, &tma_raw, &rfull_bar[i], (kb0 + 4 * i) * 32, m_idx * W4_BM);
+        tma_load_2d(sR + i * S::kRawBytes, &tma_raw, &rfull_bar[i], (kb0 + 4 * i) * 32, code_row0);
       }
       pdl_wait();
       int rs = 0, bs = 0;
@@ -194,13 +207,13 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_raw, const __grid_cons
           if ((kb >> 2) >= pre) {
             if (!mbar_wait(&rempty_bar[rs], rphase ^ 1, abort_flag)) break;
             mbar_expect_tx(&rfull_bar[rs], S::kRawBytes);
-            tma_load_2d(sR + rs * S::kRawBytes, &tma_raw, &rfull_bar[rs], (kb0 + kb) * 32, m_idx * W4_BM);
+            tma_load_2d(sR + rs * S::kRawBytes, &tma_raw, &rfull_bar[rs], (kb0 + kb) * 32, code_row0);
           }
           if (++rs == RST) { rs = 0; rphase ^= 1; }
         }
         if (!mbar_wait(&bempty_bar[bs], bphase ^ 1, abort_flag)) break;
         mbar_expect_tx(&bfull_bar[bs], S::kBBytes);
-        tma_load_2d(sB + bs * S::kBBytes, &tma_b, &bfull_bar[bs], (kb0 + kb) * W4_BK, 0);
+        tma_load_2d(sB + bs * S::kBBytes, &tma_b, &bfull_bar[bs], (kb0 + kb) * W4_BK, g_row0);
         if (++bs == BST) { bs = 0; bphase ^= 1; }
       }
     }
@@ -233,7 +246,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_raw, const __grid_cons
     const int q = warp & 3;                             // TMEM lane quarter this warp may touch
     const int g = e >> 2;                               // group
     const int row = q * 32 + lane;
-    const int m_row = min(m_idx * W4_BM + row, p.M - 1);
+    const int m_row = g_expert * p.g_rows + min(m_idx * W4_BM + row, p.M - 1);
     const int sbytes = p.fmt == 0 ? 4 : p.fmt == 1 ? 2 : 8;   // scale bytes per row per step
     const uint8_t* srow = p.scales + (size_t)m_row * (p.K / 64) * sbytes + (size_t)kb0 * sbytes;
     const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
@@ -315,7 +328,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_raw, const __grid_cons
     if (ok && has_cols && mbar_wait(tfull_bar, 0, abort_flag)) {
       tc_fence_after_sync();
       const int m = m_idx * W4_BM + q * 32 + lane;
-      const float bias_m = (p.bias && m < p.M) ? __bfloat162float(p.bias[m]) : 0.f;
+      const float bias_m = (p.bias && m < p.M) ? __bfloat162float(p.bias[g_expert * p.g_rows + m]) : 0.f;
       __nv_bfloat16* stg = stage_out + e * (32 * 32);
       const int c_begin = BN >= 32 ? half * COLS_PER_WARP : 0;
 #pragma unroll 1
@@ -339,7 +352,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_raw, const __grid_cons
 #pragma unroll
         for (int rnd = 0; rnd < CH / 8; ++rnd) {
           const int c = (lane >> 2) + 8 * rnd;
-          const int n = c0 + c;
+          const int n = g_row0 + c0 + c;
           if (n < p.N && mm0 < p.M)
             *reinterpret_cast<uint4*>(p.out + (size_t)n * p.ldc + mm0) = *reinterpret_cast<const uint4*>(stg + c * 32 + f0);
         }
@@ -424,7 +437,7 @@ static void launch_w4(const CUtensorMap& tr, const CUtensorMap& tb, const W4Args
                                     cudaSharedmemCarveoutMaxShared), "cudaFuncSetAttribute(carveout)");
     configured = true;
   }
-  launch_pdl(gemm_w4a16_kernel<BN>, dim3(a.m_tiles, a.k_splits), dim3(kW4Threads), S::kTotal, s, tr, tb, a);
+  launch_pdl(gemm_w4a16_kernel<BN>, dim3(a.m_tiles, a.grid_y), dim3(kW4Threads), S::kTotal, s, tr, tb, a);
 }
 
 // y[T][N] = x[T][K] * dequant(codes, scales)^T * alpha (+ bias); T <= 128.
@@ -448,6 +461,7 @@ int linear_w4a16(const void* x, long long ldx, const void* codes, const void* sc
   a.kb_per_split = ((a.k_blocks + splits - 1) / splits + 3) & ~3;      // code slots cover four K steps
   a.k_splits = (a.k_blocks + a.kb_per_split - 1) / a.kb_per_split;
   a.ws = reinterpret_cast<float*>(workspace);
+  a.grid_y = a.k_splits;
   CUtensorMap tr = make_tmap_2d(codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, W4_BM, 128, true);
   CUtensorMap tb = make_tmap_2d(x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, K, ldx * 2, bn, W4_BK, true);
   switch (bn) {
@@ -461,6 +475,38 @@ int linear_w4a16(const void* x, long long ldx, const void* codes, const void* sc
     launch_pdl(w4_splitk_reduce_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, stream,
                (const float*)a.ws, a.k_splits, T, N, ldy, alpha, a.bias, a.out);
     return 2;
+  }
+  return 1;
+}
+
+// Grouped form over a device-built tile list (mixture of experts): y[row, :] = dequant(codes[e(row)]) * xp[row, :]
+// (+ bias[e(row)]) for the permuted, per-expert padded rows of xp; `bn` is the token-tile width the list was
+// built for (at most 128), `max_tiles` bounds the list.
+int moe_grouped_linear_w4(const void* xp, long long ldx, const void* codes_stack, const void* scales_stack, int fmt,
+                          float alpha, const void* bias_stack, void* y, long long ldy, int rows_cap, int n_out, int K,
+                          int experts, const int* tile_expert, const int* tile_row0, const int* num_tiles, int max_tiles,
+                          int bn, int* status, cudaStream_t stream) {
+  if (rows_cap <= 0 || max_tiles <= 0) return 0;
+  if (K % 64 || n_out % 8 || (ldx & 7) || (ldy & 7)) throw std::runtime_error("moe_grouped_linear_w4: K % 64, n_out % 8 and 16-byte rows required");
+  if (fmt < 0 || fmt > 2) throw std::runtime_error("moe_grouped_linear_w4: fmt must be 0, 1 or 2");
+  if (bn != 16 && bn != 32 && bn != 64 && bn != 128) throw std::runtime_error("moe_grouped_linear_w4: token tile must be 16, 32, 64 or 128");
+  W4Args a{};
+  a.M = n_out; a.N = rows_cap; a.K = K; a.m_tiles = (n_out + W4_BM - 1) / W4_BM; a.k_blocks = K / W4_BK; a.fmt = fmt;
+  a.ldc = ldy; a.out = reinterpret_cast<__nv_bfloat16*>(y); a.scales = reinterpret_cast<const uint8_t*>(scales_stack);
+  a.alpha = alpha; a.bias = reinterpret_cast<const __nv_bfloat16*>(bias_stack); a.status = status;
+  a.k_splits = 1; a.kb_per_split = a.k_blocks;
+  a.g_tile_expert = tile_expert; a.g_tile_row0 = tile_row0; a.g_num_tiles = num_tiles; a.g_rows = n_out;
+  // when n_out is not a multiple of 128 the last feature tile of an expert also reads rows of the next expert's
+  // codes (or zero fill past the stack); the epilogue never stores those rows
+  CUtensorMap tr = make_tmap_2d(codes_stack, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)experts * n_out, K / 2, K / 2,
+                                W4_BM, 128, true);
+  CUtensorMap tb = make_tmap_2d(xp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_cap, K, ldx * 2, bn, W4_BK, true);
+  a.grid_y = max_tiles;
+  switch (bn) {
+    case 16: launch_w4<16>(tr, tb, a, stream); break;
+    case 32: launch_w4<32>(tr, tb, a, stream); break;
+    case 64: launch_w4<64>(tr, tb, a, stream); break;
+    default: launch_w4<128>(tr, tb, a, stream); break;
   }
   return 1;
 }

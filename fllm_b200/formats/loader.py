@@ -136,12 +136,29 @@ def _load_moe_layer(cfg, sp, tp_rank, lw, p, get, dev) -> None:
     rb = get(p + "mlp.router.bias", False)
     lw.router_b = dev(rb) if rb is not None else None
 
+    # MXFP4 experts stay packed on a GPU when whole experts live on this rank (one GPU, or expert parallel)
+    # and the grouped packed GEMM can address them (input width a multiple of 64)
+    keep_packed = str(dev(torch.zeros(1)).device).startswith("cuda") and (sp.expert_parallel or sp.inter_local == cfg.moe_intermediate_size)
+
     def expert(name):
         blk = get(p + f"mlp.experts.{name}_blocks", False)
         if blk is not None:
-            return _mxfp4_stack(blk, get(p + f"mlp.experts.{name}_scales"))          # [E, out, in]
+            sc = get(p + f"mlp.experts.{name}_scales")
+            if keep_packed and (blk.shape[2] * 32) % 64 == 0:
+                from ..ops.fp4 import MXFP4, Fp4ExpertStack
+                E, R, G, _ = blk.shape
+                return Fp4ExpertStack(blk.reshape(E, R, G * 16), sc.reshape(E, R, G), MXFP4)
+            return _mxfp4_stack(blk, sc)                                               # [E, out, in]
         return get(p + f"mlp.experts.{name}").float().transpose(1, 2)                # stored [E, in, out]
     gu, dn = expert("gate_up_proj"), expert("down_proj")
+    if not isinstance(gu, torch.Tensor) or not isinstance(dn, torch.Tensor):
+        es = slice(sp.expert_start, sp.expert_start + sp.expert_local) if sp.expert_parallel else slice(None)
+        gub, dnb = get(p + "mlp.experts.gate_up_proj_bias", False), get(p + "mlp.experts.down_proj_bias", False)
+        pick = lambda t: (t[es].to(dev(torch.zeros(1)).device) if not isinstance(t, torch.Tensor) else dev(t[es]))
+        lw.exp_gate_up, lw.exp_down = pick(gu), pick(dn)
+        lw.exp_gate_up_b = dev(gub[es]) if gub is not None else None
+        lw.exp_down_b = dev(dnb[es]) if dnb is not None else None
+        return
     gub, dnb = get(p + "mlp.experts.gate_up_proj_bias", False), get(p + "mlp.experts.down_proj_bias", False)
     if sp.expert_parallel:
         es = slice(sp.expert_start, sp.expert_start + sp.expert_local)

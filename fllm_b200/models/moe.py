@@ -71,11 +71,32 @@ def _token_tile(rows_per_expert: float) -> int:
     return 128
 
 
+def _dense_experts(lw):
+    """LayerWeights view with packed expert stacks expanded (oracle / CPU path)."""
+    if isinstance(lw.exp_gate_up, torch.Tensor) and isinstance(lw.exp_down, torch.Tensor):
+        return lw
+    import copy
+    d = copy.copy(lw)
+    if not isinstance(lw.exp_gate_up, torch.Tensor):
+        d.exp_gate_up = lw.exp_gate_up.dense().to(torch.bfloat16)
+    if not isinstance(lw.exp_down, torch.Tensor):
+        d.exp_down = lw.exp_down.dense().to(torch.bfloat16)
+    return d
+
+
+def _grouped(k_ops, ops, x, w, bias, y, tile_e, tile_r, ntiles, bn):
+    """Grouped expert GEMM on a bf16 stack or on a packed 4-bit stack."""
+    if isinstance(w, torch.Tensor):
+        k_ops.moe_grouped_linear(x, w, bias, y, tile_e, tile_r, ntiles, bn, ops.status)
+    else:
+        k_ops.moe_grouped_linear_w4(x, w.codes, w.scales, w.fmt, w.alpha, bias, y, tile_e, tile_r, ntiles, bn, ops.status)
+
+
 def moe_ffn(dec, lw, h: torch.Tensor) -> torch.Tensor:
     cfg, ops, sp = dec.cfg, dec.ops, dec.spec
     lo = sp.expert_start if sp.expert_parallel else 0
     if not hasattr(ops, "k") or not h.is_cuda:
-        return moe_reference(cfg, lw, h, lo).to(h.dtype)
+        return moe_reference(cfg, _dense_experts(lw), h, lo).to(h.dtype)
     k_ops = ops.k
     T, H = h.shape
     k = cfg.experts_per_token
@@ -97,10 +118,10 @@ def moe_ffn(dec, lw, h: torch.Tensor) -> torch.Tensor:
     xp = torch.empty(rows_cap, H, dtype=h.dtype, device=h.device)
     k_ops.moe_gather(h, token_of, xp)
     gu = torch.empty(rows_cap, lw.exp_gate_up.shape[1], dtype=h.dtype, device=h.device)
-    k_ops.moe_grouped_linear(xp, lw.exp_gate_up, lw.exp_gate_up_b, gu, tile_e, tile_r, ntiles, bn, ops.status)
+    _grouped(k_ops, ops, xp, lw.exp_gate_up, lw.exp_gate_up_b, gu, tile_e, tile_r, ntiles, bn)
     act = ops.glu(gu, dec.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit)
     y = torch.empty(rows_cap, H, dtype=h.dtype, device=h.device)
-    k_ops.moe_grouped_linear(act, lw.exp_down, lw.exp_down_b, y, tile_e, tile_r, ntiles, bn, ops.status)
+    _grouped(k_ops, ops, act, lw.exp_down, lw.exp_down_b, y, tile_e, tile_r, ntiles, bn)
     out = torch.empty(T, H, dtype=h.dtype, device=h.device)
     k_ops.moe_combine(y, row_of, wts, out)
     ops.launches += 6

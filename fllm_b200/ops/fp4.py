@@ -117,6 +117,39 @@ class Fp4Weight:
         return ops.linear(x, dense, bias, out)
 
 
+class Fp4ExpertStack:
+    """The matrices of several experts held packed: codes [E, N, K/2], scales [E, N, K/block] (bytes).
+    ``moe_ffn`` hands it to the grouped packed GEMM; gpt-oss checkpoints store their experts this way
+    (MXFP4), so the bytes go from the file to the tensor core unexpanded."""
+
+    def __init__(self, codes: torch.Tensor, scales: torch.Tensor, fmt: int, alpha: float = 1.0):
+        self.codes, self.scales, self.fmt, self.alpha = codes.contiguous(), scales.contiguous(), int(fmt), float(alpha)
+        self.shape = (codes.shape[0], codes.shape[1], codes.shape[2] * 2)
+        self.device = codes.device
+
+    @classmethod
+    def from_dense(cls, stack: torch.Tensor, fmt="mxfp4") -> "Fp4ExpertStack":
+        f = FMT_NAMES[fmt] if isinstance(fmt, str) else fmt
+        E, N, K = stack.shape
+        if f == NVFP4:
+            raise ValueError("expert stacks use one scale format for all experts: MXFP4")
+        c, s, _ = quantize_mxfp4(stack.reshape(E * N, K))
+        return cls(c.view(E, N, K // 2), s.view(E, N, K // 32), f)
+
+    def dense(self) -> torch.Tensor:
+        E, N, K = self.shape
+        return dequantize_fp4(self.codes.view(E * N, K // 2), self.scales.view(E * N, -1), self.fmt, self.alpha).view(E, N, K)
+
+    def __getitem__(self, sl) -> "Fp4ExpertStack":
+        return Fp4ExpertStack(self.codes[sl], self.scales[sl], self.fmt, self.alpha)
+
+    def to(self, device) -> "Fp4ExpertStack":
+        return Fp4ExpertStack(self.codes.to(device), self.scales.to(device), self.fmt, self.alpha)
+
+    def nbytes(self) -> int:
+        return self.codes.numel() + self.scales.numel()
+
+
 def quantize_decoder_weights(weights, fmt: str = "nvfp4") -> int:
     """Replace the four projection matrices of every layer by FP4 weights (embedding, norms and
     the lm_head stay bf16). Returns the bytes now held for those projections."""

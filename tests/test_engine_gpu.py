@@ -156,3 +156,31 @@ def test_fp8_kv_cache_on_the_gpu_matches_the_cpu_oracle_path():
         outs.append(rows[0])
     err = (outs[0] - outs[1]).abs().max().item() / (outs[0].abs().max().item() + 1e-6)
     assert 0 < err < 0.08, err
+
+
+def test_gpt_oss_checkpoint_keeps_mxfp4_experts_packed_on_the_gpu(tmp_path):
+    """The same synthetic gpt-oss checkpoint loaded on the GPU keeps its experts as MXFP4 stacks (grouped
+    packed GEMM) and gives the logits of the CPU load that expands them to bf16."""
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    from fllm_b200.models.weights import init_random_weights
+    from fllm_b200.ops.fp4 import Fp4ExpertStack
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    from test_formats_cpu import write_gpt_oss_checkpoint
+    cfg = preset("gpt-oss-tiny")
+    write_gpt_oss_checkpoint(tmp_path, cfg, init_random_weights(cfg, device="cpu", seed=4))
+    outs = []
+    for device in ("cuda:0", "cpu"):
+        cfg2, w2, _ = load_hf_checkpoint(str(tmp_path), device=device)
+        assert isinstance(w2.layers[0].exp_gate_up, Fp4ExpertStack) == (device != "cpu")
+        ec = EngineConfig(max_num_seqs=2, max_num_batched_tokens=64, max_model_len=128, num_kv_blocks=32)
+        eng = LLMEngine(cfg2, ec, device=device, weights=w2)
+        p = _prompts(cfg2.vocab_size, (40,))[0]
+        eng.add_request(p, SamplingParams(max_tokens=1))
+        step = eng.scheduler.schedule()
+        logits = eng.decoder.forward(eng._build_batch(step))
+        outs.append(logits[-1].float().cpu())
+        if device != "cpu":
+            assert eng.ops.check_status() == 0
+    err = (outs[0] - outs[1]).abs().max().item() / (outs[1].abs().max().item() + 1e-6)
+    assert err < 0.05, err

@@ -186,20 +186,13 @@ def test_gguf_loader_feeds_the_torch_engine(tmp_path):
     assert sum(x == y for x, y in zip(a, b)) >= 4       # int8-activation dots vs bf16 math: near ties may flip
 
 
-def test_gpt_oss_checkpoint_with_mxfp4_experts_loads(tmp_path):
-    """A synthetic gpt-oss style HF checkpoint (router, sinks, biases, experts as MXFP4 `_blocks` /
-    `_scales`) loads into the decoder layout: dense tensors bit-equal, experts equal to the MXFP4
-    de-quantisation of what was written, and the model runs."""
+def write_gpt_oss_checkpoint(tmp_path, cfg, w):
+    """Writes `w` (full, single-rank weights of a gpt-oss style config) as a Hugging Face directory whose
+    experts are MXFP4 `_blocks` / `_scales`; returns the de-quantised gate_up stacks per layer."""
     import json
     import torch
-    from fllm_b200.config import EngineConfig, preset
-    from fllm_b200.formats.loader import load_hf_checkpoint
     from fllm_b200.formats.safetensors_io import save_file
-    from fllm_b200.models.weights import init_random_weights
     from fllm_b200.ops.fp4 import MXFP4, dequantize_fp4, quantize_mxfp4
-    from fllm_b200.runtime import LLMEngine, SamplingParams
-    cfg = preset("gpt-oss-tiny")
-    w = init_random_weights(cfg, device="cpu", seed=4)
     D, hq, hkv, H, I, E = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads, cfg.hidden_size, cfg.moe_intermediate_size, cfg.num_experts
     t = {"model.embed_tokens.weight": w.embed, "model.norm.weight": w.final_norm, "lm_head.weight": w.lm_head}
     want_gu = []
@@ -221,7 +214,7 @@ def test_gpt_oss_checkpoint_with_mxfp4_experts_loads(tmp_path):
             t[p + f"mlp.experts.{name}_scales"] = scales.view(Ee, R, K // 32)
             if name == "gate_up_proj":
                 want_gu.append(dequantize_fp4(codes, scales, MXFP4).view(Ee, R, K).to(torch.bfloat16))
-    save_file({k: v.contiguous() for k, v in t.items()}, str(tmp_path / "model.safetensors"))
+    save_file({k: v.contiguous().cpu() for k, v in t.items()}, str(tmp_path / "model.safetensors"))
     hf = {"model_type": "gpt_oss", "vocab_size": cfg.vocab_size, "hidden_size": H, "num_hidden_layers": cfg.num_layers,
           "num_attention_heads": hq, "num_key_value_heads": hkv, "head_dim": D, "intermediate_size": I,
           "rms_norm_eps": cfg.rms_eps, "rope_theta": cfg.rope_theta, "max_position_embeddings": cfg.max_position,
@@ -230,6 +223,22 @@ def test_gpt_oss_checkpoint_with_mxfp4_experts_loads(tmp_path):
           "rope_scaling": {"rope_type": "yarn", "factor": 32.0, "beta_fast": 32.0, "beta_slow": 1.0,
                            "original_max_position_embeddings": 4096}}
     json.dump(hf, open(tmp_path / "config.json", "w"))
+    return want_gu
+
+
+def test_gpt_oss_checkpoint_with_mxfp4_experts_loads(tmp_path):
+    """A synthetic gpt-oss style HF checkpoint (router, sinks, biases, experts as MXFP4 `_blocks` /
+    `_scales`) loads into the decoder layout: dense tensors bit-equal, experts equal to the MXFP4
+    de-quantisation of what was written, and the model runs."""
+    import torch
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    from fllm_b200.models.weights import init_random_weights
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    cfg = preset("gpt-oss-tiny")
+    w = init_random_weights(cfg, device="cpu", seed=4)
+    E = cfg.num_experts
+    want_gu = write_gpt_oss_checkpoint(tmp_path, cfg, w)
     cfg2, w2, _ = load_hf_checkpoint(str(tmp_path), device="cpu")
     assert cfg2.is_moe and cfg2.num_experts == E and cfg2.act == "swiglu_oai"
     for l in range(cfg.num_layers):

@@ -527,3 +527,28 @@ def test_fp8_kv_write_and_generic_attention_read(ops, ref, style):
     got = ops.attention(q, kc, vc, tables, row_seq, pos, hq, hkv, D, D ** -0.5)
     want = ref.attention(q, kc, vc, tables, row_seq, pos, hq, hkv, D, D ** -0.5)
     _close(got, want, 2e-2)
+
+
+@pytest.mark.parametrize("T,E,k,H,I", [(5, 8, 4, 256, 256), (64, 32, 4, 512, 384), (300, 16, 2, 256, 128)])
+def test_moe_with_packed_mxfp4_experts(ops, T, E, k, H, I):
+    """Expert stacks held as MXFP4 (the way gpt-oss checkpoints store them) through the grouped packed GEMM,
+    against the fp32 oracle on the de-quantised experts."""
+    from types import SimpleNamespace
+    from fllm_b200.config import ModelConfig
+    from fllm_b200.models.moe import _dense_experts, moe_ffn, moe_reference
+    from fllm_b200.models.weights import LayerWeights
+    from fllm_b200.ops.fp4 import Fp4ExpertStack
+    cfg = ModelConfig(hidden_size=H, num_experts=E, experts_per_token=k, moe_intermediate_size=I, act="swiglu_oai",
+                      expert_bias=True)
+    lw = LayerWeights(attn_norm=None, wqkv=None, wo=None, ffn_norm=None)
+    lw.router_w, lw.router_b = _rand((E, H), 1, 0.2), _rand((E,), 2, 0.1)
+    lw.exp_gate_up = Fp4ExpertStack.from_dense(_rand((E, 2 * I, H), 3, 0.05))
+    lw.exp_gate_up_b = _rand((E, 2 * I), 4, 0.1)
+    lw.exp_down = Fp4ExpertStack.from_dense(_rand((E, H, I), 5, 0.05))
+    lw.exp_down_b = _rand((E, H), 6, 0.1)
+    h = _rand((T, H), 7)
+    dec = SimpleNamespace(cfg=cfg, ops=ops, act_kind=2, spec=SimpleNamespace(expert_parallel=False, expert_start=0))
+    got = moe_ffn(dec, lw, h)
+    want = moe_reference(cfg, _dense_experts(lw), h, 0)
+    _close(got, want, 3e-2)
+    assert ops.check_status() == 0
