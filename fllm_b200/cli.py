@@ -206,6 +206,14 @@ def main(argv: Optional[List[str]] = None) -> int:
     s.add_argument("--reasoning-parser", default=None, choices=["think"])
     s.add_argument("--response-cache-entries", type=int, default=256, help="0 disables the response cache")
     s.set_defaults(fn=cmd_serve)
+    rt = sub.add_parser("router", help="front several serve processes (data-parallel replicas) with one port")
+    rt.add_argument("--replica", action="append", required=True, help="base URL of a replica, e.g. http://127.0.0.1:8001 (repeat)")
+    rt.add_argument("--host", default="127.0.0.1")
+    rt.add_argument("--port", type=int, default=8080)
+    rt.add_argument("--policy", default="prefix", choices=["prefix", "least_loaded", "round_robin"])
+    rt.add_argument("--log-level", default="info")
+    rt.set_defaults(fn=lambda a: (__import__("fllm_b200.server.router", fromlist=["serve_router"]).serve_router(
+        a.replica, a.host, a.port, a.policy, a.log_level), 0)[1])
     r = sub.add_parser("run", help="generate once from a prompt")
     _add_engine_flags(r)
     r.add_argument("prompt")
