@@ -161,6 +161,80 @@ class LLMEngine:
     def has_unfinished(self) -> bool:
         return self.scheduler.has_work() or self._inflight is not None
 
+    # ------------------------------------------------------------------ disaggregated prefill / decode
+    def export_request(self, request_id: str, remove: bool = True) -> dict:
+        """Prefill side of disaggregated serving: the state of a request whose prompt has been
+        processed (tokens, sampling parameters, and the KV blocks it owns, copied to the host), to be
+        handed to ``import_request`` of another engine of the same model and KV layout
+        (rust/engine/src/disagg.rs is the reference's KV hand-over)."""
+        self.drain()
+        r = self.requests.get(request_id)
+        if r is None or r.finished:
+            raise KeyError(f"no live request {request_id!r}")
+        if not r.output or r.num_computed < len(r.prompt):
+            raise ValueError("the prompt has not been processed yet")
+        n = r.num_computed
+        table = self.blocks.table(r.seq_id)[: self.blocks.blocks_needed(n)]
+        live = [i for i, b in enumerate(table) if b >= 0]            # window-pruned blocks are not shipped
+        idx = torch.tensor([table[i] for i in live], dtype=torch.long, device=self.device)
+        kv = self.kv.store.index_select(2, idx).cpu() if live else self.kv.store[:, :, :0].cpu()
+        import dataclasses
+        params = {k: v for k, v in dataclasses.asdict(dataclasses.replace(r.params, guided=None)).items() if k != "guided"}
+        blob = {"prompt": list(r.prompt), "output": list(r.output), "num_computed": n, "live_blocks": live,
+                "kv": kv.view(torch.uint8) if kv.element_size() == 1 else kv, "kv_dtype": str(self.kv.store.dtype),
+                "block_size": self.block_size, "params": params}
+        if remove:
+            self.scheduler.finish(r, "exported")
+            self.requests.pop(request_id, None)
+        return blob
+
+    def import_request(self, blob: dict, request_id: Optional[str] = None) -> str:
+        """Decode side: adopt an exported request. Its KV is copied into freshly allocated blocks and
+        the request continues as a running decode sequence."""
+        kv = blob["kv"]
+        if blob["kv_dtype"] != str(self.kv.store.dtype) or blob["block_size"] != self.block_size:
+            raise ValueError("KV layout mismatch between the exporting and the importing engine")
+        if kv.element_size() == 1 and kv.dtype != self.kv.store.dtype:
+            kv = kv.view(self.kv.store.dtype)
+        want = self.kv.store.shape
+        if tuple(kv.shape[:2]) != tuple(want[:2]) or tuple(kv.shape[3:]) != tuple(want[3:]):
+            raise ValueError(f"KV shape {tuple(kv.shape)} does not fit this engine's pool {tuple(want)}")
+        params = SamplingParams(**blob["params"])
+        params.validate(self.model_cfg.vocab_size)
+        n = int(blob["num_computed"])
+        rid = request_id or f"req-{next(self._req_ids)}"
+        req = Request(rid, next(self._seq_ids), [int(t) for t in blob["prompt"]], params)
+        req.output = [int(t) for t in blob["output"]]
+        req.num_computed = n
+        self.blocks.allocate(req.seq_id, [])
+        if not self.blocks.ensure_capacity(req.seq_id, n + 1):
+            self.blocks.free_seq(req.seq_id)
+            raise RuntimeError("not enough free KV blocks to import the request")
+        table = self.blocks.table(req.seq_id)
+        live = list(blob["live_blocks"])
+        if live:
+            dst = torch.tensor([table[i] for i in live], dtype=torch.long, device=self.device)
+            self.kv.store.index_copy_(2, dst, kv.to(self.device))
+        self.blocks.commit_tokens(req.seq_id, req.all_tokens, n, params.cache_salt.encode())
+        req.status = RequestStatus.RUNNING
+        self.scheduler.running.append(req)
+        self.requests[rid] = req
+        return rid
+
+    def prefill_only(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> "tuple[dict, list]":
+        """Run a prompt until its first token exists and export it. Other requests keep being served
+        by the same steps; their events are returned for the caller to deliver."""
+        rid = self.add_request(prompt, params)
+        events: List[TokenEvent] = []
+        r = self.requests[rid]
+        while not r.output and not r.finished:
+            events.extend(self.step())
+        events.extend(self.drain())
+        if r.finished:
+            raise RuntimeError(f"request finished during prefill: {r.finish_reason}")
+        mine = [e for e in events if e.request_id == rid]
+        return self.export_request(rid), [e for e in events if e.request_id != rid] if mine is not None else events
+
     # ------------------------------------------------------------------ batch building
     def _build_batch(self, step: ScheduledStep, pad_to: int = 0, slot: int = 0) -> StepBatch:
         seqs = step.seqs

@@ -19,6 +19,7 @@ import time
 import uuid
 from typing import Any, AsyncIterator, Dict, List, Optional
 
+import torch
 from fastapi import FastAPI, HTTPException, Request as HttpRequest
 from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
@@ -61,6 +62,20 @@ class EngineWorker:
     def abort(self, rid: str) -> None:
         self.cmds.put(("abort", rid))
 
+    async def call(self, fn):
+        """Run fn(engine) on the engine thread; fn returns (result, events) and the events (of other
+        requests that advanced meanwhile) are delivered like those of a normal step."""
+        loop = asyncio.get_running_loop()
+        fut = loop.create_future()
+        self.cmds.put(("call", fn, loop, fut))
+        return await fut
+
+    def adopt(self, loop, rid: str, n_prompt: int, fn) -> "asyncio.Queue":
+        """Register a stream for `rid`, then run fn(engine) (which must create that request)."""
+        q: asyncio.Queue = asyncio.Queue()
+        self.cmds.put(("adopt", rid, n_prompt, fn, loop, q))
+        return q
+
     def ready(self) -> bool:
         return (not self.draining and not self.stopped.is_set()
                 and time.monotonic() - self.heartbeat < self.STALL_S)
@@ -91,10 +106,39 @@ class EngineWorker:
             elif cmd[0] == "abort":
                 self.engine.abort_request(cmd[1])
                 self.streams.pop(cmd[1], None)
+            elif cmd[0] == "call":
+                _, fn, loop, fut = cmd
+                try:
+                    result, events = fn(self.engine)
+                    self._dispatch(events)
+                    loop.call_soon_threadsafe(fut.set_result, result)
+                except Exception as e:
+                    loop.call_soon_threadsafe(fut.set_exception, e)
+            elif cmd[0] == "adopt":
+                _, rid, n_prompt, fn, loop, q = cmd
+                self.streams[rid] = (loop, q, time.monotonic(), n_prompt)
+                try:
+                    fn(self.engine)
+                except Exception as e:
+                    self._emit(rid, {"error": str(e), "status": 400}, True)
             try:
                 cmd = self.cmds.get_nowait()
             except queue.Empty:
                 return
+
+    def _dispatch(self, events) -> None:
+        now = time.monotonic()
+        for ev in events:
+            ent = self.streams.get(ev.request_id)
+            if ent is not None and ev.token_ids:
+                self.metrics.inc("fllm_generation_tokens_total", len(ev.token_ids))
+            if ev.finished:
+                self.metrics.inc("fllm_requests_total")
+                if ent is not None:
+                    self.metrics.observe("fllm_e2e_request_latency_seconds", now - ent[2])
+            self._emit(ev.request_id, {"tokens": ev.token_ids, "finished": ev.finished,
+                                       "reason": ev.finish_reason, "error": ev.error,
+                                       "embedding": ev.embedding}, ev.finished)
 
     def _run(self) -> None:
         eng = self.engine
@@ -119,18 +163,7 @@ class EngineWorker:
                 if self.consecutive_failures >= 3:
                     self.stopped.set()
                 continue
-            now = time.monotonic()
-            for ev in events:
-                ent = self.streams.get(ev.request_id)
-                if ent is not None and ev.token_ids:
-                    self.metrics.inc("fllm_generation_tokens_total", len(ev.token_ids))
-                if ev.finished:
-                    self.metrics.inc("fllm_requests_total")
-                    if ent is not None:
-                        self.metrics.observe("fllm_e2e_request_latency_seconds", now - ent[2])
-                self._emit(ev.request_id, {"tokens": ev.token_ids, "finished": ev.finished,
-                                           "reason": ev.finish_reason, "error": ev.error,
-                                           "embedding": ev.embedding}, ev.finished)
+            self._dispatch(events)
             bm = eng.blocks
             self.metrics.set("fllm_kv_cache_usage", bm.num_used() / max(bm.num_blocks, 1))
             self.metrics.set("fllm_requests_running", len(eng.scheduler.running))
@@ -363,6 +396,58 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
     @app.post("/admin/cache")
     async def admin_cache_reset():
         return {"freed_blocks": engine.blocks.reset_prefix_cache(), "dropped_responses": rcache.clear()}
+
+    # disaggregated serving: a prefill server exports a processed prompt, a decode server adopts it
+    def _pack_blob(blob: dict) -> dict:
+        import base64
+        kv = blob["kv"].contiguous()
+        out = dict(blob)
+        out["kv"] = {"shape": list(kv.shape), "elem": kv.element_size(),
+                     "data": base64.b64encode(kv.view(torch.uint8).numpy().tobytes()).decode()}
+        return out
+
+    def _unpack_blob(obj: dict) -> dict:
+        import base64
+        kvd = obj["kv"]
+        raw = torch.frombuffer(bytearray(base64.b64decode(kvd["data"])), dtype=torch.uint8)
+        dt = engine.kv.store.dtype if kvd["elem"] == engine.kv.store.element_size() else None
+        if dt is None:
+            raise HTTPException(400, "KV element size does not match this engine")
+        blob = dict(obj)
+        blob["kv"] = raw.view(dt).view(*kvd["shape"])
+        return blob
+
+    @app.post("/admin/disagg/export")
+    async def disagg_export(body: dict):
+        """Process the prompt here and return the request (tokens + KV) for another server to decode."""
+        ids = chat_prompt(body["messages"], body.get("tools")) if body.get("messages") else encode_prompt(body.get("prompt", ""))
+        sp = _sampling_from(body, 256)
+        try:
+            blob = await worker.call(lambda eng: eng.prefill_only(ids, sp))
+        except (ValueError, RuntimeError, KeyError) as e:
+            raise HTTPException(400, str(e))
+        return _pack_blob(blob)
+
+    @app.post("/admin/disagg/import")
+    async def disagg_import(body: dict):
+        """Adopt an exported request and decode it to the end (non-streaming)."""
+        blob = _unpack_blob(body)
+        rid = "req-" + uuid.uuid4().hex
+        q = worker.adopt(asyncio.get_running_loop(), rid, len(blob["prompt"]), lambda eng: eng.import_request(blob, rid))
+        toks, reason = list(blob["output"]), None
+        while True:
+            item = await q.get()
+            if item.get("error"):
+                raise HTTPException(item.get("status", 500), item["error"])
+            toks.extend(item["tokens"])
+            if item["finished"]:
+                reason = item["reason"]
+                break
+        eos = getattr(tokenizer, "eos_token_id", None)
+        text = tokenizer.decode([t for t in toks if t != eos])
+        return {"id": rid, "object": "text_completion", "model": model_name,
+                "choices": [{"index": 0, "text": text, "token_ids": toks, "finish_reason": reason}],
+                "usage": usage(len(blob["prompt"]), len(toks))}
 
     @app.get("/admin/cache")
     async def admin_cache_stats():

@@ -155,3 +155,37 @@ def test_fp8_kv_cache_stays_close_to_bf16_kv():
         outs.append(rows[-1])
     err = (outs[0] - outs[1]).abs().max().item() / (outs[0].abs().max().item() + 1e-6)
     assert 0 < err < 0.08, err
+
+
+def test_disaggregated_prefill_then_decode_matches_one_engine():
+    """Prompt processed on engine A, KV handed to engine B, decoding continued there: same tokens as one
+    engine doing both; B's pool, prefix cache and limits stay consistent; layout mismatches are refused."""
+    import pytest
+    import torch
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    cfg = preset("qwen3-tiny")
+    ec = lambda **kw: EngineConfig(max_num_seqs=4, max_num_batched_tokens=32, max_model_len=160, num_kv_blocks=40, **kw)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (50, 9)]
+    sp = SamplingParams(max_tokens=12)
+    ref = LLMEngine(cfg, ec(), device="cpu", seed=2)
+    want = [ref.generate([p], sp)[0] for p in prompts]        # one at a time, like the hand-over below
+    a, b = LLMEngine(cfg, ec(), device="cpu", seed=2), LLMEngine(cfg, ec(), device="cpu", seed=2)
+    got = []
+    for p in prompts:
+        blob, others = a.prefill_only(p, SamplingParams(max_tokens=12))
+        assert others == [] and len(blob["output"]) == 1 and blob["num_computed"] == len(p)
+        assert not a.requests and a.blocks.num_used() <= a.blocks.blocks_needed(len(p))     # only cached blocks remain
+        rid = b.import_request(blob)
+        toks = list(blob["output"])
+        while b.has_unfinished():
+            for ev in b.step():
+                if ev.request_id == rid:
+                    toks.extend(ev.token_ids)
+        got.append(toks)
+    assert got == want
+    c = LLMEngine(cfg, ec(kv_cache_dtype="fp8_e4m3"), device="cpu", seed=2)
+    blob, _ = a.prefill_only(prompts[1], SamplingParams(max_tokens=4))
+    with pytest.raises(ValueError):
+        c.import_request(blob)

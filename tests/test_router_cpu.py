@@ -79,3 +79,20 @@ def test_a_dead_replica_is_skipped_and_reported(stack):
     with _router({}, "round_robin", dead) as c:
         assert c.post("/v1/completions", json={"prompt": "p"}).status_code == 503
         assert c.get("/ready").status_code == 503
+
+
+def test_disaggregated_prefill_and_decode_servers_agree_with_one_server(stack):
+    """Server A processes the prompt and exports the request; server B imports it and decodes."""
+    a, b = TestClient(stack["a"]), TestClient(stack["b"])
+    body = {"prompt": "disaggregate this prompt please", "max_tokens": 8, "temperature": 0}
+    whole = a.post("/v1/completions", json=body).json()["choices"][0]["token_ids"]
+    blob = a.post("/admin/disagg/export", json=body)
+    assert blob.status_code == 200
+    blob = blob.json()
+    assert len(blob["output"]) == 1 and blob["kv"]["shape"][2] >= 1
+    done = b.post("/admin/disagg/import", json=blob).json()
+    assert done["choices"][0]["token_ids"] == whole
+    assert done["usage"]["completion_tokens"] == len(whole)
+    # a blob for another KV layout is refused
+    bad = dict(blob, block_size=32)
+    assert b.post("/admin/disagg/import", json=bad).status_code == 400
