@@ -290,7 +290,8 @@ class EngineConfig:
     kv_cache_dtype: str = "bf16"         # bf16 | fp8_e4m3
     enable_prefix_caching: bool = True
     scheduling_policy: str = "fcfs"      # fcfs | priority
-    preemption: str = "recompute"        # recompute | swap
+    preemption: str = "recompute"        # recompute | swap (KV of a preempted request parked in host memory)
+    swap_space_gb: float = 4.0           # host memory for swapped-out KV
     decode_first: bool = True
     max_partial_prefills: int = 4
     watermark: float = 0.01

@@ -91,6 +91,8 @@ class LLMEngine:
                                    self.cfg.watermark)
         window = model_cfg.sliding_window if (model_cfg.sliding_window and model_cfg.window_pattern is None) else 0
         self.scheduler = Scheduler(self.cfg, self.blocks, window)
+        if self.cfg.preemption == "swap":
+            self.scheduler.swapper = _KvSwapper(self)
         self.requests: Dict[str, Request] = {}
         self._seq_ids = itertools.count()
         self._req_ids = itertools.count()
@@ -713,6 +715,50 @@ class LLMEngine:
         import gc
         gc.collect()
         gc.freeze()
+
+
+class _KvSwapper:
+    """Host tier for preempted requests: a victim's KV blocks are copied to (pinned) host memory instead of
+    being recomputed later, and copied back into fresh blocks when it is scheduled again. Copies are
+    ordered on the compute stream, after any step still in flight that writes those blocks."""
+
+    def __init__(self, eng: "LLMEngine"):
+        self.eng = eng
+        self.parked: Dict[int, "tuple[torch.Tensor, List[int]]"] = {}
+        self.bytes = 0
+        self.limit = int(eng.cfg.swap_space_gb * (1 << 30))
+        self.stats = {"swapped_out": 0, "swapped_in": 0, "refused": 0}
+
+    def swap_out(self, req) -> bool:
+        eng = self.eng
+        n = req.num_computed
+        table = eng.blocks.table(req.seq_id)[: eng.blocks.blocks_needed(n)]
+        live = [i for i, b in enumerate(table) if b >= 0]
+        per_block = eng.kv.store[:, :, 0].numel() * eng.kv.store.element_size()
+        if self.bytes + len(live) * per_block > self.limit:
+            self.stats["refused"] += 1
+            return False
+        idx = torch.tensor([table[i] for i in live], dtype=torch.long, device=eng.device)
+        host = eng.kv.store.index_select(2, idx).cpu() if live else eng.kv.store[:, :, :0].cpu()
+        self.parked[req.seq_id] = (host, live)
+        self.bytes += host.numel() * host.element_size()
+        self.stats["swapped_out"] += 1
+        return True
+
+    def swap_in(self, req) -> None:
+        eng = self.eng
+        host, live = self.parked.pop(req.seq_id)
+        self.bytes -= host.numel() * host.element_size()
+        table = eng.blocks.table(req.seq_id)
+        if live:
+            dst = torch.tensor([table[i] for i in live], dtype=torch.long, device=eng.device)
+            eng.kv.store.index_copy_(2, dst, host.to(eng.device, non_blocking=False))
+        self.stats["swapped_in"] += 1
+
+    def drop(self, req) -> None:
+        ent = self.parked.pop(req.seq_id, None)
+        if ent is not None:
+            self.bytes -= ent[0].numel() * ent[0].element_size()
 
 
 class _DecodeGraph:

@@ -94,6 +94,7 @@ class Request:
     preemptions: int = 0
     draft: List[int] = field(default_factory=list)   # proposed tokens awaiting verification
     logprobs: List[float] = field(default_factory=list)
+    swapped: bool = False            # preempted with its KV parked in host memory
 
     @property
     def all_tokens(self) -> List[int]:

@@ -55,6 +55,9 @@ class Scheduler:
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []
         self.window = window         # model-wide sliding window (0 when any layer attends fully)
+        # swap preemption: the engine installs an object with swap_out(req) -> bool / swap_in(req) / drop(req)
+        # that moves a request's KV blocks to host memory and back (rust/engine/src/kv_tier.rs)
+        self.swapper = None
         self.stats = {"steps": 0, "preemptions": 0, "scheduled_tokens": 0}
 
     # ------------------------------------------------------------------ queue
@@ -76,6 +79,8 @@ class Scheduler:
             for r in list(q):
                 if r.request_id == request_id:
                     q.remove(r)
+                    if r.swapped and self.swapper is not None:
+                        self.swapper.drop(r)
                     self.blocks.free_seq(r.seq_id)
                     r.status = RequestStatus.ABORTED
                     r.finish_reason = "abort"
@@ -96,9 +101,13 @@ class Scheduler:
             return False
         victim = max(cands, key=lambda r: (r.params.priority, r.arrival))
         self.running.remove(victim)
-        self.blocks.free_seq(victim.seq_id)
-        victim.num_computed = 0
         victim.draft = []
+        if (self.cfg.preemption == "swap" and self.swapper is not None and victim.is_decode
+                and self.swapper.swap_out(victim)):
+            victim.swapped = True                 # KV kept (on the host): nothing to recompute
+        else:
+            victim.num_computed = 0
+        self.blocks.free_seq(victim.seq_id)
         victim.status = RequestStatus.PREEMPTED
         victim.preemptions += 1
         self.waiting.appendleft(victim)
@@ -125,6 +134,8 @@ class Scheduler:
             for r in list(q):
                 if r.deadline_passed(now):
                     q.remove(r)
+                    if r.swapped and self.swapper is not None:
+                        self.swapper.drop(r)
                     self.blocks.free_seq(r.seq_id)
                     r.status = RequestStatus.ABORTED
                     r.finish_reason = "timeout"
@@ -166,7 +177,9 @@ class Scheduler:
             if partial >= cfg.max_partial_prefills:
                 break
             r = self.waiting[0]
-            if r.seq_id not in self.blocks.seqs:
+            if r.swapped and r.seq_id not in self.blocks.seqs:
+                self.blocks.allocate(r.seq_id, [])             # fresh table: the KV comes back from the host
+            elif r.seq_id not in self.blocks.seqs:
                 cached = self.blocks.allocate(r.seq_id, r.all_tokens, self._salt(r))
                 r.num_computed = cached
                 r.num_cached = cached
@@ -186,6 +199,10 @@ class Scheduler:
             self.waiting.popleft()
             r.status = RequestStatus.RUNNING
             self.running.append(r)
+            if r.swapped:
+                self.swapper.swap_in(r)
+                r.swapped = False
+                self.blocks.commit_tokens(r.seq_id, r.all_tokens, r.num_computed, self._salt(r))
             step.seqs.append(ScheduledSeq(r, r.num_computed, n, n == r.remaining))
             budget -= n
             if n < r.remaining:

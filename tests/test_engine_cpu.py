@@ -189,3 +189,25 @@ def test_disaggregated_prefill_then_decode_matches_one_engine():
     blob, _ = a.prefill_only(prompts[1], SamplingParams(max_tokens=4))
     with pytest.raises(ValueError):
         c.import_request(blob)
+
+
+def test_preemption_by_swap_parks_kv_on_the_host_and_keeps_output():
+    """With a pool too small for all sequences, decode sequences that get preempted have their KV copied
+    to host memory and back instead of being recomputed; output must equal the roomy run, the host tier
+    must have been used and must be empty at the end; a zero-byte tier falls back to recompute."""
+    cfg = preset("qwen3-tiny")
+    w = init_random_weights(cfg, "cpu")
+    prompts = _prompts(cfg.vocab_size, (40, 44, 48, 52))
+    mk = lambda blocks, **kw: LLMEngine(cfg, EngineConfig(max_num_batched_tokens=64, max_model_len=128, num_kv_blocks=blocks,
+                                                          enable_prefix_caching=False, watermark=0.0, **kw),
+                                        device="cpu", weights=w)
+    sp = SamplingParams(max_tokens=12)
+    want = mk(64).generate(prompts, sp)
+    tight = mk(13, preemption="swap", swap_space_gb=0.25)
+    assert tight.generate(prompts, sp) == want
+    sw = tight.scheduler.swapper
+    assert sw.stats["swapped_out"] > 0 and sw.stats["swapped_in"] == sw.stats["swapped_out"]
+    assert not sw.parked and sw.bytes == 0
+    none = mk(13, preemption="swap", swap_space_gb=0.0)
+    assert none.generate(prompts, sp) == want
+    assert none.scheduler.swapper.stats["swapped_out"] == 0 and none.scheduler.stats["preemptions"] > 0
