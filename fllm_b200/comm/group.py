@@ -115,6 +115,17 @@ class Group:
         self._wrap(dist.all_to_all_single, rc, counts, group=self.pg)
         tail = tuple(send[0].shape[1:])
         recv = [torch.empty((int(n),) + tail, dtype=send[0].dtype, device=dev) for n in rc.tolist()]
+        if self.deterministic:
+            # gloo has no list all-to-all: pairwise non-blocking sends and receives
+            recv[self.rank].copy_(send[self.rank])
+            ops = []
+            for d in range(self.size):
+                if d != self.rank:
+                    ops.append(dist.P2POp(dist.isend, send[d].contiguous(), self.ranks[d], group=self.pg))
+                    ops.append(dist.P2POp(dist.irecv, recv[d], self.ranks[d], group=self.pg))
+            for w in self._wrap(dist.batch_isend_irecv, ops) if ops else []:
+                self._wrap(w.wait)
+            return recv
         self._wrap(dist.all_to_all, recv, [t.contiguous() for t in send], group=self.pg)
         return recv
 
