@@ -375,12 +375,14 @@ class LLMEngine:
 
     def _async_ok(self) -> bool:
         return (self.cfg.async_scheduling and self.is_cuda and self.cfg.use_cuda_graphs and self.par.pp == 1
+                and hasattr(self.ops, "k")
                 and self.proposer is None)
 
     def _graph_eligible(self, step: ScheduledStep) -> bool:
         # the all-to-all kernels take the call number from the host, which a captured graph would freeze
+        # (the PyTorch reference operators read sizes back to the host, which a capture does not allow)
         return (self.is_cuda and self.cfg.use_cuda_graphs and step.all_decode and self.par.pp == 1
-                and getattr(self.decoder, "ep_a2a", None) is None
+                and hasattr(self.ops, "k") and getattr(self.decoder, "ep_a2a", None) is None
                 and not any(s.verify for s in step.seqs) and self._bucket_for(len(step.seqs)) > 0)
 
     def _precommit(self, fl) -> None:

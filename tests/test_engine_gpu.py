@@ -184,3 +184,10 @@ def test_gpt_oss_checkpoint_keeps_mxfp4_experts_packed_on_the_gpu(tmp_path):
             assert eng.ops.check_status() == 0
     err = (outs[0] - outs[1]).abs().max().item() / (outs[1].abs().max().item() + 1e-6)
     assert err < 0.05, err
+
+
+def test_smoke_entry_point():
+    """The entry point the build check runs on a GPU: tiny prefill + decode through the kernels, compared
+    with the PyTorch reference operators on the same weights (which must stay off the graph path)."""
+    import __graft_entry__ as entry
+    entry.smoke()
