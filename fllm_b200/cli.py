@@ -89,7 +89,7 @@ def cmd_serve(args) -> int:
     eng.warm_up(buckets=[b for b in eng.cfg.graph_buckets if b <= 64])
     serve(eng, tok, args.host, args.port, args.model_name or os.path.basename(args.model), args.api_key, args.log_level,
           tool_parser=args.tool_parser, reasoning_parser=args.reasoning_parser,
-          response_cache_entries=args.response_cache_entries)
+          response_cache_entries=args.response_cache_entries, otlp_endpoint=args.otlp_endpoint)
     return 0
 
 
@@ -97,12 +97,20 @@ def cmd_run(args) -> int:
     from .runtime import SamplingParams
     from .tokenizer import render_chat
     eng, tok = build_engine(args)
+    prof = None
+    if os.environ.get("FLLM_PROFILE", "0") not in ("", "0"):
+        # a CUDA-event pair around every operator call; eager steps only (events cannot sit inside a captured graph)
+        from .utils.telemetry import OpProfiler
+        eng.cfg.use_cuda_graphs = False
+        prof = eng.ops = eng.decoder.ops = OpProfiler(eng.ops)
     text = args.prompt if args.raw else render_chat(getattr(tok, "chat_template", None), [{"role": "user", "content": args.prompt}])
     ids = tok.encode(text, add_bos=True)
     sp = SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
                         seed=args.seed)
     out = eng.generate([ids], sp)[0]
     print(tok.decode(out))
+    if prof is not None:
+        print(prof.table(), file=sys.stderr)
     return 0
 
 
@@ -205,6 +213,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     s.add_argument("--tool-parser", default=None, choices=["hermes", "llama3_json", "mistral"])
     s.add_argument("--reasoning-parser", default=None, choices=["think"])
     s.add_argument("--response-cache-entries", type=int, default=256, help="0 disables the response cache")
+    s.add_argument("--otlp-endpoint", default=os.environ.get("OTEL_EXPORTER_OTLP_ENDPOINT"),
+                   help="export request spans as OTLP/HTTP JSON to <endpoint>/v1/traces")
     s.set_defaults(fn=cmd_serve)
     rt = sub.add_parser("router", help="front several serve processes (data-parallel replicas) with one port")
     rt.add_argument("--replica", action="append", required=True, help="base URL of a replica, e.g. http://127.0.0.1:8001 (repeat)")

@@ -229,7 +229,8 @@ class StopChecker:
 
 def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Optional[str] = None,
                tool_parser: Optional[str] = None, reasoning_parser: Optional[str] = None,
-               response_cache_entries: int = 256, response_cache_ttl_s: float = 600.0) -> FastAPI:
+               response_cache_entries: int = 256, response_cache_ttl_s: float = 600.0,
+               otlp_endpoint: Optional[str] = None) -> FastAPI:
     from .cache import ResponseCache, request_key
     from .parsers import REASONING_PARSERS, TOOL_PARSERS, ReasoningStream, parse_tool_calls, split_reasoning
     if tool_parser and tool_parser not in TOOL_PARSERS:
@@ -239,6 +240,8 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
     metrics = Metrics()
     worker = EngineWorker(engine, metrics)
     rcache = ResponseCache(response_cache_entries, response_cache_ttl_s)
+    from ..utils.telemetry import SpanExporter
+    spans = SpanExporter(otlp_endpoint, service=model_name)
     guided_shared: dict = {}                     # token trie + mask cache, built on first use
 
     @contextlib.asynccontextmanager
@@ -247,6 +250,7 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
             worker.start()
         yield
         worker.stop()
+        spans.shutdown()
 
     app = FastAPI(title="fllm_b200", version=__version__, lifespan=lifespan)
     app.state.worker, app.state.metrics, app.state.engine = worker, metrics, engine
@@ -285,14 +289,20 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
         q = worker.submit(asyncio.get_running_loop(), rid, prompt_ids, sp)
         chk = StopChecker(tokenizer, sp.stop)
         t0, first, last = time.monotonic(), True, None
+        span = spans.start_span("llm.request", **{"request.id": rid, "llm.prompt_tokens": len(prompt_ids),
+                                                  "llm.max_tokens": sp.max_tokens, "llm.temperature": float(sp.temperature)})
+        n_out = 0
         try:
             while True:
                 item = await q.get()
                 if item.get("error"):
+                    spans.end_span(span, ok=False, **{"error.message": str(item["error"])})
                     raise HTTPException(item.get("status", 500), item["error"])
                 now = time.monotonic()
+                n_out += len(item["tokens"])
                 if item["tokens"]:
                     if first:
+                        span.event("first_token")
                         metrics.observe("fllm_time_to_first_token_seconds", now - t0)
                         first = False
                     elif last is not None:
@@ -302,14 +312,17 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
                 text = chk.push(toks, item["finished"])
                 if chk.hit and not item["finished"]:
                     worker.abort(rid)
+                    spans.end_span(span, **{"llm.completion_tokens": n_out, "llm.finish_reason": "stop"})
                     yield {"text": text, "tokens": item["tokens"], "finished": True, "reason": "stop"}
                     return
                 yield {"text": text, "tokens": item["tokens"], "finished": item["finished"],
                        "reason": "stop" if chk.hit else item["reason"], "embedding": item.get("embedding")}
                 if item["finished"]:
+                    spans.end_span(span, **{"llm.completion_tokens": n_out, "llm.finish_reason": str(item["reason"])})
                     return
         except (asyncio.CancelledError, GeneratorExit):
             worker.abort(rid)
+            spans.end_span(span, ok=False, **{"llm.completion_tokens": n_out, "llm.finish_reason": "cancelled"})
             raise
 
     async def collect(prompt_ids, sp):
@@ -448,6 +461,10 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
         return {"id": rid, "object": "text_completion", "model": model_name,
                 "choices": [{"index": 0, "text": text, "token_ids": toks, "finish_reason": reason}],
                 "usage": usage(len(blob["prompt"]), len(toks))}
+
+    @app.get("/admin/telemetry")
+    async def admin_telemetry():
+        return spans.stats()
 
     @app.get("/admin/cache")
     async def admin_cache_stats():

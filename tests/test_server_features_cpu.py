@@ -191,3 +191,67 @@ def test_embeddings_routes_return_normalised_last_token_states(client):
     o = client.post("/api/embed", json={"input": "hello"}).json()
     assert max(abs(a - b) for a, b in zip(o["embeddings"][0], vecs[0])) < 1e-5
     assert len(client.post("/api/embeddings", json={"prompt": "hello"}).json()["embedding"]) == len(vecs[0])
+
+
+def test_request_spans_reach_an_otlp_collector_and_failures_stay_out_of_the_serving_path():
+    import http.server
+    import threading
+    from fastapi.testclient import TestClient
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.runtime import LLMEngine
+    from fllm_b200.server.app import create_app
+    from fllm_b200.tokenizer import ByteTokenizer
+    from fllm_b200.utils.telemetry import SpanExporter
+    got = []
+
+    class Collector(http.server.BaseHTTPRequestHandler):
+        def do_POST(self):
+            got.append((self.path, json.loads(self.rfile.read(int(self.headers["Content-Length"])))))
+            self.send_response(200)
+            self.end_headers()
+            self.wfile.write(b"{}")
+
+        def log_message(self, *a):
+            pass
+    srv = http.server.HTTPServer(("127.0.0.1", 0), Collector)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    cfg = preset("qwen3-tiny")
+    cfg.vocab_size = 512
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256, num_kv_blocks=64),
+                    device="cpu", eos_token_id=257)
+    app = create_app(eng, ByteTokenizer(512), "tiny", otlp_endpoint=f"http://127.0.0.1:{srv.server_port}")
+    with TestClient(app) as c:
+        for i in range(3):
+            assert c.post("/v1/completions", json={"prompt": f"span {i}", "max_tokens": 3, "temperature": 0}).status_code == 200
+        assert c.get("/admin/telemetry").json()["enabled"] is True
+    srv.shutdown()                                   # the app's shutdown flushed the exporter before this
+    spans = [s for path, body in got for rs in body["resourceSpans"] for ss in rs["scopeSpans"] for s in ss["spans"]]
+    assert got and got[0][0] == "/v1/traces" and len(spans) == 3
+    s0 = spans[0]
+    assert s0["name"] == "llm.request" and len(s0["traceId"]) == 32 and len(s0["spanId"]) == 16
+    assert int(s0["endTimeUnixNano"]) >= int(s0["startTimeUnixNano"])
+    keys = {a["key"] for a in s0["attributes"]}
+    assert {"llm.prompt_tokens", "llm.completion_tokens", "llm.finish_reason"} <= keys
+    assert any(e["name"] == "first_token" for e in s0["events"])
+    # a dead collector: spans are dropped and counted, nothing raises
+    ex = SpanExporter("http://127.0.0.1:9", batch=2, period_s=0.05)
+    for _ in range(3):
+        ex.end_span(ex.start_span("x"))
+    ex.shutdown()
+    assert ex.exported == 0 and ex.dropped == 3 and ex.failed_posts >= 1
+    off = SpanExporter("")
+    off.end_span(off.start_span("y"))
+    assert not off.enabled and off.q.qsize() == 0
+
+
+def test_operator_profiler_counts_calls_by_operator_and_size():
+    import torch
+    from fllm_b200.ops.reference import RefOps
+    from fllm_b200.utils.telemetry import OpProfiler
+    p = OpProfiler(RefOps())
+    w = torch.randn(8, 16).to(torch.bfloat16)
+    for rows in (4, 4, 200):
+        p.linear(torch.randn(rows, 16).to(torch.bfloat16), w)
+    table = p.table()
+    assert "linear" in table and "<=16" in table and ">128" in table
+    assert [l for l in table.splitlines() if l.startswith("linear") and "<=16" in l][0].split()[2] == "2"
