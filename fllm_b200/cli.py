@@ -211,7 +211,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     s.add_argument("--api-key", default=os.environ.get("FLLM_API_KEY"))
     s.add_argument("--log-level", default="info")
     s.add_argument("--tool-parser", default=None, choices=["hermes", "llama3_json", "mistral"])
-    s.add_argument("--reasoning-parser", default=None, choices=["think"])
+    s.add_argument("--reasoning-parser", default=None, choices=["think", "think_open"])
     s.add_argument("--response-cache-entries", type=int, default=256, help="0 disables the response cache")
     s.add_argument("--otlp-endpoint", default=os.environ.get("OTEL_EXPORTER_OTLP_ENDPOINT"),
                    help="export request spans as OTLP/HTTP JSON to <endpoint>/v1/traces")

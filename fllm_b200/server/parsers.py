@@ -1,9 +1,9 @@
 """Output parsers of the chat API: reasoning blocks and tool calls.
 
 * Reasoning (``--reasoning-parser``): ``think`` splits ``<think> ... </think>`` off the front of the
-  answer into ``reasoning_content`` (DeepSeek-R1 / Qwen3 style; an opening tag supplied by the chat
-  template, so that the model only writes the closing one, is handled too). ``ReasoningStream`` is
-  the incremental form used while streaming.
+  answer into ``reasoning_content`` (DeepSeek-R1 / Qwen3 style); ``think_open`` is for chat templates
+  that already end with the opening tag, so that the model only writes the closing one.
+  ``ReasoningStream`` is the incremental form used while streaming; both forms give the same split.
 * Tool calls (``--tool-parser``): ``hermes`` (``<tool_call>{json}</tool_call>``, Qwen / Hermes),
   ``llama3_json`` (the whole answer, or what follows ``<|python_tag|>``, is
   ``{"name": ..., "parameters": {...}}``, several separated by ``;``), ``mistral``
@@ -18,20 +18,20 @@ import re
 import uuid
 from typing import List, Optional, Tuple
 
-REASONING_PARSERS = ("think",)
+REASONING_PARSERS = ("think", "think_open")
 TOOL_PARSERS = ("hermes", "llama3_json", "mistral")
 
 
 # ------------------------------------------------------------------------------ reasoning
 def split_reasoning(text: str, style: str = "think") -> Tuple[Optional[str], str]:
     """-> (reasoning or None, answer)."""
-    if style != "think":
+    if style not in REASONING_PARSERS:
         raise ValueError(f"unknown reasoning parser {style!r}")
     open_t, close_t = "<think>", "</think>"
     body = text
     if body.lstrip().startswith(open_t):
         body = body.lstrip()[len(open_t):]
-    elif close_t not in body:
+    elif style != "think_open":
         return None, text
     if close_t not in body:
         return body.strip() or None, ""            # the budget ran out inside the block
@@ -43,12 +43,13 @@ class ReasoningStream:
     """Feed text pieces, get (reasoning_delta, content_delta) pairs. Holds back a tail that could be
     the beginning of a tag so that tags split across pieces are still recognised."""
 
-    def __init__(self, style: str = "think", starts_in_reasoning: bool = False):
-        if style != "think":
+    def __init__(self, style: str = "think"):
+        if style not in REASONING_PARSERS:
             raise ValueError(f"unknown reasoning parser {style!r}")
         self.open_t, self.close_t = "<think>", "</think>"
-        self.in_reasoning = starts_in_reasoning
-        self.decided = starts_in_reasoning          # whether the opening tag question is settled
+        self.in_reasoning = False
+        self.decided = False                        # whether the opening tag question is settled
+        self.assume_open = style == "think_open"    # no opening tag seen: the template supplied it
         self.strip_nl = False                       # drop the newlines that follow the closing tag
         self.buf = ""
 
@@ -71,6 +72,7 @@ class ReasoningStream:
                 if self.open_t.startswith(s) and not final:
                     break                            # could still become the opening tag
                 self.decided = True
+                self.in_reasoning = self.assume_open
                 continue
             if self.in_reasoning:
                 i = self.buf.find(self.close_t)

@@ -96,10 +96,10 @@ def test_tool_parsers_never_raise_and_keep_text_when_nothing_parses(text, style)
 
 
 @FAST
-@given(st.text(alphabet="<>/think \nab", max_size=80), st.integers(1, 9))
-def test_streaming_reasoning_split_equals_the_one_shot_split(text, cut):
-    r, a = split_reasoning(text)
-    rs = ReasoningStream()
+@given(st.text(alphabet="<>/think \nab", max_size=80), st.integers(1, 9), st.sampled_from(["think", "think_open"]))
+def test_streaming_reasoning_split_equals_the_one_shot_split(text, cut, style):
+    r, a = split_reasoning(text, style)
+    rs = ReasoningStream(style)
     pieces = [text[i:i + cut] for i in range(0, len(text), cut)] or [""]
     rr, cc = "", ""
     for i, p in enumerate(pieces):

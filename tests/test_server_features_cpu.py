@@ -79,7 +79,9 @@ def test_split_reasoning_and_stream_agree():
     r, a = split_reasoning(text)
     assert r == "first, add." and a == "The answer is 4."
     assert split_reasoning("plain answer") == (None, "plain answer")
-    assert split_reasoning("thinking only</think>done") == ("thinking only", "done")
+    assert split_reasoning("thinking only</think>done") == (None, "thinking only</think>done")
+    assert split_reasoning("thinking only</think>done", "think_open") == ("thinking only", "done")
+    assert split_reasoning("<think>a</think>b", "think_open") == ("a", "b")
     for cut in (1, 3, 7, 11):
         rs = ReasoningStream()
         pieces = [text[i:i + cut] for i in range(0, len(text), cut)]
