@@ -13,7 +13,9 @@ from fllm_b200.formats.safetensors_io import SafetensorsError, SafetensorsFile
 from fllm_b200.runtime.grammar import json_complete, json_feed, json_start
 from fllm_b200.server.parsers import ReasoningStream, parse_tool_calls, split_reasoning
 
-FAST = settings(max_examples=150, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture])
+# derandomised: the same examples on every run, so the suite is reproducible; no example database on disk
+FAST = settings(max_examples=150, deadline=None, derandomize=True, database=None,
+                suppress_health_check=[HealthCheck.function_scoped_fixture])
 
 
 @FAST
