@@ -224,6 +224,16 @@ def main(argv: Optional[List[str]] = None) -> int:
     rt.add_argument("--log-level", default="info")
     rt.set_defaults(fn=lambda a: (__import__("fllm_b200.server.router", fromlist=["serve_router"]).serve_router(
         a.replica, a.host, a.port, a.policy, a.log_level), 0)[1])
+    bs = sub.add_parser("bench-serve", help="load a running server over HTTP and report TTFT / ITL / throughput")
+    bs.add_argument("--url", default="http://127.0.0.1:8000")
+    bs.add_argument("--num-prompts", type=int, default=64)
+    bs.add_argument("--concurrency", type=int, default=16)
+    bs.add_argument("--prompt-len", type=int, default=256)
+    bs.add_argument("--max-tokens", type=int, default=64)
+    bs.add_argument("--vocab", type=int, default=1000)
+    bs.set_defaults(fn=lambda a: (print(json.dumps(__import__("fllm_b200.server.bench_serve", fromlist=["main"]).main(
+        a.url, num_prompts=a.num_prompts, concurrency=a.concurrency, prompt_len=a.prompt_len, max_tokens=a.max_tokens,
+        vocab=a.vocab), indent=1)), 0)[1])
     r = sub.add_parser("run", help="generate once from a prompt")
     _add_engine_flags(r)
     r.add_argument("prompt")

@@ -357,11 +357,16 @@ __global__ void __launch_bounds__(128) fa_decode_kernel(const FaParams p) {
   }
 }
 
-// One CTA per (head, token row): combine split partials, add the sink, normalise.
+// One warp per (token row, head): combine split partials, add the sink, normalise.
 template <int D>
-__global__ void fa_merge_kernel(const FaParams p, int T) {
-  const int head = blockIdx.x, tok = blockIdx.y;
-  const size_t base = ((size_t)tok * p.hq + head) * p.splits;
+__global__ void __launch_bounds__(128) fa_merge_kernel(const FaParams p, int T) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pair = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (pair >= T * p.hq) return;
+  const int lane = threadIdx.x & 31;
+  const int tok = pair / p.hq, head = pair - tok * p.hq;
+  const size_t base = (size_t)pair * p.splits;
   float mm = -INFINITY;
   for (int s = 0; s < p.splits; ++s) mm = fmaxf(mm, p.ws_ml[(base + s) * 2]);
   float sk = -INFINITY;
@@ -370,20 +375,23 @@ __global__ void fa_merge_kernel(const FaParams p, int T) {
     mm = fmaxf(mm, sk);
   }
   float ll = p.sinks ? exp2f(sk - mm) : 0.f;
+  constexpr int EPL = D / 32;
+  float a[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) a[e] = 0.f;
   for (int s = 0; s < p.splits; ++s) {
     const float ms = p.ws_ml[(base + s) * 2];
-    ll += ms == -INFINITY ? 0.f : p.ws_ml[(base + s) * 2 + 1] * exp2f(ms - mm);
+    if (ms == -INFINITY) continue;
+    const float w = exp2f(ms - mm);
+    ll += p.ws_ml[(base + s) * 2 + 1] * w;
+    const float* o = p.ws_o + (base + s) * D;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) a[e] += o[lane + 32 * e] * w;
   }
   const float inv = ll > 0.f ? 1.f / ll : 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float a = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
-      const float ms = p.ws_ml[(base + s) * 2];
-      if (ms != -INFINITY) a += p.ws_o[(base + s) * D + d] * exp2f(ms - mm);
-    }
-    p.out[(size_t)tok * p.ldo + (size_t)head * D + d] = __float2bfloat16(a * inv);
-  }
-  (void)T;
+  __nv_bfloat16* dst = p.out + (size_t)tok * p.ldo + (size_t)head * D;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) dst[lane + 32 * e] = __float2bfloat16(a[e] * inv);
 }
 
 // ------------------------------------------------------------------------------ prefill
@@ -565,7 +573,7 @@ static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int mi
     launch_pdl(fa_decode_kernel<D>, grid, dim3(128), DecodeSmem<D>::kTotal, s, p);
     ++launches;
     if (splits > 1) {
-      fa_merge_kernel<D><<<dim3(p.hq, tokens), D < 128 ? D : 128, 0, s>>>(p, tokens);
+      launch_pdl(fa_merge_kernel<D>, dim3((tokens * p.hq + 3) / 4), dim3(128), 0, s, p, tokens);
       ++launches;
     }
   }

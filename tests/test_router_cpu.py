@@ -96,3 +96,15 @@ def test_disaggregated_prefill_and_decode_servers_agree_with_one_server(stack):
     # a blob for another KV layout is refused
     bad = dict(blob, block_size=32)
     assert b.post("/admin/disagg/import", json=bad).status_code == 400
+
+
+def test_bench_serve_load_generator_against_an_in_process_server(stack):
+    import asyncio
+    from fllm_b200.server.bench_serve import run_load
+
+    async def go():
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=stack["a"]), base_url="http://a") as c:
+            return await run_load(c, num_prompts=6, concurrency=3, prompt_len=12, max_tokens=5, vocab=256)
+    rep = asyncio.run(go())
+    assert rep["errors"] == 0 and rep["requests"] == 6
+    assert rep["output_tok_per_s"] > 0 and rep["ttft_ms"]["p50"] is not None and rep["e2e_ms"]["p99"] >= rep["ttft_ms"]["p50"]
