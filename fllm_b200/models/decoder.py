@@ -11,6 +11,7 @@ all-reduce (baseline).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -91,6 +92,8 @@ class Decoder:
                     from ..ops.fp4 import FMT_NAMES, Fp4Weight
                     setattr(lw, name, Fp4Weight(packed[1], packed[2], FMT_NAMES[packed[0]], packed[3] if len(packed) > 3 else 1.0))
         self.capture_hidden, self.last_hidden = False, None
+        # FLLM_NVTX=1: named ranges per layer half for timeline profilers
+        self._nvtx = os.environ.get("FLLM_NVTX", "0") not in ("", "0") and dev.type == "cuda"
         self.ep_a2a = None            # comm.ep_a2a.EpAllToAll when expert parallelism dispatches rows all-to-all
         self._reduced = False
         self._dense_weights = all(isinstance(getattr(lw, n, None), torch.Tensor) for lw in self.w.layers
@@ -142,11 +145,19 @@ class Decoder:
             delta = None
         else:
             x, delta = hidden_in, delta_in
+        nvtx = self._nvtx
         for li, lw in zip(self.layer_range, self.w.layers):
+            if nvtx:
+                torch.cuda.nvtx.range_push(f"layer{li}.attn")
             h = ops.rmsnorm(x, delta, lw.attn_norm, cfg.rms_eps, cfg.norm_weight_offset)
             o = self._reduce(self._attention_block(li, lw, h, b))
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
+                torch.cuda.nvtx.range_push(f"layer{li}.ffn")
             h = ops.rmsnorm(x, o, lw.ffn_norm, cfg.rms_eps, cfg.norm_weight_offset)
             delta = self._reduce(self._ffn_block(lw, h))
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
         return x, delta
 
     # ------------------------------------------------------------------ fused tensor parallel

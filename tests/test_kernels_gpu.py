@@ -552,3 +552,61 @@ def test_moe_with_packed_mxfp4_experts(ops, T, E, k, H, I):
     want = moe_reference(cfg, _dense_experts(lw), h, 0)
     _close(got, want, 3e-2)
     assert ops.check_status() == 0
+
+
+class _Canary:
+    """Tensors carved out of a larger buffer whose margins hold a sentinel: any kernel that stores outside
+    its output shows up as a changed margin (the role a memory checker would play)."""
+    PAD = 4096
+
+    def __init__(self):
+        self.bufs = []
+
+    def empty(self, shape, dtype=torch.bfloat16):
+        n = 1
+        for d in shape:
+            n *= d
+        esz = torch.empty(0, dtype=dtype).element_size()
+        raw = torch.full((n * esz + 2 * self.PAD,), 0xA5, dtype=torch.uint8, device="cuda")
+        self.bufs.append((raw, n * esz))
+        return raw[self.PAD: self.PAD + n * esz].view(dtype).view(*shape)
+
+    def check(self):
+        for raw, nbytes in self.bufs:
+            assert bool((raw[: self.PAD] == 0xA5).all()) and bool((raw[self.PAD + nbytes:] == 0xA5).all()), "out-of-bounds store"
+
+
+@pytest.mark.parametrize("T", [1, 7, 33, 64, 100, 129, 300])
+def test_kernels_never_store_outside_their_outputs(ops, T):
+    """Odd row counts and widths that leave partial tiles, outputs placed between sentinel margins."""
+    from fllm_b200.ops.fp4 import Fp4Weight
+    from fllm_b200.ops.int4 import Int4Weight
+    c = _Canary()
+    N, K = 1000, 320
+    x, w = _rand((T, K), 1), _rand((N, K), 2, 0.05)
+    for splits in (0, 3):
+        ops.linear(x, w, out=c.empty((T, N)), force_splits=splits)
+    ops.linear(x[:, :256].contiguous(), Fp4Weight.from_dense(w[:, :256].contiguous(), "mxfp4"), out=c.empty((T, N)))
+    ops.linear(x[:, :256].contiguous(), Int4Weight.from_dense(w[:, :256].contiguous()), out=c.empty((T, N)))
+    H = 1376
+    y = c.empty((T, H))
+    ops.k.rmsnorm(_rand((T, H), 3), _rand((T, H), 4), _rand((H,), 5), y, 1e-6, 0.0)
+    g = c.empty((T, H // 2))
+    ops.k.glu(_rand((T, H), 6), g, 0, 1.702, 7.0)
+    ids, vals = c.empty((T,), torch.int32), c.empty((T,), torch.float32)
+    ops.k.argmax(_rand((T, 1003), 7), ids, vals, 0)
+    # paged attention + KV write on odd lengths
+    hq, hkv, D, bs, nb = 8, 2, 128, 16, (T + 15) // 16 + 1
+    kc, vc = c.empty((nb, hkv, bs, D)), c.empty((nb, hkv, bs, D))
+    kc.zero_(); vc.zero_()
+    qkv = _rand((T, (hq + 2 * hkv) * D), 8)
+    pos = torch.arange(T, device="cuda", dtype=torch.int32)
+    inv = (10000.0 ** (-torch.arange(0, D, 2, device="cuda").float() / D))
+    ops.rope_kv_write(qkv, pos, pos.clone(), inv, None, None, kc, vc, hq, hkv, D, D, 0, 1e-6, 1.0)
+    out = c.empty((T, hq * D))
+    tables = torch.arange(nb, device="cuda", dtype=torch.int32).view(1, nb)
+    ops.k.attention_generic(qkv[:, : hq * D].contiguous(), kc, vc, tables, torch.zeros(T, device="cuda", dtype=torch.int32),
+                            pos, out, hq, hkv, D, D ** -0.5, 0, None, 0.0)
+    torch.cuda.synchronize()
+    c.check()
+    assert ops.check_status() == 0
