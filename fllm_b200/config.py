@@ -131,7 +131,8 @@ class ModelConfig:
             rms_eps=hf.get("rms_norm_eps", 1e-5), rope_theta=hf.get("rope_theta", 10000.0),
             max_position=hf.get("max_position_embeddings", 8192),
             tie_embeddings=hf.get("tie_word_embeddings", False),
-            qk_norm=(mt in ("qwen3", "qwen3_moe")), attn_bias=hf.get("attention_bias", False),
+            qk_norm=(mt in ("qwen3", "qwen3_moe")),
+            attn_bias=hf.get("attention_bias", mt in ("qwen2", "qwen2_moe")),     # Qwen2 has q/k/v biases without a flag
             name=hf.get("_name_or_path", mt) or mt,
         )
         rs = hf.get("rope_scaling") or {}
@@ -160,6 +161,18 @@ class ModelConfig:
             cfg.num_experts = hf.get("num_local_experts") or hf.get("num_experts")
             cfg.experts_per_token = hf.get("num_experts_per_tok", 2)
             cfg.moe_intermediate_size = hf.get("moe_intermediate_size", cfg.intermediate_size)
+            # Mixtral: softmax over the selected logits. Qwen-MoE: softmax over all experts, then the selected
+            # probabilities renormalised (norm_topk_prob)
+            cfg.router_kind = "softmax_topk" if mt == "mixtral" else "softmax_all"
+        if mt in ("gemma", "gemma2"):
+            cfg.norm_weight_offset = 1.0
+            cfg.embed_scale = float(hidden) ** 0.5
+            cfg.act = "geglu"
+            cfg.tie_embeddings = hf.get("tie_word_embeddings", True)
+            cfg.logit_softcap = float(hf.get("final_logit_softcapping") or 0.0)
+            cfg.attn_softcap = float(hf.get("attn_logit_softcapping") or 0.0)
+        if mt in ("phi3", "phi"):
+            cfg.rotary_dim = int(cfg.head_dim * hf.get("partial_rotary_factor", 1.0)) or None
         if hf.get("sliding_window") and hf.get("use_sliding_window", mt == "mistral"):
             cfg.sliding_window = hf["sliding_window"]
         return cfg

@@ -132,6 +132,8 @@ def _load_moe_layer(cfg, sp, tp_rank, lw, p, get, dev) -> None:
     tensors are taken as they are ([E, in, out] in the checkpoint), MXFP4 `_blocks` / `_scales` pairs
     ([E, out, in/32, 16]) are expanded to bf16. The grouped expert GEMM runs bf16 stacks."""
     from ..models.weights import _cut_gate_up
+    if get(p + "mlp.router.weight", False) is None:
+        return _load_per_expert_moe(cfg, sp, tp_rank, lw, p, get, dev)
     lw.router_w = dev(get(p + "mlp.router.weight"))
     rb = get(p + "mlp.router.bias", False)
     lw.router_b = dev(rb) if rb is not None else None
@@ -171,6 +173,29 @@ def _load_moe_layer(cfg, sp, tp_rank, lw, p, get, dev) -> None:
         lw.exp_gate_up_b = dev(_cut_gate_up(gub, cfg, sp, dim=1)) if gub is not None else None
         if dnb is not None:
             lw.exp_down_b = dev(dnb if tp_rank == 0 else torch.zeros_like(dnb))
+
+
+def _load_per_expert_moe(cfg, sp, tp_rank, lw, p, get, dev) -> None:
+    """Mixtral (`block_sparse_moe.gate`, `experts.N.w1 / w3 / w2`) and Qwen-MoE (`mlp.gate`,
+    `experts.N.gate_proj / up_proj / down_proj`): one tensor per expert and projection, stacked here
+    into [E, 2I, H] (gate rows then up rows) and [E, H, I]."""
+    from ..models.weights import _cut_gate_up
+    if get(p + "block_sparse_moe.gate.weight", False) is not None:
+        base, names, router = p + "block_sparse_moe.", ("w1", "w3", "w2"), "block_sparse_moe.gate.weight"
+    else:
+        base, names, router = p + "mlp.", ("gate_proj", "up_proj", "down_proj"), "mlp.gate.weight"
+    lw.router_w = dev(get(p + router))
+    lw.router_b = None
+    experts = range(sp.expert_start, sp.expert_start + sp.expert_local) if sp.expert_parallel else range(cfg.num_experts)
+    gu = torch.stack([torch.cat([get(f"{base}experts.{e}.{names[0]}.weight"), get(f"{base}experts.{e}.{names[1]}.weight")], 0)
+                      for e in experts])
+    dn = torch.stack([get(f"{base}experts.{e}.{names[2]}.weight") for e in experts])
+    if sp.expert_parallel:
+        lw.exp_gate_up, lw.exp_down = dev(gu), dev(dn)
+    else:
+        lw.exp_gate_up = dev(_cut_gate_up(gu, cfg, sp, dim=1))
+        lw.exp_down = dev(dn[:, :, sp.inter_start: sp.inter_start + sp.inter_local])
+    lw.exp_gate_up_b = lw.exp_down_b = None
 
 
 def load_gguf(path: str, device="cuda", tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16, keep_packed: bool = True):

@@ -252,3 +252,84 @@ def test_gpt_oss_checkpoint_with_mxfp4_experts_loads(tmp_path):
                     device="cpu", weights=w2)
     out = eng.generate([[5, 6, 7, 8, 9]], SamplingParams(max_tokens=4))
     assert len(out[0]) == 4
+
+
+def _write_llama_like(tmp_path, cfg, w, hf_extra, moe_style=None):
+    """HF-style directory for a llama-like (optionally per-expert MoE) model from single-rank weights."""
+    import json
+    from fllm_b200.formats.safetensors_io import save_file
+    D, hq, hkv, H = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads, cfg.hidden_size
+    t = {"model.embed_tokens.weight": w.embed, "model.norm.weight": w.final_norm}
+    if not cfg.tie_embeddings:
+        t["lm_head.weight"] = w.lm_head
+    for l, lw in enumerate(w.layers):
+        p = f"model.layers.{l}."
+        t.update({p + "input_layernorm.weight": lw.attn_norm, p + "post_attention_layernorm.weight": lw.ffn_norm,
+                  p + "self_attn.q_proj.weight": lw.wqkv[: hq * D], p + "self_attn.k_proj.weight": lw.wqkv[hq * D: (hq + hkv) * D],
+                  p + "self_attn.v_proj.weight": lw.wqkv[(hq + hkv) * D:], p + "self_attn.o_proj.weight": lw.wo})
+        if cfg.attn_bias:
+            t.update({p + "self_attn.q_proj.bias": lw.bqkv[: hq * D], p + "self_attn.k_proj.bias": lw.bqkv[hq * D: (hq + hkv) * D],
+                      p + "self_attn.v_proj.bias": lw.bqkv[(hq + hkv) * D:]})
+        if cfg.qk_norm:
+            t.update({p + "self_attn.q_norm.weight": lw.q_norm, p + "self_attn.k_norm.weight": lw.k_norm})
+        if moe_style:
+            I = cfg.moe_intermediate_size
+            base, names, router = ((p + "block_sparse_moe.", ("w1", "w3", "w2"), "block_sparse_moe.gate.weight") if moe_style == "mixtral"
+                                   else (p + "mlp.", ("gate_proj", "up_proj", "down_proj"), "mlp.gate.weight"))
+            t[p + router] = lw.router_w
+            for e in range(cfg.num_experts):
+                t[f"{base}experts.{e}.{names[0]}.weight"] = lw.exp_gate_up[e, :I]
+                t[f"{base}experts.{e}.{names[1]}.weight"] = lw.exp_gate_up[e, I:]
+                t[f"{base}experts.{e}.{names[2]}.weight"] = lw.exp_down[e]
+        else:
+            I = cfg.intermediate_size
+            t.update({p + "mlp.gate_proj.weight": lw.w_gate_up[:I], p + "mlp.up_proj.weight": lw.w_gate_up[I:],
+                      p + "mlp.down_proj.weight": lw.w_down})
+    save_file({k: v.contiguous() for k, v in t.items()}, str(tmp_path / "model.safetensors"))
+    hf = {"vocab_size": cfg.vocab_size, "hidden_size": H, "num_hidden_layers": cfg.num_layers, "num_attention_heads": hq,
+          "num_key_value_heads": hkv, "head_dim": D, "intermediate_size": cfg.intermediate_size, "rms_norm_eps": cfg.rms_eps,
+          "rope_theta": cfg.rope_theta, "max_position_embeddings": 4096, "tie_word_embeddings": cfg.tie_embeddings}
+    hf.update(hf_extra)
+    json.dump(hf, open(tmp_path / "config.json", "w"))
+
+
+@pytest.mark.parametrize("family", ["mixtral", "qwen3_moe", "qwen2", "gemma"])
+def test_model_families_load_from_hf_style_checkpoints(tmp_path, family):
+    """Per-expert MoE layouts (Mixtral, Qwen-MoE), implicit q/k/v biases (Qwen2) and Gemma's conventions
+    (1 + w norms, scaled embeddings, GeGLU, tied head) map onto the one decoder and reproduce the
+    generation of the weights they were written from."""
+    import torch
+    from fllm_b200.config import EngineConfig, ModelConfig
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    from fllm_b200.models.weights import init_random_weights
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    base = dict(vocab_size=512, hidden_size=128, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=32,
+                intermediate_size=192, rms_eps=1e-6, rope_theta=10000.0)
+    if family == "mixtral":
+        cfg = ModelConfig(**base, num_experts=4, experts_per_token=2, moe_intermediate_size=192, router_kind="softmax_topk")
+        extra, style = {"model_type": "mixtral", "num_local_experts": 4, "num_experts_per_tok": 2}, "mixtral"
+    elif family == "qwen3_moe":
+        cfg = ModelConfig(**base, arch="qwen3", qk_norm=True, num_experts=4, experts_per_token=2, moe_intermediate_size=96,
+                          router_kind="softmax_all")
+        extra, style = {"model_type": "qwen3_moe", "num_experts": 4, "num_experts_per_tok": 2, "moe_intermediate_size": 96}, "qwen"
+    elif family == "qwen2":
+        cfg = ModelConfig(**base, attn_bias=True)
+        extra, style = {"model_type": "qwen2"}, None
+    else:
+        cfg = ModelConfig(**base, act="geglu", norm_weight_offset=1.0, embed_scale=128 ** 0.5, tie_embeddings=True)
+        extra, style = {"model_type": "gemma"}, None
+    w = init_random_weights(cfg, device="cpu", seed=9)
+    for lw in w.layers:
+        lw.bo = None                       # none of these families has an o_proj bias
+    _write_llama_like(tmp_path, cfg, w, extra, style)
+    cfg2, w2, _ = load_hf_checkpoint(str(tmp_path), device="cpu")
+    for field in ("num_experts", "experts_per_token", "router_kind", "attn_bias", "qk_norm", "act", "norm_weight_offset",
+                  "tie_embeddings"):
+        assert getattr(cfg2, field) == getattr(cfg, field), field
+    assert abs(cfg2.embed_scale - cfg.embed_scale) < 1e-6
+    if style:
+        assert torch.equal(w2.layers[1].exp_gate_up, w.layers[1].exp_gate_up) and torch.equal(w2.layers[0].exp_down, w.layers[0].exp_down)
+    ec = EngineConfig(max_num_seqs=2, max_num_batched_tokens=32, max_model_len=64, num_kv_blocks=16)
+    prompt = [[3, 1, 4, 1, 5, 9, 2, 6]]
+    sp = SamplingParams(max_tokens=6)
+    assert LLMEngine(cfg2, ec, device="cpu", weights=w2).generate(prompt, sp) == LLMEngine(cfg, ec, device="cpu", weights=w).generate(prompt, sp)
