@@ -106,6 +106,8 @@ def main() -> None:
     ap.add_argument("--backend", default=os.environ.get("FLLM_TP_BACKEND", "auto"),
                     help="tensor-parallel collectives: auto | fused | nccl")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--profile-prefill", action="store_true",
+                    help="bracket the third 2048-token prefill step with cudaProfilerStart/Stop and exit after the prefill")
     ap.add_argument("--profile-step", action="store_true",
                     help="bracket ONE replay of the decode step with cudaProfilerStart/Stop (for a profiler's "
                          "launch list, run with --profile-from-start off) and exit")
@@ -167,14 +169,28 @@ def main() -> None:
     t_wall = time.perf_counter()
     e0.record()
     ttft = None
+    n_prefill_steps = 0
     while any(not r.output for r in eng.requests.values()):
+        mark = args.profile_prefill and n_prefill_steps == 2
+        if mark:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
         eng.step()
+        if mark:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        n_prefill_steps += 1
         if ttft is None and any(r.output for r in eng.requests.values()):
             ttft = time.perf_counter() - t_wall
     e1.record()
     sync_all()
     prefill_ms = max_over_ranks(e0.elapsed_time(e1))
     prefill_tok_s = args.batch * args.prompt_len / (prefill_ms / 1e3)
+    if args.profile_prefill:
+        if rank == 0:
+            print(json.dumps({"profiled_prefill_step": 2, "prefill_steps": n_prefill_steps, "prefill_tok_s": prefill_tok_s}))
+        eng.close()
+        return
 
     # ---- warm-up decode steps (captures the graph)
     for _ in range(args.warmup):
