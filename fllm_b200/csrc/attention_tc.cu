@@ -395,18 +395,20 @@ __global__ void __launch_bounds__(128) fa_merge_kernel(const FaParams p, int T) 
 }
 
 // ------------------------------------------------------------------------------ prefill
-template <int D>
+template <int D, int R = 64>
 struct PrefillSmem {
-  static constexpr int kRows = 64;           // packed query rows per CTA
+  static constexpr int kRows = R;            // packed query rows per CTA: 16 per warp (64 -> 4 warps, 128 -> 8 warps
+                                             // sharing every K/V tile, which halves the K/V traffic per FLOP)
+  static constexpr int kThreads = 2 * R;
   static constexpr int kTile = 64;           // KV tokens per tile
   static constexpr int kQBytes = kRows * D * 2;
   static constexpr int kKvBytes = 2 * 2 * kTile * D * 2;   // 2 stages x (K, V)
   static constexpr int kTotal = kQBytes + kKvBytes + 128;
 };
 
-template <int D>
-__global__ void __launch_bounds__(128) fa_prefill_kernel(const FaParams p) {
-  using S = PrefillSmem<D>;
+template <int D, int R>
+__global__ void __launch_bounds__(2 * R) fa_prefill_kernel(const FaParams p) {
+  using S = PrefillSmem<D, R>;
   extern __shared__ __align__(128) uint8_t smem[];
   __nv_bfloat16* qtile = reinterpret_cast<__nv_bfloat16*>(smem);
   __nv_bfloat16* kv = reinterpret_cast<__nv_bfloat16*>(smem + S::kQBytes);
@@ -429,7 +431,7 @@ __global__ void __launch_bounds__(128) fa_prefill_kernel(const FaParams p) {
   const int tile_lo = lo_tok / S::kTile;
   const int tile_hi = (hi_tok + S::kTile - 1) / S::kTile;
 
-  for (int i = threadIdx.x; i < S::kRows * (D / 8); i += 128) {
+  for (int i = threadIdx.x; i < S::kRows * (D / 8); i += S::kThreads) {
     const int r = i / (D / 8), c = i - r * (D / 8);
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < n_rows) {
@@ -475,11 +477,11 @@ __global__ void __launch_bounds__(128) fa_prefill_kernel(const FaParams p) {
         if (page < n_pages_total) {
           const int blk = table[page];
           const size_t off = ((size_t)blk * p.hkv + kvh) * kPage * D;
-          load_rows_async<D>(ks, pg * kPage, p.k_cache + off, kPage, threadIdx.x, 128);
-          load_rows_async<D>(vs, pg * kPage, p.v_cache + off, kPage, threadIdx.x, 128);
+          load_rows_async<D>(ks, pg * kPage, p.k_cache + off, kPage, threadIdx.x, S::kThreads);
+          load_rows_async<D>(vs, pg * kPage, p.v_cache + off, kPage, threadIdx.x, S::kThreads);
         } else {
           // past the sequence: V rows must be finite because they meet P = 0 in the MMA
-          for (int i = threadIdx.x; i < kPage * (D / 8); i += 128)
+          for (int i = threadIdx.x; i < kPage * (D / 8); i += S::kThreads)
             *reinterpret_cast<uint4*>(vs + (size_t)pg * kPage * D + i * 8) = make_uint4(0, 0, 0, 0);
         }
       }
@@ -543,8 +545,10 @@ static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int mi
   if (!configured) {
     cuda_check(cudaFuncSetAttribute(fa_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     DecodeSmem<D>::kTotal), "fa_decode smem");
-    cuda_check(cudaFuncSetAttribute(fa_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    PrefillSmem<D>::kTotal), "fa_prefill smem");
+    cuda_check(cudaFuncSetAttribute(fa_prefill_kernel<D, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    PrefillSmem<D, 64>::kTotal), "fa_prefill smem");
+    cuda_check(cudaFuncSetAttribute(fa_prefill_kernel<D, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    PrefillSmem<D, 128>::kTotal), "fa_prefill smem");
     configured = true;
   }
   int launches = 0;
@@ -578,11 +582,18 @@ static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int mi
     }
   }
   if (max_q_len > decode_max_q) {
-    const int rq = PrefillSmem<D>::kRows / p.group;
+    // FLLM_FA_PREFILL_ROWS=128 selects 128 packed rows per CTA (8 warps sharing every K/V tile). Measured equal to
+    // the 64-row tile (119 vs 121 TFLOP/s at 2 x 1024 tokens): the kernel is bound by the mma.sync / softmax
+    // pipeline of each warp, not by K/V traffic, so the smaller tile stays the default.
+    static int rows_pref = -1;
+    if (rows_pref < 0) { const char* e = getenv("FLLM_FA_PREFILL_ROWS"); rows_pref = e ? atoi(e) : 64; }
+    const bool big = rows_pref >= 128 && max_q_len * p.group >= 128;
+    const int rq = (big ? 128 : 64) / p.group;
     if (rq < 1) throw std::runtime_error("attention_tc: more than 64 query heads per KV head");
     dim3 grid((max_q_len + rq - 1) / rq, p.hkv, num_seqs);
     p.splits = 1;
-    fa_prefill_kernel<D><<<grid, 128, PrefillSmem<D>::kTotal, s>>>(p);
+    if (big) fa_prefill_kernel<D, 128><<<grid, 256, PrefillSmem<D, 128>::kTotal, s>>>(p);
+    else fa_prefill_kernel<D, 64><<<grid, 128, PrefillSmem<D, 64>::kTotal, s>>>(p);
     ++launches;
   }
   cuda_check(cudaGetLastError(), "attention_tc launch");
