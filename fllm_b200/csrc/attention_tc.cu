@@ -49,6 +49,8 @@ struct FaParams {
   float softcap;         // 0 = off (applied to scale * s, before the exp)
   float scale;
   int decode_max_q;      // sequences with more query rows than this belong to the prefill kernel
+  long long num_kv_blocks;
+  int* status;
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -581,7 +583,17 @@ static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int mi
       ++launches;
     }
   }
-  if (max_q_len > decode_max_q) {
+  // Prefill tiles of at least 128 packed rows run on tcgen05 with tensor-memory accumulators; FLLM_FA_TMEM=0
+  // keeps the mma.sync kernel below for every shape.
+  static int use_tmem = -1;
+  if (use_tmem < 0) { const char* e = getenv("FLLM_FA_TMEM"); use_tmem = e ? atoi(e) : 1; }
+  if (max_q_len > decode_max_q && use_tmem && p.num_kv_blocks > 0 && max_q_len * p.group >= 128 &&
+      attention_prefill_tmem_supported(D, p.group, kPage)) {
+    attention_prefill_tmem(p.q, p.ldq, p.k_cache, p.v_cache, p.num_kv_blocks, p.block_tables, p.max_blocks, p.q_starts,
+                           p.kv_lens, p.out, p.ldo, num_seqs, max_q_len, decode_max_q + 1, p.hq, p.hkv, p.scale,
+                           p.window, p.sinks, p.softcap, p.status, s);
+    ++launches;
+  } else if (max_q_len > decode_max_q) {
     // FLLM_FA_PREFILL_ROWS=128 selects 128 packed rows per CTA (8 warps sharing every K/V tile). Measured equal to
     // the 64-row tile (119 vs 121 TFLOP/s at 2 x 1024 tokens): the kernel is bound by the mma.sync / softmax
     // pipeline of each warp, not by K/V traffic, so the smaller tile stays the default.
@@ -605,7 +617,7 @@ int attention_tc_bf16(const void* q, long long ldq, const void* k_cache, const v
                       void* out, long long ldo, int tokens, int num_seqs, int max_q_len, int min_q_len,
                       int max_kv_len, int hq, int hkv, int head_dim, int block_size, float scale,
                       int window, const float* sinks, float softcap, void* workspace,
-                      size_t workspace_bytes, cudaStream_t s) {
+                      size_t workspace_bytes, cudaStream_t s, long long num_kv_blocks, int* status) {
   if (tokens <= 0 || num_seqs <= 0) return 0;
   if (block_size != kPage) throw std::runtime_error("attention_tc: KV block size must be 16");
   if (hq % hkv) throw std::runtime_error("attention_tc: hq must be a multiple of hkv");
@@ -616,6 +628,7 @@ int attention_tc_bf16(const void* q, long long ldq, const void* k_cache, const v
   p.q_starts = q_starts; p.kv_lens = kv_lens;
   p.out = (__nv_bfloat16*)out; p.ldo = ldo;
   p.sinks = sinks;
+  p.num_kv_blocks = num_kv_blocks; p.status = status;
   p.hq = hq; p.hkv = hkv; p.group = hq / hkv;
   p.window = window;
   p.scale = scale;

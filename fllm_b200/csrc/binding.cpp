@@ -138,7 +138,8 @@ int64_t attention_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_cac
                      const Tensor& block_tables, const Tensor& q_starts, const Tensor& kv_lens, Tensor out,
                      int64_t num_seqs, int64_t max_q_len, int64_t min_q_len, int64_t max_kv_len, int64_t hq,
                      int64_t hkv, int64_t head_dim, double scale, int64_t window,
-                     const optional<Tensor>& sinks, double softcap, const optional<Tensor>& workspace) {
+                     const optional<Tensor>& sinks, double softcap, const optional<Tensor>& workspace,
+                     const optional<Tensor>& status) {
   check_bf16(q, "q"); check_rows(q, "q"); check_bf16(out, "out"); check_rows(out, "out");
   check_bf16(k_cache, "k_cache"); check_bf16(v_cache, "v_cache");
   check_i32(q_starts, "q_starts"); check_i32(kv_lens, "kv_lens");
@@ -156,7 +157,8 @@ int64_t attention_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_cac
                                  out.stride(0), (int)q.size(0), (int)num_seqs, (int)max_q_len,
                                  (int)min_q_len, (int)max_kv_len, (int)hq, (int)hkv, (int)head_dim,
                                  (int)k_cache.size(2), (float)scale, (int)window, opt_ptr<float>(sinks),
-                                 (float)softcap, ws, ws_bytes, cur_stream());
+                                 (float)softcap, ws, ws_bytes, cur_stream(), (long long)k_cache.size(0),
+                                 const_cast<int*>(opt_ptr<int>(status)));
 }
 
 void argmax(const Tensor& logits, Tensor out_ids, const optional<Tensor>& out_vals,
@@ -245,7 +247,7 @@ TORCH_LIBRARY(fllm_b200, m) {
   m.def("glu(Tensor x, Tensor(a!) out, int act_kind, float alpha, float limit) -> ()", &glu);
   m.def("gather_rows(Tensor x, Tensor rows, Tensor(a!) out) -> ()", &gather_rows);
   m.def("attention_generic(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor row_seq, Tensor positions, Tensor(a!) out, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap) -> ()", &attention_generic);
-  m.def("attention_tc(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor q_starts, Tensor kv_lens, Tensor(a!) out, int num_seqs, int max_q_len, int min_q_len, int max_kv_len, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap, Tensor? workspace) -> int", &attention_tc);
+  m.def("attention_tc(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor q_starts, Tensor kv_lens, Tensor(a!) out, int num_seqs, int max_q_len, int min_q_len, int max_kv_len, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap, Tensor? workspace, Tensor? status=None) -> int", &attention_tc);
   m.def("argmax(Tensor logits, Tensor(a!) out_ids, Tensor? out_vals, int id_offset) -> ()", &argmax);
   m.def("sample(Tensor(a!) logits, Tensor params, Tensor? pen_ids, Tensor? pen_counts, Tensor? bias_ids, Tensor? bias_vals, Tensor? allow_mask, Tensor(b!) out_ids, Tensor? out_logprobs) -> ()", &sample);
   m.def("spec_verify_greedy(Tensor draft_ids, Tensor target_ids, Tensor? n_draft, Tensor(a!) n_accept, Tensor(b!) out_tokens) -> ()", &spec_verify_greedy);

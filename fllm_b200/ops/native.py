@@ -87,7 +87,7 @@ class NativeOps:
             self.launches += self.k.attention_tc(
                 q, k_cache, v_cache, block_tables, meta.q_starts, meta.seq_lens, out, meta.num_seqs,
                 meta.max_q_len, meta.min_q_len, meta.max_kv_len, hq, hkv, head_dim, float(scale),
-                int(window), sinks, float(softcap), self.attn_ws)
+                int(window), sinks, float(softcap), self.attn_ws, self.status)
             return out
         self.k.attention_generic(q, k_cache, v_cache, block_tables, row_seq, positions, out, hq, hkv,
                                  head_dim, float(scale), int(window), sinks, float(softcap))

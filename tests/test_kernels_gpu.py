@@ -241,6 +241,48 @@ def test_attention_tc(ops, ref, D, hq, hkv, window, sinks, softcap, case):
     _close(yg, yr, 2e-2)
 
 
+@pytest.mark.parametrize("hq,hkv", [(8, 8), (8, 2), (16, 2), (32, 8), (16, 1)])
+@pytest.mark.parametrize("window,sinks,softcap", [(0, False, 0.0), (150, True, 0.0), (0, False, 30.0)])
+def test_attention_prefill_on_tensor_memory(ops, ref, hq, hkv, window, sinks, softcap):
+    """Prompts long enough for several 128-token KV tiles and several 128-row query tiles per sequence go
+    through the tcgen05 prefill kernel (head_dim 128): chunk continuation (kv > q), a ragged tail, causal
+    diagonal tiles, sliding window, sinks and soft capping against the fp32 reference; status stays 0."""
+    D = 128
+    kv_lens, q_lens = [1000, 520, 300, 131], [1000, 200, 300, 40]
+    tables, kc, vc = _paged_setup(len(kv_lens), kv_lens, hkv, D, seed=11)
+    T = sum(q_lens)
+    row_seq = torch.tensor([i for i, n in enumerate(q_lens) for _ in range(n)], dtype=torch.int32, device="cuda")
+    pos = torch.tensor([kv - n + j for kv, n in zip(kv_lens, q_lens) for j in range(n)], dtype=torch.int32, device="cuda")
+    q = _rand((T, hq * D), 7)
+    sk = torch.randn(hq, device="cuda") if sinks else None
+    meta = _tc_meta(q_lens, kv_lens)
+    y = ops.attention(q, kc, vc, tables, row_seq, pos, hq, hkv, D, D ** -0.5, window, sk, softcap, meta=meta)
+    yr = torch.empty_like(y)
+    o = 0
+    for i, (n, kv) in enumerate(zip(q_lens, kv_lens)):          # fp32 reference, one dense sequence at a time
+        blocks = tables[i, :(kv + 15) // 16].long()
+        k = kc[blocks].float().permute(1, 0, 2, 3).reshape(hkv, -1, D)[:, :kv].repeat_interleave(hq // hkv, 0)
+        v = vc[blocks].float().permute(1, 0, 2, 3).reshape(hkv, -1, D)[:, :kv].repeat_interleave(hq // hkv, 0)
+        qs = q[o:o + n].float().view(n, hq, D).permute(1, 0, 2)
+        sc = torch.einsum("hqd,hkd->hqk", qs, k) * D ** -0.5
+        if softcap > 0:
+            sc = softcap * torch.tanh(sc / softcap)
+        qpos = torch.arange(kv - n, kv, device="cuda")[:, None]
+        kpos = torch.arange(kv, device="cuda")[None, :]
+        hide = kpos > qpos
+        if window > 0:
+            hide = hide | (kpos <= qpos - window)
+        sc = sc.masked_fill(hide[None], float("-inf"))
+        if sk is not None:
+            pr = torch.softmax(torch.cat([sc, sk.float()[:, None, None].expand(hq, n, 1)], -1), -1)[..., :-1]
+        else:
+            pr = torch.softmax(sc, -1)
+        yr[o:o + n] = torch.einsum("hqk,hkd->qhd", pr, v).reshape(n, hq * D).to(y.dtype)
+        o += n
+    _close(y, yr, 2e-2)
+    assert ops.check_status() == 0
+
+
 @pytest.mark.parametrize("tp,T", [(2, 64), (4, 13), (8, 64), (8, 5), (4, 300), (2, 2048)])
 def test_fused_tp_chain_single_device_emulation(tp, T):
     """GEMM->reduce-scatter, reduce+norm+all-gather and all-gather->GEMM for `tp` virtual ranks on
