@@ -53,6 +53,7 @@ struct FaTmemParams {
   int window;
   int min_q;             // sequences with fewer query rows are not this kernel's
   float scale_log2, softcap, scale;
+  int pv_wide;           // one N=128 MMA per 16 tokens instead of two N=64 ones
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -64,10 +65,10 @@ __device__ __forceinline__ float ex2(float x) {
 // Shared-memory descriptor of an operand stored as 128-byte swizzled rows with 1024 bytes between
 // groups of eight rows, in either major-ness. For the MN-major use (V) every MMA covers one 64-wide
 // swizzle atom along N, so both offset fields describe the same stride: eight K rows = 1024 bytes.
-__device__ __forceinline__ uint64_t smem_desc_sw128_1k(uint32_t saddr) {
+__device__ __forceinline__ uint64_t smem_desc_sw128_1k(uint32_t saddr, uint32_t lbo_bytes = 1024) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)(1024 >> 4) << 16;
+  d |= (uint64_t)(lbo_bytes >> 4) << 16;
   d |= (uint64_t)(1024 >> 4) << 32;
   d |= (uint64_t)1 << 46;
   d |= (uint64_t)2 << 61;
@@ -77,25 +78,39 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_1k(uint32_t saddr) {
 // One row (thread) of the softmax over one 128-token tile: reads S from tensor memory, updates the row's
 // reference maximum and sum, writes P as bf16 over S's first 64 columns and, when the maximum of any row of
 // the warp moved by more than 2^8, rescales the warp's rows of O. `t_s` / `t_o` already carry the lane offset.
-__device__ __forceinline__ void softmax_tile(const FaTmemParams& p, uint32_t t_s, uint32_t t_o, int tok0, int lim,
-                                             int beg, bool full, bool have_o, float& m_used, float& l) {
-  const float cap_in = p.softcap > 0.f ? p.scale / p.softcap : 0.f;
+template <bool full, bool capped>
+__device__ __forceinline__ void softmax_tile_impl(const FaTmemParams& p, uint32_t t_s, uint32_t t_o, int tok0, int lim,
+                                                  int beg, bool have_o, float& m_used, float& l) {
+  const float cap_in = capped ? p.scale / p.softcap : 0.f;
   const float cap_out = p.softcap * kLog2eT;
-  uint32_t sreg[32];
-  float mx = -INFINITY;
+  // One warp per lane quarter runs this alone on its scheduler, so the instruction stream is written for
+  // instruction-level parallelism: 64 columns per tensor-memory round trip, four independent max / sum chains.
+  uint32_t sa[32], sb[32];
+  float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
-    tmem_ld_32x32(t_s + 32 * c, sreg);
+  for (int h = 0; h < 2; ++h) {
+    tmem_ld_32x32(t_s + 64 * h, sa);
+    tmem_ld_32x32(t_s + 64 * h + 32, sb);
     tmem_ld_wait();
+    const int t0 = tok0 + 64 * h;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      float s = __uint_as_float(sreg[i]);
-      s = p.softcap > 0.f ? cap_out * tanhf(s * cap_in) : s * p.scale_log2;
-      const int t = tok0 + 32 * c + i;
-      if (!full && (t >= lim || t < beg)) s = -INFINITY;
-      mx = fmaxf(mx, s);
+    for (int i = 0; i < 32; i += 2) {
+      float a0 = __uint_as_float(sa[i]), a1 = __uint_as_float(sa[i + 1]);
+      float b0 = __uint_as_float(sb[i]), b1 = __uint_as_float(sb[i + 1]);
+      if (capped) {
+        a0 = tanhf(a0 * cap_in); a1 = tanhf(a1 * cap_in); b0 = tanhf(b0 * cap_in); b1 = tanhf(b1 * cap_in);
+      }
+      if (!full) {
+        if (t0 + i >= lim || t0 + i < beg) a0 = -INFINITY;
+        if (t0 + i + 1 >= lim || t0 + i + 1 < beg) a1 = -INFINITY;
+        if (t0 + 32 + i >= lim || t0 + 32 + i < beg) b0 = -INFINITY;
+        if (t0 + 33 + i >= lim || t0 + 33 + i < beg) b1 = -INFINITY;
+      }
+      mx0 = fmaxf(mx0, a0); mx1 = fmaxf(mx1, a1); mx2 = fmaxf(mx2, b0); mx3 = fmaxf(mx3, b1);
     }
   }
+  // the scale is positive, so it commutes with the maximum
+  const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * (capped ? cap_out : p.scale_log2);
   // a row keeps its old reference maximum unless the new one is far above it; the decision is per
   // warp because the tensor memory accesses of the rescale are warp-wide
   const bool grow = mx > m_used + kLazyRescale || (m_used == -INFINITY && mx > -INFINITY);
@@ -108,48 +123,65 @@ __device__ __forceinline__ void softmax_tile(const FaTmemParams& p, uint32_t t_s
     l *= corr;
   }
   const float m_ref = m_used == -INFINITY ? 0.f : m_used;
-  float sum = 0.f;
+  float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
-    tmem_ld_32x32(t_s + 32 * c, sreg);
+  for (int h = 0; h < 2; ++h) {
+    tmem_ld_32x32(t_s + 64 * h, sa);
+    tmem_ld_32x32(t_s + 64 * h + 32, sb);
     tmem_ld_wait();
-    uint32_t pk[16];
+    const int t0 = tok0 + 64 * h;
+    uint32_t pa[16], pb[16];
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
-      float s0 = __uint_as_float(sreg[i]), s1 = __uint_as_float(sreg[i + 1]);
-      if (p.softcap > 0.f) {
-        s0 = cap_out * tanhf(s0 * cap_in) - m_ref;
-        s1 = cap_out * tanhf(s1 * cap_in) - m_ref;
+      float a0 = __uint_as_float(sa[i]), a1 = __uint_as_float(sa[i + 1]);
+      float b0 = __uint_as_float(sb[i]), b1 = __uint_as_float(sb[i + 1]);
+      if (capped) {
+        a0 = fmaf(cap_out, tanhf(a0 * cap_in), -m_ref); a1 = fmaf(cap_out, tanhf(a1 * cap_in), -m_ref);
+        b0 = fmaf(cap_out, tanhf(b0 * cap_in), -m_ref); b1 = fmaf(cap_out, tanhf(b1 * cap_in), -m_ref);
       } else {
-        s0 = fmaf(s0, p.scale_log2, -m_ref);
-        s1 = fmaf(s1, p.scale_log2, -m_ref);
+        a0 = fmaf(a0, p.scale_log2, -m_ref); a1 = fmaf(a1, p.scale_log2, -m_ref);
+        b0 = fmaf(b0, p.scale_log2, -m_ref); b1 = fmaf(b1, p.scale_log2, -m_ref);
       }
-      const int t = tok0 + 32 * c + i;
-      float p0 = ex2(s0), p1 = ex2(s1);
+      a0 = ex2(a0); a1 = ex2(a1); b0 = ex2(b0); b1 = ex2(b1);
       if (!full) {
-        if (t >= lim || t < beg) p0 = 0.f;
-        if (t + 1 >= lim || t + 1 < beg) p1 = 0.f;
+        if (t0 + i >= lim || t0 + i < beg) a0 = 0.f;
+        if (t0 + i + 1 >= lim || t0 + i + 1 < beg) a1 = 0.f;
+        if (t0 + 32 + i >= lim || t0 + 32 + i < beg) b0 = 0.f;
+        if (t0 + 33 + i >= lim || t0 + 33 + i < beg) b1 = 0.f;
       }
-      const uint32_t u = pack_bf16x2(p0, p1);
-      const float2 back = unpack_bf16x2(u);        // the sum follows the values the MMA multiplies
-      sum += back.x + back.y;
-      pk[i >> 1] = u;
+      sum0 += a0; sum1 += a1; sum2 += b0; sum3 += b1;
+      pa[i >> 1] = pack_bf16x2(a0, a1);
+      pb[i >> 1] = pack_bf16x2(b0, b1);
     }
-    tmem_st_32x16(t_s + 16 * c, pk);
+    // P columns [32h, 32h + 32) hold tokens [64h, 64h + 64): they overwrite S columns that were already read
+    tmem_st_32x16(t_s + 32 * h, pa);
+    tmem_st_32x16(t_s + 32 * h + 16, pb);
   }
-  l += sum;
+  l += (sum0 + sum1) + (sum2 + sum3);
   if (warp_grow && have_o) {
 #pragma unroll 1
-    for (int c = 0; c < 8; ++c) {
-      uint32_t orow[16];
-      tmem_ld_32x16(t_o + 16 * c, orow);
+    for (int c = 0; c < 4; ++c) {
+      tmem_ld_32x32(t_o + 32 * c, sa);
       tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 16; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * corr);
-      tmem_st_32x16(t_o + 16 * c, orow);
+      for (int i = 0; i < 32; ++i) sa[i] = __float_as_uint(__uint_as_float(sa[i]) * corr);
+      uint32_t lo[16], hi[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) { lo[i] = sa[i]; hi[i] = sa[16 + i]; }
+      tmem_st_32x16(t_o + 32 * c, lo);
+      tmem_st_32x16(t_o + 32 * c + 16, hi);
     }
   }
   tmem_st_wait();
+}
+
+// The mask and soft-cap tests are compile-time so that the common case (a tile every row sees whole, no cap)
+// carries no predicated instructions: this code runs one warp per scheduler and every issue slot counts.
+__device__ __forceinline__ void softmax_tile(const FaTmemParams& p, uint32_t t_s, uint32_t t_o, int tok0, int lim,
+                                             int beg, bool full, bool have_o, float& m_used, float& l) {
+  if (p.softcap > 0.f) softmax_tile_impl<false, true>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
+  else if (full) softmax_tile_impl<true, false>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
+  else softmax_tile_impl<false, false>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
 }
 
 // Final normalisation (with the head's sink, if any) and store of one row of O. The tensor memory loads are
@@ -253,12 +285,19 @@ fa_prefill_tmem_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_c
     if (lane == 0) {
       const int* table = p.block_tables + (size_t)seq * p.max_blocks;
       const int last_page = (kv_len + kPageT - 1) / kPageT - 1;
-      for (int it = 0; it < n_tiles; ++it) {
-        const int page0 = (tile_lo + it) * (kTileT / kPageT);
-        int rows[kTileT / kPageT];
+      // first cache row of the tile's pages; pages past the sequence repeat its last page (finite values).
+      // The next tile's table entries are requested before this tile's waits, so their latency is hidden.
+      int rows[kTileT / kPageT], nxt[kTileT / kPageT];
 #pragma unroll
-        for (int pg = 0; pg < kTileT / kPageT; ++pg)     // pages past the sequence repeat its last page: finite values
-          rows[pg] = (table[min(page0 + pg, last_page)] * p.hkv + kvh) * kPageT;
+      for (int pg = 0; pg < kTileT / kPageT; ++pg)
+        nxt[pg] = table[min(tile_lo * (kTileT / kPageT) + pg, last_page)];
+      for (int it = 0; it < n_tiles; ++it) {
+        const int page1 = (tile_lo + it + 1) * (kTileT / kPageT);
+#pragma unroll
+        for (int pg = 0; pg < kTileT / kPageT; ++pg) {
+          rows[pg] = (nxt[pg] * p.hkv + kvh) * kPageT;
+          nxt[pg] = table[min(page1 + pg, last_page)];
+        }
         if (it > 0 && !mbar_wait(k_empty, (it - 1) & 1, abort_flag)) break;
         mbar_expect_tx(k_full, kTileBytes);
 #pragma unroll
@@ -279,6 +318,7 @@ fa_prefill_tmem_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_c
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(128, 128, 1, 1);
       constexpr uint32_t idesc_pv = make_idesc(128, 64, 1, 1) | (1u << 16);     // B is MN-major
+      constexpr uint32_t idesc_pv_wide = make_idesc(128, 128, 1, 1) | (1u << 16);
       const uint32_t q_addr = smem_u32(sq), k_addr = smem_u32(sk), v_addr = smem_u32(sv);
       for (int it = 0; it < n_tiles; ++it) {
         const uint32_t ph = it & 1;
@@ -296,8 +336,12 @@ fa_prefill_tmem_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_c
 #pragma unroll
         for (int k = 0; k < kTileT / 16; ++k) {
           const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
-          tc_mma_bf16_ts(t_o, t_s + 8 * k, smem_desc_sw128_1k(v_addr + k * 2048), idesc_pv, acc);
-          tc_mma_bf16_ts(t_o + 64, t_s + 8 * k, smem_desc_sw128_1k(v_addr + kHalfBytes + k * 2048), idesc_pv, acc);
+          if (p.pv_wide) {      // the second 64-wide atom of V's rows lies one half tile further: the leading offset
+            tc_mma_bf16_ts(t_o, t_s + 8 * k, smem_desc_sw128_1k(v_addr + k * 2048, kHalfBytes), idesc_pv_wide, acc);
+          } else {
+            tc_mma_bf16_ts(t_o, t_s + 8 * k, smem_desc_sw128_1k(v_addr + k * 2048), idesc_pv, acc);
+            tc_mma_bf16_ts(t_o + 64, t_s + 8 * k, smem_desc_sw128_1k(v_addr + kHalfBytes + k * 2048), idesc_pv, acc);
+          }
         }
         tc_commit(v_empty);
         if (it == n_tiles - 1) tc_commit(o_done);
@@ -415,14 +459,19 @@ fa_prefill_tmem2_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_
     if (lane == 0) {
       const int* table = p.block_tables + (size_t)seq * p.max_blocks;
       const int last_page = (kv_len + kPageT - 1) / kPageT - 1;
+      int rows[kTileT / kPageT], nxt[kTileT / kPageT];
+#pragma unroll
+      for (int pg = 0; pg < kTileT / kPageT; ++pg)
+        nxt[pg] = table[min(tile_lo * (kTileT / kPageT) + pg, last_page)];
       for (int it = 0; it < n_tiles; ++it) {
         const int b = it & 1;
         const uint32_t prev = ((it >> 1) - 1) & 1;       // phase of the stage's previous use
-        const int page0 = (tile_lo + it) * (kTileT / kPageT);
-        int rows[kTileT / kPageT];
+        const int page1 = (tile_lo + it + 1) * (kTileT / kPageT);
 #pragma unroll
-        for (int pg = 0; pg < kTileT / kPageT; ++pg)
-          rows[pg] = (table[min(page0 + pg, last_page)] * p.hkv + kvh) * kPageT;
+        for (int pg = 0; pg < kTileT / kPageT; ++pg) {
+          rows[pg] = (nxt[pg] * p.hkv + kvh) * kPageT;
+          nxt[pg] = table[min(page1 + pg, last_page)];
+        }
         if (it >= 2 && !mbar_wait(&k_empty[b], prev, abort_flag)) break;
         mbar_expect_tx(&k_full[b], kTileBytes);
         uint8_t* kd = sk + b * kTileBytes;
@@ -445,6 +494,7 @@ fa_prefill_tmem2_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(128, 128, 1, 1);
       constexpr uint32_t idesc_pv = make_idesc(128, 64, 1, 1) | (1u << 16);     // B is MN-major
+      constexpr uint32_t idesc_pv_wide = make_idesc(128, 128, 1, 1) | (1u << 16);
       const uint32_t q_addr = smem_u32(sq), k_addr = smem_u32(sk), v_addr = smem_u32(sv);
       auto issue_s = [&](int g, int stage) {
 #pragma unroll
@@ -460,8 +510,12 @@ fa_prefill_tmem2_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_
 #pragma unroll
         for (int k = 0; k < kTileT / 16; ++k) {
           const uint32_t acc = (!first || k > 0) ? 1u : 0u;
-          tc_mma_bf16_ts(t_o, t_p + 8 * k, smem_desc_sw128_1k(vb + k * 2048), idesc_pv, acc);
-          tc_mma_bf16_ts(t_o + 64, t_p + 8 * k, smem_desc_sw128_1k(vb + kHalfBytes + k * 2048), idesc_pv, acc);
+          if (p.pv_wide) {
+            tc_mma_bf16_ts(t_o, t_p + 8 * k, smem_desc_sw128_1k(vb + k * 2048, kHalfBytes), idesc_pv_wide, acc);
+          } else {
+            tc_mma_bf16_ts(t_o, t_p + 8 * k, smem_desc_sw128_1k(vb + k * 2048), idesc_pv, acc);
+            tc_mma_bf16_ts(t_o + 64, t_p + 8 * k, smem_desc_sw128_1k(vb + kHalfBytes + k * 2048), idesc_pv, acc);
+          }
         }
       };
       bool ok = mbar_wait(&k_full[0], 0, abort_flag);
@@ -589,6 +643,9 @@ void attention_prefill_tmem(const void* q, long long ldq, const void* k_cache, c
   p.hkv = hkv; p.group = hq / hkv;
   p.window = window; p.min_q = min_q;
   p.scale = scale; p.scale_log2 = scale * kLog2eT; p.softcap = softcap;
+  static int wide = -1;
+  if (wide < 0) { const char* e = getenv("FLLM_FA_PV_WIDE"); wide = e ? atoi(e) : 1; }
+  p.pv_wide = wide;
   // Two query tiles per CTA when that still gives every SM a CTA (FLLM_FA_TMEM_TILES=1 / 2 forces a variant).
   static int forced = -1;
   if (forced < 0) { const char* e = getenv("FLLM_FA_TMEM_TILES"); forced = e ? atoi(e) : 0; }

@@ -3,7 +3,8 @@
 Each case launches ONE kernel family a handful of times on inputs larger than L2 but far below a
 GB-scale footprint, so a multi-pass capture (``ncu --set full -k regex:<kernel> -c 1``) finishes
 in seconds. Cases: gemm_decode (64 tokens x gate_up of an 8B model), gemm_prefill (2048 tokens),
-attn_decode (64 sequences at 1152 context), attn_prefill, fp8_prefill, gemm_fp4_decode (64 tokens x NVFP4 gate_up), tp_rs_gemm / tp_norm / tp_ag_gemm (fused tensor-parallel kernels, two virtual ranks).
+attn_decode (64 sequences at 1152 context), attn_prefill (2 x 1024 tokens), attn_prefill_long (4 x 4096 tokens,
+the tcgen05 kernel with two query tiles per CTA), fp8_prefill, gemm_fp4_decode (64 tokens x NVFP4 gate_up), tp_rs_gemm / tp_norm / tp_ag_gemm (fused tensor-parallel kernels, two virtual ranks).
 """
 from __future__ import annotations
 
@@ -58,7 +59,7 @@ def main(argv=None) -> None:
         wq, sw = quantize_weight_fp8_block(torch.randn(8192, 4096, **bf) * 0.02)
         lin = Fp8BlockLinear(ops, wq, sw)
         fn = lambda: lin(x)
-    elif case in ("attn_decode", "attn_prefill"):
+    elif case in ("attn_decode", "attn_prefill", "attn_prefill_long"):
         from .models.decoder import StepBatch
         B, L, bs, hq, hkv, D = 64, 1152, 16, 32, 8, 128
         nb = B * (L // bs)
@@ -70,6 +71,14 @@ def main(argv=None) -> None:
             meta = StepBatch(None, None, None, None, tables, None, num_seqs=B, num_tokens=B, max_kv_len=L,
                              seq_lens=torch.full((B,), L, device="cuda", dtype=torch.int32),
                              q_starts=torch.arange(B + 1, device="cuda", dtype=torch.int32))
+        elif case == "attn_prefill_long":
+            n, Lq = 4, 4096
+            tables = torch.arange(n * (Lq // bs), device="cuda", dtype=torch.int32).view(n, Lq // bs)
+            q = torch.randn(n * Lq, hq * D, **bf)
+            meta = StepBatch(None, None, None, None, tables, None, num_seqs=n, num_tokens=n * Lq, max_kv_len=Lq,
+                             seq_lens=torch.full((n,), Lq, device="cuda", dtype=torch.int32),
+                             q_starts=torch.arange(n + 1, device="cuda", dtype=torch.int32) * Lq,
+                             max_q_len=Lq, min_q_len=Lq)
         else:
             q = torch.randn(2048, hq * D, **bf)
             meta = StepBatch(None, None, None, None, tables, None, num_seqs=2, num_tokens=2048, max_kv_len=1024,
