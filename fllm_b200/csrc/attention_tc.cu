@@ -13,8 +13,10 @@
 //
 // Both compute S = Q K^T and O += P V with mma.sync.m16n8k16 (bf16 in, fp32 out) from
 // XOR-swizzled shared memory via ldmatrix, with an online softmax in the exp2 domain.
-// Attention is < 3 % of prefill FLOPs and bandwidth-bound in decode, so these use the
-// register-level MMA path; the GEMMs that dominate run on tcgen05 (gemm_bf16.cu).
+// Decode is bandwidth-bound and its query tile has 4 - 16 rows, far from the 128 rows of a
+// tcgen05 MMA, so it stays on the register-level MMA path. Prefill steps with head_dim 128, a
+// group size that divides 128 and at least 128 packed query rows are handed to the tcgen05 /
+// tensor-memory kernel of attention_tmem.cu; fa_prefill_kernel serves every other shape.
 //
 // KV cache layout: [block][kv_head][16][head_dim] bf16 (a head's page is contiguous).
 // Reference counterparts: rust/engine/cuda/attention4.cu:275-495 (GQA-sharing decode with
