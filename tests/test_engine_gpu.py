@@ -45,6 +45,33 @@ def test_logits_match_oracle(name):
     assert eng.ops.check_status() == 0
 
 
+def test_head_dim_128_prefill_runs_on_the_tensor_memory_attention_kernel_and_matches_oracle():
+    """head_dim 128 with chunks of 256 tokens: both chunks of the prompt (the second continues the first)
+    go through the tcgen05 prefill kernel; the last-row logits must match the dense fp32 oracle."""
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    from oracle import dense_forward
+    cfg = preset("qwen3-tiny")
+    cfg.head_dim = 128
+    ec = EngineConfig(max_num_seqs=4, max_num_batched_tokens=256, max_model_len=640, num_kv_blocks=96)
+    eng = LLMEngine(cfg, ec, device="cuda:0")
+    p = _prompts(cfg.vocab_size, (500,), seed=5)[0]
+    eng.add_request(p, SamplingParams(max_tokens=1))
+    logits = None
+    while eng.has_unfinished():
+        step = eng.scheduler.schedule()
+        batch = eng._build_batch(step)
+        out = eng.decoder.forward(batch)
+        if out.shape[0]:
+            logits = out
+        eng._commit(step, eng.decoder.greedy_tokens(out).tolist())
+    want = dense_forward(cfg, eng.weights, p)[-1]
+    got = logits[-1].float()
+    err = (got - want).abs().max().item()
+    assert err < 0.05 * want.abs().max().item() + 1e-3, err
+    assert eng.ops.check_status() == 0
+
+
 def test_graph_and_eager_decode_agree():
     from fllm_b200.config import EngineConfig, preset
     from fllm_b200.models.weights import init_random_weights
