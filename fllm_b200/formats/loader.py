@@ -28,7 +28,11 @@ def _cut_rows(t: torch.Tensor, start: int, n: int) -> torch.Tensor:
 def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16,
                        expert_parallel: bool = False):
     from .safetensors_io import open_checkpoint
-    cfg = ModelConfig.from_hf_config(json.load(open(os.path.join(directory, "config.json"))))
+    from ..ops.int4 import Int4Weight
+    from .int4_checkpoints import int4_linear
+    hf = json.load(open(os.path.join(directory, "config.json")))
+    cfg = ModelConfig.from_hf_config(hf)
+    qcfg = hf.get("quantization_config") or {}
     sp = make_shard_spec(cfg, tp, tp_rank, expert_parallel)
     ck = open_checkpoint(directory)
     D = cfg.head_dim
@@ -44,24 +48,61 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
     def dev(t):
         return t.to(device=device, dtype=dtype if t.is_floating_point() and t.element_size() > 1 else t.dtype).contiguous()
 
+    def has(name):
+        return name + ".weight" in ck or name + ".qweight" in ck
+
+    def lin(name):
+        """A projection by its module name: a tensor [N, K], or an Int4Weight for AWQ / GPTQ tensors."""
+        if name + ".qweight" in ck:
+            return int4_linear(qcfg.get("quant_method", "gptq"), get(name + ".qweight"), get(name + ".qzeros"),
+                               get(name + ".scales"), get(name + ".g_idx", False),
+                               qcfg.get("checkpoint_format", "gptq"), dtype)
+        return get(name + ".weight")
+
+    def rows(w, sl):
+        return w.rows(sl) if isinstance(w, Int4Weight) else w[sl]
+
+    def cols(w, sl):
+        if isinstance(w, Int4Weight):
+            if sl.start % 64 == 0 and sl.stop % 64 == 0:
+                return w.cols(sl)
+            w = w.dense().to(dtype)
+        return w[:, sl]
+
+    def cat(parts):
+        if all(isinstance(x, Int4Weight) for x in parts):
+            return Int4Weight.cat(parts)
+        return torch.cat([x.dense().to(dtype) if isinstance(x, Int4Weight) else x for x in parts], 0)
+
+    def put(w):
+        return w.to(device) if isinstance(w, Int4Weight) else dev(w)
+
     qs = slice(sp.q_head_start * D, (sp.q_head_start + sp.hq_local) * D)
     ks = slice(sp.kv_head_start * D, (sp.kv_head_start + sp.hkv_local) * D)
     isl = slice(sp.inter_start, sp.inter_start + sp.inter_local)
+    nq, nk, inter = cfg.num_heads * D, cfg.num_kv_heads * D, cfg.intermediate_size
     layers = []
     for l in range(cfg.num_layers):
         p = f"model.layers.{l}."
-        q, k, v = (get(p + f"self_attn.{n}_proj.weight") for n in "qkv")
-        fp8 = q.dtype == torch.float8_e4m3fn
+        if has(p + "self_attn.q_proj"):
+            q, k, v = (lin(p + f"self_attn.{n}_proj") for n in "qkv")
+        else:                                  # Phi-3: one fused q|k|v projection
+            f = lin(p + "self_attn.qkv_proj")
+            q, k, v = rows(f, slice(0, nq)), rows(f, slice(nq, nq + nk)), rows(f, slice(nq + nk, nq + 2 * nk))
+        fp8 = isinstance(q, torch.Tensor) and q.dtype == torch.float8_e4m3fn
         lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
                           ffn_norm=dev(get(p + "post_attention_layernorm.weight")))
-        o = get(p + "self_attn.o_proj.weight")
+        o = lin(p + "self_attn.o_proj")
         if cfg.is_moe:
             _load_moe_layer(cfg, sp, tp_rank, lw, p, get, dev)
-            lw.wqkv = dev(torch.cat([q[qs], k[ks], v[ks]], 0))
-            lw.wo = dev(o[:, qs])
+            lw.wqkv = put(cat([rows(q, qs), rows(k, ks), rows(v, ks)]))
+            lw.wo = put(cols(o, qs))
             g = u = d = None
-        else:
-            g, u, d = (get(p + f"mlp.{n}_proj.weight") for n in ("gate", "up", "down"))
+        elif has(p + "mlp.gate_proj"):
+            g, u, d = (lin(p + f"mlp.{n}_proj") for n in ("gate", "up", "down"))
+        else:                                  # Phi-3: one fused gate|up projection
+            f = lin(p + "mlp.gate_up_proj")
+            g, u, d = rows(f, slice(0, inter)), rows(f, slice(inter, 2 * inter)), lin(p + "mlp.down_proj")
         if cfg.is_moe:
             pass
         elif fp8:
@@ -82,10 +123,10 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
             a, b = cols(d, sc("mlp.down_proj"), isl)
             lw.packed["w_down"] = ("fp8_block", a.view(torch.uint8).to(device).contiguous(), b.to(device).contiguous())
         else:
-            lw.wqkv = dev(torch.cat([q[qs], k[ks], v[ks]], 0))
-            lw.wo = dev(o[:, qs])
-            lw.w_gate_up = dev(torch.cat([g[isl], u[isl]], 0))
-            lw.w_down = dev(d[:, isl])
+            lw.wqkv = put(cat([rows(q, qs), rows(k, ks), rows(v, ks)]))
+            lw.wo = put(cols(o, qs))
+            lw.w_gate_up = put(cat([rows(g, isl), rows(u, isl)]))
+            lw.w_down = put(cols(d, isl))
         if cfg.attn_bias:
             bq, bk, bv = (get(p + f"self_attn.{n}_proj.bias", False) for n in "qkv")
             if bq is not None:

@@ -333,3 +333,157 @@ def test_model_families_load_from_hf_style_checkpoints(tmp_path, family):
     prompt = [[3, 1, 4, 1, 5, 9, 2, 6]]
     sp = SamplingParams(max_tokens=6)
     assert LLMEngine(cfg2, ec, device="cpu", weights=w2).generate(prompt, sp) == LLMEngine(cfg, ec, device="cpu", weights=w).generate(prompt, sp)
+
+
+def _quant_groups(w, g):
+    """Asymmetric 4-bit groups of size g along K: (q uint8 [N, K], scale [N, K/g], zero [N, K/g] integers)."""
+    N, K = w.shape
+    x = w.float().view(N, K // g, g)
+    lo, hi = x.amin(-1), x.amax(-1)
+    s = ((hi - lo) / 15.0).clamp_min(1e-8).half().float()
+    z = torch.round(-lo / s).clamp(0, 15)
+    q = torch.round(x / s.unsqueeze(-1) + z.unsqueeze(-1)).clamp(0, 15).to(torch.uint8).view(N, K)
+    return q, s, z
+
+
+def test_awq_and_gptq_tensors_unpack_to_the_values_their_formula_gives():
+    """Pack random codes the way AutoAWQ / AutoGPTQ lay them out, read them back, and compare the Int4Weight
+    with (q - zero) * scale; activation-reordered GPTQ groups fall back to a dense tensor with the same values."""
+    from fllm_b200.formats.int4_checkpoints import int4_linear, pack_awq, pack_gptq, unpack_awq, unpack_gptq
+    from fllm_b200.ops.int4 import Int4Weight
+    torch.manual_seed(0)
+    N, K, g = 48, 256, 128
+    w = torch.randn(N, K)
+    q, s, z = _quant_groups(w, g)
+    want = (q.float() - z.repeat_interleave(g, 1)) * s.repeat_interleave(g, 1)
+    scales_file = s.t().contiguous().half()
+    qw, qz = pack_awq(q, z)
+    assert qw.shape == (K, N // 8) and qz.shape == (K // g, N // 8) and qw.dtype == torch.int32
+    # nibble 1 of the first word is output channel 2 (AutoAWQ's order 0 2 4 6 1 3 5 7)
+    assert (int(qw[0, 0]) >> 4) & 0xF == int(q[2, 0])
+    q2, s2, z2 = unpack_awq(qw, qz, scales_file)
+    assert torch.equal(q2, q) and torch.equal(z2, z) and torch.equal(s2, s)
+    a = int4_linear("awq", qw, qz, scales_file)
+    assert isinstance(a, Int4Weight) and a.shape == (N, K)
+    assert (a.dense() - want).abs().max().item() <= 0.02 * want.abs().max().item()      # scale / min rounded to bf16
+    for fmt, off in (("gptq", 1), ("gptq_v2", 0)):
+        zz = z.clamp(1, 15) if off else z                     # the old layout cannot store zero = 0 (it stores zero - 1)
+        want_g = (q.float() - zz.repeat_interleave(g, 1)) * s.repeat_interleave(g, 1)
+        gw, gz = pack_gptq(q, zz, off)
+        assert gw.shape == (K // 8, N) and (int(gw[0, 5]) >> 8) & 0xF == int(q[5, 2])   # nibble j = input row 8r + j
+        q3, s3, z3 = unpack_gptq(gw, gz, scales_file, off)
+        assert torch.equal(q3, q) and torch.equal(z3, zz)
+        b = int4_linear("gptq", gw, gz, scales_file, torch.arange(K, dtype=torch.int32) // g, fmt)
+        assert isinstance(b, Int4Weight)
+        assert (b.dense() - want_g).abs().max().item() <= 0.02 * want_g.abs().max().item()
+    perm = torch.randperm(K)
+    g_idx = (perm // g).to(torch.int32)                      # act-order: rows of a group are scattered
+    gw, gz = pack_gptq(q, z.clamp(1, 15), 1)
+    d = int4_linear("gptq", gw, gz, scales_file, g_idx, "gptq", torch.float32)
+    assert isinstance(d, torch.Tensor)
+    idx = g_idx.long()
+    assert torch.allclose(d, (q.float() - z.clamp(1, 15)[:, idx]) * s[:, idx])
+
+
+@pytest.mark.parametrize("method", ["awq", "gptq"])
+def test_int4_hf_checkpoint_loads_packed_and_generates_like_its_dequantised_twin(tmp_path, method):
+    """A llama-like checkpoint whose projections are AWQ / GPTQ tensors: the loader keeps them as Int4Weight
+    (also under TP2 cuts) and the engine produces the tokens of the same model with dequantised weights."""
+    import json
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.formats.int4_checkpoints import pack_awq, pack_gptq
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    from fllm_b200.formats.safetensors_io import save_file
+    from fllm_b200.models.weights import init_random_weights
+    from fllm_b200.ops.int4 import Int4Weight
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    cfg = preset("tiny-llama")
+    cfg.vocab_size, cfg.intermediate_size = 512, 512
+    w = init_random_weights(cfg, "cpu", seed=4)
+    D, hq, hkv, I, g = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads, cfg.intermediate_size, 64
+    t = {"model.embed_tokens.weight": w.embed, "model.norm.weight": w.final_norm, "lm_head.weight": w.lm_head}
+
+    def put(name, mat):
+        q, s, z = _quant_groups(mat, g)
+        if method == "gptq":
+            z = z.clamp(1, 15)
+            q = torch.round(mat.float().view(mat.shape[0], -1, g) / s.unsqueeze(-1) + z.unsqueeze(-1)).clamp(0, 15).to(torch.uint8).view(mat.shape)
+            qw, qz = pack_gptq(q, z, 1)
+            t[name + ".g_idx"] = torch.arange(mat.shape[1], dtype=torch.int32) // g
+        else:
+            qw, qz = pack_awq(q, z)
+        t[name + ".qweight"], t[name + ".qzeros"], t[name + ".scales"] = qw, qz, s.t().contiguous().half()
+        return ((q.float() - z.repeat_interleave(g, 1)) * s.repeat_interleave(g, 1))
+
+    for l, lw in enumerate(w.layers):
+        p = f"model.layers.{l}."
+        t[p + "input_layernorm.weight"], t[p + "post_attention_layernorm.weight"] = lw.attn_norm, lw.ffn_norm
+        parts = {"self_attn.q_proj": lw.wqkv[: hq * D], "self_attn.k_proj": lw.wqkv[hq * D: (hq + hkv) * D],
+                 "self_attn.v_proj": lw.wqkv[(hq + hkv) * D:], "self_attn.o_proj": lw.wo,
+                 "mlp.gate_proj": lw.w_gate_up[:I], "mlp.up_proj": lw.w_gate_up[I:], "mlp.down_proj": lw.w_down}
+        deq = {k: put(p + k, v) for k, v in parts.items()}
+        lw.wqkv = torch.cat([deq["self_attn.q_proj"], deq["self_attn.k_proj"], deq["self_attn.v_proj"]], 0)
+        lw.wo, lw.w_down = deq["self_attn.o_proj"], deq["mlp.down_proj"]
+        lw.w_gate_up = torch.cat([deq["mlp.gate_proj"], deq["mlp.up_proj"]], 0)
+    save_file({k: v.contiguous() for k, v in t.items()}, str(tmp_path / "model.safetensors"))
+    hf = {"model_type": "llama", "vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
+          "num_attention_heads": hq, "num_key_value_heads": hkv, "head_dim": D, "intermediate_size": I, "rms_norm_eps": cfg.rms_eps,
+          "rope_theta": cfg.rope_theta, "max_position_embeddings": 4096, "tie_word_embeddings": False,
+          "quantization_config": {"quant_method": method, "bits": 4, "group_size": g, "checkpoint_format": "gptq"}}
+    json.dump(hf, open(tmp_path / "config.json", "w"))
+    cfg2, w2, _ = load_hf_checkpoint(str(tmp_path), device="cpu")
+    for lw in w2.layers:
+        assert all(isinstance(getattr(lw, n), Int4Weight) for n in ("wqkv", "wo", "w_gate_up", "w_down"))
+    lw0 = w2.layers[0]
+    assert (lw0.wqkv.dense() - w.layers[0].wqkv.float()).abs().max().item() <= 0.03 * w.layers[0].wqkv.abs().max().item()
+    ec = EngineConfig(max_num_seqs=2, max_num_batched_tokens=32, max_model_len=64, num_kv_blocks=16)
+    prompt = [[3, 1, 4, 1, 5, 9, 2, 6]]
+    logits = []
+    for cc, ww in ((cfg2, w2), (cfg, w)):
+        eng = LLMEngine(cc, ec, device="cpu", weights=ww)
+        eng.add_request(prompt[0], SamplingParams(max_tokens=1))
+        step = eng.scheduler.schedule()
+        logits.append(eng.decoder.forward(eng._build_batch(step))[-1].float())
+    err = (logits[0] - logits[1]).abs().max().item() / (logits[1].abs().max().item() + 1e-6)
+    assert err < 0.05, err
+    _, w_r1, _ = load_hf_checkpoint(str(tmp_path), device="cpu", tp=2, tp_rank=1)
+    half = w2.layers[0].w_down.shape[1] // 2
+    assert w_r1.layers[0].w_down.shape == (cfg.hidden_size, half)
+    if half % 64 == 0:
+        assert isinstance(w_r1.layers[0].w_down, Int4Weight)
+        assert torch.equal(w_r1.layers[0].w_down.dense(), w2.layers[0].w_down.dense()[:, half:])
+
+
+def test_phi3_fused_projections_load_like_the_split_ones(tmp_path):
+    """Phi-3 stores q|k|v and gate|up as single tensors: same weights and tokens as the split llama form."""
+    import json
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    from fllm_b200.formats.safetensors_io import save_file
+    from fllm_b200.models.weights import init_random_weights
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    cfg = preset("tiny-llama")
+    cfg.vocab_size = 512
+    w = init_random_weights(cfg, "cpu", seed=6)
+    t = {"model.embed_tokens.weight": w.embed, "model.norm.weight": w.final_norm, "lm_head.weight": w.lm_head}
+    for l, lw in enumerate(w.layers):
+        p = f"model.layers.{l}."
+        t.update({p + "input_layernorm.weight": lw.attn_norm, p + "post_attention_layernorm.weight": lw.ffn_norm,
+                  p + "self_attn.qkv_proj.weight": lw.wqkv, p + "self_attn.o_proj.weight": lw.wo,
+                  p + "mlp.gate_up_proj.weight": lw.w_gate_up, p + "mlp.down_proj.weight": lw.w_down})
+    save_file({k: v.contiguous() for k, v in t.items()}, str(tmp_path / "model.safetensors"))
+    hf = {"model_type": "phi3", "vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
+          "num_attention_heads": cfg.num_heads, "num_key_value_heads": cfg.num_kv_heads, "intermediate_size": cfg.intermediate_size,
+          "rms_norm_eps": cfg.rms_eps, "rope_theta": cfg.rope_theta, "max_position_embeddings": 4096, "tie_word_embeddings": False}
+    json.dump(hf, open(tmp_path / "config.json", "w"))
+    cfg2, w2, _ = load_hf_checkpoint(str(tmp_path), device="cpu")
+    assert cfg2.head_dim == cfg.head_dim
+    for a, b in zip(w2.layers, w.layers):
+        assert torch.equal(a.wqkv, b.wqkv) and torch.equal(a.w_gate_up, b.w_gate_up) and torch.equal(a.w_down, b.w_down)
+    _, w_r1, _ = load_hf_checkpoint(str(tmp_path), device="cpu", tp=2, tp_rank=1)
+    I = cfg.intermediate_size
+    assert torch.equal(w_r1.layers[0].w_gate_up[: I // 2], w.layers[0].w_gate_up[I // 2: I])
+    ec = EngineConfig(max_num_seqs=2, max_num_batched_tokens=32, max_model_len=64, num_kv_blocks=16)
+    sp = SamplingParams(max_tokens=5)
+    prompt = [[3, 1, 4, 1, 5, 9, 2, 6]]
+    assert LLMEngine(cfg2, ec, device="cpu", weights=w2).generate(prompt, sp) == LLMEngine(cfg, ec, device="cpu", weights=w).generate(prompt, sp)
