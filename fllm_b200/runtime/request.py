@@ -27,6 +27,16 @@ class SamplingParams:
     logit_bias: Optional[Dict[int, float]] = None
     allowed_token_ids: Optional[Sequence[int]] = None
     bad_words_ids: Optional[Sequence[int]] = None
+    bad_words: Optional[Sequence[Sequence[int]]] = None    # banned token sequences (the last token is banned after the others)
+    typical_p: float = 1.0
+    dry_multiplier: float = 0.0
+    dry_base: float = 1.75
+    dry_allowed_length: int = 2
+    dry_sequence_breakers: Sequence[int] = ()
+    dry_penalty_last_n: int = 1024
+    mirostat_mode: int = 0               # 0 off; 1 or 2 run Mirostat 2.0
+    mirostat_tau: float = 5.0
+    mirostat_eta: float = 0.1
     logprobs: bool = False
     top_logprobs: int = 0
     n: int = 1
@@ -46,7 +56,11 @@ class SamplingParams:
         return (not self.greedy or self.repetition_penalty != 1.0 or self.presence_penalty != 0.0
                 or self.frequency_penalty != 0.0 or bool(self.logit_bias)
                 or self.allowed_token_ids is not None or bool(self.bad_words_ids) or self.logprobs
-                or self.guided is not None)
+                or self.guided is not None or self.needs_host_processors)
+
+    @property
+    def needs_host_processors(self) -> bool:
+        return (self.typical_p < 1.0 or self.dry_multiplier > 0.0 or self.mirostat_mode != 0 or bool(self.bad_words))
 
     def validate(self, vocab_size: int) -> None:
         if self.temperature < 0:
@@ -63,6 +77,14 @@ class SamplingParams:
             raise ValueError("max_tokens must be >= 1")
         if self.n != 1:
             raise ValueError("n > 1 is served by submitting n requests")
+        if not 0 < self.typical_p <= 1:
+            raise ValueError("typical_p must be in (0, 1]")
+        if self.dry_multiplier < 0 or self.dry_base < 1 or self.dry_allowed_length < 1:
+            raise ValueError("DRY needs multiplier >= 0, base >= 1, allowed_length >= 1")
+        if self.mirostat_mode not in (0, 1, 2) or self.mirostat_tau <= 0 or self.mirostat_eta <= 0:
+            raise ValueError("mirostat: mode 0, 1 or 2 with tau > 0 and eta > 0")
+        if self.mirostat_mode:
+            self.speculative = False         # the controller's state moves one sampled token at a time
         for t in list(self.stop_token_ids) + list((self.logit_bias or {}).keys()):
             if not 0 <= int(t) < vocab_size:
                 raise ValueError(f"token id {t} outside the vocabulary")
@@ -95,6 +117,7 @@ class Request:
     draft: List[int] = field(default_factory=list)   # proposed tokens awaiting verification
     logprobs: List[float] = field(default_factory=list)
     swapped: bool = False            # preempted with its KV parked in host memory
+    mirostat: Optional[object] = None  # runtime.logits_processors.Mirostat, created on first use
 
     @property
     def all_tokens(self) -> List[int]:

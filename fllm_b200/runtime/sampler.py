@@ -11,6 +11,7 @@ import numpy as np
 import torch
 
 from ..ops.reference import sample_reference
+from .logits_processors import apply_before_sampling, observe_sampled
 
 
 def _row_params(req, draw: int, default_seed: int):
@@ -38,6 +39,9 @@ def sample_step(engine, step, logits: torch.Tensor, greedy: torch.Tensor) -> tor
     idx = torch.tensor([r for r, _, _ in rows], dtype=torch.long, device=logits.device)
     sub = logits.index_select(0, idx).float().contiguous()
     vocab = sub.shape[1]
+    for i, (_, req, draw) in enumerate(rows):          # typical-p, DRY, Mirostat, banned sequences: edits of the row
+        if req.params.needs_host_processors:
+            apply_before_sampling(req, sub[i], draw)
     params = [_row_params(req, draw, engine.cfg.seed) for _, req, draw in rows]
     # sparse penalty / bias lists
     pen_lists, bias_lists = [], []
@@ -116,5 +120,8 @@ def sample_step(engine, step, logits: torch.Tensor, greedy: torch.Tensor) -> tor
             prm = params[i]
             picked.append(sample_reference(x, prm[0], prm[6], prm[1], prm[2], prm[8], prm[7]))
         ids = torch.tensor(picked, dtype=torch.int32, device=logits.device)
+    if any(req.params.mirostat_mode for _, req, _ in rows):
+        for (_, req, _), t in zip(rows, ids.tolist()):
+            observe_sampled(req, t)
     out[idx] = ids.to(out.dtype)
     return out

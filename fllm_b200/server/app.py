@@ -192,7 +192,21 @@ def _sampling_from(body: dict, default_max: int = 256, dialect: str = "openai") 
         stop_token_ids=tuple(pick("stop_token_ids", default=()) or ()), stop=tuple(stop or ()),
         logit_bias={int(k): float(v) for k, v in (g("logit_bias") or {}).items()} or None,
         allowed_token_ids=g("allowed_token_ids"), logprobs=bool(g("logprobs")),
-        priority=int(g("priority") or 0), timeout_s=g("timeout"), cache_salt=str(g("cache_salt") or ""))
+        priority=int(g("priority") or 0), timeout_s=g("timeout"), cache_salt=str(g("cache_salt") or ""),
+        typical_p=float(pick("typical_p", "typ_p", default=1.0)),
+        dry_multiplier=float(pick("dry_multiplier", default=0.0)), dry_base=float(pick("dry_base", default=1.75)),
+        dry_allowed_length=int(pick("dry_allowed_length", default=2)),
+        dry_penalty_last_n=int(pick("dry_penalty_last_n", default=1024)),
+        mirostat_mode=int(pick("mirostat", "mirostat_mode", default=0) or 0),
+        mirostat_tau=float(pick("mirostat_tau", default=5.0)), mirostat_eta=float(pick("mirostat_eta", default=0.1)))
+    # banned sequences / DRY breakers given as token-id lists are taken as they are; strings are tokenised by the caller
+    bw = pick("bad_words_ids", "bad_words")
+    if bw:
+        seqs = [[int(t) for t in (w if isinstance(w, (list, tuple)) else [w])] for w in bw if not isinstance(w, str)]
+        sp.bad_words = [q for q in seqs if q] or None
+    br = pick("dry_sequence_breakers")
+    if br:
+        sp.dry_sequence_breakers = tuple(int(t) for t in br if not isinstance(t, str))
     if sp.max_tokens < 1:
         sp.max_tokens = default_max
     return sp
@@ -340,6 +354,20 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
     def attach_guided(sp: SamplingParams, body: dict) -> None:
         """response_format json_object / json_schema (OpenAI) and format: "json" (Ollama) constrain the
         output to a JSON object through the sampler's allowed-token mask."""
+        # banned words and DRY breakers given as text become token sequences (with and without a leading space)
+        words = [w for w in (body.get("bad_words") or []) if isinstance(w, str) and w]
+        if words:
+            seqs = list(sp.bad_words or [])
+            for w in words:
+                for form in (w, " " + w):
+                    ids = [int(t) for t in tokenizer.encode(form, add_bos=False)]
+                    if ids and ids not in seqs:
+                        seqs.append(ids)
+            sp.bad_words = seqs
+        brk = [w for w in (body.get("dry_sequence_breakers") or []) if isinstance(w, str) and w]
+        if brk:
+            extra = {int(tokenizer.encode(w, add_bos=False)[-1]) for w in brk if tokenizer.encode(w, add_bos=False)}
+            sp.dry_sequence_breakers = tuple(sorted(set(sp.dry_sequence_breakers) | extra))
         rf = body.get("response_format")
         kind = rf.get("type") if isinstance(rf, dict) else None
         fmt = body.get("format")

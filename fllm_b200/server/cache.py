@@ -28,6 +28,9 @@ def request_key(model: str, prompt_ids: Sequence[int], sp) -> Optional[str]:
         "min": sp.min_tokens, "eos": sp.ignore_eos, "stop": list(sp.stop), "stop_ids": list(sp.stop_token_ids),
         "bias": sorted((sp.logit_bias or {}).items()), "allow": sorted(sp.allowed_token_ids or []),
         "bad": sorted(sp.bad_words_ids or []), "lp": sp.logprobs, "salt": sp.cache_salt,
+        "badseq": [list(w) for w in (sp.bad_words or [])], "typ": sp.typical_p,
+        "dry": [sp.dry_multiplier, sp.dry_base, sp.dry_allowed_length, list(sp.dry_sequence_breakers), sp.dry_penalty_last_n],
+        "miro": [sp.mirostat_mode, sp.mirostat_tau, sp.mirostat_eta],
         "guided": type(sp.guided).__name__ if sp.guided is not None else None,
     }
     h = hashlib.sha256(json.dumps(fields, sort_keys=True, default=str).encode())

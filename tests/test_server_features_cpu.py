@@ -171,6 +171,26 @@ def test_json_mode_output_is_always_a_json_prefix(client):
     assert json_feed(json_start(True), o["response"]) is not None
 
 
+def test_banned_words_given_as_text_and_rare_samplers_through_http(client):
+    """`bad_words` strings are tokenised by the server (byte tokenizer: one token per byte) and never show
+    up in the text; typical_p / DRY / mirostat fields are accepted on the OpenAI and Ollama routes."""
+    body = {"prompt": "ban test", "max_tokens": 12, "temperature": 0}
+    base = client.post("/v1/completions", json=body).json()["choices"][0]
+    first = base["token_ids"][0]
+    if first < 256:
+        word = bytes([first]).decode("latin-1")
+        got = client.post("/v1/completions", json={**body, "bad_words": [word]}).json()["choices"][0]
+        assert first not in got["token_ids"]
+    r = client.post("/v1/completions", json={**body, "temperature": 1.0, "seed": 3, "typical_p": 0.9, "dry_multiplier": 0.8,
+                                             "dry_sequence_breakers": ["\n"], "mirostat": 2, "mirostat_tau": 3.0})
+    assert r.status_code == 200 and len(r.json()["choices"][0]["token_ids"]) >= 1
+    o = client.post("/api/generate", json={"prompt": "x", "stream": False,
+                                           "options": {"num_predict": 6, "temperature": 0.8, "seed": 1, "typical_p": 0.5, "mirostat": 2}})
+    assert o.status_code == 200
+    bad = client.post("/v1/completions", json={**body, "typical_p": 0.0})
+    assert bad.status_code in (400, 422)
+
+
 def test_identical_greedy_requests_hit_the_response_cache(client):
     before = client.get("/admin/cache").json()["responses"]
     body = {"prompt": "cache me", "max_tokens": 6, "temperature": 0}
