@@ -14,7 +14,7 @@
 // Both compute S = Q K^T and O += P V with mma.sync.m16n8k16 (bf16 in, fp32 out) from
 // XOR-swizzled shared memory via ldmatrix, with an online softmax in the exp2 domain.
 // Decode is bandwidth-bound and its query tile has 4 - 16 rows, far from the 128 rows of a
-// tcgen05 MMA, so it stays on the register-level MMA path. Prefill steps with head_dim 128, a
+// tcgen05 MMA, so it stays on the register-level MMA path. Prefill steps with a
 // group size that divides 128 and at least 128 packed query rows are handed to the tcgen05 /
 // tensor-memory kernel of attention_tmem.cu; fa_prefill_kernel serves every other shape.
 //
@@ -592,7 +592,7 @@ static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int mi
   if (max_q_len > decode_max_q && use_tmem && p.num_kv_blocks > 0 && max_q_len * p.group >= 128 &&
       attention_prefill_tmem_supported(D, p.group, kPage)) {
     attention_prefill_tmem(p.q, p.ldq, p.k_cache, p.v_cache, p.num_kv_blocks, p.block_tables, p.max_blocks, p.q_starts,
-                           p.kv_lens, p.out, p.ldo, num_seqs, max_q_len, decode_max_q + 1, p.hq, p.hkv, p.scale,
+                           p.kv_lens, p.out, p.ldo, num_seqs, max_q_len, decode_max_q + 1, p.hq, p.hkv, D, p.scale,
                            p.window, p.sinks, p.softcap, p.status, s);
     ++launches;
   } else if (max_q_len > decode_max_q) {

@@ -12,9 +12,10 @@
 //                      P as bf16 written over S's first columns with tcgen05.st, and the rescale of
 //                      O in tensor memory when the row maximum moved by more than 2^8
 //
-// Tensor memory: S/P 128 columns + O 128 columns = 256, shared memory 97 KB, so two CTAs share an
-// SM and one CTA's softmax overlaps the other's MMAs. Every wait is bounded (ptx.cuh: mbar_wait) and
-// a timeout is reported through the status word.
+// Tensor memory: S/P 128 columns + O up to 128 columns = 256, shared memory 97 KB at head dim 128, so
+// two CTAs share an SM and one CTA's softmax overlaps the other's MMAs. Head dim 64 and 128 are template
+// instances (a tile is one or two 64-column halves). Every wait is bounded (ptx.cuh: mbar_wait) and a
+// timeout is reported through the status word.
 //
 // Reference counterpart: rust/engine/cuda/attention3.cu:57-288 (mma.sync prefill tiles).
 #include <unordered_map>
@@ -30,11 +31,11 @@ namespace {
 constexpr int kPageT = 16;
 constexpr int kRowsT = 128;        // packed query rows per CTA = tensor memory lanes
 constexpr int kTileT = 128;        // KV tokens per tile
-constexpr int kDT = 128;           // head dim
-constexpr int kHalfBytes = kRowsT * 128;           // one 64-column half of a 128-row tile
-constexpr int kTileBytes = 2 * kHalfBytes;         // 32 KB
+constexpr int kHalfBytes = kRowsT * 128;           // one 64-column half of a 128-row tile: 16 KB
+// head dim D is a template parameter (64 or 128): a 128-row tile of Q, K or V is D / 64 such halves
+template <int D> constexpr int tile_bytes() { return (D / 64) * kHalfBytes; }
 constexpr int kThreadsT = 192;
-constexpr int kSmemT = 3 * kTileBytes + 256 + 1024;  // Q, K, V, barriers, alignment slack
+template <int D> constexpr int smem_one() { return 3 * tile_bytes<D>() + 256 + 1024; }   // Q, K, V, barriers, alignment slack
 constexpr float kLog2eT = 1.4426950408889634f;
 constexpr float kLazyRescale = 8.f;                // keep a stale row maximum while exp2 stays below 2^8
 
@@ -78,7 +79,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_1k(uint32_t saddr, uint32_t 
 // One row (thread) of the softmax over one 128-token tile: reads S from tensor memory, updates the row's
 // reference maximum and sum, writes P as bf16 over S's first 64 columns and, when the maximum of any row of
 // the warp moved by more than 2^8, rescales the warp's rows of O. `t_s` / `t_o` already carry the lane offset.
-template <bool full, bool capped>
+template <int D, bool full, bool capped>
 __device__ __forceinline__ void softmax_tile_impl(const FaTmemParams& p, uint32_t t_s, uint32_t t_o, int tok0, int lim,
                                                   int beg, bool have_o, float& m_used, float& l) {
   const float cap_in = capped ? p.scale / p.softcap : 0.f;
@@ -160,7 +161,7 @@ __device__ __forceinline__ void softmax_tile_impl(const FaTmemParams& p, uint32_
   l += (sum0 + sum1) + (sum2 + sum3);
   if (warp_grow && have_o) {
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < D / 32; ++c) {
       tmem_ld_32x32(t_o + 32 * c, sa);
       tmem_ld_wait();
 #pragma unroll
@@ -177,15 +178,17 @@ __device__ __forceinline__ void softmax_tile_impl(const FaTmemParams& p, uint32_
 
 // The mask and soft-cap tests are compile-time so that the common case (a tile every row sees whole, no cap)
 // carries no predicated instructions: this code runs one warp per scheduler and every issue slot counts.
+template <int D>
 __device__ __forceinline__ void softmax_tile(const FaTmemParams& p, uint32_t t_s, uint32_t t_o, int tok0, int lim,
                                              int beg, bool full, bool have_o, float& m_used, float& l) {
-  if (p.softcap > 0.f) softmax_tile_impl<false, true>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
-  else if (full) softmax_tile_impl<true, false>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
-  else softmax_tile_impl<false, false>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
+  if (p.softcap > 0.f) softmax_tile_impl<D, false, true>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
+  else if (full) softmax_tile_impl<D, true, false>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
+  else softmax_tile_impl<D, false, false>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
 }
 
 // Final normalisation (with the head's sink, if any) and store of one row of O. The tensor memory loads are
 // warp-wide, so rows past the tile's last query take part and only skip the store.
+template <int D>
 __device__ __forceinline__ void store_row(const FaTmemParams& p, uint32_t t_o, bool valid, int token, int head,
                                           float m_used, float l) {
   float ll = l, c = 1.f;
@@ -196,9 +199,9 @@ __device__ __forceinline__ void store_row(const FaTmemParams& p, uint32_t t_o, b
     ll = ll * c + ex2(sk2 - mn);
   }
   const float inv = ll > 0.f ? c / ll : 0.f;
-  __nv_bfloat16* dst = p.out + (size_t)token * p.ldo + (size_t)head * kDT;
+  __nv_bfloat16* dst = p.out + (size_t)token * p.ldo + (size_t)head * D;
 #pragma unroll 1
-  for (int cc = 0; cc < 4; ++cc) {
+  for (int cc = 0; cc < D / 32; ++cc) {
     uint32_t orow[32];
     tmem_ld_32x32(t_o + 32 * cc, orow);
     tmem_ld_wait();
@@ -216,15 +219,17 @@ __device__ __forceinline__ void store_row(const FaTmemParams& p, uint32_t t_o, b
   }
 }
 
+template <int D>
 __global__ void __launch_bounds__(kThreadsT, 2)
 fa_prefill_tmem_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_constant__ CUtensorMap tma_v,
                        const FaTmemParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sq = smem;
-  uint8_t* sk = smem + kTileBytes;
-  uint8_t* sv = smem + 2 * kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTileBytes);
+  constexpr int TB = tile_bytes<D>();
+  uint8_t* sk = smem + TB;
+  uint8_t* sv = smem + 2 * TB;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * TB);
   uint64_t* k_full = bars + 0;
   uint64_t* v_full = bars + 1;
   uint64_t* k_empty = bars + 2;
@@ -264,12 +269,12 @@ fa_prefill_tmem_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_c
   if (warp == 0 && lane == 0) { tma_prefetch_desc(&tma_k); tma_prefetch_desc(&tma_v); }
   if (warp == 1) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
   // Q rows -> shared memory in the layout TMA's 128-byte swizzle would have produced
-  for (int i = threadIdx.x; i < kRowsT * (kDT / 8); i += kThreadsT) {
-    const int r = i >> 4, c = i & 15;
+  for (int i = threadIdx.x; i < kRowsT * (D / 8); i += kThreadsT) {
+    const int r = i / (D / 8), c = i % (D / 8);
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < n_rows) {
       const int qi = r / G, hg = r - qi * G;
-      v = *reinterpret_cast<const uint4*>(p.q + (size_t)(q0 + qi0 + qi) * p.ldq + (size_t)(kvh * G + hg) * kDT + c * 8);
+      v = *reinterpret_cast<const uint4*>(p.q + (size_t)(q0 + qi0 + qi) * p.ldq + (size_t)(kvh * G + hg) * D + c * 8);
     }
     *reinterpret_cast<uint4*>(sq + (c >> 3) * kHalfBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
   }
@@ -299,18 +304,18 @@ fa_prefill_tmem_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_c
           nxt[pg] = table[min(page1 + pg, last_page)];
         }
         if (it > 0 && !mbar_wait(k_empty, (it - 1) & 1, abort_flag)) break;
-        mbar_expect_tx(k_full, kTileBytes);
+        mbar_expect_tx(k_full, TB);
 #pragma unroll
         for (int pg = 0; pg < kTileT / kPageT; ++pg) {
-          tma_load_2d(sk + pg * 2048, &tma_k, k_full, 0, rows[pg]);
-          tma_load_2d(sk + kHalfBytes + pg * 2048, &tma_k, k_full, 64, rows[pg]);
+#pragma unroll
+          for (int h = 0; h < D / 64; ++h) tma_load_2d(sk + h * kHalfBytes + pg * 2048, &tma_k, k_full, 64 * h, rows[pg]);
         }
         if (it > 0 && !mbar_wait(v_empty, (it - 1) & 1, abort_flag)) break;
-        mbar_expect_tx(v_full, kTileBytes);
+        mbar_expect_tx(v_full, TB);
 #pragma unroll
         for (int pg = 0; pg < kTileT / kPageT; ++pg) {
-          tma_load_2d(sv + pg * 2048, &tma_v, v_full, 0, rows[pg]);
-          tma_load_2d(sv + kHalfBytes + pg * 2048, &tma_v, v_full, 64, rows[pg]);
+#pragma unroll
+          for (int h = 0; h < D / 64; ++h) tma_load_2d(sv + h * kHalfBytes + pg * 2048, &tma_v, v_full, 64 * h, rows[pg]);
         }
       }
     }
@@ -325,7 +330,7 @@ fa_prefill_tmem_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_c
         if (!mbar_wait(k_full, ph, abort_flag)) break;
         tc_fence_after_sync();
 #pragma unroll
-        for (int k = 0; k < kDT / 16; ++k) {
+        for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
           tc_mma_bf16(t_s, make_smem_desc_sw128(q_addr + off), make_smem_desc_sw128(k_addr + off), idesc_s, k > 0);
         }
@@ -336,11 +341,12 @@ fa_prefill_tmem_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_c
 #pragma unroll
         for (int k = 0; k < kTileT / 16; ++k) {
           const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
-          if (p.pv_wide) {      // the second 64-wide atom of V's rows lies one half tile further: the leading offset
+          if (D == 128 && p.pv_wide) {      // the second 64-wide atom of V's rows lies one half tile further: the leading offset
             tc_mma_bf16_ts(t_o, t_s + 8 * k, smem_desc_sw128_1k(v_addr + k * 2048, kHalfBytes), idesc_pv_wide, acc);
           } else {
             tc_mma_bf16_ts(t_o, t_s + 8 * k, smem_desc_sw128_1k(v_addr + k * 2048), idesc_pv, acc);
-            tc_mma_bf16_ts(t_o + 64, t_s + 8 * k, smem_desc_sw128_1k(v_addr + kHalfBytes + k * 2048), idesc_pv, acc);
+            if (D == 128)
+              tc_mma_bf16_ts(t_o + 64, t_s + 8 * k, smem_desc_sw128_1k(v_addr + kHalfBytes + k * 2048), idesc_pv, acc);
           }
         }
         tc_commit(v_empty);
@@ -364,7 +370,7 @@ fa_prefill_tmem_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_c
       tc_fence_after_sync();
       // whole tile visible to every row of the CTA: no per-element mask
       const bool full = p.window == 0 && tok0 + kTileT <= first_pos + 1 && n_rows == kRowsT;
-      softmax_tile(p, t_s + lane_off, t_o + lane_off, tok0, lim, beg, full, it > 0, m_used, l);
+      softmax_tile<D>(p, t_s + lane_off, t_o + lane_off, tok0, lim, beg, full, it > 0, m_used, l);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
@@ -372,7 +378,7 @@ fa_prefill_tmem_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_c
     if (ok && mbar_wait(o_done, 0, abort_flag)) {
       tc_fence_after_sync();
       const int qi = r / G, hg = r - qi * G;
-      store_row(p, t_o + lane_off, r < n_rows, q0 + qi0 + qi, kvh * G + hg, m_used, l);
+      store_row<D>(p, t_o + lane_off, r < n_rows, q0 + qi0 + qi, kvh * G + hg, m_used, l);
     }
   }
   tc_fence_before_sync();
@@ -387,17 +393,19 @@ fa_prefill_tmem_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_c
 // (PV0, next S0, PV1, next S1) so that one group's softmax runs under the other tile's MMAs; K and V are
 // double buffered. Tensor memory: S0 S1 O0 O1 = 512 columns, one CTA per SM.
 constexpr int kThreadsT2 = 320;
-constexpr int kSmemT2 = 6 * kTileBytes + 256 + 1024;
+template <int D> constexpr int smem_two() { return 6 * tile_bytes<D>() + 256 + 1024; }
 
+template <int D>
 __global__ void __launch_bounds__(kThreadsT2, 1)
 fa_prefill_tmem2_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_constant__ CUtensorMap tma_v,
                         const FaTmemParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sq = smem;                          // two query tiles
-  uint8_t* sk = smem + 2 * kTileBytes;         // two stages
-  uint8_t* sv = smem + 4 * kTileBytes;         // two stages
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileBytes);
+  constexpr int TB = tile_bytes<D>();
+  uint8_t* sk = smem + 2 * TB;                 // two stages
+  uint8_t* sv = smem + 4 * TB;                 // two stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TB);
   uint64_t* k_full = bars + 0;                 // [2] by stage
   uint64_t* v_full = bars + 2;
   uint64_t* k_empty = bars + 4;
@@ -439,15 +447,15 @@ fa_prefill_tmem2_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_
   }
   if (warp == 0 && lane == 0) { tma_prefetch_desc(&tma_k); tma_prefetch_desc(&tma_v); }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
-  for (int i = threadIdx.x; i < 2 * kRowsT * (kDT / 8); i += kThreadsT2) {
-    const int r = i >> 4, c = i & 15;
+  for (int i = threadIdx.x; i < 2 * kRowsT * (D / 8); i += kThreadsT2) {
+    const int r = i / (D / 8), c = i % (D / 8);
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < n_rows) {
       const int qi = r / G, hg = r - qi * G;
-      v = *reinterpret_cast<const uint4*>(p.q + (size_t)(q0 + qi0 + qi) * p.ldq + (size_t)(kvh * G + hg) * kDT + c * 8);
+      v = *reinterpret_cast<const uint4*>(p.q + (size_t)(q0 + qi0 + qi) * p.ldq + (size_t)(kvh * G + hg) * D + c * 8);
     }
     const int rr = r & (kRowsT - 1);
-    *reinterpret_cast<uint4*>(sq + (r >> 7) * kTileBytes + (c >> 3) * kHalfBytes + rr * 128 + (((c & 7) ^ (rr & 7)) << 4)) = v;
+    *reinterpret_cast<uint4*>(sq + (r >> 7) * TB + (c >> 3) * kHalfBytes + rr * 128 + (((c & 7) ^ (rr & 7)) << 4)) = v;
   }
   fence_proxy_async_smem();
   tc_fence_before_sync();
@@ -473,20 +481,20 @@ fa_prefill_tmem2_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_
           nxt[pg] = table[min(page1 + pg, last_page)];
         }
         if (it >= 2 && !mbar_wait(&k_empty[b], prev, abort_flag)) break;
-        mbar_expect_tx(&k_full[b], kTileBytes);
-        uint8_t* kd = sk + b * kTileBytes;
+        mbar_expect_tx(&k_full[b], TB);
+        uint8_t* kd = sk + b * TB;
 #pragma unroll
         for (int pg = 0; pg < kTileT / kPageT; ++pg) {
-          tma_load_2d(kd + pg * 2048, &tma_k, &k_full[b], 0, rows[pg]);
-          tma_load_2d(kd + kHalfBytes + pg * 2048, &tma_k, &k_full[b], 64, rows[pg]);
+#pragma unroll
+          for (int h = 0; h < D / 64; ++h) tma_load_2d(kd + h * kHalfBytes + pg * 2048, &tma_k, &k_full[b], 64 * h, rows[pg]);
         }
         if (it >= 2 && !mbar_wait(&v_empty[b], prev, abort_flag)) break;
-        mbar_expect_tx(&v_full[b], kTileBytes);
-        uint8_t* vd = sv + b * kTileBytes;
+        mbar_expect_tx(&v_full[b], TB);
+        uint8_t* vd = sv + b * TB;
 #pragma unroll
         for (int pg = 0; pg < kTileT / kPageT; ++pg) {
-          tma_load_2d(vd + pg * 2048, &tma_v, &v_full[b], 0, rows[pg]);
-          tma_load_2d(vd + kHalfBytes + pg * 2048, &tma_v, &v_full[b], 64, rows[pg]);
+#pragma unroll
+          for (int h = 0; h < D / 64; ++h) tma_load_2d(vd + h * kHalfBytes + pg * 2048, &tma_v, &v_full[b], 64 * h, rows[pg]);
         }
       }
     }
@@ -498,23 +506,24 @@ fa_prefill_tmem2_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_
       const uint32_t q_addr = smem_u32(sq), k_addr = smem_u32(sk), v_addr = smem_u32(sv);
       auto issue_s = [&](int g, int stage) {
 #pragma unroll
-        for (int k = 0; k < kDT / 16; ++k) {
+        for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          tc_mma_bf16(tmem_base + 128 * g, make_smem_desc_sw128(q_addr + g * kTileBytes + off),
-                      make_smem_desc_sw128(k_addr + stage * kTileBytes + off), idesc_s, k > 0);
+          tc_mma_bf16(tmem_base + 128 * g, make_smem_desc_sw128(q_addr + g * TB + off),
+                      make_smem_desc_sw128(k_addr + stage * TB + off), idesc_s, k > 0);
         }
       };
       auto issue_pv = [&](int g, int stage, bool first) {
         const uint32_t t_p = tmem_base + 128 * g, t_o = tmem_base + 256 + 128 * g;
-        const uint32_t vb = v_addr + stage * kTileBytes;
+        const uint32_t vb = v_addr + stage * TB;
 #pragma unroll
         for (int k = 0; k < kTileT / 16; ++k) {
           const uint32_t acc = (!first || k > 0) ? 1u : 0u;
-          if (p.pv_wide) {
+          if (D == 128 && p.pv_wide) {
             tc_mma_bf16_ts(t_o, t_p + 8 * k, smem_desc_sw128_1k(vb + k * 2048, kHalfBytes), idesc_pv_wide, acc);
           } else {
             tc_mma_bf16_ts(t_o, t_p + 8 * k, smem_desc_sw128_1k(vb + k * 2048), idesc_pv, acc);
-            tc_mma_bf16_ts(t_o + 64, t_p + 8 * k, smem_desc_sw128_1k(vb + kHalfBytes + k * 2048), idesc_pv, acc);
+            if (D == 128)
+              tc_mma_bf16_ts(t_o + 64, t_p + 8 * k, smem_desc_sw128_1k(vb + kHalfBytes + k * 2048), idesc_pv, acc);
           }
         }
       };
@@ -573,7 +582,7 @@ fa_prefill_tmem2_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_
       if (!mbar_wait(&s_full[g], it & 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       const bool full = p.window == 0 && tok0 + kTileT <= group_first + 1 && group_whole;
-      softmax_tile(p, t_s, t_o, tok0, lim, beg, full, it > 0, m_used, l);
+      softmax_tile<D>(p, t_s, t_o, tok0, lim, beg, full, it > 0, m_used, l);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[g]);
@@ -581,7 +590,7 @@ fa_prefill_tmem2_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_
     if (ok && mbar_wait(o_done, 0, abort_flag)) {
       tc_fence_after_sync();
       const int qi = r / G, hg = r - qi * G;
-      store_row(p, t_o, r < n_rows, q0 + qi0 + qi, kvh * G + hg, m_used, l);
+      store_row<D>(p, t_o, r < n_rows, q0 + qi0 + qi, kvh * G + hg, m_used, l);
     }
   }
   tc_fence_before_sync();
@@ -594,44 +603,64 @@ struct MapKey {
   const void* k;
   const void* v;
   uint64_t rows;
-  bool operator==(const MapKey& o) const { return k == o.k && v == o.v && rows == o.rows; }
+  int d;
+  bool operator==(const MapKey& o) const { return k == o.k && v == o.v && rows == o.rows && d == o.d; }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& x) const {
-    return std::hash<const void*>()(x.k) ^ (std::hash<const void*>()(x.v) * 31) ^ std::hash<uint64_t>()(x.rows);
+    return std::hash<const void*>()(x.k) ^ (std::hash<const void*>()(x.v) * 31) ^ std::hash<uint64_t>()(x.rows * 2 + x.d / 128);
   }
 };
 struct MapPair { CUtensorMap k, v; };
 
+template <int D>
+void launch_tmem(const MapPair& maps, const FaTmemParams& p, int max_q_len, int num_seqs, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    cuda_check(cudaFuncSetAttribute(fa_prefill_tmem_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_one<D>()),
+               "fa_prefill_tmem smem");
+    cuda_check(cudaFuncSetAttribute(fa_prefill_tmem2_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_two<D>()),
+               "fa_prefill_tmem2 smem");
+    configured = true;
+  }
+  // Two query tiles per CTA when that still gives every SM a CTA (FLLM_FA_TMEM_TILES=1 / 2 forces a variant).
+  static int forced = -1;
+  if (forced < 0) { const char* e = getenv("FLLM_FA_TMEM_TILES"); forced = e ? atoi(e) : 0; }
+  const int rq2 = 2 * kRowsT / p.group;
+  const long long ctas2 = (long long)((max_q_len + rq2 - 1) / rq2) * p.hkv * num_seqs;
+  const bool two = forced ? forced == 2 : (max_q_len * p.group >= 2 * kRowsT && ctas2 >= sm_count());
+  if (two) {
+    dim3 grid((max_q_len + rq2 - 1) / rq2, p.hkv, num_seqs);
+    fa_prefill_tmem2_kernel<D><<<grid, kThreadsT2, smem_two<D>(), s>>>(maps.k, maps.v, p);
+  } else {
+    const int rq = kRowsT / p.group;
+    dim3 grid((max_q_len + rq - 1) / rq, p.hkv, num_seqs);
+    fa_prefill_tmem_kernel<D><<<grid, kThreadsT, smem_one<D>(), s>>>(maps.k, maps.v, p);
+  }
+  cuda_check(cudaGetLastError(), "fa_prefill_tmem launch");
+}
+
 }  // namespace
 
 bool attention_prefill_tmem_supported(int head_dim, int group, int block_size) {
-  return head_dim == kDT && block_size == kPageT && group >= 1 && group <= 16 && (kRowsT % group) == 0;
+  return (head_dim == 64 || head_dim == 128) && block_size == kPageT && group >= 1 && group <= 16 && (kRowsT % group) == 0;
 }
 
 // Tensor maps depend only on the cache tensors, so they are built once per (K, V) pair.
 void attention_prefill_tmem(const void* q, long long ldq, const void* k_cache, const void* v_cache, long long num_blocks,
                             const int* block_tables, int max_blocks, const int* q_starts, const int* kv_lens,
                             void* out, long long ldo, int num_seqs, int max_q_len, int min_q, int hq, int hkv,
-                            float scale, int window, const float* sinks, float softcap, int* status,
+                            int head_dim, float scale, int window, const float* sinks, float softcap, int* status,
                             cudaStream_t s) {
   static std::unordered_map<MapKey, MapPair, MapKeyHash> maps;
-  static bool configured = false;
-  if (!configured) {
-    cuda_check(cudaFuncSetAttribute(fa_prefill_tmem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemT),
-               "fa_prefill_tmem smem");
-    cuda_check(cudaFuncSetAttribute(fa_prefill_tmem2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemT2),
-               "fa_prefill_tmem2 smem");
-    configured = true;
-  }
   const uint64_t rows = (uint64_t)num_blocks * hkv * kPageT;
-  const MapKey key{k_cache, v_cache, rows};
+  const MapKey key{k_cache, v_cache, rows, head_dim};
   auto it = maps.find(key);
   if (it == maps.end()) {
     if (maps.size() > 4096) maps.clear();
     MapPair mp;
-    mp.k = make_tmap_2d(k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, kDT, kDT * 2, kPageT, 64, true);
-    mp.v = make_tmap_2d(v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, kDT, kDT * 2, kPageT, 64, true);
+    mp.k = make_tmap_2d(k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, head_dim, head_dim * 2, kPageT, 64, true);
+    mp.v = make_tmap_2d(v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, head_dim, head_dim * 2, kPageT, 64, true);
     it = maps.emplace(key, mp).first;
   }
   FaTmemParams p{};
@@ -646,21 +675,8 @@ void attention_prefill_tmem(const void* q, long long ldq, const void* k_cache, c
   static int wide = -1;
   if (wide < 0) { const char* e = getenv("FLLM_FA_PV_WIDE"); wide = e ? atoi(e) : 1; }
   p.pv_wide = wide;
-  // Two query tiles per CTA when that still gives every SM a CTA (FLLM_FA_TMEM_TILES=1 / 2 forces a variant).
-  static int forced = -1;
-  if (forced < 0) { const char* e = getenv("FLLM_FA_TMEM_TILES"); forced = e ? atoi(e) : 0; }
-  const int rq2 = 2 * kRowsT / p.group;
-  const long long ctas2 = (long long)((max_q_len + rq2 - 1) / rq2) * hkv * num_seqs;
-  const bool two = forced ? forced == 2 : (max_q_len * p.group >= 2 * kRowsT && ctas2 >= sm_count());
-  if (two) {
-    dim3 grid((max_q_len + rq2 - 1) / rq2, hkv, num_seqs);
-    fa_prefill_tmem2_kernel<<<grid, kThreadsT2, kSmemT2, s>>>(it->second.k, it->second.v, p);
-  } else {
-    const int rq = kRowsT / p.group;
-    dim3 grid((max_q_len + rq - 1) / rq, hkv, num_seqs);
-    fa_prefill_tmem_kernel<<<grid, kThreadsT, kSmemT, s>>>(it->second.k, it->second.v, p);
-  }
-  cuda_check(cudaGetLastError(), "fa_prefill_tmem launch");
+  if (head_dim == 64) launch_tmem<64>(it->second, p, max_q_len, num_seqs, s);
+  else launch_tmem<128>(it->second, p, max_q_len, num_seqs, s);
 }
 
 }  // namespace fllm

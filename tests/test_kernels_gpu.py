@@ -241,13 +241,13 @@ def test_attention_tc(ops, ref, D, hq, hkv, window, sinks, softcap, case):
     _close(yg, yr, 2e-2)
 
 
-@pytest.mark.parametrize("hq,hkv", [(8, 8), (8, 2), (16, 2), (32, 8), (16, 1)])
+@pytest.mark.parametrize("D,hq,hkv", [(128, 8, 8), (128, 8, 2), (128, 16, 2), (128, 32, 8), (128, 16, 1),
+                                      (64, 8, 8), (64, 16, 2), (64, 64, 8)])
 @pytest.mark.parametrize("window,sinks,softcap", [(0, False, 0.0), (150, True, 0.0), (0, False, 30.0)])
-def test_attention_prefill_on_tensor_memory(ops, ref, hq, hkv, window, sinks, softcap):
+def test_attention_prefill_on_tensor_memory(ops, ref, D, hq, hkv, window, sinks, softcap):
     """Prompts long enough for several 128-token KV tiles and several 128-row query tiles per sequence go
-    through the tcgen05 prefill kernel (head_dim 128): chunk continuation (kv > q), a ragged tail, causal
+    through the tcgen05 prefill kernel (head_dim 128 and 64): chunk continuation (kv > q), a ragged tail, causal
     diagonal tiles, sliding window, sinks and soft capping against the fp32 reference; status stays 0."""
-    D = 128
     kv_lens, q_lens = [1000, 520, 300, 131], [1000, 200, 300, 40]
     tables, kc, vc = _paged_setup(len(kv_lens), kv_lens, hkv, D, seed=11)
     T = sum(q_lens)
