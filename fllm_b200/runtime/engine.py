@@ -656,7 +656,12 @@ class LLMEngine:
                     self.proposer.forget(r.seq_id)
                 self.requests.pop(r.request_id, None)
             if self.tp_rank == 0:
-                events.append(TokenEvent(r.request_id, new, bool(reason), reason, embedding=getattr(r, "embedding", None)))
+                ev = TokenEvent(r.request_id, new, bool(reason), reason, embedding=getattr(r, "embedding", None))
+                if r.params.logprobs and len(r.logprobs) >= len(new):
+                    ev.logprobs = r.logprobs[-len(new):]
+                    if r.params.top_logprobs > 0 and len(r.top_logprobs) >= len(new):
+                        ev.top_logprobs = r.top_logprobs[-len(new):]
+                events.append(ev)
         return events
 
     def _finish_reason(self, r: Request, new: List[int]) -> Optional[str]:

@@ -85,6 +85,10 @@ class SamplingParams:
             raise ValueError("mirostat: mode 0, 1 or 2 with tau > 0 and eta > 0")
         if self.mirostat_mode:
             self.speculative = False         # the controller's state moves one sampled token at a time
+        if not 0 <= self.top_logprobs <= 20:
+            raise ValueError("top_logprobs must be in [0, 20]")
+        if self.logprobs:
+            self.speculative = False         # one sampled row per emitted token keeps the log-probability lists aligned
         for t in list(self.stop_token_ids) + list((self.logit_bias or {}).keys()):
             if not 0 <= int(t) < vocab_size:
                 raise ValueError(f"token id {t} outside the vocabulary")
@@ -116,6 +120,7 @@ class Request:
     preemptions: int = 0
     draft: List[int] = field(default_factory=list)   # proposed tokens awaiting verification
     logprobs: List[float] = field(default_factory=list)
+    top_logprobs: List[list] = field(default_factory=list)   # per output token: [(token id, log-probability), ...]
     swapped: bool = False            # preempted with its KV parked in host memory
     mirostat: Optional[object] = None  # runtime.logits_processors.Mirostat, created on first use
 
@@ -153,3 +158,4 @@ class TokenEvent:
     logprobs: Optional[List[float]] = None
     error: Optional[str] = None
     embedding: Optional[List[float]] = None
+    top_logprobs: Optional[List[list]] = None

@@ -39,6 +39,13 @@ def sample_step(engine, step, logits: torch.Tensor, greedy: torch.Tensor) -> tor
     idx = torch.tensor([r for r, _, _ in rows], dtype=torch.long, device=logits.device)
     sub = logits.index_select(0, idx).float().contiguous()
     vocab = sub.shape[1]
+    raw_lsm = {}                                       # log-probabilities of the raw distribution (before any filter)
+    for i, (_, req, _) in enumerate(rows):
+        if req.params.logprobs:
+            raw_lsm[i] = torch.log_softmax(sub[i], -1)
+            if req.params.top_logprobs > 0:
+                lp, tid = raw_lsm[i].topk(min(req.params.top_logprobs, vocab))
+                req.top_logprobs.append(list(zip(tid.tolist(), lp.tolist())))
     for i, (_, req, draw) in enumerate(rows):          # typical-p, DRY, Mirostat, banned sequences: edits of the row
         if req.params.needs_host_processors:
             apply_before_sampling(req, sub[i], draw)
@@ -92,14 +99,7 @@ def sample_step(engine, step, logits: torch.Tensor, greedy: torch.Tensor) -> tor
         pen_ids, pen_cnt = to_dev(pen_lists, False)
         b_ids, b_vals = to_dev(bias_lists, True)
         allow_t = torch.from_numpy(allow.view(np.int32)).to(dev) if allow is not None else None
-        want_lp = any(req.params.logprobs for _, req, _ in rows)
-        res = engine.ops.sample(sub, prm, pen_ids, pen_cnt, b_ids, b_vals, allow_t, want_logprobs=want_lp)
-        ids = res[0] if want_lp else res
-        if want_lp:
-            lps = res[1].tolist()
-            for (_, req, _), lp in zip(rows, lps):
-                if req.params.logprobs:
-                    req.logprobs.append(lp)
+        ids = engine.ops.sample(sub, prm, pen_ids, pen_cnt, b_ids, b_vals, allow_t)
     else:
         picked: List[int] = []
         for i, (_, req, draw) in enumerate(rows):
@@ -120,6 +120,11 @@ def sample_step(engine, step, logits: torch.Tensor, greedy: torch.Tensor) -> tor
             prm = params[i]
             picked.append(sample_reference(x, prm[0], prm[6], prm[1], prm[2], prm[8], prm[7]))
         ids = torch.tensor(picked, dtype=torch.int32, device=logits.device)
+    if raw_lsm:
+        picked_ids = ids.tolist()
+        for i, (_, req, _) in enumerate(rows):
+            if i in raw_lsm:
+                req.logprobs.append(float(raw_lsm[i][picked_ids[i]]))
     if any(req.params.mirostat_mode for _, req, _ in rows):
         for (_, req, _), t in zip(rows, ids.tolist()):
             observe_sampled(req, t)

@@ -138,7 +138,8 @@ class EngineWorker:
                     self.metrics.observe("fllm_e2e_request_latency_seconds", now - ent[2])
             self._emit(ev.request_id, {"tokens": ev.token_ids, "finished": ev.finished,
                                        "reason": ev.finish_reason, "error": ev.error,
-                                       "embedding": ev.embedding}, ev.finished)
+                                       "embedding": ev.embedding, "logprobs": ev.logprobs,
+                                       "top_logprobs": ev.top_logprobs}, ev.finished)
 
     def _run(self) -> None:
         eng = self.engine
@@ -191,7 +192,9 @@ def _sampling_from(body: dict, default_max: int = 256, dialect: str = "openai") 
         min_tokens=int(pick("min_tokens", default=0)), ignore_eos=bool(pick("ignore_eos", default=False)),
         stop_token_ids=tuple(pick("stop_token_ids", default=()) or ()), stop=tuple(stop or ()),
         logit_bias={int(k): float(v) for k, v in (g("logit_bias") or {}).items()} or None,
-        allowed_token_ids=g("allowed_token_ids"), logprobs=bool(g("logprobs")),
+        allowed_token_ids=g("allowed_token_ids"), logprobs=g("logprobs") is not None and g("logprobs") is not False,
+        # chat: logprobs true + top_logprobs N; completions: logprobs N
+        top_logprobs=int(g("top_logprobs") or (g("logprobs") if isinstance(g("logprobs"), int) and not isinstance(g("logprobs"), bool) else 0)),
         priority=int(g("priority") or 0), timeout_s=g("timeout"), cache_salt=str(g("cache_salt") or ""),
         typical_p=float(pick("typical_p", "typ_p", default=1.0)),
         dry_multiplier=float(pick("dry_multiplier", default=0.0)), dry_base=float(pick("dry_base", default=1.75)),
@@ -330,7 +333,8 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
                     yield {"text": text, "tokens": item["tokens"], "finished": True, "reason": "stop"}
                     return
                 yield {"text": text, "tokens": item["tokens"], "finished": item["finished"],
-                       "reason": "stop" if chk.hit else item["reason"], "embedding": item.get("embedding")}
+                       "reason": "stop" if chk.hit else item["reason"], "embedding": item.get("embedding"),
+                       "logprobs": item.get("logprobs"), "top_logprobs": item.get("top_logprobs")}
                 if item["finished"]:
                     spans.end_span(span, **{"llm.completion_tokens": n_out, "llm.finish_reason": str(item["reason"])})
                     return
@@ -350,6 +354,36 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
                 reason = piece["reason"] or reason
             return "".join(text), toks, reason or "stop"
         return await rcache.get_or_compute(request_key(model_name, prompt_ids, sp), run)
+
+    async def collect_with_logprobs(prompt_ids, sp):
+        """Like `collect` for requests that ask for log-probabilities (never cached): also returns, per output
+        token, its log-probability and the list of (token id, log-probability) alternatives."""
+        text, toks, lps, tops, reason = [], [], [], [], None
+        async for piece in generate(prompt_ids, sp):
+            text.append(piece["text"])
+            toks.extend(piece["tokens"])
+            lps.extend(piece.get("logprobs") or [None] * len(piece["tokens"]))
+            tops.extend(piece.get("top_logprobs") or [[] for _ in piece["tokens"]])
+            reason = piece["reason"] or reason
+        return "".join(text), toks, reason or "stop", lps, tops
+
+    def piece_text(t: int) -> str:
+        return tokenizer.decode([t])
+
+    def chat_logprobs(toks, lps, tops) -> dict:
+        def ent(t, lp):
+            txt = piece_text(t)
+            return {"token": txt, "logprob": lp, "bytes": list(txt.encode("utf-8", "replace"))}
+        return {"content": [dict(ent(t, lp), top_logprobs=[ent(a, b) for a, b in alt]) for t, lp, alt in zip(toks, lps, tops)]}
+
+    def completion_logprobs(toks, lps, tops) -> dict:
+        texts = [piece_text(t) for t in toks]
+        offs, o = [], 0
+        for x in texts:
+            offs.append(o)
+            o += len(x)
+        return {"tokens": texts, "token_logprobs": lps, "text_offset": offs,
+                "top_logprobs": [{piece_text(a): b for a, b in alt} for alt in tops]}
 
     def attach_guided(sp: SamplingParams, body: dict) -> None:
         """response_format json_object / json_schema (OpenAI) and format: "json" (Ollama) constrain the
@@ -522,9 +556,14 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
                     yield f"data: {json.dumps(chunk)}\n\n"
                 yield "data: [DONE]\n\n"
             return sse(gen())
-        text, toks, reason = await collect(ids, sp)
+        lp_obj = None
+        if sp.logprobs:
+            text, toks, reason, lps, tops = await collect_with_logprobs(ids, sp)
+            lp_obj = completion_logprobs(toks, lps, tops)
+        else:
+            text, toks, reason = await collect(ids, sp)
         return {"id": cid, "object": "text_completion", "created": int(time.time()), "model": model_name,
-                "choices": [{"index": 0, "text": text, "token_ids": toks, "finish_reason": reason, "logprobs": None}],
+                "choices": [{"index": 0, "text": text, "token_ids": toks, "finish_reason": reason, "logprobs": lp_obj}],
                 "usage": usage(len(ids), len(toks))}
 
     def chat_prompt(messages, tools=None) -> List[int]:
@@ -579,11 +618,18 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
                     yield f"data: {json.dumps(chunk)}\n\n"
                 yield "data: [DONE]\n\n"
             return sse(gen())
-        text, toks, reason = await collect(ids, sp)
+        lp_obj = None
+        if sp.logprobs:
+            text, toks, reason, lps, tops = await collect_with_logprobs(ids, sp)
+            lp_obj = chat_logprobs(toks, lps, tops)
+        else:
+            text, toks, reason = await collect(ids, sp)
         msg, has_calls = shape_message(text)
+        choice = {"index": 0, "message": msg, "finish_reason": "tool_calls" if has_calls else reason}
+        if lp_obj is not None:
+            choice["logprobs"] = lp_obj
         return {"id": cid, "object": "chat.completion", "created": int(time.time()), "model": model_name,
-                "choices": [{"index": 0, "message": msg, "finish_reason": "tool_calls" if has_calls else reason}],
-                "usage": usage(len(ids), len(toks))}
+                "choices": [choice], "usage": usage(len(ids), len(toks))}
 
     @app.post("/v1/chat/completions/render")
     async def chat_render(body: dict):

@@ -277,3 +277,28 @@ def test_operator_profiler_counts_calls_by_operator_and_size():
     table = p.table()
     assert "linear" in table and "<=16" in table and ">128" in table
     assert [l for l in table.splitlines() if l.startswith("linear") and "<=16" in l][0].split()[2] == "2"
+
+
+def test_logprobs_and_alternatives_on_both_openai_routes(client):
+    """Greedy decoding: the chosen token is the first alternative, its log-probability equals that alternative's,
+    alternatives are sorted, and probabilities are <= 1. The completions route takes `logprobs: N`."""
+    import math
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 5,
+                                                  "temperature": 0, "logprobs": True, "top_logprobs": 3}).json()
+    content = r["choices"][0]["logprobs"]["content"]
+    assert 1 <= len(content) <= 5
+    for ent in content:
+        alts = ent["top_logprobs"]
+        assert len(alts) == 3 and alts[0]["token"] == ent["token"]
+        assert abs(alts[0]["logprob"] - ent["logprob"]) < 1e-3
+        assert alts[0]["logprob"] >= alts[1]["logprob"] >= alts[2]["logprob"]
+        assert ent["logprob"] <= 1e-6 and sum(math.exp(a["logprob"]) for a in alts) <= 1.0 + 1e-4
+        assert isinstance(ent["bytes"], list)
+    c = client.post("/v1/completions", json={"prompt": "abc", "max_tokens": 4, "temperature": 0, "logprobs": 2}).json()
+    lp = c["choices"][0]["logprobs"]
+    n = len(c["choices"][0]["token_ids"])
+    assert len(lp["tokens"]) == len(lp["token_logprobs"]) == len(lp["top_logprobs"]) == len(lp["text_offset"]) == n
+    assert all(len(d) <= 2 and len(d) >= 1 for d in lp["top_logprobs"]) and lp["text_offset"][0] == 0
+    plain = client.post("/v1/completions", json={"prompt": "abc", "max_tokens": 4, "temperature": 0}).json()
+    assert plain["choices"][0]["logprobs"] is None and plain["choices"][0]["token_ids"] == c["choices"][0]["token_ids"]
+    assert client.post("/v1/completions", json={"prompt": "abc", "logprobs": True, "top_logprobs": 50}).status_code in (400, 422)
