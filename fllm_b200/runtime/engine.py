@@ -695,6 +695,62 @@ class LLMEngine:
             return []
         return [outs[i] for i in ids]
 
+    def beam_search(self, prompt: Sequence[int], beam_width: int = 4, max_tokens: int = 32, length_penalty: float = 1.0,
+                    eos_token_id: Optional[int] = None, early_stopping: bool = True,
+                    other_events: Optional[list] = None) -> "List[tuple]":
+        """Beam search over this engine: -> [(tokens, score)] best first, score = sum of log-probabilities divided
+        by len(tokens) ** length_penalty. Every round submits one one-token request per live beam that asks for
+        its 2 x beam_width best continuations; the beams of a round run as one batch, and the prefix cache makes a
+        beam's request re-use its parent's full KV blocks, so a round computes at most one block per beam
+        Events of other requests that advance while the search steps the engine are appended to
+        `other_events` (rust/engine/src/beam.rs is the reference's beam search)."""
+        if not 1 <= beam_width <= 10:
+            raise ValueError("beam_width must be in [1, 10]")
+        eos = eos_token_id if eos_token_id is not None else self.eos_token_id
+        prompt = [int(t) for t in prompt]
+        norm = lambda toks, lp: lp / (max(len(toks), 1) ** length_penalty)
+        live: "List[tuple]" = [([], 0.0)]
+        done: "List[tuple]" = []
+        room = self.cfg.max_model_len - len(prompt) - 1
+        for _ in range(max(0, min(max_tokens, room))):
+            reqs = []
+            for toks, lp in live:
+                sp = SamplingParams(max_tokens=1, temperature=0.0, logprobs=True, top_logprobs=2 * beam_width, ignore_eos=True)
+                reqs.append((self.requests[self.add_request(prompt + toks, sp)], toks, lp))
+            mine = {r.request_id for r, _, _ in reqs}
+            while any(not r.finished for r, _, _ in reqs):
+                for ev in self.step():
+                    if other_events is not None and ev.request_id not in mine:
+                        other_events.append(ev)
+            if self.tp_rank != 0:
+                continue
+            cands = []
+            for r, toks, lp in reqs:
+                for t, l in (r.top_logprobs[0] if r.top_logprobs else []):
+                    cands.append((toks + [int(t)], lp + float(l)))
+            cands.sort(key=lambda c: -c[1])
+            live = []
+            for toks, lp in cands:
+                if eos is not None and toks[-1] == eos:
+                    if len(live) < beam_width:          # an ended hypothesis only counts while it ranks among the beams
+                        done.append((toks, lp))
+                elif len(live) < beam_width:
+                    live.append((toks, lp))
+                if len(live) >= beam_width:
+                    break
+            if not live:
+                break
+            if early_stopping and len(done) >= beam_width:
+                worst_done = sorted(norm(t, l) for t, l in done)[-beam_width]
+                # log-probabilities only fall: with a length penalty <= 1 no live beam can still overtake
+                if length_penalty <= 1.0 and max(norm(t, l) for t, l in live) <= worst_done:
+                    break
+        if self.tp_rank != 0:
+            return []
+        final = done + live
+        final.sort(key=lambda c: -norm(c[0], c[1]))
+        return [(t, norm(t, l)) for t, l in final[:beam_width]]
+
     def close(self) -> None:
         """Drop captured graphs (they pin the library communicator: it cannot be destroyed while a
         graph that captured one of its collectives is alive) and wait for the device."""

@@ -547,6 +547,26 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
         sp = _sampling_from(body, 16)
         attach_guided(sp, body)
         cid = "cmpl-" + uuid.uuid4().hex
+        if body.get("use_beam_search"):
+            # beam search (non-streaming): `n` / `best_of` hypotheses, best first, with their length-normalised scores
+            width = int(body.get("best_of") or body.get("n") or 4)
+            try:
+                def search(eng):
+                    others: list = []
+                    eos = -1 if sp.ignore_eos else getattr(tokenizer, "eos_token_id", None)     # -1: no token ends a hypothesis
+                    return eng.beam_search(ids, width, sp.max_tokens, float(body.get("length_penalty", 1.0)), eos,
+                                           bool(body.get("early_stopping", True)), others), others
+                beams = await worker.call(search)
+            except ValueError as e:
+                raise HTTPException(400, str(e))
+            eos_id = getattr(tokenizer, "eos_token_id", None)
+            choices = []
+            for i, (toks, score) in enumerate(beams[: int(body.get("n") or width)]):
+                shown = [t for t in toks if t != eos_id]
+                choices.append({"index": i, "text": tokenizer.decode(shown), "token_ids": toks, "logprobs": None,
+                                "finish_reason": "stop" if toks and toks[-1] == eos_id else "length", "beam_score": score})
+            return {"id": cid, "object": "text_completion", "created": int(time.time()), "model": model_name,
+                    "choices": choices, "usage": usage(len(ids), sum(len(c["token_ids"]) for c in choices))}
         if body.get("stream"):
             async def gen():
                 async for piece in generate(ids, sp):

@@ -211,3 +211,46 @@ def test_preemption_by_swap_parks_kv_on_the_host_and_keeps_output():
     none = mk(13, preemption="swap", swap_space_gb=0.0)
     assert none.generate(prompts, sp) == want
     assert none.scheduler.swapper.stats["swapped_out"] == 0 and none.scheduler.stats["preemptions"] > 0
+
+
+def test_beam_search_matches_a_brute_force_search_on_the_oracle():
+    """Width 1 is greedy decoding; width 3 returns sorted hypotheses whose scores are the oracle's summed
+    log-probabilities, and its best hypothesis scores like the best one of an independent beam search over
+    the dense oracle; an end-of-sequence token closes a hypothesis."""
+    cfg = preset("qwen3-tiny")
+    eng = _engine(cfg)
+    prompt = _prompts(cfg.vocab_size, (9,), seed=4)[0]
+    n = 5
+    greedy = greedy_generate(cfg, eng.weights, prompt, n)
+    one = eng.beam_search(prompt, beam_width=1, max_tokens=n, length_penalty=0.0)
+    assert one[0][0] == greedy
+
+    def logp(tokens):
+        return torch.log_softmax(dense_forward(cfg, eng.weights, tokens)[-1].float(), -1)
+
+    def seq_score(toks):
+        return sum(float(logp(prompt + toks[:i])[toks[i]]) for i in range(len(toks)))
+    W = 3
+    got = eng.beam_search(prompt, beam_width=W, max_tokens=n, length_penalty=0.0)
+    assert len(got) == W and all(len(t) == n for t, _ in got)
+    assert [s for _, s in got] == sorted((s for _, s in got), reverse=True)
+    for toks, score in got:
+        assert abs(score - seq_score(toks)) < 0.05 * n
+    beams = [([], 0.0)]
+    for _ in range(n):                                   # independent reference search
+        cands = []
+        for toks, lp in beams:
+            top = logp(prompt + toks).topk(2 * W)
+            cands += [(toks + [int(t)], lp + float(l)) for l, t in zip(top.values, top.indices)]
+        beams = sorted(cands, key=lambda c: -c[1])[:W]
+    assert abs(got[0][1] - beams[0][1]) < 0.05 * n
+    assert got[0][0] == beams[0][0] or abs(seq_score(got[0][0]) - beams[0][1]) < 0.05
+    # with a length penalty the score is the mean log-probability; an EOS ends a hypothesis early
+    eos = got[0][0][1]
+    ended = eng.beam_search(prompt, beam_width=W, max_tokens=n, length_penalty=1.0, eos_token_id=eos)
+    assert any(t[-1] == eos and len(t) < n for t, _ in ended) or all(eos not in t[:-1] for t, _ in ended)
+    for t, s in ended:
+        assert eos not in t[:-1]
+        assert abs(s - seq_score(t) / len(t)) < 0.05
+    assert eng.blocks.num_used() <= eng.blocks.blocks_needed(len(prompt) + n) * 4       # nothing leaks: only cached blocks stay
+    assert not eng.requests

@@ -302,3 +302,18 @@ def test_logprobs_and_alternatives_on_both_openai_routes(client):
     plain = client.post("/v1/completions", json={"prompt": "abc", "max_tokens": 4, "temperature": 0}).json()
     assert plain["choices"][0]["logprobs"] is None and plain["choices"][0]["token_ids"] == c["choices"][0]["token_ids"]
     assert client.post("/v1/completions", json={"prompt": "abc", "logprobs": True, "top_logprobs": 50}).status_code in (400, 422)
+
+
+def test_beam_search_over_http_returns_ranked_hypotheses(client):
+    body = {"prompt": "beam", "max_tokens": 4, "use_beam_search": True, "n": 3, "length_penalty": 0.0}
+    r = client.post("/v1/completions", json=body)
+    assert r.status_code == 200
+    ch = r.json()["choices"]
+    assert len(ch) == 3 and [c["index"] for c in ch] == [0, 1, 2]
+    scores = [c["beam_score"] for c in ch]
+    assert scores == sorted(scores, reverse=True) and all(s <= 0 for s in scores)
+    assert len({tuple(c["token_ids"]) for c in ch}) == 3
+    greedy = client.post("/v1/completions", json={"prompt": "beam", "max_tokens": 4, "temperature": 0, "ignore_eos": True}).json()
+    one = client.post("/v1/completions", json={**body, "n": 1, "ignore_eos": True}).json()["choices"][0]
+    assert one["token_ids"] == greedy["choices"][0]["token_ids"]
+    assert client.post("/v1/completions", json={**body, "n": 50}).status_code == 400
