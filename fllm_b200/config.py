@@ -57,6 +57,8 @@ class ModelConfig:
     sliding_window: int = 0              # 0 = full attention
     window_pattern: Optional[List[int]] = None   # per layer: 1 = windowed, 0 = full
     attn_sinks: bool = False             # learned per-head sink logit (gpt-oss)
+    attn_scale: Optional[float] = None   # softmax scale when it is not head_dim ** -0.5 (Gemma-2: query_pre_attn_scalar ** -0.5)
+    post_norms: bool = False             # Gemma-2: the attention and FFN outputs are normalised before the residual add
     # mixture of experts
     num_experts: int = 0
     experts_per_token: int = 0
@@ -171,6 +173,14 @@ class ModelConfig:
             cfg.tie_embeddings = hf.get("tie_word_embeddings", True)
             cfg.logit_softcap = float(hf.get("final_logit_softcapping") or 0.0)
             cfg.attn_softcap = float(hf.get("attn_logit_softcapping") or 0.0)
+        if mt == "gemma2":
+            cfg.post_norms = True
+            if hf.get("query_pre_attn_scalar"):
+                cfg.attn_scale = float(hf["query_pre_attn_scalar"]) ** -0.5
+            if hf.get("sliding_window"):
+                cfg.sliding_window = int(hf["sliding_window"])
+                lt = hf.get("layer_types")
+                cfg.window_pattern = [1 if t == "sliding_attention" else 0 for t in lt] if lt else [1, 0]
         if mt in ("phi3", "phi"):
             cfg.rotary_dim = int(cfg.head_dim * hf.get("partial_rotary_factor", 1.0)) or None
         if hf.get("sliding_window") and hf.get("use_sliding_window", mt == "mistral"):

@@ -90,8 +90,14 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
             f = lin(p + "self_attn.qkv_proj")
             q, k, v = rows(f, slice(0, nq)), rows(f, slice(nq, nq + nk)), rows(f, slice(nq + nk, nq + 2 * nk))
         fp8 = isinstance(q, torch.Tensor) and q.dtype == torch.float8_e4m3fn
-        lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
-                          ffn_norm=dev(get(p + "post_attention_layernorm.weight")))
+        if cfg.post_norms:                     # Gemma-2: post_attention_layernorm normalises the attention OUTPUT
+            lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
+                              ffn_norm=dev(get(p + "pre_feedforward_layernorm.weight")),
+                              post_attn_norm=dev(get(p + "post_attention_layernorm.weight")),
+                              post_ffn_norm=dev(get(p + "post_feedforward_layernorm.weight")))
+        else:
+            lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
+                              ffn_norm=dev(get(p + "post_attention_layernorm.weight")))
         o = lin(p + "self_attn.o_proj")
         if cfg.is_moe:
             _load_moe_layer(cfg, sp, tp_rank, lw, p, get, dev)

@@ -79,7 +79,7 @@ class Decoder:
         inv, attn = rope_inv_freq(cfg)
         self.inv_freq = torch.tensor(inv, dtype=torch.float32, device=dev)
         self.attn_factor = attn
-        self.scale = cfg.head_dim ** -0.5
+        self.scale = cfg.attn_scale if cfg.attn_scale else cfg.head_dim ** -0.5
         self.rope_style = 0 if cfg.rope_style == "neox" else 1
         self.act_kind = ACT_KIND[cfg.act]
         # packed payloads loaded from a checkpoint become weight objects that pick their own kernel
@@ -151,11 +151,15 @@ class Decoder:
                 torch.cuda.nvtx.range_push(f"layer{li}.attn")
             h = ops.rmsnorm(x, delta, lw.attn_norm, cfg.rms_eps, cfg.norm_weight_offset)
             o = self._reduce(self._attention_block(li, lw, h, b))
+            if lw.post_attn_norm is not None:
+                o = ops.rmsnorm(o, None, lw.post_attn_norm, cfg.rms_eps, cfg.norm_weight_offset)
             if nvtx:
                 torch.cuda.nvtx.range_pop()
                 torch.cuda.nvtx.range_push(f"layer{li}.ffn")
             h = ops.rmsnorm(x, o, lw.ffn_norm, cfg.rms_eps, cfg.norm_weight_offset)
             delta = self._reduce(self._ffn_block(lw, h))
+            if lw.post_ffn_norm is not None:
+                delta = ops.rmsnorm(delta, None, lw.post_ffn_norm, cfg.rms_eps, cfg.norm_weight_offset)
             if nvtx:
                 torch.cuda.nvtx.range_pop()
         return x, delta
@@ -164,7 +168,8 @@ class Decoder:
     @property
     def fused_tp(self) -> bool:
         return (self.tp is not None and getattr(self.tp, "backend", "") == "fused" and self.tp.size > 1
-                and not self.cfg.is_moe and self.first_stage and self.last_stage and self._dense_weights)
+                and not self.cfg.is_moe and not self.cfg.post_norms and self.first_stage and self.last_stage
+                and self._dense_weights)
 
     def forward_fused(self, b: StepBatch) -> torch.Tensor:
         """Whole forward with the sequence-sharded residual: every projection output leaves the

@@ -31,6 +31,8 @@ class LayerWeights:
     q_norm: Optional[torch.Tensor] = None
     k_norm: Optional[torch.Tensor] = None
     sinks: Optional[torch.Tensor] = None
+    post_attn_norm: Optional[torch.Tensor] = None   # Gemma-2: norm of the attention output before the residual add
+    post_ffn_norm: Optional[torch.Tensor] = None    # Gemma-2: norm of the FFN output before the residual add
     w_gate_up: Optional[torch.Tensor] = None
     w_down: Optional[torch.Tensor] = None
     # mixture of experts
@@ -177,6 +179,9 @@ def init_random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, se
             lw.bo = bo if tp_rank == 0 else torch.zeros_like(bo)
         if cfg.qk_norm:
             lw.q_norm, lw.k_norm = ones(D), ones(D)
+        if cfg.post_norms:               # not all ones, so that a test sees whether they are applied
+            lw.post_attn_norm = (1.0 + 0.5 * full((H,), li, 15, std=1.0)).contiguous()
+            lw.post_ffn_norm = (1.0 + 0.5 * full((H,), li, 16, std=1.0)).contiguous()
         if cfg.attn_sinks:
             s = torch.randn(cfg.num_heads, generator=gen_for(li, 14), device=device) * 0.5
             lw.sinks = s[sp.q_head_start: sp.q_head_start + sp.hq_local].float().contiguous()

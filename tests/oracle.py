@@ -53,7 +53,7 @@ def dense_forward(cfg: ModelConfig, w, tokens, round_bf16=True):
         q, k = r(rope(q)), r(rope(k))
         g = hq // hkv
         kk, vv = k.repeat_interleave(g, 1), v.repeat_interleave(g, 1)
-        s = torch.einsum("thd,shd->hts", q, kk) * D ** -0.5
+        s = torch.einsum("thd,shd->hts", q, kk) * (cfg.attn_scale if cfg.attn_scale else D ** -0.5)
         if cfg.attn_softcap > 0:
             s = cfg.attn_softcap * torch.tanh(s / cfg.attn_softcap)
         i = torch.arange(T, device=x.device)
@@ -71,6 +71,8 @@ def dense_forward(cfg: ModelConfig, w, tokens, round_bf16=True):
         o = a @ lw.wo.float().t()
         if lw.bo is not None:
             o = o + lw.bo.float()
+        if lw.post_attn_norm is not None:
+            o = _rms(r(o), lw.post_attn_norm, cfg.rms_eps, cfg.norm_weight_offset)
         x = r(x + r(o))
         h = r(_rms(x, lw.ffn_norm, cfg.rms_eps, cfg.norm_weight_offset))
         if cfg.is_moe:
@@ -79,8 +81,11 @@ def dense_forward(cfg: ModelConfig, w, tokens, round_bf16=True):
         else:
             gu = r(h @ lw.w_gate_up.float().t())
             I = gu.shape[1] // 2
-            act = r(F.silu(gu[:, :I]) * gu[:, I:])
+            gate = F.gelu(gu[:, :I], approximate="tanh") if cfg.act == "geglu" else F.silu(gu[:, :I])
+            act = r(gate * gu[:, I:])
             d = act @ lw.w_down.float().t()
+        if lw.post_ffn_norm is not None:
+            d = _rms(r(d), lw.post_ffn_norm, cfg.rms_eps, cfg.norm_weight_offset)
         x = r(x + r(d))
     h = r(_rms(x, w.final_norm, cfg.rms_eps, cfg.norm_weight_offset))
     return r(h @ w.lm_head.float().t())[:, : cfg.vocab_size]

@@ -487,3 +487,61 @@ def test_phi3_fused_projections_load_like_the_split_ones(tmp_path):
     sp = SamplingParams(max_tokens=5)
     prompt = [[3, 1, 4, 1, 5, 9, 2, 6]]
     assert LLMEngine(cfg2, ec, device="cpu", weights=w2).generate(prompt, sp) == LLMEngine(cfg, ec, device="cpu", weights=w).generate(prompt, sp)
+
+
+def test_gemma2_post_norms_scale_and_window_pattern(tmp_path):
+    """Gemma-2: the attention and FFN outputs go through their own RMSNorm before the residual add, the softmax
+    scale comes from query_pre_attn_scalar, layers alternate sliding / full attention. The engine must match the
+    dense oracle, and an HF-style checkpoint (four norm tensors per layer) must load into the same model."""
+    import json
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    from fllm_b200.formats.safetensors_io import save_file
+    from fllm_b200.models.weights import init_random_weights
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    from oracle import dense_forward, greedy_generate
+    cfg = preset("tiny-llama")
+    cfg.vocab_size, cfg.intermediate_size = 512, 512
+    cfg.post_norms, cfg.attn_scale, cfg.act = True, 24.0 ** -0.5, "geglu"
+    cfg.norm_weight_offset, cfg.embed_scale, cfg.tie_embeddings = 1.0, float(cfg.hidden_size) ** 0.5, True
+    cfg.attn_softcap, cfg.logit_softcap, cfg.sliding_window, cfg.window_pattern = 50.0, 30.0, 16, [1, 0]
+    w = init_random_weights(cfg, "cpu", seed=8)
+    w.lm_head = w.embed
+    for lw in w.layers:                                   # (1 + w) norms: keep the effective weights near one
+        lw.post_attn_norm, lw.post_ffn_norm = lw.post_attn_norm - 1.0, lw.post_ffn_norm - 1.0
+        lw.attn_norm, lw.ffn_norm = lw.attn_norm - 1.0, lw.ffn_norm - 1.0
+    w.final_norm = w.final_norm - 1.0
+    ec = EngineConfig(max_num_seqs=2, max_num_batched_tokens=32, max_model_len=96, num_kv_blocks=16)
+    prompt = [int(t) for t in torch.randint(0, 512, (40,), generator=torch.Generator().manual_seed(1))]
+    eng = LLMEngine(cfg, ec, device="cpu", weights=w)
+    assert eng.generate([prompt], SamplingParams(max_tokens=5))[0] == greedy_generate(cfg, w, prompt, 5)
+    # the post norms matter: without them the logits differ
+    a = dense_forward(cfg, w, prompt)[-1]
+    saved = [(lw.post_attn_norm, lw.post_ffn_norm) for lw in w.layers]
+    for lw in w.layers:
+        lw.post_attn_norm = lw.post_ffn_norm = None
+    assert (dense_forward(cfg, w, prompt)[-1] - a).abs().max() > 1e-3
+    for lw, (pa, pf) in zip(w.layers, saved):
+        lw.post_attn_norm, lw.post_ffn_norm = pa, pf
+    D, hq, hkv, I = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads, cfg.intermediate_size
+    t = {"model.embed_tokens.weight": w.embed, "model.norm.weight": w.final_norm}
+    for l, lw in enumerate(w.layers):
+        p = f"model.layers.{l}."
+        t.update({p + "input_layernorm.weight": lw.attn_norm, p + "post_attention_layernorm.weight": lw.post_attn_norm,
+                  p + "pre_feedforward_layernorm.weight": lw.ffn_norm, p + "post_feedforward_layernorm.weight": lw.post_ffn_norm,
+                  p + "self_attn.q_proj.weight": lw.wqkv[: hq * D], p + "self_attn.k_proj.weight": lw.wqkv[hq * D: (hq + hkv) * D],
+                  p + "self_attn.v_proj.weight": lw.wqkv[(hq + hkv) * D:], p + "self_attn.o_proj.weight": lw.wo,
+                  p + "mlp.gate_proj.weight": lw.w_gate_up[:I], p + "mlp.up_proj.weight": lw.w_gate_up[I:],
+                  p + "mlp.down_proj.weight": lw.w_down})
+    save_file({k: v.contiguous() for k, v in t.items()}, str(tmp_path / "model.safetensors"))
+    hf = {"model_type": "gemma2", "vocab_size": 512, "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
+          "num_attention_heads": hq, "num_key_value_heads": hkv, "head_dim": D, "intermediate_size": I,
+          "rms_norm_eps": cfg.rms_eps, "rope_theta": cfg.rope_theta, "max_position_embeddings": 4096,
+          "query_pre_attn_scalar": 24, "sliding_window": 16, "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0}
+    json.dump(hf, open(tmp_path / "config.json", "w"))
+    cfg2, w2, _ = load_hf_checkpoint(str(tmp_path), device="cpu")
+    assert cfg2.post_norms and abs(cfg2.attn_scale - 24.0 ** -0.5) < 1e-9 and cfg2.window_pattern == [1, 0]
+    assert cfg2.layer_window(0) == 16 and cfg2.layer_window(1) == 0 and cfg2.act == "geglu" and cfg2.tie_embeddings
+    assert torch.equal(w2.layers[1].post_ffn_norm, w.layers[1].post_ffn_norm)
+    eng2 = LLMEngine(cfg2, ec, device="cpu", weights=w2)
+    assert eng2.generate([prompt], SamplingParams(max_tokens=5))[0] == eng.generate([prompt], SamplingParams(max_tokens=5))[0]
