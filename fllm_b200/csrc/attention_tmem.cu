@@ -79,7 +79,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_1k(uint32_t saddr, uint32_t 
 // One row (thread) of the softmax over one 128-token tile: reads S from tensor memory, updates the row's
 // reference maximum and sum, writes P as bf16 over S's first 64 columns and, when the maximum of any row of
 // the warp moved by more than 2^8, rescales the warp's rows of O. `t_s` / `t_o` already carry the lane offset.
-template <int D, bool full, bool capped>
+template <int D, bool full, bool capped, bool windowed>
 __device__ __forceinline__ void softmax_tile_impl(const FaTmemParams& p, uint32_t t_s, uint32_t t_o, int tok0, int lim,
                                                   int beg, bool have_o, float& m_used, float& l) {
   const float cap_in = capped ? p.scale / p.softcap : 0.f;
@@ -93,7 +93,8 @@ __device__ __forceinline__ void softmax_tile_impl(const FaTmemParams& p, uint32_
     tmem_ld_32x32(t_s + 64 * h, sa);
     tmem_ld_32x32(t_s + 64 * h + 32, sb);
     tmem_ld_wait();
-    const int t0 = tok0 + 64 * h;
+    // columns [lo, hi) of these 64 are visible to this row: one compare (two with a window) per element
+    const int hi = lim - (tok0 + 64 * h), lo = beg - (tok0 + 64 * h);
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
       float a0 = __uint_as_float(sa[i]), a1 = __uint_as_float(sa[i + 1]);
@@ -102,10 +103,10 @@ __device__ __forceinline__ void softmax_tile_impl(const FaTmemParams& p, uint32_
         a0 = tanhf(a0 * cap_in); a1 = tanhf(a1 * cap_in); b0 = tanhf(b0 * cap_in); b1 = tanhf(b1 * cap_in);
       }
       if (!full) {
-        if (t0 + i >= lim || t0 + i < beg) a0 = -INFINITY;
-        if (t0 + i + 1 >= lim || t0 + i + 1 < beg) a1 = -INFINITY;
-        if (t0 + 32 + i >= lim || t0 + 32 + i < beg) b0 = -INFINITY;
-        if (t0 + 33 + i >= lim || t0 + 33 + i < beg) b1 = -INFINITY;
+        if (i >= hi || (windowed && i < lo)) a0 = -INFINITY;
+        if (i + 1 >= hi || (windowed && i + 1 < lo)) a1 = -INFINITY;
+        if (i + 32 >= hi || (windowed && i + 32 < lo)) b0 = -INFINITY;
+        if (i + 33 >= hi || (windowed && i + 33 < lo)) b1 = -INFINITY;
       }
       mx0 = fmaxf(mx0, a0); mx1 = fmaxf(mx1, a1); mx2 = fmaxf(mx2, b0); mx3 = fmaxf(mx3, b1);
     }
@@ -130,7 +131,7 @@ __device__ __forceinline__ void softmax_tile_impl(const FaTmemParams& p, uint32_
     tmem_ld_32x32(t_s + 64 * h, sa);
     tmem_ld_32x32(t_s + 64 * h + 32, sb);
     tmem_ld_wait();
-    const int t0 = tok0 + 64 * h;
+    const int hi = lim - (tok0 + 64 * h), lo = beg - (tok0 + 64 * h);
     uint32_t pa[16], pb[16];
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
@@ -145,10 +146,10 @@ __device__ __forceinline__ void softmax_tile_impl(const FaTmemParams& p, uint32_
       }
       a0 = ex2(a0); a1 = ex2(a1); b0 = ex2(b0); b1 = ex2(b1);
       if (!full) {
-        if (t0 + i >= lim || t0 + i < beg) a0 = 0.f;
-        if (t0 + i + 1 >= lim || t0 + i + 1 < beg) a1 = 0.f;
-        if (t0 + 32 + i >= lim || t0 + 32 + i < beg) b0 = 0.f;
-        if (t0 + 33 + i >= lim || t0 + 33 + i < beg) b1 = 0.f;
+        if (i >= hi || (windowed && i < lo)) a0 = 0.f;
+        if (i + 1 >= hi || (windowed && i + 1 < lo)) a1 = 0.f;
+        if (i + 32 >= hi || (windowed && i + 32 < lo)) b0 = 0.f;
+        if (i + 33 >= hi || (windowed && i + 33 < lo)) b1 = 0.f;
       }
       sum0 += a0; sum1 += a1; sum2 += b0; sum3 += b1;
       pa[i >> 1] = pack_bf16x2(a0, a1);
@@ -181,9 +182,10 @@ __device__ __forceinline__ void softmax_tile_impl(const FaTmemParams& p, uint32_
 template <int D>
 __device__ __forceinline__ void softmax_tile(const FaTmemParams& p, uint32_t t_s, uint32_t t_o, int tok0, int lim,
                                              int beg, bool full, bool have_o, float& m_used, float& l) {
-  if (p.softcap > 0.f) softmax_tile_impl<D, false, true>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
-  else if (full) softmax_tile_impl<D, true, false>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
-  else softmax_tile_impl<D, false, false>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
+  if (p.softcap > 0.f) softmax_tile_impl<D, false, true, true>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
+  else if (full) softmax_tile_impl<D, true, false, false>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
+  else if (p.window > 0) softmax_tile_impl<D, false, false, true>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
+  else softmax_tile_impl<D, false, false, false>(p, t_s, t_o, tok0, lim, beg, have_o, m_used, l);
 }
 
 // Final normalisation (with the head's sink, if any) and store of one row of O. The tensor memory loads are
