@@ -29,6 +29,9 @@ def _add_engine_flags(p: argparse.ArgumentParser) -> None:
     p.add_argument("--no-cuda-graphs", action="store_true")
     p.add_argument("--scheduling-policy", default="fcfs", choices=["fcfs", "priority"])
     p.add_argument("--preemption", default="recompute", choices=["recompute", "swap"])
+    p.add_argument("--kv-tier-host-gb", type=float, default=0.0, help="host memory for evicted prefix-cache blocks")
+    p.add_argument("--kv-tier-disk-dir", default=None, help="directory for blocks that fall out of the host tier (default $FLLM_KV_DISK_DIR)")
+    p.add_argument("--kv-tier-disk-gb", type=float, default=0.0)
     p.add_argument("--speculative", default="off", choices=["off", "ngram", "draft"])
     p.add_argument("--draft-model", default=None)
     p.add_argument("--draft-tokens", type=int, default=4)
@@ -53,7 +56,8 @@ def build_engine(args):
         gpu_memory_utilization=args.gpu_memory_utilization, kv_cache_dtype=args.kv_cache_type,
         num_kv_blocks=args.kv_blocks, enable_prefix_caching=not args.no_prefix_cache,
         use_cuda_graphs=not args.no_cuda_graphs, scheduling_policy=args.scheduling_policy,
-        preemption=args.preemption, speculative=args.speculative, draft_tokens=args.draft_tokens, seed=args.seed)
+        preemption=args.preemption, speculative=args.speculative, draft_tokens=args.draft_tokens, seed=args.seed,
+        kv_tier_host_gb=args.kv_tier_host_gb, kv_tier_disk_dir=args.kv_tier_disk_dir, kv_tier_disk_gb=args.kv_tier_disk_gb)
     par = ParallelConfig(tp=args.tp, pp=args.pp, expert_parallel=args.expert_parallel, ep_dispatch=args.ep_dispatch,
                          distributed_backend=args.distributed_backend)
     weights, tok_path = None, args.tokenizer

@@ -65,7 +65,12 @@ class BlockManager:
         self.pinned: set = set()
         self.seqs: Dict[int, SeqBlocks] = {}
         self.watermark_blocks = int(watermark * num_blocks)
-        self.stats = {"prefix_queries": 0, "prefix_hits": 0, "evictions": 0, "cow": 0}
+        self.stats = {"prefix_queries": 0, "prefix_hits": 0, "evictions": 0, "cow": 0, "tier_restored": 0}
+        # optional lower tier for evicted prefix blocks (runtime.kv_tier): on_evict(block, hash) is called while
+        # the block still holds its KV; tier_has(hash) / tier_restore(hash, block) bring a block back
+        self.on_evict = None
+        self.tier_has = None
+        self.tier_restore = None
 
     # ------------------------------------------------------------------ pool
     def num_free(self) -> int:
@@ -88,6 +93,8 @@ class BlockManager:
             if b is None:
                 raise MemoryError("out of KV blocks")
             h = self.cached.pop(b)
+            if self.on_evict is not None:
+                self.on_evict(b, h)
             self.hash_to_block.pop(h, None)
             self.block_hash.pop(b, None)
             self.stats["evictions"] += 1
@@ -145,6 +152,26 @@ class BlockManager:
             if self.refs[b] == 0:
                 self.cached.pop(b, None)
             self.refs[b] += 1
+        if self.tier_has is not None and self.enable_prefix_caching:
+            # the prompt may continue with blocks that were evicted to the lower tier: bring them back while the
+            # chain holds and the pool has room beyond its watermark
+            bs = self.block_size
+            parent = hashes[-1] if hashes else b""
+            for i in range(len(blocks), (len(tokens) - 1) // bs):
+                h = chain_hash(parent, tokens[i * bs:(i + 1) * bs], salt)
+                if h in self.hash_to_block or not self.tier_has(h) or not self.can_allocate(1):
+                    break
+                b = self._take()
+                if not self.tier_restore(h, b):
+                    self.refs[b] = 0
+                    self.free.append(b)
+                    break
+                self.hash_to_block[h] = b
+                self.block_hash[b] = h
+                blocks.append(b)
+                hashes.append(h)
+                parent = h
+                self.stats["tier_restored"] += 1
         sb = SeqBlocks(table=list(blocks), num_tokens=len(blocks) * self.block_size, hashes=list(hashes))
         self.seqs[seq_id] = sb
         return sb.num_tokens

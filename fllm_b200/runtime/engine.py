@@ -14,6 +14,8 @@ only one that reports events.
 """
 from __future__ import annotations
 
+import os
+
 import itertools
 import time
 from typing import Dict, Iterable, List, Optional, Sequence
@@ -91,6 +93,10 @@ class LLMEngine:
                                    self.cfg.watermark)
         window = model_cfg.sliding_window if (model_cfg.sliding_window and model_cfg.window_pattern is None) else 0
         self.scheduler = Scheduler(self.cfg, self.blocks, window)
+        self.kv_tier = None
+        disk_dir = self.cfg.kv_tier_disk_dir or os.environ.get("FLLM_KV_DISK_DIR")
+        if self.cfg.enable_prefix_caching and (self.cfg.kv_tier_host_gb > 0 or (disk_dir and self.cfg.kv_tier_disk_gb > 0)):
+            self._attach_kv_tier(disk_dir)
         if self.cfg.preemption == "swap":
             self.scheduler.swapper = _KvSwapper(self)
         self.requests: Dict[str, Request] = {}
@@ -694,6 +700,29 @@ class LLMEngine:
         if self.tp_rank != 0:
             return []
         return [outs[i] for i in ids]
+
+    def _attach_kv_tier(self, disk_dir: Optional[str]) -> None:
+        """Evicted prefix-cache blocks go to host memory / disk under their chain hash and come back when a
+        prompt reaches them again (runtime.kv_tier). Every tensor-parallel rank keeps its own shard."""
+        from .kv_tier import KvTier
+        st = self.kv.store                                   # [layers, 2, blocks, kv heads, block, head dim]
+        block_bytes = st[:, :, 0].numel() * st.element_size()
+        sig = f"{self.model_cfg.name}|{tuple(st[:, :, 0].shape)}|{st.dtype}|tp{self.tp_rank}"
+        if disk_dir and self.tp_rank:
+            disk_dir = os.path.join(disk_dir, f"rank{self.tp_rank}")
+        self.kv_tier = KvTier(sig, block_bytes, int(self.cfg.kv_tier_host_gb * (1 << 30)), disk_dir,
+                              int(self.cfg.kv_tier_disk_gb * (1 << 30)))
+
+        def evict(block: int, h: bytes) -> None:
+            self.kv_tier.put(h, st[:, :, block].contiguous().view(torch.uint8).reshape(-1).cpu())
+
+        def restore(h: bytes, block: int) -> bool:
+            blob = self.kv_tier.get(h)
+            if blob is None:
+                return False
+            st[:, :, block].copy_(blob.view(st.dtype).view(st[:, :, block].shape).to(st.device))
+            return True
+        self.blocks.on_evict, self.blocks.tier_has, self.blocks.tier_restore = evict, self.kv_tier.has, restore
 
     def beam_search(self, prompt: Sequence[int], beam_width: int = 4, max_tokens: int = 32, length_penalty: float = 1.0,
                     eos_token_id: Optional[int] = None, early_stopping: bool = True,

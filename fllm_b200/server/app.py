@@ -532,6 +532,12 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
     async def admin_cache_stats():
         return {"responses": rcache.stats(), "prefix": dict(engine.blocks.stats)}
 
+    @app.get("/admin/kv-tier")
+    async def admin_kv_tier():
+        t = getattr(engine, "kv_tier", None)
+        return {"enabled": bool(t is not None and t.enabled), **(t.info() if t is not None else {}),
+                "restored_blocks": engine.blocks.stats.get("tier_restored", 0)}
+
     # ------------------------------------------------------------------ OpenAI
     @app.get("/v1/models")
     async def models():

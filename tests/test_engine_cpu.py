@@ -254,3 +254,46 @@ def test_beam_search_matches_a_brute_force_search_on_the_oracle():
         assert abs(s - seq_score(t) / len(t)) < 0.05
     assert eng.blocks.num_used() <= eng.blocks.blocks_needed(len(prompt) + n) * 4       # nothing leaks: only cached blocks stay
     assert not eng.requests
+
+
+def test_evicted_prefix_blocks_come_back_from_the_host_and_disk_tiers(tmp_path):
+    """A pool too small to keep every prompt cached: evicted prefix blocks go to host memory, overflow to files,
+    and are restored when their prompt returns: same tokens, prompt tokens served from the cache, and a new
+    engine on the same directory finds the files (re-warm after restart); a different KV layout ignores them."""
+    cfg = preset("qwen3-tiny")
+    w = init_random_weights(cfg, "cpu")
+    prompts = _prompts(cfg.vocab_size, (70, 66, 75, 68), seed=9)
+    sp = SamplingParams(max_tokens=3)
+    kb = LLMEngine(cfg, EngineConfig(max_num_batched_tokens=96, max_model_len=128, num_kv_blocks=8), device="cpu", weights=w)
+    block_bytes = kb.kv.store[:, :, 0].numel() * kb.kv.store.element_size()
+    mk = lambda **kw: LLMEngine(cfg, EngineConfig(max_num_batched_tokens=96, max_model_len=128, num_kv_blocks=8, watermark=0.0,
+                                                  **kw), device="cpu", weights=w)
+    plain = mk()
+    want = [plain.generate([p], sp)[0] for p in prompts]
+    # host tier with room for 6 blocks, the rest spills to disk
+    eng = mk(kv_tier_host_gb=6.5 * block_bytes / (1 << 30), kv_tier_disk_dir=str(tmp_path), kv_tier_disk_gb=1.0)
+    assert eng.kv_tier is not None and eng.kv_tier.enabled
+    assert [eng.generate([p], sp)[0] for p in prompts] == want          # 4 prompts x 4 full blocks through an 8-block pool
+    t = eng.kv_tier
+    assert t.stats["stored"] >= 8 and t.stats["spilled"] >= 1 and len(t.host) <= 6
+    before = eng.blocks.stats["tier_restored"]
+    again = [eng.generate([p], sp)[0] for p in prompts]
+    assert again == want
+    assert eng.blocks.stats["tier_restored"] - before >= 8 and t.stats["host_hits"] + t.stats["disk_hits"] >= 8
+    assert t.stats["disk_hits"] >= 1
+    # restart: a fresh engine indexes the files and serves the first prompt's blocks from disk
+    on_disk = len(t.disk)
+    eng2 = mk(kv_tier_host_gb=0.0, kv_tier_disk_dir=str(tmp_path), kv_tier_disk_gb=1.0)
+    assert eng2.kv_tier.stats["rewarmed"] == on_disk >= 1
+    hit_prompt = next(p for p in prompts if eng2.blocks.tier_has(
+        __import__("fllm_b200.runtime.block_manager", fromlist=["chain_hash"]).chain_hash(b"", p[:16], b"")))
+    assert eng2.generate([hit_prompt], sp)[0] == want[prompts.index(hit_prompt)]
+    assert eng2.blocks.stats["tier_restored"] >= 1 and eng2.kv_tier.stats["disk_hits"] >= 1
+    other = LLMEngine(cfg, EngineConfig(max_num_batched_tokens=96, max_model_len=128, num_kv_blocks=8, kv_cache_dtype="fp8_e4m3",
+                                        kv_tier_disk_dir=str(tmp_path), kv_tier_disk_gb=1.0), device="cpu", weights=w)
+    assert other.kv_tier.stats["rewarmed"] == 0
+    # a disk budget of two blocks keeps two files
+    small = mk(kv_tier_host_gb=0.0, kv_tier_disk_dir=str(tmp_path / "small"), kv_tier_disk_gb=2.2 * (block_bytes + 32) / (1 << 30))
+    for p in prompts:
+        small.generate([p], sp)
+    assert len(small.kv_tier.disk) == 2 and len([f for f in (tmp_path / "small").iterdir() if f.suffix == ".kv"]) == 2

@@ -317,3 +317,8 @@ def test_beam_search_over_http_returns_ranked_hypotheses(client):
     one = client.post("/v1/completions", json={**body, "n": 1, "ignore_eos": True}).json()["choices"][0]
     assert one["token_ids"] == greedy["choices"][0]["token_ids"]
     assert client.post("/v1/completions", json={**body, "n": 50}).status_code == 400
+
+
+def test_kv_tier_admin_route(client):
+    r = client.get("/admin/kv-tier").json()
+    assert r["enabled"] is False and r["restored_blocks"] == 0
