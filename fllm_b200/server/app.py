@@ -385,6 +385,21 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
         return {"tokens": texts, "token_logprobs": lps, "text_offset": offs,
                 "top_logprobs": [{piece_text(a): b for a, b in alt} for alt in tops]}
 
+    def choice_params(body: dict, default_max: int, first: SamplingParams) -> "List[SamplingParams]":
+        """`n` choices are n requests: each with its own parameter object (a grammar state is per request) and,
+        when a seed is given, seed + index so that the choices differ but the response repeats."""
+        n = int(body.get("n") or 1)
+        if not 1 <= n <= 16:
+            raise HTTPException(400, "n must be in [1, 16]")
+        out = [first]
+        for i in range(1, n):
+            spi = _sampling_from(body, default_max)
+            attach_guided(spi, body)
+            if spi.seed is not None:
+                spi.seed = int(spi.seed) + i
+            out.append(spi)
+        return out
+
     def attach_guided(sp: SamplingParams, body: dict) -> None:
         """response_format json_object / json_schema (OpenAI) and format: "json" (Ollama) constrain the
         output to a JSON object through the sampler's allowed-token mask."""
@@ -582,15 +597,16 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
                     yield f"data: {json.dumps(chunk)}\n\n"
                 yield "data: [DONE]\n\n"
             return sse(gen())
-        lp_obj = None
-        if sp.logprobs:
-            text, toks, reason, lps, tops = await collect_with_logprobs(ids, sp)
-            lp_obj = completion_logprobs(toks, lps, tops)
-        else:
-            text, toks, reason = await collect(ids, sp)
+        async def one(spi, index):
+            if spi.logprobs:
+                text, toks, reason, lps, tops = await collect_with_logprobs(ids, spi)
+                lp_obj = completion_logprobs(toks, lps, tops)
+            else:
+                (text, toks, reason), lp_obj = await collect(ids, spi), None
+            return {"index": index, "text": text, "token_ids": toks, "finish_reason": reason, "logprobs": lp_obj}
+        choices = await asyncio.gather(*[one(spi, i) for i, spi in enumerate(choice_params(body, 16, sp))])
         return {"id": cid, "object": "text_completion", "created": int(time.time()), "model": model_name,
-                "choices": [{"index": 0, "text": text, "token_ids": toks, "finish_reason": reason, "logprobs": lp_obj}],
-                "usage": usage(len(ids), len(toks))}
+                "choices": list(choices), "usage": usage(len(ids), sum(len(c["token_ids"]) for c in choices))}
 
     def chat_prompt(messages, tools=None) -> List[int]:
         try:
@@ -644,18 +660,21 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
                     yield f"data: {json.dumps(chunk)}\n\n"
                 yield "data: [DONE]\n\n"
             return sse(gen())
-        lp_obj = None
-        if sp.logprobs:
-            text, toks, reason, lps, tops = await collect_with_logprobs(ids, sp)
-            lp_obj = chat_logprobs(toks, lps, tops)
-        else:
-            text, toks, reason = await collect(ids, sp)
-        msg, has_calls = shape_message(text)
-        choice = {"index": 0, "message": msg, "finish_reason": "tool_calls" if has_calls else reason}
-        if lp_obj is not None:
-            choice["logprobs"] = lp_obj
+        async def one(spi, index):
+            lp_obj = None
+            if spi.logprobs:
+                text, toks, reason, lps, tops = await collect_with_logprobs(ids, spi)
+                lp_obj = chat_logprobs(toks, lps, tops)
+            else:
+                text, toks, reason = await collect(ids, spi)
+            msg, has_calls = shape_message(text)
+            choice = {"index": index, "message": msg, "finish_reason": "tool_calls" if has_calls else reason}
+            if lp_obj is not None:
+                choice["logprobs"] = lp_obj
+            return choice, len(toks)
+        done = await asyncio.gather(*[one(spi, i) for i, spi in enumerate(choice_params(body, 256, sp))])
         return {"id": cid, "object": "chat.completion", "created": int(time.time()), "model": model_name,
-                "choices": [choice], "usage": usage(len(ids), len(toks))}
+                "choices": [c for c, _ in done], "usage": usage(len(ids), sum(n for _, n in done))}
 
     @app.post("/v1/chat/completions/render")
     async def chat_render(body: dict):

@@ -322,3 +322,19 @@ def test_beam_search_over_http_returns_ranked_hypotheses(client):
 def test_kv_tier_admin_route(client):
     r = client.get("/admin/kv-tier").json()
     assert r["enabled"] is False and r["restored_blocks"] == 0
+
+
+def test_n_choices_are_n_requests_with_consecutive_seeds(client):
+    body = {"prompt": "many", "max_tokens": 6, "temperature": 1.0, "seed": 5, "n": 3}
+    a = client.post("/v1/completions", json=body).json()
+    b = client.post("/v1/completions", json=body).json()
+    assert [c["index"] for c in a["choices"]] == [0, 1, 2]
+    assert [c["token_ids"] for c in a["choices"]] == [c["token_ids"] for c in b["choices"]]       # seeded: repeats
+    assert len({tuple(c["token_ids"]) for c in a["choices"]}) >= 2                               # seeds differ per choice
+    single = client.post("/v1/completions", json={**body, "n": 1, "seed": 6}).json()
+    assert single["choices"][0]["token_ids"] == a["choices"][1]["token_ids"]
+    assert a["usage"]["completion_tokens"] == sum(len(c["token_ids"]) for c in a["choices"])
+    chat = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4,
+                                                     "temperature": 0, "n": 2}).json()
+    assert len(chat["choices"]) == 2 and chat["choices"][0]["message"] == chat["choices"][1]["message"]
+    assert client.post("/v1/completions", json={**body, "n": 100}).status_code == 400
