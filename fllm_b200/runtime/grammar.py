@@ -10,6 +10,8 @@ string, after a comma in an object, ...) come back all the time.
 The reference delegates this to xgrammar / llguidance (rust/engine/src/structured.rs); here the
 recogniser covers ``response_format: {"type": "json_object"}`` (OpenAI), ``format: "json"`` (Ollama)
 and the shape of ``json_schema`` requests (any valid JSON object; schema keywords are not enforced).
+``GuidedChoice`` constrains the output to one of a list of strings (``guided_choice``) through the same
+trie walk with its own step function.
 """
 from __future__ import annotations
 
@@ -174,14 +176,17 @@ class TokenTrie:
         pieces = [None if i in special else tokenizer.decode([i]) for i in range(tokenizer.vocab_size)]
         return cls(pieces)
 
-    def allowed(self, st: State) -> List[int]:
+    def allowed(self, st, step=None) -> List[int]:
+        """Tokens all of whose characters can follow state `st` under `step(state, ch) -> state | None`
+        (the JSON recogniser by default)."""
+        step = step or json_step
         out: List[int] = []
         stack = [(0, st)]
         children, ids = self.children, self.ids
         while stack:
             node, s = stack.pop()
             for ch, nxt in children[node].items():
-                s2 = json_step(s, ch)
+                s2 = step(s, ch)
                 if s2 is None:
                     continue
                 if ids[nxt]:
@@ -228,3 +233,50 @@ class GuidedJson:
         if token_id in self.eos_ids or self.state is None:
             return
         self.state = json_feed(self.state, self.tok.decode([int(token_id)]))
+
+
+class GuidedChoice:
+    """Constraint "the output is exactly one of these strings" (``guided_choice``): the state is the text
+    produced so far, a character may follow while some choice still starts with the result, and the end
+    of sequence is allowed once the text equals a choice."""
+
+    def __init__(self, trie: TokenTrie, tokenizer, eos_ids: Sequence[int], choices: Sequence[str]):
+        self.trie, self.tok = trie, tokenizer
+        self.eos_ids = [int(e) for e in eos_ids if e is not None]
+        self.choices = [str(c) for c in choices if str(c)]
+        if not self.choices:
+            raise ValueError("guided_choice needs at least one non-empty string")
+        self.state: Optional[str] = ""
+        self.cache: dict = {}
+
+    def _step(self, prefix: str, ch: str) -> Optional[str]:
+        nxt = prefix + ch
+        return nxt if any(c.startswith(nxt) for c in self.choices) else None
+
+    @property
+    def complete(self) -> bool:
+        return self.state is not None and self.state in self.choices
+
+    def mask_words(self, vocab: int) -> np.ndarray:
+        key = (self.state, vocab)
+        m = self.cache.get(key)
+        if m is None:
+            m = np.zeros((vocab + 31) // 32, dtype=np.uint32)
+            if self.state is not None:
+                ids = np.asarray([t for t in self.trie.allowed(self.state, self._step) if t < vocab], dtype=np.int64)
+                if ids.size:
+                    np.bitwise_or.at(m, ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
+            if self.state is None or self.complete:
+                for e in self.eos_ids:
+                    if e < vocab:
+                        m[e >> 5] |= np.uint32(1 << (e & 31))
+            self.cache[key] = m
+        return m
+
+    def advance(self, token_id: int) -> None:
+        if token_id in self.eos_ids or self.state is None:
+            return
+        st: Optional[str] = self.state
+        for ch in self.tok.decode([int(token_id)]):
+            st = self._step(st, ch) if st is not None else None
+        self.state = st

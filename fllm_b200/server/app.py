@@ -417,6 +417,17 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
         if brk:
             extra = {int(tokenizer.encode(w, add_bos=False)[-1]) for w in brk if tokenizer.encode(w, add_bos=False)}
             sp.dry_sequence_breakers = tuple(sorted(set(sp.dry_sequence_breakers) | extra))
+        if body.get("guided_choice"):
+            from ..runtime.grammar import GuidedChoice, TokenTrie
+            if "trie" not in guided_shared:
+                guided_shared["trie"] = TokenTrie.from_tokenizer(tokenizer)
+                guided_shared["masks"] = {}
+            eos = [getattr(tokenizer, "eos_token_id", None), getattr(engine, "eos_token_id", None)]
+            try:
+                sp.guided = GuidedChoice(guided_shared["trie"], tokenizer, eos, body["guided_choice"])
+            except (ValueError, TypeError) as e:
+                raise HTTPException(400, str(e))
+            return
         rf = body.get("response_format")
         kind = rf.get("type") if isinstance(rf, dict) else None
         fmt = body.get("format")

@@ -338,3 +338,14 @@ def test_n_choices_are_n_requests_with_consecutive_seeds(client):
                                                      "temperature": 0, "n": 2}).json()
     assert len(chat["choices"]) == 2 and chat["choices"][0]["message"] == chat["choices"][1]["message"]
     assert client.post("/v1/completions", json={**body, "n": 100}).status_code == 400
+
+
+def test_guided_choice_outputs_exactly_one_of_the_strings(client):
+    choices = ["yes", "no", "maybe so"]
+    for temp, seed in ((0.0, None), (1.0, 1), (1.0, 2), (1.5, 3)):
+        body = {"prompt": "answer:", "max_tokens": 16, "temperature": temp, "guided_choice": choices}
+        if seed is not None:
+            body["seed"] = seed
+        r = client.post("/v1/completions", json=body).json()["choices"][0]
+        assert r["text"] in choices and r["finish_reason"] == "stop", r
+    assert client.post("/v1/completions", json={"prompt": "x", "guided_choice": [""]}).status_code == 400
