@@ -9,7 +9,8 @@ string, after a comma in an object, ...) come back all the time.
 
 The reference delegates this to xgrammar / llguidance (rust/engine/src/structured.rs); here the
 recogniser covers ``response_format: {"type": "json_object"}`` (OpenAI), ``format: "json"`` (Ollama)
-and the shape of ``json_schema`` requests (any valid JSON object; schema keywords are not enforced).
+and ``json_schema`` requests: ``JsonSchemaStep`` enforces properties / required / additionalProperties /
+type / enum / const on the top-level object; nested values are any JSON of the declared type.
 ``GuidedChoice`` constrains the output to one of a list of strings (``guided_choice``) through the same
 trie walk with its own step function.
 """
@@ -279,4 +280,149 @@ class GuidedChoice:
         st: Optional[str] = self.state
         for ch in self.tok.decode([int(token_id)]):
             st = self._step(st, ch) if st is not None else None
+        self.state = st
+
+
+# ----------------------------------------------------------------------------- JSON schema (top-level object)
+_TYPE_FIRST = {"string": '"', "number": "-0123456789", "integer": "-0123456789", "boolean": "tf", "null": "n",
+               "object": "{", "array": "["}
+_NUM_MODES = ("N-", "N0", "NI", "N.", "NF", "Ne", "Ns", "NE")
+
+
+class JsonSchemaStep:
+    """The JSON recogniser plus the keywords of an object schema that matter most for tool calls and
+    structured outputs, enforced on the TOP-LEVEL object: ``properties`` (with ``additionalProperties:
+    false`` only declared keys can be written, each once), ``required`` (the object cannot close before
+    they are all present), and per property ``type`` (also a list of types), ``enum`` and ``const``
+    (the value's JSON text must be one of the listed literals). Nested values are any JSON of the
+    declared type. State = (json state, key text being written, key whose value is open, keys done,
+    value text for enum matching); it is hashable, so masks are cached per state like the plain ones."""
+
+    def __init__(self, schema: dict):
+        import json as _json
+        if not isinstance(schema, dict) or schema.get("type", "object") != "object":
+            raise ValueError("json_schema: the top level must be an object schema")
+        self.props: Dict[str, dict] = {str(k): (v if isinstance(v, dict) else {}) for k, v in (schema.get("properties") or {}).items()}
+        self.required = frozenset(str(k) for k in (schema.get("required") or ()))
+        self.closed = schema.get("additionalProperties") is False
+        unknown = self.required - set(self.props)
+        if self.closed and unknown:
+            raise ValueError(f"json_schema: required keys without a property: {sorted(unknown)}")
+        self.literals: Dict[str, Tuple[str, ...]] = {}
+        for k, p in self.props.items():
+            vals = p["enum"] if isinstance(p.get("enum"), list) else ([p["const"]] if "const" in p else None)
+            if vals is not None:
+                self.literals[k] = tuple(_json.dumps(v, ensure_ascii=False, separators=(",", ":")) for v in vals)
+
+    def start(self):
+        return (json_start(True), None, None, frozenset(), None)
+
+    def _first_chars(self, key: str) -> Optional[str]:
+        p = self.props.get(key)
+        if p is None:
+            return None
+        if key in self.literals:
+            return "".join(sorted({lit[0] for lit in self.literals[key]}))
+        t = p.get("type")
+        if t is None:
+            return None
+        types = t if isinstance(t, list) else [t]
+        return "".join(_TYPE_FIRST.get(x, "") for x in types) or None
+
+    def __call__(self, st, ch: str):
+        js, kbuf, key, seen, vbuf = st
+        mode, aux, stack = js
+        js2 = json_step(js, ch)
+        if js2 is None:
+            return None
+        top = stack == "o"
+        if top and mode in ("K", "K2") and ch == '"':
+            return (js2, "", key, seen, None)
+        if top and mode == "S" and aux == "k":                       # inside a top-level key
+            if ch == '"':
+                if self.closed and (kbuf not in self.props or kbuf in seen):
+                    return None
+                if kbuf in seen:
+                    return None                                       # a key is written once
+                return (js2, None, kbuf, seen, None)
+            if ch == "\\":
+                return None if self.closed else (js2, None, key, seen, None)
+            if kbuf is None:
+                return (js2, None, key, seen, None)                   # free-form key (after an escape)
+            nk = kbuf + ch
+            if self.closed and not any(k.startswith(nk) and k not in seen for k in self.props):
+                return None
+            return (js2, nk, key, seen, None)
+        if top and mode == "V" and key is not None and ch not in _WS:   # first character of the key's value
+            first = self._first_chars(key)
+            if first is not None and ch not in first:
+                return None
+            if key in self.literals:
+                vbuf = ""
+        if key is not None and vbuf is not None and (len(stack) > 1 or top) and not (top and mode in ("A",)):
+            # the value's text must stay a prefix of one of the allowed literals, and end exactly on one
+            in_value = not (top and mode in ("C", "K", "K2"))
+            ended_number = top and mode in _NUM_END and json_step(_after_value(stack), ch) is not None and ch not in _DIG + ".eE"
+            if in_value and not ended_number and not (top and mode == "V" and ch in _WS):
+                nv = vbuf + ch
+                if not any(l.startswith(nv) for l in self.literals[key]):
+                    return None
+                vbuf = nv
+        p = self.props.get(key) if key is not None else None
+        if top and p is not None and mode in _NUM_MODES and ch in ".eE":
+            t = p.get("type")
+            if t == "integer" or (isinstance(t, list) and "integer" in t and "number" not in t):
+                return None
+        mode2, _, stack2 = js2
+        if key is not None and ((stack2 == "o" and mode2 in ("A", "K2")) or stack2 == ""):
+            if not (top and mode == "V" and ch in _WS) and not (stack2 == "o" and mode2 == "A" and mode == "A"):
+                if vbuf is not None and key in self.literals:
+                    done_text = vbuf if not (top and mode in _NUM_END and ch in ",} \t\n\r") else vbuf
+                    if done_text not in self.literals[key]:
+                        return None
+                seen = seen | {key}
+                key, vbuf = None, None
+        if top and stack2 == "" and not self.required <= seen:
+            return None                                               # closing before every required key is present
+        if top and mode2 == "K2" and stack2 == "o" and mode != "K2" and self.closed and all(k in seen for k in self.props):
+            return None                                               # a comma with no key left to write
+        return (js2, kbuf if (top and mode == "S" and aux == "k") else None, key, seen, vbuf)
+
+
+class GuidedJsonSchema(GuidedJson):
+    """``response_format: {"type": "json_schema", ...}``: the JSON constraint plus ``JsonSchemaStep``."""
+
+    def __init__(self, trie: TokenTrie, tokenizer, eos_ids: Sequence[int], schema: dict, cache: Optional[dict] = None):
+        super().__init__(trie, tokenizer, eos_ids, True, {} if cache is None else cache)
+        self.schema_step = JsonSchemaStep(schema)
+        self.state = self.schema_step.start()
+
+    @property
+    def complete(self) -> bool:
+        return self.state is not None and json_complete(self.state[0])
+
+    def mask_words(self, vocab: int) -> np.ndarray:
+        key = (self.state, vocab)
+        m = self.cache.get(key)
+        if m is None:
+            m = np.zeros((vocab + 31) // 32, dtype=np.uint32)
+            if self.state is not None:
+                ids = np.asarray([t for t in self.trie.allowed(self.state, self.schema_step) if t < vocab], dtype=np.int64)
+                if ids.size:
+                    np.bitwise_or.at(m, ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
+            if self.state is None or self.complete:
+                for e in self.eos_ids:
+                    if e < vocab:
+                        m[e >> 5] |= np.uint32(1 << (e & 31))
+            if len(self.cache) > 4096:
+                self.cache.clear()
+            self.cache[key] = m
+        return m
+
+    def advance(self, token_id: int) -> None:
+        if token_id in self.eos_ids or self.state is None:
+            return
+        st = self.state
+        for ch in self.tok.decode([int(token_id)]):
+            st = self.schema_step(st, ch) if st is not None else None
         self.state = st

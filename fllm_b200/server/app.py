@@ -434,11 +434,25 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
         if kind not in ("json_object", "json_schema") and fmt != "json" and not isinstance(fmt, dict) \
                 and not body.get("guided_json"):
             return
-        from ..runtime.grammar import GuidedJson, TokenTrie
+        from ..runtime.grammar import GuidedJson, GuidedJsonSchema, TokenTrie
         if "trie" not in guided_shared:
             guided_shared["trie"] = TokenTrie.from_tokenizer(tokenizer)
             guided_shared["masks"] = {}
         eos = [getattr(tokenizer, "eos_token_id", None), getattr(engine, "eos_token_id", None)]
+        schema = None
+        if kind == "json_schema":
+            js = rf.get("json_schema") or {}
+            schema = js.get("schema") if isinstance(js.get("schema"), dict) else (js if "properties" in js else None)
+        elif isinstance(body.get("guided_json"), dict):
+            schema = body["guided_json"]
+        elif isinstance(fmt, dict):
+            schema = fmt
+        if isinstance(schema, dict) and schema.get("type", "object") == "object" and isinstance(schema.get("properties"), dict):
+            try:
+                sp.guided = GuidedJsonSchema(guided_shared["trie"], tokenizer, eos, schema)
+                return
+            except ValueError as e:
+                raise HTTPException(400, str(e))
         sp.guided = GuidedJson(guided_shared["trie"], tokenizer, eos, require_object=True, cache=guided_shared["masks"])
 
     def shape_message(text: str) -> "tuple[dict, bool]":

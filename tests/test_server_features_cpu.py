@@ -349,3 +349,63 @@ def test_guided_choice_outputs_exactly_one_of_the_strings(client):
         r = client.post("/v1/completions", json=body).json()["choices"][0]
         assert r["text"] in choices and r["finish_reason"] == "stop", r
     assert client.post("/v1/completions", json={"prompt": "x", "guided_choice": [""]}).status_code == 400
+
+
+_SCHEMA = {"type": "object", "properties": {"name": {"type": "string"}, "age": {"type": "integer"}, "ok": {"type": "boolean"},
+                                            "kind": {"enum": ["a", "bb", 3]}, "tags": {"type": "array"},
+                                            "opt": {"type": ["number", "null"]}},
+           "required": ["name", "age", "kind"], "additionalProperties": False}
+
+
+def _schema_feed(step, text):
+    st = step.start()
+    for ch in text:
+        st = step(st, ch)
+        if st is None:
+            return None
+    return st
+
+
+def test_json_schema_step_accepts_and_rejects_by_the_schema():
+    from fllm_b200.runtime.grammar import JsonSchemaStep
+    step = JsonSchemaStep(_SCHEMA)
+    good = ['{"name":"x","age":12,"kind":"bb"}', '{"kind":3,"age":-4,"name":"e\\n","ok":true,"tags":[1,{"a":2}],"opt":null}',
+            ' { "age" : 7 , "name" : "" , "kind" : "a" , "opt" : 1.5e3 } ', '{"kind":3 ,"age":0,"name":"q"}']
+    for g in good:
+        st = _schema_feed(step, g)
+        assert st is not None and json_complete(st[0]), g
+        doc = json.loads(g)
+        assert set(_SCHEMA["required"]) <= set(doc) and set(doc) <= set(_SCHEMA["properties"])
+    dead = ['{"name":"x","age":12}', '{"name":1', '{"age":1.', '{"age":1e', '{"kind":"c', '{"zzz', '{"name":"x","name"',
+            '{"age":12,"kind":"a","name":"q","tags":[],"ok":false,"opt":2,', '{"kind":"b"', '{"kind":33', '{"ok":1', '{}',
+            '{"opt":"s', '{"tags":{', '{"na\\u']
+    for b in dead:
+        assert _schema_feed(step, b) is None, b
+    # open schemas take undeclared keys but still type the declared ones and wait for the required ones
+    open_step = JsonSchemaStep({"type": "object", "properties": {"n": {"type": "integer"}}, "required": ["n"]})
+    assert json_complete(_schema_feed(open_step, '{"extra":[1],"n":5}')[0])
+    assert _schema_feed(open_step, '{"extra":1}') is None and _schema_feed(open_step, '{"n":"') is None
+    with pytest.raises(ValueError):
+        JsonSchemaStep({"type": "array"})
+
+
+def test_json_schema_response_format_is_enforced_through_the_sampler(client):
+    from fllm_b200.runtime.grammar import JsonSchemaStep
+    step = JsonSchemaStep(_SCHEMA)
+    finished = 0
+    for temp, seed in ((0.0, None), (1.0, 3), (1.3, 4), (1.0, 5)):
+        body = {"messages": [{"role": "user", "content": "fill the form"}], "max_tokens": 96, "temperature": temp,
+                "response_format": {"type": "json_schema", "json_schema": {"name": "form", "schema": _SCHEMA}}}
+        if seed is not None:
+            body["seed"] = seed
+        r = client.post("/v1/chat/completions", json=body).json()["choices"][0]
+        text = r["message"]["content"] or ""
+        assert _schema_feed(step, text) is not None, text          # never leaves the schema
+        if r["finish_reason"] == "stop":
+            doc = json.loads(text)
+            assert {"name", "age", "kind"} <= set(doc) <= set(_SCHEMA["properties"])
+            assert isinstance(doc["name"], str) and isinstance(doc["age"], int) and doc["kind"] in ("a", "bb", 3)
+            finished += 1
+    o = client.post("/api/generate", json={"prompt": "x", "format": _SCHEMA, "stream": False,
+                                           "options": {"num_predict": 24, "temperature": 0}}).json()
+    assert _schema_feed(step, o["response"]) is not None
