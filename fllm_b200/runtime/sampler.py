@@ -44,8 +44,11 @@ def sample_step(engine, step, logits: torch.Tensor, greedy: torch.Tensor) -> tor
         if req.params.logprobs:
             raw_lsm[i] = torch.log_softmax(sub[i], -1)
             if req.params.top_logprobs > 0:
-                lp, tid = raw_lsm[i].topk(min(req.params.top_logprobs, vocab))
-                req.top_logprobs.append(list(zip(tid.tolist(), lp.tolist())))
+                # stable order: among equal log-probabilities (bf16 logits tie often) the lower token id comes
+                # first, which is the token a greedy pick returns
+                lp, tid = torch.sort(raw_lsm[i], descending=True, stable=True)
+                n_alt = min(req.params.top_logprobs, vocab)
+                req.top_logprobs.append(list(zip(tid[:n_alt].tolist(), lp[:n_alt].tolist())))
     for i, (_, req, draw) in enumerate(rows):          # typical-p, DRY, Mirostat, banned sequences: edits of the row
         if req.params.needs_host_processors:
             apply_before_sampling(req, sub[i], draw)

@@ -230,3 +230,38 @@ def test_smoke_entry_point():
     with the PyTorch reference operators on the same weights (which must stay off the graph path)."""
     import __graft_entry__ as entry
     entry.smoke()
+
+
+def test_rare_samplers_logprobs_and_beam_search_on_the_gpu():
+    """The host-side logit processors edit CUDA logit rows before the device sampler; log-probabilities and
+    beam search read them. Same invariants as on the CPU: bans hold, seeded runs repeat, width-1 beam = greedy."""
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    cfg = preset("qwen3-tiny")
+    ec = EngineConfig(max_num_seqs=8, max_num_batched_tokens=64, max_model_len=256, num_kv_blocks=128)
+    eng = LLMEngine(cfg, ec, device="cuda:0", seed=3)
+    prompt = _prompts(cfg.vocab_size, (12,), seed=2)
+    base = eng.generate(prompt, SamplingParams(max_tokens=8))[0]
+    banned = eng.generate(prompt, SamplingParams(max_tokens=8, bad_words=[[base[0]]]))[0]
+    assert base[0] not in banned
+    sp = dict(max_tokens=8, temperature=1.0, seed=7, typical_p=0.8, dry_multiplier=0.8, mirostat_mode=2, mirostat_tau=3.0)
+    a = eng.generate(prompt, SamplingParams(**sp))[0]
+    b = eng.generate(prompt, SamplingParams(**sp))[0]
+    assert a == b and len(a) == 8
+    rid = eng.add_request(prompt[0], SamplingParams(max_tokens=4, logprobs=True, top_logprobs=3))
+    req = eng.requests[rid]
+    evs = []
+    while eng.has_unfinished():
+        evs += [e for e in eng.step() if e.request_id == rid]
+    lps = [x for e in evs for x in (e.logprobs or [])]
+    tops = [x for e in evs for x in (e.top_logprobs or [])]
+    assert len(lps) == len(tops) == 4 and all(lp <= 1e-6 for lp in lps)
+    for tok, lp, alt in zip(req.output, lps, tops):
+        # greedy: the pick has the best alternative's log-probability (bf16 logits tie often, so the ids may differ)
+        assert abs(alt[0][1] - lp) < 1e-3 and len(alt) == 3 and alt[0][1] >= alt[1][1] >= alt[2][1]
+    one = eng.beam_search(prompt[0], beam_width=1, max_tokens=6, length_penalty=0.0, eos_token_id=-1)
+    assert len(one) == 1 and len(one[0][0]) == 6 and one[0][1] <= 0.0
+    two = eng.beam_search(prompt[0], beam_width=2, max_tokens=6, length_penalty=0.0, eos_token_id=-1)
+    assert len(two) == 2 and two[0][1] >= two[1][1] and two[0][0] != two[1][0]
+    assert not eng.requests
+    assert eng.ops.check_status() == 0
