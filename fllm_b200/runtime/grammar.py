@@ -426,3 +426,47 @@ class GuidedJsonSchema(GuidedJson):
         for ch in self.tok.decode([int(token_id)]):
             st = self.schema_step(st, ch) if st is not None else None
         self.state = st
+
+
+class GuidedToolCall(GuidedJsonSchema):
+    """A forced tool call in the Hermes / Qwen markup: ``<tool_call>`` + a JSON object
+    ``{"name": one of the offered functions, "arguments": {...}}`` + ``</tool_call>``
+    (``tool_choice: "required"`` or a named function; the reference builds such grammars in
+    rust/engine/src/tool_grammar.rs:1-8). State = (phase, inner): the literal prefix character by character, the
+    schema-constrained JSON, then the literal suffix; the end of sequence is allowed after the suffix."""
+
+    PREFIX, SUFFIX = "<tool_call>\n", "</tool_call>"
+
+    def __init__(self, trie: TokenTrie, tokenizer, eos_ids: Sequence[int], names: Sequence[str]):
+        names = [str(n) for n in names if str(n)]
+        if not names:
+            raise ValueError("tool_choice needs at least one function name")
+        schema = {"type": "object", "properties": {"name": {"enum": names}, "arguments": {"type": "object"}},
+                  "required": ["name", "arguments"], "additionalProperties": False}
+        super().__init__(trie, tokenizer, eos_ids, schema)
+        inner = self.schema_step
+
+        def step(st, ch):
+            phase, x = st
+            if phase == "pre":
+                if self.PREFIX[x] != ch:
+                    return None
+                return ("pre", x + 1) if x + 1 < len(self.PREFIX) else ("json", inner.start())
+            if phase == "json":
+                nxt = inner(x, ch)
+                if nxt is not None:
+                    return ("json", nxt)
+                if json_complete(x[0]) and ch == self.SUFFIX[0]:
+                    return ("post", 1)
+                return None
+            if phase == "post":
+                if x >= len(self.SUFFIX) or self.SUFFIX[x] != ch:
+                    return None
+                return ("post", x + 1)
+            return None
+        self.schema_step = step
+        self.state = ("pre", 0)
+
+    @property
+    def complete(self) -> bool:
+        return self.state is not None and self.state[0] == "post" and self.state[1] == len(self.SUFFIX)

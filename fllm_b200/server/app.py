@@ -417,6 +417,21 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
         if brk:
             extra = {int(tokenizer.encode(w, add_bos=False)[-1]) for w in brk if tokenizer.encode(w, add_bos=False)}
             sp.dry_sequence_breakers = tuple(sorted(set(sp.dry_sequence_breakers) | extra))
+        tc = body.get("tool_choice")
+        if body.get("tools") and tool_parser == "hermes" and (tc == "required" or (isinstance(tc, dict) and tc.get("function"))):
+            # a forced tool call: the output is the call markup with one of the offered (or the named) functions
+            from ..runtime.grammar import GuidedToolCall, TokenTrie
+            if "trie" not in guided_shared:
+                guided_shared["trie"] = TokenTrie.from_tokenizer(tokenizer)
+                guided_shared["masks"] = {}
+            names = ([tc["function"].get("name")] if isinstance(tc, dict)
+                     else [(t.get("function") or {}).get("name") for t in body["tools"] if isinstance(t, dict)])
+            eos = [getattr(tokenizer, "eos_token_id", None), getattr(engine, "eos_token_id", None)]
+            try:
+                sp.guided = GuidedToolCall(guided_shared["trie"], tokenizer, eos, [n for n in names if n])
+            except ValueError as e:
+                raise HTTPException(400, str(e))
+            return
         if body.get("guided_choice"):
             from ..runtime.grammar import GuidedChoice, TokenTrie
             if "trie" not in guided_shared:

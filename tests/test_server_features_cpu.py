@@ -409,3 +409,40 @@ def test_json_schema_response_format_is_enforced_through_the_sampler(client):
     o = client.post("/api/generate", json={"prompt": "x", "format": _SCHEMA, "stream": False,
                                            "options": {"num_predict": 24, "temperature": 0}}).json()
     assert _schema_feed(step, o["response"]) is not None
+
+
+def test_forced_tool_call_grammar(client):
+    from fllm_b200.runtime.grammar import GuidedToolCall, TokenTrie
+    from fllm_b200.tokenizer import ByteTokenizer
+    tok = ByteTokenizer(512)
+    g = GuidedToolCall(TokenTrie.from_tokenizer(tok), tok, [tok.eos_token_id], ["get_weather", "get_time"])
+
+    def feed(text):
+        st = g.state
+        for ch in text:
+            st = g.schema_step(st, ch)
+            if st is None:
+                return None
+        return st
+    full = '<tool_call>\n{"name": "get_time", "arguments": {"tz": "UTC", "n": [1, 2]}}\n</tool_call>'
+    st = feed(full)
+    assert st == ("post", len("</tool_call>"))
+    for bad in ('hello', '<tool_call>\n{"name": "other', '<tool_call>\n{"arguments": 1', '<tool_call>\n{"name": "get_time"}',
+                full + "x", '<tool_call>\n{"name": "get_time", "arguments": {}}<x'):
+        assert feed(bad) is None, bad
+    calls = parse_tool_calls(full, "hermes")[1]
+    assert calls[0]["function"]["name"] == "get_time" and json.loads(calls[0]["function"]["arguments"])["tz"] == "UTC"
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object"}}},
+             {"type": "function", "function": {"name": "get_time", "parameters": {"type": "object"}}}]
+    for choice in ("required", {"type": "function", "function": {"name": "get_time"}}):
+        r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "time?"}], "tools": tools,
+                                                      "tool_choice": choice, "max_tokens": 120, "temperature": 0})
+        assert r.status_code == 200
+        ch = r.json()["choices"][0]
+        if ch["finish_reason"] == "tool_calls":
+            names = [c["function"]["name"] for c in ch["message"]["tool_calls"]]
+            assert names and all(n in ("get_weather", "get_time") for n in names)
+            if isinstance(choice, dict):
+                assert names == ["get_time"]
+        else:                                                # ran out of tokens inside the call: still a prefix of the markup
+            assert (ch["message"].get("content") or "").startswith("<tool_call>")
