@@ -110,3 +110,61 @@ def test_streaming_reasoning_split_equals_the_one_shot_split(text, cut, style):
         cc += y
     assert (rr.strip() or None) == r
     assert cc.strip() == a.strip()
+
+
+_FORM = {"type": "object",
+         "properties": {"name": {"type": "string"}, "age": {"type": "integer"}, "ok": {"type": "boolean"},
+                        "kind": {"enum": ["a", "bb", 3, None]}, "tags": {"type": "array"}, "opt": {"type": ["number", "null"]},
+                        "meta": {"type": "object"}},
+         "required": ["name", "age", "kind"], "additionalProperties": False}
+_json_any = st.recursive(st.none() | st.booleans() | st.integers(-1000, 1000) | st.text(max_size=6),
+                         lambda ch: st.lists(ch, max_size=3) | st.dictionaries(st.text(max_size=4), ch, max_size=3), max_leaves=6)
+_form_docs = st.fixed_dictionaries(
+    {"name": st.text(max_size=8), "age": st.integers(-10**6, 10**6), "kind": st.sampled_from(["a", "bb", 3, None])},
+    optional={"ok": st.booleans(), "tags": st.lists(_json_any, max_size=3),
+              "opt": st.none() | st.integers(-99, 99) | st.floats(-1e3, 1e3, allow_nan=False).map(lambda x: round(x, 3)),
+              "meta": st.dictionaries(st.text(max_size=4), _json_any, max_size=3)})
+
+
+def _form_feed(step, text):
+    s = step.start()
+    for ch in text:
+        s = step(s, ch)
+        if s is None:
+            return None
+    return s
+
+
+@FAST
+@given(_form_docs, st.sampled_from([(",", ":"), (", ", ": "), (" , ", " : ")]), st.booleans(), st.randoms(use_true_random=False))
+def test_schema_step_accepts_every_conforming_document(doc, seps, ascii_only, rnd):
+    """Documents built from the schema, in any key order and spacing, are accepted and complete."""
+    from fllm_b200.runtime.grammar import JsonSchemaStep
+    keys = list(doc)
+    rnd.shuffle(keys)
+    text = json.dumps({k: doc[k] for k in keys}, separators=seps, ensure_ascii=ascii_only)
+    s = _form_feed(JsonSchemaStep(_FORM), text)
+    assert s is not None and json_complete(s[0]), text
+
+
+@FAST
+@given(_form_docs, st.sampled_from(["drop_required", "wrong_type", "extra_key", "bad_enum", "dup_key"]))
+def test_schema_step_never_completes_a_violating_document(doc, how):
+    from fllm_b200.runtime.grammar import JsonSchemaStep
+    d = dict(doc)
+    if how == "drop_required":
+        del d["age"]
+        text = json.dumps(d)
+    elif how == "wrong_type":
+        d["age"] = "12"
+        text = json.dumps(d)
+    elif how == "extra_key":
+        d["zzz"] = 1
+        text = json.dumps(d)
+    elif how == "bad_enum":
+        d["kind"] = "c"
+        text = json.dumps(d)
+    else:
+        text = json.dumps(d)[:-1] + ', "name": "again"}'
+    s = _form_feed(JsonSchemaStep(_FORM), text)
+    assert s is None or not json_complete(s[0]), text
