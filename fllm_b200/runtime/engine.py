@@ -751,8 +751,7 @@ class LLMEngine:
                 for ev in self.step():
                     if other_events is not None and ev.request_id not in mine:
                         other_events.append(ev)
-            if self.tp_rank != 0:
-                continue
+            # every tensor-parallel rank samples from the same gathered logits, so all ranks build the same beams
             cands = []
             for r, toks, lp in reqs:
                 for t, l in (r.top_logprobs[0] if r.top_logprobs else []):
