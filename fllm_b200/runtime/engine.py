@@ -708,8 +708,10 @@ class LLMEngine:
         st = self.kv.store                                   # [layers, 2, blocks, kv heads, block, head dim]
         block_bytes = st[:, :, 0].numel() * st.element_size()
         sig = f"{self.model_cfg.name}|{tuple(st[:, :, 0].shape)}|{st.dtype}|tp{self.tp_rank}"
-        if disk_dir and self.tp_rank:
-            disk_dir = os.path.join(disk_dir, f"rank{self.tp_rank}")
+        if self.tp_group is not None and getattr(self.tp_group, "size", 1) > 1:
+            # ranks must take identical hit / miss decisions to keep their block tables equal: the host tier is
+            # deterministic, a file that fails to read on one rank is not, so the disk tier is single-rank only
+            disk_dir = None
         self.kv_tier = KvTier(sig, block_bytes, int(self.cfg.kv_tier_host_gb * (1 << 30)), disk_dir,
                               int(self.cfg.kv_tier_disk_gb * (1 << 30)))
 
