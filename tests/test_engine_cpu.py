@@ -297,3 +297,27 @@ def test_evicted_prefix_blocks_come_back_from_the_host_and_disk_tiers(tmp_path):
     for p in prompts:
         small.generate([p], sp)
     assert len(small.kv_tier.disk) == 2 and len([f for f in (tmp_path / "small").iterdir() if f.suffix == ".kv"]) == 2
+
+
+def test_kv_tier_keeps_its_byte_budgets_and_returns_what_was_stored(tmp_path):
+    from fllm_b200.runtime.kv_tier import KvTier
+    nb = 256
+    t = KvTier("sig", nb, host_bytes=3 * nb, disk_dir=str(tmp_path), disk_bytes=4 * (nb + 32))
+    blobs = {bytes([i]) * 8: torch.full((nb,), i, dtype=torch.uint8) for i in range(12)}
+    for h, b in blobs.items():
+        t.put(h, b)
+        assert t.host_used() <= 3 * nb and t.disk_used() <= 4 * (nb + 32)
+    assert len(t.host) == 3 and len(t.disk) == 4 and t.stats["dropped"] == 12 - 7
+    newest, oldest_kept = bytes([11]) * 8, bytes([5]) * 8
+    assert torch.equal(t.get(newest), blobs[newest]) and torch.equal(t.get(oldest_kept), blobs[oldest_kept])
+    assert t.get(bytes([0]) * 8) is None and not t.has(bytes([0]) * 8)
+    t.put(newest, blobs[newest])                                 # already present: no double count
+    assert t.stats["stored"] == 12
+    again = KvTier("sig", nb, host_bytes=0, disk_dir=str(tmp_path), disk_bytes=4 * (nb + 32))
+    assert again.stats["rewarmed"] == 4 and torch.equal(again.get(oldest_kept), blobs[oldest_kept])
+    assert KvTier("other", nb, 0, str(tmp_path), 10 * nb).stats["rewarmed"] == 0
+    again.clear()
+    assert not [f for f in tmp_path.iterdir() if f.suffix == ".kv"]
+    off = KvTier("sig", nb)
+    off.put(newest, blobs[newest])
+    assert not off.enabled and not off.has(newest)
