@@ -44,6 +44,188 @@ class Timer:
         return ts[len(ts) // 2]                     # median, ms
 
 
+def run_case(case: str, reps: int = 4) -> None:
+    """One kernel family, a handful of launches, inputs larger than L2 but far below a GB-scale footprint:
+    a self-ending workload for a profiler capture or a quick look (``bench-kernel --case gemm_decode``).
+    Cases: gemm_decode (64 tokens x gate_up of an 8B model), gemm_prefill (2048 tokens), attn_decode
+    (64 sequences at 1152 context), attn_prefill (2 x 1024 tokens), attn_prefill_long (4 x 4096 tokens),
+    fp8_prefill, gemm_fp4_decode (64 tokens x NVFP4 gate_up), tp_rs_gemm / tp_norm / tp_ag_gemm (the fused
+    tensor-parallel kernels with two virtual ranks on one device)."""
+    from .ops.native import NativeOps, Fp8BlockLinear, quantize_weight_fp8_block
+    ops = NativeOps(torch.device("cuda:0"))
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+    if case in ("gemm_decode", "gemm_prefill"):
+        T = 64 if case == "gemm_decode" else 2048
+        x = torch.randn(T, 4096, **bf)
+        w = torch.randn(24576, 4096, **bf) * 0.02
+        y = torch.empty(T, 24576, **bf)
+        fn = lambda: ops.linear(x, w, out=y)
+    elif case == "gemm_fp4_decode":
+        from .ops.fp4 import Fp4Weight
+        x = torch.randn(64, 4096, **bf)
+        codes = torch.randint(0, 256, (24576, 2048), device="cuda", dtype=torch.uint8)
+        scales = torch.full((24576, 256), 0x38, device="cuda", dtype=torch.uint8)      # e4m3 1.0
+        q = Fp4Weight(codes, scales, 0, 0.01)
+        y = torch.empty(64, 24576, **bf)
+        fn = lambda: ops.linear(x, q, out=y)
+    elif case in ("tp_rs_gemm", "tp_norm", "tp_ag_gemm"):
+        # the fused tensor-parallel kernels with two virtual ranks on this one device (plain pointers instead
+        # of IPC mappings; the ranks' kernels run phase by phase): 2048 tokens, o_proj shard -> norm -> gate_up shard
+        from .comm.symm import FusedTP
+        T, H, I = 2048, 4096, 12288
+        ranks = FusedTP.local_group(2, H, T)
+        a = [torch.randn(T, H // 2, **bf) for _ in range(2)]
+        wo = [torch.randn(H, H // 2, **bf) * 0.02 for _ in range(2)]
+        wgu = torch.randn(I, H, **bf) * 0.02
+        nw = torch.ones(H, **bf)
+        res = [torch.zeros(T // 2, H, **bf) for _ in range(2)]
+
+        def fn():
+            for r in range(2):
+                ranks[r].linear_rs(a[r], wo[r], None, False)
+            for r in range(2):
+                ranks[r]._rs_expected = ranks[0]._rs_expected
+                ranks[r].norm(res[r], T, True, nw, 1e-6, 0.0, False)
+            for r in range(2):
+                ranks[r].linear_ag(T, wgu)
+    elif case == "fp8_prefill":
+        x = torch.randn(2048, 4096, **bf)
+        wq, sw = quantize_weight_fp8_block(torch.randn(8192, 4096, **bf) * 0.02)
+        lin = Fp8BlockLinear(ops, wq, sw)
+        fn = lambda: lin(x)
+    elif case in ("attn_decode", "attn_prefill", "attn_prefill_long"):
+        from .models.decoder import StepBatch
+        B, L, bs, hq, hkv, D = 64, 1152, 16, 32, 8, 128
+        nb = B * (L // bs)
+        kc = torch.randn(nb, hkv, bs, D, **bf)
+        vc = torch.randn_like(kc)
+        tables = torch.arange(nb, device="cuda", dtype=torch.int32).view(B, L // bs)
+        if case == "attn_decode":
+            q = torch.randn(B, hq * D, **bf)
+            meta = StepBatch(None, None, None, None, tables, None, num_seqs=B, num_tokens=B, max_kv_len=L,
+                             seq_lens=torch.full((B,), L, device="cuda", dtype=torch.int32),
+                             q_starts=torch.arange(B + 1, device="cuda", dtype=torch.int32))
+        elif case == "attn_prefill_long":
+            n, Lq = 4, 4096
+            tables = torch.arange(n * (Lq // bs), device="cuda", dtype=torch.int32).view(n, Lq // bs)
+            q = torch.randn(n * Lq, hq * D, **bf)
+            meta = StepBatch(None, None, None, None, tables, None, num_seqs=n, num_tokens=n * Lq, max_kv_len=Lq,
+                             seq_lens=torch.full((n,), Lq, device="cuda", dtype=torch.int32),
+                             q_starts=torch.arange(n + 1, device="cuda", dtype=torch.int32) * Lq,
+                             max_q_len=Lq, min_q_len=Lq)
+        else:
+            q = torch.randn(2048, hq * D, **bf)
+            meta = StepBatch(None, None, None, None, tables, None, num_seqs=2, num_tokens=2048, max_kv_len=1024,
+                             seq_lens=torch.full((2,), 1024, device="cuda", dtype=torch.int32),
+                             q_starts=torch.tensor([0, 1024, 2048], device="cuda", dtype=torch.int32),
+                             max_q_len=1024, min_q_len=1024)
+        fn = lambda: ops.attention(q, kc, vc, tables, None, None, hq, hkv, D, D ** -0.5, meta=meta)
+    else:
+        raise SystemExit(f"unknown case {case}")
+    for _ in range(reps):
+        fn()
+    torch.cuda.synchronize()
+    print(case, "done; kernel status", ops.check_status())
+
+
+NVLINK_GBS = 770.0       # measured peer-copy bandwidth per direction per GPU on this machine class
+
+
+def tp_half_layer(args) -> None:
+    """Roofline of the fused tensor-parallel half-layer: row-parallel GEMM -> reduce(-scatter) + residual +
+    RMSNorm (+ all-gather) -> column-parallel GEMM, against the same half-layer on library collectives.
+    Launch one process per GPU:
+
+        python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \\
+            -m fllm_b200.bench_kernel --tp-half-layer [--model qwen3-8b] [--tokens 64,2048]
+
+    Times are CUDA events on the launching stream, max over ranks, L2 flushed between iterations. The
+    roofline of a step is the slowest of: its FLOPs at the measured GEMM peak, its bytes over NVLink at
+    the measured peer-copy bandwidth, and its weight bytes from HBM at the measured copy bandwidth (the
+    last one is what binds a 64-token step)."""
+    import torch.distributed as dist
+    from .comm import Group, init_distributed, shutdown_distributed
+    from .comm.symm import FusedTP
+    from .config import preset
+    from .ops.native import NativeOps
+
+    rank, world, local = init_distributed("nccl", timeout_s=120)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    cfg = preset(args.model)
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    grp = Group()
+    ops = NativeOps(dev)
+    tokens = [int(t) for t in args.tokens.split(",")]
+    tp = FusedTP(grp, dev, H, max(tokens))
+    hbm, tflops, _ = _peaks()
+    bf = dict(device=dev, dtype=torch.bfloat16)
+    g = torch.Generator(device=dev).manual_seed(rank)
+    wo = (torch.randn(H, H // world, generator=g, **bf) * 0.02)              # row-parallel (K cut)
+    wgu = (torch.randn(2 * I // world, H, generator=g, **bf) * 0.02)         # column-parallel (N cut)
+    nw = torch.ones(H, **bf)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = []
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        tot = 0.0
+        for _ in range(args.iters):
+            flush.zero_()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            tot += e0.elapsed_time(e1)
+        t = torch.tensor([tot / args.iters], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for T in tokens:
+        a = torch.randn(T, H // world, generator=g, **bf)
+        bc = tp.use_bcast(T)
+        lo, hi = tp.my_rows(T)
+        res = torch.zeros(T if bc else max(hi - lo, 1), H, **bf)
+
+        def fused():
+            tp.linear_rs(a, wo, None, bc)
+            tp.norm(res, T, True, nw, 1e-6, 0.0, bc)
+            return ops.linear(tp.ag_local[:T], wgu) if bc else tp.linear_ag(T, wgu)
+
+        resl = torch.zeros(T, H, **bf)
+
+        def library():
+            y = ops.linear(a, wo)
+            dist.all_reduce(y)
+            h = ops.rmsnorm(resl, y, nw, 1e-6)
+            return ops.linear(h, wgu)
+
+        ms_f, ms_l = timed(fused), timed(library)
+        flops = 2.0 * T * H * (H / world) + 2.0 * T * H * (2 * I / world)
+        link = T * H * 2.0 * (world - 1) if bc else 2.0 * T * H * 2.0 * (world - 1) / world   # bytes out of one GPU
+        wbytes = 2.0 * (wo.numel() + wgu.numel())
+        t_c, t_l, t_m = flops / (tflops * 1e12), link / (NVLINK_GBS * 1e9), wbytes / (hbm * 1e9)
+        roof = max(t_c, t_l, t_m)
+        row = {"tp": world, "tokens": T, "layout": "broadcast" if bc else "scatter", "fused_us": ms_f * 1e3,
+               "library_us": ms_l * 1e3, "roof_us": roof * 1e6, "bound": "mma" if roof == t_c else "nvlink" if roof == t_l else "hbm",
+               "compute_us": t_c * 1e6, "nvlink_us": t_l * 1e6, "hbm_us": t_m * 1e6, "fused_frac": roof / (ms_f / 1e3),
+               "library_frac": roof / (ms_l / 1e3), "status": tp.check_status() | ops.check_status()}
+        rows.append(row)
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+    if rank == 0 and args.json:
+        json.dump({"peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "nvlink_gbs": NVLINK_GBS}, "rows": rows},
+                  open(args.json, "w"), indent=1)
+    dist.barrier()
+    tp.close()
+    shutdown_distributed()
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="qwen3-8b")
@@ -51,7 +233,18 @@ def main(argv=None) -> None:
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--json", default="")
     ap.add_argument("--fp4", action="store_true", help="only the packed FP4 (NVFP4 / MXFP4) decode GEMMs")
+    ap.add_argument("--case", default="", help="run ONE kernel family a few times and exit (see run_case)")
+    ap.add_argument("--reps", type=int, default=4)
+    ap.add_argument("--tp-half-layer", action="store_true",
+                    help="fused vs library tensor-parallel half-layer (one process per GPU under torch.distributed.run)")
+    ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args(argv)
+    if args.case:
+        return run_case(args.case, args.reps)
+    if args.tp_half_layer:
+        if args.tokens == ap.get_default("tokens"):
+            args.tokens = "64,2048"
+        return tp_half_layer(args)
     from .config import preset
     from .ops.native import NativeOps
 

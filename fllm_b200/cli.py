@@ -199,9 +199,9 @@ def cmd_plan_cluster(args) -> int:
     return 0
 
 
-def _pytest(marker: str, pattern: str) -> int:
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    return subprocess.call([sys.executable, "-m", "pytest", os.path.join(root, "tests"), "-q", "-m", marker, "-k", pattern])
+def _selftest(which: str) -> int:
+    from . import selftest
+    return selftest.main([which])
 
 
 def main(argv: Optional[List[str]] = None) -> int:
@@ -280,10 +280,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     b.add_argument("rest", nargs=argparse.REMAINDER)
     b.set_defaults(fn=lambda a: subprocess.call([sys.executable, os.path.join(os.path.dirname(os.path.dirname(
         os.path.abspath(__file__))), "bench.py")] + a.rest))
-    sub.add_parser("selftest-cpu").set_defaults(fn=lambda a: _pytest("not gpu", "formats or engine_cpu"))
-    sub.add_parser("selftest-gpu").set_defaults(fn=lambda a: _pytest("gpu", "kernels or engine_gpu"))
-    sub.add_parser("selftest-comm").set_defaults(fn=lambda a: _pytest("not gpu", "comm"))
-    sub.add_parser("selftest-parallel").set_defaults(fn=lambda a: _pytest("not gpu", "tp_cpu or parallel"))
+    for which in ("cpu", "gpu", "comm", "parallel"):
+        sub.add_parser(f"selftest-{which}").set_defaults(fn=lambda a, w=which: _selftest(w))
     args = ap.parse_args(argv)
     return int(args.fn(args) or 0)
 

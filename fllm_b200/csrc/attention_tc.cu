@@ -545,15 +545,12 @@ size_t attention_tc_workspace_bytes(int tokens, int hq, int head_dim, int max_sp
 template <int D>
 static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int min_q_len, int max_kv_len,
                      void* workspace, size_t workspace_bytes, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxDevices] = {};
+  if (first_call_on_device(configured)) {
     cuda_check(cudaFuncSetAttribute(fa_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     DecodeSmem<D>::kTotal), "fa_decode smem");
     cuda_check(cudaFuncSetAttribute(fa_prefill_kernel<D, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     PrefillSmem<D, 64>::kTotal), "fa_prefill smem");
-    cuda_check(cudaFuncSetAttribute(fa_prefill_kernel<D, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    PrefillSmem<D, 128>::kTotal), "fa_prefill smem");
-    configured = true;
   }
   int launches = 0;
   const int decode_max_q = 16 / p.group;            // packed rows must fit one 16-row MMA tile
@@ -565,11 +562,6 @@ static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int mi
     int splits = 1;
     // a grid of at least one CTA per SM streams KV well enough; splitting costs a merge launch
     if (ctas < sm_count()) splits = min(min((2 * sm_count() + ctas - 1) / ctas, (pages + 7) / 8), 32);
-    {
-      static int forced = -1;
-      if (forced < 0) { const char* e = getenv("FLLM_ATTN_SPLITS"); forced = e ? atoi(e) : 0; }
-      if (forced > 0) splits = min(forced, max(pages / 2, 1));
-    }
     splits = max(splits, 1);
     // partials of prefill sequences do not exist, so a mixed batch is never split
     if (max_q_len > decode_max_q || !workspace) splits = 1;
@@ -596,18 +588,13 @@ static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int mi
                            p.window, p.sinks, p.softcap, p.status, s);
     ++launches;
   } else if (max_q_len > decode_max_q) {
-    // FLLM_FA_PREFILL_ROWS=128 selects 128 packed rows per CTA (8 warps sharing every K/V tile). Measured equal to
-    // the 64-row tile (119 vs 121 TFLOP/s at 2 x 1024 tokens): the kernel is bound by the mma.sync / softmax
-    // pipeline of each warp, not by K/V traffic, so the smaller tile stays the default.
-    static int rows_pref = -1;
-    if (rows_pref < 0) { const char* e = getenv("FLLM_FA_PREFILL_ROWS"); rows_pref = e ? atoi(e) : 64; }
-    const bool big = rows_pref >= 128 && max_q_len * p.group >= 128;
-    const int rq = (big ? 128 : 64) / p.group;
+    // 64 packed rows per CTA. (128 rows, 8 warps sharing every K/V tile, measured equal - 119 vs 121 TFLOP/s at
+    // 2 x 1024 tokens: the kernel is bound by the mma.sync / softmax pipeline of each warp, not by K/V traffic.)
+    const int rq = 64 / p.group;
     if (rq < 1) throw std::runtime_error("attention_tc: more than 64 query heads per KV head");
     dim3 grid((max_q_len + rq - 1) / rq, p.hkv, num_seqs);
     p.splits = 1;
-    if (big) fa_prefill_kernel<D, 128><<<grid, 256, PrefillSmem<D, 128>::kTotal, s>>>(p);
-    else fa_prefill_kernel<D, 64><<<grid, 128, PrefillSmem<D, 64>::kTotal, s>>>(p);
+    fa_prefill_kernel<D, 64><<<grid, 128, PrefillSmem<D, 64>::kTotal, s>>>(p);
     ++launches;
   }
   cuda_check(cudaGetLastError(), "attention_tc launch");

@@ -55,6 +55,7 @@ struct FaTmemParams {
   int min_q;             // sequences with fewer query rows are not this kernel's
   float scale_log2, softcap, scale;
   int pv_wide;           // one N=128 MMA per 16 tokens instead of two N=64 ones
+  int tile_variant;      // 0: pick by shape; 1 / 2: force one / two query tiles per CTA
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -617,17 +618,15 @@ struct MapPair { CUtensorMap k, v; };
 
 template <int D>
 void launch_tmem(const MapPair& maps, const FaTmemParams& p, int max_q_len, int num_seqs, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxDevices] = {};
+  if (first_call_on_device(configured)) {
     cuda_check(cudaFuncSetAttribute(fa_prefill_tmem_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_one<D>()),
                "fa_prefill_tmem smem");
     cuda_check(cudaFuncSetAttribute(fa_prefill_tmem2_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_two<D>()),
                "fa_prefill_tmem2 smem");
-    configured = true;
   }
-  // Two query tiles per CTA when that still gives every SM a CTA (FLLM_FA_TMEM_TILES=1 / 2 forces a variant).
-  static int forced = -1;
-  if (forced < 0) { const char* e = getenv("FLLM_FA_TMEM_TILES"); forced = e ? atoi(e) : 0; }
+  // Two query tiles per CTA when that still gives every SM a CTA (tile_variant 1 / 2 forces one: tests only).
+  const int forced = p.tile_variant;
   const int rq2 = 2 * kRowsT / p.group;
   const long long ctas2 = (long long)((max_q_len + rq2 - 1) / rq2) * p.hkv * num_seqs;
   const bool two = forced ? forced == 2 : (max_q_len * p.group >= 2 * kRowsT && ctas2 >= sm_count());
@@ -653,7 +652,7 @@ void attention_prefill_tmem(const void* q, long long ldq, const void* k_cache, c
                             const int* block_tables, int max_blocks, const int* q_starts, const int* kv_lens,
                             void* out, long long ldo, int num_seqs, int max_q_len, int min_q, int hq, int hkv,
                             int head_dim, float scale, int window, const float* sinks, float softcap, int* status,
-                            cudaStream_t s) {
+                            cudaStream_t s, int tile_variant) {
   static std::unordered_map<MapKey, MapPair, MapKeyHash> maps;
   const uint64_t rows = (uint64_t)num_blocks * hkv * kPageT;
   const MapKey key{k_cache, v_cache, rows, head_dim};
@@ -674,9 +673,8 @@ void attention_prefill_tmem(const void* q, long long ldq, const void* k_cache, c
   p.hkv = hkv; p.group = hq / hkv;
   p.window = window; p.min_q = min_q;
   p.scale = scale; p.scale_log2 = scale * kLog2eT; p.softcap = softcap;
-  static int wide = -1;
-  if (wide < 0) { const char* e = getenv("FLLM_FA_PV_WIDE"); wide = e ? atoi(e) : 1; }
-  p.pv_wide = wide;
+  p.pv_wide = 1;
+  p.tile_variant = tile_variant;
   if (head_dim == 64) launch_tmem<64>(it->second, p, max_q_len, num_seqs, s);
   else launch_tmem<128>(it->second, p, max_q_len, num_seqs, s);
 }

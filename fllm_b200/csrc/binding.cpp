@@ -54,6 +54,51 @@ int64_t linear(const Tensor& x, const Tensor& w, const optional<Tensor>& bias, T
                     ws_bytes, st, (int)force_splits, cur_stream());
 }
 
+// linear with the optional behaviours of fllm::LinearExtras. glu > 0: y is [T, N / 2] (the activation runs in the
+// epilogue, or in the caller's consumer when the call deferred split-K). Returns [kernels launched, deferred splits].
+std::vector<int64_t> linear_ex(const Tensor& x, const Tensor& w, const optional<Tensor>& bias, Tensor y,
+                               const optional<Tensor>& workspace, const optional<Tensor>& status, int64_t force_splits,
+                               int64_t glu, int64_t glu_pd, double glu_alpha, double glu_limit, bool defer_reduce) {
+  check_bf16(x, "x"); check_bf16(w, "w"); check_bf16(y, "y");
+  check_rows(x, "x"); check_rows(w, "w"); check_rows(y, "y");
+  TORCH_CHECK(x.size(1) == w.size(1), "linear: K mismatch");
+  TORCH_CHECK(y.size(0) == x.size(0) && y.size(1) == (glu ? w.size(0) / 2 : w.size(0)), "linear: output shape mismatch");
+  c10::cuda::CUDAGuard guard(x.device());
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  if (workspace.has_value() && workspace->defined()) {
+    ws = workspace->data_ptr();
+    ws_bytes = workspace->nbytes();
+  }
+  int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  fllm::LinearExtras ex;
+  ex.glu = (int)glu; ex.glu_pd = (int)glu_pd; ex.glu_alpha = (float)glu_alpha; ex.glu_limit = (float)glu_limit;
+  ex.defer_reduce = defer_reduce ? 1 : 0;
+  const int n = fllm::linear_bf16(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), opt_ptr<void>(bias),
+                                  y.data_ptr(), y.stride(0), (int)x.size(0), (int)w.size(0), (int)x.size(1), ws,
+                                  ws_bytes, st, (int)force_splits, cur_stream(), &ex);
+  return {n, ex.deferred_splits};
+}
+
+inline const float* partials_ptr(const Tensor& workspace, int64_t splits, int64_t rows, int64_t cols) {
+  TORCH_CHECK(workspace.is_cuda() && workspace.is_contiguous(), "workspace must be a contiguous CUDA tensor");
+  TORCH_CHECK(splits >= 1 && (size_t)workspace.nbytes() >= fllm::kLinearPartialsOffset + (size_t)splits * rows * cols * 4,
+              "workspace too small for the split-K partials");
+  return reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(workspace.data_ptr()) + fllm::kLinearPartialsOffset);
+}
+
+// residual += bf16(sum of the split-K partials in `workspace` + bias); y = rmsnorm(residual) * w
+void rmsnorm_splitk(Tensor residual, const Tensor& workspace, int64_t splits, const optional<Tensor>& bias,
+                    const Tensor& w, Tensor y, double eps, double w_offset) {
+  check_bf16(residual, "residual"); check_bf16(w, "w"); check_bf16(y, "y");
+  check_rows(residual, "residual"); check_rows(y, "y");
+  c10::cuda::CUDAGuard guard(y.device());
+  const float* ws = partials_ptr(workspace, splits, residual.size(0), residual.size(1));
+  fllm::rmsnorm_splitk_bf16(residual.data_ptr(), residual.stride(0), ws, (int)splits, opt_ptr<void>(bias), w.data_ptr(),
+                            y.data_ptr(), y.stride(0), (int)residual.size(0), (int)residual.size(1), (float)eps,
+                            (float)w_offset, cur_stream());
+}
+
 void embed(const Tensor& ids, const Tensor& table, Tensor out, double scale) {
   check_i32(ids, "ids"); check_bf16(table, "table"); check_bf16(out, "out");
   TORCH_CHECK(table.is_contiguous() && out.is_contiguous(), "embed: contiguous tensors expected");
@@ -96,6 +141,51 @@ void rope_kv_write(Tensor qkv, const Tensor& positions, const optional<Tensor>& 
       k_cache.data_ptr(), v_cache.data_ptr(), (int)qkv.size(0), (int)hq, (int)hkv, (int)head_dim,
       (int)k_cache.size(2), (int)rot_dim, (int)rope_style, (float)eps, (float)attn_factor,
       cur_stream(), kv_fp8 ? 1 : 0);
+}
+
+// QK-norm + RoPE + KV write reading the q|k|v heads from split-K partials; rotated queries go to q_out
+void rope_kv_write_splitk(const Tensor& workspace, int64_t splits, const optional<Tensor>& bias, Tensor q_out,
+                          const Tensor& positions, const optional<Tensor>& slots, const Tensor& inv_freq,
+                          const optional<Tensor>& q_norm_w, const optional<Tensor>& k_norm_w, Tensor k_cache,
+                          Tensor v_cache, int64_t hq, int64_t hkv, int64_t head_dim, int64_t rot_dim,
+                          int64_t rope_style, double eps, double attn_factor) {
+  check_bf16(q_out, "q_out"); check_rows(q_out, "q_out"); check_i32(positions, "positions");
+  const bool kv_fp8 = k_cache.element_size() == 1;
+  TORCH_CHECK(k_cache.is_cuda() && k_cache.element_size() == v_cache.element_size() &&
+              (kv_fp8 || k_cache.scalar_type() == at::kBFloat16), "caches must be bf16 or 1-byte e4m3 tensors");
+  TORCH_CHECK(inv_freq.scalar_type() == at::kFloat && inv_freq.is_cuda(), "inv_freq must be fp32 CUDA");
+  TORCH_CHECK(q_out.size(1) == hq * head_dim, "rope_kv_write_splitk: q width mismatch");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous(),
+              "caches must be [blocks, kv_heads, block_size, head_dim]");
+  c10::cuda::CUDAGuard guard(q_out.device());
+  const int tokens = (int)q_out.size(0);
+  const float* ws = partials_ptr(workspace, splits, tokens, (hq + 2 * hkv) * head_dim);
+  fllm::rope_qknorm_kvwrite_bf16(
+      nullptr, 0, positions.data_ptr<int>(), opt_ptr<int>(slots), inv_freq.data_ptr<float>(),
+      opt_ptr<void>(q_norm_w), opt_ptr<void>(k_norm_w), k_cache.data_ptr(), v_cache.data_ptr(), tokens, (int)hq,
+      (int)hkv, (int)head_dim, (int)k_cache.size(2), (int)rot_dim, (int)rope_style, (float)eps, (float)attn_factor,
+      cur_stream(), kv_fp8 ? 1 : 0, ws, (int)splits, opt_ptr<void>(bias), q_out.data_ptr(), q_out.stride(0));
+}
+
+// glu with a column layout (0 natural, 16 blocked) and, when splits > 0, split-K partials as the source
+void glu_ex(const optional<Tensor>& x, Tensor out, int64_t act_kind, double alpha, double limit, int64_t layout,
+            const optional<Tensor>& workspace, int64_t splits, const optional<Tensor>& bias) {
+  check_bf16(out, "out"); check_rows(out, "out");
+  c10::cuda::CUDAGuard guard(out.device());
+  const float* ws = nullptr;
+  const void* xp = nullptr;
+  long long ldx = 0;
+  if (splits > 0) {
+    TORCH_CHECK(workspace.has_value(), "glu_ex: workspace expected");
+    ws = partials_ptr(*workspace, splits, out.size(0), 2 * out.size(1));
+  } else {
+    TORCH_CHECK(x.has_value(), "glu_ex: x expected");
+    check_bf16(*x, "x"); check_rows(*x, "x");
+    TORCH_CHECK(x->size(1) == 2 * out.size(1) && x->size(0) == out.size(0), "glu: shape mismatch");
+    xp = x->data_ptr(); ldx = x->stride(0);
+  }
+  fllm::glu_bf16(xp, ldx, out.data_ptr(), out.stride(0), (int)out.size(0), (int)out.size(1), (int)act_kind,
+                 (float)alpha, (float)limit, cur_stream(), (int)layout, ws, (int)splits, opt_ptr<void>(bias));
 }
 
 void glu(const Tensor& x, Tensor out, int64_t act_kind, double alpha, double limit) {
@@ -173,6 +263,33 @@ void argmax(const Tensor& logits, Tensor out_ids, const optional<Tensor>& out_va
                     (int)logits.size(1), out_ids.data_ptr<int>(), ov, (int)id_offset, cur_stream());
 }
 
+void argmax_split(const Tensor& logits, Tensor out_ids, const optional<Tensor>& out_vals, const optional<Tensor>& out_pairs,
+                  int64_t id_offset, Tensor scratch) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "argmax: bad logits");
+  const bool f32 = logits.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || logits.scalar_type() == at::kBFloat16, "argmax: logits must be fp32 or bf16");
+  check_i32(out_ids, "out_ids");
+  TORCH_CHECK(scratch.is_cuda() && scratch.is_contiguous(), "argmax_split: scratch must be a contiguous CUDA tensor");
+  c10::cuda::CUDAGuard guard(logits.device());
+  float* ov = out_vals.has_value() && out_vals->defined() ? out_vals->data_ptr<float>() : nullptr;
+  float* op = nullptr;
+  if (out_pairs.has_value() && out_pairs->defined()) {
+    TORCH_CHECK(out_pairs->scalar_type() == at::kFloat && out_pairs->is_contiguous() && out_pairs->numel() >= 2 * logits.size(0),
+                "argmax_split: out_pairs must be fp32 [rows, 2]");
+    op = out_pairs->data_ptr<float>();
+  }
+  fllm::argmax_rows_split(logits.data_ptr(), f32, logits.stride(0), (int)logits.size(0), (int)logits.size(1),
+                          out_ids.data_ptr<int>(), ov, op, (int)id_offset, scratch.data_ptr(), scratch.nbytes(), cur_stream());
+}
+
+void argmax_pairs_select(const Tensor& pairs, Tensor out_ids) {
+  TORCH_CHECK(pairs.is_cuda() && pairs.scalar_type() == at::kFloat && pairs.is_contiguous() && pairs.dim() == 3 &&
+              pairs.size(2) == 2, "argmax_pairs_select: pairs must be fp32 [ranks, rows, 2]");
+  check_i32(out_ids, "out_ids");
+  c10::cuda::CUDAGuard guard(pairs.device());
+  fllm::argmax_pairs_select(pairs.data_ptr<float>(), (int)pairs.size(0), (int)pairs.size(1), out_ids.data_ptr<int>(), cur_stream());
+}
+
 // params: uint8 tensor holding rows x sizeof(SampleRow) bytes laid out like fllm::SampleRow.
 void sample(Tensor logits, const Tensor& params, const optional<Tensor>& pen_ids,
             const optional<Tensor>& pen_counts, const optional<Tensor>& bias_ids,
@@ -241,6 +358,10 @@ int64_t sample_row_bytes() { return (int64_t)sizeof(fllm::SampleRow); }
 
 TORCH_LIBRARY(fllm_b200, m) {
   m.def("linear(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status, int force_splits) -> int", &linear);
+  m.def("linear_ex(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status, int force_splits, int glu, int glu_pd, float glu_alpha, float glu_limit, bool defer_reduce) -> int[]", &linear_ex);
+  m.def("rmsnorm_splitk(Tensor(a!) residual, Tensor workspace, int splits, Tensor? bias, Tensor w, Tensor(b!) y, float eps, float w_offset) -> ()", &rmsnorm_splitk);
+  m.def("rope_kv_write_splitk(Tensor workspace, int splits, Tensor? bias, Tensor(a!) q_out, Tensor positions, Tensor? slots, Tensor inv_freq, Tensor? q_norm_w, Tensor? k_norm_w, Tensor(b!) k_cache, Tensor(c!) v_cache, int hq, int hkv, int head_dim, int rot_dim, int rope_style, float eps, float attn_factor) -> ()", &rope_kv_write_splitk);
+  m.def("glu_ex(Tensor? x, Tensor(a!) out, int act_kind, float alpha, float limit, int layout, Tensor? workspace, int splits, Tensor? bias) -> ()", &glu_ex);
   m.def("embed(Tensor ids, Tensor table, Tensor(a!) out, float scale) -> ()", &embed);
   m.def("rmsnorm(Tensor(a!) residual, Tensor? delta, Tensor w, Tensor(b!) y, float eps, float w_offset) -> ()", &rmsnorm);
   m.def("rope_kv_write(Tensor(a!) qkv, Tensor positions, Tensor? slots, Tensor inv_freq, Tensor? q_norm_w, Tensor? k_norm_w, Tensor(b!) k_cache, Tensor(c!) v_cache, int hq, int hkv, int head_dim, int rot_dim, int rope_style, float eps, float attn_factor) -> ()", &rope_kv_write);
@@ -249,6 +370,8 @@ TORCH_LIBRARY(fllm_b200, m) {
   m.def("attention_generic(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor row_seq, Tensor positions, Tensor(a!) out, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap) -> ()", &attention_generic);
   m.def("attention_tc(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor q_starts, Tensor kv_lens, Tensor(a!) out, int num_seqs, int max_q_len, int min_q_len, int max_kv_len, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap, Tensor? workspace, Tensor? status=None) -> int", &attention_tc);
   m.def("argmax(Tensor logits, Tensor(a!) out_ids, Tensor? out_vals, int id_offset) -> ()", &argmax);
+  m.def("argmax_split(Tensor logits, Tensor(a!) out_ids, Tensor? out_vals, Tensor? out_pairs, int id_offset, Tensor(b!) scratch) -> ()", &argmax_split);
+  m.def("argmax_pairs_select(Tensor pairs, Tensor(a!) out_ids) -> ()", &argmax_pairs_select);
   m.def("sample(Tensor(a!) logits, Tensor params, Tensor? pen_ids, Tensor? pen_counts, Tensor? bias_ids, Tensor? bias_vals, Tensor? allow_mask, Tensor(b!) out_ids, Tensor? out_logprobs) -> ()", &sample);
   m.def("spec_verify_greedy(Tensor draft_ids, Tensor target_ids, Tensor? n_draft, Tensor(a!) n_accept, Tensor(b!) out_tokens) -> ()", &spec_verify_greedy);
   m.def("spec_verify_sampled(Tensor target_logits, Tensor draft_logits, Tensor draft_ids, Tensor? n_draft, Tensor params, Tensor(a!) n_accept, Tensor(b!) out_tokens) -> ()", &spec_verify_sampled);

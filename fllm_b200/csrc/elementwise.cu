@@ -145,6 +145,109 @@ void rmsnorm_bf16(void* residual, long long ld_res, const void* delta, long long
   cuda_check(cudaGetLastError(), "rmsnorm_kernel");
 }
 
+// Split-K reduction + bias + residual add + RMSNorm in one pass. The projection before the norm left
+// fp32 partial sums [splits][rows][hidden]; one CTA per row with a thread per four columns keeps as many
+// loads in flight as the stand-alone reduction kernel did. Rounding points are those of the two-kernel
+// path (delta -> bf16, updated residual -> bf16), so both paths give the same bits.
+template <int ITERS>
+__global__ void __launch_bounds__(1024)
+rmsnorm_splitk_kernel(__nv_bfloat16* __restrict__ residual, long long ld_res, const float* __restrict__ ws,
+                      int splits, int rows, const __nv_bfloat16* __restrict__ bias,
+                      const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, long long ld_y,
+                      int hidden, float eps, float w_offset) {
+  pdl_launch_dependents();
+  const int row = blockIdx.x;
+  const int nvec = hidden / 4;
+  __nv_bfloat16* xr = residual + (size_t)row * ld_res;
+  // the residual was written several kernels ago and the weights are static: fetch them before the wait
+  uint2 xv[ITERS], wv[ITERS];
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = threadIdx.x + it * blockDim.x;
+    if (i < nvec) {
+      xv[it] = reinterpret_cast<const uint2*>(xr)[i];
+      wv[it] = reinterpret_cast<const uint2*>(w)[i];
+    }
+  }
+  pdl_wait();
+  const size_t plane = (size_t)rows * hidden;
+  float vals[ITERS][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = threadIdx.x + it * blockDim.x;
+    if (i < nvec) {
+      const float* src = ws + (size_t)row * hidden + 4 * i;
+      float4 acc = __ldcg(reinterpret_cast<const float4*>(src));
+#pragma unroll 4
+      for (int sp = 1; sp < splits; ++sp) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(src + sp * plane));
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      if (bias) {
+        const uint2 bb = reinterpret_cast<const uint2*>(bias)[i];
+        const float2 b0 = unpack_bf16x2(bb.x), b1 = unpack_bf16x2(bb.y);
+        acc.x += b0.x; acc.y += b0.y; acc.z += b1.x; acc.w += b1.y;
+      }
+      const float2 d0 = unpack_bf16x2(pack_bf16x2(acc.x, acc.y)), d1 = unpack_bf16x2(pack_bf16x2(acc.z, acc.w));
+      const float2 x0 = unpack_bf16x2(xv[it].x), x1 = unpack_bf16x2(xv[it].y);
+      uint2 o;
+      o.x = pack_bf16x2(x0.x + d0.x, x0.y + d0.y);
+      o.y = pack_bf16x2(x1.x + d1.x, x1.y + d1.y);
+      reinterpret_cast<uint2*>(xr)[i] = o;
+      const float2 n0 = unpack_bf16x2(o.x), n1 = unpack_bf16x2(o.y);
+      vals[it][0] = n0.x; vals[it][1] = n0.y; vals[it][2] = n1.x; vals[it][3] = n1.y;
+      ss += n0.x * n0.x + n0.y * n0.y + n1.x * n1.x + n1.y * n1.y;
+    }
+  }
+  __shared__ float red[32];
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  const int nw = blockDim.x >> 5;
+  for (int i = 0; i < nw; ++i) tot += red[i];
+  const float inv = rsqrtf(tot / (float)hidden + eps);
+  __nv_bfloat16* yr = y + (size_t)row * ld_y;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = threadIdx.x + it * blockDim.x;
+    if (i < nvec) {
+      const float2 g0 = unpack_bf16x2(wv[it].x), g1 = unpack_bf16x2(wv[it].y);
+      uint2 o;
+      o.x = pack_bf16x2(vals[it][0] * inv * (g0.x + w_offset), vals[it][1] * inv * (g0.y + w_offset));
+      o.y = pack_bf16x2(vals[it][2] * inv * (g1.x + w_offset), vals[it][3] * inv * (g1.y + w_offset));
+      reinterpret_cast<uint2*>(yr)[i] = o;
+    }
+  }
+}
+
+void rmsnorm_splitk_bf16(void* residual, long long ld_res, const float* partials, int splits, const void* bias,
+                         const void* w, void* y, long long ld_y, int rows, int hidden, float eps, float w_offset,
+                         cudaStream_t s) {
+  if (rows <= 0) return;
+  if (hidden % 4 || hidden > 16384 || (ld_res & 3) || (ld_y & 3) || splits < 1)
+    throw std::runtime_error("rmsnorm_splitk_bf16: hidden must be a multiple of 4 and at most 16384");
+  const int nvec = hidden / 4;
+  const int threads = min(1024, (nvec + 31) / 32 * 32);
+  const int iters = (nvec + threads - 1) / threads;
+  auto* r = (__nv_bfloat16*)residual;
+  auto* b = (const __nv_bfloat16*)bias;
+  auto* ww = (const __nv_bfloat16*)w;
+  auto* yy = (__nv_bfloat16*)y;
+#define FLLM_RMS_SK(IT)                                                                                       \
+  launch_pdl(rmsnorm_splitk_kernel<IT>, dim3(rows), dim3(threads), 0, s, r, ld_res, partials, splits, rows, b, ww, yy, \
+             ld_y, hidden, eps, w_offset)
+  switch (iters) {
+    case 1: FLLM_RMS_SK(1); break;
+    case 2: FLLM_RMS_SK(2); break;
+    case 3: FLLM_RMS_SK(3); break;
+    default: FLLM_RMS_SK(4); break;
+  }
+#undef FLLM_RMS_SK
+  cuda_check(cudaGetLastError(), "rmsnorm_splitk_kernel");
+}
+
 // ---------------------------------------------------------------------------- RoPE + QK-norm + KV write
 // One warp per (token, head). Heads [0, hq) are query heads (rotated in place),
 // [hq, hq+hkv) key heads (normalised, rotated, written to the paged cache),
@@ -158,7 +261,11 @@ rope_kv_kernel(__nv_bfloat16* __restrict__ qkv, long long ld_qkv, const int* __r
                const __nv_bfloat16* __restrict__ q_norm_w, const __nv_bfloat16* __restrict__ k_norm_w,
                __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int tokens,
                int hq, int hkv, int block_size, int rot_dim, int rope_style, float eps,
-               float attn_factor, int kv_fp8) {
+               float attn_factor, int kv_fp8, const float* __restrict__ ws, int splits,
+               const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ q_out, long long ld_q) {
+  // ws != null: the projection left fp32 split-K partials [splits][tokens][heads * D] (bias not added);
+  // this kernel adds them, rounds to bf16 like the reduction kernel would, and writes the rotated query
+  // heads to q_out (the key / value heads only go to the cache).
   constexpr int EPL = D / 32;  // elements per lane
   pdl_launch_dependents();
   pdl_wait();
@@ -168,8 +275,19 @@ rope_kv_kernel(__nv_bfloat16* __restrict__ qkv, long long ld_qkv, const int* __r
   const int t = (int)(gw / heads);
   const int h = (int)(gw - (long long)t * heads);
   const int lane = threadIdx.x & 31;
-  __nv_bfloat16* src = qkv + (size_t)t * ld_qkv + (size_t)h * D;
+  __nv_bfloat16* src = qkv ? qkv + (size_t)t * ld_qkv + (size_t)h * D : nullptr;
   const int slot = slots ? slots[t] : -1;
+  const size_t width = (size_t)heads * D;
+  const size_t plane = (size_t)tokens * width;
+  const float* wsrc = ws ? ws + (size_t)t * width + (size_t)h * D : nullptr;
+  // element e of this head as the bf16 value the unfused path would have stored
+  auto ld_elem = [&](int e) -> float {
+    if (!ws) return __bfloat162float(src[e]);
+    float a = __ldcg(wsrc + e);
+    for (int sp = 1; sp < splits; ++sp) a += __ldcg(wsrc + sp * plane + e);
+    if (bias) a += __bfloat162float(bias[h * D + e]);
+    return __bfloat162float(__float2bfloat16(a));
+  };
 
   if (h >= hq + hkv) {  // value head: straight copy
     if (slot < 0) return;
@@ -179,8 +297,26 @@ rope_kv_kernel(__nv_bfloat16* __restrict__ qkv, long long ld_qkv, const int* __r
     if (kv_fp8) {                  // e4m3 cache: one byte per value, same [block][head][slot][dim] order
       uint8_t* d8 = reinterpret_cast<uint8_t*>(v_cache) + (((size_t)blk * hkv + kvh) * block_size + off) * D;
       for (int i = lane; i < D / 2; i += 32) {
-        const float2 f = unpack_bf16x2(reinterpret_cast<const uint32_t*>(src)[i]);
+        const float2 f = ws ? make_float2(ld_elem(2 * i), ld_elem(2 * i + 1))
+                            : unpack_bf16x2(reinterpret_cast<const uint32_t*>(src)[i]);
         reinterpret_cast<uint16_t*>(d8)[i] = (uint16_t)__nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
+      }
+      return;
+    }
+    if (ws) {
+      float a[EPL];            // pairs (2i, 2i+1), i = lane + 32 * (j / 2): every load of a split is independent
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) a[j] = __ldcg(wsrc + 2 * (lane + 32 * (j / 2)) + (j & 1));
+#pragma unroll 4
+      for (int sp = 1; sp < splits; ++sp) {
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) a[j] += __ldcg(wsrc + sp * plane + 2 * (lane + 32 * (j / 2)) + (j & 1));
+      }
+#pragma unroll
+      for (int j = 0; j < EPL; j += 2) {
+        const int e = 2 * (lane + 32 * (j / 2));
+        if (bias) { a[j] += __bfloat162float(bias[h * D + e]); a[j + 1] += __bfloat162float(bias[h * D + e + 1]); }
+        reinterpret_cast<uint32_t*>(dst)[lane + 32 * (j / 2)] = pack_bf16x2(a[j], a[j + 1]);
       }
       return;
     }
@@ -197,7 +333,25 @@ rope_kv_kernel(__nv_bfloat16* __restrict__ qkv, long long ld_qkv, const int* __r
   // rotate-half partner of element i (i + rot/2) then sits in the same lane whenever
   // rot/2 is a multiple of 32, and in lane l for the interleaved style we use pairs.
   float v[EPL];
-  if (rope_style == 0) {
+  int eidx[EPL];               // element index of v[j] within the head
+#pragma unroll
+  for (int j = 0; j < EPL; ++j)
+    eidx[j] = rope_style == 0 ? lane + 32 * j : 2 * (lane + 32 * (j / 2)) + (j & 1);
+  if (ws) {
+    // all EPL loads of a split are independent; four splits are in flight at a time
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) v[j] = __ldcg(wsrc + eidx[j]);
+#pragma unroll 4
+    for (int sp = 1; sp < splits; ++sp) {
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) v[j] += __ldcg(wsrc + sp * plane + eidx[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      if (bias) v[j] += __bfloat162float(bias[h * D + eidx[j]]);
+      v[j] = __bfloat162float(__float2bfloat16(v[j]));
+    }
+  } else if (rope_style == 0) {
 #pragma unroll
     for (int j = 0; j < EPL; ++j) v[j] = __bfloat162float(src[lane + 32 * j]);
   } else {
@@ -283,7 +437,7 @@ rope_kv_kernel(__nv_bfloat16* __restrict__ qkv, long long ld_qkv, const int* __r
   }
   __nv_bfloat16* dst;
   if (is_q) {
-    dst = src;
+    dst = q_out ? q_out + (size_t)t * ld_q + (size_t)h * D : src;
   } else {
     if (slot < 0) return;
     const int kvh = h - hq;
@@ -317,8 +471,10 @@ void rope_qknorm_kvwrite_bf16(void* qkv, long long ld_qkv, const int* positions,
                               const float* inv_freq, const void* q_norm_w, const void* k_norm_w,
                               void* k_cache, void* v_cache, int tokens, int hq, int hkv,
                               int head_dim, int block_size, int rot_dim, int rope_style, float eps,
-                              float attn_factor, cudaStream_t s, int kv_fp8) {
+                              float attn_factor, cudaStream_t s, int kv_fp8, const float* partials, int splits,
+                              const void* bias, void* q_out, long long ld_q) {
   if (tokens <= 0) return;
+  if (!qkv && !(partials && q_out)) throw std::runtime_error("rope_qknorm_kvwrite_bf16: no source");
   const long long warps = (long long)tokens * (hq + 2 * hkv);
   const int blocks = (int)((warps + 3) / 4);
   auto* x = (__nv_bfloat16*)qkv;
@@ -328,7 +484,8 @@ void rope_qknorm_kvwrite_bf16(void* qkv, long long ld_qkv, const int* positions,
   auto* vc = (__nv_bfloat16*)v_cache;
 #define FLLM_ROPE(DD)                                                                            \
   launch_pdl(rope_kv_kernel<DD>, dim3(blocks), dim3(128), 0, s, x, ld_qkv, positions, slots, inv_freq, qn, kn, kc, \
-             vc, tokens, hq, hkv, block_size, rot_dim, rope_style, eps, attn_factor, kv_fp8)
+             vc, tokens, hq, hkv, block_size, rot_dim, rope_style, eps, attn_factor, kv_fp8, partials, splits,    \
+             (const __nv_bfloat16*)bias, (__nv_bfloat16*)q_out, ld_q)
   switch (head_dim) {
     case 64: FLLM_ROPE(64); break;
     case 128: FLLM_ROPE(128); break;
@@ -344,17 +501,53 @@ void rope_qknorm_kvwrite_bf16(void* qkv, long long ld_qkv, const int* positions,
 // act_kind 1: gelu_tanh(gate) * up (GeGLU)
 // act_kind 2: gpt-oss clamped SwiGLU on interleaved columns (gate = x[2i], up = x[2i+1]):
 //             g = min(g, limit); u = clamp(u, -limit, limit); out = g * sigmoid(alpha g) * (u + 1)
+// layout: 0 = the kind's natural one (halves; pairs for kind 2), 16 = blocks of 16 gate columns followed
+// by the 16 up columns of the same features (the order the GEMM's gated epilogue wants its weight rows in).
+// ws != null: x is not read; the columns are the sums of fp32 split-K partials [splits][rows][2 * inter]
+// (+ bias), rounded to bf16 like the reduction kernel would have stored them.
 __global__ void glu_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                            __nv_bfloat16* __restrict__ out, long long ldo, int inter, int act_kind,
-                           float alpha, float limit) {
+                           float alpha, float limit, int layout, const float* __restrict__ ws, int splits,
+                           int rows, const __nv_bfloat16* __restrict__ bias) {
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.y;
   const int i8 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i8 >= inter) return;
-  const __nv_bfloat16* xr = x + (size_t)row * ldx;
+  const __nv_bfloat16* xr = x ? x + (size_t)row * ldx : nullptr;
   float g[8], u[8];
-  if (act_kind == 2) {
+  if (ws || layout == 16) {
+    // column of gate / up value j of this thread's 8 features
+    auto col = [&](int j, bool up) -> int {
+      const int f = i8 + j;
+      if (layout == 16) return 32 * (f >> 4) + (f & 15) + (up ? 16 : 0);
+      if (act_kind == 2) return 2 * f + (up ? 1 : 0);
+      return f + (up ? inter : 0);
+    };
+    int cg[8], cu[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { cg[j] = col(j, false); cu[j] = col(j, true); }
+    if (!ws) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { g[j] = __bfloat162float(xr[cg[j]]); u[j] = __bfloat162float(xr[cu[j]]); }
+    } else {
+      const size_t plane = (size_t)rows * 2 * inter;
+      const float* src = ws + (size_t)row * 2 * inter;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { g[j] = __ldcg(src + cg[j]); u[j] = __ldcg(src + cu[j]); }
+#pragma unroll 2
+      for (int sp = 1; sp < splits; ++sp) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { g[j] += __ldcg(src + sp * plane + cg[j]); u[j] += __ldcg(src + sp * plane + cu[j]); }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (bias) { g[j] += __bfloat162float(bias[cg[j]]); u[j] += __bfloat162float(bias[cu[j]]); }
+        g[j] = __bfloat162float(__float2bfloat16(g[j]));
+        u[j] = __bfloat162float(__float2bfloat16(u[j]));
+      }
+    }
+  } else if (act_kind == 2) {
     const uint4 a = *reinterpret_cast<const uint4*>(xr + 2 * i8);
     const uint4 b = *reinterpret_cast<const uint4*>(xr + 2 * i8 + 8);
     const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
@@ -400,12 +593,14 @@ __global__ void glu_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
 }
 
 void glu_bf16(const void* x, long long ldx, void* out, long long ldo, int rows, int inter,
-              int act_kind, float alpha, float limit, cudaStream_t s) {
+              int act_kind, float alpha, float limit, cudaStream_t s, int layout, const float* partials, int splits,
+              const void* bias) {
   if (rows <= 0) return;
   if (inter % 8) throw std::runtime_error("glu_bf16: intermediate size must be a multiple of 8");
+  if (layout == 16 && inter % 16) throw std::runtime_error("glu_bf16: the blocked layout needs a multiple of 16 features");
   dim3 grid((inter / 8 + 127) / 128, rows);
   launch_pdl(glu_kernel, grid, dim3(128), 0, s, (const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)out, ldo, inter,
-             act_kind, alpha, limit);
+             act_kind, alpha, limit, layout, partials, splits, rows, (const __nv_bfloat16*)bias);
   cuda_check(cudaGetLastError(), "glu_kernel");
 }
 

@@ -22,14 +22,20 @@
 //     rounded up to 16 / 32 / 64 / a multiple of 128 and features' is features rounded up to a
 //     multiple of 128; a call that needs more is rejected with FLLM_NOALLOC_E_TOO_LARGE and a
 //     message naming both numbers (nothing is launched).
-//   * The first call on each device looks up the device address of the scratch array (with
-//     that device current). Make that first call outside any stream capture.
+//   * Per-device set-up happens in fllm_noalloc_init(), or inside the first GEMM call on a device
+//     if init was never called there: it looks up the device address of the scratch array (with
+//     that device current) and sets the kernels' attributes. With CUDA's default lazy module
+//     loading this is also the moment the driver materialises the kernels and the 8 MiB array on
+//     that device, which takes device memory once. So run it at start-up - BEFORE the rest of the
+//     memory is handed to the KV pool, and outside any stream capture; after it, calls take no
+//     device memory at all.
 //   * All calls on a device share the one array and it keeps whatever the previous call left
 //     there. Only the arrival counters must be zero between calls, and every call leaves them at
 //     zero again; the partial sums need no clearing because each call overwrites all it reads.
 //     Two calls that overlap on the GPU (different streams, no ordering between them) would
 //     race on the array - order them on one stream or with events.
-//   * k, features and the leading dimensions must be multiples of 8; x, w, y 16-byte aligned.
+//   * k, features and the leading dimensions must be multiples of 8; x, w and y must be 16-byte
+//     aligned (checked: FLLM_NOALLOC_E_ARGS).
 #pragma once
 #include <stddef.h>
 
@@ -42,7 +48,7 @@ extern "C" {
 enum {
   FLLM_NOALLOC_OK = 0,
   FLLM_NOALLOC_E_ARGS = -1,       // null pointer, non-positive size, bad alignment or multiple
-  FLLM_NOALLOC_E_TOO_LARGE = -2,  // splits * tokens * features * 4 exceeds the scratch array
+  FLLM_NOALLOC_E_TOO_LARGE = -2,  // 64 KiB of counters + splits * padded tokens * padded features * 4 exceeds the array
   FLLM_NOALLOC_E_CUDA = -3,       // a CUDA call failed (symbol lookup, launch)
 };
 
@@ -52,6 +58,10 @@ enum {
 int fllm_linear_bf16_splitk_noalloc(const void* x, long long ldx, const void* w, long long ldw,
                                     const void* bias, void* y, long long ldy, int tokens,
                                     int features, int k, int splits, int* status, void* stream);
+
+// Per-device set-up for the current device (see the contract above). Idempotent; returns
+// FLLM_NOALLOC_OK or FLLM_NOALLOC_E_CUDA.
+int fllm_noalloc_init(void);
 
 // Message of the most recent failure on the calling thread ("" if none).
 const char* fllm_noalloc_last_error(void);

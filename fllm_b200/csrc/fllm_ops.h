@@ -9,11 +9,29 @@
 namespace fllm {
 
 // ---- dense bf16 GEMM (tcgen05) ------------------------------------------------------
+// Optional behaviour of one linear call.
+//   glu            gated activation inside the epilogue (y is then [T][N / 2]): 1 SwiGLU, 2 GeGLU (tanh),
+//                  3 clamped SwiGLU-OAI. The weight rows must interleave gate and up rows: blocks of 16
+//                  (glu_pd = 16: rows 32j..32j+15 gate, 32j+16..32j+31 up of features 16j..16j+15) or pairs
+//                  (glu_pd = 1: row 2i gate, 2i+1 up).
+//   defer_reduce   when the call picks split-K, skip its reduction kernel and leave the fp32 partial sums
+//                  [splits][T][N] (bias NOT added) at workspace + kLinearPartialsOffset; the consumer
+//                  (a norm, rope or activation kernel) adds them. deferred_splits reports the split count
+//                  (0: y is complete).
+constexpr size_t kLinearPartialsOffset = 64 * 1024;
+struct LinearExtras {
+  int glu = 0, glu_pd = 16;
+  float glu_alpha = 1.702f, glu_limit = 7.f;
+  int defer_reduce = 0;
+  int deferred_splits = 0;
+};
 // returns the number of kernels launched (2 when split-K adds its reduction)
 int linear_bf16(const void* x, long long ldx, const void* w, long long ldw, const void* bias,
                  void* y, long long ldy, int T, int N, int K, void* workspace,
-                 size_t workspace_bytes, int* status, int force_splits, cudaStream_t stream);
+                 size_t workspace_bytes, int* status, int force_splits, cudaStream_t stream,
+                 LinearExtras* ex = nullptr);
 size_t gemm_bf16_workspace_bytes(int tokens, int features);
+void gemm_bf16_prepare_device();   // per-device set-up of every tile width (attributes, module load)
 int gemm_bf16_occupancy(int bn);
 
 // Tensor-parallel hooks of the GEMM (see gemm_bf16.cu). Zero-initialise, then fill the half
@@ -33,7 +51,7 @@ struct TpLinearArgs {
 int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, const void* bias,
                    void* y, long long ldy, int T, int N, int K, void* workspace,
                    size_t workspace_bytes, int* status, int force_splits, const TpLinearArgs* tpa,
-                   cudaStream_t stream);
+                   cudaStream_t stream, LinearExtras* ex = nullptr);
 int linear_rs_expected_signals(int T, int N, int rows_per, int dest);
 
 // Sequence-sharded residual update + RMSNorm + all-gather of the normalised rows (comm_tp.cu).
@@ -135,9 +153,20 @@ void rope_qknorm_kvwrite_bf16(void* qkv, long long ld_qkv, const int* positions,
                               const float* inv_freq, const void* q_norm_w, const void* k_norm_w,
                               void* k_cache, void* v_cache, int tokens, int hq, int hkv,
                               int head_dim, int block_size, int rot_dim, int rope_style, float eps,
-                              float attn_factor, cudaStream_t s, int kv_fp8 = 0);   // kv_fp8: caches hold e4m3 bytes
+                              float attn_factor, cudaStream_t s, int kv_fp8 = 0,   // kv_fp8: caches hold e4m3 bytes
+                              // optional: read the heads from fp32 split-K partials [splits][tokens][width]
+                              // (+ bias) instead of qkv, and write the rotated query heads to q_out
+                              const float* partials = nullptr, int splits = 0, const void* bias = nullptr,
+                              void* q_out = nullptr, long long ld_q = 0);
+// residual += bf16(sum of partials + bias); y = rmsnorm(residual) * w: the split-K reduction of the
+// projection before the norm, the residual add and the norm as one kernel
+void rmsnorm_splitk_bf16(void* residual, long long ld_res, const float* partials, int splits, const void* bias,
+                         const void* w, void* y, long long ld_y, int rows, int hidden, float eps, float w_offset,
+                         cudaStream_t s);
+// layout 16: gate / up columns interleaved in blocks of 16; partials: split-K sums instead of x
 void glu_bf16(const void* x, long long ldx, void* out, long long ldo, int rows, int inter,
-              int act_kind, float alpha, float limit, cudaStream_t s);
+              int act_kind, float alpha, float limit, cudaStream_t s, int layout = 0,
+              const float* partials = nullptr, int splits = 0, const void* bias = nullptr);
 void gather_rows_bf16(const void* x, long long ldx, const int* rows, void* out, int n_rows,
                       int hidden, cudaStream_t s);
 
@@ -162,7 +191,7 @@ void attention_prefill_tmem(const void* q, long long ldq, const void* k_cache, c
                             const int* block_tables, int max_blocks, const int* q_starts, const int* kv_lens,
                             void* out, long long ldo, int num_seqs, int max_q_len, int min_q, int hq, int hkv,
                             int head_dim, float scale, int window, const float* sinks, float softcap, int* status,
-                            cudaStream_t s);
+                            cudaStream_t s, int tile_variant = 0);
 size_t attention_tc_workspace_bytes(int tokens, int hq, int head_dim, int max_splits);
 
 // ---- sampling -----------------------------------------------------------------------
@@ -180,6 +209,13 @@ struct SampleRow {
 
 void argmax_rows(const void* logits, int is_fp32, long long ld, int rows, int vocab, int* out_ids,
                  float* out_vals, int id_offset, cudaStream_t s);
+// argmax with every row cut over several CTAs; `scratch` starts with one zeroed counter per row (the kernel
+// re-zeroes them). out_pairs: optional [rows][2] = (value, float(id)).
+size_t argmax_split_scratch_bytes(int rows, int parts);
+void argmax_rows_split(const void* logits, int is_fp32, long long ld, int rows, int vocab, int* out_ids, float* out_vals,
+                       float* out_pairs, int id_offset, void* scratch, size_t scratch_bytes, cudaStream_t s);
+// winner per row among the (value, id) pairs of `ranks` vocabulary slices: pairs [ranks][rows][2]
+void argmax_pairs_select(const float* pairs, int ranks, int rows, int* out_ids, cudaStream_t s);
 void sample_rows(void* logits, int is_fp32, long long ld, int rows, int vocab, const SampleRow* prm,
                  const int* pen_ids, const int* pen_counts, int pen_stride, const int* bias_ids,
                  const float* bias_vals, int bias_stride, const uint32_t* allow_mask, int mask_words,

@@ -54,7 +54,9 @@ struct GemmArgs {
   float* ws;               // split-K partials, [k_splits][tiles][BN][128] fp32 (tile-local, column-major)
   unsigned int* tile_counters;   // one arrival counter per tile; zero between launches
   int fixup;               // split-K: 1 = last-arriving CTA finishes the tile, 0 = dense partials + reduce kernel
-  int tune;                // bit 0: 4-byte pair-exchange stores instead of the staged 16-byte ones; bit 1: no weight prefetch
+  int glu;                 // gated activation folded into the epilogue: 0 none, 1 SwiGLU, 2 GeGLU (tanh), 3 clamped SwiGLU-OAI
+  int glu_pd;              // lane / column distance between a gate row and its up row: 16 (blocks of 16) or 1 (pairs)
+  float glu_alpha, glu_limit;
   int vec16;               // 1: output rows are 16-byte aligned (transposed stores use uint4)
   const __nv_bfloat16* bias;  // per output feature (n when row-major, m when transposed)
   int* status;
@@ -163,7 +165,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
     int pre = 0;                 // leading k-blocks of the first item whose weight tile is already in flight
     if (lane == 0 && !grouped) {
       const int w = blockIdx.x;
-      if (w < total && !(p.tune & 2)) {
+      if (w < total) {
         const int split = p.cluster_red ? w % p.k_splits : w / tiles;
         const int t = p.cluster_red ? w / p.k_splits : w - split * tiles;
         const int n_idx = t / p.m_tiles;
@@ -316,10 +318,44 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
                                ? __bfloat162float(p.bias[grouped ? p.g_tile_expert[n_idx] * p.g_rows + m : m])
                                : 0.f;
       __nv_bfloat16* stg = stage_out + (warp - 2) * (32 * 32);
-      // final values of CH columns of this thread's row -> bias, bf16, memory
+      // gated activation of one (gate, up) pair
+      auto gated = [&](float g, float u) -> float {
+        if (p.glu == 1) return g / (1.f + __expf(-g)) * u;
+        if (p.glu == 2) {
+          const float c = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+          return 0.5f * g * (1.f + tanhf(c)) * u;
+        }
+        const float gg = fminf(g, p.glu_limit);
+        const float uu = fminf(fmaxf(u, -p.glu_limit), p.glu_limit);
+        return gg / (1.f + __expf(-p.glu_alpha * gg)) * (uu + 1.f);
+      };
+      // final values of CH columns of this thread's row -> bias, (activation,) bf16, memory
       auto emit = [&](int c0, const float (&v)[32]) {
         const int n0 = n_base + c0;
-        if (!p.transposed) {
+        if (!p.transposed && p.glu) {
+          // features run along the columns: a 32-column chunk holds 16 (gate, up) pairs of this token
+          if (m < p.M && n0 < p.N) {
+            float o16[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int gi = p.glu_pd == 16 ? i : 2 * i, ui = p.glu_pd == 16 ? i + 16 : 2 * i + 1;
+              float g = v[gi], u = v[ui];
+              if (p.bias) {
+                g += __bfloat162float(p.bias[n0 + gi]);
+                u += __bfloat162float(p.bias[n0 + ui]);
+              }
+              o16[i] = gated(g, u);
+            }
+            uint4 o0, o1;
+            o0.x = pack_bf16x2(o16[0], o16[1]);   o0.y = pack_bf16x2(o16[2], o16[3]);
+            o0.z = pack_bf16x2(o16[4], o16[5]);   o0.w = pack_bf16x2(o16[6], o16[7]);
+            o1.x = pack_bf16x2(o16[8], o16[9]);   o1.y = pack_bf16x2(o16[10], o16[11]);
+            o1.z = pack_bf16x2(o16[12], o16[13]); o1.w = pack_bf16x2(o16[14], o16[15]);
+            __nv_bfloat16* dst = row_ptr(m, 0) + n0 / 2;
+            reinterpret_cast<uint4*>(dst)[0] = o0;
+            reinterpret_cast<uint4*>(dst)[1] = o1;
+          }
+        } else if (!p.transposed) {
           if (m < p.M) {
 #pragma unroll
             for (int c = 0; c < CH; c += 8) {
@@ -346,18 +382,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
               }
             }
           }
-        } else if (p.tune & 1) {
-          const bool odd = lane & 1;
+        } else if (p.glu) {
+          // Features run along the lanes: the lane that holds a gate row and the lane that holds its up
+          // row (distance glu_pd) trade one value per pair of token columns, so that each computes the
+          // activation of ONE of the two columns; the warp's 16 output features of every token are then
+          // staged and leave as 16-byte stores (two lanes per token).
+          const bool hi = (lane & p.glu_pd) != 0;                 // this lane holds up rows
+          const int fl = p.glu_pd == 16 ? (lane & 15) : (lane >> 1);  // output feature within the warp's 16
 #pragma unroll
           for (int c = 0; c < CH; c += 2) {
-            const float own0 = v[c] + bias_m, own1 = v[c + 1] + bias_m;
-            const float recv = __shfl_xor_sync(0xffffffffu, odd ? own0 : own1, 1);
-            const int n = n0 + c + (odd ? 1 : 0);
-            const int mm = odd ? m - 1 : m;
-            const uint32_t packed = odd ? pack_bf16x2(recv, own1) : pack_bf16x2(own0, recv);
-            if (n < p.N && mm < p.M)
-              for (int d = 0; d < ndst; ++d) *reinterpret_cast<uint32_t*>(row_ptr(n, d) + mm) = packed;
+            const float a0 = v[c] + bias_m, a1 = v[c + 1] + bias_m;
+            const float recv = __shfl_xor_sync(0xffffffffu, hi ? a0 : a1, p.glu_pd);
+            const float g = hi ? recv : a0, u = hi ? a1 : recv;
+            stg[(c + (hi ? 1 : 0)) * 16 + fl] = __float2bfloat16(gated(g, u));
           }
+          __syncwarp();
+          const int f0 = 8 * (lane & 1);
+          const int fo = (m_idx * BM + q * 32) / 2 + f0;          // first of 8 output features
+#pragma unroll
+          for (int rnd = 0; rnd < CH / 16; ++rnd) {
+            const int c = (lane >> 1) + 16 * rnd;
+            const int n = n0 + c;
+            if (n < p.N && 2 * fo < p.M) {
+              const uint4 val = *reinterpret_cast<const uint4*>(stg + c * 16 + f0);
+              __nv_bfloat16* dst = row_ptr(n, 0) + fo;
+              if (p.vec16) {
+                *reinterpret_cast<uint4*>(dst) = val;
+              } else {
+                const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) reinterpret_cast<uint32_t*>(dst)[i] = w4[i];
+              }
+            }
+          }
+          __syncwarp();
         } else {
           // Transpose through a per-warp staging tile so that every store is 16 bytes: lanes hold
           // features (rows of D), memory wants 8 consecutive features of one token per store. Four
@@ -374,7 +432,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
             const int n = n0 + c;
             if (n < p.N && mm0 < p.M) {
               const uint4 val = *reinterpret_cast<const uint4*>(stg + c * 32 + f0);
-              for (int d = 0; d < ndst && !(p.tune & 16); ++d) {
+              for (int d = 0; d < ndst; ++d) {
                 __nv_bfloat16* dst = row_ptr(n, d) + mm0;
                 if (p.vec16) {
                   *reinterpret_cast<uint4*>(dst) = val;
@@ -498,7 +556,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
                 }
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
-                  if (sp0 + j < p.k_splits && !(p.tune & 8)) {
+                  if (sp0 + j < p.k_splits) {
 #pragma unroll
                     for (int c = 0; c < 16; ++c) v[h + c] += tv[j][c];
                   }
@@ -509,7 +567,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is reused by the next tile
       }
-      if (rs && emitted && !(p.tune & 4)) {
+      if (rs && emitted) {
         // publish this warp's share of the tile: stores -> system fence -> one flag bump per
         // destination rank that owns token rows of the tile
         // One system-scope fence per warp, not per thread: the warp barrier orders the lanes'
@@ -672,21 +730,35 @@ static bool cluster_splitk_enabled() {
   return v == 1;
 }
 
+// Function attributes are per device: a process that drives several GPUs configures each once.
+template <int BN>
+static void configure_gemm() {
+  using S = GemmSmem<BN>;
+  static bool configured[kMaxDevices] = {};
+  if (!first_call_on_device(configured)) return;
+  cuda_check(cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal),
+             "cudaFuncSetAttribute(gemm_bf16_kernel)");
+  // ask for the largest shared-memory carve-out: the narrow decode tiles rely on two CTAs per SM
+  cuda_check(cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                  cudaSharedmemCarveoutMaxShared),
+             "cudaFuncSetAttribute(carveout)");
+}
+
+// Everything the GEMM does once per device (loading its modules, setting the attributes of every tile
+// width), so that a host can pay for it at start-up instead of inside its first request.
+void gemm_bf16_prepare_device() {
+  configure_gemm<16>();
+  configure_gemm<32>();
+  configure_gemm<64>();
+  configure_gemm<128>();
+  configure_gemm<256>();
+}
+
 template <int BN>
 static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, int grid,
                         cudaStream_t stream) {
   using S = GemmSmem<BN>;
-  static bool configured = false;
-  if (!configured) {
-    cuda_check(cudaFuncSetAttribute(gemm_bf16_kernel<BN>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal),
-               "cudaFuncSetAttribute(gemm_bf16_kernel)");
-    // ask for the largest shared-memory carve-out: the narrow decode tiles rely on two CTAs per SM
-    cuda_check(cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                    cudaSharedmemCarveoutMaxShared),
-               "cudaFuncSetAttribute(carveout)");
-    configured = true;
-  }
+  configure_gemm<BN>();
   if (a.cluster_red)
     launch_pdl_cluster(gemm_bf16_kernel<BN>, dim3(grid), dim3(kGemmThreads), S::kTotal, stream, (unsigned)a.k_splits, ta,
                        tb, a);
@@ -714,6 +786,8 @@ size_t gemm_bf16_workspace_bytes(int tokens, int features) {
   const size_t t = (size_t)((tokens + 15) / 16 * 16), f = (size_t)((features + BM - 1) / BM * BM);
   return 64 * 1024 + (size_t)16 * t * f * sizeof(float);
 }
+
+static int glu_pd_ok(int pd) { return pd == 1 || pd == 16; }
 
 static int pick_bn_tokens(int t) {
   if (t <= 16) return 16;
@@ -752,16 +826,21 @@ int linear_rs_expected_signals(int T, int N, int rows_per, int dest) {
 // y[T, N] = x[T, K] * w[N, K]^T (+ bias[N]);  x row pitch ldx, y row pitch ldy (elements).
 int linear_bf16(const void* x, long long ldx, const void* w, long long ldw, const void* bias,
                  void* y, long long ldy, int T, int N, int K, void* workspace,
-                 size_t workspace_bytes, int* status, int force_splits, cudaStream_t stream) {
+                 size_t workspace_bytes, int* status, int force_splits, cudaStream_t stream, LinearExtras* ex) {
   return linear_bf16_tp(x, ldx, w, ldw, bias, y, ldy, T, N, K, workspace, workspace_bytes, status,
-                        force_splits, nullptr, stream);
+                        force_splits, nullptr, stream, ex);
 }
 
 int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, const void* bias,
                    void* y, long long ldy, int T, int N, int K, void* workspace,
                    size_t workspace_bytes, int* status, int force_splits, const TpLinearArgs* tpa,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, LinearExtras* ex) {
+  if (ex) ex->deferred_splits = 0;
   if (T <= 0 || N <= 0) return 0;
+  const int glu = ex ? ex->glu : 0;
+  const bool defer = ex && ex->defer_reduce;
+  if (glu && ((N & 31) || (tpa && tpa->rs_bufs[0]) || (glu_pd_ok(ex->glu_pd) == 0)))
+    throw std::runtime_error("linear_bf16: a gated epilogue needs N % 32 == 0, a local output and a pair distance of 1 or 16");
   if ((K & 7) || (N & 7) || (ldx & 7) || (ldw & 7) || (ldy & 1))
     throw std::runtime_error("linear_bf16: K, N and the row pitches must be multiples of 8");
   const int sms = sm_count();
@@ -821,23 +900,21 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
   if (splits > 1 && (!workspace || workspace_bytes <= kCounterBytes || (size_t)tiles * 4 > kCounterBytes || bn > 128))
     splits = 1;
   while (splits > 1 && kCounterBytes + (size_t)splits * tiles * BM * bn * sizeof(float) > workspace_bytes) --splits;
+  // A gated epilogue needs complete sums: no split-K, unless the caller takes the fp32 partials and
+  // applies the activation while it adds them.
+  if (glu && splits > 1 && !defer) splits = 1;
   // Broadcast destination + split-K: the GEMM keeps its fast local split path and the reduction
   // kernel does the pushing. Scatter destination + split-K: the last-arriving CTA finishes the tile.
   const bool push_reduce = rs && tpa->rs_bcast && splits > 1;
   a.fixup = (rs && !push_reduce) ? 1 : 0;
   if (a.fixup && force_splits <= 0) splits = min(splits, max(1, min(4, a.k_blocks / 8)));   // the in-kernel fixup is serial per tile: keep it short
-  {
-    static int tune = -1;
-    if (tune < 0) { const char* e = getenv("FLLM_GEMM_TUNE"); tune = e ? atoi(e) : 0; }
-    a.tune = tune;
-  }
   if (!a.fixup)
     while (splits > 1 && kCounterBytes + (size_t)splits * a.M * a.N * sizeof(float) > workspace_bytes) --splits;
   // On-chip reduction: the splits of a tile run as one thread-block cluster (at most 8 CTAs, one unit
   // per CTA) and add their tiles through distributed shared memory: no partial sums in global memory
   // and no second kernel. Decode orientation with a local output only.
   const int slots_now = sms * (bn <= 64 ? 2 : 1);
-  bool cluster = cluster_splitk_enabled() && swap && !rs && splits > 1 && bn <= 128 && (N % 4) == 0 &&
+  bool cluster = cluster_splitk_enabled() && !defer && !glu && swap && !rs && splits > 1 && bn <= 128 && (N % 4) == 0 &&
                  (ldy % 4) == 0 && (reinterpret_cast<uintptr_t>(y) % 8) == 0;
   if (cluster && splits > 8) splits = 8;
   a.kb_per_split = (a.k_blocks + splits - 1) / splits;
@@ -849,6 +926,11 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
   // 16-byte stores of the transposed epilogue need 16-byte aligned token rows
   a.vec16 = rs ? ((a.rs_ld & 7) == 0)
                : ((ldy & 7) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0);
+  if (glu && a.k_splits == 1) {
+    a.glu = glu; a.glu_pd = ex->glu_pd; a.glu_alpha = ex->glu_alpha; a.glu_limit = ex->glu_limit;
+    if (!swap && ((ldy & 7) || (reinterpret_cast<uintptr_t>(y) & 15)))
+      throw std::runtime_error("linear_bf16: the gated epilogue stores 16 bytes at a time; y must be 16-byte aligned");
+  }
 
   const bool push = push_reduce && a.k_splits > 1;
   if (push) {                      // the GEMM itself writes local partials only
@@ -879,6 +961,10 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
     return 2;
   }
   if (a.cluster_red) return 1;
+  if (a.k_splits > 1 && !a.fixup && defer) {
+    ex->deferred_splits = a.k_splits;      // the consumer adds the dense [split][token][feature] partials (+ bias)
+    return 1;
+  }
   if (a.k_splits > 1 && !a.fixup) {
     // dense [token][feature] partials in both orientations
     const size_t n = (size_t)T * N;

@@ -255,11 +255,10 @@ void quant_fp8_1x128(const void* x, long long ldx, void* xq, float* sx, int toke
 template <int BN>
 static void launch_fp8(const CUtensorMap& ta, const CUtensorMap& tb, const Fp8GemmArgs& a, int grid, cudaStream_t s) {
   using S = Fp8Smem<BN>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxDevices] = {};
+  if (first_call_on_device(configured)) {
     cuda_check(cudaFuncSetAttribute(gemm_fp8_block_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal),
                "cudaFuncSetAttribute(gemm_fp8_block_kernel)");
-    configured = true;
   }
   gemm_fp8_block_kernel<BN><<<grid, kF8Threads, S::kTotal, s>>>(ta, tb, a);
   cuda_check(cudaGetLastError(), "gemm_fp8_block_kernel launch");

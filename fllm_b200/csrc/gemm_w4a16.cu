@@ -429,13 +429,12 @@ void w4_dequant_bf16(const void* codes, const void* scales, int fmt, float alpha
 template <int BN>
 static void launch_w4(const CUtensorMap& tr, const CUtensorMap& tb, const W4Args& a, cudaStream_t s) {
   using S = W4Smem<BN>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxDevices] = {};
+  if (first_call_on_device(configured)) {
     cuda_check(cudaFuncSetAttribute(gemm_w4a16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal),
                "cudaFuncSetAttribute(gemm_w4a16_kernel)");
     cuda_check(cudaFuncSetAttribute(gemm_w4a16_kernel<BN>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                     cudaSharedmemCarveoutMaxShared), "cudaFuncSetAttribute(carveout)");
-    configured = true;
   }
   launch_pdl(gemm_w4a16_kernel<BN>, dim3(a.m_tiles, a.grid_y), dim3(kW4Threads), S::kTotal, s, tr, tb, a);
 }

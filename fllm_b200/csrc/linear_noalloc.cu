@@ -58,6 +58,20 @@ FLLM_EXPORT size_t fllm_noalloc_scratch_bytes(void) { return FLLM_NOALLOC_SCRATC
 
 FLLM_EXPORT const char* fllm_noalloc_last_error(void) { return g_error; }
 
+FLLM_EXPORT int fllm_noalloc_init(void) {
+  g_error[0] = 0;
+  void* scratch = nullptr;
+  const int rc = scratch_for_current_device(&scratch);
+  if (rc != FLLM_NOALLOC_OK) return rc;
+  try {
+    fllm::gemm_bf16_prepare_device();
+  } catch (const std::exception& e) {
+    snprintf(g_error, sizeof(g_error), "%s", e.what());
+    return FLLM_NOALLOC_E_CUDA;
+  }
+  return FLLM_NOALLOC_OK;
+}
+
 FLLM_EXPORT int fllm_linear_bf16_splitk_noalloc(const void* x, long long ldx, const void* w, long long ldw,
                                                 const void* bias, void* y, long long ldy, int tokens,
                                                 int features, int k, int splits, int* status, void* stream) {
@@ -67,6 +81,9 @@ FLLM_EXPORT int fllm_linear_bf16_splitk_noalloc(const void* x, long long ldx, co
     return fail(FLLM_NOALLOC_E_ARGS, "tokens, features, k and splits must be positive");
   if ((k & 7) || (features & 7) || (ldx & 7) || (ldw & 7) || (ldy & 7))
     return fail(FLLM_NOALLOC_E_ARGS, "k, features and the leading dimensions must be multiples of 8");
+  if ((reinterpret_cast<unsigned long long>(x) | reinterpret_cast<unsigned long long>(w) |
+       reinterpret_cast<unsigned long long>(y)) & 15ull)
+    return fail(FLLM_NOALLOC_E_ARGS, "x, w and y must be 16-byte aligned");
   if (splits > 16) return fail(FLLM_NOALLOC_E_ARGS, "splits must be at most 16 (got %lld)", splits);
   // partial sums are kept per tile: tokens round up to the tile width, features to 128; the first
   // 64 KiB of the array hold the per-tile arrival counters

@@ -155,6 +155,119 @@ void argmax_rows(const void* logits, int is_fp32, long long ld, int rows, int vo
   cuda_check(cudaGetLastError(), "argmax_rows_kernel");
 }
 
+// The same reduction with every row cut over `parts` CTAs (a decode batch has far fewer rows than the GPU
+// has SMs, and a 150 k-entry row is 300 KB): each CTA reduces a slice, parks (value, index) and bumps the
+// row's counter; the CTA that arrives last combines the slices and re-zeroes the counter. `better` makes the
+// result independent of the arrival order. out_pairs (optional) receives (value, float(id)) per row, the
+// message a vocabulary-parallel head exchanges.
+template <typename T>
+__global__ void __launch_bounds__(kSampThreads)
+argmax_rows_split_kernel(const T* __restrict__ logits, long long ld, int vocab, int parts, int* __restrict__ out_ids,
+                         float* __restrict__ out_vals, float* __restrict__ out_pairs, int id_offset,
+                         float2* __restrict__ part, unsigned int* __restrict__ counters) {
+  __shared__ ArgMax sm[32];
+  __shared__ int is_last;
+  const int r = blockIdx.x, pi = blockIdx.y;
+  const T* row = logits + (size_t)r * ld;
+  const int chunk = (((vocab + parts - 1) / parts) + 7) & ~7;
+  const int lo = min(vocab, pi * chunk), hi = min(vocab, lo + chunk);
+  ArgMax a{-INFINITY, 0x7fffffff};
+  int i0 = lo;
+  if constexpr (sizeof(T) == 2) {
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+      const int v0 = lo >> 3, v1 = hi >> 3;
+      const uint4* rv = reinterpret_cast<const uint4*>(row);
+      for (int v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+        const uint4 u = rv[v];
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        float best = -INFINITY;
+        int bi = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(w[j]);
+          if (f.x > best) { best = f.x; bi = 2 * j; }
+          if (f.y > best) { best = f.y; bi = 2 * j + 1; }
+        }
+        a = better(a, ArgMax{best, 8 * v + bi});
+      }
+      i0 = max(lo, v1 << 3);
+    }
+  }
+  for (int i = i0 + threadIdx.x; i < hi; i += blockDim.x) a = better(a, ArgMax{ld_logit(row, i), i});
+  a = block_argmax(a, sm);
+  if (threadIdx.x == 0) {
+    part[(size_t)r * parts + pi] = make_float2(a.v, __int_as_float(a.i));
+    __threadfence();
+    const unsigned int old = atomicAdd(counters + r, 1u);
+    is_last = old == (unsigned int)(parts - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (threadIdx.x < 32) {
+    ArgMax b{-INFINITY, 0x7fffffff};
+    for (int j = threadIdx.x; j < parts; j += 32) {
+      const float2 pv = __ldcg(part + (size_t)r * parts + j);
+      b = better(b, ArgMax{pv.x, __float_as_int(pv.y)});
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ArgMax c;
+      c.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+      c.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+      b = better(b, c);
+    }
+    if (threadIdx.x == 0) {
+      out_ids[r] = b.i + id_offset;
+      if (out_vals) out_vals[r] = b.v;
+      if (out_pairs) { out_pairs[2 * r] = b.v; out_pairs[2 * r + 1] = (float)(b.i + id_offset); }
+      counters[r] = 0;
+    }
+  }
+}
+
+size_t argmax_split_scratch_bytes(int rows, int parts) { return (size_t)rows * 4 + (size_t)rows * parts * 8 + 16; }
+
+void argmax_rows_split(const void* logits, int is_fp32, long long ld, int rows, int vocab, int* out_ids, float* out_vals,
+                       float* out_pairs, int id_offset, void* scratch, size_t scratch_bytes, cudaStream_t s) {
+  if (rows <= 0) return;
+  int parts = max(1, min(32, (2 * sm_count() + rows - 1) / rows));
+  parts = min(parts, max(1, vocab / 2048));
+  if (argmax_split_scratch_bytes(rows, parts) > scratch_bytes)
+    throw std::runtime_error("argmax_rows_split: scratch too small");
+  auto* counters = reinterpret_cast<unsigned int*>(scratch);                       // zero between launches
+  auto* part = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(scratch) + (((size_t)rows * 4 + 15) & ~(size_t)15));
+  dim3 grid(rows, parts);
+  if (is_fp32)
+    argmax_rows_split_kernel<float><<<grid, kSampThreads, 0, s>>>((const float*)logits, ld, vocab, parts, out_ids, out_vals,
+                                                                 out_pairs, id_offset, part, counters);
+  else
+    argmax_rows_split_kernel<__nv_bfloat16><<<grid, kSampThreads, 0, s>>>((const __nv_bfloat16*)logits, ld, vocab, parts,
+                                                                         out_ids, out_vals, out_pairs, id_offset, part,
+                                                                         counters);
+  cuda_check(cudaGetLastError(), "argmax_rows_split_kernel");
+}
+
+// Vocabulary-parallel greedy token: pairs[rank][row] = (best local value, its global id as a float) gathered from
+// every rank; the winner per row is the highest value, the lowest rank (= lowest id) among equals.
+__global__ void argmax_pairs_select_kernel(const float2* __restrict__ pairs, int ranks, int rows, int* __restrict__ out_ids) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float best = -INFINITY;
+  int id = 0;
+  for (int k = 0; k < ranks; ++k) {
+    const float2 pv = pairs[(size_t)k * rows + r];
+    if (pv.x > best || k == 0) { best = pv.x; id = (int)pv.y; }
+  }
+  out_ids[r] = id;
+}
+
+void argmax_pairs_select(const float* pairs, int ranks, int rows, int* out_ids, cudaStream_t s) {
+  if (rows <= 0) return;
+  argmax_pairs_select_kernel<<<(rows + 127) / 128, 128, 0, s>>>(reinterpret_cast<const float2*>(pairs), ranks, rows, out_ids);
+  cuda_check(cudaGetLastError(), "argmax_pairs_select_kernel");
+}
+
 // ---------------------------------------------------------------------------- full sampler
 template <typename T>
 __global__ void __launch_bounds__(kSampThreads)

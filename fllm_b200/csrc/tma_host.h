@@ -110,6 +110,19 @@ inline void launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, 
   cuda_check(cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...), "cudaLaunchKernelEx(cluster)");
 }
 
+// True the first time it is called on the current device for a given flag array: function attributes
+// (dynamic shared-memory limits) are per device, so a process that drives several GPUs sets them on each.
+// Use as  `static bool done[kMaxDevices] = {}; if (first_call_on_device(done)) { cudaFuncSetAttribute(...); }`
+constexpr int kMaxDevices = 64;
+inline bool first_call_on_device(bool (&done)[kMaxDevices]) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= kMaxDevices - 1;
+  if (done[dev]) return false;
+  done[dev] = true;
+  return true;
+}
+
 inline int sm_count() {
   static int n[16] = {0};
   int dev = 0;

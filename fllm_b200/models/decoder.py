@@ -98,6 +98,26 @@ class Decoder:
         self._reduced = False
         self._dense_weights = all(isinstance(getattr(lw, n, None), torch.Tensor) for lw in self.w.layers
                                   for n in ("wqkv", "wo", "w_gate_up", "w_down") if getattr(lw, n, None) is not None)
+        # split-K reductions of the projections are left to the kernel that consumes them (norm / rope)
+        self._defer = hasattr(ops, "k") and dev.type == "cuda"
+        if self._defer:
+            self._block_gate_up()
+
+    def _block_gate_up(self) -> None:
+        """Re-order the rows of every dense gate|up matrix into blocks of 16 gate rows followed by the 16 up
+        rows of the same features (once per weight object, in place), so that the GEMM epilogue holds a
+        feature's gate and up values in one warp and applies the activation itself."""
+        if self.cfg.is_moe or self.cfg.act not in ("swiglu", "geglu"):
+            return
+        for lw in self.w.layers:
+            w = lw.w_gate_up
+            if not isinstance(w, torch.Tensor) or getattr(lw, "glu_layout", 0) or (w.shape[0] // 2) % 16:
+                continue
+            I, K = w.shape[0] // 2, w.shape[1]
+            blocked = torch.stack([w[:I].view(I // 16, 16, K), w[I:].view(I // 16, 16, K)], 1).reshape(2 * I, K)
+            w.copy_(blocked)
+            del blocked
+            lw.glu_layout = 16
 
     # ------------------------------------------------------------------ pieces
     def _reduce(self, x: torch.Tensor) -> torch.Tensor:
@@ -110,17 +130,22 @@ class Decoder:
 
     def _attention_block(self, li: int, lw, h: torch.Tensor, b: StepBatch) -> torch.Tensor:
         cfg, sp, ops = self.cfg, self.spec, self.ops
-        qkv = ops.linear(h, lw.wqkv, lw.bqkv)
+        qkv = ops.linear(h, lw.wqkv, lw.bqkv, defer=self._defer)
         local = li - self.layer_range.start
         kc, vc = self.kv.k(local), self.kv.v(local)
-        ops.rope_kv_write(qkv, b.positions, b.slots, self.inv_freq, lw.q_norm, lw.k_norm, kc, vc,
-                          sp.hq_local, sp.hkv_local, cfg.head_dim, cfg.rot_dim, self.rope_style,
-                          cfg.rms_eps, self.attn_factor)
-        q = qkv[:, : sp.hq_local * cfg.head_dim]
+        q = ops.rope_kv_write(qkv, b.positions, b.slots, self.inv_freq, lw.q_norm, lw.k_norm, kc, vc,
+                              sp.hq_local, sp.hkv_local, cfg.head_dim, cfg.rot_dim, self.rope_style,
+                              cfg.rms_eps, self.attn_factor)
         a = ops.attention(q, kc, vc, b.block_tables, b.row_seq, b.positions, sp.hq_local, sp.hkv_local,
                           cfg.head_dim, self.scale, cfg.layer_window(li), lw.sinks, cfg.attn_softcap,
                           meta=b)
-        return ops.linear(a, lw.wo, lw.bo)
+        return ops.linear(a, lw.wo, lw.bo, defer=self._defer_out(lw.post_attn_norm))
+
+    def _defer_out(self, post_norm) -> bool:
+        """May a row-parallel projection hand its split-K partials to the next norm? Only when nothing
+        sits between the two: no all-reduce, no output norm, no pipeline hand-over."""
+        return (self._defer and post_norm is None and (self.tp is None or self.tp.size == 1)
+                and self.first_stage and self.last_stage)
 
     def _ffn_block(self, lw, h: torch.Tensor) -> torch.Tensor:
         cfg, ops = self.cfg, self.ops
@@ -130,9 +155,9 @@ class Decoder:
                 self._reduced = True                 # rows come back complete: nothing left to reduce
                 return moe_ffn_alltoall(self, lw, h)
             return moe_ffn(self, lw, h)
-        gu = ops.linear(h, lw.w_gate_up)
-        act = ops.glu(gu, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit)
-        return ops.linear(act, lw.w_down)
+        act = ops.linear_glu(h, lw.w_gate_up, None, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit,
+                             getattr(lw, "glu_layout", 0))
+        return ops.linear(act, lw.w_down, defer=self._defer_out(lw.post_ffn_norm))
 
     # ------------------------------------------------------------------ forward
     def forward_hidden(self, b: StepBatch, hidden_in: Optional[torch.Tensor] = None,
@@ -197,23 +222,25 @@ class Decoder:
         partials = False
         for li, lw in zip(self.layer_range, self.w.layers):
             tp.norm(x, T, partials, lw.attn_norm, cfg.rms_eps, cfg.norm_weight_offset, bc)
-            qkv = col_linear(lw.wqkv, lw.bqkv)
+            qkv = ops.linear(h_all, lw.wqkv, lw.bqkv, defer=True) if bc else col_linear(lw.wqkv, lw.bqkv)
             local = li - self.layer_range.start
             kc, vc = self.kv.k(local), self.kv.v(local)
-            ops.rope_kv_write(qkv, b.positions, b.slots, self.inv_freq, lw.q_norm, lw.k_norm, kc, vc,
-                              sp.hq_local, sp.hkv_local, cfg.head_dim, cfg.rot_dim, self.rope_style,
-                              cfg.rms_eps, self.attn_factor)
-            q = qkv[:, : sp.hq_local * cfg.head_dim]
+            q = ops.rope_kv_write(qkv, b.positions, b.slots, self.inv_freq, lw.q_norm, lw.k_norm, kc, vc,
+                                  sp.hq_local, sp.hkv_local, cfg.head_dim, cfg.rot_dim, self.rope_style,
+                                  cfg.rms_eps, self.attn_factor)
             a = ops.attention(q, kc, vc, b.block_tables, b.row_seq, b.positions, sp.hq_local, sp.hkv_local,
                               cfg.head_dim, self.scale, cfg.layer_window(li), lw.sinks, cfg.attn_softcap, meta=b)
             tp.linear_rs(a, lw.wo, lw.bo, bc)
             tp.norm(x, T, True, lw.ffn_norm, cfg.rms_eps, cfg.norm_weight_offset, bc)
-            gu = col_linear(lw.w_gate_up)
-            act = ops.glu(gu, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit)
+            layout = getattr(lw, "glu_layout", 0)
+            if bc:
+                act = ops.linear_glu(h_all, lw.w_gate_up, None, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit, layout)
+            else:
+                act = ops.glu(col_linear(lw.w_gate_up), self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit, layout)
             tp.linear_rs(act, lw.w_down, None, bc)
             partials = True
             if hasattr(ops, "launches"):
-                ops.launches += 4 if bc else 6
+                ops.launches += 4 if bc else 6       # the kernels launched through `tp` (upper bound)
         tp.norm(x, T, partials, self.w.final_norm, cfg.rms_eps, cfg.norm_weight_offset, bc)
         if bc:
             hs = h_all if (b.all_decode and b.logit_rows.numel() == T) else ops.gather_rows(h_all, b.logit_rows)
@@ -264,14 +291,12 @@ class Decoder:
         if tp is None or tp.size == 1:
             return self.ops.argmax(logits_local[:, : self.w.vocab_local] if logits_local.shape[1] != self.w.vocab_local else logits_local)
         view = logits_local[:, : max(self.w.vocab_local, 1)]
-        ids, vals = self.ops.argmax(view, id_offset=self.w.vocab_start, want_vals=True)
+        _, pair = self.ops.argmax(view, id_offset=self.w.vocab_start, want_pairs=True)     # [R, 2] (value, id)
         if self.w.vocab_local == 0:
-            vals = torch.full_like(vals, float("-inf"))
-        pair = torch.stack([vals, ids.float()], 1).contiguous()         # ids < 2^24 fit fp32 exactly
-        allp = tp.all_gather(pair)                                       # [tp, R, 2]
-        best = allp[:, :, 0].argmax(0)
+            pair[:, 0] = float("-inf")
+        allp = tp.all_gather(pair)                                       # [tp, R, 2]; ids < 2^24 fit fp32 exactly
         # ties between ranks resolve to the lowest rank = lowest token id, like a global argmax
-        return allp[best, torch.arange(pair.shape[0], device=pair.device), 1].int()
+        return self.ops.argmax_pairs_select(allp)
 
     def full_logits(self, logits_local: torch.Tensor) -> torch.Tensor:
         tp = self.tp

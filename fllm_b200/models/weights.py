@@ -44,6 +44,9 @@ class LayerWeights:
     exp_down_b: Optional[torch.Tensor] = None       # [E_local, H]
     # packed formats keep their payload here (format name -> tensors)
     packed: Dict[str, object] = field(default_factory=dict)
+    # row order of w_gate_up: 0 = gate half then up half; 16 = blocks of 16 gate rows followed by the 16 up
+    # rows of the same features (set by the decoder on a GPU, where the GEMM epilogue applies the activation)
+    glu_layout: int = 0
 
 
 @dataclass

@@ -14,6 +14,21 @@ import torch
 from ._lib import load_cuda
 
 
+class Deferred:
+    """Handle to a projection whose split-K reduction was left to its consumer: the fp32 partial sums
+    [splits][rows][cols] sit in the operator workspace (bias not added) until the next ``linear`` call.
+    ``rmsnorm``, ``rope_kv_write`` and the gated activation accept it in place of a tensor and add the
+    partials while they read them, which removes the reduction kernel from the chain."""
+    __slots__ = ("splits", "rows", "cols", "bias")
+
+    def __init__(self, splits: int, rows: int, cols: int, bias):
+        self.splits, self.rows, self.cols, self.bias = splits, rows, cols, bias
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+
 class NativeOps:
     name = "sm100a"
 
@@ -27,6 +42,7 @@ class NativeOps:
         self.attn_ws = None
         self.launches = 0            # kernels launched through this object (graph capture included)
         self._scratch = None
+        self._argmax_ws = None
 
     def scratch_bf16(self, numel: int) -> torch.Tensor:
         """Grow-only bf16 scratch (expanded weights of packed formats during prefill). Stream-ordered
@@ -36,12 +52,41 @@ class NativeOps:
         return self._scratch[:numel]
 
     # ---------------------------------------------------------------- dense
-    def linear(self, x, w, bias=None, out=None, force_splits: int = 0):
+    def linear(self, x, w, bias=None, out=None, force_splits: int = 0, defer: bool = False):
+        """y = x @ w^T (+ bias). With ``defer`` the call may return a :class:`Deferred` instead of a tensor
+        (when the kernel picked split-K): pass it on to ``rmsnorm`` / ``rope_kv_write``."""
         if not isinstance(w, torch.Tensor):          # packed weight (FP8 block, FP4, ...): it knows its kernel
             return w.apply(self, x, bias, out)
         if out is None:
             out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
-        self.launches += self.k.linear(x, w, bias, out, self.workspace, self.status, force_splits)
+        if not defer:
+            self.launches += self.k.linear(x, w, bias, out, self.workspace, self.status, force_splits)
+            return out
+        n, splits = self.k.linear_ex(x, w, bias, out, self.workspace, self.status, force_splits, 0, 16, 0.0, 0.0, True)
+        self.launches += n
+        return Deferred(splits, x.shape[0], w.shape[0], bias) if splits > 1 else out
+
+    def materialize(self, y):
+        """Tensor value of a projection result (adds a Deferred's partials with the stand-alone path)."""
+        if not isinstance(y, Deferred):
+            return y
+        raise RuntimeError("a deferred projection can only be consumed by rmsnorm, rope_kv_write or a gated activation")
+
+    def linear_glu(self, x, w, bias, act_kind=0, alpha=1.702, limit=7.0, layout=0, force_splits: int = 0):
+        """act(x @ w^T + bias) for a fused gate|up weight, [T, N/2]. With a row layout the GEMM epilogue can
+        pair up (blocks of 16, or the pairs of the clamped SwiGLU-OAI kind) the activation runs inside the GEMM;
+        when the GEMM needs split-K the activation kernel adds the partial sums instead."""
+        T, N = x.shape[0], w.shape[0]
+        pd = 16 if layout == 16 else (1 if act_kind == 2 else 0)
+        if not isinstance(w, torch.Tensor) or pd == 0 or N % 32:
+            return self.glu(self.linear(x, w, bias), act_kind, alpha, limit, layout)
+        out = torch.empty(T, N // 2, dtype=x.dtype, device=x.device)
+        n, splits = self.k.linear_ex(x, w, bias, out, self.workspace, self.status, force_splits, act_kind + 1, pd,
+                                     float(alpha), float(limit), True)
+        self.launches += n
+        if splits > 1:
+            self.k.glu_ex(None, out, act_kind, float(alpha), float(limit), layout, self.workspace, splits, bias)
+            self.launches += 1
         return out
 
     def embed(self, ids, table, scale=1.0):
@@ -52,20 +97,33 @@ class NativeOps:
 
     def rmsnorm(self, residual, delta, w, eps, w_offset=0.0):
         y = torch.empty_like(residual)
-        self.k.rmsnorm(residual, delta, w, y, float(eps), float(w_offset))
+        if isinstance(delta, Deferred):
+            self.k.rmsnorm_splitk(residual, self.workspace, delta.splits, delta.bias, w, y, float(eps), float(w_offset))
+        else:
+            self.k.rmsnorm(residual, delta, w, y, float(eps), float(w_offset))
         self.launches += 1
         return y
 
     def rope_kv_write(self, qkv, positions, slots, inv_freq, q_norm_w, k_norm_w, k_cache, v_cache,
                       hq, hkv, head_dim, rot_dim, rope_style, eps, attn_factor=1.0):
+        """QK-norm + RoPE + paged KV write; returns the rotated queries [T, hq * head_dim]."""
+        self.launches += 1
+        if isinstance(qkv, Deferred):
+            q = torch.empty(qkv.rows, hq * head_dim, dtype=torch.bfloat16, device=self.device)
+            self.k.rope_kv_write_splitk(self.workspace, qkv.splits, qkv.bias, q, positions, slots, inv_freq, q_norm_w,
+                                        k_norm_w, k_cache, v_cache, hq, hkv, head_dim, rot_dim, rope_style,
+                                        float(eps), float(attn_factor))
+            return q
         self.k.rope_kv_write(qkv, positions, slots, inv_freq, q_norm_w, k_norm_w, k_cache, v_cache,
                              hq, hkv, head_dim, rot_dim, rope_style, float(eps), float(attn_factor))
-        self.launches += 1
-        return qkv
+        return qkv[:, : hq * head_dim]
 
-    def glu(self, x, act_kind=0, alpha=1.702, limit=7.0):
+    def glu(self, x, act_kind=0, alpha=1.702, limit=7.0, layout=0):
         out = torch.empty(x.shape[0], x.shape[1] // 2, dtype=x.dtype, device=x.device)
-        self.k.glu(x, out, act_kind, float(alpha), float(limit))
+        if layout:
+            self.k.glu_ex(x, out, act_kind, float(alpha), float(limit), layout, None, 0, None)
+        else:
+            self.k.glu(x, out, act_kind, float(alpha), float(limit))
         self.launches += 1
         return out
 
@@ -95,12 +153,32 @@ class NativeOps:
         return out
 
     # ---------------------------------------------------------------- sampling
-    def argmax(self, logits, id_offset=0, want_vals=False):
-        ids = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-        vals = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device) if want_vals else None
-        self.k.argmax(logits, ids, vals, id_offset)
+    def argmax(self, logits, id_offset=0, want_vals=False, want_pairs=False):
+        """Greedy id per row (lowest index among equal maxima). want_pairs: also [rows, 2] fp32
+        (value, float(id)), the message a vocabulary-parallel head exchanges."""
+        rows = logits.shape[0]
+        ids = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        vals = torch.empty(rows, dtype=torch.float32, device=logits.device) if want_vals else None
+        pairs = torch.empty(rows, 2, dtype=torch.float32, device=logits.device) if want_pairs else None
+        if rows <= 1024:
+            if self._argmax_ws is None:     # [row counters (zero between launches) | per-slice (value, index)]
+                self._argmax_ws = torch.zeros(1024 * 4 + 1024 * 32 * 8 + 64, dtype=torch.uint8, device=self.device)
+            self.k.argmax_split(logits, ids, vals, pairs, id_offset, self._argmax_ws)
+        else:
+            self.k.argmax(logits, ids, vals, id_offset)
+            if want_pairs:
+                pairs = torch.stack([vals if vals is not None else logits.float().max(-1).values, ids.float()], 1).contiguous()
         self.launches += 1
+        if want_pairs:
+            return ids, pairs
         return (ids, vals) if want_vals else ids
+
+    def argmax_pairs_select(self, pairs):
+        """[ranks, rows, 2] gathered (value, id) pairs -> winning id per row."""
+        out = torch.empty(pairs.shape[1], dtype=torch.int32, device=pairs.device)
+        self.k.argmax_pairs_select(pairs.contiguous(), out)
+        self.launches += 1
+        return out
 
     def sample(self, logits, params, pen_ids=None, pen_counts=None, bias_ids=None, bias_vals=None,
                allow_mask=None, want_logprobs=False):

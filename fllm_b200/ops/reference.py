@@ -15,7 +15,7 @@ class RefOps:
     name = "reference"
 
     # ---------------------------------------------------------------- dense
-    def linear(self, x, w, bias=None, out=None):
+    def linear(self, x, w, bias=None, out=None, force_splits: int = 0, defer: bool = False):
         if not isinstance(w, torch.Tensor):
             return w.apply(self, x, bias, out)
         y = x.float() @ w.float().t()
@@ -26,6 +26,9 @@ class RefOps:
             out.copy_(y)
             return out
         return y
+
+    def linear_glu(self, x, w, bias, act_kind=0, alpha=1.702, limit=7.0, layout=0, force_splits: int = 0):
+        return self.glu(self.linear(x, w, bias), act_kind, alpha, limit, layout)
 
     def embed(self, ids, table, scale=1.0):
         x = table[ids.long()]
@@ -78,10 +81,22 @@ class RefOps:
             blk, off = sl // bs, sl % bs
             k_cache[blk, :, off] = k[ok].to(k_cache.dtype)
             v_cache[blk, :, off] = v[ok].to(v_cache.dtype)
-        return qkv
+        return qkv[:, : hq * head_dim]
 
-    def glu(self, x, act_kind=0, alpha=1.702, limit=7.0):
+    def glu(self, x, act_kind=0, alpha=1.702, limit=7.0, layout=0):
+        """layout 16: columns come in blocks of 16 gate values followed by the 16 up values of the same
+        features (the order the GEMM's gated epilogue pairs up)."""
         xf = x.float()
+        if layout == 16:
+            blk = xf.view(x.shape[0], -1, 2, 16)
+            g, u = blk[:, :, 0].reshape(x.shape[0], -1), blk[:, :, 1].reshape(x.shape[0], -1)
+            if act_kind == 2:
+                g = g.clamp(max=limit)
+                u = u.clamp(min=-limit, max=limit)
+                y = g * torch.sigmoid(alpha * g) * (u + 1)
+            else:
+                y = (F.silu(g) if act_kind == 0 else F.gelu(g, approximate="tanh")) * u
+            return y.to(x.dtype)
         if act_kind == 2:
             g, u = xf[:, 0::2], xf[:, 1::2]
             g = g.clamp(max=limit)
@@ -126,10 +141,17 @@ class RefOps:
         return out
 
     # ---------------------------------------------------------------- sampling
-    def argmax(self, logits, id_offset=0, want_vals=False):
+    def argmax(self, logits, id_offset=0, want_vals=False, want_pairs=False):
         vals, ids = logits.float().max(-1)
         ids = (ids + id_offset).int()
+        if want_pairs:
+            return ids, torch.stack([vals, ids.float()], 1).contiguous()
         return (ids, vals) if want_vals else ids
+
+    def argmax_pairs_select(self, pairs):
+        """[ranks, rows, 2] (value, id) pairs -> id of the highest value per row, lowest rank among equals."""
+        best = pairs[:, :, 0].argmax(0)
+        return pairs[best, torch.arange(pairs.shape[1], device=pairs.device), 1].int()
 
 
 def philox_uniform(seed: int, draw: int, idx: int) -> float:

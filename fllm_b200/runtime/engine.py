@@ -352,6 +352,9 @@ class LLMEngine:
             raise ValueError("draft and target must share the vocabulary")
         self.proposer = DraftModelProposer(self, draft_cfg, k or self.cfg.draft_tokens, seed, weights)
         self.adaptive = AdaptiveDraft(k or self.cfg.draft_tokens)
+        # the proposer marks how much of a sequence its own KV covers: stale after a recompute preemption,
+        # garbage after an abort / expiry / finish
+        self.scheduler.on_drop = lambda r: self.proposer.forget(r.seq_id)
 
     def _propose_drafts(self) -> None:
         cands = [r for r in self.scheduler.running
@@ -415,7 +418,10 @@ class LLMEngine:
             if slot < 0 or r.finished or slot >= len(r.output):
                 continue
             r.output[slot] = toks[i]
-            self.blocks.commit_tokens(r.seq_id, r.all_tokens, r.num_computed, r.params.cache_salt.encode())
+            # A request that schedule() preempted after this step was launched keeps its real token (it is in
+            # the waiting queue, its blocks are gone): only a sequence that still owns blocks registers them.
+            if r.status == RequestStatus.RUNNING and r.seq_id in self.blocks.seqs:
+                self.blocks.commit_tokens(r.seq_id, r.all_tokens, r.num_computed, r.params.cache_salt.encode())
             self.stats.decode_tokens += 1
             if r.first_token_time is None:
                 r.first_token_time = now
@@ -707,7 +713,19 @@ class LLMEngine:
         from .kv_tier import KvTier
         st = self.kv.store                                   # [layers, 2, blocks, kv heads, block, head dim]
         block_bytes = st[:, :, 0].numel() * st.element_size()
-        sig = f"{self.model_cfg.name}|{tuple(st[:, :, 0].shape)}|{st.dtype}|tp{self.tp_rank}"
+        # The signature names the model AND its weights: two checkpoints (or two random seeds) of one
+        # architecture must never re-use each other's KV files. A directory belongs to one model.
+        mc = self.model_cfg
+        probe = [self.weights.final_norm]
+        if self.weights.layers:
+            l0 = self.weights.layers[0]
+            probe += [t for t in (l0.attn_norm, l0.wqkv if isinstance(l0.wqkv, torch.Tensor) else None) if t is not None]
+        import hashlib
+        fp = hashlib.sha256()
+        for t in probe:
+            fp.update(t.detach().reshape(-1)[:4096].float().cpu().numpy().tobytes())
+        sig = (f"{mc.name}|{tuple(st[:, :, 0].shape)}|{st.dtype}|bs{self.block_size}|tp{self.tp_rank}|"
+               f"theta{mc.rope_theta}|{mc.rope_scaling.kind}:{mc.rope_scaling.factor}|w{fp.hexdigest()[:16]}")
         if self.tp_group is not None and getattr(self.tp_group, "size", 1) > 1:
             # ranks must take identical hit / miss decisions to keep their block tables equal: the host tier is
             # deterministic, a file that fails to read on one rank is not, so the disk tier is single-rank only

@@ -34,6 +34,7 @@ class ScheduledStep:
     seqs: List[ScheduledSeq] = field(default_factory=list)
     preempted: List[Request] = field(default_factory=list)
     cow: List[Tuple[int, int]] = field(default_factory=list)     # (src block, dst block) copies
+    cow_owner: List[Request] = field(default_factory=list)       # request each copy belongs to (same order as cow)
     expired: List[Request] = field(default_factory=list)
 
     @property
@@ -58,7 +59,15 @@ class Scheduler:
         # swap preemption: the engine installs an object with swap_out(req) -> bool / swap_in(req) / drop(req)
         # that moves a request's KV blocks to host memory and back (rust/engine/src/kv_tier.rs)
         self.swapper = None
+        # called with a request whose device-side state outside the block pool is stale or no longer needed
+        # (recompute preemption, abort, expiry, finish): the draft-model proposer forgets its KV marks there
+        self.on_drop = None
+        self._refund = 0             # token budget given back by victims preempted inside the current schedule()
         self.stats = {"steps": 0, "preemptions": 0, "scheduled_tokens": 0}
+
+    def _dropped(self, r: Request) -> None:
+        if self.on_drop is not None:
+            self.on_drop(r)
 
     # ------------------------------------------------------------------ queue
     def add(self, req: Request) -> None:
@@ -84,6 +93,7 @@ class Scheduler:
                     self.blocks.free_seq(r.seq_id)
                     r.status = RequestStatus.ABORTED
                     r.finish_reason = "abort"
+                    self._dropped(r)
                     return r
         return None
 
@@ -107,12 +117,19 @@ class Scheduler:
             victim.swapped = True                 # KV kept (on the host): nothing to recompute
         else:
             victim.num_computed = 0
+            self._dropped(victim)                 # its KV will be recomputed into other blocks
         self.blocks.free_seq(victim.seq_id)
         victim.status = RequestStatus.PREEMPTED
         victim.preemptions += 1
         self.waiting.appendleft(victim)
         step.preempted.append(victim)
+        # take the victim's rows, its copy-on-write pairs (their destination block was just freed and may be
+        # handed to another sequence inside this same schedule()) and its token budget back out of the step
+        self._refund += sum(s.count for s in step.seqs if s.req is victim)
         step.seqs = [s for s in step.seqs if s.req is not victim]
+        keep = [i for i, o in enumerate(step.cow_owner) if o is not victim]
+        step.cow = [step.cow[i] for i in keep]
+        step.cow_owner = [step.cow_owner[i] for i in keep]
         self.stats["preemptions"] += 1
         return True
 
@@ -121,6 +138,10 @@ class Scheduler:
             if not self._preempt_one(step, protect=req):
                 return False
         return True
+
+    def _take_refund(self) -> int:
+        n, self._refund = self._refund, 0
+        return n
 
     # ------------------------------------------------------------------ main
     def schedule(self) -> ScheduledStep:
@@ -139,6 +160,7 @@ class Scheduler:
                     self.blocks.free_seq(r.seq_id)
                     r.status = RequestStatus.ABORTED
                     r.finish_reason = "timeout"
+                    self._dropped(r)
                     step.expired.append(r)
 
         # 1. decode / verify rows of running requests (decode-first)
@@ -151,11 +173,14 @@ class Scheduler:
             count = 1 + n_draft
             if budget < count:
                 break
-            if not self._reserve(step, r, r.num_tokens + n_draft):
+            ok = self._reserve(step, r, r.num_tokens + n_draft)
+            budget += self._take_refund()
+            if not ok:
                 continue
             cow = self.blocks.cow_last_block(r.seq_id)
             if cow:
                 step.cow.append(cow)
+                step.cow_owner.append(r)
             step.seqs.append(ScheduledSeq(r, r.num_computed, count, True, verify=n_draft))
             budget -= count
 
@@ -165,7 +190,9 @@ class Scheduler:
             if r not in self.running or budget <= 0:
                 continue
             n = min(r.remaining, budget)
-            if not self._reserve(step, r, r.num_computed + n):
+            ok = self._reserve(step, r, r.num_computed + n)
+            budget += self._take_refund()
+            if not ok:
                 continue
             step.seqs.append(ScheduledSeq(r, r.num_computed, n, n == r.remaining))
             budget -= n
@@ -232,6 +259,12 @@ class Scheduler:
     def finish(self, r: Request, reason: str) -> None:
         if r in self.running:
             self.running.remove(r)
+        elif r in self.waiting:                    # a preempted request whose in-flight token ended it
+            self.waiting.remove(r)
+            if r.swapped and self.swapper is not None:
+                self.swapper.drop(r)
+                r.swapped = False
         self.blocks.free_seq(r.seq_id)
         r.status = RequestStatus.FINISHED
         r.finish_reason = reason
+        self._dropped(r)

@@ -321,3 +321,57 @@ def test_kv_tier_keeps_its_byte_budgets_and_returns_what_was_stored(tmp_path):
     off = KvTier("sig", nb)
     off.put(newest, blobs[newest])
     assert not off.enabled and not off.has(newest)
+
+
+def test_launch_ahead_commit_survives_two_preemptions_in_one_schedule():
+    """The launch-ahead protocol (placeholder commit -> schedule -> patch) when the scheduler evicts two
+    sequences of the step that is still in flight: their tokens are patched, nothing is registered for
+    a sequence that lost its blocks, and the step loop keeps running."""
+    from fllm_b200.runtime.request import RequestStatus
+    from fllm_b200.runtime.scheduler import ScheduledSeq, ScheduledStep
+
+    class _Done:
+        def synchronize(self):
+            pass
+
+    cfg = preset("qwen3-tiny")
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=64, num_kv_blocks=4,
+                                      block_size=4, enable_prefix_caching=False, watermark=0.0), device="cpu")
+    for p in _prompts(cfg.vocab_size, (3, 3, 3, 3)):
+        eng.add_request(p, SamplingParams(max_tokens=8))
+    eng.step()                                            # prefill: every sequence now holds 3 + 1 tokens in one block
+    running = list(eng.scheduler.running)
+    assert len(running) == 4 and all(r.is_decode for r in running)
+    step = ScheduledStep(seqs=[ScheduledSeq(r, r.num_computed, 1, True) for r in running])
+    fl = {"step": step, "event": _Done(), "out": torch.tensor([11, 12, 13, 14], dtype=torch.int32), "n": 4, "slots": []}
+    eng._precommit(fl)                                    # all four now need a second block; the pool has none
+    nxt = eng.scheduler.schedule()
+    victims = [r for r in running if r.status == RequestStatus.PREEMPTED]
+    assert len(victims) >= 2, "the tight pool must evict at least two sequences inside one schedule()"
+    events = eng._finalize(fl)                            # must not raise for sequences without a block table
+    assert len(events) == 4
+    for r, t in zip(running, (11, 12, 13, 14)):
+        assert r.output[-1] == t
+    assert sum(s.count for s in nxt.seqs) <= eng.cfg.max_num_batched_tokens
+
+
+def test_preempted_victim_gives_back_rows_budget_and_cow_pairs():
+    from fllm_b200.runtime.block_manager import BlockManager
+    from fllm_b200.runtime.request import Request
+    from fllm_b200.runtime.scheduler import ScheduledSeq, ScheduledStep, Scheduler
+    ec = EngineConfig(max_num_seqs=4, max_num_batched_tokens=8, max_model_len=64, num_kv_blocks=4, block_size=4,
+                      enable_prefix_caching=False, watermark=0.0)
+    bm = BlockManager(4, 4, False, 0.0)
+    sch = Scheduler(ec, bm)
+    a, b = Request("a", 0, [1, 2, 3], SamplingParams()), Request("b", 1, [4, 5, 6], SamplingParams())
+    dropped = []
+    sch.on_drop = dropped.append
+    for r in (a, b):
+        bm.allocate(r.seq_id, [])
+        bm.ensure_capacity(r.seq_id, 3)
+        sch.running.append(r)
+    step = ScheduledStep(seqs=[ScheduledSeq(b, 0, 3, True)], cow=[(0, 1)], cow_owner=[b])
+    assert sch._preempt_one(step, protect=a)
+    assert step.seqs == [] and step.cow == [] and step.cow_owner == []
+    assert sch._take_refund() == 3 and sch._take_refund() == 0
+    assert dropped == [b] and b in sch.waiting

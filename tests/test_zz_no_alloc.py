@@ -32,6 +32,7 @@ def lib():
                    ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                    ctypes.c_void_p, ctypes.c_void_p]
     so.fllm_noalloc_last_error.restype = ctypes.c_char_p
+    so.fllm_noalloc_init.restype = ctypes.c_int
     so.fllm_noalloc_scratch_bytes.restype = ctypes.c_size_t
     return so
 
@@ -49,8 +50,10 @@ def test_matches_regular_entry_point_on_two_calls_in_a_row(lib):
     g = torch.Generator(device="cuda").manual_seed(11)
     ws = torch.zeros(32 << 20, dtype=torch.uint8, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    # second call: other shape, other data, fewer splits - stale partials must not leak in
-    for T, N, K, splits, with_bias in [(64, 2048, 4096, 4, True), (24, 1024, 2048, 2, False)]:
+    assert lib.fllm_noalloc_init() == 0, lib.fllm_noalloc_last_error()
+    assert lib.fllm_noalloc_init() == 0                 # idempotent
+    # later calls: other shape, other data, fewer splits (down to none) - stale partials must not leak in
+    for T, N, K, splits, with_bias in [(64, 2048, 4096, 4, True), (24, 1024, 2048, 2, False), (64, 2048, 4096, 1, True)]:
         x = torch.randn(T, K, generator=g, device="cuda").to(torch.bfloat16)
         w = (torch.randn(N, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
         b = torch.randn(N, generator=g, device="cuda").to(torch.bfloat16) if with_bias else None
@@ -80,3 +83,6 @@ def test_rejects_what_does_not_fit_the_scratch_array(lib):
     torch.cuda.synchronize()
     assert bool((y == 1).all())                         # nothing was launched
     assert _call(lib, x[:, :K - 4], w, None, y, 1) == -1   # k not a multiple of 8
+    assert _call(lib, x.view(-1)[8:8 + 64 * K].view(64, K)[:, :K], w, None, y, 1) == 0      # 16-byte aligned offset: fine
+    odd = x.view(-1)[4:4 + 64 * K].view(64, K)           # 8-byte offset: rejected before anything is launched
+    assert _call(lib, odd, w, None, y, 1) == -1 and "aligned" in lib.fllm_noalloc_last_error().decode()

@@ -108,7 +108,7 @@ def main():
         step = e.scheduler.schedule()
         batch = e._build_batch(step)
         lg = e.decoder.full_logits(e.decoder.forward(batch)).float()
-        toks = e.decoder.greedy_tokens(e.decoder.forward(batch)) if False else lg.argmax(-1).int()
+        toks = lg.argmax(-1).int()
         e._commit(step, toks.tolist())
         return lg[-1].cpu()
 
