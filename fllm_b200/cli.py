@@ -91,9 +91,24 @@ def cmd_serve(args) -> int:
     from .server.app import serve
     eng, tok = build_engine(args)
     eng.warm_up(buckets=[b for b in eng.cfg.graph_buckets if b <= 64])
+    controller = None
+    if eng.par.world > 1:
+        # One front end for the whole rank group: rank 0 serves HTTP and announces every admission, abort and
+        # step; the other ranks run the worker loop (launch one process per GPU with torch.distributed.run).
+        from .comm import shutdown_distributed
+        from .runtime.step_control import ControlChannel, StepController
+        controller = StepController(eng, ControlChannel(timeout_s=args.control_timeout))
+        if not controller.ch.is_leader:
+            why = controller.follow()
+            eng.close()
+            if why == "comm":
+                print("[fllm_b200] control channel lost; this rank leaves", file=sys.stderr, flush=True)
+                os._exit(3)                  # a broken group cannot be torn down collectively
+            shutdown_distributed()
+            return 0
     serve(eng, tok, args.host, args.port, args.model_name or os.path.basename(args.model), args.api_key, args.log_level,
           tool_parser=args.tool_parser, reasoning_parser=args.reasoning_parser,
-          response_cache_entries=args.response_cache_entries, otlp_endpoint=args.otlp_endpoint)
+          response_cache_entries=args.response_cache_entries, otlp_endpoint=args.otlp_endpoint, controller=controller)
     return 0
 
 
@@ -217,6 +232,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     s.add_argument("--tool-parser", default=None, choices=["hermes", "llama3_json", "mistral"])
     s.add_argument("--reasoning-parser", default=None, choices=["think", "think_open"])
     s.add_argument("--response-cache-entries", type=int, default=256, help="0 disables the response cache")
+    s.add_argument("--control-timeout", type=float, default=float(os.environ.get("FLLM_CONTROL_TIMEOUT", "30")),
+                   help="seconds a rank waits for the step-control message of a multi-rank server before it gives up")
     s.add_argument("--otlp-endpoint", default=os.environ.get("OTEL_EXPORTER_OTLP_ENDPOINT"),
                    help="export request spans as OTLP/HTTP JSON to <endpoint>/v1/traces")
     s.set_defaults(fn=cmd_serve)

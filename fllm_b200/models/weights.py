@@ -49,6 +49,17 @@ class LayerWeights:
     glu_layout: int = 0
 
 
+def gate_up_natural(lw: "LayerWeights") -> torch.Tensor:
+    """The dense gate|up matrix in its natural row order (gate half, then up half), whatever order the
+    decoder re-arranged it into for the GEMM epilogue."""
+    w = lw.w_gate_up
+    if getattr(lw, "glu_layout", 0) != 16:
+        return w
+    I = w.shape[0] // 2
+    blk = w.view(I // 16, 2, 16, *w.shape[1:])
+    return torch.cat([blk[:, 0].reshape(I, *w.shape[1:]), blk[:, 1].reshape(I, *w.shape[1:])], 0)
+
+
 @dataclass
 class DecoderWeights:
     embed: torch.Tensor

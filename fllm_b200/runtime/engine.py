@@ -147,7 +147,7 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
-                    request_id: Optional[str] = None) -> str:
+                    request_id: Optional[str] = None, arrival: Optional[float] = None) -> str:
         params = params or SamplingParams()
         params.validate(self.model_cfg.vocab_size)
         prompt = [int(t) for t in prompt]
@@ -157,6 +157,8 @@ class LLMEngine:
             raise ValueError(f"prompt of {len(prompt)} tokens exceeds max_model_len={self.cfg.max_model_len}")
         rid = request_id or f"req-{next(self._req_ids)}"
         req = Request(rid, next(self._seq_ids), prompt, params)
+        if arrival is not None:          # step control: every rank files the request under the leader's clock
+            req.arrival = arrival
         self.requests[rid] = req
         self.scheduler.add(req)
         return rid

@@ -62,6 +62,7 @@ class Scheduler:
         # called with a request whose device-side state outside the block pool is stale or no longer needed
         # (recompute preemption, abort, expiry, finish): the draft-model proposer forgets its KV marks there
         self.on_drop = None
+        self.now_override = None     # step control: judge deadlines with the leader's clock instead of the local one
         self._refund = 0             # token budget given back by victims preempted inside the current schedule()
         self.stats = {"steps": 0, "preemptions": 0, "scheduled_tokens": 0}
 
@@ -147,7 +148,7 @@ class Scheduler:
     def schedule(self) -> ScheduledStep:
         cfg = self.cfg
         step = ScheduledStep()
-        now = time.monotonic()
+        now = self.now_override if self.now_override is not None else time.monotonic()
         budget = cfg.max_num_batched_tokens
 
         # deadlines

@@ -34,8 +34,12 @@ class EngineWorker:
 
     STALL_S = 30.0
 
-    def __init__(self, engine, metrics: Metrics):
+    def __init__(self, engine, metrics: Metrics, controller=None):
+        """controller: runtime.step_control.StepController when this process is the front end of a multi-rank
+        model instance; admissions, aborts and every step are then announced to the other ranks first."""
         self.engine, self.metrics = engine, metrics
+        self.controller = controller
+        self.comm_failed = False
         self.cmds: "queue.Queue[tuple]" = queue.Queue()
         self.streams: Dict[str, tuple] = {}          # request id -> (loop, asyncio.Queue, t_submit, n_prompt)
         self.heartbeat = time.monotonic()
@@ -52,6 +56,8 @@ class EngineWorker:
         self.stopped.set()
         self.cmds.put(("wake",))
         self.thread.join(timeout=10)
+        if self.controller is not None:
+            self.controller.shutdown()              # followers leave their loop
 
     # called from the asyncio side
     def submit(self, loop, rid: str, prompt: List[int], params: SamplingParams) -> "asyncio.Queue":
@@ -77,7 +83,7 @@ class EngineWorker:
         return q
 
     def ready(self) -> bool:
-        return (not self.draining and not self.stopped.is_set()
+        return (not self.draining and not self.stopped.is_set() and not self.comm_failed
                 and time.monotonic() - self.heartbeat < self.STALL_S)
 
     def _emit(self, rid: str, item: dict, final: bool) -> None:
@@ -99,13 +105,30 @@ class EngineWorker:
                 _, rid, prompt, params, loop, q = cmd
                 self.streams[rid] = (loop, q, time.monotonic(), len(prompt))
                 try:
-                    self.engine.add_request(prompt, params, request_id=rid)
+                    if self.comm_failed:
+                        raise RuntimeError("the model's rank group is down")
+                    if self.controller is not None:
+                        self.controller.admit(rid, prompt, params)
+                    else:
+                        self.engine.add_request(prompt, params, request_id=rid)
                     self.metrics.inc("fllm_prompt_tokens_total", len(prompt))
                 except Exception as e:                                   # validation errors
-                    self._emit(rid, {"error": str(e), "status": 400}, True)
+                    self._emit(rid, {"error": str(e), "status": 503 if self.comm_failed else 400}, True)
             elif cmd[0] == "abort":
-                self.engine.abort_request(cmd[1])
+                if self.controller is not None:
+                    self.controller.abort(cmd[1])
+                else:
+                    self.engine.abort_request(cmd[1])
                 self.streams.pop(cmd[1], None)
+            elif cmd[0] in ("call", "adopt") and self.controller is not None:
+                # closures cannot travel to the other ranks: these operations (beam search, embeddings,
+                # disaggregated hand-over) are single-rank features
+                err = RuntimeError("this operation is not available when one server drives several ranks")
+                if cmd[0] == "call":
+                    cmd[2].call_soon_threadsafe(cmd[3].set_exception, err)
+                else:
+                    self.streams[cmd[1]] = (cmd[4], cmd[5], time.monotonic(), cmd[2])
+                    self._emit(cmd[1], {"error": str(err), "status": 501}, True)
             elif cmd[0] == "call":
                 _, fn, loop, fut = cmd
                 try:
@@ -141,25 +164,50 @@ class EngineWorker:
                                        "embedding": ev.embedding, "logprobs": ev.logprobs,
                                        "top_logprobs": ev.top_logprobs}, ev.finished)
 
+    def _group_down(self, e: Exception) -> None:
+        """A control collective failed: the other ranks are gone or late. Every request in flight ends with
+        503, nothing new is admitted, readiness turns false; the process stays up to say so."""
+        self.comm_failed = True
+        self.draining = True
+        self.metrics.inc("fllm_comm_failures_total")
+        for rid in list(self.streams):
+            try:
+                self.engine.abort_request(rid)
+            except Exception:
+                pass
+            self._emit(rid, {"error": f"model rank group failed: {e}", "status": 503}, True)
+
     def _run(self) -> None:
+        from ..comm.group import CommError
         eng = self.engine
+        ctl = self.controller
         while not self.stopped.is_set():
             self.heartbeat = time.monotonic()
             self._drain_cmds(block=not eng.has_unfinished())
+            if self.comm_failed:
+                continue
             if not eng.has_unfinished():
+                if ctl is not None:
+                    try:
+                        ctl.idle_tick()
+                    except CommError as e:
+                        self._group_down(e)
                 continue
             try:
                 if self.inject_failure > 0:
                     self.inject_failure -= 1
                     raise RuntimeError("injected step failure")
-                events = eng.step()
+                events = ctl.step() if ctl is not None else eng.step()
                 self.consecutive_failures = 0
+            except CommError as e:
+                self._group_down(e)
+                continue
             except Exception as e:                                       # contain, fail in-flight, continue
                 self.consecutive_failures += 1
                 self.metrics.inc("fllm_worker_panics_total")
                 err_id = uuid.uuid4().hex[:12]
                 for rid in list(self.streams):
-                    eng.abort_request(rid)
+                    (ctl.abort if ctl is not None else eng.abort_request)(rid)     # followers drop them too
                     self._emit(rid, {"error": f"internal error {err_id}: {type(e).__name__}", "status": 500}, True)
                 if self.consecutive_failures >= 3:
                     self.stopped.set()
@@ -247,7 +295,9 @@ class StopChecker:
 def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Optional[str] = None,
                tool_parser: Optional[str] = None, reasoning_parser: Optional[str] = None,
                response_cache_entries: int = 256, response_cache_ttl_s: float = 600.0,
-               otlp_endpoint: Optional[str] = None) -> FastAPI:
+               otlp_endpoint: Optional[str] = None, controller=None) -> FastAPI:
+    """controller: a runtime.step_control.StepController when this process fronts a multi-rank model instance
+    (``serve --tp N`` on rank 0): every admission, abort and step is announced to the other ranks."""
     from .cache import ResponseCache, request_key
     from .parsers import REASONING_PARSERS, TOOL_PARSERS, ReasoningStream, parse_tool_calls, split_reasoning
     if tool_parser and tool_parser not in TOOL_PARSERS:
@@ -255,7 +305,7 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
     if reasoning_parser and reasoning_parser not in REASONING_PARSERS:
         raise ValueError(f"--reasoning-parser must be one of {REASONING_PARSERS}")
     metrics = Metrics()
-    worker = EngineWorker(engine, metrics)
+    worker = EngineWorker(engine, metrics, controller)
     rcache = ResponseCache(response_cache_entries, response_cache_ttl_s)
     from ..utils.telemetry import SpanExporter
     spans = SpanExporter(otlp_endpoint, service=model_name)

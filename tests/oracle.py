@@ -3,6 +3,8 @@ paged / scheduled / fused pipeline. It shares only the weight tensors with the e
 import math
 
 import torch
+
+from fllm_b200.models.weights import gate_up_natural
 import torch.nn.functional as F
 
 from fllm_b200.config import ModelConfig, rope_inv_freq
@@ -79,7 +81,7 @@ def dense_forward(cfg: ModelConfig, w, tokens, round_bf16=True):
             from fllm_b200.models.moe import moe_reference
             d = moe_reference(cfg, lw, h)
         else:
-            gu = r(h @ lw.w_gate_up.float().t())
+            gu = r(h @ gate_up_natural(lw).float().t())
             I = gu.shape[1] // 2
             gate = F.gelu(gu[:, :I], approximate="tanh") if cfg.act == "geglu" else F.silu(gu[:, :I])
             act = r(gate * gu[:, I:])

@@ -52,7 +52,7 @@ def test_rmsnorm_consumes_partials(ops, T, splits, bias):
     h0 = ops.rmsnorm(r0, y, nw, 1e-6)
     # fused: the norm adds the partials
     d = ops.linear(x, w, b, force_splits=splits, defer=True)
-    assert isinstance(d, Deferred) and d.splits == splits
+    assert isinstance(d, Deferred) and 2 <= d.splits <= splits
     r1 = res.clone()
     h1 = ops.rmsnorm(r1, d, nw, 1e-6)
     assert torch.equal(r0, r1), "updated residual must be bit-identical to the two-kernel path"
