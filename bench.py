@@ -15,6 +15,13 @@ One "step" is one engine decode step of the whole batch (64 new tokens). Two num
                  pinned-host -> device copy of the step inputs, graph replay, device -> host
                  read of the sampled ids.
 
+``--config N`` selects another of the five benchmark configurations (default 2, the one above):
+1 = tiny Llama Q4_K on the CPU engine (batch 1), 3 = Llama-3-70B-shaped block-FP8 model (TP over all
+ranks, batch 128, prompts 512-4096), 4 = gpt-oss-120b-shaped MXFP4 mixture of experts (expert parallel
+over all ranks, batch 256 x 2048), 5 = Llama-3.1-70B-shaped NVFP4 model as TP x PP2 (batch 32 x 4096).
+Weights are drawn directly in their packed format, layer by layer. ``--model`` overrides the shape
+(a tiny preset checks a configuration's plumbing on one GPU).
+
 ``--impl reference`` reports why the reference cannot run here (it is a Rust workspace;
 no Rust toolchain is installed and pip cannot install it).
 """
@@ -92,6 +99,41 @@ def reference_arm(args) -> None:
     }))
 
 
+# model preset, weight format, batch, prompt-length range, output tokens, pipeline stages, expert parallel
+CONFIGS = {
+    2: dict(model="qwen3-8b", fmt="bf16", batch=64, prompt=(1024, 1024), out=256, pp=1, ep=False),
+    3: dict(model="llama3-70b", fmt="fp8_block", batch=128, prompt=(512, 4096), out=512, pp=1, ep=False),
+    4: dict(model="gpt-oss-120b", fmt="mxfp4", batch=256, prompt=(2048, 2048), out=256, pp=1, ep=True),
+    5: dict(model="llama3-70b", fmt="nvfp4", batch=32, prompt=(4096, 4096), out=512, pp=2, ep=False),
+}
+
+
+def config1_cpu(args) -> None:
+    """Tiny Llama-architecture decoder, Q4_K weights in a synthetic GGUF, CPU engine, batch 1: prompt of 128
+    uniform-random ids, 64 greedy tokens, paged f16 KV in 16-token blocks."""
+    import tempfile
+    from fllm_b200.cpu_engine import CpuEngine, write_tiny_llama_gguf
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "tiny-llama-q4k.gguf")
+        cfg = write_tiny_llama_gguf(path, seed=0)
+        eng = CpuEngine(path)
+        for _ in range(max(args.warmup, 3)):
+            eng.bench(128, 64, seed=0)
+        runs = [eng.bench(128, 64, seed=0) for _ in range(max(1, min(args.steps, 16)))]
+        eng.close()
+    dec = statistics.median(r["decode_tok_s"] for r in runs)
+    pre = statistics.median(r["prompt_tok_s"] for r in runs)
+    print(json.dumps({
+        "metric": "decode tok/s (CPU engine, batch 1)", "value": round(dec, 1), "unit": "tok/s", "n_gpus": 0,
+        "steps": len(runs), "warmup": max(args.warmup, 3), "ms_per_step": round(1e3 / dec, 4), "higher_is_better": True,
+        "scaling": "none", "vs_baseline": None, "dtype": "q4_k weights x q8_k activations, f16 KV",
+        "data": "synthetic (uniform random token ids, N(0,0.02) weights quantised to Q4_K)",
+        "config": {"config": 1, "model": cfg.name, "global_batch": 1, "seq_len": 128, "output_tokens": 64,
+                   "parallelism": "cpu", "threads": os.cpu_count()},
+        "prefill_tok_s": round(pre, 1), "gpu_launches": 0,
+    }))
+
+
 def main() -> None:
     if os.environ.get("FLLM_HANG_DUMP"):      # debugging aid: dump all Python stacks and exit if the run stalls
         faulthandler.dump_traceback_later(int(os.environ["FLLM_HANG_DUMP"]), exit=True)
@@ -100,9 +142,11 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="qwen3-8b")
-    ap.add_argument("--batch", type=int, default=64)
-    ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5])
+    ap.add_argument("--model", default=None)
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--prompt-len", type=int, default=None)
+    ap.add_argument("--weight-format", default=None)
     ap.add_argument("--backend", default=os.environ.get("FLLM_TP_BACKEND", "auto"),
                     help="tensor-parallel collectives: auto | fused | nccl")
     ap.add_argument("--no-graphs", action="store_true")
@@ -117,6 +161,15 @@ def main() -> None:
             reference_arm(args)
         return
     args.warmup = max(args.warmup, 3)
+    if args.config == 1:
+        return config1_cpu(args)
+    conf = CONFIGS[args.config]
+    args.model = args.model or conf["model"]
+    args.batch = args.batch or conf["batch"]
+    p_lo, p_hi = conf["prompt"]
+    if args.prompt_len:
+        p_lo = p_hi = args.prompt_len
+    args.prompt_len = p_hi
 
     import torch
     from fllm_b200.comm import init_distributed
@@ -130,23 +183,34 @@ def main() -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     cfg = preset(args.model)
+    cfg.weight_format = args.weight_format or conf["fmt"]
+    pp = conf["pp"] if world % conf["pp"] == 0 and world >= conf["pp"] else 1
+    tp = world // pp
     # Prompts are prefilled 2048 tokens per step while the sequences that are already through decode
     # along (decode-first scheduling), so the first sequences are `stagger` tokens ahead of the last when
     # the timed region starts: leave room for that, or they would reach the length limit inside it.
-    stagger = -(-args.batch * args.prompt_len // 2048) + 2
+    stagger = -(-args.batch * p_hi // 2048) + 2
     out_len = args.warmup + 2 * args.steps + 8 + stagger
     ec = EngineConfig(max_num_seqs=args.batch, max_num_batched_tokens=2048, block_size=16,
-                      max_model_len=args.prompt_len + out_len + 16, enable_prefix_caching=False,
+                      max_model_len=p_hi + out_len + 16, enable_prefix_caching=False,
                       use_cuda_graphs=not args.no_graphs)
     ec.num_kv_blocks = args.batch * (-(-ec.max_model_len // 16)) + 16
-    par = ParallelConfig(tp=world)
-    tp_rt = make_tp_runtime(world, rank, dev, backend=args.backend, hidden=cfg.hidden_size,
-                            max_tokens=ec.max_num_batched_tokens)
-    eng = LLMEngine(cfg, ec, par, device=dev, tp_group=tp_rt, tp_rank=rank, seed=0)
+    par = ParallelConfig(tp=tp, pp=pp, expert_parallel=bool(conf["ep"] and cfg.is_moe and tp > 1), ep_dispatch="alltoall")
+    pp_grp, stage, tp_rank = None, 0, rank
+    if pp > 1:
+        from fllm_b200.comm import make_tp_pp_groups
+        tp_grp, pp_grp, stage, tp_rank = make_tp_pp_groups(tp, pp)
+        tp_rt = make_tp_runtime(tp, tp_rank, dev, backend=args.backend, group=tp_grp, hidden=cfg.hidden_size,
+                                max_tokens=ec.max_num_batched_tokens)
+    else:
+        tp_rt = make_tp_runtime(world, rank, dev, backend=args.backend, hidden=cfg.hidden_size,
+                                max_tokens=ec.max_num_batched_tokens)
+    eng = LLMEngine(cfg, ec, par, device=dev, tp_group=tp_rt, tp_rank=tp_rank, seed=0, pp_group=pp_grp, stage=stage)
 
     g = torch.Generator().manual_seed(1234)
-    prompts = [torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist()
-               for _ in range(args.batch)]
+    lens = [args.prompt_len] * args.batch if p_lo == p_hi else \
+        torch.randint(p_lo, p_hi + 1, (args.batch,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
     sp = SamplingParams(max_tokens=out_len + 64, ignore_eos=True)
     for p in prompts:
         eng.add_request(p, sp)
@@ -185,7 +249,7 @@ def main() -> None:
     e1.record()
     sync_all()
     prefill_ms = max_over_ranks(e0.elapsed_time(e1))
-    prefill_tok_s = args.batch * args.prompt_len / (prefill_ms / 1e3)
+    prefill_tok_s = sum(lens) / (prefill_ms / 1e3)
     if args.profile_prefill:
         if rank == 0:
             print(json.dumps({"profiled_prefill_step": 2, "prefill_steps": n_prefill_steps, "prefill_tok_s": prefill_tok_s}))
@@ -264,6 +328,8 @@ def main() -> None:
     for r in eng.requests.values():
         tt = r.token_times[-args.steps:]
         itl += [b - a for a, b in zip(tt, tt[1:])]
+    # time to first token per request (all requests are submitted together before the first step)
+    ttfts = [r.first_token_time - r.arrival for r in eng.requests.values() if r.first_token_time is not None]
     status = eng.ops.check_status()
 
     tokens = args.batch * args.steps
@@ -275,9 +341,12 @@ def main() -> None:
             "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 4),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
-            "config": {"model": cfg.name, "global_batch": args.batch, "seq_len": args.prompt_len,
-                       "parallelism": f"tp{world}", "tp_backend": getattr(tp_rt, "backend", "none"),
+            "dtype": "bf16" if cfg.weight_format == "bf16" else f"bf16 activations, {cfg.weight_format} weights",
+            "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
+            "config": {"config": args.config, "model": cfg.name, "global_batch": args.batch,
+                       "seq_len": args.prompt_len if p_lo == p_hi else f"{p_lo}-{p_hi}",
+                       "parallelism": (f"tp{tp}" + (f"xpp{pp}" if pp > 1 else "") + ("+ep" if par.expert_parallel else "")),
+                       "tp_backend": getattr(tp_rt, "backend", "none"), "weight_format": cfg.weight_format,
                        "kv": "paged bf16, 16-token blocks", "chunked_prefill": 2048,
                        "cuda_graphs": not args.no_graphs, "async_scheduling": eng._async_ok(),
                        "l2": "inputs larger than L2: 16 GB of weights + KV streamed per step"},
@@ -291,6 +360,7 @@ def main() -> None:
                     "gc_pauses_ms": sorted(gc_events, key=lambda e: -e[1])[:4]},
             "gpu_launches": (launches_per_step or 0) * args.steps + (eng.stats.kernel_launches - l0),
             "prefill_tok_s": round(prefill_tok_s, 1), "ttft_s_first": round(ttft or 0.0, 4),
+            "ttft_p50_s": round(statistics.median(ttfts), 4) if ttfts else None,
             "itl_p50_ms": round(statistics.median(itl) * 1e3, 4) if itl else None,
             "kernel_status": status,
         }))

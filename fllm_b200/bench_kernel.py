@@ -238,7 +238,13 @@ def main(argv=None) -> None:
     ap.add_argument("--tp-half-layer", action="store_true",
                     help="fused vs library tensor-parallel half-layer (one process per GPU under torch.distributed.run)")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--vs-reference", action="store_true",
+                    help="time our kernels next to the reference engine's own CUDA kernels (bench_reference.py)")
+    ap.add_argument("--ref-lib", default=None, help="path of the reference kernel library (libfllmcuda.so)")
     args = ap.parse_args(argv)
+    if args.vs_reference:
+        from .bench_reference import run as run_vs_reference
+        return run_vs_reference(args.model, args.ref_lib, args.json)
     if args.case:
         return run_case(args.case, args.reps)
     if args.tp_half_layer:

@@ -220,6 +220,10 @@ def _selftest(which: str) -> int:
 
 
 def main(argv: Optional[List[str]] = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] == "bench-kernel":            # its own option set (a REMAINDER argument would refuse leading options)
+        from .bench_kernel import main as bench_kernel_main
+        return bench_kernel_main(argv[1:]) or 0
     ap = argparse.ArgumentParser(prog="fllm_b200")
     sub = ap.add_subparsers(dest="cmd", required=True)
     s = sub.add_parser("serve", help="HTTP server (OpenAI / Anthropic / Ollama dialects on one port)")

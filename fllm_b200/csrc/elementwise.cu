@@ -159,17 +159,21 @@ rmsnorm_splitk_kernel(__nv_bfloat16* __restrict__ residual, long long ld_res, co
   const int row = blockIdx.x;
   const int nvec = hidden / 4;
   __nv_bfloat16* xr = residual + (size_t)row * ld_res;
-  // the residual was written several kernels ago and the weights are static: fetch them before the wait
+  // The norm weights are static: fetch them before the wait. The residual is NOT: programmatic launches
+  // chain (a kernel may start while the predecessor of its predecessor still runs), so everything an
+  // earlier kernel of the step wrote is read only after griddepcontrol.wait.
   uint2 xv[ITERS], wv[ITERS];
 #pragma unroll
   for (int it = 0; it < ITERS; ++it) {
     const int i = threadIdx.x + it * blockDim.x;
-    if (i < nvec) {
-      xv[it] = reinterpret_cast<const uint2*>(xr)[i];
-      wv[it] = reinterpret_cast<const uint2*>(w)[i];
-    }
+    if (i < nvec) wv[it] = reinterpret_cast<const uint2*>(w)[i];
   }
   pdl_wait();
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = threadIdx.x + it * blockDim.x;
+    if (i < nvec) xv[it] = reinterpret_cast<const uint2*>(xr)[i];
+  }
   const size_t plane = (size_t)rows * hidden;
   float vals[ITERS][4];
   float ss = 0.f;

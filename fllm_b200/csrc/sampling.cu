@@ -226,17 +226,21 @@ argmax_rows_split_kernel(const T* __restrict__ logits, long long ld, int vocab, 
   }
 }
 
-size_t argmax_split_scratch_bytes(int rows, int parts) { return (size_t)rows * 4 + (size_t)rows * parts * 8 + 16; }
+// scratch layout: [kArgmaxMaxRows row counters, zero between launches][rows * parts (value, index) pairs]. The counter
+// block has a fixed size so that calls with different row counts never park pairs where another call counts.
+constexpr int kArgmaxMaxRows = 1024;
+size_t argmax_split_scratch_bytes(int rows, int parts) { return (size_t)kArgmaxMaxRows * 4 + (size_t)rows * parts * 8; }
 
 void argmax_rows_split(const void* logits, int is_fp32, long long ld, int rows, int vocab, int* out_ids, float* out_vals,
                        float* out_pairs, int id_offset, void* scratch, size_t scratch_bytes, cudaStream_t s) {
   if (rows <= 0) return;
+  if (rows > kArgmaxMaxRows) throw std::runtime_error("argmax_rows_split: at most 1024 rows");
   int parts = max(1, min(32, (2 * sm_count() + rows - 1) / rows));
   parts = min(parts, max(1, vocab / 2048));
   if (argmax_split_scratch_bytes(rows, parts) > scratch_bytes)
     throw std::runtime_error("argmax_rows_split: scratch too small");
   auto* counters = reinterpret_cast<unsigned int*>(scratch);                       // zero between launches
-  auto* part = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(scratch) + (((size_t)rows * 4 + 15) & ~(size_t)15));
+  auto* part = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(scratch) + (size_t)kArgmaxMaxRows * 4);
   dim3 grid(rows, parts);
   if (is_fp32)
     argmax_rows_split_kernel<float><<<grid, kSampThreads, 0, s>>>((const float*)logits, ld, vocab, parts, out_ids, out_vals,

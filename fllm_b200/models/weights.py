@@ -151,13 +151,45 @@ def _randn(shape, gen, device, dtype, std=0.02):
     return (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std).to(dtype)
 
 
+def pack_layer(lw: LayerWeights, fmt: str) -> None:
+    """Replace the big matrices of one layer by their packed form, in place: ``fp8_block`` (e4m3 codes + one fp32
+    scale per 128 x 128), ``nvfp4`` (e2m1 + e4m3 scale per 16 + tensor scale) or ``mxfp4`` (e2m1 + e8m0 scale per
+    32; for mixture-of-experts layers only the expert stacks are packed, attention stays bf16 as in gpt-oss).
+    Matrices whose shape the format cannot tile stay bf16."""
+    if fmt in ("bf16", "", None):
+        return
+    if fmt == "fp8_block":
+        from ..ops.native import Fp8BlockWeight, quantize_weight_fp8_block
+        for name in ("wqkv", "wo", "w_gate_up", "w_down"):
+            w = getattr(lw, name, None)
+            if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0:
+                setattr(lw, name, Fp8BlockWeight(*quantize_weight_fp8_block(w)))
+        return
+    if fmt in ("nvfp4", "mxfp4"):
+        from ..ops.fp4 import Fp4ExpertStack, Fp4Weight
+        if lw.exp_gate_up is not None:
+            if fmt == "mxfp4" and isinstance(lw.exp_gate_up, torch.Tensor) and lw.exp_gate_up.shape[2] % 64 == 0:
+                lw.exp_gate_up = Fp4ExpertStack.from_dense(lw.exp_gate_up, fmt)
+                lw.exp_down = Fp4ExpertStack.from_dense(lw.exp_down, fmt)
+            return
+        for name in ("wqkv", "wo", "w_gate_up", "w_down"):
+            w = getattr(lw, name, None)
+            if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 64 == 0 and w.shape[0] % 8 == 0:
+                setattr(lw, name, Fp4Weight.from_dense(w, fmt))
+        return
+    raise ValueError(f"random initialisation in weight format {fmt!r} is not available (bf16, fp8_block, nvfp4, mxfp4)")
+
+
 def init_random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: int = 0,
                         tp: int = 1, tp_rank: int = 0, expert_parallel: bool = False,
                         layers: Optional[range] = None, first_stage: bool = True,
-                        last_stage: bool = True) -> DecoderWeights:
+                        last_stage: bool = True, weight_format: Optional[str] = None) -> DecoderWeights:
     """N(0, 0.02) weights, norm weights 1. Every tensor is drawn at full size from a
     generator seeded by (seed, layer, tensor) and then cut, so any (tp, pp) layout
-    holds exactly the same model as the single-device one."""
+    holds exactly the same model as the single-device one. ``weight_format`` (default: the
+    model's own) packs every layer right after it is drawn, so a 70B-class model never exists
+    in bf16 as a whole."""
+    weight_format = weight_format if weight_format is not None else cfg.weight_format
     device = torch.device(device)
     sp = make_shard_spec(cfg, tp, tp_rank, expert_parallel)
     D, H = cfg.head_dim, cfg.hidden_size
@@ -225,6 +257,7 @@ def init_random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, se
             isl = slice(sp.inter_start, sp.inter_start + sp.inter_local)
             lw.w_gate_up = torch.cat([g[isl], u[isl]], 0).contiguous()
             lw.w_down = full((H, I), li, 6)[:, isl].contiguous()
+        pack_layer(lw, weight_format)
         out_layers.append(lw)
 
     embed = full((cfg.vocab_size, H), "embed") if first_stage or cfg.tie_embeddings else \

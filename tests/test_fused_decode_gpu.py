@@ -56,7 +56,8 @@ def test_rmsnorm_consumes_partials(ops, T, splits, bias):
     r1 = res.clone()
     h1 = ops.rmsnorm(r1, d, nw, 1e-6)
     assert torch.equal(r0, r1), "updated residual must be bit-identical to the two-kernel path"
-    assert torch.equal(h0, h1)
+    # the row's sum of squares is added in another order (32 warps instead of 8): at most one bf16 step apart
+    _close(h1, h0, 1e-2)
     assert ops.check_status() == 0
 
 
@@ -162,8 +163,8 @@ def test_argmax_split(ops, rows, vocab, dtype):
 
 
 def test_decoder_step_matches_unfused_chain(ops):
-    """A tiny dense model: the fused decode chain (deferred reductions, gated epilogue) against the
-    same decoder with the fusions switched off, bit for bit."""
+    """A tiny dense model: the decode chain with the split-K reductions left to the consumers against
+    the same decoder with stand-alone reduction kernels (equal up to the summation order of the norms)."""
     from fllm_b200.config import ModelConfig
     from fllm_b200.models.decoder import Decoder, KVCache, StepBatch
     from fllm_b200.models.weights import init_random_weights
@@ -172,17 +173,17 @@ def test_decoder_step_matches_unfused_chain(ops):
     outs = []
     for fused in (True, False):
         w = init_random_weights(cfg, "cuda", seed=3)
-        kv = KVCache(cfg.num_layers, 16, 2, 16, 128, "cuda")
+        kv = KVCache(cfg.num_layers, 32, 2, 16, 128, "cuda")
         dec = Decoder(cfg, w, kv, ops)
         if not fused:
             dec._defer = False
         T = 24
         dev = "cuda"
         b = StepBatch(token_ids=torch.arange(T, dtype=torch.int32, device=dev), positions=torch.zeros(T, dtype=torch.int32, device=dev),
-                      slots=(torch.arange(T, dtype=torch.int32, device=dev) * 16) % 256, row_seq=torch.arange(T, dtype=torch.int32, device=dev),
-                      block_tables=torch.arange(T, dtype=torch.int32, device=dev).view(T, 1) % 16,
+                      slots=torch.arange(T, dtype=torch.int32, device=dev) * 16, row_seq=torch.arange(T, dtype=torch.int32, device=dev),
+                      block_tables=torch.arange(T, dtype=torch.int32, device=dev).view(T, 1),
                       logit_rows=torch.arange(T, dtype=torch.int32, device=dev), num_seqs=T, num_tokens=T, max_kv_len=1,
                       all_decode=True, q_starts=torch.arange(T + 1, dtype=torch.int32, device=dev),
                       seq_lens=torch.ones(T, dtype=torch.int32, device=dev))
         outs.append(dec.forward(b).float())
-    assert torch.equal(outs[0], outs[1])
+    _close(outs[0], outs[1], 2e-2)
