@@ -108,7 +108,9 @@ def cmd_serve(args) -> int:
             return 0
     serve(eng, tok, args.host, args.port, args.model_name or os.path.basename(args.model), args.api_key, args.log_level,
           tool_parser=args.tool_parser, reasoning_parser=args.reasoning_parser,
-          response_cache_entries=args.response_cache_entries, otlp_endpoint=args.otlp_endpoint, controller=controller)
+          response_cache_entries=args.response_cache_entries, otlp_endpoint=args.otlp_endpoint, controller=controller,
+          cors_origins=args.cors_origin, rate_limit_rps=args.rate_limit, ssl_certfile=args.ssl_certfile,
+          ssl_keyfile=args.ssl_keyfile)
     return 0
 
 
@@ -236,6 +238,10 @@ def main(argv: Optional[List[str]] = None) -> int:
     s.add_argument("--tool-parser", default=None, choices=["hermes", "llama3_json", "mistral"])
     s.add_argument("--reasoning-parser", default=None, choices=["think", "think_open"])
     s.add_argument("--response-cache-entries", type=int, default=256, help="0 disables the response cache")
+    s.add_argument("--cors-origin", action="append", default=None, help="allowed CORS origin (repeatable; '*' allows all)")
+    s.add_argument("--rate-limit", type=float, default=0.0, help="requests per second per API key / client address (0 = off)")
+    s.add_argument("--ssl-certfile", default=None)
+    s.add_argument("--ssl-keyfile", default=None)
     s.add_argument("--control-timeout", type=float, default=float(os.environ.get("FLLM_CONTROL_TIMEOUT", "30")),
                    help="seconds a rank waits for the step-control message of a multi-rank server before it gives up")
     s.add_argument("--otlp-endpoint", default=os.environ.get("OTEL_EXPORTER_OTLP_ENDPOINT"),

@@ -38,6 +38,11 @@ __device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
 
 template <int VEC_ITERS>
 __global__ void __launch_bounds__(256) tp_reduce_norm_ag_kernel(const TpNormArgs a) {
+  // Programmatic dependent launch: the next GEMM may start its prologue (and request its first weight tiles)
+  // now; this kernel itself may have started before its predecessor finished, so everything an earlier kernel
+  // of this stream wrote (the residual, the local rank's own partial rows, the counters) is read after the wait.
+  pdl_launch_dependents();
+  pdl_wait();
   const int my_rows = a.bcast ? a.tokens : tp_rows_owned(a.tokens, a.rows_per, a.my_rank);
   const int row = blockIdx.x;                         // local row index
   __shared__ float red[8];
@@ -178,11 +183,11 @@ void tp_reduce_norm_allgather(const TpNormArgs& a, cudaStream_t s) {
   const int grid = std::max(my_rows, 1);              // a rank without rows still does the bookkeeping
   const int iters = (a.hidden / 8 + 255) / 256;
   switch (iters) {
-    case 1: tp_reduce_norm_ag_kernel<1><<<grid, 256, 0, s>>>(a); break;
-    case 2: tp_reduce_norm_ag_kernel<2><<<grid, 256, 0, s>>>(a); break;
-    case 3: tp_reduce_norm_ag_kernel<3><<<grid, 256, 0, s>>>(a); break;
-    case 4: tp_reduce_norm_ag_kernel<4><<<grid, 256, 0, s>>>(a); break;
-    default: tp_reduce_norm_ag_kernel<8><<<grid, 256, 0, s>>>(a); break;
+    case 1: launch_pdl(tp_reduce_norm_ag_kernel<1>, dim3(grid), dim3(256), 0, s, a); break;
+    case 2: launch_pdl(tp_reduce_norm_ag_kernel<2>, dim3(grid), dim3(256), 0, s, a); break;
+    case 3: launch_pdl(tp_reduce_norm_ag_kernel<3>, dim3(grid), dim3(256), 0, s, a); break;
+    case 4: launch_pdl(tp_reduce_norm_ag_kernel<4>, dim3(grid), dim3(256), 0, s, a); break;
+    default: launch_pdl(tp_reduce_norm_ag_kernel<8>, dim3(grid), dim3(256), 0, s, a); break;
   }
   cuda_check(cudaGetLastError(), "tp_reduce_norm_ag_kernel");
 }

@@ -295,7 +295,8 @@ class StopChecker:
 def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Optional[str] = None,
                tool_parser: Optional[str] = None, reasoning_parser: Optional[str] = None,
                response_cache_entries: int = 256, response_cache_ttl_s: float = 600.0,
-               otlp_endpoint: Optional[str] = None, controller=None) -> FastAPI:
+               otlp_endpoint: Optional[str] = None, controller=None, cors_origins: Optional[List[str]] = None,
+               rate_limit_rps: float = 0.0) -> FastAPI:
     """controller: a runtime.step_control.StepController when this process fronts a multi-rank model instance
     (``serve --tp N`` on rank 0): every admission, abort and step is announced to the other ranks."""
     from .cache import ResponseCache, request_key
@@ -1004,11 +1005,22 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
     async def sglang_server_info():
         return {"version": __version__, "max_total_num_tokens": engine.blocks.num_blocks * engine.block_size}
 
+    # Responses / Files / Batches, rerank / score / pooling / classify, infill, Ollama model management, CORS, rate limit
+    from types import SimpleNamespace
+    from . import extra_routes
+    extra_routes.register(app, SimpleNamespace(
+        engine=engine, worker=worker, tokenizer=tokenizer, model_name=model_name, started=started, generate=generate,
+        collect=collect, embed_one=embed_one, encode_prompt=encode_prompt, chat_prompt=chat_prompt,
+        sampling_from=_sampling_from, attach_guided=attach_guided, shape_message=shape_message, usage=usage, sse=sse))
+    extra_routes.install_middleware(app, cors_origins, rate_limit_rps)
     return app
 
 
 def serve(engine, tokenizer, host: str = "127.0.0.1", port: int = 8000, model_name: str = "fllm-b200",
-          api_key: Optional[str] = None, log_level: str = "info", **app_options) -> None:
+          api_key: Optional[str] = None, log_level: str = "info", ssl_certfile: Optional[str] = None,
+          ssl_keyfile: Optional[str] = None, **app_options) -> None:
+    """ssl_certfile / ssl_keyfile: serve HTTPS (the reference's server/tls.rs)."""
     import uvicorn
+    tls = {"ssl_certfile": ssl_certfile, "ssl_keyfile": ssl_keyfile} if ssl_certfile and ssl_keyfile else {}
     uvicorn.run(create_app(engine, tokenizer, model_name, api_key, **app_options), host=host, port=port,
-                log_level=log_level)
+                log_level=log_level, **tls)
