@@ -61,6 +61,8 @@ def build_engine(args):
     par = ParallelConfig(tp=args.tp, pp=args.pp, expert_parallel=args.expert_parallel, ep_dispatch=args.ep_dispatch,
                          distributed_backend=args.distributed_backend)
     weights, tok_path = None, args.tokenizer
+    from . import hub
+    args.model = hub.resolve(args.model)          # a path, a store entry, an alias that was pulled, or a preset name
     if args.model.endswith(".gguf") or os.path.isdir(args.model):
         from .formats.loader import load_model
         cfg, weights, embedded_tok = load_model(args.model, device)
@@ -176,26 +178,117 @@ def cmd_inspect(args) -> int:
 
 def cmd_quantize(args) -> int:
     """Re-quantise the 2-D tensors of a GGUF file to another packed type."""
-    import numpy as np
-    from .formats import quant
-    from .formats.gguf import TYPE_ID, GgufReader, GgufWriter
-    r = GgufReader(args.input)
-    w = GgufWriter(args.output)
-    for k, v in r.metadata.items():
-        if k != "general.alignment":
-            w.add(k, v if not isinstance(v, np.generic) else v.item())
-    target = TYPE_ID[args.type.upper()]
-    qt = {"Q4_K": quant.Q4_K, "Q5_K": quant.Q5_K, "Q6_K": quant.Q6_K, "Q8_0": quant.Q8_0, "Q4_0": quant.Q4_0,
-          "F16": quant.F16, "BF16": quant.BF16, "MXFP4": quant.MXFP4}[args.type.upper()]
-    for t in r.tensors.values():
-        bs = quant._lib().fllm_block_size(qt)
-        if len(t.shape) == 2 and t.shape[-1] % bs == 0 and "norm" not in t.name:
-            x = r.tensor_f32(t.name)
-            w.add_tensor(t.name, t.shape, target, quant.quantize(x, qt))
+    from .formats.convert import quantize_gguf
+    print(json.dumps(quantize_gguf(args.input, args.output, args.type)))
+    return 0
+
+
+def cmd_convert(args) -> int:
+    """Hugging Face checkpoint directory -> GGUF (optionally quantised)."""
+    from .formats.convert import convert_checkpoint
+    from . import hub
+    print(json.dumps(convert_checkpoint(hub.resolve(args.input), args.output, args.type)))
+    return 0
+
+
+def cmd_gguf_tool(args) -> int:
+    from .formats import convert as C
+    if args.cmd == "gguf-set":
+        edits = {}
+        for kv in args.set or []:
+            k, _, v = kv.partition("=")
+            try:
+                edits[k] = json.loads(v)
+            except json.JSONDecodeError:
+                edits[k] = v
+        print(json.dumps(C.gguf_set(args.input, args.output, edits, args.remove or [])))
+    elif args.cmd == "gguf-split":
+        print(json.dumps(C.gguf_split(args.input, args.output_prefix, args.max_tensors)))
+    elif args.cmd == "gguf-merge":
+        print(json.dumps(C.gguf_merge(args.first_shard, args.output)))
+    else:
+        print(json.dumps(C.merge_lora_gguf(args.base, args.lora, args.output, args.type)))
+    return 0
+
+
+def cmd_store(args) -> int:
+    """pull / list / rm / show on the local model store."""
+    from . import hub
+    try:
+        if args.cmd == "pull":
+            print(json.dumps(hub.pull(args.ref, args.name, args.link)))
+        elif args.cmd == "list":
+            for e in hub.list_models():
+                print(f"{e['name']:40s} {e['bytes'] / 2 ** 30:8.2f} GiB  {e['source']}")
+            if args.catalog:
+                for k, v in sorted(hub.catalog().items()):
+                    print(f"alias {k:34s} -> {v}")
+        elif args.cmd == "rm":
+            if not hub.remove(args.name):
+                print(f"no model {args.name!r} in the store", file=sys.stderr)
+                return 1
         else:
-            w.add_tensor(t.name, t.shape, t.ggml_type, np.array(r.tensor_bytes(t.name)))
-    w.write()
-    print(f"wrote {args.output}")
+            print(json.dumps(hub.show(args.name), indent=1))
+    except hub.HubError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 1
+    return 0
+
+
+def cmd_ppl(args) -> int:
+    """Perplexity of a text file: the file is tokenised, cut into windows of --ctx tokens, each window scored."""
+    import math
+    eng, tok = build_engine(args)
+    text = open(args.file, encoding="utf-8", errors="replace").read()
+    ids = tok.encode(text, add_bos=True)
+    win = min(args.window or eng.cfg.max_model_len, eng.cfg.max_model_len)
+    total, count = 0.0, 0
+    for off in range(0, max(len(ids) - 1, 1), win):
+        chunk = ids[off: off + win]
+        if len(chunk) < 2:
+            break
+        lp = eng.score_tokens(chunk)
+        total += -sum(lp)
+        count += len(lp)
+        print(f"[{off + len(chunk)}/{len(ids)}] ppl so far {math.exp(total / max(count, 1)):.4f}", file=sys.stderr, flush=True)
+    print(json.dumps({"tokens": count, "nll": total / max(count, 1), "perplexity": math.exp(total / max(count, 1))}))
+    return 0
+
+
+def cmd_chat(args) -> int:
+    """Interactive chat in the terminal (line input; /reset clears the history, /quit leaves)."""
+    from .runtime import SamplingParams
+    from .tokenizer import render_chat
+    eng, tok = build_engine(args)
+    history: list = [{"role": "system", "content": args.system}] if args.system else []
+    sp = SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature, top_p=args.top_p, top_k=args.top_k)
+    while True:
+        try:
+            line = input("> ")
+        except EOFError:
+            break
+        if line.strip() in ("/quit", "/exit"):
+            break
+        if line.strip() == "/reset":
+            history = history[:1] if args.system else []
+            continue
+        if not line.strip():
+            continue
+        history.append({"role": "user", "content": line})
+        ids = tok.encode(render_chat(getattr(tok, "chat_template", None), history), add_bos=True)
+        rid = eng.add_request(ids, sp)
+        out: list = []
+        shown = 0
+        while eng.has_unfinished():
+            for ev in eng.step():
+                if ev.request_id == rid:
+                    out.extend(t for t in ev.token_ids if t != getattr(tok, "eos_token_id", None))
+                    text = tok.decode(out)
+                    if not text.endswith("\ufffd"):
+                        print(text[shown:], end="", flush=True)
+                        shown = len(text)
+        print()
+        history.append({"role": "assistant", "content": tok.decode(out)})
     return 0
 
 
@@ -287,6 +380,44 @@ def main(argv: Optional[List[str]] = None) -> int:
     q.add_argument("output")
     q.add_argument("type")
     q.set_defaults(fn=cmd_quantize)
+    cv = sub.add_parser("convert", help="Hugging Face checkpoint -> GGUF")
+    cv.add_argument("input")
+    cv.add_argument("output")
+    cv.add_argument("--type", default="F16")
+    cv.set_defaults(fn=cmd_convert)
+    gs = sub.add_parser("gguf-set", help="copy a GGUF with metadata keys changed")
+    gs.add_argument("input"); gs.add_argument("output")
+    gs.add_argument("--set", action="append", metavar="KEY=JSON")
+    gs.add_argument("--remove", action="append", metavar="KEY")
+    gs.set_defaults(fn=cmd_gguf_tool)
+    gsp = sub.add_parser("gguf-split")
+    gsp.add_argument("input"); gsp.add_argument("output_prefix"); gsp.add_argument("--max-tensors", type=int, default=128)
+    gsp.set_defaults(fn=cmd_gguf_tool)
+    gm = sub.add_parser("gguf-merge")
+    gm.add_argument("first_shard"); gm.add_argument("output")
+    gm.set_defaults(fn=cmd_gguf_tool)
+    ml = sub.add_parser("merge-lora", help="bake a PEFT LoRA into a GGUF")
+    ml.add_argument("base"); ml.add_argument("lora"); ml.add_argument("output"); ml.add_argument("--type", default=None)
+    ml.set_defaults(fn=cmd_gguf_tool)
+    pl = sub.add_parser("pull", help="add a model to the local store (path or hf://org/name[@rev][:file])")
+    pl.add_argument("ref"); pl.add_argument("--name", default=None); pl.add_argument("--link", action="store_true")
+    pl.set_defaults(fn=cmd_store)
+    ls = sub.add_parser("list"); ls.add_argument("--catalog", action="store_true"); ls.set_defaults(fn=cmd_store)
+    rm = sub.add_parser("rm"); rm.add_argument("name"); rm.set_defaults(fn=cmd_store)
+    sh = sub.add_parser("show"); sh.add_argument("name"); sh.set_defaults(fn=cmd_store)
+    pp = sub.add_parser("ppl", help="perplexity of a text file")
+    _add_engine_flags(pp)
+    pp.add_argument("--file", required=True)
+    pp.add_argument("--window", type=int, default=0)
+    pp.set_defaults(fn=cmd_ppl)
+    ch = sub.add_parser("chat", help="interactive chat in the terminal")
+    _add_engine_flags(ch)
+    ch.add_argument("--system", default=None)
+    ch.add_argument("--max-tokens", type=int, default=512)
+    ch.add_argument("--temperature", type=float, default=0.7)
+    ch.add_argument("--top-p", type=float, default=0.95)
+    ch.add_argument("--top-k", type=int, default=0)
+    ch.set_defaults(fn=cmd_chat)
     t = sub.add_parser("make-tiny-model")
     t.add_argument("output")
     t.add_argument("--seed", type=int, default=0)

@@ -123,9 +123,9 @@ uint8_t fllm_fp32_to_e2m1(float f) {
 int fllm_block_size(int type) {
   switch (type) {
     case FLLM_F32: case FLLM_F16: case FLLM_BF16: case FLLM_FP8_E4M3: return 1;
-    case FLLM_Q4_0: case FLLM_Q8_0: case FLLM_MXFP4: return 32;
+    case FLLM_Q4_0: case FLLM_Q4_1: case FLLM_Q5_0: case FLLM_Q5_1: case FLLM_Q8_0: case FLLM_IQ4_NL: case FLLM_MXFP4: return 32;
     case FLLM_NVFP4: return 16;
-    case FLLM_Q4_K: case FLLM_Q5_K: case FLLM_Q6_K: case FLLM_Q8_K: return 256;
+    case FLLM_Q2_K: case FLLM_Q3_K: case FLLM_Q4_K: case FLLM_Q5_K: case FLLM_Q6_K: case FLLM_Q8_K: case FLLM_IQ4_XS: return 256;
     default: return 0;
   }
 }
@@ -136,6 +136,13 @@ int fllm_block_bytes(int type) {
     case FLLM_F16: case FLLM_BF16: return 2;
     case FLLM_FP8_E4M3: return 1;
     case FLLM_Q4_0: return 18;
+    case FLLM_Q4_1: return 20;
+    case FLLM_Q5_0: return 22;
+    case FLLM_Q5_1: return 24;
+    case FLLM_Q2_K: return 84;
+    case FLLM_Q3_K: return 110;
+    case FLLM_IQ4_NL: return 18;
+    case FLLM_IQ4_XS: return 136;
     case FLLM_Q8_0: return 34;
     case FLLM_MXFP4: return 17;
     case FLLM_NVFP4: return 9;
@@ -505,6 +512,190 @@ float dot_q6_K_q8_K(const BlockQ6K* w, const BlockQ8K* a, int64_t nblocks) {
   return acc;
 }
 
+
+// ---------------------------------------------------------------------------- further GGML block types
+// The non-linear 4-bit code book of IQ4_NL / IQ4_XS (part of the file format).
+static const int8_t kIq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+static inline int nearest_code_iq4(float v) {          // index of the closest code-book entry
+  int best = 0;
+  float bd = fabsf(v - kIq4nl[0]);
+  for (int i = 1; i < 16; ++i) {
+    const float d = fabsf(v - kIq4nl[i]);
+    if (d < bd) { bd = d; best = i; }
+  }
+  return best;
+}
+
+// min / max affine fit of n values onto codes 0..nmax: x ~ d * q + m
+static inline void affine_fit(const float* x, int n, int nmax, float* d, float* m) {
+  float lo = x[0], hi = x[0];
+  for (int i = 1; i < n; ++i) { lo = std::min(lo, x[i]); hi = std::max(hi, x[i]); }
+  *m = lo;
+  *d = (hi - lo) / (float)nmax;
+}
+
+static void dequantize_block_q2k(const BlockQ2K* b, float* y) {
+  const float d = fllm_fp16_to_fp32(b->d), dmin = fllm_fp16_to_fp32(b->dmin);
+  const uint8_t* q = b->qs;
+  int is = 0;
+  for (int n = 0; n < QK_K; n += 128) {
+    for (int shift = 0; shift < 8; shift += 2) {
+      for (int half = 0; half < 2; ++half) {
+        const uint8_t sc = b->scales[is++];
+        const float dl = d * (sc & 0xF), ml = dmin * (sc >> 4);
+        for (int l = 0; l < 16; ++l) *y++ = dl * ((q[l + 16 * half] >> shift) & 3) - ml;
+      }
+    }
+    q += 32;
+  }
+}
+
+// 16 sub-blocks of 16 values: 2-bit codes with a 4-bit scale and a 4-bit minimum per sub-block
+static void quantize_block_q2k(const float* x, BlockQ2K* b) {
+  float sd[16], sm[16], maxd = 0.f, maxm = 0.f;
+  for (int j = 0; j < 16; ++j) {
+    float d, m;
+    affine_fit(x + 16 * j, 16, 3, &d, &m);
+    if (m > 0.f) { d = (m + 3.f * d) / 3.f; m = 0.f; }      // the format only stores minima <= 0 (as -min >= 0)
+    sd[j] = d; sm[j] = -m;
+    maxd = std::max(maxd, d); maxm = std::max(maxm, -m);
+  }
+  const float dd = maxd / 15.f, dm = maxm / 15.f;
+  b->d = fllm_fp32_to_fp16(dd);
+  b->dmin = fllm_fp32_to_fp16(dm);
+  const float ddr = fllm_fp16_to_fp32(b->d), dmr = fllm_fp16_to_fp32(b->dmin);
+  uint8_t L[QK_K];
+  for (int j = 0; j < 16; ++j) {
+    const int ls = ddr > 0 ? std::min(15, nearest_int(sd[j] / ddr)) : 0;
+    const int lm = dmr > 0 ? std::min(15, nearest_int(sm[j] / dmr)) : 0;
+    b->scales[j] = (uint8_t)(ls | (lm << 4));
+    const float dl = ddr * ls, ml = dmr * lm;
+    for (int i = 0; i < 16; ++i) {
+      const int q = dl > 0 ? nearest_int((x[16 * j + i] + ml) / dl) : 0;
+      L[16 * j + i] = (uint8_t)std::max(0, std::min(3, q));
+    }
+  }
+  for (int n = 0; n < QK_K; n += 128)
+    for (int l = 0; l < 32; ++l)
+      b->qs[n / 4 + l] = L[n + l] | (L[n + l + 32] << 2) | (L[n + l + 64] << 4) | (L[n + l + 96] << 6);
+}
+
+// Q3_K: 3-bit codes (2 low bits in qs, the third bit in hmask, value = code - 4), sixteen 6-bit scales (offset 32)
+static void unpack_scales_q3k(const uint8_t* s12, int8_t* sc16) {
+  for (int j = 0; j < 16; ++j) {
+    const int lo = j < 8 ? (s12[j] & 0xF) : (s12[j - 8] >> 4);
+    const int hi = (s12[8 + (j & 3)] >> (2 * (j >> 2))) & 3;
+    sc16[j] = (int8_t)((lo | (hi << 4)) - 32);
+  }
+}
+
+static void dequantize_block_q3k(const BlockQ3K* b, float* y) {
+  const float d_all = fllm_fp16_to_fp32(b->d);
+  int8_t sc[16];
+  unpack_scales_q3k(b->scales, sc);
+  const uint8_t* q = b->qs;
+  const uint8_t* hm = b->hmask;
+  uint8_t m = 1;
+  int is = 0;
+  for (int n = 0; n < QK_K; n += 128) {
+    for (int shift = 0; shift < 8; shift += 2) {
+      for (int half = 0; half < 2; ++half) {
+        const float dl = d_all * sc[is++];
+        for (int l = 0; l < 16; ++l) {
+          const int idx = l + 16 * half;
+          *y++ = dl * ((int)((q[idx] >> shift) & 3) - ((hm[idx] & m) ? 0 : 4));
+        }
+      }
+      m <<= 1;
+    }
+    q += 32;
+  }
+}
+
+static void quantize_block_q3k(const float* x, BlockQ3K* b) {
+  float sd[16], amax_s = 0.f;
+  for (int j = 0; j < 16; ++j) {
+    float amax = 0.f, mx = 0.f;
+    for (int i = 0; i < 16; ++i)
+      if (fabsf(x[16 * j + i]) > amax) { amax = fabsf(x[16 * j + i]); mx = x[16 * j + i]; }
+    sd[j] = mx / -4.f;                                     // the extreme value maps to code -4
+    amax_s = std::max(amax_s, fabsf(sd[j]));
+  }
+  const float dd = amax_s / 31.f;
+  b->d = fllm_fp32_to_fp16(dd);
+  const float ddr = fllm_fp16_to_fp32(b->d);
+  int ls[16];
+  memset(b->scales, 0, 12);
+  memset(b->hmask, 0, 32);
+  uint8_t L[QK_K];
+  for (int j = 0; j < 16; ++j) {
+    ls[j] = ddr > 0 ? std::max(-32, std::min(31, nearest_int(sd[j] / ddr))) : 0;
+    const int u = ls[j] + 32;
+    if (j < 8) b->scales[j] |= (u & 0xF); else b->scales[j - 8] |= ((u & 0xF) << 4);
+    b->scales[8 + (j & 3)] |= ((u >> 4) << (2 * (j >> 2)));
+    const float dl = ddr * ls[j];
+    for (int i = 0; i < 16; ++i) {
+      const int q = dl != 0.f ? nearest_int(x[16 * j + i] / dl) : 0;
+      L[16 * j + i] = (uint8_t)(std::max(-4, std::min(3, q)) + 4);      // 0..7
+    }
+  }
+  uint8_t m = 1;
+  int pos = 0;
+  for (int n = 0; n < QK_K; n += 128) {
+    for (int k = 0; k < 4; ++k) {
+      for (int l = 0; l < 32; ++l) {
+        const int v = L[n + 32 * k + l];
+        if (v > 3) b->hmask[l] |= m;
+      }
+      m <<= 1;
+    }
+    for (int l = 0; l < 32; ++l)
+      b->qs[pos + l] = (L[n + l] & 3) | ((L[n + l + 32] & 3) << 2) | ((L[n + l + 64] & 3) << 4) | ((L[n + l + 96] & 3) << 6);
+    pos += 32;
+  }
+}
+
+static void dequantize_block_iq4xs(const BlockIQ4XS* b, float* y) {
+  const float d = fllm_fp16_to_fp32(b->d);
+  const uint8_t* qs = b->qs;
+  for (int ib = 0; ib < QK_K / 32; ++ib) {
+    const int ls = ((b->scales_l[ib / 2] >> (4 * (ib % 2))) & 0xF) | (((b->scales_h >> (2 * ib)) & 3) << 4);
+    const float dl = d * (ls - 32);
+    for (int j = 0; j < 16; ++j) {
+      y[j] = dl * kIq4nl[qs[j] & 0xF];
+      y[j + 16] = dl * kIq4nl[qs[j] >> 4];
+    }
+    y += 32;
+    qs += 16;
+  }
+}
+
+static void quantize_block_iq4xs(const float* x, BlockIQ4XS* b) {
+  float sd[8], amax_s = 0.f;
+  for (int ib = 0; ib < 8; ++ib) {
+    float amax = 0.f, mx = 0.f;
+    for (int i = 0; i < 32; ++i)
+      if (fabsf(x[32 * ib + i]) > amax) { amax = fabsf(x[32 * ib + i]); mx = x[32 * ib + i]; }
+    sd[ib] = mx / -127.f;
+    amax_s = std::max(amax_s, fabsf(sd[ib]));
+  }
+  const float dd = amax_s / 31.f;
+  b->d = fllm_fp32_to_fp16(dd);
+  const float ddr = fllm_fp16_to_fp32(b->d);
+  b->scales_h = 0;
+  memset(b->scales_l, 0, 4);
+  for (int ib = 0; ib < 8; ++ib) {
+    const int ls = ddr > 0 ? std::max(-32, std::min(31, nearest_int(sd[ib] / ddr))) : 0;
+    const int u = ls + 32;
+    b->scales_l[ib / 2] |= (uint8_t)((u & 0xF) << (4 * (ib % 2)));
+    b->scales_h |= (uint16_t)((u >> 4) << (2 * ib));
+    const float dl = ddr * ls, id = dl != 0.f ? 1.f / dl : 0.f;
+    for (int j = 0; j < 16; ++j)
+      b->qs[16 * ib + j] = (uint8_t)(nearest_code_iq4(x[32 * ib + j] * id) | (nearest_code_iq4(x[32 * ib + 16 + j] * id) << 4));
+  }
+}
+
 // ---------------------------------------------------------------------------- row codecs
 static void quantize_row(int type, const float* x, uint8_t* out, int64_t n) {
   switch (type) {
@@ -567,6 +758,74 @@ static void quantize_row(int type, const float* x, uint8_t* out, int64_t n) {
         }
       }
     } break;
+    case FLLM_Q4_1: {
+      auto* y = (BlockQ4_1*)out;
+      for (int64_t b = 0; b < n / 32; ++b) {
+        float d, m;
+        affine_fit(x + 32 * b, 32, 15, &d, &m);
+        y[b].d = fllm_fp32_to_fp16(d);
+        y[b].m = fllm_fp32_to_fp16(m);
+        const float id = d ? 1.f / d : 0.f;
+        for (int i = 0; i < 16; ++i) {
+          const int a = std::max(0, std::min(15, nearest_int((x[32 * b + i] - m) * id)));
+          const int c = std::max(0, std::min(15, nearest_int((x[32 * b + 16 + i] - m) * id)));
+          y[b].qs[i] = (uint8_t)(a | (c << 4));
+        }
+      }
+    } break;
+    case FLLM_Q5_0: {
+      auto* y = (BlockQ5_0*)out;
+      for (int64_t b = 0; b < n / 32; ++b) {
+        float amax = 0, mx = 0;
+        for (int i = 0; i < 32; ++i)
+          if (fabsf(x[32 * b + i]) > amax) { amax = fabsf(x[32 * b + i]); mx = x[32 * b + i]; }
+        const float d = mx / -16.f, id = d ? 1.f / d : 0.f;
+        y[b].d = fllm_fp32_to_fp16(d);
+        uint32_t qh = 0;
+        for (int i = 0; i < 16; ++i) {
+          const int a = std::min(31, (int)(x[32 * b + i] * id + 16.5f));
+          const int c = std::min(31, (int)(x[32 * b + 16 + i] * id + 16.5f));
+          y[b].qs[i] = (uint8_t)((a & 0xF) | ((c & 0xF) << 4));
+          qh |= (uint32_t)((a & 0x10) >> 4) << i;
+          qh |= (uint32_t)((c & 0x10) >> 4) << (i + 16);
+        }
+        memcpy(y[b].qh, &qh, 4);
+      }
+    } break;
+    case FLLM_Q5_1: {
+      auto* y = (BlockQ5_1*)out;
+      for (int64_t b = 0; b < n / 32; ++b) {
+        float d, m;
+        affine_fit(x + 32 * b, 32, 31, &d, &m);
+        y[b].d = fllm_fp32_to_fp16(d);
+        y[b].m = fllm_fp32_to_fp16(m);
+        const float id = d ? 1.f / d : 0.f;
+        uint32_t qh = 0;
+        for (int i = 0; i < 16; ++i) {
+          const int a = std::max(0, std::min(31, nearest_int((x[32 * b + i] - m) * id)));
+          const int c = std::max(0, std::min(31, nearest_int((x[32 * b + 16 + i] - m) * id)));
+          y[b].qs[i] = (uint8_t)((a & 0xF) | ((c & 0xF) << 4));
+          qh |= (uint32_t)((a & 0x10) >> 4) << i;
+          qh |= (uint32_t)((c & 0x10) >> 4) << (i + 16);
+        }
+        memcpy(y[b].qh, &qh, 4);
+      }
+    } break;
+    case FLLM_IQ4_NL: {
+      auto* y = (BlockIQ4NL*)out;
+      for (int64_t b = 0; b < n / 32; ++b) {
+        float amax = 0, mx = 0;
+        for (int i = 0; i < 32; ++i)
+          if (fabsf(x[32 * b + i]) > amax) { amax = fabsf(x[32 * b + i]); mx = x[32 * b + i]; }
+        const float d = mx / -127.f, id = d ? 1.f / d : 0.f;
+        y[b].d = fllm_fp32_to_fp16(d);
+        for (int i = 0; i < 16; ++i)
+          y[b].qs[i] = (uint8_t)(nearest_code_iq4(x[32 * b + i] * id) | (nearest_code_iq4(x[32 * b + 16 + i] * id) << 4));
+      }
+    } break;
+    case FLLM_Q2_K: for (int64_t b = 0; b < n / QK_K; ++b) quantize_block_q2k(x + b * QK_K, (BlockQ2K*)out + b); break;
+    case FLLM_Q3_K: for (int64_t b = 0; b < n / QK_K; ++b) quantize_block_q3k(x + b * QK_K, (BlockQ3K*)out + b); break;
+    case FLLM_IQ4_XS: for (int64_t b = 0; b < n / QK_K; ++b) quantize_block_iq4xs(x + b * QK_K, (BlockIQ4XS*)out + b); break;
     case FLLM_Q4_K: for (int64_t b = 0; b < n / QK_K; ++b) quantize_block_q4k(x + b * QK_K, (BlockQ4K*)out + b); break;
     case FLLM_Q5_K: for (int64_t b = 0; b < n / QK_K; ++b) quantize_block_q5k(x + b * QK_K, (BlockQ5K*)out + b); break;
     case FLLM_Q6_K: for (int64_t b = 0; b < n / QK_K; ++b) quantize_block_q6k(x + b * QK_K, (BlockQ6K*)out + b); break;
@@ -617,6 +876,50 @@ static void dequantize_row(int type, const uint8_t* in, float* y, int64_t n) {
         }
       }
     } break;
+    case FLLM_Q4_1: {
+      auto* b = (const BlockQ4_1*)in;
+      for (int64_t k = 0; k < n / 32; ++k) {
+        const float d = fllm_fp16_to_fp32(b[k].d), m = fllm_fp16_to_fp32(b[k].m);
+        for (int i = 0; i < 16; ++i) {
+          y[32 * k + i] = d * (b[k].qs[i] & 0xF) + m;
+          y[32 * k + 16 + i] = d * (b[k].qs[i] >> 4) + m;
+        }
+      }
+    } break;
+    case FLLM_Q5_0: case FLLM_Q5_1: {
+      for (int64_t k = 0; k < n / 32; ++k) {
+        float d, m = 0.f;
+        const uint8_t *qs, *qhp;
+        if (type == FLLM_Q5_0) {
+          auto* b = (const BlockQ5_0*)in + k;
+          d = fllm_fp16_to_fp32(b->d); qs = b->qs; qhp = b->qh;
+        } else {
+          auto* b = (const BlockQ5_1*)in + k;
+          d = fllm_fp16_to_fp32(b->d); m = fllm_fp16_to_fp32(b->m); qs = b->qs; qhp = b->qh;
+        }
+        uint32_t qh;
+        memcpy(&qh, qhp, 4);
+        for (int i = 0; i < 16; ++i) {
+          const int a = (qs[i] & 0xF) | (((qh >> i) & 1) << 4);
+          const int c = (qs[i] >> 4) | (((qh >> (i + 16)) & 1) << 4);
+          y[32 * k + i] = type == FLLM_Q5_0 ? d * (a - 16) : d * a + m;
+          y[32 * k + 16 + i] = type == FLLM_Q5_0 ? d * (c - 16) : d * c + m;
+        }
+      }
+    } break;
+    case FLLM_IQ4_NL: {
+      auto* b = (const BlockIQ4NL*)in;
+      for (int64_t k = 0; k < n / 32; ++k) {
+        const float d = fllm_fp16_to_fp32(b[k].d);
+        for (int i = 0; i < 16; ++i) {
+          y[32 * k + i] = d * kIq4nl[b[k].qs[i] & 0xF];
+          y[32 * k + 16 + i] = d * kIq4nl[b[k].qs[i] >> 4];
+        }
+      }
+    } break;
+    case FLLM_Q2_K: for (int64_t b = 0; b < n / QK_K; ++b) dequantize_block_q2k((const BlockQ2K*)in + b, y + b * QK_K); break;
+    case FLLM_Q3_K: for (int64_t b = 0; b < n / QK_K; ++b) dequantize_block_q3k((const BlockQ3K*)in + b, y + b * QK_K); break;
+    case FLLM_IQ4_XS: for (int64_t b = 0; b < n / QK_K; ++b) dequantize_block_iq4xs((const BlockIQ4XS*)in + b, y + b * QK_K); break;
     case FLLM_Q4_K: for (int64_t b = 0; b < n / QK_K; ++b) dequantize_block_q4k((const BlockQ4K*)in + b, y + b * QK_K); break;
     case FLLM_Q5_K: for (int64_t b = 0; b < n / QK_K; ++b) dequantize_block_q5k((const BlockQ5K*)in + b, y + b * QK_K); break;
     case FLLM_Q6_K: for (int64_t b = 0; b < n / QK_K; ++b) dequantize_block_q6k((const BlockQ6K*)in + b, y + b * QK_K); break;

@@ -70,6 +70,7 @@ class GgufReader:
         self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
         self._buf = memoryview(self._mm)
         self.metadata: Dict[str, Any] = {}
+        self.value_types: Dict[str, int] = {}
         self.tensors: Dict[str, TensorInfo] = {}
         self._parse()
 
@@ -132,6 +133,8 @@ class GgufReader:
             vt, pos = self._scalar(pos, U32)
             val, pos = self._value(pos, vt)
             self.metadata[key] = val
+            if vt != ARR:
+                self.value_types[key] = vt           # so that a rewrite keeps u32 / i64 / f64 ... as they were
         infos = []
         for _ in range(n_tensors):
             name, pos = self._string(pos)
@@ -168,8 +171,13 @@ class GgufReader:
         return dequantize(self.tensor_bytes(name), t.ggml_type, rows, t.shape[-1]).reshape(t.shape)
 
     def close(self) -> None:
-        self._buf.release()
-        self._mm.close()
+        """Unmap the file. Zero-copy views handed out by ``tensor_bytes`` keep the mapping alive: while one
+        exists the mapping is left to the garbage collector instead."""
+        try:
+            self._buf.release()
+            self._mm.close()
+        except BufferError:
+            pass
         self._f.close()
 
 

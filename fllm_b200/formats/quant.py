@@ -9,6 +9,10 @@ import numpy as np
 from ..ops._lib import load_cpu
 
 F32, F16, Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, Q8_K, BF16, MXFP4 = 0, 1, 2, 8, 12, 13, 14, 15, 30, 39
+Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, IQ4_NL, IQ4_XS = 3, 6, 7, 10, 11, 20, 23
+TYPE_NAMES = {"F32": F32, "F16": F16, "BF16": BF16, "Q4_0": Q4_0, "Q4_1": Q4_1, "Q5_0": Q5_0, "Q5_1": Q5_1, "Q8_0": Q8_0,
+              "Q2_K": Q2_K, "Q3_K": Q3_K, "Q4_K": Q4_K, "Q5_K": Q5_K, "Q6_K": Q6_K, "IQ4_NL": IQ4_NL, "IQ4_XS": IQ4_XS,
+              "MXFP4": MXFP4}
 NVFP4, FP8_E4M3 = 1001, 1002
 _configured = False
 

@@ -697,6 +697,47 @@ class LLMEngine:
             return "length"
         return None
 
+    # ------------------------------------------------------------------ scoring
+    @torch.inference_mode()
+    def score_tokens(self, tokens: Sequence[int]) -> List[float]:
+        """Log-probability of tokens[1:] given their prefixes (natural log): len(tokens) - 1 values. The sequence is
+        fed in chunks of at most ``max_num_batched_tokens`` rows whose logits are all kept (the same batch shape a
+        speculative verification uses); its KV blocks are freed afterwards. Perplexity = exp(-mean(score))
+        (the reference's ``ppl`` sub-command, rust/engine/src/ppl.rs). Single pipeline stage only."""
+        if self.par.pp > 1:
+            raise RuntimeError("score_tokens needs a single pipeline stage")
+        tokens = [int(t) for t in tokens]
+        n = len(tokens)
+        if n < 2:
+            return []
+        if n > self.cfg.max_model_len:
+            raise ValueError(f"{n} tokens exceed max_model_len={self.cfg.max_model_len}")
+        self.drain()
+        req = Request("score-" + str(next(self._req_ids)), next(self._seq_ids), tokens[:1], SamplingParams(max_tokens=1))
+        req.draft = tokens[1:]
+        self.blocks.allocate(req.seq_id, [])
+        out: List[float] = []
+        try:
+            if not self.blocks.ensure_capacity(req.seq_id, n):
+                raise RuntimeError("not enough free KV blocks to score this sequence")
+            step_max = self.cfg.max_num_batched_tokens
+            off = 0
+            while off < n:
+                cnt = min(step_max, n - off)
+                step = ScheduledStep(seqs=[ScheduledSeq(req, off, cnt, True, verify=cnt - 1 if cnt > 1 else 0)])
+                if cnt == 1:                                  # a lone last row: still keep its logits
+                    step.seqs[0].verify = 0
+                batch = self._build_batch(step)
+                logits = self.decoder.full_logits(self.decoder.forward(batch)).float()
+                lp = torch.log_softmax(logits, -1)
+                tgt = torch.tensor(tokens[off + 1: off + cnt + 1], dtype=torch.long, device=lp.device)
+                rows = lp[: tgt.numel()] if cnt > 1 else lp[-1:][: tgt.numel()]
+                out.extend(rows.gather(1, tgt[:, None]).flatten().tolist())
+                off += cnt
+        finally:
+            self.blocks.free_seq(req.seq_id)
+        return out[: n - 1]
+
     # ------------------------------------------------------------------ convenience
     def generate(self, prompts: Iterable[Sequence[int]], params: Optional[SamplingParams] = None) -> List[List[int]]:
         ids = [self.add_request(p, params) for p in prompts]
