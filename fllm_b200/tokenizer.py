@@ -2,8 +2,11 @@
 
 * ``HFTokenizer``    a ``tokenizer.json`` (Hugging Face ``tokenizers``), with the chat template and
                      special tokens of ``tokenizer_config.json`` when present;
-* ``GgufTokenizer``  the vocabulary embedded in a GGUF file (``tokenizer.ggml.*``): byte-level BPE
-                     with merges, or a greedy longest-match over the SentencePiece-style vocabulary;
+* ``GgufTokenizer``  the vocabulary embedded in a GGUF file (``tokenizer.ggml.*``): byte-level BPE with
+                     merges and the model family's pre-tokenizer pattern (``gpt2``), SentencePiece BPE
+                     driven by the piece scores (``llama``), or unigram Viterbi (``t5`` / ``unigram``);
+                     control tokens written in the text (``<|im_start|>``) map to their ids;
+* ``TiktokenTokenizer``  a ``*.tiktoken`` rank file (base64 token, rank per line) with byte-level BPE;
 * ``ByteTokenizer``  bytes + a few specials; lets random-weight models be served and tested.
 
 The reference embeds BPE / SPM / unigram tokenizers and renders chat templates with a Jinja
@@ -94,9 +97,35 @@ def _bytes_to_unicode() -> Dict[int, str]:
     return dict(zip(bs, map(chr, cs)))
 
 
+# pre-tokenizer patterns by ``tokenizer.ggml.pre`` (the families llama.cpp names); anything else uses GPT-2's
+_PRE_GPT2 = r"'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"
+_PRE_LLAMA3 = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|"
+               r"\s+(?!\S)|\s+")
+_PRE_QWEN2 = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|"
+              r"\s+(?!\S)|\s+")
+_PRE_O200K = (r"[^\r\n\p{L}\p{N}]?[\p{Lu}\p{Lt}\p{Lm}\p{Lo}\p{M}]*[\p{Ll}\p{Lm}\p{Lo}\p{M}]+(?i:'s|'t|'re|'ve|'m|'ll|'d)?|"
+              r"[^\r\n\p{L}\p{N}]?[\p{Lu}\p{Lt}\p{Lm}\p{Lo}\p{M}]+[\p{Ll}\p{Lm}\p{Lo}\p{M}]*(?i:'s|'t|'re|'ve|'m|'ll|'d)?|"
+              r"\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n/]*|\s*[\r\n]+|\s+(?!\S)|\s+")
+PRE_PATTERNS = {"default": _PRE_GPT2, "gpt-2": _PRE_GPT2, "llama-bpe": _PRE_LLAMA3, "llama3": _PRE_LLAMA3, "smaug-bpe": _PRE_LLAMA3,
+                "qwen2": _PRE_QWEN2, "deepseek-r1-qwen": _PRE_QWEN2, "gpt-4o": _PRE_O200K, "tekken": _PRE_O200K, "o200k": _PRE_O200K}
+
+
+def _byte_bpe(parts: List[bytes], ranks: Dict[bytes, int]) -> List[bytes]:
+    """Byte-level BPE by rank (lowest rank merges first), as tiktoken files define it."""
+    while len(parts) > 1:
+        best, bi = None, -1
+        for i in range(len(parts) - 1):
+            r = ranks.get(parts[i] + parts[i + 1])
+            if r is not None and (best is None or r < best):
+                best, bi = r, i
+        if best is None:
+            break
+        parts = parts[:bi] + [parts[bi] + parts[bi + 1]] + parts[bi + 2:]
+    return parts
+
+
 class GgufTokenizer:
-    """Vocabulary embedded in a GGUF file. ``gpt2`` models use byte-level BPE with the stored
-    merges; other models use greedy longest-match over the piece table with byte fallback."""
+    """Vocabulary embedded in a GGUF file (rust/engine/src/tokenizer.rs reads the same keys)."""
 
     def __init__(self, metadata: dict):
         self.model = metadata.get("tokenizer.ggml.model", "llama")
@@ -107,13 +136,25 @@ class GgufTokenizer:
         self.index = {t: i for i, t in enumerate(self.tokens)}
         self.bos_token_id = metadata.get("tokenizer.ggml.bos_token_id")
         self.eos_token_id = metadata.get("tokenizer.ggml.eos_token_id")
+        self.unk_token_id = metadata.get("tokenizer.ggml.unknown_token_id", 0)
         self.chat_template = metadata.get("tokenizer.chat_template")
+        self.add_space_prefix = bool(metadata.get("tokenizer.ggml.add_space_prefix", True))
         merges = metadata.get("tokenizer.ggml.merges", [])
         self.ranks = {tuple(m.split(" ", 1)): i for i, m in enumerate(merges)}
+        scores = metadata.get("tokenizer.ggml.scores")
+        self.scores = [float(x) for x in scores] if scores is not None and len(scores) == len(self.tokens) else None
+        types = metadata.get("tokenizer.ggml.token_type")
+        self.types = [int(t) for t in types] if types is not None and len(types) == len(self.tokens) else None
+        # control (3) and user-defined (4) tokens are matched literally in the text before anything else
+        self.special = {t: i for i, t in enumerate(self.tokens)
+                        if self.types is not None and self.types[i] in (3, 4) and len(t) > 1}
+        self.pre = PRE_PATTERNS.get(str(metadata.get("tokenizer.ggml.pre", "default")), _PRE_GPT2)
         self.b2u = _bytes_to_unicode()
         self.u2b = {v: k for k, v in self.b2u.items()}
         self.max_piece = max((len(t) for t in self.tokens), default=1)
+        self._special_re = None
 
+    # ------------------------------------------------------------------ pieces
     def _bpe(self, word: List[str]) -> List[str]:
         while len(word) > 1:
             best, bi = None, -1
@@ -126,22 +167,82 @@ class GgufTokenizer:
             word = word[:bi] + [word[bi] + word[bi + 1]] + word[bi + 2:]
         return word
 
-    def encode(self, text: str, add_bos: bool = False) -> List[int]:
-        ids: List[int] = [self.bos_token_id] if add_bos and self.bos_token_id is not None else []
-        if self.model == "gpt2":
-            import regex
-            pat = regex.compile(r"'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+")
-            for piece in pat.findall(text):
-                word = [self.b2u[b] for b in piece.encode("utf-8")]
-                for tok in self._bpe(word):
-                    if tok in self.index:
-                        ids.append(self.index[tok])
-                    else:
-                        ids.extend(self.index.get(ch, 0) for ch in tok)
-            return ids
-        s = text.replace(" ", "▁")
-        if not s.startswith("▁"):
-            s = "▁" + s
+    def _byte_ids(self, ch: str) -> List[int]:
+        return [self.index.get(f"<0x{b:02X}>", self.unk_token_id) for b in ch.encode("utf-8")]
+
+    def _spm_bpe(self, s: str) -> List[int]:
+        """SentencePiece BPE: start from characters, always merge the adjacent pair whose concatenation is the
+        piece with the highest score (leftmost among equals); characters without a piece fall back to bytes."""
+        import heapq
+        sym = list(s)
+        n = len(sym)
+        prev, nxt = list(range(-1, n - 1)), list(range(1, n + 1))
+        alive = [True] * n
+        heap = []
+
+        def push(i):
+            j = nxt[i]
+            if j >= n:
+                return
+            t = self.index.get(sym[i] + sym[j])
+            if t is not None:
+                heapq.heappush(heap, (-self.scores[t], i, sym[i], sym[j]))
+        for i in range(n - 1):
+            push(i)
+        while heap:
+            _, i, a, b = heapq.heappop(heap)
+            j = nxt[i] if alive[i] else n
+            if not alive[i] or j >= n or not alive[j] or sym[i] != a or sym[j] != b:
+                continue                              # stale entry
+            sym[i] = a + b
+            alive[j] = False
+            nxt[i] = nxt[j]
+            if nxt[j] < n:
+                prev[nxt[j]] = i
+            if prev[i] >= 0:
+                push(prev[i])
+            push(i)
+        ids: List[int] = []
+        i = 0
+        while i < n:
+            if alive[i]:
+                t = self.index.get(sym[i])
+                ids.extend([t] if t is not None else [b for ch in sym[i] for b in self._byte_ids(ch)])
+            i += 1
+        return ids
+
+    def _unigram(self, s: str) -> List[int]:
+        """Viterbi segmentation maximising the sum of the pieces' log-probabilities; unknown characters cost a
+        fixed penalty and become bytes (or <unk>)."""
+        n = len(s)
+        best = [float("-inf")] * (n + 1)
+        back = [(0, -1)] * (n + 1)
+        best[0] = 0.0
+        unk_pen = min(self.scores) - 10.0
+        for i in range(n):
+            if best[i] == float("-inf"):
+                continue
+            for L in range(1, min(self.max_piece, n - i) + 1):
+                t = self.index.get(s[i:i + L])
+                if t is not None and (self.types is None or self.types[t] not in (3,)):
+                    sc = best[i] + self.scores[t]
+                    if sc > best[i + L]:
+                        best[i + L], back[i + L] = sc, (i, t)
+            if best[i] + unk_pen > best[i + 1]:
+                best[i + 1], back[i + 1] = best[i] + unk_pen, (i, -1)
+        out: List[int] = []
+        i = n
+        while i > 0:
+            j, t = back[i]
+            out.append(t if t >= 0 else -(i))           # negative: position of an unknown character (end index)
+            i = j
+        ids: List[int] = []
+        for t in reversed(out):
+            ids.extend([t] if t >= 0 else self._byte_ids(s[-t - 1]))
+        return ids
+
+    def _greedy(self, s: str) -> List[int]:
+        ids: List[int] = []
         i = 0
         while i < len(s):
             for n in range(min(self.max_piece, len(s) - i), 0, -1):
@@ -151,26 +252,102 @@ class GgufTokenizer:
                     i += n
                     break
             else:
-                for b in s[i].encode("utf-8"):
-                    ids.append(self.index.get(f"<0x{b:02X}>", 0))
+                ids.extend(self._byte_ids(s[i]))
                 i += 1
         return ids
 
-    def decode(self, ids: Sequence[int]) -> str:
+    def _encode_plain(self, text: str) -> List[int]:
+        if not text:
+            return []
         if self.model == "gpt2":
-            raw = "".join(self.tokens[i] for i in ids if 0 <= i < self.vocab_size)
+            import regex
+            ids: List[int] = []
+            for piece in regex.findall(self.pre, text):
+                word = [self.b2u[b] for b in piece.encode("utf-8")]
+                for tok in self._bpe(word):
+                    if tok in self.index:
+                        ids.append(self.index[tok])
+                    else:
+                        ids.extend(self.index.get(ch, self.unk_token_id) for ch in tok)
+            return ids
+        s = text.replace(" ", "\u2581")
+        if self.add_space_prefix and not s.startswith("\u2581"):
+            s = "\u2581" + s
+        if self.scores is None:
+            return self._greedy(s)
+        return self._unigram(s) if self.model in ("t5", "unigram") else self._spm_bpe(s)
+
+    # ------------------------------------------------------------------ public
+    def encode(self, text: str, add_bos: bool = False) -> List[int]:
+        ids: List[int] = [self.bos_token_id] if add_bos and self.bos_token_id is not None else []
+        if not self.special:
+            return ids + self._encode_plain(text)
+        if self._special_re is None:
+            import re
+            self._special_re = re.compile("|".join(re.escape(t) for t in sorted(self.special, key=len, reverse=True)))
+        pos = 0
+        for m in self._special_re.finditer(text):
+            ids += self._encode_plain(text[pos:m.start()])
+            ids.append(self.special[m.group(0)])
+            pos = m.end()
+        return ids + self._encode_plain(text[pos:])
+
+    def decode(self, ids: Sequence[int], skip_special: bool = True) -> str:
+        keep = [i for i in ids if 0 <= i < self.vocab_size and
+                not (skip_special and self.types is not None and self.types[i] == 3)]
+        if self.model == "gpt2":
+            raw = "".join(self.tokens[i] for i in keep)
             return bytes(self.u2b.get(ch, 32) for ch in raw).decode("utf-8", errors="replace")
         out = bytearray()
-        for i in ids:
-            if not 0 <= i < self.vocab_size:
-                continue
+        for i in keep:
             t = self.tokens[i]
             if len(t) == 6 and t.startswith("<0x") and t.endswith(">"):
                 out.append(int(t[3:5], 16))
             else:
-                out.extend(t.replace("▁", " ").encode("utf-8"))
+                out.extend(t.replace("\u2581", " ").encode("utf-8"))
         s = out.decode("utf-8", errors="replace")
-        return s[1:] if s.startswith(" ") else s
+        return s[1:] if self.add_space_prefix and s.startswith(" ") else s
+
+
+class TiktokenTokenizer:
+    """A ``*.tiktoken`` vocabulary: one ``base64(token bytes) rank`` pair per line; ids = ranks, special tokens
+    follow the ranks. Encoding is byte-level BPE by rank inside the pieces of a pre-tokenizer pattern."""
+
+    def __init__(self, path: str, pattern: str = _PRE_LLAMA3, special_tokens: Optional[List[str]] = None):
+        import base64
+        self.ranks: Dict[bytes, int] = {}
+        for line in open(path, "rb").read().splitlines():
+            if line.strip():
+                tok, rank = line.split()
+                self.ranks[base64.b64decode(tok)] = int(rank)
+        self.by_id = {v: k for k, v in self.ranks.items()}
+        base = max(self.by_id) + 1 if self.by_id else 0
+        self.special = {t: base + i for i, t in enumerate(special_tokens or ["<|begin_of_text|>", "<|end_of_text|>"])}
+        self.special_by_id = {v: k for k, v in self.special.items()}
+        self.vocab_size = base + len(self.special)
+        self.bos_token_id = self.special.get("<|begin_of_text|>")
+        self.eos_token_id = self.special.get("<|end_of_text|>")
+        self.chat_template = None
+        self.pattern = pattern
+
+    def encode(self, text: str, add_bos: bool = False) -> List[int]:
+        import re
+        import regex
+        ids: List[int] = [self.bos_token_id] if add_bos and self.bos_token_id is not None else []
+        sp = re.compile("|".join(re.escape(t) for t in sorted(self.special, key=len, reverse=True))) if self.special else None
+        pos = 0
+        spans = [(m.start(), m.end(), m.group(0)) for m in sp.finditer(text)] if sp else []
+        for a, b, tok in spans + [(len(text), len(text), None)]:
+            for piece in regex.findall(self.pattern, text[pos:a]):
+                raw = piece.encode("utf-8")
+                ids.extend(self.ranks[p] for p in _byte_bpe([bytes([c]) for c in raw], self.ranks) if p in self.ranks)
+            if tok is not None:
+                ids.append(self.special[tok])
+            pos = b
+        return ids
+
+    def decode(self, ids: Sequence[int]) -> str:
+        return b"".join(self.by_id.get(i, b"") for i in ids).decode("utf-8", errors="replace")
 
 
 def load_tokenizer(path: Optional[str], vocab_size: int):
@@ -182,5 +359,7 @@ def load_tokenizer(path: Optional[str], vocab_size: int):
                 return GgufTokenizer(r.metadata)
             finally:
                 r.close()
+        if path.endswith(".tiktoken"):
+            return TiktokenTokenizer(path)
         return HFTokenizer(path)
     return ByteTokenizer(vocab_size)
