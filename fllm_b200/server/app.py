@@ -494,6 +494,24 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
             except (ValueError, TypeError) as e:
                 raise HTTPException(400, str(e))
             return
+        # general grammars: a regular expression, a GBNF grammar (vLLM's guided_regex / guided_grammar, llama.cpp's
+        # grammar), or response_format {"type": "regex" | "grammar"}
+        rf0 = body.get("response_format") if isinstance(body.get("response_format"), dict) else {}
+        g_regex = body.get("guided_regex") or (rf0.get("pattern") if rf0.get("type") == "regex" else None)
+        g_gbnf = body.get("guided_grammar") or body.get("grammar") or (rf0.get("grammar") if rf0.get("type") == "grammar" else None)
+        if g_regex or g_gbnf:
+            from ..runtime.grammar import TokenTrie
+            from ..runtime.grammar_gbnf import GrammarError, GuidedGrammar, machine_from
+            if "trie" not in guided_shared:
+                guided_shared["trie"] = TokenTrie.from_tokenizer(tokenizer)
+                guided_shared["masks"] = {}
+            eos = [getattr(tokenizer, "eos_token_id", None), getattr(engine, "eos_token_id", None)]
+            try:
+                machine = machine_from("regex", str(g_regex)) if g_regex else machine_from("gbnf", str(g_gbnf))
+            except (GrammarError, ValueError, IndexError) as e:
+                raise HTTPException(400, f"invalid grammar: {e}")
+            sp.guided = GuidedGrammar(guided_shared["trie"], tokenizer, eos, machine)
+            return
         rf = body.get("response_format")
         kind = rf.get("type") if isinstance(rf, dict) else None
         fmt = body.get("format")
@@ -513,6 +531,15 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
             schema = body["guided_json"]
         elif isinstance(fmt, dict):
             schema = fmt
+        if isinstance(schema, dict) and schema:
+            # the whole schema (nested objects, arrays, enums, references ...) as a grammar; schemas that grammar
+            # cannot express fall back to the recogniser that enforces the top-level object only
+            from ..runtime.grammar_gbnf import GrammarError, GuidedGrammar, machine_from
+            try:
+                sp.guided = GuidedGrammar(guided_shared["trie"], tokenizer, eos, machine_from("json_schema", schema))
+                return
+            except (GrammarError, KeyError, TypeError, ValueError, IndexError, RecursionError):
+                pass
         if isinstance(schema, dict) and schema.get("type", "object") == "object" and isinstance(schema.get("properties"), dict):
             try:
                 sp.guided = GuidedJsonSchema(guided_shared["trie"], tokenizer, eos, schema)
