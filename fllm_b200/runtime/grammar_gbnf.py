@@ -283,7 +283,7 @@ def regex_to_gbnf(pattern: str) -> str:
 
 # ----------------------------------------------------------------------------- JSON schema -> GBNF
 _PRIMS = {
-    "ws": '[ \\t\\n\\r]*',
+    "ws": '([ \\t\\n\\r] [ \\t\\n\\r]?)?',          # at most two: unbounded white space lets a sampler stall inside it
     "string": '"\\"" char* "\\""',
     "char": '[^"\\\\\\x00-\\x1f] | "\\\\" (["\\\\/bfnrt] | "u" [0-9a-fA-F] [0-9a-fA-F] [0-9a-fA-F] [0-9a-fA-F])',
     "integer": '"-"? ("0" | [1-9] [0-9]*)',
