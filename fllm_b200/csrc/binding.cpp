@@ -319,33 +319,47 @@ void sample(Tensor logits, const Tensor& params, const optional<Tensor>& pen_ids
 }
 
 void spec_verify_greedy(const Tensor& draft_ids, const Tensor& target_ids,
-                        const optional<Tensor>& n_draft, Tensor n_accept, Tensor out_tokens) {
+                        const optional<Tensor>& n_draft, Tensor n_accept, Tensor out_tokens,
+                        const optional<Tensor>& row_start) {
   check_i32(draft_ids, "draft_ids"); check_i32(target_ids, "target_ids");
   check_i32(n_accept, "n_accept"); check_i32(out_tokens, "out_tokens");
   const int batch = (int)draft_ids.size(0), k = (int)draft_ids.size(1);
-  TORCH_CHECK(target_ids.size(1) == k + 1 && out_tokens.size(1) == k + 1, "spec_verify: shapes");
+  const bool ragged = row_start.has_value() && row_start->defined();
+  TORCH_CHECK(out_tokens.size(0) == batch && out_tokens.size(1) == k + 1 && n_accept.numel() == batch, "spec_verify: shapes");
+  TORCH_CHECK(ragged ? row_start->numel() == batch
+                     : (target_ids.dim() == 2 && target_ids.size(0) == batch && target_ids.size(1) == k + 1),
+              "spec_verify: target shape");
+  TORCH_CHECK(target_ids.is_contiguous() && draft_ids.is_contiguous() && out_tokens.is_contiguous(), "spec_verify: contiguous");
   c10::cuda::CUDAGuard guard(draft_ids.device());
   fllm::spec_verify_greedy(draft_ids.data_ptr<int>(), target_ids.data_ptr<int>(), batch, k,
-                           opt_ptr<int>(n_draft), n_accept.data_ptr<int>(),
+                           opt_ptr<int>(row_start), opt_ptr<int>(n_draft), n_accept.data_ptr<int>(),
                            out_tokens.data_ptr<int>(), cur_stream());
 }
 
-void spec_verify_sampled(const Tensor& target_logits, const Tensor& draft_logits,
+void spec_verify_sampled(const Tensor& target_logits, const optional<Tensor>& draft_logits,
                          const Tensor& draft_ids, const optional<Tensor>& n_draft,
-                         const Tensor& params, Tensor n_accept, Tensor out_tokens) {
+                         const Tensor& params, Tensor n_accept, Tensor out_tokens,
+                         const optional<Tensor>& row_start) {
   const bool f32 = target_logits.scalar_type() == at::kFloat;
-  TORCH_CHECK(target_logits.scalar_type() == draft_logits.scalar_type(), "spec_verify: dtype mismatch");
+  const bool has_q = draft_logits.has_value() && draft_logits->defined();
   check_i32(draft_ids, "draft_ids");
   const int batch = (int)draft_ids.size(0), k = (int)draft_ids.size(1);
-  TORCH_CHECK(target_logits.dim() == 2 && target_logits.size(0) == (int64_t)batch * (k + 1),
+  const bool ragged = row_start.has_value() && row_start->defined();
+  TORCH_CHECK(target_logits.dim() == 2 && target_logits.stride(1) == 1 &&
+              (ragged ? row_start->numel() == batch : target_logits.size(0) == (int64_t)batch * (k + 1)),
               "spec_verify: target rows");
-  TORCH_CHECK(draft_logits.dim() == 2 && draft_logits.size(0) == (int64_t)batch * k,
-              "spec_verify: draft rows");
+  if (has_q) {
+    TORCH_CHECK(target_logits.scalar_type() == draft_logits->scalar_type(), "spec_verify: dtype mismatch");
+    TORCH_CHECK(draft_logits->dim() == 2 && draft_logits->size(0) == (int64_t)batch * k &&
+                draft_logits->size(1) == target_logits.size(1) && draft_logits->stride(1) == 1, "spec_verify: draft rows");
+  }
+  TORCH_CHECK(params.numel() * params.element_size() >= (int64_t)batch * (int64_t)sizeof(fllm::SampleRow), "spec_verify: params");
+  TORCH_CHECK(out_tokens.size(0) == batch && out_tokens.size(1) == k + 1 && n_accept.numel() == batch, "spec_verify: shapes");
   c10::cuda::CUDAGuard guard(draft_ids.device());
   fllm::spec_verify_sampled(target_logits.data_ptr(), target_logits.stride(0),
-                            draft_logits.data_ptr(), draft_logits.stride(0), f32,
+                            has_q ? draft_logits->data_ptr() : nullptr, has_q ? draft_logits->stride(0) : 0, f32,
                             (int)target_logits.size(1), draft_ids.data_ptr<int>(), batch, k,
-                            opt_ptr<int>(n_draft),
+                            opt_ptr<int>(row_start), opt_ptr<int>(n_draft),
                             reinterpret_cast<const fllm::SampleRow*>(params.data_ptr()),
                             n_accept.data_ptr<int>(), out_tokens.data_ptr<int>(), cur_stream());
 }
@@ -373,8 +387,8 @@ TORCH_LIBRARY(fllm_b200, m) {
   m.def("argmax_split(Tensor logits, Tensor(a!) out_ids, Tensor? out_vals, Tensor? out_pairs, int id_offset, Tensor(b!) scratch) -> ()", &argmax_split);
   m.def("argmax_pairs_select(Tensor pairs, Tensor(a!) out_ids) -> ()", &argmax_pairs_select);
   m.def("sample(Tensor(a!) logits, Tensor params, Tensor? pen_ids, Tensor? pen_counts, Tensor? bias_ids, Tensor? bias_vals, Tensor? allow_mask, Tensor(b!) out_ids, Tensor? out_logprobs) -> ()", &sample);
-  m.def("spec_verify_greedy(Tensor draft_ids, Tensor target_ids, Tensor? n_draft, Tensor(a!) n_accept, Tensor(b!) out_tokens) -> ()", &spec_verify_greedy);
-  m.def("spec_verify_sampled(Tensor target_logits, Tensor draft_logits, Tensor draft_ids, Tensor? n_draft, Tensor params, Tensor(a!) n_accept, Tensor(b!) out_tokens) -> ()", &spec_verify_sampled);
+  m.def("spec_verify_greedy(Tensor draft_ids, Tensor target_ids, Tensor? n_draft, Tensor(a!) n_accept, Tensor(b!) out_tokens, Tensor? row_start=None) -> ()", &spec_verify_greedy);
+  m.def("spec_verify_sampled(Tensor target_logits, Tensor? draft_logits, Tensor draft_ids, Tensor? n_draft, Tensor params, Tensor(a!) n_accept, Tensor(b!) out_tokens, Tensor? row_start=None) -> ()", &spec_verify_sampled);
   m.def("sample_row_bytes() -> int", &sample_row_bytes);
   m.def("gemm_occupancy(int bn) -> int", &gemm_occupancy);
 }

@@ -220,11 +220,14 @@ void sample_rows(void* logits, int is_fp32, long long ld, int rows, int vocab, c
                  const int* pen_ids, const int* pen_counts, int pen_stride, const int* bias_ids,
                  const float* bias_vals, int bias_stride, const uint32_t* allow_mask, int mask_words,
                  int* out_ids, float* out_logprobs, cudaStream_t s);
+// row_start (optional): first verify row of each sequence in the target arrays (ragged steps); without it
+// sequence b owns rows b * (k + 1) ... b * (k + 1) + k. draft_logits may be null (point-mass drafts).
 void spec_verify_greedy(const int* draft_ids, const int* target_ids, int batch, int k,
-                        const int* n_draft, int* n_accept, int* out_tokens, cudaStream_t s);
+                        const int* row_start, const int* n_draft, int* n_accept, int* out_tokens,
+                        cudaStream_t s);
 void spec_verify_sampled(const void* target_logits, long long ld_t, const void* draft_logits,
                          long long ld_d, int is_fp32, int vocab, const int* draft_ids, int batch,
-                         int k, const int* n_draft, const SampleRow* prm, int* n_accept,
-                         int* out_tokens, cudaStream_t s);
+                         int k, const int* row_start, const int* n_draft, const SampleRow* prm,
+                         int* n_accept, int* out_tokens, cudaStream_t s);
 
 }  // namespace fllm

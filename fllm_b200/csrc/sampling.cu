@@ -412,53 +412,62 @@ void sample_rows(void* logits, int is_fp32, long long ld, int rows, int vocab, c
 // Greedy chain: target_ids[b][0..k] are the target's argmax tokens for the k+1 verify rows of
 // sequence b (row i scores the token after draft i-1). Accept drafts while they match; the
 // token at the first mismatch (or the bonus token after k matches) is emitted as well.
+//
+// The verify rows of sequence b start at row_start[b] of the target arrays when row_start is given
+// (a ragged step: sequences carry different numbers of drafts), else at b * (k + 1).
 __global__ void spec_verify_greedy_kernel(const int* __restrict__ draft_ids,
-                                          const int* __restrict__ target_ids, int k,
+                                          const int* __restrict__ target_ids, int batch, int k,
+                                          const int* __restrict__ row_start,
                                           const int* __restrict__ n_draft, int* __restrict__ n_accept,
                                           int* __restrict__ out_tokens) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
-  if (b >= gridDim.x * blockDim.x) return;
-  const int nd = n_draft ? n_draft[b] : k;
+  if (b >= batch) return;
+  const int nd = n_draft ? min(n_draft[b], k) : k;
   if (nd < 0) return;
+  const int* tgt = target_ids + (row_start ? (size_t)row_start[b] : (size_t)b * (k + 1));
   int acc = 0;
-  while (acc < nd && draft_ids[(size_t)b * k + acc] == target_ids[(size_t)b * (k + 1) + acc]) {
+  while (acc < nd && draft_ids[(size_t)b * k + acc] == tgt[acc]) {
     out_tokens[(size_t)b * (k + 1) + acc] = draft_ids[(size_t)b * k + acc];
     ++acc;
   }
-  out_tokens[(size_t)b * (k + 1) + acc] = target_ids[(size_t)b * (k + 1) + acc];
+  out_tokens[(size_t)b * (k + 1) + acc] = tgt[acc];
   n_accept[b] = acc;
 }
 
 void spec_verify_greedy(const int* draft_ids, const int* target_ids, int batch, int k,
-                        const int* n_draft, int* n_accept, int* out_tokens, cudaStream_t s) {
+                        const int* row_start, const int* n_draft, int* n_accept, int* out_tokens,
+                        cudaStream_t s) {
   if (batch <= 0) return;
-  // one thread per sequence; launch exactly `batch` threads across blocks of size 1 x batch
-  spec_verify_greedy_kernel<<<batch, 1, 0, s>>>(draft_ids, target_ids, k, n_draft, n_accept,
-                                                out_tokens);
+  spec_verify_greedy_kernel<<<(batch + 63) / 64, 64, 0, s>>>(draft_ids, target_ids, batch, k, row_start,
+                                                            n_draft, n_accept, out_tokens);
   cuda_check(cudaGetLastError(), "spec_verify_greedy_kernel");
 }
 
 // Exact rule on full distributions. One CTA per sequence. For draft position i with token x:
 // accept with probability min(1, p(x)/q(x)); at the first rejection draw from
 // normalise(max(0, p - q)); after nd acceptances draw the bonus token from p of row nd.
-// p = softmax(target_logits / T), q = softmax(draft_logits / T).
+// p = softmax(target_logits / T), q = softmax(draft_logits / T). Without draft logits (drafts that
+// come from a lookup, not from a model) q is the point mass on the draft token: it is accepted with
+// probability p(x), and the residual is p with x removed. row_start as in the greedy kernel.
 template <typename T>
 __global__ void __launch_bounds__(kSampThreads)
 spec_verify_sampled_kernel(const T* __restrict__ target_logits, long long ld_t,
                            const T* __restrict__ draft_logits, long long ld_d, int vocab,
-                           const int* __restrict__ draft_ids, int k, const int* __restrict__ n_draft,
+                           const int* __restrict__ draft_ids, int k, const int* __restrict__ row_start,
+                           const int* __restrict__ n_draft,
                            const SampleRow* __restrict__ prm, int* __restrict__ n_accept,
                            int* __restrict__ out_tokens) {
   __shared__ ArgMax sm_a[32];
   __shared__ float sm_f[32];
   const int b = blockIdx.x;
   const SampleRow p = prm[b];
-  const int nd = n_draft ? n_draft[b] : k;
+  const int nd = n_draft ? min(n_draft[b], k) : k;
   const float inv_t = p.temperature > 0.f ? 1.f / p.temperature : 1.f;
+  const size_t row0 = row_start ? (size_t)row_start[b] : (size_t)b * (k + 1);
   int acc = 0;
   int final_tok = -1;
   for (int i = 0; i <= nd; ++i) {
-    const T* trow = target_logits + ((size_t)b * (k + 1) + i) * ld_t;
+    const T* trow = target_logits + (row0 + i) * ld_t;
     // softmax statistics of the target row
     ArgMax a{-INFINITY, 0x7fffffff};
     for (int j = threadIdx.x; j < vocab; j += blockDim.x) a = better(a, ArgMax{ld_logit(trow, j), j});
@@ -478,20 +487,24 @@ spec_verify_sampled_kernel(const T* __restrict__ target_logits, long long ld_t,
       final_tok = g.i;
       break;
     }
-    const T* drow = draft_logits + ((size_t)b * k + i) * ld_d;
-    ArgMax ad{-INFINITY, 0x7fffffff};
-    for (int j = threadIdx.x; j < vocab; j += blockDim.x) ad = better(ad, ArgMax{ld_logit(drow, j), j});
-    ad = block_argmax(ad, sm_a);
-    float zd = 0.f;
-    for (int j = threadIdx.x; j < vocab; j += blockDim.x) zd += __expf((ld_logit(drow, j) - ad.v) * inv_t);
-    zd = block_sum(zd, sm_f);
+    const T* drow = draft_logits ? draft_logits + ((size_t)b * k + i) * ld_d : nullptr;
+    ArgMax ad{0.f, 0};
+    float zd = 1.f;
+    if (drow) {
+      ad = ArgMax{-INFINITY, 0x7fffffff};
+      for (int j = threadIdx.x; j < vocab; j += blockDim.x) ad = better(ad, ArgMax{ld_logit(drow, j), j});
+      ad = block_argmax(ad, sm_a);
+      zd = 0.f;
+      for (int j = threadIdx.x; j < vocab; j += blockDim.x) zd += __expf((ld_logit(drow, j) - ad.v) * inv_t);
+      zd = block_sum(zd, sm_f);
+    }
     const int x = draft_ids[(size_t)b * k + i];
     bool accept;
     if (p.temperature <= 0.f) {
       accept = (x == a.i);
     } else {
       const float px = __expf((ld_logit(trow, x) - a.v) * inv_t) / zt;
-      const float qx = __expf((ld_logit(drow, x) - ad.v) * inv_t) / zd;
+      const float qx = drow ? __expf((ld_logit(drow, x) - ad.v) * inv_t) / zd : 1.f;
       const float u = philox_uniform(p.seed, p.draw + 2 * i, 0xffffffffu);
       accept = qx <= 0.f ? true : (u < fminf(1.f, px / qx));
     }
@@ -505,7 +518,7 @@ spec_verify_sampled_kernel(const T* __restrict__ target_logits, long long ld_t,
     ArgMax g{-INFINITY, 0x7fffffff};
     for (int j = threadIdx.x; j < vocab; j += blockDim.x) {
       const float pj = __expf((ld_logit(trow, j) - a.v) * inv_t) / zt;
-      const float qj = __expf((ld_logit(drow, j) - ad.v) * inv_t) / zd;
+      const float qj = drow ? __expf((ld_logit(drow, j) - ad.v) * inv_t) / zd : (j == x ? 1.f : 0.f);
       const float rj = pj - qj;
       if (rj <= 0.f) continue;
       const float u = philox_uniform(p.seed, p.draw + 2 * i + 1, (uint32_t)j);
@@ -523,17 +536,17 @@ spec_verify_sampled_kernel(const T* __restrict__ target_logits, long long ld_t,
 
 void spec_verify_sampled(const void* target_logits, long long ld_t, const void* draft_logits,
                          long long ld_d, int is_fp32, int vocab, const int* draft_ids, int batch,
-                         int k, const int* n_draft, const SampleRow* prm, int* n_accept,
-                         int* out_tokens, cudaStream_t s) {
+                         int k, const int* row_start, const int* n_draft, const SampleRow* prm,
+                         int* n_accept, int* out_tokens, cudaStream_t s) {
   if (batch <= 0) return;
   if (is_fp32)
     spec_verify_sampled_kernel<float><<<batch, kSampThreads, 0, s>>>(
         (const float*)target_logits, ld_t, (const float*)draft_logits, ld_d, vocab, draft_ids, k,
-        n_draft, prm, n_accept, out_tokens);
+        row_start, n_draft, prm, n_accept, out_tokens);
   else
     spec_verify_sampled_kernel<__nv_bfloat16><<<batch, kSampThreads, 0, s>>>(
         (const __nv_bfloat16*)target_logits, ld_t, (const __nv_bfloat16*)draft_logits, ld_d, vocab,
-        draft_ids, k, n_draft, prm, n_accept, out_tokens);
+        draft_ids, k, row_start, n_draft, prm, n_accept, out_tokens);
   cuda_check(cudaGetLastError(), "spec_verify_sampled_kernel");
 }
 

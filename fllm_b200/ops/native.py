@@ -188,6 +188,29 @@ class NativeOps:
         self.launches += 1
         return (ids, lp) if want_logprobs else ids
 
+    def spec_verify_greedy(self, draft_ids, target_ids, n_draft=None, row_start=None):
+        """Greedy chain acceptance on the device. draft_ids [B, k]; target_ids [B, k+1] or, with row_start [B],
+        the flat ids of a ragged step. -> (n_accept [B], out_tokens [B, k+1]: accepted drafts then the target's token)."""
+        B, k = draft_ids.shape
+        n_acc = torch.zeros(B, dtype=torch.int32, device=draft_ids.device)
+        out = torch.full((B, k + 1), -1, dtype=torch.int32, device=draft_ids.device)
+        self.k.spec_verify_greedy(draft_ids, target_ids, n_draft, n_acc, out, row_start)
+        self.launches += 1
+        return n_acc, out
+
+    def spec_verify_sampled(self, target_logits, draft_logits, draft_ids, params, n_draft=None, row_start=None):
+        """Exact speculative sampling on the device (accept with min(1, p/q), residual draw at the first
+        rejection, bonus draw after the last acceptance). params: sampler rows (temperature, ..., draw, seed),
+        one per sequence; draft_logits None = point-mass drafts."""
+        B, k = draft_ids.shape
+        dev = draft_ids.device
+        prm = torch.frombuffer(bytearray(pack_sample_rows(params)), dtype=torch.uint8).to(dev)
+        n_acc = torch.zeros(B, dtype=torch.int32, device=dev)
+        out = torch.full((B, k + 1), -1, dtype=torch.int32, device=dev)
+        self.k.spec_verify_sampled(target_logits, draft_logits, draft_ids, n_draft, prm, n_acc, out, row_start)
+        self.launches += 1
+        return n_acc, out
+
     def check_status(self) -> int:
         code = int(self.status.item())
         if code:

@@ -7,6 +7,7 @@ from __future__ import annotations
 import math
 from typing import Optional
 
+import numpy as np
 import torch
 import torch.nn.functional as F
 
@@ -152,6 +153,102 @@ class RefOps:
         """[ranks, rows, 2] (value, id) pairs -> id of the highest value per row, lowest rank among equals."""
         best = pairs[:, :, 0].argmax(0)
         return pairs[best, torch.arange(pairs.shape[1], device=pairs.device), 1].int()
+
+
+    def spec_verify_greedy(self, draft_ids, target_ids, n_draft=None, row_start=None):
+        B, k = draft_ids.shape
+        d = draft_ids.cpu().tolist()
+        t = target_ids.cpu().flatten().tolist()
+        nd = n_draft.cpu().tolist() if n_draft is not None else [k] * B
+        rs = row_start.cpu().tolist() if row_start is not None else [b * (k + 1) for b in range(B)]
+        n_acc = torch.zeros(B, dtype=torch.int32)
+        out = torch.full((B, k + 1), -1, dtype=torch.int32)
+        for b in range(B):
+            acc = 0
+            while acc < min(nd[b], k) and d[b][acc] == t[rs[b] + acc]:
+                out[b, acc] = d[b][acc]
+                acc += 1
+            out[b, acc] = t[rs[b] + acc]
+            n_acc[b] = acc
+        return n_acc.to(draft_ids.device), out.to(draft_ids.device)
+
+    def spec_verify_sampled(self, target_logits, draft_logits, draft_ids, params, n_draft=None, row_start=None):
+        """Host statement of the device rule with the same counter-based random numbers."""
+        B, k = draft_ids.shape
+        tl = target_logits.float().cpu()
+        dl = draft_logits.float().cpu() if draft_logits is not None else None
+        d = draft_ids.cpu().tolist()
+        nd = n_draft.cpu().tolist() if n_draft is not None else [k] * B
+        rs = row_start.cpu().tolist() if row_start is not None else [b * (k + 1) for b in range(B)]
+        V = tl.shape[1]
+        idx = np.arange(V, dtype=np.uint64)
+        n_acc = torch.zeros(B, dtype=torch.int32)
+        out = torch.full((B, k + 1), -1, dtype=torch.int32)
+
+        def gumbel_pick(score, seed, draw):
+            u = philox_uniform_np(seed, draw, idx)
+            g = score - np.log(-np.log(u))
+            return int(np.argmax(np.where(np.isfinite(score), g, -np.inf)))
+
+        for b in range(B):
+            temp, draw, seed = float(params[b][0]), int(params[b][7]), int(params[b][8])
+            inv_t = 1.0 / temp if temp > 0 else 1.0
+            acc, final = 0, -1
+            for i in range(min(nd[b], k) + 1):
+                trow = tl[rs[b] + i].double().numpy()
+                amax = int(np.argmax(trow))
+                lt = (trow - trow[amax]) * inv_t
+                pt = np.exp(lt) / np.exp(lt).sum()
+                if i == min(nd[b], k):
+                    final = amax if temp <= 0 else gumbel_pick(lt, seed, draw + 2 * i + 1)
+                    break
+                x = d[b][i]
+                if dl is not None:
+                    drow = dl[b * k + i].double().numpy()
+                    lq = (drow - drow.max()) * inv_t
+                    q = np.exp(lq) / np.exp(lq).sum()
+                else:
+                    q = np.zeros(V)
+                    q[x] = 1.0
+                if temp <= 0:
+                    ok = x == amax
+                else:
+                    u = float(philox_uniform_np(seed, draw + 2 * i, np.array([0xFFFFFFFF], dtype=np.uint64))[0])
+                    ok = True if q[x] <= 0 else u < min(1.0, pt[x] / q[x])
+                if ok:
+                    out[b, acc] = x
+                    acc += 1
+                    continue
+                if temp <= 0:
+                    final = amax
+                    break
+                r = pt - q
+                with np.errstate(divide="ignore"):
+                    score = np.where(r > 0, np.log(np.maximum(r, 1e-300)), -np.inf)
+                final = gumbel_pick(score, seed, draw + 2 * i + 1) if (r > 0).any() else amax
+                break
+            out[b, acc] = final
+            n_acc[b] = acc
+        return n_acc.to(draft_ids.device), out.to(draft_ids.device)
+
+
+def philox_uniform_np(seed: int, draw: int, idx: "np.ndarray") -> "np.ndarray":
+    """Vector form of philox_uniform over an array of indices."""
+    M = np.uint64(0xFFFFFFFF)
+    c0 = idx.astype(np.uint64) & M
+    c1 = np.full_like(c0, np.uint64(draw & 0xFFFFFFFF))
+    c2 = np.full_like(c0, np.uint64(0x9E3779B9))
+    c3 = np.full_like(c0, np.uint64(0xBB67AE85))
+    k0, k1 = seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF
+    for _ in range(10):
+        p0 = np.uint64(0xD2511F53) * c0
+        p1 = np.uint64(0xCD9E8D57) * c2
+        hi0, lo0 = p0 >> np.uint64(32), p0 & M
+        hi1, lo1 = p1 >> np.uint64(32), p1 & M
+        c0, c1, c2, c3 = (hi1 ^ c1 ^ np.uint64(k0)) & M, lo1, (hi0 ^ c3 ^ np.uint64(k1)) & M, lo0
+        k0 = (k0 + 0x9E3779B9) & 0xFFFFFFFF
+        k1 = (k1 + 0xBB67AE85) & 0xFFFFFFFF
+    return ((c0 >> np.uint64(8)).astype(np.float64) + 0.5) / 16777216.0
 
 
 def philox_uniform(seed: int, draw: int, idx: int) -> float:

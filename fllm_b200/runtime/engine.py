@@ -359,9 +359,10 @@ class LLMEngine:
         self.scheduler.on_drop = lambda r: self.proposer.forget(r.seq_id)
 
     def _propose_drafts(self) -> None:
+        # sampled verification reads the full logit rows, which a pipeline hands over as ids only
+        modes = ("greedy", "sampled") if self.par.pp == 1 else ("greedy",)
         cands = [r for r in self.scheduler.running
-                 if r.is_decode and not r.draft and r.params.greedy and r.params.speculative
-                 and not r.params.needs_full_sampler]
+                 if r.is_decode and not r.draft and r.params.spec_mode in modes]
         if not cands:
             return
         k = self.adaptive.length() if self.adaptive else self.cfg.draft_tokens
@@ -380,6 +381,7 @@ class LLMEngine:
         else:
             for r, room in ok:
                 r.draft = self.proposer.propose(r.all_tokens, room)[:room]
+                r.draft_logits = None
 
     # ------------------------------------------------------------------ launch-ahead decode
     PLACEHOLDER = -1
@@ -564,12 +566,22 @@ class LLMEngine:
         needs_sampler = any(s.wants_logits and s.req.params.needs_full_sampler for s in step.seqs)
         if needs_sampler and self.par.pp == 1:
             tokens_dev = self._sample(step, logits, tokens_dev)
+        verdicts = None
+        if any(s.verify for s in step.seqs):
+            verdicts = self._verify_drafts(step, logits if self.par.pp == 1 else None, tokens_dev)
         n_rows = tokens_dev.shape[0]
         out = self._out_host[:n_rows]
         out.copy_(tokens_dev, non_blocking=self.is_cuda)
         if self.is_cuda:
             torch.cuda.current_stream().synchronize()
         self.stats.d2h_bytes += n_rows * 4
+        if verdicts is not None:
+            step.verified = {}
+            for idxs, res in verdicts:
+                host = res.tolist()
+                self.stats.d2h_bytes += res.numel() * 4
+                for i, rec in zip(idxs, host):
+                    step.verified[i] = (rec[0], rec[1:2 + rec[0]])
         self.stats.kernel_launches += getattr(self.ops, "launches", 0) - l0
         toks = out.tolist()
         events.extend(self._commit(step, toks))
@@ -620,6 +632,59 @@ class LLMEngine:
             g.broadcast(out, src=pp - 1)
         return out
 
+    SPEC_DRAW_BASE = 0x40000000              # keeps the acceptance draws apart from the sampler's own counter
+
+    def _verify_drafts(self, step: ScheduledStep, logits: Optional[torch.Tensor], tokens_dev: torch.Tensor):
+        """Acceptance of the step's drafts, decided on the device (rule: rust/engine/src/speculative.rs:103
+        ``verify_chain``). Greedy requests compare draft ids with the target's argmax ids; sampled requests run
+        the exact accept / residual rule on the logit rows, against the draft model's logits when the proposer
+        kept them and against a point mass otherwise. Returns [(step.seqs indices, int32 [n, k + 2] on the
+        device: accepted count, then the accepted drafts and the target's token)]; the caller reads it with
+        the step's ids."""
+        from .sampler import _row_params
+        starts, row = {}, 0
+        for i, s in enumerate(step.seqs):
+            if s.wants_logits:
+                starts[i] = row
+                row += s.count if s.verify else 1
+        out = []
+        dev = tokens_dev.device
+        for mode in ("greedy", "sampled"):
+            grp = [i for i, s in enumerate(step.seqs) if s.verify and (s.req.params.spec_mode or "greedy") == mode]
+            if not grp:
+                continue
+            if mode == "sampled" and logits is None:
+                raise RuntimeError("sampled verification needs the logit rows of the step")
+            k = max(step.seqs[i].verify for i in grp)
+            meta = np.full((len(grp), k + 2), -1, dtype=np.int32)
+            for j, i in enumerate(grp):
+                s = step.seqs[i]
+                assert starts[i] + s.verify + 1 <= row
+                meta[j, :s.verify] = s.req.draft[:s.verify]
+                meta[j, k], meta[j, k + 1] = s.verify, starts[i]
+            m = torch.from_numpy(meta).to(dev)
+            self.stats.h2d_bytes += meta.nbytes
+            draft, nd, rs = m[:, :k].contiguous(), m[:, k].contiguous(), m[:, k + 1].contiguous()
+            if mode == "greedy":
+                n_acc, toks = self.ops.spec_verify_greedy(draft, tokens_dev.contiguous(), nd, rs)
+            else:
+                full = self.decoder.full_logits(logits)
+                dls = [getattr(step.seqs[i].req, "draft_logits", None) for i in grp]
+                dl = None
+                if all(d is not None for d in dls):
+                    V = full.shape[1]
+                    dl = torch.zeros(len(grp), k, V, dtype=full.dtype, device=dev)
+                    for j, d in enumerate(dls):
+                        dl[j, :d.shape[0]] = d[:k].to(full.dtype)
+                    dl = dl.view(len(grp) * k, V)
+                params = []
+                for i in grp:
+                    r = step.seqs[i].req
+                    params.append(_row_params(r, self.SPEC_DRAW_BASE + 2 * len(r.output), self.cfg.seed))
+                n_acc, toks = self.ops.spec_verify_sampled(full, dl, draft, params, nd, rs)
+            out.append((grp, torch.cat([n_acc.view(-1, 1), toks], 1)))
+        return out
+
     def _sample(self, step: ScheduledStep, logits: torch.Tensor, greedy: torch.Tensor) -> torch.Tensor:
         from .sampler import sample_step
         full = self.decoder.full_logits(logits)
@@ -629,7 +694,8 @@ class LLMEngine:
         events: List[TokenEvent] = []
         now = time.monotonic()
         row = 0
-        for s in step.seqs:
+        verified = getattr(step, "verified", None)
+        for si, s in enumerate(step.seqs):
             r = s.req
             if not s.wants_logits:
                 self.scheduler.commit(s, [])
@@ -638,10 +704,15 @@ class LLMEngine:
             if s.verify:
                 target = toks[row:row + s.count]
                 row += s.count
-                acc = 0
-                while acc < s.verify and r.draft[acc] == target[acc]:
-                    acc += 1
-                new = r.draft[:acc] + [target[acc]]
+                if verified is not None and si in verified:
+                    acc, new = verified[si]
+                    new = list(new)
+                else:                                       # host statement of the greedy rule
+                    acc = 0
+                    while acc < s.verify and r.draft[acc] == target[acc]:
+                        acc += 1
+                    new = r.draft[:acc] + [target[acc]]
+                r.draft_logits = None
                 if self.adaptive is not None:
                     self.adaptive.update(s.verify, acc)
                 self.stats.spec_proposed += s.verify

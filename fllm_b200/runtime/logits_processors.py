@@ -1,5 +1,5 @@
 """Logit processors that run on the host before the device sampler: locally typical sampling,
-the DRY repetition penalty, Mirostat (version 2) and multi-token banned sequences.
+the DRY repetition penalty, Mirostat (versions 1 and 2) and multi-token banned sequences.
 
 They are the rarely used part of the sampling contract (rust/engine/src/sampling.rs:6-49), so they
 are kept out of the CUDA sampler: each one edits the fp32 logit row of its request (a ban or a
@@ -81,18 +81,48 @@ def banned_by_sequences(context: Sequence[int], bad_words: Sequence[Sequence[int
 
 
 class Mirostat:
-    """Mirostat 2.0 (Basu et al. 2021): tokens whose surprise exceeds mu are dropped, one of the rest is
-    drawn, and mu moves by eta * (tau - observed surprise). One instance per request."""
+    """Mirostat (Basu et al. 2021), one instance per request. Version 2 drops the tokens whose surprise
+    exceeds mu; version 1 estimates the Zipf exponent s of the distribution from its `m` most probable
+    tokens, turns mu into a top-k cut k = ((eps * 2^mu) / (1 - n^-eps))^(1/s) with eps = s - 1, and keeps
+    the k most probable tokens. In both, one of the kept tokens is drawn and mu moves by
+    eta * (tau - observed surprise)."""
 
-    def __init__(self, tau: float = 5.0, eta: float = 0.1):
-        self.tau, self.eta = tau, eta
+    def __init__(self, tau: float = 5.0, eta: float = 0.1, version: int = 2, m: int = 100):
+        self.tau, self.eta, self.version, self.m = tau, eta, int(version), int(m)
         self.mu = 2.0 * tau
         self._logp2: Optional[torch.Tensor] = None
+
+    def zipf_cut(self, logp2: torch.Tensor) -> int:
+        """Version 1's k for the current mu (at least 1, at most the vocabulary)."""
+        n = logp2.shape[-1]
+        m = max(2, min(self.m, n))
+        top = torch.topk(logp2, m).values.double() * math.log(2.0)          # natural-log probabilities, sorted
+        i = torch.arange(1, m, dtype=torch.float64)
+        t = torch.log((i + 1) / i)                                          # ln((i+1)/i)
+        b = top[:-1] - top[1:]                                              # ln(p_i / p_{i+1})
+        ok = torch.isfinite(b)
+        den = float((t[ok] * t[ok]).sum())
+        s_hat = float((t[ok] * b[ok]).sum()) / den if den > 0 else 1.0
+        eps = s_hat - 1.0
+        if abs(eps) < 1e-6 or s_hat <= 0:
+            return n
+        try:
+            k = ((eps * 2.0 ** self.mu) / (1.0 - float(n) ** (-eps))) ** (1.0 / s_hat)
+        except (OverflowError, ZeroDivisionError):
+            return n
+        if not math.isfinite(k) or isinstance(k, complex):
+            return n
+        return max(1, min(n, int(round(k))))
 
     def keep_mask(self, logits: torch.Tensor, temperature: float) -> torch.Tensor:
         t = temperature if temperature > 0 else 1.0
         logp2 = torch.log_softmax(logits.float() / t, -1) / math.log(2.0)
-        keep = (-logp2) <= self.mu
+        if self.version == 1:
+            k = self.zipf_cut(logp2)
+            keep = torch.zeros_like(logp2, dtype=torch.bool)
+            keep[torch.topk(logp2, k).indices] = True
+        else:
+            keep = (-logp2) <= self.mu
         if not bool(keep.any()):
             keep[int(torch.argmax(logp2))] = True
         trunc = torch.where(keep, logp2, torch.full_like(logp2, NEG_INF))
@@ -126,7 +156,7 @@ def apply_before_sampling(req, row: torch.Tensor, position: int) -> None:
         row.masked_fill_(~typical_keep_mask(row, p.typical_p, p.temperature), NEG_INF)
     if p.mirostat_mode != 0:
         if req.mirostat is None:
-            req.mirostat = Mirostat(p.mirostat_tau, p.mirostat_eta)
+            req.mirostat = Mirostat(p.mirostat_tau, p.mirostat_eta, version=1 if p.mirostat_mode == 1 else 2)
         row.masked_fill_(~req.mirostat.keep_mask(row, p.temperature), NEG_INF)
 
 

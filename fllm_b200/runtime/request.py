@@ -34,7 +34,7 @@ class SamplingParams:
     dry_allowed_length: int = 2
     dry_sequence_breakers: Sequence[int] = ()
     dry_penalty_last_n: int = 1024
-    mirostat_mode: int = 0               # 0 off; 1 or 2 run Mirostat 2.0
+    mirostat_mode: int = 0               # 0 off; 1 = Mirostat (Zipf top-k cut); 2 = Mirostat 2.0 (surprise cut)
     mirostat_tau: float = 5.0
     mirostat_eta: float = 0.1
     logprobs: bool = False
@@ -57,6 +57,21 @@ class SamplingParams:
                 or self.frequency_penalty != 0.0 or bool(self.logit_bias)
                 or self.allowed_token_ids is not None or bool(self.bad_words_ids) or self.logprobs
                 or self.guided is not None or self.needs_host_processors)
+
+    @property
+    def spec_mode(self) -> Optional[str]:
+        """How drafts of this request are verified: "greedy" (chain match on the argmax ids), "sampled" (the
+        exact accept / residual rule on the temperature-scaled distributions; needs the plain distribution, so
+        no truncation, penalty, bias, mask or host processor), or None (not speculated)."""
+        if not self.speculative:
+            return None
+        if not self.needs_full_sampler:
+            return "greedy"
+        plain = (self.top_k == 0 and self.top_p >= 1.0 and self.min_p <= 0.0 and self.repetition_penalty == 1.0
+                 and self.presence_penalty == 0.0 and self.frequency_penalty == 0.0 and not self.logit_bias
+                 and self.allowed_token_ids is None and not self.bad_words_ids and not self.logprobs
+                 and self.guided is None and not self.needs_host_processors)
+        return "sampled" if (plain and self.temperature > 0.0) else None
 
     @property
     def needs_host_processors(self) -> bool:
@@ -119,6 +134,7 @@ class Request:
     token_times: List[float] = field(default_factory=list)
     preemptions: int = 0
     draft: List[int] = field(default_factory=list)   # proposed tokens awaiting verification
+    draft_logits: Optional[object] = None            # [len(draft), vocab] device tensor when the drafts were sampled
     logprobs: List[float] = field(default_factory=list)
     top_logprobs: List[list] = field(default_factory=list)   # per output token: [(token id, log-probability), ...]
     swapped: bool = False            # preempted with its KV parked in host memory

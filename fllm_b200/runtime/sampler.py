@@ -29,9 +29,11 @@ def sample_step(engine, step, logits: torch.Tensor, greedy: torch.Tensor) -> tor
         if not s.wants_logits:
             continue
         n = s.count if s.verify else 1
-        for j in range(n):
-            if s.req.params.needs_full_sampler:
-                rows.append((r_i + j, s.req, len(s.req.output) + j))
+        # verify rows of a sampled request are decided by the speculative acceptance rule, not drawn here
+        if not (s.verify and s.req.params.spec_mode == "sampled"):
+            for j in range(n):
+                if s.req.params.needs_full_sampler:
+                    rows.append((r_i + j, s.req, len(s.req.output) + j))
         r_i += n
     if not rows:
         return greedy

@@ -68,45 +68,127 @@ class NgramProposer:
 
 
 class DraftModelProposer:
-    """Greedy k-token drafts from a small decoder that reuses the target's block tables."""
+    """k-token drafts from a small decoder that reuses the target's block tables.
+
+    One call = one ragged catch-up step (the tokens the draft model has not seen, built on the host into one
+    pinned staging array and sent with a single copy) and k - 1 decode steps whose inputs are made on the
+    device from the previous step's tokens (positions + 1, slots from the block table), so nothing crosses
+    the bus between draft tokens; the k tokens come back in one read at the end. Greedy requests take the
+    draft's argmax; sampled requests draw from the draft's temperature-scaled distribution with their own
+    counter-based stream and keep the logit rows, which the exact acceptance rule needs
+    (rust/engine/src/speculative.rs:103). Under tensor parallelism the draft is sharded over the same group
+    when its head counts divide, otherwise every rank runs a whole copy; both give every rank the same drafts.
+    """
+
+    DRAFT_SEED_SALT = 0x5DEECE66D
 
     def __init__(self, engine, draft_cfg, k: int = 4, seed: int = 1, weights=None):
         self.eng, self.cfg, self.k = engine, draft_cfg, k
         dev = engine.device
-        self.spec = make_shard_spec(draft_cfg)
-        self.weights = weights or init_random_weights(draft_cfg, dev, torch.bfloat16, seed)
+        tp, rank, group = 1, 0, None
+        etp = getattr(engine.par, "tp", 1)
+        if etp > 1 and weights is None and draft_cfg.num_heads % etp == 0 and draft_cfg.num_kv_heads % etp == 0:
+            tp, rank, group = etp, engine.tp_rank, engine.tp_group
+        self.spec = make_shard_spec(draft_cfg, tp, rank)
+        self.weights = weights or init_random_weights(draft_cfg, dev, torch.bfloat16, seed, tp=tp, tp_rank=rank)
         self.kv = KVCache(draft_cfg.num_layers, engine.kv.num_blocks, self.spec.hkv_local, engine.block_size,
                           draft_cfg.head_dim, dev)
-        self.decoder = Decoder(draft_cfg, self.weights, self.kv, engine.ops, self.spec)
+        self.decoder = Decoder(draft_cfg, self.weights, self.kv, engine.ops, self.spec, group)
         self.computed: Dict[int, int] = {}                  # seq id -> tokens whose draft KV is stored
+        self._stage: Optional[torch.Tensor] = None          # pinned host staging, grown on demand
+        self.h2d_copies = 0                                 # copies issued by the last propose_batch (tests read it)
 
     def forget(self, seq_id: int) -> None:
         self.computed.pop(seq_id, None)
 
-    def _batch(self, rows: List[tuple]) -> StepBatch:
-        """rows: (request, start, tokens list) - one ragged chunk per request."""
+    def _staging(self, n: int) -> torch.Tensor:
+        if self._stage is None or self._stage.numel() < n:
+            cap = max(n, 4096)
+            self._stage = torch.empty(cap, dtype=torch.int32, pin_memory=self.eng.is_cuda)
+        return self._stage[:n]
+
+    def _first_batch(self, rows: List[tuple]) -> StepBatch:
+        """rows: (request, start, tokens list) - one ragged chunk per request, one host-to-device copy."""
         eng = self.eng
         bs = eng.block_size
-        dev = eng.device
-        ids, pos, slots, rseq, lrows, qst, kvl = [], [], [], [], [], [0], []
+        B = len(rows)
+        T = sum(len(t) for _, _, t in rows)
         max_blocks = max(len(eng.blocks.table(r.seq_id)) for r, _, _ in rows)
-        tab = np.zeros((len(rows), max_blocks), dtype=np.int32)
+        # layout of the staging array: ids | pos | slots | row_seq | logit_rows | q_starts | kv_lens | table
+        sizes = [T, T, T, T, B, B + 1, B, B * max_blocks]
+        offs = np.concatenate([[0], np.cumsum(sizes)])
+        stage = self._staging(int(offs[-1]))
+        h = stage.numpy()
+        ids, pos, slots, rseq, lrows, qst, kvl, tab = (h[offs[j]:offs[j + 1]] for j in range(8))
+        tab = tab.reshape(B, max_blocks)
+        tab[:] = 0
+        at = 0
+        qst[0] = 0
         for i, (r, start, toks) in enumerate(rows):
             tb = eng.blocks.np_table(r.seq_id)
             tab[i, :tb.shape[0]] = tb
-            p = np.arange(start, start + len(toks))
-            ids += list(toks)
-            pos += p.tolist()
-            slots += (tb[p // bs] * bs + p % bs).tolist()
-            rseq += [i] * len(toks)
-            lrows.append(len(ids) - 1)
-            qst.append(len(ids))
-            kvl.append(start + len(toks))
-        t = lambda a: torch.tensor(a, dtype=torch.int32, device=dev)
-        n = [len(x[2]) for x in rows]
-        return StepBatch(t(ids), t(pos), t(slots), t(rseq), torch.from_numpy(tab).to(dev), t(lrows),
-                         num_seqs=len(rows), num_tokens=len(ids), max_kv_len=max(kvl), all_decode=False,
-                         seq_lens=t(kvl), q_starts=t(qst), max_q_len=max(n), min_q_len=min(n))
+            n = len(toks)
+            p = np.arange(start, start + n)
+            ids[at:at + n] = toks
+            pos[at:at + n] = p
+            slots[at:at + n] = tb[p // bs] * bs + p % bs
+            rseq[at:at + n] = i
+            at += n
+            lrows[i] = at - 1
+            qst[i + 1] = at
+            kvl[i] = start + n
+        d = stage.to(eng.device, non_blocking=eng.is_cuda)
+        self.h2d_copies += 1
+        v = [d[offs[j]:offs[j + 1]] for j in range(8)]
+        ns = [len(x[2]) for x in rows]
+        return StepBatch(v[0], v[1], v[2], v[3], v[7].view(B, max_blocks), v[4],
+                         num_seqs=B, num_tokens=T, max_kv_len=int(kvl.max()), all_decode=False,
+                         seq_lens=v[6], q_starts=v[5], max_q_len=max(ns), min_q_len=min(ns))
+
+    def _next_batch(self, prev: StepBatch, tokens: torch.Tensor, first: bool) -> StepBatch:
+        """The decode step after `prev`, made on the device: every sequence feeds the token it just drew."""
+        B = prev.num_seqs
+        bs = self.eng.block_size
+        if first:
+            ar = torch.arange(B, dtype=torch.int32, device=tokens.device)
+            pos = prev.seq_lens.clone()                      # the new token sits at the old visible length
+            rseq, lrows = ar, ar
+            qst = torch.arange(B + 1, dtype=torch.int32, device=tokens.device)
+        else:
+            pos = prev.positions + 1
+            rseq, lrows, qst = prev.row_seq, prev.logit_rows, prev.q_starts
+        blk = torch.gather(prev.block_tables, 1, (pos // bs).long().view(B, 1)).view(B)
+        slots = (blk * bs + pos % bs).to(torch.int32)
+        return StepBatch(tokens.to(torch.int32), pos, slots, rseq, prev.block_tables, lrows,
+                         num_seqs=B, num_tokens=B, max_kv_len=prev.max_kv_len + 1, all_decode=True,
+                         seq_lens=pos + 1, q_starts=qst, max_q_len=1, min_q_len=1)
+
+    def _draw(self, reqs: List, lg: torch.Tensor, step: int) -> torch.Tensor:
+        """Next draft token per row: argmax, or a draw from softmax(logits / T) for sampled requests."""
+        full = self.decoder.full_logits(lg)
+        toks = self.decoder.greedy_tokens(lg)
+        rows = [i for i, r in enumerate(reqs) if r.params.spec_mode == "sampled"]
+        if not rows:
+            return toks, None
+        from .sampler import _row_params
+        from ..ops.reference import sample_reference
+        idx = torch.tensor(rows, dtype=torch.long, device=lg.device)
+        sub = full.index_select(0, idx).float().contiguous()
+        prm = []
+        for i in rows:
+            t = list(_row_params(reqs[i], len(reqs[i].output) + step, self.eng.cfg.seed))
+            t[8] = (t[8] ^ self.DRAFT_SEED_SALT) & 0xFFFFFFFFFFFF        # a stream of its own
+            prm.append(tuple(t))
+        if lg.is_cuda:
+            from ..ops.native import pack_sample_rows
+            pb = torch.frombuffer(bytearray(pack_sample_rows(prm)), dtype=torch.uint8).to(lg.device)
+            ids = self.eng.ops.sample(sub, pb)
+        else:
+            ids = torch.tensor([sample_reference(sub[j], p[0], 0, 1.0, 0.0, p[8], p[7]) for j, p in enumerate(prm)],
+                               dtype=torch.int32)
+        toks = toks.clone()
+        toks[idx] = ids.to(toks.dtype)
+        return toks, (idx, full.index_select(0, idx))
 
     @torch.inference_mode()
     def propose_batch(self, reqs: List, k: Optional[int] = None) -> Dict[int, List[int]]:
@@ -114,21 +196,30 @@ class DraftModelProposer:
         k = k or self.k
         if not reqs:
             return {}
+        self.h2d_copies = 0
         rows = []
         for r in reqs:
             done = min(self.computed.get(r.seq_id, 0), r.num_tokens - 1)
             rows.append((r, done, r.all_tokens[done:]))
-        drafts: Dict[int, List[int]] = {r.seq_id: [] for r in reqs}
+        b = self._first_batch(rows)
+        drawn, kept = [], []
         for step in range(k):
-            b = self._batch(rows)
             lg = self.decoder.forward(b)
-            nxt = self.decoder.greedy_tokens(lg).tolist()
-            new_rows = []
-            for (r, start, toks), tok in zip(rows, nxt):
-                drafts[r.seq_id].append(int(tok))
-                new_rows.append((r, start + len(toks), [int(tok)]))
-            rows = new_rows
-        for r in reqs:
+            toks, keep = self._draw(reqs, lg, step)
+            drawn.append(toks)
+            kept.append(keep)
+            if step + 1 < k:
+                b = self._next_batch(b, toks, first=(step == 0))
+        host = torch.stack(drawn, 1).cpu().tolist()          # [B, k], one read for the whole call
+        drafts: Dict[int, List[int]] = {}
+        for i, r in enumerate(reqs):
+            drafts[r.seq_id] = [int(t) for t in host[i]]
+            r.draft_logits = None
             # the draft cache is valid for the verified tokens only; accepted drafts are re-fed next time
             self.computed[r.seq_id] = r.num_tokens
+        if kept[0] is not None:
+            idx = kept[0][0].tolist()
+            stack = torch.stack([kp[1] for kp in kept], 1)   # [n sampled, k, vocab]
+            for j, i in enumerate(idx):
+                reqs[i].draft_logits = stack[j]
         return drafts

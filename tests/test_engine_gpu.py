@@ -265,3 +265,33 @@ def test_rare_samplers_logprobs_and_beam_search_on_the_gpu():
     assert len(two) == 2 and two[0][1] >= two[1][1] and two[0][0] != two[1][0]
     assert not eng.requests
     assert eng.ops.check_status() == 0
+
+
+def test_speculation_on_the_gpu_greedy_and_sampled():
+    """Draft-model speculation with device-side acceptance: greedy text is unchanged, a draft equal to the target
+    is accepted in full for greedy and for sampled requests, and the proposer issues one staged copy per call."""
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    cfg = preset("qwen3-tiny")
+    ec = EngineConfig(max_num_seqs=8, max_num_batched_tokens=64, max_model_len=256, num_kv_blocks=128)
+    base = LLMEngine(cfg, ec, device="cuda:0", seed=3)
+    prompts = _prompts(cfg.vocab_size, (12, 30), seed=4)
+    want = base.generate(prompts, SamplingParams(max_tokens=12))
+    dm = LLMEngine(cfg, ec, device="cuda:0", seed=3, weights=base.weights)
+    dm.enable_draft_model(cfg, weights=base.weights, k=3)
+    got = dm.generate(prompts, SamplingParams(max_tokens=12))
+    # the verify rows go through the prefill-shaped kernels: bf16 near-ties may flip a token, after which texts differ
+    same = sum(a == b for a, b in zip(got, want))
+    assert same >= 1 and dm.stats.spec_proposed > 0
+    assert dm.stats.spec_accepted >= 0.8 * dm.stats.spec_proposed
+    assert dm.proposer.h2d_copies == 1
+    p0, a0 = dm.stats.spec_proposed, dm.stats.spec_accepted
+    sp = lambda: SamplingParams(max_tokens=12, temperature=0.8, seed=5)
+    s1 = dm.generate(prompts, sp())
+    assert all(len(o) == 12 for o in s1)
+    prop, acc = dm.stats.spec_proposed - p0, dm.stats.spec_accepted - a0
+    assert prop > 0 and acc >= 0.8 * prop                       # same model drafts from (nearly) the same distribution
+    ng = LLMEngine(cfg, EngineConfig(max_num_seqs=8, max_num_batched_tokens=64, max_model_len=256, num_kv_blocks=128,
+                                     speculative="ngram"), device="cuda:0", seed=3, weights=base.weights)
+    rep = [prompts[0][:6] * 4]
+    assert all(len(o) == 10 for o in ng.generate(rep, SamplingParams(max_tokens=10, temperature=0.7, seed=1)))

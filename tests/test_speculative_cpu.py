@@ -1,0 +1,110 @@
+"""Speculative decoding beyond the greedy chain: the exact accept / residual rule for sampled requests
+(rust/engine/src/speculative.rs:103), its wiring into the engine, and the draft proposer's batching."""
+import numpy as np
+import torch
+
+from fllm_b200.config import EngineConfig, preset
+from fllm_b200.models.weights import init_random_weights
+from fllm_b200.ops.reference import RefOps, philox_uniform, philox_uniform_np
+from fllm_b200.runtime.engine import LLMEngine
+from fllm_b200.runtime.request import SamplingParams
+
+
+def _row(temp, draw, seed):
+    return (temp, 1.0, 0.0, 1.0, 0.0, 0.0, 0, draw, seed)
+
+
+def test_vector_philox_equals_the_scalar_one():
+    idx = np.array([0, 1, 77, 0xFFFFFFFF, 123456], dtype=np.uint64)
+    a = philox_uniform_np(0xABCDEF012345, 9, idx)
+    assert np.allclose(a, [philox_uniform(0xABCDEF012345, 9, int(i)) for i in idx])
+
+
+def test_sampled_rule_emits_the_target_distribution():
+    """Whatever the draft distribution, the first emitted token is distributed as the target's p."""
+    ops = RefOps()
+    V, n = 6, 6000
+    g = torch.Generator().manual_seed(0)
+    tl = torch.randn(2, V, generator=g) * 1.5                     # rows: position 0 and the bonus row
+    dl = torch.randn(1, V, generator=g) * 1.5
+    p = torch.softmax(tl[0], -1).numpy()
+    q = torch.softmax(dl[0], -1).numpy()
+    rng = np.random.default_rng(1)
+    xs = rng.choice(V, size=n, p=q / q.sum())                     # drafts drawn from q
+    counts = np.zeros(V)
+    acc = 0
+    for t in range(n):
+        n_acc, out = ops.spec_verify_sampled(tl, dl, torch.tensor([[int(xs[t])]], dtype=torch.int32), [_row(1.0, 0, 1000 + t)])
+        counts[int(out[0, 0])] += 1
+        acc += int(n_acc[0])
+    emp = counts / n
+    assert np.abs(emp - p).max() < 0.03, (emp, p)
+    expect_acc = np.minimum(p, q).sum()                           # 1 - total variation distance
+    assert abs(acc / n - expect_acc) < 0.03
+    # point-mass drafts (no draft logits): accepted with probability p(x), otherwise a draw from p without x
+    counts[:] = 0
+    x = int(np.argmax(p))
+    for t in range(n):
+        _, out = ops.spec_verify_sampled(tl, None, torch.tensor([[x]], dtype=torch.int32), [_row(1.0, 0, 5000 + t)])
+        counts[int(out[0, 0])] += 1
+    assert np.abs(counts / n - p).max() < 0.03
+
+
+def test_ragged_rows_and_greedy_rule():
+    ops = RefOps()
+    draft = torch.tensor([[5, 6, 7], [1, 2, -1]], dtype=torch.int32)
+    flat = torch.tensor([9, 5, 6, 8, 0, 1, 2, 3], dtype=torch.int32)   # seq 0 rows 1..4, seq 1 rows 5..7
+    n_acc, out = ops.spec_verify_greedy(draft, flat, torch.tensor([3, 2], dtype=torch.int32), torch.tensor([1, 5], dtype=torch.int32))
+    assert n_acc.tolist() == [2, 2]
+    assert out[0, :3].tolist() == [5, 6, 8] and out[1].tolist()[:3] == [1, 2, 3]
+    # temperature 0 through the sampled rule is the greedy rule
+    tl = torch.full((8, 12), -5.0)
+    for r, t in enumerate(flat.tolist()):
+        tl[r, t] = 3.0
+    n2, out2 = ops.spec_verify_sampled(tl, None, draft, [_row(0.0, 0, 1), _row(0.0, 0, 2)],
+                                       torch.tensor([3, 2], dtype=torch.int32), torch.tensor([1, 5], dtype=torch.int32))
+    assert n2.tolist() == [2, 2] and out2[0, :3].tolist() == [5, 6, 8] and out2[1, :3].tolist() == [1, 2, 3]
+
+
+def _eng(cfg, w, **kw):
+    return LLMEngine(cfg, EngineConfig(max_num_batched_tokens=64, max_model_len=256, num_kv_blocks=96, **kw), device="cpu", weights=w)
+
+
+def test_engine_speculates_sampled_requests():
+    cfg = preset("qwen3-tiny")
+    w = init_random_weights(cfg, "cpu")
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (10, 23)]
+    prompts[0] = prompts[0][:5] * 4
+    sp = lambda: SamplingParams(max_tokens=12, temperature=0.8, seed=21)
+    assert sp().spec_mode == "sampled" and SamplingParams(temperature=0.8, top_k=5).spec_mode is None
+    # a draft equal to the target proposes from the same distribution: everything is accepted
+    dm = _eng(cfg, w)
+    dm.enable_draft_model(cfg, weights=w, k=3)
+    out1 = dm.generate(prompts, sp())
+    assert dm.stats.spec_proposed > 0 and dm.stats.spec_accepted == dm.stats.spec_proposed
+    assert dm.proposer.h2d_copies == 1                      # one staged copy per call, whatever k is
+    assert all(len(o) == 12 for o in out1)
+    dm2 = _eng(cfg, w)
+    dm2.enable_draft_model(cfg, weights=w, k=3)
+    assert dm2.generate(prompts, sp()) == out1              # seeded: repeatable
+    # an unrelated draft and the n-gram lookup (point-mass drafts) still produce valid seeded output
+    other = _eng(cfg, w)
+    other.enable_draft_model(cfg, k=4, seed=99)
+    o2 = other.generate(prompts, sp())
+    assert all(len(o) == 12 and all(0 <= t < cfg.vocab_size for t in o) for o in o2)
+    assert other.stats.spec_accepted < other.stats.spec_proposed
+    ng = _eng(cfg, w, speculative="ngram")
+    o3 = ng.generate(prompts, sp())
+    assert all(len(o) == 12 for o in o3)
+    # greedy and sampled requests verified in the same step
+    mixed = _eng(cfg, w)
+    mixed.enable_draft_model(cfg, weights=w, k=3)
+    base = _eng(cfg, w)
+    want = base.generate([prompts[1]], SamplingParams(max_tokens=10))[0]
+    ids = [mixed.add_request(prompts[0], sp()), mixed.add_request(prompts[1], SamplingParams(max_tokens=10))]
+    got = {}
+    while mixed.has_unfinished():
+        for ev in mixed.step():
+            got.setdefault(ev.request_id, []).extend(ev.token_ids)
+    assert got[ids[1]] == want and len(got[ids[0]]) == 12
