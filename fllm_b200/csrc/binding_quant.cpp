@@ -58,6 +58,42 @@ int64_t linear_w4a16(const Tensor& x, const Tensor& codes, const Tensor& scales,
                             y.data_ptr(), y.stride(0), (int)T, (int)N, (int)K, ws, ws_bytes, st, cur_stream());
 }
 
+// x bf16 [T, K] -> xq uint8 [T, K] (e4m3) + sf uint8 [mx_act_scale_bytes(T, K)] (e8m0 atoms per token tile)
+void quant_mx(const Tensor& x, Tensor xq, Tensor sf) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 && x.stride(0) % 4 == 0, "x: bf16 rows");
+  TORCH_CHECK(xq.is_contiguous() && xq.element_size() == 1 && xq.numel() == x.numel(), "xq: contiguous 1-byte [T, K]");
+  TORCH_CHECK(sf.is_contiguous() && sf.element_size() == 1 &&
+              (size_t)sf.numel() >= fllm::mx_act_scale_bytes((int)x.size(0), (int)x.size(1)), "sf: too small");
+  c10::cuda::CUDAGuard guard(x.device());
+  fllm::quant_mx(x.data_ptr(), x.stride(0), xq.data_ptr(), sf.data_ptr(), (int)x.size(0), (int)x.size(1), cur_stream());
+}
+
+int64_t mx_act_scale_bytes(int64_t T, int64_t K) { return (int64_t)fllm::mx_act_scale_bytes((int)T, (int)K); }
+
+// wq: e4m3 bytes [N, K] (a4 = 0) or e2m1 codes [N, K/2] (a4 = 1); sfa: weight scale atoms [ceil(N/128), K/128, 512]
+int64_t linear_mx(const Tensor& xq, const Tensor& sfb, const Tensor& wq, const Tensor& sfa, int64_t a4, double alpha,
+                  const optional<Tensor>& bias, Tensor y, const optional<Tensor>& workspace, const optional<Tensor>& status) {
+  TORCH_CHECK(xq.is_cuda() && xq.is_contiguous() && wq.is_contiguous() && xq.element_size() == 1 && wq.element_size() == 1 &&
+              xq.dim() == 2 && wq.dim() == 2, "xq, wq: contiguous byte matrices");
+  const int64_t T = xq.size(0), K = xq.size(1), N = wq.size(0);
+  TORCH_CHECK(wq.size(1) * (a4 ? 2 : 1) == K && K % 128 == 0, "K mismatch (K must be a multiple of 128)");
+  TORCH_CHECK(sfa.is_contiguous() && sfa.element_size() == 1 && sfa.numel() == ((N + 127) / 128) * (K / 128) * 512, "sfa: [ceil(N/128), K/128, 512]");
+  TORCH_CHECK(sfb.is_contiguous() && sfb.element_size() == 1 &&
+              (size_t)sfb.numel() >= fllm::mx_act_scale_bytes((int)T, (int)K), "sfb: too small");
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.stride(1) == 1 && y.size(0) == T && y.size(1) == N, "y: [T, N] bf16");
+  c10::cuda::CUDAGuard guard(xq.device());
+  const void* b = bias.has_value() && bias->defined() ? bias->data_ptr() : nullptr;
+  int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  if (workspace.has_value() && workspace->defined() && workspace->numel() * workspace->element_size() > (64 << 10)) {
+    ws = static_cast<char*>(workspace->data_ptr()) + (64 << 10);
+    ws_bytes = workspace->numel() * workspace->element_size() - (64 << 10);
+  }
+  return fllm::linear_mx(xq.data_ptr(), sfb.data_ptr(), wq.data_ptr(), sfa.data_ptr(), (int)a4, (float)alpha, b, y.data_ptr(),
+                         y.stride(0), (int)T, (int)N, (int)K, ws, ws_bytes, st, cur_stream());
+}
+
 void w4_dequant(const Tensor& codes, const Tensor& scales, int64_t fmt, double alpha, Tensor out) {
   TORCH_CHECK(codes.is_cuda() && codes.is_contiguous() && codes.dim() == 2 && out.is_contiguous() && out.scalar_type() == at::kBFloat16, "codes [N, K/2], out bf16 [N, K]");
   TORCH_CHECK(out.numel() == codes.numel() * 2 && (codes.size(1) * 2) % 32 == 0, "out: [N, K], K % 32 == 0");
@@ -71,5 +107,8 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("quant_fp8_1x128(Tensor x, Tensor(a!) xq, Tensor(b!) sx) -> ()", &quant_fp8_1x128);
   m.def("linear_fp8_block(Tensor xq, Tensor sx, Tensor wq, Tensor sw, Tensor? bias, Tensor(a!) y, Tensor? status) -> int", &linear_fp8_block);
   m.def("linear_w4a16(Tensor x, Tensor codes, Tensor scales, int fmt, float alpha, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status) -> int", &linear_w4a16);
+  m.def("quant_mx(Tensor x, Tensor(a!) xq, Tensor(b!) sf) -> ()", &quant_mx);
+  m.def("mx_act_scale_bytes(int T, int K) -> int", &mx_act_scale_bytes);
+  m.def("linear_mx(Tensor xq, Tensor sfb, Tensor wq, Tensor sfa, int a4, float alpha, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status) -> int", &linear_mx);
   m.def("w4_dequant(Tensor codes, Tensor scales, int fmt, float alpha, Tensor(a!) out) -> ()", &w4_dequant);
 }

@@ -98,6 +98,15 @@ void* symm_import(const unsigned char in[64]);
 void symm_close(void* p);
 
 // ---- block-scaled FP8 ------------------------------------------------------------------
+// Block-scaled MX GEMM (tcgen05 kind::mxf8f6f4.block_scale): e4m3 activations x e4m3 or packed e2m1 weights, one
+// e8m0 scale per 32 values on both sides, scale factors in 512-byte atoms (128 rows x 4 K slices). The token tile
+// (16 / 32 / 64 / 128) is a function of T alone, so the quantiser and the GEMM agree on the atom grouping.
+int mx_token_tile(int T);
+size_t mx_act_scale_bytes(int T, int K);
+void quant_mx(const void* x, long long ldx, void* xq, void* sf, int T, int K, cudaStream_t s);
+int linear_mx(const void* xq, const void* sfb, const void* wq, const void* sfa, int a4, float alpha, const void* bias,
+              void* y, long long ldy, int T, int N, int K, void* workspace, size_t workspace_bytes, int* status,
+              cudaStream_t stream);
 void quant_fp8_1x128(const void* x, long long ldx, void* xq, float* sx, int tokens, int K, cudaStream_t s);
 int linear_fp8_block(const void* xq, const float* sx, const void* wq, const float* sw, const void* bias, void* y,
                      long long ldy, int T, int N, int K, int* status, cudaStream_t stream);

@@ -1,0 +1,369 @@
+// Block-scaled MX GEMM on the fifth-generation tensor cores (tcgen05.mma kind::mxf8f6f4.block_scale):
+//
+//   y[T][N] = alpha * sum_k (xq[t][k] * 2^(sx[t][k/32] - 127)) * (wq[n][k] * 2^(sw[n][k/32] - 127))  (+ bias)
+//
+//   weights      MXFP8: e4m3 bytes [N][K], or MXFP4: e2m1 codes, two per byte [N][K/2] (low nibble = even k),
+//                with one e8m0 (power-of-two) scale per 32 values
+//   activations  e4m3 [T][K] + one e8m0 scale per token per 32 values, produced from bf16 by quant_mx_kernel
+//
+// The scales never touch the ALUs: they are copied from shared memory into tensor memory (tcgen05.cp) and
+// the MMA applies them to every 32-deep slice of the dot product, so a packed 4-bit weight goes from HBM to
+// the tensor core without an expansion stage (TMA's 16U4_ALIGN16B type spreads 16 codes over 16 bytes of
+// shared memory, the form the instruction reads). That is what makes a 4-bit weight cost 4.25 bits of HBM
+// traffic and nothing else.
+//
+// Scale factors travel in 512-byte atoms that cover 128 rows x 128 values of K (4 scales per row):
+//   byte (r % 32) * 16 + (r / 32) * 4 + j   holds the scale of row r, K slice j
+// which is the order in which tcgen05.cp (32 rows x 128 bits, replicated over the four lane quarters) lays
+// them into four tensor-memory columns: row r -> lane r % 32, column r / 32, byte j. The instruction
+// descriptor names the byte (the K slice) each of the four MMAs of a stage uses. Weight atoms are built at
+// load time ([N / 128][K / 128][512]); the activation quantiser writes atoms per token tile.
+//
+// Orientation: weights are the A operand (M = 128 output features per tile), tokens the B operand
+// (N = 16 ... 128 per tile), for decode and prefill alike; results are stored transposed. Few feature
+// tiles split K over grid.z (fp32 partial sums + a reduce kernel). Warp roles and TMA staging follow
+// gemm_fp8.cu; every wait is bounded and reports through the status word.
+//
+// Reference counterparts: rust/engine/cuda/nvfp4.cu:132-307 (mma.sync block-scaled FP4 for GeForce
+// Blackwell; the data-centre parts fall back to W4A16 Marlin there), rust/engine/cuda/mxfp4_moe.cu.
+#include <cuda_fp8.h>
+
+#include <algorithm>
+
+#include "fllm_ops.h"
+#include "ptx.cuh"
+#include "tma_host.h"
+
+namespace fllm {
+
+constexpr int MX_BM = 128;
+constexpr int MX_BK = 128;       // values of K per stage = one 128-byte row of shared memory for 8-bit and unpacked 4-bit
+constexpr int MX_UMMA_K = 32;
+constexpr int kMxThreads = 192;
+constexpr int kMxAtomBytes = 512;
+
+struct MxArgs {
+  int M, N, K;                   // M = output features, N = tokens
+  int m_tiles, n_tiles, k_blocks;
+  int k_splits, kb_per_split;
+  float* ws;                     // [k_splits][N][M] fp32 when k_splits > 1
+  long long ldc;
+  __nv_bfloat16* out;
+  const uint8_t* sfa;            // [m_tiles][k_blocks][512]
+  const uint8_t* sfb;            // [n_tiles][k_blocks][512]
+  float alpha;
+  const __nv_bfloat16* bias;
+  int* status;
+};
+
+template <int BN>
+struct MxSmem {
+  static constexpr int kABytes = MX_BM * MX_BK;
+  static constexpr int kBBytes = BN * MX_BK;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = BN <= 64 ? 4 : 6;
+  static constexpr int kAccCols = BN < 32 ? 32 : BN;
+  static constexpr int kTmemCols = kAccCols + 16 <= 64 ? 64 : (kAccCols + 16 <= 128 ? 128 : 256);
+  static constexpr int kSfBytes = kStages * 2 * kMxAtomBytes;
+  static constexpr int kTotal = kStages * kStageBytes + kSfBytes + 256 + 1024;
+  static_assert(4 * 32 * 32 * 2 <= kABytes, "the epilogue staging reuses the first weight stage");
+};
+
+// Shared-memory descriptor of one scale-factor atom for tcgen05.cp: K-major, no swizzle, 8-row x 16-byte
+// core matrices 128 bytes apart along the rows; a single core matrix along K.
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(128 >> 4) << 32;                 // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                          // descriptor version 1 (sm_100)
+  return d;                                        // layout type 0: no swizzle
+}
+
+__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_dst, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(sdesc) : "memory");
+}
+
+// Instruction descriptor of the block-scaled kinds: fp32 accumulate, K-major operands, e8m0 scales.
+// a_fmt / b_fmt: 0 e4m3, 1 e5m2, 5 e2m1. The scale-factor ids (bits 29-30 for A, 4-5 for B) are OR-ed in per MMA.
+__host__ __device__ constexpr uint32_t make_idesc_mx(int M, int N, int a_fmt, int b_fmt) {
+  return ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(N >> 3) << 17) | (1u << 23) |
+         ((uint32_t)(M >> 4) << 24);
+}
+
+__device__ __forceinline__ void tc_mma_mx(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+template <int BN, bool A4>
+__global__ void __launch_bounds__(kMxThreads, BN <= 64 ? 2 : 1)
+gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const MxArgs p) {
+  using S = MxSmem<BN>;
+  constexpr int STAGES = S::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * S::kABytes;
+  uint8_t* sSF = smem + STAGES * S::kStageBytes;            // per stage: A atom, B atom
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sSF + S::kSfBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tfull_bar = bars + 2 * STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_idx = blockIdx.x, m_idx = blockIdx.y;
+  const int kb0 = blockIdx.z * p.kb_per_split;
+  const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(tfull_bar, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tma_a); tma_prefetch_desc(&tma_b); }
+  if (warp == 1) { tmem_alloc(tmem_slot, S::kTmemCols); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      pdl_wait();                                              // the activations come from the kernel before
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) break;
+        // a packed 4-bit tile is counted by the bytes that leave global memory, not by the padded bytes it fills
+        mbar_expect_tx(&full_bar[stage], (A4 ? S::kABytes / 2 : S::kABytes) + S::kBBytes + 2 * kMxAtomBytes);
+        tma_load_2d(sA + stage * S::kABytes, &tma_a, &full_bar[stage], kb * MX_BK, m_idx * MX_BM);
+        tma_load_2d(sB + stage * S::kBBytes, &tma_b, &full_bar[stage], kb * MX_BK, n_idx * BN);
+        bulk_load_1d(sSF + stage * 2 * kMxAtomBytes, p.sfa + ((size_t)m_idx * p.k_blocks + kb) * kMxAtomBytes,
+                     kMxAtomBytes, &full_bar[stage]);
+        bulk_load_1d(sSF + stage * 2 * kMxAtomBytes + kMxAtomBytes,
+                     p.sfb + ((size_t)n_idx * p.k_blocks + kb) * kMxAtomBytes, kMxAtomBytes, &full_bar[stage]);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_mx(MX_BM, BN, A4 ? 5 : 0, 0);
+      const uint32_t tmem_sf = tmem_base + S::kAccCols;       // two buffers of 8 columns: A scales, B scales
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t sf_cols = tmem_sf + ((kb - kb0) & 1) * 8;
+        tc_cp_sf(sf_cols, make_sf_desc(smem_u32(sSF + stage * 2 * kMxAtomBytes)));
+        tc_cp_sf(sf_cols + 4, make_sf_desc(smem_u32(sSF + stage * 2 * kMxAtomBytes + kMxAtomBytes)));
+        const uint64_t da = make_smem_desc_sw128(smem_u32(sA + stage * S::kABytes));
+        const uint64_t db = make_smem_desc_sw128(smem_u32(sB + stage * S::kBBytes));
+#pragma unroll
+        for (int k = 0; k < MX_BK / MX_UMMA_K; ++k)
+          tc_mma_mx(tmem_base, da + 2 * k, db + 2 * k, idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4), sf_cols,
+                    sf_cols + 4, (kb > kb0 || k > 0) ? 1u : 0u);
+        tc_commit(&empty_bar[stage]);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+      if (ok) tc_commit(tfull_bar);
+    }
+  } else {
+    const int q = warp & 3;
+    const int e = warp - 2;
+    if (kb1 > kb0 && mbar_wait(tfull_bar, 0, abort_flag)) {
+      tc_fence_after_sync();
+      const int m = m_idx * MX_BM + q * 32 + lane;
+      const int n_base = n_idx * BN;
+      const float bias_m = (p.bias && m < p.M) ? __bfloat162float(p.bias[m]) : 0.f;
+      const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+      __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(sA) + e * (32 * 32);
+      constexpr int CH = BN < 32 ? 16 : 32;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += CH) {
+        uint32_t r[CH];
+        if constexpr (CH == 32) tmem_ld_32x32(t_lane + c0, r);
+        else tmem_ld_32x16(t_lane + c0, r);
+        tmem_ld_wait();
+        if (p.k_splits > 1) {                                  // fp32 partial sums, lanes along features: coalesced
+          float* wsp = p.ws + (size_t)blockIdx.z * p.N * p.M;
+#pragma unroll
+          for (int c = 0; c < CH; ++c)
+            if (n_base + c0 + c < p.N && m < p.M) wsp[(size_t)(n_base + c0 + c) * p.M + m] = __uint_as_float(r[c]);
+          continue;
+        }
+#pragma unroll
+        for (int c = 0; c < CH; ++c) stg[c * 32 + lane] = __float2bfloat16(__uint_as_float(r[c]) * p.alpha + bias_m);
+        __syncwarp();
+        const int f0 = 8 * (lane & 3);
+        const int mm0 = m_idx * MX_BM + q * 32 + f0;
+#pragma unroll
+        for (int rnd = 0; rnd < CH / 8; ++rnd) {
+          const int c = (lane >> 2) + 8 * rnd;
+          const int n = n_base + c0 + c;
+          if (n < p.N && mm0 < p.M)
+            *reinterpret_cast<uint4*>(p.out + (size_t)n * p.ldc + mm0) = *reinterpret_cast<const uint4*>(stg + c * 32 + f0);
+        }
+        __syncwarp();
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after_sync(); tmem_dealloc(tmem_base, S::kTmemCols); }
+  if (threadIdx.x == 0 && *abort_flag && p.status) atomicCAS(p.status, FLLM_OK, FLLM_ERR_MBAR_TIMEOUT);
+}
+
+// out[n][m] = bf16(alpha * sum_s ws[s][n][m] + bias[m])
+__global__ void mx_splitk_reduce_kernel(const float* __restrict__ ws, int splits, int rows, int cols, long long ldc,
+                                        float alpha, const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t n = (size_t)rows * cols;
+  const size_t i4 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i4 >= n) return;
+  float4 acc = *reinterpret_cast<const float4*>(ws + i4);
+  for (int s = 1; s < splits; ++s) {
+    const float4 v = *reinterpret_cast<const float4*>(ws + (size_t)s * n + i4);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  const int r = (int)(i4 / cols);
+  const int c = (int)(i4 - (size_t)r * cols);
+  float b[4] = {0.f, 0.f, 0.f, 0.f};
+  if (bias) for (int i = 0; i < 4; ++i) b[i] = __bfloat162float(bias[c + i]);
+  uint2 o;
+  o.x = pack_bf16x2(acc.x * alpha + b[0], acc.y * alpha + b[1]);
+  o.y = pack_bf16x2(acc.z * alpha + b[2], acc.w * alpha + b[3]);
+  *reinterpret_cast<uint2*>(out + (size_t)r * ldc + c) = o;
+}
+
+// x bf16 [T][K] -> e4m3 [T][K] + e8m0 scales per 32 values in atoms of `bn`-token tiles:
+// sf[(t / bn) * (K / 128) + kb][512]. One warp per (token, 128-value block); eight lanes share a scale.
+// The scale is the smallest power of two that brings the group's largest magnitude under 448. Rows past
+// T inside the last tile get zero scales.
+__global__ void quant_mx_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ xq,
+                                uint8_t* __restrict__ sf, int tokens, int padded_tokens, int K, int bn) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int kb_n = K / 128;
+  const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (gw >= (long long)padded_tokens * kb_n) return;
+  const int t = (int)(gw / kb_n), kb = (int)(gw - (long long)t * kb_n), lane = threadIdx.x & 31;
+  const int r = t % bn;
+  uint8_t* atom = sf + ((size_t)(t / bn) * kb_n + kb) * kMxAtomBytes + (r & 31) * 16 + (r >> 5) * 4;
+  if (t >= tokens) {
+    if ((lane & 7) == 0) atom[lane >> 3] = 0;
+    return;
+  }
+  const uint2 raw = *reinterpret_cast<const uint2*>(x + (size_t)t * ldx + kb * 128 + lane * 4);
+  const float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y);
+  float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+  // smallest e with amax * 2^-e <= 448: e = ceil(log2(amax / 448)); frexp gives amax / 448 = f * 2^ex, f in [0.5, 1)
+  int e = -127;
+  if (amax > 0.f) {
+    int ex;
+    const float f = frexpf(amax / 448.f, &ex);          // the division is exact where the quotient is a power of two
+    e = f == 0.5f ? ex - 1 : ex;
+    e = max(-127, min(127, e));
+  }
+  const float inv = exp2f((float)-e);
+  __nv_fp8x4_e4m3 q(make_float4(a.x * inv, a.y * inv, b.x * inv, b.y * inv));
+  *reinterpret_cast<uint32_t*>(xq + (size_t)t * K + kb * 128 + lane * 4) = *reinterpret_cast<uint32_t*>(&q);
+  if ((lane & 7) == 0) atom[lane >> 3] = (uint8_t)(e + 127);
+}
+
+int mx_token_tile(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128; }
+
+size_t mx_act_scale_bytes(int T, int K) {
+  const int bn = mx_token_tile(T);
+  return (size_t)((T + bn - 1) / bn) * (K / 128) * kMxAtomBytes;
+}
+
+void quant_mx(const void* x, long long ldx, void* xq, void* sf, int T, int K, cudaStream_t s) {
+  if (T <= 0) return;
+  if (K % 128) throw std::runtime_error("quant_mx: K must be a multiple of 128");
+  const int bn = mx_token_tile(T);
+  const int padded = (T + bn - 1) / bn * bn;
+  const long long groups = (long long)padded * (K / 128);
+  launch_pdl(quant_mx_kernel, dim3((unsigned)((groups + 7) / 8)), dim3(256), 0, s, (const __nv_bfloat16*)x, ldx,
+             (uint8_t*)xq, (uint8_t*)sf, T, padded, K, bn);
+}
+
+template <int BN, bool A4>
+static void launch_mx(const CUtensorMap& ta, const CUtensorMap& tb, const MxArgs& a, cudaStream_t s) {
+  using S = MxSmem<BN>;
+  static bool configured[kMaxDevices] = {};
+  if (first_call_on_device(configured)) {
+    cuda_check(cudaFuncSetAttribute(gemm_mx_kernel<BN, A4>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal),
+               "cudaFuncSetAttribute(gemm_mx_kernel)");
+  }
+  launch_pdl(gemm_mx_kernel<BN, A4>, dim3(a.n_tiles, a.m_tiles, a.k_splits), dim3(kMxThreads), (size_t)S::kTotal, s, ta, tb, a);
+}
+
+// y[T][N] = alpha * dequant(xq, sfb) * dequant(wq, sfa)^T (+ bias). a4: the weights are packed e2m1 codes.
+int linear_mx(const void* xq, const void* sfb, const void* wq, const void* sfa, int a4, float alpha, const void* bias,
+              void* y, long long ldy, int T, int N, int K, void* workspace, size_t workspace_bytes, int* status,
+              cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (K % 128 || N % 8 || (ldy & 7)) throw std::runtime_error("linear_mx: K % 128, N % 8 and 16-byte output rows required");
+  if ((reinterpret_cast<uintptr_t>(wq) & 31) || (reinterpret_cast<uintptr_t>(sfa) & 15) || (reinterpret_cast<uintptr_t>(sfb) & 15))
+    throw std::runtime_error("linear_mx: operands must be 32-byte (weights) and 16-byte (scales) aligned");
+  MxArgs a{};
+  a.M = N; a.N = T; a.K = K;
+  a.m_tiles = (N + MX_BM - 1) / MX_BM; a.k_blocks = K / MX_BK;
+  const int bn = mx_token_tile(T);
+  a.n_tiles = (T + bn - 1) / bn;
+  a.ldc = ldy; a.out = reinterpret_cast<__nv_bfloat16*>(y);
+  a.sfa = reinterpret_cast<const uint8_t*>(sfa); a.sfb = reinterpret_cast<const uint8_t*>(sfb);
+  a.alpha = alpha; a.bias = reinterpret_cast<const __nv_bfloat16*>(bias); a.status = status;
+  // Few tiles cannot pull the whole HBM bandwidth: split K over grid.z until the machine is full.
+  const int slots = sm_count() * (bn <= 64 ? 2 : 1);
+  const int tiles = a.m_tiles * a.n_tiles;
+  int splits = 1;
+  if (tiles * 2 <= slots && a.k_blocks >= 8) splits = std::min(std::min(slots / tiles, a.k_blocks / 4), 8);
+  while (splits > 1 && (!workspace || (size_t)splits * T * N * 4 > workspace_bytes)) --splits;
+  a.kb_per_split = (a.k_blocks + splits - 1) / splits;
+  a.k_splits = (a.k_blocks + a.kb_per_split - 1) / a.kb_per_split;
+  a.ws = reinterpret_cast<float*>(workspace);
+  CUtensorMap ta = a4 ? make_tmap_2d(wq, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 1, N, K, K / 2, MX_BM, MX_BK, true)
+                      : make_tmap_2d(wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, MX_BM, MX_BK, true);
+  CUtensorMap tb = make_tmap_2d(xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, T, K, K, bn, MX_BK, true);
+#define FLLM_MX_LAUNCH(BN_)                                                    \
+  if (a4) launch_mx<BN_, true>(ta, tb, a, stream);                            \
+  else launch_mx<BN_, false>(ta, tb, a, stream)
+  switch (bn) {
+    case 16: FLLM_MX_LAUNCH(16); break;
+    case 32: FLLM_MX_LAUNCH(32); break;
+    case 64: FLLM_MX_LAUNCH(64); break;
+    default: FLLM_MX_LAUNCH(128); break;
+  }
+#undef FLLM_MX_LAUNCH
+  if (a.k_splits > 1) {
+    const size_t n = (size_t)T * N;
+    launch_pdl(mx_splitk_reduce_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, stream,
+               (const float*)a.ws, a.k_splits, T, N, ldy, alpha, a.bias, a.out);
+    return 2;
+  }
+  return 1;
+}
+
+}  // namespace fllm

@@ -770,44 +770,49 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ scoring
     @torch.inference_mode()
-    def score_tokens(self, tokens: Sequence[int]) -> List[float]:
-        """Log-probability of tokens[1:] given their prefixes (natural log): len(tokens) - 1 values. The sequence is
-        fed in chunks of at most ``max_num_batched_tokens`` rows whose logits are all kept (the same batch shape a
-        speculative verification uses); its KV blocks are freed afterwards. Perplexity = exp(-mean(score))
-        (the reference's ``ppl`` sub-command, rust/engine/src/ppl.rs). Single pipeline stage only."""
+    def token_logits(self, tokens: Sequence[int]) -> torch.Tensor:
+        """Teacher-forced logits: row i is the fp32 distribution over the token after tokens[:i + 1]
+        ([len(tokens), vocab], on the engine's device). The sequence is fed in chunks of at most
+        ``max_num_batched_tokens`` rows whose logits are all kept (the batch shape a speculative verification
+        uses); its KV blocks are freed afterwards. Single pipeline stage only."""
         if self.par.pp > 1:
-            raise RuntimeError("score_tokens needs a single pipeline stage")
+            raise RuntimeError("token_logits needs a single pipeline stage")
         tokens = [int(t) for t in tokens]
         n = len(tokens)
-        if n < 2:
-            return []
+        if n < 1:
+            raise ValueError("no tokens")
         if n > self.cfg.max_model_len:
             raise ValueError(f"{n} tokens exceed max_model_len={self.cfg.max_model_len}")
         self.drain()
         req = Request("score-" + str(next(self._req_ids)), next(self._seq_ids), tokens[:1], SamplingParams(max_tokens=1))
         req.draft = tokens[1:]
         self.blocks.allocate(req.seq_id, [])
-        out: List[float] = []
+        out = []
         try:
             if not self.blocks.ensure_capacity(req.seq_id, n):
-                raise RuntimeError("not enough free KV blocks to score this sequence")
+                raise RuntimeError("not enough free KV blocks for this sequence")
             step_max = self.cfg.max_num_batched_tokens
             off = 0
             while off < n:
                 cnt = min(step_max, n - off)
-                step = ScheduledStep(seqs=[ScheduledSeq(req, off, cnt, True, verify=cnt - 1 if cnt > 1 else 0)])
-                if cnt == 1:                                  # a lone last row: still keep its logits
-                    step.seqs[0].verify = 0
+                step = ScheduledStep(seqs=[ScheduledSeq(req, off, cnt, True, verify=cnt - 1)])
                 batch = self._build_batch(step)
                 logits = self.decoder.full_logits(self.decoder.forward(batch)).float()
-                lp = torch.log_softmax(logits, -1)
-                tgt = torch.tensor(tokens[off + 1: off + cnt + 1], dtype=torch.long, device=lp.device)
-                rows = lp[: tgt.numel()] if cnt > 1 else lp[-1:][: tgt.numel()]
-                out.extend(rows.gather(1, tgt[:, None]).flatten().tolist())
+                out.append(logits[-1:] if cnt == 1 else logits[:cnt])
                 off += cnt
         finally:
             self.blocks.free_seq(req.seq_id)
-        return out[: n - 1]
+        return torch.cat(out)
+
+    def score_tokens(self, tokens: Sequence[int]) -> List[float]:
+        """Log-probability of tokens[1:] given their prefixes (natural log): len(tokens) - 1 values.
+        Perplexity = exp(-mean(score)) (the reference's ``ppl`` sub-command, rust/engine/src/ppl.rs)."""
+        tokens = [int(t) for t in tokens]
+        if len(tokens) < 2:
+            return []
+        lp = torch.log_softmax(self.token_logits(tokens)[:-1], -1)
+        tgt = torch.tensor(tokens[1:], dtype=torch.long, device=lp.device)
+        return lp.gather(1, tgt[:, None]).flatten().tolist()
 
     # ------------------------------------------------------------------ convenience
     def generate(self, prompts: Iterable[Sequence[int]], params: Optional[SamplingParams] = None) -> List[List[int]]:

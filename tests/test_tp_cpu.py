@@ -51,7 +51,7 @@ def test_tp_matches_single_device_on_cpu(world, model):
     # partial sums are rounded to bf16 before they are added, so a near-tie may flip late in a
     # sequence; the logits themselves must agree closely
     assert res["logit_err"] < 2e-2, res
-    assert res["agree"] >= 0.8 * res["total"], res
+    assert res["worst_gap"] < 0.02, res
 
 
 @pytest.mark.parametrize("world,pp", [(2, 2), (3, 3), (4, 2)])
@@ -61,4 +61,4 @@ def test_pipeline_and_tp_x_pp_match_single_device_on_cpu(world, pp):
     if world == pp:
         assert res["agree"] == res["total"], res          # pure PP computes the same bits
     else:
-        assert res["agree"] >= 0.8 * res["total"], res
+        assert res["worst_gap"] < 0.02, res

@@ -24,7 +24,7 @@ def test_tp_matches_single_device_on_gpus(world, backend):
     assert res["backend"] == backend
     # bf16 reductions in a different order may flip a near-tie late in a sequence
     assert res["logit_err"] < 3e-2, res
-    assert res["agree"] >= 0.7 * res["total"], res
+    assert res["worst_gap"] < 0.02, res            # a token may differ only where the single-device logits nearly tie
     assert res["graph_steps"] > 0
 
 
@@ -46,4 +46,4 @@ def test_gpt_oss_expert_parallel_modes_on_gpus(mode):
     res = run_ranks(2, ["cuda", "nccl", "gpt-oss-tiny", "1", mode], timeout=300)
     assert res["status"] == 0, res
     assert res["logit_err"] < 3e-2, res
-    assert res["agree"] >= 0.7 * res["total"], res
+    assert res["worst_gap"] < 0.02, res

@@ -117,11 +117,19 @@ def main():
     status = 0
     if hasattr(tp_rt, "check_status"):
         status = tp_rt.check_status()
+    # every token of the parallel run, teacher-forced through the single-device engine: how far below the best
+    # logit it sits, as a fraction of the row's logit span (0 = the single-device choice, a hair = a bf16 near-tie)
+    worst_gap = 0.0
+    for p_, o in zip(prompts, got):
+        lg = single.token_logits(p_ + o)[len(p_) - 1:len(p_) - 1 + len(o)]
+        for j, t in enumerate(o):
+            row = lg[j]
+            worst_gap = max(worst_gap, float((row.max() - row[t]) / (row.max() - row.min())))
     if rank == 0:
         agree = sum(a == b for o, r in zip(got, want) for a, b in zip(o, r))
         total = sum(len(o) for o in want)
         print(json.dumps({"backend": getattr(tp_rt, "backend", "?"), "world": world, "agree": agree, "total": total,
-                          "status": status, "graph_steps": eng.stats.graph_steps, "logit_err": logit_err}), flush=True)
+                          "worst_gap": worst_gap, "status": status, "graph_steps": eng.stats.graph_steps, "logit_err": logit_err}), flush=True)
     from fllm_b200.comm import shutdown_distributed
     eng.close()
     single.close()
