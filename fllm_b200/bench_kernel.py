@@ -49,7 +49,8 @@ def run_case(case: str, reps: int = 4) -> None:
     a self-ending workload for a profiler capture or a quick look (``bench-kernel --case gemm_decode``).
     Cases: gemm_decode (64 tokens x gate_up of an 8B model), gemm_prefill (2048 tokens), attn_decode
     (64 sequences at 1152 context), attn_prefill (2 x 1024 tokens), attn_prefill_long (4 x 4096 tokens),
-    fp8_prefill, gemm_fp4_decode (64 tokens x NVFP4 gate_up), tp_rs_gemm / tp_norm / tp_ag_gemm (the fused
+    fp8_prefill, gemm_fp4_decode (64 tokens x NVFP4 gate_up), gemm_mx4_decode / gemm_mx4_prefill / gemm_mx8_decode /
+    gemm_nvf4_decode / gemm_nvf4_prefill (block-scaled MXFP4 / MXFP8 / NVFP4 gate_up), tp_rs_gemm / tp_norm / tp_ag_gemm (the fused
     tensor-parallel kernels with two virtual ranks on one device)."""
     from .ops.native import NativeOps, Fp8BlockLinear, quantize_weight_fp8_block
     ops = NativeOps(torch.device("cuda:0"))
@@ -67,6 +68,20 @@ def run_case(case: str, reps: int = 4) -> None:
         scales = torch.full((24576, 256), 0x38, device="cuda", dtype=torch.uint8)      # e4m3 1.0
         q = Fp4Weight(codes, scales, 0, 0.01)
         y = torch.empty(64, 24576, **bf)
+        fn = lambda: ops.linear(x, q, out=y)
+    elif case in ("gemm_mx4_decode", "gemm_mx4_prefill", "gemm_mx8_decode", "gemm_nvf4_decode", "gemm_nvf4_prefill"):
+        from .ops.mx import MxWeight, Nvfp4TcWeight
+        T = 2048 if case.endswith("prefill") else 64
+        x = torch.randn(T, 4096, **bf)
+        a4 = "mx4" in case
+        if "nvf4" in case:
+            q = Nvfp4TcWeight(torch.randint(0, 256, (24576, 2048), device="cuda", dtype=torch.uint8),
+                              torch.full((24576, 256), 0x38, device="cuda", dtype=torch.uint8), 0.01)       # e4m3 1.0
+        else:
+            q = MxWeight(torch.randint(0, 256, (24576, 2048 if a4 else 4096), device="cuda", dtype=torch.uint8).clamp_(0, 0x7E),
+                         torch.full((24576, 128), 120, device="cuda", dtype=torch.uint8), a4)
+        q.atoms
+        y = torch.empty(T, 24576, **bf)
         fn = lambda: ops.linear(x, q, out=y)
     elif case in ("tp_rs_gemm", "tp_norm", "tp_ag_gemm"):
         # the fused tensor-parallel kernels with two virtual ranks on this one device (plain pointers instead
@@ -265,21 +280,35 @@ def main(argv=None) -> None:
     rows = []
     if args.fp4:
         from .ops.fp4 import Fp4Weight
+        from .ops.mx import MxWeight, Nvfp4TcWeight
         print(f"# peaks ({src}): {hbm} GB/s; bytes = packed weight + scales + activations")
+        print("# nvfp4 / mxfp4: packed weights expanded in the kernel, bf16 activations (W4A16);")
+        print("# mx4a8 / mx8a8: block-scaled MMA on MXFP4 / MXFP8 weights and MXFP8 activations, quantiser included;")
+        print("# nvf4a4: block-scaled MMA on NVFP4 weights and NVFP4 activations, quantiser included")
         for name, (N, K) in shapes.items():
             if name == "lm_head":
                 continue
             w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
-            for fmt in ("nvfp4", "mxfp4"):
-                q = Fp4Weight.from_dense(w, fmt)
-                for T in (1, 16, 64, 128):
+            for fmt in ("nvfp4", "mxfp4", "mx4a8", "mx8a8", "nvf4a4"):
+                if fmt in ("nvfp4", "mxfp4"):
+                    q = Fp4Weight.from_dense(w, fmt)
+                elif fmt == "nvf4a4":
+                    q = Nvfp4TcWeight.from_dense(w.float())
+                    q.atoms
+                else:
+                    q = MxWeight.from_dense(w.float(), "mxfp4" if fmt == "mx4a8" else "mxfp8")
+                    q.atoms                                                   # built once, at load time
+                for T in (1, 16, 64, 128, 2048):
+                    if T > 128 and fmt in ("nvfp4", "mxfp4"):
+                        continue
                     x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
                     y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
                     ms = timer(lambda: ops.linear(x, q, out=y))
                     ms16 = timer(lambda: ops.linear(x, w, out=y))
                     byts = q.nbytes() + 2.0 * (T * K + T * N)
                     print(f"{name:8s} {fmt:6s} T={T:4d} N={N:6d} K={K:6d} {ms * 1e3:8.1f} us  (bf16 {ms16 * 1e3:7.1f} us)  "
-                          f"{byts / ms / 1e6:6.0f} GB/s  frac {byts / (hbm * 1e9) / (ms / 1e3):.2f}")
+                          f"{byts / ms / 1e6:6.0f} GB/s  frac {byts / (hbm * 1e9) / (ms / 1e3):.2f}  "
+                          f"{2.0 * T * N * K / ms / 1e9:7.1f} TFLOP/s")
                     rows.append({"op": name, "fmt": fmt, "T": T, "us": ms * 1e3, "bf16_us": ms16 * 1e3, "gbs": byts / ms / 1e6})
             del w
         print("kernel status word:", ops.check_status())

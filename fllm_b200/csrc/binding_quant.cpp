@@ -58,29 +58,50 @@ int64_t linear_w4a16(const Tensor& x, const Tensor& codes, const Tensor& scales,
                             y.data_ptr(), y.stride(0), (int)T, (int)N, (int)K, ws, ws_bytes, st, cur_stream());
 }
 
-// x bf16 [T, K] -> xq uint8 [T, K] (e4m3) + sf uint8 [mx_act_scale_bytes(T, K)] (e8m0 atoms per token tile)
+// x bf16 [T, K] -> xq uint8 [T, K] (e4m3) + sf uint8 [mx_act_scale_bytes(T, K, 0)] (e8m0 atoms per token tile)
 void quant_mx(const Tensor& x, Tensor xq, Tensor sf) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 && x.stride(0) % 4 == 0, "x: bf16 rows");
   TORCH_CHECK(xq.is_contiguous() && xq.element_size() == 1 && xq.numel() == x.numel(), "xq: contiguous 1-byte [T, K]");
   TORCH_CHECK(sf.is_contiguous() && sf.element_size() == 1 &&
-              (size_t)sf.numel() >= fllm::mx_act_scale_bytes((int)x.size(0), (int)x.size(1)), "sf: too small");
+              (size_t)sf.numel() >= fllm::mx_act_scale_bytes((int)x.size(0), (int)x.size(1), 0), "sf: too small");
   c10::cuda::CUDAGuard guard(x.device());
   fllm::quant_mx(x.data_ptr(), x.stride(0), xq.data_ptr(), sf.data_ptr(), (int)x.size(0), (int)x.size(1), cur_stream());
 }
 
-int64_t mx_act_scale_bytes(int64_t T, int64_t K) { return (int64_t)fllm::mx_act_scale_bytes((int)T, (int)K); }
+// x bf16 [T, K] -> xq uint8 [T, K/2] (e2m1 pairs) + sf uint8 [mx_act_scale_bytes(T, K, 2)] (e4m3 atoms) + tok_scale fp32 [T]
+void quant_nvfp4(const Tensor& x, Tensor xq, Tensor sf, Tensor tok_scale) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 && x.stride(0) % 8 == 0, "x: bf16 rows");
+  TORCH_CHECK(xq.is_contiguous() && xq.element_size() == 1 && xq.numel() * 2 == x.numel(), "xq: contiguous bytes [T, K/2]");
+  TORCH_CHECK(sf.is_contiguous() && sf.element_size() == 1 &&
+              (size_t)sf.numel() >= fllm::mx_act_scale_bytes((int)x.size(0), (int)x.size(1), 2), "sf: too small");
+  TORCH_CHECK(tok_scale.is_contiguous() && tok_scale.scalar_type() == at::kFloat && tok_scale.numel() >= x.size(0), "tok_scale: fp32 [T]");
+  c10::cuda::CUDAGuard guard(x.device());
+  fllm::quant_nvfp4(x.data_ptr(), x.stride(0), xq.data_ptr(), sf.data_ptr(), tok_scale.data_ptr<float>(), (int)x.size(0),
+                    (int)x.size(1), cur_stream());
+}
 
-// wq: e4m3 bytes [N, K] (a4 = 0) or e2m1 codes [N, K/2] (a4 = 1); sfa: weight scale atoms [ceil(N/128), K/128, 512]
-int64_t linear_mx(const Tensor& xq, const Tensor& sfb, const Tensor& wq, const Tensor& sfa, int64_t a4, double alpha,
-                  const optional<Tensor>& bias, Tensor y, const optional<Tensor>& workspace, const optional<Tensor>& status) {
+int64_t mx_act_scale_bytes(int64_t T, int64_t K, int64_t kind) { return (int64_t)fllm::mx_act_scale_bytes((int)T, (int)K, (int)kind); }
+
+// kind 0: wq e4m3 [N, K], xq e4m3 [T, K]; kind 1: wq e2m1 codes [N, K/2], xq e4m3 [T, K]; kind 2: both e2m1 codes.
+// sfa: weight scale atoms [ceil(N/128), K/128 (K/64 for kind 2), 512]
+int64_t linear_mx(const Tensor& xq, const Tensor& sfb, const Tensor& wq, const Tensor& sfa, int64_t kind, double alpha,
+                  const optional<Tensor>& tok_scale, const optional<Tensor>& bias, Tensor y, const optional<Tensor>& workspace,
+                  const optional<Tensor>& status) {
   TORCH_CHECK(xq.is_cuda() && xq.is_contiguous() && wq.is_contiguous() && xq.element_size() == 1 && wq.element_size() == 1 &&
               xq.dim() == 2 && wq.dim() == 2, "xq, wq: contiguous byte matrices");
-  const int64_t T = xq.size(0), K = xq.size(1), N = wq.size(0);
-  TORCH_CHECK(wq.size(1) * (a4 ? 2 : 1) == K && K % 128 == 0, "K mismatch (K must be a multiple of 128)");
-  TORCH_CHECK(sfa.is_contiguous() && sfa.element_size() == 1 && sfa.numel() == ((N + 127) / 128) * (K / 128) * 512, "sfa: [ceil(N/128), K/128, 512]");
+  TORCH_CHECK(kind >= 0 && kind <= 2, "kind: 0, 1 or 2");
+  const int64_t T = xq.size(0), K = xq.size(1) * (kind == 2 ? 2 : 1), N = wq.size(0);
+  const int64_t atom_k = kind == 2 ? 64 : 128;
+  TORCH_CHECK(wq.size(1) * (kind == 0 ? 1 : 2) == K && K % (kind == 2 ? 256 : 128) == 0, "K mismatch (multiple of 128; 256 for NVFP4)");
+  TORCH_CHECK(sfa.is_contiguous() && sfa.element_size() == 1 && sfa.numel() == ((N + 127) / 128) * (K / atom_k) * 512, "sfa: [ceil(N/128), K/atom, 512]");
   TORCH_CHECK(sfb.is_contiguous() && sfb.element_size() == 1 &&
-              (size_t)sfb.numel() >= fllm::mx_act_scale_bytes((int)T, (int)K), "sfb: too small");
+              (size_t)sfb.numel() >= fllm::mx_act_scale_bytes((int)T, (int)K, (int)kind), "sfb: too small");
   TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.stride(1) == 1 && y.size(0) == T && y.size(1) == N, "y: [T, N] bf16");
+  const float* ts = nullptr;
+  if (tok_scale.has_value() && tok_scale->defined()) {
+    TORCH_CHECK(tok_scale->scalar_type() == at::kFloat && tok_scale->is_contiguous() && tok_scale->numel() >= T, "tok_scale: fp32 [T]");
+    ts = tok_scale->data_ptr<float>();
+  }
   c10::cuda::CUDAGuard guard(xq.device());
   const void* b = bias.has_value() && bias->defined() ? bias->data_ptr() : nullptr;
   int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
@@ -90,8 +111,8 @@ int64_t linear_mx(const Tensor& xq, const Tensor& sfb, const Tensor& wq, const T
     ws = static_cast<char*>(workspace->data_ptr()) + (64 << 10);
     ws_bytes = workspace->numel() * workspace->element_size() - (64 << 10);
   }
-  return fllm::linear_mx(xq.data_ptr(), sfb.data_ptr(), wq.data_ptr(), sfa.data_ptr(), (int)a4, (float)alpha, b, y.data_ptr(),
-                         y.stride(0), (int)T, (int)N, (int)K, ws, ws_bytes, st, cur_stream());
+  return fllm::linear_mx(xq.data_ptr(), sfb.data_ptr(), wq.data_ptr(), sfa.data_ptr(), (int)kind, (float)alpha, ts, b,
+                         y.data_ptr(), y.stride(0), (int)T, (int)N, (int)K, ws, ws_bytes, st, cur_stream());
 }
 
 void w4_dequant(const Tensor& codes, const Tensor& scales, int64_t fmt, double alpha, Tensor out) {
@@ -108,7 +129,8 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("linear_fp8_block(Tensor xq, Tensor sx, Tensor wq, Tensor sw, Tensor? bias, Tensor(a!) y, Tensor? status) -> int", &linear_fp8_block);
   m.def("linear_w4a16(Tensor x, Tensor codes, Tensor scales, int fmt, float alpha, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status) -> int", &linear_w4a16);
   m.def("quant_mx(Tensor x, Tensor(a!) xq, Tensor(b!) sf) -> ()", &quant_mx);
-  m.def("mx_act_scale_bytes(int T, int K) -> int", &mx_act_scale_bytes);
-  m.def("linear_mx(Tensor xq, Tensor sfb, Tensor wq, Tensor sfa, int a4, float alpha, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status) -> int", &linear_mx);
+  m.def("quant_nvfp4(Tensor x, Tensor(a!) xq, Tensor(b!) sf, Tensor(c!) tok_scale) -> ()", &quant_nvfp4);
+  m.def("mx_act_scale_bytes(int T, int K, int kind) -> int", &mx_act_scale_bytes);
+  m.def("linear_mx(Tensor xq, Tensor sfb, Tensor wq, Tensor sfa, int kind, float alpha, Tensor? tok_scale, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status) -> int", &linear_mx);
   m.def("w4_dequant(Tensor codes, Tensor scales, int fmt, float alpha, Tensor(a!) out) -> ()", &w4_dequant);
 }

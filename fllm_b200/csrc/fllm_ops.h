@@ -98,15 +98,17 @@ void* symm_import(const unsigned char in[64]);
 void symm_close(void* p);
 
 // ---- block-scaled FP8 ------------------------------------------------------------------
-// Block-scaled MX GEMM (tcgen05 kind::mxf8f6f4.block_scale): e4m3 activations x e4m3 or packed e2m1 weights, one
-// e8m0 scale per 32 values on both sides, scale factors in 512-byte atoms (128 rows x 4 K slices). The token tile
-// (16 / 32 / 64 / 128) is a function of T alone, so the quantiser and the GEMM agree on the atom grouping.
+// Block-scaled GEMMs (tcgen05 kind::mxf8f6f4 / kind::mxf4nvf4 .block_scale). kind 0: e4m3 weights, kind 1: packed
+// e2m1 weights, both with e4m3 activations and one e8m0 scale per 32 values; kind 2: NVFP4 on both sides (packed
+// e2m1, one e4m3 scale per 16, tensor scale x per-token scale). Scale factors travel in 512-byte atoms (128 rows x
+// 4 scales). The token tile (16 / 32 / 64 / 128) is a function of T alone, so quantiser and GEMM agree on the atoms.
 int mx_token_tile(int T);
-size_t mx_act_scale_bytes(int T, int K);
+size_t mx_act_scale_bytes(int T, int K, int kind);
 void quant_mx(const void* x, long long ldx, void* xq, void* sf, int T, int K, cudaStream_t s);
-int linear_mx(const void* xq, const void* sfb, const void* wq, const void* sfa, int a4, float alpha, const void* bias,
-              void* y, long long ldy, int T, int N, int K, void* workspace, size_t workspace_bytes, int* status,
-              cudaStream_t stream);
+void quant_nvfp4(const void* x, long long ldx, void* xq, void* sf, float* tok_scale, int T, int K, cudaStream_t s);
+int linear_mx(const void* xq, const void* sfb, const void* wq, const void* sfa, int kind, float alpha,
+              const float* tok_scale, const void* bias, void* y, long long ldy, int T, int N, int K, void* workspace,
+              size_t workspace_bytes, int* status, cudaStream_t stream);
 void quant_fp8_1x128(const void* x, long long ldx, void* xq, float* sx, int tokens, int K, cudaStream_t s);
 int linear_fp8_block(const void* xq, const float* sx, const void* wq, const float* sw, const void* bias, void* y,
                      long long ldy, int T, int N, int K, int* status, cudaStream_t stream);

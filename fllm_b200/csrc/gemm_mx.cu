@@ -24,8 +24,15 @@
 // tiles split K over grid.z (fp32 partial sums + a reduce kernel). Warp roles and TMA staging follow
 // gemm_fp8.cu; every wait is bounded and reports through the status word.
 //
+// A third kind runs NVFP4 on both sides (kind::mxf4nvf4.block_scale.block16): packed e2m1 codes for weights and
+// activations (256 values of K per 128-byte row, so a stage carries twice the K of the 8-bit kinds), one e4m3
+// scale per 16 values (four per row per MMA of K = 64: a whole atom per MMA), the weight's tensor scale and a
+// per-token activation scale applied in the epilogue. The activation quantiser (quant_nvfp4_kernel) derives the
+// token scale from the token's largest magnitude, so no calibration pass is needed.
+//
 // Reference counterparts: rust/engine/cuda/nvfp4.cu:132-307 (mma.sync block-scaled FP4 for GeForce
 // Blackwell; the data-centre parts fall back to W4A16 Marlin there), rust/engine/cuda/mxfp4_moe.cu.
+#include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
 #include <algorithm>
@@ -37,8 +44,6 @@
 namespace fllm {
 
 constexpr int MX_BM = 128;
-constexpr int MX_BK = 128;       // values of K per stage = one 128-byte row of shared memory for 8-bit and unpacked 4-bit
-constexpr int MX_UMMA_K = 32;
 constexpr int kMxThreads = 192;
 constexpr int kMxAtomBytes = 512;
 
@@ -52,21 +57,30 @@ struct MxArgs {
   const uint8_t* sfa;            // [m_tiles][k_blocks][512]
   const uint8_t* sfb;            // [n_tiles][k_blocks][512]
   float alpha;
+  const float* tok_scale;        // [N] per-token factor (NVFP4 activations), or null
   const __nv_bfloat16* bias;
   int* status;
 };
 
-template <int BN>
+// KIND: 0 = e4m3 weights, 1 = packed e2m1 weights unpacked by TMA (both kind::mxf8f6f4, e8m0 scales per 32,
+// 128 values of K per stage), 2 = packed e2m1 on both sides (kind::mxf4nvf4, e4m3 scales per 16, 256 per stage).
+constexpr int kMxKindE4M3 = 0, kMxKindE2M1A8 = 1, kMxKindNvf4 = 2;
+
+template <int BN, int KIND>
 struct MxSmem {
-  static constexpr int kABytes = MX_BM * MX_BK;
-  static constexpr int kBBytes = BN * MX_BK;
+  static constexpr int kABytes = MX_BM * 128;                   // 128-byte rows in shared memory for every kind
+  static constexpr int kBBytes = BN * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStageK = KIND == kMxKindNvf4 ? 256 : 128;
+  static constexpr int kAtoms = KIND == kMxKindNvf4 ? 4 : 1;     // scale atoms per operand per stage
   static constexpr int kStages = BN <= 64 ? 4 : 6;
   static constexpr int kAccCols = BN < 32 ? 32 : BN;
-  static constexpr int kTmemCols = kAccCols + 16 <= 64 ? 64 : (kAccCols + 16 <= 128 ? 128 : 256);
-  static constexpr int kSfBytes = kStages * 2 * kMxAtomBytes;
+  static constexpr int kSfCols = 2 * 8 * kAtoms;                // two buffers of (A, B) x 4 columns per atom
+  static constexpr int kTmemCols = kAccCols + kSfCols <= 64 ? 64 : (kAccCols + kSfCols <= 128 ? 128 : 256);
+  static constexpr int kSfBytes = kStages * 2 * kAtoms * kMxAtomBytes;
   static constexpr int kTotal = kStages * kStageBytes + kSfBytes + 256 + 1024;
   static_assert(4 * 32 * 32 * 2 <= kABytes, "the epilogue staging reuses the first weight stage");
+  static_assert(kAccCols + kSfCols <= 256, "tensor memory columns");
 };
 
 // Shared-memory descriptor of one scale-factor atom for tcgen05.cp: K-major, no swizzle, 8-row x 16-byte
@@ -83,10 +97,11 @@ __device__ __forceinline__ void tc_cp_sf(uint32_t tmem_dst, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(sdesc) : "memory");
 }
 
-// Instruction descriptor of the block-scaled kinds: fp32 accumulate, K-major operands, e8m0 scales.
-// a_fmt / b_fmt: 0 e4m3, 1 e5m2, 5 e2m1. The scale-factor ids (bits 29-30 for A, 4-5 for B) are OR-ed in per MMA.
-__host__ __device__ constexpr uint32_t make_idesc_mx(int M, int N, int a_fmt, int b_fmt) {
-  return ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(N >> 3) << 17) | (1u << 23) |
+// Instruction descriptor of the block-scaled kinds: fp32 accumulate, K-major operands. kind::mxf8f6f4 formats:
+// 0 e4m3, 1 e5m2, 5 e2m1; kind::mxf4nvf4: 1 e2m1. Bit 23: the scales are e8m0 (set) or e4m3 (clear). The
+// scale-factor ids (bits 29-30 for A, 4-5 for B) are OR-ed in per MMA.
+__host__ __device__ constexpr uint32_t make_idesc_mx(int M, int N, int a_fmt, int b_fmt, int e8m0) {
+  return ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)e8m0 << 23) |
          ((uint32_t)(M >> 4) << 24);
 }
 
@@ -100,6 +115,16 @@ __device__ __forceinline__ void tc_mma_mx(uint32_t tmem_d, uint64_t desc_a, uint
       : "memory");
 }
 
+__device__ __forceinline__ void tc_mma_nvf4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -107,10 +132,11 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
       : "memory");
 }
 
-template <int BN, bool A4>
+template <int BN, int KIND>
 __global__ void __launch_bounds__(kMxThreads, BN <= 64 ? 2 : 1)
 gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const MxArgs p) {
-  using S = MxSmem<BN>;
+  using S = MxSmem<BN, KIND>;
+  constexpr int SF_STAGE = 2 * S::kAtoms * kMxAtomBytes;      // bytes of scale factors per stage (A atoms, then B atoms)
   constexpr int STAGES = S::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -149,36 +175,46 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       uint32_t phase = 0;
       for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) break;
-        // a packed 4-bit tile is counted by the bytes that leave global memory, not by the padded bytes it fills
-        mbar_expect_tx(&full_bar[stage], (A4 ? S::kABytes / 2 : S::kABytes) + S::kBBytes + 2 * kMxAtomBytes);
-        tma_load_2d(sA + stage * S::kABytes, &tma_a, &full_bar[stage], kb * MX_BK, m_idx * MX_BM);
-        tma_load_2d(sB + stage * S::kBBytes, &tma_b, &full_bar[stage], kb * MX_BK, n_idx * BN);
-        bulk_load_1d(sSF + stage * 2 * kMxAtomBytes, p.sfa + ((size_t)m_idx * p.k_blocks + kb) * kMxAtomBytes,
-                     kMxAtomBytes, &full_bar[stage]);
-        bulk_load_1d(sSF + stage * 2 * kMxAtomBytes + kMxAtomBytes,
-                     p.sfb + ((size_t)n_idx * p.k_blocks + kb) * kMxAtomBytes, kMxAtomBytes, &full_bar[stage]);
+        // a 4-bit tile that TMA unpacks is counted by the bytes that leave global memory, not by the padded bytes it fills
+        mbar_expect_tx(&full_bar[stage], (KIND == kMxKindE2M1A8 ? S::kABytes / 2 : S::kABytes) + S::kBBytes + SF_STAGE);
+        // x coordinates are in elements of the tensor map: K values for the 8-bit and unpacking maps, bytes for packed codes
+        const int xa = KIND == kMxKindNvf4 ? kb * 128 : kb * S::kStageK;
+        tma_load_2d(sA + stage * S::kABytes, &tma_a, &full_bar[stage], xa, m_idx * MX_BM);
+        tma_load_2d(sB + stage * S::kBBytes, &tma_b, &full_bar[stage], xa, n_idx * BN);
+        bulk_load_1d(sSF + stage * SF_STAGE, p.sfa + ((size_t)m_idx * p.k_blocks + kb) * (SF_STAGE / 2), SF_STAGE / 2,
+                     &full_bar[stage]);
+        bulk_load_1d(sSF + stage * SF_STAGE + SF_STAGE / 2, p.sfb + ((size_t)n_idx * p.k_blocks + kb) * (SF_STAGE / 2),
+                     SF_STAGE / 2, &full_bar[stage]);
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_mx(MX_BM, BN, A4 ? 5 : 0, 0);
-      const uint32_t tmem_sf = tmem_base + S::kAccCols;       // two buffers of 8 columns: A scales, B scales
+      constexpr uint32_t idesc = KIND == kMxKindNvf4 ? make_idesc_mx(MX_BM, BN, 1, 1, 0)
+                                                     : make_idesc_mx(MX_BM, BN, KIND == kMxKindE2M1A8 ? 5 : 0, 0, 1);
+      constexpr int SFC = 4 * S::kAtoms;                      // columns of one operand's scales per buffer
+      const uint32_t tmem_sf = tmem_base + S::kAccCols;       // two buffers: A scales, then B scales
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t sf_cols = tmem_sf + ((kb - kb0) & 1) * 8;
-        tc_cp_sf(sf_cols, make_sf_desc(smem_u32(sSF + stage * 2 * kMxAtomBytes)));
-        tc_cp_sf(sf_cols + 4, make_sf_desc(smem_u32(sSF + stage * 2 * kMxAtomBytes + kMxAtomBytes)));
+        const uint32_t sf_cols = tmem_sf + ((kb - kb0) & 1) * 2 * SFC;
+#pragma unroll
+        for (int a = 0; a < 2 * S::kAtoms; ++a)
+          tc_cp_sf(sf_cols + 4 * a, make_sf_desc(smem_u32(sSF + stage * SF_STAGE + a * kMxAtomBytes)));
         const uint64_t da = make_smem_desc_sw128(smem_u32(sA + stage * S::kABytes));
         const uint64_t db = make_smem_desc_sw128(smem_u32(sB + stage * S::kBBytes));
 #pragma unroll
-        for (int k = 0; k < MX_BK / MX_UMMA_K; ++k)
-          tc_mma_mx(tmem_base, da + 2 * k, db + 2 * k, idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4), sf_cols,
-                    sf_cols + 4, (kb > kb0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) {                         // four MMAs of 32 bytes of K each
+          const uint32_t acc = (kb > kb0 || k > 0) ? 1u : 0u;
+          if constexpr (KIND == kMxKindNvf4)                  // K = 64: a whole atom (four scales per row) per MMA
+            tc_mma_nvf4(tmem_base, da + 2 * k, db + 2 * k, idesc, sf_cols + 4 * k, sf_cols + SFC + 4 * k, acc);
+          else                                                // K = 32: byte k of the atom's columns
+            tc_mma_mx(tmem_base, da + 2 * k, db + 2 * k, idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4), sf_cols,
+                      sf_cols + SFC, acc);
+        }
         tc_commit(&empty_bar[stage]);
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
@@ -209,7 +245,10 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           continue;
         }
 #pragma unroll
-        for (int c = 0; c < CH; ++c) stg[c * 32 + lane] = __float2bfloat16(__uint_as_float(r[c]) * p.alpha + bias_m);
+        for (int c = 0; c < CH; ++c) {
+          const float ts = p.tok_scale ? p.tok_scale[min(n_base + c0 + c, p.N - 1)] : 1.f;
+          stg[c * 32 + lane] = __float2bfloat16(__uint_as_float(r[c]) * (p.alpha * ts) + bias_m);
+        }
         __syncwarp();
         const int f0 = 8 * (lane & 3);
         const int mm0 = m_idx * MX_BM + q * 32 + f0;
@@ -232,7 +271,8 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 
 // out[n][m] = bf16(alpha * sum_s ws[s][n][m] + bias[m])
 __global__ void mx_splitk_reduce_kernel(const float* __restrict__ ws, int splits, int rows, int cols, long long ldc,
-                                        float alpha, const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out) {
+                                        float alpha, const float* __restrict__ tok_scale,
+                                        const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t n = (size_t)rows * cols;
@@ -247,6 +287,7 @@ __global__ void mx_splitk_reduce_kernel(const float* __restrict__ ws, int splits
   const int c = (int)(i4 - (size_t)r * cols);
   float b[4] = {0.f, 0.f, 0.f, 0.f};
   if (bias) for (int i = 0; i < 4; ++i) b[i] = __bfloat162float(bias[c + i]);
+  if (tok_scale) alpha *= tok_scale[r];
   uint2 o;
   o.x = pack_bf16x2(acc.x * alpha + b[0], acc.y * alpha + b[1]);
   o.y = pack_bf16x2(acc.z * alpha + b[2], acc.w * alpha + b[3]);
@@ -291,11 +332,79 @@ __global__ void quant_mx_kernel(const __nv_bfloat16* __restrict__ x, long long l
   if ((lane & 7) == 0) atom[lane >> 3] = (uint8_t)(e + 127);
 }
 
+// x bf16 [T][K] -> packed e2m1 codes [T][K/2] + e4m3 scales per 16 values in atoms of `bn`-token tiles
+// (sf[(t / bn) * (K / 64) + k64][512]) + one fp32 scale per token: value = code * block_scale * tok_scale.
+// tok_scale = (largest magnitude of the token) / (6 * 448), so the block scales use the whole e4m3 range.
+// One CTA per token; a thread owns 16-value groups g = tid, tid + 256, ... (at most 8: K <= 32768).
+__global__ void __launch_bounds__(256)
+quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ xq, uint8_t* __restrict__ sf,
+                   float* __restrict__ tok_scale, int tokens, int K, int bn) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[8];
+  const int t = blockIdx.x;
+  const int groups = K / 16, k64_n = K / 64;
+  const int r = t % bn;
+  uint8_t* atoms = sf + (size_t)(t / bn) * k64_n * kMxAtomBytes + (r & 31) * 16 + (r >> 5) * 4;
+  if (t >= tokens) {                                     // padding rows of the last tile: zero scales
+    for (int g = threadIdx.x; g < groups; g += 256) atoms[(size_t)(g >> 2) * kMxAtomBytes + (g & 3)] = 0;
+    return;
+  }
+  constexpr int MAXG = 8;
+  uint4 v[MAXG][2];
+  float gmax[MAXG];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXG; ++i) {
+    const int g = threadIdx.x + i * 256;
+    gmax[i] = 0.f;
+    if (g < groups) {
+      const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * ldx + g * 16);
+      v[i][0] = src[0];
+      v[i][1] = src[1];
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float2 f = unpack_bf16x2(w[j]);
+        gmax[i] = fmaxf(gmax[i], fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
+      amax = fmaxf(amax, gmax[i]);
+    }
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+  const float ts = amax > 0.f ? amax / (6.f * 448.f) : 1.f;
+  if (threadIdx.x == 0) tok_scale[t] = ts;
+#pragma unroll
+  for (int i = 0; i < MAXG; ++i) {
+    const int g = threadIdx.x + i * 256;
+    if (g >= groups) continue;
+    const __nv_fp8_storage_t sb = __nv_cvt_float_to_fp8(gmax[i] / 6.f / ts, __NV_SATFINITE, __NV_E4M3);
+    const float sbf = __half2float(__half(__nv_cvt_fp8_to_halfraw(sb, __NV_E4M3)));
+    const float inv = sbf > 0.f ? 1.f / (sbf * ts) : 0.f;
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(v[i]);
+    uint32_t out[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float2 f = unpack_bf16x2(w[j]);
+      const uint32_t c2 = __nv_cvt_float2_to_fp4x2(make_float2(f.x * inv, f.y * inv), __NV_E2M1, cudaRoundNearest);
+      out[j >> 2] |= (c2 & 0xFFu) << (8 * (j & 3));
+    }
+    *reinterpret_cast<uint2*>(xq + (size_t)t * (K / 2) + g * 8) = make_uint2(out[0], out[1]);
+    atoms[(size_t)(g >> 2) * kMxAtomBytes + (g & 3)] = sb;
+  }
+}
+
 int mx_token_tile(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128; }
 
-size_t mx_act_scale_bytes(int T, int K) {
+// Bytes of the activation scale atoms for T tokens: one e8m0 per 32 values (kind 0 / 1) or one e4m3 per 16 (kind 2).
+size_t mx_act_scale_bytes(int T, int K, int kind) {
   const int bn = mx_token_tile(T);
-  return (size_t)((T + bn - 1) / bn) * (K / 128) * kMxAtomBytes;
+  return (size_t)((T + bn - 1) / bn) * (K / (kind == kMxKindNvf4 ? 64 : 128)) * kMxAtomBytes;
 }
 
 void quant_mx(const void* x, long long ldx, void* xq, void* sf, int T, int K, cudaStream_t s) {
@@ -308,33 +417,56 @@ void quant_mx(const void* x, long long ldx, void* xq, void* sf, int T, int K, cu
              (uint8_t*)xq, (uint8_t*)sf, T, padded, K, bn);
 }
 
-template <int BN, bool A4>
-static void launch_mx(const CUtensorMap& ta, const CUtensorMap& tb, const MxArgs& a, cudaStream_t s) {
-  using S = MxSmem<BN>;
-  static bool configured[kMaxDevices] = {};
-  if (first_call_on_device(configured)) {
-    cuda_check(cudaFuncSetAttribute(gemm_mx_kernel<BN, A4>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal),
-               "cudaFuncSetAttribute(gemm_mx_kernel)");
-  }
-  launch_pdl(gemm_mx_kernel<BN, A4>, dim3(a.n_tiles, a.m_tiles, a.k_splits), dim3(kMxThreads), (size_t)S::kTotal, s, ta, tb, a);
+void quant_nvfp4(const void* x, long long ldx, void* xq, void* sf, float* tok_scale, int T, int K, cudaStream_t s) {
+  if (T <= 0) return;
+  if (K % 256 || K > 32768 || (ldx & 7)) throw std::runtime_error("quant_nvfp4: K must be a multiple of 256, at most 32768, rows 16-byte aligned");
+  const int bn = mx_token_tile(T);
+  const int padded = (T + bn - 1) / bn * bn;
+  launch_pdl(quant_nvfp4_kernel, dim3((unsigned)padded), dim3(256), 0, s, (const __nv_bfloat16*)x, ldx, (uint8_t*)xq,
+             (uint8_t*)sf, tok_scale, T, K, bn);
 }
 
-// y[T][N] = alpha * dequant(xq, sfb) * dequant(wq, sfa)^T (+ bias). a4: the weights are packed e2m1 codes.
-int linear_mx(const void* xq, const void* sfb, const void* wq, const void* sfa, int a4, float alpha, const void* bias,
-              void* y, long long ldy, int T, int N, int K, void* workspace, size_t workspace_bytes, int* status,
-              cudaStream_t stream) {
+template <int BN, int KIND>
+static void launch_mx(const CUtensorMap& ta, const CUtensorMap& tb, const MxArgs& a, cudaStream_t s) {
+  using S = MxSmem<BN, KIND>;
+  static bool configured[kMaxDevices] = {};
+  if (first_call_on_device(configured)) {
+    cuda_check(cudaFuncSetAttribute(gemm_mx_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal),
+               "cudaFuncSetAttribute(gemm_mx_kernel)");
+  }
+  launch_pdl(gemm_mx_kernel<BN, KIND>, dim3(a.n_tiles, a.m_tiles, a.k_splits), dim3(kMxThreads), (size_t)S::kTotal, s, ta, tb, a);
+}
+
+template <int KIND>
+static void launch_mx_bn(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const MxArgs& a, cudaStream_t s) {
+  switch (bn) {
+    case 16: launch_mx<16, KIND>(ta, tb, a, s); break;
+    case 32: launch_mx<32, KIND>(ta, tb, a, s); break;
+    case 64: launch_mx<64, KIND>(ta, tb, a, s); break;
+    default: launch_mx<128, KIND>(ta, tb, a, s); break;
+  }
+}
+
+// y[T][N] = alpha * tok_scale[t] * dequant(xq, sfb) * dequant(wq, sfa)^T (+ bias).
+// kind 0: e4m3 weights [N][K] x e4m3 activations [T][K]; kind 1: e2m1 weights [N][K/2] x e4m3 activations;
+// kind 2: e2m1 weights [N][K/2] x e2m1 activations [T][K/2] with e4m3 scales per 16 (NVFP4).
+int linear_mx(const void* xq, const void* sfb, const void* wq, const void* sfa, int kind, float alpha,
+              const float* tok_scale, const void* bias, void* y, long long ldy, int T, int N, int K, void* workspace,
+              size_t workspace_bytes, int* status, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
-  if (K % 128 || N % 8 || (ldy & 7)) throw std::runtime_error("linear_mx: K % 128, N % 8 and 16-byte output rows required");
+  if (kind < 0 || kind > 2) throw std::runtime_error("linear_mx: kind must be 0, 1 or 2");
+  const int stage_k = kind == kMxKindNvf4 ? 256 : 128;
+  if (K % stage_k || N % 8 || (ldy & 7)) throw std::runtime_error("linear_mx: K % 128 (256 for NVFP4), N % 8 and 16-byte output rows required");
   if ((reinterpret_cast<uintptr_t>(wq) & 31) || (reinterpret_cast<uintptr_t>(sfa) & 15) || (reinterpret_cast<uintptr_t>(sfb) & 15))
     throw std::runtime_error("linear_mx: operands must be 32-byte (weights) and 16-byte (scales) aligned");
   MxArgs a{};
   a.M = N; a.N = T; a.K = K;
-  a.m_tiles = (N + MX_BM - 1) / MX_BM; a.k_blocks = K / MX_BK;
+  a.m_tiles = (N + MX_BM - 1) / MX_BM; a.k_blocks = K / stage_k;
   const int bn = mx_token_tile(T);
   a.n_tiles = (T + bn - 1) / bn;
   a.ldc = ldy; a.out = reinterpret_cast<__nv_bfloat16*>(y);
   a.sfa = reinterpret_cast<const uint8_t*>(sfa); a.sfb = reinterpret_cast<const uint8_t*>(sfb);
-  a.alpha = alpha; a.bias = reinterpret_cast<const __nv_bfloat16*>(bias); a.status = status;
+  a.alpha = alpha; a.tok_scale = tok_scale; a.bias = reinterpret_cast<const __nv_bfloat16*>(bias); a.status = status;
   // Few tiles cannot pull the whole HBM bandwidth: split K over grid.z until the machine is full.
   const int slots = sm_count() * (bn <= 64 ? 2 : 1);
   const int tiles = a.m_tiles * a.n_tiles;
@@ -344,23 +476,19 @@ int linear_mx(const void* xq, const void* sfb, const void* wq, const void* sfa, 
   a.kb_per_split = (a.k_blocks + splits - 1) / splits;
   a.k_splits = (a.k_blocks + a.kb_per_split - 1) / a.kb_per_split;
   a.ws = reinterpret_cast<float*>(workspace);
-  CUtensorMap ta = a4 ? make_tmap_2d(wq, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 1, N, K, K / 2, MX_BM, MX_BK, true)
-                      : make_tmap_2d(wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, MX_BM, MX_BK, true);
-  CUtensorMap tb = make_tmap_2d(xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, T, K, K, bn, MX_BK, true);
-#define FLLM_MX_LAUNCH(BN_)                                                    \
-  if (a4) launch_mx<BN_, true>(ta, tb, a, stream);                            \
-  else launch_mx<BN_, false>(ta, tb, a, stream)
-  switch (bn) {
-    case 16: FLLM_MX_LAUNCH(16); break;
-    case 32: FLLM_MX_LAUNCH(32); break;
-    case 64: FLLM_MX_LAUNCH(64); break;
-    default: FLLM_MX_LAUNCH(128); break;
-  }
-#undef FLLM_MX_LAUNCH
+  CUtensorMap ta, tb;
+  if (kind == kMxKindE2M1A8) ta = make_tmap_2d(wq, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 1, N, K, K / 2, MX_BM, 128, true);
+  else if (kind == kMxKindNvf4) ta = make_tmap_2d(wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, MX_BM, 128, true);
+  else ta = make_tmap_2d(wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, MX_BM, 128, true);
+  if (kind == kMxKindNvf4) tb = make_tmap_2d(xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, T, K / 2, K / 2, bn, 128, true);
+  else tb = make_tmap_2d(xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, T, K, K, bn, 128, true);
+  if (kind == kMxKindE4M3) launch_mx_bn<kMxKindE4M3>(bn, ta, tb, a, stream);
+  else if (kind == kMxKindE2M1A8) launch_mx_bn<kMxKindE2M1A8>(bn, ta, tb, a, stream);
+  else launch_mx_bn<kMxKindNvf4>(bn, ta, tb, a, stream);
   if (a.k_splits > 1) {
     const size_t n = (size_t)T * N;
     launch_pdl(mx_splitk_reduce_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, stream,
-               (const float*)a.ws, a.k_splits, T, N, ldy, alpha, a.bias, a.out);
+               (const float*)a.ws, a.k_splits, T, N, ldy, alpha, tok_scale, a.bias, a.out);
     return 2;
   }
   return 1;

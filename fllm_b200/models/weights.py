@@ -153,8 +153,10 @@ def _randn(shape, gen, device, dtype, std=0.02):
 
 def pack_layer(lw: LayerWeights, fmt: str) -> None:
     """Replace the big matrices of one layer by their packed form, in place: ``fp8_block`` (e4m3 codes + one fp32
-    scale per 128 x 128), ``nvfp4`` (e2m1 + e4m3 scale per 16 + tensor scale) or ``mxfp4`` (e2m1 + e8m0 scale per
-    32; for mixture-of-experts layers only the expert stacks are packed, attention stays bf16 as in gpt-oss).
+    scale per 128 x 128), ``nvfp4`` (e2m1 + e4m3 scale per 16 + tensor scale), ``mxfp4`` (e2m1 + e8m0 scale per
+    32; for mixture-of-experts layers only the expert stacks are packed, attention stays bf16 as in gpt-oss), or
+    the block-scaled tensor-core pairs ``mxfp8`` / ``mxfp4_a8`` (MXFP8 / MXFP4 weights x MXFP8 activations) and
+    ``nvfp4_a4`` (NVFP4 weights x NVFP4 activations).
     Matrices whose shape the format cannot tile stay bf16."""
     if fmt in ("bf16", "", None):
         return
@@ -177,7 +179,22 @@ def pack_layer(lw: LayerWeights, fmt: str) -> None:
             if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 64 == 0 and w.shape[0] % 8 == 0:
                 setattr(lw, name, Fp4Weight.from_dense(w, fmt))
         return
-    raise ValueError(f"random initialisation in weight format {fmt!r} is not available (bf16, fp8_block, nvfp4, mxfp4)")
+    if fmt in ("mxfp8", "mxfp4_a8", "nvfp4_a4"):
+        # block-scaled tensor-core formats: MXFP8 or MXFP4 weights with activations quantised to MXFP8 on the fly,
+        # or NVFP4 weights with activations quantised to NVFP4 per token
+        from ..ops.mx import MxWeight, Nvfp4TcWeight
+        if lw.exp_gate_up is not None:
+            return
+        for name in ("wqkv", "wo", "w_gate_up", "w_down"):
+            w = getattr(lw, name, None)
+            if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 256 == 0 and w.shape[0] % 8 == 0:
+                if fmt == "nvfp4_a4":
+                    setattr(lw, name, Nvfp4TcWeight.from_dense(w))
+                else:
+                    setattr(lw, name, MxWeight.from_dense(w, "mxfp8" if fmt == "mxfp8" else "mxfp4"))
+        return
+    raise ValueError(f"random initialisation in weight format {fmt!r} is not available "
+                     "(bf16, fp8_block, nvfp4, mxfp4, mxfp8, mxfp4_a8, nvfp4_a4)")
 
 
 def init_random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: int = 0,

@@ -2,7 +2,8 @@
 e8m0 power-of-two scale per 32 values along K, multiplied by activations that are quantised on the fly to
 MXFP8 (e4m3 + e8m0 per 32). The product runs on ``tcgen05.mma kind::mxf8f6f4.block_scale``
 (``csrc/gemm_mx.cu``): packed bytes go from HBM through TMA straight into the tensor core, the scales through
-tensor memory; no expansion stage and no scale arithmetic on the ALUs.
+tensor memory; no expansion stage and no scale arithmetic on the ALUs. ``Nvfp4TcWeight`` is the NVFP4 pair of the
+same kernel family (``kind::mxf4nvf4``): e2m1 on both sides, e4m3 scales per 16 values.
 
 The kernel reads scale factors in 512-byte atoms (128 rows x 4 K-slices; byte ``(r % 32) * 16 + (r // 32) * 4
 + j``); ``sf_atoms`` builds them from the row-major scales a checkpoint stores (gpt-oss ``*_scales``,
@@ -13,7 +14,9 @@ from __future__ import annotations
 
 import torch
 
-from .fp4 import MXFP4, Fp4Weight, _unpack_values, quantize_mxfp4
+from .fp4 import MXFP4, NVFP4, Fp4Weight, _e2m1_codes, _pack, _unpack_values, quantize_mxfp4, quantize_nvfp4
+
+KIND_E4M3, KIND_E2M1_A8, KIND_NVFP4 = 0, 1, 2
 
 ATOM = 512
 
@@ -51,6 +54,81 @@ def quantize_act_reference(x: torch.Tensor) -> torch.Tensor:
     q, s = quantize_mxfp8(x)
     T, K = x.shape
     return (q.view(torch.float8_e4m3fn).float().view(T, K // 32, 32) * e8m0_to_float(s).unsqueeze(-1)).view(T, K)
+
+
+def quantize_act_nvfp4(x: torch.Tensor):
+    """Host statement of the device NVFP4 activation quantiser: (codes uint8 [T, K/2], e4m3 scales uint8 [T, K/16],
+    token scales fp32 [T]); value = code * block_scale * token_scale, token_scale = amax(token) / (6 * 448)."""
+    T, K = x.shape
+    xf = x.float()
+    amax = xf.abs().amax(-1)
+    ts = torch.where(amax > 0, amax / (6.0 * 448.0), torch.ones_like(amax))
+    blk = xf.view(T, K // 16, 16)
+    sb = (blk.abs().amax(-1) / 6.0 / ts.unsqueeze(-1)).clamp_max(448.0).to(torch.float8_e4m3fn)
+    sbf = sb.float()
+    inv = torch.where(sbf > 0, 1.0 / (sbf * ts.unsqueeze(-1)), torch.zeros_like(sbf))
+    codes = _e2m1_codes(blk * inv.unsqueeze(-1)).view(T, K)
+    return _pack(codes), sb.view(torch.uint8).contiguous(), ts
+
+
+def dequantize_act_nvfp4(codes: torch.Tensor, scales: torch.Tensor, ts: torch.Tensor) -> torch.Tensor:
+    T = codes.shape[0]
+    K = codes.shape[1] * 2
+    v = _unpack_values(codes).view(T, K // 16, 16) * scales.view(torch.float8_e4m3fn).float().unsqueeze(-1)
+    return v.view(T, K) * ts.view(T, 1)
+
+
+class Nvfp4TcWeight:
+    """NVFP4 weights for the block-scaled tensor-core path (W4A4): the checkpoint's codes [N, K/2], e4m3 scales per
+    16 values and tensor scale, multiplied by activations quantised to NVFP4 per token on the fly
+    (``tcgen05.mma kind::mxf4nvf4.block_scale.block16``). K must be a multiple of 256."""
+
+    def __init__(self, codes: torch.Tensor, scales: torch.Tensor, alpha: float):
+        self.q, self.scales, self.alpha = codes.contiguous(), scales.contiguous(), float(alpha)
+        self.shape = (codes.shape[0], codes.shape[1] * 2)
+        self.device = codes.device
+        self._atoms = None
+
+    @classmethod
+    def from_dense(cls, w: torch.Tensor) -> "Nvfp4TcWeight":
+        return cls(*quantize_nvfp4(w))
+
+    @classmethod
+    def from_fp4(cls, w: Fp4Weight) -> "Nvfp4TcWeight":
+        if w.fmt != NVFP4:
+            raise ValueError("not an NVFP4 weight")
+        return cls(w.codes, w.scales, w.alpha)
+
+    def to(self, device) -> "Nvfp4TcWeight":
+        return Nvfp4TcWeight(self.q.to(device), self.scales.to(device), self.alpha)
+
+    @property
+    def atoms(self) -> torch.Tensor:
+        if self._atoms is None:
+            self._atoms = sf_atoms(self.scales)
+        return self._atoms
+
+    def dense(self) -> torch.Tensor:
+        from .fp4 import dequantize_fp4
+        return dequantize_fp4(self.q, self.scales, NVFP4, self.alpha)
+
+    def nbytes(self) -> int:
+        return self.q.numel() + self.scales.numel()
+
+    def apply(self, ops, x, bias=None, out=None):
+        T, K = x.shape
+        N = self.shape[0]
+        if not x.is_cuda or not hasattr(ops, "k"):                  # PyTorch statement of the same arithmetic
+            y = dequantize_act_nvfp4(*quantize_act_nvfp4(x)) @ self.dense().t()
+            return (y + bias.float() if bias is not None else y).to(x.dtype)
+        xq = torch.empty(T, K // 2, dtype=torch.uint8, device=x.device)
+        sf = torch.empty(ops.k.mx_act_scale_bytes(T, K, KIND_NVFP4), dtype=torch.uint8, device=x.device)
+        ts = torch.empty(T, dtype=torch.float32, device=x.device)
+        ops.k.quant_nvfp4(x if x.stride(1) == 1 else x.contiguous(), xq, sf, ts)
+        y = out if out is not None else torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+        ops.launches += 1 + ops.k.linear_mx(xq, sf, self.q, self.atoms, KIND_NVFP4, self.alpha, ts, bias, y, ops.workspace,
+                                            ops.status)
+        return y
 
 
 class MxWeight:
@@ -99,12 +177,13 @@ class MxWeight:
     def apply(self, ops, x, bias=None, out=None):
         T, K = x.shape
         N = self.shape[0]
-        if not x.is_cuda:                                           # CPU statement of the same arithmetic
+        if not x.is_cuda or not hasattr(ops, "k"):                  # PyTorch statement of the same arithmetic
             y = quantize_act_reference(x) @ self.dense().t()
             return (y + bias.float() if bias is not None else y).to(x.dtype)
         xq = torch.empty(T, K, dtype=torch.uint8, device=x.device)
-        sf = torch.empty(ops.k.mx_act_scale_bytes(T, K), dtype=torch.uint8, device=x.device)
+        sf = torch.empty(ops.k.mx_act_scale_bytes(T, K, KIND_E4M3), dtype=torch.uint8, device=x.device)
         ops.k.quant_mx(x if x.stride(1) == 1 else x.contiguous(), xq, sf)
         y = out if out is not None else torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
-        ops.launches += 1 + ops.k.linear_mx(xq, sf, self.q, self.atoms, int(self.a4), 1.0, bias, y, ops.workspace, ops.status)
+        ops.launches += 1 + ops.k.linear_mx(xq, sf, self.q, self.atoms, KIND_E2M1_A8 if self.a4 else KIND_E4M3, 1.0, None, bias,
+                                            y, ops.workspace, ops.status)
         return y
