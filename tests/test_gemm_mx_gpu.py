@@ -145,5 +145,7 @@ def test_engine_runs_block_scaled_weight_formats(fmt):
             assert eng.ops.check_status() == 0
             out = eng.generate([prompt], SamplingParams(max_tokens=6))[0]     # decode steps (1 token) run the same kernels
             assert len(out) == 6
-    err = (lg[0] - lg[1]).abs().max().item() / (lg[0].abs().max().item() + 1e-6)
-    assert err < (0.08 if fmt != "nvfp4_a4" else 0.15), err          # a value on a rounding boundary of the activation format moves a whole step
+    # a value on a rounding boundary of the activation format moves a whole step (large for 4-bit activations), and
+    # the step travels through the remaining layers: compare the logit rows as vectors
+    err = ((lg[0] - lg[1]).norm() / lg[0].norm()).item()
+    assert err < (0.06 if fmt != "nvfp4_a4" else 0.25), err
