@@ -356,6 +356,12 @@ def main(argv=None) -> None:
         ms = timer(lambda: ops.attention(q, kc, vc, tables, row_seq, pos, hq, hkv, D, D ** -0.5, meta=m))
         print(f"{label:18s} {B:4d} ctx={L} {ms:9.4f} ms  {byts / ms / 1e6:7.0f} GB/s  frac {byts / (hbm * 1e9) / (ms / 1e3):.2f}")
         rows.append({"op": label, "B": B, "ctx": L, "ms": ms, "gbs": byts / ms / 1e6})
+    kc8, vc8 = kc.to(torch.float8_e4m3fn), vc.to(torch.float8_e4m3fn)
+    for label, m in (("attn_dec_tc_e4m3", meta), ("attn_dec_generic_e4m3", None)):
+        ms = timer(lambda: ops.attention(q, kc8, vc8, tables, row_seq, pos, hq, hkv, D, D ** -0.5, meta=m))
+        print(f"{label:18s} {B:4d} ctx={L} {ms:9.4f} ms  {byts / 2 / ms / 1e6:7.0f} GB/s  frac {byts / 2 / (hbm * 1e9) / (ms / 1e3):.2f}")
+        rows.append({"op": label, "B": B, "ctx": L, "ms": ms, "gbs": byts / 2 / ms / 1e6})
+    del kc8, vc8
     # prefill attention: one 2048-token chunk of two 1024-token prompts
     Tq = 2048
     qp = torch.randn(Tq, hq * D, device="cuda", dtype=torch.bfloat16)

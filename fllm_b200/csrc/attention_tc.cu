@@ -21,6 +21,9 @@
 // KV cache layout: [block][kv_head][16][head_dim] bf16 (a head's page is contiguous).
 // Reference counterparts: rust/engine/cuda/attention4.cu:275-495 (GQA-sharing decode with
 // split-KV and merge), rust/engine/cuda/attention3.cu:57-288 (prefill tiles).
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
 #include "fllm_ops.h"
 #include "ptx.cuh"
 #include "tma_host.h"
@@ -82,6 +85,30 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// F16 selects the element type of the 16-bit operands: bf16 (the cache's own type) or f16 (an e4m3 cache is
+// widened to f16, which holds every e4m3 value exactly, with one conversion instruction per pair).
+template <bool F16>
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (F16) mma_f16(d, a, b0, b1);
+  else mma_bf16(d, a, b0, b1);
+}
+template <bool F16>
+__device__ __forceinline__ uint32_t pack_16x2(float lo, float hi) {
+  if constexpr (F16) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  } else {
+    return pack_bf16x2(lo, hi);
+  }
+}
+
 // Row-major tile of rows x D bf16 in shared memory; 16-byte chunk c of row r lives at chunk
 // index (c ^ (r & 7)) so that ldmatrix row fetches hit distinct banks.
 template <int D>
@@ -101,7 +128,7 @@ __device__ __forceinline__ void load_rows_async(__nv_bfloat16* tile, int row0, c
 }
 
 // S[16 x (8*NB)] += Q[16 x D] * K[tokens x D]^T for the NB token blocks starting at row tok0.
-template <int D, int NB>
+template <int D, int NB, bool F16 = false>
 __device__ __forceinline__ void qk_tile(float (&s)[NB][4], const uint32_t (&qf)[D / 16][4],
                                         __nv_bfloat16* ktile, int tok0, int lane) {
   static_assert(NB % 2 == 0, "token blocks are processed in pairs");
@@ -112,14 +139,14 @@ __device__ __forceinline__ void qk_tile(float (&s)[NB][4], const uint32_t (&qf)[
       uint32_t b[4];
       const int j = lane >> 3;
       ldsm_x4(b, tile_ptr<D>(ktile, tok0 + (nb + (j >> 1)) * 8 + (lane & 7), 2 * kk + (j & 1)));
-      mma_bf16(s[nb], qf[kk], b[0], b[1]);
-      mma_bf16(s[nb + 1], qf[kk], b[2], b[3]);
+      mma_16816<F16>(s[nb], qf[kk], b[0], b[1]);
+      mma_16816<F16>(s[nb + 1], qf[kk], b[2], b[3]);
     }
   }
 }
 
 // O[16 x D] += P[16 x (16*KT)] * V[tokens x D] for KT 16-token groups starting at row tok0.
-template <int D, int KT>
+template <int D, int KT, bool F16 = false>
 __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const uint32_t (&pf)[KT][4],
                                         __nv_bfloat16* vtile, int tok0, int lane) {
 #pragma unroll
@@ -129,15 +156,15 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const uint32_t (&p
       uint32_t b[4];
       const int j = lane >> 3;
       ldsm_x4_t(b, tile_ptr<D>(vtile, tok0 + kt * 16 + (j & 1) * 8 + (lane & 7), db + (j >> 1)));
-      mma_bf16(o[db], pf[kt], b[0], b[1]);
-      mma_bf16(o[db + 1], pf[kt], b[2], b[3]);
+      mma_16816<F16>(o[db], pf[kt], b[0], b[1]);
+      mma_16816<F16>(o[db + 1], pf[kt], b[2], b[3]);
     }
   }
 }
 
 // Online-softmax update for the two rows (g, g+8) a thread holds. `lim0/lim1` = number of
 // visible tokens for each row, `beg0/beg1` = first visible token (sliding window).
-template <int NB, int D>
+template <int NB, int D, bool F16 = false>
 __device__ __forceinline__ void softmax_update(float (&s)[NB][4], uint32_t (&pf)[NB / 2][4],
                                                float (&o)[D / 8][4], float (&m)[2], float (&l)[2],
                                                int tok_base, int lane, int lim0, int lim1, int beg0,
@@ -174,8 +201,8 @@ __device__ __forceinline__ void softmax_update(float (&s)[NB][4], uint32_t (&pf)
     const float p2 = exp2f(s[nb][2] - b1), p3 = exp2f(s[nb][3] - b1);
     sum0 += p0 + p1;
     sum1 += p2 + p3;
-    pf[nb >> 1][(nb & 1) * 2 + 0] = pack_bf16x2(p0, p1);
-    pf[nb >> 1][(nb & 1) * 2 + 1] = pack_bf16x2(p2, p3);
+    pf[nb >> 1][(nb & 1) * 2 + 0] = pack_16x2<F16>(p0, p1);
+    pf[nb >> 1][(nb & 1) * 2 + 1] = pack_16x2<F16>(p2, p3);
   }
   l[0] = l[0] * c0 + sum0;
   l[1] = l[1] * c1 + sum1;
@@ -189,22 +216,27 @@ __device__ __forceinline__ void softmax_update(float (&s)[NB][4], uint32_t (&pf)
 }
 
 // ------------------------------------------------------------------------------ decode
-template <int D>
+// KV8: the cache holds e4m3 bytes. Pages arrive raw (half the bytes of a bf16 page); the warp that owns a page
+// widens it to f16 into a private pair of swizzled tiles right before its MMAs.
+template <int D, bool KV8 = false>
 struct DecodeSmem {
   static constexpr int kStages = 3;
   static constexpr int kPageElems = kPage * D;
   static constexpr int kQBytes = 16 * D * 2;
-  static constexpr int kRingBytes = 4 * kStages * 2 * kPageElems * 2;   // 4 warps x stages x (K,V)
+  static constexpr int kPageBytes = kPageElems * (KV8 ? 1 : 2);          // one K or V page as it arrives
+  static constexpr int kWarpRing = kStages * 2 * kPageBytes;             // stages x (K, V)
+  static constexpr int kWarpTiles = KV8 ? 2 * kPageElems * 2 : 0;        // widened K and V tiles
+  static constexpr int kRingBytes = 4 * (kWarpRing + kWarpTiles);
   static constexpr int kMergeBytes = 4 * 16 * D * 4 + 4 * 16 * 2 * 4;
   static constexpr int kTotal = kQBytes + (kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes) + 128;
 };
 
-template <int D>
+template <int D, bool KV8 = false>
 __global__ void __launch_bounds__(128) fa_decode_kernel(const FaParams p) {
-  using S = DecodeSmem<D>;
+  using S = DecodeSmem<D, KV8>;
   extern __shared__ __align__(128) uint8_t smem[];
   __nv_bfloat16* qtile = reinterpret_cast<__nv_bfloat16*>(smem);
-  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem + S::kQBytes);
+  uint8_t* ring = smem + S::kQBytes;
   const int kvh = blockIdx.x, seq = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.group;
@@ -234,6 +266,14 @@ __global__ void __launch_bounds__(128) fa_decode_kernel(const FaParams p) {
     if (r < n_rows) {
       const int qi = r / G, hg = r - qi * G;
       v = *reinterpret_cast<const uint4*>(p.q + (size_t)(q0 + qi) * p.ldq + (size_t)(kvh * G + hg) * D + c * 8);
+      if constexpr (KV8) {                                        // the MMAs run on f16 operands
+        uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack_bf16x2(w[e]);
+          w[e] = pack_16x2<true>(f.x, f.y);
+        }
+      }
     }
     *reinterpret_cast<uint4*>(tile_ptr<D>(qtile, r, c)) = v;
   }
@@ -262,16 +302,27 @@ __global__ void __launch_bounds__(128) fa_decode_kernel(const FaParams p) {
   for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-  __nv_bfloat16* my_ring = ring + (size_t)warp * S::kStages * 2 * S::kPageElems;
+  uint8_t* my_ring = ring + (size_t)warp * (S::kWarpRing + S::kWarpTiles);
+  __nv_bfloat16* my_tiles = reinterpret_cast<__nv_bfloat16*>(my_ring + S::kWarpRing);     // KV8 only
   const int* table = p.block_tables + (size_t)seq * p.max_blocks;
   auto issue = [&](int it) {
     const int pg = pg0 + warp + 4 * it;
     if (pg < pg1) {
       const int blk = table[pg];
       const size_t off = ((size_t)blk * p.hkv + kvh) * S::kPageElems;
-      __nv_bfloat16* ks = my_ring + (size_t)(it % S::kStages) * 2 * S::kPageElems;
-      load_rows_async<D>(ks, 0, p.k_cache + off, kPage, lane, 32);
-      load_rows_async<D>(ks + S::kPageElems, 0, p.v_cache + off, kPage, lane, 32);
+      uint8_t* st = my_ring + (size_t)(it % S::kStages) * 2 * S::kPageBytes;
+      if constexpr (KV8) {                                        // raw bytes, row-major, no swizzle
+        const uint8_t* kg = reinterpret_cast<const uint8_t*>(p.k_cache) + off;
+        const uint8_t* vg = reinterpret_cast<const uint8_t*>(p.v_cache) + off;
+        for (int i = lane; i < S::kPageBytes / 16; i += 32) {
+          cp_async16(st + i * 16, kg + i * 16);
+          cp_async16(st + S::kPageBytes + i * 16, vg + i * 16);
+        }
+      } else {
+        __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(st);
+        load_rows_async<D>(ks, 0, p.k_cache + off, kPage, lane, 32);
+        load_rows_async<D>(ks + S::kPageElems, 0, p.v_cache + off, kPage, lane, 32);
+      }
     }
     cp_async_commit();
   };
@@ -282,17 +333,42 @@ __global__ void __launch_bounds__(128) fa_decode_kernel(const FaParams p) {
     issue(it + S::kStages - 1);
     cp_async_wait<S::kStages - 1>();
     __syncwarp();
-    __nv_bfloat16* ks = my_ring + (size_t)(it % S::kStages) * 2 * S::kPageElems;
+    uint8_t* st = my_ring + (size_t)(it % S::kStages) * 2 * S::kPageBytes;
+    __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(st);
     __nv_bfloat16* vs = ks + S::kPageElems;
+    if constexpr (KV8) {
+      // widen this page pair: 16 e4m3 bytes -> two 16-byte chunks of f16 in the swizzled tiles
+      ks = my_tiles;
+      vs = my_tiles + S::kPageElems;
+      constexpr int CPR = D / 16;                                 // 16-byte chunks of raw bytes per row
+      for (int i = lane; i < 2 * kPage * CPR; i += 32) {
+        const int which = i / (kPage * CPR), c16 = i - which * (kPage * CPR);
+        const int r = c16 / CPR, cc = c16 - r * CPR;
+        const uint4 raw = *reinterpret_cast<const uint4*>(st + which * S::kPageBytes + r * D + cc * 16);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        uint32_t h[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[e] & 0xFFFFu), __NV_E4M3);
+          const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[e] >> 16), __NV_E4M3);
+          h[2 * e] = (uint32_t)lo.x | ((uint32_t)lo.y << 16);
+          h[2 * e + 1] = (uint32_t)hi.x | ((uint32_t)hi.y << 16);
+        }
+        __nv_bfloat16* tile = which ? vs : ks;
+        *reinterpret_cast<uint4*>(tile_ptr<D>(tile, r, 2 * cc)) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4*>(tile_ptr<D>(tile, r, 2 * cc + 1)) = make_uint4(h[4], h[5], h[6], h[7]);
+      }
+      __syncwarp();
+    }
     const int tok_base = (pg0 + warp + 4 * it) * kPage;
     float s[2][4];
 #pragma unroll
     for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-    qk_tile<D, 2>(s, qf, ks, 0, lane);
+    qk_tile<D, 2, KV8>(s, qf, ks, 0, lane);
     uint32_t pf[1][4];
-    softmax_update<2, D>(s, pf, o, m, l, tok_base, lane, lim0, lim1, beg0, beg1, p.scale_log2,
-                         p.softcap, p.scale);
-    pv_tile<D, 1>(o, pf, vs, 0, lane);
+    softmax_update<2, D, KV8>(s, pf, o, m, l, tok_base, lane, lim0, lim1, beg0, beg1, p.scale_log2,
+                              p.softcap, p.scale);
+    pv_tile<D, 1, KV8>(o, pf, vs, 0, lane);
     __syncwarp();
   }
   cp_async_wait<0>();
@@ -544,17 +620,21 @@ size_t attention_tc_workspace_bytes(int tokens, int hq, int head_dim, int max_sp
 
 template <int D>
 static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int min_q_len, int max_kv_len,
-                     void* workspace, size_t workspace_bytes, cudaStream_t s) {
+                     void* workspace, size_t workspace_bytes, cudaStream_t s, bool kv_fp8) {
   static bool configured[kMaxDevices] = {};
   if (first_call_on_device(configured)) {
     cuda_check(cudaFuncSetAttribute(fa_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     DecodeSmem<D>::kTotal), "fa_decode smem");
+    cuda_check(cudaFuncSetAttribute(fa_decode_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    DecodeSmem<D, true>::kTotal), "fa_decode (e4m3 cache) smem");
     cuda_check(cudaFuncSetAttribute(fa_prefill_kernel<D, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     PrefillSmem<D, 64>::kTotal), "fa_prefill smem");
   }
   int launches = 0;
   const int decode_max_q = 16 / p.group;            // packed rows must fit one 16-row MMA tile
   p.decode_max_q = decode_max_q;
+  if (kv_fp8 && (decode_max_q < 1 || max_q_len > decode_max_q))
+    throw std::runtime_error("attention_tc: an e4m3 cache is read by the decode kernel only (query rows x group <= 16)");
   if (decode_max_q >= 1 && min_q_len <= decode_max_q) {
     // split the KV range when the grid alone cannot fill the machine
     const int ctas = num_seqs * p.hkv;
@@ -570,7 +650,8 @@ static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int mi
     p.ws_o = reinterpret_cast<float*>(workspace);
     p.ws_ml = p.ws_o ? p.ws_o + (size_t)tokens * p.hq * splits * D : nullptr;
     dim3 grid(p.hkv, num_seqs, splits);
-    launch_pdl(fa_decode_kernel<D>, grid, dim3(128), DecodeSmem<D>::kTotal, s, p);
+    if (kv_fp8) launch_pdl(fa_decode_kernel<D, true>, grid, dim3(128), DecodeSmem<D, true>::kTotal, s, p);
+    else launch_pdl(fa_decode_kernel<D>, grid, dim3(128), DecodeSmem<D>::kTotal, s, p);
     ++launches;
     if (splits > 1) {
       launch_pdl(fa_merge_kernel<D>, dim3((tokens * p.hq + 3) / 4), dim3(128), 0, s, p, tokens);
@@ -606,7 +687,7 @@ int attention_tc_bf16(const void* q, long long ldq, const void* k_cache, const v
                       void* out, long long ldo, int tokens, int num_seqs, int max_q_len, int min_q_len,
                       int max_kv_len, int hq, int hkv, int head_dim, int block_size, float scale,
                       int window, const float* sinks, float softcap, void* workspace,
-                      size_t workspace_bytes, cudaStream_t s, long long num_kv_blocks, int* status) {
+                      size_t workspace_bytes, cudaStream_t s, long long num_kv_blocks, int* status, int kv_fp8) {
   if (tokens <= 0 || num_seqs <= 0) return 0;
   if (block_size != kPage) throw std::runtime_error("attention_tc: KV block size must be 16");
   if (hq % hkv) throw std::runtime_error("attention_tc: hq must be a multiple of hkv");
@@ -625,8 +706,8 @@ int attention_tc_bf16(const void* q, long long ldq, const void* k_cache, const v
   p.softcap = softcap;
   if (p.group > 16) throw std::runtime_error("attention_tc: at most 16 query heads per KV head");
   switch (head_dim) {
-    case 64: return launch_tc<64>(p, tokens, num_seqs, max_q_len, min_q_len, max_kv_len, workspace, workspace_bytes, s);
-    case 128: return launch_tc<128>(p, tokens, num_seqs, max_q_len, min_q_len, max_kv_len, workspace, workspace_bytes, s);
+    case 64: return launch_tc<64>(p, tokens, num_seqs, max_q_len, min_q_len, max_kv_len, workspace, workspace_bytes, s, kv_fp8 != 0);
+    case 128: return launch_tc<128>(p, tokens, num_seqs, max_q_len, min_q_len, max_kv_len, workspace, workspace_bytes, s, kv_fp8 != 0);
     default: throw std::runtime_error("attention_tc: head_dim must be 64 or 128");
   }
 }

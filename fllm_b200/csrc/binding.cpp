@@ -231,7 +231,10 @@ int64_t attention_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_cac
                      const optional<Tensor>& sinks, double softcap, const optional<Tensor>& workspace,
                      const optional<Tensor>& status) {
   check_bf16(q, "q"); check_rows(q, "q"); check_bf16(out, "out"); check_rows(out, "out");
-  check_bf16(k_cache, "k_cache"); check_bf16(v_cache, "v_cache");
+  const bool kv_fp8 = k_cache.element_size() == 1;            // e4m3 bytes: the decode kernel widens them to f16
+  TORCH_CHECK(k_cache.is_cuda() && v_cache.is_cuda() && k_cache.is_contiguous() && v_cache.is_contiguous() &&
+              k_cache.element_size() == v_cache.element_size() && (kv_fp8 || k_cache.scalar_type() == at::kBFloat16),
+              "caches must be contiguous bf16 or 1-byte e4m3 tensors");
   check_i32(q_starts, "q_starts"); check_i32(kv_lens, "kv_lens");
   TORCH_CHECK(block_tables.scalar_type() == at::kInt && block_tables.dim() == 2 &&
               block_tables.stride(1) == 1 && block_tables.stride(0) == block_tables.size(1),
@@ -248,7 +251,7 @@ int64_t attention_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_cac
                                  (int)min_q_len, (int)max_kv_len, (int)hq, (int)hkv, (int)head_dim,
                                  (int)k_cache.size(2), (float)scale, (int)window, opt_ptr<float>(sinks),
                                  (float)softcap, ws, ws_bytes, cur_stream(), (long long)k_cache.size(0),
-                                 const_cast<int*>(opt_ptr<int>(status)));
+                                 const_cast<int*>(opt_ptr<int>(status)), kv_fp8 ? 1 : 0);
 }
 
 void argmax(const Tensor& logits, Tensor out_ids, const optional<Tensor>& out_vals,

@@ -115,6 +115,22 @@ int64_t linear_mx(const Tensor& xq, const Tensor& sfb, const Tensor& wq, const T
                          y.data_ptr(), y.stride(0), (int)T, (int)N, (int)K, ws, ws_bytes, st, cur_stream());
 }
 
+// the dp4a path of linear_w4a16 for at most 4 tokens (same operands)
+int64_t gemv_w4(const Tensor& x, const Tensor& codes, const Tensor& scales, int64_t fmt, double alpha,
+                const optional<Tensor>& bias, Tensor y) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "x: bf16 rows");
+  TORCH_CHECK(codes.is_contiguous() && codes.element_size() == 1 && codes.dim() == 2 && codes.size(1) * 2 == x.size(1), "codes: [N, K/2] bytes");
+  const int64_t T = x.size(0), N = codes.size(0), K = x.size(1);
+  TORCH_CHECK(fllm::gemv_w4_supported((int)T, (int)K), "gemv_w4: at most 4 tokens, K % 32 == 0");
+  TORCH_CHECK(scales.is_contiguous() && scales.numel() * scales.element_size() == N * (K / (fmt == 0 ? 16 : 32)) * (fmt == 2 ? 4 : 1),
+              "scales: one byte per block (FP4) or {bf16 scale, bf16 min} per 32 values (INT4G)");
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.stride(1) == 1 && y.size(0) == T && y.size(1) == N, "y: [T, N] bf16");
+  c10::cuda::CUDAGuard guard(x.device());
+  const void* b = bias.has_value() && bias->defined() ? bias->data_ptr() : nullptr;
+  return fllm::gemv_w4(x.data_ptr(), x.stride(0), codes.data_ptr(), scales.data_ptr(), (int)fmt, (float)alpha, b, y.data_ptr(),
+                       y.stride(0), (int)T, (int)N, (int)K, cur_stream());
+}
+
 void w4_dequant(const Tensor& codes, const Tensor& scales, int64_t fmt, double alpha, Tensor out) {
   TORCH_CHECK(codes.is_cuda() && codes.is_contiguous() && codes.dim() == 2 && out.is_contiguous() && out.scalar_type() == at::kBFloat16, "codes [N, K/2], out bf16 [N, K]");
   TORCH_CHECK(out.numel() == codes.numel() * 2 && (codes.size(1) * 2) % 32 == 0, "out: [N, K], K % 32 == 0");
@@ -132,5 +148,6 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("quant_nvfp4(Tensor x, Tensor(a!) xq, Tensor(b!) sf, Tensor(c!) tok_scale) -> ()", &quant_nvfp4);
   m.def("mx_act_scale_bytes(int T, int K, int kind) -> int", &mx_act_scale_bytes);
   m.def("linear_mx(Tensor xq, Tensor sfb, Tensor wq, Tensor sfa, int kind, float alpha, Tensor? tok_scale, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status) -> int", &linear_mx);
+  m.def("gemv_w4(Tensor x, Tensor codes, Tensor scales, int fmt, float alpha, Tensor? bias, Tensor(a!) y) -> int", &gemv_w4);
   m.def("w4_dequant(Tensor codes, Tensor scales, int fmt, float alpha, Tensor(a!) out) -> ()", &w4_dequant);
 }

@@ -98,6 +98,11 @@ void* symm_import(const unsigned char in[64]);
 void symm_close(void* p);
 
 // ---- block-scaled FP8 ------------------------------------------------------------------
+// Packed 4-bit weights x at most 4 tokens on dp4a (int8 activations quantised inside the kernel); formats as linear_w4a16.
+bool gemv_w4_supported(int T, int K);
+int gemv_w4(const void* x, long long ldx, const void* codes, const void* scales, int fmt, float alpha, const void* bias,
+            void* y, long long ldy, int T, int N, int K, cudaStream_t stream);
+
 // Block-scaled GEMMs (tcgen05 kind::mxf8f6f4 / kind::mxf4nvf4 .block_scale). kind 0: e4m3 weights, kind 1: packed
 // e2m1 weights, both with e4m3 activations and one e8m0 scale per 32 values; kind 2: NVFP4 on both sides (packed
 // e2m1, one e4m3 scale per 16, tensor scale x per-token scale). Scale factors travel in 512-byte atoms (128 rows x
@@ -195,7 +200,8 @@ int attention_tc_bf16(const void* q, long long ldq, const void* k_cache, const v
                       void* out, long long ldo, int tokens, int num_seqs, int max_q_len, int min_q_len,
                       int max_kv_len, int hq, int hkv, int head_dim, int block_size, float scale,
                       int window, const float* sinks, float softcap, void* workspace,
-                      size_t workspace_bytes, cudaStream_t s, long long num_kv_blocks = 0, int* status = nullptr);
+                      size_t workspace_bytes, cudaStream_t s, long long num_kv_blocks = 0, int* status = nullptr,
+                      int kv_fp8 = 0);   // kv_fp8: the caches hold e4m3 bytes (decode-shaped batches only)
 // Prefill on tcgen05 with tensor-memory accumulators (head_dim 64 or 128, group size dividing 128).
 bool attention_prefill_tmem_supported(int head_dim, int group, int block_size);
 void attention_prefill_tmem(const void* q, long long ldq, const void* k_cache, const void* v_cache, long long num_blocks,

@@ -106,6 +106,11 @@ class Fp4Weight:
         if not x.is_cuda:                                        # CPU oracle path
             y = x.float() @ self.dense().to(x.device).t()
             return (y + bias.float() if bias is not None else y).to(x.dtype)
+        if T <= 4 and K % 32 == 0 and T * K * 1.25 <= 160 * 1024 and x.stride(0) % 8 == 0:
+            # a handful of tokens: integer dot products on the packed codes (csrc/gemv_w4.cu)
+            y = out if out is not None else torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+            ops.launches += ops.k.gemv_w4(x, self.codes, self.scales, self.fmt, self.alpha, bias, y)
+            return y
         if T <= 128:
             y = out if out is not None else torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
             ops.launches += ops.k.linear_w4a16(x, self.codes, self.scales, self.fmt, self.alpha, bias, y,

@@ -9,8 +9,9 @@ are re-laid once at load time into two planar arrays
   [v0 v2 v4 v6 v1 v3 v5 v7], so that ``(word >> 4j) & 0x000F000F`` is the pair (v2j, v2j+1);
 * ``sm``     bf16 [N, K/32, 2] = {scale, min}
 
-and stay packed in HBM (4 bits + 1 bit of scale per weight). Steps of at most 128 tokens run the
-packed tcgen05 GEMM of ``csrc/gemm_w4a16.cu`` (format 2); longer steps expand to bf16 scratch.
+and stay packed in HBM (4 bits + 1 bit of scale per weight). Steps of at most 4 tokens run the dp4a
+kernel of ``csrc/gemv_w4.cu`` (int8 activations), steps of at most 128 tokens the packed tcgen05 GEMM of
+``csrc/gemm_w4a16.cu`` (format 2); longer steps expand to bf16 scratch.
 The reference keeps these types packed too and runs them through per-type kernels
 (rust/engine/cuda/qgemm4k.cu, marlin_q4k.cu, mmvq.cu, marlin_vllm/*; device re-layout at
 rust/engine/src/backend/cuda.rs:1798-1935).
@@ -21,6 +22,7 @@ import numpy as np
 import torch
 
 INT4G = 2
+GEMV_MAX_TOKENS = 4
 _ORDER = (0, 2, 4, 6, 1, 3, 5, 7)          # nibble j of a word holds value _ORDER[j]
 
 
@@ -117,6 +119,11 @@ class Int4Weight:
         if not x.is_cuda:
             y = x.float() @ self.dense().to(torch.bfloat16).float().t()
             return (y + bias.float() if bias is not None else y).to(x.dtype)
+        if T <= GEMV_MAX_TOKENS and K % 32 == 0 and T * K * 1.25 <= 160 * 1024 and x.stride(0) % 8 == 0:
+            # a handful of tokens: integer dot products on the packed codes (csrc/gemv_w4.cu)
+            y = out if out is not None else torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+            ops.launches += ops.k.gemv_w4(x, self.codes, self.sm.view(torch.uint8).view(N, -1), INT4G, 1.0, bias, y)
+            return y
         if T <= 128:
             y = out if out is not None else torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
             ops.launches += ops.k.linear_w4a16(x, self.codes, self.sm.view(torch.uint8).view(N, -1), INT4G, 1.0, bias, y,

@@ -137,9 +137,12 @@ class NativeOps:
     def attention(self, q, k_cache, v_cache, block_tables, row_seq, positions, hq, hkv, head_dim,
                   scale, window=0, sinks=None, softcap=0.0, meta=None):
         out = torch.empty(q.shape[0], hq * head_dim, dtype=q.dtype, device=q.device)
+        kv8 = k_cache.element_size() == 1
         if (self.use_tc_attention and meta is not None and meta.q_starts is not None
-                and head_dim in (64, 128) and hq // hkv <= 16 and k_cache.element_size() == 2):
-            # (an fp8 KV cache is read by the generic kernel: the tensor-core kernels load bf16 tiles)
+                and head_dim in (64, 128) and hq // hkv <= 16
+                and (not kv8 or meta.max_q_len * (hq // hkv) <= 16)):
+            # (an e4m3 KV cache: decode-shaped batches run the tensor-core decode kernel, which widens the pages to
+            # f16 in shared memory; batches with prefill chunks fall through to the generic kernel)
             if self.attn_ws is None:
                 self.attn_ws = torch.empty(64 << 20, dtype=torch.uint8, device=self.device)
             self.launches += self.k.attention_tc(

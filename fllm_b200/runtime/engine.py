@@ -588,11 +588,21 @@ class LLMEngine:
         self.stats.steps += 1
         return events
 
+    def _pp_recv_buffer(self, index: int, rows: int, hidden: int) -> torch.Tensor:
+        """Receive buffer of micro-batch `index`: one per micro-batch in flight, grown on demand and kept."""
+        bufs = self.__dict__.setdefault("_pp_recv_bufs", {})
+        buf = bufs.get(index)
+        if buf is None or buf.shape[0] < rows:
+            buf = torch.empty(max(rows, 64), hidden, dtype=torch.bfloat16, device=self.device)
+            bufs[index] = buf
+        return buf[:rows]
+
     def _pipeline_forward(self, step: ScheduledStep) -> torch.Tensor:
         """One step over pipeline stages. The step is cut into micro-batches by sequence
         (rust/engine/src/parallel/decoder_shard.rs:313-341); every stage runs them in order, so
         stage s works on micro-batch i while stage s+1 works on i-1. The hand-over is the bf16
-        residual stream [rows, hidden] sent device to device with the library's p2p (the reference
+        residual stream [rows, hidden] sent device to device with the library's p2p, all receives of a step
+        posted up front into per-micro-batch buffers so that transfer and compute overlap (the reference
         copies it through host memory, rust/engine/src/rust_decoder.rs:5900-5911). The last stage
         samples; the ids are broadcast so that every rank commits the same tokens."""
         from .scheduler import ScheduledStep as _Step
@@ -605,12 +615,20 @@ class LLMEngine:
                    for i, sub in enumerate(subs)]
         H = self.model_cfg.hidden_size
         toks, pending = [], []
+        # Every hand-over of the step is posted before the first layer runs, each into a buffer of its own: the
+        # library's point-to-point stream then only waits for the sender, so micro-batch i + 1 crosses NVLink while
+        # micro-batch i computes (posted one at a time, each receive would queue behind the previous compute).
+        recvs = []
+        if not self.first_stage:
+            for i, sub in enumerate(subs):
+                buf = self._pp_recv_buffer(i, sub.num_tokens, H)
+                recvs.append((g.irecv(buf, self.stage - 1), buf))
         for i, sub in enumerate(subs):
             b = batches[i] if batches[i] is not None else self._build_batch(sub, slot=i % len(self._stage_bufs))
             x_in = None
             if not self.first_stage:
-                x_in = torch.empty(sub.num_tokens, H, dtype=torch.bfloat16, device=self.device)
-                g.recv(x_in, self.stage - 1)
+                w, x_in = recvs[i]
+                w.wait()                                   # device-side wait on the NCCL path; host wait on gloo
             x, delta = self.decoder.forward_hidden(b, hidden_in=x_in)
             if not self.last_stage:
                 out = (x.float() + delta.float()).to(x.dtype) if delta is not None else x

@@ -699,3 +699,67 @@ def test_kernels_never_store_outside_their_outputs(ops, T):
     torch.cuda.synchronize()
     c.check()
     assert ops.check_status() == 0
+
+
+@pytest.mark.parametrize("fmt", ["int4g", "mxfp4", "nvfp4"])
+@pytest.mark.parametrize("T", [1, 2, 3, 4])
+@pytest.mark.parametrize("N,K", [(256, 256), (1000, 320), (6144, 4096), (520, 12288)])
+def test_gemv_w4_dp4a(ops, fmt, T, N, K):
+    """The few-token path of the packed 4-bit weights (dp4a on int8 activations quantised per 32 values inside the
+    kernel) against fp32 math on the same quantised activations and the dequantised weights."""
+    from fllm_b200.ops.fp4 import Fp4Weight
+    from fllm_b200.ops.int4 import Int4Weight
+    x = _rand((T, K), 11 + T)
+    w = _rand((N, K), 12, 0.05)
+    bias = _rand((N,), 13) if T % 2 == 0 else None
+    if fmt == "int4g":
+        q = Int4Weight.from_dense(w)
+        dense = q.dense().float()
+        y = torch.empty(T, N, dtype=torch.bfloat16, device="cuda")
+        ops.k.gemv_w4(x, q.codes, q.sm.view(torch.uint8).view(N, -1), 2, 1.0, bias, y)
+    else:
+        q = Fp4Weight.from_dense(w, fmt)
+        dense = q.dense().float()
+        y = torch.empty(T, N, dtype=torch.bfloat16, device="cuda")
+        ops.k.gemv_w4(x, q.codes, q.scales, q.fmt, q.alpha, bias, y)
+    xb = x.float().view(T, K // 32, 32)
+    d = xb.abs().amax(-1, keepdim=True) / 127.0
+    xq = torch.where(d > 0, torch.round(xb / d.clamp_min(1e-30)), torch.zeros_like(xb)) * d
+    ref = xq.view(T, K) @ dense.t() + (bias.float() if bias is not None else 0)
+    _close(y, ref, 1e-2)
+    _close(y, x.float() @ dense.t() + (bias.float() if bias is not None else 0), 3e-2)
+    # the weight classes take this path by themselves for up to 4 tokens
+    y2 = ops.linear(x, q, bias)
+    assert torch.equal(y2, y)
+    assert ops.check_status() == 0
+
+
+@pytest.mark.parametrize("D,hq,hkv", [(128, 8, 2), (64, 8, 8), (128, 32, 8), (64, 16, 2)])
+@pytest.mark.parametrize("window,sinks,softcap", [(0, False, 0.0), (40, True, 0.0), (0, False, 30.0)])
+@pytest.mark.parametrize("case", ["decode", "decode_few", "verify"])
+def test_attention_tc_decode_reads_e4m3_cache(ops, ref, D, hq, hkv, window, sinks, softcap, case):
+    """An e4m3 KV pool through the tensor-core decode kernel (pages widened to f16 in shared memory) against the
+    fp32 reference on the same e4m3 values, and against the generic kernel."""
+    if case == "decode":
+        kv_lens, q_lens = [1, 17, 64, 130, 700, 33, 16, 257], [1] * 8
+    elif case == "decode_few":
+        kv_lens, q_lens = [900, 35], [1, 1]
+    else:
+        n = max(1, min(4, 16 // (hq // hkv)))
+        kv_lens, q_lens = [100, 37, 260], [n, n, n]
+    tables, kc, vc = _paged_setup(len(kv_lens), kv_lens, hkv, D, seed=3)
+    kc8, vc8 = kc.to(torch.float8_e4m3fn), vc.to(torch.float8_e4m3fn)
+    T = sum(q_lens)
+    row_seq = torch.tensor([i for i, n in enumerate(q_lens) for _ in range(n)], dtype=torch.int32, device="cuda")
+    pos = torch.tensor([kv - n + j for kv, n in zip(kv_lens, q_lens) for j in range(n)], dtype=torch.int32, device="cuda")
+    q = _rand((T, hq * D), 5)
+    sk = torch.randn(hq, device="cuda") if sinks else None
+    meta = _tc_meta(q_lens, kv_lens)
+    l0 = ops.launches
+    y = ops.attention(q, kc8, vc8, tables, row_seq, pos, hq, hkv, D, D ** -0.5, window, sk, softcap, meta=meta)
+    assert ops.launches - l0 in (1, 2)                       # decode kernel (+ merge), not the generic one's count of 1 only
+    yr = ref.attention(q, kc8.to(torch.bfloat16), vc8.to(torch.bfloat16), tables, row_seq, pos, hq, hkv, D, D ** -0.5, window, sk, softcap)
+    _close(y, yr, 2e-2)
+    yg = ops.attention(q, kc8, vc8, tables, row_seq, pos, hq, hkv, D, D ** -0.5, window, sk, softcap)
+    _close(yg, y, 2e-2)
+    assert ops.check_status() == 0

@@ -62,3 +62,14 @@ def test_pipeline_and_tp_x_pp_match_single_device_on_cpu(world, pp):
         assert res["agree"] == res["total"], res          # pure PP computes the same bits
     else:
         assert res["worst_gap"] < 0.02, res
+
+
+@pytest.mark.parametrize("world,pp,spec", [(2, 1, "ngram"), (2, 1, "draft"), (4, 2, "ngram"), (2, 2, "draft")])
+def test_speculation_under_tensor_and_pipeline_parallelism(world, pp, spec):
+    """Drafts are proposed identically on every rank (n-gram lookup, or a draft model sharded over the same TP
+    group) and verified on the parallel engine: the text stays the single-device greedy text."""
+    res = run_ranks(world, ["cpu", "gloo", "qwen3-tiny", str(pp), "none", spec])
+    assert res["spec_proposed"] > 0, res
+    assert res["worst_gap"] < 0.02, res
+    if spec == "draft":
+        assert res["spec_accepted"] >= 0.7 * res["spec_proposed"], res

@@ -75,6 +75,7 @@ def main():
     device_kind, backend, model = sys.argv[1], sys.argv[2], sys.argv[3]
     pp = int(sys.argv[4]) if len(sys.argv) > 4 else 1
     ep_mode = sys.argv[5] if len(sys.argv) > 5 else "none"          # none | allreduce | alltoall
+    spec = sys.argv[6] if len(sys.argv) > 6 else "off"               # off | ngram | draft: speculation on the parallel engine
     rank, world, local = init_distributed("gloo" if device_kind == "cpu" else "nccl", timeout_s=120)
     dev = torch.device("cpu") if device_kind == "cpu" else torch.device("cuda", local)
     cfg = preset(model)
@@ -85,6 +86,9 @@ def main():
     g = torch.Generator().manual_seed(5)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (7, 40, 21, 90, 3)]
     sp = SamplingParams(max_tokens=10)
+    if spec != "off":
+        prompts[1] = prompts[1][:8] * 5                                 # repetition gives the n-gram lookup something to find
+        sp = SamplingParams(max_tokens=14)
     single = LLMEngine(cfg, ec, ParallelConfig(tp=1), device=dev, seed=3)
     want = single.generate(prompts, sp)
     from fllm_b200.comm import make_tp_pp_groups
@@ -97,8 +101,13 @@ def main():
         tp_rt = LibraryTP(grp)
     par = ParallelConfig(tp=tp, pp=pp, expert_parallel=ep_mode != "none",
                          ep_dispatch=ep_mode if ep_mode != "none" else "allreduce")
+    if spec == "ngram":
+        import dataclasses
+        ec = dataclasses.replace(ec, speculative="ngram")
     eng = LLMEngine(cfg, ec, par, device=dev, tp_group=tp_rt, tp_rank=tp_rank, seed=3,
                     pp_group=pp_grp, stage=stage)
+    if spec == "draft":
+        eng.enable_draft_model(cfg, k=3, seed=3)                         # same seed: the draft equals the target
     got = eng.generate(prompts, sp)
 
     def last_logits(e):
@@ -129,7 +138,8 @@ def main():
         agree = sum(a == b for o, r in zip(got, want) for a, b in zip(o, r))
         total = sum(len(o) for o in want)
         print(json.dumps({"backend": getattr(tp_rt, "backend", "?"), "world": world, "agree": agree, "total": total,
-                          "worst_gap": worst_gap, "status": status, "graph_steps": eng.stats.graph_steps, "logit_err": logit_err}), flush=True)
+                          "worst_gap": worst_gap, "status": status, "spec_proposed": eng.stats.spec_proposed,
+                          "spec_accepted": eng.stats.spec_accepted, "graph_steps": eng.stats.graph_steps, "logit_err": logit_err}), flush=True)
     from fllm_b200.comm import shutdown_distributed
     eng.close()
     single.close()
