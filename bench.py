@@ -147,6 +147,8 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--weight-format", default=None)
+    ap.add_argument("--kv-cache-type", default="bf16", choices=["bf16", "fp8_e4m3"],
+                    help="element type of the paged KV pool (the headline configuration uses bf16)")
     ap.add_argument("--backend", default=os.environ.get("FLLM_TP_BACKEND", "auto"),
                     help="tensor-parallel collectives: auto | fused | nccl")
     ap.add_argument("--no-graphs", action="store_true")
@@ -193,7 +195,7 @@ def main() -> None:
     out_len = args.warmup + 2 * args.steps + 8 + stagger
     ec = EngineConfig(max_num_seqs=args.batch, max_num_batched_tokens=2048, block_size=16,
                       max_model_len=p_hi + out_len + 16, enable_prefix_caching=False,
-                      use_cuda_graphs=not args.no_graphs)
+                      use_cuda_graphs=not args.no_graphs, kv_cache_dtype=args.kv_cache_type)
     ec.num_kv_blocks = args.batch * (-(-ec.max_model_len // 16)) + 16
     par = ParallelConfig(tp=tp, pp=pp, expert_parallel=bool(conf["ep"] and cfg.is_moe and tp > 1), ep_dispatch="alltoall")
     pp_grp, stage, tp_rank = None, 0, rank
@@ -346,7 +348,7 @@ def main() -> None:
             "config": {"config": args.config, "model": cfg.name, "global_batch": args.batch,
                        "seq_len": args.prompt_len if p_lo == p_hi else f"{p_lo}-{p_hi}",
                        "parallelism": (f"tp{tp}" + (f"xpp{pp}" if pp > 1 else "") + ("+ep" if par.expert_parallel else "")),
-                       "tp_backend": getattr(tp_rt, "backend", "none"), "weight_format": cfg.weight_format,
+                       "tp_backend": getattr(tp_rt, "backend", "none"), "weight_format": cfg.weight_format, "kv_cache": args.kv_cache_type,
                        "kv": "paged bf16, 16-token blocks", "chunked_prefill": 2048,
                        "cuda_graphs": not args.no_graphs, "async_scheduling": eng._async_ok(),
                        "l2": "inputs larger than L2: 16 GB of weights + KV streamed per step"},

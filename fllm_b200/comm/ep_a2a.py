@@ -33,7 +33,8 @@ class EpAllToAll:
         # worst case every entry of every rank lands here; a smaller `cap` is reported through the status word
         self.cap = cap if cap is not None else self.max_entries * ranks
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.epoch = 0
+        # the call number lives on the device (dispatch advances it), so a captured graph replays the layer as is
+        self.call_ctr = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._owned: List[int] = []
         if tables is None:
             tables = self._exchange(group)
@@ -95,21 +96,20 @@ class EpAllToAll:
     # ------------------------------------------------------------------ steps (all asynchronous on the current stream)
     def dispatch(self, x: torch.Tensor, ids: torch.Tensor) -> None:
         """x: [tokens, hidden] rows this rank owns; ids: [tokens, k] global expert ids (int32)."""
-        self.epoch += 1
-        self.k_ops.ep_dispatch(self.ctx, x, ids, self.epoch, self.status)
+        self.k_ops.ep_dispatch(self.ctx, x, ids, 0, self.status, self.call_ctr)
 
     def ingest(self) -> "tuple[torch.Tensor, torch.Tensor]":
         """-> (expert id per received row [cap] (-1 = unused), row count [1]); rows are in ``recv_x``."""
-        self.k_ops.ep_ingest(self.ctx, self.epoch, self.ids_recv, self.count, self.status)
+        self.k_ops.ep_ingest(self.ctx, 0, self.ids_recv, self.count, self.status, self.call_ctr)
         return self.ids_recv, self.count
 
     def return_rows(self, y: torch.Tensor, row_of: torch.Tensor) -> None:
         """y: expert outputs in permuted order; row_of: [cap] permuted row of every received row."""
-        self.k_ops.ep_return(self.ctx, y, row_of, self.count, self.epoch)
+        self.k_ops.ep_return(self.ctx, y, row_of, self.count, 0, self.call_ctr)
 
     def wait_returns(self) -> torch.Tensor:
         """After this, ``comb_y[token * k + slot]`` holds the output of that (token, slot)."""
-        self.k_ops.ep_wait_returns(self.ctx, self.epoch, self.status)
+        self.k_ops.ep_wait_returns(self.ctx, 0, self.status, self.call_ctr)
         return self.comb_y
 
     def check_status(self) -> int:

@@ -101,40 +101,51 @@ int64_t ep_ctx_create(int64_t ranks, int64_t my_rank, int64_t cap, int64_t hidde
   return (int64_t)g_ep.size() - 1;
 }
 
+// the rank's call counter: one int32 / uint32 in device memory, or none (host-passed call number)
+unsigned* ctr_ptr(const optional<Tensor>& t) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->element_size() == 4 && t->numel() >= 1, "call counter: one 32-bit integer on the device");
+  return reinterpret_cast<unsigned*>(t->data_ptr());
+}
+
 const fllm::EpArgs& ep_at(int64_t h) {
   TORCH_CHECK(h >= 0 && h < (int64_t)g_ep.size(), "invalid expert-parallel context handle");
   return g_ep[h];
 }
 
-void ep_dispatch(int64_t h, const Tensor& x, const Tensor& ids, int64_t epoch, const optional<Tensor>& status) {
+void ep_dispatch(int64_t h, const Tensor& x, const Tensor& ids, int64_t epoch, const optional<Tensor>& status,
+                 const optional<Tensor>& call_ctr) {
   const auto& a = ep_at(h);
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 && x.size(1) == a.hidden, "x: [tokens, hidden] bf16");
   TORCH_CHECK(ids.scalar_type() == at::kInt && ids.is_contiguous() && ids.dim() == 2 && ids.size(0) == x.size(0), "ids: [tokens, k] int32");
   c10::cuda::CUDAGuard guard(x.device());
-  fllm::ep_dispatch(a, x.data_ptr(), x.stride(0), ids.data_ptr<int>(), (int)x.size(0), (int)ids.size(1), (unsigned)epoch,
+  fllm::ep_dispatch(a, x.data_ptr(), x.stride(0), ids.data_ptr<int>(), (int)x.size(0), (int)ids.size(1), (unsigned)epoch, ctr_ptr(call_ctr),
                     status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr, cur_stream());
 }
 
-void ep_ingest(int64_t h, int64_t epoch, Tensor ids_out, Tensor count_out, const optional<Tensor>& status) {
+void ep_ingest(int64_t h, int64_t epoch, Tensor ids_out, Tensor count_out, const optional<Tensor>& status,
+               const optional<Tensor>& call_ctr) {
   const auto& a = ep_at(h);
   TORCH_CHECK(ids_out.scalar_type() == at::kInt && ids_out.is_contiguous() && ids_out.numel() == a.cap, "ids_out: [cap] int32");
   TORCH_CHECK(count_out.scalar_type() == at::kInt && count_out.numel() >= 1, "count_out: int32");
   c10::cuda::CUDAGuard guard(ids_out.device());
-  fllm::ep_ingest(a, (unsigned)epoch, ids_out.data_ptr<int>(), count_out.data_ptr<int>(),
+  fllm::ep_ingest(a, (unsigned)epoch, ctr_ptr(call_ctr), ids_out.data_ptr<int>(), count_out.data_ptr<int>(),
                   status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr, cur_stream());
 }
 
-void ep_return(int64_t h, const Tensor& y, const Tensor& row_of, const Tensor& count, int64_t epoch) {
+void ep_return(int64_t h, const Tensor& y, const Tensor& row_of, const Tensor& count, int64_t epoch,
+               const optional<Tensor>& call_ctr) {
   const auto& a = ep_at(h);
   TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.stride(1) == 1 && y.size(1) == a.hidden, "y: [rows, hidden] bf16");
   TORCH_CHECK(row_of.scalar_type() == at::kInt && row_of.is_contiguous() && row_of.numel() == a.cap, "row_of: [cap] int32");
   c10::cuda::CUDAGuard guard(y.device());
-  fllm::ep_return(a, y.data_ptr(), y.stride(0), row_of.data_ptr<int>(), count.data_ptr<int>(), (unsigned)epoch, cur_stream());
+  fllm::ep_return(a, y.data_ptr(), y.stride(0), row_of.data_ptr<int>(), count.data_ptr<int>(), (unsigned)epoch, ctr_ptr(call_ctr),
+                  cur_stream());
 }
 
-void ep_wait_returns(int64_t h, int64_t epoch, const Tensor& status) {
+void ep_wait_returns(int64_t h, int64_t epoch, const Tensor& status, const optional<Tensor>& call_ctr) {
   c10::cuda::CUDAGuard guard(status.device());
-  fllm::ep_wait_returns(ep_at(h), (unsigned)epoch, status.data_ptr<int>(), cur_stream());
+  fllm::ep_wait_returns(ep_at(h), (unsigned)epoch, ctr_ptr(call_ctr), status.data_ptr<int>(), cur_stream());
 }
 }  // namespace
 
@@ -146,8 +157,8 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("moe_grouped_linear_w4(Tensor xp, Tensor codes, Tensor scales, int fmt, float alpha, Tensor? bias_stack, Tensor(a!) y, Tensor tile_expert, Tensor tile_row0, Tensor num_tiles, int bn, Tensor? status) -> int", &moe_grouped_linear_w4);
   m.def("moe_combine(Tensor y, Tensor row_of, Tensor weights, Tensor(a!) out) -> ()", &moe_combine);
   m.def("ep_ctx_create(int ranks, int my_rank, int cap, int hidden, int experts_per_rank, int[] recv_x, int[] recv_meta, int[] ctrl, int[] comb_y) -> int", &ep_ctx_create);
-  m.def("ep_dispatch(int ctx, Tensor x, Tensor ids, int epoch, Tensor? status) -> ()", &ep_dispatch);
-  m.def("ep_ingest(int ctx, int epoch, Tensor(a!) ids_out, Tensor(b!) count_out, Tensor? status) -> ()", &ep_ingest);
-  m.def("ep_return(int ctx, Tensor y, Tensor row_of, Tensor count, int epoch) -> ()", &ep_return);
-  m.def("ep_wait_returns(int ctx, int epoch, Tensor(a!) status) -> ()", &ep_wait_returns);
+  m.def("ep_dispatch(int ctx, Tensor x, Tensor ids, int epoch, Tensor? status, Tensor(a!)? call_ctr=None) -> ()", &ep_dispatch);
+  m.def("ep_ingest(int ctx, int epoch, Tensor(a!) ids_out, Tensor(b!) count_out, Tensor? status, Tensor? call_ctr=None) -> ()", &ep_ingest);
+  m.def("ep_return(int ctx, Tensor y, Tensor row_of, Tensor count, int epoch, Tensor? call_ctr=None) -> ()", &ep_return);
+  m.def("ep_wait_returns(int ctx, int epoch, Tensor(a!) status, Tensor? call_ctr=None) -> ()", &ep_wait_returns);
 }

@@ -138,12 +138,14 @@ struct EpArgs {
   void* comb_y[kMaxEp];       // [max entries][hidden] bf16 on each rank
   int ranks, my_rank, cap, hidden, experts_per_rank;
 };
+// call_ctr: the rank's device-side call counter (dispatch advances it, the others read it); null = use `epoch`.
 void ep_dispatch(const EpArgs& a, const void* x, long long ldx, const int* ids, int tokens, int k, unsigned epoch,
-                 int* status, cudaStream_t s);
-void ep_ingest(const EpArgs& a, unsigned epoch, int* ids_out, int* count_out, int* status, cudaStream_t s);
-void ep_return(const EpArgs& a, const void* y, long long ldy, const int* row_of, const int* count, unsigned epoch,
+                 unsigned* call_ctr, int* status, cudaStream_t s);
+void ep_ingest(const EpArgs& a, unsigned epoch, const unsigned* call_ctr, int* ids_out, int* count_out, int* status,
                cudaStream_t s);
-void ep_wait_returns(const EpArgs& a, unsigned epoch, int* status, cudaStream_t s);
+void ep_return(const EpArgs& a, const void* y, long long ldy, const int* row_of, const int* count, unsigned epoch,
+               const unsigned* call_ctr, cudaStream_t s);
+void ep_wait_returns(const EpArgs& a, unsigned epoch, const unsigned* call_ctr, int* status, cudaStream_t s);
 
 // ---- mixture of experts ---------------------------------------------------------------
 int moe_grouped_linear_bf16(const void* xp, long long ldx, const void* w_stack, long long ldw,

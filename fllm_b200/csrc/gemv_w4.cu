@@ -13,10 +13,13 @@
 //   1 MXFP4  e2m1 codes in index order + e8m0 scale per 32; 0 NVFP4: + e4m3 scale per 16 and a tensor scale.
 //            e2m1 magnitudes {0, .5, 1, 1.5, 2, 3, 4, 6} are doubled into int8 by a byte-permute table.
 //
-// One warp owns four output rows at a time (four independent 16-byte loads per lane in flight); a CTA of
-// eight warps covers 32 rows. Reference counterparts: rust/engine/cuda/mmvq.cu:50,173,375 (dp4a GEMV on q8_1
-// activations), rust/engine/cuda/gemv2.cu.
+// One warp owns four output rows at a time (four independent 16-byte loads per lane, and the next four already
+// in flight); CTAs are persistent (at most three per SM), so the activations are quantised once per CTA.
+// Reference counterparts: rust/engine/cuda/mmvq.cu:50,173,375 (dp4a GEMV on q8_1 activations),
+// rust/engine/cuda/gemv2.cu.
 #include <cuda_fp8.h>
+
+#include <algorithm>
 
 #include "fllm_ops.h"
 #include "ptx.cuh"
@@ -103,90 +106,122 @@ gemv_w4_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const uint8_t
   __syncthreads();
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row0 = blockIdx.x * kGvRowsPerCta + warp * kGvRowsPerWarp;
-  if (row0 >= N) return;
+  // Persistent CTAs: the activations are quantised once per CTA, then every warp walks (row group, K slice)
+  // items with the next item's codes already in flight while the current one is multiplied.
+  const int kiters = (nblk + 31) / 32;                                 // K slices of 32 blocks per row group
+  const int n_groups = (N + kGvRowsPerWarp - 1) / kGvRowsPerWarp;      // row groups of 4 rows
+  const int warps_total = gridDim.x * (kGvThreads / 32);
+  const int gwarp = blockIdx.x * (kGvThreads / 32) + warp;
+  const long long items = (long long)((n_groups - gwarp + warps_total - 1) / warps_total) * kiters;   // this warp's items
+  if (gwarp >= n_groups) return;
+
+  auto item_row0 = [&](long long it) { return (int)((gwarp + (it / kiters) * warps_total) * kGvRowsPerWarp); };
+  auto load_item = [&](long long it, uint4 (&w)[kGvRowsPerWarp], uint32_t (&sc)[kGvRowsPerWarp]) {
+    const int row0 = item_row0(it);
+    const int b = (int)(it % kiters) * 32 + lane;
+#pragma unroll
+    for (int r = 0; r < kGvRowsPerWarp; ++r) {
+      const int row = min(row0 + r, N - 1);
+      w[r] = make_uint4(0, 0, 0, 0);
+      sc[r] = 0;
+      if (b < nblk) {
+        w[r] = *reinterpret_cast<const uint4*>(codes + (size_t)row * (K / 2) + b * 16);
+        if constexpr (FMT == 2) sc[r] = reinterpret_cast<const uint32_t*>(scales)[(size_t)row * nblk + b];
+        else if constexpr (FMT == 1) sc[r] = scales[(size_t)row * nblk + b];
+        else sc[r] = reinterpret_cast<const uint16_t*>(scales)[(size_t)row * nblk + b];
+      }
+    }
+  };
+
   float acc[kGvRowsPerWarp][T];
 #pragma unroll
   for (int r = 0; r < kGvRowsPerWarp; ++r)
 #pragma unroll
     for (int t = 0; t < T; ++t) acc[r][t] = 0.f;
 
-  for (int b = lane; b < nblk; b += 32) {
-    uint4 w[kGvRowsPerWarp];
+  uint4 w[kGvRowsPerWarp], wn[kGvRowsPerWarp];
+  uint32_t sc[kGvRowsPerWarp], scn[kGvRowsPerWarp];
+  load_item(0, w, sc);
+  for (long long it = 0; it < items; ++it) {
+    if (it + 1 < items) load_item(it + 1, wn, scn);
+    const int row0 = item_row0(it);
+    const int b = (int)(it % kiters) * 32 + lane;
+    if (b < nblk) {
+      uint4 a0[T], a1[T];
+      float2 sx[T];
 #pragma unroll
-    for (int r = 0; r < kGvRowsPerWarp; ++r) {
-      const int row = min(row0 + r, N - 1);
-      w[r] = *reinterpret_cast<const uint4*>(codes + (size_t)row * (K / 2) + b * 16);
-    }
-    uint4 a0[T], a1[T];
-    float2 sx[T];
+      for (int t = 0; t < T; ++t) {
+        const uint4* ap = reinterpret_cast<const uint4*>(xq + (size_t)t * K + b * 32);
+        a0[t] = ap[0];
+        a1[t] = ap[1];
+        sx[t] = xs[t * nblk + b];
+      }
 #pragma unroll
-    for (int t = 0; t < T; ++t) {
-      const uint4* ap = reinterpret_cast<const uint4*>(xq + (size_t)t * K + b * 32);
-      a0[t] = ap[0];
-      a1[t] = ap[1];
-      sx[t] = xs[t * nblk + b];
-    }
+      for (int r = 0; r < kGvRowsPerWarp; ++r) {
+        const uint32_t cw[4] = {w[r].x, w[r].y, w[r].z, w[r].w};
+        if constexpr (FMT == 2) {
+          const float2 smf = unpack_bf16x2(sc[r]);                                  // {scale, min}
 #pragma unroll
-    for (int r = 0; r < kGvRowsPerWarp; ++r) {
-      const int row = min(row0 + r, N - 1);
-      const uint32_t cw[4] = {w[r].x, w[r].y, w[r].z, w[r].w};
-      if constexpr (FMT == 2) {
-        const uint32_t sm = reinterpret_cast<const uint32_t*>(scales)[(size_t)row * nblk + b];
-        const float2 smf = unpack_bf16x2(sm);                                     // {scale, min}
+          for (int t = 0; t < T; ++t) {
+            const uint32_t av[8] = {a0[t].x, a0[t].y, a0[t].z, a0[t].w, a1[t].x, a1[t].y, a1[t].z, a1[t].w};
+            int isum = 0;
 #pragma unroll
-        for (int t = 0; t < T; ++t) {
-          const uint32_t av[8] = {a0[t].x, a0[t].y, a0[t].z, a0[t].w, a1[t].x, a1[t].y, a1[t].z, a1[t].w};
-          int isum = 0;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            isum = __dp4a((int)(cw[j] & 0x0F0F0F0Fu), (int)av[2 * j], isum);
-            isum = __dp4a((int)((cw[j] >> 4) & 0x0F0F0F0Fu), (int)av[2 * j + 1], isum);
+            for (int j = 0; j < 4; ++j) {
+              isum = __dp4a((int)(cw[j] & 0x0F0F0F0Fu), (int)av[2 * j], isum);
+              isum = __dp4a((int)((cw[j] >> 4) & 0x0F0F0F0Fu), (int)av[2 * j + 1], isum);
+            }
+            acc[r][t] += smf.x * (sx[t].x * (float)isum) - smf.y * sx[t].y;
           }
-          acc[r][t] += smf.x * (sx[t].x * (float)isum) - smf.y * sx[t].y;
-        }
-      } else {
-        // index order: the low half-word of a code word holds values 0..3, the high half-word 4..7
-        uint32_t q8[8];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          q8[2 * j] = e2m1x4_to_s8(cw[j] & 0xFFFFu);
-          q8[2 * j + 1] = e2m1x4_to_s8(cw[j] >> 16);
-        }
-        float s_lo, s_hi;                                                          // scales of values 0..15 and 16..31, halved (codes were doubled)
-        if constexpr (FMT == 1) {
-          const uint32_t e = scales[(size_t)row * nblk + b];
-          s_lo = s_hi = e ? __uint_as_float(e << 23) * 0.5f : 0.f;
         } else {
-          const uint16_t two = reinterpret_cast<const uint16_t*>(scales)[(size_t)row * nblk + b];
-          const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(two, __NV_E4M3);
-          const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&h2));
-          s_lo = f2.x * 0.5f;
-          s_hi = f2.y * 0.5f;
-        }
-#pragma unroll
-        for (int t = 0; t < T; ++t) {
-          const uint32_t av[8] = {a0[t].x, a0[t].y, a0[t].z, a0[t].w, a1[t].x, a1[t].y, a1[t].z, a1[t].w};
-          int i_lo = 0, i_hi = 0;
+          // index order: the low half-word of a code word holds values 0..3, the high half-word 4..7
+          uint32_t q8[8];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            i_lo = __dp4a((int)q8[j], (int)av[j], i_lo);
-            i_hi = __dp4a((int)q8[4 + j], (int)av[4 + j], i_hi);
+            q8[2 * j] = e2m1x4_to_s8(cw[j] & 0xFFFFu);
+            q8[2 * j + 1] = e2m1x4_to_s8(cw[j] >> 16);
           }
-          acc[r][t] += sx[t].x * (s_lo * (float)i_lo + s_hi * (float)i_hi);
+          float s_lo, s_hi;                                                          // scales of values 0..15 and 16..31, halved (codes were doubled)
+          if constexpr (FMT == 1) {
+            const uint32_t e = sc[r];
+            s_lo = s_hi = e ? __uint_as_float(e << 23) * 0.5f : 0.f;
+          } else {
+            const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)sc[r], __NV_E4M3);
+            const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+            s_lo = f2.x * 0.5f;
+            s_hi = f2.y * 0.5f;
+          }
+#pragma unroll
+          for (int t = 0; t < T; ++t) {
+            const uint32_t av[8] = {a0[t].x, a0[t].y, a0[t].z, a0[t].w, a1[t].x, a1[t].y, a1[t].z, a1[t].w};
+            int i_lo = 0, i_hi = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              i_lo = __dp4a((int)q8[j], (int)av[j], i_lo);
+              i_hi = __dp4a((int)q8[4 + j], (int)av[4 + j], i_hi);
+            }
+            acc[r][t] += sx[t].x * (s_lo * (float)i_lo + s_hi * (float)i_hi);
+          }
         }
       }
     }
-  }
+    if ((it + 1) % kiters == 0) {                                      // last K slice of this row group: reduce and store
 #pragma unroll
-  for (int r = 0; r < kGvRowsPerWarp; ++r)
+      for (int r = 0; r < kGvRowsPerWarp; ++r)
 #pragma unroll
-    for (int t = 0; t < T; ++t) {
-      const float v = warp_sum(acc[r][t]);
-      const int row = row0 + r;
-      if (lane == 0 && row < N)
-        y[(size_t)t * ldy + row] = __float2bfloat16(v * alpha + (bias ? __bfloat162float(bias[row]) : 0.f));
+        for (int t = 0; t < T; ++t) {
+          const float v = warp_sum(acc[r][t]);
+          const int row = row0 + r;
+          if (lane == 0 && row < N)
+            y[(size_t)t * ldy + row] = __float2bfloat16(v * alpha + (bias ? __bfloat162float(bias[row]) : 0.f));
+          acc[r][t] = 0.f;
+        }
     }
+#pragma unroll
+    for (int r = 0; r < kGvRowsPerWarp; ++r) {
+      w[r] = wn[r];
+      sc[r] = scn[r];
+    }
+  }
 }
 
 template <int T, int FMT>
@@ -197,7 +232,8 @@ static void launch_gemv(const void* x, long long ldx, const void* codes, const v
   if (first_call_on_device(configured))
     cuda_check(cudaFuncSetAttribute(gemv_w4_kernel<T, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024),
                "cudaFuncSetAttribute(gemv_w4_kernel)");
-  launch_pdl(gemv_w4_kernel<T, FMT>, dim3((N + kGvRowsPerCta - 1) / kGvRowsPerCta), dim3(kGvThreads), smem, s,
+  const int ctas = std::min((N + kGvRowsPerCta - 1) / kGvRowsPerCta, sm_count() * 3);
+  launch_pdl(gemv_w4_kernel<T, FMT>, dim3(ctas), dim3(kGvThreads), smem, s,
              (const __nv_bfloat16*)x, ldx, (const uint8_t*)codes, (const uint8_t*)scales, alpha, (const __nv_bfloat16*)bias,
              (__nv_bfloat16*)y, ldy, N, K);
 }

@@ -13,9 +13,12 @@
 //   ep_wait       (token owner)  wait for every expert owner's flag; moe_combine then forms the
 //                                weighted sum locally
 //
-// Flags carry the call number (monotonic, passed by the host: every rank makes the same calls in the
-// same order), so nothing is reset between calls except the row counter, which its owner clears
-// before it publishes the return flag: no sender can claim a row of the next call earlier.
+// Flags carry the call number (monotonic; every rank makes the same calls in the same order), so nothing
+// is reset between calls except the row counter, which its owner clears before it publishes the return
+// flag: no sender can claim a row of the next call earlier. The call number lives in device memory
+// (`call_ctr`, local to the rank): the dispatch kernel uses counter + 1 and its last CTA stores that
+// value back, the three kernels after it read the stored value. A captured graph therefore replays
+// with the right number without the host. (A host-passed number is still accepted when no counter is given.)
 // Every wait is poll-bounded and reports FLLM_ERR_PEER_TIMEOUT through the status word.
 //
 // The reference does this on the host (rust/engine/src/parallel/decoder_shard.rs:442-446 dispatch,
@@ -40,9 +43,11 @@ struct EpPeers {
 
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ ids, int entries, int k,
-                   const EpPeers p, uint32_t epoch, int* __restrict__ status) {
+                   const EpPeers p, uint32_t epoch, uint32_t* __restrict__ call_ctr, int* __restrict__ status) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = p.hidden / 8;
+  // read before this CTA reports itself done: the store below happens after every CTA did
+  if (call_ctr) epoch = *reinterpret_cast<volatile uint32_t*>(call_ctr) + 1;
   for (int i = blockIdx.x * 8 + warp; i < entries; i += gridDim.x * 8) {
     const int e = ids[i];
     const int dst = e / p.experts_per_rank;
@@ -66,6 +71,7 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int
     uint32_t* done = p.ctrl[p.my_rank] + 24;
     if (atomicAdd(done, 1u) == gridDim.x - 1) {
       *done = 0;
+      if (call_ctr) *call_ctr = epoch;
       __threadfence_system();
       for (int d = 0; d < p.ranks; ++d) st_release_sys(p.ctrl[d] + 8 + p.my_rank, epoch);
     }
@@ -74,9 +80,10 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int
 
 // One CTA. ids_out[cap]: expert id of each received row, -1 for unused rows.
 __global__ void __launch_bounds__(1024)
-ep_ingest_kernel(const EpPeers p, uint32_t epoch, int* __restrict__ ids_out, int* __restrict__ count_out,
-                 int* __restrict__ status) {
+ep_ingest_kernel(const EpPeers p, uint32_t epoch, const uint32_t* __restrict__ call_ctr, int* __restrict__ ids_out,
+                 int* __restrict__ count_out, int* __restrict__ status) {
   __shared__ int ok;
+  if (call_ctr) epoch = *call_ctr;
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
   if (threadIdx.x < p.ranks) {
@@ -94,10 +101,11 @@ ep_ingest_kernel(const EpPeers p, uint32_t epoch, int* __restrict__ ids_out, int
 // y: expert outputs in permuted order; row_of[slot]: permuted row of received row `slot`.
 __global__ void __launch_bounds__(256)
 ep_return_kernel(const __nv_bfloat16* __restrict__ y, long long ldy, const int* __restrict__ row_of,
-                 const int* __restrict__ count, const EpPeers p, uint32_t epoch) {
+                 const int* __restrict__ count, const EpPeers p, uint32_t epoch, const uint32_t* __restrict__ call_ctr) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = p.hidden / 8;
   const int n = *count;
+  if (call_ctr) epoch = *call_ctr;
   for (int s = blockIdx.x * 8 + warp; s < n; s += gridDim.x * 8) {
     const int4 m = p.recv_meta[p.my_rank][s];
     const int row = row_of[s];
@@ -119,7 +127,8 @@ ep_return_kernel(const __nv_bfloat16* __restrict__ y, long long ldy, const int* 
   }
 }
 
-__global__ void ep_wait_kernel(const EpPeers p, uint32_t epoch, int* __restrict__ status) {
+__global__ void ep_wait_kernel(const EpPeers p, uint32_t epoch, const uint32_t* __restrict__ call_ctr, int* __restrict__ status) {
+  if (call_ctr) epoch = *call_ctr;
   if (threadIdx.x < p.ranks) {
     if (!wait_flag_ge(p.ctrl[p.my_rank] + 16 + threadIdx.x, epoch, kEpWaitPolls) && status)
       atomicCAS(status, FLLM_OK, FLLM_ERR_PEER_TIMEOUT);
@@ -141,29 +150,30 @@ static EpPeers to_peers(const EpArgs& a) {
 }
 
 void ep_dispatch(const EpArgs& a, const void* x, long long ldx, const int* ids, int tokens, int k, unsigned epoch,
-                 int* status, cudaStream_t s) {
+                 unsigned* call_ctr, int* status, cudaStream_t s) {
   const EpPeers p = to_peers(a);
   const int entries = tokens * k;
   const int blocks = std::max(1, std::min((entries + 7) / 8, 2 * sm_count()));
-  ep_dispatch_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)x, ldx, ids, entries, k, p, epoch, status);
+  ep_dispatch_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)x, ldx, ids, entries, k, p, epoch, call_ctr, status);
   cuda_check(cudaGetLastError(), "ep_dispatch_kernel");
 }
 
-void ep_ingest(const EpArgs& a, unsigned epoch, int* ids_out, int* count_out, int* status, cudaStream_t s) {
-  ep_ingest_kernel<<<1, 1024, 0, s>>>(to_peers(a), epoch, ids_out, count_out, status);
+void ep_ingest(const EpArgs& a, unsigned epoch, const unsigned* call_ctr, int* ids_out, int* count_out, int* status,
+               cudaStream_t s) {
+  ep_ingest_kernel<<<1, 1024, 0, s>>>(to_peers(a), epoch, call_ctr, ids_out, count_out, status);
   cuda_check(cudaGetLastError(), "ep_ingest_kernel");
 }
 
 void ep_return(const EpArgs& a, const void* y, long long ldy, const int* row_of, const int* count, unsigned epoch,
-               cudaStream_t s) {
+               const unsigned* call_ctr, cudaStream_t s) {
   const EpPeers p = to_peers(a);
   const int blocks = std::max(1, std::min((a.cap + 7) / 8, 2 * sm_count()));
-  ep_return_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)y, ldy, row_of, count, p, epoch);
+  ep_return_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)y, ldy, row_of, count, p, epoch, call_ctr);
   cuda_check(cudaGetLastError(), "ep_return_kernel");
 }
 
-void ep_wait_returns(const EpArgs& a, unsigned epoch, int* status, cudaStream_t s) {
-  ep_wait_kernel<<<1, 32, 0, s>>>(to_peers(a), epoch, status);
+void ep_wait_returns(const EpArgs& a, unsigned epoch, const unsigned* call_ctr, int* status, cudaStream_t s) {
+  ep_wait_kernel<<<1, 32, 0, s>>>(to_peers(a), epoch, call_ctr, status);
   cuda_check(cudaGetLastError(), "ep_wait_kernel");
 }
 

@@ -392,10 +392,10 @@ class LLMEngine:
                 and self.proposer is None)
 
     def _graph_eligible(self, step: ScheduledStep) -> bool:
-        # the all-to-all kernels take the call number from the host, which a captured graph would freeze
-        # (the PyTorch reference operators read sizes back to the host, which a capture does not allow)
+        # (the PyTorch reference operators read sizes back to the host, which a capture does not allow; the
+        # expert-parallel all-to-all keeps its call number on the device, so it replays inside a graph)
         return (self.is_cuda and self.cfg.use_cuda_graphs and step.all_decode and self.par.pp == 1
-                and hasattr(self.ops, "k") and getattr(self.decoder, "ep_a2a", None) is None
+                and hasattr(self.ops, "k")
                 and not any(s.verify for s in step.seqs) and self._bucket_for(len(step.seqs)) > 0)
 
     def _precommit(self, fl) -> None:
