@@ -50,7 +50,8 @@ def run_case(case: str, reps: int = 4) -> None:
     Cases: gemm_decode (64 tokens x gate_up of an 8B model), gemm_prefill (2048 tokens), attn_decode
     (64 sequences at 1152 context), attn_prefill (2 x 1024 tokens), attn_prefill_long (4 x 4096 tokens),
     fp8_prefill, gemm_fp4_decode (64 tokens x NVFP4 gate_up), gemm_mx4_decode / gemm_mx4_prefill / gemm_mx8_decode /
-    gemm_nvf4_decode / gemm_nvf4_prefill (block-scaled MXFP4 / MXFP8 / NVFP4 gate_up), tp_rs_gemm / tp_norm / tp_ag_gemm (the fused
+    gemm_nvf4_decode / gemm_nvf4_prefill (block-scaled MXFP4 / MXFP8 / NVFP4 gate_up), gemv_q4k (one token x 4-bit
+    gate_up on the dp4a kernel), tp_rs_gemm / tp_norm / tp_ag_gemm (the fused
     tensor-parallel kernels with two virtual ranks on one device)."""
     from .ops.native import NativeOps, Fp8BlockLinear, quantize_weight_fp8_block
     ops = NativeOps(torch.device("cuda:0"))
@@ -82,6 +83,13 @@ def run_case(case: str, reps: int = 4) -> None:
                          torch.full((24576, 128), 120, device="cuda", dtype=torch.uint8), a4)
         q.atoms
         y = torch.empty(T, 24576, **bf)
+        fn = lambda: ops.linear(x, q, out=y)
+    elif case == "gemv_q4k":
+        from .ops.int4 import Int4Weight
+        x = torch.randn(1, 4096, **bf)
+        q = Int4Weight(torch.randint(0, 256, (24576, 2048), device="cuda", dtype=torch.uint8),
+                       torch.full((24576, 128, 2), 0.01, device="cuda", dtype=torch.bfloat16))
+        y = torch.empty(1, 24576, **bf)
         fn = lambda: ops.linear(x, q, out=y)
     elif case in ("tp_rs_gemm", "tp_norm", "tp_ag_gemm"):
         # the fused tensor-parallel kernels with two virtual ranks on this one device (plain pointers instead

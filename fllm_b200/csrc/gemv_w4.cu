@@ -13,8 +13,8 @@
 //   1 MXFP4  e2m1 codes in index order + e8m0 scale per 32; 0 NVFP4: + e4m3 scale per 16 and a tensor scale.
 //            e2m1 magnitudes {0, .5, 1, 1.5, 2, 3, 4, 6} are doubled into int8 by a byte-permute table.
 //
-// One warp owns four output rows at a time (four independent 16-byte loads per lane, and the next four already
-// in flight); CTAs are persistent (at most three per SM), so the activations are quantised once per CTA.
+// One warp owns eight (one or two tokens) or four output rows at a time (as many independent 16-byte loads per lane,
+// and the next group's already in flight); CTAs are persistent (at most three per SM), so the activations are quantised once per CTA.
 // Reference counterparts: rust/engine/cuda/mmvq.cu:50,173,375 (dp4a GEMV on q8_1 activations),
 // rust/engine/cuda/gemv2.cu.
 #include <cuda_fp8.h>
@@ -28,9 +28,9 @@
 namespace fllm {
 
 constexpr int kGvThreads = 256;
-constexpr int kGvRowsPerWarp = 4;
-constexpr int kGvRowsPerCta = (kGvThreads / 32) * kGvRowsPerWarp;
 constexpr int kGvMaxT = 4;
+// rows a warp multiplies at a time: its loads in flight per item. One or two tokens leave registers for eight.
+__host__ __device__ constexpr int gv_rows_per_warp(int T) { return T <= 2 ? 8 : 4; }
 
 __device__ __forceinline__ uint32_t gv_prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t d;
@@ -105,11 +105,12 @@ gemv_w4_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const uint8_t
   }
   __syncthreads();
 
+  constexpr int kGvRowsPerWarp = gv_rows_per_warp(T);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Persistent CTAs: the activations are quantised once per CTA, then every warp walks (row group, K slice)
   // items with the next item's codes already in flight while the current one is multiplied.
   const int kiters = (nblk + 31) / 32;                                 // K slices of 32 blocks per row group
-  const int n_groups = (N + kGvRowsPerWarp - 1) / kGvRowsPerWarp;      // row groups of 4 rows
+  const int n_groups = (N + kGvRowsPerWarp - 1) / kGvRowsPerWarp;      // row groups of kGvRowsPerWarp rows
   const int warps_total = gridDim.x * (kGvThreads / 32);
   const int gwarp = blockIdx.x * (kGvThreads / 32) + warp;
   const long long items = (long long)((n_groups - gwarp + warps_total - 1) / warps_total) * kiters;   // this warp's items
@@ -232,7 +233,14 @@ static void launch_gemv(const void* x, long long ldx, const void* codes, const v
   if (first_call_on_device(configured))
     cuda_check(cudaFuncSetAttribute(gemv_w4_kernel<T, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024),
                "cudaFuncSetAttribute(gemv_w4_kernel)");
-  const int ctas = std::min((N + kGvRowsPerCta - 1) / kGvRowsPerCta, sm_count() * 3);
+  int per_sm = 1;
+  cuda_check(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_w4_kernel<T, FMT>, kGvThreads, smem), "gemv_w4 occupancy");
+  const int resident = sm_count() * std::max(per_sm, 1);
+  // equal work per CTA: as many rounds of row blocks as the resident CTAs need, then the fewest CTAs for that many rounds
+  const int rows_per_cta = (kGvThreads / 32) * gv_rows_per_warp(T);
+  const int row_blocks = (N + rows_per_cta - 1) / rows_per_cta;
+  const int rounds = (row_blocks + resident - 1) / resident;
+  const int ctas = (row_blocks + rounds - 1) / rounds;
   launch_pdl(gemv_w4_kernel<T, FMT>, dim3(ctas), dim3(kGvThreads), smem, s,
              (const __nv_bfloat16*)x, ldx, (const uint8_t*)codes, (const uint8_t*)scales, alpha, (const __nv_bfloat16*)bias,
              (__nv_bfloat16*)y, ldy, N, K);
