@@ -47,7 +47,8 @@ class Timer:
 def run_case(case: str, reps: int = 4) -> None:
     """One kernel family, a handful of launches, inputs larger than L2 but far below a GB-scale footprint:
     a self-ending workload for a profiler capture or a quick look (``bench-kernel --case gemm_decode``).
-    Cases: gemm_decode (64 tokens x gate_up of an 8B model), gemm_prefill (2048 tokens), attn_decode
+    Cases: gemm_decode (64 tokens x gate_up of an 8B model), gemm_prefill (2048 tokens), gemm_pair_prefill (the same on
+    CTA pairs, cta_group::2), attn_decode
     (64 sequences at 1152 context), attn_prefill (2 x 1024 tokens), attn_prefill_long (4 x 4096 tokens),
     fp8_prefill, gemm_fp4_decode (64 tokens x NVFP4 gate_up), gemm_mx4_decode / gemm_mx4_prefill / gemm_mx8_decode /
     gemm_nvf4_decode / gemm_nvf4_prefill (block-scaled MXFP4 / MXFP8 / NVFP4 gate_up), gemv_q4k (one token x 4-bit
@@ -56,12 +57,12 @@ def run_case(case: str, reps: int = 4) -> None:
     from .ops.native import NativeOps, Fp8BlockLinear, quantize_weight_fp8_block
     ops = NativeOps(torch.device("cuda:0"))
     bf = dict(device="cuda", dtype=torch.bfloat16)
-    if case in ("gemm_decode", "gemm_prefill"):
+    if case in ("gemm_decode", "gemm_prefill", "gemm_pair_prefill"):
         T = 64 if case == "gemm_decode" else 2048
         x = torch.randn(T, 4096, **bf)
         w = torch.randn(24576, 4096, **bf) * 0.02
         y = torch.empty(T, 24576, **bf)
-        fn = lambda: ops.linear(x, w, out=y)
+        fn = (lambda: ops.k.linear_pair(x, w, None, y, ops.status)) if case == "gemm_pair_prefill" else (lambda: ops.linear(x, w, out=y))
     elif case == "gemm_fp4_decode":
         from .ops.fp4 import Fp4Weight
         x = torch.randn(64, 4096, **bf)
@@ -334,6 +335,11 @@ def main(argv=None) -> None:
             y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
             ms = timer(lambda: ops.linear(x, w, out=y))
             ms_lib = timer(lambda: torch.matmul(x, w.t(), out=y))
+            if T >= 256 and N >= 256 and N % 8 == 0:                 # the CTA-pair kernel on its own, whatever the planner picks
+                ms_pair = timer(lambda: ops.k.linear_pair(x, w, None, y, ops.status))
+                print(f"{name + ' (pair)':10s} {T:6d} {N:7d} {K:6d} {ms_pair:9.4f} {ms_lib:9.4f} {2.0 * T * N * K / ms_pair / 1e9:8.1f}")
+                rows.append({"op": name + "_pair", "T": T, "N": N, "K": K, "ms": ms_pair, "cublas_ms": ms_lib,
+                             "tflops": 2.0 * T * N * K / ms_pair / 1e9})
             flops = 2.0 * T * N * K
             byts = 2.0 * (T * K + N * K + T * N)
             t_c, t_m = flops / (tflops * 1e12), byts / (hbm * 1e9)

@@ -54,6 +54,19 @@ int64_t linear(const Tensor& x, const Tensor& w, const optional<Tensor>& bias, T
                     ws_bytes, st, (int)force_splits, cur_stream());
 }
 
+// y = x @ w^T (+ bias) on CTA pairs (cta_group::2, 256 x 256 tiles): at least 256 tokens.
+int64_t linear_pair(const Tensor& x, const Tensor& w, const optional<Tensor>& bias, Tensor y, const optional<Tensor>& status) {
+  check_bf16(x, "x"); check_bf16(w, "w"); check_bf16(y, "y");
+  check_rows(x, "x"); check_rows(w, "w"); check_rows(y, "y");
+  TORCH_CHECK(x.size(1) == w.size(1), "linear_pair: K mismatch");
+  TORCH_CHECK(y.size(0) == x.size(0) && y.size(1) == w.size(0), "linear_pair: output shape mismatch");
+  TORCH_CHECK(fllm::linear_bf16_pair_supported((int)x.size(0), (int)w.size(0), (int)x.size(1)), "linear_pair: shape not supported");
+  c10::cuda::CUDAGuard guard(x.device());
+  int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  return fllm::linear_bf16_pair(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), opt_ptr<void>(bias), y.data_ptr(),
+                                y.stride(0), (int)x.size(0), (int)w.size(0), (int)x.size(1), st, cur_stream());
+}
+
 // linear with the optional behaviours of fllm::LinearExtras. glu > 0: y is [T, N / 2] (the activation runs in the
 // epilogue, or in the caller's consumer when the call deferred split-K). Returns [kernels launched, deferred splits].
 std::vector<int64_t> linear_ex(const Tensor& x, const Tensor& w, const optional<Tensor>& bias, Tensor y,
@@ -375,6 +388,7 @@ int64_t sample_row_bytes() { return (int64_t)sizeof(fllm::SampleRow); }
 
 TORCH_LIBRARY(fllm_b200, m) {
   m.def("linear(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status, int force_splits) -> int", &linear);
+  m.def("linear_pair(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y, Tensor? status) -> int", &linear_pair);
   m.def("linear_ex(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status, int force_splits, int glu, int glu_pd, float glu_alpha, float glu_limit, bool defer_reduce) -> int[]", &linear_ex);
   m.def("rmsnorm_splitk(Tensor(a!) residual, Tensor workspace, int splits, Tensor? bias, Tensor w, Tensor(b!) y, float eps, float w_offset) -> ()", &rmsnorm_splitk);
   m.def("rope_kv_write_splitk(Tensor workspace, int splits, Tensor? bias, Tensor(a!) q_out, Tensor positions, Tensor? slots, Tensor inv_freq, Tensor? q_norm_w, Tensor? k_norm_w, Tensor(b!) k_cache, Tensor(c!) v_cache, int hq, int hkv, int head_dim, int rot_dim, int rope_style, float eps, float attn_factor) -> ()", &rope_kv_write_splitk);

@@ -763,3 +763,19 @@ def test_attention_tc_decode_reads_e4m3_cache(ops, ref, D, hq, hkv, window, sink
     yg = ops.attention(q, kc8, vc8, tables, row_seq, pos, hq, hkv, D, D ** -0.5, window, sk, softcap)
     _close(yg, y, 2e-2)
     assert ops.check_status() == 0
+
+
+@pytest.mark.parametrize("T", [256, 300, 1024, 2048])
+@pytest.mark.parametrize("N,K", [(512, 512), (4096, 4096), (1000, 320), (6144, 4096), (256, 12288)])
+def test_linear_on_cta_pairs(ops, T, N, K):
+    """tcgen05 cta_group::2 GEMM (256 x 256 tiles over two SMs) against fp32 math: ragged token and feature edges,
+    a K that is not a multiple of the stage depth, bias, several tiles per cluster."""
+    x = _rand((T, K), 21)
+    w = _rand((N, K), 22, 0.05)
+    bias = _rand((N,), 23) if T % 512 == 0 else None
+    y = torch.full((T + 2, N), 7.0, dtype=torch.bfloat16, device="cuda")     # two sentinel rows after the output
+    ops.k.linear_pair(x, w, bias, y[:T], ops.status)
+    ref = x.float() @ w.float().t() + (bias.float() if bias is not None else 0)
+    _close(y[:T], ref, 1e-2)
+    assert bool((y[T:] == 7.0).all())
+    assert ops.check_status() == 0
