@@ -101,7 +101,7 @@ void symm_close(void* p);
 // Large-batch bf16 GEMM on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles): T >= 256, N >= 256, N % 8 == 0, K % 8 == 0.
 bool linear_bf16_pair_supported(int T, int N, int K);
 int linear_bf16_pair(const void* x, long long ldx, const void* w, long long ldw, const void* bias, void* y, long long ldy,
-                     int T, int N, int K, int* status, cudaStream_t stream);
+                     int T, int N, int K, int* status, cudaStream_t stream, const struct LinearExtras* ex = nullptr);
 
 // Packed 4-bit weights x at most 4 tokens on dp4a (int8 activations quantised inside the kernel); formats as linear_w4a16.
 bool gemv_w4_supported(int T, int K);

@@ -844,6 +844,10 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
   if ((K & 7) || (N & 7) || (ldx & 7) || (ldw & 7) || (ldy & 1))
     throw std::runtime_error("linear_bf16: K, N and the row pitches must be multiples of 8");
   const int sms = sm_count();
+  // Large local products go to the CTA-pair kernel (cta_group::2, 256 x 256 tiles) once its tiles fill the machine.
+  if (!tpa && force_splits <= 0 && (ldy & 7) == 0 && linear_bf16_pair_supported(T, N, K) &&
+      (long long)((T + 255) / 256) * ((N + 255) / 256) >= sms / 2)
+    return linear_bf16_pair(x, ldx, w, ldw, bias, y, ldy, T, N, K, status, stream, glu ? ex : nullptr);
   GemmArgs a{};
   a.K = K;
   a.k_blocks = (K + BK - 1) / BK;

@@ -4,7 +4,7 @@
 // of x and only its own half (128 feature rows) of the weight tile; one thread of the even CTA issues
 // tcgen05.mma.cta_group::2 (256 x 256 x 16 per instruction) and the hardware feeds both tensor cores with
 // both halves of the weight tile. Against the one-CTA 128 x 256 tile of gemm_bf16.cu a stage shrinks from
-// 48 KB to 32 KB per SM for the same arithmetic, so six stages instead of four cover the load latency, and
+// 48 KB to 32 KB per SM for the same arithmetic, so seven stages instead of four cover the load latency, and
 // every weight byte is read from shared memory by one SM instead of two.
 //
 //   TMA (both CTAs, `.cta_group::2` form: the bytes of both land on the even CTA's barrier; no cluster multicast)
@@ -27,7 +27,7 @@ namespace fllm {
 constexpr int P2_ROWS = 128;                 // rows of either operand per CTA per stage
 constexpr int P2_BK = 64;                    // 64 bf16 = one 128-byte swizzle row
 constexpr int P2_TILE = 256;                 // tile edge of the pair (tokens and features)
-constexpr int P2_STAGES = 6;
+constexpr int P2_STAGES = 7;
 constexpr int kP2Threads = 192;
 constexpr int kP2OperandBytes = P2_ROWS * P2_BK * 2;          // 16 KB
 constexpr int kP2StageBytes = 2 * kP2OperandBytes;            // x rows + weight rows
@@ -41,6 +41,9 @@ struct Gemm2Args {
   __nv_bfloat16* out;
   const __nv_bfloat16* bias;
   int* status;
+  int glu;                                   // 0 none; 1 SwiGLU, 2 GeGLU (tanh), 3 clamped SwiGLU-OAI: out is [M, N / 2]
+  int glu_pd;                                // distance between a gate column and its up column: 16 (blocks of 16) or 1 (pairs)
+  float glu_alpha, glu_limit;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -186,12 +189,46 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_co
       const int n_base = n_idx * P2_TILE;
       const uint32_t t_row = tmem_base + buf * P2_TILE + ((uint32_t)(q * 32) << 16);
       __nv_bfloat16* dst = p.out + (size_t)m * p.ldc + n_base;
+      auto gated = [&](float g, float u) -> float {
+        if (p.glu == 1) return g / (1.f + __expf(-g)) * u;
+        if (p.glu == 2) {
+          const float c = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+          return 0.5f * g * (1.f + tanhf(c)) * u;
+        }
+        const float gg = fminf(g, p.glu_limit);
+        const float uu = fminf(fmaxf(u, -p.glu_limit), p.glu_limit);
+        return gg / (1.f + __expf(-p.glu_alpha * gg)) * (uu + 1.f);
+      };
 #pragma unroll 1
       for (int c0 = 0; c0 < P2_TILE; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(t_row + c0, r);
         tmem_ld_wait();
-        if (m < p.M) {
+        if (p.glu) {
+          // features run along the columns: a 32-column chunk holds 16 (gate, up) pairs of this token
+          const int n0 = n_base + c0;
+          if (m < p.M && n0 < p.N) {
+            uint32_t o[8];
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+              float v2[2];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int gi = p.glu_pd == 16 ? i + h : 2 * (i + h), ui = p.glu_pd == 16 ? i + h + 16 : 2 * (i + h) + 1;
+                float g = __uint_as_float(r[gi]), u = __uint_as_float(r[ui]);
+                if (p.bias) {
+                  g += __bfloat162float(p.bias[n0 + gi]);
+                  u += __bfloat162float(p.bias[n0 + ui]);
+                }
+                v2[h] = gated(g, u);
+              }
+              o[i >> 1] = pack_bf16x2(v2[0], v2[1]);
+            }
+            uint4* d4 = reinterpret_cast<uint4*>(p.out + (size_t)m * p.ldc + n0 / 2);
+            d4[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            d4[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          }
+        } else if (m < p.M) {
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {
             const int n = n_base + c0 + c;
@@ -223,12 +260,16 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_co
 
 bool linear_bf16_pair_supported(int T, int N, int K) { return T >= 256 && N % 8 == 0 && N >= 256 && K % 8 == 0 && K >= P2_BK; }
 
-// y[T, N] = x[T, K] * w[N, K]^T (+ bias[N]); row pitches in elements.
+// y[T, N] = x[T, K] * w[N, K]^T (+ bias[N]); row pitches in elements. With ex->glu the gated activation runs in the
+// epilogue and y is [T, N / 2] (N a multiple of 32).
 int linear_bf16_pair(const void* x, long long ldx, const void* w, long long ldw, const void* bias, void* y, long long ldy,
-                     int T, int N, int K, int* status, cudaStream_t stream) {
+                     int T, int N, int K, int* status, cudaStream_t stream, const LinearExtras* ex) {
   if (!linear_bf16_pair_supported(T, N, K)) throw std::runtime_error("linear_bf16_pair: needs >= 256 tokens, N >= 256, N % 8 == 0, K % 8 == 0");
   if ((ldy & 7)) throw std::runtime_error("linear_bf16_pair: output rows must be 16-byte aligned");
+  const int glu = ex ? ex->glu : 0;
+  if (glu && ((N & 31) || (ex->glu_pd != 16 && ex->glu_pd != 1))) throw std::runtime_error("linear_bf16_pair: GLU needs N % 32 == 0 and a pair distance of 16 or 1");
   Gemm2Args a{};
+  if (glu) { a.glu = glu; a.glu_pd = ex->glu_pd; a.glu_alpha = ex->glu_alpha; a.glu_limit = ex->glu_limit; }
   a.M = T; a.N = N; a.K = K;
   a.m_tiles = (T + P2_TILE - 1) / P2_TILE; a.n_tiles = (N + P2_TILE - 1) / P2_TILE; a.k_blocks = (K + P2_BK - 1) / P2_BK;
   a.ldc = ldy; a.out = reinterpret_cast<__nv_bfloat16*>(y); a.bias = reinterpret_cast<const __nv_bfloat16*>(bias); a.status = status;

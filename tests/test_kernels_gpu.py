@@ -779,3 +779,17 @@ def test_linear_on_cta_pairs(ops, T, N, K):
     _close(y[:T], ref, 1e-2)
     assert bool((y[T:] == 7.0).all())
     assert ops.check_status() == 0
+
+
+@pytest.mark.parametrize("kind,layout", [(0, 16), (1, 16), (2, 16), (2, 0)])
+def test_large_batch_linear_glu_goes_through_the_pair_kernel(ops, ref, kind, layout):
+    """2048 tokens x a gate|up matrix: the planner picks the CTA-pair kernel and its epilogue applies the gated
+    activation (blocked-16 and pairwise layouts)."""
+    T, N, K = 2048, 4096, 1024
+    x = _rand((T, K), 31)
+    w = _rand((N, K), 32, 0.05)
+    bias = _rand((N,), 33)
+    y = ops.linear_glu(x, w, bias, kind, 1.702, 7.0, layout)
+    yr = ref.linear_glu(x, w, bias, kind, 1.702, 7.0, layout)
+    _close(y, yr, 2e-2)
+    assert ops.check_status() == 0
