@@ -66,7 +66,7 @@ class ModelConfig:
     router_kind: str = "softmax_topk"    # softmax over the selected top-k logits
     expert_bias: bool = False
     # weight format of the big matrices
-    weight_format: str = "bf16"          # bf16 | fp8_block | nvfp4 | mxfp4 | mxfp8 | mxfp4_a8 | nvfp4_a4 | q4_k | ...
+    weight_format: str = "bf16"          # bf16 | fp8_block | nvfp4 | mxfp4 | mxfp8 | mxfp4_a8 | nvfp4_a4 | int8_w8a8 | fp8_w8a8 | q4_k | ...
     name: str = "model"
 
     # ---- derived

@@ -84,6 +84,38 @@ int64_t mx_act_scale_bytes(int64_t T, int64_t K, int64_t kind) { return (int64_t
 
 // kind 0: wq e4m3 [N, K], xq e4m3 [T, K]; kind 1: wq e2m1 codes [N, K/2], xq e4m3 [T, K]; kind 2: both e2m1 codes.
 // sfa: weight scale atoms [ceil(N/128), K/128 (K/64 for kind 2), 512]
+void quant_rows_8bit(const Tensor& x, Tensor xq, Tensor tok_scale, bool is_int8) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 && x.stride(0) % 8 == 0 && x.size(1) % 8 == 0, "x: bf16 rows, K % 8 == 0");
+  TORCH_CHECK(xq.is_contiguous() && xq.element_size() == 1 && xq.numel() == x.numel(), "xq: contiguous 1-byte [T, K]");
+  TORCH_CHECK(tok_scale.is_contiguous() && tok_scale.scalar_type() == at::kFloat && tok_scale.numel() >= x.size(0), "tok_scale: fp32 [T]");
+  c10::cuda::CUDAGuard guard(x.device());
+  fllm::quant_rows_8bit(x.data_ptr(), x.stride(0), xq.data_ptr(), tok_scale.data_ptr<float>(), (int)x.size(0), (int)x.size(1),
+                        is_int8 ? 1 : 0, cur_stream());
+}
+
+// y = (xq * tok_scale) (wq * feat_scale)^T (+ bias): e4m3 (is_int8 false) or int8 codes on both sides, one scale per row
+int64_t linear_w8a8(const Tensor& xq, const Tensor& tok_scale, const Tensor& wq, const Tensor& feat_scale, bool is_int8,
+                    const optional<Tensor>& bias, Tensor y, const optional<Tensor>& workspace, const optional<Tensor>& status) {
+  TORCH_CHECK(xq.is_cuda() && xq.is_contiguous() && wq.is_contiguous() && xq.element_size() == 1 && wq.element_size() == 1 &&
+              xq.dim() == 2 && wq.dim() == 2 && xq.size(1) == wq.size(1) && xq.size(1) % 128 == 0, "xq, wq: contiguous byte matrices, K % 128 == 0");
+  const int64_t T = xq.size(0), K = xq.size(1), N = wq.size(0);
+  TORCH_CHECK(tok_scale.scalar_type() == at::kFloat && tok_scale.is_contiguous() && tok_scale.numel() >= T, "tok_scale: fp32 [T]");
+  TORCH_CHECK(feat_scale.scalar_type() == at::kFloat && feat_scale.is_contiguous() && feat_scale.numel() == N, "feat_scale: fp32 [N]");
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.stride(1) == 1 && y.size(0) == T && y.size(1) == N, "y: [T, N] bf16");
+  c10::cuda::CUDAGuard guard(xq.device());
+  const void* b = bias.has_value() && bias->defined() ? bias->data_ptr() : nullptr;
+  int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  if (workspace.has_value() && workspace->defined() && workspace->numel() * workspace->element_size() > (64 << 10)) {
+    ws = static_cast<char*>(workspace->data_ptr()) + (64 << 10);
+    ws_bytes = workspace->numel() * workspace->element_size() - (64 << 10);
+  }
+  return fllm::linear_mx(xq.data_ptr(), nullptr, wq.data_ptr(), nullptr, is_int8 ? 4 : 3, 1.f, tok_scale.data_ptr<float>(),
+                         feat_scale.data_ptr<float>(), b, y.data_ptr(), y.stride(0), (int)T, (int)N, (int)K, ws, ws_bytes, st,
+                         cur_stream());
+}
+
 int64_t linear_mx(const Tensor& xq, const Tensor& sfb, const Tensor& wq, const Tensor& sfa, int64_t kind, double alpha,
                   const optional<Tensor>& tok_scale, const optional<Tensor>& bias, Tensor y, const optional<Tensor>& workspace,
                   const optional<Tensor>& status) {
@@ -111,7 +143,7 @@ int64_t linear_mx(const Tensor& xq, const Tensor& sfb, const Tensor& wq, const T
     ws = static_cast<char*>(workspace->data_ptr()) + (64 << 10);
     ws_bytes = workspace->numel() * workspace->element_size() - (64 << 10);
   }
-  return fllm::linear_mx(xq.data_ptr(), sfb.data_ptr(), wq.data_ptr(), sfa.data_ptr(), (int)kind, (float)alpha, ts, b,
+  return fllm::linear_mx(xq.data_ptr(), sfb.data_ptr(), wq.data_ptr(), sfa.data_ptr(), (int)kind, (float)alpha, ts, nullptr, b,
                          y.data_ptr(), y.stride(0), (int)T, (int)N, (int)K, ws, ws_bytes, st, cur_stream());
 }
 
@@ -145,6 +177,8 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("linear_fp8_block(Tensor xq, Tensor sx, Tensor wq, Tensor sw, Tensor? bias, Tensor(a!) y, Tensor? status) -> int", &linear_fp8_block);
   m.def("linear_w4a16(Tensor x, Tensor codes, Tensor scales, int fmt, float alpha, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status) -> int", &linear_w4a16);
   m.def("quant_mx(Tensor x, Tensor(a!) xq, Tensor(b!) sf) -> ()", &quant_mx);
+  m.def("quant_rows_8bit(Tensor x, Tensor(a!) xq, Tensor(b!) tok_scale, bool is_int8) -> ()", &quant_rows_8bit);
+  m.def("linear_w8a8(Tensor xq, Tensor tok_scale, Tensor wq, Tensor feat_scale, bool is_int8, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status) -> int", &linear_w8a8);
   m.def("quant_nvfp4(Tensor x, Tensor(a!) xq, Tensor(b!) sf, Tensor(c!) tok_scale) -> ()", &quant_nvfp4);
   m.def("mx_act_scale_bytes(int T, int K, int kind) -> int", &mx_act_scale_bytes);
   m.def("linear_mx(Tensor xq, Tensor sfb, Tensor wq, Tensor sfa, int kind, float alpha, Tensor? tok_scale, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status) -> int", &linear_mx);

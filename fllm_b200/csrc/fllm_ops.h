@@ -116,9 +116,11 @@ int mx_token_tile(int T);
 size_t mx_act_scale_bytes(int T, int K, int kind);
 void quant_mx(const void* x, long long ldx, void* xq, void* sf, int T, int K, cudaStream_t s);
 void quant_nvfp4(const void* x, long long ldx, void* xq, void* sf, float* tok_scale, int T, int K, cudaStream_t s);
+// kinds 3 / 4: e4m3 / int8 on both sides without scale atoms (sfa = sfb = null): feat_scale[N] and tok_scale[T].
+void quant_rows_8bit(const void* x, long long ldx, void* xq, float* tok_scale, int T, int K, int is_int8, cudaStream_t s);
 int linear_mx(const void* xq, const void* sfb, const void* wq, const void* sfa, int kind, float alpha,
-              const float* tok_scale, const void* bias, void* y, long long ldy, int T, int N, int K, void* workspace,
-              size_t workspace_bytes, int* status, cudaStream_t stream);
+              const float* tok_scale, const float* feat_scale, const void* bias, void* y, long long ldy, int T, int N, int K,
+              void* workspace, size_t workspace_bytes, int* status, cudaStream_t stream);
 void quant_fp8_1x128(const void* x, long long ldx, void* xq, float* sx, int tokens, int K, cudaStream_t s);
 int linear_fp8_block(const void* xq, const float* sx, const void* wq, const float* sw, const void* bias, void* y,
                      long long ldy, int T, int N, int K, int* status, cudaStream_t stream);

@@ -30,6 +30,11 @@
 // per-token activation scale applied in the epilogue. The activation quantiser (quant_nvfp4_kernel) derives the
 // token scale from the token's largest magnitude, so no calibration pass is needed.
 //
+// Two more kinds share the tile loop without block scales: e4m3 x e4m3 (kind::f8f6f4) and int8 x int8 (kind::i8,
+// int32 accumulators) with one scale per output feature and one per token, applied in the epilogue. They are the
+// W8A8 forms of per-channel FP8 and SmoothQuant-style INT8 checkpoints (dynamic per-token activation scales,
+// quant_rows_8bit_kernel).
+//
 // Reference counterparts: rust/engine/cuda/nvfp4.cu:132-307 (mma.sync block-scaled FP4 for GeForce
 // Blackwell; the data-centre parts fall back to W4A16 Marlin there), rust/engine/cuda/mxfp4_moe.cu.
 #include <cuda_fp4.h>
@@ -57,14 +62,17 @@ struct MxArgs {
   const uint8_t* sfa;            // [m_tiles][k_blocks][512]
   const uint8_t* sfb;            // [n_tiles][k_blocks][512]
   float alpha;
-  const float* tok_scale;        // [N] per-token factor (NVFP4 activations), or null
+  const float* tok_scale;        // [N] per-token factor (NVFP4 and row-scaled activations), or null
+  const float* feat_scale;       // [M] per-feature factor (row-scaled 8-bit weights), or null
   const __nv_bfloat16* bias;
   int* status;
 };
 
 // KIND: 0 = e4m3 weights, 1 = packed e2m1 weights unpacked by TMA (both kind::mxf8f6f4, e8m0 scales per 32,
 // 128 values of K per stage), 2 = packed e2m1 on both sides (kind::mxf4nvf4, e4m3 scales per 16, 256 per stage).
-constexpr int kMxKindE4M3 = 0, kMxKindE2M1A8 = 1, kMxKindNvf4 = 2;
+// 3 = e4m3 x e4m3 and 4 = int8 x int8 without block scales (one scale per feature and per token, in the epilogue).
+constexpr int kMxKindE4M3 = 0, kMxKindE2M1A8 = 1, kMxKindNvf4 = 2, kMxKindRowF8 = 3, kMxKindRowI8 = 4;
+__host__ __device__ constexpr bool mx_kind_has_sf(int kind) { return kind <= kMxKindNvf4; }
 
 template <int BN, int KIND>
 struct MxSmem {
@@ -72,11 +80,11 @@ struct MxSmem {
   static constexpr int kBBytes = BN * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStageK = KIND == kMxKindNvf4 ? 256 : 128;
-  static constexpr int kAtoms = KIND == kMxKindNvf4 ? 4 : 1;     // scale atoms per operand per stage
+  static constexpr int kAtoms = KIND == kMxKindNvf4 ? 4 : (mx_kind_has_sf(KIND) ? 1 : 0);   // scale atoms per operand per stage
   // two CTAs per SM when BN <= 64: the NVFP4 stage carries 4 KB of scale atoms, so three stages fit twice
   static constexpr int kStages = BN <= 64 ? (KIND == kMxKindNvf4 ? 3 : 4) : 6;
   static constexpr int kAccCols = BN < 32 ? 32 : BN;
-  static constexpr int kSfCols = 2 * 8 * kAtoms;                // two buffers of (A, B) x 4 columns per atom
+  static constexpr int kSfCols = kAtoms ? 2 * 8 * kAtoms : 0;   // two buffers of (A, B) x 4 columns per atom
   static constexpr int kTmemCols = kAccCols + kSfCols <= 64 ? 64 : (kAccCols + kSfCols <= 128 ? 128 : 256);
   static constexpr int kSfBytes = kStages * 2 * kAtoms * kMxAtomBytes;
   static constexpr int kTotal = kStages * kStageBytes + kSfBytes + 256 + 1024;
@@ -125,6 +133,19 @@ __device__ __forceinline__ void tc_mma_nvf4(uint32_t tmem_d, uint64_t desc_a, ui
       "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
       : "memory");
+}
+
+// int8 x int8 -> int32 accumulators; idesc: D format S32 (2 at bits 4-5), signed operands (format 1)
+__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__host__ __device__ constexpr uint32_t make_idesc_i8(int M, int N) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -183,17 +204,21 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         const int xa = KIND == kMxKindNvf4 ? kb * 128 : kb * S::kStageK;
         tma_load_2d(sA + stage * S::kABytes, &tma_a, &full_bar[stage], xa, m_idx * MX_BM);
         tma_load_2d(sB + stage * S::kBBytes, &tma_b, &full_bar[stage], xa, n_idx * BN);
-        bulk_load_1d(sSF + stage * SF_STAGE, p.sfa + ((size_t)m_idx * p.k_blocks + kb) * (SF_STAGE / 2), SF_STAGE / 2,
-                     &full_bar[stage]);
-        bulk_load_1d(sSF + stage * SF_STAGE + SF_STAGE / 2, p.sfb + ((size_t)n_idx * p.k_blocks + kb) * (SF_STAGE / 2),
-                     SF_STAGE / 2, &full_bar[stage]);
+        if constexpr (SF_STAGE > 0) {
+          bulk_load_1d(sSF + stage * SF_STAGE, p.sfa + ((size_t)m_idx * p.k_blocks + kb) * (SF_STAGE / 2), SF_STAGE / 2,
+                       &full_bar[stage]);
+          bulk_load_1d(sSF + stage * SF_STAGE + SF_STAGE / 2, p.sfb + ((size_t)n_idx * p.k_blocks + kb) * (SF_STAGE / 2),
+                       SF_STAGE / 2, &full_bar[stage]);
+        }
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = KIND == kMxKindNvf4 ? make_idesc_mx(MX_BM, BN, 1, 1, 0)
-                                                     : make_idesc_mx(MX_BM, BN, KIND == kMxKindE2M1A8 ? 5 : 0, 0, 1);
+      constexpr uint32_t idesc = KIND == kMxKindNvf4    ? make_idesc_mx(MX_BM, BN, 1, 1, 0)
+                                 : KIND == kMxKindRowF8 ? make_idesc(MX_BM, BN, 0, 0)
+                                 : KIND == kMxKindRowI8 ? make_idesc_i8(MX_BM, BN)
+                                                        : make_idesc_mx(MX_BM, BN, KIND == kMxKindE2M1A8 ? 5 : 0, 0, 1);
       constexpr int SFC = 4 * S::kAtoms;                      // columns of one operand's scales per buffer
       const uint32_t tmem_sf = tmem_base + S::kAccCols;       // two buffers: A scales, then B scales
       int stage = 0;
@@ -211,7 +236,11 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < 4; ++k) {                         // four MMAs of 32 bytes of K each
           const uint32_t acc = (kb > kb0 || k > 0) ? 1u : 0u;
-          if constexpr (KIND == kMxKindNvf4)                  // K = 64: a whole atom (four scales per row) per MMA
+          if constexpr (KIND == kMxKindRowF8)
+            tc_mma_f8f6f4(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);
+          else if constexpr (KIND == kMxKindRowI8)
+            tc_mma_i8(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);
+          else if constexpr (KIND == kMxKindNvf4)             // K = 64: a whole atom (four scales per row) per MMA
             tc_mma_nvf4(tmem_base, da + 2 * k, db + 2 * k, idesc, sf_cols + 4 * k, sf_cols + SFC + 4 * k, acc);
           else                                                // K = 32: byte k of the atom's columns
             tc_mma_mx(tmem_base, da + 2 * k, db + 2 * k, idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4), sf_cols,
@@ -230,6 +259,11 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const int m = m_idx * MX_BM + q * 32 + lane;
       const int n_base = n_idx * BN;
       const float bias_m = (p.bias && m < p.M) ? __bfloat162float(p.bias[m]) : 0.f;
+      const float fs = (p.feat_scale && m < p.M) ? p.feat_scale[m] : 1.f;
+      auto acc_f = [](uint32_t v) -> float {                   // the accumulator as a float (int32 for the int8 kind)
+        if constexpr (KIND == kMxKindRowI8) return (float)(int)v;
+        else return __uint_as_float(v);
+      };
       const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
       __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(sA) + e * (32 * 32);
       constexpr int CH = BN < 32 ? 16 : 32;
@@ -243,13 +277,13 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           float* wsp = p.ws + (size_t)blockIdx.z * p.N * p.M;
 #pragma unroll
           for (int c = 0; c < CH; ++c)
-            if (n_base + c0 + c < p.N && m < p.M) wsp[(size_t)(n_base + c0 + c) * p.M + m] = __uint_as_float(r[c]);
+            if (n_base + c0 + c < p.N && m < p.M) wsp[(size_t)(n_base + c0 + c) * p.M + m] = acc_f(r[c]) * fs;
           continue;
         }
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
           const float ts = p.tok_scale ? p.tok_scale[min(n_base + c0 + c, p.N - 1)] : 1.f;
-          stg[c * 32 + lane] = __float2bfloat16(__uint_as_float(r[c]) * (p.alpha * ts) + bias_m);
+          stg[c * 32 + lane] = __float2bfloat16(acc_f(r[c]) * (p.alpha * ts * fs) + bias_m);
         }
         __syncwarp();
         const int f0 = 8 * (lane & 3);
@@ -401,6 +435,66 @@ quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* 
   }
 }
 
+// x bf16 [T][K] -> 8-bit codes [T][K] with one scale per token (largest magnitude / 127 for int8, / 448 for e4m3).
+// One CTA per token.
+template <bool I8>
+__global__ void __launch_bounds__(256)
+quant_rows_8bit_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ xq, float* __restrict__ tok_scale,
+                       int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[8];
+  const int t = blockIdx.x;
+  const __nv_bfloat16* row = x + (size_t)t * ldx;
+  float amax = 0.f;
+  for (int i = threadIdx.x * 8; i < K; i += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack_bf16x2(w[e]);
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+  const float qmax = I8 ? 127.f : 448.f;
+  const float scale = amax > 0.f ? amax / qmax : 1.f;
+  const float inv = 1.f / scale;
+  if (threadIdx.x == 0) tok_scale[t] = scale;
+  for (int i = threadIdx.x * 8; i < K; i += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[2] = {0u, 0u};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack_bf16x2(w[e]);
+      uint32_t two;
+      if constexpr (I8) {
+        const int a = max(-127, min(127, __float2int_rn(f.x * inv))), b = max(-127, min(127, __float2int_rn(f.y * inv)));
+        two = (uint32_t)(a & 0xFF) | ((uint32_t)(b & 0xFF) << 8);
+      } else {
+        two = __nv_cvt_float2_to_fp8x2(make_float2(f.x * inv, f.y * inv), __NV_SATFINITE, __NV_E4M3);
+      }
+      o[e >> 1] |= two << (16 * (e & 1));
+    }
+    *reinterpret_cast<uint2*>(xq + (size_t)t * K + i) = make_uint2(o[0], o[1]);
+  }
+}
+
+void quant_rows_8bit(const void* x, long long ldx, void* xq, float* tok_scale, int T, int K, int is_int8, cudaStream_t s) {
+  if (T <= 0) return;
+  if (K % 8 || (ldx & 7)) throw std::runtime_error("quant_rows_8bit: K and the row pitch must be multiples of 8");
+  if (is_int8)
+    launch_pdl(quant_rows_8bit_kernel<true>, dim3((unsigned)T), dim3(256), 0, s, (const __nv_bfloat16*)x, ldx, (uint8_t*)xq, tok_scale, K);
+  else
+    launch_pdl(quant_rows_8bit_kernel<false>, dim3((unsigned)T), dim3(256), 0, s, (const __nv_bfloat16*)x, ldx, (uint8_t*)xq, tok_scale, K);
+}
+
 int mx_token_tile(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128; }
 
 // Bytes of the activation scale atoms for T tokens: one e8m0 per 32 values (kind 0 / 1) or one e4m3 per 16 (kind 2).
@@ -451,15 +545,19 @@ static void launch_mx_bn(int bn, const CUtensorMap& ta, const CUtensorMap& tb, c
 
 // y[T][N] = alpha * tok_scale[t] * dequant(xq, sfb) * dequant(wq, sfa)^T (+ bias).
 // kind 0: e4m3 weights [N][K] x e4m3 activations [T][K]; kind 1: e2m1 weights [N][K/2] x e4m3 activations;
-// kind 2: e2m1 weights [N][K/2] x e2m1 activations [T][K/2] with e4m3 scales per 16 (NVFP4).
+// kind 2: e2m1 weights [N][K/2] x e2m1 activations [T][K/2] with e4m3 scales per 16 (NVFP4);
+// kind 3 / 4: e4m3 / int8 weights [N][K] x activations [T][K] with feat_scale[N] and tok_scale[T] (no scale atoms).
 int linear_mx(const void* xq, const void* sfb, const void* wq, const void* sfa, int kind, float alpha,
-              const float* tok_scale, const void* bias, void* y, long long ldy, int T, int N, int K, void* workspace,
-              size_t workspace_bytes, int* status, cudaStream_t stream) {
+              const float* tok_scale, const float* feat_scale, const void* bias, void* y, long long ldy, int T, int N, int K,
+              void* workspace, size_t workspace_bytes, int* status, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
-  if (kind < 0 || kind > 2) throw std::runtime_error("linear_mx: kind must be 0, 1 or 2");
+  if (kind < 0 || kind > 4) throw std::runtime_error("linear_mx: kind must be 0 ... 4");
+  if (mx_kind_has_sf(kind) ? (!sfa || !sfb) : (!feat_scale || !tok_scale))
+    throw std::runtime_error("linear_mx: block-scaled kinds need scale atoms, row-scaled kinds need feature and token scales");
   const int stage_k = kind == kMxKindNvf4 ? 256 : 128;
   if (K % stage_k || N % 8 || (ldy & 7)) throw std::runtime_error("linear_mx: K % 128 (256 for NVFP4), N % 8 and 16-byte output rows required");
-  if ((reinterpret_cast<uintptr_t>(wq) & 31) || (reinterpret_cast<uintptr_t>(sfa) & 15) || (reinterpret_cast<uintptr_t>(sfb) & 15))
+  if ((reinterpret_cast<uintptr_t>(wq) & 31) || (reinterpret_cast<uintptr_t>(xq) & 15) || (reinterpret_cast<uintptr_t>(sfa) & 15) ||
+      (reinterpret_cast<uintptr_t>(sfb) & 15))
     throw std::runtime_error("linear_mx: operands must be 32-byte (weights) and 16-byte (scales) aligned");
   MxArgs a{};
   a.M = N; a.N = T; a.K = K;
@@ -468,7 +566,7 @@ int linear_mx(const void* xq, const void* sfb, const void* wq, const void* sfa, 
   a.n_tiles = (T + bn - 1) / bn;
   a.ldc = ldy; a.out = reinterpret_cast<__nv_bfloat16*>(y);
   a.sfa = reinterpret_cast<const uint8_t*>(sfa); a.sfb = reinterpret_cast<const uint8_t*>(sfb);
-  a.alpha = alpha; a.tok_scale = tok_scale; a.bias = reinterpret_cast<const __nv_bfloat16*>(bias); a.status = status;
+  a.alpha = alpha; a.tok_scale = tok_scale; a.feat_scale = feat_scale; a.bias = reinterpret_cast<const __nv_bfloat16*>(bias); a.status = status;
   // Few tiles cannot pull the whole HBM bandwidth: split K over grid.z until the machine is full.
   const int slots = sm_count() * (bn <= 64 ? 2 : 1);
   const int tiles = a.m_tiles * a.n_tiles;
@@ -486,7 +584,9 @@ int linear_mx(const void* xq, const void* sfb, const void* wq, const void* sfa, 
   else tb = make_tmap_2d(xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, T, K, K, bn, 128, true);
   if (kind == kMxKindE4M3) launch_mx_bn<kMxKindE4M3>(bn, ta, tb, a, stream);
   else if (kind == kMxKindE2M1A8) launch_mx_bn<kMxKindE2M1A8>(bn, ta, tb, a, stream);
-  else launch_mx_bn<kMxKindNvf4>(bn, ta, tb, a, stream);
+  else if (kind == kMxKindNvf4) launch_mx_bn<kMxKindNvf4>(bn, ta, tb, a, stream);
+  else if (kind == kMxKindRowF8) launch_mx_bn<kMxKindRowF8>(bn, ta, tb, a, stream);
+  else launch_mx_bn<kMxKindRowI8>(bn, ta, tb, a, stream);
   if (a.k_splits > 1) {
     const size_t n = (size_t)T * N;
     launch_pdl(mx_splitk_reduce_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, stream,

@@ -179,6 +179,16 @@ def pack_layer(lw: LayerWeights, fmt: str) -> None:
             if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 64 == 0 and w.shape[0] % 8 == 0:
                 setattr(lw, name, Fp4Weight.from_dense(w, fmt))
         return
+    if fmt in ("int8_w8a8", "fp8_w8a8"):
+        # per-channel 8-bit weights, activations quantised per token on the fly (tcgen05 kind::i8 / kind::f8f6f4)
+        from ..ops.mx import W8A8Weight
+        if lw.exp_gate_up is not None:
+            return
+        for name in ("wqkv", "wo", "w_gate_up", "w_down"):
+            w = getattr(lw, name, None)
+            if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 128 == 0 and w.shape[0] % 8 == 0:
+                setattr(lw, name, W8A8Weight.from_dense(w, "int8" if fmt == "int8_w8a8" else "fp8"))
+        return
     if fmt in ("mxfp8", "mxfp4_a8", "nvfp4_a4"):
         # block-scaled tensor-core formats: MXFP8 or MXFP4 weights with activations quantised to MXFP8 on the fly,
         # or NVFP4 weights with activations quantised to NVFP4 per token
@@ -194,7 +204,7 @@ def pack_layer(lw: LayerWeights, fmt: str) -> None:
                     setattr(lw, name, MxWeight.from_dense(w, "mxfp8" if fmt == "mxfp8" else "mxfp4"))
         return
     raise ValueError(f"random initialisation in weight format {fmt!r} is not available "
-                     "(bf16, fp8_block, nvfp4, mxfp4, mxfp8, mxfp4_a8, nvfp4_a4)")
+                     "(bf16, fp8_block, nvfp4, mxfp4, mxfp8, mxfp4_a8, nvfp4_a4, int8_w8a8, fp8_w8a8)")
 
 
 def init_random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: int = 0,

@@ -131,6 +131,65 @@ class Nvfp4TcWeight:
         return y
 
 
+def quantize_rows_8bit(x: torch.Tensor, is_int8: bool):
+    """Per-row symmetric 8-bit quantisation (what the device quantiser does to activations and what a per-channel
+    W8A8 checkpoint holds for weights): (codes uint8 [R, K], fp32 scales [R]); value = code * scale."""
+    xf = x.float()
+    amax = xf.abs().amax(-1)
+    qmax = 127.0 if is_int8 else 448.0
+    scale = torch.where(amax > 0, amax / qmax, torch.ones_like(amax))
+    v = xf * (1.0 / scale).unsqueeze(-1)
+    if is_int8:
+        q = torch.round(v).clamp(-127, 127).to(torch.int8).view(torch.uint8)
+    else:
+        q = v.clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+    return q.contiguous(), scale.contiguous()
+
+
+def dequantize_rows_8bit(q: torch.Tensor, scale: torch.Tensor, is_int8: bool) -> torch.Tensor:
+    v = q.view(torch.int8).float() if is_int8 else q.view(torch.float8_e4m3fn).float()
+    return v * scale.view(-1, 1).float()
+
+
+class W8A8Weight:
+    """Per-channel 8-bit weights (int8 or e4m3 codes [N, K] + one fp32 scale per output feature) multiplied by
+    activations quantised per token on the fly, on ``tcgen05.mma kind::i8`` (int32 accumulators) or ``kind::f8f6f4``:
+    the W8A8 form of SmoothQuant / compressed-tensors INT8 and per-channel FP8 checkpoints
+    (rust/engine/cuda/int8_gemm.cu, rust/engine/cuda/fp8_gemm.cu:44-78 in the reference). K % 128 == 0."""
+
+    def __init__(self, q: torch.Tensor, scale: torch.Tensor, is_int8: bool):
+        self.q, self.scale, self.is_int8 = q.contiguous(), scale.float().contiguous(), bool(is_int8)
+        self.shape = tuple(q.shape)
+        self.device = q.device
+
+    @classmethod
+    def from_dense(cls, w: torch.Tensor, fmt: str = "int8") -> "W8A8Weight":
+        q, s = quantize_rows_8bit(w, fmt == "int8")
+        return cls(q, s, fmt == "int8")
+
+    def to(self, device) -> "W8A8Weight":
+        return W8A8Weight(self.q.to(device), self.scale.to(device), self.is_int8)
+
+    def dense(self) -> torch.Tensor:
+        return dequantize_rows_8bit(self.q, self.scale, self.is_int8)
+
+    def nbytes(self) -> int:
+        return self.q.numel() + self.scale.numel() * 4
+
+    def apply(self, ops, x, bias=None, out=None):
+        T, K = x.shape
+        N = self.shape[0]
+        if not x.is_cuda or not hasattr(ops, "k"):
+            y = dequantize_rows_8bit(*quantize_rows_8bit(x, self.is_int8), self.is_int8) @ self.dense().t()
+            return (y + bias.float() if bias is not None else y).to(x.dtype)
+        xq = torch.empty(T, K, dtype=torch.uint8, device=x.device)
+        ts = torch.empty(T, dtype=torch.float32, device=x.device)
+        ops.k.quant_rows_8bit(x if x.stride(1) == 1 else x.contiguous(), xq, ts, self.is_int8)
+        y = out if out is not None else torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+        ops.launches += 1 + ops.k.linear_w8a8(xq, ts, self.q, self.scale, self.is_int8, bias, y, ops.workspace, ops.status)
+        return y
+
+
 class MxWeight:
     """A [N, K] matrix in MXFP8 (``a4`` False: e4m3 bytes [N, K]) or MXFP4 (``a4`` True: codes [N, K/2])."""
 

@@ -122,18 +122,41 @@ def test_linear_nvfp4_block_scaled_matches_fp32_math(ops, T, N, K):
     assert (got - (full + (bias.float() if bias is not None else 0))).norm() / full.norm() < 0.25
 
 
-@pytest.mark.parametrize("fmt", ["mxfp8", "mxfp4_a8", "nvfp4_a4"])
+@pytest.mark.parametrize("fmt", ["int8", "fp8"])
+@pytest.mark.parametrize("T", [1, 16, 33, 64, 128, 300])
+@pytest.mark.parametrize("N,K", [(256, 512), (4096, 4096), (392, 1024), (1024, 12288)])
+def test_linear_w8a8_row_scaled(ops, fmt, T, N, K):
+    """int8 x int8 (kind::i8, int32 accumulators) and e4m3 x e4m3 with one scale per feature and per token against
+    fp32 math on the same codes; the int8 product is exact up to the final rounding."""
+    from fllm_b200.ops.mx import W8A8Weight, dequantize_rows_8bit, quantize_rows_8bit
+    g = torch.Generator().manual_seed(T * 13 + N)
+    w = torch.randn(N, K, generator=g) * 0.05 * (1.0 + torch.arange(N).float().unsqueeze(1) % 7)
+    x = (torch.randn(T, K, generator=g) * (1.0 + torch.arange(T).float().unsqueeze(1) % 5)).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g).to(torch.bfloat16) if T % 2 == 0 else None
+    q = W8A8Weight.from_dense(w, fmt)
+    xq_ref, ts_ref = quantize_rows_8bit(x, fmt == "int8")
+    want = dequantize_rows_8bit(xq_ref, ts_ref, fmt == "int8") @ q.dense().t()
+    if bias is not None:
+        want = want + bias.float()
+    got = q.to("cuda").apply(ops, x.cuda(), bias.cuda() if bias is not None else None).float().cpu()
+    assert ops.check_status() == 0
+    err = (got - want).abs().max().item() / (want.abs().max().item() + 1e-9)
+    assert err < 1e-2, err
+
+
+@pytest.mark.parametrize("fmt", ["mxfp8", "mxfp4_a8", "nvfp4_a4", "int8_w8a8", "fp8_w8a8"])
 def test_engine_runs_block_scaled_weight_formats(fmt):
     """qwen3-tiny with every projection in a block-scaled format: the GPU logits of a prompt against the PyTorch
     statement of the same arithmetic (same packed weights, same activation quantisation rule)."""
     from fllm_b200.config import EngineConfig, preset
     from fllm_b200.models.weights import init_random_weights
-    from fllm_b200.ops.mx import MxWeight, Nvfp4TcWeight
+    from fllm_b200.ops.mx import MxWeight, Nvfp4TcWeight, W8A8Weight
     from fllm_b200.runtime import LLMEngine, SamplingParams
     from fllm_b200.ops.reference import RefOps
     cfg = preset("qwen3-tiny")
     w = init_random_weights(cfg, "cuda:0", seed=2, weight_format=fmt)
-    assert isinstance(w.layers[0].wqkv, (MxWeight, Nvfp4TcWeight)) and isinstance(w.layers[0].w_down, (MxWeight, Nvfp4TcWeight))
+    kinds = (MxWeight, Nvfp4TcWeight, W8A8Weight)
+    assert isinstance(w.layers[0].wqkv, kinds) and isinstance(w.layers[0].w_down, kinds)
     ec = EngineConfig(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256, num_kv_blocks=64, use_cuda_graphs=False)
     g = torch.Generator().manual_seed(1)
     prompt = torch.randint(0, cfg.vocab_size, (40,), generator=g).tolist()
