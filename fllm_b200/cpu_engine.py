@@ -22,8 +22,10 @@ class _CpuConfig(ctypes.Structure):
                [("eps", ctypes.c_float), ("rope_theta", ctypes.c_float)]
 
 
-def write_tiny_llama_gguf(path: str, cfg: Optional[ModelConfig] = None, seed: int = 0, qtype: int = quant.Q4_K) -> ModelConfig:
-    """N(0, 0.02) weights from `seed`, quantised to `qtype`; norm weights f32 = 1."""
+def write_tiny_llama_gguf(path: str, cfg: Optional[ModelConfig] = None, seed: int = 0, qtype: int = quant.Q4_K,
+                          qtype_for=None) -> ModelConfig:
+    """N(0, 0.02) weights from `seed`, quantised to `qtype`; norm weights f32 = 1. `qtype_for(name)` may name another
+    type for single tensors (a Q4_K_M file keeps attn_v and ffn_down in Q6_K)."""
     cfg = cfg or preset("tiny-llama")
     rng = np.random.default_rng(seed)
     w = GgufWriter(path)
@@ -45,7 +47,8 @@ def write_tiny_llama_gguf(path: str, cfg: Optional[ModelConfig] = None, seed: in
         # rows that the block size does not divide fall back: Q8_0 for multiples of 32, else f16
         # (the 688-wide FFN input of the tiny model is neither a multiple of 256 nor of 32)
         if cols % 256 == 0:
-            qt, tn = qtype, tname
+            qt = qtype_for(name) if qtype_for is not None and qtype_for(name) is not None else qtype
+            tn = {quant.Q4_K: "Q4_K", quant.Q6_K: "Q6_K", quant.Q8_0: "Q8_0", quant.Q5_K: "Q5_K"}[qt]
         elif cols % 32 == 0:
             qt, tn = quant.Q8_0, "Q8_0"
         else:

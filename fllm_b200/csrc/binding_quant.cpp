@@ -163,6 +163,35 @@ int64_t gemv_w4(const Tensor& x, const Tensor& codes, const Tensor& scales, int6
                        y.stride(0), (int)T, (int)N, (int)K, cur_stream());
 }
 
+// planes of ops/intk.py: codes (low nibbles [N, K/2] or int8 [N, K]), high-bit words, sub-scales, fp16 super-scales
+int64_t gemv_wk(const Tensor& x, const Tensor& codes, const Tensor& high, const Tensor& sub, const Tensor& sup, int64_t fmt,
+                const optional<Tensor>& bias, Tensor y) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "x: bf16 rows");
+  const int64_t T = x.size(0), K = x.size(1), N = codes.size(0);
+  TORCH_CHECK(fllm::gemv_wk_supported((int)T, (int)K, (int)fmt), "gemv_wk: at most 4 tokens, fmt 5 / 6 / 8, K % 256 == 0 (32 for Q8_0)");
+  TORCH_CHECK(codes.is_contiguous() && codes.element_size() == 1 && codes.dim() == 2 && codes.size(1) == (fmt == 8 ? K : K / 2), "codes: planar bytes");
+  TORCH_CHECK(sup.is_contiguous() && sup.scalar_type() == at::kHalf && sup.numel() == N * (fmt == 8 ? K / 32 : (fmt == 5 ? K / 128 : K / 256)), "sup: fp16 super-scales");
+  if (fmt != 8) {
+    TORCH_CHECK(high.is_contiguous() && high.element_size() == 4 && high.numel() == N * (K / 32) * (fmt == 6 ? 2 : 1), "high: bit planes");
+    TORCH_CHECK(sub.is_contiguous() && sub.element_size() == 1 && sub.numel() == N * (K / 16), "sub: one byte per 16 values");
+  }
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.stride(1) == 1 && y.size(0) == T && y.size(1) == N, "y: [T, N] bf16");
+  c10::cuda::CUDAGuard guard(x.device());
+  const void* b = bias.has_value() && bias->defined() ? bias->data_ptr() : nullptr;
+  return fllm::gemv_wk(x.data_ptr(), x.stride(0), codes.data_ptr(), high.data_ptr(), sub.data_ptr(), sup.data_ptr(), (int)fmt, b,
+                       y.data_ptr(), y.stride(0), (int)T, (int)N, (int)K, cur_stream());
+}
+
+void wk_dequant(const Tensor& codes, const Tensor& high, const Tensor& sub, const Tensor& sup, int64_t fmt, Tensor out) {
+  TORCH_CHECK(codes.is_cuda() && codes.is_contiguous() && codes.dim() == 2 && out.is_contiguous() && out.scalar_type() == at::kBFloat16 &&
+              out.dim() == 2 && out.size(0) == codes.size(0), "codes planar bytes, out bf16 [N, K]");
+  TORCH_CHECK(codes.size(1) == (fmt == 8 ? out.size(1) : out.size(1) / 2) && sup.scalar_type() == at::kHalf &&
+              high.is_contiguous() && sub.is_contiguous() && sup.is_contiguous(), "plane shapes");
+  c10::cuda::CUDAGuard guard(codes.device());
+  fllm::wk_dequant_bf16(codes.data_ptr(), high.data_ptr(), sub.data_ptr(), sup.data_ptr(), (int)fmt, out.data_ptr(), out.size(0),
+                        (int)out.size(1), cur_stream());
+}
+
 void w4_dequant(const Tensor& codes, const Tensor& scales, int64_t fmt, double alpha, Tensor out) {
   TORCH_CHECK(codes.is_cuda() && codes.is_contiguous() && codes.dim() == 2 && out.is_contiguous() && out.scalar_type() == at::kBFloat16, "codes [N, K/2], out bf16 [N, K]");
   TORCH_CHECK(out.numel() == codes.numel() * 2 && (codes.size(1) * 2) % 32 == 0, "out: [N, K], K % 32 == 0");
@@ -183,5 +212,7 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("mx_act_scale_bytes(int T, int K, int kind) -> int", &mx_act_scale_bytes);
   m.def("linear_mx(Tensor xq, Tensor sfb, Tensor wq, Tensor sfa, int kind, float alpha, Tensor? tok_scale, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status) -> int", &linear_mx);
   m.def("gemv_w4(Tensor x, Tensor codes, Tensor scales, int fmt, float alpha, Tensor? bias, Tensor(a!) y) -> int", &gemv_w4);
+  m.def("gemv_wk(Tensor x, Tensor codes, Tensor high, Tensor sub, Tensor sup, int fmt, Tensor? bias, Tensor(a!) y) -> int", &gemv_wk);
+  m.def("wk_dequant(Tensor codes, Tensor high, Tensor sub, Tensor sup, int fmt, Tensor(a!) out) -> ()", &wk_dequant);
   m.def("w4_dequant(Tensor codes, Tensor scales, int fmt, float alpha, Tensor(a!) out) -> ()", &w4_dequant);
 }

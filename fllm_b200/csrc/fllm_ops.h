@@ -108,6 +108,13 @@ bool gemv_w4_supported(int T, int K);
 int gemv_w4(const void* x, long long ldx, const void* codes, const void* scales, int fmt, float alpha, const void* bias,
             void* y, long long ldy, int T, int N, int K, cudaStream_t stream);
 
+// GGUF Q5_K (fmt 5) / Q6_K (6) / Q8_0 (8) in planar device form: dp4a product for at most 4 tokens, bf16 expansion.
+bool gemv_wk_supported(int T, int K, int fmt);
+int gemv_wk(const void* x, long long ldx, const void* codes, const void* high, const void* sub, const void* sup, int fmt,
+            const void* bias, void* y, long long ldy, int T, int N, int K, cudaStream_t stream);
+void wk_dequant_bf16(const void* codes, const void* high, const void* sub, const void* sup, int fmt, void* out,
+                     long long rows, int K, cudaStream_t s);
+
 // Block-scaled GEMMs (tcgen05 kind::mxf8f6f4 / kind::mxf4nvf4 .block_scale). kind 0: e4m3 weights, kind 1: packed
 // e2m1 weights, both with e4m3 activations and one e8m0 scale per 32 values; kind 2: NVFP4 on both sides (packed
 // e2m1, one e4m3 scale per 16, tensor scale x per-token scale). Scale factors travel in 512-byte atoms (128 rows x

@@ -246,10 +246,12 @@ def _load_per_expert_moe(cfg, sp, tp_rank, lw, p, get, dev) -> None:
 
 
 def load_gguf(path: str, device="cuda", tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16, keep_packed: bool = True):
-    """GGUF -> weights. On a GPU, projections whose tensors are all 4-bit group types (Q4_K, Q4_0,
-    Q4_1) stay packed as ``Int4Weight`` when `keep_packed`; every other type is expanded to bf16."""
+    """GGUF -> weights. On a GPU (`keep_packed`), 4-bit group types (Q4_K, Q4_0, Q4_1) stay packed as
+    ``Int4Weight``, Q5_K / Q6_K / Q8_0 as ``IntKWeight`` planes, fused projections of mixed types as a
+    ``StackedWeight``; every other type is expanded to bf16."""
     from ..cpu_engine import config_from_gguf
     from ..ops.int4 import Int4Weight
+    from ..ops.intk import IntKWeight, StackedWeight
     from .gguf import GgufReader
     r = GgufReader(path)
     cfg = config_from_gguf(r)
@@ -262,25 +264,33 @@ def load_gguf(path: str, device="cuda", tp: int = 1, tp_rank: int = 0, dtype=tor
     isl = slice(sp.inter_start, sp.inter_start + sp.inter_local)
     packed_ok = keep_packed and torch.device(device).type == "cuda"
 
-    def int4(name):
+    def packed(name):
+        """The tensor in its packed device form (4-bit group types, Q5_K / Q6_K / Q8_0 planes), or None."""
         info = r.tensors[name]
-        if not packed_ok or info.type_name not in ("Q4_K", "Q4_0", "Q4_1"):
+        if not packed_ok or len(info.shape) < 2:
             return None
-        rows, cols = int(info.shape[-2] if len(info.shape) > 1 else 1), int(info.shape[-1])
-        if cols % 64:
-            return None
-        return Int4Weight.from_gguf(info.type_name, r.tensor_bytes(name), rows, cols)
+        rows, cols = int(info.shape[-2]), int(info.shape[-1])
+        if info.type_name in ("Q4_K", "Q4_0", "Q4_1") and cols % 64 == 0:
+            return Int4Weight.from_gguf(info.type_name, r.tensor_bytes(name), rows, cols)
+        if IntKWeight.supports(info.type_name, cols):
+            return IntKWeight.from_gguf(info.type_name, r.tensor_bytes(name), rows, cols)
+        return None
 
     def fused_rows(names, cuts):
-        """Row-concatenation of row-cut tensors: packed when every part has an INT4 form."""
-        parts = [int4(n) for n in names]
-        if all(p is not None for p in parts):
+        """Row-concatenation of row-cut tensors: one INT4 weight when every part has that form, a stack of
+        differently typed parts when some are packed (a Q4_K_M file mixes Q4_K and Q6_K inside q|k|v), else bf16."""
+        parts = [packed(n) for n in names]
+        if all(isinstance(p, Int4Weight) for p in parts):
             return Int4Weight.cat([p.rows(c) for p, c in zip(parts, cuts)]).to(device)
+        if any(p is not None for p in parts):
+            return StackedWeight([p.rows(c).to(device) if p is not None else dev(t(n)[c])
+                                  for p, n, c in zip(parts, names, cuts)])
         return dev(torch.cat([t(n)[c] for n, c in zip(names, cuts)], 0))
 
     def col_cut(name, cut):
-        p = int4(name)
-        if p is not None and cut.start % 64 == 0 and cut.stop % 64 == 0:
+        p = packed(name)
+        unit = 64 if isinstance(p, Int4Weight) else (32 if getattr(p, "fmt", 0) == 8 else 256)
+        if p is not None and cut.start % unit == 0 and cut.stop % unit == 0:
             return p.cols(cut).to(device)
         return dev(t(name)[:, cut])
 

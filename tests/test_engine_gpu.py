@@ -295,3 +295,39 @@ def test_speculation_on_the_gpu_greedy_and_sampled():
                                      speculative="ngram"), device="cuda:0", seed=3, weights=base.weights)
     rep = [prompts[0][:6] * 4]
     assert all(len(o) == 10 for o in ng.generate(rep, SamplingParams(max_tokens=10, temperature=0.7, seed=1)))
+
+
+def test_gguf_mixed_k_quants_stay_packed_on_the_gpu(tmp_path):
+    """A Q4_K_M-style file (attn_v and ffn_down in Q6_K, token embeddings in Q8_0-eligible shapes) keeps every
+    projection packed: q|k|v becomes a stack of differently typed parts. Same logits as the bf16 expansion, for a
+    prompt (GEMM path) and for single-token decode steps (dp4a path)."""
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.cpu_engine import write_tiny_llama_gguf
+    from fllm_b200.formats import quant
+    from fllm_b200.formats.loader import load_gguf
+    from fllm_b200.ops.int4 import Int4Weight
+    from fllm_b200.ops.intk import IntKWeight, StackedWeight
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    cfg0 = preset("tiny-llama")
+    cfg0.intermediate_size = 1024
+    path = str(tmp_path / "mixed.gguf")
+    write_tiny_llama_gguf(path, cfg0, seed=5,
+                          qtype_for=lambda n: quant.Q6_K if ("attn_v" in n or "ffn_down" in n) else (quant.Q5_K if "attn_output" in n else None))
+    outs, toks = [], []
+    for packed in (True, False):
+        cfg, w, _ = load_gguf(path, "cuda:0", keep_packed=packed)
+        if packed:
+            lw = w.layers[0]
+            assert isinstance(lw.wqkv, StackedWeight) and isinstance(lw.wqkv.parts[2], IntKWeight) and isinstance(lw.wqkv.parts[0], Int4Weight)
+            assert isinstance(lw.w_down, IntKWeight) and lw.w_down.fmt == 6 and isinstance(lw.wo, IntKWeight) and lw.wo.fmt == 5
+            assert isinstance(lw.w_gate_up, Int4Weight)
+        ec = EngineConfig(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256, num_kv_blocks=64, use_cuda_graphs=False)
+        eng = LLMEngine(cfg, ec, device="cuda:0", weights=w)
+        p = _prompts(cfg.vocab_size, (70,))[0]
+        lg = eng.token_logits(p)
+        outs.append(lg[-1].float().cpu())
+        toks.append(eng.generate([p], SamplingParams(max_tokens=6))[0])
+        assert eng.ops.check_status() == 0
+    err = (outs[0] - outs[1]).abs().max().item()
+    assert err < 0.05 * outs[1].abs().max().item() + 1e-3, err
+    assert len(toks[0]) == 6

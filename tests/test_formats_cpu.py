@@ -545,3 +545,32 @@ def test_gemma2_post_norms_scale_and_window_pattern(tmp_path):
     assert torch.equal(w2.layers[1].post_ffn_norm, w.layers[1].post_ffn_norm)
     eng2 = LLMEngine(cfg2, ec, device="cpu", weights=w2)
     assert eng2.generate([prompt], SamplingParams(max_tokens=5))[0] == eng.generate([prompt], SamplingParams(max_tokens=5))[0]
+
+
+def test_planar_device_forms_of_q5k_q6k_q80_equal_the_codecs():
+    """The re-laid planes of the 5 / 6 / 8-bit GGUF types decode to exactly what the file blocks decode to, keep
+    the file's bits per weight, survive row and column cuts, and stack with other weight kinds."""
+    import numpy as np
+    import torch
+    from fllm_b200.formats import quant as Q
+    from fllm_b200.ops.int4 import Int4Weight
+    from fllm_b200.ops.intk import IntKWeight, StackedWeight
+    from fllm_b200.ops.reference import RefOps
+    rng = np.random.default_rng(0)
+    for name, tid, bpw in (("Q8_0", Q.Q8_0, 8.5), ("Q6_K", Q.Q6_K, 6.5625), ("Q5_K", Q.Q5_K, 5.625)):
+        w = (rng.standard_normal((48, 512)) * 0.05).astype(np.float32)
+        raw = Q.quantize(w, tid)
+        want = Q.dequantize(raw, tid, 48, 512)
+        k = IntKWeight.from_gguf(name, raw, 48, 512)
+        assert np.array_equal(k.dense().numpy(), want)
+        assert abs(k.nbytes() * 8 / (48 * 512) - bpw) < 0.01
+        cut = k.rows(slice(8, 24)).cols(slice(256, 512))
+        assert np.array_equal(cut.dense().numpy(), want[8:24, 256:512])
+    K = 512
+    ws = [(rng.standard_normal((n, K)) * 0.05).astype(np.float32) for n in (64, 32, 32)]
+    st = StackedWeight([Int4Weight.from_gguf("Q4_K", Q.quantize(ws[0], Q.Q4_K), 64, K),
+                        IntKWeight.from_gguf("Q6_K", Q.quantize(ws[1], Q.Q6_K), 32, K), torch.from_numpy(ws[2]).bfloat16()])
+    x = torch.randn(3, K).bfloat16()
+    y = RefOps().linear(x, st)
+    ref = x.float() @ st.dense().t()
+    assert st.shape == (128, K) and float((y.float() - ref).abs().max() / ref.abs().max()) < 1e-2

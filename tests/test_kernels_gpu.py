@@ -793,3 +793,34 @@ def test_large_batch_linear_glu_goes_through_the_pair_kernel(ops, ref, kind, lay
     yr = ref.linear_glu(x, w, bias, kind, 1.702, 7.0, layout)
     _close(y, yr, 2e-2)
     assert ops.check_status() == 0
+
+
+@pytest.mark.parametrize("qname", ["Q5_K", "Q6_K", "Q8_0"])
+@pytest.mark.parametrize("T", [1, 2, 4, 9])
+@pytest.mark.parametrize("N,K", [(256, 256), (1000, 512), (4096, 4096), (520, 12288)])
+def test_packed_5_6_8_bit_weights(ops, qname, T, N, K):
+    """Q5_K / Q6_K / Q8_0 in their planar device form: the dp4a product (up to 4 tokens) against fp32 math on the
+    int8-quantised activations, the bf16 expansion bit for bit against the codec, longer steps through the GEMM."""
+    import numpy as np
+    from fllm_b200.formats import quant as Q
+    from fllm_b200.ops.intk import IntKWeight
+    rng = np.random.default_rng(N + K + T)
+    w = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    tid = {"Q5_K": Q.Q5_K, "Q6_K": Q.Q6_K, "Q8_0": Q.Q8_0}[qname]
+    raw = Q.quantize(w, tid)
+    dense = torch.from_numpy(Q.dequantize(raw, tid, N, K)).cuda()
+    q = IntKWeight.from_gguf(qname, raw, N, K, device="cuda")
+    assert abs(q.nbytes() * 8 / (N * K) - {"Q5_K": 5.625, "Q6_K": 6.5625, "Q8_0": 8.5}[qname]) < 0.01
+    out = torch.empty(N, K, dtype=torch.bfloat16, device="cuda")
+    ops.k.wk_dequant(q.codes, q.high, q.sub, q.sup, q.fmt, out)
+    assert torch.equal(out.float(), dense.to(torch.bfloat16).float())
+    x = _rand((T, K), 41 + T)
+    bias = _rand((N,), 42) if T % 2 == 0 else None
+    y = ops.linear(x, q, bias)
+    if T <= 4:
+        xb = x.float().view(T, K // 32, 32)
+        d = xb.abs().amax(-1, keepdim=True) / 127.0
+        xq = torch.where(d > 0, torch.round(xb / d.clamp_min(1e-30)), torch.zeros_like(xb)) * d
+        _close(y, xq.view(T, K) @ dense.t() + (bias.float() if bias is not None else 0), 1e-2)
+    _close(y, x.float() @ dense.t() + (bias.float() if bias is not None else 0), 3e-2)
+    assert ops.check_status() == 0
