@@ -89,8 +89,37 @@ def build_engine(args):
     return eng, tokenizer
 
 
+def _encoder_dir(path: str) -> bool:
+    """A Hugging Face directory whose config names a BERT-family encoder."""
+    cfg = os.path.join(path, "config.json")
+    if not os.path.isfile(cfg):
+        return False
+    try:
+        return json.load(open(cfg)).get("model_type") in ("bert", "roberta", "xlm-roberta")
+    except (OSError, ValueError):
+        return False
+
+
+def cmd_serve_encoder(args, path: str) -> int:
+    """`serve` on an encoder checkpoint: embeddings / pooling / classify / score / rerank routes."""
+    import torch
+    from .models.encoder import Encoder, load_hf_encoder
+    from .ops import get_ops
+    from .server.encoder_app import serve_encoder
+    from .tokenizer import load_tokenizer
+    dev = args.device if getattr(args, "device", None) else ("cuda:0" if torch.cuda.is_available() else "cpu")
+    cfg, w = load_hf_encoder(path, dev, torch.bfloat16 if str(dev).startswith("cuda") else torch.float32)
+    enc = Encoder(cfg, w, get_ops("cuda" if str(dev).startswith("cuda") else "cpu"), dev)
+    tok = load_tokenizer(path if os.path.exists(os.path.join(path, "tokenizer.json")) else None, cfg.vocab_size)
+    serve_encoder(enc, tok, args.host, args.port, args.model_name or os.path.basename(path.rstrip("/")), args.api_key, args.log_level,
+                  ssl_certfile=args.ssl_certfile, ssl_keyfile=args.ssl_keyfile)
+    return 0
+
+
 def cmd_serve(args) -> int:
     from .server.app import serve
+    if args.model and os.path.isdir(args.model) and _encoder_dir(args.model):
+        return cmd_serve_encoder(args, args.model)
     eng, tok = build_engine(args)
     eng.warm_up(buckets=[b for b in eng.cfg.graph_buckets if b <= 64])
     controller = None

@@ -56,6 +56,7 @@ struct FaParams {
   int decode_max_q;      // sequences with more query rows than this belong to the prefill kernel
   long long num_kv_blocks;
   int* status;
+  int bidir;             // 1: no causal mask (encoders): prefill kernels only
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -505,7 +506,7 @@ __global__ void __launch_bounds__(2 * R) fa_prefill_kernel(const FaParams p) {
   const int n_rows = nq * G;
   const int kv_len = p.kv_lens[seq];
   const int first_pos = kv_len - qn + qi0;        // absolute position of the tile's first query
-  const int hi_tok = first_pos + nq;              // exclusive
+  const int hi_tok = p.bidir ? kv_len : first_pos + nq;              // exclusive
   int lo_tok = 0;
   if (p.window > 0) lo_tok = max(0, first_pos - p.window + 1);
   const int tile_lo = lo_tok / S::kTile;
@@ -529,7 +530,7 @@ __global__ void __launch_bounds__(2 * R) fa_prefill_kernel(const FaParams p) {
   const int g = lane >> 2;
   auto row_limits = [&](int r, int& lim, int& beg) {
     if (r < n_rows) {
-      lim = first_pos + r / G + 1;
+      lim = p.bidir ? kv_len : first_pos + r / G + 1;
       beg = p.window > 0 ? max(0, lim - p.window) : 0;
     } else {
       lim = 0;
@@ -631,7 +632,8 @@ static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int mi
                                     PrefillSmem<D, 64>::kTotal), "fa_prefill smem");
   }
   int launches = 0;
-  const int decode_max_q = 16 / p.group;            // packed rows must fit one 16-row MMA tile
+  // packed rows must fit one 16-row MMA tile; a bidirectional batch (encoder) goes to the prefill kernels whole
+  const int decode_max_q = p.bidir ? 0 : 16 / p.group;
   p.decode_max_q = decode_max_q;
   if (kv_fp8 && (decode_max_q < 1 || max_q_len > decode_max_q))
     throw std::runtime_error("attention_tc: an e4m3 cache is read by the decode kernel only (query rows x group <= 16)");
@@ -666,7 +668,7 @@ static int launch_tc(FaParams p, int tokens, int num_seqs, int max_q_len, int mi
       attention_prefill_tmem_supported(D, p.group, kPage)) {
     attention_prefill_tmem(p.q, p.ldq, p.k_cache, p.v_cache, p.num_kv_blocks, p.block_tables, p.max_blocks, p.q_starts,
                            p.kv_lens, p.out, p.ldo, num_seqs, max_q_len, decode_max_q + 1, p.hq, p.hkv, D, p.scale,
-                           p.window, p.sinks, p.softcap, p.status, s);
+                           p.window, p.sinks, p.softcap, p.status, s, 0, p.bidir);
     ++launches;
   } else if (max_q_len > decode_max_q) {
     // 64 packed rows per CTA. (128 rows, 8 warps sharing every K/V tile, measured equal - 119 vs 121 TFLOP/s at
@@ -687,7 +689,7 @@ int attention_tc_bf16(const void* q, long long ldq, const void* k_cache, const v
                       void* out, long long ldo, int tokens, int num_seqs, int max_q_len, int min_q_len,
                       int max_kv_len, int hq, int hkv, int head_dim, int block_size, float scale,
                       int window, const float* sinks, float softcap, void* workspace,
-                      size_t workspace_bytes, cudaStream_t s, long long num_kv_blocks, int* status, int kv_fp8) {
+                      size_t workspace_bytes, cudaStream_t s, long long num_kv_blocks, int* status, int kv_fp8, int bidir) {
   if (tokens <= 0 || num_seqs <= 0) return 0;
   if (block_size != kPage) throw std::runtime_error("attention_tc: KV block size must be 16");
   if (hq % hkv) throw std::runtime_error("attention_tc: hq must be a multiple of hkv");
@@ -698,7 +700,7 @@ int attention_tc_bf16(const void* q, long long ldq, const void* k_cache, const v
   p.q_starts = q_starts; p.kv_lens = kv_lens;
   p.out = (__nv_bfloat16*)out; p.ldo = ldo;
   p.sinks = sinks;
-  p.num_kv_blocks = num_kv_blocks; p.status = status;
+  p.num_kv_blocks = num_kv_blocks; p.status = status; p.bidir = bidir;
   p.hq = hq; p.hkv = hkv; p.group = hq / hkv;
   p.window = window;
   p.scale = scale;

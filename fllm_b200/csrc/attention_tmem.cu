@@ -56,6 +56,7 @@ struct FaTmemParams {
   float scale_log2, softcap, scale;
   int pv_wide;           // one N=128 MMA per 16 tokens instead of two N=64 ones
   int tile_variant;      // 0: pick by shape; 1 / 2: force one / two query tiles per CTA
+  int bidir;             // 1: no causal mask, every query row sees all kv_len tokens (encoders)
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -257,7 +258,7 @@ fa_prefill_tmem_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_c
   const int n_rows = nq * G;
   const int kv_len = p.kv_lens[seq];
   const int first_pos = kv_len - qn + qi0;
-  const int hi_tok = first_pos + nq;
+  const int hi_tok = p.bidir ? kv_len : first_pos + nq;
   const int lo_tok = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
   const int tile_lo = lo_tok / kTileT;
   const int tile_hi = (hi_tok + kTileT - 1) / kTileT;
@@ -362,7 +363,7 @@ fa_prefill_tmem_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_c
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     int lim = 0, beg = 0;
     if (r < n_rows) {
-      lim = first_pos + r / G + 1;
+      lim = p.bidir ? kv_len : first_pos + r / G + 1;
       beg = p.window > 0 ? max(0, lim - p.window) : 0;
     }
     float m_used = -INFINITY, l = 0.f;
@@ -372,7 +373,7 @@ fa_prefill_tmem_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_c
       if (!mbar_wait(s_full, it & 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       // whole tile visible to every row of the CTA: no per-element mask
-      const bool full = p.window == 0 && tok0 + kTileT <= first_pos + 1 && n_rows == kRowsT;
+      const bool full = p.window == 0 && tok0 + kTileT <= (p.bidir ? kv_len : first_pos + 1) && n_rows == kRowsT;
       softmax_tile<D>(p, t_s + lane_off, t_o + lane_off, tok0, lim, beg, full, it > 0, m_used, l);
       tc_fence_before_sync();
       __syncwarp();
@@ -433,7 +434,7 @@ fa_prefill_tmem2_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_
   const int n_rows = nq * G;
   const int kv_len = p.kv_lens[seq];
   const int first_pos = kv_len - qn + qi0;
-  const int hi_tok = first_pos + nq;
+  const int hi_tok = p.bidir ? kv_len : first_pos + nq;
   const int lo_tok = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
   const int tile_lo = lo_tok / kTileT;
   const int tile_hi = (hi_tok + kTileT - 1) / kTileT;
@@ -573,7 +574,7 @@ fa_prefill_tmem2_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_
     const uint32_t t_s = tmem_base + 128 * g + lane_off, t_o = tmem_base + 256 + 128 * g + lane_off;
     int lim = 0, beg = 0;
     if (r < n_rows) {
-      lim = first_pos + r / G + 1;
+      lim = p.bidir ? kv_len : first_pos + r / G + 1;
       beg = p.window > 0 ? max(0, lim - p.window) : 0;
     }
     const int group_first = first_pos + (g * kRowsT) / G;
@@ -584,7 +585,7 @@ fa_prefill_tmem2_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_
       const int tok0 = (tile_lo + it) * kTileT;
       if (!mbar_wait(&s_full[g], it & 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
-      const bool full = p.window == 0 && tok0 + kTileT <= group_first + 1 && group_whole;
+      const bool full = p.window == 0 && tok0 + kTileT <= (p.bidir ? kv_len : group_first + 1) && group_whole;
       softmax_tile<D>(p, t_s, t_o, tok0, lim, beg, full, it > 0, m_used, l);
       tc_fence_before_sync();
       __syncwarp();
@@ -652,7 +653,7 @@ void attention_prefill_tmem(const void* q, long long ldq, const void* k_cache, c
                             const int* block_tables, int max_blocks, const int* q_starts, const int* kv_lens,
                             void* out, long long ldo, int num_seqs, int max_q_len, int min_q, int hq, int hkv,
                             int head_dim, float scale, int window, const float* sinks, float softcap, int* status,
-                            cudaStream_t s, int tile_variant) {
+                            cudaStream_t s, int tile_variant, int bidir) {
   static std::unordered_map<MapKey, MapPair, MapKeyHash> maps;
   const uint64_t rows = (uint64_t)num_blocks * hkv * kPageT;
   const MapKey key{k_cache, v_cache, rows, head_dim};
@@ -675,6 +676,7 @@ void attention_prefill_tmem(const void* q, long long ldq, const void* k_cache, c
   p.scale = scale; p.scale_log2 = scale * kLog2eT; p.softcap = softcap;
   p.pv_wide = 1;
   p.tile_variant = tile_variant;
+  p.bidir = bidir;
   if (head_dim == 64) launch_tmem<64>(it->second, p, max_q_len, num_seqs, s);
   else launch_tmem<128>(it->second, p, max_q_len, num_seqs, s);
 }

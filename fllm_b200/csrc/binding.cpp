@@ -242,7 +242,7 @@ int64_t attention_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_cac
                      int64_t num_seqs, int64_t max_q_len, int64_t min_q_len, int64_t max_kv_len, int64_t hq,
                      int64_t hkv, int64_t head_dim, double scale, int64_t window,
                      const optional<Tensor>& sinks, double softcap, const optional<Tensor>& workspace,
-                     const optional<Tensor>& status) {
+                     const optional<Tensor>& status, bool bidirectional) {
   check_bf16(q, "q"); check_rows(q, "q"); check_bf16(out, "out"); check_rows(out, "out");
   const bool kv_fp8 = k_cache.element_size() == 1;            // e4m3 bytes: the decode kernel widens them to f16
   TORCH_CHECK(k_cache.is_cuda() && v_cache.is_cuda() && k_cache.is_contiguous() && v_cache.is_contiguous() &&
@@ -264,7 +264,7 @@ int64_t attention_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_cac
                                  (int)min_q_len, (int)max_kv_len, (int)hq, (int)hkv, (int)head_dim,
                                  (int)k_cache.size(2), (float)scale, (int)window, opt_ptr<float>(sinks),
                                  (float)softcap, ws, ws_bytes, cur_stream(), (long long)k_cache.size(0),
-                                 const_cast<int*>(opt_ptr<int>(status)), kv_fp8 ? 1 : 0);
+                                 const_cast<int*>(opt_ptr<int>(status)), kv_fp8 ? 1 : 0, bidirectional ? 1 : 0);
 }
 
 void argmax(const Tensor& logits, Tensor out_ids, const optional<Tensor>& out_vals,
@@ -399,7 +399,7 @@ TORCH_LIBRARY(fllm_b200, m) {
   m.def("glu(Tensor x, Tensor(a!) out, int act_kind, float alpha, float limit) -> ()", &glu);
   m.def("gather_rows(Tensor x, Tensor rows, Tensor(a!) out) -> ()", &gather_rows);
   m.def("attention_generic(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor row_seq, Tensor positions, Tensor(a!) out, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap) -> ()", &attention_generic);
-  m.def("attention_tc(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor q_starts, Tensor kv_lens, Tensor(a!) out, int num_seqs, int max_q_len, int min_q_len, int max_kv_len, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap, Tensor? workspace, Tensor? status=None) -> int", &attention_tc);
+  m.def("attention_tc(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor q_starts, Tensor kv_lens, Tensor(a!) out, int num_seqs, int max_q_len, int min_q_len, int max_kv_len, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap, Tensor? workspace, Tensor? status=None, bool bidirectional=False) -> int", &attention_tc);
   m.def("argmax(Tensor logits, Tensor(a!) out_ids, Tensor? out_vals, int id_offset) -> ()", &argmax);
   m.def("argmax_split(Tensor logits, Tensor(a!) out_ids, Tensor? out_vals, Tensor? out_pairs, int id_offset, Tensor(b!) scratch) -> ()", &argmax_split);
   m.def("argmax_pairs_select(Tensor pairs, Tensor(a!) out_ids) -> ()", &argmax_pairs_select);

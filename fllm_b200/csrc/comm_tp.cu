@@ -182,6 +182,19 @@ void tp_reduce_norm_allgather(const TpNormArgs& a, cudaStream_t s) {
   const int my_rows = a.bcast ? a.tokens : std::max(0, std::min(a.tokens, lo + a.rows_per) - lo);
   const int grid = std::max(my_rows, 1);              // a rank without rows still does the bookkeeping
   const int iters = (a.hidden / 8 + 255) / 256;
+  static int norm_pdl = -1;
+  if (norm_pdl < 0) { const char* e = getenv("FLLM_TP_NORM_PDL"); norm_pdl = e ? atoi(e) : 1; }
+  if (!norm_pdl) {
+    switch (iters) {
+      case 1: tp_reduce_norm_ag_kernel<1><<<grid, 256, 0, s>>>(a); break;
+      case 2: tp_reduce_norm_ag_kernel<2><<<grid, 256, 0, s>>>(a); break;
+      case 3: tp_reduce_norm_ag_kernel<3><<<grid, 256, 0, s>>>(a); break;
+      case 4: tp_reduce_norm_ag_kernel<4><<<grid, 256, 0, s>>>(a); break;
+      default: tp_reduce_norm_ag_kernel<8><<<grid, 256, 0, s>>>(a); break;
+    }
+    cuda_check(cudaGetLastError(), "tp_reduce_norm_ag_kernel");
+    return;
+  }
   switch (iters) {
     case 1: launch_pdl(tp_reduce_norm_ag_kernel<1>, dim3(grid), dim3(256), 0, s, a); break;
     case 2: launch_pdl(tp_reduce_norm_ag_kernel<2>, dim3(grid), dim3(256), 0, s, a); break;

@@ -217,14 +217,15 @@ int attention_tc_bf16(const void* q, long long ldq, const void* k_cache, const v
                       int max_kv_len, int hq, int hkv, int head_dim, int block_size, float scale,
                       int window, const float* sinks, float softcap, void* workspace,
                       size_t workspace_bytes, cudaStream_t s, long long num_kv_blocks = 0, int* status = nullptr,
-                      int kv_fp8 = 0);   // kv_fp8: the caches hold e4m3 bytes (decode-shaped batches only)
+                      int kv_fp8 = 0,    // the caches hold e4m3 bytes (decode-shaped batches only)
+                      int bidir = 0);    // no causal mask: every query row sees all kv_len tokens (encoder batches)
 // Prefill on tcgen05 with tensor-memory accumulators (head_dim 64 or 128, group size dividing 128).
 bool attention_prefill_tmem_supported(int head_dim, int group, int block_size);
 void attention_prefill_tmem(const void* q, long long ldq, const void* k_cache, const void* v_cache, long long num_blocks,
                             const int* block_tables, int max_blocks, const int* q_starts, const int* kv_lens,
                             void* out, long long ldo, int num_seqs, int max_q_len, int min_q, int hq, int hkv,
                             int head_dim, float scale, int window, const float* sinks, float softcap, int* status,
-                            cudaStream_t s, int tile_variant = 0);
+                            cudaStream_t s, int tile_variant = 0, int bidir = 0);
 size_t attention_tc_workspace_bytes(int tokens, int hq, int head_dim, int max_splits);
 
 // ---- sampling -----------------------------------------------------------------------

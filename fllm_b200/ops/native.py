@@ -135,12 +135,14 @@ class NativeOps:
 
     # ---------------------------------------------------------------- attention
     def attention(self, q, k_cache, v_cache, block_tables, row_seq, positions, hq, hkv, head_dim,
-                  scale, window=0, sinks=None, softcap=0.0, meta=None):
+                  scale, window=0, sinks=None, softcap=0.0, meta=None, bidirectional=False):
+        """bidirectional: no causal mask (encoders); `positions` must then hold the last position of each row's
+        sequence (the generic kernel's visibility limit), the tensor-core kernels take the flag."""
         out = torch.empty(q.shape[0], hq * head_dim, dtype=q.dtype, device=q.device)
         kv8 = k_cache.element_size() == 1
         if (self.use_tc_attention and meta is not None and meta.q_starts is not None
                 and head_dim in (64, 128) and hq // hkv <= 16
-                and (not kv8 or meta.max_q_len * (hq // hkv) <= 16)):
+                and (not kv8 or (meta.max_q_len * (hq // hkv) <= 16 and not bidirectional))):
             # (an e4m3 KV cache: decode-shaped batches run the tensor-core decode kernel, which widens the pages to
             # f16 in shared memory; batches with prefill chunks fall through to the generic kernel)
             if self.attn_ws is None:
@@ -148,7 +150,7 @@ class NativeOps:
             self.launches += self.k.attention_tc(
                 q, k_cache, v_cache, block_tables, meta.q_starts, meta.seq_lens, out, meta.num_seqs,
                 meta.max_q_len, meta.min_q_len, meta.max_kv_len, hq, hkv, head_dim, float(scale),
-                int(window), sinks, float(softcap), self.attn_ws, self.status)
+                int(window), sinks, float(softcap), self.attn_ws, self.status, bool(bidirectional))
             return out
         self.k.attention_generic(q, k_cache, v_cache, block_tables, row_seq, positions, out, hq, hkv,
                                  head_dim, float(scale), int(window), sinks, float(softcap))

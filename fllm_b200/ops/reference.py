@@ -114,7 +114,9 @@ class RefOps:
 
     # ---------------------------------------------------------------- attention
     def attention(self, q, k_cache, v_cache, block_tables, row_seq, positions, hq, hkv, head_dim,
-                  scale, window=0, sinks=None, softcap=0.0, meta=None):
+                  scale, window=0, sinks=None, softcap=0.0, meta=None, bidirectional=False):
+        """`positions[t]` is the last visible token of row t: a causal decoder passes the row's own position, an
+        encoder (bidirectional) the last position of the row's sequence."""
         T = q.shape[0]
         bs = k_cache.shape[2]
         out = torch.empty(T, hq * head_dim, dtype=q.dtype, device=q.device)

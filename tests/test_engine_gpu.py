@@ -331,3 +331,23 @@ def test_gguf_mixed_k_quants_stay_packed_on_the_gpu(tmp_path):
     err = (outs[0] - outs[1]).abs().max().item()
     assert err < 0.05 * outs[1].abs().max().item() + 1e-3, err
     assert len(toks[0]) == 6
+
+
+def test_encoder_on_the_gpu_matches_the_pytorch_path():
+    """A BERT-shaped encoder (random weights): hidden states, pooled embeddings and classifier logits from the native
+    operators (tcgen05 GEMMs, bidirectional attention kernels) against the PyTorch operators on the same weights."""
+    from fllm_b200.models.encoder import Encoder, EncoderConfig, init_random_encoder
+    from fllm_b200.ops import get_ops
+    from fllm_b200.ops.reference import RefOps
+    cfg = EncoderConfig(vocab_size=1000, hidden_size=256, num_layers=2, num_heads=4, intermediate_size=512, max_position=512, num_labels=2)
+    w = init_random_encoder(cfg, "cuda:0", torch.bfloat16, seed=1)
+    g = torch.Generator().manual_seed(2)
+    seqs = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (7, 150, 33, 300)]
+    nat = Encoder(cfg, w, get_ops("cuda"), "cuda:0")
+    ref = Encoder(cfg, w, RefOps(), "cuda:0")
+    a, b = nat.forward(seqs).float(), ref.forward(seqs).float()
+    assert (a - b).abs().max().item() < 0.05 * b.abs().max().item()
+    ea, eb = nat.embed(seqs), ref.embed(seqs)
+    assert torch.nn.functional.cosine_similarity(ea, eb).min().item() > 0.999
+    assert (nat.classify(seqs) - ref.classify(seqs)).abs().max().item() < 0.05
+    assert nat.ops.check_status() == 0

@@ -824,3 +824,27 @@ def test_packed_5_6_8_bit_weights(ops, qname, T, N, K):
         _close(y, xq.view(T, K) @ dense.t() + (bias.float() if bias is not None else 0), 1e-2)
     _close(y, x.float() @ dense.t() + (bias.float() if bias is not None else 0), 3e-2)
     assert ops.check_status() == 0
+
+
+@pytest.mark.parametrize("D,heads", [(64, 12), (128, 8), (64, 4)])
+@pytest.mark.parametrize("lens", [[5, 12, 33], [200, 64, 130, 17], [700, 300]])
+def test_bidirectional_attention_for_encoders(ops, ref, D, heads, lens):
+    """No causal mask: every query row of a packed sequence sees the whole sequence. The tensor-core prefill kernels
+    (tcgen05 for long rows, mma.sync for short ones) with the flag, and the generic kernel through the visibility
+    limit alone, against the fp32 reference."""
+    tables, kc, vc = _paged_setup(len(lens), lens, heads, D, seed=9)
+    T = sum(lens)
+    row_seq = torch.tensor([i for i, n in enumerate(lens) for _ in range(n)], dtype=torch.int32, device="cuda")
+    vis = torch.tensor([n - 1 for n in lens for _ in range(n)], dtype=torch.int32, device="cuda")
+    q = _rand((T, heads * D), 6)
+    meta = _tc_meta(lens, lens)
+    y = ops.attention(q, kc, vc, tables, row_seq, vis, heads, heads, D, D ** -0.5, meta=meta, bidirectional=True)
+    yr = ref.attention(q, kc, vc, tables, row_seq, vis, heads, heads, D, D ** -0.5)
+    _close(y, yr, 2e-2)
+    yg = ops.attention(q, kc, vc, tables, row_seq, vis, heads, heads, D, D ** -0.5)       # generic kernel
+    _close(yg, yr, 2e-2)
+    # the causal result differs (the flag really changes the mask)
+    pos = torch.tensor([j for n in lens for j in range(n)], dtype=torch.int32, device="cuda")
+    yc = ops.attention(q, kc, vc, tables, row_seq, pos, heads, heads, D, D ** -0.5, meta=meta)
+    assert (yc.float() - y.float()).abs().max().item() > 1e-2
+    assert ops.check_status() == 0
