@@ -4,6 +4,11 @@
 // logit soft-capping. This is the always-correct path and the oracle for the
 // tensor-core kernels; its role matches rust/engine/cuda/attention.cu:41-115.
 //
+// Tree attention (speculative draft trees, rust/engine/cuda/attn_tree.cu:33): the rows of a sequence are the
+// nodes of a draft tree whose keys / values sit behind the committed context in slot order. Row t then sees
+// token j if j < tree_base[t] (context) or bit (j - tree_base[t]) of tree_mask[t] is set (its ancestors and
+// itself): the M x M mask of a tree of at most 64 nodes is one 64-bit word per row.
+//
 // KV cache layout: [block][kv_head][block_size][head_dim], bf16 or e4m3 bytes (fp8 KV cache: values are
 // stored unscaled, e4m3 covers +-448; the reference's counterpart is rust/engine/cuda/kv_quant.cu).
 #include <cuda_fp8.h>
@@ -29,7 +34,8 @@ attn_generic_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
                     int max_blocks, const int* __restrict__ row_seq,
                     const int* __restrict__ positions, __nv_bfloat16* __restrict__ out,
                     long long ldo, int hq, int hkv, int block_size, float scale, int window,
-                    const float* __restrict__ sinks, float softcap) {
+                    const float* __restrict__ sinks, float softcap,
+                    const unsigned long long* __restrict__ tree_mask, const int* __restrict__ tree_base) {
   constexpr int EPL = D / 32;
   const int h = blockIdx.x;
   const int t = blockIdx.y;
@@ -40,6 +46,14 @@ attn_generic_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
   const int kv_len = pos + 1;
   const int kv_begin = (window > 0 && kv_len > window) ? kv_len - window : 0;
   const int* table = block_tables + (size_t)seq * max_blocks;
+  const unsigned long long tmask = tree_mask ? tree_mask[t] : ~0ull;
+  const int tbase = tree_mask ? tree_base[t] : kv_len;
+  auto visible = [&](int j) -> bool {
+    if (j >= kv_len) return false;
+    if (j < tbase) return true;
+    const int b = j - tbase;
+    return b < 64 && ((tmask >> b) & 1ull);
+  };
 
   float qv[EPL];
   {
@@ -60,7 +74,7 @@ attn_generic_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
     for (int u = 0; u < UN; ++u) {
       const int j = base + u;
       s[u] = 0.f;
-      if (j < kv_len) {
+      if (visible(j)) {
         const int blk = table[j / block_size];
         const size_t off = (((size_t)blk * hkv + kvh) * block_size + (j % block_size)) * D + lane * EPL;
         const KV* kp = k_cache + off;
@@ -82,7 +96,7 @@ attn_generic_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
     }
 #pragma unroll
     for (int u = 0; u < UN; ++u) {
-      if (base + u < kv_len) {
+      if (visible(base + u)) {
         float sc = s[u];
         if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
         const float mn = fmaxf(m, sc);
@@ -128,7 +142,8 @@ void attention_generic_bf16(const void* q, long long ldq, const void* k_cache, c
                             const int* block_tables, int max_blocks, const int* row_seq,
                             const int* positions, void* out, long long ldo, int tokens, int hq,
                             int hkv, int head_dim, int block_size, float scale, int window,
-                            const float* sinks, float softcap, cudaStream_t s, int kv_fp8) {
+                            const float* sinks, float softcap, cudaStream_t s, int kv_fp8,
+                            const unsigned long long* tree_mask, const int* tree_base) {
   if (tokens <= 0) return;
   dim3 grid(hq, tokens);
 #define FLLM_ATT(DD)                                                                           \
@@ -136,12 +151,12 @@ void attention_generic_bf16(const void* q, long long ldq, const void* k_cache, c
     if (kv_fp8)                                                                                \
       attn_generic_kernel<DD, uint8_t><<<grid, 128, 0, s>>>(                                   \
           (const __nv_bfloat16*)q, ldq, (const uint8_t*)k_cache, (const uint8_t*)v_cache, block_tables, max_blocks, \
-          row_seq, positions, (__nv_bfloat16*)out, ldo, hq, hkv, block_size, scale, window, sinks, softcap); \
+          row_seq, positions, (__nv_bfloat16*)out, ldo, hq, hkv, block_size, scale, window, sinks, softcap, tree_mask, tree_base); \
     else                                                                                       \
       attn_generic_kernel<DD, __nv_bfloat16><<<grid, 128, 0, s>>>(                             \
           (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_tables, \
           max_blocks, row_seq, positions, (__nv_bfloat16*)out, ldo, hq, hkv, block_size, scale, window, sinks, \
-          softcap);                                                                            \
+          softcap, tree_mask, tree_base);                                                      \
   } while (0)
   switch (head_dim) {
     case 64: FLLM_ATT(64); break;

@@ -220,10 +220,21 @@ void gather_rows(const Tensor& x, const Tensor& rows, Tensor out) {
 void attention_generic(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
                        const Tensor& block_tables, const Tensor& row_seq, const Tensor& positions,
                        Tensor out, int64_t hq, int64_t hkv, int64_t head_dim, double scale,
-                       int64_t window, const optional<Tensor>& sinks, double softcap) {
+                       int64_t window, const optional<Tensor>& sinks, double softcap,
+                       const optional<Tensor>& tree_mask, const optional<Tensor>& tree_base) {
   check_bf16(q, "q"); check_rows(q, "q"); check_bf16(out, "out"); check_rows(out, "out");
   check_i32(block_tables, "block_tables"); check_i32(row_seq, "row_seq");
   check_i32(positions, "positions");
+  const unsigned long long* tm = nullptr;
+  const int* tb = nullptr;
+  if (tree_mask.has_value() && tree_mask->defined()) {        // draft trees: one 64-bit ancestor mask and one context length per row
+    TORCH_CHECK(tree_base.has_value() && tree_base->defined(), "attention_generic: tree_mask needs tree_base");
+    TORCH_CHECK(tree_mask->scalar_type() == at::kLong && tree_mask->is_contiguous() && tree_mask->numel() == q.size(0), "tree_mask: int64 [rows]");
+    check_i32(*tree_base, "tree_base");
+    TORCH_CHECK(tree_base->numel() == q.size(0), "tree_base: int32 [rows]");
+    tm = reinterpret_cast<const unsigned long long*>(tree_mask->data_ptr<int64_t>());
+    tb = tree_base->data_ptr<int>();
+  }
   const bool kv_fp8 = k_cache.element_size() == 1;            // e4m3 bytes instead of bf16
   TORCH_CHECK(k_cache.is_cuda() && k_cache.is_contiguous() && v_cache.is_contiguous() &&
               k_cache.element_size() == v_cache.element_size() && (kv_fp8 || k_cache.scalar_type() == at::kBFloat16),
@@ -234,7 +245,7 @@ void attention_generic(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
                                row_seq.data_ptr<int>(), positions.data_ptr<int>(), out.data_ptr(),
                                out.stride(0), (int)q.size(0), (int)hq, (int)hkv, (int)head_dim,
                                (int)k_cache.size(2), (float)scale, (int)window,
-                               opt_ptr<float>(sinks), (float)softcap, cur_stream(), kv_fp8 ? 1 : 0);
+                               opt_ptr<float>(sinks), (float)softcap, cur_stream(), kv_fp8 ? 1 : 0, tm, tb);
 }
 
 int64_t attention_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
@@ -398,7 +409,7 @@ TORCH_LIBRARY(fllm_b200, m) {
   m.def("rope_kv_write(Tensor(a!) qkv, Tensor positions, Tensor? slots, Tensor inv_freq, Tensor? q_norm_w, Tensor? k_norm_w, Tensor(b!) k_cache, Tensor(c!) v_cache, int hq, int hkv, int head_dim, int rot_dim, int rope_style, float eps, float attn_factor) -> ()", &rope_kv_write);
   m.def("glu(Tensor x, Tensor(a!) out, int act_kind, float alpha, float limit) -> ()", &glu);
   m.def("gather_rows(Tensor x, Tensor rows, Tensor(a!) out) -> ()", &gather_rows);
-  m.def("attention_generic(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor row_seq, Tensor positions, Tensor(a!) out, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap) -> ()", &attention_generic);
+  m.def("attention_generic(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor row_seq, Tensor positions, Tensor(a!) out, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap, Tensor? tree_mask=None, Tensor? tree_base=None) -> ()", &attention_generic);
   m.def("attention_tc(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor q_starts, Tensor kv_lens, Tensor(a!) out, int num_seqs, int max_q_len, int min_q_len, int max_kv_len, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap, Tensor? workspace, Tensor? status=None, bool bidirectional=False) -> int", &attention_tc);
   m.def("argmax(Tensor logits, Tensor(a!) out_ids, Tensor? out_vals, int id_offset) -> ()", &argmax);
   m.def("argmax_split(Tensor logits, Tensor(a!) out_ids, Tensor? out_vals, Tensor? out_pairs, int id_offset, Tensor(b!) scratch) -> ()", &argmax_split);

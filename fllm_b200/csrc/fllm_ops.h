@@ -207,7 +207,8 @@ void attention_generic_bf16(const void* q, long long ldq, const void* k_cache, c
                             const int* block_tables, int max_blocks, const int* row_seq,
                             const int* positions, void* out, long long ldo, int tokens, int hq,
                             int hkv, int head_dim, int block_size, float scale, int window,
-                            const float* sinks, float softcap, cudaStream_t s, int kv_fp8 = 0);
+                            const float* sinks, float softcap, cudaStream_t s, int kv_fp8 = 0,
+                            const unsigned long long* tree_mask = nullptr, const int* tree_base = nullptr);   // draft trees: see the kernel
 
 // Tensor-core paged attention over a ragged batch described per sequence (q_starts, kv_lens).
 // Returns the number of kernels launched.

@@ -157,6 +157,17 @@ class NativeOps:
         self.launches += 1
         return out
 
+    def attention_tree(self, q, k_cache, v_cache, block_tables, row_seq, positions, tree_mask, tree_base, hq, hkv,
+                       head_dim, scale, window=0, sinks=None, softcap=0.0):
+        """Attention for the nodes of draft trees: row t sees the first tree_base[t] tokens of its sequence and the
+        tree nodes whose bit is set in tree_mask[t] (int64, bit i = node i, stored at position tree_base[t] + i);
+        positions[t] = tree_base[t] + nodes - 1."""
+        out = torch.empty(q.shape[0], hq * head_dim, dtype=q.dtype, device=q.device)
+        self.k.attention_generic(q, k_cache, v_cache, block_tables, row_seq, positions, out, hq, hkv, head_dim,
+                                 float(scale), int(window), sinks, float(softcap), tree_mask, tree_base)
+        self.launches += 1
+        return out
+
     # ---------------------------------------------------------------- sampling
     def argmax(self, logits, id_offset=0, want_vals=False, want_pairs=False):
         """Greedy id per row (lowest index among equal maxima). want_pairs: also [rows, 2] fp32

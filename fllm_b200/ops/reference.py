@@ -143,6 +143,32 @@ class RefOps:
             out[t] = torch.einsum("hn,hnd->hd", p, v).reshape(-1).to(q.dtype)
         return out
 
+    def attention_tree(self, q, k_cache, v_cache, block_tables, row_seq, positions, tree_mask, tree_base, hq, hkv,
+                       head_dim, scale, window=0, sinks=None, softcap=0.0):
+        """Rows are nodes of draft trees: the context plus the ancestors named by a 64-bit mask per row."""
+        T = q.shape[0]
+        bs = k_cache.shape[2]
+        out = torch.empty(T, hq * head_dim, dtype=q.dtype, device=q.device)
+        qf = q.float().view(T, hq, head_dim)
+        g = hq // hkv
+        for t in range(T):
+            seq, n, base, mask = int(row_seq[t]), int(positions[t]) + 1, int(tree_base[t]), int(tree_mask[t]) & ((1 << 64) - 1)
+            nblk = (n + bs - 1) // bs
+            blocks = block_tables[seq, :nblk].long()
+            k = k_cache[blocks].float().permute(1, 0, 2, 3).reshape(hkv, nblk * bs, head_dim)[:, :n]
+            v = v_cache[blocks].float().permute(1, 0, 2, 3).reshape(hkv, nblk * bs, head_dim)[:, :n]
+            vis = torch.tensor([j < base or ((mask >> (j - base)) & 1) == 1 for j in range(n)], device=q.device)
+            s = torch.einsum("hd,hnd->hn", qf[t], k.repeat_interleave(g, 0)) * scale
+            if softcap > 0:
+                s = softcap * torch.tanh(s / softcap)
+            s = s.masked_fill(~vis[None, :], float("-inf"))
+            if sinks is not None:
+                p = torch.softmax(torch.cat([s, sinks.float()[:, None]], 1), -1)[:, :-1]
+            else:
+                p = torch.softmax(s, -1)
+            out[t] = torch.einsum("hn,hnd->hd", p, v.repeat_interleave(g, 0)).reshape(-1).to(q.dtype)
+        return out
+
     # ---------------------------------------------------------------- sampling
     def argmax(self, logits, id_offset=0, want_vals=False, want_pairs=False):
         vals, ids = logits.float().max(-1)

@@ -67,6 +67,72 @@ class NgramProposer:
         return []
 
 
+class DraftTree:
+    """A tree of draft tokens for one sequence (rust/engine/src/speculative.rs:146 ``verify_tree``): node i carries
+    `tokens[i]` and hangs under `parents[i]` (-1 = directly under the last committed token); parents come before their
+    children. At most 64 nodes, so a node's visibility over the tree is one 64-bit word."""
+
+    def __init__(self, tokens: Sequence[int], parents: Sequence[int]):
+        if len(tokens) != len(parents) or not 0 < len(tokens) <= 64:
+            raise ValueError("a draft tree has 1 to 64 nodes, one parent per node")
+        for i, p in enumerate(parents):
+            if not -1 <= p < i:
+                raise ValueError("parents must precede their children")
+        self.tokens, self.parents = [int(t) for t in tokens], [int(p) for p in parents]
+
+    def __len__(self) -> int:
+        return len(self.tokens)
+
+    @classmethod
+    def from_chains(cls, chains: Sequence[Sequence[int]]) -> "DraftTree":
+        """Merge several candidate continuations into a prefix tree."""
+        tokens, parents, index = [], [], {}
+        for ch in chains:
+            par = -1
+            for t in ch:
+                key = (par, int(t))
+                if key not in index:
+                    if len(tokens) == 64:
+                        break
+                    index[key] = len(tokens)
+                    tokens.append(int(t))
+                    parents.append(par)
+                par = index[key]
+        return cls(tokens, parents)
+
+    def depths(self) -> List[int]:
+        d = []
+        for p in self.parents:
+            d.append(0 if p < 0 else d[p] + 1)
+        return d
+
+    def masks(self) -> List[int]:
+        """Per node: bit j set when node j is the node itself or one of its ancestors (the row of the M x M mask)."""
+        m = []
+        for i, p in enumerate(self.parents):
+            m.append((1 << i) | (m[p] if p >= 0 else 0))
+        return m
+
+    def masks_i64(self) -> List[int]:
+        """The masks as signed 64-bit integers (what an int64 tensor holds)."""
+        return [x - (1 << 64) if x >= (1 << 63) else x for x in self.masks()]
+
+    def verify_greedy(self, root_target: int, node_targets: Sequence[int]) -> "tuple[List[int], int]":
+        """The longest root-to-node path the target agrees with. `root_target` is the target's token after the
+        committed context, `node_targets[i]` its token after node i (given the node's ancestors). Returns
+        (indices of the accepted nodes in path order, the token to emit after them)."""
+        children: Dict[int, List[int]] = {}
+        for i, p in enumerate(self.parents):
+            children.setdefault(p, []).append(i)
+        path, cur, want = [], -1, int(root_target)
+        while True:
+            nxt = next((c for c in children.get(cur, []) if self.tokens[c] == want), None)
+            if nxt is None:
+                return path, want
+            path.append(nxt)
+            cur, want = nxt, int(node_targets[nxt])
+
+
 class DraftModelProposer:
     """k-token drafts from a small decoder that reuses the target's block tables.
 

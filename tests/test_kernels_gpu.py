@@ -848,3 +848,24 @@ def test_bidirectional_attention_for_encoders(ops, ref, D, heads, lens):
     yc = ops.attention(q, kc, vc, tables, row_seq, pos, heads, heads, D, D ** -0.5, meta=meta)
     assert (yc.float() - y.float()).abs().max().item() > 1e-2
     assert ops.check_status() == 0
+
+
+@pytest.mark.parametrize("D,hq,hkv", [(128, 8, 2), (64, 8, 8)])
+def test_tree_attention_kernel(ops, ref, D, hq, hkv):
+    """Draft-tree rows (context + ancestors through a 64-bit mask per row) on the generic kernel against the
+    reference; two sequences with different trees and contexts, a 64-node tree among them."""
+    from fllm_b200.runtime.speculative import DraftTree
+    trees = [DraftTree.from_chains([[5, 6, 7], [5, 9], [4, 4, 4]]),
+             DraftTree(list(range(64)), [-1] + [i // 2 for i in range(63)])]
+    ctxs = [37, 130]
+    kv_lens = [c + len(t) for c, t in zip(ctxs, trees)]
+    tables, kc, vc = _paged_setup(2, kv_lens, hkv, D, seed=4)
+    rows = sum(len(t) for t in trees)
+    row_seq = torch.tensor([i for i, t in enumerate(trees) for _ in range(len(t))], dtype=torch.int32, device="cuda")
+    pos = torch.tensor([kv_lens[i] - 1 for i, t in enumerate(trees) for _ in range(len(t))], dtype=torch.int32, device="cuda")
+    base = torch.tensor([ctxs[i] for i, t in enumerate(trees) for _ in range(len(t))], dtype=torch.int32, device="cuda")
+    mask = torch.tensor([m for t in trees for m in t.masks_i64()], dtype=torch.int64, device="cuda")
+    q = _rand((rows, hq * D), 8)
+    y = ops.attention_tree(q, kc, vc, tables, row_seq, pos, mask, base, hq, hkv, D, D ** -0.5)
+    yr = ref.attention_tree(q, kc, vc, tables, row_seq, pos, mask, base, hq, hkv, D, D ** -0.5)
+    _close(y, yr, 2e-2)

@@ -108,3 +108,50 @@ def test_engine_speculates_sampled_requests():
         for ev in mixed.step():
             got.setdefault(ev.request_id, []).extend(ev.token_ids)
     assert got[ids[1]] == want and len(got[ids[0]]) == 12
+
+
+def test_draft_tree_masks_and_greedy_verification():
+    from fllm_b200.runtime.speculative import DraftTree
+    tree = DraftTree.from_chains([[5, 6, 7], [5, 9], [4, 4, 4]])
+    assert tree.tokens == [5, 6, 7, 9, 4, 4, 4] and tree.parents == [-1, 0, 1, 0, -1, 4, 5]
+    assert tree.depths() == [0, 1, 2, 1, 0, 1, 2]
+    assert tree.masks() == [0b1, 0b11, 0b111, 0b1001, 0b10000, 0b110000, 0b1110000]
+    # the target wants 5, then 9 after node 0, then 2 after node 3: path [0, 3], bonus token 2
+    assert tree.verify_greedy(5, [9, 0, 0, 2, 0, 0, 0]) == ([0, 3], 2)
+    assert tree.verify_greedy(8, [0] * 7) == ([], 8)
+    assert tree.verify_greedy(4, [0, 0, 0, 0, 4, 4, 1]) == ([4, 5, 6], 1)
+    import pytest
+    with pytest.raises(ValueError):
+        DraftTree([1, 2], [0, -1])
+
+
+def test_tree_attention_reference_equals_chain_attention_on_each_path():
+    """A node of a draft tree must see exactly what it would see if its root-to-node path were a plain sequence."""
+    from fllm_b200.runtime.speculative import DraftTree
+    ops = RefOps()
+    g = torch.Generator().manual_seed(0)
+    hq, hkv, D, bs, ctx = 4, 2, 64, 16, 21
+    tree = DraftTree.from_chains([[5, 6, 7], [5, 9], [4, 4]])
+    M = len(tree)
+    nblk = (ctx + M + bs - 1) // bs
+    kc = torch.randn(nblk, hkv, bs, D, generator=g)
+    vc = torch.randn(nblk, hkv, bs, D, generator=g)
+    tables = torch.arange(nblk, dtype=torch.int32).view(1, nblk)
+    q = torch.randn(M, hq * D, generator=g)
+    rs = torch.zeros(M, dtype=torch.int32)
+    pos = torch.full((M,), ctx + M - 1, dtype=torch.int32)
+    y = ops.attention_tree(q, kc, vc, tables, rs, pos, torch.tensor(tree.masks_i64()), torch.full((M,), ctx, dtype=torch.int32),
+                           hq, hkv, D, D ** -0.5)
+    flat_k = kc.permute(1, 0, 2, 3).reshape(hkv, nblk * bs, D)
+    flat_v = vc.permute(1, 0, 2, 3).reshape(hkv, nblk * bs, D)
+    for i in range(M):
+        path, p = [i], tree.parents[i]
+        while p >= 0:
+            path.append(p)
+            p = tree.parents[p]
+        idx = list(range(ctx)) + [ctx + j for j in sorted(path)]
+        k = flat_k[:, idx].repeat_interleave(hq // hkv, 0)
+        v = flat_v[:, idx].repeat_interleave(hq // hkv, 0)
+        s = torch.einsum("hd,hnd->hn", q[i].view(hq, D), k) * D ** -0.5
+        want = torch.einsum("hn,hnd->hd", torch.softmax(s, -1), v).reshape(-1)
+        assert (y[i] - want).abs().max().item() < 1e-4
