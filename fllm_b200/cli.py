@@ -128,7 +128,9 @@ def cmd_serve(args) -> int:
         # step; the other ranks run the worker loop (launch one process per GPU with torch.distributed.run).
         from .comm import shutdown_distributed
         from .runtime.step_control import ControlChannel, StepController
-        controller = StepController(eng, ControlChannel(timeout_s=args.control_timeout))
+        from .server.app import make_guided_builder
+        controller = StepController(eng, ControlChannel(timeout_s=args.control_timeout),
+                                    guided_builder=make_guided_builder(eng, tok, args.tool_parser))
         if not controller.ch.is_leader:
             why = controller.follow()
             eng.close()

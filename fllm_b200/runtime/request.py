@@ -46,6 +46,7 @@ class SamplingParams:
     speculative: bool = True
     embed: bool = False                  # return the final-norm hidden state of the last prompt token (embeddings API)
     guided: Optional[object] = None      # runtime.grammar.GuidedJson: per-step allowed-token mask + advance()
+    guided_spec: Optional[dict] = None   # the request fields `guided` was built from (travels to the other ranks)
 
     @property
     def greedy(self) -> bool:

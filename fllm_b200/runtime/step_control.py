@@ -33,10 +33,10 @@ KEEPALIVE_S = 2.0           # an idle leader still talks this often, so follower
 
 
 def params_to_wire(p: SamplingParams) -> dict:
-    """Sampling parameters as plain data. A grammar object does not travel: constrained requests are
-    refused at admission under step control."""
-    if p.guided is not None:
-        raise ValueError("grammar-constrained decoding is not available when one server drives several ranks")
+    """Sampling parameters as plain data. A grammar object does not travel; the request fields it was built from
+    (`guided_spec`) do, and every rank rebuilds the same recogniser from them."""
+    if p.guided is not None and not p.guided_spec:
+        raise ValueError("a grammar-constrained request needs its source fields (guided_spec) to reach the other ranks")
     d = dataclasses.asdict(dataclasses.replace(p, guided=None))
     d.pop("guided", None)
     if d.get("logit_bias"):
@@ -44,11 +44,17 @@ def params_to_wire(p: SamplingParams) -> dict:
     return d
 
 
-def params_from_wire(d: dict) -> SamplingParams:
+def params_from_wire(d: dict, guided_builder=None) -> SamplingParams:
+    """`guided_builder(spec)` rebuilds the grammar object of a constrained request (server.app.make_guided_builder)."""
     d = dict(d)
     if d.get("logit_bias"):
         d["logit_bias"] = {int(k): float(v) for k, v in d["logit_bias"].items()}
-    return SamplingParams(**d)
+    sp = SamplingParams(**d)
+    if sp.guided_spec:
+        if guided_builder is None:
+            raise ValueError("a grammar-constrained request arrived but this rank has no grammar builder")
+        sp.guided = guided_builder(sp.guided_spec)
+    return sp
 
 
 class ControlChannel:
@@ -85,8 +91,10 @@ class ControlChannel:
 class StepController:
     """Leader side: queues admissions / aborts and announces every step. Follower side: ``follow()``."""
 
-    def __init__(self, engine, channel: ControlChannel):
-        self.engine, self.ch = engine, channel
+    def __init__(self, engine, channel: ControlChannel, guided_builder=None):
+        """guided_builder(spec) -> grammar object: how a follower rebuilds the recogniser of a constrained request
+        (server.app.make_guided_builder(engine, tokenizer, tool_parser)); None refuses such requests on followers."""
+        self.engine, self.ch, self.guided_builder = engine, channel, guided_builder
         self.pending: List[dict] = []
         self.last_sent = time.monotonic()
         self.steps = 0
@@ -138,7 +146,8 @@ class StepController:
         for c in msg["cmds"]:
             if c["op"] == "add":
                 # one clock for the whole group: deadlines and priority ties use the leader's arrival time
-                eng.add_request(c["prompt"], params_from_wire(c["params"]), request_id=c["rid"], arrival=c["arrival"])
+                eng.add_request(c["prompt"], params_from_wire(c["params"], self.guided_builder), request_id=c["rid"],
+                                arrival=c["arrival"])
             elif c["op"] == "abort":
                 eng.abort_request(c["rid"])
 

@@ -292,6 +292,95 @@ class StopChecker:
         return out
 
 
+GUIDED_KEYS = ("tools", "tool_choice", "guided_choice", "guided_regex", "guided_grammar", "grammar", "response_format",
+               "format", "guided_json")
+
+
+def make_guided_builder(engine, tokenizer, tool_parser):
+    """-> build(body) giving the grammar object of a request (or None): forced tool calls, guided_choice, regular
+    expressions, GBNF grammars, JSON mode and JSON schemas. Only the fields in GUIDED_KEYS are read, so the same
+    fields rebuild the same recogniser on every rank of a tensor-parallel group. Raises ValueError on a bad grammar."""
+    guided_shared: dict = {}
+
+    def build(body: dict):
+        tc = body.get("tool_choice")
+        if body.get("tools") and tool_parser == "hermes" and (tc == "required" or (isinstance(tc, dict) and tc.get("function"))):
+            # a forced tool call: the output is the call markup with one of the offered (or the named) functions
+            from ..runtime.grammar import GuidedToolCall, TokenTrie
+            if "trie" not in guided_shared:
+                guided_shared["trie"] = TokenTrie.from_tokenizer(tokenizer)
+                guided_shared["masks"] = {}
+            names = ([tc["function"].get("name")] if isinstance(tc, dict)
+                     else [(t.get("function") or {}).get("name") for t in body["tools"] if isinstance(t, dict)])
+            eos = [getattr(tokenizer, "eos_token_id", None), getattr(engine, "eos_token_id", None)]
+            try:
+                return GuidedToolCall(guided_shared["trie"], tokenizer, eos, [n for n in names if n])
+            except ValueError as e:
+                raise ValueError(str(e))
+        if body.get("guided_choice"):
+            from ..runtime.grammar import GuidedChoice, TokenTrie
+            if "trie" not in guided_shared:
+                guided_shared["trie"] = TokenTrie.from_tokenizer(tokenizer)
+                guided_shared["masks"] = {}
+            eos = [getattr(tokenizer, "eos_token_id", None), getattr(engine, "eos_token_id", None)]
+            try:
+                return GuidedChoice(guided_shared["trie"], tokenizer, eos, body["guided_choice"])
+            except (ValueError, TypeError) as e:
+                raise ValueError(str(e))
+        # general grammars: a regular expression, a GBNF grammar (vLLM's guided_regex / guided_grammar, llama.cpp's
+        # grammar), or response_format {"type": "regex" | "grammar"}
+        rf0 = body.get("response_format") if isinstance(body.get("response_format"), dict) else {}
+        g_regex = body.get("guided_regex") or (rf0.get("pattern") if rf0.get("type") == "regex" else None)
+        g_gbnf = body.get("guided_grammar") or body.get("grammar") or (rf0.get("grammar") if rf0.get("type") == "grammar" else None)
+        if g_regex or g_gbnf:
+            from ..runtime.grammar import TokenTrie
+            from ..runtime.grammar_gbnf import GrammarError, GuidedGrammar, machine_from
+            if "trie" not in guided_shared:
+                guided_shared["trie"] = TokenTrie.from_tokenizer(tokenizer)
+                guided_shared["masks"] = {}
+            eos = [getattr(tokenizer, "eos_token_id", None), getattr(engine, "eos_token_id", None)]
+            try:
+                machine = machine_from("regex", str(g_regex)) if g_regex else machine_from("gbnf", str(g_gbnf))
+            except (GrammarError, ValueError, IndexError) as e:
+                raise ValueError(f"invalid grammar: {e}")
+            return GuidedGrammar(guided_shared["trie"], tokenizer, eos, machine)
+        rf = body.get("response_format")
+        kind = rf.get("type") if isinstance(rf, dict) else None
+        fmt = body.get("format")
+        if kind not in ("json_object", "json_schema") and fmt != "json" and not isinstance(fmt, dict) \
+                and not body.get("guided_json"):
+            return None
+        from ..runtime.grammar import GuidedJson, GuidedJsonSchema, TokenTrie
+        if "trie" not in guided_shared:
+            guided_shared["trie"] = TokenTrie.from_tokenizer(tokenizer)
+            guided_shared["masks"] = {}
+        eos = [getattr(tokenizer, "eos_token_id", None), getattr(engine, "eos_token_id", None)]
+        schema = None
+        if kind == "json_schema":
+            js = rf.get("json_schema") or {}
+            schema = js.get("schema") if isinstance(js.get("schema"), dict) else (js if "properties" in js else None)
+        elif isinstance(body.get("guided_json"), dict):
+            schema = body["guided_json"]
+        elif isinstance(fmt, dict):
+            schema = fmt
+        if isinstance(schema, dict) and schema:
+            # the whole schema (nested objects, arrays, enums, references ...) as a grammar; schemas that grammar
+            # cannot express fall back to the recogniser that enforces the top-level object only
+            from ..runtime.grammar_gbnf import GrammarError, GuidedGrammar, machine_from
+            try:
+                return GuidedGrammar(guided_shared["trie"], tokenizer, eos, machine_from("json_schema", schema))
+            except (GrammarError, KeyError, TypeError, ValueError, IndexError, RecursionError):
+                pass
+        if isinstance(schema, dict) and schema.get("type", "object") == "object" and isinstance(schema.get("properties"), dict):
+            try:
+                return GuidedJsonSchema(guided_shared["trie"], tokenizer, eos, schema)
+            except ValueError as e:
+                raise ValueError(str(e))
+        return GuidedJson(guided_shared["trie"], tokenizer, eos, require_object=True, cache=guided_shared["masks"])
+
+    return build
+
+
 def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Optional[str] = None,
                tool_parser: Optional[str] = None, reasoning_parser: Optional[str] = None,
                response_cache_entries: int = 256, response_cache_ttl_s: float = 600.0,
@@ -451,6 +540,8 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
             out.append(spi)
         return out
 
+    build_guided = make_guided_builder(engine, tokenizer, tool_parser)
+
     def attach_guided(sp: SamplingParams, body: dict) -> None:
         """response_format json_object / json_schema (OpenAI) and format: "json" (Ollama) constrain the
         output to a JSON object through the sampler's allowed-token mask."""
@@ -468,85 +559,13 @@ def create_app(engine, tokenizer, model_name: str = "fllm-b200", api_key: Option
         if brk:
             extra = {int(tokenizer.encode(w, add_bos=False)[-1]) for w in brk if tokenizer.encode(w, add_bos=False)}
             sp.dry_sequence_breakers = tuple(sorted(set(sp.dry_sequence_breakers) | extra))
-        tc = body.get("tool_choice")
-        if body.get("tools") and tool_parser == "hermes" and (tc == "required" or (isinstance(tc, dict) and tc.get("function"))):
-            # a forced tool call: the output is the call markup with one of the offered (or the named) functions
-            from ..runtime.grammar import GuidedToolCall, TokenTrie
-            if "trie" not in guided_shared:
-                guided_shared["trie"] = TokenTrie.from_tokenizer(tokenizer)
-                guided_shared["masks"] = {}
-            names = ([tc["function"].get("name")] if isinstance(tc, dict)
-                     else [(t.get("function") or {}).get("name") for t in body["tools"] if isinstance(t, dict)])
-            eos = [getattr(tokenizer, "eos_token_id", None), getattr(engine, "eos_token_id", None)]
-            try:
-                sp.guided = GuidedToolCall(guided_shared["trie"], tokenizer, eos, [n for n in names if n])
-            except ValueError as e:
-                raise HTTPException(400, str(e))
-            return
-        if body.get("guided_choice"):
-            from ..runtime.grammar import GuidedChoice, TokenTrie
-            if "trie" not in guided_shared:
-                guided_shared["trie"] = TokenTrie.from_tokenizer(tokenizer)
-                guided_shared["masks"] = {}
-            eos = [getattr(tokenizer, "eos_token_id", None), getattr(engine, "eos_token_id", None)]
-            try:
-                sp.guided = GuidedChoice(guided_shared["trie"], tokenizer, eos, body["guided_choice"])
-            except (ValueError, TypeError) as e:
-                raise HTTPException(400, str(e))
-            return
-        # general grammars: a regular expression, a GBNF grammar (vLLM's guided_regex / guided_grammar, llama.cpp's
-        # grammar), or response_format {"type": "regex" | "grammar"}
-        rf0 = body.get("response_format") if isinstance(body.get("response_format"), dict) else {}
-        g_regex = body.get("guided_regex") or (rf0.get("pattern") if rf0.get("type") == "regex" else None)
-        g_gbnf = body.get("guided_grammar") or body.get("grammar") or (rf0.get("grammar") if rf0.get("type") == "grammar" else None)
-        if g_regex or g_gbnf:
-            from ..runtime.grammar import TokenTrie
-            from ..runtime.grammar_gbnf import GrammarError, GuidedGrammar, machine_from
-            if "trie" not in guided_shared:
-                guided_shared["trie"] = TokenTrie.from_tokenizer(tokenizer)
-                guided_shared["masks"] = {}
-            eos = [getattr(tokenizer, "eos_token_id", None), getattr(engine, "eos_token_id", None)]
-            try:
-                machine = machine_from("regex", str(g_regex)) if g_regex else machine_from("gbnf", str(g_gbnf))
-            except (GrammarError, ValueError, IndexError) as e:
-                raise HTTPException(400, f"invalid grammar: {e}")
-            sp.guided = GuidedGrammar(guided_shared["trie"], tokenizer, eos, machine)
-            return
-        rf = body.get("response_format")
-        kind = rf.get("type") if isinstance(rf, dict) else None
-        fmt = body.get("format")
-        if kind not in ("json_object", "json_schema") and fmt != "json" and not isinstance(fmt, dict) \
-                and not body.get("guided_json"):
-            return
-        from ..runtime.grammar import GuidedJson, GuidedJsonSchema, TokenTrie
-        if "trie" not in guided_shared:
-            guided_shared["trie"] = TokenTrie.from_tokenizer(tokenizer)
-            guided_shared["masks"] = {}
-        eos = [getattr(tokenizer, "eos_token_id", None), getattr(engine, "eos_token_id", None)]
-        schema = None
-        if kind == "json_schema":
-            js = rf.get("json_schema") or {}
-            schema = js.get("schema") if isinstance(js.get("schema"), dict) else (js if "properties" in js else None)
-        elif isinstance(body.get("guided_json"), dict):
-            schema = body["guided_json"]
-        elif isinstance(fmt, dict):
-            schema = fmt
-        if isinstance(schema, dict) and schema:
-            # the whole schema (nested objects, arrays, enums, references ...) as a grammar; schemas that grammar
-            # cannot express fall back to the recogniser that enforces the top-level object only
-            from ..runtime.grammar_gbnf import GrammarError, GuidedGrammar, machine_from
-            try:
-                sp.guided = GuidedGrammar(guided_shared["trie"], tokenizer, eos, machine_from("json_schema", schema))
-                return
-            except (GrammarError, KeyError, TypeError, ValueError, IndexError, RecursionError):
-                pass
-        if isinstance(schema, dict) and schema.get("type", "object") == "object" and isinstance(schema.get("properties"), dict):
-            try:
-                sp.guided = GuidedJsonSchema(guided_shared["trie"], tokenizer, eos, schema)
-                return
-            except ValueError as e:
-                raise HTTPException(400, str(e))
-        sp.guided = GuidedJson(guided_shared["trie"], tokenizer, eos, require_object=True, cache=guided_shared["masks"])
+        try:
+            g = build_guided(body)
+        except ValueError as e:
+            raise HTTPException(400, str(e))
+        if g is not None:
+            sp.guided = g
+            sp.guided_spec = {k: body[k] for k in GUIDED_KEYS if k in body}
 
     def shape_message(text: str) -> "tuple[dict, bool]":
         """Assistant message of a finished chat turn: reasoning split off, tool calls parsed."""

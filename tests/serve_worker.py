@@ -34,7 +34,10 @@ def main():
                     eos_token_id=None)
     prompts = [[5, 6, 7, 8, 9, 10, 11], list(range(20, 60)), [3, 1, 4, 1, 5, 9, 2, 6]]
     want = eng.generate(prompts, SamplingParams(max_tokens=6)) if mode == "tokens" else None   # every rank takes part
-    ctl = StepController(eng, ControlChannel(timeout_s=float(os.environ.get("CONTROL_TIMEOUT", "8"))))
+    from fllm_b200.server.app import make_guided_builder
+    from fllm_b200.tokenizer import ByteTokenizer
+    ctl = StepController(eng, ControlChannel(timeout_s=float(os.environ.get("CONTROL_TIMEOUT", "8"))),
+                         guided_builder=make_guided_builder(eng, ByteTokenizer(512), None))
     out = {"rank": rank, "mode": mode}
     if rank != 0:
         if mode == "leaver":
@@ -69,10 +72,12 @@ def main():
             # a sampled request goes through the full sampler on every rank (seeded, so identical everywhere)
             r = c.post("/v1/completions", json={"prompt": prompts[0], "max_tokens": 4, "temperature": 0.8, "seed": 7})
             out["sampled_status"] = r.status_code
-            # a constrained request is refused at admission and never reaches the followers
-            r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "max_tokens": 4,
-                                                     "response_format": {"type": "json_object"}})
+            # a constrained request: every rank rebuilds the recogniser from the request's fields, so the masks agree
+            r = c.post("/v1/completions", json={"prompt": "x", "max_tokens": 12, "temperature": 0, "guided_regex": "[ab]{3}c"})
             out["guided_status"] = r.status_code
+            out["guided_text"] = r.json()["choices"][0]["text"] if r.status_code == 200 else r.text
+            r = c.post("/v1/completions", json={"prompt": "x", "max_tokens": 4, "guided_regex": "(unclosed"})
+            out["bad_grammar_status"] = r.status_code
             r = c.post("/v1/completions", json={"prompt": prompts[2], "max_tokens": 3, "temperature": 0})
             out["after_refusal_status"] = r.status_code
         else:

@@ -48,7 +48,9 @@ def test_http_request_to_rank0_is_served_by_both_ranks():
     r0, r1 = _run(2, "tokens")
     assert r0["total"] == 18 and r0["agree"] == r0["total"], r0
     assert r0["ready"] == 200 and r0["sampled_status"] == 200
-    assert r0["guided_status"] == 400 and r0["after_refusal_status"] == 200
+    import re
+    assert r0["guided_status"] == 200 and re.fullmatch("[ab]{3}c", r0["guided_text"]), r0
+    assert r0["bad_grammar_status"] == 400 and r0["after_refusal_status"] == 200
     assert r1["ended"] == "stop" and r1["steps"] > 0
 
 
