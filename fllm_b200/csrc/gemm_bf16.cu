@@ -907,12 +907,6 @@ int linear_bf16_tp(const void* x, long long ldx, const void* w, long long ldw, c
   // A gated epilogue needs complete sums: no split-K, unless the caller takes the fp32 partials and
   // applies the activation while it adds them.
   if (glu && splits > 1 && !defer) splits = 1;
-  // Broadcast destination with a short K (the per-rank slice of a row-parallel projection at tensor-parallel
-  // degree 4 - 8): the whole product is a few microseconds, so a second kernel that adds split-K partials and
-  // pushes them costs more than the few idle SMs; the epilogue pushes straight to the peers.
-  static int push_kb = -1;
-  if (push_kb < 0) { const char* e = getenv("FLLM_TP_PUSH_KB"); push_kb = e ? atoi(e) : 24; }
-  if (rs && tpa->rs_bcast && force_splits <= 0 && a.k_blocks <= push_kb) splits = 1;
   // Broadcast destination + split-K: the GEMM keeps its fast local split path and the reduction
   // kernel does the pushing. Scatter destination + split-K: the last-arriving CTA finishes the tile.
   const bool push_reduce = rs && tpa->rs_bcast && splits > 1;
