@@ -145,6 +145,40 @@ def build_cpu(verbose: bool = False) -> Path:
     return LIB_CPU
 
 
+SAN_FLAGS = ["-O1", "-g", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-fopenmp", "-fno-omit-frame-pointer",
+             "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"]
+LIB_CPU_SAN = BUILD / "_cpu_sanitized.so"
+
+
+def build_cpu_sanitized(verbose: bool = False) -> Path:
+    """The CPU engine and codecs with AddressSanitizer + UndefinedBehaviorSanitizer (a separate library under
+    build/, loaded by `python -m fllm_b200 selftest-cpu --sanitize` in a child process with the ASan runtime
+    preloaded). Plays the role of the reference's sanitizer builds of its host code."""
+    BUILD.mkdir(exist_ok=True)
+    headers = sorted(CPU_SRC.glob("*.h"))
+    jobs, objs = [], []
+    for src in sorted(CPU_SRC.glob("*.cpp")):
+        obj = BUILD / ("cpusan_" + src.stem + ".o")
+        objs.append(obj)
+        jobs.append((src, obj, ["g++", *SAN_FLAGS, "-I", CPU_SRC, "-c", src, "-o", obj], headers))
+    changed = _compile_many(jobs, verbose)
+    if changed or not LIB_CPU_SAN.exists():
+        tmp = LIB_CPU_SAN.with_suffix(".so.tmp")
+        _run(["g++", "-shared", "-fopenmp", "-fsanitize=address,undefined", "-o", tmp, *objs], verbose)
+        os.replace(tmp, LIB_CPU_SAN)
+    return LIB_CPU_SAN
+
+
+def sanitizer_runtime() -> str:
+    """Path of the AddressSanitizer runtime to preload into a Python child process ('' when the compiler has none)."""
+    import subprocess
+    try:
+        p = subprocess.run(["gcc", "-print-file-name=libasan.so"], capture_output=True, text=True, check=True).stdout.strip()
+    except (OSError, subprocess.CalledProcessError):
+        return ""
+    return os.path.realpath(p) if os.path.sep in p and os.path.exists(p) else ""
+
+
 def build_all(verbose: bool = False) -> None:
     build_cpu(verbose)
     build_cuda(verbose)

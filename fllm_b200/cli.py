@@ -469,7 +469,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     b.add_argument("rest", nargs=argparse.REMAINDER)
     b.set_defaults(fn=lambda a: subprocess.call([sys.executable, os.path.join(os.path.dirname(os.path.dirname(
         os.path.abspath(__file__))), "bench.py")] + a.rest))
-    for which in ("cpu", "gpu", "comm", "parallel"):
+    for which in ("cpu", "gpu", "comm", "parallel", "sanitize"):
         sub.add_parser(f"selftest-{which}").set_defaults(fn=lambda a, w=which: _selftest(w))
     args = ap.parse_args(argv)
     return int(args.fn(args) or 0)

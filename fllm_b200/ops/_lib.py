@@ -43,6 +43,10 @@ def have_cuda_lib() -> bool:
 def load_cpu(build_if_missing: bool = True) -> ctypes.CDLL:
     if _state["cpu"] is not None:
         return _state["cpu"]
+    alt = os.environ.get("FLLM_CPU_LIB")          # another build of the same library (the sanitizer build)
+    if alt:
+        _state["cpu"] = ctypes.CDLL(alt)
+        return _state["cpu"]
     if not _LIB_CPU.exists():
         if not build_if_missing:
             raise RuntimeError(f"native library {_LIB_CPU} is missing; run `python -m fllm_b200._build`")

@@ -122,6 +122,28 @@ def selftest_cpu() -> int:
                  ("native cpu engine on a packed tiny model", _check_cpu_native_engine)])
 
 
+def selftest_sanitize() -> int:
+    """The CPU self-test again in a child process against the AddressSanitizer + UBSan build of the native CPU
+    library (`_build.build_cpu_sanitized`), the sanitizer runtime preloaded. Any report fails the run."""
+    from . import _build
+    rt = _build.sanitizer_runtime()
+    if not rt:
+        print("sanitize: the compiler ships no AddressSanitizer runtime; skipped")
+        return 0
+    lib = _build.build_cpu_sanitized()
+    env = dict(os.environ, LD_PRELOAD=rt, FLLM_CPU_LIB=str(lib), OMP_NUM_THREADS="2",
+               ASAN_OPTIONS="detect_leaks=0:abort_on_error=0:exitcode=23", UBSAN_OPTIONS="print_stacktrace=1:halt_on_error=1")
+    p = subprocess.run([sys.executable, "-m", "fllm_b200.selftest", "cpu"], env=env, capture_output=True, text=True, timeout=1200)
+    bad = [l for l in p.stderr.splitlines() if "AddressSanitizer" in l or "runtime error:" in l]
+    print(p.stdout[-2000:])
+    if p.returncode != 0 or bad:
+        print("\n".join(bad[:20]) or p.stderr[-2000:])
+        print(f"sanitize: FAILED (exit {p.returncode})")
+        return 1
+    print("sanitize: clean (AddressSanitizer + UndefinedBehaviorSanitizer)")
+    return 0
+
+
 # ------------------------------------------------------------------------------------------- GPU
 def _gpu_ops():
     from .ops.native import NativeOps
@@ -333,7 +355,8 @@ def main(argv=None) -> int:
         sys.stdout.flush()
         os._exit(0)               # leave without tearing the process group down rank by rank
     which = argv[0] if argv else "cpu"
-    return {"cpu": selftest_cpu, "gpu": selftest_gpu, "comm": selftest_comm, "parallel": selftest_parallel}[which]()
+    return {"cpu": selftest_cpu, "gpu": selftest_gpu, "comm": selftest_comm, "parallel": selftest_parallel,
+            "sanitize": selftest_sanitize}[which]()
 
 
 if __name__ == "__main__":

@@ -66,3 +66,13 @@ def test_cli_quantize_set_split_merge_and_ppl(store, capsys):
     assert cli(["ppl", "--model", src, "--device", "cpu", "--ctx", "128", "--kv-blocks", "32", "--file", str(text)]) == 0
     out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert out["tokens"] > 50 and out["perplexity"] > 1.0
+
+
+def test_sanitizer_build_of_the_cpu_library_runs_clean():
+    """AddressSanitizer + UBSan build of the native CPU engine / codecs: the CPU self-test in a child process."""
+    from fllm_b200 import _build, selftest
+    if not _build.sanitizer_runtime():
+        import pytest
+        pytest.skip("no AddressSanitizer runtime with this compiler")
+    assert selftest.selftest_sanitize() == 0
+    assert _build.LIB_CPU_SAN.exists()
