@@ -70,11 +70,16 @@ class SafetensorsFile:
 
 
 def open_checkpoint(directory: str) -> Dict[str, Tuple[SafetensorsFile, str]]:
-    """name -> (file, name) over every *.safetensors of a checkpoint directory (index-aware)."""
+    """name -> (file, name) over every *.safetensors of a checkpoint directory (index-aware); a directory that holds
+    ``pytorch_model.bin`` files instead is read through ``formats.torch_zip``."""
     files = {}
     out: Dict[str, Tuple[SafetensorsFile, str]] = {}
     idx = os.path.join(directory, "model.safetensors.index.json")
     names = sorted(f for f in os.listdir(directory) if f.endswith(".safetensors"))
+    if not names and not os.path.exists(idx):
+        # a PyTorch zip checkpoint (pytorch_model.bin and shards): same interface, read without running its pickle
+        from .torch_zip import open_torch_checkpoint
+        return open_torch_checkpoint(directory)
     if os.path.exists(idx):
         wm = json.load(open(idx))["weight_map"]
         for tname, fname in wm.items():

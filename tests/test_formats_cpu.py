@@ -574,3 +574,38 @@ def test_planar_device_forms_of_q5k_q6k_q80_equal_the_codecs():
     y = RefOps().linear(x, st)
     ref = x.float() @ st.dense().t()
     assert st.shape == (128, K) and float((y.float() - ref).abs().max() / ref.abs().max()) < 1e-2
+
+
+def test_pytorch_zip_checkpoints_are_read_without_running_their_pickle(tmp_path):
+    import collections
+    import os
+    import pickle
+    import zipfile
+    import pytest
+    import torch
+    from fllm_b200.formats.safetensors_io import open_checkpoint
+    from fllm_b200.formats.torch_zip import TorchZipError, TorchZipFile
+    sd = collections.OrderedDict(a=torch.randn(3, 4), b=torch.randn(5, 6).bfloat16(), c=torch.arange(10)[2:8],
+                                 t=torch.randn(4, 6).t(), s=torch.tensor(3.5), p=torch.nn.Parameter(torch.randn(2, 2)),
+                                 h=torch.randn(7).half())
+    d = tmp_path / "ck"
+    d.mkdir()
+    torch.save(sd, str(d / "pytorch_model.bin"))
+    ck = open_checkpoint(str(d))
+    assert set(ck) == set(sd)
+    for k, v in sd.items():
+        got = ck[k][0].tensor(k)
+        assert got.dtype == v.dtype and torch.equal(got, v.detach()), k
+
+    class Evil:
+        def __reduce__(self):
+            return (os.system, ("true",))
+    bad = str(tmp_path / "bad.bin")
+    with zipfile.ZipFile(bad, "w") as z:
+        z.writestr("archive/data.pkl", pickle.dumps({"x": Evil()}))
+    with pytest.raises(TorchZipError):
+        TorchZipFile(bad)
+    with open(str(tmp_path / "junk.bin"), "wb") as f:
+        f.write(b"not a zip at all")
+    with pytest.raises(TorchZipError):
+        TorchZipFile(str(tmp_path / "junk.bin"))
