@@ -21,7 +21,7 @@ void quant_fp8_1x128(const Tensor& x, Tensor xq, Tensor sx) {
 }
 
 int64_t linear_fp8_block(const Tensor& xq, const Tensor& sx, const Tensor& wq, const Tensor& sw, const optional<Tensor>& bias,
-                         Tensor y, const optional<Tensor>& status) {
+                         Tensor y, const optional<Tensor>& status, const optional<Tensor>& workspace) {
   TORCH_CHECK(xq.is_cuda() && xq.is_contiguous() && wq.is_contiguous() && xq.element_size() == 1 && wq.element_size() == 1, "xq, wq: contiguous e4m3 bytes");
   TORCH_CHECK(xq.dim() == 2 && wq.dim() == 2 && xq.size(1) == wq.size(1), "K mismatch");
   const int64_t T = xq.size(0), N = wq.size(0), K = xq.size(1);
@@ -31,8 +31,14 @@ int64_t linear_fp8_block(const Tensor& xq, const Tensor& sx, const Tensor& wq, c
   c10::cuda::CUDAGuard guard(xq.device());
   const void* b = bias.has_value() && bias->defined() ? bias->data_ptr() : nullptr;
   int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  void* ws = nullptr;
+  size_t ws_bytes = 0;                 // the first 64 KiB of the shared workspace hold the dense GEMM's tile counters
+  if (workspace.has_value() && workspace->defined() && workspace->numel() * workspace->element_size() > (64 << 10)) {
+    ws = static_cast<char*>(workspace->data_ptr()) + (64 << 10);
+    ws_bytes = workspace->numel() * workspace->element_size() - (64 << 10);
+  }
   return fllm::linear_fp8_block(xq.data_ptr(), sx.data_ptr<float>(), wq.data_ptr(), sw.data_ptr<float>(), b, y.data_ptr(),
-                                y.stride(0), (int)T, (int)N, (int)K, st, cur_stream());
+                                y.stride(0), (int)T, (int)N, (int)K, st, cur_stream(), ws, ws_bytes);
 }
 
 // codes uint8 [N, K/2]; scales uint8 [N, K/16] e4m3 (fmt 0), [N, K/32] e8m0 (fmt 1) or bf16 [N, K/32, 2] = {scale, min} (fmt 2)
@@ -203,7 +209,7 @@ void w4_dequant(const Tensor& codes, const Tensor& scales, int64_t fmt, double a
 
 TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("quant_fp8_1x128(Tensor x, Tensor(a!) xq, Tensor(b!) sx) -> ()", &quant_fp8_1x128);
-  m.def("linear_fp8_block(Tensor xq, Tensor sx, Tensor wq, Tensor sw, Tensor? bias, Tensor(a!) y, Tensor? status) -> int", &linear_fp8_block);
+  m.def("linear_fp8_block(Tensor xq, Tensor sx, Tensor wq, Tensor sw, Tensor? bias, Tensor(a!) y, Tensor? status, Tensor? workspace=None) -> int", &linear_fp8_block);
   m.def("linear_w4a16(Tensor x, Tensor codes, Tensor scales, int fmt, float alpha, Tensor? bias, Tensor(a!) y, Tensor? workspace, Tensor? status) -> int", &linear_w4a16);
   m.def("quant_mx(Tensor x, Tensor(a!) xq, Tensor(b!) sf) -> ()", &quant_mx);
   m.def("quant_rows_8bit(Tensor x, Tensor(a!) xq, Tensor(b!) tok_scale, bool is_int8) -> ()", &quant_rows_8bit);

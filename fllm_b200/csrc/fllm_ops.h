@@ -130,7 +130,8 @@ int linear_mx(const void* xq, const void* sfb, const void* wq, const void* sfa, 
               void* workspace, size_t workspace_bytes, int* status, cudaStream_t stream);
 void quant_fp8_1x128(const void* x, long long ldx, void* xq, float* sx, int tokens, int K, cudaStream_t s);
 int linear_fp8_block(const void* xq, const float* sx, const void* wq, const float* sw, const void* bias, void* y,
-                     long long ldy, int T, int N, int K, int* status, cudaStream_t stream);
+                     long long ldy, int T, int N, int K, int* status, cudaStream_t stream, void* workspace = nullptr,
+                     size_t workspace_bytes = 0);   // workspace: fp32 split-K partials (few tiles, or K above 8192)
 
 // ---- packed 4-bit weights x bf16 activations (fmt 0 = NVFP4: e4m3 scale per 16; 1 = MXFP4: e8m0 per 32)
 int linear_w4a16(const void* x, long long ldx, const void* codes, const void* scales, int fmt, float alpha,

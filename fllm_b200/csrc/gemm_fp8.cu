@@ -40,6 +40,8 @@ struct Fp8GemmArgs {
   const float* sw;          // [features / 128][k_blocks]
   const __nv_bfloat16* bias;
   int* status;
+  int k_splits, kb_per_split;   // work items are (tile, split): few tiles cannot pull the whole HBM bandwidth otherwise
+  float* ws;                    // [k_splits][tokens][features] fp32 partial sums when k_splits > 1
 };
 
 template <int BN>
@@ -85,7 +87,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const int tiles = p.m_tiles * p.n_tiles;
+  const int tiles = p.m_tiles * p.n_tiles * p.k_splits;      // work items: the split is the fastest index
 
   if (warp == 0) {
     if (lane == 0) {
@@ -93,8 +95,10 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       uint32_t phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < tiles && ok; w += gridDim.x) {
-        const int n_idx = w / p.m_tiles, m_idx = w - n_idx * p.m_tiles;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int split = w % p.k_splits, t = w / p.k_splits;
+        const int n_idx = t / p.m_tiles, m_idx = t - n_idx * p.m_tiles;
+        const int kb0 = split * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&full_bar[stage], S::kStageBytes);
           tma_load_2d(sA + stage * S::kABytes, &tma_a, &full_bar[stage], kb * F8_BK, m_idx * F8_BM);
@@ -110,7 +114,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       uint32_t phase = 0, buf_phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < tiles && ok; w += gridDim.x) {
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int split = w % p.k_splits;
+        const int kb0 = split * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           // each K block gets its own accumulator: wait until the epilogue drained this buffer
           if (!mbar_wait(&tempty_bar[buf], buf_phase ^ 1, abort_flag)) { ok = false; break; }
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
@@ -135,14 +141,16 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     uint32_t buf_phase = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < tiles && ok; w += gridDim.x) {
-      const int n_idx = w / p.m_tiles, m_idx = w - n_idx * p.m_tiles;
+      const int split = w % p.k_splits, t = w / p.k_splits;
+      const int n_idx = t / p.m_tiles, m_idx = t - n_idx * p.m_tiles;
+      const int kb0 = split * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
       const int m = m_idx * F8_BM + q * 32 + lane;
       const int n_base = n_idx * BN;
       if (p.transposed) {
         // token scales of the tile: s_scale[kb][c] = sx[n_base + c][kb]
         asm volatile("bar.sync 1, 128;" ::: "memory");              // previous tile finished reading
-        for (int i = etid; i < p.k_blocks * BN; i += 128) {
-          const int kb = i / BN, c = i - kb * BN;
+        for (int i = etid; i < (kb1 - kb0) * BN; i += 128) {
+          const int kb = kb0 + i / BN, c = i % BN;
           const int tok = n_base + c;
           s_scale[i] = tok < p.N ? p.sx[(size_t)tok * p.k_blocks + kb] : 0.f;
         }
@@ -151,7 +159,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       float acc[BN];
 #pragma unroll
       for (int c = 0; c < BN; ++c) acc[c] = 0.f;
-      for (int kb = 0; kb < p.k_blocks && ok; ++kb) {
+      for (int kb = kb0; kb < kb1 && ok; ++kb) {
         if (!mbar_wait(&tfull_bar[buf], buf_phase, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t t_row = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
@@ -173,7 +181,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           tmem_ld_wait();
           if (p.transposed) {
 #pragma unroll
-            for (int c = 0; c < CH; ++c) acc[c0 + c] += __uint_as_float(r[c]) * (row_scale * s_scale[kb * BN + c0 + c]);
+            for (int c = 0; c < CH; ++c) acc[c0 + c] += __uint_as_float(r[c]) * (row_scale * s_scale[(kb - kb0) * BN + c0 + c]);
           } else {
 #pragma unroll
             for (int c = 0; c < CH; ++c) {
@@ -190,7 +198,18 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       }
       if (!ok) break;
       // store
-      if (!p.transposed) {
+      if (p.k_splits > 1) {                                   // fp32 partial sums [split][token][feature]; bias in the reduction
+        float* wsp = p.ws + (size_t)split * (p.transposed ? (size_t)p.N * p.M : (size_t)p.M * p.N);
+        if (p.transposed) {                                   // lanes run along features: coalesced
+#pragma unroll
+          for (int c = 0; c < BN; ++c)
+            if (n_base + c < p.N && m < p.M) wsp[(size_t)(n_base + c) * p.M + m] = acc[c];
+        } else if (m < p.M) {
+#pragma unroll
+          for (int c = 0; c < BN; c += 4)
+            if (n_base + c < p.N) *reinterpret_cast<float4*>(wsp + (size_t)m * p.N + n_base + c) = make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
+        }
+      } else if (!p.transposed) {
         if (m < p.M) {
           __nv_bfloat16* dst = p.out + (size_t)m * p.ldc + n_base;
 #pragma unroll
@@ -225,6 +244,27 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   __syncthreads();
   if (warp == 1) { tc_fence_after_sync(); tmem_dealloc(tmem_base, S::kTmemCols); }
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicCAS(p.status, FLLM_OK, FLLM_ERR_MBAR_TIMEOUT);
+}
+
+// out[t][n] = bf16(sum_s ws[s][t][n] + bias[n])
+__global__ void fp8_splitk_reduce_kernel(const float* __restrict__ ws, int splits, int rows, int cols, long long ldc,
+                                         const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out) {
+  const size_t n = (size_t)rows * cols;
+  const size_t i4 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i4 >= n) return;
+  float4 acc = *reinterpret_cast<const float4*>(ws + i4);
+  for (int s = 1; s < splits; ++s) {
+    const float4 v = *reinterpret_cast<const float4*>(ws + (size_t)s * n + i4);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  const int r = (int)(i4 / cols);
+  const int c = (int)(i4 - (size_t)r * cols);
+  float b[4] = {0.f, 0.f, 0.f, 0.f};
+  if (bias) for (int i = 0; i < 4; ++i) b[i] = __bfloat162float(bias[c + i]);
+  uint2 o;
+  o.x = pack_bf16x2(acc.x + b[0], acc.y + b[1]);
+  o.y = pack_bf16x2(acc.z + b[2], acc.w + b[3]);
+  *reinterpret_cast<uint2*>(out + (size_t)r * ldc + c) = o;
 }
 
 // x bf16 [T][K] -> e4m3 [T][K] and scales [T][K/128] (amax / 448 per 128 values). One warp per group.
@@ -266,7 +306,8 @@ static void launch_fp8(const CUtensorMap& ta, const CUtensorMap& tb, const Fp8Ge
 
 // y[T][N] = dequant(xq, sx) * dequant(wq, sw)^T (+ bias)
 int linear_fp8_block(const void* xq, const float* sx, const void* wq, const float* sw, const void* bias, void* y,
-                     long long ldy, int T, int N, int K, int* status, cudaStream_t stream) {
+                     long long ldy, int T, int N, int K, int* status, cudaStream_t stream, void* workspace,
+                     size_t workspace_bytes) {
   if (T <= 0 || N <= 0) return 0;
   if (K % 128 || N % 128) throw std::runtime_error("linear_fp8_block: N and K must be multiples of 128");
   if (K / 128 > 64 * 4) throw std::runtime_error("linear_fp8_block: K above 32768 is not supported");
@@ -274,7 +315,7 @@ int linear_fp8_block(const void* xq, const float* sx, const void* wq, const floa
   a.K = K; a.k_blocks = K / 128;
   a.out = reinterpret_cast<__nv_bfloat16*>(y); a.ldc = ldy;
   a.sx = sx; a.sw = sw; a.bias = reinterpret_cast<const __nv_bfloat16*>(bias); a.status = status;
-  const bool swap = T <= 64 && a.k_blocks <= 64;      // the tile's token scales must fit shared memory
+  const bool swap = T <= 64;                          // decode: features fill the 128-row MMA dimension
   int bn;
   CUtensorMap ta, tb;
   if (swap) {
@@ -290,12 +331,31 @@ int linear_fp8_block(const void* xq, const float* sx, const void* wq, const floa
   }
   a.m_tiles = (a.M + F8_BM - 1) / F8_BM;
   a.n_tiles = (a.N + bn - 1) / bn;
-  const int grid = std::min(a.m_tiles * a.n_tiles, sm_count() * (bn <= 64 ? 2 : 1));
+  // Few tiles cannot pull the whole HBM bandwidth: split K until the machine is full. A split's token scales must
+  // also fit their shared-memory block (64 K blocks).
+  const int slots = sm_count() * (bn <= 64 ? 2 : 1);
+  const int tiles = a.m_tiles * a.n_tiles;
+  int splits = 1;
+  if (tiles * 2 <= slots && a.k_blocks >= 8) splits = std::min(std::min(slots / tiles, a.k_blocks / 4), 16);
+  splits = std::max(splits, (a.k_blocks + 63) / 64);
+  while (splits > (a.k_blocks + 63) / 64 && (!workspace || (size_t)splits * T * N * 4 > workspace_bytes || (N & 3))) --splits;
+  if (splits > 1 && (!workspace || (size_t)splits * T * N * 4 > workspace_bytes || (N & 3)))
+    throw std::runtime_error("linear_fp8_block: K above 8192 needs a split-K workspace");
+  a.kb_per_split = (a.k_blocks + splits - 1) / splits;
+  a.k_splits = (a.k_blocks + a.kb_per_split - 1) / a.kb_per_split;
+  a.ws = reinterpret_cast<float*>(workspace);
+  const int grid = std::min(tiles * a.k_splits, slots);
   switch (bn) {
     case 16: launch_fp8<16>(ta, tb, a, grid, stream); break;
     case 32: launch_fp8<32>(ta, tb, a, grid, stream); break;
     case 64: launch_fp8<64>(ta, tb, a, grid, stream); break;
     default: launch_fp8<128>(ta, tb, a, grid, stream); break;
+  }
+  if (a.k_splits > 1) {
+    const size_t n = (size_t)T * N;
+    fp8_splitk_reduce_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, stream>>>(a.ws, a.k_splits, T, N, ldy, a.bias, a.out);
+    cuda_check(cudaGetLastError(), "fp8_splitk_reduce_kernel");
+    return 2;
   }
   return 1;
 }

@@ -272,8 +272,7 @@ class Fp8BlockWeight:
         sx = torch.empty(T, K // 128, dtype=torch.float32, device=x.device)
         ops.k.quant_fp8_1x128(x.contiguous(), xq, sx)
         y = out if out is not None else torch.empty(T, self.shape[0], dtype=torch.bfloat16, device=x.device)
-        ops.k.linear_fp8_block(xq, sx, self.wq, self.sw, bias, y, ops.status)
-        ops.launches += 2
+        ops.launches += 1 + ops.k.linear_fp8_block(xq, sx, self.wq, self.sw, bias, y, ops.status, ops.workspace)
         return y
 
 

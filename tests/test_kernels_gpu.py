@@ -429,7 +429,7 @@ def test_moe_native_matches_reference(ops, T, E, k, H, I, act, lo_frac):
 
 
 @pytest.mark.parametrize("T", [1, 16, 33, 64, 100, 300, 2048])
-@pytest.mark.parametrize("N,K", [(256, 256), (1024, 4096), (3584, 8192)])
+@pytest.mark.parametrize("N,K", [(256, 256), (1024, 4096), (3584, 8192), (1280, 12288)])
 def test_linear_fp8_block(ops, T, N, K):
     """Block-scaled e4m3 GEMM against fp32 math on the de-quantised operands (so only the
     accumulation order and the bf16 output rounding differ), and against the unquantised product
@@ -438,7 +438,8 @@ def test_linear_fp8_block(ops, T, N, K):
     x = _rand((T, K), 1)
     w = _rand((N, K), 2, 0.05)
     wq, sw = quantize_weight_fp8_block(w)
-    lin = Fp8BlockLinear(ops, wq, sw)
+    bias = _rand((N,), 3) if T % 2 == 0 else None          # split-K adds it in the reduction, the single pass in the epilogue
+    lin = Fp8BlockLinear(ops, wq, sw, bias)
     y = lin(x)
     # oracle on the same quantised values
     xq = torch.empty(T, K, dtype=torch.uint8, device="cuda")
@@ -446,9 +447,10 @@ def test_linear_fp8_block(ops, T, N, K):
     ops.k.quant_fp8_1x128(x, xq, sx)
     xd = xq.view(torch.float8_e4m3fn).float().view(T, K // 128, 128) * sx[:, :, None]
     wd = wq.view(torch.float8_e4m3fn).float().view(N // 128, 128, K // 128, 128) * sw[:, None, :, None]
-    ref = xd.view(T, K) @ wd.view(N, K).t()
+    badd = bias.float() if bias is not None else 0
+    ref = xd.view(T, K) @ wd.view(N, K).t() + badd
     _close(y, ref, 1e-2)
-    _close(y, x.float() @ w.float().t(), 8e-2)
+    _close(y, x.float() @ w.float().t() + badd, 8e-2)
     # the activation quantiser itself: amax / 448 scales, values within one e4m3 step
     amax = x.float().view(T, K // 128, 128).abs().amax(-1).clamp_min(1e-10)
     assert torch.allclose(sx, amax / 448.0, rtol=1e-6)
