@@ -32,7 +32,7 @@ def _add_engine_flags(p: argparse.ArgumentParser) -> None:
     p.add_argument("--kv-tier-host-gb", type=float, default=0.0, help="host memory for evicted prefix-cache blocks")
     p.add_argument("--kv-tier-disk-dir", default=None, help="directory for blocks that fall out of the host tier (default $FLLM_KV_DISK_DIR)")
     p.add_argument("--kv-tier-disk-gb", type=float, default=0.0)
-    p.add_argument("--speculative", default="off", choices=["off", "ngram", "draft"])
+    p.add_argument("--speculative", default="off", choices=["off", "ngram", "suffix", "draft"])
     p.add_argument("--draft-model", default=None)
     p.add_argument("--draft-tokens", type=int, default=4)
     p.add_argument("-tp", "--tensor-parallel", dest="tp", type=int, default=1)

@@ -325,7 +325,7 @@ class EngineConfig:
     graph_buckets: Sequence[int] = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
     async_scheduling: bool = True
     multi_step: int = 1
-    speculative: str = "off"             # off | draft | ngram
+    speculative: str = "off"             # off | draft | ngram | suffix
     draft_tokens: int = 4
     seed: int = 0
     step_deadline_s: float = 120.0       # watchdog: a step slower than this fails the batch

@@ -109,6 +109,10 @@ class LLMEngine:
             from .speculative import AdaptiveDraft, NgramProposer
             self.proposer = NgramProposer(self.cfg.draft_tokens)
             self.adaptive = AdaptiveDraft(self.cfg.draft_tokens)
+        elif self.cfg.speculative == "suffix":
+            from .speculative import AdaptiveDraft, SuffixProposer
+            self.proposer = SuffixProposer(self.cfg.draft_tokens)
+            self.adaptive = AdaptiveDraft(self.cfg.draft_tokens)
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self._graph_pool = None
         self._inflight = None                # launch-ahead: the decode step whose ids are still on the device
@@ -757,6 +761,8 @@ class LLMEngine:
                 self.scheduler.finish(r, reason)
                 if hasattr(self.proposer, "forget"):
                     self.proposer.forget(r.seq_id)
+                if hasattr(self.proposer, "observe"):
+                    self.proposer.observe(r.prompt + r.output)       # the shared suffix index learns finished texts
                 self.requests.pop(r.request_id, None)
             if self.tp_rank == 0:
                 ev = TokenEvent(r.request_id, new, bool(reason), reason, embedding=getattr(r, "embedding", None))

@@ -3,6 +3,7 @@
 Sources of drafts (rust/engine/src/draft.rs:23-78, rust/engine/src/scheduler.rs:1163-1226):
 * ``NgramProposer``  prompt-lookup: find the latest earlier occurrence of the sequence's last
   n-gram in its own tokens and propose what followed it;
+* ``SuffixProposer``  the same lookup, then a shared index over everything the server generated before;
 * ``DraftModelProposer``  a small decoder that shares the target's block tables (its KV lives at
   the same slots of its own, thinner pool), catches up on the tokens it has not seen and then
   decodes ``k`` tokens greedily for the whole batch.
@@ -64,6 +65,42 @@ class NgramProposer:
                     follow = toks[start + n:start + n + k]
                     if follow:
                         return follow
+        return []
+
+
+class SuffixProposer:
+    """Drafts from what this server has generated before (rust/engine/src/draft.rs:365-446, the suffix source): a
+    bounded index from the last `n` tokens of any finished output (or prompt) to the tokens that followed them.
+    A lookup tries the sequence's own context first (the n-gram rule) and then the shared index, longest n first.
+    Repeated answers, boiler-plate and code completions accept long drafts across requests."""
+
+    def __init__(self, k: int = 4, max_n: int = 4, min_n: int = 2, capacity: int = 200_000):
+        self.k, self.max_n, self.min_n, self.capacity = k, max_n, min_n, capacity
+        self.own = NgramProposer(k, max_n=max_n, min_n=1)
+        self.index: "Dict[tuple, List[int]]" = {}
+        self.hits = self.lookups = 0
+
+    def observe(self, tokens: Sequence[int]) -> None:
+        """Index a finished sequence (prompt + output)."""
+        toks = [int(t) for t in tokens]
+        for n in range(self.min_n, self.max_n + 1):
+            for i in range(len(toks) - n):
+                if len(self.index) >= self.capacity:
+                    self.index.pop(next(iter(self.index)))          # oldest entry out
+                self.index[tuple(toks[i:i + n])] = toks[i + n:i + n + self.k]
+
+    def propose(self, tokens: Sequence[int], k: Optional[int] = None) -> List[int]:
+        k = k or self.k
+        self.lookups += 1
+        got = self.own.propose(tokens, k)
+        if got:
+            return got
+        toks = list(tokens[-self.max_n:])
+        for n in range(min(self.max_n, len(toks)), self.min_n - 1, -1):
+            nxt = self.index.get(tuple(toks[len(toks) - n:]))
+            if nxt:
+                self.hits += 1
+                return nxt[:k]
         return []
 
 

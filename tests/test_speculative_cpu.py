@@ -155,3 +155,24 @@ def test_tree_attention_reference_equals_chain_attention_on_each_path():
         s = torch.einsum("hd,hnd->hn", q[i].view(hq, D), k) * D ** -0.5
         want = torch.einsum("hn,hnd->hd", torch.softmax(s, -1), v).reshape(-1)
         assert (y[i] - want).abs().max().item() < 1e-4
+
+
+def test_suffix_proposer_drafts_from_earlier_requests():
+    from fllm_b200.runtime.speculative import SuffixProposer
+    p = SuffixProposer(k=4, max_n=3, min_n=2)
+    assert p.propose([1, 2, 3, 4]) == []
+    p.observe([9, 8, 7, 6, 5, 4, 3])
+    assert p.propose([100, 8, 7]) == [6, 5, 4, 3]            # a different request ends in a known 2-gram
+    assert p.propose([8, 7, 6, 50, 8, 7]) == [6, 50, 8, 7]   # its own context wins over the shared index
+    # through the engine: the second, identical request is drafted from the first one's text and keeps it
+    cfg = preset("qwen3-tiny")
+    w = init_random_weights(cfg, "cpu")
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, cfg.vocab_size, (17,), generator=g).tolist()
+    base = _eng(cfg, w).generate([prompt], SamplingParams(max_tokens=12))[0]
+    eng = _eng(cfg, w, speculative="suffix")
+    first = eng.generate([prompt], SamplingParams(max_tokens=12))[0]
+    steps0, acc0 = eng.stats.steps, eng.stats.spec_accepted
+    second = eng.generate([prompt], SamplingParams(max_tokens=12))[0]
+    assert first == base and second == base
+    assert eng.stats.spec_accepted - acc0 >= 6 and eng.stats.steps - steps0 < steps0
