@@ -124,6 +124,83 @@ def _byte_bpe(parts: List[bytes], ranks: Dict[bytes, int]) -> List[bytes]:
     return parts
 
 
+def rwkv_unescape(text: str) -> bytes:
+    """Bytes of one RWKV "world" vocabulary entry as llama.cpp files store it: the Python ``repr`` of the byte string
+    without its quotes (``\\x00``, ``\\n``, ``\\t``, ``\\r``, ``\\\\``, ``\\'``, ``\\"``; everything else stands for itself,
+    non-ASCII characters as their UTF-8 bytes)."""
+    out = bytearray()
+    i, n = 0, len(text)
+    simple = {"n": 10, "t": 9, "r": 13, "\\": 92, "'": 39, '"': 34, "a": 7, "b": 8, "f": 12, "v": 11, "0": 0}
+    while i < n:
+        ch = text[i]
+        if ch == "\\" and i + 1 < n:
+            nx = text[i + 1]
+            hx = text[i + 2:i + 4]
+            if nx == "x" and len(hx) == 2 and all(c in "0123456789abcdefABCDEF" for c in hx):
+                out.append(int(text[i + 2:i + 4], 16))
+                i += 4
+                continue
+            if nx in simple:
+                out.append(simple[nx])
+                i += 2
+                continue
+        out.extend(ch.encode("utf-8"))
+        i += 1
+    return bytes(out)
+
+
+class RwkvVocab:
+    """The RWKV "world" tokenizer (``tokenizer.ggml.model == "rwkv"``; rust/engine/src/tokenizer_rwkv.rs:1-5): the
+    vocabulary is a list of byte strings and a text is cut greedily into the longest entry at every byte position,
+    with no pre-tokenisation and no merges. The entries sit in a byte trie stored as flat arrays (first child per
+    byte through one dict per node would cost a Python object per node; here a node is a row of ``next`` keyed by
+    ``node * 256 + byte``), so a lookup is one dict probe per byte."""
+
+    def __init__(self, escaped: Sequence[str]):
+        self.entries: List[bytes] = [rwkv_unescape(t) for t in escaped]
+        self.next: Dict[int, int] = {}
+        self.terminal: List[int] = [-1]                   # node -> token id, -1 when no entry ends here
+        for tid, e in enumerate(self.entries):
+            if not e:
+                continue
+            node = 0
+            for b in e:
+                key = node * 256 + b
+                nx = self.next.get(key)
+                if nx is None:
+                    nx = len(self.terminal)
+                    self.next[key] = nx
+                    self.terminal.append(-1)
+                node = nx
+            if self.terminal[node] < 0:                   # the first of two equal entries keeps the id
+                self.terminal[node] = tid
+
+    def encode_bytes(self, data: bytes, unk: int = 0) -> List[int]:
+        ids: List[int] = []
+        i, n = 0, len(data)
+        nxt, term = self.next, self.terminal
+        while i < n:
+            node, best, best_end = 0, -1, i
+            j = i
+            while j < n:
+                node = nxt.get(node * 256 + data[j])
+                if node is None:
+                    break
+                j += 1
+                if term[node] >= 0:
+                    best, best_end = term[node], j
+            if best < 0:                                  # a byte with no entry: the world vocabulary has all 256
+                ids.append(unk)
+                i += 1
+            else:
+                ids.append(best)
+                i = best_end
+        return ids
+
+    def decode_bytes(self, ids: Sequence[int]) -> bytes:
+        return b"".join(self.entries[i] for i in ids if 0 <= i < len(self.entries))
+
+
 class GgufTokenizer:
     """Vocabulary embedded in a GGUF file (rust/engine/src/tokenizer.rs reads the same keys)."""
 
@@ -153,6 +230,9 @@ class GgufTokenizer:
         self.u2b = {v: k for k, v in self.b2u.items()}
         self.max_piece = max((len(t) for t in self.tokens), default=1)
         self._special_re = None
+        self.rwkv = RwkvVocab(self.tokens) if self.model == "rwkv" else None
+        if self.rwkv is not None:
+            self.special = {}                             # the world vocabulary has no control tokens inside text
 
     # ------------------------------------------------------------------ pieces
     def _bpe(self, word: List[str]) -> List[str]:
@@ -259,6 +339,8 @@ class GgufTokenizer:
     def _encode_plain(self, text: str) -> List[int]:
         if not text:
             return []
+        if self.rwkv is not None:
+            return self.rwkv.encode_bytes(text.encode("utf-8"), self.unk_token_id or 0)
         if self.model == "gpt2":
             import regex
             ids: List[int] = []
@@ -295,6 +377,8 @@ class GgufTokenizer:
     def decode(self, ids: Sequence[int], skip_special: bool = True) -> str:
         keep = [i for i in ids if 0 <= i < self.vocab_size and
                 not (skip_special and self.types is not None and self.types[i] == 3)]
+        if self.rwkv is not None:
+            return self.rwkv.decode_bytes(keep).decode("utf-8", errors="replace")
         if self.model == "gpt2":
             raw = "".join(self.tokens[i] for i in keep)
             return bytes(self.u2b.get(ch, 32) for ch in raw).decode("utf-8", errors="replace")

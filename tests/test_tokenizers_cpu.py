@@ -72,3 +72,25 @@ def test_tiktoken_rank_file(tmp_path):
     enc = tiktoken.Encoding("t", pat_str=tk.pattern, mergeable_ranks=tk.ranks, special_tokens=tk.special)
     for s in ("hello world hello", "say hello, world!", "héllo wörld"):
         assert tk.encode(s) == enc.encode(s)
+
+
+def test_rwkv_world_vocabulary_greedy_longest_match():
+    """Entries are Python byte reprs; encoding takes the longest entry at each byte position; every byte has an
+    entry, so any text round-trips (rust/engine/src/tokenizer_rwkv.rs:134-155 checks the same two properties)."""
+    from fllm_b200.tokenizer import GgufTokenizer, rwkv_unescape
+    assert rwkv_unescape(r"\x00") == b"\x00" and rwkv_unescape(r"\n") == b"\n" and rwkv_unescape(r"\\") == b"\\"
+    assert rwkv_unescape(r"\'") == b"'" and rwkv_unescape(r"\xc3\xbc") == "ü".encode() and rwkv_unescape("a b") == b"a b"
+
+    def esc(b: bytes) -> str:
+        return repr(b)[2:-1]
+    single = [bytes([i]) for i in range(256)]
+    words = [b"he", b"hello", b"hell", b" world", b" wor", "ü".encode(), "üb".encode(), b"\n\n", b"it's"]
+    tokens = ["<eot>"] + [esc(b) for b in single] + [esc(w) for w in words]
+    tok = GgufTokenizer({"tokenizer.ggml.model": "rwkv", "tokenizer.ggml.tokens": tokens})
+    ids = tok.encode("hello world")
+    assert ids == [1 + 256 + 1, 1 + 256 + 3]
+    assert tok.encode("hellx") == [1 + 256 + 2, 1 + ord("x")]
+    assert tok.encode("über") == [1 + 256 + 6, 1 + ord("e"), 1 + ord("r")]
+    assert tok.encode("it's\n\n") == [1 + 256 + 8, 1 + 256 + 7]
+    for text in ["hello world", "über\n\nhell", "日本語 ok", "it's \\ fine"]:
+        assert tok.decode(tok.encode(text)) == text
