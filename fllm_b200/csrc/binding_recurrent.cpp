@@ -1,0 +1,122 @@
+// torch.ops.fllm_b200 bindings of the recurrent token mixers (recurrent.cu).
+#include <ATen/ATen.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/library.h>
+
+#include "fllm_ops.h"
+
+namespace {
+using at::Tensor;
+using c10::optional;
+inline cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+inline bool rows_bf16(const Tensor& t) { return t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && t.stride(1) == 1; }
+inline const void* opt_ptr(const optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+inline const float* opt_f32(const optional<Tensor>& t) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->scalar_type() == at::kFloat && t->is_contiguous(), "parameter vectors are contiguous fp32");
+  return t->data_ptr<float>();
+}
+inline long long opt_ld(const optional<Tensor>& t) { return t.has_value() && t->defined() ? t->stride(0) : 0; }
+inline void check_batch(const Tensor& q_starts, const Tensor& seq_state, const Tensor& positions) {
+  TORCH_CHECK(q_starts.scalar_type() == at::kInt && seq_state.scalar_type() == at::kInt && positions.scalar_type() == at::kInt &&
+                  q_starts.is_contiguous() && seq_state.is_contiguous() && positions.is_contiguous() &&
+                  q_starts.numel() == seq_state.numel() + 1,
+              "q_starts [B + 1], seq_state [B], positions [T]: contiguous int32");
+}
+
+void causal_conv1d(const Tensor& x, const Tensor& w, const optional<Tensor>& bias, Tensor state, const Tensor& q_starts,
+                   const Tensor& seq_state, const Tensor& positions, Tensor y, bool act) {
+  TORCH_CHECK(rows_bf16(x) && rows_bf16(y) && x.sizes() == y.sizes(), "x, y: bf16 rows of one shape");
+  const int64_t C = x.size(1), W = w.size(1);
+  TORCH_CHECK(w.scalar_type() == at::kFloat && w.is_contiguous() && w.dim() == 2 && w.size(0) == C, "w: fp32 [C, W]");
+  TORCH_CHECK(state.scalar_type() == at::kBFloat16 && state.is_contiguous() && state.dim() == 3 && state.size(1) == W - 1 && state.size(2) == C,
+              "state: bf16 [slots, W - 1, C]");
+  check_batch(q_starts, seq_state, positions);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rc = fllm::causal_conv1d(x.data_ptr(), x.stride(0), w.data_ptr<float>(), opt_f32(bias), state.data_ptr(), q_starts.data_ptr<int>(),
+                                     seq_state.data_ptr<int>(), positions.data_ptr<int>(), y.data_ptr(), y.stride(0), (int)seq_state.numel(),
+                                     (int)C, (int)W, act ? 1 : 0, cur_stream());
+  TORCH_CHECK(rc == 0, "causal_conv1d: unsupported arguments (code ", rc, "): even C and strides, 2 <= W <= 4, y distinct from x");
+}
+
+void mamba2_scan(const Tensor& x, const Tensor& dt, const Tensor& Bm, const Tensor& Cm, const Tensor& A, const optional<Tensor>& D,
+                 const optional<Tensor>& dt_bias, Tensor state, const Tensor& q_starts, const Tensor& seq_state, const Tensor& positions,
+                 Tensor y, int64_t H, int64_t P, int64_t G, int64_t N, double dt_min, double dt_max) {
+  TORCH_CHECK(rows_bf16(x) && rows_bf16(dt) && rows_bf16(Bm) && rows_bf16(Cm) && rows_bf16(y), "activations: bf16 rows");
+  TORCH_CHECK(x.size(1) == H * P && y.size(1) == H * P && dt.size(1) == H && Bm.size(1) == G * N && Cm.size(1) == G * N, "widths");
+  TORCH_CHECK(state.scalar_type() == at::kFloat && state.is_contiguous() && state.dim() == 4 && state.size(1) == H && state.size(2) == P &&
+                  state.size(3) == N, "state: fp32 [slots, H, P, N]");
+  check_batch(q_starts, seq_state, positions);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rc = fllm::mamba2_scan(x.data_ptr(), x.stride(0), dt.data_ptr(), dt.stride(0), Bm.data_ptr(), Bm.stride(0), Cm.data_ptr(),
+                                   Cm.stride(0), opt_f32(A), opt_f32(D), opt_f32(dt_bias), state.data_ptr<float>(), q_starts.data_ptr<int>(),
+                                   seq_state.data_ptr<int>(), positions.data_ptr<int>(), y.data_ptr(), y.stride(0), (int)seq_state.numel(),
+                                   (int)H, (int)P, (int)G, (int)N, (float)dt_min, (float)dt_max, cur_stream());
+  TORCH_CHECK(rc == 0, "mamba2_scan: unsupported arguments (code ", rc, "): state width 16 / 32 / 64 / 128 / 256, B and C 16-byte aligned");
+}
+
+void mamba1_scan(const Tensor& x, const Tensor& dt, const Tensor& Bm, const Tensor& Cm, const optional<Tensor>& z, const Tensor& A,
+                 const optional<Tensor>& D, const optional<Tensor>& dt_bias, Tensor state, const Tensor& q_starts, const Tensor& seq_state,
+                 const Tensor& positions, Tensor y) {
+  TORCH_CHECK(rows_bf16(x) && rows_bf16(dt) && rows_bf16(Bm) && rows_bf16(Cm) && rows_bf16(y), "activations: bf16 rows");
+  const int64_t Dm = x.size(1), N = Bm.size(1);
+  TORCH_CHECK(A.scalar_type() == at::kFloat && A.is_contiguous() && A.dim() == 2 && A.size(0) == Dm && A.size(1) == N, "A: fp32 [D, N]");
+  TORCH_CHECK(state.scalar_type() == at::kFloat && state.is_contiguous() && state.dim() == 3 && state.size(1) == Dm && state.size(2) == N,
+              "state: fp32 [slots, D, N]");
+  check_batch(q_starts, seq_state, positions);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rc = fllm::mamba1_scan(x.data_ptr(), x.stride(0), dt.data_ptr(), dt.stride(0), Bm.data_ptr(), Bm.stride(0), Cm.data_ptr(),
+                                   Cm.stride(0), opt_ptr(z), opt_ld(z), A.data_ptr<float>(), opt_f32(D), opt_f32(dt_bias),
+                                   state.data_ptr<float>(), q_starts.data_ptr<int>(), seq_state.data_ptr<int>(), positions.data_ptr<int>(),
+                                   y.data_ptr(), y.stride(0), (int)seq_state.numel(), (int)Dm, (int)N, cur_stream());
+  TORCH_CHECK(rc == 0, "mamba1_scan: unsupported arguments (code ", rc, "): state width 8 / 16, B and C 16-byte aligned");
+}
+
+void matrix_state_scan(int64_t kind, const Tensor& r, const Tensor& k, const Tensor& v, const optional<Tensor>& a, const optional<Tensor>& b,
+                       const Tensor& w, const optional<Tensor>& u, const optional<Tensor>& beta, Tensor state, const Tensor& q_starts,
+                       const Tensor& seq_state, const Tensor& positions, Tensor y, int64_t H, int64_t DK, int64_t DV, int64_t kv_ratio,
+                       bool l2norm, double q_scale) {
+  TORCH_CHECK(rows_bf16(r) && rows_bf16(k) && rows_bf16(v) && rows_bf16(y), "activations: bf16 rows");
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kFloat && w.dim() == 2 && w.stride(1) == 1, "w: fp32 rows of log decays");
+  TORCH_CHECK(v.size(1) == H * DV && y.size(1) == H * DV && r.size(1) == (H / kv_ratio) * DK && k.size(1) == r.size(1), "widths");
+  TORCH_CHECK(w.size(1) == (kind == 2 ? H : r.size(1)), "w: one decay per head (kind 2) or per key channel");
+  TORCH_CHECK(kind != 1 || (a.has_value() && b.has_value() && rows_bf16(*a) && rows_bf16(*b)), "RWKV-7 needs a and b");
+  TORCH_CHECK(kind != 0 || (u.has_value() && u->numel() == r.size(1)), "RWKV-6 needs the bonus u");
+  TORCH_CHECK(kind < 2 || (beta.has_value() && rows_bf16(*beta) && beta->size(1) == H), "delta rules need beta [T, H]");
+  TORCH_CHECK(state.scalar_type() == at::kFloat && state.is_contiguous() && state.dim() == 4 && state.size(1) == H && state.size(2) == DV &&
+                  state.size(3) == DK, "state: fp32 [slots, H, DV, DK]");
+  check_batch(q_starts, seq_state, positions);
+  c10::cuda::CUDAGuard guard(r.device());
+  const int rc = fllm::matrix_state_scan((int)kind, r.data_ptr(), r.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), opt_ptr(a),
+                                         opt_ld(a), opt_ptr(b), opt_ld(b), w.data_ptr<float>(), w.stride(0), opt_f32(u), opt_ptr(beta),
+                                         opt_ld(beta), state.data_ptr<float>(), q_starts.data_ptr<int>(), seq_state.data_ptr<int>(),
+                                         positions.data_ptr<int>(), y.data_ptr(), y.stride(0), (int)seq_state.numel(), (int)H, (int)DK, (int)DV,
+                                         (int)kv_ratio, l2norm ? 1 : 0, (float)q_scale, cur_stream());
+  TORCH_CHECK(rc == 0, "matrix_state_scan: unsupported arguments (code ", rc, "): key width 32 / 64 / 128 / 256, 16-byte aligned rows");
+}
+
+void gated_rmsnorm(const Tensor& x, const optional<Tensor>& z, const Tensor& w, Tensor y, int64_t group_size, double eps, bool norm_before_gate) {
+  TORCH_CHECK(rows_bf16(x) && rows_bf16(y) && x.sizes() == y.sizes(), "x, y: bf16 rows of one shape");
+  TORCH_CHECK(w.scalar_type() == at::kBFloat16 && w.is_contiguous() && x.size(1) % group_size == 0, "w: bf16; D a multiple of the group");
+  TORCH_CHECK(!z.has_value() || !z->defined() || (rows_bf16(*z) && z->sizes() == x.sizes()), "z: bf16 rows like x");
+  c10::cuda::CUDAGuard guard(x.device());
+  fllm::gated_rmsnorm(x.data_ptr(), x.stride(0), opt_ptr(z), opt_ld(z), w.data_ptr(), (int)w.numel(), y.data_ptr(), y.stride(0), (int)x.size(0),
+                      (int)x.size(1), (int)group_size, (float)eps, norm_before_gate ? 1 : 0, cur_stream());
+}
+}  // namespace
+
+TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
+  m.def("causal_conv1d(Tensor x, Tensor w, Tensor? bias, Tensor(a!) state, Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y, bool act) -> ()",
+        &causal_conv1d);
+  m.def("mamba2_scan(Tensor x, Tensor dt, Tensor Bm, Tensor Cm, Tensor A, Tensor? D, Tensor? dt_bias, Tensor(a!) state, Tensor q_starts, "
+        "Tensor seq_state, Tensor positions, Tensor(b!) y, int H, int P, int G, int N, float dt_min, float dt_max) -> ()",
+        &mamba2_scan);
+  m.def("mamba1_scan(Tensor x, Tensor dt, Tensor Bm, Tensor Cm, Tensor? z, Tensor A, Tensor? D, Tensor? dt_bias, Tensor(a!) state, "
+        "Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y) -> ()",
+        &mamba1_scan);
+  m.def("matrix_state_scan(int kind, Tensor r, Tensor k, Tensor v, Tensor? a, Tensor? b, Tensor w, Tensor? u, Tensor? beta, Tensor(a!) state, "
+        "Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y, int H, int DK, int DV, int kv_ratio, bool l2norm, float q_scale) -> ()",
+        &matrix_state_scan);
+  m.def("gated_rmsnorm(Tensor x, Tensor? z, Tensor w, Tensor(a!) y, int group_size, float eps, bool norm_before_gate) -> ()", &gated_rmsnorm);
+}

@@ -266,4 +266,29 @@ void spec_verify_sampled(const void* target_logits, long long ld_t, const void* 
                          int k, const int* row_start, const int* n_draft, const SampleRow* prm,
                          int* n_accept, int* out_tokens, cudaStream_t s);
 
+// ---- recurrent token mixers on ragged batches (recurrent.cu) -------------------------------------------------------
+// q_starts [B + 1] first token row per sequence, seq_state [B] row of the state pool, positions [T]: a sequence whose
+// first token of the step is at position 0 starts from zeros. Activations bf16 with leading dimensions in elements;
+// scan states fp32, convolution windows bf16 [slots][W - 1][C]. A negative return value means an argument was rejected
+// before anything was launched.
+int causal_conv1d(const void* x, long long ldx, const float* w, const float* bias, void* state, const int* q_starts,
+                  const int* seq_state, const int* positions, void* y, long long ldy, int B, int C, int W, int act,
+                  cudaStream_t stream);
+int mamba2_scan(const void* x, long long ldx, const void* dt, long long lddt, const void* Bm, long long ldb, const void* Cm,
+                long long ldc, const float* A, const float* D, const float* dt_bias, float* state, const int* q_starts,
+                const int* seq_state, const int* positions, void* y, long long ldy, int B, int H, int P, int G, int N,
+                float dt_min, float dt_max, cudaStream_t stream);
+int mamba1_scan(const void* x, long long ldx, const void* dt, long long lddt, const void* Bm, long long ldb, const void* Cm,
+                long long ldc, const void* z, long long ldz, const float* A, const float* D, const float* dt_bias, float* state,
+                const int* q_starts, const int* seq_state, const int* positions, void* y, long long ldy, int B, int Dm, int N,
+                cudaStream_t stream);
+// kind: 0 RWKV-6, 1 RWKV-7, 2 gated delta rule (one decay per head), 3 delta rule with a decay per key channel
+int matrix_state_scan(int kind, const void* r, long long ldr, const void* k, long long ldk, const void* v, long long ldv,
+                      const void* a, long long lda, const void* b, long long ldb, const float* w, long long ldw, const float* u,
+                      const void* beta, long long ldbeta, float* state, const int* q_starts, const int* seq_state,
+                      const int* positions, void* y, long long ldy, int B, int H, int DK, int DV, int kv_ratio, int l2norm,
+                      float q_scale, cudaStream_t stream);
+void gated_rmsnorm(const void* x, long long ldx, const void* z, long long ldz, const void* w, int wlen, void* y, long long ldy, int T,
+                   int D, int group_size, float eps, int norm_before_gate, cudaStream_t stream);
+
 }  // namespace fllm

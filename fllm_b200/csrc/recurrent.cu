@@ -1,0 +1,486 @@
+// Recurrent token mixers on ragged batches: depthwise causal convolution, the Mamba-1 and Mamba-2 selective scans,
+// and the matrix-state family (RWKV-6, RWKV-7, gated delta rule, Kimi delta attention) plus the gated RMSNorm that
+// follows a scan. The reference keeps one file per family (rust/engine/cuda/mamba1.cu, mamba2.cu, rwkv.cu,
+// deltanet.cu, kda.cu, shortconv.cu) and a chunk-parallel scan (scan.cu); here every family walks its tokens with the
+// state held in registers, one CTA per (sequence, head, slice of state rows): a step touches each state element
+// once, so the work per token is the state size and the per-token inputs are prefetched one token ahead. With 148 SMs
+// the grid is sequences x heads x row tiles, which covers the machine from one 2048-token prefill chunk upwards.
+//
+// Batch layout (shared by every kernel): q_starts[B + 1] = first token row of each sequence, seq_state[B] = row of the
+// state pool that belongs to the sequence, positions[T]: a sequence whose first token of the step sits at position 0
+// starts from a zero state. States live in fp32 (convolution windows in bf16: they are copies of bf16 inputs).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "fllm_ops.h"
+
+namespace fllm {
+namespace {
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+
+// n consecutive bf16 values (n a multiple of 8, 16-byte aligned) widened into fp32 registers
+template <int N>
+__device__ __forceinline__ void load_bf16(const bf16* __restrict__ p, float (&out)[N]) {
+  static_assert(N % 8 == 0, "slices are whole 16-byte words");
+#pragma unroll
+  for (int i = 0; i < N / 8; ++i) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p + 8 * i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      out[8 * i + 2 * j] = f.x;
+      out[8 * i + 2 * j + 1] = f.y;
+    }
+  }
+}
+template <int N>
+__device__ __forceinline__ void load_f32(const float* __restrict__ p, float (&out)[N]) {
+#pragma unroll
+  for (int i = 0; i < N / 4; ++i) {
+    const float4 v = *reinterpret_cast<const float4*>(p + 4 * i);
+    out[4 * i] = v.x, out[4 * i + 1] = v.y, out[4 * i + 2] = v.z, out[4 * i + 3] = v.w;
+  }
+}
+template <int N>
+__device__ __forceinline__ void store_f32(float* __restrict__ p, const float (&v)[N]) {
+#pragma unroll
+  for (int i = 0; i < N / 4; ++i)
+    *reinterpret_cast<float4*>(p + 4 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+}
+// sum over the LANES consecutive lanes that share one state row (LANES a power of two up to 32)
+template <int LANES>
+__device__ __forceinline__ float row_sum(float v) {
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ------------------------------------------------------------------------------------------ causal conv1d
+// One CTA per (128 channels, sequence): the tokens of the sequence are spread over threadIdx.y, every thread owns two
+// neighbouring channels. Only this CTA reads the sequence's window for its channels, so after a barrier it moves the
+// window forward in place.
+template <int W>
+__global__ void __launch_bounds__(256) conv1d_kernel(const bf16* __restrict__ x, long long ldx, const float* __restrict__ w,
+                                                     const float* __restrict__ bias, bf16* __restrict__ state,
+                                                     const int* __restrict__ q_starts, const int* __restrict__ seq_state,
+                                                     const int* __restrict__ positions, bf16* __restrict__ y, long long ldy,
+                                                     int C, int act) {
+  const int s = blockIdx.y;
+  const int c = (blockIdx.x * 64 + threadIdx.x) * 2;
+  const int t0 = q_starts[s], n = q_starts[s + 1] - t0;
+  if (n <= 0) return;
+  const bool active = c < C;
+  const bool fresh = positions[t0] == 0;
+  bf16* st = state + (long long)seq_state[s] * (W - 1) * C;
+  float wv[2][W], hist[2][W - 1], bv[2] = {0.f, 0.f};
+  if (active) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) wv[0][j] = w[(long long)c * W + j], wv[1][j] = w[(long long)(c + 1) * W + j];
+    if (bias != nullptr) bv[0] = bias[c], bv[1] = bias[c + 1];
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j) {
+      float2 h = make_float2(0.f, 0.f);
+      if (!fresh) h = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(st + (long long)j * C + c));
+      hist[0][j] = h.x, hist[1][j] = h.y;
+    }
+    for (int p = threadIdx.y; p < n; p += blockDim.y) {
+      float a0 = bv[0], a1 = bv[1];
+#pragma unroll
+      for (int j = 0; j < W; ++j) {
+        const int i = p - (W - 1) + j;
+        float2 v;
+        if (i >= 0) v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + (long long)(t0 + i) * ldx + c));
+        else v = make_float2(hist[0][(W - 1) + i], hist[1][(W - 1) + i]);
+        a0 = fmaf(wv[0][j], v.x, a0), a1 = fmaf(wv[1][j], v.y, a1);
+      }
+      if (act) a0 = silu_f(a0), a1 = silu_f(a1);
+      *reinterpret_cast<__nv_bfloat162*>(y + (long long)(t0 + p) * ldy + c) = __floats2bfloat162_rn(a0, a1);
+    }
+  }
+  __syncthreads();
+  if (active && threadIdx.y == 0) {
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j) {
+      const int i = n - (W - 1) + j;
+      __nv_bfloat162 v;
+      if (i >= 0) v = *reinterpret_cast<const __nv_bfloat162*>(x + (long long)(t0 + i) * ldx + c);
+      else v = __floats2bfloat162_rn(hist[0][(W - 1) + i], hist[1][(W - 1) + i]);
+      *reinterpret_cast<__nv_bfloat162*>(st + (long long)j * C + c) = v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------ Mamba-2 (SSD)
+// h[p][n] = exp(dt A) h[p][n] + dt x[p] B[n];  y[p] = sum_n h[p][n] C[n] + D x[p]      (one A, dt, D per head)
+struct Mamba2Args {
+  const bf16 *x, *dt, *Bm, *Cm;
+  long long ldx, lddt, ldb, ldc, ldy;
+  const float *A, *D, *dt_bias;
+  float* state;                 // [slots][H][P][N]
+  const int *q_starts, *seq_state, *positions;
+  bf16* y;
+  int H, P, G;
+  float dt_min, dt_max;
+};
+
+template <int N, int NPT>
+__global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Args a) {
+  constexpr int TPN = N / NPT, ROWS = 128 / TPN;
+  const int ptiles = (a.P + ROWS - 1) / ROWS;
+  const int h = blockIdx.x / ptiles, p = (blockIdx.x % ptiles) * ROWS + threadIdx.x / TPN;
+  const int ln = threadIdx.x % TPN, s = blockIdx.y;
+  const int t0 = a.q_starts[s], n = a.q_starts[s + 1] - t0;
+  if (n <= 0) return;
+  const bool valid = p < a.P;
+  const int pc = valid ? p : a.P - 1;                        // lanes of a ragged last tile repeat the last row, unstored
+  float* st = a.state + (((long long)a.seq_state[s] * a.H + h) * a.P + pc) * N + ln * NPT;
+  float hs[NPT];
+  if (a.positions[t0] == 0) {
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) hs[i] = 0.f;
+  } else {
+    load_f32<NPT>(st, hs);
+  }
+  const int g = h / (a.H / a.G);
+  const float A = a.A[h], D = a.D != nullptr ? a.D[h] : 0.f, dtb = a.dt_bias != nullptr ? a.dt_bias[h] : 0.f;
+  const bf16* xp = a.x + (long long)t0 * a.ldx + h * a.P + pc;
+  const bf16* dtp = a.dt + (long long)t0 * a.lddt + h;
+  const bf16* bp = a.Bm + (long long)t0 * a.ldb + g * N + ln * NPT;
+  const bf16* cp = a.Cm + (long long)t0 * a.ldc + g * N + ln * NPT;
+  bf16* yp = a.y + (long long)t0 * a.ldy + h * a.P + pc;
+  float Bn[NPT], Cn[NPT], xn = __bfloat162float(*xp), dtn = __bfloat162float(*dtp);
+  load_bf16<NPT>(bp, Bn);
+  load_bf16<NPT>(cp, Cn);
+  for (int t = 0; t < n; ++t) {
+    float Bc[NPT], Cc[NPT];
+    const float xv = xn;
+    float dt = softplus_f(dtn + dtb);
+    dt = fminf(fmaxf(dt, a.dt_min), a.dt_max);
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) Bc[i] = Bn[i], Cc[i] = Cn[i];
+    if (t + 1 < n) {                                          // next token's inputs travel while this one is applied
+      xp += a.ldx, dtp += a.lddt, bp += a.ldb, cp += a.ldc;
+      xn = __bfloat162float(*xp), dtn = __bfloat162float(*dtp);
+      load_bf16<NPT>(bp, Bn);
+      load_bf16<NPT>(cp, Cn);
+    }
+    const float dA = __expf(dt * A), dx = dt * xv;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      hs[i] = fmaf(hs[i], dA, dx * Bc[i]);
+      acc = fmaf(hs[i], Cc[i], acc);
+    }
+    acc = row_sum<TPN>(acc);
+    if (ln == 0 && valid) *yp = __float2bfloat16(fmaf(D, xv, acc));
+    yp += a.ldy;
+  }
+  if (valid) store_f32<NPT>(st, hs);
+}
+
+// ------------------------------------------------------------------------------------------ Mamba-1
+// h[d][n] = exp(dt[d] A[d][n]) h[d][n] + dt[d] B[n] x[d];  y[d] = (sum_n h[d][n] C[n] + D[d] x[d]) * silu(z[d])
+struct Mamba1Args {
+  const bf16 *x, *dt, *Bm, *Cm, *z;
+  long long ldx, lddt, ldb, ldc, ldz, ldy;
+  const float *A, *D, *dt_bias;   // A [Dm][N]
+  float* state;                   // [slots][Dm][N]
+  const int *q_starts, *seq_state, *positions;
+  bf16* y;
+  int Dm;
+};
+
+template <int N>
+__global__ void __launch_bounds__(128) mamba1_scan_kernel(const Mamba1Args a) {
+  const int d = blockIdx.x * 128 + threadIdx.x, s = blockIdx.y;
+  const int t0 = a.q_starts[s], n = a.q_starts[s + 1] - t0;
+  if (n <= 0 || d >= a.Dm) return;
+  float* st = a.state + ((long long)a.seq_state[s] * a.Dm + d) * N;
+  float hs[N], A[N];
+  load_f32<N>(a.A + (long long)d * N, A);
+  if (a.positions[t0] == 0) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) hs[i] = 0.f;
+  } else {
+    load_f32<N>(st, hs);
+  }
+  const float D = a.D != nullptr ? a.D[d] : 0.f, dtb = a.dt_bias != nullptr ? a.dt_bias[d] : 0.f;
+  for (int t = t0; t < t0 + n; ++t) {
+    float Bc[N], Cc[N];
+    load_bf16<N>(a.Bm + (long long)t * a.ldb, Bc);           // the same words for the whole warp: one broadcast fetch
+    load_bf16<N>(a.Cm + (long long)t * a.ldc, Cc);
+    const float xv = __bfloat162float(a.x[(long long)t * a.ldx + d]);
+    const float dt = softplus_f(__bfloat162float(a.dt[(long long)t * a.lddt + d]) + dtb);
+    const float dx = dt * xv;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      hs[i] = fmaf(hs[i], __expf(dt * A[i]), dx * Bc[i]);
+      acc = fmaf(hs[i], Cc[i], acc);
+    }
+    acc = fmaf(D, xv, acc);
+    if (a.z != nullptr) acc *= silu_f(__bfloat162float(a.z[(long long)t * a.ldz + d]));
+    a.y[(long long)t * a.ldy + d] = __float2bfloat16(acc);
+  }
+  store_f32<N>(st, hs);
+}
+
+// ------------------------------------------------------------------------------------------ matrix-state family
+// State S[v][k] per head, one thread row per v with DK / NPT lanes along k. d = exp(w) is the decay.
+//   kRwkv6      y = sum_k r (u k v + S);               S = S d + k v
+//   kRwkv7      sa = sum_k S a;  S = S d + sa b + v k;   y = sum_k S r
+//   kGatedDelta S = S d (one d per head);  m = sum_k S k;  S += k (v - m) beta;  y = sum_k S q
+//   kKda        as kGatedDelta with one d per key channel
+enum { kRwkv6 = 0, kRwkv7 = 1, kGatedDelta = 2, kKda = 3 };
+struct MatrixStateArgs {
+  const bf16 *r, *k, *v, *a, *b;     // r doubles as q; a, b only RWKV-7
+  const float* w;                    // log decay: [T][H*DK] (per channel) or [T][H] (kGatedDelta)
+  const float* u;                    // RWKV-6 bonus [H*DK]
+  const bf16* beta;                  // [T][H] delta-rule step size (already through its sigmoid)
+  long long ldr, ldk, ldv, lda, ldb, ldw, ldbeta, ldy;
+  float* state;                      // [slots][H][DV][DK]
+  const int *q_starts, *seq_state, *positions;
+  bf16* y;
+  int H, DV, kv_ratio;               // value heads per key head (q, k, w of head h come from head h / kv_ratio)
+  int l2norm;                        // delta kinds: normalise q and k over DK inside the kernel
+  float q_scale;
+};
+
+template <int KIND, int DK>
+__global__ void __launch_bounds__(128) matrix_state_kernel(const MatrixStateArgs a) {
+  constexpr int NPT = 16, TPK = DK / NPT, ROWS = 128 / TPK;
+  const int vtiles = (a.DV + ROWS - 1) / ROWS;
+  const int h = blockIdx.x / vtiles, v = (blockIdx.x % vtiles) * ROWS + threadIdx.x / TPK;
+  const int lk = threadIdx.x % TPK, s = blockIdx.y;
+  const int t0 = a.q_starts[s], n = a.q_starts[s + 1] - t0;
+  if (n <= 0) return;
+  const bool valid = v < a.DV;
+  const int vc = valid ? v : a.DV - 1;
+  const int hk = h / a.kv_ratio;
+  float* st = a.state + (((long long)a.seq_state[s] * a.H + h) * a.DV + vc) * DK + lk * NPT;
+  float S[NPT];
+  if (a.positions[t0] == 0) {
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) S[i] = 0.f;
+  } else {
+    load_f32<NPT>(st, S);
+  }
+  float u[NPT];
+  if (KIND == kRwkv6) load_f32<NPT>(a.u + (long long)hk * DK + lk * NPT, u);
+  const long long ko = (long long)hk * DK + lk * NPT;
+  for (int t = t0; t < t0 + n; ++t) {
+    float r[NPT], k[NPT], d[NPT];
+    load_bf16<NPT>(a.r + t * a.ldr + ko, r);
+    load_bf16<NPT>(a.k + t * a.ldk + ko, k);
+    const float vv = __bfloat162float(a.v[t * a.ldv + (long long)h * a.DV + vc]);
+    if (KIND == kGatedDelta) {
+      const float dh = __expf(a.w[t * a.ldw + h]);
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) d[i] = dh;
+    } else {
+      load_f32<NPT>(a.w + t * a.ldw + ko, d);
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) d[i] = __expf(d[i]);
+    }
+    float out = 0.f;
+    if (KIND == kRwkv6) {
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        const float kv = k[i] * vv;
+        out = fmaf(r[i], fmaf(u[i], kv, S[i]), out);
+        S[i] = fmaf(S[i], d[i], kv);
+      }
+      out = row_sum<TPK>(out);
+    } else if (KIND == kRwkv7) {
+      float av[NPT], bv[NPT], sa = 0.f;
+      load_bf16<NPT>(a.a + t * a.lda + ko, av);
+      load_bf16<NPT>(a.b + t * a.ldb + ko, bv);
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) sa = fmaf(S[i], av[i], sa);
+      sa = row_sum<TPK>(sa);
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        S[i] = fmaf(S[i], d[i], fmaf(sa, bv[i], vv * k[i]));
+        out = fmaf(S[i], r[i], out);
+      }
+      out = row_sum<TPK>(out);
+    } else {
+      float qs = a.q_scale;
+      if (a.l2norm) {
+        float qq = 0.f, kk = 0.f;
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) qq = fmaf(r[i], r[i], qq), kk = fmaf(k[i], k[i], kk);
+        qq = row_sum<TPK>(qq), kk = row_sum<TPK>(kk);
+        qs *= rsqrtf(qq + 1e-6f);
+        const float ks = rsqrtf(kk + 1e-6f);
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) k[i] *= ks;
+      }
+      float m = 0.f;
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        S[i] *= d[i];
+        m = fmaf(S[i], k[i], m);
+      }
+      m = row_sum<TPK>(m);
+      const float delta = (vv - m) * __bfloat162float(a.beta[t * a.ldbeta + h]);
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        S[i] = fmaf(k[i], delta, S[i]);
+        out = fmaf(S[i], r[i], out);
+      }
+      out = row_sum<TPK>(out) * qs;
+    }
+    if (lk == 0 && valid) a.y[t * a.ldy + (long long)h * a.DV + vc] = __float2bfloat16(out);
+  }
+  if (valid) store_f32<NPT>(st, S);
+}
+
+// ------------------------------------------------------------------------------------------ gated RMSNorm
+// Per (token, group of `gs` channels): mode 0  y = rmsnorm(x * silu(z)) * w   (Mamba-2: gate first)
+//                                      mode 1  y = rmsnorm(x) * w * silu(z)   (gated delta net: norm first)
+// w has `wlen` entries (D for Mamba-2, the head width when every head shares one weight). One warp per group.
+// y may be x (every element is read and then written by the same thread).
+__global__ void __launch_bounds__(128) gated_rmsnorm_kernel(const bf16* x, long long ldx, const bf16* __restrict__ z, long long ldz,
+                                                            const bf16* __restrict__ w, int wlen, bf16* y, long long ldy, int T, int D,
+                                                            int gs, float eps, int mode) {
+  const int groups = D / gs;
+  const long long item = (long long)blockIdx.x * 4 + threadIdx.x / 32;
+  if (item >= (long long)T * groups) return;
+  const int t = (int)(item / groups), g = (int)(item % groups), lane = threadIdx.x % 32;
+  const bf16* xr = x + t * ldx + (long long)g * gs;
+  const bf16* zr = z != nullptr ? z + t * ldz + (long long)g * gs : nullptr;
+  float ss = 0.f;
+  for (int i = lane; i < gs; i += 32) {
+    float v = __bfloat162float(xr[i]);
+    if (mode == 0 && zr != nullptr) v *= silu_f(__bfloat162float(zr[i]));
+    ss = fmaf(v, v, ss);
+  }
+  ss = row_sum<32>(ss);
+  const float inv = rsqrtf(ss / gs + eps);
+  bf16* yr = y + t * ldy + (long long)g * gs;
+  for (int i = lane; i < gs; i += 32) {
+    float v = __bfloat162float(xr[i]);
+    const float gate = zr != nullptr ? silu_f(__bfloat162float(zr[i])) : 1.f;
+    if (mode == 0) v *= gate;
+    v = v * inv * __bfloat162float(w[(g * gs + i) % wlen]);
+    if (mode == 1) v *= gate;
+    yr[i] = __float2bfloat16(v);
+  }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------- launchers
+// Every launcher returns 0 on success or a negative code naming the argument it rejected, before any launch.
+int causal_conv1d(const void* x, long long ldx, const float* w, const float* bias, void* state, const int* q_starts,
+                  const int* seq_state, const int* positions, void* y, long long ldy, int B, int C, int W, int act,
+                  cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (C % 2 || (ldx % 2) || (ldy % 2) || x == y) return -1;
+  if (W < 2 || W > 4) return -2;
+  const dim3 grid((C / 2 + 63) / 64, B), block(64, 4);
+  auto xs = static_cast<const bf16*>(x);
+  auto ys = static_cast<bf16*>(y);
+  auto ss = static_cast<bf16*>(state);
+  if (W == 2) conv1d_kernel<2><<<grid, block, 0, stream>>>(xs, ldx, w, bias, ss, q_starts, seq_state, positions, ys, ldy, C, act);
+  if (W == 3) conv1d_kernel<3><<<grid, block, 0, stream>>>(xs, ldx, w, bias, ss, q_starts, seq_state, positions, ys, ldy, C, act);
+  if (W == 4) conv1d_kernel<4><<<grid, block, 0, stream>>>(xs, ldx, w, bias, ss, q_starts, seq_state, positions, ys, ldy, C, act);
+  return 0;
+}
+
+int mamba2_scan(const void* x, long long ldx, const void* dt, long long lddt, const void* Bm, long long ldb, const void* Cm,
+                long long ldc, const float* A, const float* D, const float* dt_bias, float* state, const int* q_starts,
+                const int* seq_state, const int* positions, void* y, long long ldy, int B, int H, int P, int G, int N,
+                float dt_min, float dt_max, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (!aligned16(Bm) || !aligned16(Cm) || (ldb % 8) || (ldc % 8) || G <= 0 || H % G) return -1;
+  Mamba2Args a{static_cast<const bf16*>(x), static_cast<const bf16*>(dt), static_cast<const bf16*>(Bm), static_cast<const bf16*>(Cm),
+               ldx, lddt, ldb, ldc, ldy, A, D, dt_bias, state, q_starts, seq_state, positions, static_cast<bf16*>(y), H, P, G,
+               dt_min, dt_max};
+#define FLLM_M2(N_, NPT_)                                                                     \
+  {                                                                                           \
+    constexpr int rows = 128 / (N_ / NPT_);                                                   \
+    mamba2_scan_kernel<N_, NPT_><<<dim3(H * ((P + rows - 1) / rows), B), 128, 0, stream>>>(a); \
+    return 0;                                                                                 \
+  }
+  switch (N) {
+    case 16: FLLM_M2(16, 16)
+    case 32: FLLM_M2(32, 16)
+    case 64: FLLM_M2(64, 16)
+    case 128: FLLM_M2(128, 16)
+    case 256: FLLM_M2(256, 16)
+  }
+#undef FLLM_M2
+  return -2;
+}
+
+int mamba1_scan(const void* x, long long ldx, const void* dt, long long lddt, const void* Bm, long long ldb, const void* Cm,
+                long long ldc, const void* z, long long ldz, const float* A, const float* D, const float* dt_bias, float* state,
+                const int* q_starts, const int* seq_state, const int* positions, void* y, long long ldy, int B, int Dm, int N,
+                cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (!aligned16(Bm) || !aligned16(Cm) || (ldb % 8) || (ldc % 8)) return -1;
+  Mamba1Args a{static_cast<const bf16*>(x), static_cast<const bf16*>(dt), static_cast<const bf16*>(Bm), static_cast<const bf16*>(Cm),
+               static_cast<const bf16*>(z), ldx, lddt, ldb, ldc, ldz, ldy, A, D, dt_bias, state, q_starts, seq_state, positions,
+               static_cast<bf16*>(y), Dm};
+  const dim3 grid((Dm + 127) / 128, B);
+  if (N == 16) mamba1_scan_kernel<16><<<grid, 128, 0, stream>>>(a);
+  else if (N == 8) mamba1_scan_kernel<8><<<grid, 128, 0, stream>>>(a);
+  else return -2;
+  return 0;
+}
+
+int matrix_state_scan(int kind, const void* r, long long ldr, const void* k, long long ldk, const void* v, long long ldv,
+                      const void* a_, long long lda, const void* b_, long long ldb, const float* w, long long ldw, const float* u,
+                      const void* beta, long long ldbeta, float* state, const int* q_starts, const int* seq_state,
+                      const int* positions, void* y, long long ldy, int B, int H, int DK, int DV, int kv_ratio, int l2norm,
+                      float q_scale, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (!aligned16(r) || !aligned16(k) || (ldr % 8) || (ldk % 8) || kv_ratio <= 0 || H % kv_ratio) return -1;
+  if (kind != kGatedDelta && (!aligned16(w) || (ldw % 4))) return -1;
+  if (kind == kRwkv7 && (!aligned16(a_) || !aligned16(b_) || (lda % 8) || (ldb % 8))) return -1;
+  if (kind == kRwkv6 && !aligned16(u)) return -1;
+  MatrixStateArgs m{static_cast<const bf16*>(r), static_cast<const bf16*>(k), static_cast<const bf16*>(v), static_cast<const bf16*>(a_),
+                    static_cast<const bf16*>(b_), w, u, static_cast<const bf16*>(beta), ldr, ldk, ldv, lda, ldb, ldw, ldbeta, ldy, state,
+                    q_starts, seq_state, positions, static_cast<bf16*>(y), H, DV, kv_ratio, l2norm, q_scale};
+#define FLLM_MS(KIND_, DK_)                                                                        \
+  {                                                                                                \
+    constexpr int rows = 128 / (DK_ / 16);                                                         \
+    matrix_state_kernel<KIND_, DK_><<<dim3(H * ((DV + rows - 1) / rows), B), 128, 0, stream>>>(m); \
+    return 0;                                                                                      \
+  }
+#define FLLM_MS_DK(KIND_)           \
+  switch (DK) {                     \
+    case 32: FLLM_MS(KIND_, 32)     \
+    case 64: FLLM_MS(KIND_, 64)     \
+    case 128: FLLM_MS(KIND_, 128)   \
+    case 256: FLLM_MS(KIND_, 256)   \
+    default: return -2;             \
+  }
+  switch (kind) {
+    case kRwkv6: FLLM_MS_DK(kRwkv6)
+    case kRwkv7: FLLM_MS_DK(kRwkv7)
+    case kGatedDelta: FLLM_MS_DK(kGatedDelta)
+    case kKda: FLLM_MS_DK(kKda)
+  }
+#undef FLLM_MS_DK
+#undef FLLM_MS
+  return -3;
+}
+
+void gated_rmsnorm(const void* x, long long ldx, const void* z, long long ldz, const void* w, int wlen, void* y, long long ldy, int T,
+                   int D, int group_size, float eps, int norm_before_gate, cudaStream_t stream) {
+  if (T <= 0) return;
+  const long long items = (long long)T * (D / group_size);
+  gated_rmsnorm_kernel<<<(unsigned)((items + 3) / 4), 128, 0, stream>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(z), ldz,
+                                                                       static_cast<const bf16*>(w), wlen, static_cast<bf16*>(y), ldy, T, D,
+                                                                       group_size, eps, norm_before_gate);
+}
+
+}  // namespace fllm

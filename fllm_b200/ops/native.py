@@ -12,6 +12,7 @@ from typing import Optional
 import torch
 
 from ._lib import load_cuda
+from .recurrent import RecurrentNative
 
 
 class Deferred:
@@ -29,7 +30,7 @@ class Deferred:
         return (self.rows, self.cols)
 
 
-class NativeOps:
+class NativeOps(RecurrentNative):
     name = "sm100a"
 
     def __init__(self, device: torch.device, workspace_bytes: int = 96 << 20):

@@ -1,0 +1,183 @@
+"""Recurrent token mixers: the fp32 PyTorch statement of each op (``RecurrentRef``, mixed into the reference ops)
+and the wrappers of the sm_100a kernels (``RecurrentNative``, mixed into the native ops).
+
+Ops and their reference counterparts: depthwise causal convolution (rust/engine/cuda/shortconv.cu and the
+convolution halves of mamba1.cu / mamba2.cu / deltanet.cu), Mamba-1 and Mamba-2 selective scans
+(rust/engine/cuda/mamba1.cu, mamba2.cu), the matrix-state recurrences of RWKV-6 / RWKV-7 (rust/engine/cuda/rwkv.cu),
+the gated delta rule (deltanet.cu) and its per-channel-decay form (kda.cu), and the gated RMSNorm after a scan.
+
+Every op works on a ragged batch: ``q_starts`` [B + 1] (first token row of each sequence), ``seq_state`` [B] (row of
+the state pool) and ``positions`` [T]; a sequence whose first token of the step sits at position 0 starts from zeros.
+States are updated in place.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+RWKV6, RWKV7, GATED_DELTA, KDA = 0, 1, 2, 3
+
+
+def _seqs(q_starts, seq_state, positions):
+    qs = q_starts.tolist()
+    slots = seq_state.tolist()
+    for s in range(len(slots)):
+        t0, t1 = qs[s], qs[s + 1]
+        if t1 > t0:
+            yield t0, t1, slots[s], int(positions[t0]) == 0
+
+
+class RecurrentRef:
+    def causal_conv1d(self, x, w, bias, state, q_starts, seq_state, positions, act=True):
+        """y[t, c] = act(bias[c] + sum_j w[c, j] * x[t - (W - 1) + j, c]) inside each sequence; the W - 1 inputs before
+        the step come from ``state`` [slots, W - 1, C], which ends up holding the last W - 1 inputs."""
+        W = w.shape[1]
+        y = torch.empty_like(x)
+        for t0, t1, slot, fresh in _seqs(q_starts, seq_state, positions):
+            hist = torch.zeros(W - 1, x.shape[1], dtype=torch.float32, device=x.device) if fresh else state[slot].float()
+            full = torch.cat([hist, x[t0:t1].float()], 0)                      # [n + W - 1, C]
+            acc = torch.zeros(t1 - t0, x.shape[1], dtype=torch.float32, device=x.device)
+            for j in range(W):
+                acc += full[j:j + t1 - t0] * w[:, j].float()
+            if bias is not None:
+                acc += bias.float()
+            y[t0:t1] = (F.silu(acc) if act else acc).to(x.dtype)
+            state[slot] = full[-(W - 1):].to(state.dtype)
+        return y
+
+    def mamba2_scan(self, x, dt, Bm, Cm, A, D, dt_bias, state, q_starts, seq_state, positions, H, P, G, N,
+                    dt_min=0.0, dt_max=float("inf")):
+        """h = exp(dt A) h + dt x (x) B;  y = h C + D x per head; dt = clamp(softplus(dt + dt_bias))."""
+        y = torch.empty_like(x)
+        rep = H // G
+        for t0, t1, slot, fresh in _seqs(q_starts, seq_state, positions):
+            h = torch.zeros(H, P, N, dtype=torch.float32, device=x.device) if fresh else state[slot].clone()
+            for t in range(t0, t1):
+                d = F.softplus(dt[t].float() + (dt_bias if dt_bias is not None else 0.0)).clamp(dt_min, dt_max)      # [H]
+                xv = x[t].float().view(H, P)
+                Bv = Bm[t].float().view(G, N).repeat_interleave(rep, 0)
+                Cv = Cm[t].float().view(G, N).repeat_interleave(rep, 0)
+                h = h * torch.exp(d * A.float())[:, None, None] + (d[:, None] * xv)[:, :, None] * Bv[:, None, :]
+                out = (h * Cv[:, None, :]).sum(-1)
+                if D is not None:
+                    out = out + D.float()[:, None] * xv
+                y[t] = out.reshape(-1).to(x.dtype)
+            state[slot] = h
+        return y
+
+    def mamba1_scan(self, x, dt, Bm, Cm, z, A, D, dt_bias, state, q_starts, seq_state, positions):
+        """h[d, n] = exp(dt[d] A[d, n]) h + dt[d] B[n] x[d];  y = (h C + D x) * silu(z)."""
+        y = torch.empty_like(x)
+        for t0, t1, slot, fresh in _seqs(q_starts, seq_state, positions):
+            h = torch.zeros_like(state[slot]) if fresh else state[slot].clone()
+            for t in range(t0, t1):
+                d = F.softplus(dt[t].float() + (dt_bias if dt_bias is not None else 0.0))                          # [Dm]
+                xv = x[t].float()
+                h = h * torch.exp(d[:, None] * A.float()) + (d * xv)[:, None] * Bm[t].float()[None, :]
+                out = (h * Cm[t].float()[None, :]).sum(-1)
+                if D is not None:
+                    out = out + D.float() * xv
+                if z is not None:
+                    out = out * F.silu(z[t].float())
+                y[t] = out.to(x.dtype)
+            state[slot] = h
+        return y
+
+    def matrix_state_scan(self, kind, r, k, v, a, b, w, u, beta, state, q_starts, seq_state, positions, H, DK, DV,
+                          kv_ratio=1, l2norm=False, q_scale=1.0):
+        """State S[v, k] per head; ``w`` holds log decays (fp32). See the kinds at the top of the module:
+        RWKV-6  y = sum_k r (u k v + S), S = S d + k v;  RWKV-7  sa = S a, S = S d + sa b + v k, y = S r;
+        delta rules  S = S d, m = S k, S += (v - m) beta k, y = S q * q_scale (q, k L2-normalised when asked)."""
+        y = torch.empty(r.shape[0], H * DV, dtype=r.dtype, device=r.device)
+        for t0, t1, slot, fresh in _seqs(q_starts, seq_state, positions):
+            S = torch.zeros(H, DV, DK, dtype=torch.float32, device=r.device) if fresh else state[slot].clone()
+            for t in range(t0, t1):
+                rv = r[t].float().view(-1, DK).repeat_interleave(kv_ratio, 0)                                   # [H, DK]
+                kv = k[t].float().view(-1, DK).repeat_interleave(kv_ratio, 0)
+                vv = v[t].float().view(H, DV)
+                if kind == GATED_DELTA:
+                    d = torch.exp(w[t].float())[:, None].expand(H, DK)
+                else:
+                    d = torch.exp(w[t].float().view(-1, DK)).repeat_interleave(kv_ratio, 0)
+                if kind == RWKV6:
+                    uu = u.float().view(-1, DK).repeat_interleave(kv_ratio, 0)
+                    kvm = vv[:, :, None] * kv[:, None, :]
+                    out = ((uu[:, None, :] * kvm + S) * rv[:, None, :]).sum(-1)
+                    S = S * d[:, None, :] + kvm
+                elif kind == RWKV7:
+                    av = a[t].float().view(-1, DK).repeat_interleave(kv_ratio, 0)
+                    bv = b[t].float().view(-1, DK).repeat_interleave(kv_ratio, 0)
+                    sa = (S * av[:, None, :]).sum(-1)
+                    S = S * d[:, None, :] + sa[:, :, None] * bv[:, None, :] + vv[:, :, None] * kv[:, None, :]
+                    out = (S * rv[:, None, :]).sum(-1)
+                else:
+                    qs = torch.full((H, 1), float(q_scale), device=r.device)
+                    if l2norm:
+                        qs = qs * torch.rsqrt((rv * rv).sum(-1, keepdim=True) + 1e-6)
+                        kv = kv * torch.rsqrt((kv * kv).sum(-1, keepdim=True) + 1e-6)
+                    S = S * d[:, None, :]
+                    m = (S * kv[:, None, :]).sum(-1)
+                    delta = (vv - m) * beta[t].float()[:, None]
+                    S = S + delta[:, :, None] * kv[:, None, :]
+                    out = (S * rv[:, None, :]).sum(-1) * qs
+                y[t] = out.reshape(-1).to(r.dtype)
+            state[slot] = S
+        return y
+
+    def gated_rmsnorm(self, x, z, w, eps, group_size=0, norm_before_gate=False):
+        """Mamba-2: rmsnorm(x * silu(z)) * w over groups; gated delta net: rmsnorm(x) * w * silu(z) (norm first).
+        ``w`` may be shorter than the row (one weight vector per head): it repeats."""
+        T, D = x.shape
+        gs = group_size or D
+        xf = x.float()
+        gate = F.silu(z.float()) if z is not None else None
+        if gate is not None and not norm_before_gate:
+            xf = xf * gate
+        xg = xf.view(T, D // gs, gs)
+        xg = xg * torch.rsqrt(xg.pow(2).mean(-1, keepdim=True) + eps)
+        wf = w.float().repeat(D // w.numel())
+        out = xg.reshape(T, D) * wf
+        if gate is not None and norm_before_gate:
+            out = out * gate
+        return out.to(x.dtype)
+
+
+class RecurrentNative:
+    """Kernel wrappers; ``self.k`` is the loaded extension and ``self.launches`` the launch counter of the ops object."""
+
+    def causal_conv1d(self, x, w, bias, state, q_starts, seq_state, positions, act=True):
+        y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        self.k.causal_conv1d(x, w, bias, state, q_starts, seq_state, positions, y, bool(act))
+        self.launches += 1
+        return y
+
+    def mamba2_scan(self, x, dt, Bm, Cm, A, D, dt_bias, state, q_starts, seq_state, positions, H, P, G, N,
+                    dt_min=0.0, dt_max=float("inf")):
+        y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        self.k.mamba2_scan(x, dt, Bm, Cm, A, D, dt_bias, state, q_starts, seq_state, positions, y, H, P, G, N,
+                           float(dt_min), float(min(dt_max, 3.0e38)))
+        self.launches += 1
+        return y
+
+    def mamba1_scan(self, x, dt, Bm, Cm, z, A, D, dt_bias, state, q_starts, seq_state, positions):
+        y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        self.k.mamba1_scan(x, dt, Bm, Cm, z, A, D, dt_bias, state, q_starts, seq_state, positions, y)
+        self.launches += 1
+        return y
+
+    def matrix_state_scan(self, kind, r, k, v, a, b, w, u, beta, state, q_starts, seq_state, positions, H, DK, DV,
+                          kv_ratio=1, l2norm=False, q_scale=1.0):
+        y = torch.empty(r.shape[0], H * DV, dtype=r.dtype, device=r.device)
+        self.k.matrix_state_scan(int(kind), r, k, v, a, b, w, u, beta, state, q_starts, seq_state, positions, y, H, DK,
+                                 DV, int(kv_ratio), bool(l2norm), float(q_scale))
+        self.launches += 1
+        return y
+
+    def gated_rmsnorm(self, x, z, w, eps, group_size=0, norm_before_gate=False):
+        y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        self.k.gated_rmsnorm(x, z, w, y, int(group_size or x.shape[1]), float(eps), bool(norm_before_gate))
+        self.launches += 1
+        return y

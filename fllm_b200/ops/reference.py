@@ -11,8 +11,10 @@ import numpy as np
 import torch
 import torch.nn.functional as F
 
+from .recurrent import RecurrentRef
 
-class RefOps:
+
+class RefOps(RecurrentRef):
     name = "reference"
 
     # ---------------------------------------------------------------- dense

@@ -1,0 +1,146 @@
+"""Recurrent mixer kernels against the fp32 PyTorch statement of the same ops (fllm_b200/ops/recurrent.py), on ragged
+batches that mix fresh prompts, continued chunks and single decode rows (the reference checks its recurrent ops the
+same way in rust/engine/src/backend/selftest/rwkv.rs and selftest.rs: device op vs host reference on random data)."""
+import pytest
+import torch
+
+from fllm_b200.ops.recurrent import GATED_DELTA, KDA, RWKV6, RWKV7
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from fllm_b200.ops.native import NativeOps
+    from fllm_b200.ops.reference import RefOps
+    return NativeOps(torch.device("cuda")), RefOps()
+
+
+def ragged(lens, fresh, slots, device="cuda"):
+    """q_starts, seq_state, positions for sequences of the given step lengths; a non-fresh one continues at 37."""
+    qs, pos, t = [0], [], 0
+    for n, f in zip(lens, fresh):
+        t += n
+        qs.append(t)
+        pos += list(range(0 if f else 37, (0 if f else 37) + n))
+    mk = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+    return mk(qs), mk(slots), mk(pos), t
+
+
+def rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-9))
+
+
+CASES = [([5, 1, 17, 1], [True, False, False, True], [3, 0, 2, 5]), ([1, 1, 1], [False, False, False], [1, 2, 0]),
+         ([300], [True], [4])]
+
+
+@pytest.mark.parametrize("W", [2, 3, 4])
+@pytest.mark.parametrize("case", CASES)
+def test_causal_conv1d(ops, W, case):
+    nat, ref = ops
+    qs, ss, pos, T = ragged(*case)
+    C = 328
+    g = torch.Generator(device="cuda").manual_seed(W)
+    x = torch.randn(T, C + 8, device="cuda", generator=g).bfloat16()[:, 8:]             # a strided view
+    w = torch.randn(C, W, device="cuda", generator=g) * 0.5
+    bias = torch.randn(C, device="cuda", generator=g)
+    st = torch.randn(6, W - 1, C, device="cuda", generator=g).bfloat16()
+    st_ref = st.clone()
+    y = nat.causal_conv1d(x, w, bias, st, qs, ss, pos, act=True)
+    y_ref = ref.causal_conv1d(x, w, bias, st_ref, qs, ss, pos, act=True)
+    torch.cuda.synchronize()
+    assert rel(y, y_ref) < 1e-2
+    assert torch.equal(st, st_ref)                                # windows are copies of inputs: exact
+
+
+@pytest.mark.parametrize("N,P,H,G", [(128, 64, 8, 2), (64, 64, 4, 1), (16, 32, 6, 3), (256, 80, 2, 1), (32, 64, 4, 4)])
+@pytest.mark.parametrize("case", CASES)
+def test_mamba2_scan(ops, N, P, H, G, case):
+    nat, ref = ops
+    qs, ss, pos, T = ragged(*case)
+    g = torch.Generator(device="cuda").manual_seed(N + P)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    proj = rn(T, (H * P + 2 * G * N + H + 7) // 8 * 8).bfloat16()   # x | B | C | dt as views of one projection
+    x, Bm, Cm, dt = proj[:, :H * P], proj[:, H * P:H * P + G * N], proj[:, H * P + G * N:H * P + 2 * G * N], proj[:, H * P + 2 * G * N:H * P + 2 * G * N + H]
+    A = -torch.exp(rn(H) * 0.5)
+    D, dtb = rn(H), rn(H) * 0.5
+    st = rn(6, H, P, N) * 0.5
+    st_ref = st.clone()
+    y = nat.mamba2_scan(x, dt, Bm, Cm, A, D, dtb, st, qs, ss, pos, H, P, G, N, 0.001, 100.0)
+    y_ref = ref.mamba2_scan(x, dt, Bm, Cm, A, D, dtb, st_ref, qs, ss, pos, H, P, G, N, 0.001, 100.0)
+    torch.cuda.synchronize()
+    assert rel(y, y_ref) < 1e-2
+    assert rel(st, st_ref) < 1e-4
+
+
+@pytest.mark.parametrize("N", [16, 8])
+@pytest.mark.parametrize("case", CASES)
+def test_mamba1_scan(ops, N, case):
+    nat, ref = ops
+    qs, ss, pos, T = ragged(*case)
+    Dm = 200
+    g = torch.Generator(device="cuda").manual_seed(N)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    x, dt, z = rn(T, Dm).bfloat16(), rn(T, Dm).bfloat16(), rn(T, Dm).bfloat16()
+    bc = rn(T, 2 * N).bfloat16()
+    Bm, Cm = bc[:, :N], bc[:, N:]
+    A = -torch.exp(rn(Dm, N) * 0.5)
+    D, dtb = rn(Dm), rn(Dm) * 0.5
+    st = rn(6, Dm, N) * 0.5
+    st_ref = st.clone()
+    if N == 8:                                                     # 8 bf16 = one 16-byte word: views stay aligned
+        Bm, Cm = Bm.contiguous(), Cm.contiguous()
+    y = nat.mamba1_scan(x, dt, Bm, Cm, z, A, D, dtb, st, qs, ss, pos)
+    y_ref = ref.mamba1_scan(x, dt, Bm, Cm, z, A, D, dtb, st_ref, qs, ss, pos)
+    torch.cuda.synchronize()
+    assert rel(y, y_ref) < 1e-2
+    assert rel(st, st_ref) < 1e-4
+
+
+@pytest.mark.parametrize("kind", [RWKV6, RWKV7, GATED_DELTA, KDA])
+@pytest.mark.parametrize("DK,DV,H,ratio", [(64, 64, 4, 1), (128, 128, 4, 2), (32, 48, 2, 1), (256, 64, 2, 1)])
+@pytest.mark.parametrize("case", CASES)
+def test_matrix_state_scan(ops, kind, DK, DV, H, ratio, case):
+    nat, ref = ops
+    if kind in (RWKV6, RWKV7, KDA) and ratio != 1:
+        ratio = 1
+    qs, ss, pos, T = ragged(*case)
+    g = torch.Generator(device="cuda").manual_seed(kind * 7 + DK)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    Hk = H // ratio
+    r, k = rn(T, Hk * DK).bfloat16(), (rn(T, Hk * DK) * (0.3 if kind != RWKV7 else 1.0)).bfloat16()
+    v = rn(T, H * DV).bfloat16()
+    a = b = u = beta = None
+    if kind == RWKV7:                                              # a = -kk, b = kk * gate with kk a unit vector per head
+        kk = torch.nn.functional.normalize(rn(T, Hk, DK), dim=-1)
+        a = (-kk).reshape(T, -1).bfloat16()
+        b = (kk * torch.sigmoid(rn(T, Hk, DK))).reshape(T, -1).bfloat16()
+        k = (k.float() * 0.3).bfloat16()
+    if kind == RWKV6:
+        u = rn(Hk * DK) * 0.5
+    if kind in (GATED_DELTA, KDA):
+        beta = torch.sigmoid(rn(T, H)).bfloat16()
+    w = -torch.exp(rn(T, H if kind == GATED_DELTA else Hk * DK) - 1.0)
+    st = rn(6, H, DV, DK) * 0.3
+    st_ref = st.clone()
+    l2 = kind in (GATED_DELTA, KDA)
+    y = nat.matrix_state_scan(kind, r, k, v, a, b, w, u, beta, st, qs, ss, pos, H, DK, DV, ratio, l2, DK ** -0.5)
+    y_ref = ref.matrix_state_scan(kind, r, k, v, a, b, w, u, beta, st_ref, qs, ss, pos, H, DK, DV, ratio, l2, DK ** -0.5)
+    torch.cuda.synchronize()
+    assert rel(y, y_ref) < 1e-2
+    assert rel(st, st_ref) < 1e-4
+
+
+@pytest.mark.parametrize("gs,before", [(0, False), (64, False), (128, True), (40, True)])
+def test_gated_rmsnorm(ops, gs, before):
+    nat, ref = ops
+    T, D = 37, 640
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x, z = torch.randn(T, D, device="cuda", generator=g).bfloat16(), torch.randn(T, D, device="cuda", generator=g).bfloat16()
+    w = torch.randn(gs if before else D, device="cuda", generator=g).bfloat16()
+    y = nat.gated_rmsnorm(x, z, w, 1e-5, gs, before)
+    y_ref = ref.gated_rmsnorm(x, z, w, 1e-5, gs, before)
+    assert rel(y, y_ref) < 1e-2
+    y2 = nat.gated_rmsnorm(x, None, w, 1e-5, gs, before)
+    assert rel(y2, ref.gated_rmsnorm(x, None, w, 1e-5, gs, before)) < 1e-2
