@@ -65,6 +65,13 @@ class ModelConfig:
     moe_intermediate_size: int = 0
     router_kind: str = "softmax_topk"    # softmax over the selected top-k logits
     expert_bias: bool = False
+    # recurrent and hybrid families: the token mixer of each layer (None = attention everywhere) and whether the
+    # layer has a gated FFN behind it ("glu") or is the mixer alone ("none"); `ssm` holds the mixer shapes
+    # (d_inner, d_state, d_conv, n_groups, head_dim, n_heads, dt_rank, norm_groups, dt_min, dt_max, conv_bias,
+    # num_k_heads, num_v_heads, head_k_dim, head_v_dim, bcdt_rms ...)
+    layer_kinds: Optional[List[str]] = None      # attention | mamba1 | mamba2 | gated_delta | shortconv
+    ffn_kinds: Optional[List[str]] = None        # glu | none
+    ssm: Dict[str, Any] = field(default_factory=dict)
     # weight format of the big matrices
     weight_format: str = "bf16"          # bf16 | fp8_block | nvfp4 | mxfp4 | mxfp8 | mxfp4_a8 | nvfp4_a4 | int8_w8a8 | fp8_w8a8 | q4_k | ...
     name: str = "model"
@@ -85,6 +92,16 @@ class ModelConfig:
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
+
+    def layer_kind(self, layer: int) -> str:
+        return self.layer_kinds[layer] if self.layer_kinds else "attention"
+
+    def ffn_kind(self, layer: int) -> str:
+        return self.ffn_kinds[layer] if self.ffn_kinds else "glu"
+
+    @property
+    def has_recurrent(self) -> bool:
+        return bool(self.layer_kinds) and any(k != "attention" for k in self.layer_kinds)
 
     def layer_window(self, layer: int) -> int:
         if self.sliding_window <= 0:
@@ -122,6 +139,16 @@ class ModelConfig:
     def from_hf_config(cls, hf: Dict[str, Any]) -> "ModelConfig":
         """Map a Hugging Face ``config.json`` to the decoder description."""
         mt = hf.get("model_type", "llama")
+        rp = hf.get("rope_parameters") or {}
+        if rp:                                 # newer configs keep the RoPE base and scaling in one dictionary
+            hf = dict(hf)
+            hf.setdefault("rope_theta", rp.get("rope_theta", 10000.0))
+            if rp.get("rope_type", "default") != "default" and not hf.get("rope_scaling"):
+                hf["rope_scaling"] = rp
+            if rp.get("partial_rotary_factor") is not None:
+                hf.setdefault("partial_rotary_factor", rp["partial_rotary_factor"])
+        if mt in RECURRENT_MODEL_TYPES:
+            return recurrent_from_hf(cls, hf)
         heads = hf["num_attention_heads"]
         hidden = hf["hidden_size"]
         cfg = cls(
@@ -186,6 +213,86 @@ class ModelConfig:
         if hf.get("sliding_window") and hf.get("use_sliding_window", mt == "mistral"):
             cfg.sliding_window = hf["sliding_window"]
         return cfg
+
+
+RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2")
+
+
+def _limit(v, default: float) -> float:
+    """One end of a time-step limit as a config file spells it: a number, or infinity as a string / tagged value."""
+    if isinstance(v, dict):
+        v = next(iter(v.values()), None)
+    try:
+        f = float(v)
+    except (TypeError, ValueError):
+        return default
+    return max(min(f, 1e30), -1e30)
+
+
+def recurrent_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
+    """Recurrent and hybrid families (the reference describes them in rust/engine/src/config.rs next to the
+    attention fields and in rust/engine/src/hybrid_config.rs): which mixer each layer runs and its shapes."""
+    mt = hf["model_type"]
+    hidden, L = hf["hidden_size"], hf["num_hidden_layers"]
+    if mt in ("mamba", "falcon_mamba"):
+        d_inner = hf.get("intermediate_size") or hf.get("expand", 2) * hidden
+        rank = hf.get("time_step_rank", "auto")
+        rank = -(-hidden // 16) if rank == "auto" else int(rank)
+        return cls(arch=mt, name=hf.get("_name_or_path") or mt, vocab_size=hf["vocab_size"], hidden_size=hidden,
+                   num_layers=L, num_heads=1, num_kv_heads=1, head_dim=64, intermediate_size=0,
+                   rms_eps=hf.get("layer_norm_epsilon", 1e-5), tie_embeddings=hf.get("tie_word_embeddings", True),
+                   layer_kinds=["mamba1"] * L, ffn_kinds=["none"] * L,
+                   ssm=dict(d_inner=d_inner, d_state=hf.get("state_size", 16), d_conv=hf.get("conv_kernel", 4),
+                            dt_rank=rank, conv_bias=hf.get("use_conv_bias", True), proj_bias=hf.get("use_bias", False),
+                            bcdt_rms=(mt == "falcon_mamba"), mixer_rms_eps=hf.get("mixer_rms_eps", 1e-6)))
+    if mt == "mamba2":
+        H, P = hf.get("num_heads", 128), hf.get("head_dim", 64)
+        lim = hf.get("time_step_limit") or (0.0, float("inf"))
+        return cls(arch=mt, name=hf.get("_name_or_path") or mt, vocab_size=hf["vocab_size"], hidden_size=hidden,
+                   num_layers=L, num_heads=1, num_kv_heads=1, head_dim=64, intermediate_size=0,
+                   rms_eps=hf.get("layer_norm_epsilon", 1e-5), tie_embeddings=hf.get("tie_word_embeddings", False),
+                   layer_kinds=["mamba2"] * L, ffn_kinds=["none"] * L,
+                   ssm=dict(d_inner=H * P, d_state=hf.get("state_size", 128), d_conv=hf.get("conv_kernel", 4),
+                            n_groups=hf.get("n_groups", 8), head_dim=P, n_heads=H, norm_groups=1,
+                            conv_bias=hf.get("use_conv_bias", True), proj_bias=hf.get("use_bias", False),
+                            dt_min=_limit(lim[0], 0.0), dt_max=_limit(lim[1], 1e30)))
+    heads = hf["num_attention_heads"]
+    head_dim = hf.get("head_dim") or hidden // heads
+    base = dict(arch=mt, name=hf.get("_name_or_path") or mt, vocab_size=hf["vocab_size"], hidden_size=hidden, num_layers=L,
+                num_heads=heads, num_kv_heads=hf.get("num_key_value_heads", heads), head_dim=head_dim,
+                rope_theta=hf.get("rope_theta", 10000.0), max_position=hf.get("max_position_embeddings", 8192))
+    if mt == "bamba":
+        H = hf.get("mamba_n_heads", 128)
+        P = hf.get("mamba_d_head", "auto")
+        P = hf.get("mamba_expand", 2) * hidden // H if P == "auto" else int(P)
+        attn = set(hf.get("attn_layer_indices") or [])
+        lim = hf.get("time_step_limit") or (0.0, float("inf"))
+        rot = int(head_dim * hf.get("partial_rotary_factor", 0.5))
+        return cls(**base, intermediate_size=hf["intermediate_size"], rms_eps=hf.get("rms_norm_eps", 1e-5),
+                   tie_embeddings=hf.get("tie_word_embeddings", False), attn_bias=hf.get("attention_bias", False),
+                   rotary_dim=rot if rot != head_dim else None,
+                   layer_kinds=["attention" if i in attn else "mamba2" for i in range(L)],
+                   ssm=dict(d_inner=H * P, d_state=hf.get("mamba_d_state", 256), d_conv=hf.get("mamba_d_conv", 4),
+                            n_groups=hf.get("mamba_n_groups", 1), head_dim=P, n_heads=H, norm_groups=1,
+                            conv_bias=hf.get("mamba_conv_bias", True), proj_bias=hf.get("mamba_proj_bias", False),
+                            dt_min=_limit(lim[0], 0.0), dt_max=_limit(lim[1], 1e30)))
+    if mt == "lfm2":
+        inter = hf.get("intermediate_size") or hf.get("block_ff_dim", 4 * hidden)
+        if hf.get("block_auto_adjust_ff_dim", True):                # the checkpoint's FFN width: 2/3, multiplier, rounded up
+            inter = int(2 * inter / 3)
+            if hf.get("block_ffn_dim_multiplier") is not None:
+                inter = int(hf["block_ffn_dim_multiplier"] * inter)
+            mult = hf.get("block_multiple_of", 256)
+            inter = mult * ((inter + mult - 1) // mult)
+        kinds = hf.get("layer_types")
+        if not kinds:
+            full = set(hf.get("full_attn_idxs") or range(L))
+            kinds = ["full_attention" if i in full else "conv" for i in range(L)]
+        return cls(**base, intermediate_size=inter, rms_eps=hf.get("norm_eps", 1e-5),
+                   tie_embeddings=hf.get("tie_word_embeddings", True), qk_norm=True,
+                   layer_kinds=["attention" if k == "full_attention" else "shortconv" for k in kinds],
+                   ssm=dict(d_conv=hf.get("conv_L_cache", 3), conv_bias=hf.get("conv_bias", False)))
+    raise ValueError(f"no recurrent mapping for model_type {mt!r}")
 
 
 def rope_inv_freq(cfg: ModelConfig) -> "tuple[List[float], float]":
@@ -269,6 +376,24 @@ def preset(name: str) -> ModelConfig:
                            rope_scaling=RopeScaling(kind="yarn", factor=32.0, beta_fast=32.0,
                                                     beta_slow=1.0, original_max_position=4096),
                            max_position=131072)
+    if n in ("mamba2-2.7b", "mamba2-tiny"):
+        tiny = n.endswith("tiny")
+        hidden, L, H = (256, 2, 8) if tiny else (2560, 64, 80)
+        return ModelConfig(arch="mamba2", name=n, vocab_size=4096 if tiny else 50288, hidden_size=hidden, num_layers=L,
+                           num_heads=1, num_kv_heads=1, head_dim=64, intermediate_size=0, tie_embeddings=True,
+                           layer_kinds=["mamba2"] * L, ffn_kinds=["none"] * L,
+                           ssm=dict(d_inner=H * 64, d_state=128, d_conv=4, n_groups=1, head_dim=64, n_heads=H,
+                                    norm_groups=1, conv_bias=True, dt_min=0.0, dt_max=1e30))
+    if n in ("bamba-9b", "bamba-tiny"):
+        tiny = n.endswith("tiny")
+        hidden, L, H = (256, 3, 8) if tiny else (4096, 32, 128)
+        attn = {1} if tiny else {9, 18, 27}
+        return ModelConfig(arch="bamba", name=n, vocab_size=4096 if tiny else 128256, hidden_size=hidden, num_layers=L,
+                           num_heads=4 if tiny else 32, num_kv_heads=2 if tiny else 8, head_dim=64 if tiny else 128,
+                           rotary_dim=32 if tiny else 64, intermediate_size=512 if tiny else 14336,
+                           layer_kinds=["attention" if i in attn else "mamba2" for i in range(L)],
+                           ssm=dict(d_inner=H * 64, d_state=128, d_conv=4, n_groups=1, head_dim=64, n_heads=H,
+                                    norm_groups=1, conv_bias=True, dt_min=0.0, dt_max=1e30))
     raise KeyError(f"unknown model preset {name!r}")
 
 

@@ -48,6 +48,13 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
     def dev(t):
         return t.to(device=device, dtype=dtype if t.is_floating_point() and t.element_size() > 1 else t.dtype).contiguous()
 
+    if cfg.has_recurrent:
+        if tp > 1:
+            raise NotImplementedError("recurrent layers are not cut over tensor-parallel ranks")
+        from .recurrent_loader import load_hf_recurrent
+        tok = directory if os.path.exists(os.path.join(directory, "tokenizer.json")) else None
+        return cfg, load_hf_recurrent(cfg, get, device, dtype), tok
+
     def has(name):
         return name + ".weight" in ck or name + ".qweight" in ck
 

@@ -1,0 +1,96 @@
+"""Hugging Face checkpoints of the recurrent and hybrid families (model types ``mamba``, ``falcon_mamba``,
+``mamba2``, ``bamba``, ``lfm2``) into the decoder's weight containers.
+
+The reference reads the same families from GGUF files in rust/engine/src/rust_decoder.rs (``load_layers_ex``) and
+rust/engine/src/rust_decoder/hybrid.rs; the tensor roles are the same, the names here are the Hugging Face ones.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config import ModelConfig
+from ..models.recurrent import pack_mamba1, pack_mamba2
+from ..models.weights import DecoderWeights, LayerWeights
+
+
+def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
+    """``get(name, required=True)`` returns a checkpoint tensor (or None)."""
+    def dev(t):
+        return t.to(device=device, dtype=dtype).contiguous()
+
+    def attention(lw, p, q_norm=None, k_norm=None, o_name="o_proj"):
+        lw.wqkv = dev(torch.cat([get(p + f"{n}_proj.weight") for n in "qkv"], 0))
+        lw.wo = dev(get(p + o_name + ".weight"))
+        if cfg.attn_bias and get(p + "q_proj.bias", False) is not None:
+            lw.bqkv = dev(torch.cat([get(p + f"{n}_proj.bias") for n in "qkv"]))
+            bo = get(p + o_name + ".bias", False)
+            lw.bo = dev(bo) if bo is not None else None
+        if q_norm is not None:
+            lw.q_norm, lw.k_norm = dev(get(q_norm)), dev(get(k_norm))
+
+    def glu(lw, p, gate, up, down):
+        lw.w_gate_up = dev(torch.cat([get(p + gate + ".weight"), get(p + up + ".weight")], 0))
+        lw.w_down = dev(get(p + down + ".weight"))
+
+    s = cfg.ssm
+    layers = []
+    mt = cfg.arch
+    for l in range(cfg.num_layers):
+        kind = cfg.layer_kind(l)
+        if mt in ("mamba", "falcon_mamba", "mamba2"):
+            p = f"backbone.layers.{l}."
+            lw = LayerWeights(attn_norm=dev(get(p + "norm.weight")), wqkv=None, wo=None, ffn_norm=None)
+            m = p + "mixer."
+            if kind == "mamba1":
+                lw.mixer = pack_mamba1(get(m + "in_proj.weight"), get(m + "conv1d.weight"), get(m + "conv1d.bias", False),
+                                       get(m + "x_proj.weight"), get(m + "dt_proj.weight"), get(m + "dt_proj.bias"),
+                                       get(m + "A_log"), get(m + "D"), get(m + "out_proj.weight"), s["d_state"], s["dt_rank"],
+                                       dtype, device, get(m + "in_proj.bias", False), get(m + "out_proj.bias", False))
+            else:
+                lw.mixer = pack_mamba2(get(m + "in_proj.weight"), get(m + "conv1d.weight"), get(m + "conv1d.bias", False),
+                                       get(m + "dt_bias"), get(m + "A_log"), get(m + "D"), get(m + "norm.weight"),
+                                       get(m + "out_proj.weight"), dtype, device, get(m + "in_proj.bias", False),
+                                       get(m + "out_proj.bias", False))
+        elif mt == "bamba":
+            p = f"model.layers.{l}."
+            lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
+                              ffn_norm=dev(get(p + "pre_ff_layernorm.weight")))
+            if kind == "attention":
+                attention(lw, p + "self_attn.")
+            else:
+                m = p + "mamba."
+                lw.mixer = pack_mamba2(get(m + "in_proj.weight"), get(m + "conv1d.weight"), get(m + "conv1d.bias", False),
+                                       get(m + "dt_bias"), get(m + "A_log"), get(m + "D"), get(m + "norm.weight"),
+                                       get(m + "out_proj.weight"), dtype, device, get(m + "in_proj.bias", False),
+                                       get(m + "out_proj.bias", False))
+            glu(lw, p + "feed_forward.", "gate_proj", "up_proj", "down_proj")
+        elif mt == "lfm2":
+            p = f"model.layers.{l}."
+            lw = LayerWeights(attn_norm=dev(get(p + "operator_norm.weight")), wqkv=None, wo=None,
+                              ffn_norm=dev(get(p + "ffn_norm.weight")))
+            if kind == "attention":
+                attention(lw, p + "self_attn.", p + "self_attn.q_layernorm.weight", p + "self_attn.k_layernorm.weight", "out_proj")
+            else:
+                m = p + "conv."
+                cw = get(m + "conv.weight")
+                lw.mixer = dict(in_proj=dev(get(m + "in_proj.weight")), conv_w=cw.reshape(cw.shape[0], -1).float().to(device).contiguous(),
+                                out_proj=dev(get(m + "out_proj.weight")))
+                for name, key in (("conv_b", "conv.bias"), ("in_proj_b", "in_proj.bias"), ("out_proj_b", "out_proj.bias")):
+                    t = get(m + key, False)
+                    if t is not None:
+                        lw.mixer[name] = t.float().to(device).contiguous() if name == "conv_b" else dev(t)
+            glu(lw, p + "feed_forward.", "w1", "w3", "w2")
+        else:
+            raise ValueError(f"no recurrent loader for {mt!r}")
+        layers.append(lw)
+    if mt in ("mamba", "falcon_mamba", "mamba2"):
+        embed, final = get("backbone.embeddings.weight"), get("backbone.norm_f.weight")
+    elif mt == "bamba":
+        embed, final = get("model.embed_tokens.weight"), get("model.final_layernorm.weight")
+    else:
+        embed, final = get("model.embed_tokens.weight"), get("model.embedding_norm.weight")
+    head = get("lm_head.weight", False)
+    embed_d = dev(embed)
+    head_d = embed_d if (head is None or cfg.tie_embeddings) else dev(head)
+    return DecoderWeights(embed=embed_d, layers=layers, final_norm=dev(final), lm_head=head_d, vocab_start=0,
+                          vocab_local=cfg.vocab_size)

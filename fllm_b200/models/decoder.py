@@ -41,6 +41,7 @@ class StepBatch:
     min_q_len: int = 1
     seq_lens: Optional[torch.Tensor] = None      # [B] int32 visible KV length per sequence
     q_starts: Optional[torch.Tensor] = None      # [B+1] int32 first token row of each sequence
+    seq_state: Optional[torch.Tensor] = None     # [B] int32 row of the recurrent-state pools (hybrid families)
 
 
 class KVCache:
@@ -69,12 +70,15 @@ class KVCache:
 class Decoder:
     def __init__(self, cfg: ModelConfig, weights: DecoderWeights, kv: KVCache, ops, spec: Optional[ShardSpec] = None,
                  tp_group=None, layer_range: Optional[range] = None, first_stage: bool = True,
-                 last_stage: bool = True):
+                 last_stage: bool = True, rstate=None):
         self.cfg, self.w, self.kv, self.ops = cfg, weights, kv, ops
+        self.rstate = rstate          # models.recurrent.RecurrentState when some layer is recurrent
         self.spec = spec or make_shard_spec(cfg)
         self.tp = tp_group            # object with all_reduce / all_gather (or None)
         self.layer_range = layer_range or range(cfg.num_layers)
         self.first_stage, self.last_stage = first_stage, last_stage
+        # the KV pool holds only this stage's attention layers
+        self.kv_index = {li: i for i, li in enumerate(l for l in self.layer_range if cfg.layer_kind(l) == "attention")}
         dev = weights.final_norm.device
         inv, attn = rope_inv_freq(cfg)
         self.inv_freq = torch.tensor(inv, dtype=torch.float32, device=dev)
@@ -131,7 +135,7 @@ class Decoder:
     def _attention_block(self, li: int, lw, h: torch.Tensor, b: StepBatch) -> torch.Tensor:
         cfg, sp, ops = self.cfg, self.spec, self.ops
         qkv = ops.linear(h, lw.wqkv, lw.bqkv, defer=self._defer)
-        local = li - self.layer_range.start
+        local = self.kv_index[li]
         kc, vc = self.kv.k(local), self.kv.v(local)
         q = ops.rope_kv_write(qkv, b.positions, b.slots, self.inv_freq, lw.q_norm, lw.k_norm, kc, vc,
                               sp.hq_local, sp.hkv_local, cfg.head_dim, cfg.rot_dim, self.rope_style,
@@ -175,7 +179,17 @@ class Decoder:
             if nvtx:
                 torch.cuda.nvtx.range_push(f"layer{li}.attn")
             h = ops.rmsnorm(x, delta, lw.attn_norm, cfg.rms_eps, cfg.norm_weight_offset)
-            o = self._reduce(self._attention_block(li, lw, h, b))
+            kind = cfg.layer_kind(li)
+            if kind == "attention":
+                o = self._reduce(self._attention_block(li, lw, h, b))
+            else:
+                from .recurrent import MIXERS
+                o = MIXERS[kind](self, li, lw, h, b)
+            if lw.ffn_norm is None:                    # a mixer-only layer (Mamba): its output is the residual delta
+                delta = o
+                if nvtx:
+                    torch.cuda.nvtx.range_pop()
+                continue
             if lw.post_attn_norm is not None:
                 o = ops.rmsnorm(o, None, lw.post_attn_norm, cfg.rms_eps, cfg.norm_weight_offset)
             if nvtx:
@@ -194,7 +208,7 @@ class Decoder:
     def fused_tp(self) -> bool:
         return (self.tp is not None and getattr(self.tp, "backend", "") == "fused" and self.tp.size > 1
                 and not self.cfg.is_moe and not self.cfg.post_norms and self.first_stage and self.last_stage
-                and self._dense_weights)
+                and self._dense_weights and not self.cfg.has_recurrent)
 
     def forward_fused(self, b: StepBatch) -> torch.Tensor:
         """Whole forward with the sequence-sharded residual: every projection output leaves the

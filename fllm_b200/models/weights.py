@@ -42,6 +42,8 @@ class LayerWeights:
     exp_gate_up_b: Optional[torch.Tensor] = None    # [E_local, 2*I]
     exp_down: Optional[torch.Tensor] = None         # [E_local, H, I]
     exp_down_b: Optional[torch.Tensor] = None       # [E_local, H]
+    # recurrent layers (Mamba, delta rule, short convolution): the mixer's tensors by name; wqkv / wo stay None
+    mixer: Optional[Dict[str, torch.Tensor]] = None
     # packed formats keep their payload here (format name -> tensors)
     packed: Dict[str, object] = field(default_factory=dict)
     # row order of w_gate_up: 0 = gate half then up half; 16 = blocks of 16 gate rows followed by the 16 up
@@ -82,6 +84,8 @@ class DecoderWeights:
         add(self.embed); add(self.final_norm); add(self.lm_head)
         for l in self.layers:
             for v in vars(l).values():
+                add(v)
+            for v in (l.mixer or {}).values():
                 add(v)
         return n
 
@@ -234,6 +238,19 @@ def init_random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, se
     ones = lambda n: torch.ones(n, device=device, dtype=dtype)
     out_layers = []
     for li in layers:
+        if cfg.layer_kind(li) != "attention":
+            from .recurrent import init_random_mixer
+            if tp > 1:
+                raise NotImplementedError("recurrent layers are not cut over tensor-parallel ranks")
+            has_ffn = cfg.ffn_kind(li) != "none"
+            lw = LayerWeights(attn_norm=ones(H), wqkv=None, wo=None, ffn_norm=ones(H) if has_ffn else None,
+                              mixer=init_random_mixer(cfg, cfg.layer_kind(li), full, li, dtype, device))
+            if has_ffn:
+                I = cfg.intermediate_size
+                lw.w_gate_up = torch.cat([full((I, H), li, 4), full((I, H), li, 5)], 0).contiguous()
+                lw.w_down = full((H, I), li, 6)
+            out_layers.append(lw)
+            continue
         wq = full((cfg.q_size, H), li, 0)
         wk = full((cfg.kv_size, H), li, 1)
         wv = full((cfg.kv_size, H), li, 2)

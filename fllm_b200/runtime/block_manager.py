@@ -32,6 +32,7 @@ class SeqBlocks:
     num_tokens: int = 0                                  # tokens whose KV is (or will be) stored
     hashes: List[bytes] = field(default_factory=list)    # chain hash of each full, registered block
     first_live_block: int = 0                            # blocks before this were pruned (window)
+    state_slot: int = -1                                 # row of the recurrent-state pools (hybrid models)
     _np: Optional["np.ndarray"] = None                   # int32 mirror of `table` for batch building
     _np_len: int = 0
     _np_dirty: bool = True
@@ -58,6 +59,7 @@ class BlockManager:
         self.num_blocks, self.block_size = num_blocks, block_size
         self.enable_prefix_caching = enable_prefix_caching
         self.refs = [0] * num_blocks
+        self.state_free: Optional[List[int]] = None          # rows of the recurrent-state pools (hybrid models only)
         self.free: List[int] = list(range(num_blocks - 1, -1, -1))   # never-used / invalidated blocks
         self.cached: "OrderedDict[int, bytes]" = OrderedDict()       # ref==0 blocks with valid content (LRU)
         self.hash_to_block: Dict[bytes, int] = {}
@@ -173,6 +175,10 @@ class BlockManager:
                 parent = h
                 self.stats["tier_restored"] += 1
         sb = SeqBlocks(table=list(blocks), num_tokens=len(blocks) * self.block_size, hashes=list(hashes))
+        if self.state_free is not None:
+            if not self.state_free:
+                raise RuntimeError("no free recurrent-state row: more live sequences than max_num_seqs allows")
+            sb.state_slot = self.state_free.pop()
         self.seqs[seq_id] = sb
         return sb.num_tokens
 
@@ -234,6 +240,8 @@ class BlockManager:
         return b, nb
 
     def fork(self, parent_id: int, child_id: int) -> None:
+        if self.state_free is not None:
+            raise NotImplementedError("sequences of a recurrent model cannot be forked: their state is not paged")
         p = self.seqs[parent_id]
         for b in p.table:
             if b >= 0:
@@ -272,12 +280,21 @@ class BlockManager:
         sb = self.seqs.pop(seq_id, None)
         if sb is None:
             return
+        if sb.state_slot >= 0:
+            self.state_free.append(sb.state_slot)
         for b in reversed(sb.table):       # tail blocks become eviction candidates first
             if b >= 0:
                 self._release(b)
 
     def table(self, seq_id: int) -> List[int]:
         return self.seqs[seq_id].table
+
+    def enable_state_slots(self, n: int) -> None:
+        """Give every sequence one of ``n`` rows of the recurrent-state pools for as long as it holds blocks."""
+        self.state_free = list(range(n - 1, -1, -1))
+
+    def state_slot(self, seq_id: int) -> int:
+        return self.seqs[seq_id].state_slot
 
     def np_table(self, seq_id: int) -> np.ndarray:
         return self.seqs[seq_id].np_table()

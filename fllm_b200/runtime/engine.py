@@ -14,6 +14,7 @@ only one that reports events.
 """
 from __future__ import annotations
 
+import dataclasses
 import os
 
 import itertools
@@ -71,17 +72,31 @@ class LLMEngine:
             model_cfg, self.device, torch.bfloat16, seed, tp, tp_rank, self.par.expert_parallel,
             layers=self.layer_range, first_stage=self.first_stage, last_stage=self.last_stage)
         self.eos_token_id = eos_token_id
+        if model_cfg.has_recurrent:
+            # A recurrent state cannot be shared, rolled back or rebuilt from cached KV blocks: prompts are always
+            # computed from their first token, rejected drafts would need a state snapshot per position, and a
+            # preempted sequence is recomputed.
+            if tp > 1:
+                raise NotImplementedError("recurrent layers are not cut over tensor-parallel ranks")
+            self.cfg = dataclasses.replace(self.cfg, enable_prefix_caching=False, speculative="off", preemption="recompute")
         self.block_size = self.cfg.block_size
         self.max_blocks_per_seq = -(-self.cfg.max_model_len // self.block_size)
         num_blocks = self.cfg.num_kv_blocks or self._size_kv_pool()
         if self.cfg.kv_cache_dtype not in ("bf16", "fp8", "fp8_e4m3"):
             raise ValueError("kv_cache_dtype must be bf16 or fp8_e4m3")
         kv_dtype = torch.bfloat16 if self.cfg.kv_cache_dtype == "bf16" else torch.float8_e4m3fn
-        self.kv = KVCache(len(self.layer_range), num_blocks, self.spec.hkv_local, self.block_size,
+        self.kv = KVCache(self._kv_layers(), num_blocks, self.spec.hkv_local, self.block_size,
                           model_cfg.head_dim, self.device, kv_dtype)
+        self.rstate = None
+        if model_cfg.has_recurrent:
+            # one state row per running sequence, a few spare for sequences between two owners, and the scratch
+            # row that padding sequences of a captured step write to
+            from ..models.recurrent import RecurrentState
+            self.rstate = RecurrentState(model_cfg, self.layer_range, self.cfg.max_num_seqs + 9, self.device,
+                                         self.weights.final_norm.dtype)
         self.decoder = Decoder(model_cfg, self.weights, self.kv, self.ops, self.spec, tp_group,
                                layer_range=self.layer_range, first_stage=self.first_stage,
-                               last_stage=self.last_stage)
+                               last_stage=self.last_stage, rstate=self.rstate)
         # expert parallel with all-to-all dispatch: peer buffers for the rows each rank owns
         if (self.is_cuda and model_cfg.is_moe and self.par.expert_parallel and self.par.ep_dispatch == "alltoall"
                 and tp > 1 and getattr(tp_group, "group", None) is not None):
@@ -91,6 +106,8 @@ class LLMEngine:
                                              model_cfg.experts_per_token, self.device, group=tp_group.group)
         self.blocks = BlockManager(num_blocks, self.block_size, self.cfg.enable_prefix_caching,
                                    self.cfg.watermark)
+        if self.rstate is not None:
+            self.blocks.enable_state_slots(self.rstate.slots - 1)
         window = model_cfg.sliding_window if (model_cfg.sliding_window and model_cfg.window_pattern is None) else 0
         self.scheduler = Scheduler(self.cfg, self.blocks, window)
         self.kv_tier = None
@@ -118,7 +135,7 @@ class LLMEngine:
         self._inflight = None                # launch-ahead: the decode step whose ids are still on the device
         # staging: [ids | positions | slots | row_seq | logit_rows | block tables]
         max_rows = max(self.cfg.max_num_seqs, self._bucket_for(self.cfg.max_num_seqs))
-        cap = 5 * max(self.cfg.max_num_batched_tokens, max_rows) + max_rows * (self.max_blocks_per_seq + 2) + 64
+        cap = 5 * max(self.cfg.max_num_batched_tokens, max_rows) + max_rows * (self.max_blocks_per_seq + 3) + 64
         # one staging pair per pipeline micro-batch in flight (slot 0 is the only one without PP)
         self._stage_bufs = []
         for _ in range(max(1, self.par.pp)):
@@ -136,14 +153,21 @@ class LLMEngine:
                                      pin_memory=self.is_cuda)
 
     # ------------------------------------------------------------------ sizing
+    def _kv_layers(self) -> int:
+        """Attention layers of this stage (at least one, so that the pool tensors exist)."""
+        return max(1, sum(1 for li in self.layer_range if self.model_cfg.layer_kind(li) == "attention"))
+
     def _size_kv_pool(self) -> int:
-        per_block = KVCache.bytes_per_block(len(self.layer_range), self.spec.hkv_local,
+        per_block = KVCache.bytes_per_block(self._kv_layers(), self.spec.hkv_local,
                                             self.block_size, self.model_cfg.head_dim,
                                             2 if self.cfg.kv_cache_dtype == "bf16" else 1)
         if self.is_cuda:
             free, total = torch.cuda.mem_get_info(self.device)
             budget = int(total * self.cfg.gpu_memory_utilization) - (total - free)
             budget -= 4 << 30           # activations, graphs, workspaces
+            if self.model_cfg.has_recurrent:
+                from ..models.recurrent import RecurrentState
+                budget -= RecurrentState.bytes_per_slot(self.model_cfg, self.layer_range) * (self.cfg.max_num_seqs + 9)
         else:
             budget = 256 << 20
         want = self.cfg.max_num_seqs * self.max_blocks_per_seq
@@ -275,6 +299,8 @@ class LLMEngine:
         qst = h[o_qs:o_qs + Bp + 1]
         kvl = h[o_kl:o_kl + Bp]
         tab = h[o_tab:o_tab + Bp * max_blocks].reshape(Bp, max_blocks)
+        o_ss = o_tab + Bp * max_blocks
+        sst = h[o_ss:o_ss + Bp] if self.rstate is not None else None
         max_q, min_q = 1, 1 << 30
         t = 0
         for i, s in enumerate(seqs):
@@ -296,6 +322,8 @@ class LLMEngine:
             tab[i, :tb.shape[0]] = tb
             qst[i] = t
             kvl[i] = s.start + n
+            if sst is not None:
+                sst[i] = self.blocks.state_slot(r.seq_id)
             max_q, min_q = max(max_q, n), min(min_q, n)
             if s.wants_logits:
                 if s.verify:
@@ -312,11 +340,13 @@ class LLMEngine:
             rows.extend(range(T, Tp))
             qst[B:Bp] = np.arange(T, Tp, dtype=np.int32)      # one padding row per padding sequence
             kvl[B:Bp] = 1
+            if sst is not None:
+                sst[B:Bp] = self.rstate.slots - 1
             min_q = 1
         qst[Bp] = Tp
         R = len(rows)
         lrow[:R] = rows
-        used = o_tab + Bp * max_blocks
+        used = o_ss + (Bp if sst is not None else 0)
         if self.is_cuda:
             dev[:used].copy_(host_t[:used], non_blocking=True)
         else:
@@ -327,6 +357,7 @@ class LLMEngine:
             row_seq=dev[3 * Tp:4 * Tp], logit_rows=dev[4 * Tp:4 * Tp + R],
             block_tables=dev[o_tab:o_tab + Bp * max_blocks].view(Bp, max_blocks),
             q_starts=dev[o_qs:o_qs + Bp + 1], seq_lens=dev[o_kl:o_kl + Bp],
+            seq_state=dev[o_ss:o_ss + Bp] if sst is not None else None,
             num_seqs=Bp, num_tokens=T, max_kv_len=max_kv, all_decode=step.all_decode,
             max_q_len=max_q, min_q_len=min(min_q, max_q))
 
@@ -1028,6 +1059,7 @@ class _DecodeGraph:
             token_ids=dev[0:n], positions=dev[n:2 * n], slots=dev[2 * n:3 * n], row_seq=dev[3 * n:4 * n],
             logit_rows=dev[4 * n:5 * n], block_tables=dev[o_tab:o_tab + n * mb].view(n, mb),
             q_starts=dev[o_qs:o_qs + n + 1], seq_lens=dev[o_kl:o_kl + n],
+            seq_state=dev[o_tab + n * mb:o_tab + n * mb + n] if eng.rstate is not None else None,
             num_seqs=n, num_tokens=n, max_kv_len=eng.cfg.max_model_len, all_decode=True,
             max_q_len=1, min_q_len=1)
         # harmless contents for warm-up / capture: all rows padded
@@ -1038,6 +1070,8 @@ class _DecodeGraph:
         dev[o_qs:o_qs + n + 1].copy_(torch.arange(n + 1, dtype=torch.int32, device=dev.device))
         dev[o_kl:o_kl + n].fill_(1)
         dev[o_tab:o_tab + n * mb].zero_()
+        if eng.rstate is not None:           # warm-up and capture write the scratch row only
+            dev[o_tab + n * mb:o_tab + n * mb + n].fill_(eng.rstate.slots - 1)
         stream = torch.cuda.Stream(device=eng.device)
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):

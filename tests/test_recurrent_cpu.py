@@ -1,0 +1,146 @@
+"""Recurrent and hybrid families on CPU: teacher-forced logits of tiny random checkpoints against Hugging Face
+`transformers` (fp32, chunked prefill so that states cross step boundaries), and scheduling invariants of the state
+rows (chunked = one shot = one sequence at a time; rows are returned when sequences finish)."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from fllm_b200.config import EngineConfig, ModelConfig
+from fllm_b200.runtime.engine import LLMEngine
+from fllm_b200.runtime.request import SamplingParams
+
+
+def _tiny(kind):
+    torch.manual_seed(0)
+    if kind == "mamba":
+        from transformers import MambaConfig, MambaForCausalLM
+        return MambaForCausalLM(MambaConfig(vocab_size=300, hidden_size=64, state_size=16, num_hidden_layers=2, expand=2,
+                                            conv_kernel=4, time_step_rank=4, use_mambapy=False))
+    if kind == "mamba2":
+        from transformers import Mamba2Config, Mamba2ForCausalLM
+        return Mamba2ForCausalLM(Mamba2Config(vocab_size=300, hidden_size=64, state_size=16, num_hidden_layers=2, num_heads=4,
+                                              head_dim=32, n_groups=2, expand=2, conv_kernel=4, chunk_size=8))
+    if kind == "bamba":
+        from transformers import BambaConfig, BambaForCausalLM
+        return BambaForCausalLM(BambaConfig(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=3,
+                                            num_attention_heads=4, num_key_value_heads=2, attn_layer_indices=[1], mamba_n_heads=4,
+                                            mamba_d_head=32, mamba_n_groups=1, mamba_d_state=16, mamba_d_conv=4, mamba_expand=2,
+                                            mamba_chunk_size=8, max_position_embeddings=256))
+    if kind == "lfm2":
+        from transformers import Lfm2Config, Lfm2ForCausalLM
+        return Lfm2ForCausalLM(Lfm2Config(vocab_size=300, hidden_size=64, intermediate_size=192, num_hidden_layers=3,
+                                          num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256,
+                                          layer_types=["conv", "full_attention", "conv"], conv_L_cache=3, block_multiple_of=16))
+    raise ValueError(kind)
+
+
+@pytest.mark.parametrize("kind", ["mamba", "mamba2", "bamba", "lfm2"])
+def test_recurrent_families_match_transformers(tmp_path, kind):
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    m = _tiny(kind).eval().float()
+    with torch.no_grad():                      # spread the parameters a trained model would not leave at their init
+        for n, p in m.named_parameters():
+            if n.endswith(("norm.weight", "layernorm.weight", "norm_f.weight", ".D", "dt_bias")):
+                p.add_(0.3 * torch.randn_like(p))
+    d = str(tmp_path / kind)
+    m.save_pretrained(d, safe_serialization=True)
+    cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
+    assert cfg.has_recurrent
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16),
+                    device="cpu", weights=w)
+    toks = torch.randint(0, 300, (45,), generator=torch.Generator().manual_seed(1)).tolist()
+    got = eng.token_logits(toks)               # three steps of at most 16 rows: the states cross two boundaries
+    with torch.no_grad():
+        want = m(torch.tensor([toks])).logits[0].float()
+    scale = float(want.abs().max())
+    # the paged KV pool holds bf16 whatever the activation type: families with attention layers see its rounding
+    tol = 2e-2 if "attention" in cfg.layer_kinds else 1e-4
+    assert float((got - want).abs().max()) < tol * scale, (float((got - want).abs().max()), scale)
+    assert not eng.blocks.seqs and len(eng.blocks.state_free) == eng.rstate.slots - 1
+
+
+def _synthetic(kinds, ssm):
+    return ModelConfig(vocab_size=200, hidden_size=64, num_layers=len(kinds), num_heads=2, num_kv_heads=1, head_dim=32,
+                       intermediate_size=128, layer_kinds=kinds, ffn_kinds=["none" if k == "mamba1" else "glu" for k in kinds],
+                       ssm=ssm, tie_embeddings=True)
+
+
+SYNTHETIC = [
+    (["mamba2", "attention", "mamba2"], dict(d_inner=128, d_state=16, d_conv=4, n_groups=1, head_dim=32, n_heads=4, norm_groups=1)),
+    (["mamba1", "mamba1"], dict(d_inner=128, d_state=16, d_conv=4, dt_rank=4)),
+    (["gated_delta", "attention"], dict(num_k_heads=2, num_v_heads=4, head_k_dim=32, head_v_dim=32, d_conv=4)),
+    (["shortconv", "attention"], dict(d_conv=3, conv_bias=True)),
+]
+
+
+@pytest.mark.parametrize("kinds,ssm", SYNTHETIC)
+def test_state_rows_follow_the_schedule(kinds, ssm):
+    """The same prompts through one big step, through 16-token chunks interleaved with other sequences' decode
+    steps, and one sequence at a time give the same greedy tokens; every state row comes back."""
+    cfg = _synthetic(kinds, ssm)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 200, (n,), generator=g).tolist() for n in (37, 5, 70)]
+
+    def run(chunk, ps):
+        ec = EngineConfig(max_num_seqs=4, max_num_batched_tokens=chunk, max_model_len=256, num_kv_blocks=64, block_size=16)
+        eng = LLMEngine(cfg, ec, device="cpu", seed=1)
+        assert not eng.cfg.enable_prefix_caching and eng.cfg.speculative == "off"
+        out = eng.generate(ps, SamplingParams(max_tokens=6, temperature=0.0))
+        assert len(eng.blocks.state_free) == eng.rstate.slots - 1
+        return out
+    one = run(256, prompts)
+    assert run(16, prompts) == one
+    assert [run(256, [p])[0] for p in prompts] == one
+
+
+def test_gated_delta_mixer_matches_transformers():
+    """The gated delta rule layer against the Qwen3-Next module of `transformers` (its plain PyTorch path) with the
+    module's interleaved projection rows re-ordered into [q | k | v | z | beta | a]."""
+    from transformers.models.qwen3_next.configuration_qwen3_next import Qwen3NextConfig
+    from transformers.models.qwen3_next.modeling_qwen3_next import Qwen3NextGatedDeltaNet
+    from fllm_b200.models.recurrent import RecurrentState, gated_delta_mixer, pack_gated_delta
+    from fllm_b200.ops.reference import RefOps
+    torch.manual_seed(0)
+    Hk, Hv, Dk, Dv, H = 2, 4, 32, 32, 64
+    hc = Qwen3NextConfig(hidden_size=H, linear_num_key_heads=Hk, linear_num_value_heads=Hv, linear_key_head_dim=Dk,
+                         linear_value_head_dim=Dv, linear_conv_kernel_dim=4, num_hidden_layers=1, vocab_size=100, rms_norm_eps=1e-6)
+    mod = Qwen3NextGatedDeltaNet(hc, 0).eval().float()
+    with torch.no_grad():
+        mod.norm.weight.add_(0.3 * torch.randn_like(mod.norm.weight))
+        mod.dt_bias.add_(0.3 * torch.randn_like(mod.dt_bias))
+    r = Hv // Hk
+    qkvz = mod.in_proj_qkvz.weight.detach().view(Hk, 2 * Dk + 2 * r * Dv, H)      # per key head: q | k | v (r heads) | z (r heads)
+    ba = mod.in_proj_ba.weight.detach().view(Hk, 2 * r, H)
+    q, k = qkvz[:, :Dk].reshape(-1, H), qkvz[:, Dk:2 * Dk].reshape(-1, H)
+    v, z = qkvz[:, 2 * Dk:2 * Dk + r * Dv].reshape(-1, H), qkvz[:, 2 * Dk + r * Dv:].reshape(-1, H)
+    b, a = ba[:, :r].reshape(-1, H), ba[:, r:].reshape(-1, H)
+    mixer = pack_gated_delta(q, k, v, z, b, a, mod.conv1d.weight.detach(), mod.dt_bias.detach(), mod.A_log.detach(),
+                             mod.norm.weight.detach(), mod.out_proj.weight.detach(), torch.float32, "cpu")
+    cfg = _synthetic(["gated_delta"], dict(num_k_heads=Hk, num_v_heads=Hv, head_k_dim=Dk, head_v_dim=Dv, d_conv=4, norm_eps=1e-6))
+
+    class Dec:
+        pass
+    dec = Dec()
+    dec.cfg, dec.ops = cfg, RefOps()
+    dec.rstate = RecurrentState(cfg, range(1), 3, "cpu", torch.float32)
+
+    class LW:
+        pass
+    lw = LW()
+    lw.mixer = mixer
+
+    class B:
+        pass
+    x = torch.randn(1, 21, H)
+    with torch.no_grad():
+        want = mod(x)[0] if isinstance(mod(x), tuple) else mod(x)
+    got = []
+    for t0, t1 in ((0, 9), (9, 10), (10, 21)):                    # a chunk, one decode row, another chunk
+        bt = B()
+        bt.q_starts = torch.tensor([0, t1 - t0], dtype=torch.int32)
+        bt.seq_state = torch.tensor([1], dtype=torch.int32)
+        bt.positions = torch.arange(t0, t1, dtype=torch.int32)
+        got.append(gated_delta_mixer(dec, 0, lw, x[0, t0:t1], bt))
+    got = torch.cat(got)
+    assert float((got - want.reshape(21, H)).abs().max()) < 1e-4

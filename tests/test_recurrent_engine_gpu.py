@@ -1,0 +1,67 @@
+"""Hybrid and recurrent models through the engine on a GPU: the sm_100a kernels against the PyTorch statement of the
+same ops on the same weights, chunked prefill against one shot, and captured decode steps against eager ones."""
+import pytest
+import torch
+
+from fllm_b200.config import EngineConfig, ModelConfig, preset
+from fllm_b200.runtime.engine import LLMEngine
+from fllm_b200.runtime.request import SamplingParams
+
+pytestmark = pytest.mark.gpu
+
+
+def _cfg(kinds, ssm):
+    return ModelConfig(vocab_size=512, hidden_size=256, num_layers=len(kinds), num_heads=4, num_kv_heads=2, head_dim=64,
+                       intermediate_size=512, layer_kinds=kinds, ffn_kinds=["none" if k == "mamba1" else "glu" for k in kinds],
+                       ssm=ssm, tie_embeddings=True)
+
+
+CASES = [
+    (["mamba2", "attention", "mamba2"], dict(d_inner=512, d_state=128, d_conv=4, n_groups=2, head_dim=64, n_heads=8, norm_groups=1, conv_bias=True)),
+    (["mamba1", "mamba1"], dict(d_inner=512, d_state=16, d_conv=4, dt_rank=16, conv_bias=True)),
+    (["gated_delta", "attention", "gated_delta"], dict(num_k_heads=2, num_v_heads=4, head_k_dim=128, head_v_dim=128, d_conv=4)),
+    (["shortconv", "attention", "shortconv"], dict(d_conv=3, conv_bias=True)),
+]
+
+
+def _engine(cfg, ops=None, chunk=64, graphs=False, weights=None):
+    ec = EngineConfig(max_num_seqs=8, max_num_batched_tokens=chunk, max_model_len=512, num_kv_blocks=128, block_size=16,
+                      use_cuda_graphs=graphs)
+    return LLMEngine(cfg, ec, device="cuda:0", seed=3, ops=ops, weights=weights)
+
+
+@pytest.mark.parametrize("kinds,ssm", CASES)
+def test_native_kernels_match_reference_ops(kinds, ssm):
+    from fllm_b200.ops.reference import RefOps
+    cfg = _cfg(kinds, ssm)
+    nat = _engine(cfg)
+    assert type(nat.ops).__name__ == "NativeOps"
+    ref = _engine(cfg, ops=RefOps(), weights=nat.weights)
+    toks = torch.randint(0, 512, (150,), generator=torch.Generator().manual_seed(5)).tolist()
+    a, b = nat.token_logits(toks), ref.token_logits(toks)                   # three steps: states cross two boundaries
+    err = float((a - b).norm() / b.norm())
+    assert err < 2e-2, err
+    assert int(nat.ops.status.item()) == 0
+
+
+@pytest.mark.parametrize("kinds,ssm", CASES)
+def test_schedule_and_graphs_do_not_change_tokens(kinds, ssm):
+    cfg = _cfg(kinds, ssm)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (37, 5, 150, 64)]
+    sp = SamplingParams(max_tokens=12, temperature=0.0)
+    base = _engine(cfg, chunk=512)
+    want = base.generate(prompts, sp)
+    w = base.weights
+    assert _engine(cfg, chunk=48, weights=w).generate(prompts, sp) == want
+    eng = _engine(cfg, chunk=512, graphs=True, weights=w)
+    assert eng.generate(prompts, sp) == want
+    assert eng.generate(prompts[:2], sp) == want[:2]                        # rows are reused by later requests
+    assert len(eng.blocks.state_free) == eng.rstate.slots - 1
+
+
+def test_hybrid_presets_decode():
+    for name in ("mamba2-tiny", "bamba-tiny"):
+        eng = _engine(preset(name), chunk=256, graphs=True)
+        out = eng.generate([[1, 2, 3, 4, 5] * 9, [7] * 20], SamplingParams(max_tokens=8, temperature=0.0))
+        assert [len(o) for o in out] == [8, 8]
