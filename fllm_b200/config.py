@@ -69,9 +69,12 @@ class ModelConfig:
     # layer has a gated FFN behind it ("glu") or is the mixer alone ("none"); `ssm` holds the mixer shapes
     # (d_inner, d_state, d_conv, n_groups, head_dim, n_heads, dt_rank, norm_groups, dt_min, dt_max, conv_bias,
     # num_k_heads, num_v_heads, head_k_dim, head_v_dim, bcdt_rms ...)
-    layer_kinds: Optional[List[str]] = None      # attention | mamba1 | mamba2 | gated_delta | shortconv
+    layer_kinds: Optional[List[str]] = None      # attention | mla | mamba1 | mamba2 | gated_delta | shortconv
     ffn_kinds: Optional[List[str]] = None        # glu | none
     ssm: Dict[str, Any] = field(default_factory=dict)
+    # multi-head latent attention (layer kind "mla"): q_lora_rank (0 = one query projection), kv_lora_rank,
+    # qk_nope_head_dim, qk_rope_head_dim, v_head_dim; head_dim is then qk_nope + qk_rope and rotary_dim qk_rope
+    mla: Dict[str, Any] = field(default_factory=dict)
     # weight format of the big matrices
     weight_format: str = "bf16"          # bf16 | fp8_block | nvfp4 | mxfp4 | mxfp8 | mxfp4_a8 | nvfp4_a4 | int8_w8a8 | fp8_w8a8 | q4_k | ...
     name: str = "model"
@@ -101,7 +104,11 @@ class ModelConfig:
 
     @property
     def has_recurrent(self) -> bool:
-        return bool(self.layer_kinds) and any(k != "attention" for k in self.layer_kinds)
+        return bool(self.layer_kinds) and any(k not in ("attention", "mla") for k in self.layer_kinds)
+
+    @property
+    def has_mla(self) -> bool:
+        return bool(self.layer_kinds) and "mla" in self.layer_kinds
 
     def layer_window(self, layer: int) -> int:
         if self.sliding_window <= 0:
@@ -149,6 +156,8 @@ class ModelConfig:
                 hf.setdefault("partial_rotary_factor", rp["partial_rotary_factor"])
         if mt in RECURRENT_MODEL_TYPES:
             return recurrent_from_hf(cls, hf)
+        if mt in ("deepseek_v2", "deepseek_v3"):
+            return mla_from_hf(cls, hf)
         heads = hf["num_attention_heads"]
         hidden = hf["hidden_size"]
         cfg = cls(
@@ -213,6 +222,39 @@ class ModelConfig:
         if hf.get("sliding_window") and hf.get("use_sliding_window", mt == "mistral"):
             cfg.sliding_window = hf["sliding_window"]
         return cfg
+
+
+def _yarn_mscale(factor: float, m: float) -> float:
+    return 1.0 if factor <= 1.0 or not m else 0.1 * m * math.log(factor) + 1.0
+
+
+def mla_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
+    """DeepSeek-V2 / V3 with dense feed-forward layers (rust/engine/src/config.rs reads the same attention shapes from
+    GGUF metadata). Checkpoints with routed experts need the family's router (grouped top-k, shared experts) and are
+    refused."""
+    mt = hf["model_type"]
+    L, hidden, heads = hf["num_hidden_layers"], hf["hidden_size"], hf["num_attention_heads"]
+    if hf.get("n_routed_experts") and hf.get("first_k_dense_replace", 0) < L:
+        raise NotImplementedError(f"{mt}: layers with routed and shared experts are not supported, only dense feed-forward layers")
+    dn, dr = hf.get("qk_nope_head_dim", 128), hf.get("qk_rope_head_dim", 64)
+    cfg = cls(arch=mt, name=hf.get("_name_or_path") or mt, vocab_size=hf["vocab_size"], hidden_size=hidden, num_layers=L,
+              num_heads=heads, num_kv_heads=1, head_dim=dn + dr, rotary_dim=dr, rope_style="pair",
+              intermediate_size=hf["intermediate_size"], rms_eps=hf.get("rms_norm_eps", 1e-6),
+              rope_theta=hf.get("rope_theta", 10000.0), max_position=hf.get("max_position_embeddings", 4096),
+              tie_embeddings=hf.get("tie_word_embeddings", False), layer_kinds=["mla"] * L,
+              mla=dict(q_lora_rank=hf.get("q_lora_rank") or 0, kv_lora_rank=hf.get("kv_lora_rank", 512), qk_nope_head_dim=dn,
+                       qk_rope_head_dim=dr, v_head_dim=hf.get("v_head_dim", 128)))
+    rs = hf.get("rope_scaling") or {}
+    if (rs.get("rope_type") or rs.get("type")) == "yarn":
+        f = float(rs.get("factor", 1.0))
+        af = rs.get("attention_factor")
+        if af is None and rs.get("mscale") and rs.get("mscale_all_dim"):
+            af = _yarn_mscale(f, rs["mscale"]) / _yarn_mscale(f, rs["mscale_all_dim"])
+        cfg.rope_scaling = RopeScaling(kind="yarn", factor=f, original_max_position=rs.get("original_max_position_embeddings", 4096),
+                                       beta_fast=rs.get("beta_fast", 32.0), beta_slow=rs.get("beta_slow", 1.0), attn_factor=af)
+        if mt == "deepseek_v3" and rs.get("mscale_all_dim"):        # V3 also scales the softmax by mscale squared
+            cfg.attn_scale = (dn + dr) ** -0.5 * _yarn_mscale(f, rs["mscale_all_dim"]) ** 2
+    return cfg
 
 
 RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2")
@@ -394,6 +436,14 @@ def preset(name: str) -> ModelConfig:
                            layer_kinds=["attention" if i in attn else "mamba2" for i in range(L)],
                            ssm=dict(d_inner=H * 64, d_state=128, d_conv=4, n_groups=1, head_dim=64, n_heads=H,
                                     norm_groups=1, conv_bias=True, dt_min=0.0, dt_max=1e30))
+    if n in ("deepseek-v2-lite-dense", "mla-tiny"):
+        # the attention of DeepSeek-V2-Lite (16 heads, 512 + 64 latent rows) with dense feed-forward layers throughout
+        tiny = n == "mla-tiny"
+        hidden, L, H = (256, 2, 4) if tiny else (2048, 27, 16)
+        return ModelConfig(arch="deepseek_v2", name=n, vocab_size=4096 if tiny else 102400, hidden_size=hidden, num_layers=L,
+                           num_heads=H, num_kv_heads=1, head_dim=192, rotary_dim=64, rope_style="pair",
+                           intermediate_size=512 if tiny else 10944, rms_eps=1e-6, layer_kinds=["mla"] * L,
+                           mla=dict(q_lora_rank=0, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128))
     raise KeyError(f"unknown model preset {name!r}")
 
 

@@ -104,6 +104,24 @@ void gated_rmsnorm(const Tensor& x, const optional<Tensor>& z, const Tensor& w, 
   fllm::gated_rmsnorm(x.data_ptr(), x.stride(0), opt_ptr(z), opt_ld(z), w.data_ptr(), (int)w.numel(), y.data_ptr(), y.stride(0), (int)x.size(0),
                       (int)x.size(1), (int)group_size, (float)eps, norm_before_gate ? 1 : 0, cur_stream());
 }
+
+void attention_mla(const Tensor& q, const Tensor& cache, const Tensor& block_tables, const Tensor& row_seq, const Tensor& positions, Tensor out,
+                   double scale) {
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.dim() == 3 && q.is_contiguous() && q.size(2) == 576,
+              "q: contiguous bf16 [T, H, 576]");
+  TORCH_CHECK(cache.scalar_type() == at::kBFloat16 && cache.dim() == 3 && cache.is_contiguous() && cache.size(2) == 576,
+              "cache: contiguous bf16 [blocks, block_size, 576]");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.is_contiguous() && out.dim() == 3 && out.size(0) == q.size(0) &&
+                  out.size(1) == q.size(1) && out.size(2) == 512, "out: contiguous bf16 [T, H, 512]");
+  TORCH_CHECK(block_tables.scalar_type() == at::kInt && block_tables.dim() == 2 && block_tables.stride(1) == 1 &&
+                  row_seq.scalar_type() == at::kInt && positions.scalar_type() == at::kInt && row_seq.is_contiguous() &&
+                  positions.is_contiguous() && row_seq.numel() >= q.size(0) && positions.numel() >= q.size(0),
+              "block_tables [B, max_blocks], row_seq [T], positions [T]: int32");
+  c10::cuda::CUDAGuard guard(q.device());
+  fllm::attention_mla_bf16(q.data_ptr(), q.stride(0), cache.data_ptr(), block_tables.data_ptr<int>(), (int)block_tables.stride(0),
+                           row_seq.data_ptr<int>(), positions.data_ptr<int>(), out.data_ptr(), out.stride(0), (int)q.size(0), (int)q.size(1),
+                           (int)cache.size(1), (float)scale, cur_stream());
+}
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
@@ -118,5 +136,7 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("matrix_state_scan(int kind, Tensor r, Tensor k, Tensor v, Tensor? a, Tensor? b, Tensor w, Tensor? u, Tensor? beta, Tensor(a!) state, "
         "Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y, int H, int DK, int DV, int kv_ratio, bool l2norm, float q_scale) -> ()",
         &matrix_state_scan);
+  m.def("attention_mla(Tensor q, Tensor cache, Tensor block_tables, Tensor row_seq, Tensor positions, Tensor(a!) out, float scale) -> ()",
+        &attention_mla);
   m.def("gated_rmsnorm(Tensor x, Tensor? z, Tensor w, Tensor(a!) y, int group_size, float eps, bool norm_before_gate) -> ()", &gated_rmsnorm);
 }

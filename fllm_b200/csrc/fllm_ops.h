@@ -291,4 +291,9 @@ int matrix_state_scan(int kind, const void* r, long long ldr, const void* k, lon
 void gated_rmsnorm(const void* x, long long ldx, const void* z, long long ldz, const void* w, int wlen, void* y, long long ldy, int T,
                    int D, int group_size, float eps, int norm_before_gate, cudaStream_t stream);
 
+// Latent attention (attention_mla.cu): q [tokens][H][576] = absorbed query | rotated query part, cache
+// [blocks][block_size][576] = latent | rotated key part, out [tokens][H][512].
+void attention_mla_bf16(const void* q, long long ldq, const void* cache, const int* block_tables, int max_blocks, const int* row_seq,
+                        const int* positions, void* out, long long ldo, int tokens, int H, int block_size, float scale, cudaStream_t s);
+
 }  // namespace fllm

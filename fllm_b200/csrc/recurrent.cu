@@ -373,6 +373,81 @@ __global__ void __launch_bounds__(128) gated_rmsnorm_kernel(const bf16* x, long 
   }
 }
 
+// The same for wide groups (Mamba-2 normalises the whole inner width at once): one CTA of 256 threads per (token, group),
+// two channels per thread and step, the (gated) row kept in registers between the two passes when it fits (up to 8192 channels).
+__global__ void __launch_bounds__(256) gated_rmsnorm_wide_kernel(const bf16* x, long long ldx, const bf16* __restrict__ z, long long ldz,
+                                                                 const bf16* __restrict__ w, int wlen, bf16* y, long long ldy, int D, int gs,
+                                                                 float eps, int mode) {
+  constexpr int KEEP = 16;                                 // pairs kept per thread: 256 * 16 * 2 = 8192 channels
+  const int groups = D / gs;
+  const int t = blockIdx.x / groups, g = blockIdx.x % groups;
+  const __nv_bfloat162* xr = reinterpret_cast<const __nv_bfloat162*>(x + t * ldx + (long long)g * gs);
+  const __nv_bfloat162* zr = z != nullptr ? reinterpret_cast<const __nv_bfloat162*>(z + t * ldz + (long long)g * gs) : nullptr;
+  const int pairs = gs / 2;
+  float2 keep[KEEP];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < KEEP; ++i) {
+    const int p = threadIdx.x + i * 256;
+    keep[i] = make_float2(0.f, 0.f);
+    if (p < pairs) {
+      keep[i] = __bfloat1622float2(xr[p]);
+      if (mode == 0 && zr != nullptr) {
+        const float2 zz = __bfloat1622float2(zr[p]);
+        keep[i].x *= silu_f(zz.x), keep[i].y *= silu_f(zz.y);
+      }
+      ss = fmaf(keep[i].x, keep[i].x, fmaf(keep[i].y, keep[i].y, ss));
+    }
+  }
+  for (int p = threadIdx.x + KEEP * 256; p < pairs; p += 256) {     // beyond the kept part: read again in the second pass
+    float2 v = __bfloat1622float2(xr[p]);
+    if (mode == 0 && zr != nullptr) {
+      const float2 zz = __bfloat1622float2(zr[p]);
+      v.x *= silu_f(zz.x), v.y *= silu_f(zz.y);
+    }
+    ss = fmaf(v.x, v.x, fmaf(v.y, v.y, ss));
+  }
+  __shared__ float part[8];
+  ss = row_sum<32>(ss);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += part[i];
+  const float inv = rsqrtf(tot / gs + eps);
+  __nv_bfloat162* yr = reinterpret_cast<__nv_bfloat162*>(y + t * ldy + (long long)g * gs);
+  auto weight = [&](int p) {
+    const int c = (g * gs + 2 * p) % wlen;
+    return make_float2(__bfloat162float(w[c]), __bfloat162float(w[(c + 1) % wlen]));
+  };
+#pragma unroll
+  for (int i = 0; i < KEEP; ++i) {
+    const int p = threadIdx.x + i * 256;
+    if (p < pairs) {
+      const float2 ww = weight(p);
+      float2 v = make_float2(keep[i].x * inv * ww.x, keep[i].y * inv * ww.y);
+      if (mode == 1 && zr != nullptr) {
+        const float2 zz = __bfloat1622float2(zr[p]);
+        v.x *= silu_f(zz.x), v.y *= silu_f(zz.y);
+      }
+      yr[p] = __floats2bfloat162_rn(v.x, v.y);
+    }
+  }
+  for (int p = threadIdx.x + KEEP * 256; p < pairs; p += 256) {
+    float2 v = __bfloat1622float2(xr[p]);
+    float2 gt = make_float2(1.f, 1.f);
+    if (zr != nullptr) {
+      const float2 zz = __bfloat1622float2(zr[p]);
+      gt = make_float2(silu_f(zz.x), silu_f(zz.y));
+    }
+    if (mode == 0) v.x *= gt.x, v.y *= gt.y;
+    const float2 ww = weight(p);
+    v = make_float2(v.x * inv * ww.x, v.y * inv * ww.y);
+    if (mode == 1) v.x *= gt.x, v.y *= gt.y;
+    yr[p] = __floats2bfloat162_rn(v.x, v.y);
+  }
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 }  // namespace
 
@@ -478,6 +553,15 @@ void gated_rmsnorm(const void* x, long long ldx, const void* z, long long ldz, c
                    int D, int group_size, float eps, int norm_before_gate, cudaStream_t stream) {
   if (T <= 0) return;
   const long long items = (long long)T * (D / group_size);
+  const bool pairs_ok = group_size % 2 == 0 && ldx % 2 == 0 && ldy % 2 == 0 && (z == nullptr || ldz % 2 == 0) &&
+                        (reinterpret_cast<uintptr_t>(x) & 3) == 0 && (reinterpret_cast<uintptr_t>(y) & 3) == 0 &&
+                        (reinterpret_cast<uintptr_t>(z) & 3) == 0;
+  if (group_size >= 1024 && pairs_ok) {
+    gated_rmsnorm_wide_kernel<<<(unsigned)items, 256, 0, stream>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(z), ldz,
+                                                                   static_cast<const bf16*>(w), wlen, static_cast<bf16*>(y), ldy, D,
+                                                                   group_size, eps, norm_before_gate);
+    return;
+  }
   gated_rmsnorm_kernel<<<(unsigned)((items + 3) / 4), 128, 0, stream>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(z), ldz,
                                                                        static_cast<const bf16*>(w), wlen, static_cast<bf16*>(y), ldy, T, D,
                                                                        group_size, eps, norm_before_gate);

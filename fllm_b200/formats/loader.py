@@ -48,9 +48,9 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
     def dev(t):
         return t.to(device=device, dtype=dtype if t.is_floating_point() and t.element_size() > 1 else t.dtype).contiguous()
 
-    if cfg.has_recurrent:
+    if cfg.layer_kinds:
         if tp > 1:
-            raise NotImplementedError("recurrent layers are not cut over tensor-parallel ranks")
+            raise NotImplementedError("recurrent and latent-attention layers are not cut over tensor-parallel ranks")
         from .recurrent_loader import load_hf_recurrent
         tok = directory if os.path.exists(os.path.join(directory, "tokenizer.json")) else None
         return cfg, load_hf_recurrent(cfg, get, device, dtype), tok

@@ -1,5 +1,6 @@
 """Hugging Face checkpoints of the recurrent and hybrid families (model types ``mamba``, ``falcon_mamba``,
-``mamba2``, ``bamba``, ``lfm2``) into the decoder's weight containers.
+``mamba2``, ``bamba``, ``lfm2``) and of the latent-attention family (``deepseek_v2``, ``deepseek_v3`` with dense
+feed-forward layers) into the decoder's weight containers.
 
 The reference reads the same families from GGUF files in rust/engine/src/rust_decoder.rs (``load_layers_ex``) and
 rust/engine/src/rust_decoder/hybrid.rs; the tensor roles are the same, the names here are the Hugging Face ones.
@@ -80,6 +81,17 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
                     if t is not None:
                         lw.mixer[name] = t.float().to(device).contiguous() if name == "conv_b" else dev(t)
             glu(lw, p + "feed_forward.", "w1", "w3", "w2")
+        elif mt in ("deepseek_v2", "deepseek_v3"):
+            from ..models.mla import pack_mla
+            p = f"model.layers.{l}."
+            lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
+                              ffn_norm=dev(get(p + "post_attention_layernorm.weight")))
+            a = p + "self_attn."
+            opt = lambda name: get(a + name, False)
+            lw.mixer = pack_mla(opt("q_a_proj.weight"), opt("q_a_layernorm.weight"), opt("q_b_proj.weight"), opt("q_proj.weight"),
+                                get(a + "kv_a_proj_with_mqa.weight"), get(a + "kv_a_layernorm.weight"), get(a + "kv_b_proj.weight"),
+                                get(a + "o_proj.weight"), cfg, dtype, device)
+            glu(lw, p + "mlp.", "gate_proj", "up_proj", "down_proj")
         else:
             raise ValueError(f"no recurrent loader for {mt!r}")
         layers.append(lw)
@@ -87,6 +99,8 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
         embed, final = get("backbone.embeddings.weight"), get("backbone.norm_f.weight")
     elif mt == "bamba":
         embed, final = get("model.embed_tokens.weight"), get("model.final_layernorm.weight")
+    elif mt in ("deepseek_v2", "deepseek_v3"):
+        embed, final = get("model.embed_tokens.weight"), get("model.norm.weight")
     else:
         embed, final = get("model.embed_tokens.weight"), get("model.embedding_norm.weight")
     head = get("lm_head.weight", False)

@@ -78,7 +78,7 @@ class Decoder:
         self.layer_range = layer_range or range(cfg.num_layers)
         self.first_stage, self.last_stage = first_stage, last_stage
         # the KV pool holds only this stage's attention layers
-        self.kv_index = {li: i for i, li in enumerate(l for l in self.layer_range if cfg.layer_kind(l) == "attention")}
+        self.kv_index = {li: i for i, li in enumerate(l for l in self.layer_range if cfg.layer_kind(l) in ("attention", "mla"))}
         dev = weights.final_norm.device
         inv, attn = rope_inv_freq(cfg)
         self.inv_freq = torch.tensor(inv, dtype=torch.float32, device=dev)
@@ -182,6 +182,9 @@ class Decoder:
             kind = cfg.layer_kind(li)
             if kind == "attention":
                 o = self._reduce(self._attention_block(li, lw, h, b))
+            elif kind == "mla":
+                from .mla import mla_block
+                o = mla_block(self, li, lw, h, b)
             else:
                 from .recurrent import MIXERS
                 o = MIXERS[kind](self, li, lw, h, b)
@@ -208,7 +211,7 @@ class Decoder:
     def fused_tp(self) -> bool:
         return (self.tp is not None and getattr(self.tp, "backend", "") == "fused" and self.tp.size > 1
                 and not self.cfg.is_moe and not self.cfg.post_norms and self.first_stage and self.last_stage
-                and self._dense_weights and not self.cfg.has_recurrent)
+                and self._dense_weights and not self.cfg.layer_kinds)
 
     def forward_fused(self, b: StepBatch) -> torch.Tensor:
         """Whole forward with the sequence-sharded residual: every projection output leaves the

@@ -241,10 +241,14 @@ def init_random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, se
         if cfg.layer_kind(li) != "attention":
             from .recurrent import init_random_mixer
             if tp > 1:
-                raise NotImplementedError("recurrent layers are not cut over tensor-parallel ranks")
+                raise NotImplementedError("recurrent and latent-attention layers are not cut over tensor-parallel ranks")
             has_ffn = cfg.ffn_kind(li) != "none"
-            lw = LayerWeights(attn_norm=ones(H), wqkv=None, wo=None, ffn_norm=ones(H) if has_ffn else None,
-                              mixer=init_random_mixer(cfg, cfg.layer_kind(li), full, li, dtype, device))
+            if cfg.layer_kind(li) == "mla":
+                from .mla import init_random_mla
+                mixer = init_random_mla(cfg, full, li, dtype, device)
+            else:
+                mixer = init_random_mixer(cfg, cfg.layer_kind(li), full, li, dtype, device)
+            lw = LayerWeights(attn_norm=ones(H), wqkv=None, wo=None, ffn_norm=ones(H) if has_ffn else None, mixer=mixer)
             if has_ffn:
                 I = cfg.intermediate_size
                 lw.w_gate_up = torch.cat([full((I, H), li, 4), full((I, H), li, 5)], 0).contiguous()

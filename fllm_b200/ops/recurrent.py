@@ -145,6 +145,22 @@ class RecurrentRef:
         return out.to(x.dtype)
 
 
+    def attention_mla(self, q, cache, block_tables, row_seq, positions, latent, scale):
+        """Latent attention: q [T, H, W] against cache rows [blocks, block_size, W]; the values are the first
+        ``latent`` entries of the same rows. Returns [T, H, latent]."""
+        T, H, W = q.shape
+        R = latent
+        bs = cache.shape[1]
+        out = torch.empty(T, H, R, dtype=q.dtype, device=q.device)
+        for t in range(T):
+            n = int(positions[t]) + 1
+            nblk = (n + bs - 1) // bs
+            rows = cache[block_tables[int(row_seq[t]), :nblk].long()].reshape(nblk * bs, W)[:n].float()
+            p = torch.softmax(q[t].float() @ rows.T * scale, -1)
+            out[t] = (p @ rows[:, :R]).to(q.dtype)
+        return out
+
+
 class RecurrentNative:
     """Kernel wrappers; ``self.k`` is the loaded extension and ``self.launches`` the launch counter of the ops object."""
 
@@ -181,3 +197,12 @@ class RecurrentNative:
         self.k.gated_rmsnorm(x, z, w, y, int(group_size or x.shape[1]), float(eps), bool(norm_before_gate))
         self.launches += 1
         return y
+
+    def attention_mla(self, q, cache, block_tables, row_seq, positions, latent, scale):
+        T, H, W = q.shape
+        if (W, latent) != (576, 512):            # the kernel is built for the 512 + 64 rows of the DeepSeek family
+            return RecurrentRef.attention_mla(self, q, cache, block_tables, row_seq, positions, latent, scale)
+        out = torch.empty(T, H, latent, dtype=q.dtype, device=q.device)
+        self.k.attention_mla(q, cache, block_tables, row_seq, positions, out, float(scale))
+        self.launches += 1
+        return out

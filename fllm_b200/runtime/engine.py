@@ -72,6 +72,11 @@ class LLMEngine:
             model_cfg, self.device, torch.bfloat16, seed, tp, tp_rank, self.par.expert_parallel,
             layers=self.layer_range, first_stage=self.first_stage, last_stage=self.last_stage)
         self.eos_token_id = eos_token_id
+        if model_cfg.has_mla:
+            # the latent pool has its own layout: the host / disk tiers, swapping and block export read the K / V pool
+            if tp > 1:
+                raise NotImplementedError("latent-attention layers are not cut over tensor-parallel ranks")
+            self.cfg = dataclasses.replace(self.cfg, kv_tier_host_gb=0.0, kv_tier_disk_gb=0.0, preemption="recompute")
         if model_cfg.has_recurrent:
             # A recurrent state cannot be shared, rolled back or rebuilt from cached KV blocks: prompts are always
             # computed from their first token, rejected drafts would need a state snapshot per position, and a
@@ -85,8 +90,15 @@ class LLMEngine:
         if self.cfg.kv_cache_dtype not in ("bf16", "fp8", "fp8_e4m3"):
             raise ValueError("kv_cache_dtype must be bf16 or fp8_e4m3")
         kv_dtype = torch.bfloat16 if self.cfg.kv_cache_dtype == "bf16" else torch.float8_e4m3fn
-        self.kv = KVCache(self._kv_layers(), num_blocks, self.spec.hkv_local, self.block_size,
-                          model_cfg.head_dim, self.device, kv_dtype)
+        if model_cfg.has_mla:
+            from ..models.mla import MlaCache
+            if kv_dtype != torch.bfloat16:
+                raise ValueError("the latent cache of multi-head latent attention is bf16")
+            self.kv = MlaCache(self._kv_layers(), num_blocks, self.block_size,
+                               model_cfg.mla["kv_lora_rank"] + model_cfg.mla["qk_rope_head_dim"], self.device)
+        else:
+            self.kv = KVCache(self._kv_layers(), num_blocks, self.spec.hkv_local, self.block_size,
+                              model_cfg.head_dim, self.device, kv_dtype)
         self.rstate = None
         if model_cfg.has_recurrent:
             # one state row per running sequence, a few spare for sequences between two owners, and the scratch
@@ -155,12 +167,16 @@ class LLMEngine:
     # ------------------------------------------------------------------ sizing
     def _kv_layers(self) -> int:
         """Attention layers of this stage (at least one, so that the pool tensors exist)."""
-        return max(1, sum(1 for li in self.layer_range if self.model_cfg.layer_kind(li) == "attention"))
+        return max(1, sum(1 for li in self.layer_range if self.model_cfg.layer_kind(li) in ("attention", "mla")))
 
     def _size_kv_pool(self) -> int:
         per_block = KVCache.bytes_per_block(self._kv_layers(), self.spec.hkv_local,
                                             self.block_size, self.model_cfg.head_dim,
                                             2 if self.cfg.kv_cache_dtype == "bf16" else 1)
+        if self.model_cfg.has_mla:
+            from ..models.mla import MlaCache
+            per_block = MlaCache.bytes_per_block(self._kv_layers(), self.block_size,
+                                                 self.model_cfg.mla["kv_lora_rank"] + self.model_cfg.mla["qk_rope_head_dim"])
         if self.is_cuda:
             free, total = torch.cuda.mem_get_info(self.device)
             budget = int(total * self.cfg.gpu_memory_utilization) - (total - free)

@@ -144,3 +144,40 @@ def test_gated_delta_mixer_matches_transformers():
         got.append(gated_delta_mixer(dec, 0, lw, x[0, t0:t1], bt))
     got = torch.cat(got)
     assert float((got - want.reshape(21, H)).abs().max()) < 1e-4
+
+
+@pytest.mark.parametrize("version,q_lora", [(2, None), (2, 24), (3, 24)])
+def test_latent_attention_matches_transformers(tmp_path, version, q_lora):
+    """DeepSeek-V2 / V3 with dense feed-forward layers: absorbed latent attention over the 1-row-per-token cache against
+    the expanded attention of `transformers`, with YaRN scaling (V3 also scales the softmax)."""
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    torch.manual_seed(0)
+    common = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=4, kv_lora_rank=32, q_lora_rank=q_lora, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                  first_k_dense_replace=2, n_routed_experts=4, n_shared_experts=1, num_experts_per_tok=2, moe_intermediate_size=32,
+                  max_position_embeddings=256,
+                  rope_parameters=dict(rope_type="yarn", rope_theta=10000.0, factor=4.0, original_max_position_embeddings=64,
+                                       beta_fast=32.0, beta_slow=1.0, mscale=1.0, mscale_all_dim=0.7))
+    if version == 2:
+        from transformers import DeepseekV2Config, DeepseekV2ForCausalLM
+        m = DeepseekV2ForCausalLM(DeepseekV2Config(**common))
+    else:
+        from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
+        m = DeepseekV3ForCausalLM(DeepseekV3Config(n_group=1, topk_group=1, **common))
+    m = m.eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "layernorm" in n or n.endswith("norm.weight"):
+                p.add_(0.3 * torch.randn_like(p))
+    d = str(tmp_path / f"ds{version}")
+    m.save_pretrained(d, safe_serialization=True)
+    cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
+    assert cfg.has_mla and not cfg.has_recurrent and cfg.rope_scaling.kind == "yarn"
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=32, max_model_len=256, num_kv_blocks=32, block_size=16),
+                    device="cpu", weights=w)
+    toks = torch.randint(0, 300, (150,), generator=torch.Generator().manual_seed(1)).tolist()      # beyond the original 64 positions
+    got = eng.token_logits(toks)
+    with torch.no_grad():
+        want = m(torch.tensor([toks])).logits[0].float()
+    scale = float(want.abs().max())
+    assert float((got - want).abs().max()) < 2e-2 * scale, (float((got - want).abs().max()), scale)     # the latent pool is bf16

@@ -132,15 +132,42 @@ def test_matrix_state_scan(ops, kind, DK, DV, H, ratio, case):
     assert rel(st, st_ref) < 1e-4
 
 
-@pytest.mark.parametrize("gs,before", [(0, False), (64, False), (128, True), (40, True)])
-def test_gated_rmsnorm(ops, gs, before):
+@pytest.mark.parametrize("gs,before,D", [(0, False, 640), (64, False, 640), (128, True, 640), (40, True, 640),
+                                          (0, False, 5120), (2048, False, 4096), (0, True, 10240), (0, False, 1026)])
+def test_gated_rmsnorm(ops, gs, before, D):
     nat, ref = ops
-    T, D = 37, 640
+    T = 37
     g = torch.Generator(device="cuda").manual_seed(3)
     x, z = torch.randn(T, D, device="cuda", generator=g).bfloat16(), torch.randn(T, D, device="cuda", generator=g).bfloat16()
-    w = torch.randn(gs if before else D, device="cuda", generator=g).bfloat16()
+    w = torch.randn((gs or D) if before else D, device="cuda", generator=g).bfloat16()
     y = nat.gated_rmsnorm(x, z, w, 1e-5, gs, before)
     y_ref = ref.gated_rmsnorm(x, z, w, 1e-5, gs, before)
     assert rel(y, y_ref) < 1e-2
     y2 = nat.gated_rmsnorm(x, None, w, 1e-5, gs, before)
     assert rel(y2, ref.gated_rmsnorm(x, None, w, 1e-5, gs, before)) < 1e-2
+
+
+@pytest.mark.parametrize("H", [4, 16, 6])
+def test_latent_attention_kernel(ops, H):
+    """Ragged rows (two prefill chunks and decode rows) over a paged latent pool with shuffled blocks."""
+    nat, ref = ops
+    g = torch.Generator(device="cuda").manual_seed(H)
+    bs, nblocks = 16, 40
+    cache = (torch.randn(nblocks + 1, bs, 576, device="cuda", generator=g) * 0.5).bfloat16()
+    lens = [(0, 33), (100, 1), (17, 20), (299, 1)]                 # (tokens before the step, rows in the step)
+    perm = torch.randperm(nblocks, device="cuda", generator=g).int()
+    tables = torch.zeros(len(lens), 20, dtype=torch.int32, device="cuda")
+    row_seq, pos, used = [], [], 0
+    for s, (past, n) in enumerate(lens):
+        need = (past + n + bs - 1) // bs
+        tables[s, :need] = perm[used:used + need]
+        used += need
+        row_seq += [s] * n
+        pos += list(range(past, past + n))
+    row_seq = torch.tensor(row_seq, dtype=torch.int32, device="cuda")
+    pos = torch.tensor(pos, dtype=torch.int32, device="cuda")
+    q = torch.randn(len(pos), H, 576, device="cuda", generator=g).bfloat16()
+    out = nat.attention_mla(q, cache, tables, row_seq, pos, 512, 576 ** -0.5)
+    want = ref.attention_mla(q, cache, tables, row_seq, pos, 512, 576 ** -0.5)
+    torch.cuda.synchronize()
+    assert rel(out, want) < 1e-2
