@@ -58,8 +58,23 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
     def has(name):
         return name + ".weight" in ck or name + ".qweight" in ck
 
+    mlx_q = hf.get("quantization") if isinstance(hf.get("quantization"), dict) else None
+    if mlx_q is None and isinstance(qcfg, dict) and "group_size" in qcfg and "bits" in qcfg and "quant_method" not in qcfg:
+        mlx_q = qcfg
+
     def lin(name):
-        """A projection by its module name: a tensor [N, K], or an Int4Weight for AWQ / GPTQ tensors."""
+        """A projection by its module name: a tensor [N, K], or an Int4Weight for AWQ / GPTQ / MLX 4-bit tensors;
+        bitsandbytes 4-bit layers are expanded."""
+        if mlx_q is not None and name + ".scales" in ck and name + ".biases" in ck:
+            from .extra_quant import mlx_linear
+            per = mlx_q.get(name) if isinstance(mlx_q.get(name), dict) else mlx_q       # a layer may override bits / group
+            return mlx_linear(get(name + ".weight"), get(name + ".scales"), get(name + ".biases"), int(per.get("bits", 4)),
+                              int(per.get("group_size", 64)), dtype)
+        if name + ".weight.absmax" in ck:
+            from .extra_quant import bnb_linear
+            w = bnb_linear(get, name, dtype)
+            if w is not None:
+                return w
         if name + ".qweight" in ck:
             return int4_linear(qcfg.get("quant_method", "gptq"), get(name + ".qweight"), get(name + ".qzeros"),
                                get(name + ".scales"), get(name + ".g_idx", False),

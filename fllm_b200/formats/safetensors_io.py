@@ -18,7 +18,8 @@ import torch
 _DT = {"F32": (np.float32, torch.float32), "F16": (np.float16, torch.float16), "BF16": (np.uint16, torch.bfloat16),
        "I32": (np.int32, torch.int32), "I64": (np.int64, torch.int64), "U8": (np.uint8, torch.uint8),
        "I8": (np.int8, torch.int8), "F8_E4M3": (np.uint8, torch.float8_e4m3fn), "F8_E5M2": (np.uint8, torch.float8_e5m2),
-       "BOOL": (np.bool_, torch.bool), "I16": (np.int16, torch.int16), "F64": (np.float64, torch.float64)}
+       "BOOL": (np.bool_, torch.bool), "I16": (np.int16, torch.int16), "F64": (np.float64, torch.float64),
+       "U16": (np.uint16, torch.uint16), "U32": (np.uint32, torch.uint32), "U64": (np.uint64, torch.uint64)}
 _NAME = {v[1]: k for k, v in _DT.items()}
 
 

@@ -609,3 +609,97 @@ def test_pytorch_zip_checkpoints_are_read_without_running_their_pickle(tmp_path)
         f.write(b"not a zip at all")
     with pytest.raises(TorchZipError):
         TorchZipFile(str(tmp_path / "junk.bin"))
+
+
+@pytest.mark.parametrize("family", ["mlx4", "mlx8", "bnb_nf4", "bnb_nf4_double"])
+def test_mlx_affine_and_bitsandbytes_layers_load(tmp_path, family):
+    """A llama-like checkpoint whose projections are MLX affine tensors (uint32 words, scales, biases) or bitsandbytes
+    4-bit tensors (nibble pairs, absmax per 64 values, optionally double-quantised): packed the way the formats define,
+    read back by the loader; 4-bit MLX layers stay packed, the others are expanded; logits follow the dequantised twin."""
+    import json
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.formats.extra_quant import NF4_MAP
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    from fllm_b200.formats.safetensors_io import save_file
+    from fllm_b200.models.weights import init_random_weights
+    from fllm_b200.ops.int4 import Int4Weight
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    cfg = preset("tiny-llama")
+    cfg.vocab_size, cfg.intermediate_size = 512, 512
+    w = init_random_weights(cfg, "cpu", seed=8)
+    D, hq, hkv, I, g = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads, cfg.intermediate_size, 64
+    t = {"model.embed_tokens.weight": w.embed, "model.norm.weight": w.final_norm, "lm_head.weight": w.lm_head}
+    nf4 = torch.tensor(NF4_MAP)
+
+    def put(name, mat):
+        mat = mat.float()
+        N, K = mat.shape
+        if family.startswith("mlx"):
+            bits = 4 if family == "mlx4" else 8
+            grp = mat.view(N, K // g, g)
+            lo, hi = grp.min(-1).values, grp.max(-1).values
+            s = ((hi - lo) / (2 ** bits - 1)).clamp_min(1e-8).half().float()
+            b = lo.half().float()
+            q = torch.round((grp - b[..., None]) / s[..., None]).clamp(0, 2 ** bits - 1).to(torch.int64).view(N, K)
+            per = 32 // bits
+            words = (q.view(N, K // per, per) << (torch.arange(per) * bits)).sum(-1)
+            t[name + ".weight"] = words.to(torch.uint32) if hasattr(torch, "uint32") else words.to(torch.int32)
+            t[name + ".scales"], t[name + ".biases"] = s.half(), b.half()
+            return (q.view(N, K // g, g).float() * s[..., None] + b[..., None]).view(N, K)
+        flat = mat.reshape(-1, 64)
+        absmax = flat.abs().max(-1).values.clamp_min(1e-8)
+        code = ((flat / absmax[:, None])[..., None] - nf4).abs().argmin(-1)                   # nearest codebook entry
+        pairs = code.view(-1, 2)
+        t[name + ".weight"] = ((pairs[:, 0] << 4) | pairs[:, 1]).to(torch.uint8).view(-1, 1)
+        t[name + ".weight.quant_map"] = nf4.clone()
+        state = {"quant_type": "nf4", "blocksize": 64, "dtype": "bfloat16", "shape": [N, K]}
+        used = absmax
+        if family.endswith("double"):
+            offset = float(absmax.mean())
+            res = (absmax - offset).reshape(-1, 256) if absmax.numel() % 256 == 0 else None
+            assert res is not None
+            nmax = res.abs().max(-1).values.clamp_min(1e-8)
+            nmap = torch.linspace(-1, 1, 256)
+            ncode = ((res / nmax[:, None])[..., None] - nmap).abs().argmin(-1)
+            t[name + ".weight.absmax"] = ncode.reshape(-1).to(torch.uint8)
+            t[name + ".weight.nested_absmax"], t[name + ".weight.nested_quant_map"] = nmax, nmap
+            state.update(nested_blocksize=256, nested_offset=offset, nested_dtype="float32")
+            used = (nmap[ncode] * nmax[:, None]).reshape(-1) + offset
+        else:
+            t[name + ".weight.absmax"] = absmax
+        t[name + ".weight.quant_state.bitsandbytes__nf4"] = torch.tensor(list(json.dumps(state).encode()), dtype=torch.uint8)
+        return (nf4[code] * used[:, None]).view(N, K)
+
+    for l, lw in enumerate(w.layers):
+        p = f"model.layers.{l}."
+        t[p + "input_layernorm.weight"], t[p + "post_attention_layernorm.weight"] = lw.attn_norm, lw.ffn_norm
+        parts = {"self_attn.q_proj": lw.wqkv[: hq * D], "self_attn.k_proj": lw.wqkv[hq * D: (hq + hkv) * D],
+                 "self_attn.v_proj": lw.wqkv[(hq + hkv) * D:], "self_attn.o_proj": lw.wo,
+                 "mlp.gate_proj": lw.w_gate_up[:I], "mlp.up_proj": lw.w_gate_up[I:], "mlp.down_proj": lw.w_down}
+        deq = {k: put(p + k, v) for k, v in parts.items()}
+        lw.wqkv = torch.cat([deq["self_attn.q_proj"], deq["self_attn.k_proj"], deq["self_attn.v_proj"]], 0).bfloat16()
+        lw.wo, lw.w_down = deq["self_attn.o_proj"].bfloat16(), deq["mlp.down_proj"].bfloat16()
+        lw.w_gate_up = torch.cat([deq["mlp.gate_proj"], deq["mlp.up_proj"]], 0).bfloat16()
+    save_file({k: v.contiguous() for k, v in t.items()}, str(tmp_path / "model.safetensors"))
+    hf = {"model_type": "llama", "vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
+          "num_attention_heads": hq, "num_key_value_heads": hkv, "head_dim": D, "intermediate_size": I, "rms_norm_eps": cfg.rms_eps,
+          "rope_theta": cfg.rope_theta, "max_position_embeddings": 4096, "tie_word_embeddings": False}
+    if family.startswith("mlx"):
+        hf["quantization"] = {"group_size": g, "bits": 4 if family == "mlx4" else 8}
+    else:
+        hf["quantization_config"] = {"quant_method": "bitsandbytes", "load_in_4bit": True, "bnb_4bit_quant_type": "nf4",
+                                     "bnb_4bit_use_double_quant": family.endswith("double")}
+    json.dump(hf, open(tmp_path / "config.json", "w"))
+    cfg2, w2, _ = load_hf_checkpoint(str(tmp_path), device="cpu")
+    packed = all(isinstance(getattr(lw, n), Int4Weight) for lw in w2.layers for n in ("wqkv", "wo", "w_gate_up", "w_down"))
+    assert packed == (family == "mlx4")
+    a, b = w2.layers[0].w_down, w.layers[0].w_down.float()
+    a = a.dense().float() if isinstance(a, Int4Weight) else a.float()
+    assert (a - b).abs().max().item() <= 0.02 * b.abs().max().item()
+    ec = EngineConfig(max_num_seqs=2, max_num_batched_tokens=32, max_model_len=64, num_kv_blocks=16)
+    logits = []
+    for cc, ww in ((cfg2, w2), (cfg, w)):
+        eng = LLMEngine(cc, ec, device="cpu", weights=ww)
+        logits.append(eng.token_logits([3, 1, 4, 1, 5, 9, 2, 6]))
+    err = (logits[0] - logits[1]).abs().max().item() / (logits[1].abs().max().item() + 1e-6)
+    assert err < 0.05, err
