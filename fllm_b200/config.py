@@ -257,7 +257,7 @@ def mla_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     return cfg
 
 
-RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2")
+RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7")
 
 
 def _limit(v, default: float) -> float:
@@ -298,6 +298,14 @@ def recurrent_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
                             n_groups=hf.get("n_groups", 8), head_dim=P, n_heads=H, norm_groups=1,
                             conv_bias=hf.get("use_conv_bias", True), proj_bias=hf.get("use_bias", False),
                             dt_min=_limit(lim[0], 0.0), dt_max=_limit(lim[1], 1e30)))
+    if mt == "rwkv7":
+        N = hf.get("head_dim", 64)
+        inter = hf.get("intermediate_size") or int(hf.get("hidden_ratio", 4.0) * hidden)
+        return cls(arch=mt, name=hf.get("_name_or_path") or mt, vocab_size=hf["vocab_size"], hidden_size=hidden, num_layers=L,
+                   num_heads=hidden // N, num_kv_heads=hidden // N, head_dim=N, intermediate_size=inter,
+                   rms_eps=hf.get("norm_eps", 1e-5), tie_embeddings=False, layer_kinds=["rwkv7"] * L, ffn_kinds=["none"] * L,
+                   ssm=dict(head_dim=N, d_conv=2, decay_rank=hf.get("decay_low_rank_dim", 64), a_rank=hf.get("a_low_rank_dim", 64),
+                            v_rank=hf.get("v_low_rank_dim", 32), gate_rank=hf.get("gate_low_rank_dim", 128)))
     heads = hf["num_attention_heads"]
     head_dim = hf.get("head_dim") or hidden // heads
     base = dict(arch=mt, name=hf.get("_name_or_path") or mt, vocab_size=hf["vocab_size"], hidden_size=hidden, num_layers=L,
@@ -444,6 +452,13 @@ def preset(name: str) -> ModelConfig:
                            num_heads=H, num_kv_heads=1, head_dim=192, rotary_dim=64, rope_style="pair",
                            intermediate_size=512 if tiny else 10944, rms_eps=1e-6, layer_kinds=["mla"] * L,
                            mla=dict(q_lora_rank=0, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128))
+    if n in ("rwkv7-1.5b", "rwkv7-tiny"):
+        tiny = n.endswith("tiny")
+        hidden, L = (256, 2) if tiny else (2048, 24)
+        ranks = dict(decay_rank=32, a_rank=32, v_rank=16, gate_rank=64) if tiny else dict(decay_rank=96, a_rank=96, v_rank=64, gate_rank=256)
+        return ModelConfig(arch="rwkv7", name=n, vocab_size=4096 if tiny else 65536, hidden_size=hidden, num_layers=L,
+                           num_heads=hidden // 64, num_kv_heads=hidden // 64, head_dim=64, intermediate_size=4 * hidden,
+                           layer_kinds=["rwkv7"] * L, ffn_kinds=["none"] * L, ssm=dict(head_dim=64, d_conv=2, **ranks))
     raise KeyError(f"unknown model preset {name!r}")
 
 

@@ -53,6 +53,9 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
             raise NotImplementedError("recurrent and latent-attention layers are not cut over tensor-parallel ranks")
         from .recurrent_loader import load_hf_recurrent
         tok = directory if os.path.exists(os.path.join(directory, "tokenizer.json")) else None
+        if cfg.arch == "rwkv7":
+            from ..models.rwkv import weights_from_state_dict
+            return cfg, weights_from_state_dict(cfg, {k: get(k) for k in ck}, device, dtype), tok
         return cfg, load_hf_recurrent(cfg, get, device, dtype), tok
 
     def has(name):

@@ -169,6 +169,9 @@ class Decoder:
         """Runs this stage's layers. Returns (residual, pending_delta): the residual
         stream and the last projection output that has not been added yet."""
         cfg, ops = self.cfg, self.ops
+        if cfg.arch == "rwkv7":
+            from .rwkv import rwkv7_forward_hidden
+            return rwkv7_forward_hidden(self, b)
         if self.first_stage:
             x = ops.embed(b.token_ids, self.w.embed, cfg.embed_scale)
             delta = None
@@ -282,7 +285,11 @@ class Decoder:
     def logits(self, x: torch.Tensor, delta: Optional[torch.Tensor], b: StepBatch) -> torch.Tensor:
         """Final norm + LM head on the requested rows -> [R, vocab_local]."""
         cfg, ops = self.cfg, self.ops
-        h = ops.rmsnorm(x, delta, self.w.final_norm, cfg.rms_eps, cfg.norm_weight_offset)
+        if cfg.arch == "rwkv7":
+            from .rwkv import rwkv7_final_norm
+            h = rwkv7_final_norm(self, x)
+        else:
+            h = ops.rmsnorm(x, delta, self.w.final_norm, cfg.rms_eps, cfg.norm_weight_offset)
         if b.all_decode and b.logit_rows.numel() == h.shape[0]:
             hs = h                     # every row is a decode row: no gather needed
         else:

@@ -32,7 +32,7 @@ def conv_channels(cfg: ModelConfig, kind: str) -> int:
         return s["d_inner"] + 2 * s["n_groups"] * s["d_state"]
     if kind == "gated_delta":
         return 2 * s["num_k_heads"] * s["head_k_dim"] + s["num_v_heads"] * s["head_v_dim"]
-    if kind == "shortconv":
+    if kind in ("shortconv", "rwkv7"):
         return cfg.hidden_size
     raise ValueError(kind)
 
@@ -45,6 +45,8 @@ def scan_state_shape(cfg: ModelConfig, kind: str):
         return (s["n_heads"], s["head_dim"], s["d_state"])
     if kind == "gated_delta":
         return (s["num_v_heads"], s["head_v_dim"], s["head_k_dim"])
+    if kind == "rwkv7":
+        return (cfg.hidden_size // s["head_dim"], s["head_dim"], s["head_dim"])
     return None
 
 
@@ -56,11 +58,14 @@ class RecurrentState:
         self.slots = slots
         self.conv: Dict[int, torch.Tensor] = {}
         self.scan: Dict[int, torch.Tensor] = {}
+        self.shift2: Dict[int, torch.Tensor] = {}          # RWKV: the channel mix has a token shift of its own
         W = cfg.ssm.get("d_conv", 4)
         for li in layer_range:
             kind = cfg.layer_kind(li)
-            if kind == "attention":
+            if kind in ("attention", "mla"):
                 continue
+            if kind == "rwkv7":
+                self.shift2[li] = torch.zeros(slots, W - 1, cfg.hidden_size, dtype=act_dtype, device=device)
             self.conv[li] = torch.zeros(slots, W - 1, conv_channels(cfg, kind), dtype=act_dtype, device=device)
             shape = scan_state_shape(cfg, kind)
             if shape is not None:
@@ -72,9 +77,9 @@ class RecurrentState:
         W = cfg.ssm.get("d_conv", 4)
         for li in layer_range:
             kind = cfg.layer_kind(li)
-            if kind == "attention":
+            if kind in ("attention", "mla"):
                 continue
-            n += (W - 1) * conv_channels(cfg, kind) * 2
+            n += (W - 1) * conv_channels(cfg, kind) * (4 if kind == "rwkv7" else 2)
             shape = scan_state_shape(cfg, kind)
             if shape is not None:
                 k = 4
@@ -84,7 +89,7 @@ class RecurrentState:
         return n
 
     def nbytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in list(self.conv.values()) + list(self.scan.values()))
+        return sum(t.numel() * t.element_size() for d in (self.conv, self.scan, self.shift2) for t in d.values())
 
 
 def _batch_meta(b):

@@ -70,6 +70,7 @@ class DecoderWeights:
     lm_head: torch.Tensor               # [vocab_local(padded), H]
     vocab_start: int = 0
     vocab_local: int = 0
+    final_norm_b: Optional[torch.Tensor] = None      # families whose blocks are LayerNorms (RWKV)
 
     def nbytes(self) -> int:
         n = 0
@@ -222,6 +223,11 @@ def init_random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, se
     in bf16 as a whole."""
     weight_format = weight_format if weight_format is not None else cfg.weight_format
     device = torch.device(device)
+    if cfg.arch == "rwkv7":
+        from .rwkv import random_rwkv7_state_dict, weights_from_state_dict
+        if tp > 1 or (layers is not None and len(layers) != cfg.num_layers):
+            raise NotImplementedError("RWKV models run on one rank and one pipeline stage")
+        return weights_from_state_dict(cfg, random_rwkv7_state_dict(cfg, seed), device, dtype)
     sp = make_shard_spec(cfg, tp, tp_rank, expert_parallel)
     D, H = cfg.head_dim, cfg.hidden_size
     layers = range(cfg.num_layers) if layers is None else layers

@@ -181,3 +181,76 @@ def test_latent_attention_matches_transformers(tmp_path, version, q_lora):
         want = m(torch.tensor([toks])).logits[0].float()
     scale = float(want.abs().max())
     assert float((got - want).abs().max()) < 2e-2 * scale, (float((got - want).abs().max()), scale)     # the latent pool is bf16
+
+
+def _rwkv7_oracle(sd, cfg, ids):
+    """RWKV-7 one token at a time in fp32, with the states in a dictionary: the published recurrence written without
+    any of the engine's pieces (no ragged batch, no kernels, no packed weights)."""
+    import torch.nn.functional as F
+    C, N, eps = cfg.hidden_size, cfg.ssm["head_dim"], cfg.rms_eps
+    H = C // N
+    ln = lambda x, n: F.layer_norm(x, (C,), sd[n + ".weight"], sd[n + ".bias"], eps)
+    st = {}
+    out = []
+    for tok in ids:
+        x = sd["model.embeddings.weight"][tok]
+        v_first = None
+        for l in range(cfg.num_layers):
+            g = lambda n: sd[f"model.layers.{l}.{n}"]
+            if l == 0:
+                x = ln(x, "model.layers.0.pre_norm")
+            h = ln(x, f"model.layers.{l}.attn_norm")
+            xx = st.get(("a", l), torch.zeros(C)) - h
+            st[("a", l)] = h
+            mix = {c: h + xx * g("attn.x_" + c).reshape(-1) for c in "rwkvag"}
+            r, k, v = g("attn.r_proj.weight") @ mix["r"], g("attn.k_proj.weight") @ mix["k"], g("attn.v_proj.weight") @ mix["v"]
+            low = lambda n, vec, act=lambda t: t: g(f"attn.{n}_lora.lora.2.weight") @ act(g(f"attn.{n}_lora.lora.0.weight") @ vec)
+            decay = torch.exp(-0.6065306597126334 * torch.sigmoid(low("w", mix["w"], torch.tanh) + g("attn.w_lora.lora.2.bias")))
+            if l == 0:
+                v_first = v
+            else:
+                v = v + (v_first - v) * torch.sigmoid(low("v", mix["v"]) + g("attn.v_lora.lora.2.bias"))
+            a = torch.sigmoid(low("a", mix["a"]) + g("attn.a_lora.lora.2.bias"))
+            gate = low("g", mix["g"], torch.sigmoid)
+            kk = F.normalize((k * g("attn.k_k")).view(H, N), dim=-1).view(-1)
+            k = k * (1 + (a - 1) * g("attn.k_a"))
+            S = st.get(("s", l), torch.zeros(H, N, N))
+            sa = torch.einsum("hvk,hk->hv", S, -kk.view(H, N))
+            S = S * decay.view(H, 1, N) + sa[:, :, None] * (kk * a).view(H, 1, N) + v.view(H, N, 1) * k.view(H, 1, N)
+            st[("s", l)] = S
+            y = torch.einsum("hvk,hk->hv", S, r.view(H, N)).reshape(1, C)
+            y = F.group_norm(y, H, g("attn.g_norm.weight"), g("attn.g_norm.bias"), N * eps).reshape(-1)
+            y = y + ((r.view(H, N) * k.view(H, N) * g("attn.r_k")).sum(-1, keepdim=True) * v.view(H, N)).reshape(-1)
+            x = x + g("attn.o_proj.weight") @ (y * gate)
+            h2 = ln(x, f"model.layers.{l}.ffn_norm")
+            xx = st.get(("f", l), torch.zeros(C)) - h2
+            st[("f", l)] = h2
+            x = x + g("ffn.value.weight") @ torch.relu(g("ffn.key.weight") @ (h2 + xx * g("ffn.x_k").reshape(-1))) ** 2
+        out.append(sd["lm_head.weight"] @ ln(x, "model.norm"))
+    return torch.stack(out)
+
+
+def test_rwkv7_matches_token_by_token_recurrence(tmp_path):
+    import json
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    from fllm_b200.formats.safetensors_io import save_file
+    from fllm_b200.models.rwkv import random_rwkv7_state_dict
+    hf = {"model_type": "rwkv7", "architectures": ["RWKV7ForCausalLM"], "hidden_size": 64, "num_hidden_layers": 3, "head_dim": 16,
+          "decay_low_rank_dim": 8, "a_low_rank_dim": 8, "v_low_rank_dim": 8, "gate_low_rank_dim": 16, "intermediate_size": 256,
+          "norm_eps": 1e-5, "vocab_size": 300}
+    cfg = ModelConfig.from_hf_config(hf)
+    sd = random_rwkv7_state_dict(cfg, seed=3)
+    json.dump(hf, open(tmp_path / "config.json", "w"))
+    save_file(sd, str(tmp_path / "model.safetensors"))
+    cfg2, w, _ = load_hf_checkpoint(str(tmp_path), device="cpu", dtype=torch.float32)
+    assert cfg2.arch == "rwkv7" and cfg2.has_recurrent
+    eng = LLMEngine(cfg2, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16),
+                    device="cpu", weights=w)
+    toks = torch.randint(0, 300, (40,), generator=torch.Generator().manual_seed(2)).tolist()
+    got = eng.token_logits(toks)                       # 16 + 16 + 8 rows: every state crosses two step boundaries
+    want = _rwkv7_oracle(sd, cfg, toks)
+    assert float((got - want).abs().max()) < 1e-3 * float(want.abs().max())
+    # decode after a chunked prefill equals decode after a one-shot prefill
+    sp = SamplingParams(max_tokens=6, temperature=0.0)
+    big = LLMEngine(cfg2, EngineConfig(max_num_seqs=2, max_num_batched_tokens=64, max_model_len=128, num_kv_blocks=32), device="cpu", weights=w)
+    assert eng.generate([toks[:37], toks[:5]], sp) == big.generate([toks[:37], toks[:5]], sp)

@@ -76,6 +76,20 @@ def test_latent_attention_engine():
     assert _engine(cfg, chunk=512, graphs=True, weights=nat.weights).generate(prompts, sp) == want
 
 
+def test_rwkv7_engine():
+    from fllm_b200.ops.reference import RefOps
+    cfg = preset("rwkv7-tiny")
+    nat = _engine(cfg)
+    ref = _engine(cfg, ops=RefOps(), weights=nat.weights)
+    toks = torch.randint(0, 4096, (150,), generator=torch.Generator().manual_seed(5)).tolist()
+    a, b = nat.token_logits(toks), ref.token_logits(toks)
+    assert float((a - b).norm() / b.norm()) < 3e-2
+    prompts = [toks[:37], toks[40:45], toks]
+    sp = SamplingParams(max_tokens=10, temperature=0.0)
+    want = _engine(cfg, chunk=512, weights=nat.weights).generate(prompts, sp)
+    assert _engine(cfg, chunk=512, graphs=True, weights=nat.weights).generate(prompts, sp) == want
+
+
 def test_hybrid_presets_decode():
     for name in ("mamba2-tiny", "bamba-tiny"):
         eng = _engine(preset(name), chunk=256, graphs=True)
