@@ -63,14 +63,22 @@ class ModelConfig:
     num_experts: int = 0
     experts_per_token: int = 0
     moe_intermediate_size: int = 0
-    router_kind: str = "softmax_topk"    # softmax over the selected top-k logits
+    router_kind: str = "softmax_topk"    # softmax_topk | softmax_all | deepseek_v2 | deepseek_v3
     expert_bias: bool = False
+    # DeepSeek routers: always-on shared experts (one dense GLU of this width, 0 = none), a factor on the routed
+    # weights, group-limited selection (experts in `router_groups` groups, the best `router_topk_groups` kept) and
+    # whether the selected weights are renormalised
+    shared_intermediate_size: int = 0
+    router_scale: float = 1.0
+    router_groups: int = 1
+    router_topk_groups: int = 1
+    router_norm_topk: bool = False
     # recurrent and hybrid families: the token mixer of each layer (None = attention everywhere) and whether the
     # layer has a gated FFN behind it ("glu") or is the mixer alone ("none"); `ssm` holds the mixer shapes
     # (d_inner, d_state, d_conv, n_groups, head_dim, n_heads, dt_rank, norm_groups, dt_min, dt_max, conv_bias,
     # num_k_heads, num_v_heads, head_k_dim, head_v_dim, bcdt_rms ...)
     layer_kinds: Optional[List[str]] = None      # attention | mla | mamba1 | mamba2 | gated_delta | shortconv
-    ffn_kinds: Optional[List[str]] = None        # glu | none
+    ffn_kinds: Optional[List[str]] = None        # glu | moe | none
     ssm: Dict[str, Any] = field(default_factory=dict)
     # multi-head latent attention (layer kind "mla"): q_lora_rank (0 = one query projection), kv_lora_rank,
     # qk_nope_head_dim, qk_rope_head_dim, v_head_dim; head_dim is then qk_nope + qk_rope and rotary_dim qk_rope
@@ -229,13 +237,12 @@ def _yarn_mscale(factor: float, m: float) -> float:
 
 
 def mla_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
-    """DeepSeek-V2 / V3 with dense feed-forward layers (rust/engine/src/config.rs reads the same attention shapes from
-    GGUF metadata). Checkpoints with routed experts need the family's router (grouped top-k, shared experts) and are
-    refused."""
+    """DeepSeek-V2 / V3 (rust/engine/src/config.rs reads the same shapes from GGUF metadata): latent attention in every
+    layer, dense feed-forward layers first, then routed experts with always-on shared experts and the family's routers
+    (V2: softmax scores, optionally group-limited; V3: sigmoid scores with a selection bias, groups ranked by their two
+    best experts, renormalised weights)."""
     mt = hf["model_type"]
     L, hidden, heads = hf["num_hidden_layers"], hf["hidden_size"], hf["num_attention_heads"]
-    if hf.get("n_routed_experts") and hf.get("first_k_dense_replace", 0) < L:
-        raise NotImplementedError(f"{mt}: layers with routed and shared experts are not supported, only dense feed-forward layers")
     dn, dr = hf.get("qk_nope_head_dim", 128), hf.get("qk_rope_head_dim", 64)
     cfg = cls(arch=mt, name=hf.get("_name_or_path") or mt, vocab_size=hf["vocab_size"], hidden_size=hidden, num_layers=L,
               num_heads=heads, num_kv_heads=1, head_dim=dn + dr, rotary_dim=dr, rope_style="pair",
@@ -244,6 +251,20 @@ def mla_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
               tie_embeddings=hf.get("tie_word_embeddings", False), layer_kinds=["mla"] * L,
               mla=dict(q_lora_rank=hf.get("q_lora_rank") or 0, kv_lora_rank=hf.get("kv_lora_rank", 512), qk_nope_head_dim=dn,
                        qk_rope_head_dim=dr, v_head_dim=hf.get("v_head_dim", 128)))
+    dense_first = hf.get("first_k_dense_replace", 0)
+    if hf.get("n_routed_experts") and dense_first < L:
+        step = hf.get("moe_layer_freq", 1) or 1
+        cfg.ffn_kinds = ["moe" if (i >= dense_first and i % step == 0) else "glu" for i in range(L)]
+        cfg.num_experts = hf["n_routed_experts"]
+        cfg.experts_per_token = hf.get("num_experts_per_tok") or 2
+        cfg.moe_intermediate_size = hf.get("moe_intermediate_size", cfg.intermediate_size)
+        cfg.shared_intermediate_size = (hf.get("n_shared_experts") or 0) * cfg.moe_intermediate_size
+        cfg.router_scale = float(hf.get("routed_scaling_factor", 1.0))
+        cfg.router_norm_topk = bool(hf.get("norm_topk_prob", mt == "deepseek_v3"))
+        grouped = mt == "deepseek_v3" or hf.get("topk_method") == "group_limited_greedy"
+        cfg.router_groups = (hf.get("n_group") or 1) if grouped else 1
+        cfg.router_topk_groups = (hf.get("topk_group") or 1) if grouped else 1
+        cfg.router_kind = mt
     rs = hf.get("rope_scaling") or {}
     if (rs.get("rope_type") or rs.get("type")) == "yarn":
         f = float(rs.get("factor", 1.0))
@@ -459,6 +480,16 @@ def preset(name: str) -> ModelConfig:
         return ModelConfig(arch="rwkv7", name=n, vocab_size=4096 if tiny else 65536, hidden_size=hidden, num_layers=L,
                            num_heads=hidden // 64, num_kv_heads=hidden // 64, head_dim=64, intermediate_size=4 * hidden,
                            layer_kinds=["rwkv7"] * L, ffn_kinds=["none"] * L, ssm=dict(head_dim=64, d_conv=2, **ranks))
+    if n in ("deepseek-v2-lite", "deepseek-moe-tiny"):
+        tiny = n.endswith("tiny")
+        hidden, L, H = (256, 3, 4) if tiny else (2048, 27, 16)
+        return ModelConfig(arch="deepseek_v2", name=n, vocab_size=4096 if tiny else 102400, hidden_size=hidden, num_layers=L,
+                           num_heads=H, num_kv_heads=1, head_dim=192, rotary_dim=64, rope_style="pair",
+                           intermediate_size=512 if tiny else 10944, rms_eps=1e-6, layer_kinds=["mla"] * L,
+                           ffn_kinds=["glu"] + ["moe"] * (L - 1), num_experts=8 if tiny else 64, experts_per_token=2 if tiny else 6,
+                           moe_intermediate_size=128 if tiny else 1408, shared_intermediate_size=256 if tiny else 2816,
+                           router_kind="deepseek_v2", router_scale=1.0, router_norm_topk=False,
+                           mla=dict(q_lora_rank=0, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128))
     raise KeyError(f"unknown model preset {name!r}")
 
 

@@ -91,7 +91,26 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
             lw.mixer = pack_mla(opt("q_a_proj.weight"), opt("q_a_layernorm.weight"), opt("q_b_proj.weight"), opt("q_proj.weight"),
                                 get(a + "kv_a_proj_with_mqa.weight"), get(a + "kv_a_layernorm.weight"), get(a + "kv_b_proj.weight"),
                                 get(a + "o_proj.weight"), cfg, dtype, device)
-            glu(lw, p + "mlp.", "gate_proj", "up_proj", "down_proj")
+            if cfg.ffn_kind(l) == "moe":
+                mp = p + "mlp."
+                lw.router_w = dev(get(mp + "gate.weight"))
+                sel = get(mp + "gate.e_score_correction_bias", False)
+                if sel is not None:
+                    lw.router_select_b = sel.float().to(device).contiguous()
+                fused = get(mp + "experts.gate_up_proj", False)
+                if fused is not None:                                # one [E, 2I, H] and one [E, H, I] tensor
+                    lw.exp_gate_up, lw.exp_down = dev(fused), dev(get(mp + "experts.down_proj"))
+                else:                                                # one module per expert
+                    E = cfg.num_experts
+                    lw.exp_gate_up = dev(torch.stack([torch.cat([get(mp + f"experts.{e}.gate_proj.weight"),
+                                                                 get(mp + f"experts.{e}.up_proj.weight")], 0) for e in range(E)]))
+                    lw.exp_down = dev(torch.stack([get(mp + f"experts.{e}.down_proj.weight") for e in range(E)]))
+                if cfg.shared_intermediate_size:
+                    lw.shared_gate_up = dev(torch.cat([get(mp + "shared_experts.gate_proj.weight"),
+                                                       get(mp + "shared_experts.up_proj.weight")], 0))
+                    lw.shared_down = dev(get(mp + "shared_experts.down_proj.weight"))
+            else:
+                glu(lw, p + "mlp.", "gate_proj", "up_proj", "down_proj")
         else:
             raise ValueError(f"no recurrent loader for {mt!r}")
         layers.append(lw)

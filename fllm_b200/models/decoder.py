@@ -153,12 +153,16 @@ class Decoder:
 
     def _ffn_block(self, lw, h: torch.Tensor) -> torch.Tensor:
         cfg, ops = self.cfg, self.ops
-        if cfg.is_moe:
+        if lw.router_w is not None:
             from .moe import moe_ffn, moe_ffn_alltoall
             if self.ep_a2a is not None:
                 self._reduced = True                 # rows come back complete: nothing left to reduce
                 return moe_ffn_alltoall(self, lw, h)
-            return moe_ffn(self, lw, h)
+            y = moe_ffn(self, lw, h)
+            if lw.shared_gate_up is not None:        # always-on shared experts: one dense GLU beside the routed ones
+                act = ops.linear_glu(h, lw.shared_gate_up, None, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit, 0)
+                y = y + ops.linear(act, lw.shared_down)
+            return y
         act = ops.linear_glu(h, lw.w_gate_up, None, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit,
                              getattr(lw, "glu_layout", 0))
         return ops.linear(act, lw.w_down, defer=self._defer_out(lw.post_ffn_norm))

@@ -9,6 +9,8 @@ a partial sum that the caller reduces like a dense FFN output.
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 import torch.nn.functional as F
 
@@ -24,8 +26,35 @@ def _act(cfg, gu: torch.Tensor) -> torch.Tensor:
     return (F.silu(g) if cfg.act == "swiglu" else F.gelu(g, approximate="tanh")) * u
 
 
-def route_reference(cfg, logits: torch.Tensor):
+def route_deepseek(cfg, logits: torch.Tensor, bias: Optional[torch.Tensor]):
+    """The DeepSeek routers in plain tensor ops (the selection is [T, E]-sized work). V2: softmax scores, experts
+    outside the best groups (by their best expert) masked, top-k, weights = scores. V3: sigmoid scores, selection on
+    scores + bias with groups ranked by the sum of their two best, weights = unbiased scores, renormalised. Both scale
+    the weights by ``router_scale``."""
+    k, E, G = cfg.experts_per_token, cfg.num_experts, max(cfg.router_groups, 1)
+    lf = logits.float()
+    if cfg.router_kind == "deepseek_v3":
+        scores = torch.sigmoid(lf)
+        choice = scores + (bias.float() if bias is not None else 0.0)
+        group_rank = choice.view(-1, G, E // G).topk(min(2, E // G), dim=-1)[0].sum(-1)
+    else:
+        scores = torch.softmax(lf, -1)
+        choice = scores
+        group_rank = choice.view(-1, G, E // G).max(-1).values
+    if G > 1:
+        keep = torch.zeros_like(group_rank).scatter_(1, group_rank.topk(cfg.router_topk_groups, dim=-1)[1], 1.0)
+        choice = choice.masked_fill(keep[:, :, None].expand(-1, G, E // G).reshape(-1, E) == 0, 0.0)
+    ids = choice.topk(k, dim=-1)[1]
+    w = scores.gather(1, ids)
+    if cfg.router_norm_topk:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return ids.int(), (w * cfg.router_scale).contiguous()
+
+
+def route_reference(cfg, logits: torch.Tensor, bias: Optional[torch.Tensor] = None):
     """Top-k ids [T, k] and weights [T, k] (fp32)."""
+    if cfg.router_kind in ("deepseek_v2", "deepseek_v3"):
+        return route_deepseek(cfg, logits, bias)
     k = cfg.experts_per_token
     lf = logits.float()
     vals, ids = torch.topk(lf, k, dim=-1)
@@ -42,9 +71,10 @@ def moe_reference(cfg, lw, h: torch.Tensor, expert_lo: int = 0, round_bf16: bool
     r = (lambda t: t.to(torch.bfloat16).float()) if round_bf16 else (lambda t: t)
     hf = h.float()
     logits = hf @ lw.router_w.float().t()
+    select_bias = getattr(lw, "router_select_b", None)
     if lw.router_b is not None:
         logits = logits + lw.router_b.float()
-    ids, w = route_reference(cfg, r(logits))
+    ids, w = route_reference(cfg, r(logits), select_bias)
     out = torch.zeros(h.shape[0], lw.exp_down.shape[1], dtype=torch.float32, device=h.device)
     e_local = lw.exp_gate_up.shape[0]
     for e in range(e_local):
@@ -104,7 +134,10 @@ def moe_ffn(dec, lw, h: torch.Tensor) -> torch.Tensor:
     logits = ops.linear(h, lw.router_w, lw.router_b)
     ids = torch.empty(T, k, dtype=torch.int32, device=h.device)
     wts = torch.empty(T, k, dtype=torch.float32, device=h.device)
-    k_ops.moe_route(logits, None, k, cfg.router_kind != "softmax_topk", ids, wts)
+    if cfg.router_kind in ("deepseek_v2", "deepseek_v3"):
+        ids, wts = route_deepseek(cfg, logits, getattr(lw, "router_select_b", None))
+    else:
+        k_ops.moe_route(logits, None, k, cfg.router_kind != "softmax_topk", ids, wts)
     share = e_local / cfg.num_experts
     bn = _token_tile(T * k * share / max(e_local, 1))
     rows_cap = -(-(T * k + e_local * (bn - 1)) // bn) * bn

@@ -42,6 +42,9 @@ class LayerWeights:
     exp_gate_up_b: Optional[torch.Tensor] = None    # [E_local, 2*I]
     exp_down: Optional[torch.Tensor] = None         # [E_local, H, I]
     exp_down_b: Optional[torch.Tensor] = None       # [E_local, H]
+    router_select_b: Optional[torch.Tensor] = None  # [E] added to the scores for the selection only (DeepSeek-V3)
+    shared_gate_up: Optional[torch.Tensor] = None   # [2*Is, H] always-on shared experts as one dense GLU
+    shared_down: Optional[torch.Tensor] = None      # [H, Is]
     # recurrent layers (Mamba, delta rule, short convolution): the mixer's tensors by name; wqkv / wo stay None
     mixer: Optional[Dict[str, torch.Tensor]] = None
     # packed formats keep their payload here (format name -> tensors)
@@ -255,7 +258,16 @@ def init_random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, se
             else:
                 mixer = init_random_mixer(cfg, cfg.layer_kind(li), full, li, dtype, device)
             lw = LayerWeights(attn_norm=ones(H), wqkv=None, wo=None, ffn_norm=ones(H) if has_ffn else None, mixer=mixer)
-            if has_ffn:
+            if cfg.ffn_kind(li) == "moe":
+                E, I, Is = cfg.num_experts, cfg.moe_intermediate_size, cfg.shared_intermediate_size
+                lw.router_w = full((E, H), li, 20, std=0.5)
+                if cfg.router_kind == "deepseek_v3":
+                    lw.router_select_b = full((E,), li, 21, std=0.1).float()
+                lw.exp_gate_up, lw.exp_down = full((E, 2 * I, H), li, 22), full((E, H, I), li, 23)
+                if Is:
+                    lw.shared_gate_up = torch.cat([full((Is, H), li, 26), full((Is, H), li, 27)], 0).contiguous()
+                    lw.shared_down = full((H, Is), li, 28)
+            elif has_ffn:
                 I = cfg.intermediate_size
                 lw.w_gate_up = torch.cat([full((I, H), li, 4), full((I, H), li, 5)], 0).contiguous()
                 lw.w_down = full((H, I), li, 6)

@@ -105,7 +105,7 @@ class LLMEngine:
             # row that padding sequences of a captured step write to
             from ..models.recurrent import RecurrentState
             self.rstate = RecurrentState(model_cfg, self.layer_range, self.cfg.max_num_seqs + 9, self.device,
-                                         self.weights.final_norm.dtype)
+                                         self.weights.embed.dtype)
         self.decoder = Decoder(model_cfg, self.weights, self.kv, self.ops, self.spec, tp_group,
                                layer_range=self.layer_range, first_stage=self.first_stage,
                                last_stage=self.last_stage, rstate=self.rstate)

@@ -254,3 +254,61 @@ def test_rwkv7_matches_token_by_token_recurrence(tmp_path):
     sp = SamplingParams(max_tokens=6, temperature=0.0)
     big = LLMEngine(cfg2, EngineConfig(max_num_seqs=2, max_num_batched_tokens=64, max_model_len=128, num_kv_blocks=32), device="cpu", weights=w)
     assert eng.generate([toks[:37], toks[:5]], sp) == big.generate([toks[:37], toks[:5]], sp)
+
+
+@pytest.mark.parametrize("version", [2, 3])
+def test_deepseek_routed_and_shared_experts_match_transformers(tmp_path, version):
+    """First layer dense, then routed experts with shared experts: V2 with softmax scores and plain top-k, V3 with
+    sigmoid scores, a selection bias, groups ranked by their two best experts and renormalised weights."""
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    torch.manual_seed(0)
+    common = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+                  num_key_value_heads=4, kv_lora_rank=32, q_lora_rank=None, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                  first_k_dense_replace=1, n_routed_experts=8, n_shared_experts=2, num_experts_per_tok=3, moe_intermediate_size=32,
+                  n_group=4, topk_group=2, routed_scaling_factor=1.5, max_position_embeddings=256)
+    if version == 2:
+        from transformers import DeepseekV2Config, DeepseekV2ForCausalLM
+        # (the group-limited V2 router of this transformers version reads an attribute it never sets; "greedy" is
+        # the router of the published V2-Lite checkpoints)
+        m = DeepseekV2ForCausalLM(DeepseekV2Config(topk_method="greedy", norm_topk_prob=False, **common))
+    else:
+        from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
+        m = DeepseekV3ForCausalLM(DeepseekV3Config(norm_topk_prob=True, **common))
+    m = m.eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if n.endswith("gate.weight"):
+                p.mul_(20.0)                                     # spread the scores so that the selection is not a coin toss
+            if n.endswith("e_score_correction_bias"):
+                p.copy_(0.2 * torch.randn_like(p))
+        for n, b in m.named_buffers():
+            if n.endswith("e_score_correction_bias"):
+                b.copy_(0.2 * torch.randn_like(b))
+    d = str(tmp_path / f"dsmoe{version}")
+    m.save_pretrained(d, safe_serialization=True)
+    cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
+    assert cfg.ffn_kinds == ["glu", "moe", "moe"] and cfg.shared_intermediate_size == 64
+    assert cfg.router_groups == (1 if version == 2 else 4)
+    assert w.layers[1].router_w is not None and w.layers[0].router_w is None
+    assert (w.layers[1].router_select_b is not None) == (version == 3)
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=32, max_model_len=128, num_kv_blocks=32, block_size=16),
+                    device="cpu", weights=w)
+    toks = torch.randint(0, 300, (50,), generator=torch.Generator().manual_seed(1)).tolist()
+    got = eng.token_logits(toks)
+    with torch.no_grad():
+        want = m(torch.tensor([toks])).logits[0].float()
+    err = (got - want).abs().max(dim=1).values / float(want.abs().max())
+    # bf16 rounding of the router scores can flip a near-tie for a single token; the rest must agree closely
+    assert float(err.median()) < 2e-2 and int((err > 5e-2).sum()) <= 2, err
+
+
+def test_group_limited_router_keeps_the_best_groups():
+    """V2 group-limited routing: only experts of the `topk_group` groups with the highest best score can be chosen."""
+    from fllm_b200.models.moe import route_deepseek
+    cfg = ModelConfig(num_experts=8, experts_per_token=3, router_kind="deepseek_v2", router_groups=4, router_topk_groups=2,
+                      router_scale=2.0, router_norm_topk=False)
+    logits = torch.tensor([[5.0, 0.1, 0.2, 0.3, 4.0, 3.9, 3.0, 2.9]])       # groups (0,1) (2,3) (4,5) (6,7): best are 0 and 2
+    ids, w = route_deepseek(cfg, logits, None)
+    assert sorted(ids[0].tolist()) == [0, 4, 5]                             # expert 6 (3.0) loses to 5 although its group is third
+    p = torch.softmax(logits, -1)[0]
+    assert torch.allclose(w[0].sort().values, (2.0 * p[[0, 4, 5]]).sort().values)

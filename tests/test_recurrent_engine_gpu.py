@@ -76,6 +76,21 @@ def test_latent_attention_engine():
     assert _engine(cfg, chunk=512, graphs=True, weights=nat.weights).generate(prompts, sp) == want
 
 
+def test_deepseek_moe_engine():
+    """Latent attention + routed experts (family router in tensor ops, grouped GEMMs) + shared experts on the GPU against
+    the PyTorch statement on the same weights."""
+    from fllm_b200.ops.reference import RefOps
+    cfg = preset("deepseek-moe-tiny")
+    nat = _engine(cfg)
+    ref = _engine(cfg, ops=RefOps(), weights=nat.weights)
+    toks = torch.randint(0, 4096, (100,), generator=torch.Generator().manual_seed(5)).tolist()
+    a, b = nat.token_logits(toks), ref.token_logits(toks)
+    err = (a - b).norm(dim=1) / b.norm(dim=1)
+    assert float(err.median()) < 2e-2 and int((err > 0.1).sum()) <= 3, err          # a near-tie in the router may flip a row
+    out = _engine(cfg, chunk=512, graphs=True, weights=nat.weights).generate([toks[:20], toks[30:70]], SamplingParams(max_tokens=8, temperature=0.0))
+    assert [len(o) for o in out] == [8, 8]
+
+
 def test_rwkv7_engine():
     from fllm_b200.ops.reference import RefOps
     cfg = preset("rwkv7-tiny")
