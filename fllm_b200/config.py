@@ -536,6 +536,7 @@ class EngineConfig:
     scheduling_policy: str = "fcfs"      # fcfs | priority
     preemption: str = "recompute"        # recompute | swap (KV of a preempted request parked in host memory)
     swap_space_gb: float = 4.0           # host memory for swapped-out KV
+    state_cache_gb: float = 0.0          # recurrent models: host memory for state checkpoints on block boundaries (0 = no prefix reuse)
     kv_tier_host_gb: float = 0.0         # host memory for evicted prefix-cache blocks (0 = no tier)
     kv_tier_disk_dir: Optional[str] = None   # directory for blocks that fall out of the host tier (default: $FLLM_KV_DISK_DIR)
     kv_tier_disk_gb: float = 0.0

@@ -217,6 +217,13 @@ void gather_rows(const Tensor& x, const Tensor& rows, Tensor out) {
                          (int)rows.numel(), (int)x.size(1), cur_stream());
 }
 
+void softcap_(Tensor x, double cap) {
+  check_bf16(x, "x"); check_rows(x, "x");
+  TORCH_CHECK(cap > 0, "softcap_: the cap must be positive");
+  c10::cuda::CUDAGuard guard(x.device());
+  fllm::softcap_rows_bf16(x.data_ptr(), x.stride(0), (int)x.size(0), (int)x.size(1), (float)cap, cur_stream());
+}
+
 void attention_generic(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
                        const Tensor& block_tables, const Tensor& row_seq, const Tensor& positions,
                        Tensor out, int64_t hq, int64_t hkv, int64_t head_dim, double scale,
@@ -409,6 +416,7 @@ TORCH_LIBRARY(fllm_b200, m) {
   m.def("rope_kv_write(Tensor(a!) qkv, Tensor positions, Tensor? slots, Tensor inv_freq, Tensor? q_norm_w, Tensor? k_norm_w, Tensor(b!) k_cache, Tensor(c!) v_cache, int hq, int hkv, int head_dim, int rot_dim, int rope_style, float eps, float attn_factor) -> ()", &rope_kv_write);
   m.def("glu(Tensor x, Tensor(a!) out, int act_kind, float alpha, float limit) -> ()", &glu);
   m.def("gather_rows(Tensor x, Tensor rows, Tensor(a!) out) -> ()", &gather_rows);
+  m.def("softcap_(Tensor(a!) x, float cap) -> ()", &softcap_);
   m.def("attention_generic(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor row_seq, Tensor positions, Tensor(a!) out, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap, Tensor? tree_mask=None, Tensor? tree_base=None) -> ()", &attention_generic);
   m.def("attention_tc(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor q_starts, Tensor kv_lens, Tensor(a!) out, int num_seqs, int max_q_len, int min_q_len, int max_kv_len, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap, Tensor? workspace, Tensor? status=None, bool bidirectional=False) -> int", &attention_tc);
   m.def("argmax(Tensor logits, Tensor(a!) out_ids, Tensor? out_vals, int id_offset) -> ()", &argmax);

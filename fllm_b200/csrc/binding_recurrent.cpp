@@ -105,22 +105,45 @@ void gated_rmsnorm(const Tensor& x, const optional<Tensor>& z, const Tensor& w, 
                       (int)x.size(1), (int)group_size, (float)eps, norm_before_gate ? 1 : 0, cur_stream());
 }
 
-void attention_mla(const Tensor& q, const Tensor& cache, const Tensor& block_tables, const Tensor& row_seq, const Tensor& positions, Tensor out,
-                   double scale) {
-  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.dim() == 3 && q.is_contiguous() && q.size(2) == 576,
-              "q: contiguous bf16 [T, H, 576]");
+// q_abs [H, T, 512] or [T, H, 512] (any strides with a unit inner one), q_pe [T, H, 64], out like q_abs
+void attention_mla(const Tensor& q_abs, const Tensor& q_pe, const Tensor& cache, const Tensor& block_tables, const Tensor& row_seq,
+                   const Tensor& positions, Tensor out, bool head_major, double scale) {
+  TORCH_CHECK(q_abs.is_cuda() && q_abs.scalar_type() == at::kBFloat16 && q_abs.dim() == 3 && q_abs.stride(2) == 1 && q_abs.size(2) == 512,
+              "q_abs: bf16 [., ., 512] with a unit inner stride");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.dim() == 3 && out.stride(2) == 1 && out.sizes() == q_abs.sizes(), "out: like q_abs");
+  const int td = head_major ? 1 : 0, hd = head_major ? 0 : 1;
+  const int64_t T = q_abs.size(td), H = q_abs.size(hd);
+  TORCH_CHECK(q_pe.scalar_type() == at::kBFloat16 && q_pe.is_contiguous() && q_pe.dim() == 3 && q_pe.size(0) == T && q_pe.size(1) == H &&
+                  q_pe.size(2) == 64, "q_pe: contiguous bf16 [T, H, 64]");
   TORCH_CHECK(cache.scalar_type() == at::kBFloat16 && cache.dim() == 3 && cache.is_contiguous() && cache.size(2) == 576,
               "cache: contiguous bf16 [blocks, block_size, 576]");
-  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.is_contiguous() && out.dim() == 3 && out.size(0) == q.size(0) &&
-                  out.size(1) == q.size(1) && out.size(2) == 512, "out: contiguous bf16 [T, H, 512]");
   TORCH_CHECK(block_tables.scalar_type() == at::kInt && block_tables.dim() == 2 && block_tables.stride(1) == 1 &&
                   row_seq.scalar_type() == at::kInt && positions.scalar_type() == at::kInt && row_seq.is_contiguous() &&
-                  positions.is_contiguous() && row_seq.numel() >= q.size(0) && positions.numel() >= q.size(0),
+                  positions.is_contiguous() && row_seq.numel() >= T && positions.numel() >= T,
               "block_tables [B, max_blocks], row_seq [T], positions [T]: int32");
+  c10::cuda::CUDAGuard guard(q_abs.device());
+  fllm::attention_mla_bf16(q_abs.data_ptr(), q_abs.stride(td), q_abs.stride(hd), q_pe.data_ptr(), cache.data_ptr(), block_tables.data_ptr<int>(),
+                           (int)block_tables.stride(0), row_seq.data_ptr<int>(), positions.data_ptr<int>(), out.data_ptr(), out.stride(td),
+                           out.stride(hd), (int)T, (int)H, (int)cache.size(1), (float)scale, cur_stream());
+}
+
+// ckv bf16 [T, >= 576] rows, q bf16 [T, H, head] contiguous with the rotary values of a head at rope_offset
+void mla_prepare(const Tensor& ckv, const Tensor& q, int64_t rope_offset, const Tensor& positions, const Tensor& slots, const Tensor& inv_freq,
+                 double attn_factor, const Tensor& norm_w, double eps, Tensor cache, Tensor q_pe) {
+  TORCH_CHECK(rows_bf16(ckv) && ckv.size(1) >= 576, "ckv: bf16 rows of at least 576 values");
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.dim() == 3 && q.is_contiguous() && rope_offset + 64 <= q.size(2) &&
+                  q.size(0) == ckv.size(0), "q: contiguous bf16 [T, H, head]");
+  TORCH_CHECK(inv_freq.scalar_type() == at::kFloat && inv_freq.is_contiguous() && inv_freq.numel() == 32, "inv_freq: fp32 [32]");
+  TORCH_CHECK(norm_w.scalar_type() == at::kBFloat16 && norm_w.is_contiguous() && norm_w.numel() == 512, "norm_w: bf16 [512]");
+  TORCH_CHECK(cache.scalar_type() == at::kBFloat16 && cache.is_contiguous() && cache.dim() == 3 && cache.size(2) == 576, "cache: bf16 [blocks, block_size, 576]");
+  TORCH_CHECK(q_pe.scalar_type() == at::kBFloat16 && q_pe.is_contiguous() && q_pe.dim() == 3 && q_pe.size(0) == q.size(0) &&
+                  q_pe.size(1) == q.size(1) && q_pe.size(2) == 64, "q_pe: contiguous bf16 [T, H, 64]");
+  TORCH_CHECK(positions.scalar_type() == at::kInt && slots.scalar_type() == at::kInt && positions.is_contiguous() && slots.is_contiguous() &&
+                  positions.numel() >= q.size(0) && slots.numel() >= q.size(0), "positions, slots: int32 [T]");
   c10::cuda::CUDAGuard guard(q.device());
-  fllm::attention_mla_bf16(q.data_ptr(), q.stride(0), cache.data_ptr(), block_tables.data_ptr<int>(), (int)block_tables.stride(0),
-                           row_seq.data_ptr<int>(), positions.data_ptr<int>(), out.data_ptr(), out.stride(0), (int)q.size(0), (int)q.size(1),
-                           (int)cache.size(1), (float)scale, cur_stream());
+  fllm::mla_prepare_bf16(ckv.data_ptr(), ckv.stride(0), q.data_ptr(), q.stride(0), (int)q.stride(1), (int)rope_offset, positions.data_ptr<int>(),
+                         slots.data_ptr<int>(), inv_freq.data_ptr<float>(), (float)attn_factor, norm_w.data_ptr(), (float)eps, cache.data_ptr(),
+                         q_pe.data_ptr(), (int)q.size(0), (int)q.size(1), cur_stream());
 }
 }  // namespace
 
@@ -136,7 +159,9 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("matrix_state_scan(int kind, Tensor r, Tensor k, Tensor v, Tensor? a, Tensor? b, Tensor w, Tensor? u, Tensor? beta, Tensor(a!) state, "
         "Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y, int H, int DK, int DV, int kv_ratio, bool l2norm, float q_scale) -> ()",
         &matrix_state_scan);
-  m.def("attention_mla(Tensor q, Tensor cache, Tensor block_tables, Tensor row_seq, Tensor positions, Tensor(a!) out, float scale) -> ()",
-        &attention_mla);
+  m.def("attention_mla(Tensor q_abs, Tensor q_pe, Tensor cache, Tensor block_tables, Tensor row_seq, Tensor positions, Tensor(a!) out, "
+        "bool head_major, float scale) -> ()", &attention_mla);
+  m.def("mla_prepare(Tensor ckv, Tensor q, int rope_offset, Tensor positions, Tensor slots, Tensor inv_freq, float attn_factor, Tensor norm_w, "
+        "float eps, Tensor(a!) cache, Tensor(b!) q_pe) -> ()", &mla_prepare);
   m.def("gated_rmsnorm(Tensor x, Tensor? z, Tensor w, Tensor(a!) y, int group_size, float eps, bool norm_before_gate) -> ()", &gated_rmsnorm);
 }

@@ -8,6 +8,8 @@
 // dtype is a run-time switch; here bf16 is the only activation dtype.
 #include <cuda_fp8.h>
 
+#include <algorithm>
+
 #include "fllm_ops.h"
 #include "ptx.cuh"
 #include "tma_host.h"
@@ -624,6 +626,28 @@ void gather_rows_bf16(const void* x, long long ldx, const int* rows, void* out, 
   gather_rows_kernel<<<n_rows, 128, 0, s>>>((const __nv_bfloat16*)x, ldx, rows,
                                             (__nv_bfloat16*)out, hidden);
   cuda_check(cudaGetLastError(), "gather_rows_kernel");
+}
+
+// ---- logit soft-cap: x = cap * tanh(x / cap), in place over bf16 rows (Gemma-2 final logits; the reference keeps it with
+// its small architecture ops in rust/engine/cuda/arch_ops.cu) -------------------------------------------------------
+__global__ void softcap_rows_kernel(__nv_bfloat16* __restrict__ x, long long ldx, int cols, float cap, float inv_cap) {
+  __nv_bfloat16* row = x + (size_t)blockIdx.y * ldx;
+  for (int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2; c < cols; c += gridDim.x * blockDim.x * 2) {
+    if (c + 1 < cols) {
+      const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row + c));
+      *reinterpret_cast<__nv_bfloat162*>(row + c) = __floats2bfloat162_rn(cap * tanhf(v.x * inv_cap), cap * tanhf(v.y * inv_cap));
+    } else {
+      row[c] = __float2bfloat16(cap * tanhf(__bfloat162float(row[c]) * inv_cap));
+    }
+  }
+}
+
+void softcap_rows_bf16(void* x, long long ldx, int rows, int cols, float cap, cudaStream_t s) {
+  if (rows <= 0 || cols <= 0) return;
+  if ((ldx & 1) || (reinterpret_cast<uintptr_t>(x) & 3)) throw std::runtime_error("softcap_rows_bf16: even leading dimension, 4-byte aligned rows");
+  const int bx = std::min((cols / 2 + 255) / 256, 64);
+  softcap_rows_kernel<<<dim3(std::max(bx, 1), rows), 256, 0, s>>>((__nv_bfloat16*)x, ldx, cols, cap, 1.f / cap);
+  cuda_check(cudaGetLastError(), "softcap_rows_kernel");
 }
 
 }  // namespace fllm

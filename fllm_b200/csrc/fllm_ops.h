@@ -291,9 +291,19 @@ int matrix_state_scan(int kind, const void* r, long long ldr, const void* k, lon
 void gated_rmsnorm(const void* x, long long ldx, const void* z, long long ldz, const void* w, int wlen, void* y, long long ldy, int T,
                    int D, int group_size, float eps, int norm_before_gate, cudaStream_t stream);
 
-// Latent attention (attention_mla.cu): q [tokens][H][576] = absorbed query | rotated query part, cache
-// [blocks][block_size][576] = latent | rotated key part, out [tokens][H][512].
-void attention_mla_bf16(const void* q, long long ldq, const void* cache, const int* block_tables, int max_blocks, const int* row_seq,
-                        const int* positions, void* out, long long ldo, int tokens, int H, int block_size, float scale, cudaStream_t s);
+// Latent attention (attention_mla.cu). Element (t, h, e) of the absorbed query part sits at q_abs[t * qa_t + h * qa_h + e]
+// (e < 512), the rotated part in q_pe [tokens][H][64]; cache [blocks][block_size][576] = latent | rotated key part; output
+// element (t, h, e) at out[t * o_t + h * o_h + e].
+void attention_mla_bf16(const void* q_abs, long long qa_t, long long qa_h, const void* q_pe, const void* cache, const int* block_tables,
+                        int max_blocks, const int* row_seq, const int* positions, void* out, long long o_t, long long o_h, int tokens,
+                        int H, int block_size, float scale, cudaStream_t s);
+// RMSNorm of the latent + rotation of the shared key part into the cache row of each token (slot < 0: no write), and rotation
+// of every head's rotary query values into q_pe [tokens][H][64].
+void mla_prepare_bf16(const void* ckv, long long ldc, const void* q, long long ldq, int q_head_stride, int q_rope_offset,
+                      const int* positions, const int* slots, const float* inv_freq, float attn_factor, const void* norm_w, float eps,
+                      void* cache, void* q_pe, int tokens, int H, cudaStream_t s);
+
+// x = cap * tanh(x / cap) in place over bf16 rows
+void softcap_rows_bf16(void* x, long long ldx, int rows, int cols, float cap, cudaStream_t s);
 
 }  // namespace fllm

@@ -273,7 +273,7 @@ class Decoder:
             if hasattr(ops, "launches"):
                 ops.launches += 1
             if cfg.logit_softcap > 0:
-                lg = (cfg.logit_softcap * torch.tanh(lg.float() / cfg.logit_softcap)).to(lg.dtype)
+                lg = ops.softcap_(lg, cfg.logit_softcap)
             return lg
         # the head runs on every row (it is the consumer that retires the gathered rows); the
         # wanted rows are selected afterwards
@@ -283,7 +283,7 @@ class Decoder:
         if not (b.all_decode and b.logit_rows.numel() == T):
             lg = lg.index_select(0, b.logit_rows.long())
         if cfg.logit_softcap > 0:
-            lg = (cfg.logit_softcap * torch.tanh(lg.float() / cfg.logit_softcap)).to(lg.dtype)
+            lg = ops.softcap_(lg, cfg.logit_softcap)
         return lg
 
     def logits(self, x: torch.Tensor, delta: Optional[torch.Tensor], b: StepBatch) -> torch.Tensor:
@@ -302,7 +302,7 @@ class Decoder:
             self.last_hidden = hs                  # [logit rows, hidden]: the embeddings API reads it
         lg = ops.linear(hs, self.w.lm_head)
         if cfg.logit_softcap > 0:
-            lg = (cfg.logit_softcap * torch.tanh(lg.float() / cfg.logit_softcap)).to(lg.dtype)
+            lg = ops.softcap_(lg, cfg.logit_softcap)
         return lg
 
     def forward(self, b: StepBatch) -> torch.Tensor:

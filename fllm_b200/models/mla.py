@@ -17,11 +17,11 @@ from ..config import ModelConfig
 
 
 class MlaCache:
-    """Paged latent pool [layers, blocks + 1, block_size, width]; the extra block takes the writes of padding rows."""
+    """Paged latent pool [layers, blocks, block_size, width]."""
 
     def __init__(self, num_layers: int, num_blocks: int, block_size: int, width: int, device, dtype=torch.bfloat16):
         self.num_blocks, self.block_size, self.width = num_blocks, block_size, width
-        self.store = torch.zeros(num_layers, num_blocks + 1, block_size, width, device=device, dtype=dtype)
+        self.store = torch.zeros(num_layers, num_blocks, block_size, width, device=device, dtype=dtype)
 
     def layer(self, i: int) -> torch.Tensor:
         return self.store[i]
@@ -29,16 +29,6 @@ class MlaCache:
     @staticmethod
     def bytes_per_block(num_layers: int, block_size: int, width: int, elem: int = 2) -> int:
         return num_layers * block_size * width * elem
-
-
-def _rope_pairs(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    """Rotate neighbouring pairs (x[2i], x[2i+1]) by the angle of frequency i; x [..., d], cos / sin [T, d/2]
-    broadcast over the dimensions between the first and the last."""
-    xf = x.float().unflatten(-1, (-1, 2))
-    a, b = xf[..., 0], xf[..., 1]
-    while cos.dim() < a.dim():
-        cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
-    return torch.stack([a * cos - b * sin, a * sin + b * cos], -1).flatten(-2).to(x.dtype)
 
 
 def mla_block(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
@@ -51,19 +41,12 @@ def mla_block(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
     else:
         q = ops.linear(h, m["q_proj"])
     q = q.view(T, H, dn + dr)
-    ckv = ops.linear(h, m["kv_a"])[:, :R + dr]
-    ang = b.positions.float()[:, None] * dec.inv_freq[None, :]
-    cos, sin = torch.cos(ang) * dec.attn_factor, torch.sin(ang) * dec.attn_factor
-    latent = ops.rmsnorm(ckv[:, :R].contiguous(), None, m["kv_a_norm"], cfg.rms_eps)
-    row = torch.cat([latent, _rope_pairs(ckv[:, R:], cos, sin)], -1)
+    ckv = ops.linear(h, m["kv_a"])                                     # [T, pad8(R + dr)]
     cache = dec.kv.layer(dec.kv_index[li])
-    flat = cache.view(-1, R + dr)
-    scratch = dec.kv.num_blocks * dec.kv.block_size                   # first row of the extra block
-    flat.index_copy_(0, torch.where(b.slots < 0, torch.full_like(b.slots, scratch), b.slots).long(), row.to(flat.dtype))
-    q_abs = torch.bmm(q[:, :, :dn].transpose(0, 1), m["w_uk"]).transpose(0, 1)              # [T, H, R]
-    qfull = torch.cat([q_abs, _rope_pairs(q[:, :, dn:], cos, sin)], -1).contiguous()        # [T, H, R + dr]
-    o_lat = ops.attention_mla(qfull, cache, b.block_tables, b.row_seq, b.positions, R, dec.scale)       # [T, H, R]
-    o = torch.bmm(o_lat.transpose(0, 1), m["w_uv"]).transpose(0, 1).reshape(T, H * dv)
+    q_pe = ops.mla_prepare(ckv, q, dn, b.positions, b.slots, dec.inv_freq, dec.attn_factor, m["kv_a_norm"], cfg.rms_eps, cache)
+    q_abs = torch.bmm(q[:, :, :dn].transpose(0, 1), m["w_uk"])                                # [H, T, R]
+    o_lat = ops.attention_mla(q_abs, q_pe, cache, b.block_tables, b.row_seq, b.positions, dec.scale)     # [H, T, R]
+    o = torch.bmm(o_lat, m["w_uv"]).transpose(0, 1).reshape(T, H * dv)
     return ops.linear(o, m["wo"], m.get("bo"))
 
 

@@ -158,6 +158,12 @@ class NativeOps(RecurrentNative):
         self.launches += 1
         return out
 
+    def softcap_(self, x, cap: float):
+        """x = cap * tanh(x / cap) in place (final-logit soft-cap)."""
+        self.k.softcap_(x, float(cap))
+        self.launches += 1
+        return x
+
     def attention_tree(self, q, k_cache, v_cache, block_tables, row_seq, positions, tree_mask, tree_base, hq, hkv,
                        head_dim, scale, window=0, sinks=None, softcap=0.0):
         """Attention for the nodes of draft trees: row t sees the first tree_base[t] tokens of its sequence and the

@@ -145,19 +145,43 @@ class RecurrentRef:
         return out.to(x.dtype)
 
 
-    def attention_mla(self, q, cache, block_tables, row_seq, positions, latent, scale):
-        """Latent attention: q [T, H, W] against cache rows [blocks, block_size, W]; the values are the first
-        ``latent`` entries of the same rows. Returns [T, H, latent]."""
-        T, H, W = q.shape
-        R = latent
+    def mla_prepare(self, ckv, q, rope_offset, positions, slots, inv_freq, attn_factor, norm_w, eps, cache):
+        """Latent attention, per token: RMSNorm of the latent part of ``ckv`` [T, R + dr] and rotation of its last dr
+        values (neighbouring pairs) into cache row ``slots[t]`` (negative: no write); returns the rotated rotary part
+        of every head of ``q`` [T, H, head] as [T, H, dr]."""
+        dr = 2 * inv_freq.numel()
+        R = cache.shape[-1] - dr
+        ang = positions[:ckv.shape[0]].float()[:, None] * inv_freq[None, :]
+        cos, sin = torch.cos(ang) * attn_factor, torch.sin(ang) * attn_factor
+
+        def rot(x):                                   # [T, ..., dr]
+            xf = x.float().unflatten(-1, (-1, 2))
+            a, b = xf[..., 0], xf[..., 1]
+            c, s_ = cos, sin
+            while c.dim() < a.dim():
+                c, s_ = c.unsqueeze(1), s_.unsqueeze(1)
+            return torch.stack([a * c - b * s_, a * s_ + b * c], -1).flatten(-2)
+        lat = ckv[:, :R].float()
+        lat = lat * torch.rsqrt(lat.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()
+        row = torch.cat([lat, rot(ckv[:, R:R + dr])], -1).to(cache.dtype)
+        keep = slots[:ckv.shape[0]] >= 0
+        cache.view(-1, R + dr)[slots[:ckv.shape[0]][keep].long()] = row[keep]
+        return rot(q[:, :, rope_offset:rope_offset + dr]).to(q.dtype)
+
+    def attention_mla(self, q_abs, q_pe, cache, block_tables, row_seq, positions, scale):
+        """Latent attention: absorbed queries ``q_abs`` [H, T, R] and rotated parts ``q_pe`` [T, H, dr] against cache rows
+        [blocks, block_size, R + dr]; the values are the first R entries of the same rows. Returns [H, T, R]."""
+        H, T, R = q_abs.shape
+        W = cache.shape[-1]
         bs = cache.shape[1]
-        out = torch.empty(T, H, R, dtype=q.dtype, device=q.device)
+        out = torch.empty(H, T, R, dtype=q_abs.dtype, device=q_abs.device)
         for t in range(T):
             n = int(positions[t]) + 1
             nblk = (n + bs - 1) // bs
             rows = cache[block_tables[int(row_seq[t]), :nblk].long()].reshape(nblk * bs, W)[:n].float()
-            p = torch.softmax(q[t].float() @ rows.T * scale, -1)
-            out[t] = (p @ rows[:, :R]).to(q.dtype)
+            qt = torch.cat([q_abs[:, t].float(), q_pe[t].float()], -1)
+            p = torch.softmax(qt @ rows.T * scale, -1)
+            out[:, t] = (p @ rows[:, :R]).to(out.dtype)
         return out
 
 
@@ -198,11 +222,18 @@ class RecurrentNative:
         self.launches += 1
         return y
 
-    def attention_mla(self, q, cache, block_tables, row_seq, positions, latent, scale):
-        T, H, W = q.shape
-        if (W, latent) != (576, 512):            # the kernel is built for the 512 + 64 rows of the DeepSeek family
-            return RecurrentRef.attention_mla(self, q, cache, block_tables, row_seq, positions, latent, scale)
-        out = torch.empty(T, H, latent, dtype=q.dtype, device=q.device)
-        self.k.attention_mla(q, cache, block_tables, row_seq, positions, out, float(scale))
+    def mla_prepare(self, ckv, q, rope_offset, positions, slots, inv_freq, attn_factor, norm_w, eps, cache):
+        if cache.shape[-1] != 576 or inv_freq.numel() != 32:      # the kernels are built for the 512 + 64 rows of the DeepSeek family
+            return RecurrentRef.mla_prepare(self, ckv, q, rope_offset, positions, slots, inv_freq, attn_factor, norm_w, eps, cache)
+        q_pe = torch.empty(q.shape[0], q.shape[1], 64, dtype=q.dtype, device=q.device)
+        self.k.mla_prepare(ckv, q, int(rope_offset), positions, slots, inv_freq, float(attn_factor), norm_w, float(eps), cache, q_pe)
+        self.launches += 1
+        return q_pe
+
+    def attention_mla(self, q_abs, q_pe, cache, block_tables, row_seq, positions, scale):
+        if cache.shape[-1] != 576 or q_abs.shape[-1] != 512:
+            return RecurrentRef.attention_mla(self, q_abs, q_pe, cache, block_tables, row_seq, positions, scale)
+        out = torch.empty(q_abs.shape, dtype=q_abs.dtype, device=q_abs.device)
+        self.k.attention_mla(q_abs, q_pe, cache, block_tables, row_seq, positions, out, True, float(scale))
         self.launches += 1
         return out

@@ -145,6 +145,10 @@ class RefOps(RecurrentRef):
             out[t] = torch.einsum("hn,hnd->hd", p, v).reshape(-1).to(q.dtype)
         return out
 
+    def softcap_(self, x, cap: float):
+        x.copy_((cap * torch.tanh(x.float() / cap)).to(x.dtype))
+        return x
+
     def attention_tree(self, q, k_cache, v_cache, block_tables, row_seq, positions, tree_mask, tree_base, hq, hkv,
                        head_dim, scale, window=0, sinks=None, softcap=0.0):
         """Rows are nodes of draft trees: the context plus the ancestors named by a 64-bit mask per row."""

@@ -60,6 +60,10 @@ class BlockManager:
         self.enable_prefix_caching = enable_prefix_caching
         self.refs = [0] * num_blocks
         self.state_free: Optional[List[int]] = None          # rows of the recurrent-state pools (hybrid models only)
+        # recurrent-state checkpoints: a cached prefix is usable only up to a block whose hash has a state copy;
+        # state_restore(hash, row) writes that copy into the new sequence's row
+        self.state_has = None
+        self.state_restore = None
         self.free: List[int] = list(range(num_blocks - 1, -1, -1))   # never-used / invalidated blocks
         self.cached: "OrderedDict[int, bytes]" = OrderedDict()       # ref==0 blocks with valid content (LRU)
         self.hash_to_block: Dict[bytes, int] = {}
@@ -141,6 +145,10 @@ class BlockManager:
             blocks.append(b)
             hashes.append(h)
             parent = h
+        if self.state_has is not None:
+            while hashes and not self.state_has(hashes[-1]):
+                blocks.pop()
+                hashes.pop()
         if blocks:
             self.stats["prefix_hits"] += 1
         return blocks, hashes
@@ -154,7 +162,7 @@ class BlockManager:
             if self.refs[b] == 0:
                 self.cached.pop(b, None)
             self.refs[b] += 1
-        if self.tier_has is not None and self.enable_prefix_caching:
+        if self.tier_has is not None and self.enable_prefix_caching and self.state_has is None:
             # the prompt may continue with blocks that were evicted to the lower tier: bring them back while the
             # chain holds and the pool has room beyond its watermark
             bs = self.block_size
@@ -179,6 +187,11 @@ class BlockManager:
             if not self.state_free:
                 raise RuntimeError("no free recurrent-state row: more live sequences than max_num_seqs allows")
             sb.state_slot = self.state_free.pop()
+            if hashes and self.state_restore is not None and not self.state_restore(hashes[-1], sb.state_slot):
+                # the copy went away between the match and now: compute the prompt from its first token
+                for b in blocks:
+                    self._release(b)
+                sb.table, sb.hashes, sb.num_tokens = [], [], 0
         self.seqs[seq_id] = sb
         return sb.num_tokens
 

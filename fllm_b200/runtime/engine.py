@@ -83,7 +83,11 @@ class LLMEngine:
             # preempted sequence is recomputed.
             if tp > 1:
                 raise NotImplementedError("recurrent layers are not cut over tensor-parallel ranks")
-            self.cfg = dataclasses.replace(self.cfg, enable_prefix_caching=False, speculative="off", preemption="recompute")
+            # With state checkpoints (state_cache_gb > 0) a prefix is reusable at the block boundaries where a copy
+            # of the state was kept; without them prefix caching is off.
+            keep_prefix = self.cfg.enable_prefix_caching and self.cfg.state_cache_gb > 0
+            self.cfg = dataclasses.replace(self.cfg, enable_prefix_caching=keep_prefix, speculative="off", preemption="recompute",
+                                           kv_tier_host_gb=0.0, kv_tier_disk_gb=0.0)
         self.block_size = self.cfg.block_size
         self.max_blocks_per_seq = -(-self.cfg.max_model_len // self.block_size)
         num_blocks = self.cfg.num_kv_blocks or self._size_kv_pool()
@@ -122,6 +126,12 @@ class LLMEngine:
             self.blocks.enable_state_slots(self.rstate.slots - 1)
         window = model_cfg.sliding_window if (model_cfg.sliding_window and model_cfg.window_pattern is None) else 0
         self.scheduler = Scheduler(self.cfg, self.blocks, window)
+        self.state_ckpt = None
+        if self.rstate is not None and self.cfg.enable_prefix_caching:
+            from .state_cache import StateCheckpoints
+            self.state_ckpt = StateCheckpoints(self.rstate, int(self.cfg.state_cache_gb * (1 << 30)))
+            self.blocks.state_has, self.blocks.state_restore = self.state_ckpt.has, self.state_ckpt.restore
+            self.scheduler.chunk_align = self.block_size
         self.kv_tier = None
         disk_dir = self.cfg.kv_tier_disk_dir or os.environ.get("FLLM_KV_DISK_DIR")
         if self.cfg.enable_prefix_caching and (self.cfg.kv_tier_host_gb > 0 or (disk_dir and self.cfg.kv_tier_disk_gb > 0)):
@@ -769,6 +779,11 @@ class LLMEngine:
             if not s.wants_logits:
                 self.scheduler.commit(s, [])
                 self.stats.prefill_tokens += s.count
+                end = s.start + s.count
+                if self.state_ckpt is not None and end % self.block_size == 0 and r.seq_id in self.blocks.seqs:
+                    sb = self.blocks.seqs[r.seq_id]
+                    if len(sb.hashes) >= end // self.block_size:       # the chunk's last block is registered: keep its state
+                        self.state_ckpt.save(sb.hashes[end // self.block_size - 1], sb.state_slot)
                 continue
             if s.verify:
                 target = toks[row:row + s.count]

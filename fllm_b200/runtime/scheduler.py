@@ -63,6 +63,7 @@ class Scheduler:
         # (recompute preemption, abort, expiry, finish): the draft-model proposer forgets its KV marks there
         self.on_drop = None
         self.now_override = None     # step control: judge deadlines with the leader's clock instead of the local one
+        self.chunk_align = 0         # recurrent-state checkpoints: prompt chunks end on multiples of this
         self._refund = 0             # token budget given back by victims preempted inside the current schedule()
         self.stats = {"steps": 0, "preemptions": 0, "scheduled_tokens": 0}
 
@@ -140,6 +141,19 @@ class Scheduler:
                 return False
         return True
 
+    def _chunk(self, r, budget: int) -> int:
+        """Tokens of ``r`` to feed this step. With ``chunk_align`` set (recurrent-state checkpoints) a prompt chunk
+        ends on a multiple of it whenever one lies inside the chunk: before the budget's end, and before the last
+        prompt token, so that a copy of the state can be kept on a block boundary close to the prompt's end."""
+        n = min(r.remaining, budget)
+        a = self.chunk_align
+        if a and r.remaining > 1:
+            end = min(r.num_computed + n, r.num_tokens - 1)
+            cut = end // a * a
+            if cut > r.num_computed:
+                n = cut - r.num_computed
+        return n
+
     def _take_refund(self) -> int:
         n, self._refund = self._refund, 0
         return n
@@ -190,7 +204,7 @@ class Scheduler:
         for r in prefilling:
             if r not in self.running or budget <= 0:
                 continue
-            n = min(r.remaining, budget)
+            n = self._chunk(r, budget)
             ok = self._reserve(step, r, r.num_computed + n)
             budget += self._take_refund()
             if not ok:
@@ -211,7 +225,7 @@ class Scheduler:
                 cached = self.blocks.allocate(r.seq_id, r.all_tokens, self._salt(r))
                 r.num_computed = cached
                 r.num_cached = cached
-            n = min(r.remaining, budget)
+            n = self._chunk(r, budget)
             need = self.blocks.blocks_needed(r.num_computed + n) - len(self.blocks.table(r.seq_id))
             if not self.blocks.can_allocate(max(need, 0)) or not self.blocks.ensure_capacity(r.seq_id, r.num_computed + n):
                 # not enough room right now: leave it queued (its cached prefix stays referenced)

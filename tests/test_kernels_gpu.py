@@ -871,3 +871,14 @@ def test_tree_attention_kernel(ops, ref, D, hq, hkv):
     y = ops.attention_tree(q, kc, vc, tables, row_seq, pos, mask, base, hq, hkv, D, D ** -0.5)
     yr = ref.attention_tree(q, kc, vc, tables, row_seq, pos, mask, base, hq, hkv, D, D ** -0.5)
     _close(y, yr, 2e-2)
+
+
+def test_logit_softcap_kernel():
+    from fllm_b200.ops.native import NativeOps
+    ops = NativeOps(torch.device("cuda"))
+    x = (torch.randn(7, 1001, device="cuda") * 40).bfloat16()
+    view = torch.empty(7, 1010, device="cuda", dtype=torch.bfloat16)[:, :1001]
+    view.copy_(x)
+    want = (30.0 * torch.tanh(x.float() / 30.0))
+    ops.softcap_(view, 30.0)
+    assert (view.float() - want).abs().max().item() <= 0.13          # bf16 steps near +-30

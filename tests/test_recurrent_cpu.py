@@ -312,3 +312,33 @@ def test_group_limited_router_keeps_the_best_groups():
     assert sorted(ids[0].tolist()) == [0, 4, 5]                             # expert 6 (3.0) loses to 5 although its group is third
     p = torch.softmax(logits, -1)[0]
     assert torch.allclose(w[0].sort().values, (2.0 * p[[0, 4, 5]]).sort().values)
+
+
+@pytest.mark.parametrize("kinds,ssm", SYNTHETIC[:2])
+def test_state_checkpoints_reuse_a_prompt_prefix(kinds, ssm):
+    """With state checkpoints a second request that shares a prompt prefix starts behind the last block boundary whose
+    state was kept, and generates what it generates without the cache; a preempted-and-recomputed run is covered by
+    the same path."""
+    cfg = _synthetic(kinds, ssm)
+    g = torch.Generator().manual_seed(0)
+    shared = torch.randint(0, 200, (70,), generator=g).tolist()
+    p1, p2 = shared + [3, 4, 5], shared + [9, 8, 7, 6]
+    sp = SamplingParams(max_tokens=6, temperature=0.0)
+
+    def engine(gb):
+        ec = EngineConfig(max_num_seqs=4, max_num_batched_tokens=256, max_model_len=256, num_kv_blocks=64, block_size=16,
+                          state_cache_gb=gb)
+        return LLMEngine(cfg, ec, device="cpu", seed=1)
+    plain = engine(0.0)
+    want = [plain.generate([p], sp)[0] for p in (p1, p2, p1)]
+    eng = engine(0.25)
+    assert eng.cfg.enable_prefix_caching and eng.scheduler.chunk_align == 16
+    got1 = eng.generate([p1], sp)[0]
+    assert eng.state_ckpt.stats["saved"] >= 1 and eng.state_ckpt.stats["restored"] == 0
+    before = eng.stats.prefill_tokens
+    got2 = eng.generate([p2], sp)[0]
+    assert eng.state_ckpt.stats["restored"] == 1
+    assert eng.stats.prefill_tokens - before <= len(p2) - 64            # the first four blocks were not computed again
+    got3 = eng.generate([p1], sp)[0]                                      # the whole aligned prefix of p1 is there: 64 tokens reused
+    assert [got1, got2, got3] == want
+    assert len(eng.blocks.state_free) == eng.rstate.slots - 1

@@ -166,8 +166,31 @@ def test_latent_attention_kernel(ops, H):
         pos += list(range(past, past + n))
     row_seq = torch.tensor(row_seq, dtype=torch.int32, device="cuda")
     pos = torch.tensor(pos, dtype=torch.int32, device="cuda")
-    q = torch.randn(len(pos), H, 576, device="cuda", generator=g).bfloat16()
-    out = nat.attention_mla(q, cache, tables, row_seq, pos, 512, 576 ** -0.5)
-    want = ref.attention_mla(q, cache, tables, row_seq, pos, 512, 576 ** -0.5)
+    T = len(pos)
+    q_abs = torch.randn(H, T, 512, device="cuda", generator=g).bfloat16()
+    q_pe = torch.randn(T, H, 64, device="cuda", generator=g).bfloat16()
+    out = nat.attention_mla(q_abs, q_pe, cache, tables, row_seq, pos, 576 ** -0.5)
+    want = ref.attention_mla(q_abs, q_pe, cache, tables, row_seq, pos, 576 ** -0.5)
     torch.cuda.synchronize()
     assert rel(out, want) < 1e-2
+
+
+def test_latent_prepare_kernel(ops):
+    """RMSNorm + rotation into cache rows (padding rows write nothing) and the rotated query parts."""
+    nat, ref = ops
+    g = torch.Generator(device="cuda").manual_seed(9)
+    T, H = 23, 6
+    ckv = torch.randn(T, 576, device="cuda", generator=g).bfloat16()
+    q = torch.randn(T, H, 192, device="cuda", generator=g).bfloat16()
+    pos = torch.randint(0, 5000, (T,), device="cuda", generator=g).int()
+    slots = torch.randperm(16 * 8, device="cuda", generator=g)[:T].int()
+    slots[5] = -1
+    inv_freq = (10000.0 ** (-torch.arange(32, device="cuda").float() / 32)).contiguous()
+    w = (1 + 0.3 * torch.randn(512, device="cuda", generator=g)).bfloat16()
+    c1 = torch.zeros(8, 16, 576, device="cuda", dtype=torch.bfloat16)
+    c2 = c1.clone()
+    a = nat.mla_prepare(ckv, q, 128, pos, slots, inv_freq, 1.3, w, 1e-6, c1)
+    b = ref.mla_prepare(ckv, q, 128, pos, slots, inv_freq, 1.3, w, 1e-6, c2)
+    torch.cuda.synchronize()
+    assert rel(a, b) < 1e-2 and rel(c1, c2) < 1e-2
+    assert int((c1.view(-1, 576).abs().sum(-1) > 0).sum()) == T - 1
