@@ -32,6 +32,8 @@ def _add_engine_flags(p: argparse.ArgumentParser) -> None:
     p.add_argument("--kv-tier-host-gb", type=float, default=0.0, help="host memory for evicted prefix-cache blocks")
     p.add_argument("--kv-tier-disk-dir", default=None, help="directory for blocks that fall out of the host tier (default $FLLM_KV_DISK_DIR)")
     p.add_argument("--kv-tier-disk-gb", type=float, default=0.0)
+    p.add_argument("--state-cache-gb", type=float, default=0.0,
+                   help="recurrent / hybrid models: host memory for state checkpoints on block boundaries (prefix reuse)")
     p.add_argument("--speculative", default="off", choices=["off", "ngram", "suffix", "draft"])
     p.add_argument("--draft-model", default=None)
     p.add_argument("--draft-tokens", type=int, default=4)
@@ -57,7 +59,8 @@ def build_engine(args):
         num_kv_blocks=args.kv_blocks, enable_prefix_caching=not args.no_prefix_cache,
         use_cuda_graphs=not args.no_cuda_graphs, scheduling_policy=args.scheduling_policy,
         preemption=args.preemption, speculative=args.speculative, draft_tokens=args.draft_tokens, seed=args.seed,
-        kv_tier_host_gb=args.kv_tier_host_gb, kv_tier_disk_dir=args.kv_tier_disk_dir, kv_tier_disk_gb=args.kv_tier_disk_gb)
+        kv_tier_host_gb=args.kv_tier_host_gb, kv_tier_disk_dir=args.kv_tier_disk_dir, kv_tier_disk_gb=args.kv_tier_disk_gb,
+        state_cache_gb=getattr(args, "state_cache_gb", 0.0))
     par = ParallelConfig(tp=args.tp, pp=args.pp, expert_parallel=args.expert_parallel, ep_dispatch=args.ep_dispatch,
                          distributed_backend=args.distributed_backend)
     weights, tok_path = None, args.tokenizer

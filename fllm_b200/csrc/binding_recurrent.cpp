@@ -106,8 +106,16 @@ void gated_rmsnorm(const Tensor& x, const optional<Tensor>& z, const Tensor& w, 
 }
 
 // q_abs [H, T, 512] or [T, H, 512] (any strides with a unit inner one), q_pe [T, H, 64], out like q_abs
+int64_t attention_mla_splits(int64_t tokens, int64_t H, int64_t max_kv_len) {
+  return fllm::attention_mla_splits((int)tokens, (int)H, (int)max_kv_len);
+}
+int64_t attention_mla_workspace_bytes(int64_t tokens, int64_t H, int64_t splits) {
+  return (int64_t)fllm::attention_mla_workspace_bytes((int)tokens, (int)H, (int)splits);
+}
+
+// splits = 0: the CUDA-core kernel; >= 1: the tensor-core kernel over that many key slices (workspace needed above 1)
 void attention_mla(const Tensor& q_abs, const Tensor& q_pe, const Tensor& cache, const Tensor& block_tables, const Tensor& row_seq,
-                   const Tensor& positions, Tensor out, bool head_major, double scale) {
+                   const Tensor& positions, Tensor out, bool head_major, double scale, int64_t splits, const optional<Tensor>& workspace) {
   TORCH_CHECK(q_abs.is_cuda() && q_abs.scalar_type() == at::kBFloat16 && q_abs.dim() == 3 && q_abs.stride(2) == 1 && q_abs.size(2) == 512,
               "q_abs: bf16 [., ., 512] with a unit inner stride");
   TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.dim() == 3 && out.stride(2) == 1 && out.sizes() == q_abs.sizes(), "out: like q_abs");
@@ -122,6 +130,20 @@ void attention_mla(const Tensor& q_abs, const Tensor& q_pe, const Tensor& cache,
                   positions.is_contiguous() && row_seq.numel() >= T && positions.numel() >= T,
               "block_tables [B, max_blocks], row_seq [T], positions [T]: int32");
   c10::cuda::CUDAGuard guard(q_abs.device());
+  if (splits >= 1) {
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
+    if (workspace.has_value() && workspace->defined()) {
+      TORCH_CHECK(workspace->is_cuda() && workspace->is_contiguous(), "workspace: contiguous CUDA tensor");
+      ws = workspace->data_ptr();
+      ws_bytes = workspace->numel() * workspace->element_size();
+    }
+    fllm::attention_mla_tc_bf16(q_abs.data_ptr(), q_abs.stride(td), q_abs.stride(hd), q_pe.data_ptr(), cache.data_ptr(),
+                                block_tables.data_ptr<int>(), (int)block_tables.stride(0), row_seq.data_ptr<int>(), positions.data_ptr<int>(),
+                                out.data_ptr(), out.stride(td), out.stride(hd), (int)T, (int)H, (int)cache.size(1), (float)scale, (int)splits,
+                                ws, ws_bytes, cur_stream());
+    return;
+  }
   fllm::attention_mla_bf16(q_abs.data_ptr(), q_abs.stride(td), q_abs.stride(hd), q_pe.data_ptr(), cache.data_ptr(), block_tables.data_ptr<int>(),
                            (int)block_tables.stride(0), row_seq.data_ptr<int>(), positions.data_ptr<int>(), out.data_ptr(), out.stride(td),
                            out.stride(hd), (int)T, (int)H, (int)cache.size(1), (float)scale, cur_stream());
@@ -160,7 +182,9 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
         "Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y, int H, int DK, int DV, int kv_ratio, bool l2norm, float q_scale) -> ()",
         &matrix_state_scan);
   m.def("attention_mla(Tensor q_abs, Tensor q_pe, Tensor cache, Tensor block_tables, Tensor row_seq, Tensor positions, Tensor(a!) out, "
-        "bool head_major, float scale) -> ()", &attention_mla);
+        "bool head_major, float scale, int splits, Tensor? workspace) -> ()", &attention_mla);
+  m.def("attention_mla_splits(int tokens, int H, int max_kv_len) -> int", &attention_mla_splits);
+  m.def("attention_mla_workspace_bytes(int tokens, int H, int splits) -> int", &attention_mla_workspace_bytes);
   m.def("mla_prepare(Tensor ckv, Tensor q, int rope_offset, Tensor positions, Tensor slots, Tensor inv_freq, float attn_factor, Tensor norm_w, "
         "float eps, Tensor(a!) cache, Tensor(b!) q_pe) -> ()", &mla_prepare);
   m.def("gated_rmsnorm(Tensor x, Tensor? z, Tensor w, Tensor(a!) y, int group_size, float eps, bool norm_before_gate) -> ()", &gated_rmsnorm);

@@ -297,6 +297,13 @@ void gated_rmsnorm(const void* x, long long ldx, const void* z, long long ldz, c
 void attention_mla_bf16(const void* q_abs, long long qa_t, long long qa_h, const void* q_pe, const void* cache, const int* block_tables,
                         int max_blocks, const int* row_seq, const int* positions, void* out, long long o_t, long long o_h, int tokens,
                         int H, int block_size, float scale, cudaStream_t s);
+// Tensor-core form of the same attention (16 heads per CTA as the rows of m16n8k16 MMAs, 64-key tiles by cp.async, split over
+// `splits` key slices with a merge kernel; workspace of attention_mla_workspace_bytes when splits > 1).
+size_t attention_mla_workspace_bytes(int tokens, int H, int splits);
+int attention_mla_splits(int tokens, int H, int max_kv_len);
+void attention_mla_tc_bf16(const void* q_abs, long long qa_t, long long qa_h, const void* q_pe, const void* cache, const int* block_tables,
+                           int max_blocks, const int* row_seq, const int* positions, void* out, long long o_t, long long o_h, int tokens,
+                           int H, int block_size, float scale, int splits, void* workspace, size_t workspace_bytes, cudaStream_t s);
 // RMSNorm of the latent + rotation of the shared key part into the cache row of each token (slot < 0: no write), and rotation
 // of every head's rotary query values into q_pe [tokens][H][64].
 void mla_prepare_bf16(const void* ckv, long long ldc, const void* q, long long ldq, int q_head_stride, int q_rope_offset,

@@ -14,6 +14,8 @@
 // Reference counterparts: rust/engine/cuda/moe.cu:40-150 (moe_route2), :159-205 (moe_align),
 // :533-597 (combine2). The reference routes on the host inside a device group
 // (rust/engine/src/rust_decoder.rs:7621-7729); here nothing leaves the device.
+#include <algorithm>
+
 #include "fllm_ops.h"
 #include "ptx.cuh"
 #include "tma_host.h"
@@ -92,12 +94,14 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
                                                          int* __restrict__ row_of, int* __restrict__ token_of,
                                                          int rows_cap, int* __restrict__ tile_expert,
                                                          int* __restrict__ tile_row0, int* __restrict__ num_tiles,
-                                                         int max_tiles) {
+                                                         int max_tiles, int staged) {
   __shared__ int cnt[256], off[257], fill[256];
+  extern __shared__ int ids_s[];              // the first `staged` ids: the per-expert scans below read them from here
   for (int e = threadIdx.x; e < 256; e += blockDim.x) { cnt[e] = 0; fill[e] = 0; }
   __syncthreads();
   for (int i = threadIdx.x; i < entries; i += blockDim.x) {
     const int e = ids[i];
+    if (i < staged) ids_s[i] = e;
     if (e >= expert_lo && e < expert_hi) atomicAdd(&cnt[e - expert_lo], 1);
   }
   __syncthreads();
@@ -125,7 +129,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
   for (int e = threadIdx.x; e < local; e += blockDim.x) {
     int pos = off[e];
     for (int i = 0; i < entries; ++i) {
-      if (ids[i] == e + expert_lo) {
+      if ((i < staged ? ids_s[i] : ids[i]) == e + expert_lo) {
         row_of[i] = pos;
         if (pos < rows_cap) token_of[pos] = i / k;
         ++pos;
@@ -142,8 +146,9 @@ void moe_align(const int* ids, int tokens, int k, int experts, int expert_lo, in
                int* token_of, int rows_cap, int* tile_expert, int* tile_row0, int* num_tiles, int max_tiles,
                cudaStream_t s) {
   if (expert_hi - expert_lo > 256) throw std::runtime_error("moe_align: at most 256 local experts");
-  moe_align_kernel<<<1, 1024, 0, s>>>(ids, tokens * k, experts, expert_lo, expert_hi, bn, k, row_of, token_of,
-                                      rows_cap, tile_expert, tile_row0, num_tiles, max_tiles);
+  const int staged = std::min(tokens * k, 10240);              // 40 KiB of dynamic shared memory at most
+  moe_align_kernel<<<1, 1024, (size_t)staged * sizeof(int), s>>>(ids, tokens * k, experts, expert_lo, expert_hi, bn, k, row_of, token_of,
+                                                                 rows_cap, tile_expert, tile_row0, num_tiles, max_tiles, staged);
   cuda_check(cudaGetLastError(), "moe_align_kernel");
 }
 

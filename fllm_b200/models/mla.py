@@ -45,7 +45,7 @@ def mla_block(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
     cache = dec.kv.layer(dec.kv_index[li])
     q_pe = ops.mla_prepare(ckv, q, dn, b.positions, b.slots, dec.inv_freq, dec.attn_factor, m["kv_a_norm"], cfg.rms_eps, cache)
     q_abs = torch.bmm(q[:, :, :dn].transpose(0, 1), m["w_uk"])                                # [H, T, R]
-    o_lat = ops.attention_mla(q_abs, q_pe, cache, b.block_tables, b.row_seq, b.positions, dec.scale)     # [H, T, R]
+    o_lat = ops.attention_mla(q_abs, q_pe, cache, b.block_tables, b.row_seq, b.positions, dec.scale, b.max_kv_len)     # [H, T, R]
     o = torch.bmm(o_lat, m["w_uv"]).transpose(0, 1).reshape(T, H * dv)
     return ops.linear(o, m["wo"], m.get("bo"))
 

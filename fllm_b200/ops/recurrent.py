@@ -168,7 +168,7 @@ class RecurrentRef:
         cache.view(-1, R + dr)[slots[:ckv.shape[0]][keep].long()] = row[keep]
         return rot(q[:, :, rope_offset:rope_offset + dr]).to(q.dtype)
 
-    def attention_mla(self, q_abs, q_pe, cache, block_tables, row_seq, positions, scale):
+    def attention_mla(self, q_abs, q_pe, cache, block_tables, row_seq, positions, scale, max_kv_len=0, tensor_cores=True, splits=None):
         """Latent attention: absorbed queries ``q_abs`` [H, T, R] and rotated parts ``q_pe`` [T, H, dr] against cache rows
         [blocks, block_size, R + dr]; the values are the first R entries of the same rows. Returns [H, T, R]."""
         H, T, R = q_abs.shape
@@ -230,10 +230,24 @@ class RecurrentNative:
         self.launches += 1
         return q_pe
 
-    def attention_mla(self, q_abs, q_pe, cache, block_tables, row_seq, positions, scale):
+    def attention_mla(self, q_abs, q_pe, cache, block_tables, row_seq, positions, scale, max_kv_len=0, tensor_cores=True, splits=None):
+        """``max_kv_len`` (host-side bound on the context of the step's rows) sizes the split over key slices."""
         if cache.shape[-1] != 576 or q_abs.shape[-1] != 512:
             return RecurrentRef.attention_mla(self, q_abs, q_pe, cache, block_tables, row_seq, positions, scale)
+        H, T = q_abs.shape[0], q_abs.shape[1]
         out = torch.empty(q_abs.shape, dtype=q_abs.dtype, device=q_abs.device)
-        self.k.attention_mla(q_abs, q_pe, cache, block_tables, row_seq, positions, out, True, float(scale))
-        self.launches += 1
+        if not tensor_cores:
+            self.k.attention_mla(q_abs, q_pe, cache, block_tables, row_seq, positions, out, True, float(scale), 0, None)
+            self.launches += 1
+            return out
+        if splits is None:
+            splits = int(self.k.attention_mla_splits(T, H, int(max_kv_len))) if max_kv_len else 1
+        ws = None
+        if splits > 1:
+            need = int(self.k.attention_mla_workspace_bytes(T, H, splits))
+            ws = getattr(self, "_mla_ws", None)
+            if ws is None or ws.numel() < need:           # grow-only; the warm-up before a graph capture sizes it
+                ws = self._mla_ws = torch.empty(need, dtype=torch.uint8, device=q_abs.device)
+        self.k.attention_mla(q_abs, q_pe, cache, block_tables, row_seq, positions, out, True, float(scale), int(splits), ws)
+        self.launches += 2 if splits > 1 else 1
         return out

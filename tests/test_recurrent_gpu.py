@@ -147,7 +147,7 @@ def test_gated_rmsnorm(ops, gs, before, D):
     assert rel(y2, ref.gated_rmsnorm(x, None, w, 1e-5, gs, before)) < 1e-2
 
 
-@pytest.mark.parametrize("H", [4, 16, 6])
+@pytest.mark.parametrize("H", [4, 16, 6, 40])
 def test_latent_attention_kernel(ops, H):
     """Ragged rows (two prefill chunks and decode rows) over a paged latent pool with shuffled blocks."""
     nat, ref = ops
@@ -169,10 +169,15 @@ def test_latent_attention_kernel(ops, H):
     T = len(pos)
     q_abs = torch.randn(H, T, 512, device="cuda", generator=g).bfloat16()
     q_pe = torch.randn(T, H, 64, device="cuda", generator=g).bfloat16()
-    out = nat.attention_mla(q_abs, q_pe, cache, tables, row_seq, pos, 576 ** -0.5)
     want = ref.attention_mla(q_abs, q_pe, cache, tables, row_seq, pos, 576 ** -0.5)
+    out = nat.attention_mla(q_abs, q_pe, cache, tables, row_seq, pos, 576 ** -0.5, tensor_cores=False)
     torch.cuda.synchronize()
     assert rel(out, want) < 1e-2
+    for splits in (1, 2, 4):                                      # tensor-core kernel; slices beyond a short row's keys are empty
+        out = nat.attention_mla(q_abs, q_pe, cache, tables, row_seq, pos, 576 ** -0.5, splits=splits)
+        torch.cuda.synchronize()
+        assert rel(out, want) < 1e-2, splits
+    assert int(nat.k.attention_mla_splits(4, 16, 4096)) > 1 and int(nat.k.attention_mla_splits(2048, 16, 4096)) == 1
 
 
 def test_latent_prepare_kernel(ops):
