@@ -53,7 +53,9 @@ def run_case(case: str, reps: int = 4) -> None:
     fp8_prefill, gemm_fp4_decode (64 tokens x NVFP4 gate_up), gemm_mx4_decode / gemm_mx4_prefill / gemm_mx8_decode /
     gemm_nvf4_decode / gemm_nvf4_prefill (block-scaled MXFP4 / MXFP8 / NVFP4 gate_up), gemv_q4k (one token x 4-bit
     gate_up on the dp4a kernel), tp_rs_gemm / tp_norm / tp_ag_gemm (the fused
-    tensor-parallel kernels with two virtual ranks on one device)."""
+    tensor-parallel kernels with two virtual ranks on one device), mla_decode / mla_decode_cc / mla_prefill (latent
+    attention on the tensor-core and the CUDA-core kernel), mamba2_decode / mamba2_prefill / gdn_decode (recurrent
+    scans; these print their CUDA-event time and the state or cache bytes per second)."""
     from .ops.native import NativeOps, Fp8BlockLinear, quantize_weight_fp8_block
     ops = NativeOps(torch.device("cuda:0"))
     bf = dict(device="cuda", dtype=torch.bfloat16)
@@ -144,8 +146,51 @@ def run_case(case: str, reps: int = 4) -> None:
                              q_starts=torch.tensor([0, 1024, 2048], device="cuda", dtype=torch.int32),
                              max_q_len=1024, min_q_len=1024)
         fn = lambda: ops.attention(q, kc, vc, tables, None, None, hq, hkv, D, D ** -0.5, meta=meta)
+    elif case in ("mla_decode", "mla_decode_cc", "mla_prefill"):
+        # latent attention of DeepSeek-V2-Lite (16 heads): 64 sequences at 1152 tokens of context, or a 1024-token prefill
+        # chunk of 2 sequences; the pool (64 x 1152 x 576 bf16 = 85 MB for decode) is read once per launch
+        H, bs = 16, 16
+        B, L, Lq = (64, 1152, 1) if case != "mla_prefill" else (2, 1024, 1024)
+        nblk = B * (L // bs)
+        cache = (torch.randn(nblk, bs, 576, **bf) * 0.3)
+        tables = torch.arange(nblk, device="cuda", dtype=torch.int32).view(B, L // bs)
+        row_seq = torch.arange(B, device="cuda", dtype=torch.int32).repeat_interleave(Lq)
+        pos = (torch.arange(L - Lq, L, device="cuda", dtype=torch.int32)).repeat(B)
+        q_abs, q_pe = torch.randn(H, B * Lq, 512, **bf), torch.randn(B * Lq, H, 64, **bf)
+        tc = case != "mla_decode_cc"
+        fn = lambda: ops.attention_mla(q_abs, q_pe, cache, tables, row_seq, pos, 576 ** -0.5, L, tensor_cores=tc)
+        nbytes = cache.numel() * 2
+    elif case in ("mamba2_decode", "mamba2_prefill", "gdn_decode"):
+        # Mamba-2 2.7B layer (80 heads x 64 x 128 state): 64 decode rows (state 2.6 MB per sequence, read and written), or one
+        # 2048-token chunk; gated delta rule of Qwen3-Next (32 value heads x 128 x 128)
+        B, n = (64, 1) if case != "mamba2_prefill" else (1, 2048)
+        T = B * n
+        qs = torch.arange(0, T + 1, n, device="cuda", dtype=torch.int32)
+        ss = torch.arange(B, device="cuda", dtype=torch.int32)
+        pos = (torch.arange(n, device="cuda", dtype=torch.int32) + (0 if n > 1 else 100)).repeat(B)
+        if case == "gdn_decode":
+            from .ops.recurrent import GATED_DELTA
+            Hv, Hk, D = 32, 16, 128
+            r, k = torch.randn(T, Hk * D, **bf), torch.randn(T, Hk * D, **bf)
+            v, beta = torch.randn(T, Hv * D, **bf), torch.rand(T, Hv, **bf)
+            w = -torch.rand(T, Hv, device="cuda")
+            st = torch.zeros(B, Hv, D, D, device="cuda")
+            fn = lambda: ops.matrix_state_scan(GATED_DELTA, r, k, v, None, None, w, None, beta, st, qs, ss, pos, Hv, D, D, 2, True, D ** -0.5)
+        else:
+            Hh, P, N = 80, 64, 128
+            x, dt = torch.randn(T, Hh * P, **bf), torch.randn(T, Hh, **bf)
+            Bm, Cm = torch.randn(T, N, **bf), torch.randn(T, N, **bf)
+            A, D_, dtb = -torch.rand(Hh, device="cuda"), torch.ones(Hh, device="cuda"), torch.zeros(Hh, device="cuda")
+            st = torch.zeros(B, Hh, P, N, device="cuda")
+            fn = lambda: ops.mamba2_scan(x, dt, Bm, Cm, A, D_, dtb, st, qs, ss, pos, Hh, P, 1, N, 0.0, 1e30)
+        nbytes = st.numel() * 4 * 2
     else:
         raise SystemExit(f"unknown case {case}")
+    if case.startswith(("mla_", "mamba2_", "gdn_")):
+        ms = Timer()(fn)
+        hbm, _, which = _peaks()
+        print(json.dumps({"case": case, "us": round(ms * 1e3, 1), "bytes": nbytes, "gbs": round(nbytes / ms / 1e6, 1),
+                          "frac_of_" + which + "_copy_bw": round(nbytes / (ms * 1e-3) / (hbm * 1e9), 3)}))
     for _ in range(reps):
         fn()
     torch.cuda.synchronize()

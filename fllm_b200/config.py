@@ -73,6 +73,8 @@ class ModelConfig:
     router_groups: int = 1
     router_topk_groups: int = 1
     router_norm_topk: bool = False
+    shared_gate: bool = False            # the shared experts' output is scaled by sigmoid(h . g) (Qwen3-Next)
+    attn_out_gate: bool = False          # the query projection also emits a gate: attention output * sigmoid(gate) (Qwen3-Next)
     # recurrent and hybrid families: the token mixer of each layer (None = attention everywhere) and whether the
     # layer has a gated FFN behind it ("glu") or is the mixer alone ("none"); `ssm` holds the mixer shapes
     # (d_inner, d_state, d_conv, n_groups, head_dim, n_heads, dt_rank, norm_groups, dt_min, dt_max, conv_bias,
@@ -278,7 +280,7 @@ def mla_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     return cfg
 
 
-RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7")
+RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next")
 
 
 def _limit(v, default: float) -> float:
@@ -347,6 +349,21 @@ def recurrent_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
                             n_groups=hf.get("mamba_n_groups", 1), head_dim=P, n_heads=H, norm_groups=1,
                             conv_bias=hf.get("mamba_conv_bias", True), proj_bias=hf.get("mamba_proj_bias", False),
                             dt_min=_limit(lim[0], 0.0), dt_max=_limit(lim[1], 1e30)))
+    if mt == "qwen3_next":
+        kinds = hf.get("layer_types") or ["linear_attention" if (i + 1) % 4 else "full_attention" for i in range(L)]
+        E, step, dense = hf.get("num_experts", 0), hf.get("decoder_sparse_step", 1) or 1, set(hf.get("mlp_only_layers") or [])
+        rot = int(head_dim * hf.get("partial_rotary_factor", 0.25))
+        return cls(**base, intermediate_size=hf["intermediate_size"], rms_eps=hf.get("rms_norm_eps", 1e-6),
+                   tie_embeddings=hf.get("tie_word_embeddings", False), qk_norm=True, norm_weight_offset=1.0,
+                   attn_out_gate=True, rotary_dim=rot if rot != head_dim else None,
+                   layer_kinds=["attention" if k == "full_attention" else "gated_delta" for k in kinds],
+                   ffn_kinds=["moe" if (E > 0 and i not in dense and (i + 1) % step == 0) else "glu" for i in range(L)],
+                   num_experts=E, experts_per_token=hf.get("num_experts_per_tok", 10),
+                   moe_intermediate_size=hf.get("moe_intermediate_size", 512), router_kind="softmax_all",
+                   shared_intermediate_size=hf.get("shared_expert_intermediate_size", 0) if E else 0, shared_gate=bool(E),
+                   ssm=dict(num_k_heads=hf.get("linear_num_key_heads", 16), num_v_heads=hf.get("linear_num_value_heads", 32),
+                            head_k_dim=hf.get("linear_key_head_dim", 128), head_v_dim=hf.get("linear_value_head_dim", 128),
+                            d_conv=hf.get("linear_conv_kernel_dim", 4), norm_eps=hf.get("rms_norm_eps", 1e-6)))
     if mt == "lfm2":
         inter = hf.get("intermediate_size") or hf.get("block_ff_dim", 4 * hidden)
         if hf.get("block_auto_adjust_ff_dim", True):                # the checkpoint's FFN width: 2/3, multiplier, rounded up

@@ -95,9 +95,9 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
                                                          int rows_cap, int* __restrict__ tile_expert,
                                                          int* __restrict__ tile_row0, int* __restrict__ num_tiles,
                                                          int max_tiles, int staged) {
-  __shared__ int cnt[256], off[257], fill[256];
+  __shared__ int cnt[512], off[513], fill[512];
   extern __shared__ int ids_s[];              // the first `staged` ids: the per-expert scans below read them from here
-  for (int e = threadIdx.x; e < 256; e += blockDim.x) { cnt[e] = 0; fill[e] = 0; }
+  for (int e = threadIdx.x; e < 512; e += blockDim.x) { cnt[e] = 0; fill[e] = 0; }
   __syncthreads();
   for (int i = threadIdx.x; i < entries; i += blockDim.x) {
     const int e = ids[i];
@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
 void moe_align(const int* ids, int tokens, int k, int experts, int expert_lo, int expert_hi, int bn, int* row_of,
                int* token_of, int rows_cap, int* tile_expert, int* tile_row0, int* num_tiles, int max_tiles,
                cudaStream_t s) {
-  if (expert_hi - expert_lo > 256) throw std::runtime_error("moe_align: at most 256 local experts");
+  if (expert_hi - expert_lo > 512) throw std::runtime_error("moe_align: at most 512 local experts");
   const int staged = std::min(tokens * k, 10240);              // 40 KiB of dynamic shared memory at most
   moe_align_kernel<<<1, 1024, (size_t)staged * sizeof(int), s>>>(ids, tokens * k, experts, expert_lo, expert_hi, bn, k, row_of, token_of,
                                                                  rows_cap, tile_expert, tile_row0, num_tiles, max_tiles, staged);

@@ -81,6 +81,49 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
                     if t is not None:
                         lw.mixer[name] = t.float().to(device).contiguous() if name == "conv_b" else dev(t)
             glu(lw, p + "feed_forward.", "w1", "w3", "w2")
+        elif mt == "qwen3_next":
+            from ..models.recurrent import pack_gated_delta
+            p = f"model.layers.{l}."
+            lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
+                              ffn_norm=dev(get(p + "post_attention_layernorm.weight")))
+            if kind == "attention":
+                a, D, Hq = p + "self_attn.", cfg.head_dim, cfg.num_heads
+                qg = get(a + "q_proj.weight").view(Hq, 2, D, cfg.hidden_size)         # per head: query rows, then gate rows
+                lw.wqkv = dev(torch.cat([qg[:, 0].reshape(Hq * D, -1), get(a + "k_proj.weight"), get(a + "v_proj.weight")], 0))
+                lw.w_attn_gate = dev(qg[:, 1].reshape(Hq * D, -1))
+                lw.wo = dev(get(a + "o_proj.weight"))
+                # the family's norms multiply by 1 + w; the fused QK-norm kernel multiplies by w
+                lw.q_norm, lw.k_norm = dev(get(a + "q_norm.weight").float() + 1.0), dev(get(a + "k_norm.weight").float() + 1.0)
+            else:
+                m = p + "linear_attn."
+                Hk, Hv, Dk, Dv = s["num_k_heads"], s["num_v_heads"], s["head_k_dim"], s["head_v_dim"]
+                r = Hv // Hk
+                Hd = cfg.hidden_size
+                qkvz = get(m + "in_proj_qkvz.weight").view(Hk, 2 * Dk + 2 * r * Dv, Hd)      # per key head: q | k | v | z
+                ba = get(m + "in_proj_ba.weight").view(Hk, 2 * r, Hd)
+                lw.mixer = pack_gated_delta(qkvz[:, :Dk].reshape(-1, Hd), qkvz[:, Dk:2 * Dk].reshape(-1, Hd),
+                                            qkvz[:, 2 * Dk:2 * Dk + r * Dv].reshape(-1, Hd), qkvz[:, 2 * Dk + r * Dv:].reshape(-1, Hd),
+                                            ba[:, :r].reshape(-1, Hd), ba[:, r:].reshape(-1, Hd), get(m + "conv1d.weight"),
+                                            get(m + "dt_bias"), get(m + "A_log"), get(m + "norm.weight"), get(m + "out_proj.weight"),
+                                            dtype, device)
+            if cfg.ffn_kind(l) == "moe":
+                mp = p + "mlp."
+                lw.router_w = dev(get(mp + "gate.weight"))
+                fused = get(mp + "experts.gate_up_proj", False)
+                if fused is not None:
+                    lw.exp_gate_up, lw.exp_down = dev(fused), dev(get(mp + "experts.down_proj"))
+                else:
+                    E = cfg.num_experts
+                    lw.exp_gate_up = dev(torch.stack([torch.cat([get(mp + f"experts.{e}.gate_proj.weight"),
+                                                                 get(mp + f"experts.{e}.up_proj.weight")], 0) for e in range(E)]))
+                    lw.exp_down = dev(torch.stack([get(mp + f"experts.{e}.down_proj.weight") for e in range(E)]))
+                if cfg.shared_intermediate_size:
+                    lw.shared_gate_up = dev(torch.cat([get(mp + "shared_expert.gate_proj.weight"), get(mp + "shared_expert.up_proj.weight")], 0))
+                    lw.shared_down = dev(get(mp + "shared_expert.down_proj.weight"))
+                    g1 = get(mp + "shared_expert_gate.weight")                         # [1, H] -> 8 rows for the GEMM's width rule
+                    lw.shared_gate_w = dev(torch.cat([g1, torch.zeros(7, g1.shape[1], dtype=g1.dtype)], 0))
+            else:
+                glu(lw, p + "mlp.", "gate_proj", "up_proj", "down_proj")
         elif mt in ("deepseek_v2", "deepseek_v3"):
             from ..models.mla import pack_mla
             p = f"model.layers.{l}."
@@ -118,7 +161,7 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
         embed, final = get("backbone.embeddings.weight"), get("backbone.norm_f.weight")
     elif mt == "bamba":
         embed, final = get("model.embed_tokens.weight"), get("model.final_layernorm.weight")
-    elif mt in ("deepseek_v2", "deepseek_v3"):
+    elif mt in ("deepseek_v2", "deepseek_v3", "qwen3_next"):
         embed, final = get("model.embed_tokens.weight"), get("model.norm.weight")
     else:
         embed, final = get("model.embed_tokens.weight"), get("model.embedding_norm.weight")

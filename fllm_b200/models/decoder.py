@@ -134,7 +134,8 @@ class Decoder:
 
     def _attention_block(self, li: int, lw, h: torch.Tensor, b: StepBatch) -> torch.Tensor:
         cfg, sp, ops = self.cfg, self.spec, self.ops
-        qkv = ops.linear(h, lw.wqkv, lw.bqkv, defer=self._defer)
+        gated = lw.w_attn_gate is not None
+        qkv = ops.linear(h, lw.wqkv, lw.bqkv, defer=self._defer and not gated)
         local = self.kv_index[li]
         kc, vc = self.kv.k(local), self.kv.v(local)
         q = ops.rope_kv_write(qkv, b.positions, b.slots, self.inv_freq, lw.q_norm, lw.k_norm, kc, vc,
@@ -143,6 +144,8 @@ class Decoder:
         a = ops.attention(q, kc, vc, b.block_tables, b.row_seq, b.positions, sp.hq_local, sp.hkv_local,
                           cfg.head_dim, self.scale, cfg.layer_window(li), lw.sinks, cfg.attn_softcap,
                           meta=b)
+        if gated:                                # the attention output passes through a sigmoid gate of its own projection
+            a = (a.float() * torch.sigmoid(ops.linear(h, lw.w_attn_gate).float())).to(a.dtype)
         return ops.linear(a, lw.wo, lw.bo, defer=self._defer_out(lw.post_attn_norm))
 
     def _defer_out(self, post_norm) -> bool:
@@ -161,7 +164,10 @@ class Decoder:
             y = moe_ffn(self, lw, h)
             if lw.shared_gate_up is not None:        # always-on shared experts: one dense GLU beside the routed ones
                 act = ops.linear_glu(h, lw.shared_gate_up, None, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit, 0)
-                y = y + ops.linear(act, lw.shared_down)
+                ys = ops.linear(act, lw.shared_down)
+                if lw.shared_gate_w is not None:
+                    ys = (ys.float() * torch.sigmoid(ops.linear(h, lw.shared_gate_w)[:, :1].float())).to(ys.dtype)
+                y = y + ys
             return y
         act = ops.linear_glu(h, lw.w_gate_up, None, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit,
                              getattr(lw, "glu_layout", 0))

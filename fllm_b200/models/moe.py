@@ -136,6 +136,9 @@ def moe_ffn(dec, lw, h: torch.Tensor) -> torch.Tensor:
     wts = torch.empty(T, k, dtype=torch.float32, device=h.device)
     if cfg.router_kind in ("deepseek_v2", "deepseek_v3"):
         ids, wts = route_deepseek(cfg, logits, getattr(lw, "router_select_b", None))
+    elif cfg.num_experts > 256 or k > 8:         # beyond the routing kernel's register budget: the same rule in tensor ops
+        ids, wts = route_reference(cfg, logits)
+        wts = wts.contiguous()
     else:
         k_ops.moe_route(logits, None, k, cfg.router_kind != "softmax_topk", ids, wts)
     share = e_local / cfg.num_experts

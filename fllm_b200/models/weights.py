@@ -45,6 +45,8 @@ class LayerWeights:
     router_select_b: Optional[torch.Tensor] = None  # [E] added to the scores for the selection only (DeepSeek-V3)
     shared_gate_up: Optional[torch.Tensor] = None   # [2*Is, H] always-on shared experts as one dense GLU
     shared_down: Optional[torch.Tensor] = None      # [H, Is]
+    shared_gate_w: Optional[torch.Tensor] = None    # [8, H] (row 0 used): sigmoid(h . w) scales the shared experts' output
+    w_attn_gate: Optional[torch.Tensor] = None      # [hq*D, H] output gate of the attention (Qwen3-Next)
     # recurrent layers (Mamba, delta rule, short convolution): the mixer's tensors by name; wqkv / wo stay None
     mixer: Optional[Dict[str, torch.Tensor]] = None
     # packed formats keep their payload here (format name -> tensors)

@@ -342,3 +342,35 @@ def test_state_checkpoints_reuse_a_prompt_prefix(kinds, ssm):
     got3 = eng.generate([p1], sp)[0]                                      # the whole aligned prefix of p1 is there: 64 tokens reused
     assert [got1, got2, got3] == want
     assert len(eng.blocks.state_free) == eng.rstate.slots - 1
+
+
+def test_qwen3_next_matches_transformers(tmp_path):
+    """Gated delta rule layers + gated full attention (partial rotary, 1 + w norms) + routed experts with a gated shared
+    expert, against `transformers` on a random tiny checkpoint."""
+    from transformers import Qwen3NextConfig, Qwen3NextForCausalLM
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    torch.manual_seed(0)
+    hc = Qwen3NextConfig(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=32, linear_conv_kernel_dim=4, linear_key_head_dim=32, linear_value_head_dim=32,
+                         linear_num_key_heads=2, linear_num_value_heads=4, moe_intermediate_size=32, shared_expert_intermediate_size=48,
+                         num_experts_per_tok=2, num_experts=8, max_position_embeddings=256, mlp_only_layers=[0])
+    m = Qwen3NextForCausalLM(hc).eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if n.endswith(("norm.weight", "layernorm.weight", "dt_bias")):
+                p.add_(0.3 * torch.randn_like(p))
+            if n.endswith("mlp.gate.weight"):
+                p.mul_(20.0)
+    d = str(tmp_path / "q3n")
+    m.save_pretrained(d, safe_serialization=True)
+    cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
+    assert cfg.layer_kinds == ["gated_delta"] * 3 + ["attention"] and cfg.ffn_kinds == ["glu", "moe", "moe", "moe"]
+    assert cfg.rot_dim == 8 and cfg.attn_out_gate and w.layers[3].w_attn_gate is not None and w.layers[1].shared_gate_w is not None
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16),
+                    device="cpu", weights=w)
+    toks = torch.randint(0, 300, (45,), generator=torch.Generator().manual_seed(1)).tolist()
+    got = eng.token_logits(toks)
+    with torch.no_grad():
+        want = m(torch.tensor([toks])).logits[0].float()
+    err = (got - want).abs().max(dim=1).values / float(want.abs().max())
+    assert float(err.median()) < 2e-2 and int((err > 5e-2).sum()) <= 2, err
