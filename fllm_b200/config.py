@@ -74,6 +74,7 @@ class ModelConfig:
     router_topk_groups: int = 1
     router_norm_topk: bool = False
     shared_gate: bool = False            # the shared experts' output is scaled by sigmoid(h . g) (Qwen3-Next)
+    use_rope: bool = True                # False: attention layers carry no position signal of their own (Jamba)
     attn_out_gate: bool = False          # the query projection also emits a gate: attention output * sigmoid(gate) (Qwen3-Next)
     # recurrent and hybrid families: the token mixer of each layer (None = attention everywhere) and whether the
     # layer has a gated FFN behind it ("glu") or is the mixer alone ("none"); `ssm` holds the mixer shapes
@@ -280,7 +281,7 @@ def mla_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     return cfg
 
 
-RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next")
+RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "jamba")
 
 
 def _limit(v, default: float) -> float:
@@ -364,6 +365,21 @@ def recurrent_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
                    ssm=dict(num_k_heads=hf.get("linear_num_key_heads", 16), num_v_heads=hf.get("linear_num_value_heads", 32),
                             head_k_dim=hf.get("linear_key_head_dim", 128), head_v_dim=hf.get("linear_value_head_dim", 128),
                             d_conv=hf.get("linear_conv_kernel_dim", 4), norm_eps=hf.get("rms_norm_eps", 1e-6)))
+    if mt == "jamba":
+        ap, ao = hf.get("attn_layer_period", 8), hf.get("attn_layer_offset", 4)
+        ep, eo = hf.get("expert_layer_period", 2), hf.get("expert_layer_offset", 1)
+        E = hf.get("num_experts", 16)
+        rank = hf.get("mamba_dt_rank", "auto")
+        rank = -(-hidden // 16) if rank == "auto" else int(rank)
+        return cls(**base, intermediate_size=hf["intermediate_size"], rms_eps=hf.get("rms_norm_eps", 1e-6),
+                   tie_embeddings=hf.get("tie_word_embeddings", False), use_rope=False,
+                   layer_kinds=["attention" if i % ap == ao else "mamba1" for i in range(L)],
+                   ffn_kinds=["moe" if (E > 1 and i % ep == eo) else "glu" for i in range(L)],
+                   num_experts=E if E > 1 else 0, experts_per_token=hf.get("num_experts_per_tok", 2),
+                   moe_intermediate_size=hf["intermediate_size"], router_kind="deepseek_v2", router_norm_topk=False,
+                   ssm=dict(d_inner=hf.get("mamba_expand", 2) * hidden, d_state=hf.get("mamba_d_state", 16),
+                            d_conv=hf.get("mamba_d_conv", 4), dt_rank=rank, conv_bias=hf.get("mamba_conv_bias", True),
+                            proj_bias=hf.get("mamba_proj_bias", False), bcdt_rms=True, mixer_rms_eps=hf.get("rms_norm_eps", 1e-6)))
     if mt == "lfm2":
         inter = hf.get("intermediate_size") or hf.get("block_ff_dim", 4 * hidden)
         if hf.get("block_auto_adjust_ff_dim", True):                # the checkpoint's FFN width: 2/3, multiplier, rounded up

@@ -81,6 +81,33 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
                     if t is not None:
                         lw.mixer[name] = t.float().to(device).contiguous() if name == "conv_b" else dev(t)
             glu(lw, p + "feed_forward.", "w1", "w3", "w2")
+        elif mt == "jamba":
+            p = f"model.layers.{l}."
+            lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
+                              ffn_norm=dev(get(p + "pre_ff_layernorm.weight")))
+            if kind == "attention":
+                attention(lw, p + "self_attn.")
+            else:
+                m = p + "mamba."
+                lw.mixer = pack_mamba1(get(m + "in_proj.weight"), get(m + "conv1d.weight"), get(m + "conv1d.bias", False),
+                                       get(m + "x_proj.weight"), get(m + "dt_proj.weight"), get(m + "dt_proj.bias"),
+                                       get(m + "A_log"), get(m + "D"), get(m + "out_proj.weight"), s["d_state"], s["dt_rank"],
+                                       dtype, device, get(m + "in_proj.bias", False), get(m + "out_proj.bias", False))
+                for name, key in (("dt_norm_w", "dt_layernorm"), ("b_norm_w", "b_layernorm"), ("c_norm_w", "c_layernorm")):
+                    lw.mixer[name] = dev(get(m + key + ".weight"))
+            if cfg.ffn_kind(l) == "moe":
+                mp = p + "feed_forward."
+                lw.router_w = dev(get(mp + "router.weight"))
+                fused = get(mp + "experts.gate_up_proj", False)
+                if fused is not None:
+                    lw.exp_gate_up, lw.exp_down = dev(fused), dev(get(mp + "experts.down_proj"))
+                else:
+                    E = cfg.num_experts
+                    lw.exp_gate_up = dev(torch.stack([torch.cat([get(mp + f"experts.{e}.gate_proj.weight"),
+                                                                 get(mp + f"experts.{e}.up_proj.weight")], 0) for e in range(E)]))
+                    lw.exp_down = dev(torch.stack([get(mp + f"experts.{e}.down_proj.weight") for e in range(E)]))
+            else:
+                glu(lw, p + "feed_forward.", "gate_proj", "up_proj", "down_proj")
         elif mt == "qwen3_next":
             from ..models.recurrent import pack_gated_delta
             p = f"model.layers.{l}."
@@ -159,7 +186,7 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
         layers.append(lw)
     if mt in ("mamba", "falcon_mamba", "mamba2"):
         embed, final = get("backbone.embeddings.weight"), get("backbone.norm_f.weight")
-    elif mt == "bamba":
+    elif mt in ("bamba", "jamba"):
         embed, final = get("model.embed_tokens.weight"), get("model.final_layernorm.weight")
     elif mt in ("deepseek_v2", "deepseek_v3", "qwen3_next"):
         embed, final = get("model.embed_tokens.weight"), get("model.norm.weight")

@@ -81,6 +81,8 @@ class Decoder:
         self.kv_index = {li: i for i, li in enumerate(l for l in self.layer_range if cfg.layer_kind(l) in ("attention", "mla"))}
         dev = weights.final_norm.device
         inv, attn = rope_inv_freq(cfg)
+        if not cfg.use_rope:                       # a zero frequency table turns the rotation into the identity
+            inv = [0.0] * len(inv)
         self.inv_freq = torch.tensor(inv, dtype=torch.float32, device=dev)
         self.attn_factor = attn
         self.scale = cfg.attn_scale if cfg.attn_scale else cfg.head_dim ** -0.5

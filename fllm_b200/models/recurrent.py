@@ -117,8 +117,10 @@ def mamba1_mixer(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
     if s.get("bcdt_rms"):
         eps = s.get("mixer_rms_eps", 1e-6)
         R = s["dt_rank"]
-        dtl = torch.nn.functional.pad(_rms(dtl[:, :R], eps), (0, dtl.shape[1] - R))
-        Bm, Cm = _rms(Bm, eps), _rms(Cm, eps)
+        dtn, Bm, Cm = _rms(dtl[:, :R], eps), _rms(Bm, eps), _rms(Cm, eps)
+        if "dt_norm_w" in m:                           # Jamba: the three norms carry weights
+            dtn, Bm, Cm = dtn * m["dt_norm_w"], Bm * m["b_norm_w"], Cm * m["c_norm_w"]
+        dtl = torch.nn.functional.pad(dtn, (0, dtl.shape[1] - R))
     dt = ops.linear(dtl, m["dt_proj"])
     y = ops.mamba1_scan(x, dt, Bm, Cm, xz[:, Di:2 * Di], m["A"], m["D"], m["dt_bias"], dec.rstate.scan[li], qs, ss, pos)
     return ops.linear(y, m["out_proj"], m.get("out_proj_b"))

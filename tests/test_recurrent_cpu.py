@@ -32,10 +32,21 @@ def _tiny(kind):
         return Lfm2ForCausalLM(Lfm2Config(vocab_size=300, hidden_size=64, intermediate_size=192, num_hidden_layers=3,
                                           num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256,
                                           layer_types=["conv", "full_attention", "conv"], conv_L_cache=3, block_multiple_of=16))
+    if kind == "jamba":
+        from transformers import JambaConfig, JambaForCausalLM
+        return JambaForCausalLM(JambaConfig(vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
+                                            num_attention_heads=4, num_key_value_heads=2, num_experts=4, num_experts_per_tok=2,
+                                            expert_layer_period=2, expert_layer_offset=1, attn_layer_period=2, attn_layer_offset=1,
+                                            mamba_d_state=16, mamba_d_conv=4, mamba_expand=2, mamba_dt_rank=8, use_mamba_kernels=False,
+                                            max_position_embeddings=256))
+    if kind == "falcon_mamba":
+        from transformers import FalconMambaConfig, FalconMambaForCausalLM
+        return FalconMambaForCausalLM(FalconMambaConfig(vocab_size=300, hidden_size=64, state_size=16, num_hidden_layers=2, expand=2,
+                                                        conv_kernel=4, time_step_rank=8, use_mambapy=False))
     raise ValueError(kind)
 
 
-@pytest.mark.parametrize("kind", ["mamba", "mamba2", "bamba", "lfm2"])
+@pytest.mark.parametrize("kind", ["mamba", "mamba2", "bamba", "lfm2", "jamba", "falcon_mamba"])
 def test_recurrent_families_match_transformers(tmp_path, kind):
     from fllm_b200.formats.loader import load_hf_checkpoint
     m = _tiny(kind).eval().float()
@@ -43,6 +54,8 @@ def test_recurrent_families_match_transformers(tmp_path, kind):
         for n, p in m.named_parameters():
             if n.endswith(("norm.weight", "layernorm.weight", "norm_f.weight", ".D", "dt_bias")):
                 p.add_(0.3 * torch.randn_like(p))
+            if n.endswith("router.weight"):
+                p.mul_(20.0)                                  # clear routing decisions
     d = str(tmp_path / kind)
     m.save_pretrained(d, safe_serialization=True)
     cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
