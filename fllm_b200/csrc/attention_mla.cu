@@ -135,9 +135,9 @@ __global__ void __launch_bounds__(NW * 32) mla_attn_kernel(const bf16* __restric
 // ------------------------------------------------------------------------------------------ tensor-core path
 // One CTA per (query row, 16 heads, slice of the keys): the 16 heads are the M rows of m16n8k16 MMAs, so the latent
 // row of a key is read from shared memory once for all of them. Per tile of 64 keys (double-buffered cp.async):
-//   warp w computes S[16 x 16] for keys 16 w .. 16 w + 15 over the 576-wide rows (Q fragments by ldmatrix from shared
+//   warp w of 8 computes S[16 x 8] for keys 8 w .. 8 w + 7 over the 576-wide rows (Q fragments by ldmatrix from shared
 //   memory), the row maxima meet in shared memory, P = exp2(S - max) goes to shared memory as bf16, and every warp
-//   accumulates O[16 x 128] for its quarter of the 512 latent columns from the whole P (values = the first 512
+//   accumulates O[16 x 64] for its eighth of the 512 latent columns from the whole P (values = the first 512
 //   entries of the same key rows, read by transposing ldmatrix).
 // With more than one key slice per row the CTAs leave (max, sum, unnormalised O) in a workspace and a second kernel
 // merges them.
@@ -175,24 +175,29 @@ __device__ __forceinline__ bf16* tile_at(bf16* base, int row, int chunk) {
   return base + row * W + ((chunk ^ (row & 7)) << 3);
 }
 
+constexpr int kTcWarps = 8;
+
 struct MlaTcSmem {
   bf16 q[16 * kRow];
   bf16 k[2][kTile * kRow];
   bf16 p[16 * kTile];
-  float wmax[4][16];
-  float wsum[4][16];
+  float wmax[kTcWarps][16];
+  float wsum[kTcWarps][16];
 };
 
 // part_o [rows][splits][512] fp32 and part_ml [rows][splits][2] with rows = tokens * Hpad (Hpad = head groups * 16)
-__global__ void __launch_bounds__(128) mla_tc_kernel(const bf16* __restrict__ q_abs, long long qa_t, long long qa_h,
-                                                     const bf16* __restrict__ q_pe, const bf16* __restrict__ cache,
-                                                     const int* __restrict__ block_tables, int max_blocks,
-                                                     const int* __restrict__ row_seq, const int* __restrict__ positions,
-                                                     bf16* __restrict__ out, long long o_t, long long o_h, int H, int block_size,
-                                                     float scale_log2, int splits, float* __restrict__ part_o,
-                                                     float* __restrict__ part_ml) {
+__global__ void __launch_bounds__(kTcWarps * 32) mla_tc_kernel(const bf16* __restrict__ q_abs, long long qa_t, long long qa_h,
+                                                               const bf16* __restrict__ q_pe, const bf16* __restrict__ cache,
+                                                               const int* __restrict__ block_tables, int max_blocks,
+                                                               const int* __restrict__ row_seq, const int* __restrict__ positions,
+                                                               bf16* __restrict__ out, long long o_t, long long o_h, int H,
+                                                               int block_size, float scale_log2, int splits,
+                                                               float* __restrict__ part_o, float* __restrict__ part_ml) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   MlaTcSmem& sm = *reinterpret_cast<MlaTcSmem*>(smem_raw);
+  constexpr int NT = kTcWarps * 32;
+  constexpr int KPW = kTile / kTcWarps;                      // 8 keys per warp in the S phase = one n-tile
+  constexpr int CPW = kLatent / kTcWarps;                    // 64 latent columns per warp in the P V phase
   const int h0 = blockIdx.x * 16, t = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3, j4 = lane >> 3;
@@ -205,7 +210,7 @@ __global__ void __launch_bounds__(128) mla_tc_kernel(const bf16* __restrict__ q_
 
   // queries of the 16 heads (zero rows past the last head)
   constexpr int CPR = kRow / 8;                              // 72 chunks of 16 bytes per row
-  for (int i = tid; i < 16 * CPR; i += 128) {
+  for (int i = tid; i < 16 * CPR; i += NT) {
     const int r = i / CPR, c = i - r * CPR;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (h0 + r < H) {
@@ -215,23 +220,31 @@ __global__ void __launch_bounds__(128) mla_tc_kernel(const bf16* __restrict__ q_
     }
     *reinterpret_cast<uint4*>(tile_at<kRow>(sm.q, r, c)) = v;
   }
+  // A warp brings in its KPW rows of the tile: lane r looks up the cache row of key r once, the address travels by
+  // shuffle, and the 32 lanes copy the row's 72 chunks in three steps.
   auto load_tile = [&](int tile, int buf) {
-    const int key0 = tile * kTile;
-    for (int i = tid; i < kTile * CPR; i += 128) {
-      const int r = i / CPR, c = i - r * CPR;
-      const int key = key0 + r;
-      bf16* dst = tile_at<kRow>(sm.k[buf], r, c);
-      if (key < kv_len) {
-        const bf16* src = cache + ((size_t)table[key / block_size] * block_size + (key % block_size)) * kRow + c * 8;
-        cp_async16(dst, src);
-      } else {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);   // masked keys must not feed NaNs into P V
+    const int key0 = tile * kTile + warp * KPW;
+    const bf16* mine = nullptr;
+    if (lane < KPW && key0 + lane < kv_len) {
+      const int key = key0 + lane;
+      mine = cache + ((size_t)table[key / block_size] * block_size + (key % block_size)) * kRow;
+    }
+#pragma unroll
+    for (int r = 0; r < KPW; ++r) {
+      const unsigned long long addr = __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(mine), r);
+      const bf16* src = reinterpret_cast<const bf16*>(addr);
+      const int row = warp * KPW + r;
+#pragma unroll
+      for (int c = lane; c < CPR; c += 32) {
+        bf16* dst = tile_at<kRow>(sm.k[buf], row, c);
+        if (src != nullptr) cp_async16(dst, src + c * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);   // masked keys must not feed NaNs into P V
       }
     }
   };
-  float o[16][4];
+  float o[CPW / 8][4];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  for (int i = 0; i < CPW / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   if (tile_lo < tile_hi) load_tile(tile_lo, 0);
   cp_async_commit();
@@ -242,26 +255,24 @@ __global__ void __launch_bounds__(128) mla_tc_kernel(const bf16* __restrict__ q_
     cp_async_wait<1>();
     __syncthreads();
     bf16* kt = sm.k[buf];
-    // ---- S = Q K^T for this warp's 16 keys
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll 4
-    for (int kk = 0; kk < kRow / 16; ++kk) {
-      uint32_t a[4], b[4];
-      ldsm_x4(a, tile_at<kRow>(sm.q, lane & 15, 2 * kk + (lane >> 4)));
-      ldsm_x4(b, tile_at<kRow>(kt, warp * 16 + (j4 >> 1) * 8 + (lane & 7), 2 * kk + (j4 & 1)));
-      mma_bf16(s[0], a, b[0], b[1]);
-      mma_bf16(s[1], a, b[2], b[3]);
+    // ---- S = Q K^T for this warp's 8 keys, two k-steps per round (one ldmatrix.x4 brings both B fragments)
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 3
+    for (int kk = 0; kk < kRow / 16; kk += 2) {
+      uint32_t a0[4], a1[4], b[4];
+      ldsm_x4(a0, tile_at<kRow>(sm.q, lane & 15, 2 * kk + (lane >> 4)));
+      ldsm_x4(a1, tile_at<kRow>(sm.q, lane & 15, 2 * kk + 2 + (lane >> 4)));
+      ldsm_x4(b, tile_at<kRow>(kt, warp * KPW + (lane & 7), 2 * kk + j4));
+      mma_bf16(s, a0, b[0], b[1]);
+      mma_bf16(s, a1, b[2], b[3]);
     }
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-    for (int nb = 0; nb < 2; ++nb) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = tile * kTile + warp * 16 + nb * 8 + 2 * tq + (e & 1);
-        const float v = key < kv_len ? s[nb][e] * scale_log2 : -INFINITY;
-        s[nb][e] = v;
-        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
-      }
+    for (int e = 0; e < 4; ++e) {
+      const int key = tile * kTile + warp * KPW + 2 * tq + (e & 1);
+      const float v = key < kv_len ? s[e] * scale_log2 : -INFINITY;
+      s[e] = v;
+      if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
     }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
@@ -271,33 +282,29 @@ __global__ void __launch_bounds__(128) mla_tc_kernel(const bf16* __restrict__ q_
     __syncthreads();
     float mn0 = m0, mn1 = m1;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) mn0 = fmaxf(mn0, sm.wmax[w][g]), mn1 = fmaxf(mn1, sm.wmax[w][g + 8]);
+    for (int w = 0; w < kTcWarps; ++w) mn0 = fmaxf(mn0, sm.wmax[w][g]), mn1 = fmaxf(mn1, sm.wmax[w][g + 8]);
     // a tile inside [tile_lo, tile_hi) starts below kv_len, so every row has seen a finite score by now
     const float c0 = m0 == -INFINITY ? 0.f : exp2f(m0 - mn0), c1 = m1 == -INFINITY ? 0.f : exp2f(m1 - mn1);
     m0 = mn0, m1 = mn1;
-    float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-    for (int nb = 0; nb < 2; ++nb) {
-      const float p0 = exp2f(s[nb][0] - mn0), p1 = exp2f(s[nb][1] - mn0);
-      const float p2 = exp2f(s[nb][2] - mn1), p3 = exp2f(s[nb][3] - mn1);
-      sum0 += p0 + p1, sum1 += p2 + p3;
-      const int col = warp * 16 + nb * 8 + 2 * tq;
+    {
+      const float p0 = exp2f(s[0] - mn0), p1 = exp2f(s[1] - mn0), p2 = exp2f(s[2] - mn1), p3 = exp2f(s[3] - mn1);
+      l0 = l0 * c0 + p0 + p1, l1 = l1 * c1 + p2 + p3;
+      const int col = warp * KPW + 2 * tq;
       *reinterpret_cast<__nv_bfloat162*>(tile_at<kTile>(sm.p, g, col >> 3) + (col & 7)) = __floats2bfloat162_rn(p0, p1);
       *reinterpret_cast<__nv_bfloat162*>(tile_at<kTile>(sm.p, g + 8, col >> 3) + (col & 7)) = __floats2bfloat162_rn(p2, p3);
     }
-    l0 = l0 * c0 + sum0, l1 = l1 * c1 + sum1;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) o[i][0] *= c0, o[i][1] *= c0, o[i][2] *= c1, o[i][3] *= c1;
+    for (int i = 0; i < CPW / 8; ++i) o[i][0] *= c0, o[i][1] *= c0, o[i][2] *= c1, o[i][3] *= c1;
     __syncthreads();
-    // ---- O += P V for this warp's 128 latent columns
+    // ---- O += P V for this warp's 64 latent columns
 #pragma unroll
     for (int kq = 0; kq < kTile / 16; ++kq) {
       uint32_t pa[4];
       ldsm_x4(pa, tile_at<kTile>(sm.p, lane & 15, 2 * kq + (lane >> 4)));
 #pragma unroll
-      for (int db = 0; db < 16; db += 2) {
+      for (int db = 0; db < CPW / 8; db += 2) {
         uint32_t b[4];
-        ldsm_x4_t(b, tile_at<kRow>(kt, kq * 16 + (j4 & 1) * 8 + (lane & 7), warp * 16 + db + (j4 >> 1)));
+        ldsm_x4_t(b, tile_at<kRow>(kt, kq * 16 + (j4 & 1) * 8 + (lane & 7), warp * (CPW / 8) + db + (j4 >> 1)));
         mma_bf16(o[db], pa, b[0], b[1]);
         mma_bf16(o[db + 1], pa, b[2], b[3]);
       }
@@ -305,20 +312,21 @@ __global__ void __launch_bounds__(128) mla_tc_kernel(const bf16* __restrict__ q_
     __syncthreads();                                          // P, the maxima and this key buffer are free again
   }
   cp_async_wait<0>();
-  // ---- row sums over the quad and the four warps
+  // ---- row sums over the quad and the warps
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
   if (tq == 0) sm.wsum[warp][g] = l0, sm.wsum[warp][g + 8] = l1;
   __syncthreads();
-  const float L0 = sm.wsum[0][g] + sm.wsum[1][g] + sm.wsum[2][g] + sm.wsum[3][g];
-  const float L1 = sm.wsum[0][g + 8] + sm.wsum[1][g + 8] + sm.wsum[2][g + 8] + sm.wsum[3][g + 8];
+  float L0 = 0.f, L1 = 0.f;
+#pragma unroll
+  for (int w = 0; w < kTcWarps; ++w) L0 += sm.wsum[w][g], L1 += sm.wsum[w][g + 8];
   if (splits == 1) {
     const float i0 = L0 > 0.f ? 1.f / L0 : 0.f, i1 = L1 > 0.f ? 1.f / L1 : 0.f;
 #pragma unroll
-    for (int db = 0; db < 16; ++db) {
-      const int col = warp * 128 + db * 8 + 2 * tq;
+    for (int db = 0; db < CPW / 8; ++db) {
+      const int col = warp * CPW + db * 8 + 2 * tq;
       if (h0 + g < H)
         *reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * o_t + (size_t)(h0 + g) * o_h + col) = __floats2bfloat162_rn(o[db][0] * i0, o[db][1] * i0);
       if (h0 + g + 8 < H)
@@ -332,8 +340,8 @@ __global__ void __launch_bounds__(128) mla_tc_kernel(const bf16* __restrict__ q_
     part_ml[2 * r1] = m1, part_ml[2 * r1 + 1] = L1;
   }
 #pragma unroll
-  for (int db = 0; db < 16; ++db) {
-    const int col = warp * 128 + db * 8 + 2 * tq;
+  for (int db = 0; db < CPW / 8; ++db) {
+    const int col = warp * CPW + db * 8 + 2 * tq;
     *reinterpret_cast<float2*>(part_o + r0 * kLatent + col) = make_float2(o[db][0], o[db][1]);
     *reinterpret_cast<float2*>(part_o + r1 * kLatent + col) = make_float2(o[db][2], o[db][3]);
   }
@@ -449,7 +457,7 @@ void attention_mla_tc_bf16(const void* q_abs, long long qa_t, long long qa_h, co
   const int groups = (H + 15) / 16;
   float* po = static_cast<float*>(workspace);
   float* pml = splits > 1 ? po + (size_t)tokens * groups * 16 * splits * kLatent : nullptr;
-  mla_tc_kernel<<<dim3(groups, tokens, splits), 128, sizeof(MlaTcSmem), s>>>(
+  mla_tc_kernel<<<dim3(groups, tokens, splits), kTcWarps * 32, sizeof(MlaTcSmem), s>>>(
       static_cast<const bf16*>(q_abs), qa_t, qa_h, static_cast<const bf16*>(q_pe), static_cast<const bf16*>(cache), block_tables, max_blocks,
       row_seq, positions, static_cast<bf16*>(out), o_t, o_h, H, block_size, scale * kLog2e, splits, po, pml);
   if (splits > 1)

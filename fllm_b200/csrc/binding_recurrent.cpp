@@ -42,17 +42,28 @@ void causal_conv1d(const Tensor& x, const Tensor& w, const optional<Tensor>& bia
 
 void mamba2_scan(const Tensor& x, const Tensor& dt, const Tensor& Bm, const Tensor& Cm, const Tensor& A, const optional<Tensor>& D,
                  const optional<Tensor>& dt_bias, Tensor state, const Tensor& q_starts, const Tensor& seq_state, const Tensor& positions,
-                 Tensor y, int64_t H, int64_t P, int64_t G, int64_t N, double dt_min, double dt_max) {
+                 Tensor y, int64_t H, int64_t P, int64_t G, int64_t N, double dt_min, double dt_max, int64_t seg_len, int64_t segs,
+                 const optional<Tensor>& seg_scratch) {
   TORCH_CHECK(rows_bf16(x) && rows_bf16(dt) && rows_bf16(Bm) && rows_bf16(Cm) && rows_bf16(y), "activations: bf16 rows");
   TORCH_CHECK(x.size(1) == H * P && y.size(1) == H * P && dt.size(1) == H && Bm.size(1) == G * N && Cm.size(1) == G * N, "widths");
   TORCH_CHECK(state.scalar_type() == at::kFloat && state.is_contiguous() && state.dim() == 4 && state.size(1) == H && state.size(2) == P &&
                   state.size(3) == N, "state: fp32 [slots, H, P, N]");
   check_batch(q_starts, seq_state, positions);
   c10::cuda::CUDAGuard guard(x.device());
+  float *seg_state = nullptr, *seg_dt = nullptr;
+  const int64_t B = seq_state.numel();
+  if (seg_len > 0 && segs > 1) {                 // scratch: [B][segs - 1][H][P][N] end / start states, then [B][segs - 1][H] step sums
+    const int64_t n_state = B * (segs - 1) * H * P * N, n_dt = B * (segs - 1) * H;
+    TORCH_CHECK(seg_scratch.has_value() && seg_scratch->scalar_type() == at::kFloat && seg_scratch->is_contiguous() &&
+                    seg_scratch->numel() >= n_state + n_dt, "seg_scratch: fp32, at least B * (segs - 1) * (H * P * N + H) values");
+    seg_state = seg_scratch->data_ptr<float>();
+    seg_dt = seg_state + n_state;
+  }
   const int rc = fllm::mamba2_scan(x.data_ptr(), x.stride(0), dt.data_ptr(), dt.stride(0), Bm.data_ptr(), Bm.stride(0), Cm.data_ptr(),
                                    Cm.stride(0), opt_f32(A), opt_f32(D), opt_f32(dt_bias), state.data_ptr<float>(), q_starts.data_ptr<int>(),
-                                   seq_state.data_ptr<int>(), positions.data_ptr<int>(), y.data_ptr(), y.stride(0), (int)seq_state.numel(),
-                                   (int)H, (int)P, (int)G, (int)N, (float)dt_min, (float)dt_max, cur_stream());
+                                   seq_state.data_ptr<int>(), positions.data_ptr<int>(), y.data_ptr(), y.stride(0), (int)B,
+                                   (int)H, (int)P, (int)G, (int)N, (float)dt_min, (float)dt_max, (int)seg_len, (int)segs, seg_state, seg_dt,
+                                   cur_stream());
   TORCH_CHECK(rc == 0, "mamba2_scan: unsupported arguments (code ", rc, "): state width 16 / 32 / 64 / 128 / 256, B and C 16-byte aligned");
 }
 
@@ -173,7 +184,8 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("causal_conv1d(Tensor x, Tensor w, Tensor? bias, Tensor(a!) state, Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y, bool act) -> ()",
         &causal_conv1d);
   m.def("mamba2_scan(Tensor x, Tensor dt, Tensor Bm, Tensor Cm, Tensor A, Tensor? D, Tensor? dt_bias, Tensor(a!) state, Tensor q_starts, "
-        "Tensor seq_state, Tensor positions, Tensor(b!) y, int H, int P, int G, int N, float dt_min, float dt_max) -> ()",
+        "Tensor seq_state, Tensor positions, Tensor(b!) y, int H, int P, int G, int N, float dt_min, float dt_max, int seg_len, int segs, "
+        "Tensor? seg_scratch) -> ()",
         &mamba2_scan);
   m.def("mamba1_scan(Tensor x, Tensor dt, Tensor Bm, Tensor Cm, Tensor? z, Tensor A, Tensor? D, Tensor? dt_bias, Tensor(a!) state, "
         "Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y) -> ()",

@@ -116,6 +116,14 @@ __global__ void __launch_bounds__(256) conv1d_kernel(const bf16* __restrict__ x,
 
 // ------------------------------------------------------------------------------------------ Mamba-2 (SSD)
 // h[p][n] = exp(dt A) h[p][n] + dt x[p] B[n];  y[p] = sum_n h[p][n] C[n] + D x[p]      (one A, dt, D per head)
+//
+// Long prompts of few sequences leave most SMs idle if a sequence is walked by one CTA per (head, row tile). The
+// recurrence is diagonal, so a sequence can be cut into segments of `seg_len` tokens that run side by side:
+//   kLocal    every segment but the last runs from a zero state and leaves its end state and the sum of its time steps;
+//   combine   start state of segment s + 1 = end state of s + exp(A sum dt_s) * start state of s (a short serial pass);
+//   kFinal    every segment runs again from its true start state and writes y; the last segment stores the state.
+// Twice the arithmetic, `segs` times the parallelism. kWhole is the plain walk (decode, short chunks, large batches).
+enum { kWhole = 0, kLocal = 1, kFinal = 2 };
 struct Mamba2Args {
   const bf16 *x, *dt, *Bm, *Cm;
   long long ldx, lddt, ldb, ldc, ldy;
@@ -125,61 +133,110 @@ struct Mamba2Args {
   bf16* y;
   int H, P, G;
   float dt_min, dt_max;
+  int seg_len, segs;            // segmented modes only
+  float* seg_state;             // [B][segs - 1][H][P][N]: end states (kLocal), then start states of segments 1.. (combine)
+  float* seg_dt;                // [B][segs - 1][H]: sum of the time steps of a segment
 };
 
-template <int N, int NPT>
+template <int N, int NPT, int MODE>
 __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Args a) {
   constexpr int TPN = N / NPT, ROWS = 128 / TPN;
   const int ptiles = (a.P + ROWS - 1) / ROWS;
   const int h = blockIdx.x / ptiles, p = (blockIdx.x % ptiles) * ROWS + threadIdx.x / TPN;
-  const int ln = threadIdx.x % TPN, s = blockIdx.y;
+  const int ln = threadIdx.x % TPN, s = blockIdx.y, seg = MODE == kWhole ? 0 : blockIdx.z;
   const int t0 = a.q_starts[s], n = a.q_starts[s + 1] - t0;
   if (n <= 0) return;
   const bool valid = p < a.P;
   const int pc = valid ? p : a.P - 1;                        // lanes of a ragged last tile repeat the last row, unstored
   float* st = a.state + (((long long)a.seq_state[s] * a.H + h) * a.P + pc) * N + ln * NPT;
+  float* sg = nullptr;                                       // this thread's slice of seg_state[s][.]
+  if (MODE != kWhole) sg = a.seg_state + ((((long long)s * (a.segs - 1)) * a.H + h) * a.P + pc) * N + ln * NPT;
+  const long long seg_stride = (long long)a.H * a.P * N;
+  // tokens [lo, hi) of the sequence's step
+  // (the last segment of kFinal runs to the end of the step even if `segs` was sized for a shorter one)
+  const int lo = MODE == kWhole ? 0 : min(n, seg * a.seg_len);
+  const int hi = (MODE == kWhole || (MODE == kFinal && seg == a.segs - 1)) ? n : min(n, (seg + 1) * a.seg_len);
   float hs[NPT];
-  if (a.positions[t0] == 0) {
+  const bool from_pool = MODE == kWhole || (MODE == kFinal && seg == 0);
+  if (MODE == kLocal || (from_pool && a.positions[t0] == 0)) {
 #pragma unroll
     for (int i = 0; i < NPT; ++i) hs[i] = 0.f;
-  } else {
+  } else if (from_pool) {
     load_f32<NPT>(st, hs);
+  } else {
+    load_f32<NPT>(sg + (seg - 1) * seg_stride, hs);
   }
   const int g = h / (a.H / a.G);
   const float A = a.A[h], D = a.D != nullptr ? a.D[h] : 0.f, dtb = a.dt_bias != nullptr ? a.dt_bias[h] : 0.f;
-  const bf16* xp = a.x + (long long)t0 * a.ldx + h * a.P + pc;
-  const bf16* dtp = a.dt + (long long)t0 * a.lddt + h;
-  const bf16* bp = a.Bm + (long long)t0 * a.ldb + g * N + ln * NPT;
-  const bf16* cp = a.Cm + (long long)t0 * a.ldc + g * N + ln * NPT;
-  bf16* yp = a.y + (long long)t0 * a.ldy + h * a.P + pc;
-  float Bn[NPT], Cn[NPT], xn = __bfloat162float(*xp), dtn = __bfloat162float(*dtp);
-  load_bf16<NPT>(bp, Bn);
-  load_bf16<NPT>(cp, Cn);
-  for (int t = 0; t < n; ++t) {
-    float Bc[NPT], Cc[NPT];
-    const float xv = xn;
-    float dt = softplus_f(dtn + dtb);
-    dt = fminf(fmaxf(dt, a.dt_min), a.dt_max);
+  float dt_sum = 0.f;
+  if (lo < hi) {
+    const long long tb = t0 + lo;
+    const bf16* xp = a.x + tb * a.ldx + h * a.P + pc;
+    const bf16* dtp = a.dt + tb * a.lddt + h;
+    const bf16* bp = a.Bm + tb * a.ldb + g * N + ln * NPT;
+    const bf16* cp = a.Cm + tb * a.ldc + g * N + ln * NPT;
+    bf16* yp = a.y + tb * a.ldy + h * a.P + pc;
+    float Bn[NPT], Cn[NPT], xn = __bfloat162float(*xp), dtn = __bfloat162float(*dtp);
+    load_bf16<NPT>(bp, Bn);
+    if (MODE != kLocal) load_bf16<NPT>(cp, Cn);
+    for (int t = lo; t < hi; ++t) {
+      float Bc[NPT], Cc[NPT];
+      const float xv = xn;
+      float dt = softplus_f(dtn + dtb);
+      dt = fminf(fmaxf(dt, a.dt_min), a.dt_max);
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) Bc[i] = Bn[i], Cc[i] = Cn[i];
-    if (t + 1 < n) {                                          // next token's inputs travel while this one is applied
-      xp += a.ldx, dtp += a.lddt, bp += a.ldb, cp += a.ldc;
-      xn = __bfloat162float(*xp), dtn = __bfloat162float(*dtp);
-      load_bf16<NPT>(bp, Bn);
-      load_bf16<NPT>(cp, Cn);
-    }
-    const float dA = __expf(dt * A), dx = dt * xv;
-    float acc = 0.f;
+      for (int i = 0; i < NPT; ++i) Bc[i] = Bn[i], Cc[i] = Cn[i];
+      if (t + 1 < hi) {                                       // next token's inputs travel while this one is applied
+        xp += a.ldx, dtp += a.lddt, bp += a.ldb, cp += a.ldc;
+        xn = __bfloat162float(*xp), dtn = __bfloat162float(*dtp);
+        load_bf16<NPT>(bp, Bn);
+        if (MODE != kLocal) load_bf16<NPT>(cp, Cn);
+      }
+      const float dA = __expf(dt * A), dx = dt * xv;
+      dt_sum += dt;
+      if (MODE == kLocal) {
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      hs[i] = fmaf(hs[i], dA, dx * Bc[i]);
-      acc = fmaf(hs[i], Cc[i], acc);
+        for (int i = 0; i < NPT; ++i) hs[i] = fmaf(hs[i], dA, dx * Bc[i]);
+      } else {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};                  // four chains instead of one of NPT dependent adds
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+          hs[i] = fmaf(hs[i], dA, dx * Bc[i]);
+          acc[i & 3] = fmaf(hs[i], Cc[i], acc[i & 3]);
+        }
+        const float tot = row_sum<TPN>((acc[0] + acc[1]) + (acc[2] + acc[3]));
+        if (ln == 0 && valid) *yp = __float2bfloat16(fmaf(D, xv, tot));
+        yp += a.ldy;
+      }
     }
-    acc = row_sum<TPN>(acc);
-    if (ln == 0 && valid) *yp = __float2bfloat16(fmaf(D, xv, acc));
-    yp += a.ldy;
   }
-  if (valid) store_f32<NPT>(st, hs);
+  if (MODE == kLocal) {
+    if (valid) store_f32<NPT>(sg + seg * seg_stride, hs);
+    if (blockIdx.x % ptiles == 0 && threadIdx.x == 0) a.seg_dt[((long long)s * (a.segs - 1) + seg) * a.H + h] = dt_sum;
+  } else if (valid && (MODE == kWhole || seg == a.segs - 1)) {
+    store_f32<NPT>(st, hs);
+  }
+}
+
+// start[seg + 1] = end_local[seg] + exp(A sum dt[seg]) * start[seg], in place over seg_state; one thread per four state values
+__global__ void mamba2_combine_kernel(const Mamba2Args a, int N) {
+  const long long per_seq = (long long)a.H * a.P * N;
+  const long long i4 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const int s = blockIdx.y;
+  if (i4 >= per_seq) return;
+  const int t0 = a.q_starts[s];
+  if (a.q_starts[s + 1] - t0 <= 0) return;
+  const int h = (int)(i4 / ((long long)a.P * N));
+  float4 carry = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (a.positions[t0] != 0) carry = *reinterpret_cast<const float4*>(a.state + (long long)a.seq_state[s] * per_seq + i4);
+  float* sg = a.seg_state + (long long)s * (a.segs - 1) * per_seq + i4;
+  const float A = a.A[h];
+  for (int seg = 0; seg < a.segs - 1; ++seg) {
+    const float d = __expf(A * a.seg_dt[((long long)s * (a.segs - 1) + seg) * a.H + h]);
+    float4 e = *reinterpret_cast<const float4*>(sg + seg * per_seq);
+    carry = make_float4(fmaf(carry.x, d, e.x), fmaf(carry.y, d, e.y), fmaf(carry.z, d, e.z), fmaf(carry.w, d, e.w));
+    *reinterpret_cast<float4*>(sg + seg * per_seq) = carry;
+  }
 }
 
 // ------------------------------------------------------------------------------------------ Mamba-1
@@ -469,20 +526,32 @@ int causal_conv1d(const void* x, long long ldx, const float* w, const float* bia
   return 0;
 }
 
+// seg_len > 0 with segs > 1: the sequence-parallel form (seg_state: B * (segs - 1) * H * P * N floats, seg_dt: B * (segs - 1) * H
+// floats); segs must cover the longest sequence of the step (segs * seg_len >= its tokens).
 int mamba2_scan(const void* x, long long ldx, const void* dt, long long lddt, const void* Bm, long long ldb, const void* Cm,
                 long long ldc, const float* A, const float* D, const float* dt_bias, float* state, const int* q_starts,
                 const int* seq_state, const int* positions, void* y, long long ldy, int B, int H, int P, int G, int N,
-                float dt_min, float dt_max, cudaStream_t stream) {
+                float dt_min, float dt_max, int seg_len, int segs, float* seg_state, float* seg_dt, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (!aligned16(Bm) || !aligned16(Cm) || (ldb % 8) || (ldc % 8) || G <= 0 || H % G) return -1;
+  const bool segmented = seg_len > 0 && segs > 1;
+  if (segmented && (seg_state == nullptr || seg_dt == nullptr || !aligned16(seg_state))) return -3;
   Mamba2Args a{static_cast<const bf16*>(x), static_cast<const bf16*>(dt), static_cast<const bf16*>(Bm), static_cast<const bf16*>(Cm),
                ldx, lddt, ldb, ldc, ldy, A, D, dt_bias, state, q_starts, seq_state, positions, static_cast<bf16*>(y), H, P, G,
-               dt_min, dt_max};
-#define FLLM_M2(N_, NPT_)                                                                     \
-  {                                                                                           \
-    constexpr int rows = 128 / (N_ / NPT_);                                                   \
-    mamba2_scan_kernel<N_, NPT_><<<dim3(H * ((P + rows - 1) / rows), B), 128, 0, stream>>>(a); \
-    return 0;                                                                                 \
+               dt_min, dt_max, seg_len, segs, seg_state, seg_dt};
+#define FLLM_M2(N_, NPT_)                                                                                          \
+  {                                                                                                                \
+    constexpr int rows = 128 / (N_ / NPT_);                                                                        \
+    const unsigned gx = H * ((P + rows - 1) / rows);                                                               \
+    if (!segmented) {                                                                                              \
+      mamba2_scan_kernel<N_, NPT_, kWhole><<<dim3(gx, B), 128, 0, stream>>>(a);                                    \
+    } else {                                                                                                       \
+      mamba2_scan_kernel<N_, NPT_, kLocal><<<dim3(gx, B, segs - 1), 128, 0, stream>>>(a);                          \
+      const long long per_seq = (long long)H * P * N_;                                                             \
+      mamba2_combine_kernel<<<dim3((unsigned)((per_seq / 4 + 255) / 256), B), 256, 0, stream>>>(a, N_);            \
+      mamba2_scan_kernel<N_, NPT_, kFinal><<<dim3(gx, B, segs), 128, 0, stream>>>(a);                              \
+    }                                                                                                              \
+    return 0;                                                                                                      \
   }
   switch (N) {
     case 16: FLLM_M2(16, 16)

@@ -49,7 +49,7 @@ class RecurrentRef:
         return y
 
     def mamba2_scan(self, x, dt, Bm, Cm, A, D, dt_bias, state, q_starts, seq_state, positions, H, P, G, N,
-                    dt_min=0.0, dt_max=float("inf")):
+                    dt_min=0.0, dt_max=float("inf"), max_q_len=0, seg_len=None):
         """h = exp(dt A) h + dt x (x) B;  y = h C + D x per head; dt = clamp(softplus(dt + dt_bias))."""
         y = torch.empty_like(x)
         rep = H // G
@@ -195,11 +195,24 @@ class RecurrentNative:
         return y
 
     def mamba2_scan(self, x, dt, Bm, Cm, A, D, dt_bias, state, q_starts, seq_state, positions, H, P, G, N,
-                    dt_min=0.0, dt_max=float("inf")):
+                    dt_min=0.0, dt_max=float("inf"), max_q_len=0, seg_len=None):
+        """``max_q_len`` (host-side bound on the tokens of a sequence in this step) lets long prompts of few sequences run
+        sequence-parallel: segments of ``seg_len`` tokens side by side, a short combine pass, then the outputs."""
         y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        B = seq_state.numel()
+        if seg_len is None:
+            ctas = B * H * max(1, P * max(N // 16, 1) // 128)
+            seg_len = 128 if (max_q_len >= 512 and ctas < 4 * 148) else 0
+        segs = -(-int(max_q_len) // seg_len) if seg_len else 1
+        scratch = None
+        if segs > 1:
+            need = B * (segs - 1) * (H * P * N + H)
+            scratch = getattr(self, "_scan_scratch", None)
+            if scratch is None or scratch.numel() < need:
+                scratch = self._scan_scratch = torch.empty(need, dtype=torch.float32, device=x.device)
         self.k.mamba2_scan(x, dt, Bm, Cm, A, D, dt_bias, state, q_starts, seq_state, positions, y, H, P, G, N,
-                           float(dt_min), float(min(dt_max, 3.0e38)))
-        self.launches += 1
+                           float(dt_min), float(min(dt_max, 3.0e38)), int(seg_len if segs > 1 else 0), int(segs), scratch)
+        self.launches += 3 if segs > 1 else 1
         return y
 
     def mamba1_scan(self, x, dt, Bm, Cm, z, A, D, dt_bias, state, q_starts, seq_state, positions):

@@ -74,6 +74,31 @@ def test_mamba2_scan(ops, N, P, H, G, case):
     assert rel(st, st_ref) < 1e-4
 
 
+@pytest.mark.parametrize("seg_len", [64, 128])
+def test_mamba2_scan_sequence_parallel(ops, seg_len):
+    """Segments side by side + combine + second pass give the plain walk's outputs and states: a fresh long prompt, a
+    continued one, a short one (most of its segments empty) and a decode row in one step; also when `segs` is sized
+    for fewer tokens than the longest sequence has."""
+    nat, ref = ops
+    lens, fresh, slots = [700, 300, 40, 1], [True, False, True, False], [3, 0, 2, 5]
+    qs, ss, pos, T = ragged(lens, fresh, slots)
+    H, P, G, N = 8, 64, 2, 128
+    g = torch.Generator(device="cuda").manual_seed(seg_len)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    x, dt = rn(T, H * P).bfloat16(), rn(T, H).bfloat16()
+    Bm, Cm = rn(T, G * N).bfloat16(), rn(T, G * N).bfloat16()
+    A, D, dtb = -torch.exp(rn(H) * 0.5), rn(H), rn(H) * 0.5 - 1.0
+    st0 = rn(6, H, P, N) * 0.5
+    st_ref = st0.clone()
+    y_ref = ref.mamba2_scan(x, dt, Bm, Cm, A, D, dtb, st_ref, qs, ss, pos, H, P, G, N, 0.001, 100.0)
+    for max_q in (700, 500):
+        st = st0.clone()
+        y = nat.mamba2_scan(x, dt, Bm, Cm, A, D, dtb, st, qs, ss, pos, H, P, G, N, 0.001, 100.0, max_q_len=max_q, seg_len=seg_len)
+        torch.cuda.synchronize()
+        assert rel(y, y_ref) < 1e-2 and rel(st, st_ref) < 1e-3, max_q
+    assert nat.launches >= 6                                     # three launches per segmented call
+
+
 @pytest.mark.parametrize("N", [16, 8])
 @pytest.mark.parametrize("case", CASES)
 def test_mamba1_scan(ops, N, case):
