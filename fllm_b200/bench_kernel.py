@@ -182,7 +182,7 @@ def run_case(case: str, reps: int = 4) -> None:
             Bm, Cm = torch.randn(T, N, **bf), torch.randn(T, N, **bf)
             A, D_, dtb = -torch.rand(Hh, device="cuda"), torch.ones(Hh, device="cuda"), torch.zeros(Hh, device="cuda")
             st = torch.zeros(B, Hh, P, N, device="cuda")
-            fn = lambda: ops.mamba2_scan(x, dt, Bm, Cm, A, D_, dtb, st, qs, ss, pos, Hh, P, 1, N, 0.0, 1e30)
+            fn = lambda: ops.mamba2_scan(x, dt, Bm, Cm, A, D_, dtb, st, qs, ss, pos, Hh, P, 1, N, 0.0, 1e30, max_q_len=n)
         nbytes = st.numel() * 4 * 2
     else:
         raise SystemExit(f"unknown case {case}")

@@ -85,13 +85,26 @@ void mamba1_scan(const Tensor& x, const Tensor& dt, const Tensor& Bm, const Tens
 }
 
 void matrix_state_scan(int64_t kind, const Tensor& r, const Tensor& k, const Tensor& v, const optional<Tensor>& a, const optional<Tensor>& b,
-                       const Tensor& w, const optional<Tensor>& u, const optional<Tensor>& beta, Tensor state, const Tensor& q_starts,
+                       const optional<Tensor>& w_opt, const optional<Tensor>& u, const optional<Tensor>& beta, Tensor state, const Tensor& q_starts,
                        const Tensor& seq_state, const Tensor& positions, Tensor y, int64_t H, int64_t DK, int64_t DV, int64_t kv_ratio,
-                       bool l2norm, double q_scale) {
+                       bool l2norm, double q_scale, const optional<Tensor>& gate_raw, const optional<Tensor>& gate_A,
+                       const optional<Tensor>& gate_dt_bias) {
   TORCH_CHECK(rows_bf16(r) && rows_bf16(k) && rows_bf16(v) && rows_bf16(y), "activations: bf16 rows");
-  TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kFloat && w.dim() == 2 && w.stride(1) == 1, "w: fp32 rows of log decays");
   TORCH_CHECK(v.size(1) == H * DV && y.size(1) == H * DV && r.size(1) == (H / kv_ratio) * DK && k.size(1) == r.size(1), "widths");
-  TORCH_CHECK(w.size(1) == (kind == 2 ? H : r.size(1)), "w: one decay per head (kind 2) or per key channel");
+  const bool raw = !(w_opt.has_value() && w_opt->defined());
+  const float* w_ptr = nullptr;
+  long long w_ld = 0;
+  if (!raw) {
+    const Tensor& w = *w_opt;
+    TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kFloat && w.dim() == 2 && w.stride(1) == 1, "w: fp32 rows of log decays");
+    TORCH_CHECK(w.size(1) == (kind == 2 ? H : r.size(1)), "w: one decay per head (kind 2) or per key channel");
+    w_ptr = w.data_ptr<float>();
+    w_ld = w.stride(0);
+  } else {
+    TORCH_CHECK(kind == 2 && gate_raw.has_value() && rows_bf16(*gate_raw) && gate_raw->size(1) == H && gate_A.has_value() &&
+                    gate_dt_bias.has_value() && gate_A->numel() == H && gate_dt_bias->numel() == H,
+                "raw gates: kind 2 with gate_raw bf16 [T, H], gate_A and gate_dt_bias fp32 [H]");
+  }
   TORCH_CHECK(kind != 1 || (a.has_value() && b.has_value() && rows_bf16(*a) && rows_bf16(*b)), "RWKV-7 needs a and b");
   TORCH_CHECK(kind != 0 || (u.has_value() && u->numel() == r.size(1)), "RWKV-6 needs the bonus u");
   TORCH_CHECK(kind < 2 || (beta.has_value() && rows_bf16(*beta) && beta->size(1) == H), "delta rules need beta [T, H]");
@@ -100,10 +113,11 @@ void matrix_state_scan(int64_t kind, const Tensor& r, const Tensor& k, const Ten
   check_batch(q_starts, seq_state, positions);
   c10::cuda::CUDAGuard guard(r.device());
   const int rc = fllm::matrix_state_scan((int)kind, r.data_ptr(), r.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), opt_ptr(a),
-                                         opt_ld(a), opt_ptr(b), opt_ld(b), w.data_ptr<float>(), w.stride(0), opt_f32(u), opt_ptr(beta),
+                                         opt_ld(a), opt_ptr(b), opt_ld(b), w_ptr, w_ld, opt_f32(u), opt_ptr(beta),
                                          opt_ld(beta), state.data_ptr<float>(), q_starts.data_ptr<int>(), seq_state.data_ptr<int>(),
                                          positions.data_ptr<int>(), y.data_ptr(), y.stride(0), (int)seq_state.numel(), (int)H, (int)DK, (int)DV,
-                                         (int)kv_ratio, l2norm ? 1 : 0, (float)q_scale, cur_stream());
+                                         (int)kv_ratio, l2norm ? 1 : 0, (float)q_scale, opt_ptr(gate_raw), opt_ld(gate_raw), opt_f32(gate_A),
+                                         opt_f32(gate_dt_bias), cur_stream());
   TORCH_CHECK(rc == 0, "matrix_state_scan: unsupported arguments (code ", rc, "): key width 32 / 64 / 128 / 256, 16-byte aligned rows");
 }
 
@@ -190,8 +204,9 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
   m.def("mamba1_scan(Tensor x, Tensor dt, Tensor Bm, Tensor Cm, Tensor? z, Tensor A, Tensor? D, Tensor? dt_bias, Tensor(a!) state, "
         "Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y) -> ()",
         &mamba1_scan);
-  m.def("matrix_state_scan(int kind, Tensor r, Tensor k, Tensor v, Tensor? a, Tensor? b, Tensor w, Tensor? u, Tensor? beta, Tensor(a!) state, "
-        "Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y, int H, int DK, int DV, int kv_ratio, bool l2norm, float q_scale) -> ()",
+  m.def("matrix_state_scan(int kind, Tensor r, Tensor k, Tensor v, Tensor? a, Tensor? b, Tensor? w, Tensor? u, Tensor? beta, Tensor(a!) state, "
+        "Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y, int H, int DK, int DV, int kv_ratio, bool l2norm, float q_scale, "
+        "Tensor? gate_raw, Tensor? gate_A, Tensor? gate_dt_bias) -> ()",
         &matrix_state_scan);
   m.def("attention_mla(Tensor q_abs, Tensor q_pe, Tensor cache, Tensor block_tables, Tensor row_seq, Tensor positions, Tensor(a!) out, "
         "bool head_major, float scale, int splits, Tensor? workspace) -> ()", &attention_mla);

@@ -282,12 +282,15 @@ int mamba1_scan(const void* x, long long ldx, const void* dt, long long lddt, co
                 long long ldc, const void* z, long long ldz, const float* A, const float* D, const float* dt_bias, float* state,
                 const int* q_starts, const int* seq_state, const int* positions, void* y, long long ldy, int B, int Dm, int N,
                 cudaStream_t stream);
-// kind: 0 RWKV-6, 1 RWKV-7, 2 gated delta rule (one decay per head), 3 delta rule with a decay per key channel
+// kind: 0 RWKV-6, 1 RWKV-7, 2 gated delta rule (one decay per head), 3 delta rule with a decay per key channel.
+// Kind 2 with w == nullptr takes raw gates: beta = logit of the step size, gate_raw [T][H] = logit of the decay,
+// log decay = gate_A[h] * softplus(gate_raw + gate_dt_bias[h]).
 int matrix_state_scan(int kind, const void* r, long long ldr, const void* k, long long ldk, const void* v, long long ldv,
                       const void* a, long long lda, const void* b, long long ldb, const float* w, long long ldw, const float* u,
                       const void* beta, long long ldbeta, float* state, const int* q_starts, const int* seq_state,
                       const int* positions, void* y, long long ldy, int B, int H, int DK, int DV, int kv_ratio, int l2norm,
-                      float q_scale, cudaStream_t stream);
+                      float q_scale, const void* gate_raw, long long ldgate, const float* gate_A, const float* gate_dt_bias,
+                      cudaStream_t stream);
 void gated_rmsnorm(const void* x, long long ldx, const void* z, long long ldz, const void* w, int wlen, void* y, long long ldy, int T,
                    int D, int group_size, float eps, int norm_before_gate, cudaStream_t stream);
 

@@ -305,6 +305,11 @@ struct MatrixStateArgs {
   int H, DV, kv_ratio;               // value heads per key head (q, k, w of head h come from head h / kv_ratio)
   int l2norm;                        // delta kinds: normalise q and k over DK inside the kernel
   float q_scale;
+  // kGatedDelta with raw gates (w == nullptr): beta holds the logit of the step size, gate_raw [T][H] the logit a of the
+  // decay; step size = sigmoid(beta), log decay = gate_A[h] * softplus(a + gate_dt_bias[h])
+  const bf16* gate_raw;
+  long long ldgate;
+  const float *gate_A, *gate_dt_bias;
 };
 
 template <int KIND, int DK>
@@ -335,7 +340,9 @@ __global__ void __launch_bounds__(128) matrix_state_kernel(const MatrixStateArgs
     load_bf16<NPT>(a.k + t * a.ldk + ko, k);
     const float vv = __bfloat162float(a.v[t * a.ldv + (long long)h * a.DV + vc]);
     if (KIND == kGatedDelta) {
-      const float dh = __expf(a.w[t * a.ldw + h]);
+      const float dh = a.w != nullptr
+                           ? __expf(a.w[t * a.ldw + h])
+                           : __expf(a.gate_A[h] * softplus_f(__bfloat162float(a.gate_raw[t * a.ldgate + h]) + a.gate_dt_bias[h]));
 #pragma unroll
       for (int i = 0; i < NPT; ++i) d[i] = dh;
     } else {
@@ -384,7 +391,9 @@ __global__ void __launch_bounds__(128) matrix_state_kernel(const MatrixStateArgs
         m = fmaf(S[i], k[i], m);
       }
       m = row_sum<TPK>(m);
-      const float delta = (vv - m) * __bfloat162float(a.beta[t * a.ldbeta + h]);
+      float step = __bfloat162float(a.beta[t * a.ldbeta + h]);
+      if (KIND == kGatedDelta && a.w == nullptr) step = 1.f / (1.f + __expf(-step));
+      const float delta = (vv - m) * step;
 #pragma unroll
       for (int i = 0; i < NPT; ++i) {
         S[i] = fmaf(k[i], delta, S[i]);
@@ -584,15 +593,18 @@ int matrix_state_scan(int kind, const void* r, long long ldr, const void* k, lon
                       const void* a_, long long lda, const void* b_, long long ldb, const float* w, long long ldw, const float* u,
                       const void* beta, long long ldbeta, float* state, const int* q_starts, const int* seq_state,
                       const int* positions, void* y, long long ldy, int B, int H, int DK, int DV, int kv_ratio, int l2norm,
-                      float q_scale, cudaStream_t stream) {
+                      float q_scale, const void* gate_raw, long long ldgate, const float* gate_A, const float* gate_dt_bias,
+                      cudaStream_t stream) {
   if (B <= 0) return 0;
   if (!aligned16(r) || !aligned16(k) || (ldr % 8) || (ldk % 8) || kv_ratio <= 0 || H % kv_ratio) return -1;
+  if (w == nullptr && (kind != kGatedDelta || gate_raw == nullptr || gate_A == nullptr || gate_dt_bias == nullptr)) return -4;
   if (kind != kGatedDelta && (!aligned16(w) || (ldw % 4))) return -1;
   if (kind == kRwkv7 && (!aligned16(a_) || !aligned16(b_) || (lda % 8) || (ldb % 8))) return -1;
   if (kind == kRwkv6 && !aligned16(u)) return -1;
   MatrixStateArgs m{static_cast<const bf16*>(r), static_cast<const bf16*>(k), static_cast<const bf16*>(v), static_cast<const bf16*>(a_),
                     static_cast<const bf16*>(b_), w, u, static_cast<const bf16*>(beta), ldr, ldk, ldv, lda, ldb, ldw, ldbeta, ldy, state,
-                    q_starts, seq_state, positions, static_cast<bf16*>(y), H, DV, kv_ratio, l2norm, q_scale};
+                    q_starts, seq_state, positions, static_cast<bf16*>(y), H, DV, kv_ratio, l2norm, q_scale,
+                    static_cast<const bf16*>(gate_raw), ldgate, gate_A, gate_dt_bias};
 #define FLLM_MS(KIND_, DK_)                                                                        \
   {                                                                                                \
     constexpr int rows = 128 / (DK_ / 16);                                                         \

@@ -142,7 +142,8 @@ def mamba2_mixer(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
 
 
 def gated_delta_mixer(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
-    """in_proj -> (q, k, v | z | beta, a); (q, k, v) = silu(conv(q, k, v)); decay = -exp(A_log) softplus(a + dt_bias);
+    """in_proj -> (q, k, v | z | beta, a); (q, k, v) = silu(conv(q, k, v)); log decay = -exp(A_log) softplus(a + dt_bias)
+    and step size = sigmoid(beta), both computed inside the scan;
     delta rule with L2-normalised q, k; per-head rmsnorm(y) * w * silu(z); out_proj."""
     s, m, ops = dec.cfg.ssm, lw.mixer, dec.ops
     qs, ss, pos = _batch_meta(b)
@@ -151,11 +152,10 @@ def gated_delta_mixer(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
     proj = ops.linear(h, m["in_proj"])                                  # [q | k | v | z | beta | a] (+ padding)
     qkv = ops.causal_conv1d(proj[:, :2 * K + V], m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=True)
     z = proj[:, 2 * K + V:2 * K + 2 * V]
-    ba = proj[:, 2 * K + 2 * V:2 * K + 2 * V + 2 * Hv].float()
-    beta = torch.sigmoid(ba[:, :Hv]).to(h.dtype)
-    g = (m["A"] * torch.nn.functional.softplus(ba[:, Hv:] + m["dt_bias"])).contiguous()          # fp32 [T, Hv], negative
-    y = ops.matrix_state_scan(GATED_DELTA, qkv[:, :K], qkv[:, K:2 * K], qkv[:, 2 * K:], None, None, g, None, beta,
-                              dec.rstate.scan[li], qs, ss, pos, Hv, Dk, Dv, Hv // Hk, True, Dk ** -0.5)
+    o = 2 * K + 2 * V                                                   # the step-size and decay logits go to the scan raw
+    y = ops.matrix_state_scan(GATED_DELTA, qkv[:, :K], qkv[:, K:2 * K], qkv[:, 2 * K:], None, None, None, None, proj[:, o:o + Hv],
+                              dec.rstate.scan[li], qs, ss, pos, Hv, Dk, Dv, Hv // Hk, True, Dk ** -0.5,
+                              gate_raw=proj[:, o + Hv:o + 2 * Hv], gate_A=m["A"], gate_dt_bias=m["dt_bias"])
     y = ops.gated_rmsnorm(y, z, m["norm_w"], s.get("norm_eps", dec.cfg.rms_eps), Dv, True)
     return ops.linear(y, m["out_proj"])
 

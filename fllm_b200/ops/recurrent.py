@@ -87,10 +87,13 @@ class RecurrentRef:
         return y
 
     def matrix_state_scan(self, kind, r, k, v, a, b, w, u, beta, state, q_starts, seq_state, positions, H, DK, DV,
-                          kv_ratio=1, l2norm=False, q_scale=1.0):
+                          kv_ratio=1, l2norm=False, q_scale=1.0, gate_raw=None, gate_A=None, gate_dt_bias=None):
         """State S[v, k] per head; ``w`` holds log decays (fp32). See the kinds at the top of the module:
         RWKV-6  y = sum_k r (u k v + S), S = S d + k v;  RWKV-7  sa = S a, S = S d + sa b + v k, y = S r;
         delta rules  S = S d, m = S k, S += (v - m) beta k, y = S q * q_scale (q, k L2-normalised when asked)."""
+        if w is None:            # gated delta rule with raw gates: step size and decay from their logits
+            beta = torch.sigmoid(beta.float())
+            w = gate_A.float() * F.softplus(gate_raw.float() + gate_dt_bias.float())
         y = torch.empty(r.shape[0], H * DV, dtype=r.dtype, device=r.device)
         for t0, t1, slot, fresh in _seqs(q_starts, seq_state, positions):
             S = torch.zeros(H, DV, DK, dtype=torch.float32, device=r.device) if fresh else state[slot].clone()
@@ -222,10 +225,10 @@ class RecurrentNative:
         return y
 
     def matrix_state_scan(self, kind, r, k, v, a, b, w, u, beta, state, q_starts, seq_state, positions, H, DK, DV,
-                          kv_ratio=1, l2norm=False, q_scale=1.0):
+                          kv_ratio=1, l2norm=False, q_scale=1.0, gate_raw=None, gate_A=None, gate_dt_bias=None):
         y = torch.empty(r.shape[0], H * DV, dtype=r.dtype, device=r.device)
         self.k.matrix_state_scan(int(kind), r, k, v, a, b, w, u, beta, state, q_starts, seq_state, positions, y, H, DK,
-                                 DV, int(kv_ratio), bool(l2norm), float(q_scale))
+                                 DV, int(kv_ratio), bool(l2norm), float(q_scale), gate_raw, gate_A, gate_dt_bias)
         self.launches += 1
         return y
 

@@ -224,3 +224,23 @@ def test_latent_prepare_kernel(ops):
     torch.cuda.synchronize()
     assert rel(a, b) < 1e-2 and rel(c1, c2) < 1e-2
     assert int((c1.view(-1, 576).abs().sum(-1) > 0).sum()) == T - 1
+
+
+def test_gated_delta_raw_gates(ops):
+    """The scan computes the step size and the decay from their logits (views of one projection output)."""
+    nat, ref = ops
+    qs, ss, pos, T = ragged([5, 1, 17, 1], [True, False, False, True], [3, 0, 2, 5])
+    Hv, Hk, D = 4, 2, 128
+    g = torch.Generator(device="cuda").manual_seed(11)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    r, k, v = rn(T, Hk * D).bfloat16(), (rn(T, Hk * D) * 0.3).bfloat16(), rn(T, Hv * D).bfloat16()
+    ba = rn(T, 2 * Hv + 8).bfloat16()
+    A, dtb = -torch.exp(rn(Hv) * 0.5), rn(Hv) * 0.5
+    st = rn(6, Hv, D, D) * 0.3
+    st_ref = st.clone()
+    args = (GATED_DELTA, r, k, v, None, None, None, None, ba[:, :Hv])
+    kw = dict(gate_raw=ba[:, Hv:2 * Hv], gate_A=A, gate_dt_bias=dtb)
+    y = nat.matrix_state_scan(*args, st, qs, ss, pos, Hv, D, D, 2, True, D ** -0.5, **kw)
+    y_ref = ref.matrix_state_scan(*args, st_ref, qs, ss, pos, Hv, D, D, 2, True, D ** -0.5, **kw)
+    torch.cuda.synchronize()
+    assert rel(y, y_ref) < 1e-2 and rel(st, st_ref) < 1e-4
