@@ -43,7 +43,7 @@ void causal_conv1d(const Tensor& x, const Tensor& w, const optional<Tensor>& bia
 void mamba2_scan(const Tensor& x, const Tensor& dt, const Tensor& Bm, const Tensor& Cm, const Tensor& A, const optional<Tensor>& D,
                  const optional<Tensor>& dt_bias, Tensor state, const Tensor& q_starts, const Tensor& seq_state, const Tensor& positions,
                  Tensor y, int64_t H, int64_t P, int64_t G, int64_t N, double dt_min, double dt_max, int64_t seg_len, int64_t segs,
-                 const optional<Tensor>& seg_scratch) {
+                 const optional<Tensor>& seg_scratch, int64_t skip_from) {
   TORCH_CHECK(rows_bf16(x) && rows_bf16(dt) && rows_bf16(Bm) && rows_bf16(Cm) && rows_bf16(y), "activations: bf16 rows");
   TORCH_CHECK(x.size(1) == H * P && y.size(1) == H * P && dt.size(1) == H && Bm.size(1) == G * N && Cm.size(1) == G * N, "widths");
   TORCH_CHECK(state.scalar_type() == at::kFloat && state.is_contiguous() && state.dim() == 4 && state.size(1) == H && state.size(2) == P &&
@@ -63,7 +63,7 @@ void mamba2_scan(const Tensor& x, const Tensor& dt, const Tensor& Bm, const Tens
                                    Cm.stride(0), opt_f32(A), opt_f32(D), opt_f32(dt_bias), state.data_ptr<float>(), q_starts.data_ptr<int>(),
                                    seq_state.data_ptr<int>(), positions.data_ptr<int>(), y.data_ptr(), y.stride(0), (int)B,
                                    (int)H, (int)P, (int)G, (int)N, (float)dt_min, (float)dt_max, (int)seg_len, (int)segs, seg_state, seg_dt,
-                                   cur_stream());
+                                   (int)skip_from, cur_stream());
   TORCH_CHECK(rc == 0, "mamba2_scan: unsupported arguments (code ", rc, "): state width 16 / 32 / 64 / 128 / 256, B and C 16-byte aligned");
 }
 
@@ -199,7 +199,7 @@ TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
         &causal_conv1d);
   m.def("mamba2_scan(Tensor x, Tensor dt, Tensor Bm, Tensor Cm, Tensor A, Tensor? D, Tensor? dt_bias, Tensor(a!) state, Tensor q_starts, "
         "Tensor seq_state, Tensor positions, Tensor(b!) y, int H, int P, int G, int N, float dt_min, float dt_max, int seg_len, int segs, "
-        "Tensor? seg_scratch) -> ()",
+        "Tensor? seg_scratch, int skip_from) -> ()",
         &mamba2_scan);
   m.def("mamba1_scan(Tensor x, Tensor dt, Tensor Bm, Tensor Cm, Tensor? z, Tensor A, Tensor? D, Tensor? dt_bias, Tensor(a!) state, "
         "Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y) -> ()",

@@ -277,7 +277,8 @@ int causal_conv1d(const void* x, long long ldx, const float* w, const float* bia
 int mamba2_scan(const void* x, long long ldx, const void* dt, long long lddt, const void* Bm, long long ldb, const void* Cm,
                 long long ldc, const float* A, const float* D, const float* dt_bias, float* state, const int* q_starts,
                 const int* seq_state, const int* positions, void* y, long long ldy, int B, int H, int P, int G, int N,
-                float dt_min, float dt_max, int seg_len, int segs, float* seg_state, float* seg_dt, cudaStream_t stream);
+                float dt_min, float dt_max, int seg_len, int segs, float* seg_state, float* seg_dt, int skip_from,
+                cudaStream_t stream);
 int mamba1_scan(const void* x, long long ldx, const void* dt, long long lddt, const void* Bm, long long ldb, const void* Cm,
                 long long ldc, const void* z, long long ldz, const float* A, const float* D, const float* dt_bias, float* state,
                 const int* q_starts, const int* seq_state, const int* positions, void* y, long long ldy, int B, int Dm, int N,

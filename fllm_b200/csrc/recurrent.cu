@@ -133,6 +133,7 @@ struct Mamba2Args {
   bf16* y;
   int H, P, G;
   float dt_min, dt_max;
+  int skip_from;                // sequences with at least this many tokens in the step are left to another path (0 = none)
   int seg_len, segs;            // segmented modes only
   float* seg_state;             // [B][segs - 1][H][P][N]: end states (kLocal), then start states of segments 1.. (combine)
   float* seg_dt;                // [B][segs - 1][H]: sum of the time steps of a segment
@@ -145,7 +146,7 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Args a) {
   const int h = blockIdx.x / ptiles, p = (blockIdx.x % ptiles) * ROWS + threadIdx.x / TPN;
   const int ln = threadIdx.x % TPN, s = blockIdx.y, seg = MODE == kWhole ? 0 : blockIdx.z;
   const int t0 = a.q_starts[s], n = a.q_starts[s + 1] - t0;
-  if (n <= 0) return;
+  if (n <= 0 || (a.skip_from > 0 && n >= a.skip_from)) return;
   const bool valid = p < a.P;
   const int pc = valid ? p : a.P - 1;                        // lanes of a ragged last tile repeat the last row, unstored
   float* st = a.state + (((long long)a.seq_state[s] * a.H + h) * a.P + pc) * N + ln * NPT;
@@ -225,7 +226,8 @@ __global__ void mamba2_combine_kernel(const Mamba2Args a, int N) {
   const int s = blockIdx.y;
   if (i4 >= per_seq) return;
   const int t0 = a.q_starts[s];
-  if (a.q_starts[s + 1] - t0 <= 0) return;
+  const int n = a.q_starts[s + 1] - t0;
+  if (n <= 0 || (a.skip_from > 0 && n >= a.skip_from)) return;
   const int h = (int)(i4 / ((long long)a.P * N));
   float4 carry = make_float4(0.f, 0.f, 0.f, 0.f);
   if (a.positions[t0] != 0) carry = *reinterpret_cast<const float4*>(a.state + (long long)a.seq_state[s] * per_seq + i4);
@@ -540,14 +542,15 @@ int causal_conv1d(const void* x, long long ldx, const float* w, const float* bia
 int mamba2_scan(const void* x, long long ldx, const void* dt, long long lddt, const void* Bm, long long ldb, const void* Cm,
                 long long ldc, const float* A, const float* D, const float* dt_bias, float* state, const int* q_starts,
                 const int* seq_state, const int* positions, void* y, long long ldy, int B, int H, int P, int G, int N,
-                float dt_min, float dt_max, int seg_len, int segs, float* seg_state, float* seg_dt, cudaStream_t stream) {
+                float dt_min, float dt_max, int seg_len, int segs, float* seg_state, float* seg_dt, int skip_from,
+                cudaStream_t stream) {
   if (B <= 0) return 0;
   if (!aligned16(Bm) || !aligned16(Cm) || (ldb % 8) || (ldc % 8) || G <= 0 || H % G) return -1;
   const bool segmented = seg_len > 0 && segs > 1;
   if (segmented && (seg_state == nullptr || seg_dt == nullptr || !aligned16(seg_state))) return -3;
   Mamba2Args a{static_cast<const bf16*>(x), static_cast<const bf16*>(dt), static_cast<const bf16*>(Bm), static_cast<const bf16*>(Cm),
                ldx, lddt, ldb, ldc, ldy, A, D, dt_bias, state, q_starts, seq_state, positions, static_cast<bf16*>(y), H, P, G,
-               dt_min, dt_max, seg_len, segs, seg_state, seg_dt};
+               dt_min, dt_max, skip_from, seg_len, segs, seg_state, seg_dt};
 #define FLLM_M2(N_, NPT_)                                                                                          \
   {                                                                                                                \
     constexpr int rows = 128 / (N_ / NPT_);                                                                        \

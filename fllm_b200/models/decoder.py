@@ -42,6 +42,7 @@ class StepBatch:
     seq_lens: Optional[torch.Tensor] = None      # [B] int32 visible KV length per sequence
     q_starts: Optional[torch.Tensor] = None      # [B+1] int32 first token row of each sequence
     seq_state: Optional[torch.Tensor] = None     # [B] int32 row of the recurrent-state pools (hybrid families)
+    host_seqs: Optional[list] = None             # the same on the host for steps with long prompt chunks: (first row, rows, state row, fresh)
 
 
 class KVCache:

@@ -136,7 +136,7 @@ def mamba2_mixer(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
     xbc = ops.causal_conv1d(zxd[:, Di:Di + C], m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=True)
     y = ops.mamba2_scan(xbc[:, :Di], zxd[:, Di + C:Di + C + H], xbc[:, Di:Di + G * N], xbc[:, Di + G * N:], m["A"], m["D"],
                         m["dt_bias"], dec.rstate.scan[li], qs, ss, pos, H, P, G, N, s.get("dt_min", 0.0),
-                        s.get("dt_max", 1e30), getattr(b, "max_q_len", 0))
+                        s.get("dt_max", 1e30), getattr(b, "max_q_len", 0), None, getattr(b, "host_seqs", None))
     y = ops.gated_rmsnorm(y, zxd[:, :Di], m["norm_w"], s.get("norm_eps", dec.cfg.rms_eps), Di // s.get("norm_groups", 1), False)
     return ops.linear(y, m["out_proj"], m.get("out_proj_b"))
 

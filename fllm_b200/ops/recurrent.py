@@ -19,6 +19,11 @@ import torch
 import torch.nn.functional as F
 
 RWKV6, RWKV7, GATED_DELTA, KDA = 0, 1, 2, 3
+# Mamba-2 prompt chunks from this many tokens on take the matrix form (``ssd_chunked``) instead of the token walk; 0 = never.
+# Off by default: as a chain of PyTorch operators (about 40 launches per layer and sequence over [chunks, heads, 128, 128]
+# tensors) it measured slower than the sequence-parallel scan kernel on a B200 (Mamba-2 2.7B prefill 15.3 k against
+# 16.6 k tok/s); it is kept as the tested statement of the algorithm a fused kernel would implement.
+SSD_MIN_TOKENS = int(__import__("os").environ.get("FLLM_SSD_MIN_TOKENS", "0"))
 
 
 def _seqs(q_starts, seq_state, positions):
@@ -28,6 +33,55 @@ def _seqs(q_starts, seq_state, positions):
         t0, t1 = qs[s], qs[s + 1]
         if t1 > t0:
             yield t0, t1, slots[s], int(positions[t0]) == 0
+
+
+def ssd_chunked(x, dt, Bm, Cm, A, D, dt_bias, h0, H, P, G, N, dt_min=0.0, dt_max=float("inf"), chunk=128):
+    """One sequence of the Mamba-2 recurrence in its matrix form (the state-space duality of the Mamba-2 paper): inside
+    chunks of ``chunk`` tokens the outputs are (C B^T masked by the decay between the two positions) X, a chunk hands
+    B^T (decay to the chunk's end * X) to the next one, and the carried state enters each chunk through C. All of it is
+    batched matrix products (tensor cores through the library GEMM on a GPU) instead of a walk over the tokens; the
+    reference gets the same effect with its chunk-parallel scan (rust/engine/cuda/scan.cu, 64-token chunks).
+
+    x [n, H*P], dt [n, H] (raw), Bm / Cm [n, G*N], h0 [H, P, N] fp32 or None. Returns (y [n, H*P] in x's type, final
+    state [H, P, N] fp32)."""
+    n = x.shape[0]
+    r = H // G
+    dev = x.device
+    dtf = F.softplus(dt.float() + (dt_bias.float() if dt_bias is not None else 0.0)).clamp(dt_min, dt_max)     # [n, H]
+    xf = x.float().view(n, H, P)
+    Xd = xf * dtf[:, :, None]
+    Ad = dtf * A.float()                                                     # [n, H], log decay per step (negative)
+    Bf, Cf = Bm.float().view(n, G, N), Cm.float().view(n, G, N)
+    pad = (-n) % chunk
+    if pad:                                                                   # zero steps: decay 1, no input
+        Xd = F.pad(Xd, (0, 0, 0, 0, 0, pad))
+        Ad = F.pad(Ad, (0, 0, 0, pad))
+        Bf, Cf = F.pad(Bf, (0, 0, 0, 0, 0, pad)), F.pad(Cf, (0, 0, 0, 0, 0, pad))
+    c, Q = (n + pad) // chunk, chunk
+    Xc = Xd.view(c, Q, G, r, P)
+    Bc, Cc = Bf.view(c, Q, G, N), Cf.view(c, Q, G, N)
+    Acs = torch.cumsum(Ad.view(c, Q, G, r), 1)                                # [c, Q, G, r] log decay from the chunk start
+    # inside a chunk: y[l] += sum_{s <= l} (C[l] . B[s]) exp(Acs[l] - Acs[s]) X[s]
+    CB = torch.einsum("clgn,csgn->cgls", Cc, Bc)                              # [c, G, Q, Q]
+    diff = Acs.permute(0, 2, 3, 1)[..., :, None] - Acs.permute(0, 2, 3, 1)[..., None, :]        # [c, G, r, Q(l), Q(s)]
+    tril = torch.ones(Q, Q, dtype=torch.bool, device=dev).tril()
+    M = torch.exp(diff.masked_fill(~tril, float("-inf"))) * CB[:, :, None]
+    Y = torch.matmul(M, Xc.permute(0, 2, 3, 1, 4))                            # [c, G, r, Q, P]
+    # what a chunk adds to the state: sum_l B[l] (decay from l to the chunk end) X[l]
+    to_end = torch.exp(Acs[:, -1:, :, :] - Acs)                               # [c, Q, G, r]
+    add = torch.einsum("clgrp,clgn->cgrpn", Xc * to_end[..., None], Bc)       # [c, G, r, P, N]
+    chunk_decay = torch.exp(Acs[:, -1])                                        # [c, G, r]
+    h = h0.float().view(G, r, P, N) if h0 is not None else torch.zeros(G, r, P, N, dtype=torch.float32, device=dev)
+    starts = []
+    for ci in range(c):                                                        # the carried state: c short steps
+        starts.append(h)
+        h = h * chunk_decay[ci, :, :, None, None] + add[ci]
+    S0 = torch.stack(starts)                                                   # [c, G, r, P, N] state entering each chunk
+    Y = Y + torch.einsum("clgn,cgrpn->cgrlp", Cc, S0) * torch.exp(Acs).permute(0, 2, 3, 1)[..., None]
+    y = Y.permute(0, 3, 1, 2, 4).reshape(c * Q, H, P)[:n]
+    if D is not None:
+        y = y + D.float()[:, None] * xf
+    return y.reshape(n, H * P).to(x.dtype), h.reshape(H, P, N)
 
 
 class RecurrentRef:
@@ -49,7 +103,7 @@ class RecurrentRef:
         return y
 
     def mamba2_scan(self, x, dt, Bm, Cm, A, D, dt_bias, state, q_starts, seq_state, positions, H, P, G, N,
-                    dt_min=0.0, dt_max=float("inf"), max_q_len=0, seg_len=None):
+                    dt_min=0.0, dt_max=float("inf"), max_q_len=0, seg_len=None, host_seqs=None):
         """h = exp(dt A) h + dt x (x) B;  y = h C + D x per head; dt = clamp(softplus(dt + dt_bias))."""
         y = torch.empty_like(x)
         rep = H // G
@@ -198,11 +252,26 @@ class RecurrentNative:
         return y
 
     def mamba2_scan(self, x, dt, Bm, Cm, A, D, dt_bias, state, q_starts, seq_state, positions, H, P, G, N,
-                    dt_min=0.0, dt_max=float("inf"), max_q_len=0, seg_len=None):
+                    dt_min=0.0, dt_max=float("inf"), max_q_len=0, seg_len=None, host_seqs=None):
         """``max_q_len`` (host-side bound on the tokens of a sequence in this step) lets long prompts of few sequences run
-        sequence-parallel: segments of ``seg_len`` tokens side by side, a short combine pass, then the outputs."""
+        sequence-parallel: segments of ``seg_len`` tokens side by side, a short combine pass, then the outputs.
+        ``host_seqs`` (the step's sequences as (first row, rows, state row, fresh) known on the host) sends prompt chunks
+        of ``SSD_MIN_TOKENS`` tokens or more through the matrix form (``ssd_chunked``: batched matrix products on tensor
+        cores); the scan kernel then leaves those sequences alone."""
         y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
         B = seq_state.numel()
+        skip = 0
+        if host_seqs:
+            long = [q for q in host_seqs if SSD_MIN_TOKENS and q[1] >= SSD_MIN_TOKENS]
+            for t0, n, slot, fresh in long:
+                yv, hf = ssd_chunked(x[t0:t0 + n], dt[t0:t0 + n], Bm[t0:t0 + n], Cm[t0:t0 + n], A, D, dt_bias,
+                                     None if fresh else state[slot], H, P, G, N, dt_min, min(dt_max, 3.0e38))
+                y[t0:t0 + n] = yv
+                state[slot] = hf
+            if long:
+                if len(long) == len(host_seqs):
+                    return y
+                skip, max_q_len = SSD_MIN_TOKENS, SSD_MIN_TOKENS - 1
         if seg_len is None:
             ctas = B * H * max(1, P * max(N // 16, 1) // 128)
             seg_len = 128 if (max_q_len >= 512 and ctas < 4 * 148) else 0
@@ -214,7 +283,7 @@ class RecurrentNative:
             if scratch is None or scratch.numel() < need:
                 scratch = self._scan_scratch = torch.empty(need, dtype=torch.float32, device=x.device)
         self.k.mamba2_scan(x, dt, Bm, Cm, A, D, dt_bias, state, q_starts, seq_state, positions, y, H, P, G, N,
-                           float(dt_min), float(min(dt_max, 3.0e38)), int(seg_len if segs > 1 else 0), int(segs), scratch)
+                           float(dt_min), float(min(dt_max, 3.0e38)), int(seg_len if segs > 1 else 0), int(segs), scratch, int(skip))
         self.launches += 3 if segs > 1 else 1
         return y
 

@@ -378,7 +378,12 @@ class LLMEngine:
         else:
             dev[:used] = host_t[:used]
         self.stats.h2d_bytes += used * 4
+        host_seqs = None
+        if sst is not None and max_q >= 512 and not pad_to:
+            # long prompt chunks of recurrent layers may take a matrix form that is set up from the host
+            host_seqs = [(int(qst[i]), s.count, int(sst[i]), s.start == 0) for i, s in enumerate(seqs)]
         return StepBatch(
+            host_seqs=host_seqs,
             token_ids=dev[0:Tp], positions=dev[Tp:2 * Tp], slots=dev[2 * Tp:3 * Tp],
             row_seq=dev[3 * Tp:4 * Tp], logit_rows=dev[4 * Tp:4 * Tp + R],
             block_tables=dev[o_tab:o_tab + Bp * max_blocks].view(Bp, max_blocks),

@@ -387,3 +387,23 @@ def test_qwen3_next_matches_transformers(tmp_path):
         want = m(torch.tensor([toks])).logits[0].float()
     err = (got - want).abs().max(dim=1).values / float(want.abs().max())
     assert float(err.median()) < 2e-2 and int((err > 5e-2).sum()) <= 2, err
+
+
+@pytest.mark.parametrize("n,H,P,G,N,Q,fresh", [(300, 4, 16, 2, 16, 64, True), (129, 6, 8, 1, 32, 128, False), (64, 2, 8, 2, 16, 64, False)])
+def test_mamba2_matrix_form_equals_the_walk(n, H, P, G, N, Q, fresh):
+    """The chunked matrix form of the Mamba-2 recurrence (prefill path on a GPU) against the token walk: outputs and the
+    final state, from zeros or from a carried state, with a ragged last chunk."""
+    from fllm_b200.ops.recurrent import ssd_chunked
+    from fllm_b200.ops.reference import RefOps
+    torch.manual_seed(n)
+    x, dt = torch.randn(n, H * P), torch.randn(n, H)
+    Bm, Cm = torch.randn(n, G * N), torch.randn(n, G * N)
+    A, D, dtb = -torch.exp(torch.randn(H) * 0.5), torch.randn(H), torch.randn(H) * 0.5 - 1
+    st = torch.randn(2, H, P, N) * 0.5
+    st_ref = st.clone()
+    qs, ss = torch.tensor([0, n], dtype=torch.int32), torch.tensor([1], dtype=torch.int32)
+    pos = torch.arange(0 if fresh else 5, (0 if fresh else 5) + n, dtype=torch.int32)
+    y_ref = RefOps().mamba2_scan(x, dt, Bm, Cm, A, D, dtb, st_ref, qs, ss, pos, H, P, G, N, 0.001, 100.0)
+    y, hf = ssd_chunked(x, dt, Bm, Cm, A, D, dtb, None if fresh else st[1], H, P, G, N, 0.001, 100.0, Q)
+    assert float((y - y_ref).abs().max()) < 1e-4 * float(y_ref.abs().max())
+    assert float((hf - st_ref[1]).abs().max()) < 1e-4 * float(st_ref[1].abs().max())

@@ -24,8 +24,8 @@ CASES = [
 ]
 
 
-def _engine(cfg, ops=None, chunk=64, graphs=False, weights=None):
-    ec = EngineConfig(max_num_seqs=8, max_num_batched_tokens=chunk, max_model_len=512, num_kv_blocks=128, block_size=16,
+def _engine(cfg, ops=None, chunk=64, graphs=False, weights=None, max_len=512):
+    ec = EngineConfig(max_num_seqs=8, max_num_batched_tokens=chunk, max_model_len=max_len, num_kv_blocks=max_len // 2, block_size=16,
                       use_cuda_graphs=graphs)
     return LLMEngine(cfg, ec, device="cuda:0", seed=3, ops=ops, weights=weights)
 
@@ -103,6 +103,25 @@ def test_rwkv7_engine():
     sp = SamplingParams(max_tokens=10, temperature=0.0)
     want = _engine(cfg, chunk=512, weights=nat.weights).generate(prompts, sp)
     assert _engine(cfg, chunk=512, graphs=True, weights=nat.weights).generate(prompts, sp) == want
+
+
+def test_long_prompt_chunks_take_the_matrix_form(monkeypatch):
+    """With the switch on, prompt chunks of 512 tokens or more run the Mamba-2 layers in their matrix form; a decode row
+    of another sequence in the same step stays on the scan kernel. Logits against the PyTorch operators, tokens against
+    a run whose chunks are too short for the matrix form."""
+    import fllm_b200.ops.recurrent as rec
+    from fllm_b200.ops.reference import RefOps
+    monkeypatch.setattr(rec, "SSD_MIN_TOKENS", 512)
+    cfg = preset("bamba-tiny")
+    nat = _engine(cfg, chunk=1024, max_len=1024)
+    ref = _engine(cfg, ops=RefOps(), chunk=1024, weights=nat.weights, max_len=1024)
+    toks = torch.randint(0, 4096, (400,), generator=torch.Generator().manual_seed(5)).tolist() * 2       # 800 tokens
+    a, b = nat.token_logits(toks[:500] + toks[:200]), ref.token_logits(toks[:500] + toks[:200])
+    assert float((a - b).norm() / b.norm()) < 2e-2
+    sp = SamplingParams(max_tokens=8, temperature=0.0)
+    prompts = [toks[:300], toks, toks[100:140]]
+    want = _engine(cfg, chunk=256, weights=nat.weights, max_len=1024).generate(prompts, sp)
+    assert _engine(cfg, chunk=1024, weights=nat.weights, max_len=1024).generate(prompts, sp) == want
 
 
 def test_hybrid_presets_decode():
