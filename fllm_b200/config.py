@@ -281,7 +281,7 @@ def mla_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     return cfg
 
 
-RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "jamba")
+RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "jamba", "granitemoehybrid")
 
 
 def _limit(v, default: float) -> float:
@@ -365,6 +365,27 @@ def recurrent_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
                    ssm=dict(num_k_heads=hf.get("linear_num_key_heads", 16), num_v_heads=hf.get("linear_num_value_heads", 32),
                             head_k_dim=hf.get("linear_key_head_dim", 128), head_v_dim=hf.get("linear_value_head_dim", 128),
                             d_conv=hf.get("linear_conv_kernel_dim", 4), norm_eps=hf.get("rms_norm_eps", 1e-6)))
+    if mt == "granitemoehybrid":
+        H = hf.get("mamba_n_heads", 128)
+        P = hf.get("mamba_d_head", "auto")
+        P = hf.get("mamba_expand", 2) * hidden // H if P == "auto" else int(P)
+        kinds = hf.get("layer_types") or ["mamba"] * L
+        E = hf.get("num_local_experts") or 0
+        lim = hf.get("time_step_limit") or (0.0, float("inf"))
+        # the residual and logit multipliers are folded into the weights by the loader (residual_mult, logits_div)
+        return cls(**base, intermediate_size=hf.get("shared_intermediate_size", 1024), rms_eps=hf.get("rms_norm_eps", 1e-6),
+                   tie_embeddings=hf.get("tie_word_embeddings", False), attn_bias=hf.get("attention_bias", False),
+                   embed_scale=float(hf.get("embedding_multiplier") or 1.0), attn_scale=float(hf.get("attention_multiplier") or head_dim ** -0.5),
+                   use_rope=(hf.get("position_embedding_type") or "rope") == "rope",
+                   layer_kinds=["attention" if k == "attention" else "mamba2" for k in kinds],
+                   ffn_kinds=["moe" if E else "glu"] * L, num_experts=E, experts_per_token=hf.get("num_experts_per_tok", 2) if E else 0,
+                   moe_intermediate_size=hf["intermediate_size"] if E else 0, router_kind="softmax_topk",
+                   shared_intermediate_size=hf.get("shared_intermediate_size", 1024) if E else 0,
+                   ssm=dict(d_inner=H * P, d_state=hf.get("mamba_d_state", 256), d_conv=hf.get("mamba_d_conv", 4),
+                            n_groups=hf.get("mamba_n_groups", 1), head_dim=P, n_heads=H, norm_groups=1,
+                            conv_bias=hf.get("mamba_conv_bias", True), proj_bias=hf.get("mamba_proj_bias", False),
+                            dt_min=_limit(lim[0], 0.0), dt_max=_limit(lim[1], 1e30),
+                            residual_mult=float(hf.get("residual_multiplier") or 1.0), logits_div=float(hf.get("logits_scaling") or 1.0)))
     if mt == "jamba":
         ap, ao = hf.get("attn_layer_period", 8), hf.get("attn_layer_offset", 4)
         ep, eo = hf.get("expert_layer_period", 2), hf.get("expert_layer_offset", 1)

@@ -81,6 +81,32 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
                     if t is not None:
                         lw.mixer[name] = t.float().to(device).contiguous() if name == "conv_b" else dev(t)
             glu(lw, p + "feed_forward.", "w1", "w3", "w2")
+        elif mt == "granitemoehybrid":
+            rm = s.get("residual_mult", 1.0)                  # block output * rm: folded into each block's last projection
+            p = f"model.layers.{l}."
+            lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
+                              ffn_norm=dev(get(p + "post_attention_layernorm.weight")))
+            if kind == "attention":
+                attention(lw, p + "self_attn.")
+                lw.wo = dev(get(p + "self_attn.o_proj.weight").float() * rm)
+                if lw.bo is not None:
+                    lw.bo = dev(lw.bo.float() * rm)
+            else:
+                m = p + "mamba."
+                ob = get(m + "out_proj.bias", False)
+                lw.mixer = pack_mamba2(get(m + "in_proj.weight"), get(m + "conv1d.weight"), get(m + "conv1d.bias", False),
+                                       get(m + "dt_bias"), get(m + "A_log"), get(m + "D"), get(m + "norm.weight"),
+                                       get(m + "out_proj.weight").float() * rm, dtype, device, get(m + "in_proj.bias", False),
+                                       ob.float() * rm if ob is not None else None)
+            shared_in, shared_out = get(p + "shared_mlp.input_linear.weight"), get(p + "shared_mlp.output_linear.weight").float() * rm
+            if cfg.ffn_kind(l) == "moe":
+                mp = p + "block_sparse_moe."
+                lw.router_w = dev(get(mp + "router.layer.weight"))
+                lw.exp_gate_up = dev(get(mp + "input_linear.weight"))
+                lw.exp_down = dev(get(mp + "output_linear.weight").float() * rm)
+                lw.shared_gate_up, lw.shared_down = dev(shared_in), dev(shared_out)
+            else:
+                lw.w_gate_up, lw.w_down = dev(shared_in), dev(shared_out)
         elif mt == "jamba":
             p = f"model.layers.{l}."
             lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
@@ -188,12 +214,15 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
         embed, final = get("backbone.embeddings.weight"), get("backbone.norm_f.weight")
     elif mt in ("bamba", "jamba"):
         embed, final = get("model.embed_tokens.weight"), get("model.final_layernorm.weight")
-    elif mt in ("deepseek_v2", "deepseek_v3", "qwen3_next"):
+    elif mt in ("deepseek_v2", "deepseek_v3", "qwen3_next", "granitemoehybrid"):
         embed, final = get("model.embed_tokens.weight"), get("model.norm.weight")
     else:
         embed, final = get("model.embed_tokens.weight"), get("model.embedding_norm.weight")
     head = get("lm_head.weight", False)
     embed_d = dev(embed)
     head_d = embed_d if (head is None or cfg.tie_embeddings) else dev(head)
+    div = s.get("logits_div", 1.0) if s else 1.0
+    if div != 1.0:                                           # logits / div: a head of its own, scaled once
+        head_d = dev((embed if (head is None or cfg.tie_embeddings) else head).float() / div)
     return DecoderWeights(embed=embed_d, layers=layers, final_norm=dev(final), lm_head=head_d, vocab_start=0,
                           vocab_local=cfg.vocab_size)

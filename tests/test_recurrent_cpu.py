@@ -39,6 +39,15 @@ def _tiny(kind):
                                             expert_layer_period=2, expert_layer_offset=1, attn_layer_period=2, attn_layer_offset=1,
                                             mamba_d_state=16, mamba_d_conv=4, mamba_expand=2, mamba_dt_rank=8, use_mamba_kernels=False,
                                             max_position_embeddings=256))
+    if kind in ("granite_dense", "granite_moe"):
+        from transformers import GraniteMoeHybridConfig, GraniteMoeHybridForCausalLM
+        return GraniteMoeHybridForCausalLM(GraniteMoeHybridConfig(
+            vocab_size=300, hidden_size=64, intermediate_size=48, shared_intermediate_size=96, num_hidden_layers=3,
+            num_attention_heads=4, num_key_value_heads=2, num_local_experts=0 if kind == "granite_dense" else 4, num_experts_per_tok=2,
+            layer_types=["mamba", "attention", "mamba"], mamba_n_heads=4, mamba_d_head=32, mamba_n_groups=1, mamba_d_state=16,
+            mamba_d_conv=4, mamba_expand=2, mamba_chunk_size=8, embedding_multiplier=3.0, logits_scaling=2.0, residual_multiplier=0.5,
+            attention_multiplier=0.2, position_embedding_type="nope" if kind == "granite_dense" else "rope",
+            max_position_embeddings=256))
     if kind == "falcon_mamba":
         from transformers import FalconMambaConfig, FalconMambaForCausalLM
         return FalconMambaForCausalLM(FalconMambaConfig(vocab_size=300, hidden_size=64, state_size=16, num_hidden_layers=2, expand=2,
@@ -46,7 +55,7 @@ def _tiny(kind):
     raise ValueError(kind)
 
 
-@pytest.mark.parametrize("kind", ["mamba", "mamba2", "bamba", "lfm2", "jamba", "falcon_mamba"])
+@pytest.mark.parametrize("kind", ["mamba", "mamba2", "bamba", "lfm2", "jamba", "falcon_mamba", "granite_dense", "granite_moe"])
 def test_recurrent_families_match_transformers(tmp_path, kind):
     from fllm_b200.formats.loader import load_hf_checkpoint
     m = _tiny(kind).eval().float()
@@ -54,7 +63,7 @@ def test_recurrent_families_match_transformers(tmp_path, kind):
         for n, p in m.named_parameters():
             if n.endswith(("norm.weight", "layernorm.weight", "norm_f.weight", ".D", "dt_bias")):
                 p.add_(0.3 * torch.randn_like(p))
-            if n.endswith("router.weight"):
+            if n.endswith(("router.weight", "router.layer.weight")):
                 p.mul_(20.0)                                  # clear routing decisions
     d = str(tmp_path / kind)
     m.save_pretrained(d, safe_serialization=True)
