@@ -281,7 +281,7 @@ def mla_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     return cfg
 
 
-RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "jamba", "granitemoehybrid")
+RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "jamba", "granitemoehybrid", "rwkv6")
 
 
 def _limit(v, default: float) -> float:
@@ -322,6 +322,14 @@ def recurrent_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
                             n_groups=hf.get("n_groups", 8), head_dim=P, n_heads=H, norm_groups=1,
                             conv_bias=hf.get("use_conv_bias", True), proj_bias=hf.get("use_bias", False),
                             dt_min=_limit(lim[0], 0.0), dt_max=_limit(lim[1], 1e30)))
+    if mt == "rwkv6":
+        N = hf.get("head_size", 64)
+        inter = hf.get("intermediate_size") or int(hidden * 3.5) // 32 * 32
+        return cls(arch=mt, name=hf.get("_name_or_path") or mt, vocab_size=hf["vocab_size"], hidden_size=hidden, num_layers=L,
+                   num_heads=hidden // N, num_kv_heads=hidden // N, head_dim=N, intermediate_size=inter,
+                   rms_eps=hf.get("layer_norm_epsilon", 1e-5), tie_embeddings=False, layer_kinds=["rwkv6"] * L, ffn_kinds=["none"] * L,
+                   ssm=dict(head_dim=N, d_conv=2, head_size_divisor=hf.get("head_size_divisor", 8),
+                            mix_rank=hf.get("time_mix_extra_dim", 32), decay_rank=hf.get("time_decay_extra_dim", 64)))
     if mt == "rwkv7":
         N = hf.get("head_dim", 64)
         inter = hf.get("intermediate_size") or int(hf.get("hidden_ratio", 4.0) * hidden)
@@ -527,6 +535,10 @@ def preset(name: str) -> ModelConfig:
                            num_heads=H, num_kv_heads=1, head_dim=192, rotary_dim=64, rope_style="pair",
                            intermediate_size=512 if tiny else 10944, rms_eps=1e-6, layer_kinds=["mla"] * L,
                            mla=dict(q_lora_rank=0, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128))
+    if n == "rwkv6-tiny":
+        return ModelConfig(arch="rwkv6", name=n, vocab_size=4096, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=4,
+                           head_dim=64, intermediate_size=896, layer_kinds=["rwkv6"] * 2, ffn_kinds=["none"] * 2,
+                           ssm=dict(head_dim=64, d_conv=2, head_size_divisor=8, mix_rank=32, decay_rank=64))
     if n in ("rwkv7-1.5b", "rwkv7-tiny"):
         tiny = n.endswith("tiny")
         hidden, L = (256, 2) if tiny else (2048, 24)

@@ -56,6 +56,9 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
         if cfg.arch == "rwkv7":
             from ..models.rwkv import weights_from_state_dict
             return cfg, weights_from_state_dict(cfg, {k: get(k) for k in ck}, device, dtype), tok
+        if cfg.arch == "rwkv6":
+            from ..models.rwkv import rwkv6_weights_from_state_dict
+            return cfg, rwkv6_weights_from_state_dict(cfg, {k: get(k) for k in ck}, device, dtype), tok
         return cfg, load_hf_recurrent(cfg, get, device, dtype), tok
 
     def has(name):

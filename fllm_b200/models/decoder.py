@@ -185,6 +185,9 @@ class Decoder:
         if cfg.arch == "rwkv7":
             from .rwkv import rwkv7_forward_hidden
             return rwkv7_forward_hidden(self, b)
+        if cfg.arch == "rwkv6":
+            from .rwkv import rwkv6_forward_hidden
+            return rwkv6_forward_hidden(self, b)
         if self.first_stage:
             x = ops.embed(b.token_ids, self.w.embed, cfg.embed_scale)
             delta = None
@@ -298,7 +301,7 @@ class Decoder:
     def logits(self, x: torch.Tensor, delta: Optional[torch.Tensor], b: StepBatch) -> torch.Tensor:
         """Final norm + LM head on the requested rows -> [R, vocab_local]."""
         cfg, ops = self.cfg, self.ops
-        if cfg.arch == "rwkv7":
+        if cfg.arch in ("rwkv7", "rwkv6"):
             from .rwkv import rwkv7_final_norm
             h = rwkv7_final_norm(self, x)
         else:

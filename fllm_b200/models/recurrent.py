@@ -32,7 +32,7 @@ def conv_channels(cfg: ModelConfig, kind: str) -> int:
         return s["d_inner"] + 2 * s["n_groups"] * s["d_state"]
     if kind == "gated_delta":
         return 2 * s["num_k_heads"] * s["head_k_dim"] + s["num_v_heads"] * s["head_v_dim"]
-    if kind in ("shortconv", "rwkv7"):
+    if kind in ("shortconv", "rwkv7", "rwkv6"):
         return cfg.hidden_size
     raise ValueError(kind)
 
@@ -45,7 +45,7 @@ def scan_state_shape(cfg: ModelConfig, kind: str):
         return (s["n_heads"], s["head_dim"], s["d_state"])
     if kind == "gated_delta":
         return (s["num_v_heads"], s["head_v_dim"], s["head_k_dim"])
-    if kind == "rwkv7":
+    if kind in ("rwkv7", "rwkv6"):
         return (cfg.hidden_size // s["head_dim"], s["head_dim"], s["head_dim"])
     return None
 
@@ -64,7 +64,7 @@ class RecurrentState:
             kind = cfg.layer_kind(li)
             if kind in ("attention", "mla"):
                 continue
-            if kind == "rwkv7":
+            if kind in ("rwkv7", "rwkv6"):
                 self.shift2[li] = torch.zeros(slots, W - 1, cfg.hidden_size, dtype=act_dtype, device=device)
             self.conv[li] = torch.zeros(slots, W - 1, conv_channels(cfg, kind), dtype=act_dtype, device=device)
             shape = scan_state_shape(cfg, kind)
@@ -79,7 +79,7 @@ class RecurrentState:
             kind = cfg.layer_kind(li)
             if kind in ("attention", "mla"):
                 continue
-            n += (W - 1) * conv_channels(cfg, kind) * (4 if kind == "rwkv7" else 2)
+            n += (W - 1) * conv_channels(cfg, kind) * (4 if kind in ("rwkv7", "rwkv6") else 2)
             shape = scan_state_shape(cfg, kind)
             if shape is not None:
                 k = 4

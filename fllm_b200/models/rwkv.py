@@ -1,11 +1,13 @@
-"""RWKV-7 ("Goose") as a family of the decoder runner: LayerNorm blocks, token shift, low-rank decay / value-mix /
+"""RWKV-6 ("Finch") and RWKV-7 ("Goose") as families of the decoder runner. RWKV-7: LayerNorm blocks, token shift, low-rank decay / value-mix /
 in-context-learning-rate / gate branches, the generalised delta-rule state per head, a per-head GroupNorm with the
 r.k bonus, and the squared-ReLU channel mix.
 
 The reference runs the family in rust/engine/src/rust_decoder/rwkv.rs with the state update in rust/engine/cuda/rwkv.cu
 and keeps a PyTorch transcription of the official recurrence in scripts/rwkv_reference.py. Tensor names are those of the
 Hugging Face ``RWKV7ForCausalLM`` layout (``model.layers.N.attn.*``, ``attn_norm``, ``ffn_norm``, ``ffn.*``, ``pre_norm`` in
-layer 0).
+layer 0). RWKV-6 (``Rwkv6ForCausalLM`` layout: ``rwkv.blocks.N.attention.*``, ``ln1``, ``ln2``, ``feed_forward.*``, ``pre_ln`` in
+block 0) has data-dependent mixing coefficients and decays from low-rank branches, a bonus vector for the current token,
+a SiLU gate and a receptance-gated channel mix.
 
 Token shift is a two-tap causal convolution with taps (+1, -1): its output is ``previous - current`` and its window
 is the previous row, kept per sequence in the state pool, so chunked prefill and decode need no special case.
@@ -18,7 +20,7 @@ import torch
 import torch.nn.functional as F
 
 from ..config import ModelConfig
-from ..ops.recurrent import RWKV7
+from ..ops.recurrent import RWKV6, RWKV7
 
 DECAY_SCALE = -0.6065306597126334            # -exp(-0.5): decay = exp(DECAY_SCALE * sigmoid(.)) lies in (0.545, 1)
 
@@ -175,4 +177,119 @@ def weights_from_state_dict(cfg: ModelConfig, sd: Dict[str, torch.Tensor], devic
     w = DecoderWeights(embed=bf(get("model.embeddings.weight")), layers=layers, final_norm=get("model.norm.weight").float().to(device),
                        lm_head=bf(get("lm_head.weight")), vocab_start=0, vocab_local=cfg.vocab_size)
     w.final_norm_b = get("model.norm.bias").float().to(device)
+    return w
+
+
+# ================================================================================================ RWKV-6
+def rwkv6_forward_hidden(dec, b):
+    cfg, ops, st = dec.cfg, dec.ops, dec.rstate
+    eps, N = cfg.rms_eps, cfg.ssm["head_dim"]
+    C = cfg.hidden_size
+    H = C // N
+    qs, ss, pos = b.q_starts, b.seq_state, b.positions
+    x = ops.embed(b.token_ids, dec.w.embed, 1.0)
+    T = x.shape[0]
+    taps = getattr(dec, "_shift_taps", None)
+    if taps is None:
+        taps = dec._shift_taps = _shift_taps(C, x.device)
+    lin = ops.linear
+    gn_eps = 1e-5 * cfg.ssm.get("head_size_divisor", 8) ** 2
+    for li, lw in zip(dec.layer_range, dec.w.layers):
+        m = lw.mixer
+        if "pre_norm_w" in m:
+            x = _ln(x, m["pre_norm_w"], m["pre_norm_b"], eps)
+        h = _ln(x, lw.attn_norm, m["attn_norm_b"], eps)
+        xx = ops.causal_conv1d(h, taps, None, st.conv[li], qs, ss, pos, act=False)
+        lo = torch.tanh(lin(h + xx * m["maa_x"], m["maa_w1"]).float()).to(h.dtype)              # [T, 5 d]
+        d = lo.shape[1] // 5
+        xw, xk, xv, xr, xg = (h + xx * (m["maa_" + c] + lin(lo[:, j * d:(j + 1) * d].contiguous(), m["maa_w2_" + c]))
+                              for j, c in enumerate("wkvrg"))
+        r, k, v = lin(xr, m["r_proj"]), lin(xk, m["k_proj"]), lin(xv, m["v_proj"])
+        gate = torch.nn.functional.silu(lin(xg, m["g_proj"]).float())
+        wraw = m["decay"] + lin(torch.tanh(lin(xw, m["decay_w1"]).float()).to(h.dtype), m["decay_w2"]).float()
+        w = (-torch.exp(wraw)).contiguous()                                                         # fp32 log decay
+        y = ops.matrix_state_scan(RWKV6, r, k, v, None, None, w, m["bonus"], None, st.scan[li], qs, ss, pos, H, N, N, 1, False, 1.0)
+        yf = F.group_norm(y.float(), H, m["g_norm_w"], m["g_norm_b"], gn_eps)
+        x = x + lin((yf * gate).to(h.dtype), m["o_proj"])
+        h2 = _ln(x, lw.ffn_norm, m["ffn_norm_b"], eps)
+        xx2 = ops.causal_conv1d(h2, taps, None, st.shift2[li], qs, ss, pos, act=False)
+        kk = torch.relu(lin(h2 + xx2 * m["ffn_maa_k"], m["ffn_key"]).float()).square().to(h.dtype)
+        rr = torch.sigmoid(lin(h2 + xx2 * m["ffn_maa_r"], m["ffn_recept"]).float())
+        x = x + (rr * lin(kk, m["ffn_value"]).float()).to(h.dtype)
+    return x, None
+
+
+def pack_rwkv6_layer(get, p: str, dtype, device) -> Dict[str, torch.Tensor]:
+    bf = lambda t: t.to(device=device, dtype=dtype).contiguous()
+    vec = lambda t: t.reshape(-1).to(device=device, dtype=dtype).contiguous()
+    f32 = lambda t: t.float().to(device).contiguous()
+    m = {"attn_norm_b": f32(get(p + "ln1.bias")), "ffn_norm_b": f32(get(p + "ln2.bias"))}
+    if get(p + "pre_ln.weight", False) is not None:
+        m["pre_norm_w"], m["pre_norm_b"] = f32(get(p + "pre_ln.weight")), f32(get(p + "pre_ln.bias"))
+    a = p + "attention."
+    m["maa_x"] = vec(get(a + "time_maa_x"))
+    for c in "wkvrg":
+        m["maa_" + c] = vec(get(a + "time_maa_" + c))
+    m["maa_w1"] = bf(get(a + "time_maa_w1").t())                       # stored as x @ W: [C, 5 d] -> [5 d, C]
+    w2 = get(a + "time_maa_w2")                                        # [5, d, C]
+    for j, c in enumerate("wkvrg"):
+        m["maa_w2_" + c] = bf(w2[j].t())
+    m["decay"] = f32(get(a + "time_decay").reshape(-1))
+    m["decay_w1"], m["decay_w2"] = bf(get(a + "time_decay_w1").t()), bf(get(a + "time_decay_w2").t())
+    m["bonus"] = f32(get(a + "time_faaaa").reshape(-1))
+    for name, key in (("r_proj", "receptance"), ("k_proj", "key"), ("v_proj", "value"), ("g_proj", "gate"), ("o_proj", "output")):
+        m[name] = bf(get(a + key + ".weight"))
+    m["g_norm_w"], m["g_norm_b"] = f32(get(a + "ln_x.weight")), f32(get(a + "ln_x.bias"))
+    f = p + "feed_forward."
+    m["ffn_maa_k"], m["ffn_maa_r"] = vec(get(f + "time_maa_k")), vec(get(f + "time_maa_r"))
+    m["ffn_key"], m["ffn_recept"], m["ffn_value"] = bf(get(f + "key.weight")), bf(get(f + "receptance.weight")), bf(get(f + "value.weight"))
+    return m
+
+
+def random_rwkv6_state_dict(cfg: ModelConfig, seed: int = 0) -> Dict[str, torch.Tensor]:
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *s, std=0.15: torch.randn(*s, generator=g) * std
+    ru = lambda *s, lo=0.0, hi=1.0: lo + (hi - lo) * torch.rand(*s, generator=g)
+    C, V, L, N, I = cfg.hidden_size, cfg.vocab_size, cfg.num_layers, cfg.ssm["head_dim"], cfg.intermediate_size
+    H, d, dd = C // N, cfg.ssm["mix_rank"], cfg.ssm["decay_rank"]
+    sd = {"rwkv.embeddings.weight": rn(V, C, std=0.5), "head.weight": rn(V, C, std=C ** -0.5),
+          "rwkv.ln_out.weight": ru(C, lo=0.8, hi=1.2), "rwkv.ln_out.bias": rn(C, std=0.1)}
+    for l in range(L):
+        p = f"rwkv.blocks.{l}."
+        for n in (["pre_ln"] if l == 0 else []) + ["ln1", "ln2"]:
+            sd[p + n + ".weight"], sd[p + n + ".bias"] = ru(C, lo=0.8, hi=1.2), rn(C, std=0.1)
+        a = p + "attention."
+        for c in "xwkvrg":
+            sd[a + "time_maa_" + c] = ru(1, 1, C)
+        sd[a + "time_maa_w1"], sd[a + "time_maa_w2"] = rn(C, 5 * d, std=C ** -0.5), rn(5, d, C, std=d ** -0.5)
+        sd[a + "time_decay"] = rn(1, 1, C, std=1.0) - 1.0
+        sd[a + "time_decay_w1"], sd[a + "time_decay_w2"] = rn(C, dd, std=C ** -0.5), rn(dd, C, std=dd ** -0.5)
+        sd[a + "time_faaaa"] = rn(H, N, std=0.3)
+        for n in ("receptance", "key", "value", "gate", "output"):
+            sd[a + n + ".weight"] = rn(C, C, std=C ** -0.5)
+        sd[a + "ln_x.weight"], sd[a + "ln_x.bias"] = ru(C, lo=0.8, hi=1.2), rn(C, std=0.1)
+        f = p + "feed_forward."
+        sd[f + "time_maa_k"], sd[f + "time_maa_r"] = ru(1, 1, C), ru(1, 1, C)
+        sd[f + "key.weight"], sd[f + "receptance.weight"], sd[f + "value.weight"] = rn(I, C, std=C ** -0.5), rn(C, C, std=C ** -0.5), rn(C, I, std=I ** -0.5)
+    return sd
+
+
+def rwkv6_weights_from_state_dict(cfg: ModelConfig, sd: Dict[str, torch.Tensor], device, dtype):
+    from .weights import DecoderWeights, LayerWeights
+
+    def get(name, required=True):
+        if name not in sd:
+            if required:
+                raise KeyError(f"checkpoint has no tensor {name!r}")
+            return None
+        return sd[name]
+    bf = lambda t: t.to(device=device, dtype=dtype).contiguous()
+    layers = []
+    for l in range(cfg.num_layers):
+        p = f"rwkv.blocks.{l}."
+        layers.append(LayerWeights(attn_norm=get(p + "ln1.weight").float().to(device), wqkv=None, wo=None,
+                                   ffn_norm=get(p + "ln2.weight").float().to(device), mixer=pack_rwkv6_layer(get, p, dtype, device)))
+    w = DecoderWeights(embed=bf(get("rwkv.embeddings.weight")), layers=layers, final_norm=get("rwkv.ln_out.weight").float().to(device),
+                       lm_head=bf(get("head.weight")), vocab_start=0, vocab_local=cfg.vocab_size)
+    w.final_norm_b = get("rwkv.ln_out.bias").float().to(device)
     return w

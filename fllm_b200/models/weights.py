@@ -233,6 +233,11 @@ def init_random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, se
         if tp > 1 or (layers is not None and len(layers) != cfg.num_layers):
             raise NotImplementedError("RWKV models run on one rank and one pipeline stage")
         return weights_from_state_dict(cfg, random_rwkv7_state_dict(cfg, seed), device, dtype)
+    if cfg.arch == "rwkv6":
+        from .rwkv import random_rwkv6_state_dict, rwkv6_weights_from_state_dict
+        if tp > 1 or (layers is not None and len(layers) != cfg.num_layers):
+            raise NotImplementedError("RWKV models run on one rank and one pipeline stage")
+        return rwkv6_weights_from_state_dict(cfg, random_rwkv6_state_dict(cfg, seed), device, dtype)
     sp = make_shard_spec(cfg, tp, tp_rank, expert_parallel)
     D, H = cfg.head_dim, cfg.hidden_size
     layers = range(cfg.num_layers) if layers is None else layers

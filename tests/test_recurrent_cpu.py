@@ -416,3 +416,68 @@ def test_mamba2_matrix_form_equals_the_walk(n, H, P, G, N, Q, fresh):
     y, hf = ssd_chunked(x, dt, Bm, Cm, A, D, dtb, None if fresh else st[1], H, P, G, N, 0.001, 100.0, Q)
     assert float((y - y_ref).abs().max()) < 1e-4 * float(y_ref.abs().max())
     assert float((hf - st_ref[1]).abs().max()) < 1e-4 * float(st_ref[1].abs().max())
+
+
+def _rwkv6_oracle(sd, cfg, ids):
+    """RWKV-6 one token at a time in fp32 with the states in a dictionary (the published recurrence, state [head, key,
+    value]), written without any of the engine's pieces."""
+    import torch.nn.functional as F
+    C, N, eps = cfg.hidden_size, cfg.ssm["head_dim"], cfg.rms_eps
+    H = C // N
+    ln = lambda x, n: F.layer_norm(x, (C,), sd[n + ".weight"], sd[n + ".bias"], eps)
+    st, out = {}, []
+    for tok in ids:
+        x = sd["rwkv.embeddings.weight"][tok]
+        for l in range(cfg.num_layers):
+            p = f"rwkv.blocks.{l}."
+            a = lambda n: sd[p + "attention." + n]
+            if l == 0:
+                x = ln(x, p + "pre_ln")
+            h = ln(x, p + "ln1")
+            xx = st.get(("a", l), torch.zeros(C)) - h
+            st[("a", l)] = h
+            xxx = h + xx * a("time_maa_x").reshape(-1)
+            d = a("time_maa_w2").shape[1]
+            lo = torch.tanh(xxx @ a("time_maa_w1")).reshape(5, 1, d)
+            mix = torch.bmm(lo, a("time_maa_w2")).reshape(5, -1)
+            xw, xk, xv, xr, xg = (h + xx * (a("time_maa_" + c).reshape(-1) + mix[j]) for j, c in enumerate("wkvrg"))
+            r, k, v = a("receptance.weight") @ xr, a("key.weight") @ xk, a("value.weight") @ xv
+            gate = F.silu(a("gate.weight") @ xg)
+            w = a("time_decay").reshape(-1) + torch.tanh(xw @ a("time_decay_w1")) @ a("time_decay_w2")
+            decay = torch.exp(-torch.exp(w)).view(H, N)
+            S = st.get(("s", l), torch.zeros(H, N, N))
+            kv = k.view(H, N, 1) * v.view(H, 1, N)
+            y = torch.einsum("hk,hkv->hv", r.view(H, N), a("time_faaaa")[:, :, None] * kv + S).reshape(1, C)
+            st[("s", l)] = kv + decay[:, :, None] * S
+            y = F.group_norm(y, H, a("ln_x.weight"), a("ln_x.bias"), 1e-5 * cfg.ssm["head_size_divisor"] ** 2).reshape(-1)
+            x = x + a("output.weight") @ (y * gate)
+            h2 = ln(x, p + "ln2")
+            xx = st.get(("f", l), torch.zeros(C)) - h2
+            st[("f", l)] = h2
+            f = lambda n: sd[p + "feed_forward." + n]
+            kk = torch.relu(f("key.weight") @ (h2 + xx * f("time_maa_k").reshape(-1))) ** 2
+            x = x + torch.sigmoid(f("receptance.weight") @ (h2 + xx * f("time_maa_r").reshape(-1))) * (f("value.weight") @ kk)
+        out.append(sd["head.weight"] @ ln(x, "rwkv.ln_out"))
+    return torch.stack(out)
+
+
+def test_rwkv6_matches_token_by_token_recurrence(tmp_path):
+    import json
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    from fllm_b200.formats.safetensors_io import save_file
+    from fllm_b200.models.rwkv import random_rwkv6_state_dict
+    hf = {"model_type": "rwkv6", "architectures": ["Rwkv6ForCausalLM"], "hidden_size": 64, "num_hidden_layers": 3, "head_size": 16,
+          "head_size_divisor": 8, "intermediate_size": 224, "layer_norm_epsilon": 1e-5, "vocab_size": 300, "time_mix_extra_dim": 8,
+          "time_decay_extra_dim": 16}
+    cfg = ModelConfig.from_hf_config(hf)
+    sd = random_rwkv6_state_dict(cfg, seed=4)
+    json.dump(hf, open(tmp_path / "config.json", "w"))
+    save_file(sd, str(tmp_path / "model.safetensors"))
+    cfg2, w, _ = load_hf_checkpoint(str(tmp_path), device="cpu", dtype=torch.float32)
+    assert cfg2.arch == "rwkv6"
+    eng = LLMEngine(cfg2, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16),
+                    device="cpu", weights=w)
+    toks = torch.randint(0, 300, (40,), generator=torch.Generator().manual_seed(2)).tolist()
+    got = eng.token_logits(toks)
+    want = _rwkv6_oracle(sd, cfg, toks)
+    assert float((got - want).abs().max()) < 1e-3 * float(want.abs().max())

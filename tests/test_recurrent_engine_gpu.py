@@ -91,9 +91,10 @@ def test_deepseek_moe_engine():
     assert [len(o) for o in out] == [8, 8]
 
 
-def test_rwkv7_engine():
+@pytest.mark.parametrize("name", ["rwkv7-tiny", "rwkv6-tiny"])
+def test_rwkv_engine(name):
     from fllm_b200.ops.reference import RefOps
-    cfg = preset("rwkv7-tiny")
+    cfg = preset(name)
     nat = _engine(cfg)
     ref = _engine(cfg, ops=RefOps(), weights=nat.weights)
     toks = torch.randint(0, 4096, (150,), generator=torch.Generator().manual_seed(5)).tolist()
