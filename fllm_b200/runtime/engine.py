@@ -151,6 +151,14 @@ class LLMEngine:
         elif self.cfg.speculative == "suffix":
             from .speculative import AdaptiveDraft, SuffixProposer
             self.proposer = SuffixProposer(self.cfg.draft_tokens)
+            # disk tier: $FLLM_SUFFIX_DIR/suffix-<model digest>.bin is read now and rewritten when the engine closes
+            sdir = os.environ.get("FLLM_SUFFIX_DIR")
+            if sdir:
+                import hashlib
+                self._suffix_digest = hashlib.blake2b(repr((model_cfg.name, model_cfg.vocab_size, model_cfg.hidden_size,
+                                                            model_cfg.num_layers)).encode(), digest_size=16).digest()
+                self._suffix_path = os.path.join(sdir, f"suffix-{self._suffix_digest.hex()}.bin")
+                self.proposer.load(self._suffix_path, self._suffix_digest)
             self.adaptive = AdaptiveDraft(self.cfg.draft_tokens)
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self._graph_pool = None
@@ -1012,6 +1020,12 @@ class LLMEngine:
     def close(self) -> None:
         """Drop captured graphs (they pin the library communicator: it cannot be destroyed while a
         graph that captured one of its collectives is alive) and wait for the device."""
+        if getattr(self, "_suffix_path", None) and self.tp_rank == 0 and self.stage == 0:
+            try:
+                os.makedirs(os.path.dirname(self._suffix_path), exist_ok=True)
+                self.proposer.save(self._suffix_path, self._suffix_digest)
+            except OSError:
+                pass                      # the tier is an optimisation: a full or read-only disk must not fail a shutdown
         self._graphs.clear()
         self._graph_pool = None
         import gc

@@ -74,15 +74,72 @@ class SuffixProposer:
     A lookup tries the sequence's own context first (the n-gram rule) and then the shared index, longest n first.
     Repeated answers, boiler-plate and code completions accept long drafts across requests."""
 
-    def __init__(self, k: int = 4, max_n: int = 4, min_n: int = 2, capacity: int = 200_000):
+    MAGIC = b"FLLMSFX1"
+
+    def __init__(self, k: int = 4, max_n: int = 4, min_n: int = 2, capacity: int = 200_000, max_documents: int = 4096):
         self.k, self.max_n, self.min_n, self.capacity = k, max_n, min_n, capacity
         self.own = NgramProposer(k, max_n=max_n, min_n=1)
         self.index: "Dict[tuple, List[int]]" = {}
         self.hits = self.lookups = 0
+        self.documents: "List[List[int]]" = []          # what the index was built from: this is what a restart needs
+        self.max_documents = max_documents
+
+    # ------------------------------------------------------------------ disk tier
+    def save(self, path: str, digest: bytes) -> None:
+        """The observed documents in one file (the index is rebuilt on load): magic | digest length u32 | digest |
+        document count u64 | per document: token count u32, tokens i32. Written under a temporary name and renamed,
+        so a crash leaves the old file or none (rust/engine/src/mem/suffix_tier.rs:1-16 keeps the same kind of file,
+        one per model fingerprint, so that speculation does not start cold after a restart)."""
+        import os
+        import struct
+        tmp = path + ".tmp"
+        with open(tmp, "wb") as f:
+            f.write(self.MAGIC + struct.pack("<I", len(digest)) + digest + struct.pack("<Q", len(self.documents)))
+            for d in self.documents:
+                f.write(struct.pack("<I", len(d)) + struct.pack(f"<{len(d)}i", *d))
+        os.replace(tmp, path)
+
+    def load(self, path: str, digest: bytes) -> int:
+        """Re-index the documents of a file written for the same model digest; a missing, foreign, truncated or damaged
+        file counts as absent. Returns the number of documents taken."""
+        import os
+        import struct
+        try:
+            raw = open(path, "rb").read()
+        except OSError:
+            return 0
+        try:
+            if raw[:8] != self.MAGIC:
+                return 0
+            (dl,) = struct.unpack_from("<I", raw, 8)
+            if dl > 256 or raw[12:12 + dl] != digest:
+                return 0
+            at = 12 + dl
+            (count,) = struct.unpack_from("<Q", raw, at)
+            at += 8
+            if count > (16 << 20):
+                return 0
+            docs = []
+            for _ in range(count):
+                (n,) = struct.unpack_from("<I", raw, at)
+                at += 4
+                if at + 4 * n > len(raw):
+                    return 0
+                docs.append(list(struct.unpack_from(f"<{n}i", raw, at)))
+                at += 4 * n
+        except struct.error:
+            return 0
+        for d in docs:
+            self.observe(d)
+        return len(docs)
 
     def observe(self, tokens: Sequence[int]) -> None:
         """Index a finished sequence (prompt + output)."""
         toks = [int(t) for t in tokens]
+        if toks and max(toks) < (1 << 31):
+            self.documents.append(toks)
+            if len(self.documents) > self.max_documents:
+                del self.documents[0]
         for n in range(self.min_n, self.max_n + 1):
             for i in range(len(toks) - n):
                 if len(self.index) >= self.capacity:

@@ -176,3 +176,28 @@ def test_suffix_proposer_drafts_from_earlier_requests():
     second = eng.generate([prompt], SamplingParams(max_tokens=12))[0]
     assert first == base and second == base
     assert eng.stats.spec_accepted - acc0 >= 6 and eng.stats.steps - steps0 < steps0
+
+
+def test_suffix_index_survives_a_restart(tmp_path, monkeypatch):
+    """The suffix source keeps its documents in $FLLM_SUFFIX_DIR under the model's digest: a second engine drafts from the
+    first one's outputs; a file of another model or a damaged file counts as absent."""
+    from fllm_b200.config import EngineConfig, preset
+    from fllm_b200.runtime import LLMEngine, SamplingParams
+    from fllm_b200.runtime.speculative import SuffixProposer
+    monkeypatch.setenv("FLLM_SUFFIX_DIR", str(tmp_path))
+    cfg = preset("tiny-llama")
+    cfg.vocab_size = 512
+    ec = EngineConfig(max_num_seqs=2, max_num_batched_tokens=64, max_model_len=128, num_kv_blocks=32, speculative="suffix", draft_tokens=3)
+    a = LLMEngine(cfg, ec, device="cpu", seed=2)
+    prompt = [5, 9, 2, 7, 11, 3]
+    out = a.generate([prompt], SamplingParams(max_tokens=12, temperature=0.0))[0]
+    a.close()
+    files = list(tmp_path.glob("suffix-*.bin"))
+    assert len(files) == 1
+    b = LLMEngine(cfg, ec, device="cpu", seed=2)
+    assert b.proposer.documents == [prompt + out]
+    assert b.proposer.propose([99, 98, 5, 9]) == [2, 7, 11]            # drafts come from the other engine's text
+    other = SuffixProposer(3)
+    assert other.load(str(files[0]), b"another model") == 0
+    files[0].write_bytes(files[0].read_bytes()[:-5])
+    assert SuffixProposer(3).load(str(files[0]), b._suffix_digest) == 0
