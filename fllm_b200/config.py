@@ -74,6 +74,8 @@ class ModelConfig:
     router_topk_groups: int = 1
     router_norm_topk: bool = False
     shared_gate: bool = False            # the shared experts' output is scaled by sigmoid(h . g) (Qwen3-Next)
+    qk_norm_offset: float = 0.0          # 1.0: the per-head q / k norms multiply by 1 + w (Gemma-3)
+    rope_local_theta: float = 0.0        # > 0: windowed layers rotate with this base and no scaling (Gemma-3)
     use_rope: bool = True                # False: attention layers carry no position signal of their own (Jamba)
     attn_out_gate: bool = False          # the query projection also emits a gate: attention output * sigmoid(gate) (Qwen3-Next)
     # recurrent and hybrid families: the token mixer of each layer (None = attention everywhere) and whether the
@@ -157,7 +159,13 @@ class ModelConfig:
     def from_hf_config(cls, hf: Dict[str, Any]) -> "ModelConfig":
         """Map a Hugging Face ``config.json`` to the decoder description."""
         mt = hf.get("model_type", "llama")
+        if mt == "gemma3" and isinstance(hf.get("text_config"), dict):     # the multimodal wrapper: its language model
+            hf = dict(hf["text_config"], model_type="gemma3_text")
+            mt = "gemma3_text"
         rp = hf.get("rope_parameters") or {}
+        rp_local = None
+        if isinstance(rp.get("full_attention"), dict):                     # per layer type: global layers / windowed layers
+            rp_local, rp = rp.get("sliding_attention") or {}, rp["full_attention"]
         if rp:                                 # newer configs keep the RoPE base and scaling in one dictionary
             hf = dict(hf)
             hf.setdefault("rope_theta", rp.get("rope_theta", 10000.0))
@@ -213,14 +221,21 @@ class ModelConfig:
             # Mixtral: softmax over the selected logits. Qwen-MoE: softmax over all experts, then the selected
             # probabilities renormalised (norm_topk_prob)
             cfg.router_kind = "softmax_topk" if mt == "mixtral" else "softmax_all"
-        if mt in ("gemma", "gemma2"):
+        if mt in ("gemma", "gemma2", "gemma3_text"):
             cfg.norm_weight_offset = 1.0
             cfg.embed_scale = float(hidden) ** 0.5
             cfg.act = "geglu"
             cfg.tie_embeddings = hf.get("tie_word_embeddings", True)
             cfg.logit_softcap = float(hf.get("final_logit_softcapping") or 0.0)
             cfg.attn_softcap = float(hf.get("attn_logit_softcapping") or 0.0)
-        if mt == "gemma2":
+        if mt == "gemma3_text":               # Gemma-3: QK-norm with 1 + w weights, a RoPE base of their own for windowed layers
+            cfg.qk_norm, cfg.qk_norm_offset = True, 1.0
+            cfg.rope_local_theta = float((rp_local or {}).get("rope_theta", hf.get("rope_local_base_freq", 10000.0)))
+            if not hf.get("layer_types") and hf.get("sliding_window"):
+                pat = hf.get("sliding_window_pattern", 6)
+                hf = dict(hf, layer_types=["full_attention" if (i + 1) % pat == 0 else "sliding_attention"
+                                           for i in range(hf["num_hidden_layers"])])
+        if mt in ("gemma2", "gemma3_text"):
             cfg.post_norms = True
             if hf.get("query_pre_attn_scalar"):
                 cfg.attn_scale = float(hf["query_pre_attn_scalar"]) ** -0.5
@@ -228,6 +243,10 @@ class ModelConfig:
                 cfg.sliding_window = int(hf["sliding_window"])
                 lt = hf.get("layer_types")
                 cfg.window_pattern = [1 if t == "sliding_attention" else 0 for t in lt] if lt else [1, 0]
+        if mt == "granite":                   # llama with four multipliers; the residual and logit ones are folded into weights at load
+            cfg.embed_scale = float(hf.get("embedding_multiplier") or 1.0)
+            if hf.get("attention_multiplier"):
+                cfg.attn_scale = float(hf["attention_multiplier"])
         if mt in ("phi3", "phi"):
             cfg.rotary_dim = int(cfg.head_dim * hf.get("partial_rotary_factor", 1.0)) or None
         if hf.get("sliding_window") and hf.get("use_sliding_window", mt == "mistral"):

@@ -105,6 +105,8 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
     def put(w):
         return w.to(device) if isinstance(w, Int4Weight) else dev(w)
 
+    res_mult = float(hf.get("residual_multiplier") or 1.0) if hf.get("model_type") == "granite" else 1.0
+    logit_div = float(hf.get("logits_scaling") or 1.0) if hf.get("model_type") == "granite" else 1.0
     qs = slice(sp.q_head_start * D, (sp.q_head_start + sp.hq_local) * D)
     ks = slice(sp.kv_head_start * D, (sp.kv_head_start + sp.hkv_local) * D)
     isl = slice(sp.inter_start, sp.inter_start + sp.inter_local)
@@ -170,6 +172,13 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
                 lw.bo = dev(bo if tp_rank == 0 else torch.zeros_like(bo))
         if cfg.qk_norm:
             lw.q_norm, lw.k_norm = dev(get(p + "self_attn.q_norm.weight")), dev(get(p + "self_attn.k_norm.weight"))
+            if cfg.qk_norm_offset:             # the fused kernel multiplies by w: fold the 1 + w convention into it
+                lw.q_norm, lw.k_norm = dev(lw.q_norm.float() + cfg.qk_norm_offset), dev(lw.k_norm.float() + cfg.qk_norm_offset)
+        if res_mult != 1.0:                    # Granite: block output * multiplier, folded into the block's last projection
+            for name in ("wo", "bo", "w_down"):
+                t = getattr(lw, name, None)
+                if isinstance(t, torch.Tensor):
+                    setattr(lw, name, dev(t.float() * res_mult))
         if cfg.attn_sinks:
             sk = get(p + "self_attn.sinks", False)
             if sk is not None:
@@ -179,6 +188,8 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
     head = get("lm_head.weight", False)
     if head is None or cfg.tie_embeddings:
         head = embed
+    if logit_div != 1.0:                       # logits / divisor: a scaled head of its own
+        head = head.float() / logit_div
     v0, vl = 0, cfg.vocab_size
     if tp > 1:
         v0 = tp_rank * sp.vocab_chunk
@@ -262,15 +273,32 @@ def _load_per_expert_moe(cfg, sp, tp_rank, lw, p, get, dev) -> None:
     lw.router_w = dev(get(p + router))
     lw.router_b = None
     experts = range(sp.expert_start, sp.expert_start + sp.expert_local) if sp.expert_parallel else range(cfg.num_experts)
-    gu = torch.stack([torch.cat([get(f"{base}experts.{e}.{names[0]}.weight"), get(f"{base}experts.{e}.{names[1]}.weight")], 0)
-                      for e in experts])
-    dn = torch.stack([get(f"{base}experts.{e}.{names[2]}.weight") for e in experts])
+    fused = get(base + "experts.gate_up_proj", False)
+    if fused is not None:                      # newer checkpoints: one [E, 2I, H] and one [E, H, I] tensor per layer
+        es = slice(experts.start, experts.stop)
+        gu, dn = fused[es], get(base + "experts.down_proj")[es]
+    else:
+        gu = torch.stack([torch.cat([get(f"{base}experts.{e}.{names[0]}.weight"), get(f"{base}experts.{e}.{names[1]}.weight")], 0)
+                          for e in experts])
+        dn = torch.stack([get(f"{base}experts.{e}.{names[2]}.weight") for e in experts])
     if sp.expert_parallel:
         lw.exp_gate_up, lw.exp_down = dev(gu), dev(dn)
     else:
         lw.exp_gate_up = dev(_cut_gate_up(gu, cfg, sp, dim=1))
         lw.exp_down = dev(dn[:, :, sp.inter_start: sp.inter_start + sp.inter_local])
     lw.exp_gate_up_b = lw.exp_down_b = None
+    sg = get(base + "shared_expert.gate_proj.weight", False)
+    if sg is not None:                         # Qwen2-MoE: an always-on expert whose output is scaled by sigmoid(h . g)
+        su, sd = get(base + "shared_expert.up_proj.weight"), get(base + "shared_expert.down_proj.weight")
+        Is = sg.shape[0]
+        per = Is // sp.tp if (sp.tp > 1 and Is % (sp.tp * 8) == 0) else Is
+        if sp.tp > 1 and per == Is:
+            raise ValueError(f"the shared expert's width {Is} cannot be divided over tp={sp.tp}")
+        sl = slice(sp.tp_rank * per, (sp.tp_rank + 1) * per) if sp.tp > 1 else slice(0, Is)
+        lw.shared_gate_up, lw.shared_down = dev(torch.cat([sg[sl], su[sl]], 0)), dev(sd[:, sl])
+        g1 = get(base + "shared_expert_gate.weight", False)
+        if g1 is not None:
+            lw.shared_gate_w = dev(torch.cat([g1, torch.zeros(7, g1.shape[1], dtype=g1.dtype)], 0))
 
 
 def load_gguf(path: str, device="cuda", tp: int = 1, tp_rank: int = 0, dtype=torch.bfloat16, keep_packed: bool = True):

@@ -85,6 +85,11 @@ class Decoder:
         if not cfg.use_rope:                       # a zero frequency table turns the rotation into the identity
             inv = [0.0] * len(inv)
         self.inv_freq = torch.tensor(inv, dtype=torch.float32, device=dev)
+        self.inv_freq_local = None
+        if cfg.rope_local_theta > 0:               # windowed layers: their own base, never scaled
+            rot = cfg.rot_dim
+            self.inv_freq_local = torch.tensor([cfg.rope_local_theta ** (-(2.0 * i) / rot) for i in range(rot // 2)],
+                                               dtype=torch.float32, device=dev)
         self.attn_factor = attn
         self.scale = cfg.attn_scale if cfg.attn_scale else cfg.head_dim ** -0.5
         self.rope_style = 0 if cfg.rope_style == "neox" else 1
@@ -141,9 +146,10 @@ class Decoder:
         qkv = ops.linear(h, lw.wqkv, lw.bqkv, defer=self._defer and not gated)
         local = self.kv_index[li]
         kc, vc = self.kv.k(local), self.kv.v(local)
-        q = ops.rope_kv_write(qkv, b.positions, b.slots, self.inv_freq, lw.q_norm, lw.k_norm, kc, vc,
-                              sp.hq_local, sp.hkv_local, cfg.head_dim, cfg.rot_dim, self.rope_style,
-                              cfg.rms_eps, self.attn_factor)
+        local_rope = self.inv_freq_local is not None and cfg.layer_window(li) > 0
+        q = ops.rope_kv_write(qkv, b.positions, b.slots, self.inv_freq_local if local_rope else self.inv_freq, lw.q_norm, lw.k_norm,
+                              kc, vc, sp.hq_local, sp.hkv_local, cfg.head_dim, cfg.rot_dim, self.rope_style,
+                              cfg.rms_eps, 1.0 if local_rope else self.attn_factor)
         a = ops.attention(q, kc, vc, b.block_tables, b.row_seq, b.positions, sp.hq_local, sp.hkv_local,
                           cfg.head_dim, self.scale, cfg.layer_window(li), lw.sinks, cfg.attn_softcap,
                           meta=b)
@@ -230,7 +236,7 @@ class Decoder:
     def fused_tp(self) -> bool:
         return (self.tp is not None and getattr(self.tp, "backend", "") == "fused" and self.tp.size > 1
                 and not self.cfg.is_moe and not self.cfg.post_norms and self.first_stage and self.last_stage
-                and self._dense_weights and not self.cfg.layer_kinds)
+                and self._dense_weights and not self.cfg.layer_kinds and not self.cfg.rope_local_theta)
 
     def forward_fused(self, b: StepBatch) -> torch.Tensor:
         """Whole forward with the sequence-sharded residual: every projection output leaves the

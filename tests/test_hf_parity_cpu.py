@@ -1,0 +1,77 @@
+"""The attention families against Hugging Face `transformers` itself: a random tiny model of each type is saved, read by
+the loader and run through the engine (fp32 weights, chunked prefill); teacher-forced logits must agree with the
+`transformers` forward pass up to the rounding of the bf16 KV pool."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from fllm_b200.config import EngineConfig
+from fllm_b200.runtime.engine import LLMEngine
+
+BASE = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+            max_position_embeddings=256)
+
+
+def _model(kind):
+    import transformers as tf
+    torch.manual_seed(0)
+    if kind == "llama":
+        return tf.LlamaForCausalLM(tf.LlamaConfig(**BASE))
+    if kind == "llama3_rope":
+        return tf.LlamaForCausalLM(tf.LlamaConfig(**BASE, rope_parameters=dict(rope_type="llama3", rope_theta=10000.0, factor=8.0,
+                                                  low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=32)))
+    if kind == "mistral":
+        return tf.MistralForCausalLM(tf.MistralConfig(**BASE, sliding_window=24))
+    if kind == "qwen2":
+        return tf.Qwen2ForCausalLM(tf.Qwen2Config(**BASE))
+    if kind == "qwen3":
+        return tf.Qwen3ForCausalLM(tf.Qwen3Config(**BASE, head_dim=32))
+    if kind == "gemma":
+        return tf.GemmaForCausalLM(tf.GemmaConfig(**BASE, head_dim=16))
+    if kind == "gemma2":
+        return tf.Gemma2ForCausalLM(tf.Gemma2Config(**BASE, head_dim=16, sliding_window=24, query_pre_attn_scalar=20,
+                                                    final_logit_softcapping=20.0, attn_logit_softcapping=30.0))
+    if kind == "gemma3":
+        return tf.Gemma3ForCausalLM(tf.Gemma3TextConfig(**BASE, head_dim=16, sliding_window=24, query_pre_attn_scalar=20,
+                                                        layer_types=["sliding_attention", "full_attention"],
+                                                        rope_parameters=dict(full_attention=dict(rope_type="linear", factor=4.0, rope_theta=100000.0),
+                                                                             sliding_attention=dict(rope_type="default", rope_theta=5000.0))))
+    if kind == "granite":
+        return tf.GraniteForCausalLM(tf.GraniteConfig(**BASE, embedding_multiplier=3.0, logits_scaling=2.0, residual_multiplier=0.5,
+                                                      attention_multiplier=0.2, tie_word_embeddings=True))
+    if kind == "phi3":
+        return tf.Phi3ForCausalLM(tf.Phi3Config(**BASE, pad_token_id=0))
+    if kind == "mixtral":
+        return tf.MixtralForCausalLM(tf.MixtralConfig(**BASE, num_local_experts=4, num_experts_per_tok=2))
+    if kind == "qwen3_moe":
+        return tf.Qwen3MoeForCausalLM(tf.Qwen3MoeConfig(**BASE, head_dim=32, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
+                                                         norm_topk_prob=True))
+    if kind == "qwen2_moe":
+        return tf.Qwen2MoeForCausalLM(tf.Qwen2MoeConfig(**BASE, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
+                                                         shared_expert_intermediate_size=64, norm_topk_prob=False))
+    raise ValueError(kind)
+
+
+@pytest.mark.parametrize("kind", ["llama", "llama3_rope", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "granite", "phi3", "mixtral", "qwen3_moe",
+                                  "qwen2_moe"])
+def test_attention_families_match_transformers(tmp_path, kind):
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    m = _model(kind).eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "norm" in n:
+                p.add_(0.3 * torch.randn_like(p))
+            if n.endswith(("mlp.gate.weight", "block_sparse_moe.gate.weight")):
+                p.mul_(20.0)                                  # clear routing decisions
+    d = str(tmp_path / kind)
+    m.save_pretrained(d, safe_serialization=True)
+    cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16),
+                    device="cpu", weights=w)
+    toks = torch.randint(0, 300, (45,), generator=torch.Generator().manual_seed(1)).tolist()
+    got = eng.token_logits(toks)
+    with torch.no_grad():
+        want = m(torch.tensor([toks])).logits[0].float()
+    err = (got - want).abs().max(dim=1).values / float(want.abs().max())
+    assert float(err.median()) < 2e-2 and int((err > 5e-2).sum()) <= (2 if "moe" in kind or kind == "mixtral" else 0), err
