@@ -76,6 +76,7 @@ class ModelConfig:
     shared_gate: bool = False            # the shared experts' output is scaled by sigmoid(h . g) (Qwen3-Next)
     qk_norm_offset: float = 0.0          # 1.0: the per-head q / k norms multiply by 1 + w (Gemma-3)
     rope_local_theta: float = 0.0        # > 0: windowed layers rotate with this base and no scaling (Gemma-3)
+    rope_layers: Optional[List[int]] = None   # per layer: 1 = rotary embedding, 0 = none (SmolLM3); None = every layer
     use_rope: bool = True                # False: attention layers carry no position signal of their own (Jamba)
     attn_out_gate: bool = False          # the query projection also emits a gate: attention output * sigmoid(gate) (Qwen3-Next)
     # recurrent and hybrid families: the token mixer of each layer (None = attention everywhere) and whether the
@@ -177,6 +178,9 @@ class ModelConfig:
             return recurrent_from_hf(cls, hf)
         if mt in ("deepseek_v2", "deepseek_v3"):
             return mla_from_hf(cls, hf)
+        if mt not in ATTENTION_MODEL_TYPES:
+            raise ValueError(f"model_type {mt!r} is not among the families this engine runs "
+                             f"({', '.join(sorted(ATTENTION_MODEL_TYPES + RECURRENT_MODEL_TYPES + ('deepseek_v2', 'deepseek_v3')))})")
         heads = hf["num_attention_heads"]
         hidden = hf["hidden_size"]
         cfg = cls(
@@ -243,15 +247,31 @@ class ModelConfig:
                 cfg.sliding_window = int(hf["sliding_window"])
                 lt = hf.get("layer_types")
                 cfg.window_pattern = [1 if t == "sliding_attention" else 0 for t in lt] if lt else [1, 0]
+        if mt in ("glm", "ernie4_5", "helium"):       # these rotate neighbouring pairs (x[2i], x[2i+1])
+            cfg.rope_style = "pair"
+        if mt == "glm":
+            cfg.rotary_dim = int(cfg.head_dim * hf.get("partial_rotary_factor", 0.5)) or None
+            cfg.attn_bias = hf.get("attention_bias", True)
+        if mt == "smollm3" and hf.get("no_rope_layers"):          # 1 = the layer rotates, 0 = no position signal in that layer
+            cfg.rope_layers = [int(v) for v in hf["no_rope_layers"]]
         if mt == "granite":                   # llama with four multipliers; the residual and logit ones are folded into weights at load
             cfg.embed_scale = float(hf.get("embedding_multiplier") or 1.0)
             if hf.get("attention_multiplier"):
                 cfg.attn_scale = float(hf["attention_multiplier"])
         if mt in ("phi3", "phi"):
             cfg.rotary_dim = int(cfg.head_dim * hf.get("partial_rotary_factor", 1.0)) or None
-        if hf.get("sliding_window") and hf.get("use_sliding_window", mt == "mistral"):
+        if hf.get("sliding_window") and hf.get("use_sliding_window", mt in ("mistral", "ministral")):
             cfg.sliding_window = hf["sliding_window"]
+            lt = hf.get("layer_types")
+            if lt and cfg.window_pattern is None and any(t != "sliding_attention" for t in lt):
+                cfg.window_pattern = [1 if t == "sliding_attention" else 0 for t in lt]
         return cfg
+
+
+# decoder families whose layers are attention + gated FFN (or routed experts) and that the generic mapping covers; every one
+# of them is checked against `transformers` in tests/test_hf_parity_cpu.py
+ATTENTION_MODEL_TYPES = ("llama", "mistral", "ministral", "qwen2", "qwen3", "qwen2_moe", "qwen3_moe", "mixtral", "gemma", "gemma2",
+                         "gemma3_text", "phi3", "gpt_oss", "granite", "seed_oss", "glm", "ernie4_5", "helium", "smollm3")
 
 
 def _yarn_mscale(factor: float, m: float) -> float:

@@ -86,6 +86,7 @@ class Decoder:
             inv = [0.0] * len(inv)
         self.inv_freq = torch.tensor(inv, dtype=torch.float32, device=dev)
         self.inv_freq_local = None
+        self._inv_freq_zero = None
         if cfg.rope_local_theta > 0:               # windowed layers: their own base, never scaled
             rot = cfg.rot_dim
             self.inv_freq_local = torch.tensor([cfg.rope_local_theta ** (-(2.0 * i) / rot) for i in range(rot // 2)],
@@ -147,7 +148,12 @@ class Decoder:
         local = self.kv_index[li]
         kc, vc = self.kv.k(local), self.kv.v(local)
         local_rope = self.inv_freq_local is not None and cfg.layer_window(li) > 0
-        q = ops.rope_kv_write(qkv, b.positions, b.slots, self.inv_freq_local if local_rope else self.inv_freq, lw.q_norm, lw.k_norm,
+        inv = self.inv_freq_local if local_rope else self.inv_freq
+        if cfg.rope_layers is not None and not cfg.rope_layers[li]:
+            if self._inv_freq_zero is None:
+                self._inv_freq_zero = torch.zeros_like(self.inv_freq)
+            inv = self._inv_freq_zero
+        q = ops.rope_kv_write(qkv, b.positions, b.slots, inv, lw.q_norm, lw.k_norm,
                               kc, vc, sp.hq_local, sp.hkv_local, cfg.head_dim, cfg.rot_dim, self.rope_style,
                               cfg.rms_eps, 1.0 if local_rope else self.attn_factor)
         a = ops.attention(q, kc, vc, b.block_tables, b.row_seq, b.positions, sp.hq_local, sp.hkv_local,
@@ -236,7 +242,7 @@ class Decoder:
     def fused_tp(self) -> bool:
         return (self.tp is not None and getattr(self.tp, "backend", "") == "fused" and self.tp.size > 1
                 and not self.cfg.is_moe and not self.cfg.post_norms and self.first_stage and self.last_stage
-                and self._dense_weights and not self.cfg.layer_kinds and not self.cfg.rope_local_theta)
+                and self._dense_weights and not self.cfg.layer_kinds and not self.cfg.rope_local_theta and self.cfg.rope_layers is None)
 
     def forward_fused(self, b: StepBatch) -> torch.Tensor:
         """Whole forward with the sequence-sharded residual: every projection output leaves the

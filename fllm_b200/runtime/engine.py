@@ -91,15 +91,18 @@ class LLMEngine:
         self.block_size = self.cfg.block_size
         self.max_blocks_per_seq = -(-self.cfg.max_model_len // self.block_size)
         num_blocks = self.cfg.num_kv_blocks or self._size_kv_pool()
-        if self.cfg.kv_cache_dtype not in ("bf16", "fp8", "fp8_e4m3"):
+        if self.cfg.kv_cache_dtype not in ("bf16", "fp8", "fp8_e4m3", "fp32"):
             raise ValueError("kv_cache_dtype must be bf16 or fp8_e4m3")
-        kv_dtype = torch.bfloat16 if self.cfg.kv_cache_dtype == "bf16" else torch.float8_e4m3fn
+        # fp32: only with the PyTorch operators (exact comparisons against other implementations on the CPU)
+        kv_dtype = {"bf16": torch.bfloat16, "fp32": torch.float32}.get(self.cfg.kv_cache_dtype, torch.float8_e4m3fn)
+        if kv_dtype == torch.float32 and hasattr(self.ops, "k"):
+            raise ValueError("an fp32 KV pool is for the reference operators only")
         if model_cfg.has_mla:
             from ..models.mla import MlaCache
-            if kv_dtype != torch.bfloat16:
+            if kv_dtype not in (torch.bfloat16, torch.float32):
                 raise ValueError("the latent cache of multi-head latent attention is bf16")
             self.kv = MlaCache(self._kv_layers(), num_blocks, self.block_size,
-                               model_cfg.mla["kv_lora_rank"] + model_cfg.mla["qk_rope_head_dim"], self.device)
+                               model_cfg.mla["kv_lora_rank"] + model_cfg.mla["qk_rope_head_dim"], self.device, kv_dtype)
         else:
             self.kv = KVCache(self._kv_layers(), num_blocks, self.spec.hkv_local, self.block_size,
                               model_cfg.head_dim, self.device, kv_dtype)

@@ -1,6 +1,7 @@
 """The attention families against Hugging Face `transformers` itself: a random tiny model of each type is saved, read by
 the loader and run through the engine (fp32 weights, chunked prefill); teacher-forced logits must agree with the
-`transformers` forward pass up to the rounding of the bf16 KV pool."""
+`transformers` forward pass (the KV pool is fp32 here too; the projections that feed the attention scores are scaled up so
+that a wrong rotation, mask or window moves the logits)."""
 import pytest
 import torch
 
@@ -31,7 +32,8 @@ def _model(kind):
         return tf.GemmaForCausalLM(tf.GemmaConfig(**BASE, head_dim=16))
     if kind == "gemma2":
         return tf.Gemma2ForCausalLM(tf.Gemma2Config(**BASE, head_dim=16, sliding_window=24, query_pre_attn_scalar=20,
-                                                    final_logit_softcapping=20.0, attn_logit_softcapping=30.0))
+                                                    final_logit_softcapping=20.0, attn_logit_softcapping=30.0,
+                                                    attn_implementation="eager"))      # the fused attention path of the library drops the soft-cap
     if kind == "gemma3":
         return tf.Gemma3ForCausalLM(tf.Gemma3TextConfig(**BASE, head_dim=16, sliding_window=24, query_pre_attn_scalar=20,
                                                         layer_types=["sliding_attention", "full_attention"],
@@ -40,6 +42,18 @@ def _model(kind):
     if kind == "granite":
         return tf.GraniteForCausalLM(tf.GraniteConfig(**BASE, embedding_multiplier=3.0, logits_scaling=2.0, residual_multiplier=0.5,
                                                       attention_multiplier=0.2, tie_word_embeddings=True))
+    if kind == "seed_oss":
+        return tf.SeedOssForCausalLM(tf.SeedOssConfig(**BASE, head_dim=16, pad_token_id=0))
+    if kind == "ernie4_5":
+        return tf.Ernie4_5ForCausalLM(tf.Ernie4_5Config(**BASE, pad_token_id=0))
+    if kind == "glm":
+        return tf.GlmForCausalLM(tf.GlmConfig(**BASE, head_dim=16, pad_token_id=0))
+    if kind == "helium":
+        return tf.HeliumForCausalLM(tf.HeliumConfig(**BASE, head_dim=16, pad_token_id=0))
+    if kind == "ministral":
+        return tf.MinistralForCausalLM(tf.MinistralConfig(**BASE, head_dim=16, pad_token_id=0, sliding_window=24))
+    if kind == "smollm3":
+        return tf.SmolLM3ForCausalLM(tf.SmolLM3Config(**BASE, pad_token_id=0, no_rope_layers=[1, 0]))
     if kind == "phi3":
         return tf.Phi3ForCausalLM(tf.Phi3Config(**BASE, pad_token_id=0))
     if kind == "mixtral":
@@ -53,7 +67,8 @@ def _model(kind):
     raise ValueError(kind)
 
 
-@pytest.mark.parametrize("kind", ["llama", "llama3_rope", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "granite", "phi3", "mixtral", "qwen3_moe",
+@pytest.mark.parametrize("kind", ["llama", "llama3_rope", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "granite", "seed_oss", "ernie4_5", "glm", "helium",
+                                  "ministral", "smollm3", "phi3", "mixtral", "qwen3_moe",
                                   "qwen2_moe"])
 def test_attention_families_match_transformers(tmp_path, kind):
     from fllm_b200.formats.loader import load_hf_checkpoint
@@ -64,14 +79,25 @@ def test_attention_families_match_transformers(tmp_path, kind):
                 p.add_(0.3 * torch.randn_like(p))
             if n.endswith(("mlp.gate.weight", "block_sparse_moe.gate.weight")):
                 p.mul_(20.0)                                  # clear routing decisions
+            if n.endswith(("q_proj.weight", "k_proj.weight", "qkv_proj.weight")):
+                p.mul_(12.0)                                  # peaked attention: a wrong rotation or mask moves the logits
     d = str(tmp_path / kind)
     m.save_pretrained(d, safe_serialization=True)
     cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
-    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16),
-                    device="cpu", weights=w)
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16,
+                                      kv_cache_dtype="fp32"), device="cpu", weights=w)
     toks = torch.randint(0, 300, (45,), generator=torch.Generator().manual_seed(1)).tolist()
     got = eng.token_logits(toks)
     with torch.no_grad():
         want = m(torch.tensor([toks])).logits[0].float()
     err = (got - want).abs().max(dim=1).values / float(want.abs().max())
-    assert float(err.median()) < 2e-2 and int((err > 5e-2).sum()) <= (2 if "moe" in kind or kind == "mixtral" else 0), err
+    # fp32 end to end (KV pool included); routed models round their router scores to bf16, which may flip a near-tie
+    routed = "moe" in kind or kind == "mixtral"        # the routed path rounds activations to bf16 between its stages, like the kernels
+    assert float(err.median()) < (1e-2 if routed else 2e-3) and int((err > (5e-2 if routed else 1e-2)).sum()) <= (2 if routed else 0), err
+
+
+def test_unknown_families_are_refused():
+    """A model type without a mapping must not run as if it were a Llama."""
+    from fllm_b200.config import ModelConfig
+    with pytest.raises(ValueError, match="not among the families"):
+        ModelConfig.from_hf_config(dict(model_type="stablelm", vocab_size=10, hidden_size=8, num_hidden_layers=1, num_attention_heads=1))

@@ -65,20 +65,28 @@ def test_recurrent_families_match_transformers(tmp_path, kind):
                 p.add_(0.3 * torch.randn_like(p))
             if n.endswith(("router.weight", "router.layer.weight")):
                 p.mul_(20.0)                                  # clear routing decisions
+            if n.endswith(("q_proj.weight", "k_proj.weight")):
+                p.mul_(12.0)                                  # peaked attention: a wrong rotation or mask moves the logits
     d = str(tmp_path / kind)
     m.save_pretrained(d, safe_serialization=True)
     cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
     assert cfg.has_recurrent
-    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16),
-                    device="cpu", weights=w)
+    if kind == "bamba":
+        # The config rotates half of each head (as the published checkpoints were trained and as the engine does); this
+        # version of the oracle rotates the whole head whatever the config says, so the width follows the oracle here.
+        assert cfg.rot_dim == cfg.head_dim // 2
+        cfg.rotary_dim = None
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16,
+                                      kv_cache_dtype="fp32"), device="cpu", weights=w)
     toks = torch.randint(0, 300, (45,), generator=torch.Generator().manual_seed(1)).tolist()
     got = eng.token_logits(toks)               # three steps of at most 16 rows: the states cross two boundaries
     with torch.no_grad():
         want = m(torch.tensor([toks])).logits[0].float()
     scale = float(want.abs().max())
-    # the paged KV pool holds bf16 whatever the activation type: families with attention layers see its rounding
-    tol = 2e-2 if "attention" in cfg.layer_kinds else 1e-4
-    assert float((got - want).abs().max()) < tol * scale, (float((got - want).abs().max()), scale)
+    err = (got - want).abs().max(dim=1).values / scale
+    # fp32 end to end; routed layers round their router scores to bf16, which may flip a near-tie for a token
+    routed = bool(cfg.ffn_kinds) and "moe" in cfg.ffn_kinds
+    assert float(err.median()) < (1e-2 if routed else 2e-3) and int((err > (5e-2 if routed else 1e-2)).sum()) <= (2 if routed else 0), err
     assert not eng.blocks.seqs and len(eng.blocks.state_free) == eng.rstate.slots - 1
 
 
@@ -191,18 +199,20 @@ def test_latent_attention_matches_transformers(tmp_path, version, q_lora):
         for n, p in m.named_parameters():
             if "layernorm" in n or n.endswith("norm.weight"):
                 p.add_(0.3 * torch.randn_like(p))
+            if n.endswith(("q_proj.weight", "q_b_proj.weight", "kv_b_proj.weight", "kv_a_proj_with_mqa.weight")):
+                p.mul_(6.0)                                   # peaked attention
     d = str(tmp_path / f"ds{version}")
     m.save_pretrained(d, safe_serialization=True)
     cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
     assert cfg.has_mla and not cfg.has_recurrent and cfg.rope_scaling.kind == "yarn"
-    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=32, max_model_len=256, num_kv_blocks=32, block_size=16),
-                    device="cpu", weights=w)
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=32, max_model_len=256, num_kv_blocks=32, block_size=16,
+                                      kv_cache_dtype="fp32"), device="cpu", weights=w)
     toks = torch.randint(0, 300, (150,), generator=torch.Generator().manual_seed(1)).tolist()      # beyond the original 64 positions
     got = eng.token_logits(toks)
     with torch.no_grad():
         want = m(torch.tensor([toks])).logits[0].float()
     scale = float(want.abs().max())
-    assert float((got - want).abs().max()) < 2e-2 * scale, (float((got - want).abs().max()), scale)     # the latent pool is bf16
+    assert float((got - want).abs().max()) < 2e-3 * scale, (float((got - want).abs().max()), scale)
 
 
 def _rwkv7_oracle(sd, cfg, ids):
@@ -266,8 +276,8 @@ def test_rwkv7_matches_token_by_token_recurrence(tmp_path):
     save_file(sd, str(tmp_path / "model.safetensors"))
     cfg2, w, _ = load_hf_checkpoint(str(tmp_path), device="cpu", dtype=torch.float32)
     assert cfg2.arch == "rwkv7" and cfg2.has_recurrent
-    eng = LLMEngine(cfg2, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16),
-                    device="cpu", weights=w)
+    eng = LLMEngine(cfg2, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16,
+                                      kv_cache_dtype="fp32"), device="cpu", weights=w)
     toks = torch.randint(0, 300, (40,), generator=torch.Generator().manual_seed(2)).tolist()
     got = eng.token_logits(toks)                       # 16 + 16 + 8 rows: every state crosses two step boundaries
     want = _rwkv7_oracle(sd, cfg, toks)
@@ -313,15 +323,15 @@ def test_deepseek_routed_and_shared_experts_match_transformers(tmp_path, version
     assert cfg.router_groups == (1 if version == 2 else 4)
     assert w.layers[1].router_w is not None and w.layers[0].router_w is None
     assert (w.layers[1].router_select_b is not None) == (version == 3)
-    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=32, max_model_len=128, num_kv_blocks=32, block_size=16),
-                    device="cpu", weights=w)
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=32, max_model_len=128, num_kv_blocks=32, block_size=16,
+                                      kv_cache_dtype="fp32"), device="cpu", weights=w)
     toks = torch.randint(0, 300, (50,), generator=torch.Generator().manual_seed(1)).tolist()
     got = eng.token_logits(toks)
     with torch.no_grad():
         want = m(torch.tensor([toks])).logits[0].float()
     err = (got - want).abs().max(dim=1).values / float(want.abs().max())
     # bf16 rounding of the router scores can flip a near-tie for a single token; the rest must agree closely
-    assert float(err.median()) < 2e-2 and int((err > 5e-2).sum()) <= 2, err
+    assert float(err.median()) < 1e-2 and int((err > 5e-2).sum()) <= 2, err
 
 
 def test_group_limited_router_keeps_the_best_groups():
@@ -388,14 +398,14 @@ def test_qwen3_next_matches_transformers(tmp_path):
     cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
     assert cfg.layer_kinds == ["gated_delta"] * 3 + ["attention"] and cfg.ffn_kinds == ["glu", "moe", "moe", "moe"]
     assert cfg.rot_dim == 8 and cfg.attn_out_gate and w.layers[3].w_attn_gate is not None and w.layers[1].shared_gate_w is not None
-    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16),
-                    device="cpu", weights=w)
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16,
+                                      kv_cache_dtype="fp32"), device="cpu", weights=w)
     toks = torch.randint(0, 300, (45,), generator=torch.Generator().manual_seed(1)).tolist()
     got = eng.token_logits(toks)
     with torch.no_grad():
         want = m(torch.tensor([toks])).logits[0].float()
     err = (got - want).abs().max(dim=1).values / float(want.abs().max())
-    assert float(err.median()) < 2e-2 and int((err > 5e-2).sum()) <= 2, err
+    assert float(err.median()) < 1e-2 and int((err > 5e-2).sum()) <= 2, err
 
 
 @pytest.mark.parametrize("n,H,P,G,N,Q,fresh", [(300, 4, 16, 2, 16, 64, True), (129, 6, 8, 1, 32, 128, False), (64, 2, 8, 2, 16, 64, False)])
@@ -475,8 +485,8 @@ def test_rwkv6_matches_token_by_token_recurrence(tmp_path):
     save_file(sd, str(tmp_path / "model.safetensors"))
     cfg2, w, _ = load_hf_checkpoint(str(tmp_path), device="cpu", dtype=torch.float32)
     assert cfg2.arch == "rwkv6"
-    eng = LLMEngine(cfg2, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16),
-                    device="cpu", weights=w)
+    eng = LLMEngine(cfg2, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16,
+                                      kv_cache_dtype="fp32"), device="cpu", weights=w)
     toks = torch.randint(0, 300, (40,), generator=torch.Generator().manual_seed(2)).tolist()
     got = eng.token_logits(toks)
     want = _rwkv6_oracle(sd, cfg, toks)
