@@ -76,6 +76,14 @@ class ModelConfig:
     shared_gate: bool = False            # the shared experts' output is scaled by sigmoid(h . g) (Qwen3-Next)
     qk_norm_offset: float = 0.0          # 1.0: the per-head q / k norms multiply by 1 + w (Gemma-3)
     rope_local_theta: float = 0.0        # > 0: windowed layers rotate with this base and no scaling (Gemma-3)
+    # block variants of the pre-Llama families: LayerNorm (with or without bias) instead of RMSNorm, a plain two-matrix MLP
+    # (activation in `act`: gelu | gelu_tanh | relu2 | silu | relu) instead of the gated one, attention and MLP side by side
+    # from one residual read (with one shared norm or one norm each), biases on the MLP and the head
+    norm_kind: str = "rms"               # rms | layernorm | layernorm_nobias
+    mlp_kind: str = "glu"                # glu | plain
+    parallel_block: bool = False
+    parallel_norms: int = 1              # parallel blocks: 1 = attention and MLP read the same normed input, 2 = a norm each
+    mlp_bias: bool = False
     rope_layers: Optional[List[int]] = None   # per layer: 1 = rotary embedding, 0 = none (SmolLM3); None = every layer
     use_rope: bool = True                # False: attention layers carry no position signal of their own (Jamba)
     attn_out_gate: bool = False          # the query projection also emits a gate: attention output * sigmoid(gate) (Qwen3-Next)
@@ -178,9 +186,11 @@ class ModelConfig:
             return recurrent_from_hf(cls, hf)
         if mt in ("deepseek_v2", "deepseek_v3"):
             return mla_from_hf(cls, hf)
+        if mt in CLASSIC_MODEL_TYPES:
+            return classic_from_hf(cls, hf)
         if mt not in ATTENTION_MODEL_TYPES:
             raise ValueError(f"model_type {mt!r} is not among the families this engine runs "
-                             f"({', '.join(sorted(ATTENTION_MODEL_TYPES + RECURRENT_MODEL_TYPES + ('deepseek_v2', 'deepseek_v3')))})")
+                             f"({', '.join(sorted(ATTENTION_MODEL_TYPES + CLASSIC_MODEL_TYPES + RECURRENT_MODEL_TYPES + ('deepseek_v2', 'deepseek_v3')))})")
         heads = hf["num_attention_heads"]
         hidden = hf["hidden_size"]
         cfg = cls(
@@ -272,6 +282,60 @@ class ModelConfig:
 # of them is checked against `transformers` in tests/test_hf_parity_cpu.py
 ATTENTION_MODEL_TYPES = ("llama", "mistral", "ministral", "qwen2", "qwen3", "qwen2_moe", "qwen3_moe", "mixtral", "gemma", "gemma2",
                          "gemma3_text", "phi3", "gpt_oss", "granite", "seed_oss", "glm", "ernie4_5", "helium", "smollm3")
+
+
+CLASSIC_MODEL_TYPES = ("starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere")
+_ACT_NAMES = {"gelu": "gelu", "gelu_new": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh", "gelu_fast": "gelu_tanh", "relu2": "relu2",
+              "silu": "silu", "swish": "silu", "relu": "relu"}
+
+
+def classic_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
+    """Families built from LayerNorm, plain MLPs or parallel blocks (the reference covers them through the same decoder,
+    rust/engine/src/config.rs fields `norm`, `ffn`, `parallel_residual`)."""
+    mt = hf["model_type"]
+    hidden, L, heads = hf["hidden_size"], hf["num_hidden_layers"], hf["num_attention_heads"]
+    head_dim = hf.get("head_dim") or hidden // heads
+    act = _ACT_NAMES.get(hf.get("hidden_act", "gelu"), "gelu")
+    cfg = cls(arch=mt, name=hf.get("_name_or_path") or mt, vocab_size=hf["vocab_size"], hidden_size=hidden, num_layers=L, num_heads=heads,
+              num_kv_heads=hf.get("num_key_value_heads") or heads, head_dim=head_dim, intermediate_size=hf.get("intermediate_size", 4 * hidden),
+              rope_theta=hf.get("rope_theta", 10000.0), max_position=hf.get("max_position_embeddings", 4096),
+              tie_embeddings=hf.get("tie_word_embeddings", False))
+    prf = hf.get("partial_rotary_factor", hf.get("rotary_pct"))
+    if prf is not None and float(prf) < 1.0:
+        cfg.rotary_dim = int(head_dim * float(prf)) or None
+    if mt == "starcoder2":
+        cfg.norm_kind, cfg.mlp_kind, cfg.act, cfg.rms_eps = "layernorm", "plain", act, hf.get("norm_epsilon", 1e-5)
+        cfg.attn_bias = cfg.mlp_bias = bool(hf.get("use_bias", True))
+        cfg.tie_embeddings = hf.get("tie_word_embeddings", True)
+        if hf.get("sliding_window"):
+            cfg.sliding_window = int(hf["sliding_window"])
+    elif mt == "stablelm":
+        if hf.get("qk_layernorm") or hf.get("use_parallel_residual"):
+            raise NotImplementedError("stablelm with per-head QK LayerNorm or parallel residual is not supported")
+        cfg.norm_kind, cfg.rms_eps, cfg.attn_bias = "layernorm", hf.get("layer_norm_eps", 1e-5), bool(hf.get("use_qkv_bias", False))
+    elif mt == "nemotron":                # LayerNorm whose weight is stored minus one, squared-ReLU MLP
+        cfg.norm_kind, cfg.norm_weight_offset, cfg.rms_eps = "layernorm", 1.0, hf.get("norm_eps", 1e-5)
+        cfg.mlp_kind, cfg.act, cfg.attn_bias, cfg.mlp_bias = "plain", act, bool(hf.get("attention_bias", False)), bool(hf.get("mlp_bias", False))
+    elif mt == "arcee":
+        cfg.mlp_kind, cfg.act, cfg.rms_eps = "plain", act, hf.get("rms_norm_eps", 1e-5)
+        cfg.attn_bias, cfg.mlp_bias = bool(hf.get("attention_bias", False)), bool(hf.get("mlp_bias", False))
+    elif mt == "phi":
+        if hf.get("qk_layernorm"):
+            raise NotImplementedError("phi with QK LayerNorm is not supported")
+        cfg.norm_kind, cfg.mlp_kind, cfg.act, cfg.rms_eps = "layernorm", "plain", act, hf.get("layer_norm_eps", 1e-5)
+        cfg.parallel_block, cfg.parallel_norms, cfg.attn_bias, cfg.mlp_bias = True, 1, True, True
+    elif mt == "gpt_neox":
+        cfg.norm_kind, cfg.mlp_kind, cfg.act, cfg.rms_eps = "layernorm", "plain", act, hf.get("layer_norm_eps", 1e-5)
+        cfg.parallel_block, cfg.parallel_norms = bool(hf.get("use_parallel_residual", True)), 2
+        cfg.attn_bias, cfg.mlp_bias = bool(hf.get("attention_bias", True)), True
+    elif mt == "cohere":
+        if hf.get("use_qk_norm"):
+            raise NotImplementedError("cohere with QK norm is not supported")
+        cfg.norm_kind, cfg.rms_eps, cfg.parallel_block, cfg.parallel_norms = "layernorm_nobias", hf.get("layer_norm_eps", 1e-5), True, 1
+        cfg.rope_style, cfg.tie_embeddings = "pair", hf.get("tie_word_embeddings", True)
+        cfg.attn_bias = bool(hf.get("attention_bias", False))
+        cfg.ssm = dict(logit_mult=float(hf.get("logit_scale") or 1.0))       # folded into the head at load
+    return cfg
 
 
 def _yarn_mscale(factor: float, m: float) -> float:

@@ -217,6 +217,34 @@ void gather_rows(const Tensor& x, const Tensor& rows, Tensor out) {
                          (int)rows.numel(), (int)x.size(1), cur_stream());
 }
 
+void add_layernorm(Tensor x, const optional<Tensor>& delta, const Tensor& w, const optional<Tensor>& b, Tensor y, double eps, double w_offset) {
+  check_bf16(x, "x"); check_rows(x, "x"); check_bf16(y, "y"); check_rows(y, "y"); check_bf16(w, "w");
+  TORCH_CHECK(y.sizes() == x.sizes() && w.is_contiguous() && w.numel() == x.size(1), "add_layernorm: shapes");
+  const void* d = nullptr;
+  long long ldd = 0;
+  if (delta.has_value() && delta->defined()) {
+    check_bf16(*delta, "delta"); check_rows(*delta, "delta");
+    TORCH_CHECK(delta->sizes() == x.sizes(), "add_layernorm: delta shape");
+    d = delta->data_ptr();
+    ldd = delta->stride(0);
+  }
+  const void* bp = nullptr;
+  if (b.has_value() && b->defined()) {
+    check_bf16(*b, "b");
+    TORCH_CHECK(b->is_contiguous() && b->numel() == x.size(1), "add_layernorm: bias shape");
+    bp = b->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  fllm::add_layernorm_bf16(x.data_ptr(), x.stride(0), d, ldd, w.data_ptr(), bp, y.data_ptr(), y.stride(0), (int)x.size(0), (int)x.size(1),
+                           (float)eps, (float)w_offset, cur_stream());
+}
+
+void act_(Tensor x, int64_t kind) {
+  check_bf16(x, "x"); check_rows(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  fllm::act_rows_bf16(x.data_ptr(), x.stride(0), (int)x.size(0), (int)x.size(1), (int)kind, cur_stream());
+}
+
 void softcap_(Tensor x, double cap) {
   check_bf16(x, "x"); check_rows(x, "x");
   TORCH_CHECK(cap > 0, "softcap_: the cap must be positive");
@@ -417,6 +445,8 @@ TORCH_LIBRARY(fllm_b200, m) {
   m.def("glu(Tensor x, Tensor(a!) out, int act_kind, float alpha, float limit) -> ()", &glu);
   m.def("gather_rows(Tensor x, Tensor rows, Tensor(a!) out) -> ()", &gather_rows);
   m.def("softcap_(Tensor(a!) x, float cap) -> ()", &softcap_);
+  m.def("add_layernorm(Tensor(a!) x, Tensor? delta, Tensor w, Tensor? b, Tensor(b!) y, float eps, float w_offset) -> ()", &add_layernorm);
+  m.def("act_(Tensor(a!) x, int kind) -> ()", &act_);
   m.def("attention_generic(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor row_seq, Tensor positions, Tensor(a!) out, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap, Tensor? tree_mask=None, Tensor? tree_base=None) -> ()", &attention_generic);
   m.def("attention_tc(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_tables, Tensor q_starts, Tensor kv_lens, Tensor(a!) out, int num_seqs, int max_q_len, int min_q_len, int max_kv_len, int hq, int hkv, int head_dim, float scale, int window, Tensor? sinks, float softcap, Tensor? workspace, Tensor? status=None, bool bidirectional=False) -> int", &attention_tc);
   m.def("argmax(Tensor logits, Tensor(a!) out_ids, Tensor? out_vals, int id_offset) -> ()", &argmax);

@@ -650,4 +650,113 @@ void softcap_rows_bf16(void* x, long long ldx, int rows, int cols, float cap, cu
   cuda_check(cudaGetLastError(), "softcap_rows_kernel");
 }
 
+// ---- LayerNorm with the residual update in front (GPT-NeoX / Phi / StarCoder2 / Cohere / Nemotron blocks): x += delta (in place, when
+// delta is given), y = (x - mean) * rstd * (w + w_offset) + b. One CTA per row, the row kept in registers between the passes
+// (up to 16384 columns), two-pass variance. -----------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) add_layernorm_kernel(__nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ delta,
+                                                            long long ldd, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
+                                                            __nv_bfloat16* __restrict__ y, long long ldy, int cols, float eps, float w_offset) {
+  constexpr int KEEP = 32;                                  // pairs per thread: 256 * 32 * 2 columns
+  const int row = blockIdx.x, pairs = cols / 2;
+  __nv_bfloat162* xr = reinterpret_cast<__nv_bfloat162*>(x + (size_t)row * ldx);
+  const __nv_bfloat162* dr = delta ? reinterpret_cast<const __nv_bfloat162*>(delta + (size_t)row * ldd) : nullptr;
+  float2 v[KEEP];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < KEEP; ++i) {
+    const int p = threadIdx.x + i * 256;
+    v[i] = make_float2(0.f, 0.f);
+    if (p < pairs) {
+      v[i] = __bfloat1622float2(xr[p]);
+      if (dr) {
+        const float2 d = __bfloat1622float2(dr[p]);
+        const __nv_bfloat162 r = __floats2bfloat162_rn(v[i].x + d.x, v[i].y + d.y);     // the stored residual is what gets normalised
+        xr[p] = r;
+        v[i] = __bfloat1622float2(r);
+      }
+      sum += v[i].x + v[i].y;
+    }
+  }
+  __shared__ float part[8];
+  __shared__ float stat[2];
+  sum = warp_sum(sum);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += part[i];
+    stat[0] = t / cols;
+  }
+  __syncthreads();
+  const float mean = stat[0];
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < KEEP; ++i) {
+    const int p = threadIdx.x + i * 256;
+    if (p < pairs) sq += (v[i].x - mean) * (v[i].x - mean) + (v[i].y - mean) * (v[i].y - mean);
+  }
+  sq = warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += part[i];
+    stat[1] = rsqrtf(t / cols + eps);
+  }
+  __syncthreads();
+  const float rstd = stat[1];
+  __nv_bfloat162* yr = reinterpret_cast<__nv_bfloat162*>(y + (size_t)row * ldy);
+  const __nv_bfloat162* wr = reinterpret_cast<const __nv_bfloat162*>(w);
+  const __nv_bfloat162* br = b ? reinterpret_cast<const __nv_bfloat162*>(b) : nullptr;
+#pragma unroll
+  for (int i = 0; i < KEEP; ++i) {
+    const int p = threadIdx.x + i * 256;
+    if (p < pairs) {
+      const float2 ww = __bfloat1622float2(wr[p]);
+      const float2 bb = br ? __bfloat1622float2(br[p]) : make_float2(0.f, 0.f);
+      yr[p] = __floats2bfloat162_rn((v[i].x - mean) * rstd * (ww.x + w_offset) + bb.x, (v[i].y - mean) * rstd * (ww.y + w_offset) + bb.y);
+    }
+  }
+}
+
+void add_layernorm_bf16(void* x, long long ldx, const void* delta, long long ldd, const void* w, const void* b, void* y, long long ldy,
+                        int rows, int cols, float eps, float w_offset, cudaStream_t s) {
+  if (rows <= 0) return;
+  if ((cols & 1) || cols > 16384 || (ldx & 1) || (ldd & 1) || (ldy & 1))
+    throw std::runtime_error("add_layernorm_bf16: an even width of at most 16384 and even leading dimensions are required");
+  add_layernorm_kernel<<<rows, 256, 0, s>>>((__nv_bfloat16*)x, ldx, (const __nv_bfloat16*)delta, ldd, (const __nv_bfloat16*)w,
+                                            (const __nv_bfloat16*)b, (__nv_bfloat16*)y, ldy, cols, eps, w_offset);
+  cuda_check(cudaGetLastError(), "add_layernorm_kernel");
+}
+
+// ---- activation of a plain MLP, in place over bf16 rows: 0 gelu (erf), 1 gelu (tanh), 2 squared relu, 3 silu, 4 relu -------------
+__global__ void act_rows_kernel(__nv_bfloat16* __restrict__ x, long long ldx, int cols, int kind) {
+  __nv_bfloat16* row = x + (size_t)blockIdx.y * ldx;
+  for (int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2; c < cols; c += gridDim.x * blockDim.x * 2) {
+    float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row + c));
+    float* f = &v.x;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float t = f[i];
+      float r;
+      if (kind == 0) r = 0.5f * t * (1.f + erff(t * 0.70710678118654752f));
+      else if (kind == 1) r = 0.5f * t * (1.f + tanhf(0.7978845608028654f * (t + 0.044715f * t * t * t)));
+      else if (kind == 2) r = t > 0.f ? t * t : 0.f;
+      else if (kind == 3) r = t / (1.f + __expf(-t));
+      else r = fmaxf(t, 0.f);
+      f[i] = r;
+    }
+    *reinterpret_cast<__nv_bfloat162*>(row + c) = __floats2bfloat162_rn(v.x, v.y);
+  }
+}
+
+void act_rows_bf16(void* x, long long ldx, int rows, int cols, int kind, cudaStream_t s) {
+  if (rows <= 0 || cols <= 0) return;
+  if ((cols & 1) || (ldx & 1) || (reinterpret_cast<uintptr_t>(x) & 3) || kind < 0 || kind > 4)
+    throw std::runtime_error("act_rows_bf16: an even width and leading dimension, 4-byte aligned rows, kind 0..4");
+  const int bx = std::max(1, std::min((cols / 2 + 255) / 256, 64));
+  act_rows_kernel<<<dim3(bx, rows), 256, 0, s>>>((__nv_bfloat16*)x, ldx, cols, kind);
+  cuda_check(cudaGetLastError(), "act_rows_kernel");
+}
+
 }  // namespace fllm

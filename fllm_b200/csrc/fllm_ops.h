@@ -317,4 +317,10 @@ void mla_prepare_bf16(const void* ckv, long long ldc, const void* q, long long l
 // x = cap * tanh(x / cap) in place over bf16 rows
 void softcap_rows_bf16(void* x, long long ldx, int rows, int cols, float cap, cudaStream_t s);
 
+// x += delta (in place, delta may be null), y = LayerNorm(x) * (w + w_offset) + b (b may be null)
+void add_layernorm_bf16(void* x, long long ldx, const void* delta, long long ldd, const void* w, const void* b, void* y, long long ldy,
+                        int rows, int cols, float eps, float w_offset, cudaStream_t s);
+// in-place activation: 0 gelu (erf), 1 gelu (tanh), 2 squared relu, 3 silu, 4 relu
+void act_rows_bf16(void* x, long long ldx, int rows, int cols, int kind, cudaStream_t s);
+
 }  // namespace fllm

@@ -1,0 +1,84 @@
+"""Hugging Face checkpoints of the families built from LayerNorm, plain MLPs or parallel blocks (StarCoder2, StableLM,
+Nemotron, Arcee, Phi, GPT-NeoX / Pythia, Cohere) into the decoder's weight containers (one rank).
+
+The reference reads these families from GGUF files through the same decoder (rust/engine/src/rust_decoder.rs
+``load_layers_ex``: `norm` kinds, `ffn` kinds, parallel residual); the tensor roles are the same, the names here are the
+Hugging Face ones.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config import ModelConfig
+from ..models.weights import DecoderWeights, LayerWeights
+
+# per family: (layer prefix, attention prefix, q/k/v names or fused name, output name, first norm, second norm, MLP in, MLP out)
+_NAMES = {
+    "starcoder2": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", "input_layernorm", "post_attention_layernorm",
+                   "mlp.c_fc", "mlp.c_proj"),
+    "stablelm": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", "input_layernorm", "post_attention_layernorm",
+                 None, "mlp.down_proj"),
+    "nemotron": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", "input_layernorm", "post_attention_layernorm",
+                 "mlp.up_proj", "mlp.down_proj"),
+    "arcee": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", "input_layernorm", "post_attention_layernorm",
+              "mlp.up_proj", "mlp.down_proj"),
+    "phi": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "dense", "input_layernorm", None, "mlp.fc1", "mlp.fc2"),
+    "gpt_neox": ("gpt_neox.layers.{}.", "attention.", "query_key_value", "dense", "input_layernorm", "post_attention_layernorm",
+                 "mlp.dense_h_to_4h", "mlp.dense_4h_to_h"),
+    "cohere": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", "input_layernorm", None, None, "mlp.down_proj"),
+}
+
+
+def load_hf_classic(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
+    """``get(name, required=True)`` returns a checkpoint tensor (or None)."""
+    def dev(t):
+        return t.to(device=device, dtype=dtype).contiguous()
+
+    def opt(name):
+        t = get(name, False)
+        return dev(t) if t is not None else None
+
+    lp, ap, qkv, o_name, n1, n2, mlp_in, mlp_out = _NAMES[cfg.arch]
+    H, D, hq, hkv = cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
+    layers = []
+    for l in range(cfg.num_layers):
+        p = lp.format(l)
+        lw = LayerWeights(attn_norm=dev(get(p + n1 + ".weight")), wqkv=None, wo=None,
+                          ffn_norm=dev(get(p + n2 + ".weight")) if n2 else None)
+        lw.attn_norm_b, lw.ffn_norm_b = opt(p + n1 + ".bias"), opt(p + n2 + ".bias") if n2 else None
+        if isinstance(qkv, tuple):
+            lw.wqkv = dev(torch.cat([get(p + ap + n + ".weight") for n in qkv], 0))
+            bs = [get(p + ap + n + ".bias", False) for n in qkv]
+            if bs[0] is not None:
+                lw.bqkv = dev(torch.cat(bs))
+        else:                                   # GPT-NeoX: one matrix whose rows go head by head as (q, k, v)
+            w = get(p + ap + qkv + ".weight").view(hq, 3, D, H)
+            lw.wqkv = dev(torch.cat([w[:, 0].reshape(hq * D, H), w[:, 1].reshape(hq * D, H), w[:, 2].reshape(hq * D, H)], 0))
+            bb = get(p + ap + qkv + ".bias", False)
+            if bb is not None:
+                bb = bb.view(hq, 3, D)
+                lw.bqkv = dev(torch.cat([bb[:, 0].reshape(-1), bb[:, 1].reshape(-1), bb[:, 2].reshape(-1)]))
+        lw.wo, lw.bo = dev(get(p + ap + o_name + ".weight")), opt(p + ap + o_name + ".bias")
+        if cfg.mlp_kind == "plain":
+            lw.w_gate_up, lw.b_up = dev(get(p + mlp_in + ".weight")), opt(p + mlp_in + ".bias")
+        else:
+            lw.w_gate_up = dev(torch.cat([get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")], 0))
+        lw.w_down, lw.b_down = dev(get(p + mlp_out + ".weight")), opt(p + mlp_out + ".bias")
+        layers.append(lw)
+    if cfg.arch == "gpt_neox":
+        embed, fin, head = "gpt_neox.embed_in.weight", "gpt_neox.final_layer_norm", "embed_out.weight"
+    elif cfg.arch == "phi":
+        embed, fin, head = "model.embed_tokens.weight", "model.final_layernorm", "lm_head.weight"
+    else:
+        embed, fin, head = "model.embed_tokens.weight", "model.norm", "lm_head.weight"
+    e = dev(get(embed))
+    hw = get(head, False)
+    head_d = e if (hw is None or cfg.tie_embeddings) else dev(hw)
+    mult = cfg.ssm.get("logit_mult", 1.0) if cfg.ssm else 1.0
+    if mult != 1.0:                             # Cohere: logits * scale, as a head of its own
+        head_d = dev((get(embed) if (hw is None or cfg.tie_embeddings) else hw).float() * mult)
+    w = DecoderWeights(embed=e, layers=layers, final_norm=dev(get(fin + ".weight")), lm_head=head_d, vocab_start=0,
+                       vocab_local=cfg.vocab_size)
+    w.final_norm_b = opt(fin + ".bias")
+    w.lm_head_b = opt("lm_head.bias")
+    return w

@@ -17,7 +17,7 @@ from typing import Optional, Tuple
 import numpy as np
 import torch
 
-from ..config import ModelConfig
+from ..config import CLASSIC_MODEL_TYPES, ModelConfig
 from ..models.weights import DecoderWeights, LayerWeights, make_shard_spec
 
 
@@ -48,6 +48,12 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
     def dev(t):
         return t.to(device=device, dtype=dtype if t.is_floating_point() and t.element_size() > 1 else t.dtype).contiguous()
 
+    if cfg.arch in CLASSIC_MODEL_TYPES:
+        if tp > 1:
+            raise NotImplementedError(f"{cfg.arch} runs on one rank")
+        from .classic_loader import load_hf_classic
+        tok = directory if os.path.exists(os.path.join(directory, "tokenizer.json")) else None
+        return cfg, load_hf_classic(cfg, get, device, dtype), tok
     if cfg.layer_kinds:
         if tp > 1:
             raise NotImplementedError("recurrent and latent-attention layers are not cut over tensor-parallel ranks")

@@ -94,7 +94,7 @@ class Decoder:
         self.attn_factor = attn
         self.scale = cfg.attn_scale if cfg.attn_scale else cfg.head_dim ** -0.5
         self.rope_style = 0 if cfg.rope_style == "neox" else 1
-        self.act_kind = ACT_KIND[cfg.act]
+        self.act_kind = ACT_KIND.get(cfg.act, 0)
         # packed payloads loaded from a checkpoint become weight objects that pick their own kernel
         for lw in self.w.layers:
             for name, packed in list(lw.packed.items()):
@@ -169,8 +169,18 @@ class Decoder:
         return (self._defer and post_norm is None and (self.tp is None or self.tp.size == 1)
                 and self.first_stage and self.last_stage)
 
+    def _norm(self, x, delta, w, b=None):
+        """The block norm of the family: RMSNorm, or LayerNorm with / without bias; `delta` is added to `x` in place first."""
+        cfg = self.cfg
+        if cfg.norm_kind == "rms":
+            return self.ops.rmsnorm(x, delta, w, cfg.rms_eps, cfg.norm_weight_offset)
+        return self.ops.layernorm(x, delta, w, b, cfg.rms_eps, cfg.norm_weight_offset)
+
     def _ffn_block(self, lw, h: torch.Tensor) -> torch.Tensor:
         cfg, ops = self.cfg, self.ops
+        if cfg.mlp_kind == "plain":               # two matrices and an activation between them
+            u = ops.act_(ops.linear(h, lw.w_gate_up, lw.b_up), cfg.act)
+            return ops.linear(u, lw.w_down, lw.b_down)
         if lw.router_w is not None:
             from .moe import moe_ffn, moe_ffn_alltoall
             if self.ep_a2a is not None:
@@ -209,8 +219,15 @@ class Decoder:
         for li, lw in zip(self.layer_range, self.w.layers):
             if nvtx:
                 torch.cuda.nvtx.range_push(f"layer{li}.attn")
-            h = ops.rmsnorm(x, delta, lw.attn_norm, cfg.rms_eps, cfg.norm_weight_offset)
+            h = self._norm(x, delta, lw.attn_norm, lw.attn_norm_b)
             kind = cfg.layer_kind(li)
+            if cfg.parallel_block:                    # attention and MLP side by side from one read of the residual
+                o = ops.materialize(self._reduce(self._attention_block(li, lw, h, b)))
+                h2 = h if cfg.parallel_norms == 1 else self._norm(x, None, lw.ffn_norm, lw.ffn_norm_b)
+                delta = o + ops.materialize(self._reduce(self._ffn_block(lw, h2)))
+                if nvtx:
+                    torch.cuda.nvtx.range_pop()
+                continue
             if kind == "attention":
                 o = self._reduce(self._attention_block(li, lw, h, b))
             elif kind == "mla":
@@ -229,7 +246,7 @@ class Decoder:
             if nvtx:
                 torch.cuda.nvtx.range_pop()
                 torch.cuda.nvtx.range_push(f"layer{li}.ffn")
-            h = ops.rmsnorm(x, o, lw.ffn_norm, cfg.rms_eps, cfg.norm_weight_offset)
+            h = self._norm(x, o, lw.ffn_norm, lw.ffn_norm_b)
             delta = self._reduce(self._ffn_block(lw, h))
             if lw.post_ffn_norm is not None:
                 delta = ops.rmsnorm(delta, None, lw.post_ffn_norm, cfg.rms_eps, cfg.norm_weight_offset)
@@ -242,7 +259,8 @@ class Decoder:
     def fused_tp(self) -> bool:
         return (self.tp is not None and getattr(self.tp, "backend", "") == "fused" and self.tp.size > 1
                 and not self.cfg.is_moe and not self.cfg.post_norms and self.first_stage and self.last_stage
-                and self._dense_weights and not self.cfg.layer_kinds and not self.cfg.rope_local_theta and self.cfg.rope_layers is None)
+                and self._dense_weights and not self.cfg.layer_kinds and not self.cfg.rope_local_theta and self.cfg.rope_layers is None
+                and self.cfg.norm_kind == "rms" and self.cfg.mlp_kind == "glu" and not self.cfg.parallel_block)
 
     def forward_fused(self, b: StepBatch) -> torch.Tensor:
         """Whole forward with the sequence-sharded residual: every projection output leaves the
@@ -317,14 +335,14 @@ class Decoder:
             from .rwkv import rwkv7_final_norm
             h = rwkv7_final_norm(self, x)
         else:
-            h = ops.rmsnorm(x, delta, self.w.final_norm, cfg.rms_eps, cfg.norm_weight_offset)
+            h = self._norm(x, delta, self.w.final_norm, self.w.final_norm_b)
         if b.all_decode and b.logit_rows.numel() == h.shape[0]:
             hs = h                     # every row is a decode row: no gather needed
         else:
             hs = ops.gather_rows(h, b.logit_rows)
         if self.capture_hidden:
             self.last_hidden = hs                  # [logit rows, hidden]: the embeddings API reads it
-        lg = ops.linear(hs, self.w.lm_head)
+        lg = ops.linear(hs, self.w.lm_head, self.w.lm_head_b)
         if cfg.logit_softcap > 0:
             lg = ops.softcap_(lg, cfg.logit_softcap)
         return lg

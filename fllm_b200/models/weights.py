@@ -47,6 +47,11 @@ class LayerWeights:
     shared_down: Optional[torch.Tensor] = None      # [H, Is]
     shared_gate_w: Optional[torch.Tensor] = None    # [8, H] (row 0 used): sigmoid(h . w) scales the shared experts' output
     w_attn_gate: Optional[torch.Tensor] = None      # [hq*D, H] output gate of the attention (Qwen3-Next)
+    # LayerNorm families: norm biases; plain MLPs keep their first matrix in w_gate_up and carry biases
+    attn_norm_b: Optional[torch.Tensor] = None
+    ffn_norm_b: Optional[torch.Tensor] = None
+    b_up: Optional[torch.Tensor] = None
+    b_down: Optional[torch.Tensor] = None
     # recurrent layers (Mamba, delta rule, short convolution): the mixer's tensors by name; wqkv / wo stay None
     mixer: Optional[Dict[str, torch.Tensor]] = None
     # packed formats keep their payload here (format name -> tensors)
@@ -75,7 +80,8 @@ class DecoderWeights:
     lm_head: torch.Tensor               # [vocab_local(padded), H]
     vocab_start: int = 0
     vocab_local: int = 0
-    final_norm_b: Optional[torch.Tensor] = None      # families whose blocks are LayerNorms (RWKV)
+    final_norm_b: Optional[torch.Tensor] = None      # families whose blocks are LayerNorms (RWKV, GPT-NeoX, Phi, ...)
+    lm_head_b: Optional[torch.Tensor] = None         # Phi
 
     def nbytes(self) -> int:
         n = 0

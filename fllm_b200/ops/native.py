@@ -158,6 +158,21 @@ class NativeOps(RecurrentNative):
         self.launches += 1
         return out
 
+    def layernorm(self, residual, delta, w, b, eps, w_offset=0.0):
+        """LayerNorm(residual (+= delta)) * (w + w_offset) + b in one kernel."""
+        delta = self.materialize(delta) if delta is not None else None
+        out = torch.empty_like(residual)
+        self.k.add_layernorm(residual, delta, w, b, out, float(eps), float(w_offset))
+        self.launches += 1
+        return out
+
+    ACTS = {"gelu": 0, "gelu_tanh": 1, "relu2": 2, "silu": 3, "relu": 4}
+
+    def act_(self, x, kind: str):
+        self.k.act_(x, self.ACTS[kind])
+        self.launches += 1
+        return x
+
     def softcap_(self, x, cap: float):
         """x = cap * tanh(x / cap) in place (final-logit soft-cap)."""
         self.k.softcap_(x, float(cap))

@@ -145,6 +145,25 @@ class RefOps(RecurrentRef):
             out[t] = torch.einsum("hn,hnd->hd", p, v).reshape(-1).to(q.dtype)
         return out
 
+    def materialize(self, y):
+        return y
+
+    def layernorm(self, residual, delta, w, b, eps, w_offset=0.0):
+        """Returns LayerNorm(residual) * (w + w_offset) + b; when delta is given, residual += delta in place first."""
+        if delta is not None:
+            residual.copy_((residual.float() + delta.float()).to(residual.dtype))
+        x = residual.float()
+        y = F.layer_norm(x, (x.shape[-1],), w.float() + w_offset, b.float() if b is not None else None, eps)
+        return y.to(residual.dtype)
+
+    def act_(self, x, kind: str):
+        """Activation of a plain MLP, in place: gelu | gelu_tanh | relu2 | silu | relu."""
+        xf = x.float()
+        y = {"gelu": F.gelu, "gelu_tanh": lambda t: F.gelu(t, approximate="tanh"), "relu2": lambda t: F.relu(t).square(),
+             "silu": F.silu, "relu": F.relu}[kind](xf)
+        x.copy_(y.to(x.dtype))
+        return x
+
     def softcap_(self, x, cap: float):
         x.copy_((cap * torch.tanh(x.float() / cap)).to(x.dtype))
         return x

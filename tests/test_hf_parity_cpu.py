@@ -54,6 +54,21 @@ def _model(kind):
         return tf.MinistralForCausalLM(tf.MinistralConfig(**BASE, head_dim=16, pad_token_id=0, sliding_window=24))
     if kind == "smollm3":
         return tf.SmolLM3ForCausalLM(tf.SmolLM3Config(**BASE, pad_token_id=0, no_rope_layers=[1, 0]))
+    if kind == "starcoder2":
+        return tf.Starcoder2ForCausalLM(tf.Starcoder2Config(**BASE, sliding_window=24))
+    if kind == "stablelm":
+        return tf.StableLmForCausalLM(tf.StableLmConfig(**BASE, use_qkv_bias=True))
+    if kind == "nemotron":
+        return tf.NemotronForCausalLM(tf.NemotronConfig(**BASE, head_dim=16))
+    if kind == "arcee":
+        return tf.ArceeForCausalLM(tf.ArceeConfig(**BASE, head_dim=16))
+    if kind == "phi":
+        return tf.PhiForCausalLM(tf.PhiConfig(**BASE))
+    if kind == "gpt_neox":
+        neox = {k: v for k, v in BASE.items() if k != "num_key_value_heads"}
+        return tf.GPTNeoXForCausalLM(tf.GPTNeoXConfig(**neox))
+    if kind == "cohere":
+        return tf.CohereForCausalLM(tf.CohereConfig(**BASE, pad_token_id=0, logit_scale=0.25))
     if kind == "phi3":
         return tf.Phi3ForCausalLM(tf.Phi3Config(**BASE, pad_token_id=0))
     if kind == "mixtral":
@@ -68,7 +83,7 @@ def _model(kind):
 
 
 @pytest.mark.parametrize("kind", ["llama", "llama3_rope", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "granite", "seed_oss", "ernie4_5", "glm", "helium",
-                                  "ministral", "smollm3", "phi3", "mixtral", "qwen3_moe",
+                                  "ministral", "smollm3", "starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "phi3", "mixtral", "qwen3_moe",
                                   "qwen2_moe"])
 def test_attention_families_match_transformers(tmp_path, kind):
     from fllm_b200.formats.loader import load_hf_checkpoint
@@ -77,9 +92,11 @@ def test_attention_families_match_transformers(tmp_path, kind):
         for n, p in m.named_parameters():
             if "norm" in n:
                 p.add_(0.3 * torch.randn_like(p))
+            if n.endswith(".bias") and "norm" not in n:
+                p.add_(0.05 * torch.randn_like(p))            # biases start at zero: make them count
             if n.endswith(("mlp.gate.weight", "block_sparse_moe.gate.weight")):
                 p.mul_(20.0)                                  # clear routing decisions
-            if n.endswith(("q_proj.weight", "k_proj.weight", "qkv_proj.weight")):
+            if n.endswith(("q_proj.weight", "k_proj.weight", "qkv_proj.weight", "query_key_value.weight")):
                 p.mul_(12.0)                                  # peaked attention: a wrong rotation or mask moves the logits
     d = str(tmp_path / kind)
     m.save_pretrained(d, safe_serialization=True)
@@ -100,4 +117,4 @@ def test_unknown_families_are_refused():
     """A model type without a mapping must not run as if it were a Llama."""
     from fllm_b200.config import ModelConfig
     with pytest.raises(ValueError, match="not among the families"):
-        ModelConfig.from_hf_config(dict(model_type="stablelm", vocab_size=10, hidden_size=8, num_hidden_layers=1, num_attention_heads=1))
+        ModelConfig.from_hf_config(dict(model_type="olmo2", vocab_size=10, hidden_size=8, num_hidden_layers=1, num_attention_heads=1))

@@ -882,3 +882,25 @@ def test_logit_softcap_kernel():
     want = (30.0 * torch.tanh(x.float() / 30.0))
     ops.softcap_(view, 30.0)
     assert (view.float() - want).abs().max().item() <= 0.13          # bf16 steps near +-30
+
+
+@pytest.mark.parametrize("cols,bias,delta", [(256, True, True), (5120, False, True), (770, True, False)])
+def test_add_layernorm_and_activations(cols, bias, delta):
+    from fllm_b200.ops.native import NativeOps
+    from fllm_b200.ops.reference import RefOps
+    nat, ref = NativeOps(torch.device("cuda")), RefOps()
+    g = torch.Generator(device="cuda").manual_seed(cols)
+    x = torch.randn(37, cols, device="cuda", generator=g).bfloat16()
+    d = torch.randn(37, cols, device="cuda", generator=g).bfloat16() if delta else None
+    w = (1 + 0.3 * torch.randn(cols, device="cuda", generator=g)).bfloat16()
+    b = torch.randn(cols, device="cuda", generator=g).bfloat16() if bias else None
+    x1, x2 = x.clone(), x.clone()
+    y1 = nat.layernorm(x1, d, w, b, 1e-5, 1.0)
+    y2 = ref.layernorm(x2, d, w, b, 1e-5, 1.0)
+    assert torch.equal(x1, x2)                                          # the residual update is the same bf16 sum
+    assert (y1.float() - y2.float()).abs().max().item() <= 0.05
+    for kind in ("gelu", "gelu_tanh", "relu2", "silu", "relu"):
+        a = (torch.randn(9, cols, device="cuda", generator=g) * 2).bfloat16()
+        want = ref.act_(a.clone(), kind)
+        got = nat.act_(a.clone(), kind)
+        assert (got.float() - want.float()).abs().max().item() <= 0.04 * max(1.0, want.float().abs().max().item())
