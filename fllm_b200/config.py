@@ -171,6 +171,9 @@ class ModelConfig:
         if mt == "gemma3" and isinstance(hf.get("text_config"), dict):     # the multimodal wrapper: its language model
             hf = dict(hf["text_config"], model_type="gemma3_text")
             mt = "gemma3_text"
+        if mt in ("qwen3_5", "qwen3_5_moe") and isinstance(hf.get("text_config"), dict):
+            hf = dict(hf["text_config"])
+            mt = hf.setdefault("model_type", mt + "_text")
         rp = hf.get("rope_parameters") or {}
         rp_local = None
         if isinstance(rp.get("full_attention"), dict):                     # per layer type: global layers / windowed layers
@@ -384,7 +387,7 @@ def mla_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     return cfg
 
 
-RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "jamba", "granitemoehybrid", "rwkv6")
+RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "jamba", "granitemoehybrid", "rwkv6")
 
 
 def _limit(v, default: float) -> float:
@@ -461,11 +464,11 @@ def recurrent_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
                             n_groups=hf.get("mamba_n_groups", 1), head_dim=P, n_heads=H, norm_groups=1,
                             conv_bias=hf.get("mamba_conv_bias", True), proj_bias=hf.get("mamba_proj_bias", False),
                             dt_min=_limit(lim[0], 0.0), dt_max=_limit(lim[1], 1e30)))
-    if mt == "qwen3_next":
+    if mt in ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text"):
         kinds = hf.get("layer_types") or ["linear_attention" if (i + 1) % 4 else "full_attention" for i in range(L)]
         E, step, dense = hf.get("num_experts", 0), hf.get("decoder_sparse_step", 1) or 1, set(hf.get("mlp_only_layers") or [])
         rot = int(head_dim * hf.get("partial_rotary_factor", 0.25))
-        return cls(**base, intermediate_size=hf["intermediate_size"], rms_eps=hf.get("rms_norm_eps", 1e-6),
+        return cls(**base, intermediate_size=hf.get("intermediate_size") or hf.get("moe_intermediate_size", 0), rms_eps=hf.get("rms_norm_eps", 1e-6),
                    tie_embeddings=hf.get("tie_word_embeddings", False), qk_norm=True, norm_weight_offset=1.0,
                    attn_out_gate=True, rotary_dim=rot if rot != head_dim else None,
                    layer_kinds=["attention" if k == "full_attention" else "gated_delta" for k in kinds],

@@ -36,6 +36,8 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
     s = cfg.ssm
     layers = []
     mt = cfg.arch
+    # language model inside a multimodal wrapper: model.language_model.*
+    root = "model.language_model." if get("model.language_model.embed_tokens.weight", False) is not None else "model."
     for l in range(cfg.num_layers):
         kind = cfg.layer_kind(l)
         if mt in ("mamba", "falcon_mamba", "mamba2"):
@@ -134,9 +136,9 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
                     lw.exp_down = dev(torch.stack([get(mp + f"experts.{e}.down_proj.weight") for e in range(E)]))
             else:
                 glu(lw, p + "feed_forward.", "gate_proj", "up_proj", "down_proj")
-        elif mt == "qwen3_next":
+        elif mt in ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text"):
             from ..models.recurrent import pack_gated_delta
-            p = f"model.layers.{l}."
+            p = f"{root}layers.{l}."
             lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
                               ffn_norm=dev(get(p + "post_attention_layernorm.weight")))
             if kind == "attention":
@@ -152,13 +154,17 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
                 Hk, Hv, Dk, Dv = s["num_k_heads"], s["num_v_heads"], s["head_k_dim"], s["head_v_dim"]
                 r = Hv // Hk
                 Hd = cfg.hidden_size
-                qkvz = get(m + "in_proj_qkvz.weight").view(Hk, 2 * Dk + 2 * r * Dv, Hd)      # per key head: q | k | v | z
-                ba = get(m + "in_proj_ba.weight").view(Hk, 2 * r, Hd)
-                lw.mixer = pack_gated_delta(qkvz[:, :Dk].reshape(-1, Hd), qkvz[:, Dk:2 * Dk].reshape(-1, Hd),
-                                            qkvz[:, 2 * Dk:2 * Dk + r * Dv].reshape(-1, Hd), qkvz[:, 2 * Dk + r * Dv:].reshape(-1, Hd),
-                                            ba[:, :r].reshape(-1, Hd), ba[:, r:].reshape(-1, Hd), get(m + "conv1d.weight"),
-                                            get(m + "dt_bias"), get(m + "A_log"), get(m + "norm.weight"), get(m + "out_proj.weight"),
-                                            dtype, device)
+                if get(m + "in_proj_qkv.weight", False) is not None:      # Qwen3.5: q | k | v rows in order, z / beta / a apart
+                    qkv_w = get(m + "in_proj_qkv.weight")
+                    parts = (qkv_w[:Hk * Dk], qkv_w[Hk * Dk:2 * Hk * Dk], qkv_w[2 * Hk * Dk:], get(m + "in_proj_z.weight"),
+                             get(m + "in_proj_b.weight"), get(m + "in_proj_a.weight"))
+                else:                                                      # Qwen3-Next: rows grouped per key head
+                    qkvz = get(m + "in_proj_qkvz.weight").view(Hk, 2 * Dk + 2 * r * Dv, Hd)      # q | k | v | z
+                    ba = get(m + "in_proj_ba.weight").view(Hk, 2 * r, Hd)
+                    parts = (qkvz[:, :Dk].reshape(-1, Hd), qkvz[:, Dk:2 * Dk].reshape(-1, Hd), qkvz[:, 2 * Dk:2 * Dk + r * Dv].reshape(-1, Hd),
+                             qkvz[:, 2 * Dk + r * Dv:].reshape(-1, Hd), ba[:, :r].reshape(-1, Hd), ba[:, r:].reshape(-1, Hd))
+                lw.mixer = pack_gated_delta(*parts, get(m + "conv1d.weight"), get(m + "dt_bias"), get(m + "A_log"), get(m + "norm.weight"),
+                                            get(m + "out_proj.weight"), dtype, device)
             if cfg.ffn_kind(l) == "moe":
                 mp = p + "mlp."
                 lw.router_w = dev(get(mp + "gate.weight"))
@@ -214,7 +220,9 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
         embed, final = get("backbone.embeddings.weight"), get("backbone.norm_f.weight")
     elif mt in ("bamba", "jamba"):
         embed, final = get("model.embed_tokens.weight"), get("model.final_layernorm.weight")
-    elif mt in ("deepseek_v2", "deepseek_v3", "qwen3_next", "granitemoehybrid"):
+    elif mt in ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text"):
+        embed, final = get(root + "embed_tokens.weight"), get(root + "norm.weight")
+    elif mt in ("deepseek_v2", "deepseek_v3", "granitemoehybrid"):
         embed, final = get("model.embed_tokens.weight"), get("model.norm.weight")
     else:
         embed, final = get("model.embed_tokens.weight"), get("model.embedding_norm.weight")

@@ -112,7 +112,8 @@ class Decoder:
         self._dense_weights = all(isinstance(getattr(lw, n, None), torch.Tensor) for lw in self.w.layers
                                   for n in ("wqkv", "wo", "w_gate_up", "w_down") if getattr(lw, n, None) is not None)
         # split-K reductions of the projections are left to the kernel that consumes them (norm / rope)
-        self._defer = hasattr(ops, "k") and dev.type == "cuda"
+        # (only the RMSNorm, rope and gated-activation kernels take partials: LayerNorm families and parallel blocks do not defer)
+        self._defer = hasattr(ops, "k") and dev.type == "cuda" and cfg.norm_kind == "rms" and not cfg.parallel_block
         if self._defer:
             self._block_gate_up()
 

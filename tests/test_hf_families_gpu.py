@@ -1,0 +1,65 @@
+"""Model families from random `transformers` checkpoints on the GPU: the sm_100a operators against the PyTorch operators on
+the same bf16 weights (teacher-forced logits over chunked prefill)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+transformers = pytest.importorskip("transformers")
+
+BASE = dict(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+            max_position_embeddings=512)
+
+
+def _model(kind):
+    import transformers as tf
+    torch.manual_seed(0)
+    if kind == "phi":
+        return tf.PhiForCausalLM(tf.PhiConfig(**BASE))
+    if kind == "gpt_neox":
+        return tf.GPTNeoXForCausalLM(tf.GPTNeoXConfig(**{k: v for k, v in BASE.items() if k != "num_key_value_heads"}))
+    if kind == "nemotron":
+        return tf.NemotronForCausalLM(tf.NemotronConfig(**BASE, head_dim=64))
+    if kind == "starcoder2":
+        return tf.Starcoder2ForCausalLM(tf.Starcoder2Config(**BASE, sliding_window=48))
+    if kind == "cohere":
+        return tf.CohereForCausalLM(tf.CohereConfig(**BASE, pad_token_id=0, logit_scale=0.25))
+    if kind == "glm":
+        return tf.GlmForCausalLM(tf.GlmConfig(**BASE, head_dim=64, pad_token_id=0))
+    if kind == "gemma3":
+        return tf.Gemma3ForCausalLM(tf.Gemma3TextConfig(**BASE, head_dim=64, sliding_window=48, query_pre_attn_scalar=64,
+                                                        layer_types=["sliding_attention", "full_attention"]))
+    if kind == "qwen2_moe":
+        return tf.Qwen2MoeForCausalLM(tf.Qwen2MoeConfig(**BASE, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=128,
+                                                         shared_expert_intermediate_size=256, norm_topk_prob=False))
+    if kind == "jamba":
+        return tf.JambaForCausalLM(tf.JambaConfig(**BASE, num_experts=4, num_experts_per_tok=2, expert_layer_period=2, expert_layer_offset=1,
+                                                  attn_layer_period=2, attn_layer_offset=1, mamba_d_state=16, mamba_d_conv=4, mamba_expand=2,
+                                                  mamba_dt_rank=16, use_mamba_kernels=False))
+    if kind == "qwen3_next":
+        return tf.Qwen3NextForCausalLM(tf.Qwen3NextConfig(**BASE, head_dim=64, linear_conv_kernel_dim=4, linear_key_head_dim=64,
+                                                           linear_value_head_dim=64, linear_num_key_heads=2, linear_num_value_heads=4,
+                                                           moe_intermediate_size=128, shared_expert_intermediate_size=128,
+                                                           num_experts_per_tok=2, num_experts=4, layer_types=["linear_attention", "full_attention"]))
+    raise ValueError(kind)
+
+
+@pytest.mark.parametrize("kind", ["phi", "gpt_neox", "nemotron", "starcoder2", "cohere", "glm", "gemma3", "qwen2_moe", "jamba", "qwen3_next"])
+def test_native_operators_match_reference_operators(tmp_path, kind):
+    from fllm_b200.config import EngineConfig
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    from fllm_b200.ops.reference import RefOps
+    from fllm_b200.runtime.engine import LLMEngine
+    m = _model(kind).eval()
+    d = str(tmp_path / kind)
+    m.save_pretrained(d, safe_serialization=True)
+    cfg, w, _ = load_hf_checkpoint(d, device="cuda:0")
+    ec = EngineConfig(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=512, num_kv_blocks=128, block_size=16)
+    nat = LLMEngine(cfg, ec, device="cuda:0", weights=w)
+    assert type(nat.ops).__name__ == "NativeOps"
+    ref = LLMEngine(cfg, ec, device="cuda:0", weights=w, ops=RefOps())
+    toks = torch.randint(0, 512, (150,), generator=torch.Generator().manual_seed(3)).tolist()
+    a, b = nat.token_logits(toks), ref.token_logits(toks)
+    err = (a - b).norm(dim=1) / b.norm(dim=1)
+    routed = kind in ("qwen2_moe", "jamba", "qwen3_next")
+    assert float(err.median()) < 3e-2 and int((err > 0.15).sum()) <= (3 if routed else 0), err
+    assert int(nat.ops.status.item()) == 0

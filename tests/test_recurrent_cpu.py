@@ -491,3 +491,41 @@ def test_rwkv6_matches_token_by_token_recurrence(tmp_path):
     got = eng.token_logits(toks)
     want = _rwkv6_oracle(sd, cfg, toks)
     assert float((got - want).abs().max()) < 1e-3 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_qwen3_5_text_matches_transformers(tmp_path, moe):
+    """Qwen3.5 (text): the Qwen3-Next layer kinds with the delta-rule projections stored apart (q | k | v, z, beta, a), dense
+    or routed feed-forward layers."""
+    import transformers as tf
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    torch.manual_seed(0)
+    common = dict(vocab_size=300, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                  linear_conv_kernel_dim=4, linear_key_head_dim=32, linear_value_head_dim=32, linear_num_key_heads=2, linear_num_value_heads=4,
+                  max_position_embeddings=256, pad_token_id=0)
+    if moe:
+        m = tf.Qwen3_5MoeForCausalLM(tf.Qwen3_5MoeTextConfig(**common, moe_intermediate_size=32, shared_expert_intermediate_size=48,
+                                                             num_experts_per_tok=2, num_experts=8))
+    else:
+        m = tf.Qwen3_5ForCausalLM(tf.Qwen3_5TextConfig(**common, intermediate_size=128))
+    m = m.eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if n.endswith(("q_proj.weight", "k_proj.weight")):
+                p.mul_(12.0)
+            if "norm" in n or n.endswith("dt_bias"):
+                p.add_(0.3 * torch.randn_like(p))
+            if n.endswith("mlp.gate.weight"):
+                p.mul_(20.0)
+    d = str(tmp_path / "q35")
+    m.save_pretrained(d, safe_serialization=True)
+    cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
+    assert cfg.layer_kinds == ["gated_delta"] * 3 + ["attention"] and cfg.ffn_kinds == (["moe"] * 4 if moe else ["glu"] * 4)
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16,
+                                      kv_cache_dtype="fp32"), device="cpu", weights=w)
+    toks = torch.randint(0, 300, (45,), generator=torch.Generator().manual_seed(1)).tolist()
+    got = eng.token_logits(toks)
+    with torch.no_grad():
+        want = m(torch.tensor([toks])).logits[0].float()
+    err = (got - want).abs().max(dim=1).values / float(want.abs().max())
+    assert float(err.median()) < (1e-2 if moe else 2e-3) and int((err > (5e-2 if moe else 1e-2)).sum()) <= (2 if moe else 0), err
