@@ -79,7 +79,8 @@ class ModelConfig:
     # block variants of the pre-Llama families: LayerNorm (with or without bias) instead of RMSNorm, a plain two-matrix MLP
     # (activation in `act`: gelu | gelu_tanh | relu2 | silu | relu) instead of the gated one, attention and MLP side by side
     # from one residual read (with one shared norm or one norm each), biases on the MLP and the head
-    norm_kind: str = "rms"               # rms | layernorm | layernorm_nobias
+    norm_kind: str = "rms"               # rms | layernorm | layernorm_nobias | none (OLMo-2: only the block outputs are normalised)
+    qk_norm_full: bool = False           # RMSNorm over the whole q and the whole k projection (all heads at once, OLMo-2)
     mlp_kind: str = "glu"                # glu | plain
     parallel_block: bool = False
     parallel_norms: int = 1              # parallel blocks: 1 = attention and MLP read the same normed input, 2 = a norm each
@@ -287,7 +288,7 @@ ATTENTION_MODEL_TYPES = ("llama", "mistral", "ministral", "qwen2", "qwen3", "qwe
                          "gemma3_text", "phi3", "gpt_oss", "granite", "seed_oss", "glm", "ernie4_5", "helium", "smollm3")
 
 
-CLASSIC_MODEL_TYPES = ("starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere")
+CLASSIC_MODEL_TYPES = ("starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "olmo2", "olmo3")
 _ACT_NAMES = {"gelu": "gelu", "gelu_new": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh", "gelu_fast": "gelu_tanh", "relu2": "relu2",
               "silu": "silu", "swish": "silu", "relu": "relu"}
 
@@ -331,6 +332,13 @@ def classic_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
         cfg.norm_kind, cfg.mlp_kind, cfg.act, cfg.rms_eps = "layernorm", "plain", act, hf.get("layer_norm_eps", 1e-5)
         cfg.parallel_block, cfg.parallel_norms = bool(hf.get("use_parallel_residual", True)), 2
         cfg.attn_bias, cfg.mlp_bias = bool(hf.get("attention_bias", True)), True
+    elif mt in ("olmo2", "olmo3"):        # no norm in front of a block: its output is normalised instead; q and k normalised over all heads
+        cfg.norm_kind, cfg.post_norms, cfg.qk_norm_full, cfg.rms_eps = "none", True, True, hf.get("rms_norm_eps", 1e-6)
+        cfg.attn_bias = bool(hf.get("attention_bias", False))
+        lt = hf.get("layer_types")
+        if mt == "olmo3" and hf.get("sliding_window") and lt:
+            cfg.sliding_window = int(hf["sliding_window"])
+            cfg.window_pattern = [1 if t == "sliding_attention" else 0 for t in lt]
     elif mt == "cohere":
         if hf.get("use_qk_norm"):
             raise NotImplementedError("cohere with QK norm is not supported")

@@ -26,6 +26,8 @@ _NAMES = {
     "gpt_neox": ("gpt_neox.layers.{}.", "attention.", "query_key_value", "dense", "input_layernorm", "post_attention_layernorm",
                  "mlp.dense_h_to_4h", "mlp.dense_4h_to_h"),
     "cohere": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", "input_layernorm", None, None, "mlp.down_proj"),
+    "olmo2": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", None, None, None, "mlp.down_proj"),
+    "olmo3": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", None, None, None, "mlp.down_proj"),
 }
 
 
@@ -43,9 +45,14 @@ def load_hf_classic(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
     layers = []
     for l in range(cfg.num_layers):
         p = lp.format(l)
-        lw = LayerWeights(attn_norm=dev(get(p + n1 + ".weight")), wqkv=None, wo=None,
+        lw = LayerWeights(attn_norm=dev(get(p + n1 + ".weight")) if n1 else None, wqkv=None, wo=None,
                           ffn_norm=dev(get(p + n2 + ".weight")) if n2 else None)
-        lw.attn_norm_b, lw.ffn_norm_b = opt(p + n1 + ".bias"), opt(p + n2 + ".bias") if n2 else None
+        lw.attn_norm_b, lw.ffn_norm_b = opt(p + n1 + ".bias") if n1 else None, opt(p + n2 + ".bias") if n2 else None
+        if cfg.post_norms:                      # OLMo-2: the norms sit behind the blocks
+            lw.post_attn_norm = dev(get(p + "post_attention_layernorm.weight"))
+            lw.post_ffn_norm = dev(get(p + "post_feedforward_layernorm.weight"))
+        if cfg.qk_norm_full:
+            lw.q_norm_full, lw.k_norm_full = dev(get(p + ap + "q_norm.weight")), dev(get(p + ap + "k_norm.weight"))
         if isinstance(qkv, tuple):
             lw.wqkv = dev(torch.cat([get(p + ap + n + ".weight") for n in qkv], 0))
             bs = [get(p + ap + n + ".bias", False) for n in qkv]

@@ -113,7 +113,8 @@ class Decoder:
                                   for n in ("wqkv", "wo", "w_gate_up", "w_down") if getattr(lw, n, None) is not None)
         # split-K reductions of the projections are left to the kernel that consumes them (norm / rope)
         # (only the RMSNorm, rope and gated-activation kernels take partials: LayerNorm families and parallel blocks do not defer)
-        self._defer = hasattr(ops, "k") and dev.type == "cuda" and cfg.norm_kind == "rms" and not cfg.parallel_block
+        self._defer = (hasattr(ops, "k") and dev.type == "cuda" and cfg.norm_kind == "rms" and not cfg.parallel_block
+                       and not cfg.qk_norm_full)
         if self._defer:
             self._block_gate_up()
 
@@ -146,6 +147,10 @@ class Decoder:
         cfg, sp, ops = self.cfg, self.spec, self.ops
         gated = lw.w_attn_gate is not None
         qkv = ops.linear(h, lw.wqkv, lw.bqkv, defer=self._defer and not gated)
+        if lw.q_norm_full is not None:             # RMSNorm over all heads of q and of k at once, before the rotation
+            nq, nk = sp.hq_local * cfg.head_dim, sp.hkv_local * cfg.head_dim
+            qkv[:, :nq] = ops.rmsnorm(qkv[:, :nq].contiguous(), None, lw.q_norm_full, cfg.rms_eps, 0.0)
+            qkv[:, nq:nq + nk] = ops.rmsnorm(qkv[:, nq:nq + nk].contiguous(), None, lw.k_norm_full, cfg.rms_eps, 0.0)
         local = self.kv_index[li]
         kc, vc = self.kv.k(local), self.kv.v(local)
         local_rope = self.inv_freq_local is not None and cfg.layer_window(li) > 0
@@ -173,8 +178,12 @@ class Decoder:
     def _norm(self, x, delta, w, b=None):
         """The block norm of the family: RMSNorm, or LayerNorm with / without bias; `delta` is added to `x` in place first."""
         cfg = self.cfg
-        if cfg.norm_kind == "rms":
+        if cfg.norm_kind == "rms" or (cfg.norm_kind == "none" and w is not None):     # (the final norm of a "none" family is an RMSNorm)
             return self.ops.rmsnorm(x, delta, w, cfg.rms_eps, cfg.norm_weight_offset)
+        if cfg.norm_kind == "none":                # the block reads the residual stream as it is
+            if delta is not None:
+                x.add_(self.ops.materialize(delta))
+            return x
         return self.ops.layernorm(x, delta, w, b, cfg.rms_eps, cfg.norm_weight_offset)
 
     def _ffn_block(self, lw, h: torch.Tensor) -> torch.Tensor:
@@ -237,7 +246,7 @@ class Decoder:
             else:
                 from .recurrent import MIXERS
                 o = MIXERS[kind](self, li, lw, h, b)
-            if lw.ffn_norm is None:                    # a mixer-only layer (Mamba): its output is the residual delta
+            if cfg.ffn_kind(li) == "none":            # a mixer-only layer (Mamba): its output is the residual delta
                 delta = o
                 if nvtx:
                     torch.cuda.nvtx.range_pop()

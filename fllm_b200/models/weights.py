@@ -51,6 +51,8 @@ class LayerWeights:
     attn_norm_b: Optional[torch.Tensor] = None
     ffn_norm_b: Optional[torch.Tensor] = None
     b_up: Optional[torch.Tensor] = None
+    q_norm_full: Optional[torch.Tensor] = None      # [hq*D] / [hkv*D]: norms over the whole projections (OLMo-2)
+    k_norm_full: Optional[torch.Tensor] = None
     b_down: Optional[torch.Tensor] = None
     # recurrent layers (Mamba, delta rule, short convolution): the mixer's tensors by name; wqkv / wo stay None
     mixer: Optional[Dict[str, torch.Tensor]] = None

@@ -69,6 +69,10 @@ def _model(kind):
         return tf.GPTNeoXForCausalLM(tf.GPTNeoXConfig(**neox))
     if kind == "cohere":
         return tf.CohereForCausalLM(tf.CohereConfig(**BASE, pad_token_id=0, logit_scale=0.25))
+    if kind == "olmo2":
+        return tf.Olmo2ForCausalLM(tf.Olmo2Config(**BASE, pad_token_id=0))
+    if kind == "olmo3":
+        return tf.Olmo3ForCausalLM(tf.Olmo3Config(**BASE, pad_token_id=0, sliding_window=24, layer_types=["sliding_attention", "full_attention"]))
     if kind == "phi3":
         return tf.Phi3ForCausalLM(tf.Phi3Config(**BASE, pad_token_id=0))
     if kind == "mixtral":
@@ -83,7 +87,7 @@ def _model(kind):
 
 
 @pytest.mark.parametrize("kind", ["llama", "llama3_rope", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "granite", "seed_oss", "ernie4_5", "glm", "helium",
-                                  "ministral", "smollm3", "starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "phi3", "mixtral", "qwen3_moe",
+                                  "ministral", "smollm3", "starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "olmo2", "olmo3", "phi3", "mixtral", "qwen3_moe",
                                   "qwen2_moe"])
 def test_attention_families_match_transformers(tmp_path, kind):
     from fllm_b200.formats.loader import load_hf_checkpoint
@@ -117,4 +121,4 @@ def test_unknown_families_are_refused():
     """A model type without a mapping must not run as if it were a Llama."""
     from fllm_b200.config import ModelConfig
     with pytest.raises(ValueError, match="not among the families"):
-        ModelConfig.from_hf_config(dict(model_type="olmo2", vocab_size=10, hidden_size=8, num_hidden_layers=1, num_attention_heads=1))
+        ModelConfig.from_hf_config(dict(model_type="bloom", vocab_size=10, hidden_size=8, num_hidden_layers=1, num_attention_heads=1))
