@@ -261,9 +261,11 @@ class ModelConfig:
                 cfg.sliding_window = int(hf["sliding_window"])
                 lt = hf.get("layer_types")
                 cfg.window_pattern = [1 if t == "sliding_attention" else 0 for t in lt] if lt else [1, 0]
-        if mt in ("glm", "ernie4_5", "helium"):       # these rotate neighbouring pairs (x[2i], x[2i+1])
+        if mt in ("glm", "glm4", "ernie4_5", "helium"):       # these rotate neighbouring pairs (x[2i], x[2i+1])
             cfg.rope_style = "pair"
-        if mt == "glm":
+        if mt == "glm4":                      # GLM-4-0414: the attention and MLP outputs are normalised too
+            cfg.post_norms = True
+        if mt in ("glm", "glm4"):
             cfg.rotary_dim = int(cfg.head_dim * hf.get("partial_rotary_factor", 0.5)) or None
             cfg.attn_bias = hf.get("attention_bias", True)
         if mt == "smollm3" and hf.get("no_rope_layers"):          # 1 = the layer rotates, 0 = no position signal in that layer
@@ -285,7 +287,7 @@ class ModelConfig:
 # decoder families whose layers are attention + gated FFN (or routed experts) and that the generic mapping covers; every one
 # of them is checked against `transformers` in tests/test_hf_parity_cpu.py
 ATTENTION_MODEL_TYPES = ("llama", "mistral", "ministral", "qwen2", "qwen3", "qwen2_moe", "qwen3_moe", "mixtral", "gemma", "gemma2",
-                         "gemma3_text", "phi3", "gpt_oss", "granite", "seed_oss", "glm", "ernie4_5", "helium", "smollm3")
+                         "gemma3_text", "phi3", "gpt_oss", "granite", "seed_oss", "glm", "glm4", "ernie4_5", "helium", "smollm3")
 
 
 CLASSIC_MODEL_TYPES = ("starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "olmo2", "olmo3")

@@ -126,7 +126,12 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
             f = lin(p + "self_attn.qkv_proj")
             q, k, v = rows(f, slice(0, nq)), rows(f, slice(nq, nq + nk)), rows(f, slice(nq + nk, nq + 2 * nk))
         fp8 = isinstance(q, torch.Tensor) and q.dtype == torch.float8_e4m3fn
-        if cfg.post_norms:                     # Gemma-2: post_attention_layernorm normalises the attention OUTPUT
+        if cfg.post_norms and has(p + "self_attn.q_proj") and (p + "post_self_attn_layernorm.weight") in ck:      # GLM-4
+            lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
+                              ffn_norm=dev(get(p + "post_attention_layernorm.weight")),
+                              post_attn_norm=dev(get(p + "post_self_attn_layernorm.weight")),
+                              post_ffn_norm=dev(get(p + "post_mlp_layernorm.weight")))
+        elif cfg.post_norms:                   # Gemma-2: post_attention_layernorm normalises the attention OUTPUT
             lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
                               ffn_norm=dev(get(p + "pre_feedforward_layernorm.weight")),
                               post_attn_norm=dev(get(p + "post_attention_layernorm.weight")),

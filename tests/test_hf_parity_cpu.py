@@ -48,6 +48,8 @@ def _model(kind):
         return tf.Ernie4_5ForCausalLM(tf.Ernie4_5Config(**BASE, pad_token_id=0))
     if kind == "glm":
         return tf.GlmForCausalLM(tf.GlmConfig(**BASE, head_dim=16, pad_token_id=0))
+    if kind == "glm4":
+        return tf.Glm4ForCausalLM(tf.Glm4Config(**BASE, head_dim=16, pad_token_id=0))
     if kind == "helium":
         return tf.HeliumForCausalLM(tf.HeliumConfig(**BASE, head_dim=16, pad_token_id=0))
     if kind == "ministral":
@@ -86,7 +88,7 @@ def _model(kind):
     raise ValueError(kind)
 
 
-@pytest.mark.parametrize("kind", ["llama", "llama3_rope", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "granite", "seed_oss", "ernie4_5", "glm", "helium",
+@pytest.mark.parametrize("kind", ["llama", "llama3_rope", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "granite", "seed_oss", "ernie4_5", "glm", "glm4", "helium",
                                   "ministral", "smollm3", "starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "olmo2", "olmo3", "phi3", "mixtral", "qwen3_moe",
                                   "qwen2_moe"])
 def test_attention_families_match_transformers(tmp_path, kind):
