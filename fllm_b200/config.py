@@ -101,6 +101,7 @@ class ModelConfig:
     # weight format of the big matrices
     weight_format: str = "bf16"          # bf16 | fp8_block | nvfp4 | mxfp4 | mxfp8 | mxfp4_a8 | nvfp4_a4 | int8_w8a8 | fp8_w8a8 | q4_k | ...
     name: str = "model"
+    arch_alias: str = ""                 # loader family when several model types share one (the Granite MoE variants)
 
     # ---- derived
     @property
@@ -397,7 +398,7 @@ def mla_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     return cfg
 
 
-RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "jamba", "granitemoehybrid", "rwkv6")
+RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "jamba", "granitemoehybrid", "granitemoe", "granitemoeshared", "rwkv6")
 
 
 def _limit(v, default: float) -> float:
@@ -489,15 +490,18 @@ def recurrent_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
                    ssm=dict(num_k_heads=hf.get("linear_num_key_heads", 16), num_v_heads=hf.get("linear_num_value_heads", 32),
                             head_k_dim=hf.get("linear_key_head_dim", 128), head_v_dim=hf.get("linear_value_head_dim", 128),
                             d_conv=hf.get("linear_conv_kernel_dim", 4), norm_eps=hf.get("rms_norm_eps", 1e-6)))
-    if mt == "granitemoehybrid":
+    if mt in ("granitemoehybrid", "granitemoe", "granitemoeshared"):
         H = hf.get("mamba_n_heads", 128)
         P = hf.get("mamba_d_head", "auto")
         P = hf.get("mamba_expand", 2) * hidden // H if P == "auto" else int(P)
         kinds = hf.get("layer_types") or ["mamba"] * L
+        if mt != "granitemoehybrid":          # the attention-only members of the family
+            kinds = ["attention"] * L
+            hf = dict(hf, shared_intermediate_size=hf.get("shared_intermediate_size", 0) if mt == "granitemoeshared" else 0)
         E = hf.get("num_local_experts") or 0
         lim = hf.get("time_step_limit") or (0.0, float("inf"))
         # the residual and logit multipliers are folded into the weights by the loader (residual_mult, logits_div)
-        return cls(**base, intermediate_size=hf.get("shared_intermediate_size", 1024), rms_eps=hf.get("rms_norm_eps", 1e-6),
+        return cls(**base, arch_alias="granitemoehybrid", intermediate_size=hf.get("shared_intermediate_size", 1024), rms_eps=hf.get("rms_norm_eps", 1e-6),
                    tie_embeddings=hf.get("tie_word_embeddings", False), attn_bias=hf.get("attention_bias", False),
                    embed_scale=float(hf.get("embedding_multiplier") or 1.0), attn_scale=float(hf.get("attention_multiplier") or head_dim ** -0.5),
                    use_rope=(hf.get("position_embedding_type") or "rope") == "rope",

@@ -35,7 +35,7 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
 
     s = cfg.ssm
     layers = []
-    mt = cfg.arch
+    mt = cfg.arch_alias or cfg.arch
     # language model inside a multimodal wrapper: model.language_model.*
     root = "model.language_model." if get("model.language_model.embed_tokens.weight", False) is not None else "model."
     for l in range(cfg.num_layers):
@@ -100,13 +100,15 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
                                        get(m + "dt_bias"), get(m + "A_log"), get(m + "D"), get(m + "norm.weight"),
                                        get(m + "out_proj.weight").float() * rm, dtype, device, get(m + "in_proj.bias", False),
                                        ob.float() * rm if ob is not None else None)
-            shared_in, shared_out = get(p + "shared_mlp.input_linear.weight"), get(p + "shared_mlp.output_linear.weight").float() * rm
+            shared_in = get(p + "shared_mlp.input_linear.weight", False)
+            shared_out = get(p + "shared_mlp.output_linear.weight").float() * rm if shared_in is not None else None
             if cfg.ffn_kind(l) == "moe":
                 mp = p + "block_sparse_moe."
                 lw.router_w = dev(get(mp + "router.layer.weight"))
                 lw.exp_gate_up = dev(get(mp + "input_linear.weight"))
                 lw.exp_down = dev(get(mp + "output_linear.weight").float() * rm)
-                lw.shared_gate_up, lw.shared_down = dev(shared_in), dev(shared_out)
+                if shared_in is not None:
+                    lw.shared_gate_up, lw.shared_down = dev(shared_in), dev(shared_out)
             else:
                 lw.w_gate_up, lw.w_down = dev(shared_in), dev(shared_out)
         elif mt == "jamba":

@@ -122,6 +122,24 @@ def _grouped(k_ops, ops, x, w, bias, y, tile_e, tile_r, ntiles, bn):
         k_ops.moe_grouped_linear_w4(x, w.codes, w.scales, w.fmt, w.alpha, bias, y, tile_e, tile_r, ntiles, bn, ops.status)
 
 
+def _router_logits(ops, lw, h: torch.Tensor) -> torch.Tensor:
+    """Router scores [T, E] (a view when the GEMM needs the expert count padded to a multiple of 8, e.g. 60 experts)."""
+    E = lw.router_w.shape[0]
+    if E % 8 == 0:
+        return ops.linear(h, lw.router_w, lw.router_b)
+    pad = getattr(lw, "_router_pad", None)
+    if pad is None:
+        Ep = (E + 7) // 8 * 8
+        wp = torch.zeros(Ep, lw.router_w.shape[1], dtype=lw.router_w.dtype, device=lw.router_w.device)
+        wp[:E] = lw.router_w
+        bp = None
+        if lw.router_b is not None:
+            bp = torch.zeros(Ep, dtype=lw.router_b.dtype, device=lw.router_b.device)
+            bp[:E] = lw.router_b
+        pad = lw._router_pad = (wp, bp)
+    return ops.linear(h, pad[0], pad[1])[:, :E]
+
+
 def moe_ffn(dec, lw, h: torch.Tensor) -> torch.Tensor:
     cfg, ops, sp = dec.cfg, dec.ops, dec.spec
     lo = sp.expert_start if sp.expert_parallel else 0
@@ -131,7 +149,7 @@ def moe_ffn(dec, lw, h: torch.Tensor) -> torch.Tensor:
     T, H = h.shape
     k = cfg.experts_per_token
     e_local = lw.exp_gate_up.shape[0]
-    logits = ops.linear(h, lw.router_w, lw.router_b)
+    logits = _router_logits(ops, lw, h)
     ids = torch.empty(T, k, dtype=torch.int32, device=h.device)
     wts = torch.empty(T, k, dtype=torch.float32, device=h.device)
     if cfg.router_kind in ("deepseek_v2", "deepseek_v3"):
