@@ -398,7 +398,7 @@ def mla_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     return cfg
 
 
-RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "jamba", "granitemoehybrid", "granitemoe", "granitemoeshared", "rwkv6")
+RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "jamba", "granitemoehybrid", "granitemoe", "granitemoeshared", "glm4_moe", "rwkv6")
 
 
 def _limit(v, default: float) -> float:
@@ -490,6 +490,18 @@ def recurrent_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
                    ssm=dict(num_k_heads=hf.get("linear_num_key_heads", 16), num_v_heads=hf.get("linear_num_value_heads", 32),
                             head_k_dim=hf.get("linear_key_head_dim", 128), head_v_dim=hf.get("linear_value_head_dim", 128),
                             d_conv=hf.get("linear_conv_kernel_dim", 4), norm_eps=hf.get("rms_norm_eps", 1e-6)))
+    if mt == "glm4_moe":                  # GLM-4.5: llama-style attention (partial rotary, optional per-head QK-norm) + the DeepSeek-V3 router
+        dense_first, E = hf.get("first_k_dense_replace", 1), hf.get("n_routed_experts", 0)
+        rot = int(head_dim * hf.get("partial_rotary_factor", 0.5))
+        return cls(**base, intermediate_size=hf["intermediate_size"], rms_eps=hf.get("rms_norm_eps", 1e-5),
+                   tie_embeddings=hf.get("tie_word_embeddings", False), attn_bias=hf.get("attention_bias", False),
+                   qk_norm=bool(hf.get("use_qk_norm", False)), rotary_dim=rot if rot != head_dim else None,
+                   layer_kinds=["attention"] * L, ffn_kinds=["moe" if (E and i >= dense_first) else "glu" for i in range(L)],
+                   num_experts=E, experts_per_token=hf.get("num_experts_per_tok", 8), moe_intermediate_size=hf.get("moe_intermediate_size", 1408),
+                   shared_intermediate_size=(hf.get("n_shared_experts") or 0) * hf.get("moe_intermediate_size", 1408),
+                   router_kind="deepseek_v3", router_scale=float(hf.get("routed_scaling_factor", 1.0)),
+                   router_norm_topk=bool(hf.get("norm_topk_prob", True)), router_groups=hf.get("n_group") or 1,
+                   router_topk_groups=hf.get("topk_group") or 1)
     if mt in ("granitemoehybrid", "granitemoe", "granitemoeshared"):
         H = hf.get("mamba_n_heads", 128)
         P = hf.get("mamba_d_head", "auto")

@@ -33,6 +33,24 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
         lw.w_gate_up = dev(torch.cat([get(p + gate + ".weight"), get(p + up + ".weight")], 0))
         lw.w_down = dev(get(p + down + ".weight"))
 
+    def deepseek_moe(lw, mp):
+        """Router (+ selection bias), routed experts (one fused pair of tensors or one module per expert), shared experts."""
+        lw.router_w = dev(get(mp + "gate.weight"))
+        sel = get(mp + "gate.e_score_correction_bias", False)
+        if sel is not None:
+            lw.router_select_b = sel.float().to(device).contiguous()
+        fused = get(mp + "experts.gate_up_proj", False)
+        if fused is not None:
+            lw.exp_gate_up, lw.exp_down = dev(fused), dev(get(mp + "experts.down_proj"))
+        else:
+            E = cfg.num_experts
+            lw.exp_gate_up = dev(torch.stack([torch.cat([get(mp + f"experts.{e}.gate_proj.weight"),
+                                                         get(mp + f"experts.{e}.up_proj.weight")], 0) for e in range(E)]))
+            lw.exp_down = dev(torch.stack([get(mp + f"experts.{e}.down_proj.weight") for e in range(E)]))
+        if cfg.shared_intermediate_size:
+            lw.shared_gate_up = dev(torch.cat([get(mp + "shared_experts.gate_proj.weight"), get(mp + "shared_experts.up_proj.weight")], 0))
+            lw.shared_down = dev(get(mp + "shared_experts.down_proj.weight"))
+
     s = cfg.ssm
     layers = []
     mt = cfg.arch_alias or cfg.arch
@@ -83,6 +101,18 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
                     if t is not None:
                         lw.mixer[name] = t.float().to(device).contiguous() if name == "conv_b" else dev(t)
             glu(lw, p + "feed_forward.", "w1", "w3", "w2")
+        elif mt == "glm4_moe":
+            p = f"model.layers.{l}."
+            lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
+                              ffn_norm=dev(get(p + "post_attention_layernorm.weight")))
+            if cfg.qk_norm:
+                attention(lw, p + "self_attn.", p + "self_attn.q_norm.weight", p + "self_attn.k_norm.weight")
+            else:
+                attention(lw, p + "self_attn.")
+            if cfg.ffn_kind(l) == "moe":
+                deepseek_moe(lw, p + "mlp.")
+            else:
+                glu(lw, p + "mlp.", "gate_proj", "up_proj", "down_proj")
         elif mt == "granitemoehybrid":
             rm = s.get("residual_mult", 1.0)                  # block output * rm: folded into each block's last projection
             p = f"model.layers.{l}."
@@ -196,23 +226,7 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
                                 get(a + "kv_a_proj_with_mqa.weight"), get(a + "kv_a_layernorm.weight"), get(a + "kv_b_proj.weight"),
                                 get(a + "o_proj.weight"), cfg, dtype, device)
             if cfg.ffn_kind(l) == "moe":
-                mp = p + "mlp."
-                lw.router_w = dev(get(mp + "gate.weight"))
-                sel = get(mp + "gate.e_score_correction_bias", False)
-                if sel is not None:
-                    lw.router_select_b = sel.float().to(device).contiguous()
-                fused = get(mp + "experts.gate_up_proj", False)
-                if fused is not None:                                # one [E, 2I, H] and one [E, H, I] tensor
-                    lw.exp_gate_up, lw.exp_down = dev(fused), dev(get(mp + "experts.down_proj"))
-                else:                                                # one module per expert
-                    E = cfg.num_experts
-                    lw.exp_gate_up = dev(torch.stack([torch.cat([get(mp + f"experts.{e}.gate_proj.weight"),
-                                                                 get(mp + f"experts.{e}.up_proj.weight")], 0) for e in range(E)]))
-                    lw.exp_down = dev(torch.stack([get(mp + f"experts.{e}.down_proj.weight") for e in range(E)]))
-                if cfg.shared_intermediate_size:
-                    lw.shared_gate_up = dev(torch.cat([get(mp + "shared_experts.gate_proj.weight"),
-                                                       get(mp + "shared_experts.up_proj.weight")], 0))
-                    lw.shared_down = dev(get(mp + "shared_experts.down_proj.weight"))
+                deepseek_moe(lw, p + "mlp.")
             else:
                 glu(lw, p + "mlp.", "gate_proj", "up_proj", "down_proj")
         else:
@@ -224,7 +238,7 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
         embed, final = get("model.embed_tokens.weight"), get("model.final_layernorm.weight")
     elif mt in ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text"):
         embed, final = get(root + "embed_tokens.weight"), get(root + "norm.weight")
-    elif mt in ("deepseek_v2", "deepseek_v3", "granitemoehybrid"):
+    elif mt in ("deepseek_v2", "deepseek_v3", "granitemoehybrid", "glm4_moe"):
         embed, final = get("model.embed_tokens.weight"), get("model.norm.weight")
     else:
         embed, final = get("model.embed_tokens.weight"), get("model.embedding_norm.weight")

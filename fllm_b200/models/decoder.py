@@ -104,6 +104,15 @@ class Decoder:
                 elif packed[0] in ("nvfp4", "mxfp4"):
                     from ..ops.fp4 import FMT_NAMES, Fp4Weight
                     setattr(lw, name, Fp4Weight(packed[1], packed[2], FMT_NAMES[packed[0]], packed[3] if len(packed) > 3 else 1.0))
+        # the GEMMs take row counts in multiples of 8: a head with an odd vocabulary (added tokens) gets zero rows; the
+        # logits beyond vocab_local are cut off by the consumers
+        head = self.w.lm_head
+        if dev.type == "cuda" and isinstance(head, torch.Tensor) and head.shape[0] % 8 and head.shape[0] > 0:
+            padded = torch.zeros((head.shape[0] + 7) // 8 * 8, head.shape[1], dtype=head.dtype, device=head.device)
+            padded[:head.shape[0]] = head
+            self.w.lm_head = padded
+            if self.w.lm_head_b is not None:
+                self.w.lm_head_b = torch.nn.functional.pad(self.w.lm_head_b, (0, padded.shape[0] - head.shape[0]))
         self.capture_hidden, self.last_hidden = False, None
         # FLLM_NVTX=1: named ranges per layer half for timeline profilers
         self._nvtx = os.environ.get("FLLM_NVTX", "0") not in ("", "0") and dev.type == "cuda"

@@ -23,6 +23,8 @@ def _model(kind):
         return tf.Starcoder2ForCausalLM(tf.Starcoder2Config(**BASE, sliding_window=48))
     if kind == "cohere":
         return tf.CohereForCausalLM(tf.CohereConfig(**BASE, pad_token_id=0, logit_scale=0.25))
+    if kind == "llama_odd_vocab":               # 515 rows in the head: not a multiple of the GEMM's 8
+        return tf.LlamaForCausalLM(tf.LlamaConfig(**dict(BASE, vocab_size=515)))
     if kind == "olmo2":
         return tf.Olmo2ForCausalLM(tf.Olmo2Config(**BASE, pad_token_id=0))
     if kind == "glm":
@@ -45,7 +47,7 @@ def _model(kind):
     raise ValueError(kind)
 
 
-@pytest.mark.parametrize("kind", ["phi", "gpt_neox", "nemotron", "starcoder2", "cohere", "olmo2", "glm", "gemma3", "qwen2_moe", "jamba", "qwen3_next"])
+@pytest.mark.parametrize("kind", ["llama_odd_vocab", "phi", "gpt_neox", "nemotron", "starcoder2", "cohere", "olmo2", "glm", "gemma3", "qwen2_moe", "jamba", "qwen3_next"])
 def test_native_operators_match_reference_operators(tmp_path, kind):
     from fllm_b200.config import EngineConfig
     from fllm_b200.formats.loader import load_hf_checkpoint

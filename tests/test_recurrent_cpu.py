@@ -538,3 +538,42 @@ def test_qwen3_5_text_matches_transformers(tmp_path, moe):
         want = m(torch.tensor([toks])).logits[0].float()
     err = (got - want).abs().max(dim=1).values / float(want.abs().max())
     assert float(err.median()) < (1e-2 if moe else 2e-3) and int((err > (5e-2 if moe else 1e-2)).sum()) <= (2 if moe else 0), err
+
+
+@pytest.mark.parametrize("qk_norm", [False, True])
+def test_glm4_moe_matches_transformers(tmp_path, qk_norm):
+    """GLM-4.5: partial rotary attention with biases (and optional per-head QK-norm), a dense first layer, then routed experts with
+    the sigmoid / selection-bias / group router and a shared expert."""
+    import transformers as tf
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    torch.manual_seed(0)
+    m = tf.Glm4MoeForCausalLM(tf.Glm4MoeConfig(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+                                               num_key_value_heads=2, head_dim=16, attention_bias=True, moe_intermediate_size=32,
+                                               num_experts_per_tok=2, n_shared_experts=1, n_routed_experts=8, routed_scaling_factor=1.5,
+                                               n_group=2, topk_group=1, first_k_dense_replace=1, use_qk_norm=qk_norm,
+                                               max_position_embeddings=256, pad_token_id=0)).eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "norm" in n:
+                p.add_(0.3 * torch.randn_like(p))
+            if n.endswith(("q_proj.weight", "k_proj.weight")):
+                p.mul_(12.0)
+            if n.endswith("gate.weight"):
+                p.mul_(20.0)
+            if n.endswith(".bias") and "norm" not in n:
+                p.add_(0.05 * torch.randn_like(p))
+        for n, b in m.named_buffers():
+            if n.endswith("e_score_correction_bias"):
+                b.copy_(0.2 * torch.randn_like(b))
+    d = str(tmp_path / "glm45")
+    m.save_pretrained(d, safe_serialization=True)
+    cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
+    assert cfg.ffn_kinds == ["glu", "moe", "moe"] and cfg.rot_dim == 8 and cfg.router_kind == "deepseek_v3" and cfg.qk_norm == qk_norm
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16,
+                                      kv_cache_dtype="fp32"), device="cpu", weights=w)
+    toks = torch.randint(0, 300, (45,), generator=torch.Generator().manual_seed(1)).tolist()
+    got = eng.token_logits(toks)
+    with torch.no_grad():
+        want = m(torch.tensor([toks])).logits[0].float()
+    err = (got - want).abs().max(dim=1).values / float(want.abs().max())
+    assert float(err.median()) < 1e-2 and int((err > 5e-2).sum()) <= 2, err
