@@ -80,6 +80,8 @@ class ModelConfig:
     # (activation in `act`: gelu | gelu_tanh | relu2 | silu | relu) instead of the gated one, attention and MLP side by side
     # from one residual read (with one shared norm or one norm each), biases on the MLP and the head
     norm_kind: str = "rms"               # rms | layernorm | layernorm_nobias | none (OLMo-2: only the block outputs are normalised)
+    learned_positions: bool = False      # a learned position table is added to the token embeddings (GPT-2, OPT)
+    position_offset: int = 0
     qk_norm_full: bool = False           # RMSNorm over the whole q and the whole k projection (all heads at once, OLMo-2)
     mlp_kind: str = "glu"                # glu | plain
     parallel_block: bool = False
@@ -291,7 +293,7 @@ ATTENTION_MODEL_TYPES = ("llama", "mistral", "ministral", "qwen2", "qwen3", "qwe
                          "gemma3_text", "phi3", "gpt_oss", "granite", "seed_oss", "glm", "glm4", "ernie4_5", "helium", "smollm3")
 
 
-CLASSIC_MODEL_TYPES = ("starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "olmo2", "olmo3")
+CLASSIC_MODEL_TYPES = ("starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "olmo2", "olmo3", "gpt2", "opt")
 _ACT_NAMES = {"gelu": "gelu", "gelu_new": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh", "gelu_fast": "gelu_tanh", "relu2": "relu2",
               "silu": "silu", "swish": "silu", "relu": "relu"}
 
@@ -300,6 +302,14 @@ def classic_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     """Families built from LayerNorm, plain MLPs or parallel blocks (the reference covers them through the same decoder,
     rust/engine/src/config.rs fields `norm`, `ffn`, `parallel_residual`)."""
     mt = hf["model_type"]
+    if mt == "gpt2":                      # its own field names
+        hf = dict(hf, hidden_size=hf["n_embd"], num_hidden_layers=hf["n_layer"], num_attention_heads=hf["n_head"],
+                  intermediate_size=hf.get("n_inner") or 4 * hf["n_embd"], max_position_embeddings=hf.get("n_positions", 1024),
+                  hidden_act=hf.get("activation_function", "gelu_new"))
+    if mt == "opt":
+        if hf.get("word_embed_proj_dim") not in (None, hf["hidden_size"]) or not hf.get("do_layer_norm_before", True):
+            raise NotImplementedError("OPT with projected embeddings or post-LayerNorm blocks (350m) is not supported")
+        hf = dict(hf, intermediate_size=hf["ffn_dim"], hidden_act=hf.get("activation_function", "relu"))
     hidden, L, heads = hf["hidden_size"], hf["num_hidden_layers"], hf["num_attention_heads"]
     head_dim = hf.get("head_dim") or hidden // heads
     act = _ACT_NAMES.get(hf.get("hidden_act", "gelu"), "gelu")
@@ -335,6 +345,12 @@ def classic_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
         cfg.norm_kind, cfg.mlp_kind, cfg.act, cfg.rms_eps = "layernorm", "plain", act, hf.get("layer_norm_eps", 1e-5)
         cfg.parallel_block, cfg.parallel_norms = bool(hf.get("use_parallel_residual", True)), 2
         cfg.attn_bias, cfg.mlp_bias = bool(hf.get("attention_bias", True)), True
+    elif mt in ("gpt2", "opt"):           # learned absolute positions, LayerNorm, plain MLP, biases everywhere, tied head
+        cfg.norm_kind, cfg.mlp_kind, cfg.act = "layernorm", "plain", act
+        cfg.rms_eps = hf.get("layer_norm_epsilon", 1e-5)
+        cfg.use_rope, cfg.learned_positions, cfg.attn_bias, cfg.mlp_bias = False, True, True, True
+        cfg.position_offset = 2 if mt == "opt" else 0            # OPT's table starts two rows in
+        cfg.tie_embeddings = hf.get("tie_word_embeddings", True)
     elif mt in ("olmo2", "olmo3"):        # no norm in front of a block: its output is normalised instead; q and k normalised over all heads
         cfg.norm_kind, cfg.post_norms, cfg.qk_norm_full, cfg.rms_eps = "none", True, True, hf.get("rms_norm_eps", 1e-6)
         cfg.attn_bias = bool(hf.get("attention_bias", False))

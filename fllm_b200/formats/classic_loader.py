@@ -26,6 +26,9 @@ _NAMES = {
     "gpt_neox": ("gpt_neox.layers.{}.", "attention.", "query_key_value", "dense", "input_layernorm", "post_attention_layernorm",
                  "mlp.dense_h_to_4h", "mlp.dense_4h_to_h"),
     "cohere": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", "input_layernorm", None, None, "mlp.down_proj"),
+    "gpt2": ("transformer.h.{}.", "attn.", "c_attn", "c_proj", "ln_1", "ln_2", "mlp.c_fc", "mlp.c_proj"),
+    "opt": ("model.decoder.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "out_proj", "self_attn_layer_norm", "final_layer_norm",
+            "fc1", "fc2"),
     "olmo2": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", None, None, None, "mlp.down_proj"),
     "olmo3": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", None, None, None, "mlp.down_proj"),
 }
@@ -42,6 +45,14 @@ def load_hf_classic(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
 
     lp, ap, qkv, o_name, n1, n2, mlp_in, mlp_out = _NAMES[cfg.arch]
     H, D, hq, hkv = cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
+    if cfg.arch == "gpt2":                      # GPT-2 stores its matrices as [in, out]
+        inner = get
+
+        def get(name, required=True):            # noqa: F811 (a transposing view of the reader for this family's matrices)
+            t = inner(name, required)
+            if t is not None and t.dim() == 2 and name.endswith(".weight") and (".attn.c_" in name or ".mlp.c_" in name):
+                return t.t()
+            return t
     layers = []
     for l in range(cfg.num_layers):
         p = lp.format(l)
@@ -58,6 +69,8 @@ def load_hf_classic(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
             bs = [get(p + ap + n + ".bias", False) for n in qkv]
             if bs[0] is not None:
                 lw.bqkv = dev(torch.cat(bs))
+        elif cfg.arch == "gpt2":                # one matrix: all q rows, all k rows, all v rows
+            lw.wqkv, lw.bqkv = dev(get(p + ap + qkv + ".weight")), opt(p + ap + qkv + ".bias")
         else:                                   # GPT-NeoX: one matrix whose rows go head by head as (q, k, v)
             w = get(p + ap + qkv + ".weight").view(hq, 3, D, H)
             lw.wqkv = dev(torch.cat([w[:, 0].reshape(hq * D, H), w[:, 1].reshape(hq * D, H), w[:, 2].reshape(hq * D, H)], 0))
@@ -72,7 +85,11 @@ def load_hf_classic(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
             lw.w_gate_up = dev(torch.cat([get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")], 0))
         lw.w_down, lw.b_down = dev(get(p + mlp_out + ".weight")), opt(p + mlp_out + ".bias")
         layers.append(lw)
-    if cfg.arch == "gpt_neox":
+    if cfg.arch == "gpt2":
+        embed, fin, head = "transformer.wte.weight", "transformer.ln_f", "lm_head.weight"
+    elif cfg.arch == "opt":
+        embed, fin, head = "model.decoder.embed_tokens.weight", "model.decoder.final_layer_norm", "lm_head.weight"
+    elif cfg.arch == "gpt_neox":
         embed, fin, head = "gpt_neox.embed_in.weight", "gpt_neox.final_layer_norm", "embed_out.weight"
     elif cfg.arch == "phi":
         embed, fin, head = "model.embed_tokens.weight", "model.final_layernorm", "lm_head.weight"
@@ -87,5 +104,7 @@ def load_hf_classic(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
     w = DecoderWeights(embed=e, layers=layers, final_norm=dev(get(fin + ".weight")), lm_head=head_d, vocab_start=0,
                        vocab_local=cfg.vocab_size)
     w.final_norm_b = opt(fin + ".bias")
+    if cfg.learned_positions:
+        w.pos_embed = dev(get("transformer.wpe.weight" if cfg.arch == "gpt2" else "model.decoder.embed_positions.weight"))
     w.lm_head_b = opt("lm_head.bias")
     return w

@@ -231,6 +231,9 @@ class Decoder:
             return rwkv6_forward_hidden(self, b)
         if self.first_stage:
             x = ops.embed(b.token_ids, self.w.embed, cfg.embed_scale)
+            if cfg.learned_positions:              # the same row gather on the position table
+                pos_ids = b.positions + cfg.position_offset if cfg.position_offset else b.positions
+                x = x + ops.embed(pos_ids, self.w.pos_embed, 1.0)
             delta = None
         else:
             x, delta = hidden_in, delta_in

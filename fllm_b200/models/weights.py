@@ -84,6 +84,7 @@ class DecoderWeights:
     vocab_local: int = 0
     final_norm_b: Optional[torch.Tensor] = None      # families whose blocks are LayerNorms (RWKV, GPT-NeoX, Phi, ...)
     lm_head_b: Optional[torch.Tensor] = None         # Phi
+    pos_embed: Optional[torch.Tensor] = None         # [positions, H] learned absolute positions (GPT-2, OPT)
 
     def nbytes(self) -> int:
         n = 0

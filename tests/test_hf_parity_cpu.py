@@ -71,6 +71,11 @@ def _model(kind):
         return tf.GPTNeoXForCausalLM(tf.GPTNeoXConfig(**neox))
     if kind == "cohere":
         return tf.CohereForCausalLM(tf.CohereConfig(**BASE, pad_token_id=0, logit_scale=0.25))
+    if kind == "gpt2":
+        return tf.GPT2LMHeadModel(tf.GPT2Config(vocab_size=300, n_positions=256, n_embd=64, n_layer=2, n_head=4))
+    if kind == "opt":
+        return tf.OPTForCausalLM(tf.OPTConfig(vocab_size=300, hidden_size=64, num_hidden_layers=2, ffn_dim=128, num_attention_heads=4,
+                                               max_position_embeddings=256, word_embed_proj_dim=64))
     if kind == "olmo2":
         return tf.Olmo2ForCausalLM(tf.Olmo2Config(**BASE, pad_token_id=0))
     if kind == "olmo3":
@@ -89,7 +94,7 @@ def _model(kind):
 
 
 @pytest.mark.parametrize("kind", ["llama", "llama3_rope", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "granite", "seed_oss", "ernie4_5", "glm", "glm4", "helium",
-                                  "ministral", "smollm3", "starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "olmo2", "olmo3", "phi3", "mixtral", "qwen3_moe",
+                                  "ministral", "smollm3", "starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "gpt2", "opt", "olmo2", "olmo3", "phi3", "mixtral", "qwen3_moe",
                                   "qwen2_moe"])
 def test_attention_families_match_transformers(tmp_path, kind):
     from fllm_b200.formats.loader import load_hf_checkpoint
@@ -102,7 +107,7 @@ def test_attention_families_match_transformers(tmp_path, kind):
                 p.add_(0.05 * torch.randn_like(p))            # biases start at zero: make them count
             if n.endswith(("mlp.gate.weight", "block_sparse_moe.gate.weight")):
                 p.mul_(20.0)                                  # clear routing decisions
-            if n.endswith(("q_proj.weight", "k_proj.weight", "qkv_proj.weight", "query_key_value.weight")):
+            if n.endswith(("q_proj.weight", "k_proj.weight", "qkv_proj.weight", "query_key_value.weight", "c_attn.weight")):
                 p.mul_(12.0)                                  # peaked attention: a wrong rotation or mask moves the logits
     d = str(tmp_path / kind)
     m.save_pretrained(d, safe_serialization=True)
