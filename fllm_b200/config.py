@@ -414,7 +414,7 @@ def mla_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     return cfg
 
 
-RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "jamba", "granitemoehybrid", "granitemoe", "granitemoeshared", "glm4_moe", "rwkv6")
+RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "jamba", "granitemoehybrid", "granitemoe", "granitemoeshared", "glm4_moe", "ernie4_5_moe", "rwkv6")
 
 
 def _limit(v, default: float) -> float:
@@ -506,6 +506,17 @@ def recurrent_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
                    ssm=dict(num_k_heads=hf.get("linear_num_key_heads", 16), num_v_heads=hf.get("linear_num_value_heads", 32),
                             head_k_dim=hf.get("linear_key_head_dim", 128), head_v_dim=hf.get("linear_value_head_dim", 128),
                             d_conv=hf.get("linear_conv_kernel_dim", 4), norm_eps=hf.get("rms_norm_eps", 1e-6)))
+    if mt == "ernie4_5_moe":              # ERNIE 4.5: pair-style rotation, softmax router with a selection bias, renormalised weights
+        E, start, step = hf.get("moe_num_experts", 0), hf.get("moe_layer_start_index", 1), hf.get("moe_layer_interval", 1) or 1
+        end = hf.get("moe_layer_end_index", -1)
+        end = L - 1 if end in (None, -1) else end
+        I = hf.get("moe_intermediate_size", 1536)
+        return cls(**base, arch_alias="glm4_moe", rope_style="pair", intermediate_size=hf["intermediate_size"],
+                   rms_eps=hf.get("rms_norm_eps", 1e-5), tie_embeddings=hf.get("tie_word_embeddings", True),
+                   attn_bias=bool(hf.get("use_bias", False)), layer_kinds=["attention"] * L,
+                   ffn_kinds=["moe" if (E and start <= i <= end and (i + 1) % step == 0) else "glu" for i in range(L)],
+                   num_experts=E, experts_per_token=hf.get("moe_k", 6), moe_intermediate_size=I,
+                   shared_intermediate_size=(hf.get("moe_num_shared_experts") or 0) * I, router_kind="deepseek_v2", router_norm_topk=True)
     if mt == "glm4_moe":                  # GLM-4.5: llama-style attention (partial rotary, optional per-head QK-norm) + the DeepSeek-V3 router
         dense_first, E = hf.get("first_k_dense_replace", 1), hf.get("n_routed_experts", 0)
         rot = int(head_dim * hf.get("partial_rotary_factor", 0.5))

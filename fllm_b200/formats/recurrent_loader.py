@@ -37,8 +37,11 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
         """Router (+ selection bias), routed experts (one fused pair of tensors or one module per expert), shared experts."""
         lw.router_w = dev(get(mp + "gate.weight"))
         sel = get(mp + "gate.e_score_correction_bias", False)
+        for alt in ("gate.moe_statics.e_score_correction_bias", "moe_statics.e_score_correction_bias"):      # ERNIE 4.5
+            if sel is None:
+                sel = get(mp + alt, False)
         if sel is not None:
-            lw.router_select_b = sel.float().to(device).contiguous()
+            lw.router_select_b = sel.float().reshape(-1).to(device).contiguous()
         fused = get(mp + "experts.gate_up_proj", False)
         if fused is not None:
             lw.exp_gate_up, lw.exp_down = dev(fused), dev(get(mp + "experts.down_proj"))

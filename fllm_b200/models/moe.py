@@ -39,7 +39,7 @@ def route_deepseek(cfg, logits: torch.Tensor, bias: Optional[torch.Tensor]):
         group_rank = choice.view(-1, G, E // G).topk(min(2, E // G), dim=-1)[0].sum(-1)
     else:
         scores = torch.softmax(lf, -1)
-        choice = scores
+        choice = scores + bias.float() if bias is not None else scores         # ERNIE 4.5: a selection bias on softmax scores
         group_rank = choice.view(-1, G, E // G).max(-1).values
     if G > 1:
         keep = torch.zeros_like(group_rank).scatter_(1, group_rank.topk(cfg.router_topk_groups, dim=-1)[1], 1.0)

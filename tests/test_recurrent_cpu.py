@@ -577,3 +577,37 @@ def test_glm4_moe_matches_transformers(tmp_path, qk_norm):
         want = m(torch.tensor([toks])).logits[0].float()
     err = (got - want).abs().max(dim=1).values / float(want.abs().max())
     assert float(err.median()) < 1e-2 and int((err > 5e-2).sum()) <= 2, err
+
+
+def test_ernie4_5_moe_matches_transformers(tmp_path):
+    """ERNIE 4.5 MoE: pair-style rotation, a dense first layer, softmax router whose selection adds a bias, weights renormalised,
+    shared experts."""
+    import transformers as tf
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    torch.manual_seed(0)
+    m = tf.Ernie4_5_MoeForCausalLM(tf.Ernie4_5_MoeConfig(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=3,
+                                                         num_attention_heads=4, num_key_value_heads=2, moe_intermediate_size=32, moe_k=2,
+                                                         moe_num_experts=8, moe_num_shared_experts=2, moe_layer_start_index=1,
+                                                         max_position_embeddings=256)).eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "norm" in n:
+                p.add_(0.3 * torch.randn_like(p))
+            if n.endswith(("q_proj.weight", "k_proj.weight")):
+                p.mul_(12.0)
+            if n.endswith("gate.weight"):
+                p.mul_(20.0)
+            if n.endswith("e_score_correction_bias"):
+                p.copy_(0.05 * torch.randn_like(p))
+    d = str(tmp_path / "ernie")
+    m.save_pretrained(d, safe_serialization=True)
+    cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
+    assert cfg.ffn_kinds == ["glu", "moe", "moe"] and cfg.rope_style == "pair" and w.layers[1].router_select_b is not None
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16,
+                                      kv_cache_dtype="fp32"), device="cpu", weights=w)
+    toks = torch.randint(0, 300, (45,), generator=torch.Generator().manual_seed(1)).tolist()
+    got = eng.token_logits(toks)
+    with torch.no_grad():
+        want = m(torch.tensor([toks])).logits[0].float()
+    err = (got - want).abs().max(dim=1).values / float(want.abs().max())
+    assert float(err.median()) < 1e-2 and int((err > 5e-2).sum()) <= 2, err
