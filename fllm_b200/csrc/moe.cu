@@ -125,20 +125,29 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
   __syncthreads();
   for (int i = threadIdx.x; i < rows_cap; i += blockDim.x) token_of[i] = -1;
   __syncthreads();
-  // deterministic placement: entries of an expert keep their (token, slot) order
-  for (int e = threadIdx.x; e < local; e += blockDim.x) {
-    int pos = off[e];
-    for (int i = 0; i < entries; ++i) {
-      if ((i < staged ? ids_s[i] : ids[i]) == e + expert_lo) {
-        row_of[i] = pos;
-        if (pos < rows_cap) token_of[pos] = i / k;
-        ++pos;
+  // Deterministic placement: entries of an expert keep their (token, slot) order. The entries are taken 1024 at a time,
+  // one per thread; the warps of a round go one after the other, and inside a warp the lanes that drew the same expert
+  // rank themselves with a match mask, so no thread ever scans the list.
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int base = 0; base < entries; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    const int e = i < entries ? (i < staged ? ids_s[i] : ids[i]) - expert_lo : -1;
+    const bool valid = e >= 0 && e < local;
+    const int warps = min((int)(blockDim.x >> 5), (entries - base + 31) >> 5);
+    for (int w = 0; w < warps; ++w) {
+      if (warp == w) {
+        const unsigned same = __match_any_sync(0xffffffffu, valid ? e : -1 - lane);      // other lanes with this expert
+        if (valid) {
+          const int pos = off[e] + fill[e] + __popc(same & ((1u << lane) - 1u));
+          row_of[i] = pos;
+          if (pos < rows_cap) token_of[pos] = i / k;
+        }
+        __syncwarp();
+        if (valid && lane == __ffs(same) - 1) fill[e] += __popc(same);
       }
+      __syncthreads();
     }
-  }
-  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
-    const int e = ids[i];
-    if (e < expert_lo || e >= expert_hi) row_of[i] = -1;
+    if (i < entries && !valid) row_of[i] = -1;
   }
 }
 
