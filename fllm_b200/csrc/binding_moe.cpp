@@ -22,6 +22,20 @@ void moe_route(const Tensor& logits, const optional<Tensor>& bias, int64_t k, bo
                   softmax_all ? 1 : 0, ids.data_ptr<int>(), weights.data_ptr<float>(), cur_stream());
 }
 
+void moe_route_scored(const Tensor& logits, const optional<Tensor>& select_bias, int64_t k, int64_t score_kind, bool renorm, double scale,
+                      Tensor ids, Tensor weights) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kBFloat16 && logits.dim() == 2 && logits.stride(1) == 1, "logits: bf16 rows");
+  TORCH_CHECK(ids.scalar_type() == at::kInt && weights.scalar_type() == at::kFloat && ids.is_contiguous() && weights.is_contiguous(), "ids int32, weights fp32");
+  const float* sb = nullptr;
+  if (select_bias.has_value() && select_bias->defined()) {
+    TORCH_CHECK(select_bias->scalar_type() == at::kFloat && select_bias->is_contiguous() && select_bias->numel() == logits.size(1), "select_bias: fp32 [experts]");
+    sb = select_bias->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(logits.device());
+  fllm::moe_route_scored(logits.data_ptr(), logits.stride(0), sb, (int)logits.size(0), (int)logits.size(1), (int)k, (int)score_kind,
+                         renorm ? 1 : 0, (float)scale, ids.data_ptr<int>(), weights.data_ptr<float>(), cur_stream());
+}
+
 void moe_align(const Tensor& ids, int64_t experts, int64_t expert_lo, int64_t expert_hi, int64_t bn, Tensor row_of,
                Tensor token_of, Tensor tile_expert, Tensor tile_row0, Tensor num_tiles) {
   TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kInt && ids.dim() == 2 && ids.is_contiguous(), "ids: [tokens, k] int32");
@@ -150,6 +164,8 @@ void ep_wait_returns(int64_t h, int64_t epoch, const Tensor& status, const optio
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
+  m.def("moe_route_scored(Tensor logits, Tensor? select_bias, int k, int score_kind, bool renorm, float scale, Tensor(a!) ids, Tensor(b!) weights) -> ()",
+        &moe_route_scored);
   m.def("moe_route(Tensor logits, Tensor? bias, int k, bool softmax_all, Tensor(a!) ids, Tensor(b!) weights) -> ()", &moe_route);
   m.def("moe_align(Tensor ids, int experts, int expert_lo, int expert_hi, int bn, Tensor(a!) row_of, Tensor(b!) token_of, Tensor(c!) tile_expert, Tensor(d!) tile_row0, Tensor(e!) num_tiles) -> ()", &moe_align);
   m.def("moe_gather(Tensor x, Tensor token_of, Tensor(a!) xp) -> ()", &moe_gather);

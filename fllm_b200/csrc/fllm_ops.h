@@ -167,6 +167,9 @@ int moe_grouped_linear_bf16(const void* xp, long long ldx, const void* w_stack, 
                             const void* bias_stack, void* y, long long ldy, int rows_cap, int n_out, int K,
                             int experts, const int* tile_expert, const int* tile_row0, const int* num_tiles,
                             int max_tiles, int bn, int* status, cudaStream_t stream);
+// score-weighted routers (score_kind 1 softmax over all experts, 2 sigmoid; selection on score + select_bias; optional renormalisation; scale)
+void moe_route_scored(const void* logits, long long ld, const float* select_bias, int tokens, int experts, int k, int score_kind,
+                      int renorm, float scale, int* ids, float* weights, cudaStream_t s);
 void moe_route(const void* logits, long long ld, const void* bias, int tokens, int experts, int k, int softmax_all,
                int* ids, float* weights, cudaStream_t s);
 void moe_align(const int* ids, int tokens, int k, int experts, int expert_lo, int expert_hi, int bn, int* row_of,

@@ -77,6 +77,84 @@ __global__ void moe_route_kernel(const __nv_bfloat16* __restrict__ logits, long 
   }
 }
 
+// Routers that weigh experts by their score: score = softmax over all experts (score_kind 1) or sigmoid (2) of the logit; the
+// k experts with the largest score + select_bias are taken (the bias only steers the choice: DeepSeek-V3, GLM-4.5, ERNIE 4.5);
+// weights = the scores of the chosen experts, renormalised on request, times `scale`. One warp per token, up to 256 experts.
+__global__ void moe_route_scored_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, const float* __restrict__ select_bias,
+                                        int tokens, int experts, int k, int score_kind, int renorm, float scale, int* __restrict__ ids,
+                                        float* __restrict__ weights) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  constexpr int MAXPL = 8;
+  float sc[MAXPL], ch[MAXPL];
+  float vmax = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < MAXPL; ++i) {
+    const int e = lane + 32 * i;
+    sc[i] = e < experts ? __bfloat162float(logits[(size_t)t * ld + e]) : -INFINITY;
+    vmax = fmaxf(vmax, sc[i]);
+  }
+  if (score_kind == 1) {
+    vmax = warp_max(vmax);
+    float den = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) {
+      sc[i] = sc[i] == -INFINITY ? 0.f : __expf(sc[i] - vmax);
+      den += sc[i];
+    }
+    den = warp_sum(den);
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) sc[i] /= den;
+  } else {
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) sc[i] = sc[i] == -INFINITY ? 0.f : 1.f / (1.f + __expf(-sc[i]));
+  }
+#pragma unroll
+  for (int i = 0; i < MAXPL; ++i) {
+    const int e = lane + 32 * i;
+    ch[i] = e < experts ? sc[i] + (select_bias ? select_bias[e] : 0.f) : -INFINITY;
+  }
+  float sel_s[8];
+  int sel_e[8];
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY, best_s = 0.f;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) {
+      const int e = lane + 32 * i;
+      if (ch[i] > best || (ch[i] == best && e < best_e)) { best = ch[i]; best_e = e; best_s = sc[i]; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o), os = __shfl_xor_sync(0xffffffffu, best_s, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; best_s = os; }
+    }
+    sel_s[j] = best_s;
+    sel_e[j] = best_e;
+    if ((best_e & 31) == lane) ch[best_e >> 5] = -INFINITY;    // remove the winner
+  }
+  if (lane == 0) {
+    float sum = 0.f;
+    for (int j = 0; j < k; ++j) sum += sel_s[j];
+    const float f = (renorm ? 1.f / (sum + 1e-20f) : 1.f) * scale;
+    for (int j = 0; j < k; ++j) {
+      ids[(size_t)t * k + j] = sel_e[j];
+      weights[(size_t)t * k + j] = sel_s[j] * f;
+    }
+  }
+}
+
+void moe_route_scored(const void* logits, long long ld, const float* select_bias, int tokens, int experts, int k, int score_kind,
+                      int renorm, float scale, int* ids, float* weights, cudaStream_t s) {
+  if (tokens <= 0) return;
+  if (experts > 256 || k > 8 || (score_kind != 1 && score_kind != 2)) throw std::runtime_error("moe_route_scored: at most 256 experts, top-8, score kind 1 or 2");
+  moe_route_scored_kernel<<<(tokens + 3) / 4, 128, 0, s>>>((const __nv_bfloat16*)logits, ld, select_bias, tokens, experts, k, score_kind,
+                                                           renorm, scale, ids, weights);
+  cuda_check(cudaGetLastError(), "moe_route_scored_kernel");
+}
+
 void moe_route(const void* logits, long long ld, const void* bias, int tokens, int experts, int k, int softmax_all,
                int* ids, float* weights, cudaStream_t s) {
   if (tokens <= 0) return;

@@ -153,7 +153,11 @@ def moe_ffn(dec, lw, h: torch.Tensor) -> torch.Tensor:
     ids = torch.empty(T, k, dtype=torch.int32, device=h.device)
     wts = torch.empty(T, k, dtype=torch.float32, device=h.device)
     if cfg.router_kind in ("deepseek_v2", "deepseek_v3"):
-        ids, wts = route_deepseek(cfg, logits, getattr(lw, "router_select_b", None))
+        if cfg.router_groups <= 1 and cfg.num_experts <= 256 and k <= 8:        # one kernel; grouped selection stays in tensor ops
+            k_ops.moe_route_scored(logits, getattr(lw, "router_select_b", None), k, 2 if cfg.router_kind == "deepseek_v3" else 1,
+                                   bool(cfg.router_norm_topk), float(cfg.router_scale), ids, wts)
+        else:
+            ids, wts = route_deepseek(cfg, logits, getattr(lw, "router_select_b", None))
     elif cfg.num_experts > 256 or k > 8:         # beyond the routing kernel's register budget: the same rule in tensor ops
         ids, wts = route_reference(cfg, logits)
         wts = wts.contiguous()

@@ -904,3 +904,28 @@ def test_add_layernorm_and_activations(cols, bias, delta):
         want = ref.act_(a.clone(), kind)
         got = nat.act_(a.clone(), kind)
         assert (got.float() - want.float()).abs().max().item() <= 0.04 * max(1.0, want.float().abs().max().item())
+
+
+@pytest.mark.parametrize("kind,E,k,bias,norm", [("deepseek_v2", 64, 6, False, False), ("deepseek_v3", 128, 8, True, True),
+                                                 ("deepseek_v2", 60, 4, True, True), ("deepseek_v3", 8, 2, False, False)])
+def test_score_weighted_router_kernel(kind, E, k, bias, norm):
+    """The router kernel of the DeepSeek / GLM-4.5 / ERNIE 4.5 families against the same rule in tensor operations."""
+    from fllm_b200.config import ModelConfig
+    from fllm_b200.models.moe import route_deepseek
+    from fllm_b200.ops.native import NativeOps
+    ops = NativeOps(torch.device("cuda"))
+    cfg = ModelConfig(num_experts=E, experts_per_token=k, router_kind=kind, router_scale=2.5, router_norm_topk=norm)
+    g = torch.Generator(device="cuda").manual_seed(E + k)
+    Ep = (E + 7) // 8 * 8
+    logits = (torch.randn(77, Ep, device="cuda", generator=g) * 3).bfloat16()[:, :E]       # a view with a wider pitch
+    sb = (torch.randn(E, device="cuda", generator=g) * 0.2) if bias else None
+    want_ids, want_w = route_deepseek(cfg, logits, sb)
+    ids = torch.empty(77, k, dtype=torch.int32, device="cuda")
+    w = torch.empty(77, k, dtype=torch.float32, device="cuda")
+    ops.k.moe_route_scored(logits, sb, k, 2 if kind == "deepseek_v3" else 1, norm, 2.5, ids, w)
+    so, sw = ids.long().sort(1), want_ids.long().sort(1)
+    same = (so.values == sw.values).all(1)
+    assert int((~same).sum()) <= 1                                   # a tie between two experts may resolve differently
+    a = torch.gather(w, 1, so.indices)[same]
+    b = torch.gather(want_w, 1, sw.indices)[same]
+    assert float((a - b).abs().max()) < 2e-3 * float(b.abs().max())
