@@ -676,6 +676,14 @@ def preset(name: str) -> ModelConfig:
                            layer_kinds=["mamba2"] * L, ffn_kinds=["none"] * L,
                            ssm=dict(d_inner=H * 64, d_state=128, d_conv=4, n_groups=1, head_dim=64, n_heads=H,
                                     norm_groups=1, conv_bias=True, dt_min=0.0, dt_max=1e30))
+    if n in ("falcon-mamba-7b", "mamba1-tiny"):
+        tiny = n.endswith("tiny")
+        hidden, L = (256, 2) if tiny else (4096, 64)
+        return ModelConfig(arch="falcon_mamba", name=n, vocab_size=4096 if tiny else 65024, hidden_size=hidden, num_layers=L,
+                           num_heads=1, num_kv_heads=1, head_dim=64, intermediate_size=0, tie_embeddings=False,
+                           layer_kinds=["mamba1"] * L, ffn_kinds=["none"] * L,
+                           ssm=dict(d_inner=2 * hidden, d_state=16, d_conv=4, dt_rank=hidden // 16, conv_bias=True,
+                                    proj_bias=False, bcdt_rms=True, mixer_rms_eps=1e-6))
     if n in ("bamba-9b", "bamba-tiny"):
         tiny = n.endswith("tiny")
         hidden, L, H = (256, 3, 8) if tiny else (4096, 32, 128)

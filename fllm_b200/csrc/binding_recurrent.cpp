@@ -26,7 +26,7 @@ inline void check_batch(const Tensor& q_starts, const Tensor& seq_state, const T
 }
 
 void causal_conv1d(const Tensor& x, const Tensor& w, const optional<Tensor>& bias, Tensor state, const Tensor& q_starts,
-                   const Tensor& seq_state, const Tensor& positions, Tensor y, bool act) {
+                   const Tensor& seq_state, const Tensor& positions, Tensor y, bool act, int64_t max_q_len) {
   TORCH_CHECK(rows_bf16(x) && rows_bf16(y) && x.sizes() == y.sizes(), "x, y: bf16 rows of one shape");
   const int64_t C = x.size(1), W = w.size(1);
   TORCH_CHECK(w.scalar_type() == at::kFloat && w.is_contiguous() && w.dim() == 2 && w.size(0) == C, "w: fp32 [C, W]");
@@ -36,7 +36,7 @@ void causal_conv1d(const Tensor& x, const Tensor& w, const optional<Tensor>& bia
   c10::cuda::CUDAGuard guard(x.device());
   const int rc = fllm::causal_conv1d(x.data_ptr(), x.stride(0), w.data_ptr<float>(), opt_f32(bias), state.data_ptr(), q_starts.data_ptr<int>(),
                                      seq_state.data_ptr<int>(), positions.data_ptr<int>(), y.data_ptr(), y.stride(0), (int)seq_state.numel(),
-                                     (int)C, (int)W, act ? 1 : 0, cur_stream());
+                                     (int)C, (int)W, act ? 1 : 0, (int)(max_q_len > 0 ? max_q_len : x.size(0)), cur_stream());
   TORCH_CHECK(rc == 0, "causal_conv1d: unsupported arguments (code ", rc, "): even C and strides, 2 <= W <= 4, y distinct from x");
 }
 
@@ -52,10 +52,10 @@ void mamba2_scan(const Tensor& x, const Tensor& dt, const Tensor& Bm, const Tens
   c10::cuda::CUDAGuard guard(x.device());
   float *seg_state = nullptr, *seg_dt = nullptr;
   const int64_t B = seq_state.numel();
-  if (seg_len > 0 && segs > 1) {                 // scratch: [B][segs - 1][H][P][N] end / start states, then [B][segs - 1][H] step sums
-    const int64_t n_state = B * (segs - 1) * H * P * N, n_dt = B * (segs - 1) * H;
+  if (seg_len > 0 && segs > 1) {                 // scratch: B * segs states of [H][P][N], then [B][segs - 1][H] step sums
+    const int64_t n_state = B * segs * H * P * N, n_dt = B * (segs - 1) * H;
     TORCH_CHECK(seg_scratch.has_value() && seg_scratch->scalar_type() == at::kFloat && seg_scratch->is_contiguous() &&
-                    seg_scratch->numel() >= n_state + n_dt, "seg_scratch: fp32, at least B * (segs - 1) * (H * P * N + H) values");
+                    seg_scratch->numel() >= n_state + n_dt, "seg_scratch: fp32, at least B * (segs * H * P * N + (segs - 1) * H) values");
     seg_state = seg_scratch->data_ptr<float>();
     seg_dt = seg_state + n_state;
   }
@@ -69,7 +69,7 @@ void mamba2_scan(const Tensor& x, const Tensor& dt, const Tensor& Bm, const Tens
 
 void mamba1_scan(const Tensor& x, const Tensor& dt, const Tensor& Bm, const Tensor& Cm, const optional<Tensor>& z, const Tensor& A,
                  const optional<Tensor>& D, const optional<Tensor>& dt_bias, Tensor state, const Tensor& q_starts, const Tensor& seq_state,
-                 const Tensor& positions, Tensor y) {
+                 const Tensor& positions, Tensor y, int64_t seg_len, int64_t segs, const optional<Tensor>& seg_scratch) {
   TORCH_CHECK(rows_bf16(x) && rows_bf16(dt) && rows_bf16(Bm) && rows_bf16(Cm) && rows_bf16(y), "activations: bf16 rows");
   const int64_t Dm = x.size(1), N = Bm.size(1);
   TORCH_CHECK(A.scalar_type() == at::kFloat && A.is_contiguous() && A.dim() == 2 && A.size(0) == Dm && A.size(1) == N, "A: fp32 [D, N]");
@@ -77,10 +77,20 @@ void mamba1_scan(const Tensor& x, const Tensor& dt, const Tensor& Bm, const Tens
               "state: fp32 [slots, D, N]");
   check_batch(q_starts, seq_state, positions);
   c10::cuda::CUDAGuard guard(x.device());
+  float *seg_state = nullptr, *seg_dt = nullptr;
+  const int64_t B = seq_state.numel();
+  if (seg_len > 0 && segs > 1) {                 // scratch: B * segs states of [Dm][N], then [B][segs - 1][Dm] step sums
+    const int64_t n_state = B * segs * Dm * N, n_dt = B * (segs - 1) * Dm;
+    TORCH_CHECK(seg_scratch.has_value() && seg_scratch->scalar_type() == at::kFloat && seg_scratch->is_contiguous() &&
+                    seg_scratch->numel() >= n_state + n_dt, "seg_scratch: fp32, at least B * Dm * (segs * N + segs - 1) values");
+    seg_state = seg_scratch->data_ptr<float>();
+    seg_dt = seg_state + n_state;
+  }
   const int rc = fllm::mamba1_scan(x.data_ptr(), x.stride(0), dt.data_ptr(), dt.stride(0), Bm.data_ptr(), Bm.stride(0), Cm.data_ptr(),
                                    Cm.stride(0), opt_ptr(z), opt_ld(z), A.data_ptr<float>(), opt_f32(D), opt_f32(dt_bias),
                                    state.data_ptr<float>(), q_starts.data_ptr<int>(), seq_state.data_ptr<int>(), positions.data_ptr<int>(),
-                                   y.data_ptr(), y.stride(0), (int)seq_state.numel(), (int)Dm, (int)N, cur_stream());
+                                   y.data_ptr(), y.stride(0), (int)B, (int)Dm, (int)N, (int)seg_len, (int)segs, seg_state, seg_dt,
+                                   cur_stream());
   TORCH_CHECK(rc == 0, "mamba1_scan: unsupported arguments (code ", rc, "): state width 8 / 16, B and C 16-byte aligned");
 }
 
@@ -195,14 +205,14 @@ void mla_prepare(const Tensor& ckv, const Tensor& q, int64_t rope_offset, const 
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(fllm_b200, m) {
-  m.def("causal_conv1d(Tensor x, Tensor w, Tensor? bias, Tensor(a!) state, Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y, bool act) -> ()",
+  m.def("causal_conv1d(Tensor x, Tensor w, Tensor? bias, Tensor(a!) state, Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y, bool act, int max_q_len) -> ()",
         &causal_conv1d);
   m.def("mamba2_scan(Tensor x, Tensor dt, Tensor Bm, Tensor Cm, Tensor A, Tensor? D, Tensor? dt_bias, Tensor(a!) state, Tensor q_starts, "
         "Tensor seq_state, Tensor positions, Tensor(b!) y, int H, int P, int G, int N, float dt_min, float dt_max, int seg_len, int segs, "
         "Tensor? seg_scratch, int skip_from) -> ()",
         &mamba2_scan);
   m.def("mamba1_scan(Tensor x, Tensor dt, Tensor Bm, Tensor Cm, Tensor? z, Tensor A, Tensor? D, Tensor? dt_bias, Tensor(a!) state, "
-        "Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y) -> ()",
+        "Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y, int seg_len, int segs, Tensor? seg_scratch) -> ()",
         &mamba1_scan);
   m.def("matrix_state_scan(int kind, Tensor r, Tensor k, Tensor v, Tensor? a, Tensor? b, Tensor? w, Tensor? u, Tensor? beta, Tensor(a!) state, "
         "Tensor q_starts, Tensor seq_state, Tensor positions, Tensor(b!) y, int H, int DK, int DV, int kv_ratio, bool l2norm, float q_scale, "

@@ -276,7 +276,9 @@ void spec_verify_sampled(const void* target_logits, long long ld_t, const void* 
 // before anything was launched.
 int causal_conv1d(const void* x, long long ldx, const float* w, const float* bias, void* state, const int* q_starts,
                   const int* seq_state, const int* positions, void* y, long long ldy, int B, int C, int W, int act,
-                  cudaStream_t stream);
+                  int max_q_len, cudaStream_t stream);   // max_q_len: host-side bound on a sequence's tokens in the step
+// Segmented scans (seg_len > 0, segs > 1): seg_state holds B * segs states (segs - 1 per sequence, then one start state per
+// sequence), seg_dt B * (segs - 1) sums of time steps per head (Mamba-2) or channel (Mamba-1).
 int mamba2_scan(const void* x, long long ldx, const void* dt, long long lddt, const void* Bm, long long ldb, const void* Cm,
                 long long ldc, const float* A, const float* D, const float* dt_bias, float* state, const int* q_starts,
                 const int* seq_state, const int* positions, void* y, long long ldy, int B, int H, int P, int G, int N,
@@ -285,7 +287,7 @@ int mamba2_scan(const void* x, long long ldx, const void* dt, long long lddt, co
 int mamba1_scan(const void* x, long long ldx, const void* dt, long long lddt, const void* Bm, long long ldb, const void* Cm,
                 long long ldc, const void* z, long long ldz, const float* A, const float* D, const float* dt_bias, float* state,
                 const int* q_starts, const int* seq_state, const int* positions, void* y, long long ldy, int B, int Dm, int N,
-                cudaStream_t stream);
+                int seg_len, int segs, float* seg_state, float* seg_dt, cudaStream_t stream);
 // kind: 0 RWKV-6, 1 RWKV-7, 2 gated delta rule (one decay per head), 3 delta rule with a decay per key channel.
 // Kind 2 with w == nullptr takes raw gates: beta = logit of the step size, gate_raw [T][H] = logit of the decay,
 // log decay = gate_A[h] * softplus(gate_raw + gate_dt_bias[h]).

@@ -9,6 +9,7 @@
 // Batch layout (shared by every kernel): q_starts[B + 1] = first token row of each sequence, seq_state[B] = row of the
 // state pool that belongs to the sequence, positions[T]: a sequence whose first token of the step sits at position 0
 // starts from a zero state. States live in fp32 (convolution windows in bf16: they are copies of bf16 inputs).
+#include <algorithm>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -60,19 +61,21 @@ __device__ __forceinline__ float row_sum(float v) {
 }
 
 // ------------------------------------------------------------------------------------------ causal conv1d
-// One CTA per (128 channels, sequence): the tokens of the sequence are spread over threadIdx.y, every thread owns two
-// neighbouring channels. Only this CTA reads the sequence's window for its channels, so after a barrier it moves the
-// window forward in place.
+// One CTA per (128 channels, sequence, run of `seg_tokens` tokens): the tokens of the run are spread over threadIdx.y,
+// every thread owns two neighbouring channels. Only the CTA of a sequence's first run reads the sequence's window for
+// its channels (later runs see their whole history in x, which nothing writes), so after a barrier that CTA moves the
+// window forward in place. The last run of the grid goes on to the sequence's end.
 template <int W>
 __global__ void __launch_bounds__(256) conv1d_kernel(const bf16* __restrict__ x, long long ldx, const float* __restrict__ w,
                                                      const float* __restrict__ bias, bf16* __restrict__ state,
                                                      const int* __restrict__ q_starts, const int* __restrict__ seq_state,
                                                      const int* __restrict__ positions, bf16* __restrict__ y, long long ldy,
-                                                     int C, int act) {
+                                                     int C, int act, int seg_tokens) {
   const int s = blockIdx.y;
   const int c = (blockIdx.x * 64 + threadIdx.x) * 2;
   const int t0 = q_starts[s], n = q_starts[s + 1] - t0;
-  if (n <= 0) return;
+  const int p_lo = blockIdx.z * seg_tokens, p_hi = blockIdx.z + 1 == gridDim.z ? n : min(n, p_lo + seg_tokens);
+  if (n <= 0 || (p_lo >= n && blockIdx.z != 0)) return;
   const bool active = c < C;
   const bool fresh = positions[t0] == 0;
   bf16* st = state + (long long)seq_state[s] * (W - 1) * C;
@@ -84,10 +87,10 @@ __global__ void __launch_bounds__(256) conv1d_kernel(const bf16* __restrict__ x,
 #pragma unroll
     for (int j = 0; j < W - 1; ++j) {
       float2 h = make_float2(0.f, 0.f);
-      if (!fresh) h = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(st + (long long)j * C + c));
+      if (!fresh && blockIdx.z == 0) h = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(st + (long long)j * C + c));
       hist[0][j] = h.x, hist[1][j] = h.y;
     }
-    for (int p = threadIdx.y; p < n; p += blockDim.y) {
+    for (int p = p_lo + threadIdx.y; p < p_hi; p += blockDim.y) {
       float a0 = bv[0], a1 = bv[1];
 #pragma unroll
       for (int j = 0; j < W; ++j) {
@@ -101,6 +104,7 @@ __global__ void __launch_bounds__(256) conv1d_kernel(const bf16* __restrict__ x,
       *reinterpret_cast<__nv_bfloat162*>(y + (long long)(t0 + p) * ldy + c) = __floats2bfloat162_rn(a0, a1);
     }
   }
+  if (blockIdx.z != 0) return;
   __syncthreads();
   if (active && threadIdx.y == 0) {
 #pragma unroll
@@ -136,6 +140,8 @@ struct Mamba2Args {
   int skip_from;                // sequences with at least this many tokens in the step are left to another path (0 = none)
   int seg_len, segs;            // segmented modes only
   float* seg_state;             // [B][segs - 1][H][P][N]: end states (kLocal), then start states of segments 1.. (combine)
+  float* seg_start0;            // [B][H][P][N]: a continued sequence's state before the step, copied by combine, so that
+                                // kFinal's first segment does not read the pool row that its last segment overwrites
   float* seg_dt;                // [B][segs - 1][H]: sum of the time steps of a segment
 };
 
@@ -163,7 +169,7 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Args a) {
 #pragma unroll
     for (int i = 0; i < NPT; ++i) hs[i] = 0.f;
   } else if (from_pool) {
-    load_f32<NPT>(st, hs);
+    load_f32<NPT>(MODE == kFinal ? a.seg_start0 + (((long long)s * a.H + h) * a.P + pc) * N + ln * NPT : st, hs);
   } else {
     load_f32<NPT>(sg + (seg - 1) * seg_stride, hs);
   }
@@ -230,7 +236,10 @@ __global__ void mamba2_combine_kernel(const Mamba2Args a, int N) {
   if (n <= 0 || (a.skip_from > 0 && n >= a.skip_from)) return;
   const int h = (int)(i4 / ((long long)a.P * N));
   float4 carry = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (a.positions[t0] != 0) carry = *reinterpret_cast<const float4*>(a.state + (long long)a.seq_state[s] * per_seq + i4);
+  if (a.positions[t0] != 0) {
+    carry = *reinterpret_cast<const float4*>(a.state + (long long)a.seq_state[s] * per_seq + i4);
+    *reinterpret_cast<float4*>(a.seg_start0 + (long long)s * per_seq + i4) = carry;
+  }
   float* sg = a.seg_state + (long long)s * (a.segs - 1) * per_seq + i4;
   const float A = a.A[h];
   for (int seg = 0; seg < a.segs - 1; ++seg) {
@@ -251,30 +260,48 @@ struct Mamba1Args {
   const int *q_starts, *seq_state, *positions;
   bf16* y;
   int Dm;
+  int seg_len, segs;              // sequence-parallel form (see the Mamba-2 kernel): segments, then combine, then the outputs
+  float* seg_state;               // [B][segs - 1][Dm][N]
+  float* seg_start0;              // [B][Dm][N]: a continued sequence's state before the step (written by combine)
+  float* seg_dt;                  // [B][segs - 1][Dm]: sum of a channel's time steps over a segment
 };
 
-template <int N>
+template <int N, int MODE>
 __global__ void __launch_bounds__(128) mamba1_scan_kernel(const Mamba1Args a) {
-  const int d = blockIdx.x * 128 + threadIdx.x, s = blockIdx.y;
+  const int d = blockIdx.x * 128 + threadIdx.x, s = blockIdx.y, seg = MODE == kWhole ? 0 : blockIdx.z;
   const int t0 = a.q_starts[s], n = a.q_starts[s + 1] - t0;
   if (n <= 0 || d >= a.Dm) return;
   float* st = a.state + ((long long)a.seq_state[s] * a.Dm + d) * N;
+  const long long seg_stride = (long long)a.Dm * N;
+  float* sg = MODE == kWhole ? nullptr : a.seg_state + ((long long)s * (a.segs - 1) * a.Dm + d) * N;
+  const int lo = MODE == kWhole ? 0 : min(n, seg * a.seg_len);
+  const int hi = (MODE == kWhole || (MODE == kFinal && seg == a.segs - 1)) ? n : min(n, (seg + 1) * a.seg_len);
   float hs[N], A[N];
   load_f32<N>(a.A + (long long)d * N, A);
-  if (a.positions[t0] == 0) {
+  const bool from_pool = MODE == kWhole || (MODE == kFinal && seg == 0);
+  if (MODE == kLocal || (from_pool && a.positions[t0] == 0)) {
 #pragma unroll
     for (int i = 0; i < N; ++i) hs[i] = 0.f;
+  } else if (from_pool) {
+    load_f32<N>(MODE == kFinal ? a.seg_start0 + ((long long)s * a.Dm + d) * N : st, hs);
   } else {
-    load_f32<N>(st, hs);
+    load_f32<N>(sg + (seg - 1) * seg_stride, hs);
   }
   const float D = a.D != nullptr ? a.D[d] : 0.f, dtb = a.dt_bias != nullptr ? a.dt_bias[d] : 0.f;
-  for (int t = t0; t < t0 + n; ++t) {
+  float dt_sum = 0.f;
+  for (int t = t0 + lo; t < t0 + hi; ++t) {
     float Bc[N], Cc[N];
     load_bf16<N>(a.Bm + (long long)t * a.ldb, Bc);           // the same words for the whole warp: one broadcast fetch
-    load_bf16<N>(a.Cm + (long long)t * a.ldc, Cc);
+    if (MODE != kLocal) load_bf16<N>(a.Cm + (long long)t * a.ldc, Cc);
     const float xv = __bfloat162float(a.x[(long long)t * a.ldx + d]);
     const float dt = softplus_f(__bfloat162float(a.dt[(long long)t * a.lddt + d]) + dtb);
     const float dx = dt * xv;
+    dt_sum += dt;
+    if (MODE == kLocal) {
+#pragma unroll
+      for (int i = 0; i < N; ++i) hs[i] = fmaf(hs[i], __expf(dt * A[i]), dx * Bc[i]);
+      continue;
+    }
     float acc = 0.f;
 #pragma unroll
     for (int i = 0; i < N; ++i) {
@@ -285,7 +312,38 @@ __global__ void __launch_bounds__(128) mamba1_scan_kernel(const Mamba1Args a) {
     if (a.z != nullptr) acc *= silu_f(__bfloat162float(a.z[(long long)t * a.ldz + d]));
     a.y[(long long)t * a.ldy + d] = __float2bfloat16(acc);
   }
-  store_f32<N>(st, hs);
+  if (MODE == kLocal) {
+    store_f32<N>(sg + seg * seg_stride, hs);
+    a.seg_dt[((long long)s * (a.segs - 1) + seg) * a.Dm + d] = dt_sum;
+  } else if (MODE == kWhole || seg == a.segs - 1) {
+    store_f32<N>(st, hs);
+  }
+}
+
+// start[seg + 1] = end_local[seg] + exp(A sum dt[seg]) * start[seg] per channel and state entry, in place over seg_state
+template <int N>
+__global__ void mamba1_combine_kernel(const Mamba1Args a) {
+  const int d = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
+  const int t0 = a.q_starts[s];
+  if (d >= a.Dm || a.q_starts[s + 1] - t0 <= 0) return;
+  float carry[N], A[N];
+  load_f32<N>(a.A + (long long)d * N, A);
+  if (a.positions[t0] != 0) {
+    load_f32<N>(a.state + ((long long)a.seq_state[s] * a.Dm + d) * N, carry);
+    store_f32<N>(a.seg_start0 + ((long long)s * a.Dm + d) * N, carry);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) carry[i] = 0.f;
+  }
+  float* sg = a.seg_state + ((long long)s * (a.segs - 1) * a.Dm + d) * N;
+  for (int seg = 0; seg < a.segs - 1; ++seg) {
+    const float sdt = a.seg_dt[((long long)s * (a.segs - 1) + seg) * a.Dm + d];
+    float e[N];
+    load_f32<N>(sg + (long long)seg * a.Dm * N, e);
+#pragma unroll
+    for (int i = 0; i < N; ++i) carry[i] = fmaf(carry[i], __expf(A[i] * sdt), e[i]);
+    store_f32<N>(sg + (long long)seg * a.Dm * N, carry);
+  }
 }
 
 // ------------------------------------------------------------------------------------------ matrix-state family
@@ -523,17 +581,19 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // Every launcher returns 0 on success or a negative code naming the argument it rejected, before any launch.
 int causal_conv1d(const void* x, long long ldx, const float* w, const float* bias, void* state, const int* q_starts,
                   const int* seq_state, const int* positions, void* y, long long ldy, int B, int C, int W, int act,
-                  cudaStream_t stream) {
+                  int max_q_len, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (C % 2 || (ldx % 2) || (ldy % 2) || x == y) return -1;
   if (W < 2 || W > 4) return -2;
-  const dim3 grid((C / 2 + 63) / 64, B), block(64, 4);
+  constexpr int seg_tokens = 64;                       // 16 tokens per thread
+  const int runs = std::min(std::max((max_q_len + seg_tokens - 1) / seg_tokens, 1), 65535);
+  const dim3 grid((C / 2 + 63) / 64, B, runs), block(64, 4);
   auto xs = static_cast<const bf16*>(x);
   auto ys = static_cast<bf16*>(y);
   auto ss = static_cast<bf16*>(state);
-  if (W == 2) conv1d_kernel<2><<<grid, block, 0, stream>>>(xs, ldx, w, bias, ss, q_starts, seq_state, positions, ys, ldy, C, act);
-  if (W == 3) conv1d_kernel<3><<<grid, block, 0, stream>>>(xs, ldx, w, bias, ss, q_starts, seq_state, positions, ys, ldy, C, act);
-  if (W == 4) conv1d_kernel<4><<<grid, block, 0, stream>>>(xs, ldx, w, bias, ss, q_starts, seq_state, positions, ys, ldy, C, act);
+  if (W == 2) conv1d_kernel<2><<<grid, block, 0, stream>>>(xs, ldx, w, bias, ss, q_starts, seq_state, positions, ys, ldy, C, act, seg_tokens);
+  if (W == 3) conv1d_kernel<3><<<grid, block, 0, stream>>>(xs, ldx, w, bias, ss, q_starts, seq_state, positions, ys, ldy, C, act, seg_tokens);
+  if (W == 4) conv1d_kernel<4><<<grid, block, 0, stream>>>(xs, ldx, w, bias, ss, q_starts, seq_state, positions, ys, ldy, C, act, seg_tokens);
   return 0;
 }
 
@@ -550,7 +610,8 @@ int mamba2_scan(const void* x, long long ldx, const void* dt, long long lddt, co
   if (segmented && (seg_state == nullptr || seg_dt == nullptr || !aligned16(seg_state))) return -3;
   Mamba2Args a{static_cast<const bf16*>(x), static_cast<const bf16*>(dt), static_cast<const bf16*>(Bm), static_cast<const bf16*>(Cm),
                ldx, lddt, ldb, ldc, ldy, A, D, dt_bias, state, q_starts, seq_state, positions, static_cast<bf16*>(y), H, P, G,
-               dt_min, dt_max, skip_from, seg_len, segs, seg_state, seg_dt};
+               dt_min, dt_max, skip_from, seg_len, segs, seg_state,
+               segmented ? seg_state + (long long)B * (segs - 1) * H * P * N : nullptr, seg_dt};
 #define FLLM_M2(N_, NPT_)                                                                                          \
   {                                                                                                                \
     constexpr int rows = 128 / (N_ / NPT_);                                                                        \
@@ -579,17 +640,31 @@ int mamba2_scan(const void* x, long long ldx, const void* dt, long long lddt, co
 int mamba1_scan(const void* x, long long ldx, const void* dt, long long lddt, const void* Bm, long long ldb, const void* Cm,
                 long long ldc, const void* z, long long ldz, const float* A, const float* D, const float* dt_bias, float* state,
                 const int* q_starts, const int* seq_state, const int* positions, void* y, long long ldy, int B, int Dm, int N,
-                cudaStream_t stream) {
+                int seg_len, int segs, float* seg_state, float* seg_dt, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (!aligned16(Bm) || !aligned16(Cm) || (ldb % 8) || (ldc % 8)) return -1;
+  const bool segmented = seg_len > 0 && segs > 1;
+  if (segmented && (seg_state == nullptr || seg_dt == nullptr || !aligned16(seg_state))) return -3;
   Mamba1Args a{static_cast<const bf16*>(x), static_cast<const bf16*>(dt), static_cast<const bf16*>(Bm), static_cast<const bf16*>(Cm),
                static_cast<const bf16*>(z), ldx, lddt, ldb, ldc, ldz, ldy, A, D, dt_bias, state, q_starts, seq_state, positions,
-               static_cast<bf16*>(y), Dm};
-  const dim3 grid((Dm + 127) / 128, B);
-  if (N == 16) mamba1_scan_kernel<16><<<grid, 128, 0, stream>>>(a);
-  else if (N == 8) mamba1_scan_kernel<8><<<grid, 128, 0, stream>>>(a);
-  else return -2;
-  return 0;
+               static_cast<bf16*>(y), Dm, seg_len, segs, seg_state,
+               segmented ? seg_state + (long long)B * (segs - 1) * Dm * N : nullptr, seg_dt};
+  const unsigned gx = (Dm + 127) / 128;
+#define FLLM_M1(N_)                                                                           \
+  {                                                                                           \
+    if (!segmented) {                                                                         \
+      mamba1_scan_kernel<N_, kWhole><<<dim3(gx, B), 128, 0, stream>>>(a);                     \
+    } else {                                                                                  \
+      mamba1_scan_kernel<N_, kLocal><<<dim3(gx, B, segs - 1), 128, 0, stream>>>(a);           \
+      mamba1_combine_kernel<N_><<<dim3(gx, B), 128, 0, stream>>>(a);                          \
+      mamba1_scan_kernel<N_, kFinal><<<dim3(gx, B, segs), 128, 0, stream>>>(a);               \
+    }                                                                                         \
+    return 0;                                                                                 \
+  }
+  if (N == 16) FLLM_M1(16)
+  if (N == 8) FLLM_M1(8)
+#undef FLLM_M1
+  return -2;
 }
 
 int matrix_state_scan(int kind, const void* r, long long ldr, const void* k, long long ldk, const void* v, long long ldv,

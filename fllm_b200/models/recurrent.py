@@ -111,7 +111,7 @@ def mamba1_mixer(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
     qs, ss, pos = _batch_meta(b)
     Di, N = s["d_inner"], s["d_state"]
     xz = ops.linear(h, m["in_proj"], m.get("in_proj_b"))
-    x = ops.causal_conv1d(xz[:, :Di], m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=True)
+    x = ops.causal_conv1d(xz[:, :Di], m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=True, max_q_len=b.max_q_len)
     bcd = ops.linear(x, m["x_proj"])
     Bm, Cm, dtl = bcd[:, :N], bcd[:, N:2 * N], bcd[:, 2 * N:]
     if s.get("bcdt_rms"):
@@ -122,7 +122,8 @@ def mamba1_mixer(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
             dtn, Bm, Cm = dtn * m["dt_norm_w"], Bm * m["b_norm_w"], Cm * m["c_norm_w"]
         dtl = torch.nn.functional.pad(dtn, (0, dtl.shape[1] - R))
     dt = ops.linear(dtl, m["dt_proj"])
-    y = ops.mamba1_scan(x, dt, Bm, Cm, xz[:, Di:2 * Di], m["A"], m["D"], m["dt_bias"], dec.rstate.scan[li], qs, ss, pos)
+    y = ops.mamba1_scan(x, dt, Bm, Cm, xz[:, Di:2 * Di], m["A"], m["D"], m["dt_bias"], dec.rstate.scan[li], qs, ss, pos,
+                        getattr(b, "max_q_len", 0))
     return ops.linear(y, m["out_proj"], m.get("out_proj_b"))
 
 
@@ -133,7 +134,7 @@ def mamba2_mixer(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
     Di, N, G, H, P = s["d_inner"], s["d_state"], s["n_groups"], s["n_heads"], s["head_dim"]
     C = Di + 2 * G * N
     zxd = ops.linear(h, m["in_proj"], m.get("in_proj_b"))
-    xbc = ops.causal_conv1d(zxd[:, Di:Di + C], m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=True)
+    xbc = ops.causal_conv1d(zxd[:, Di:Di + C], m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=True, max_q_len=b.max_q_len)
     y = ops.mamba2_scan(xbc[:, :Di], zxd[:, Di + C:Di + C + H], xbc[:, Di:Di + G * N], xbc[:, Di + G * N:], m["A"], m["D"],
                         m["dt_bias"], dec.rstate.scan[li], qs, ss, pos, H, P, G, N, s.get("dt_min", 0.0),
                         s.get("dt_max", 1e30), getattr(b, "max_q_len", 0), None, getattr(b, "host_seqs", None))
@@ -150,7 +151,7 @@ def gated_delta_mixer(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
     Hk, Hv, Dk, Dv = s["num_k_heads"], s["num_v_heads"], s["head_k_dim"], s["head_v_dim"]
     K, V = Hk * Dk, Hv * Dv
     proj = ops.linear(h, m["in_proj"])                                  # [q | k | v | z | beta | a] (+ padding)
-    qkv = ops.causal_conv1d(proj[:, :2 * K + V], m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=True)
+    qkv = ops.causal_conv1d(proj[:, :2 * K + V], m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=True, max_q_len=b.max_q_len)
     z = proj[:, 2 * K + V:2 * K + 2 * V]
     o = 2 * K + 2 * V                                                   # the step-size and decay logits go to the scan raw
     y = ops.matrix_state_scan(GATED_DELTA, qkv[:, :K], qkv[:, K:2 * K], qkv[:, 2 * K:], None, None, None, None, proj[:, o:o + Hv],
@@ -167,7 +168,7 @@ def shortconv_mixer(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
     Hd = dec.cfg.hidden_size
     bcx = ops.linear(h, m["in_proj"], m.get("in_proj_b"))
     bx = bcx[:, :Hd] * bcx[:, 2 * Hd:3 * Hd]
-    y = ops.causal_conv1d(bx, m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=False)
+    y = ops.causal_conv1d(bx, m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=False, max_q_len=b.max_q_len)
     return ops.linear(bcx[:, Hd:2 * Hd] * y, m["out_proj"], m.get("out_proj_b"))
 
 

@@ -24,6 +24,8 @@ RWKV6, RWKV7, GATED_DELTA, KDA = 0, 1, 2, 3
 # tensors) it measured slower than the sequence-parallel scan kernel on a B200 (Mamba-2 2.7B prefill 15.3 k against
 # 16.6 k tok/s); it is kept as the tested statement of the algorithm a fused kernel would implement.
 SSD_MIN_TOKENS = int(__import__("os").environ.get("FLLM_SSD_MIN_TOKENS", "0"))
+# Tokens per segment of the sequence-parallel Mamba scans (0: always one walk per sequence).
+SCAN_SEG_LEN = int(__import__("os").environ.get("FLLM_SCAN_SEG_LEN", "128"))
 
 
 def _seqs(q_starts, seq_state, positions):
@@ -85,7 +87,7 @@ def ssd_chunked(x, dt, Bm, Cm, A, D, dt_bias, h0, H, P, G, N, dt_min=0.0, dt_max
 
 
 class RecurrentRef:
-    def causal_conv1d(self, x, w, bias, state, q_starts, seq_state, positions, act=True):
+    def causal_conv1d(self, x, w, bias, state, q_starts, seq_state, positions, act=True, max_q_len=0):
         """y[t, c] = act(bias[c] + sum_j w[c, j] * x[t - (W - 1) + j, c]) inside each sequence; the W - 1 inputs before
         the step come from ``state`` [slots, W - 1, C], which ends up holding the last W - 1 inputs."""
         W = w.shape[1]
@@ -122,7 +124,7 @@ class RecurrentRef:
             state[slot] = h
         return y
 
-    def mamba1_scan(self, x, dt, Bm, Cm, z, A, D, dt_bias, state, q_starts, seq_state, positions):
+    def mamba1_scan(self, x, dt, Bm, Cm, z, A, D, dt_bias, state, q_starts, seq_state, positions, max_q_len=0, seg_len=None):
         """h[d, n] = exp(dt[d] A[d, n]) h + dt[d] B[n] x[d];  y = (h C + D x) * silu(z)."""
         y = torch.empty_like(x)
         for t0, t1, slot, fresh in _seqs(q_starts, seq_state, positions):
@@ -245,9 +247,9 @@ class RecurrentRef:
 class RecurrentNative:
     """Kernel wrappers; ``self.k`` is the loaded extension and ``self.launches`` the launch counter of the ops object."""
 
-    def causal_conv1d(self, x, w, bias, state, q_starts, seq_state, positions, act=True):
+    def causal_conv1d(self, x, w, bias, state, q_starts, seq_state, positions, act=True, max_q_len=0):
         y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
-        self.k.causal_conv1d(x, w, bias, state, q_starts, seq_state, positions, y, bool(act))
+        self.k.causal_conv1d(x, w, bias, state, q_starts, seq_state, positions, y, bool(act), int(max_q_len))   # 0: bounded by the rows
         self.launches += 1
         return y
 
@@ -274,11 +276,11 @@ class RecurrentNative:
                 skip, max_q_len = SSD_MIN_TOKENS, SSD_MIN_TOKENS - 1
         if seg_len is None:
             ctas = B * H * max(1, P * max(N // 16, 1) // 128)
-            seg_len = 128 if (max_q_len >= 512 and ctas < 4 * 148) else 0
+            seg_len = SCAN_SEG_LEN if (max_q_len >= 512 and ctas < 4 * 148) else 0
         segs = -(-int(max_q_len) // seg_len) if seg_len else 1
         scratch = None
         if segs > 1:
-            need = B * (segs - 1) * (H * P * N + H)
+            need = B * (segs * H * P * N + (segs - 1) * H)
             scratch = getattr(self, "_scan_scratch", None)
             if scratch is None or scratch.numel() < need:
                 scratch = self._scan_scratch = torch.empty(need, dtype=torch.float32, device=x.device)
@@ -287,10 +289,22 @@ class RecurrentNative:
         self.launches += 3 if segs > 1 else 1
         return y
 
-    def mamba1_scan(self, x, dt, Bm, Cm, z, A, D, dt_bias, state, q_starts, seq_state, positions):
+    def mamba1_scan(self, x, dt, Bm, Cm, z, A, D, dt_bias, state, q_starts, seq_state, positions, max_q_len=0, seg_len=None):
+        """Long prompts of few sequences run sequence-parallel (``max_q_len``: host-side bound on a sequence's tokens in the step)."""
         y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
-        self.k.mamba1_scan(x, dt, Bm, Cm, z, A, D, dt_bias, state, q_starts, seq_state, positions, y)
-        self.launches += 1
+        B, Dm, N = seq_state.numel(), x.shape[1], A.shape[1]
+        if seg_len is None:
+            seg_len = SCAN_SEG_LEN if (max_q_len >= 512 and B * ((Dm + 127) // 128) < 4 * 148) else 0
+        segs = -(-int(max_q_len) // seg_len) if seg_len else 1
+        scratch = None
+        if segs > 1:
+            need = B * Dm * (segs * N + segs - 1)
+            scratch = getattr(self, "_scan_scratch", None)
+            if scratch is None or scratch.numel() < need:
+                scratch = self._scan_scratch = torch.empty(need, dtype=torch.float32, device=x.device)
+        self.k.mamba1_scan(x, dt, Bm, Cm, z, A, D, dt_bias, state, q_starts, seq_state, positions, y,
+                           int(seg_len if segs > 1 else 0), int(segs), scratch)
+        self.launches += 3 if segs > 1 else 1
         return y
 
     def matrix_state_scan(self, kind, r, k, v, a, b, w, u, beta, state, q_starts, seq_state, positions, H, DK, DV,

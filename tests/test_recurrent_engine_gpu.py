@@ -126,7 +126,23 @@ def test_long_prompt_chunks_take_the_matrix_form(monkeypatch):
 
 
 def test_hybrid_presets_decode():
-    for name in ("mamba2-tiny", "bamba-tiny"):
+    for name in ("mamba2-tiny", "bamba-tiny", "mamba1-tiny"):
         eng = _engine(preset(name), chunk=256, graphs=True)
         out = eng.generate([[1, 2, 3, 4, 5] * 9, [7] * 20], SamplingParams(max_tokens=8, temperature=0.0))
         assert [len(o) for o in out] == [8, 8]
+
+
+def test_mamba1_long_prompt_sequence_parallel():
+    """A prompt long enough for the segmented Mamba-1 scan gives the chunk-by-chunk walk's tokens and the fp32
+    reference's logits."""
+    from fllm_b200.ops.reference import RefOps
+    cfg = preset("mamba1-tiny")
+    nat = _engine(cfg, chunk=1024, max_len=1024)
+    ref = _engine(cfg, ops=RefOps(), chunk=1024, weights=nat.weights, max_len=1024)
+    toks = torch.randint(0, 4096, (800,), generator=torch.Generator().manual_seed(6)).tolist()
+    a, b = nat.token_logits(toks[:700]), ref.token_logits(toks[:700])
+    assert float((a - b).norm() / b.norm()) < 2e-2
+    sp = SamplingParams(max_tokens=8, temperature=0.0)
+    prompts = [toks[:300], toks, toks[100:140]]
+    want = _engine(cfg, chunk=256, weights=nat.weights, max_len=1024).generate(prompts, sp)
+    assert _engine(cfg, chunk=1024, weights=nat.weights, max_len=1024).generate(prompts, sp) == want

@@ -54,6 +54,24 @@ def test_causal_conv1d(ops, W, case):
     assert torch.equal(st, st_ref)                                # windows are copies of inputs: exact
 
 
+@pytest.mark.parametrize("max_q", [0, 100, 700])
+def test_causal_conv1d_token_runs(ops, max_q):
+    """Long sequences are cut into runs of tokens over the grid; a bound below the longest sequence stays correct (the
+    last run goes on to the end), and continued sequences still read and move their windows."""
+    nat, ref = ops
+    qs, ss, pos, T = ragged([700, 130, 2, 1], [False, True, False, False], [3, 0, 2, 5])
+    C, W = 328, 4
+    g = torch.Generator(device="cuda").manual_seed(max_q)
+    x = torch.randn(T, C, device="cuda", generator=g).bfloat16()
+    w, bias = torch.randn(C, W, device="cuda", generator=g) * 0.5, torch.randn(C, device="cuda", generator=g)
+    st = torch.randn(6, W - 1, C, device="cuda", generator=g).bfloat16()
+    st_ref = st.clone()
+    y = nat.causal_conv1d(x, w, bias, st, qs, ss, pos, act=True, max_q_len=max_q)
+    y_ref = ref.causal_conv1d(x, w, bias, st_ref, qs, ss, pos, act=True)
+    torch.cuda.synchronize()
+    assert rel(y, y_ref) < 1e-2 and torch.equal(st, st_ref)
+
+
 @pytest.mark.parametrize("N,P,H,G", [(128, 64, 8, 2), (64, 64, 4, 1), (16, 32, 6, 3), (256, 80, 2, 1), (32, 64, 4, 4)])
 @pytest.mark.parametrize("case", CASES)
 def test_mamba2_scan(ops, N, P, H, G, case):
@@ -244,3 +262,24 @@ def test_gated_delta_raw_gates(ops):
     y_ref = ref.matrix_state_scan(*args, st_ref, qs, ss, pos, Hv, D, D, 2, True, D ** -0.5, **kw)
     torch.cuda.synchronize()
     assert rel(y, y_ref) < 1e-2 and rel(st, st_ref) < 1e-4
+
+
+@pytest.mark.parametrize("seg_len", [64, 128])
+def test_mamba1_scan_sequence_parallel(ops, seg_len):
+    nat, ref = ops
+    lens, fresh, slots = [700, 300, 40, 1], [True, False, True, False], [3, 0, 2, 5]
+    qs, ss, pos, T = ragged(lens, fresh, slots)
+    Dm, N = 200, 16
+    g = torch.Generator(device="cuda").manual_seed(seg_len + 1)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    x, dt, z = rn(T, Dm).bfloat16(), (rn(T, Dm) - 1.0).bfloat16(), rn(T, Dm).bfloat16()
+    bc = rn(T, 2 * N).bfloat16()
+    A, D, dtb = -torch.exp(rn(Dm, N) * 0.5), rn(Dm), rn(Dm) * 0.5
+    st0 = rn(6, Dm, N) * 0.5
+    st_ref = st0.clone()
+    y_ref = ref.mamba1_scan(x, dt, bc[:, :N], bc[:, N:], z, A, D, dtb, st_ref, qs, ss, pos)
+    for max_q in (700, 500):
+        st = st0.clone()
+        y = nat.mamba1_scan(x, dt, bc[:, :N], bc[:, N:], z, A, D, dtb, st, qs, ss, pos, max_q_len=max_q, seg_len=seg_len)
+        torch.cuda.synchronize()
+        assert rel(y, y_ref) < 1e-2 and rel(st, st_ref) < 1e-3, max_q
