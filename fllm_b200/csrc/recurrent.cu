@@ -125,7 +125,8 @@ __global__ void __launch_bounds__(256) conv1d_kernel(const bf16* __restrict__ x,
 // recurrence is diagonal, so a sequence can be cut into segments of `seg_len` tokens that run side by side:
 //   kLocal    every segment but the last runs from a zero state and leaves its end state and the sum of its time steps;
 //   combine   start state of segment s + 1 = end state of s + exp(A sum dt_s) * start state of s (a short serial pass);
-//   kFinal    every segment runs again from its true start state and writes y; the last segment stores the state.
+//   kFinal    every segment runs again from its true start state and writes y; the segment with the sequence's last token
+//             stores the state. Sequences of one segment (decode rows of a mixed step) run only here, as the plain walk.
 // Twice the arithmetic, `segs` times the parallelism. kWhole is the plain walk (decode, short chunks, large batches).
 enum { kWhole = 0, kLocal = 1, kFinal = 2 };
 struct Mamba2Args {
@@ -161,15 +162,19 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Args a) {
   const long long seg_stride = (long long)a.H * a.P * N;
   // tokens [lo, hi) of the sequence's step
   // (the last segment of kFinal runs to the end of the step even if `segs` was sized for a shorter one)
-  const int lo = MODE == kWhole ? 0 : min(n, seg * a.seg_len);
-  const int hi = (MODE == kWhole || (MODE == kFinal && seg == a.segs - 1)) ? n : min(n, (seg + 1) * a.seg_len);
+  // the segment that holds the sequence's last token stores the state; segments after it (short sequences, decode rows of a
+  // mixed step) have nothing to do, and a sequence of one segment runs as the plain walk inside kFinal
+  const int seg_last = MODE == kWhole ? 0 : min(a.segs - 1, (n - 1) / a.seg_len);
+  if ((MODE == kLocal && seg >= seg_last) || (MODE == kFinal && seg > seg_last)) return;
+  const int lo = MODE == kWhole ? 0 : seg * a.seg_len;
+  const int hi = (MODE == kWhole || (MODE == kFinal && seg == seg_last)) ? n : (seg + 1) * a.seg_len;
   float hs[NPT];
   const bool from_pool = MODE == kWhole || (MODE == kFinal && seg == 0);
   if (MODE == kLocal || (from_pool && a.positions[t0] == 0)) {
 #pragma unroll
     for (int i = 0; i < NPT; ++i) hs[i] = 0.f;
   } else if (from_pool) {
-    load_f32<NPT>(MODE == kFinal ? a.seg_start0 + (((long long)s * a.H + h) * a.P + pc) * N + ln * NPT : st, hs);
+    load_f32<NPT>(MODE == kFinal && seg_last > 0 ? a.seg_start0 + (((long long)s * a.H + h) * a.P + pc) * N + ln * NPT : st, hs);
   } else {
     load_f32<NPT>(sg + (seg - 1) * seg_stride, hs);
   }
@@ -220,7 +225,7 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Args a) {
   if (MODE == kLocal) {
     if (valid) store_f32<NPT>(sg + seg * seg_stride, hs);
     if (blockIdx.x % ptiles == 0 && threadIdx.x == 0) a.seg_dt[((long long)s * (a.segs - 1) + seg) * a.H + h] = dt_sum;
-  } else if (valid && (MODE == kWhole || seg == a.segs - 1)) {
+  } else if (valid && (MODE == kWhole || seg == seg_last)) {
     store_f32<NPT>(st, hs);
   }
 }
@@ -234,6 +239,8 @@ __global__ void mamba2_combine_kernel(const Mamba2Args a, int N) {
   const int t0 = a.q_starts[s];
   const int n = a.q_starts[s + 1] - t0;
   if (n <= 0 || (a.skip_from > 0 && n >= a.skip_from)) return;
+  const int seg_last = min(a.segs - 1, (n - 1) / a.seg_len);
+  if (seg_last == 0) return;
   const int h = (int)(i4 / ((long long)a.P * N));
   float4 carry = make_float4(0.f, 0.f, 0.f, 0.f);
   if (a.positions[t0] != 0) {
@@ -242,7 +249,7 @@ __global__ void mamba2_combine_kernel(const Mamba2Args a, int N) {
   }
   float* sg = a.seg_state + (long long)s * (a.segs - 1) * per_seq + i4;
   const float A = a.A[h];
-  for (int seg = 0; seg < a.segs - 1; ++seg) {
+  for (int seg = 0; seg < seg_last; ++seg) {
     const float d = __expf(A * a.seg_dt[((long long)s * (a.segs - 1) + seg) * a.H + h]);
     float4 e = *reinterpret_cast<const float4*>(sg + seg * per_seq);
     carry = make_float4(fmaf(carry.x, d, e.x), fmaf(carry.y, d, e.y), fmaf(carry.z, d, e.z), fmaf(carry.w, d, e.w));
@@ -274,8 +281,10 @@ __global__ void __launch_bounds__(128) mamba1_scan_kernel(const Mamba1Args a) {
   float* st = a.state + ((long long)a.seq_state[s] * a.Dm + d) * N;
   const long long seg_stride = (long long)a.Dm * N;
   float* sg = MODE == kWhole ? nullptr : a.seg_state + ((long long)s * (a.segs - 1) * a.Dm + d) * N;
-  const int lo = MODE == kWhole ? 0 : min(n, seg * a.seg_len);
-  const int hi = (MODE == kWhole || (MODE == kFinal && seg == a.segs - 1)) ? n : min(n, (seg + 1) * a.seg_len);
+  const int seg_last = MODE == kWhole ? 0 : min(a.segs - 1, (n - 1) / a.seg_len);
+  if ((MODE == kLocal && seg >= seg_last) || (MODE == kFinal && seg > seg_last)) return;
+  const int lo = MODE == kWhole ? 0 : seg * a.seg_len;
+  const int hi = (MODE == kWhole || (MODE == kFinal && seg == seg_last)) ? n : (seg + 1) * a.seg_len;
   float hs[N], A[N];
   load_f32<N>(a.A + (long long)d * N, A);
   const bool from_pool = MODE == kWhole || (MODE == kFinal && seg == 0);
@@ -283,7 +292,7 @@ __global__ void __launch_bounds__(128) mamba1_scan_kernel(const Mamba1Args a) {
 #pragma unroll
     for (int i = 0; i < N; ++i) hs[i] = 0.f;
   } else if (from_pool) {
-    load_f32<N>(MODE == kFinal ? a.seg_start0 + ((long long)s * a.Dm + d) * N : st, hs);
+    load_f32<N>(MODE == kFinal && seg_last > 0 ? a.seg_start0 + ((long long)s * a.Dm + d) * N : st, hs);
   } else {
     load_f32<N>(sg + (seg - 1) * seg_stride, hs);
   }
@@ -315,7 +324,7 @@ __global__ void __launch_bounds__(128) mamba1_scan_kernel(const Mamba1Args a) {
   if (MODE == kLocal) {
     store_f32<N>(sg + seg * seg_stride, hs);
     a.seg_dt[((long long)s * (a.segs - 1) + seg) * a.Dm + d] = dt_sum;
-  } else if (MODE == kWhole || seg == a.segs - 1) {
+  } else if (MODE == kWhole || seg == seg_last) {
     store_f32<N>(st, hs);
   }
 }
@@ -325,7 +334,10 @@ template <int N>
 __global__ void mamba1_combine_kernel(const Mamba1Args a) {
   const int d = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
   const int t0 = a.q_starts[s];
-  if (d >= a.Dm || a.q_starts[s + 1] - t0 <= 0) return;
+  const int n = a.q_starts[s + 1] - t0;
+  if (d >= a.Dm || n <= 0) return;
+  const int seg_last = min(a.segs - 1, (n - 1) / a.seg_len);
+  if (seg_last == 0) return;
   float carry[N], A[N];
   load_f32<N>(a.A + (long long)d * N, A);
   if (a.positions[t0] != 0) {
@@ -336,7 +348,7 @@ __global__ void mamba1_combine_kernel(const Mamba1Args a) {
     for (int i = 0; i < N; ++i) carry[i] = 0.f;
   }
   float* sg = a.seg_state + ((long long)s * (a.segs - 1) * a.Dm + d) * N;
-  for (int seg = 0; seg < a.segs - 1; ++seg) {
+  for (int seg = 0; seg < seg_last; ++seg) {
     const float sdt = a.seg_dt[((long long)s * (a.segs - 1) + seg) * a.Dm + d];
     float e[N];
     load_f32<N>(sg + (long long)seg * a.Dm * N, e);

@@ -275,7 +275,8 @@ class RecurrentNative:
                     return y
                 skip, max_q_len = SSD_MIN_TOKENS, SSD_MIN_TOKENS - 1
         if seg_len is None:
-            ctas = B * H * max(1, P * max(N // 16, 1) // 128)
+            # CTAs that walk long sequences (a mixed step's decode rows finish at once and do not fill the GPU)
+            ctas = max(1, min(B, x.shape[0] // 256)) * H * max(1, P * max(N // 16, 1) // 128)
             seg_len = SCAN_SEG_LEN if (max_q_len >= 512 and ctas < 4 * 148) else 0
         segs = -(-int(max_q_len) // seg_len) if seg_len else 1
         scratch = None
@@ -294,7 +295,8 @@ class RecurrentNative:
         y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
         B, Dm, N = seq_state.numel(), x.shape[1], A.shape[1]
         if seg_len is None:
-            seg_len = SCAN_SEG_LEN if (max_q_len >= 512 and B * ((Dm + 127) // 128) < 4 * 148) else 0
+            ctas = max(1, min(B, x.shape[0] // 256)) * ((Dm + 127) // 128)          # those that walk long sequences
+            seg_len = SCAN_SEG_LEN if (max_q_len >= 512 and ctas < 4 * 148) else 0
         segs = -(-int(max_q_len) // seg_len) if seg_len else 1
         scratch = None
         if segs > 1:
