@@ -74,6 +74,7 @@ class ModelConfig:
     router_topk_groups: int = 1
     router_norm_topk: bool = False
     shared_gate: bool = False            # the shared experts' output is scaled by sigmoid(h . g) (Qwen3-Next)
+    moe_latent_size: int = 0             # > 0: routed experts work on a down-projection of the hidden state (Nemotron-H)
     qk_norm_offset: float = 0.0          # 1.0: the per-head q / k norms multiply by 1 + w (Gemma-3)
     rope_local_theta: float = 0.0        # > 0: windowed layers rotate with this base and no scaling (Gemma-3)
     # block variants of the pre-Llama families: LayerNorm (with or without bias) instead of RMSNorm, a plain two-matrix MLP
@@ -94,7 +95,8 @@ class ModelConfig:
     # layer has a gated FFN behind it ("glu") or is the mixer alone ("none"); `ssm` holds the mixer shapes
     # (d_inner, d_state, d_conv, n_groups, head_dim, n_heads, dt_rank, norm_groups, dt_min, dt_max, conv_bias,
     # num_k_heads, num_v_heads, head_k_dim, head_v_dim, bcdt_rms ...)
-    layer_kinds: Optional[List[str]] = None      # attention | mla | mamba1 | mamba2 | gated_delta | shortconv
+    layer_kinds: Optional[List[str]] = None      # attention | mla | mamba1 | mamba2 | gated_delta | shortconv | none (FFN-only block)
+                                                 # | attention+mamba2 (both read the block's input, their outputs add: Falcon-H1)
     ffn_kinds: Optional[List[str]] = None        # glu | moe | none
     ssm: Dict[str, Any] = field(default_factory=dict)
     # multi-head latent attention (layer kind "mla"): q_lora_rank (0 = one query projection), kv_lora_rank,
@@ -130,7 +132,11 @@ class ModelConfig:
 
     @property
     def has_recurrent(self) -> bool:
-        return bool(self.layer_kinds) and any(k not in ("attention", "mla") for k in self.layer_kinds)
+        return bool(self.layer_kinds) and any(k not in ("attention", "mla", "none") for k in self.layer_kinds)
+
+    def has_kv(self, layer: int) -> bool:
+        """Whether the layer keeps keys and values (or latent rows) in the paged pool."""
+        return self.layer_kind(layer) in ("attention", "mla", "attention+mamba2")
 
     @property
     def has_mla(self) -> bool:
@@ -414,7 +420,7 @@ def mla_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     return cfg
 
 
-RECURRENT_MODEL_TYPES = ("mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "jamba", "granitemoehybrid", "granitemoe", "granitemoeshared", "glm4_moe", "ernie4_5_moe", "rwkv6")
+RECURRENT_MODEL_TYPES = ("falcon_h1", "nemotron_h", "nemotron_h_moe", "mamba", "falcon_mamba", "mamba2", "bamba", "lfm2", "rwkv7", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "jamba", "granitemoehybrid", "granitemoe", "granitemoeshared", "glm4_moe", "ernie4_5_moe", "rwkv6")
 
 
 def _limit(v, default: float) -> float:
@@ -428,10 +434,51 @@ def _limit(v, default: float) -> float:
     return max(min(f, 1e30), -1e30)
 
 
+def nemotron_h_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
+    """Nemotron-H (the reference lists it with the Mamba-2 hybrids in docs/architectures.md and reads its per-layer
+    pattern in rust/engine/src/config.rs): every block is ONE of a Mamba-2 mixer, an attention without rotary
+    embedding, a two-matrix relu^2 MLP, or a mixture of such MLPs (sigmoid router with a selection bias, optional
+    latent projection around the routed experts, a shared MLP on the hidden state), behind one RMSNorm."""
+    blocks = hf.get("layers_block_type")
+    if not blocks:
+        names = {"M": "mamba", "*": "attention", "-": "mlp", "E": "moe"}
+        blocks = [names[c] for c in hf.get("hybrid_override_pattern", "")]
+    if not blocks:
+        raise ValueError("nemotron_h: the config names no block pattern (layers_block_type / hybrid_override_pattern)")
+    hidden, heads = hf["hidden_size"], hf["num_attention_heads"]
+    H, P = hf.get("mamba_num_heads", 128), hf.get("mamba_head_dim", 64)
+    G = hf.get("n_groups", hf.get("mamba_n_groups", 8))
+    lim = hf.get("time_step_limit") or hf.get("mamba_dt_limit") or (0.0, float("inf"))
+    E = hf.get("n_routed_experts", 0) if "moe" in blocks else 0
+    kind = {"mamba": "mamba2", "attention": "attention", "mlp": "none", "moe": "none"}
+    ffn = {"mamba": "none", "attention": "none", "mlp": "glu", "moe": "moe"}
+    return cls(arch="nemotron_h", name=hf.get("_name_or_path") or "nemotron_h", vocab_size=hf["vocab_size"], hidden_size=hidden,
+               num_layers=len(blocks), num_heads=heads, num_kv_heads=hf.get("num_key_value_heads", heads),
+               head_dim=hf.get("head_dim") or hf.get("attention_head_dim") or hidden // heads,
+               max_position=hf.get("max_position_embeddings", 8192), use_rope=False,
+               intermediate_size=hf.get("intermediate_size", 0), rms_eps=hf.get("layer_norm_epsilon", hf.get("rms_norm_eps", 1e-5)),
+               tie_embeddings=hf.get("tie_word_embeddings", False), attn_bias=hf.get("attention_bias", False),
+               mlp_kind="plain", act=hf.get("mlp_hidden_act", "relu2"), mlp_bias=bool(hf.get("mlp_bias", False)),
+               layer_kinds=[kind[b] for b in blocks], ffn_kinds=[ffn[b] for b in blocks],
+               num_experts=E, experts_per_token=hf.get("num_experts_per_tok", 2) if E else 0,
+               moe_intermediate_size=hf.get("moe_intermediate_size", 0) if E else 0,
+               shared_intermediate_size=(hf.get("moe_shared_expert_intermediate_size", 0) if hf.get("n_shared_experts", 1) else 0) if E else 0,
+               moe_latent_size=(hf.get("moe_latent_size") or 0) if E else 0,
+               router_kind="deepseek_v3", router_scale=float(hf.get("routed_scaling_factor", 1.0)),
+               router_norm_topk=bool(hf.get("norm_topk_prob", True)), router_groups=hf.get("n_group") or 1,
+               router_topk_groups=hf.get("topk_group") or 1,
+               ssm=dict(d_inner=H * P, d_state=hf.get("ssm_state_size", 128), d_conv=hf.get("conv_kernel", hf.get("mamba_d_conv", 4)),
+                        n_groups=G, head_dim=P, n_heads=H, norm_groups=G,
+                        conv_bias=hf.get("use_conv_bias", True), proj_bias=hf.get("use_bias", hf.get("mamba_proj_bias", False)),
+                        dt_min=_limit(lim[0], 0.0), dt_max=_limit(lim[1], 1e30)))
+
+
 def recurrent_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     """Recurrent and hybrid families (the reference describes them in rust/engine/src/config.rs next to the
     attention fields and in rust/engine/src/hybrid_config.rs): which mixer each layer runs and its shapes."""
     mt = hf["model_type"]
+    if mt in ("nemotron_h", "nemotron_h_moe"):
+        return nemotron_h_from_hf(cls, hf)
     hidden, L = hf["hidden_size"], hf["num_hidden_layers"]
     if mt in ("mamba", "falcon_mamba"):
         d_inner = hf.get("intermediate_size") or hf.get("expand", 2) * hidden
@@ -476,6 +523,30 @@ def recurrent_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     base = dict(arch=mt, name=hf.get("_name_or_path") or mt, vocab_size=hf["vocab_size"], hidden_size=hidden, num_layers=L,
                 num_heads=heads, num_kv_heads=hf.get("num_key_value_heads", heads), head_dim=head_dim,
                 rope_theta=hf.get("rope_theta", 10000.0), max_position=hf.get("max_position_embeddings", 8192))
+    if mt == "falcon_h1":
+        # Falcon-H1 (docs/architectures.md of the reference: Mamba-2 and attention side by side in every layer, the mu-P
+        # multipliers folded into the weights): the loader scales the projections, `embed_scale` the embeddings
+        H = hf.get("mamba_n_heads", 128)
+        Di = hf.get("mamba_d_ssm") or hf.get("mamba_expand", 2) * hidden
+        P = hf.get("mamba_d_head", "auto")
+        P = Di // H if P in ("auto", None) else int(P)
+        lim = hf.get("time_step_limit") or (0.0, float("inf"))
+        rope = hf.get("rope_parameters") or {}
+        base["rope_theta"] = rope.get("rope_theta", hf.get("rope_theta", 10000.0))
+        gate_mode = "gate_only" if not hf.get("mamba_rms_norm", False) else \
+            ("norm_before_gate" if hf.get("mamba_norm_before_gate", True) else "norm_after_gate")
+        return cls(**base, intermediate_size=hf["intermediate_size"], rms_eps=hf.get("rms_norm_eps", 1e-5),
+                   tie_embeddings=hf.get("tie_word_embeddings", False), attn_bias=hf.get("attention_bias", False),
+                   embed_scale=float(hf.get("embedding_multiplier", 1.0)),
+                   layer_kinds=["attention+mamba2"] * L,
+                   ssm=dict(d_inner=Di, d_state=hf.get("mamba_d_state", 256), d_conv=hf.get("mamba_d_conv", 4),
+                            n_groups=hf.get("mamba_n_groups", 1), head_dim=P, n_heads=H, norm_groups=hf.get("mamba_n_groups", 1),
+                            gate_mode=gate_mode, conv_bias=hf.get("mamba_conv_bias", True), proj_bias=hf.get("mamba_proj_bias", False),
+                            dt_min=_limit(lim[0], 0.0), dt_max=_limit(lim[1], 1e30),
+                            mup=dict(ssm=list(hf.get("ssm_multipliers") or [1.0] * 5), ssm_in=float(hf.get("ssm_in_multiplier", 1.0)),
+                                     ssm_out=float(hf.get("ssm_out_multiplier", 1.0)), attn_in=float(hf.get("attention_in_multiplier", 1.0)),
+                                     attn_out=float(hf.get("attention_out_multiplier", 1.0)), key=float(hf.get("key_multiplier", 1.0)),
+                                     mlp=list(hf.get("mlp_multipliers") or [1.0, 1.0]), head=float(hf.get("lm_head_multiplier", 1.0)))))
     if mt == "bamba":
         H = hf.get("mamba_n_heads", 128)
         P = hf.get("mamba_d_head", "auto")

@@ -59,6 +59,10 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
     mt = cfg.arch_alias or cfg.arch
     # language model inside a multimodal wrapper: model.language_model.*
     root = "model.language_model." if get("model.language_model.embed_tokens.weight", False) is not None else "model."
+    # Nemotron-H checkpoints: backbone.embedding(s) / backbone.layers; the in-memory module names say model.embeddings
+    nemo_embed = next((n for n in ("backbone.embeddings.weight", "backbone.embedding.weight", "model.embeddings.weight",
+                                   "model.embedding.weight") if get(n, False) is not None), None) if mt == "nemotron_h" else None
+    nemo_root = (nemo_embed or "backbone.").split(".")[0] + "."
     for l in range(cfg.num_layers):
         kind = cfg.layer_kind(l)
         if mt in ("mamba", "falcon_mamba", "mamba2"):
@@ -75,6 +79,63 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
                                        get(m + "dt_bias"), get(m + "A_log"), get(m + "D"), get(m + "norm.weight"),
                                        get(m + "out_proj.weight"), dtype, device, get(m + "in_proj.bias", False),
                                        get(m + "out_proj.bias", False))
+        elif mt == "nemotron_h":
+            p = f"{nemo_root}layers.{l}."
+            lw = LayerWeights(attn_norm=dev(get(p + "norm.weight")), wqkv=None, wo=None, ffn_norm=None)
+            m = p + "mixer."
+            if kind == "mamba2":
+                lw.mixer = pack_mamba2(get(m + "in_proj.weight"), get(m + "conv1d.weight"), get(m + "conv1d.bias", False),
+                                       get(m + "dt_bias"), get(m + "A_log"), get(m + "D"), get(m + "norm.weight"),
+                                       get(m + "out_proj.weight"), dtype, device, get(m + "in_proj.bias", False),
+                                       get(m + "out_proj.bias", False))
+            elif kind == "attention":
+                attention(lw, m)
+            elif cfg.ffn_kind(l) == "moe":          # two-matrix experts: the "gate / up" stack holds the up projections alone
+                lw.router_w = dev(get(m + "gate.weight"))
+                sel = get(m + "gate.e_score_correction_bias", False)
+                if sel is not None:
+                    lw.router_select_b = sel.float().reshape(-1).to(device).contiguous()
+                up = get(m + "experts.up_proj", False)
+                if up is not None:
+                    lw.exp_gate_up, lw.exp_down = dev(up), dev(get(m + "experts.down_proj"))
+                else:
+                    E = cfg.num_experts
+                    lw.exp_gate_up = dev(torch.stack([get(m + f"experts.{e}.up_proj.weight") for e in range(E)]))
+                    lw.exp_down = dev(torch.stack([get(m + f"experts.{e}.down_proj.weight") for e in range(E)]))
+                if cfg.shared_intermediate_size:
+                    lw.shared_gate_up = dev(get(m + "shared_experts.up_proj.weight"))
+                    lw.shared_down = dev(get(m + "shared_experts.down_proj.weight"))
+                if cfg.moe_latent_size:
+                    lw.moe_latent_in, lw.moe_latent_out = dev(get(m + "fc1_latent_proj.weight")), dev(get(m + "fc2_latent_proj.weight"))
+            else:
+                lw.w_gate_up, lw.w_down = dev(get(m + "up_proj.weight")), dev(get(m + "down_proj.weight"))
+                if cfg.mlp_bias:
+                    lw.b_up, lw.b_down = dev(get(m + "up_proj.bias")), dev(get(m + "down_proj.bias"))
+        elif mt == "falcon_h1":                      # the mu-P multipliers become part of the matrices they scale
+            p, mu = f"model.layers.{l}.", s["mup"]
+            lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
+                              ffn_norm=dev(get(p + "pre_ff_layernorm.weight")))
+            a = p + "self_attn."
+            scale = {"q": mu["attn_in"], "k": mu["attn_in"] * mu["key"], "v": mu["attn_in"]}
+            lw.wqkv = dev(torch.cat([get(a + f"{n}_proj.weight").float() * scale[n] for n in "qkv"], 0))
+            lw.wo = dev(get(a + "o_proj.weight").float() * mu["attn_out"])
+            if cfg.attn_bias and get(a + "q_proj.bias", False) is not None:
+                lw.bqkv = dev(torch.cat([get(a + f"{n}_proj.bias").float() * (mu["key"] if n == "k" else 1.0) for n in "qkv"]))
+                bo = get(a + "o_proj.bias", False)
+                lw.bo = dev(bo.float() * mu["attn_out"]) if bo is not None else None
+            m = p + "mamba."
+            Di, GN, Hm = s["d_inner"], s["n_groups"] * s["d_state"], s["n_heads"]
+            rows = torch.cat([torch.full((n,), float(v)) for n, v in zip((Di, Di, GN, GN, Hm), mu["ssm"])])     # z, x, B, C, dt
+            w_in, b_in = get(m + "in_proj.weight").float(), get(m + "in_proj.bias", False)
+            w_out, b_out = get(m + "out_proj.weight").float(), get(m + "out_proj.bias", False)
+            lw.mixer = pack_mamba2(w_in * rows[:, None] * mu["ssm_in"], get(m + "conv1d.weight"), get(m + "conv1d.bias", False),
+                                   get(m + "dt_bias"), get(m + "A_log"), get(m + "D"),
+                                   get(m + "norm.weight", False) if s["gate_mode"] != "gate_only" else torch.ones(Di),
+                                   w_out * mu["ssm_out"], dtype, device, b_in.float() * rows if b_in is not None else None,
+                                   b_out.float() * mu["ssm_out"] if b_out is not None else None)
+            f = p + "feed_forward."
+            lw.w_gate_up = dev(torch.cat([get(f + "gate_proj.weight").float() * mu["mlp"][0], get(f + "up_proj.weight").float()], 0))
+            lw.w_down = dev(get(f + "down_proj.weight").float() * mu["mlp"][1])
         elif mt == "bamba":
             p = f"model.layers.{l}."
             lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
@@ -237,7 +298,9 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
         layers.append(lw)
     if mt in ("mamba", "falcon_mamba", "mamba2"):
         embed, final = get("backbone.embeddings.weight"), get("backbone.norm_f.weight")
-    elif mt in ("bamba", "jamba"):
+    elif mt == "nemotron_h":
+        embed, final = get(nemo_embed or "backbone.embeddings.weight"), get(nemo_root + "norm_f.weight")
+    elif mt in ("bamba", "jamba", "falcon_h1"):
         embed, final = get("model.embed_tokens.weight"), get("model.final_layernorm.weight")
     elif mt in ("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text"):
         embed, final = get(root + "embed_tokens.weight"), get(root + "norm.weight")
@@ -249,6 +312,8 @@ def load_hf_recurrent(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
     embed_d = dev(embed)
     head_d = embed_d if (head is None or cfg.tie_embeddings) else dev(head)
     div = s.get("logits_div", 1.0) if s else 1.0
+    if mt == "falcon_h1":                                    # logits * lm_head_multiplier
+        div = 1.0 / s["mup"]["head"]
     if div != 1.0:                                           # logits / div: a head of its own, scaled once
         head_d = dev((embed if (head is None or cfg.tie_embeddings) else head).float() / div)
     return DecoderWeights(embed=embed_d, layers=layers, final_norm=dev(final), lm_head=head_d, vocab_start=0,

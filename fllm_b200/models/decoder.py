@@ -79,7 +79,7 @@ class Decoder:
         self.layer_range = layer_range or range(cfg.num_layers)
         self.first_stage, self.last_stage = first_stage, last_stage
         # the KV pool holds only this stage's attention layers
-        self.kv_index = {li: i for i, li in enumerate(l for l in self.layer_range if cfg.layer_kind(l) in ("attention", "mla"))}
+        self.kv_index = {li: i for i, li in enumerate(l for l in self.layer_range if cfg.has_kv(l))}
         dev = weights.final_norm.device
         inv, attn = rope_inv_freq(cfg)
         if not cfg.use_rope:                       # a zero frequency table turns the rotation into the identity
@@ -197,22 +197,28 @@ class Decoder:
 
     def _ffn_block(self, lw, h: torch.Tensor) -> torch.Tensor:
         cfg, ops = self.cfg, self.ops
-        if cfg.mlp_kind == "plain":               # two matrices and an activation between them
-            u = ops.act_(ops.linear(h, lw.w_gate_up, lw.b_up), cfg.act)
-            return ops.linear(u, lw.w_down, lw.b_down)
         if lw.router_w is not None:
             from .moe import moe_ffn, moe_ffn_alltoall
             if self.ep_a2a is not None:
                 self._reduced = True                 # rows come back complete: nothing left to reduce
                 return moe_ffn_alltoall(self, lw, h)
-            y = moe_ffn(self, lw, h)
-            if lw.shared_gate_up is not None:        # always-on shared experts: one dense GLU beside the routed ones
-                act = ops.linear_glu(h, lw.shared_gate_up, None, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit, 0)
+            if lw.moe_latent_in is not None:         # the router reads the hidden state, the experts a projection of it
+                y = ops.linear(moe_ffn(self, lw, h, ops.linear(h, lw.moe_latent_in)), lw.moe_latent_out)
+            else:
+                y = moe_ffn(self, lw, h)
+            if lw.shared_gate_up is not None:        # always-on shared experts: one dense MLP beside the routed ones
+                if cfg.mlp_kind == "plain":
+                    act = ops.act_(ops.linear(h, lw.shared_gate_up), cfg.act)
+                else:
+                    act = ops.linear_glu(h, lw.shared_gate_up, None, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit, 0)
                 ys = ops.linear(act, lw.shared_down)
                 if lw.shared_gate_w is not None:
                     ys = (ys.float() * torch.sigmoid(ops.linear(h, lw.shared_gate_w)[:, :1].float())).to(ys.dtype)
                 y = y + ys
             return y
+        if cfg.mlp_kind == "plain":               # two matrices and an activation between them
+            u = ops.act_(ops.linear(h, lw.w_gate_up, lw.b_up), cfg.act)
+            return ops.linear(u, lw.w_down, lw.b_down)
         act = ops.linear_glu(h, lw.w_gate_up, None, self.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit,
                              getattr(lw, "glu_layout", 0))
         return ops.linear(act, lw.w_down, defer=self._defer_out(lw.post_ffn_norm))
@@ -250,8 +256,16 @@ class Decoder:
                 if nvtx:
                     torch.cuda.nvtx.range_pop()
                 continue
+            if kind == "none":                        # a block that is only a feed-forward network behind its norm
+                delta = self._reduce(self._ffn_block(lw, h))
+                if nvtx:
+                    torch.cuda.nvtx.range_pop()
+                continue
             if kind == "attention":
                 o = self._reduce(self._attention_block(li, lw, h, b))
+            elif kind == "attention+mamba2":          # two mixers on one normed input
+                from .recurrent import mamba2_mixer
+                o = ops.materialize(self._reduce(self._attention_block(li, lw, h, b))) + mamba2_mixer(self, li, lw, h, b)
             elif kind == "mla":
                 from .mla import mla_block
                 o = mla_block(self, li, lw, h, b)

@@ -16,6 +16,9 @@ import torch.nn.functional as F
 
 
 def _act(cfg, gu: torch.Tensor) -> torch.Tensor:
+    if cfg.mlp_kind == "plain":                  # experts of two matrices: the activation alone
+        return {"gelu": F.gelu, "gelu_tanh": lambda t: F.gelu(t, approximate="tanh"), "relu2": lambda t: F.relu(t).square(),
+                "silu": F.silu, "relu": F.relu}[cfg.act](gu)
     if cfg.act == "swiglu_oai":
         g, u = gu[..., 0::2], gu[..., 1::2]
         g = g.clamp(max=cfg.swiglu_limit)
@@ -66,11 +69,15 @@ def route_reference(cfg, logits: torch.Tensor, bias: Optional[torch.Tensor] = No
     return ids.int(), w
 
 
-def moe_reference(cfg, lw, h: torch.Tensor, expert_lo: int = 0, round_bf16: bool = True) -> torch.Tensor:
-    """fp32 math on the experts stored in `lw` (global ids expert_lo .. expert_lo + E_local)."""
+def moe_reference(cfg, lw, h: torch.Tensor, expert_lo: int = 0, round_bf16: bool = True,
+                  xe: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 math on the experts stored in `lw` (global ids expert_lo .. expert_lo + E_local). ``xe``: the rows the
+    experts read when they are not the rows the router reads (a latent projection)."""
     r = (lambda t: t.to(torch.bfloat16).float()) if round_bf16 else (lambda t: t)
     hf = h.float()
     logits = hf @ lw.router_w.float().t()
+    if xe is not None:
+        hf = xe.float()
     select_bias = getattr(lw, "router_select_b", None)
     if lw.router_b is not None:
         logits = logits + lw.router_b.float()
@@ -140,13 +147,14 @@ def _router_logits(ops, lw, h: torch.Tensor) -> torch.Tensor:
     return ops.linear(h, pad[0], pad[1])[:, :E]
 
 
-def moe_ffn(dec, lw, h: torch.Tensor) -> torch.Tensor:
+def moe_ffn(dec, lw, h: torch.Tensor, xe: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``h``: the rows the router reads; ``xe``: the rows the experts read and write when they differ (None: ``h``)."""
     cfg, ops, sp = dec.cfg, dec.ops, dec.spec
     lo = sp.expert_start if sp.expert_parallel else 0
     if not hasattr(ops, "k") or not h.is_cuda:
-        return moe_reference(cfg, _dense_experts(lw), h, lo).to(h.dtype)
+        return moe_reference(cfg, _dense_experts(lw), h, lo, h.dtype != torch.float32, xe).to(h.dtype)
     k_ops = ops.k
-    T, H = h.shape
+    T, H = (h if xe is None else xe).shape
     k = cfg.experts_per_token
     e_local = lw.exp_gate_up.shape[0]
     logits = _router_logits(ops, lw, h)
@@ -174,10 +182,10 @@ def moe_ffn(dec, lw, h: torch.Tensor) -> torch.Tensor:
     ntiles = torch.zeros(2, **i32)
     k_ops.moe_align(ids, cfg.num_experts, lo, lo + e_local, bn, row_of, token_of, tile_e, tile_r, ntiles)
     xp = torch.empty(rows_cap, H, dtype=h.dtype, device=h.device)
-    k_ops.moe_gather(h, token_of, xp)
+    k_ops.moe_gather(h if xe is None else xe, token_of, xp)
     gu = torch.empty(rows_cap, lw.exp_gate_up.shape[1], dtype=h.dtype, device=h.device)
     _grouped(k_ops, ops, xp, lw.exp_gate_up, lw.exp_gate_up_b, gu, tile_e, tile_r, ntiles, bn)
-    act = ops.glu(gu, dec.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit)
+    act = ops.act_(gu, cfg.act) if cfg.mlp_kind == "plain" else ops.glu(gu, dec.act_kind, cfg.swiglu_alpha, cfg.swiglu_limit)
     y = torch.empty(rows_cap, H, dtype=h.dtype, device=h.device)
     _grouped(k_ops, ops, act, lw.exp_down, lw.exp_down_b, y, tile_e, tile_r, ntiles, bn)
     out = torch.empty(T, H, dtype=h.dtype, device=h.device)

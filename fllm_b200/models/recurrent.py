@@ -13,6 +13,7 @@ from __future__ import annotations
 from typing import Dict, Optional
 
 import torch
+import torch.nn.functional as F
 
 from ..config import ModelConfig
 from ..ops.recurrent import GATED_DELTA
@@ -22,6 +23,10 @@ RECURRENT_KINDS = ("mamba1", "mamba2", "gated_delta", "shortconv")
 
 def pad8(n: int) -> int:
     return (n + 7) // 8 * 8
+
+
+def _state_kind(kind: str) -> str:
+    return "mamba2" if kind == "attention+mamba2" else kind
 
 
 def conv_channels(cfg: ModelConfig, kind: str) -> int:
@@ -61,8 +66,8 @@ class RecurrentState:
         self.shift2: Dict[int, torch.Tensor] = {}          # RWKV: the channel mix has a token shift of its own
         W = cfg.ssm.get("d_conv", 4)
         for li in layer_range:
-            kind = cfg.layer_kind(li)
-            if kind in ("attention", "mla"):
+            kind = _state_kind(cfg.layer_kind(li))
+            if kind in ("attention", "mla", "none"):
                 continue
             if kind in ("rwkv7", "rwkv6"):
                 self.shift2[li] = torch.zeros(slots, W - 1, cfg.hidden_size, dtype=act_dtype, device=device)
@@ -76,8 +81,8 @@ class RecurrentState:
         n = 0
         W = cfg.ssm.get("d_conv", 4)
         for li in layer_range:
-            kind = cfg.layer_kind(li)
-            if kind in ("attention", "mla"):
+            kind = _state_kind(cfg.layer_kind(li))
+            if kind in ("attention", "mla", "none"):
                 continue
             n += (W - 1) * conv_channels(cfg, kind) * (4 if kind in ("rwkv7", "rwkv6") else 2)
             shape = scan_state_shape(cfg, kind)
@@ -111,7 +116,7 @@ def mamba1_mixer(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
     qs, ss, pos = _batch_meta(b)
     Di, N = s["d_inner"], s["d_state"]
     xz = ops.linear(h, m["in_proj"], m.get("in_proj_b"))
-    x = ops.causal_conv1d(xz[:, :Di], m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=True, max_q_len=b.max_q_len)
+    x = ops.causal_conv1d(xz[:, :Di], m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=True, max_q_len=getattr(b, "max_q_len", 0))
     bcd = ops.linear(x, m["x_proj"])
     Bm, Cm, dtl = bcd[:, :N], bcd[:, N:2 * N], bcd[:, 2 * N:]
     if s.get("bcdt_rms"):
@@ -134,11 +139,16 @@ def mamba2_mixer(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
     Di, N, G, H, P = s["d_inner"], s["d_state"], s["n_groups"], s["n_heads"], s["head_dim"]
     C = Di + 2 * G * N
     zxd = ops.linear(h, m["in_proj"], m.get("in_proj_b"))
-    xbc = ops.causal_conv1d(zxd[:, Di:Di + C], m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=True, max_q_len=b.max_q_len)
+    xbc = ops.causal_conv1d(zxd[:, Di:Di + C], m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=True, max_q_len=getattr(b, "max_q_len", 0))
     y = ops.mamba2_scan(xbc[:, :Di], zxd[:, Di + C:Di + C + H], xbc[:, Di:Di + G * N], xbc[:, Di + G * N:], m["A"], m["D"],
                         m["dt_bias"], dec.rstate.scan[li], qs, ss, pos, H, P, G, N, s.get("dt_min", 0.0),
                         s.get("dt_max", 1e30), getattr(b, "max_q_len", 0), None, getattr(b, "host_seqs", None))
-    y = ops.gated_rmsnorm(y, zxd[:, :Di], m["norm_w"], s.get("norm_eps", dec.cfg.rms_eps), Di // s.get("norm_groups", 1), False)
+    mode = s.get("gate_mode", "norm_after_gate")
+    if mode == "gate_only":                       # Falcon-H1 without the mixer norm: y * silu(z)
+        y = y * F.silu(zxd[:, :Di])
+    else:
+        y = ops.gated_rmsnorm(y, zxd[:, :Di], m["norm_w"], s.get("norm_eps", dec.cfg.rms_eps), Di // s.get("norm_groups", 1),
+                              mode == "norm_before_gate")
     return ops.linear(y, m["out_proj"], m.get("out_proj_b"))
 
 
@@ -151,7 +161,7 @@ def gated_delta_mixer(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
     Hk, Hv, Dk, Dv = s["num_k_heads"], s["num_v_heads"], s["head_k_dim"], s["head_v_dim"]
     K, V = Hk * Dk, Hv * Dv
     proj = ops.linear(h, m["in_proj"])                                  # [q | k | v | z | beta | a] (+ padding)
-    qkv = ops.causal_conv1d(proj[:, :2 * K + V], m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=True, max_q_len=b.max_q_len)
+    qkv = ops.causal_conv1d(proj[:, :2 * K + V], m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=True, max_q_len=getattr(b, "max_q_len", 0))
     z = proj[:, 2 * K + V:2 * K + 2 * V]
     o = 2 * K + 2 * V                                                   # the step-size and decay logits go to the scan raw
     y = ops.matrix_state_scan(GATED_DELTA, qkv[:, :K], qkv[:, K:2 * K], qkv[:, 2 * K:], None, None, None, None, proj[:, o:o + Hv],
@@ -168,7 +178,7 @@ def shortconv_mixer(dec, li: int, lw, h: torch.Tensor, b) -> torch.Tensor:
     Hd = dec.cfg.hidden_size
     bcx = ops.linear(h, m["in_proj"], m.get("in_proj_b"))
     bx = bcx[:, :Hd] * bcx[:, 2 * Hd:3 * Hd]
-    y = ops.causal_conv1d(bx, m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=False, max_q_len=b.max_q_len)
+    y = ops.causal_conv1d(bx, m["conv_w"], m.get("conv_b"), dec.rstate.conv[li], qs, ss, pos, act=False, max_q_len=getattr(b, "max_q_len", 0))
     return ops.linear(bcx[:, Hd:2 * Hd] * y, m["out_proj"], m.get("out_proj_b"))
 
 

@@ -62,7 +62,7 @@ def rwkv7_forward_hidden(dec, b):
         if "pre_norm_w" in m:
             x = _ln(x, m["pre_norm_w"], m["pre_norm_b"], eps)
         h = _ln(x, lw.attn_norm, m["attn_norm_b"], eps)
-        xx = ops.causal_conv1d(h, taps, None, st.conv[li], qs, ss, pos, act=False, max_q_len=b.max_q_len)
+        xx = ops.causal_conv1d(h, taps, None, st.conv[li], qs, ss, pos, act=False, max_q_len=getattr(b, "max_q_len", 0))
         xr, xw, xk, xv, xa, xg = (h + xx * m["x_" + c] for c in "rwkvag")
         r, k, v = lin(xr, m["r_proj"]), lin(xk, m["k_proj"]), lin(xv, m["v_proj"])
         w = (DECAY_SCALE * torch.sigmoid(lora(m, "w", xw, torch.tanh).float())).contiguous()        # fp32 log decay
@@ -83,7 +83,7 @@ def rwkv7_forward_hidden(dec, b):
         y = ((yf + bonus.view(T, C)) * g.float()).to(h.dtype)
         x = x + lin(y, m["o_proj"])
         h2 = _ln(x, lw.ffn_norm, m["ffn_norm_b"], eps)
-        xx2 = ops.causal_conv1d(h2, taps, None, st.shift2[li], qs, ss, pos, act=False, max_q_len=b.max_q_len)
+        xx2 = ops.causal_conv1d(h2, taps, None, st.shift2[li], qs, ss, pos, act=False, max_q_len=getattr(b, "max_q_len", 0))
         kx = h2 + xx2 * m["ffn_x_k"]
         x = x + lin(torch.relu(lin(kx, m["ffn_key"]).float()).square().to(h.dtype), m["ffn_value"])
     return x, None
@@ -199,7 +199,7 @@ def rwkv6_forward_hidden(dec, b):
         if "pre_norm_w" in m:
             x = _ln(x, m["pre_norm_w"], m["pre_norm_b"], eps)
         h = _ln(x, lw.attn_norm, m["attn_norm_b"], eps)
-        xx = ops.causal_conv1d(h, taps, None, st.conv[li], qs, ss, pos, act=False, max_q_len=b.max_q_len)
+        xx = ops.causal_conv1d(h, taps, None, st.conv[li], qs, ss, pos, act=False, max_q_len=getattr(b, "max_q_len", 0))
         lo = torch.tanh(lin(h + xx * m["maa_x"], m["maa_w1"]).float()).to(h.dtype)              # [T, 5 d]
         d = lo.shape[1] // 5
         xw, xk, xv, xr, xg = (h + xx * (m["maa_" + c] + lin(lo[:, j * d:(j + 1) * d].contiguous(), m["maa_w2_" + c]))
@@ -212,7 +212,7 @@ def rwkv6_forward_hidden(dec, b):
         yf = F.group_norm(y.float(), H, m["g_norm_w"], m["g_norm_b"], gn_eps)
         x = x + lin((yf * gate).to(h.dtype), m["o_proj"])
         h2 = _ln(x, lw.ffn_norm, m["ffn_norm_b"], eps)
-        xx2 = ops.causal_conv1d(h2, taps, None, st.shift2[li], qs, ss, pos, act=False, max_q_len=b.max_q_len)
+        xx2 = ops.causal_conv1d(h2, taps, None, st.shift2[li], qs, ss, pos, act=False, max_q_len=getattr(b, "max_q_len", 0))
         kk = torch.relu(lin(h2 + xx2 * m["ffn_maa_k"], m["ffn_key"]).float()).square().to(h.dtype)
         rr = torch.sigmoid(lin(h2 + xx2 * m["ffn_maa_r"], m["ffn_recept"]).float())
         x = x + (rr * lin(kk, m["ffn_value"]).float()).to(h.dtype)

@@ -45,6 +45,8 @@ class LayerWeights:
     router_select_b: Optional[torch.Tensor] = None  # [E] added to the scores for the selection only (DeepSeek-V3)
     shared_gate_up: Optional[torch.Tensor] = None   # [2*Is, H] always-on shared experts as one dense GLU
     shared_down: Optional[torch.Tensor] = None      # [H, Is]
+    moe_latent_in: Optional[torch.Tensor] = None    # [latent, H], [H, latent]: projections around the routed experts
+    moe_latent_out: Optional[torch.Tensor] = None
     shared_gate_w: Optional[torch.Tensor] = None    # [8, H] (row 0 used): sigmoid(h . w) scales the shared experts' output
     w_attn_gate: Optional[torch.Tensor] = None      # [hq*D, H] output gate of the attention (Qwen3-Next)
     # LayerNorm families: norm biases; plain MLPs keep their first matrix in w_gate_up and carry biases
@@ -271,6 +273,8 @@ def init_random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, se
             if cfg.layer_kind(li) == "mla":
                 from .mla import init_random_mla
                 mixer = init_random_mla(cfg, full, li, dtype, device)
+            elif cfg.layer_kind(li) == "none":
+                mixer = None
             else:
                 mixer = init_random_mixer(cfg, cfg.layer_kind(li), full, li, dtype, device)
             lw = LayerWeights(attn_norm=ones(H), wqkv=None, wo=None, ffn_norm=ones(H) if has_ffn else None, mixer=mixer)

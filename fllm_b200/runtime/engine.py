@@ -188,7 +188,7 @@ class LLMEngine:
     # ------------------------------------------------------------------ sizing
     def _kv_layers(self) -> int:
         """Attention layers of this stage (at least one, so that the pool tensors exist)."""
-        return max(1, sum(1 for li in self.layer_range if self.model_cfg.layer_kind(li) in ("attention", "mla")))
+        return max(1, sum(1 for li in self.layer_range if self.model_cfg.has_kv(li)))
 
     def _size_kv_pool(self) -> int:
         per_block = KVCache.bytes_per_block(self._kv_layers(), self.spec.hkv_local,

@@ -46,10 +46,21 @@ def _model(kind):
                                                            linear_value_head_dim=64, linear_num_key_heads=2, linear_num_value_heads=4,
                                                            moe_intermediate_size=128, shared_expert_intermediate_size=128,
                                                            num_experts_per_tok=2, num_experts=4, layer_types=["linear_attention", "full_attention"]))
+    if kind in ("nemotron_h", "nemotron_h_latent"):
+        return tf.NemotronHForCausalLM(tf.NemotronHConfig(
+            vocab_size=512, hidden_size=256, layers_block_type=["mamba", "moe", "attention", "moe"], num_attention_heads=4,
+            num_key_value_heads=2, head_dim=64, intermediate_size=512, ssm_state_size=128, mamba_num_heads=8, mamba_head_dim=64,
+            n_groups=2, n_routed_experts=8, moe_intermediate_size=128, moe_shared_expert_intermediate_size=256,
+            num_experts_per_tok=2, moe_latent_size=128 if kind.endswith("latent") else None, max_position_embeddings=512))
+    if kind == "falcon_h1":
+        return tf.FalconH1ForCausalLM(tf.FalconH1Config(**BASE, mamba_d_ssm=512, mamba_n_heads=8, mamba_n_groups=2, mamba_d_state=128,
+                                                        ssm_multipliers=[0.9, 1.1, 1.2, 0.8, 1.3], attention_in_multiplier=1.2,
+                                                        ssm_out_multiplier=0.6, embedding_multiplier=2.5))
     raise ValueError(kind)
 
 
-@pytest.mark.parametrize("kind", ["llama_odd_vocab", "gpt2", "phi", "gpt_neox", "nemotron", "starcoder2", "cohere", "olmo2", "glm", "gemma3", "qwen2_moe", "jamba", "qwen3_next"])
+@pytest.mark.parametrize("kind", ["llama_odd_vocab", "gpt2", "phi", "gpt_neox", "nemotron", "starcoder2", "cohere", "olmo2", "glm", "gemma3", "qwen2_moe", "jamba", "qwen3_next", "nemotron_h",
+                                  "nemotron_h_latent", "falcon_h1"])
 def test_native_operators_match_reference_operators(tmp_path, kind):
     from fllm_b200.config import EngineConfig
     from fllm_b200.formats.loader import load_hf_checkpoint
@@ -58,7 +69,7 @@ def test_native_operators_match_reference_operators(tmp_path, kind):
     m = _model(kind).eval()
     with torch.no_grad():
         for n, p in m.named_parameters():
-            if n.endswith(("mlp.gate.weight", "router.weight")):
+            if n.endswith(("mlp.gate.weight", "router.weight", "mixer.gate.weight")):
                 p.mul_(20.0)                                   # clear routing decisions: bf16 scores must not flip experts
     d = str(tmp_path / kind)
     m.save_pretrained(d, safe_serialization=True)
@@ -70,6 +81,6 @@ def test_native_operators_match_reference_operators(tmp_path, kind):
     toks = torch.randint(0, min(512, cfg.vocab_size), (150,), generator=torch.Generator().manual_seed(3)).tolist()
     a, b = nat.token_logits(toks), ref.token_logits(toks)
     err = (a - b).norm(dim=1) / b.norm(dim=1)
-    routed = kind in ("qwen2_moe", "jamba", "qwen3_next")
+    routed = kind in ("qwen2_moe", "jamba", "qwen3_next", "nemotron_h", "nemotron_h_latent")
     assert float(err.median()) < 3e-2 and int((err > 0.15).sum()) <= (3 if routed else 0), err
     assert int(nat.ops.status.item()) == 0

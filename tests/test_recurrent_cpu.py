@@ -611,3 +611,95 @@ def test_ernie4_5_moe_matches_transformers(tmp_path):
         want = m(torch.tensor([toks])).logits[0].float()
     err = (got - want).abs().max(dim=1).values / float(want.abs().max())
     assert float(err.median()) < 1e-2 and int((err > 5e-2).sum()) <= 2, err
+
+
+def _nemotron_h(latent, hidden=64, vocab=300):
+    import transformers as tf
+    torch.manual_seed(0)
+    m = tf.NemotronHForCausalLM(tf.NemotronHConfig(
+        vocab_size=vocab, hidden_size=hidden, layers_block_type=["mamba", "moe", "attention", "moe", "mamba"], num_attention_heads=4,
+        num_key_value_heads=2, head_dim=hidden // 4, intermediate_size=2 * hidden, ssm_state_size=16, mamba_num_heads=8,
+        mamba_head_dim=hidden // 4, n_groups=2, n_routed_experts=8, moe_intermediate_size=hidden // 2,
+        moe_shared_expert_intermediate_size=hidden, num_experts_per_tok=2, moe_latent_size=latent, routed_scaling_factor=1.5)).eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "norm" in n:
+                p.add_(0.3 * torch.randn_like(p))
+            if n.endswith(("q_proj.weight", "k_proj.weight")):
+                p.mul_(12.0)
+            if "experts." in n and p.dim() == 3:
+                p.normal_(0, 0.2)
+            if n.endswith("gate.weight"):
+                p.normal_(0, 1.0)
+        for n, b in m.named_buffers():
+            if n.endswith("e_score_correction_bias"):
+                b.normal_(0, 0.2)
+    return m
+
+
+@pytest.mark.parametrize("latent", [None, 32])
+def test_nemotron_h_matches_transformers(tmp_path, latent):
+    """Nemotron-H: one mixer per block (Mamba-2 with a grouped gated norm, attention without rotary embedding, a mixture of
+    two-matrix relu^2 experts behind a sigmoid router with a selection bias, with and without the latent projection
+    around the routed experts, a shared MLP on the hidden state)."""
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    m = _nemotron_h(latent)
+    d = str(tmp_path / "nemotron_h")
+    m.save_pretrained(d, safe_serialization=True)
+    cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
+    assert cfg.layer_kinds == ["mamba2", "none", "attention", "none", "mamba2"] and cfg.ffn_kinds == ["none", "moe", "none", "moe", "none"]
+    assert not cfg.use_rope and cfg.mlp_kind == "plain" and cfg.act == "relu2" and cfg.moe_latent_size == (latent or 0)
+    assert (w.layers[1].moe_latent_in is not None) == bool(latent) and w.layers[1].exp_gate_up.shape[1] == 32
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16,
+                                      kv_cache_dtype="fp32"), device="cpu", weights=w)
+    toks = torch.randint(0, 300, (45,), generator=torch.Generator().manual_seed(1)).tolist()
+    got = eng.token_logits(toks)
+    with torch.no_grad():
+        want = m(torch.tensor([toks])).logits[0].float()
+    assert float((got - want).abs().max() / want.abs().max()) < 2e-3
+
+
+def test_nemotron_h_pattern_string():
+    """Older configs spell the blocks as a pattern string: M Mamba-2, * attention, - MLP, E experts."""
+    from fllm_b200.config import ModelConfig
+    cfg = ModelConfig.from_hf_config(dict(model_type="nemotron_h", vocab_size=300, hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
+                                   hybrid_override_pattern="M-M*-", intermediate_size=128, mamba_num_heads=8, mamba_head_dim=16,
+                                   ssm_state_size=16, n_groups=2))
+    assert cfg.layer_kinds == ["mamba2", "none", "mamba2", "attention", "none"] and cfg.ffn_kinds == ["none", "glu", "none", "none", "glu"]
+    assert cfg.num_experts == 0 and cfg.num_layers == 5 and cfg.has_recurrent
+
+
+@pytest.mark.parametrize("norm,before,bias", [(False, True, False), (True, True, True), (True, False, False)])
+def test_falcon_h1_matches_transformers(tmp_path, norm, before, bias):
+    """Falcon-H1: Mamba-2 and attention read the same normed input and their outputs add; every mu-P multiplier (embeddings,
+    head, the five sections of the mixer's input projection, its input and output, attention input / keys / output, the
+    MLP's gate and output) is folded into the weights; the mixer's gate with no norm, norm then gate, gate then norm."""
+    import transformers as tf
+    from fllm_b200.formats.loader import load_hf_checkpoint
+    torch.manual_seed(0)
+    m = tf.FalconH1ForCausalLM(tf.FalconH1Config(
+        vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+        mamba_d_ssm=96, mamba_n_heads=6, mamba_n_groups=2, mamba_d_state=16, mamba_rms_norm=norm, mamba_norm_before_gate=before,
+        mamba_proj_bias=bias, attention_bias=bias, lm_head_multiplier=0.7, embedding_multiplier=2.5, mlp_multipliers=[0.8, 1.3],
+        key_multiplier=1.7, attention_out_multiplier=0.9, attention_in_multiplier=1.2, ssm_multipliers=[0.9, 1.1, 1.2, 0.8, 1.3],
+        ssm_in_multiplier=1.4, ssm_out_multiplier=0.6, max_position_embeddings=256)).eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "norm" in n:
+                p.add_(0.3 * torch.randn_like(p))
+            if n.endswith(("q_proj.weight", "k_proj.weight")):
+                p.mul_(12.0)
+            if n.endswith("bias") and "conv" not in n and "dt_" not in n:
+                p.normal_(0, 0.1)
+    d = str(tmp_path / "falcon_h1")
+    m.save_pretrained(d, safe_serialization=True)
+    cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
+    assert cfg.layer_kinds == ["attention+mamba2"] * 2 and cfg.has_recurrent and cfg.has_kv(1)
+    assert cfg.ssm["gate_mode"] == ("gate_only" if not norm else "norm_before_gate" if before else "norm_after_gate")
+    eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16,
+                                      kv_cache_dtype="fp32"), device="cpu", weights=w)
+    toks = torch.randint(0, 300, (45,), generator=torch.Generator().manual_seed(1)).tolist()
+    got = eng.token_logits(toks)
+    with torch.no_grad():
+        want = m(torch.tensor([toks])).logits[0].float()
+    assert float((got - want).abs().max() / want.abs().max()) < 2e-3
