@@ -18,7 +18,7 @@ from typing import Any, Dict, List, Optional, Sequence
 
 @dataclass
 class RopeScaling:
-    kind: str = "none"            # none | linear | llama3 | yarn
+    kind: str = "none"            # none | linear | llama3 | yarn | factors (one divisor per frequency, as GGUF files store it)
     factor: float = 1.0
     low_freq_factor: float = 1.0
     high_freq_factor: float = 4.0
@@ -26,6 +26,8 @@ class RopeScaling:
     beta_fast: float = 32.0
     beta_slow: float = 1.0
     attn_factor: Optional[float] = None
+    truncate: bool = True         # YaRN: the two correction dimensions are rounded outward (False: GPT-OSS keeps them fractional)
+    freq_factors: Optional[List[float]] = None
 
 
 @dataclass
@@ -228,7 +230,7 @@ class ModelConfig:
                 high_freq_factor=rs.get("high_freq_factor", 4.0),
                 original_max_position=rs.get("original_max_position_embeddings", 8192),
                 beta_fast=rs.get("beta_fast", 32.0), beta_slow=rs.get("beta_slow", 1.0),
-                attn_factor=rs.get("attention_factor"))
+                attn_factor=rs.get("attention_factor"), truncate=bool(rs.get("truncate", True)))
         if mt == "gpt_oss":
             cfg.act = "swiglu_oai"
             cfg.attn_sinks = True
@@ -248,6 +250,9 @@ class ModelConfig:
             # Mixtral: softmax over the selected logits. Qwen-MoE: softmax over all experts, then the selected
             # probabilities renormalised (norm_topk_prob)
             cfg.router_kind = "softmax_topk" if mt == "mixtral" else "softmax_all"
+            if mt in ("qwen2_moe", "qwen3_moe") and not hf.get("norm_topk_prob", False):
+                # the selected probabilities are used as they are (Qwen1.5-MoE, Qwen2-57B-A14B): the score-weighted router
+                cfg.router_kind, cfg.router_norm_topk, cfg.router_scale = "deepseek_v2", False, 1.0
         if mt in ("gemma", "gemma2", "gemma3_text"):
             cfg.norm_weight_offset = 1.0
             cfg.embed_scale = float(hidden) ** 0.5
@@ -414,7 +419,8 @@ def mla_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
         if af is None and rs.get("mscale") and rs.get("mscale_all_dim"):
             af = _yarn_mscale(f, rs["mscale"]) / _yarn_mscale(f, rs["mscale_all_dim"])
         cfg.rope_scaling = RopeScaling(kind="yarn", factor=f, original_max_position=rs.get("original_max_position_embeddings", 4096),
-                                       beta_fast=rs.get("beta_fast", 32.0), beta_slow=rs.get("beta_slow", 1.0), attn_factor=af)
+                                       beta_fast=rs.get("beta_fast", 32.0), beta_slow=rs.get("beta_slow", 1.0), attn_factor=af,
+                                       truncate=bool(rs.get("truncate", True)))
         if mt == "deepseek_v3" and rs.get("mscale_all_dim"):        # V3 also scales the softmax by mscale squared
             cfg.attn_scale = (dn + dr) ** -0.5 * _yarn_mscale(f, rs["mscale_all_dim"]) ** 2
     return cfg
@@ -572,7 +578,8 @@ def recurrent_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
                    layer_kinds=["attention" if k == "full_attention" else "gated_delta" for k in kinds],
                    ffn_kinds=["moe" if (E > 0 and i not in dense and (i + 1) % step == 0) else "glu" for i in range(L)],
                    num_experts=E, experts_per_token=hf.get("num_experts_per_tok", 10),
-                   moe_intermediate_size=hf.get("moe_intermediate_size", 512), router_kind="softmax_all",
+                   moe_intermediate_size=hf.get("moe_intermediate_size", 512),
+                   router_kind="softmax_all" if hf.get("norm_topk_prob", True) else "deepseek_v2", router_norm_topk=False,
                    shared_intermediate_size=hf.get("shared_expert_intermediate_size", 0) if E else 0, shared_gate=bool(E),
                    ssm=dict(num_k_heads=hf.get("linear_num_key_heads", 16), num_v_heads=hf.get("linear_num_value_heads", 32),
                             head_k_dim=hf.get("linear_key_head_dim", 128), head_v_dim=hf.get("linear_value_head_dim", 128),
@@ -668,6 +675,10 @@ def rope_inv_freq(cfg: ModelConfig) -> "tuple[List[float], float]":
     attn = 1.0
     if rs.kind == "linear":
         base = [f / rs.factor for f in base]
+    elif rs.kind == "factors":
+        if len(rs.freq_factors or ()) != len(base):
+            raise ValueError(f"rope frequency factors: {len(rs.freq_factors or ())} values for {len(base)} frequencies")
+        base = [f / d for f, d in zip(base, rs.freq_factors)]
     elif rs.kind == "llama3":
         lo_wl = rs.original_max_position / rs.low_freq_factor
         hi_wl = rs.original_max_position / rs.high_freq_factor
@@ -687,8 +698,10 @@ def rope_inv_freq(cfg: ModelConfig) -> "tuple[List[float], float]":
         def corr_dim(n_rot: float) -> float:
             return (rot * math.log(rs.original_max_position / (n_rot * 2 * math.pi))) / (
                 2 * math.log(cfg.rope_theta))
-        lo = max(math.floor(corr_dim(rs.beta_fast)), 0)
-        hi = min(math.ceil(corr_dim(rs.beta_slow)), rot // 2 - 1)
+        lo, hi = corr_dim(rs.beta_fast), corr_dim(rs.beta_slow)
+        if rs.truncate:
+            lo, hi = math.floor(lo), math.ceil(hi)
+        lo, hi = max(lo, 0), min(hi, rot - 1)
         out = []
         for i, f in enumerate(base):
             ramp = min(max((i - lo) / max(hi - lo, 1e-3), 0.0), 1.0)
@@ -737,7 +750,7 @@ def preset(name: str) -> ModelConfig:
                            num_experts=8 if tiny else 128, experts_per_token=4,
                            moe_intermediate_size=256 if tiny else 2880, weight_format="bf16",
                            rope_scaling=RopeScaling(kind="yarn", factor=32.0, beta_fast=32.0,
-                                                    beta_slow=1.0, original_max_position=4096),
+                                                    beta_slow=1.0, original_max_position=4096, truncate=False),
                            max_position=131072)
     if n in ("mamba2-2.7b", "mamba2-tiny"):
         tiny = n.endswith("tiny")

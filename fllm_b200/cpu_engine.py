@@ -10,7 +10,7 @@ from typing import List, Optional, Sequence
 
 import numpy as np
 
-from .config import ModelConfig, preset
+from .config import ModelConfig, RopeScaling, preset
 from .formats import quant
 from .formats.gguf import TYPE_ID, GgufReader, GgufWriter
 from .ops._lib import load_cpu
@@ -87,7 +87,19 @@ def config_from_gguf(r: GgufReader) -> ModelConfig:
     vocab = g("vocab_size")
     if vocab is None:
         vocab = r.tensors["token_embd.weight"].shape[0]
+    head_dim = int(g("attention.key_length", hidden // heads))
+    rot = g("rope.dimension_count")
+    scaling = RopeScaling()
+    kind = g("rope.scaling.type")
+    if kind in ("linear", "yarn"):
+        scaling = RopeScaling(kind=kind, factor=float(g("rope.scaling.factor", 1.0)),
+                              original_max_position=int(g("rope.scaling.original_context_length", g("context_length", 4096))),
+                              beta_fast=float(m.get("fllm.rope.yarn_beta_fast", 32.0)), beta_slow=float(m.get("fllm.rope.yarn_beta_slow", 1.0)),
+                              truncate=bool(m.get("fllm.rope.yarn_truncate", True)), attn_factor=m.get("fllm.rope.yarn_attn_factor"))
+    elif "rope_freqs.weight" in r.tensors:         # one divisor per frequency (Llama-3 style scaling, stored as a tensor)
+        scaling = RopeScaling(kind="factors", freq_factors=[float(v) for v in r.tensor_f32("rope_freqs.weight").reshape(-1)])
     return ModelConfig(
+        rope_scaling=scaling, rotary_dim=int(rot) if rot is not None and int(rot) != head_dim else None,
         arch="llama" if arch not in ("qwen3", "gpt_oss") else arch, name=str(m.get("general.name", arch)),
         vocab_size=int(vocab), hidden_size=hidden, num_layers=int(g("block_count")), num_heads=heads,
         num_kv_heads=int(g("attention.head_count_kv", heads)), head_dim=int(g("attention.key_length", hidden // heads)),

@@ -148,6 +148,26 @@ def convert_checkpoint(directory: str, out_path: str, out_type: str = "F16") -> 
     w.add(f"{arch}.rope.freq_base", float(cfg.rope_theta))
     w.add("fllm.rope_style", 0 if cfg.rope_style == "neox" else 1)
     w.add("fllm.tie_embeddings", bool(cfg.tie_embeddings))
+    if cfg.rotary_dim and cfg.rotary_dim != cfg.head_dim:
+        w.add(f"{arch}.rope.dimension_count", int(cfg.rotary_dim))
+    rs = cfg.rope_scaling
+    if rs.kind in ("linear", "yarn"):            # the keys llama.cpp reads; the YaRN ramp ends and factor under keys of this project
+        w.add(f"{arch}.rope.scaling.type", rs.kind)
+        w.add(f"{arch}.rope.scaling.factor", float(rs.factor))
+        w.add(f"{arch}.rope.scaling.original_context_length", int(rs.original_max_position))
+        if rs.kind == "yarn":
+            w.add("fllm.rope.yarn_beta_fast", float(rs.beta_fast))
+            w.add("fllm.rope.yarn_beta_slow", float(rs.beta_slow))
+            w.add("fllm.rope.yarn_truncate", bool(rs.truncate))
+            if rs.attn_factor is not None:
+                w.add("fllm.rope.yarn_attn_factor", float(rs.attn_factor))
+    elif rs.kind in ("llama3", "factors"):       # one divisor per frequency, the tensor llama.cpp calls rope_freqs
+        from ..config import RopeScaling, rope_inv_freq as rope_frequencies
+        import copy
+        plain = copy.copy(cfg)
+        plain.rope_scaling = RopeScaling()
+        div = np.asarray(rope_frequencies(plain)[0], dtype=np.float64) / np.asarray(rope_frequencies(cfg)[0], dtype=np.float64)
+        w.add_tensor("rope_freqs.weight", (len(div),), TYPE_ID["F32"], div.astype(np.float32))
     has_tok = _tokenizer_metadata(directory, w, cfg.vocab_size)
     counts: Dict[str, int] = {}
     skipped: List[str] = []

@@ -56,6 +56,31 @@ def test_convert_bf16_reloads_as_the_same_model(hf_dir, tmp_path):
     assert torch.equal(w_g.lm_head, w_h.lm_head)
 
 
+@pytest.mark.parametrize("scaling", [
+    dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=64),
+    dict(rope_type="yarn", factor=32.0, beta_fast=32.0, beta_slow=1.0, truncate=False, original_max_position_embeddings=128),
+    dict(rope_type="linear", factor=4.0)])
+def test_convert_keeps_the_rope_scaling(hf_dir, tmp_path, scaling):
+    """The converted file rotates with the frequencies of the directory it came from: Llama-3 scaling as one divisor
+    per frequency (the rope_freqs tensor), linear and YaRN scaling as metadata (with the YaRN ramp's rounding mode)."""
+    from fllm_b200.config import rope_inv_freq
+    d, _ = hf_dir
+    d2 = str(tmp_path / "scaled")
+    os.makedirs(d2)
+    os.symlink(os.path.join(d, "model.safetensors"), os.path.join(d2, "model.safetensors"))
+    hf = json.load(open(os.path.join(d, "config.json")))
+    json.dump(dict(hf, rope_scaling=scaling), open(os.path.join(d2, "config.json"), "w"))
+    out = str(tmp_path / "scaled.gguf")
+    convert_checkpoint(d2, out, "BF16")
+    cfg_g, _, _ = load_gguf(out, "cpu")
+    cfg_h, _, _ = load_hf_checkpoint(d2, "cpu")
+    assert cfg_h.rope_scaling.kind == scaling["rope_type"]
+    assert cfg_g.rope_scaling.kind == ("factors" if scaling["rope_type"] == "llama3" else scaling["rope_type"])
+    (fg, ag), (fh, ah) = rope_inv_freq(cfg_g), rope_inv_freq(cfg_h)
+    assert ag == pytest.approx(ah) and fg == pytest.approx(fh, rel=1e-6)
+    assert fh != pytest.approx(rope_inv_freq(load_hf_checkpoint(d, "cpu")[0])[0], rel=1e-3)      # the scaling does something
+
+
 @pytest.mark.parametrize("qt", ["Q4_K", "Q5_0", "Q3_K", "IQ4_NL"])
 def test_convert_quantised_and_requantise(hf_dir, tmp_path, qt):
     d, cfg = hf_dir

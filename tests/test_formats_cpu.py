@@ -311,7 +311,7 @@ def test_model_families_load_from_hf_style_checkpoints(tmp_path, family):
     elif family == "qwen3_moe":
         cfg = ModelConfig(**base, arch="qwen3", qk_norm=True, num_experts=4, experts_per_token=2, moe_intermediate_size=96,
                           router_kind="softmax_all")
-        extra, style = {"model_type": "qwen3_moe", "num_experts": 4, "num_experts_per_tok": 2, "moe_intermediate_size": 96}, "qwen"
+        extra, style = {"model_type": "qwen3_moe", "num_experts": 4, "num_experts_per_tok": 2, "moe_intermediate_size": 96, "norm_topk_prob": True}, "qwen"
     elif family == "qwen2":
         cfg = ModelConfig(**base, attn_bias=True)
         extra, style = {"model_type": "qwen2"}, None
