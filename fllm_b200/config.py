@@ -86,6 +86,7 @@ class ModelConfig:
     learned_positions: bool = False      # a learned position table is added to the token embeddings (GPT-2, OPT)
     position_offset: int = 0
     qk_norm_full: bool = False           # RMSNorm over the whole q and the whole k projection (all heads at once, OLMo-2)
+    clip_qkv: float = 0.0                # > 0: the q / k / v projections are clamped to [-clip, clip] (OLMo)
     mlp_kind: str = "glu"                # glu | plain
     parallel_block: bool = False
     parallel_norms: int = 1              # parallel blocks: 1 = attention and MLP read the same normed input, 2 = a norm each
@@ -250,10 +251,12 @@ class ModelConfig:
             # Mixtral: softmax over the selected logits. Qwen-MoE: softmax over all experts, then the selected
             # probabilities renormalised (norm_topk_prob)
             cfg.router_kind = "softmax_topk" if mt == "mixtral" else "softmax_all"
-            if mt in ("qwen2_moe", "qwen3_moe") and not hf.get("norm_topk_prob", False):
+            if mt in ("qwen2_moe", "qwen3_moe", "olmoe") and not hf.get("norm_topk_prob", False):
                 # the selected probabilities are used as they are (Qwen1.5-MoE, Qwen2-57B-A14B): the score-weighted router
                 cfg.router_kind, cfg.router_norm_topk, cfg.router_scale = "deepseek_v2", False, 1.0
-        if mt in ("gemma", "gemma2", "gemma3_text"):
+        if mt == "olmoe":                     # OLMoE: q and k normalised over all heads, optional clamp of q / k / v
+            cfg.qk_norm_full, cfg.clip_qkv = True, float(hf.get("clip_qkv") or 0.0)
+        if mt in ("gemma", "gemma2", "gemma3_text", "vaultgemma"):
             cfg.norm_weight_offset = 1.0
             cfg.embed_scale = float(hidden) ** 0.5
             cfg.act = "geglu"
@@ -267,8 +270,8 @@ class ModelConfig:
                 pat = hf.get("sliding_window_pattern", 6)
                 hf = dict(hf, layer_types=["full_attention" if (i + 1) % pat == 0 else "sliding_attention"
                                            for i in range(hf["num_hidden_layers"])])
-        if mt in ("gemma2", "gemma3_text"):
-            cfg.post_norms = True
+        if mt in ("gemma2", "gemma3_text", "vaultgemma"):
+            cfg.post_norms = mt != "vaultgemma"           # VaultGemma: Gemma-2 without the norms behind the blocks
             if hf.get("query_pre_attn_scalar"):
                 cfg.attn_scale = float(hf["query_pre_attn_scalar"]) ** -0.5
             if hf.get("sliding_window"):
@@ -300,11 +303,12 @@ class ModelConfig:
 
 # decoder families whose layers are attention + gated FFN (or routed experts) and that the generic mapping covers; every one
 # of them is checked against `transformers` in tests/test_hf_parity_cpu.py
-ATTENTION_MODEL_TYPES = ("llama", "mistral", "ministral", "qwen2", "qwen3", "qwen2_moe", "qwen3_moe", "mixtral", "gemma", "gemma2",
-                         "gemma3_text", "phi3", "gpt_oss", "granite", "seed_oss", "glm", "glm4", "ernie4_5", "helium", "smollm3")
+ATTENTION_MODEL_TYPES = ("llama", "mistral", "ministral", "qwen2", "qwen3", "qwen2_moe", "qwen3_moe", "olmoe", "mixtral", "gemma", "gemma2",
+                         "gemma3_text", "vaultgemma", "phi3", "gpt_oss", "granite", "seed_oss", "glm", "glm4", "ernie4_5", "helium", "smollm3")
 
 
-CLASSIC_MODEL_TYPES = ("starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "olmo2", "olmo3", "gpt2", "opt")
+CLASSIC_MODEL_TYPES = ("starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "cohere2", "olmo", "olmo2", "olmo3", "exaone4", "gpt2",
+                       "gpt_bigcode", "opt")
 _ACT_NAMES = {"gelu": "gelu", "gelu_new": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh", "gelu_fast": "gelu_tanh", "relu2": "relu2",
               "silu": "silu", "swish": "silu", "relu": "relu"}
 
@@ -313,7 +317,7 @@ def classic_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     """Families built from LayerNorm, plain MLPs or parallel blocks (the reference covers them through the same decoder,
     rust/engine/src/config.rs fields `norm`, `ffn`, `parallel_residual`)."""
     mt = hf["model_type"]
-    if mt == "gpt2":                      # its own field names
+    if mt in ("gpt2", "gpt_bigcode"):     # their own field names
         hf = dict(hf, hidden_size=hf["n_embd"], num_hidden_layers=hf["n_layer"], num_attention_heads=hf["n_head"],
                   intermediate_size=hf.get("n_inner") or 4 * hf["n_embd"], max_position_embeddings=hf.get("n_positions", 1024),
                   hidden_act=hf.get("activation_function", "gelu_new"))
@@ -356,12 +360,17 @@ def classic_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
         cfg.norm_kind, cfg.mlp_kind, cfg.act, cfg.rms_eps = "layernorm", "plain", act, hf.get("layer_norm_eps", 1e-5)
         cfg.parallel_block, cfg.parallel_norms = bool(hf.get("use_parallel_residual", True)), 2
         cfg.attn_bias, cfg.mlp_bias = bool(hf.get("attention_bias", True)), True
-    elif mt in ("gpt2", "opt"):           # learned absolute positions, LayerNorm, plain MLP, biases everywhere, tied head
+    elif mt in ("gpt2", "opt", "gpt_bigcode"):           # learned absolute positions, LayerNorm, plain MLP, biases everywhere, tied head
         cfg.norm_kind, cfg.mlp_kind, cfg.act = "layernorm", "plain", act
         cfg.rms_eps = hf.get("layer_norm_epsilon", 1e-5)
         cfg.use_rope, cfg.learned_positions, cfg.attn_bias, cfg.mlp_bias = False, True, True, True
         cfg.position_offset = 2 if mt == "opt" else 0            # OPT's table starts two rows in
         cfg.tie_embeddings = hf.get("tie_word_embeddings", True)
+        if mt == "gpt_bigcode" and hf.get("multi_query", True):          # one key / value head for all query heads
+            cfg.num_kv_heads = 1
+    elif mt == "olmo":                    # LayerNorm without weights, optionally clamped q / k / v
+        cfg.norm_kind, cfg.rms_eps, cfg.attn_bias = "layernorm_nobias", 1e-5, bool(hf.get("attention_bias", False))
+        cfg.clip_qkv = float(hf.get("clip_qkv") or 0.0)
     elif mt in ("olmo2", "olmo3"):        # no norm in front of a block: its output is normalised instead; q and k normalised over all heads
         cfg.norm_kind, cfg.post_norms, cfg.qk_norm_full, cfg.rms_eps = "none", True, True, hf.get("rms_norm_eps", 1e-6)
         cfg.attn_bias = bool(hf.get("attention_bias", False))
@@ -369,13 +378,26 @@ def classic_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
         if mt == "olmo3" and hf.get("sliding_window") and lt:
             cfg.sliding_window = int(hf["sliding_window"])
             cfg.window_pattern = [1 if t == "sliding_attention" else 0 for t in lt]
-    elif mt == "cohere":
+    elif mt == "exaone4":                 # blocks normalised at their output, per-head QK-norm, windowed layers rotate and global ones do not
+        cfg.norm_kind, cfg.post_norms, cfg.qk_norm, cfg.rms_eps = "none", True, True, hf.get("rms_norm_eps", 1e-5)
+        lt = hf.get("layer_types")
+        if hf.get("sliding_window") and lt and "sliding_attention" in lt:
+            cfg.sliding_window = int(hf["sliding_window"])
+            cfg.window_pattern = [1 if t == "sliding_attention" else 0 for t in lt]
+            cfg.rope_layers = list(cfg.window_pattern)
+    elif mt in ("cohere", "cohere2"):
         if hf.get("use_qk_norm"):
             raise NotImplementedError("cohere with QK norm is not supported")
         cfg.norm_kind, cfg.rms_eps, cfg.parallel_block, cfg.parallel_norms = "layernorm_nobias", hf.get("layer_norm_eps", 1e-5), True, 1
         cfg.rope_style, cfg.tie_embeddings = "pair", hf.get("tie_word_embeddings", True)
         cfg.attn_bias = bool(hf.get("attention_bias", False))
         cfg.ssm = dict(logit_mult=float(hf.get("logit_scale") or 1.0))       # folded into the head at load
+        if mt == "cohere2":               # windowed layers rotate, the global ones carry no position signal
+            pat = hf.get("sliding_window_pattern", 4)
+            lt = hf.get("layer_types") or ["sliding_attention" if (i + 1) % pat else "full_attention" for i in range(L)]
+            cfg.window_pattern = [1 if t == "sliding_attention" else 0 for t in lt]
+            cfg.rope_layers = list(cfg.window_pattern)
+            cfg.sliding_window = int(hf.get("sliding_window") or 4096)
     return cfg
 
 

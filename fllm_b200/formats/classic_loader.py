@@ -26,10 +26,14 @@ _NAMES = {
     "gpt_neox": ("gpt_neox.layers.{}.", "attention.", "query_key_value", "dense", "input_layernorm", "post_attention_layernorm",
                  "mlp.dense_h_to_4h", "mlp.dense_4h_to_h"),
     "cohere": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", "input_layernorm", None, None, "mlp.down_proj"),
+    "cohere2": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", "input_layernorm", None, None, "mlp.down_proj"),
+    "olmo": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", None, None, None, "mlp.down_proj"),
+    "gpt_bigcode": ("transformer.h.{}.", "attn.", "c_attn", "c_proj", "ln_1", "ln_2", "mlp.c_fc", "mlp.c_proj"),
     "gpt2": ("transformer.h.{}.", "attn.", "c_attn", "c_proj", "ln_1", "ln_2", "mlp.c_fc", "mlp.c_proj"),
     "opt": ("model.decoder.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "out_proj", "self_attn_layer_norm", "final_layer_norm",
             "fc1", "fc2"),
     "olmo2": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", None, None, None, "mlp.down_proj"),
+    "exaone4": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", None, None, None, "mlp.down_proj"),
     "olmo3": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", None, None, None, "mlp.down_proj"),
 }
 
@@ -59,9 +63,13 @@ def load_hf_classic(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
         lw = LayerWeights(attn_norm=dev(get(p + n1 + ".weight")) if n1 else None, wqkv=None, wo=None,
                           ffn_norm=dev(get(p + n2 + ".weight")) if n2 else None)
         lw.attn_norm_b, lw.ffn_norm_b = opt(p + n1 + ".bias") if n1 else None, opt(p + n2 + ".bias") if n2 else None
+        if cfg.arch == "olmo":                  # LayerNorm without parameters
+            lw.attn_norm = lw.ffn_norm = torch.ones(H, device=device, dtype=dtype)
         if cfg.post_norms:                      # OLMo-2: the norms sit behind the blocks
             lw.post_attn_norm = dev(get(p + "post_attention_layernorm.weight"))
             lw.post_ffn_norm = dev(get(p + "post_feedforward_layernorm.weight"))
+        if cfg.qk_norm:
+            lw.q_norm, lw.k_norm = dev(get(p + ap + "q_norm.weight")), dev(get(p + ap + "k_norm.weight"))
         if cfg.qk_norm_full:
             lw.q_norm_full, lw.k_norm_full = dev(get(p + ap + "q_norm.weight")), dev(get(p + ap + "k_norm.weight"))
         if isinstance(qkv, tuple):
@@ -69,7 +77,7 @@ def load_hf_classic(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
             bs = [get(p + ap + n + ".bias", False) for n in qkv]
             if bs[0] is not None:
                 lw.bqkv = dev(torch.cat(bs))
-        elif cfg.arch == "gpt2":                # one matrix: all q rows, all k rows, all v rows
+        elif cfg.arch == "gpt2" or (cfg.arch == "gpt_bigcode" and hkv == 1):      # one matrix: all q rows, all k rows, all v rows
             lw.wqkv, lw.bqkv = dev(get(p + ap + qkv + ".weight")), opt(p + ap + qkv + ".bias")
         else:                                   # GPT-NeoX: one matrix whose rows go head by head as (q, k, v)
             w = get(p + ap + qkv + ".weight").view(hq, 3, D, H)
@@ -85,7 +93,7 @@ def load_hf_classic(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
             lw.w_gate_up = dev(torch.cat([get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")], 0))
         lw.w_down, lw.b_down = dev(get(p + mlp_out + ".weight")), opt(p + mlp_out + ".bias")
         layers.append(lw)
-    if cfg.arch == "gpt2":
+    if cfg.arch in ("gpt2", "gpt_bigcode"):
         embed, fin, head = "transformer.wte.weight", "transformer.ln_f", "lm_head.weight"
     elif cfg.arch == "opt":
         embed, fin, head = "model.decoder.embed_tokens.weight", "model.decoder.final_layer_norm", "lm_head.weight"
@@ -101,10 +109,11 @@ def load_hf_classic(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
     mult = cfg.ssm.get("logit_mult", 1.0) if cfg.ssm else 1.0
     if mult != 1.0:                             # Cohere: logits * scale, as a head of its own
         head_d = dev((get(embed) if (hw is None or cfg.tie_embeddings) else hw).float() * mult)
-    w = DecoderWeights(embed=e, layers=layers, final_norm=dev(get(fin + ".weight")), lm_head=head_d, vocab_start=0,
+    fin_w = torch.ones(H, device=device, dtype=dtype) if cfg.arch == "olmo" else dev(get(fin + ".weight"))
+    w = DecoderWeights(embed=e, layers=layers, final_norm=fin_w, lm_head=head_d, vocab_start=0,
                        vocab_local=cfg.vocab_size)
     w.final_norm_b = opt(fin + ".bias")
     if cfg.learned_positions:
-        w.pos_embed = dev(get("transformer.wpe.weight" if cfg.arch == "gpt2" else "model.decoder.embed_positions.weight"))
+        w.pos_embed = dev(get("transformer.wpe.weight" if cfg.arch in ("gpt2", "gpt_bigcode") else "model.decoder.embed_positions.weight"))
     w.lm_head_b = opt("lm_head.bias")
     return w

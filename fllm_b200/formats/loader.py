@@ -137,8 +137,10 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
                               post_attn_norm=dev(get(p + "post_attention_layernorm.weight")),
                               post_ffn_norm=dev(get(p + "post_feedforward_layernorm.weight")))
         else:
+            # VaultGemma names its second norm like Gemma-2 does, without having the norms behind the blocks
+            second = "pre_feedforward_layernorm" if (p + "pre_feedforward_layernorm.weight") in ck else "post_attention_layernorm"
             lw = LayerWeights(attn_norm=dev(get(p + "input_layernorm.weight")), wqkv=None, wo=None,
-                              ffn_norm=dev(get(p + "post_attention_layernorm.weight")))
+                              ffn_norm=dev(get(p + second + ".weight")))
         o = lin(p + "self_attn.o_proj")
         if cfg.is_moe:
             _load_moe_layer(cfg, sp, tp_rank, lw, p, get, dev)
@@ -181,6 +183,10 @@ def load_hf_checkpoint(directory: str, device="cuda", tp: int = 1, tp_rank: int 
             bo = get(p + "self_attn.o_proj.bias", False)
             if bo is not None:
                 lw.bo = dev(bo if tp_rank == 0 else torch.zeros_like(bo))
+        if cfg.qk_norm_full:                   # one norm over all heads of q, one over all heads of k (one rank)
+            if tp > 1:
+                raise NotImplementedError("QK-norm over all heads is not cut over tensor-parallel ranks")
+            lw.q_norm_full, lw.k_norm_full = dev(get(p + "self_attn.q_norm.weight")), dev(get(p + "self_attn.k_norm.weight"))
         if cfg.qk_norm:
             lw.q_norm, lw.k_norm = dev(get(p + "self_attn.q_norm.weight")), dev(get(p + "self_attn.k_norm.weight"))
             if cfg.qk_norm_offset:             # the fused kernel multiplies by w: fold the 1 + w convention into it

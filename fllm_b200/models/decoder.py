@@ -123,7 +123,7 @@ class Decoder:
         # split-K reductions of the projections are left to the kernel that consumes them (norm / rope)
         # (only the RMSNorm, rope and gated-activation kernels take partials: LayerNorm families and parallel blocks do not defer)
         self._defer = (hasattr(ops, "k") and dev.type == "cuda" and cfg.norm_kind == "rms" and not cfg.parallel_block
-                       and not cfg.qk_norm_full)
+                       and not cfg.qk_norm_full and not cfg.clip_qkv)
         if self._defer:
             self._block_gate_up()
 
@@ -160,6 +160,8 @@ class Decoder:
             nq, nk = sp.hq_local * cfg.head_dim, sp.hkv_local * cfg.head_dim
             qkv[:, :nq] = ops.rmsnorm(qkv[:, :nq].contiguous(), None, lw.q_norm_full, cfg.rms_eps, 0.0)
             qkv[:, nq:nq + nk] = ops.rmsnorm(qkv[:, nq:nq + nk].contiguous(), None, lw.k_norm_full, cfg.rms_eps, 0.0)
+        if cfg.clip_qkv > 0:                       # after the full-width norms where a family has both (OLMoE)
+            qkv = ops.materialize(qkv).clamp_(-cfg.clip_qkv, cfg.clip_qkv)
         local = self.kv_index[li]
         kc, vc = self.kv.k(local), self.kv.v(local)
         local_rope = self.inv_freq_local is not None and cfg.layer_window(li) > 0

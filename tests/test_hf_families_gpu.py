@@ -56,11 +56,21 @@ def _model(kind):
         return tf.FalconH1ForCausalLM(tf.FalconH1Config(**BASE, mamba_d_ssm=512, mamba_n_heads=8, mamba_n_groups=2, mamba_d_state=128,
                                                         ssm_multipliers=[0.9, 1.1, 1.2, 0.8, 1.3], attention_in_multiplier=1.2,
                                                         ssm_out_multiplier=0.6, embedding_multiplier=2.5))
+    if kind == "olmoe":
+        return tf.OlmoeForCausalLM(tf.OlmoeConfig(**dict(BASE, intermediate_size=128), pad_token_id=0, num_experts=8, num_experts_per_tok=2,
+                                                  clip_qkv=4.0))
+    if kind == "exaone4":
+        return tf.Exaone4ForCausalLM(tf.Exaone4Config(**BASE, pad_token_id=0, head_dim=64, sliding_window=48, sliding_window_pattern=2,
+                                                      layer_types=["sliding_attention", "full_attention"]))
+    if kind == "cohere2":
+        return tf.Cohere2ForCausalLM(tf.Cohere2Config(**BASE, pad_token_id=0, logit_scale=0.25, sliding_window=48,
+                                                      layer_types=["sliding_attention", "full_attention"]))
     raise ValueError(kind)
 
 
 @pytest.mark.parametrize("kind", ["llama_odd_vocab", "gpt2", "phi", "gpt_neox", "nemotron", "starcoder2", "cohere", "olmo2", "glm", "gemma3", "qwen2_moe", "jamba", "qwen3_next", "nemotron_h",
-                                  "nemotron_h_latent", "falcon_h1"])
+                                  "nemotron_h_latent", "falcon_h1", "olmoe", "exaone4",
+                                  "cohere2"])
 def test_native_operators_match_reference_operators(tmp_path, kind):
     from fllm_b200.config import EngineConfig
     from fllm_b200.formats.loader import load_hf_checkpoint
@@ -81,6 +91,6 @@ def test_native_operators_match_reference_operators(tmp_path, kind):
     toks = torch.randint(0, min(512, cfg.vocab_size), (150,), generator=torch.Generator().manual_seed(3)).tolist()
     a, b = nat.token_logits(toks), ref.token_logits(toks)
     err = (a - b).norm(dim=1) / b.norm(dim=1)
-    routed = kind in ("qwen2_moe", "jamba", "qwen3_next", "nemotron_h", "nemotron_h_latent")
+    routed = kind in ("qwen2_moe", "jamba", "qwen3_next", "nemotron_h", "nemotron_h_latent", "olmoe")
     assert float(err.median()) < 3e-2 and int((err > 0.15).sum()) <= (3 if routed else 0), err
     assert int(nat.ops.status.item()) == 0

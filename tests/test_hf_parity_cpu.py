@@ -92,6 +92,22 @@ def _model(kind):
                                                          norm_topk_prob=False))
     if kind == "gpt_oss":                       # YaRN with fractional correction dimensions, sinks, windowed layers, clamped GLU
         return tf.GptOssForCausalLM(tf.GptOssConfig(**BASE, head_dim=16, num_local_experts=4, num_experts_per_tok=2, sliding_window=24))
+    if kind == "olmo":                          # LayerNorm without weights, clamped q / k / v
+        return tf.OlmoForCausalLM(tf.OlmoConfig(**BASE, pad_token_id=0, clip_qkv=1.5))
+    if kind == "olmoe":                         # full-width QK-norm then the clamp, raw softmax weights for the selected experts
+        return tf.OlmoeForCausalLM(tf.OlmoeConfig(**BASE, pad_token_id=0, num_experts=8, num_experts_per_tok=2, clip_qkv=4.0))
+    if kind == "cohere2":                       # windowed layers rotate, global layers carry no position signal
+        return tf.Cohere2ForCausalLM(tf.Cohere2Config(**BASE, pad_token_id=0, logit_scale=0.25, sliding_window=24,
+                                                      layer_types=["sliding_attention", "full_attention"]))
+    if kind == "exaone4":
+        return tf.Exaone4ForCausalLM(tf.Exaone4Config(**BASE, pad_token_id=0, sliding_window=24, sliding_window_pattern=2,
+                                                      layer_types=["sliding_attention", "full_attention"]))
+    if kind == "vaultgemma":
+        return tf.VaultGemmaForCausalLM(tf.VaultGemmaConfig(**BASE, head_dim=16, sliding_window=24, query_pre_attn_scalar=20,
+                                                            final_logit_softcapping=20.0, attn_logit_softcapping=30.0,
+                                                            attn_implementation="eager"))
+    if kind == "gpt_bigcode":                   # GPT-2 blocks with one key / value head
+        return tf.GPTBigCodeForCausalLM(tf.GPTBigCodeConfig(vocab_size=300, n_positions=256, n_embd=64, n_layer=2, n_head=4))
     if kind == "qwen2_moe":
         return tf.Qwen2MoeForCausalLM(tf.Qwen2MoeConfig(**BASE, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
                                                          shared_expert_intermediate_size=64, norm_topk_prob=False))
@@ -100,7 +116,7 @@ def _model(kind):
 
 @pytest.mark.parametrize("kind", ["llama", "llama3_rope", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "granite", "seed_oss", "ernie4_5", "glm", "glm4", "helium",
                                   "ministral", "smollm3", "starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "gpt2", "opt", "olmo2", "olmo3", "phi3", "mixtral", "qwen3_moe",
-                                  "qwen2_moe", "qwen3_moe_raw_weights", "gpt_oss"])
+                                  "qwen2_moe", "qwen3_moe_raw_weights", "gpt_oss", "olmo", "olmoe", "cohere2", "exaone4", "vaultgemma", "gpt_bigcode"])
 def test_attention_families_match_transformers(tmp_path, kind):
     from fllm_b200.formats.loader import load_hf_checkpoint
     m = _model(kind).eval().float()
