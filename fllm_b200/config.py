@@ -307,7 +307,7 @@ ATTENTION_MODEL_TYPES = ("llama", "mistral", "ministral", "qwen2", "qwen3", "qwe
                          "gemma3_text", "vaultgemma", "phi3", "gpt_oss", "granite", "seed_oss", "glm", "glm4", "ernie4_5", "helium", "smollm3")
 
 
-CLASSIC_MODEL_TYPES = ("starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "cohere2", "olmo", "olmo2", "olmo3", "exaone4", "gpt2",
+CLASSIC_MODEL_TYPES = ("starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "cohere2", "olmo", "olmo2", "olmo3", "exaone4", "falcon", "gpt2",
                        "gpt_bigcode", "opt")
 _ACT_NAMES = {"gelu": "gelu", "gelu_new": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh", "gelu_fast": "gelu_tanh", "relu2": "relu2",
               "silu": "silu", "swish": "silu", "relu": "relu"}
@@ -321,6 +321,13 @@ def classic_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
         hf = dict(hf, hidden_size=hf["n_embd"], num_hidden_layers=hf["n_layer"], num_attention_heads=hf["n_head"],
                   intermediate_size=hf.get("n_inner") or 4 * hf["n_embd"], max_position_embeddings=hf.get("n_positions", 1024),
                   hidden_act=hf.get("activation_function", "gelu_new"))
+    if mt == "falcon":                    # its own field names; three layouts of the fused q|k|v rows
+        if hf.get("alibi"):
+            raise NotImplementedError("falcon with ALiBi position biases is not supported")
+        new = bool(hf.get("new_decoder_architecture", False))
+        kv = (hf.get("num_kv_heads") or hf["num_attention_heads"]) if new else (1 if hf.get("multi_query", True) else hf["num_attention_heads"])
+        hf = dict(hf, num_key_value_heads=kv, intermediate_size=hf.get("ffn_hidden_size") or 4 * hf["hidden_size"],
+                  hidden_act=hf.get("activation", "gelu"))
     if mt == "opt":
         if hf.get("word_embed_proj_dim") not in (None, hf["hidden_size"]) or not hf.get("do_layer_norm_before", True):
             raise NotImplementedError("OPT with projected embeddings or post-LayerNorm blocks (350m) is not supported")
@@ -378,6 +385,13 @@ def classic_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
         if mt == "olmo3" and hf.get("sliding_window") and lt:
             cfg.sliding_window = int(hf["sliding_window"])
             cfg.window_pattern = [1 if t == "sliding_attention" else 0 for t in lt]
+    elif mt == "falcon":
+        new = bool(hf.get("new_decoder_architecture", False))
+        cfg.norm_kind, cfg.mlp_kind, cfg.act, cfg.rms_eps = "layernorm", "plain", act, hf.get("layer_norm_epsilon", 1e-5)
+        cfg.parallel_block = new or bool(hf.get("parallel_attn", True))
+        cfg.parallel_norms = 2 if (new and (hf.get("num_ln_in_parallel_attn") or 2) == 2) else 1
+        cfg.attn_bias = cfg.mlp_bias = bool(hf.get("bias", False))
+        cfg.ssm = dict(qkv_layout="grouped" if new else ("flat" if cfg.num_kv_heads == 1 else "per_head"))
     elif mt == "exaone4":                 # blocks normalised at their output, per-head QK-norm, windowed layers rotate and global ones do not
         cfg.norm_kind, cfg.post_norms, cfg.qk_norm, cfg.rms_eps = "none", True, True, hf.get("rms_norm_eps", 1e-5)
         lt = hf.get("layer_types")

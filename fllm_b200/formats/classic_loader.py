@@ -29,6 +29,8 @@ _NAMES = {
     "cohere2": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", "input_layernorm", None, None, "mlp.down_proj"),
     "olmo": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", None, None, None, "mlp.down_proj"),
     "gpt_bigcode": ("transformer.h.{}.", "attn.", "c_attn", "c_proj", "ln_1", "ln_2", "mlp.c_fc", "mlp.c_proj"),
+    "falcon": ("transformer.h.{}.", "self_attention.", "query_key_value", "dense", "input_layernorm", "post_attention_layernorm",
+               "mlp.dense_h_to_4h", "mlp.dense_4h_to_h"),
     "gpt2": ("transformer.h.{}.", "attn.", "c_attn", "c_proj", "ln_1", "ln_2", "mlp.c_fc", "mlp.c_proj"),
     "opt": ("model.decoder.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "out_proj", "self_attn_layer_norm", "final_layer_norm",
             "fc1", "fc2"),
@@ -48,6 +50,8 @@ def load_hf_classic(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
         return dev(t) if t is not None else None
 
     lp, ap, qkv, o_name, n1, n2, mlp_in, mlp_out = _NAMES[cfg.arch]
+    if cfg.arch == "falcon" and cfg.parallel_block:          # one shared norm, or a norm each under names of their own
+        n1, n2 = ("ln_attn", "ln_mlp") if cfg.parallel_norms == 2 else ("input_layernorm", None)
     H, D, hq, hkv = cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
     if cfg.arch == "gpt2":                      # GPT-2 stores its matrices as [in, out]
         inner = get
@@ -77,7 +81,15 @@ def load_hf_classic(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
             bs = [get(p + ap + n + ".bias", False) for n in qkv]
             if bs[0] is not None:
                 lw.bqkv = dev(torch.cat(bs))
-        elif cfg.arch == "gpt2" or (cfg.arch == "gpt_bigcode" and hkv == 1):      # one matrix: all q rows, all k rows, all v rows
+        elif cfg.arch == "falcon" and cfg.ssm["qkv_layout"] == "grouped":     # per key / value head: its query heads, its key, its value
+            g = hq // hkv
+            w = get(p + ap + qkv + ".weight").view(hkv, g + 2, D, H)
+            lw.wqkv = dev(torch.cat([w[:, :g].reshape(hq * D, H), w[:, g].reshape(hkv * D, H), w[:, g + 1].reshape(hkv * D, H)], 0))
+            bb = get(p + ap + qkv + ".bias", False)
+            if bb is not None:
+                bb = bb.view(hkv, g + 2, D)
+                lw.bqkv = dev(torch.cat([bb[:, :g].reshape(-1), bb[:, g].reshape(-1), bb[:, g + 1].reshape(-1)]))
+        elif cfg.arch == "gpt2" or (cfg.arch in ("gpt_bigcode", "falcon") and hkv == 1):      # one matrix: all q rows, all k rows, all v rows
             lw.wqkv, lw.bqkv = dev(get(p + ap + qkv + ".weight")), opt(p + ap + qkv + ".bias")
         else:                                   # GPT-NeoX: one matrix whose rows go head by head as (q, k, v)
             w = get(p + ap + qkv + ".weight").view(hq, 3, D, H)
@@ -93,7 +105,9 @@ def load_hf_classic(cfg: ModelConfig, get, device, dtype) -> DecoderWeights:
             lw.w_gate_up = dev(torch.cat([get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")], 0))
         lw.w_down, lw.b_down = dev(get(p + mlp_out + ".weight")), opt(p + mlp_out + ".bias")
         layers.append(lw)
-    if cfg.arch in ("gpt2", "gpt_bigcode"):
+    if cfg.arch == "falcon":
+        embed, fin, head = "transformer.word_embeddings.weight", "transformer.ln_f", "lm_head.weight"
+    elif cfg.arch in ("gpt2", "gpt_bigcode"):
         embed, fin, head = "transformer.wte.weight", "transformer.ln_f", "lm_head.weight"
     elif cfg.arch == "opt":
         embed, fin, head = "model.decoder.embed_tokens.weight", "model.decoder.final_layer_norm", "lm_head.weight"

@@ -108,6 +108,13 @@ def _model(kind):
                                                             attn_implementation="eager"))
     if kind == "gpt_bigcode":                   # GPT-2 blocks with one key / value head
         return tf.GPTBigCodeForCausalLM(tf.GPTBigCodeConfig(vocab_size=300, n_positions=256, n_embd=64, n_layer=2, n_head=4))
+    if kind.startswith("falcon"):               # the three layouts of the fused q|k|v rows, one or two norms, parallel or sequential blocks
+        kw = {"falcon_new": dict(new_decoder_architecture=True, num_kv_heads=2),
+              "falcon_new_one_norm": dict(new_decoder_architecture=True, num_kv_heads=2, num_ln_in_parallel_attn=1),
+              "falcon_mq": dict(multi_query=True, parallel_attn=True),
+              "falcon_mha_sequential": dict(multi_query=False, parallel_attn=False, bias=True)}[kind]
+        return tf.FalconForCausalLM(tf.FalconConfig(vocab_size=300, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, alibi=False,
+                                                    max_position_embeddings=256, **kw))
     if kind == "qwen2_moe":
         return tf.Qwen2MoeForCausalLM(tf.Qwen2MoeConfig(**BASE, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
                                                          shared_expert_intermediate_size=64, norm_topk_prob=False))
@@ -116,7 +123,8 @@ def _model(kind):
 
 @pytest.mark.parametrize("kind", ["llama", "llama3_rope", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "granite", "seed_oss", "ernie4_5", "glm", "glm4", "helium",
                                   "ministral", "smollm3", "starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "gpt2", "opt", "olmo2", "olmo3", "phi3", "mixtral", "qwen3_moe",
-                                  "qwen2_moe", "qwen3_moe_raw_weights", "gpt_oss", "olmo", "olmoe", "cohere2", "exaone4", "vaultgemma", "gpt_bigcode"])
+                                  "qwen2_moe", "qwen3_moe_raw_weights", "gpt_oss", "olmo", "olmoe", "cohere2", "exaone4", "vaultgemma", "gpt_bigcode",
+                                  "falcon_new", "falcon_new_one_norm", "falcon_mq", "falcon_mha_sequential"])
 def test_attention_families_match_transformers(tmp_path, kind):
     from fllm_b200.formats.loader import load_hf_checkpoint
     m = _model(kind).eval().float()
@@ -133,7 +141,7 @@ def test_attention_families_match_transformers(tmp_path, kind):
             if "experts" in n and p.dim() == 3:
                 p.mul_(5.0)                                   # the routed share of the output is large enough to show its weights
             if n.endswith(("q_proj.weight", "k_proj.weight", "qkv_proj.weight", "query_key_value.weight", "c_attn.weight")):
-                p.mul_(12.0)                                  # peaked attention: a wrong rotation or mask moves the logits
+                p.mul_(6.0 if kind.startswith("falcon") else 12.0)                                  # peaked attention: a wrong rotation or mask moves the logits
     d = str(tmp_path / kind)
     m.save_pretrained(d, safe_serialization=True)
     cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
