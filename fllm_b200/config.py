@@ -181,6 +181,9 @@ class ModelConfig:
     def from_hf_config(cls, hf: Dict[str, Any]) -> "ModelConfig":
         """Map a Hugging Face ``config.json`` to the decoder description."""
         mt = hf.get("model_type", "llama")
+        if mt in ("glm4_moe_lite", "kimi_k2"):    # DeepSeek-V3 under another name: the same tensors, router and latent attention
+            hf = dict(hf, model_type="deepseek_v3")
+            mt = "deepseek_v3"
         if mt == "gemma3" and isinstance(hf.get("text_config"), dict):     # the multimodal wrapper: its language model
             hf = dict(hf["text_config"], model_type="gemma3_text")
             mt = "gemma3_text"
@@ -254,6 +257,11 @@ class ModelConfig:
             if mt in ("qwen2_moe", "qwen3_moe", "olmoe") and not hf.get("norm_topk_prob", False):
                 # the selected probabilities are used as they are (Qwen1.5-MoE, Qwen2-57B-A14B): the score-weighted router
                 cfg.router_kind, cfg.router_norm_topk, cfg.router_scale = "deepseek_v2", False, 1.0
+        if mt == "minimax_m2":                # q and k normalised over all heads, partial rotary, sigmoid router with a selection bias
+            cfg.qk_norm_full = bool(hf.get("use_qk_norm", True))
+            cfg.router_kind, cfg.router_norm_topk, cfg.router_scale = "deepseek_v3", True, float(hf.get("routed_scaling_factor") or 1.0)
+            rot = hf.get("rotary_dim") or int(cfg.head_dim * float(hf.get("partial_rotary_factor", 1.0)))
+            cfg.rotary_dim = rot if rot != cfg.head_dim else None
         if mt == "olmoe":                     # OLMoE: q and k normalised over all heads, optional clamp of q / k / v
             cfg.qk_norm_full, cfg.clip_qkv = True, float(hf.get("clip_qkv") or 0.0)
         if mt in ("gemma", "gemma2", "gemma3_text", "vaultgemma"):
@@ -303,7 +311,7 @@ class ModelConfig:
 
 # decoder families whose layers are attention + gated FFN (or routed experts) and that the generic mapping covers; every one
 # of them is checked against `transformers` in tests/test_hf_parity_cpu.py
-ATTENTION_MODEL_TYPES = ("llama", "mistral", "ministral", "qwen2", "qwen3", "qwen2_moe", "qwen3_moe", "olmoe", "mixtral", "gemma", "gemma2",
+ATTENTION_MODEL_TYPES = ("llama", "mistral", "ministral", "qwen2", "qwen3", "qwen2_moe", "qwen3_moe", "olmoe", "minimax_m2", "mixtral", "gemma", "gemma2",
                          "gemma3_text", "vaultgemma", "phi3", "gpt_oss", "granite", "seed_oss", "glm", "glm4", "ernie4_5", "helium", "smollm3")
 
 

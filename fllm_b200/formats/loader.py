@@ -289,6 +289,9 @@ def _load_per_expert_moe(cfg, sp, tp_rank, lw, p, get, dev) -> None:
         base, names, router = p + "mlp.", ("gate_proj", "up_proj", "down_proj"), "mlp.gate.weight"
     lw.router_w = dev(get(p + router))
     lw.router_b = None
+    sel = get(base + "e_score_correction_bias", False)            # MiniMax-M2: a bias that only steers the selection
+    if sel is not None:
+        lw.router_select_b = sel.float().reshape(-1).to(lw.router_w.device).contiguous()
     experts = range(sp.expert_start, sp.expert_start + sp.expert_local) if sp.expert_parallel else range(cfg.num_experts)
     fused = get(base + "experts.gate_up_proj", False)
     if fused is not None:                      # newer checkpoints: one [E, 2I, H] and one [E, H, I] tensor per layer

@@ -115,6 +115,13 @@ def _model(kind):
               "falcon_mha_sequential": dict(multi_query=False, parallel_attn=False, bias=True)}[kind]
         return tf.FalconForCausalLM(tf.FalconConfig(vocab_size=300, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, alibi=False,
                                                     max_position_embeddings=256, **kw))
+    if kind == "minimax_m2":                    # full-width QK-norm, half of each head rotated, sigmoid router with a selection bias
+        return tf.MiniMaxM2ForCausalLM(tf.MiniMaxM2Config(**dict(BASE, intermediate_size=32), head_dim=16, num_local_experts=8, num_experts_per_tok=2,
+                                                          rope_parameters=dict(rope_type="default", rope_theta=10000.0, partial_rotary_factor=0.5)))
+    if kind == "glm4_moe_lite":                 # DeepSeek-V3's tensors under another model type (as Kimi-K2 is)
+        return tf.Glm4MoeLiteForCausalLM(tf.Glm4MoeLiteConfig(**dict(BASE, num_key_value_heads=4), moe_intermediate_size=32, n_routed_experts=8,
+                                                              num_experts_per_tok=2, q_lora_rank=24, kv_lora_rank=32, qk_nope_head_dim=16,
+                                                              qk_rope_head_dim=8, v_head_dim=16, first_k_dense_replace=1, n_group=2, topk_group=1))
     if kind == "qwen2_moe":
         return tf.Qwen2MoeForCausalLM(tf.Qwen2MoeConfig(**BASE, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
                                                          shared_expert_intermediate_size=64, norm_topk_prob=False))
@@ -124,7 +131,7 @@ def _model(kind):
 @pytest.mark.parametrize("kind", ["llama", "llama3_rope", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "granite", "seed_oss", "ernie4_5", "glm", "glm4", "helium",
                                   "ministral", "smollm3", "starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "gpt2", "opt", "olmo2", "olmo3", "phi3", "mixtral", "qwen3_moe",
                                   "qwen2_moe", "qwen3_moe_raw_weights", "gpt_oss", "olmo", "olmoe", "cohere2", "exaone4", "vaultgemma", "gpt_bigcode",
-                                  "falcon_new", "falcon_new_one_norm", "falcon_mq", "falcon_mha_sequential"])
+                                  "falcon_new", "falcon_new_one_norm", "falcon_mq", "falcon_mha_sequential", "minimax_m2", "glm4_moe_lite"])
 def test_attention_families_match_transformers(tmp_path, kind):
     from fllm_b200.formats.loader import load_hf_checkpoint
     m = _model(kind).eval().float()
@@ -136,6 +143,8 @@ def test_attention_families_match_transformers(tmp_path, kind):
                 p.add_(0.05 * torch.randn_like(p))            # biases start at zero: make them count
             if n.endswith(("mlp.gate.weight", "block_sparse_moe.gate.weight")):
                 p.mul_(20.0)                                  # clear routing decisions
+            if n.endswith("q_b_proj.weight"):
+                p.mul_(12.0)
             if n.endswith("sinks"):
                 p.normal_(0, 1.0)
             if "experts" in n and p.dim() == 3:
@@ -143,6 +152,10 @@ def test_attention_families_match_transformers(tmp_path, kind):
             if n.endswith(("q_proj.weight", "k_proj.weight", "qkv_proj.weight", "query_key_value.weight", "c_attn.weight")):
                 p.mul_(6.0 if kind.startswith("falcon") else 12.0)                                  # peaked attention: a wrong rotation or mask moves the logits
     d = str(tmp_path / kind)
+    with torch.no_grad():
+        for n, b in m.named_buffers():
+            if n.endswith("e_score_correction_bias"):
+                b.normal_(0, 0.2)
     m.save_pretrained(d, safe_serialization=True)
     cfg, w, _ = load_hf_checkpoint(d, device="cpu", dtype=torch.float32)
     eng = LLMEngine(cfg, EngineConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=128, num_kv_blocks=32, block_size=16,
