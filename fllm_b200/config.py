@@ -181,7 +181,7 @@ class ModelConfig:
     def from_hf_config(cls, hf: Dict[str, Any]) -> "ModelConfig":
         """Map a Hugging Face ``config.json`` to the decoder description."""
         mt = hf.get("model_type", "llama")
-        if mt in ("glm4_moe_lite", "kimi_k2"):    # DeepSeek-V3 under another name: the same tensors, router and latent attention
+        if mt in ("glm4_moe_lite", "kimi_k2", "youtu"):    # DeepSeek-V3 under another name (Youtu: its dense form): the same tensors, router and latent attention
             hf = dict(hf, model_type="deepseek_v3")
             mt = "deepseek_v3"
         if mt == "gemma3" and isinstance(hf.get("text_config"), dict):     # the multimodal wrapper: its language model
@@ -301,7 +301,7 @@ class ModelConfig:
                 cfg.attn_scale = float(hf["attention_multiplier"])
         if mt in ("phi3", "phi"):
             cfg.rotary_dim = int(cfg.head_dim * hf.get("partial_rotary_factor", 1.0)) or None
-        if hf.get("sliding_window") and hf.get("use_sliding_window", mt in ("mistral", "ministral")):
+        if hf.get("sliding_window") and hf.get("use_sliding_window", mt in ("mistral", "ministral", "cwm")):
             cfg.sliding_window = hf["sliding_window"]
             lt = hf.get("layer_types")
             if lt and cfg.window_pattern is None and any(t != "sliding_attention" for t in lt):
@@ -311,11 +311,11 @@ class ModelConfig:
 
 # decoder families whose layers are attention + gated FFN (or routed experts) and that the generic mapping covers; every one
 # of them is checked against `transformers` in tests/test_hf_parity_cpu.py
-ATTENTION_MODEL_TYPES = ("llama", "mistral", "ministral", "qwen2", "qwen3", "qwen2_moe", "qwen3_moe", "olmoe", "minimax_m2", "mixtral", "gemma", "gemma2",
+ATTENTION_MODEL_TYPES = ("llama", "mistral", "ministral", "cwm", "qwen2", "qwen3", "qwen2_moe", "qwen3_moe", "olmoe", "minimax_m2", "mixtral", "gemma", "gemma2",
                          "gemma3_text", "vaultgemma", "phi3", "gpt_oss", "granite", "seed_oss", "glm", "glm4", "ernie4_5", "helium", "smollm3")
 
 
-CLASSIC_MODEL_TYPES = ("starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "cohere2", "olmo", "olmo2", "olmo3", "exaone4", "falcon", "gpt2",
+CLASSIC_MODEL_TYPES = ("starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "cohere2", "olmo", "olmo2", "olmo3", "exaone4", "falcon", "jais2", "gpt2",
                        "gpt_bigcode", "opt")
 _ACT_NAMES = {"gelu": "gelu", "gelu_new": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh", "gelu_fast": "gelu_tanh", "relu2": "relu2",
               "silu": "silu", "swish": "silu", "relu": "relu"}
@@ -363,6 +363,9 @@ def classic_from_hf(cls, hf: Dict[str, Any]) -> "ModelConfig":
     elif mt == "nemotron":                # LayerNorm whose weight is stored minus one, squared-ReLU MLP
         cfg.norm_kind, cfg.norm_weight_offset, cfg.rms_eps = "layernorm", 1.0, hf.get("norm_eps", 1e-5)
         cfg.mlp_kind, cfg.act, cfg.attn_bias, cfg.mlp_bias = "plain", act, bool(hf.get("attention_bias", False)), bool(hf.get("mlp_bias", False))
+    elif mt == "jais2":                   # Llama blocks with LayerNorm (weight and bias) and a squared-ReLU two-matrix MLP
+        cfg.norm_kind, cfg.rms_eps = "layernorm", hf.get("layer_norm_eps", 1e-5)
+        cfg.mlp_kind, cfg.act, cfg.attn_bias, cfg.mlp_bias = "plain", act, bool(hf.get("attention_bias", True)), bool(hf.get("mlp_bias", True))
     elif mt == "arcee":
         cfg.mlp_kind, cfg.act, cfg.rms_eps = "plain", act, hf.get("rms_norm_eps", 1e-5)
         cfg.attn_bias, cfg.mlp_bias = bool(hf.get("attention_bias", False)), bool(hf.get("mlp_bias", False))

@@ -20,6 +20,8 @@ _NAMES = {
                  None, "mlp.down_proj"),
     "nemotron": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", "input_layernorm", "post_attention_layernorm",
                  "mlp.up_proj", "mlp.down_proj"),
+    "jais2": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", "input_layernorm", "post_attention_layernorm",
+              "mlp.up_proj", "mlp.down_proj"),
     "arcee": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "o_proj", "input_layernorm", "post_attention_layernorm",
               "mlp.up_proj", "mlp.down_proj"),
     "phi": ("model.layers.{}.", "self_attn.", ("q_proj", "k_proj", "v_proj"), "dense", "input_layernorm", None, "mlp.fc1", "mlp.fc2"),

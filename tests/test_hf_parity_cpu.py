@@ -122,6 +122,13 @@ def _model(kind):
         return tf.Glm4MoeLiteForCausalLM(tf.Glm4MoeLiteConfig(**dict(BASE, num_key_value_heads=4), moe_intermediate_size=32, n_routed_experts=8,
                                                               num_experts_per_tok=2, q_lora_rank=24, kv_lora_rank=32, qk_nope_head_dim=16,
                                                               qk_rope_head_dim=8, v_head_dim=16, first_k_dense_replace=1, n_group=2, topk_group=1))
+    if kind == "cwm":                           # Llama with windowed and global layers
+        return tf.CwmForCausalLM(tf.CwmConfig(**BASE, pad_token_id=0, sliding_window=24, layer_types=["sliding_attention", "full_attention"]))
+    if kind == "jais2":                         # Llama blocks with LayerNorm and a squared-ReLU two-matrix MLP, biases everywhere
+        return tf.Jais2ForCausalLM(tf.Jais2Config(**BASE, pad_token_id=0))
+    if kind == "youtu":                         # latent attention in front of a dense FFN
+        return tf.YoutuForCausalLM(tf.YoutuConfig(**dict(BASE, num_key_value_heads=4), pad_token_id=0, q_lora_rank=24, kv_lora_rank=32,
+                                                  qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16))
     if kind == "qwen2_moe":
         return tf.Qwen2MoeForCausalLM(tf.Qwen2MoeConfig(**BASE, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
                                                          shared_expert_intermediate_size=64, norm_topk_prob=False))
@@ -131,7 +138,7 @@ def _model(kind):
 @pytest.mark.parametrize("kind", ["llama", "llama3_rope", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "granite", "seed_oss", "ernie4_5", "glm", "glm4", "helium",
                                   "ministral", "smollm3", "starcoder2", "stablelm", "nemotron", "arcee", "phi", "gpt_neox", "cohere", "gpt2", "opt", "olmo2", "olmo3", "phi3", "mixtral", "qwen3_moe",
                                   "qwen2_moe", "qwen3_moe_raw_weights", "gpt_oss", "olmo", "olmoe", "cohere2", "exaone4", "vaultgemma", "gpt_bigcode",
-                                  "falcon_new", "falcon_new_one_norm", "falcon_mq", "falcon_mha_sequential", "minimax_m2", "glm4_moe_lite"])
+                                  "falcon_new", "falcon_new_one_norm", "falcon_mq", "falcon_mha_sequential", "minimax_m2", "glm4_moe_lite", "cwm", "jais2", "youtu"])
 def test_attention_families_match_transformers(tmp_path, kind):
     from fllm_b200.formats.loader import load_hf_checkpoint
     m = _model(kind).eval().float()
