@@ -90,18 +90,31 @@ __global__ void __launch_bounds__(256) conv1d_kernel(const bf16* __restrict__ x,
       if (!fresh && blockIdx.z == 0) h = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(st + (long long)j * C + c));
       hist[0][j] = h.x, hist[1][j] = h.y;
     }
-    for (int p = p_lo + threadIdx.y; p < p_hi; p += blockDim.y) {
-      float a0 = bv[0], a1 = bv[1];
+    // each row of threads walks a contiguous piece of the run with the last W - 1 inputs in registers: one load per token
+    const int per = (p_hi - p_lo + (int)blockDim.y - 1) / (int)blockDim.y;
+    const int a0 = p_lo + (int)threadIdx.y * per, a1 = min(p_hi, a0 + per);
+    float win[2][W - 1];
 #pragma unroll
-      for (int j = 0; j < W; ++j) {
-        const int i = p - (W - 1) + j;
-        float2 v;
+    for (int j = 0; j < W - 1; ++j) {
+      const int i = a0 - (W - 1) + j;
+      float2 v = make_float2(0.f, 0.f);
+      if (a0 < a1) {
         if (i >= 0) v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + (long long)(t0 + i) * ldx + c));
         else v = make_float2(hist[0][(W - 1) + i], hist[1][(W - 1) + i]);
-        a0 = fmaf(wv[0][j], v.x, a0), a1 = fmaf(wv[1][j], v.y, a1);
       }
-      if (act) a0 = silu_f(a0), a1 = silu_f(a1);
-      *reinterpret_cast<__nv_bfloat162*>(y + (long long)(t0 + p) * ldy + c) = __floats2bfloat162_rn(a0, a1);
+      win[0][j] = v.x, win[1][j] = v.y;
+    }
+#pragma unroll 4
+    for (int p = a0; p < a1; ++p) {
+      const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + (long long)(t0 + p) * ldx + c));
+      float o0 = fmaf(wv[0][W - 1], v.x, bv[0]), o1 = fmaf(wv[1][W - 1], v.y, bv[1]);
+#pragma unroll
+      for (int j = 0; j < W - 1; ++j) o0 = fmaf(wv[0][j], win[0][j], o0), o1 = fmaf(wv[1][j], win[1][j], o1);
+#pragma unroll
+      for (int j = 0; j + 1 < W - 1; ++j) win[0][j] = win[0][j + 1], win[1][j] = win[1][j + 1];
+      win[0][W - 2] = v.x, win[1][W - 2] = v.y;
+      if (act) o0 = silu_f(o0), o1 = silu_f(o1);
+      *reinterpret_cast<__nv_bfloat162*>(y + (long long)(t0 + p) * ldy + c) = __floats2bfloat162_rn(o0, o1);
     }
   }
   if (blockIdx.z != 0) return;
